@@ -1,0 +1,358 @@
+// Persistent, warp-specialised bf16 GEMM for sm_100a:
+//     D[M,N] = epilogue( A[M,K] * B[N,K]^T )
+// Operands come through (non-multicast) TMA into 128-byte-swizzled shared memory, the product is
+// issued by one thread with tcgen05.mma (128 x 256 x 16 per instruction), fp32 accumulators sit in
+// TMEM and are double buffered (2 x 256 columns) so that the epilogue of tile i overlaps the main
+// loop of tile i+1.
+//
+// Either operand may be "MN-major" (stored transposed, i.e. A as [K,M] or B as [K,N]); this is what
+// lets dgrad (dX = dY * W) and wgrad (dW = dY^T * X) run on the same kernel without transposes.
+//
+// Roles:  warp 0 = TMA producer, warp 1 = TMEM owner + MMA issuer, warps 2..5 = epilogue.
+// Covers the reference's XLA:GPU / cuBLAS matmuls behind every Dense layer
+// (src/maxdiffusion/models/attention_flax.py:2471-2525, models/wan/transformers/transformer_wan.py:220-330)
+// together with the elementwise fusions XLA places after them (bias, GELU-tanh, gated residual).
+#include "host_common.h"
+
+namespace mdb {
+
+namespace gemm {
+constexpr int BM = 128;
+constexpr int BN = 256;
+constexpr int BK = 64;
+constexpr int STAGES = 4;
+constexpr int A_BYTES = BM * BK * 2;  // 16 KiB
+constexpr int B_BYTES = BN * BK * 2;  // 32 KiB
+constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+constexpr int NUM_THREADS = 192;
+constexpr int TMEM_COLS = 512;
+constexpr int GROUP_M = 8;
+constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*align slack*/ + 256 /*barriers*/;
+
+enum Epilogue : int {
+  kEpiNone = 0,       // out = acc*alpha + bias
+  kEpiGeluTanh = 1,   // out = gelu_tanh(acc*alpha + bias)
+  kEpiGatedRes = 2,   // out = residual + gate[batch(row), col] * (acc*alpha + bias)
+  kEpiSilu = 3,       // out = silu(acc*alpha + bias)
+  kEpiAddRes = 4,     // out = residual + acc*alpha + bias
+};
+
+struct Params {
+  int M, N, K;
+  void* out;
+  long long ldo;
+  const __nv_bfloat16* bias;      // [N] or nullptr
+  const __nv_bfloat16* residual;  // [M, ldr] or nullptr
+  long long ldr;
+  const float* gate;              // [num_batches, gate_ld] fp32 or nullptr
+  long long gate_ld;
+  int rows_per_batch;
+  int epi;
+  int out_f32;
+  float alpha;
+  DeviceStatus* status;
+};
+
+__device__ __forceinline__ void tile_coords(int tile, int num_m, int num_n, int& m_idx, int& n_idx) {
+  // Grouped rasterisation: GROUP_M row-blocks share each sweep over the column-blocks so that
+  // concurrently running CTAs reuse both operands out of L2.
+  const int tiles_per_group = GROUP_M * num_n;
+  const int group = tile / tiles_per_group;
+  const int first_m = group * GROUP_M;
+  const int rows = min(GROUP_M, num_m - first_m);
+  const int local = tile - group * tiles_per_group;
+  m_idx = first_m + local % rows;
+  n_idx = local / rows;
+}
+
+template <bool A_MN, bool B_MN>
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b, const Params p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES * STAGE_BYTES);
+  uint64_t* full_bar = bars;                    // [STAGES]
+  uint64_t* empty_bar = bars + STAGES;          // [STAGES]
+  uint64_t* tmem_full = bars + 2 * STAGES;      // [2]
+  uint64_t* tmem_empty = bars + 2 * STAGES + 2; // [2]
+  uint32_t* tmem_ptr_smem = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 4);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_ptr_smem + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int num_m = (p.M + BM - 1) / BM;
+  const int num_n = (p.N + BN - 1) / BN;
+  const int num_tiles = num_m * num_n;
+  const int num_kb = (p.K + BK - 1) / BK;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(&tmem_full[a], 1);
+      mbar_init(&tmem_empty[a], 128);
+    }
+    *abort_flag = 0;
+    fence_mbar_init();
+    prefetch_tensormap(&tmap_a);
+    prefetch_tensormap(&tmap_b);
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_ptr_smem, TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_ptr_smem;
+
+  if (warp == 0) {
+    // ------------------------------ TMA producer ------------------------------
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      int issued = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+        int m_idx, n_idx;
+        tile_coords(tile, num_m, num_n, m_idx, n_idx);
+        const int m0 = m_idx * BM, n0 = n_idx * BN;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait(&empty_bar[stage], phase ^ 1u, abort_flag, p.status, 10)) { ok = false; break; }
+          uint8_t* sa = smem + stage * STAGE_BYTES;
+          uint8_t* sb = sa + A_BYTES;
+          mbar_expect_tx(&full_bar[stage], STAGE_BYTES);
+          const int k0 = kb * BK;
+          if (A_MN) {
+#pragma unroll
+            for (int c = 0; c < BM / 64; ++c) tma_load_2d(sa + c * (BK * 128), &tmap_a, &full_bar[stage], m0 + c * 64, k0);
+          } else {
+            tma_load_2d(sa, &tmap_a, &full_bar[stage], k0, m0);
+          }
+          if (B_MN) {
+#pragma unroll
+            for (int c = 0; c < BN / 64; ++c) tma_load_2d(sb + c * (BK * 128), &tmap_b, &full_bar[stage], n0 + c * 64, k0);
+          } else {
+            tma_load_2d(sb, &tmap_b, &full_bar[stage], k0, n0);
+          }
+          ++issued;
+          if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+        }
+      }
+      if (!ok) {
+        // Give the copies already in flight a bounded chance to land before the CTA exits.
+        const int pending = issued < STAGES ? issued : STAGES;
+        for (int i = 0; i < pending; ++i) {
+          int s = (stage - 1 - i + 2 * STAGES) % STAGES;
+          uint32_t ph = (i < stage) ? phase : (phase ^ 1u);
+          for (int spin = 0; spin < (1 << 16) && !mbar_try_wait(&full_bar[s], ph); ++spin) {}
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------ MMA issuer --------------------------------
+    if (lane == 0) {
+      constexpr uint32_t idesc = make_idesc_bf16(BM, BN, A_MN, B_MN);
+      int stage = 0;
+      uint32_t phase = 0;
+      int it = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++it) {
+        const int acc = it & 1;
+        const uint32_t acc_phase = (it >> 1) & 1u;
+        if (!mbar_wait(&tmem_empty[acc], acc_phase ^ 1u, abort_flag, p.status, 20)) { ok = false; break; }
+        tc_fence_after_sync();
+        const uint32_t d_tmem = tmem_base + acc * BN;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait(&full_bar[stage], phase, abort_flag, p.status, 21)) { ok = false; break; }
+          tc_fence_after_sync();
+          const uint32_t sa = smem_u32(smem + stage * STAGE_BYTES);
+          const uint32_t sb = sa + A_BYTES;
+#pragma unroll
+          for (int k = 0; k < BK / 16; ++k) {
+            const uint64_t da = A_MN ? make_smem_desc(sa + k * 2048, BK * 128, 1024)
+                                     : make_smem_desc(sa + k * 32, 16, 1024);
+            const uint64_t db = B_MN ? make_smem_desc(sb + k * 2048, BK * 128, 1024)
+                                     : make_smem_desc(sb + k * 32, 16, 1024);
+            umma_ss(d_tmem, da, db, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+          }
+          umma_commit(&empty_bar[stage]);
+          if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+        }
+        if (ok) umma_commit(&tmem_full[acc]);
+      }
+    }
+  } else {
+    // ------------------------------ Epilogue ----------------------------------
+    const int quarter = warp & 3;  // TMEM lanes 32*quarter .. +31 are reachable from this warp
+    const int row_in_tile = quarter * 32 + lane;
+    int it = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++it) {
+      int m_idx, n_idx;
+      tile_coords(tile, num_m, num_n, m_idx, n_idx);
+      const int acc = it & 1;
+      const uint32_t acc_phase = (it >> 1) & 1u;
+      if (!mbar_wait(&tmem_full[acc], acc_phase, abort_flag, p.status, 30)) { ok = false; break; }
+      tc_fence_after_sync();
+      const long long row = static_cast<long long>(m_idx) * BM + row_in_tile;
+      const bool row_ok = row < p.M;
+      const int batch = (p.rows_per_batch > 0) ? static_cast<int>(row / p.rows_per_batch) : 0;
+      const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc * BN;
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; ++c) {
+        const int col0 = n_idx * BN + c * 32;
+        if (col0 >= p.N) break;  // uniform across the CTA
+        uint32_t r[32];
+        tmem_ld_x32(taddr + c * 32, r);
+        tmem_wait_ld();
+        if (row_ok) {
+#pragma unroll
+          for (int v = 0; v < 4; ++v) {  // 4 groups of 8 columns
+            const int col = col0 + v * 8;
+            if (col >= p.N) break;
+            float x[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) x[j] = __uint_as_float(r[v * 8 + j]) * p.alpha;
+            if (p.bias) {
+              const uint4 bv = *reinterpret_cast<const uint4*>(p.bias + col);
+              const uint32_t bw[4] = {bv.x, bv.y, bv.z, bv.w};
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                float2 f = unpack_bf16x2(bw[j]);
+                x[2 * j] += f.x;
+                x[2 * j + 1] += f.y;
+              }
+            }
+            if (p.epi == kEpiGeluTanh) {
+#pragma unroll
+              for (int j = 0; j < 8; ++j) x[j] = gelu_tanh(x[j]);
+            } else if (p.epi == kEpiSilu) {
+#pragma unroll
+              for (int j = 0; j < 8; ++j) x[j] = x[j] / (1.0f + __expf(-x[j]));
+            } else if (p.epi == kEpiGatedRes || p.epi == kEpiAddRes) {
+              const uint4 rv = *reinterpret_cast<const uint4*>(p.residual + row * p.ldr + col);
+              const uint32_t rw[4] = {rv.x, rv.y, rv.z, rv.w};
+              float g[8];
+              if (p.epi == kEpiGatedRes) {
+                const float4 g0 = *reinterpret_cast<const float4*>(p.gate + batch * p.gate_ld + col);
+                const float4 g1 = *reinterpret_cast<const float4*>(p.gate + batch * p.gate_ld + col + 4);
+                g[0] = g0.x; g[1] = g0.y; g[2] = g0.z; g[3] = g0.w;
+                g[4] = g1.x; g[5] = g1.y; g[6] = g1.z; g[7] = g1.w;
+              } else {
+#pragma unroll
+                for (int j = 0; j < 8; ++j) g[j] = 1.0f;
+              }
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                float2 f = unpack_bf16x2(rw[j]);
+                x[2 * j] = f.x + g[2 * j] * x[2 * j];
+                x[2 * j + 1] = f.y + g[2 * j + 1] * x[2 * j + 1];
+              }
+            }
+            if (p.out_f32) {
+              float* o = reinterpret_cast<float*>(p.out) + row * p.ldo + col;
+              *reinterpret_cast<float4*>(o) = make_float4(x[0], x[1], x[2], x[3]);
+              *reinterpret_cast<float4*>(o + 4) = make_float4(x[4], x[5], x[6], x[7]);
+            } else {
+              __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(p.out) + row * p.ldo + col;
+              uint4 ov;
+              ov.x = pack_bf16x2(x[0], x[1]);
+              ov.y = pack_bf16x2(x[2], x[3]);
+              ov.z = pack_bf16x2(x[4], x[5]);
+              ov.w = pack_bf16x2(x[6], x[7]);
+              *reinterpret_cast<uint4*>(o) = ov;
+            }
+          }
+        }
+      }
+      tc_fence_before_sync();
+      mbar_arrive(&tmem_empty[acc]);
+    }
+  }
+
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+}
+
+template <bool A_MN, bool B_MN>
+int launch(const CUtensorMap& ta, const CUtensorMap& tb, const Params& p, cudaStream_t stream) {
+  auto kern = gemm_kernel<A_MN, B_MN>;
+  static bool configured = false;
+  if (!configured) {
+    MDB_CHECK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
+    configured = true;
+  }
+  const int num_tiles = ((p.M + BM - 1) / BM) * ((p.N + BN - 1) / BN);
+  const int grid = num_tiles < sm_count() ? num_tiles : sm_count();
+  kern<<<grid, NUM_THREADS, SMEM_BYTES, stream>>>(ta, tb, p);
+  return static_cast<int>(cudaGetLastError());
+}
+
+}  // namespace gemm
+}  // namespace mdb
+
+// C entry point. A is [M,K] with leading dimension lda (a_mn_major = 0) or [K,M] (a_mn_major = 1);
+// B is [N,K] (b_mn_major = 0) or [K,N] (b_mn_major = 1). All leading dimensions are in elements and
+// must be multiples of 8; N must be a multiple of 8. Returns 0 or a CUDA / encoder error code.
+extern "C" int mdb_gemm_bf16(const void* A, const void* B, void* out, const void* bias, const void* residual,
+                             const void* gate, int M, int N, int K, long long lda, long long ldb, long long ldo,
+                             long long ldr, long long gate_ld, int rows_per_batch, int a_mn_major, int b_mn_major,
+                             int epi, int out_f32, float alpha, void* stream_ptr) {
+  using namespace mdb;
+  using namespace mdb::gemm;
+  if (M <= 0 || N <= 0 || K <= 0) return 0;
+  if ((N & 7) || (lda & 7) || (ldb & 7) || (ldo & 3) || (!out_f32 && (ldo & 7))) return 3001;
+  if ((epi == kEpiGatedRes || epi == kEpiAddRes) && (!residual || (ldr & 7))) return 3002;
+  if (epi == kEpiGatedRes && (!gate || (gate_ld & 3))) return 3003;
+  CUtensorMap ta, tb;
+  int rc;
+  if (a_mn_major) {
+    uint64_t dims[2] = {static_cast<uint64_t>(M), static_cast<uint64_t>(K)};
+    uint64_t str[1] = {static_cast<uint64_t>(lda) * 2};
+    uint32_t box[2] = {64, BK};
+    rc = encode_tmap_bf16(&ta, A, 2, dims, str, box);
+  } else {
+    uint64_t dims[2] = {static_cast<uint64_t>(K), static_cast<uint64_t>(M)};
+    uint64_t str[1] = {static_cast<uint64_t>(lda) * 2};
+    uint32_t box[2] = {BK, BM};
+    rc = encode_tmap_bf16(&ta, A, 2, dims, str, box);
+  }
+  if (rc) return rc;
+  if (b_mn_major) {
+    uint64_t dims[2] = {static_cast<uint64_t>(N), static_cast<uint64_t>(K)};
+    uint64_t str[1] = {static_cast<uint64_t>(ldb) * 2};
+    uint32_t box[2] = {64, BK};
+    rc = encode_tmap_bf16(&tb, B, 2, dims, str, box);
+  } else {
+    uint64_t dims[2] = {static_cast<uint64_t>(K), static_cast<uint64_t>(N)};
+    uint64_t str[1] = {static_cast<uint64_t>(ldb) * 2};
+    uint32_t box[2] = {BK, BN};
+    rc = encode_tmap_bf16(&tb, B, 2, dims, str, box);
+  }
+  if (rc) return rc;
+  Params p;
+  p.M = M; p.N = N; p.K = K;
+  p.out = out; p.ldo = ldo;
+  p.bias = static_cast<const __nv_bfloat16*>(bias);
+  p.residual = static_cast<const __nv_bfloat16*>(residual);
+  p.ldr = ldr;
+  p.gate = static_cast<const float*>(gate);
+  p.gate_ld = gate_ld;
+  p.rows_per_batch = rows_per_batch;
+  p.epi = epi;
+  p.out_f32 = out_f32;
+  p.alpha = alpha;
+  p.status = status_buffer();
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_ptr);
+  if (a_mn_major) {
+    return b_mn_major ? launch<true, true>(ta, tb, p, stream) : launch<true, false>(ta, tb, p, stream);
+  }
+  return b_mn_major ? launch<false, true>(ta, tb, p, stream) : launch<false, false>(ta, tb, p, stream);
+}

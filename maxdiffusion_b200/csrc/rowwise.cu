@@ -1,0 +1,672 @@
+// Memory-bound row-wise kernels (one pass over HBM each): fp32 LayerNorm + AdaLN modulation,
+// RMSNorm (+ rotary embedding), their backward passes with deterministic column reductions,
+// GELU, gated residual, bias-gradient column sums.
+//
+// They stand in for the XLA fusions the reference relies on:
+//   LayerNorm*(1+scale)+shift  src/maxdiffusion/models/wan/transformers/transformer_wan.py:486-489,519-522
+//   gated residual             :499,526-528
+//   RMSNorm + RoPE on q/k      src/maxdiffusion/models/attention_flax.py:2596-2620,2655-2677
+//
+// Shape convention: x is [rows, C] bf16 row-major, C a multiple of 8 and at most 8192. Each CTA
+// (256 threads) walks a strip of rows; thread t owns the 8-element vectors t, t+256, ... of every
+// row, so per-column partial sums live in registers for the whole strip and are written once per
+// CTA to a scratch buffer [gridDim.x * gridDim.y, n_sums, C]; a second kernel folds the partials
+// in a fixed order (bitwise reproducible).
+#include "host_common.h"
+
+namespace mdb {
+namespace rw {
+
+constexpr int THREADS = 256;
+constexpr int MAXV = 4;  // vectors of 8 per thread -> C <= 8192
+
+__device__ __forceinline__ void load8(const __nv_bfloat16* p, float (&x)[8]) {
+  const uint4 v = *reinterpret_cast<const uint4*>(p);
+  const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    float2 f = unpack_bf16x2(w[j]);
+    x[2 * j] = f.x;
+    x[2 * j + 1] = f.y;
+  }
+}
+__device__ __forceinline__ void store8(__nv_bfloat16* p, const float (&x)[8]) {
+  uint4 v;
+  v.x = pack_bf16x2(x[0], x[1]);
+  v.y = pack_bf16x2(x[2], x[3]);
+  v.z = pack_bf16x2(x[4], x[5]);
+  v.w = pack_bf16x2(x[6], x[7]);
+  *reinterpret_cast<uint4*>(p) = v;
+}
+__device__ __forceinline__ void loadf8(const float* p, float (&x)[8]) {
+  const float4 a = *reinterpret_cast<const float4*>(p);
+  const float4 b = *reinterpret_cast<const float4*>(p + 4);
+  x[0] = a.x; x[1] = a.y; x[2] = a.z; x[3] = a.w;
+  x[4] = b.x; x[5] = b.y; x[6] = b.z; x[7] = b.w;
+}
+__device__ __forceinline__ void storef8(float* p, const float (&x)[8]) {
+  *reinterpret_cast<float4*>(p) = make_float4(x[0], x[1], x[2], x[3]);
+  *reinterpret_cast<float4*>(p + 4) = make_float4(x[4], x[5], x[6], x[7]);
+}
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+// Sum over the CTA; every thread gets the result. `red` is 8 floats of shared memory.
+__device__ __forceinline__ float block_sum(float v, float* red) {
+  v = warp_sum(v);
+  __syncthreads();
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = v;
+  __syncthreads();
+  float t = 0.0f;
+#pragma unroll
+  for (int i = 0; i < THREADS / 32; ++i) t += red[i];
+  return t;
+}
+// Sum over aligned groups of 16 lanes (one 128-channel head).
+__device__ __forceinline__ float half_warp_sum(float v) {
+#pragma unroll
+  for (int o = 8; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+
+struct Strip {
+  long long begin, end;  // rows of this CTA
+  int batch;
+};
+// grid = (ctas_per_batch, num_batches); rows of one batch are contiguous.
+__device__ __forceinline__ Strip my_strip(int rows_per_batch) {
+  Strip s;
+  const int per = (rows_per_batch + gridDim.x - 1) / gridDim.x;
+  const long long base = static_cast<long long>(blockIdx.y) * rows_per_batch;
+  const int b = min(rows_per_batch, static_cast<int>(blockIdx.x) * per);
+  const int e = min(rows_per_batch, b + per);
+  s.begin = base + b;
+  s.end = base + e;
+  s.batch = blockIdx.y;
+  return s;
+}
+
+// ---------------------------------------------------------------------------------------
+// LayerNorm (fp32 statistics) with optional affine (gamma, beta: bf16 [C]) and optional
+// modulation (scale, shift: fp32 [num_batches, mod_ld]):  y = ((x-mean)*rstd*gamma+beta)*(1+scale)+shift
+// ---------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(THREADS)
+ln_fwd_kernel(const __nv_bfloat16* __restrict__ x, __nv_bfloat16* __restrict__ y,
+              const __nv_bfloat16* __restrict__ gamma, const __nv_bfloat16* __restrict__ beta,
+              const float* __restrict__ scale, const float* __restrict__ shift, long long mod_ld, int rows_per_batch,
+              int C, float eps, float* __restrict__ mean_out, float* __restrict__ rstd_out) {
+  __shared__ float red[8];
+  const Strip s = my_strip(rows_per_batch);
+  const int nvec = C >> 3;
+  for (long long row = s.begin; row < s.end; ++row) {
+    float v[MAXV][8];
+    float sum = 0.0f;
+#pragma unroll
+    for (int k = 0; k < MAXV; ++k) {
+      const int vi = threadIdx.x + k * THREADS;
+      if (vi < nvec) {
+        load8(x + row * C + vi * 8, v[k]);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) sum += v[k][j];
+      }
+    }
+    const float mean = block_sum(sum, red) / C;
+    float sq = 0.0f;
+#pragma unroll
+    for (int k = 0; k < MAXV; ++k) {
+      const int vi = threadIdx.x + k * THREADS;
+      if (vi < nvec) {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          const float d = v[k][j] - mean;
+          sq += d * d;
+        }
+      }
+    }
+    const float rstd = rsqrtf(block_sum(sq, red) / C + eps);
+    if (threadIdx.x == 0) {
+      if (mean_out) mean_out[row] = mean;
+      if (rstd_out) rstd_out[row] = rstd;
+    }
+#pragma unroll
+    for (int k = 0; k < MAXV; ++k) {
+      const int vi = threadIdx.x + k * THREADS;
+      if (vi < nvec) {
+        float o[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) o[j] = (v[k][j] - mean) * rstd;
+        if (gamma) {
+          float g[8];
+          load8(gamma + vi * 8, g);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) o[j] *= g[j];
+        }
+        if (beta) {
+          float b[8];
+          load8(beta + vi * 8, b);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) o[j] += b[j];
+        }
+        if (scale) {
+          float sc[8], sh[8];
+          loadf8(scale + s.batch * mod_ld + vi * 8, sc);
+          loadf8(shift + s.batch * mod_ld + vi * 8, sh);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) o[j] = o[j] * (1.0f + sc[j]) + sh[j];
+        }
+        store8(y + row * C + vi * 8, o);
+      }
+    }
+  }
+}
+
+// Backward of the above. Writes dx and per-CTA partial column sums
+//   partial[cta][0][c] = sum_rows dy*xhat (-> dscale, or dgamma when affine)
+//   partial[cta][1][c] = sum_rows dy      (-> dshift, or dbeta)
+// (for the modulated form the first sum is taken after the affine, i.e. d/dscale of y).
+__global__ void __launch_bounds__(THREADS)
+ln_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ x,
+              const float* __restrict__ mean_in, const float* __restrict__ rstd_in,
+              const __nv_bfloat16* __restrict__ gamma, const float* __restrict__ scale, long long mod_ld,
+              int rows_per_batch, int C, __nv_bfloat16* __restrict__ dx, float* __restrict__ partial) {
+  __shared__ float red[8];
+  const Strip s = my_strip(rows_per_batch);
+  const int nvec = C >> 3;
+  float acc0[MAXV][8], acc1[MAXV][8];
+#pragma unroll
+  for (int k = 0; k < MAXV; ++k)
+#pragma unroll
+    for (int j = 0; j < 8; ++j) acc0[k][j] = acc1[k][j] = 0.0f;
+
+  for (long long row = s.begin; row < s.end; ++row) {
+    const float mean = mean_in[row], rstd = rstd_in[row];
+    float g[MAXV][8], xh[MAXV][8];
+    float s1 = 0.0f, s2 = 0.0f;
+#pragma unroll
+    for (int k = 0; k < MAXV; ++k) {
+      const int vi = threadIdx.x + k * THREADS;
+      if (vi < nvec) {
+        float d[8], xv[8];
+        load8(dy + row * C + vi * 8, d);
+        load8(x + row * C + vi * 8, xv);
+        float w[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) w[j] = 1.0f;
+        if (scale) {
+          float sc[8];
+          loadf8(scale + s.batch * mod_ld + vi * 8, sc);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) w[j] = 1.0f + sc[j];
+        }
+        if (gamma) {
+          float gm[8];
+          load8(gamma + vi * 8, gm);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) w[j] *= gm[j];
+        }
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          xh[k][j] = (xv[j] - mean) * rstd;
+          g[k][j] = d[j] * w[j];
+          s1 += g[k][j];
+          s2 += g[k][j] * xh[k][j];
+          acc0[k][j] += d[j] * xh[k][j];
+          acc1[k][j] += d[j];
+        }
+      }
+    }
+    const float m1 = block_sum(s1, red) / C;
+    const float m2 = block_sum(s2, red) / C;
+#pragma unroll
+    for (int k = 0; k < MAXV; ++k) {
+      const int vi = threadIdx.x + k * THREADS;
+      if (vi < nvec) {
+        float o[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) o[j] = rstd * (g[k][j] - m1 - xh[k][j] * m2);
+        store8(dx + row * C + vi * 8, o);
+      }
+    }
+  }
+  if (partial) {
+    const long long cta = static_cast<long long>(blockIdx.y) * gridDim.x + blockIdx.x;
+#pragma unroll
+    for (int k = 0; k < MAXV; ++k) {
+      const int vi = threadIdx.x + k * THREADS;
+      if (vi < nvec) {
+        storef8(partial + (cta * 2 + 0) * C + vi * 8, acc0[k]);
+        storef8(partial + (cta * 2 + 1) * C + vi * 8, acc1[k]);
+      }
+    }
+  }
+}
+
+// out[b][s][c] = sum over the CTAs of batch b of partial[cta][s][c]  (fixed order)
+__global__ void fold_partials_kernel(const float* __restrict__ partial, float* __restrict__ out, int ctas_per_batch,
+                                     int n_sums, int C, int accumulate) {
+  const int idx = blockIdx.x * blockDim.x + threadIdx.x;  // over n_sums*C
+  const int b = blockIdx.y;
+  if (idx >= n_sums * C) return;
+  float t = 0.0f;
+  for (int i = 0; i < ctas_per_batch; ++i) {
+    t += partial[(static_cast<long long>(b) * ctas_per_batch + i) * n_sums * C + idx];
+  }
+  float* o = out + static_cast<long long>(b) * n_sums * C + idx;
+  *o = accumulate ? (*o + t) : t;
+}
+
+// ---------------------------------------------------------------------------------------
+// RMSNorm over groups of `group` channels (group == C: across all heads; group == 128: per head),
+// learned weight w [C or 128], followed by an optional rotary embedding on interleaved pairs of
+// each 128-wide head: cos/sin are fp32 [rows_per_batch, 64].
+// ---------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(THREADS)
+rms_rope_fwd_kernel(const __nv_bfloat16* __restrict__ x, long long ldx, __nv_bfloat16* __restrict__ y, long long ldy,
+                    const __nv_bfloat16* __restrict__ w, int w_per_head, const float* __restrict__ cos_t,
+                    const float* __restrict__ sin_t, int rows_per_batch, int C, int group, float eps,
+                    float* __restrict__ rstd_out) {
+  __shared__ float red[8];
+  const Strip s = my_strip(rows_per_batch);
+  const int nvec = C >> 3;
+  for (long long row = s.begin; row < s.end; ++row) {
+    const int pos = static_cast<int>(row - static_cast<long long>(s.batch) * rows_per_batch);
+    float v[MAXV][8];
+    float sq[MAXV];
+    float total = 0.0f;
+#pragma unroll
+    for (int k = 0; k < MAXV; ++k) {
+      const int vi = threadIdx.x + k * THREADS;
+      sq[k] = 0.0f;
+      if (vi < nvec) {
+        load8(x + row * ldx + vi * 8, v[k]);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) sq[k] += v[k][j] * v[k][j];
+      }
+      total += sq[k];
+    }
+    float rstd_all = 0.0f;
+    if (group == C) rstd_all = rsqrtf(block_sum(total, red) / C + eps);
+#pragma unroll
+    for (int k = 0; k < MAXV; ++k) {
+      const int vi = threadIdx.x + k * THREADS;
+      float rstd = rstd_all;
+      if (group != C) rstd = rsqrtf(half_warp_sum(sq[k]) / 128.0f + eps);  // all lanes take part
+      if (vi < nvec) {
+        if (rstd_out) {
+          if (group == C) {
+            if (threadIdx.x == 0 && k == 0) rstd_out[row] = rstd;
+          } else if ((vi & 15) == 0) {
+            rstd_out[row * (C >> 7) + (vi >> 4)] = rstd;
+          }
+        }
+        float o[8];
+        if (w) {
+          float wv[8];
+          load8(w + (w_per_head ? (vi & 15) * 8 : vi * 8), wv);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) o[j] = v[k][j] * rstd * wv[j];
+        } else {
+#pragma unroll
+          for (int j = 0; j < 8; ++j) o[j] = v[k][j] * rstd;
+        }
+        if (cos_t) {
+          const int pair0 = (vi & 15) * 4;  // 4 pairs per vector, 64 pairs per head
+          const float4 cv = *reinterpret_cast<const float4*>(cos_t + static_cast<long long>(pos) * 64 + pair0);
+          const float4 sv = *reinterpret_cast<const float4*>(sin_t + static_cast<long long>(pos) * 64 + pair0);
+          const float c4[4] = {cv.x, cv.y, cv.z, cv.w};
+          const float s4[4] = {sv.x, sv.y, sv.z, sv.w};
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const float a = o[2 * j], b = o[2 * j + 1];
+            o[2 * j] = a * c4[j] - b * s4[j];
+            o[2 * j + 1] = a * s4[j] + b * c4[j];
+          }
+        }
+        store8(y + row * ldy + vi * 8, o);
+      }
+    }
+  }
+}
+
+// Backward: dy is the gradient w.r.t. the rotated output. partial[cta][0][c] = sum_rows dyn*xhat
+// (gradient of w before folding heads when w_per_head).
+__global__ void __launch_bounds__(THREADS)
+rms_rope_bwd_kernel(const __nv_bfloat16* __restrict__ dy, long long lddy, const __nv_bfloat16* __restrict__ x,
+                    long long ldx, const float* __restrict__ rstd_in, const __nv_bfloat16* __restrict__ w,
+                    int w_per_head, const float* __restrict__ cos_t, const float* __restrict__ sin_t,
+                    int rows_per_batch, int C, int group, __nv_bfloat16* __restrict__ dx, long long lddx,
+                    float* __restrict__ partial) {
+  __shared__ float red[8];
+  const Strip s = my_strip(rows_per_batch);
+  const int nvec = C >> 3;
+  float acc[MAXV][8];
+#pragma unroll
+  for (int k = 0; k < MAXV; ++k)
+#pragma unroll
+    for (int j = 0; j < 8; ++j) acc[k][j] = 0.0f;
+
+  for (long long row = s.begin; row < s.end; ++row) {
+    const int pos = static_cast<int>(row - static_cast<long long>(s.batch) * rows_per_batch);
+    float g[MAXV][8], xh[MAXV][8];
+    float dot[MAXV];
+    float total = 0.0f;
+#pragma unroll
+    for (int k = 0; k < MAXV; ++k) {
+      const int vi = threadIdx.x + k * THREADS;
+      dot[k] = 0.0f;
+      if (vi < nvec) {
+        float d[8], xv[8];
+        load8(dy + row * lddy + vi * 8, d);
+        load8(x + row * ldx + vi * 8, xv);
+        if (cos_t) {
+          const int pair0 = (vi & 15) * 4;
+          const float4 cv = *reinterpret_cast<const float4*>(cos_t + static_cast<long long>(pos) * 64 + pair0);
+          const float4 sv = *reinterpret_cast<const float4*>(sin_t + static_cast<long long>(pos) * 64 + pair0);
+          const float c4[4] = {cv.x, cv.y, cv.z, cv.w};
+          const float s4[4] = {sv.x, sv.y, sv.z, sv.w};
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const float a = d[2 * j], b = d[2 * j + 1];
+            d[2 * j] = a * c4[j] + b * s4[j];
+            d[2 * j + 1] = -a * s4[j] + b * c4[j];
+          }
+        }
+        const float rstd = (group == C) ? rstd_in[row] : rstd_in[row * (C >> 7) + (vi >> 4)];
+        float wv[8];
+        if (w) {
+          load8(w + (w_per_head ? (vi & 15) * 8 : vi * 8), wv);
+        } else {
+#pragma unroll
+          for (int j = 0; j < 8; ++j) wv[j] = 1.0f;
+        }
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          xh[k][j] = xv[j] * rstd;
+          g[k][j] = d[j] * wv[j];
+          dot[k] += g[k][j] * xh[k][j];
+          acc[k][j] += d[j] * xh[k][j];
+          g[k][j] *= rstd;
+        }
+      }
+      total += dot[k];
+    }
+    float mean_all = 0.0f;
+    if (group == C) mean_all = block_sum(total, red) / C;
+#pragma unroll
+    for (int k = 0; k < MAXV; ++k) {
+      const int vi = threadIdx.x + k * THREADS;
+      float mdot = mean_all;
+      if (group != C) mdot = half_warp_sum(dot[k]) / 128.0f;
+      if (vi < nvec) {
+        const float rstd = (group == C) ? rstd_in[row] : rstd_in[row * (C >> 7) + (vi >> 4)];
+        float o[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) o[j] = g[k][j] - xh[k][j] * mdot * rstd;
+        store8(dx + row * lddx + vi * 8, o);
+      }
+    }
+  }
+  if (partial) {
+    const long long cta = static_cast<long long>(blockIdx.y) * gridDim.x + blockIdx.x;
+#pragma unroll
+    for (int k = 0; k < MAXV; ++k) {
+      const int vi = threadIdx.x + k * THREADS;
+      if (vi < nvec) storef8(partial + cta * C + vi * 8, acc[k]);
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------------------
+// Gated residual:  out = res + gate[b] * y   (gate fp32 [num_batches, gate_ld], may be nullptr -> 1)
+// backward: dy = dout * gate ; partial[cta][0][c] = sum_rows dout * y (-> dgate)
+// ---------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(THREADS)
+gated_res_fwd_kernel(const __nv_bfloat16* __restrict__ res, const __nv_bfloat16* __restrict__ y,
+                     const float* __restrict__ gate, long long gate_ld, int rows_per_batch, int C,
+                     __nv_bfloat16* __restrict__ out) {
+  const Strip s = my_strip(rows_per_batch);
+  const int nvec = C >> 3;
+  for (int k = 0; k < MAXV; ++k) {
+    const int vi = threadIdx.x + k * THREADS;
+    if (vi >= nvec) break;
+    float g[8];
+    if (gate) {
+      loadf8(gate + s.batch * gate_ld + vi * 8, g);
+    } else {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) g[j] = 1.0f;
+    }
+    for (long long row = s.begin; row < s.end; ++row) {
+      float r[8], v[8], o[8];
+      load8(res + row * C + vi * 8, r);
+      load8(y + row * C + vi * 8, v);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) o[j] = r[j] + g[j] * v[j];
+      store8(out + row * C + vi * 8, o);
+    }
+  }
+}
+
+__global__ void __launch_bounds__(THREADS)
+gated_res_bwd_kernel(const __nv_bfloat16* __restrict__ dout, const __nv_bfloat16* __restrict__ y,
+                     const float* __restrict__ gate, long long gate_ld, int rows_per_batch, int C,
+                     __nv_bfloat16* __restrict__ dy, float* __restrict__ partial) {
+  const Strip s = my_strip(rows_per_batch);
+  const int nvec = C >> 3;
+  const long long cta = static_cast<long long>(blockIdx.y) * gridDim.x + blockIdx.x;
+  for (int k = 0; k < MAXV; ++k) {
+    const int vi = threadIdx.x + k * THREADS;
+    if (vi >= nvec) break;
+    float g[8], acc[8];
+    loadf8(gate + s.batch * gate_ld + vi * 8, g);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) acc[j] = 0.0f;
+    for (long long row = s.begin; row < s.end; ++row) {
+      float d[8], v[8], o[8];
+      load8(dout + row * C + vi * 8, d);
+      load8(y + row * C + vi * 8, v);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        o[j] = d[j] * g[j];
+        acc[j] += d[j] * v[j];
+      }
+      store8(dy + row * C + vi * 8, o);
+    }
+    storef8(partial + cta * C + vi * 8, acc);
+  }
+}
+
+// Column sums of a bf16 matrix (bias gradient): partial[cta][0][c] = sum_rows x
+__global__ void __launch_bounds__(THREADS)
+colsum_kernel(const __nv_bfloat16* __restrict__ x, long long ldx, int rows_per_batch, int C,
+              float* __restrict__ partial) {
+  const Strip s = my_strip(rows_per_batch);
+  const int nvec = C >> 3;
+  const long long cta = static_cast<long long>(blockIdx.y) * gridDim.x + blockIdx.x;
+  for (int vi = threadIdx.x; vi < nvec; vi += THREADS) {
+    float acc[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) acc[j] = 0.0f;
+    for (long long row = s.begin; row < s.end; ++row) {
+      float v[8];
+      load8(x + row * ldx + vi * 8, v);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) acc[j] += v[j];
+    }
+    storef8(partial + cta * C + vi * 8, acc);
+  }
+}
+
+// ---------------------------------------------------------------------------------------
+// Flat elementwise: GELU(tanh) forward / backward, SiLU-gate (a * silu(b)), plain add.
+// ---------------------------------------------------------------------------------------
+__global__ void gelu_fwd_kernel(const __nv_bfloat16* __restrict__ u, __nv_bfloat16* __restrict__ y, long long nvec) {
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < nvec;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    float v[8];
+    load8(u + i * 8, v);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) v[j] = gelu_tanh(v[j]);
+    store8(y + i * 8, v);
+  }
+}
+__global__ void gelu_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ u,
+                                __nv_bfloat16* __restrict__ du, long long nvec) {
+  const float k0 = 0.7978845608028654f, k1 = 0.044715f;
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < nvec;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    float d[8], v[8], o[8];
+    load8(dy + i * 8, d);
+    load8(u + i * 8, v);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const float x = v[j];
+      const float t = tanhf(k0 * (x + k1 * x * x * x));
+      const float dt = (1.0f - t * t) * k0 * (1.0f + 3.0f * k1 * x * x);
+      o[j] = d[j] * (0.5f * (1.0f + t) + 0.5f * x * dt);
+    }
+    store8(du + i * 8, o);
+  }
+}
+
+}  // namespace rw
+}  // namespace mdb
+
+// ---------------------------------------------------------------------------------------
+// C entry points. `ctas_per_batch` chooses the strip width; `scratch` must hold
+// ctas_per_batch * num_batches * n_sums * C floats. Return 0 or a CUDA error code.
+// ---------------------------------------------------------------------------------------
+using namespace mdb;
+using namespace mdb::rw;
+
+static inline int check_c(int C) { return (C <= 0 || (C & 7) || C > THREADS * MAXV * 8) ? 3201 : 0; }
+
+extern "C" int mdb_ln_fwd(const void* x, void* y, const void* gamma, const void* beta, const float* scale,
+                          const float* shift, long long mod_ld, int num_batches, int rows_per_batch, int C, float eps,
+                          float* mean_out, float* rstd_out, int ctas_per_batch, void* stream) {
+  if (int rc = check_c(C)) return rc;
+  if (num_batches <= 0 || rows_per_batch <= 0) return 0;
+  dim3 grid(ctas_per_batch, num_batches);
+  ln_fwd_kernel<<<grid, THREADS, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const __nv_bfloat16*>(x), static_cast<__nv_bfloat16*>(y), static_cast<const __nv_bfloat16*>(gamma),
+      static_cast<const __nv_bfloat16*>(beta), scale, shift, mod_ld, rows_per_batch, C, eps, mean_out, rstd_out);
+  return static_cast<int>(cudaGetLastError());
+}
+
+// out_sums: fp32 [num_batches, 2, C] (dscale/dshift per batch, or dgamma/dbeta with num_batches folded by caller)
+extern "C" int mdb_ln_bwd(const void* dy, const void* x, const float* mean, const float* rstd, const void* gamma,
+                          const float* scale, long long mod_ld, int num_batches, int rows_per_batch, int C, void* dx,
+                          float* out_sums, float* scratch, int ctas_per_batch, void* stream) {
+  if (int rc = check_c(C)) return rc;
+  if (num_batches <= 0 || rows_per_batch <= 0) return 0;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  dim3 grid(ctas_per_batch, num_batches);
+  ln_bwd_kernel<<<grid, THREADS, 0, st>>>(static_cast<const __nv_bfloat16*>(dy), static_cast<const __nv_bfloat16*>(x),
+                                          mean, rstd, static_cast<const __nv_bfloat16*>(gamma), scale, mod_ld,
+                                          rows_per_batch, C, static_cast<__nv_bfloat16*>(dx),
+                                          out_sums ? scratch : nullptr);
+  if (out_sums) {
+    dim3 g2((2 * C + 255) / 256, num_batches);
+    fold_partials_kernel<<<g2, 256, 0, st>>>(scratch, out_sums, ctas_per_batch, 2, C, 0);
+  }
+  return static_cast<int>(cudaGetLastError());
+}
+
+extern "C" int mdb_rms_rope_fwd(const void* x, long long ldx, void* y, long long ldy, const void* w, int w_per_head,
+                                const float* cos_t, const float* sin_t, int num_batches, int rows_per_batch, int C,
+                                int group, float eps, float* rstd_out, int ctas_per_batch, void* stream) {
+  if (int rc = check_c(C)) return rc;
+  if ((group != C && group != 128) || (C & 127)) return 3202;
+  if (num_batches <= 0 || rows_per_batch <= 0) return 0;
+  dim3 grid(ctas_per_batch, num_batches);
+  rms_rope_fwd_kernel<<<grid, THREADS, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const __nv_bfloat16*>(x), ldx, static_cast<__nv_bfloat16*>(y), ldy,
+      static_cast<const __nv_bfloat16*>(w), w_per_head, cos_t, sin_t, rows_per_batch, C, group, eps, rstd_out);
+  return static_cast<int>(cudaGetLastError());
+}
+
+// dw_out: fp32 [C] summed over batches (accumulated over `num_batches` folds).
+extern "C" int mdb_rms_rope_bwd(const void* dy, long long lddy, const void* x, long long ldx, const float* rstd,
+                                const void* w, int w_per_head, const float* cos_t, const float* sin_t,
+                                int num_batches, int rows_per_batch, int C, int group, void* dx, long long lddx,
+                                float* dw_out, float* scratch, int ctas_per_batch, void* stream) {
+  if (int rc = check_c(C)) return rc;
+  if ((group != C && group != 128) || (C & 127)) return 3202;
+  if (num_batches <= 0 || rows_per_batch <= 0) return 0;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  dim3 grid(ctas_per_batch, num_batches);
+  rms_rope_bwd_kernel<<<grid, THREADS, 0, st>>>(
+      static_cast<const __nv_bfloat16*>(dy), lddy, static_cast<const __nv_bfloat16*>(x), ldx, rstd,
+      static_cast<const __nv_bfloat16*>(w), w_per_head, cos_t, sin_t, rows_per_batch, C, group,
+      static_cast<__nv_bfloat16*>(dx), lddx, dw_out ? scratch : nullptr);
+  if (dw_out) {
+    // fold all CTAs of all batches into one [C] vector
+    dim3 g2((C + 255) / 256, 1);
+    fold_partials_kernel<<<g2, 256, 0, st>>>(scratch, dw_out, ctas_per_batch * num_batches, 1, C, 0);
+  }
+  return static_cast<int>(cudaGetLastError());
+}
+
+extern "C" int mdb_gated_res_fwd(const void* res, const void* y, const float* gate, long long gate_ld,
+                                 int num_batches, int rows_per_batch, int C, void* out, int ctas_per_batch,
+                                 void* stream) {
+  if (int rc = check_c(C)) return rc;
+  if (num_batches <= 0 || rows_per_batch <= 0) return 0;
+  dim3 grid(ctas_per_batch, num_batches);
+  gated_res_fwd_kernel<<<grid, THREADS, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const __nv_bfloat16*>(res), static_cast<const __nv_bfloat16*>(y), gate, gate_ld, rows_per_batch, C,
+      static_cast<__nv_bfloat16*>(out));
+  return static_cast<int>(cudaGetLastError());
+}
+
+// dgate_out: fp32 [num_batches, C]
+extern "C" int mdb_gated_res_bwd(const void* dout, const void* y, const float* gate, long long gate_ld,
+                                 int num_batches, int rows_per_batch, int C, void* dy, float* dgate_out,
+                                 float* scratch, int ctas_per_batch, void* stream) {
+  if (int rc = check_c(C)) return rc;
+  if (num_batches <= 0 || rows_per_batch <= 0) return 0;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  dim3 grid(ctas_per_batch, num_batches);
+  gated_res_bwd_kernel<<<grid, THREADS, 0, st>>>(static_cast<const __nv_bfloat16*>(dout),
+                                                 static_cast<const __nv_bfloat16*>(y), gate, gate_ld, rows_per_batch,
+                                                 C, static_cast<__nv_bfloat16*>(dy), scratch);
+  dim3 g2((C + 255) / 256, num_batches);
+  fold_partials_kernel<<<g2, 256, 0, st>>>(scratch, dgate_out, ctas_per_batch, 1, C, 0);
+  return static_cast<int>(cudaGetLastError());
+}
+
+// out: fp32 [C] = column sums of x [rows, C] (leading dimension ldx)
+extern "C" int mdb_colsum(const void* x, long long ldx, int rows, int C, float* out, float* scratch,
+                          int ctas, void* stream) {
+  if (C <= 0 || (C & 7)) return 3201;
+  if (rows <= 0) return 0;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  dim3 grid(ctas, 1);
+  colsum_kernel<<<grid, THREADS, 0, st>>>(static_cast<const __nv_bfloat16*>(x), ldx, rows, C, scratch);
+  dim3 g2((C + 255) / 256, 1);
+  fold_partials_kernel<<<g2, 256, 0, st>>>(scratch, out, ctas, 1, C, 0);
+  return static_cast<int>(cudaGetLastError());
+}
+
+extern "C" int mdb_gelu_fwd(const void* u, void* y, long long n, void* stream) {
+  if (n & 7) return 3203;
+  if (n == 0) return 0;
+  const long long nvec = n >> 3;
+  const int blocks = static_cast<int>(nvec / 256 + 1 < 148 * 8 ? nvec / 256 + 1 : 148 * 8);
+  gelu_fwd_kernel<<<blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(static_cast<const __nv_bfloat16*>(u),
+                                                                          static_cast<__nv_bfloat16*>(y), nvec);
+  return static_cast<int>(cudaGetLastError());
+}
+extern "C" int mdb_gelu_bwd(const void* dy, const void* u, void* du, long long n, void* stream) {
+  if (n & 7) return 3203;
+  if (n == 0) return 0;
+  const long long nvec = n >> 3;
+  const int blocks = static_cast<int>(nvec / 256 + 1 < 148 * 8 ? nvec / 256 + 1 : 148 * 8);
+  gelu_bwd_kernel<<<blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const __nv_bfloat16*>(dy), static_cast<const __nv_bfloat16*>(u), static_cast<__nv_bfloat16*>(du),
+      nvec);
+  return static_cast<int>(cudaGetLastError());
+}

@@ -1,0 +1,134 @@
+"""ctypes loader for the sm_100a kernel library (`maxdiffusion_b200/_kernels.so`).
+
+The library is built in-tree by `maxdiffusion_b200.build`. On a machine with a GPU every op in
+`maxdiffusion_b200.ops` requires it and raises if it is missing — there is no silent PyTorch
+fallback for CUDA tensors. On CPU the ops run their pure-PyTorch reference implementation.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+import threading
+from pathlib import Path
+
+import torch
+
+_LIB = None
+_LOCK = threading.Lock()
+LIB_PATH = Path(__file__).resolve().parent.parent / "_kernels.so"
+
+# launch counter: every successful kernel-library call increments it (bench.py reports it)
+_launches = 0
+
+
+class KernelError(RuntimeError):
+  pass
+
+
+def lib() -> ctypes.CDLL:
+  global _LIB
+  if _LIB is not None:
+    return _LIB
+  with _LOCK:
+    if _LIB is None:
+      if not LIB_PATH.exists():
+        if os.environ.get("MDB200_NO_AUTOBUILD") == "1":
+          raise KernelError(f"{LIB_PATH} is missing; run `python -m maxdiffusion_b200.build`")
+        from maxdiffusion_b200 import build as _build
+
+        _build.build(verbose=False)
+      _LIB = ctypes.CDLL(str(LIB_PATH))
+      _declare(_LIB)
+  return _LIB
+
+
+def available() -> bool:
+  """True when CUDA tensors can be served by the kernel library."""
+  return torch.cuda.is_available()
+
+
+def use_kernels(*tensors: torch.Tensor) -> bool:
+  """Dispatch rule: CUDA bf16 tensors go to the hand-written kernels, everything else to the reference."""
+  t = tensors[0]
+  return t.is_cuda
+
+
+def stream() -> ctypes.c_void_p:
+  return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def ptr(t: torch.Tensor | None) -> ctypes.c_void_p:
+  return ctypes.c_void_p(0 if t is None else t.data_ptr())
+
+
+def check(rc: int, what: str) -> None:
+  global _launches
+  if rc != 0:
+    raise KernelError(f"{what} failed with code {rc}")
+  _launches += 1
+
+
+def launch_count() -> int:
+  return _launches
+
+
+def read_status(clear: bool = True) -> tuple[int, int, int, int]:
+  """Returns (code, where, block, detail) of the device status word; code 0 means no kernel gave up a wait."""
+  out = (ctypes.c_uint * 4)()
+  rc = lib().mdb_read_status(out, 1 if clear else 0)
+  if rc != 0:
+    raise KernelError(f"mdb_read_status failed with code {rc}")
+  return tuple(int(v) for v in out)
+
+
+def raise_on_device_status() -> None:
+  code, where, block, detail = read_status(clear=True)
+  if code != 0:
+    names = {1: "mbarrier wait timed out", 2: "flag wait timed out", 3: "bad argument"}
+    raise KernelError(f"device status: {names.get(code, code)} at site {where}, block {block}, detail {detail}")
+
+
+def _declare(L: ctypes.CDLL) -> None:
+  c_void_p, c_int, c_ll, c_float = ctypes.c_void_p, ctypes.c_int, ctypes.c_longlong, ctypes.c_float
+  c_ull = ctypes.c_ulonglong
+  L.mdb_read_status.argtypes = [ctypes.POINTER(ctypes.c_uint), c_int]
+  L.mdb_read_status.restype = c_int
+  L.mdb_sm_count.restype = c_int
+  L.mdb_gemm_bf16.argtypes = [c_void_p] * 6 + [c_int] * 3 + [c_ll] * 5 + [c_int] * 5 + [c_float, c_void_p]
+  L.mdb_gemm_bf16.restype = c_int
+  L.mdb_flash_fwd.argtypes = ([c_void_p, ctypes.POINTER(c_void_p), ctypes.POINTER(c_void_p), c_void_p, c_void_p]
+                              + [c_int] * 4 + [ctypes.POINTER(c_int)] + [c_ll] * 12 + [c_float, c_void_p, ctypes.c_uint,
+                                                                                      c_void_p])
+  L.mdb_flash_fwd.restype = c_int
+  L.mdb_ln_fwd.argtypes = [c_void_p] * 6 + [c_ll, c_int, c_int, c_int, c_float, c_void_p, c_void_p, c_int, c_void_p]
+  L.mdb_ln_fwd.restype = c_int
+  L.mdb_ln_bwd.argtypes = [c_void_p] * 6 + [c_ll, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p]
+  L.mdb_ln_bwd.restype = c_int
+  L.mdb_rms_rope_fwd.argtypes = [c_void_p, c_ll, c_void_p, c_ll, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int,
+                                 c_int, c_int, c_float, c_void_p, c_int, c_void_p]
+  L.mdb_rms_rope_fwd.restype = c_int
+  L.mdb_rms_rope_bwd.argtypes = [c_void_p, c_ll, c_void_p, c_ll, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int,
+                                 c_int, c_int, c_int, c_void_p, c_ll, c_void_p, c_void_p, c_int, c_void_p]
+  L.mdb_rms_rope_bwd.restype = c_int
+  L.mdb_gated_res_fwd.argtypes = [c_void_p, c_void_p, c_void_p, c_ll, c_int, c_int, c_int, c_void_p, c_int, c_void_p]
+  L.mdb_gated_res_fwd.restype = c_int
+  L.mdb_gated_res_bwd.argtypes = [c_void_p, c_void_p, c_void_p, c_ll, c_int, c_int, c_int, c_void_p, c_void_p,
+                                  c_void_p, c_int, c_void_p]
+  L.mdb_gated_res_bwd.restype = c_int
+  L.mdb_colsum.argtypes = [c_void_p, c_ll, c_int, c_int, c_void_p, c_void_p, c_int, c_void_p]
+  L.mdb_colsum.restype = c_int
+  L.mdb_gelu_fwd.argtypes = [c_void_p, c_void_p, c_ll, c_void_p]
+  L.mdb_gelu_fwd.restype = c_int
+  L.mdb_gelu_bwd.argtypes = [c_void_p, c_void_p, c_void_p, c_ll, c_void_p]
+  L.mdb_gelu_bwd.restype = c_int
+  L.mdb_adamw.argtypes = [c_void_p] * 4 + [c_ll] + [c_float] * 9 + [c_ull, c_int, c_int, c_int, c_void_p]
+  L.mdb_adamw.restype = c_int
+  L.mdb_sumsq_maxabs.argtypes = [c_void_p, c_ll, c_int, c_void_p, c_void_p, c_int, c_void_p]
+  L.mdb_sumsq_maxabs.restype = c_int
+  for name, fn in _OPTIONAL.items():
+    if hasattr(L, name):
+      fn(L)
+
+
+# symbols added by later kernels register their signatures here
+_OPTIONAL: dict = {}

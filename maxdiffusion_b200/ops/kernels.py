@@ -1,0 +1,227 @@
+"""Thin, typed Python wrappers over the C entry points of `_kernels.so` (no autograd here).
+
+Every function takes CUDA tensors, checks layout assumptions, launches on the current stream and
+returns freshly allocated outputs. `maxdiffusion_b200.ops.functional` builds the differentiable ops
+on top of these.
+"""
+from __future__ import annotations
+
+import ctypes
+import math
+from typing import Sequence
+
+import torch
+
+from . import _lib
+
+_EPI = {"none": 0, "gelu_tanh": 1, "gated_res": 2, "silu": 3, "add_res": 4}
+_TARGET_CTAS = 148 * 4
+
+
+def _ctas_per_batch(num_batches: int, rows_per_batch: int) -> int:
+  return max(1, min(rows_per_batch, _TARGET_CTAS // max(1, num_batches)))
+
+
+def _rowmajor(t: torch.Tensor) -> torch.Tensor:
+  return t if t.stride(-1) == 1 else t.contiguous()
+
+
+def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = False, bias=None, epi: str = "none",
+         residual=None, gate=None, rows_per_batch: int = 0, out=None, out_dtype=torch.bfloat16, alpha: float = 1.0):
+  """D[M,N] = epi(alpha * A·Bᵀ + bias) on the tcgen05 GEMM. A: [M,K] (or [K,M] if a_mn); B: [N,K] (or [K,N])."""
+  assert a.dtype == torch.bfloat16 and b.dtype == torch.bfloat16 and a.dim() == 2 and b.dim() == 2
+  a, b = _rowmajor(a), _rowmajor(b)
+  K, M = (a.shape if a_mn else a.shape[::-1])
+  Kb, N = (b.shape if b_mn else b.shape[::-1])
+  assert K == Kb, f"contraction mismatch {a.shape} {b.shape} a_mn={a_mn} b_mn={b_mn}"
+  if out is None:
+    out = torch.empty((M, N), device=a.device, dtype=out_dtype)
+  assert out.stride(-1) == 1 and out.shape == (M, N)
+  if residual is not None:
+    residual = _rowmajor(residual)
+    assert residual.dtype == torch.bfloat16
+  if gate is not None:
+    assert gate.dtype == torch.float32 and gate.stride(-1) == 1
+  if bias is not None:
+    assert bias.dtype == torch.bfloat16 and bias.is_contiguous()
+  rc = _lib.lib().mdb_gemm_bf16(
+      _lib.ptr(a), _lib.ptr(b), _lib.ptr(out), _lib.ptr(bias), _lib.ptr(residual), _lib.ptr(gate), M, N, K,
+      a.stride(0), b.stride(0), out.stride(0), residual.stride(0) if residual is not None else 0,
+      gate.stride(0) if gate is not None and gate.dim() == 2 else 0, rows_per_batch, int(a_mn), int(b_mn), _EPI[epi],
+      int(out.dtype == torch.float32), float(alpha), _lib.stream())
+  _lib.check(rc, "mdb_gemm_bf16")
+  return out
+
+
+def flash_fwd(q: torch.Tensor, k_list: Sequence[torch.Tensor], v_list: Sequence[torch.Tensor], scale: float | None = None,
+              return_lse: bool = True, seg_flags: torch.Tensor | None = None, flag_target: int = 0):
+  """Flash attention forward over KV segments. q: [B,Sq,H,128]; k/v: lists of [B,Skv_i,H,128] sharing strides."""
+  if isinstance(k_list, torch.Tensor):
+    k_list, v_list = [k_list], [v_list]
+  B, Sq, H, D = q.shape
+  assert D == 128 and q.dtype == torch.bfloat16 and q.stride(-1) == 1
+  k0, v0 = k_list[0], v_list[0]
+  for k, v in zip(k_list, v_list):
+    assert k.dtype == torch.bfloat16 and v.dtype == torch.bfloat16
+    assert k.stride() == k0.stride() and v.stride() == v0.stride() and k.stride(-1) == 1 and v.stride(-1) == 1
+  n = len(k_list)
+  out = torch.empty((B, Sq, H, D), device=q.device, dtype=torch.bfloat16)
+  lse = torch.empty((B, H, Sq), device=q.device, dtype=torch.float32) if return_lse else None
+  kp = (ctypes.c_void_p * n)(*[k.data_ptr() for k in k_list])
+  vp = (ctypes.c_void_p * n)(*[v.data_ptr() for v in v_list])
+  lens = (ctypes.c_int * n)(*[k.shape[1] for k in k_list])
+  scale = scale if scale is not None else 1.0 / math.sqrt(D)
+  rc = _lib.lib().mdb_flash_fwd(
+      _lib.ptr(q), kp, vp, _lib.ptr(out), _lib.ptr(lse), B, H, Sq, n, lens,
+      q.stride(0), q.stride(1), q.stride(2), k0.stride(0), k0.stride(1), k0.stride(2),
+      v0.stride(0), v0.stride(1), v0.stride(2), out.stride(0), out.stride(1), out.stride(2),
+      float(scale), _lib.ptr(seg_flags), int(flag_target), _lib.stream())
+  _lib.check(rc, "mdb_flash_fwd")
+  return (out, lse) if return_lse else out
+
+
+def ln_fwd(x, gamma=None, beta=None, scale=None, shift=None, eps=1e-6, save_stats=False):
+  """x: [B,S,C] bf16 contiguous; scale/shift: fp32 [B,C] (row stride arbitrary)."""
+  assert x.dtype == torch.bfloat16 and x.is_contiguous()
+  B, S, C = x.shape
+  y = torch.empty_like(x)
+  mean = torch.empty((B, S), device=x.device, dtype=torch.float32) if save_stats else None
+  rstd = torch.empty((B, S), device=x.device, dtype=torch.float32) if save_stats else None
+  if scale is not None:
+    assert scale.dtype == torch.float32 and shift.dtype == torch.float32
+    assert scale.stride(-1) == 1 and shift.stride(-1) == 1 and scale.stride(0) == shift.stride(0)
+  rc = _lib.lib().mdb_ln_fwd(_lib.ptr(x), _lib.ptr(y), _lib.ptr(gamma), _lib.ptr(beta), _lib.ptr(scale),
+                             _lib.ptr(shift), scale.stride(0) if scale is not None else 0, B, S, C, float(eps),
+                             _lib.ptr(mean), _lib.ptr(rstd), _ctas_per_batch(B, S), _lib.stream())
+  _lib.check(rc, "mdb_ln_fwd")
+  return (y, mean, rstd) if save_stats else y
+
+
+def ln_bwd(dy, x, mean, rstd, gamma=None, scale=None, need_sums=True):
+  """Returns dx and fp32 sums [B,2,C]: (sum dy*xhat, sum dy) per batch."""
+  assert dy.is_contiguous() and x.is_contiguous()
+  B, S, C = x.shape
+  dx = torch.empty_like(x)
+  cpb = _ctas_per_batch(B, S)
+  sums = scratch = None
+  if need_sums:
+    sums = torch.empty((B, 2, C), device=x.device, dtype=torch.float32)
+    scratch = torch.empty((B * cpb * 2 * C,), device=x.device, dtype=torch.float32)
+  rc = _lib.lib().mdb_ln_bwd(_lib.ptr(dy), _lib.ptr(x), _lib.ptr(mean), _lib.ptr(rstd), _lib.ptr(gamma),
+                             _lib.ptr(scale), scale.stride(0) if scale is not None else 0, B, S, C, _lib.ptr(dx),
+                             _lib.ptr(sums), _lib.ptr(scratch), cpb, _lib.stream())
+  _lib.check(rc, "mdb_ln_bwd")
+  return dx, sums
+
+
+def rms_rope_fwd(x, w=None, cos=None, sin=None, heads=1, per_head=False, eps=1e-6, save_stats=False):
+  """x: [B,S,C] bf16 (row stride arbitrary, e.g. a slice of a fused QKV output) -> [B,S,H,D] contiguous."""
+  B, S, C = x.shape
+  assert x.dtype == torch.bfloat16 and x.stride(-1) == 1 and x.stride(0) == S * x.stride(1)
+  y = torch.empty((B, S, C), device=x.device, dtype=torch.bfloat16)
+  group = 128 if per_head else C
+  rstd = None
+  if save_stats:
+    rstd = torch.empty((B, S, heads) if per_head else (B, S), device=x.device, dtype=torch.float32)
+  if cos is not None:
+    assert cos.dtype == torch.float32 and cos.shape == (S, 64) and cos.is_contiguous() and sin.is_contiguous()
+  rc = _lib.lib().mdb_rms_rope_fwd(_lib.ptr(x), x.stride(1), _lib.ptr(y), C, _lib.ptr(w), int(per_head),
+                                   _lib.ptr(cos), _lib.ptr(sin), B, S, C, group, float(eps), _lib.ptr(rstd),
+                                   _ctas_per_batch(B, S), _lib.stream())
+  _lib.check(rc, "mdb_rms_rope_fwd")
+  y = y.view(B, S, heads, C // heads)
+  return (y, rstd) if save_stats else y
+
+
+def rms_rope_bwd(dy, x, rstd, w=None, cos=None, sin=None, per_head=False, need_dw=True):
+  """dy: [B,S,H,D] (any strides with unit inner stride over [H*D]); returns dx [B,S,C] and dw fp32 [C]."""
+  B, S, C = x.shape
+  dy2 = dy.reshape(B, S, C) if dy.is_contiguous() else dy.contiguous().view(B, S, C)
+  dx = torch.empty((B, S, C), device=x.device, dtype=torch.bfloat16)
+  cpb = _ctas_per_batch(B, S)
+  group = 128 if per_head else C
+  dw = scratch = None
+  if need_dw and w is not None:
+    dw = torch.empty((C,), device=x.device, dtype=torch.float32)
+    scratch = torch.empty((B * cpb * C,), device=x.device, dtype=torch.float32)
+  rc = _lib.lib().mdb_rms_rope_bwd(_lib.ptr(dy2), C, _lib.ptr(x), x.stride(1), _lib.ptr(rstd), _lib.ptr(w),
+                                   int(per_head), _lib.ptr(cos), _lib.ptr(sin), B, S, C, group, _lib.ptr(dx), C,
+                                   _lib.ptr(dw), _lib.ptr(scratch), cpb, _lib.stream())
+  _lib.check(rc, "mdb_rms_rope_bwd")
+  if dw is not None and per_head:
+    dw = dw.view(C // 128, 128).sum(0)
+  return dx, dw
+
+
+def gated_res_fwd(res, y, gate=None):
+  assert res.is_contiguous() and y.is_contiguous() and res.dtype == torch.bfloat16
+  B, S, C = res.shape
+  out = torch.empty_like(res)
+  rc = _lib.lib().mdb_gated_res_fwd(_lib.ptr(res), _lib.ptr(y), _lib.ptr(gate), gate.stride(0) if gate is not None else 0,
+                                    B, S, C, _lib.ptr(out), _ctas_per_batch(B, S), _lib.stream())
+  _lib.check(rc, "mdb_gated_res_fwd")
+  return out
+
+
+def gated_res_bwd(dout, y, gate):
+  assert dout.is_contiguous() and y.is_contiguous()
+  B, S, C = y.shape
+  dy = torch.empty_like(y)
+  cpb = _ctas_per_batch(B, S)
+  dgate = torch.empty((B, C), device=y.device, dtype=torch.float32)
+  scratch = torch.empty((B * cpb * C,), device=y.device, dtype=torch.float32)
+  rc = _lib.lib().mdb_gated_res_bwd(_lib.ptr(dout), _lib.ptr(y), _lib.ptr(gate), gate.stride(0), B, S, C, _lib.ptr(dy),
+                                    _lib.ptr(dgate), _lib.ptr(scratch), cpb, _lib.stream())
+  _lib.check(rc, "mdb_gated_res_bwd")
+  return dy, dgate
+
+
+def colsum(x2d):
+  """fp32 column sums of a bf16 [rows, C] matrix (bias gradient)."""
+  assert x2d.dim() == 2 and x2d.stride(-1) == 1 and x2d.dtype == torch.bfloat16
+  rows, C = x2d.shape
+  ctas = max(1, min(rows, _TARGET_CTAS))
+  out = torch.empty((C,), device=x2d.device, dtype=torch.float32)
+  scratch = torch.empty((ctas * C,), device=x2d.device, dtype=torch.float32)
+  rc = _lib.lib().mdb_colsum(_lib.ptr(x2d), x2d.stride(0), rows, C, _lib.ptr(out), _lib.ptr(scratch), ctas,
+                             _lib.stream())
+  _lib.check(rc, "mdb_colsum")
+  return out
+
+
+def gelu_fwd(u):
+  assert u.is_contiguous() and u.dtype == torch.bfloat16
+  y = torch.empty_like(u)
+  _lib.check(_lib.lib().mdb_gelu_fwd(_lib.ptr(u), _lib.ptr(y), u.numel(), _lib.stream()), "mdb_gelu_fwd")
+  return y
+
+
+def gelu_bwd(dy, u):
+  assert u.is_contiguous() and dy.is_contiguous()
+  du = torch.empty_like(u)
+  _lib.check(_lib.lib().mdb_gelu_bwd(_lib.ptr(dy), _lib.ptr(u), _lib.ptr(du), u.numel(), _lib.stream()),
+             "mdb_gelu_bwd")
+  return du
+
+
+def adamw(p, g, m, v, *, lr, b1, b2, eps, wd, step, grad_scale=1.0, clip_value=0.0, seed=0, stochastic=True):
+  """Fused in-place AdamW on flat buffers. p: bf16; g: bf16|fp32; m, v: bf16|fp32 (same dtype)."""
+  assert p.dtype == torch.bfloat16 and p.is_contiguous() and g.is_contiguous() and m.is_contiguous()
+  assert m.dtype == v.dtype and g.numel() == p.numel() == m.numel() == v.numel()
+  rc = _lib.lib().mdb_adamw(_lib.ptr(p), _lib.ptr(g), _lib.ptr(m), _lib.ptr(v), p.numel(), float(lr), float(b1),
+                            float(b2), float(eps), float(wd), float(1 - b1**step), float(1 - b2**step),
+                            float(grad_scale), float(clip_value), int(seed) & (2**64 - 1), int(stochastic),
+                            int(g.dtype == torch.float32), int(m.dtype == torch.float32), _lib.stream())
+  _lib.check(rc, "mdb_adamw")
+
+
+def sumsq_maxabs(x, out=None, accumulate=False):
+  """out (fp32 [2]) = {sum x², max |x|}; with accumulate the result is folded into `out`."""
+  assert x.is_contiguous()
+  if out is None:
+    out = torch.zeros((2,), device=x.device, dtype=torch.float32)
+  scratch = torch.empty((2048,), device=x.device, dtype=torch.float32)
+  rc = _lib.lib().mdb_sumsq_maxabs(_lib.ptr(x), x.numel(), int(x.dtype == torch.float32), _lib.ptr(out),
+                                   _lib.ptr(scratch), int(accumulate), _lib.stream())
+  _lib.check(rc, "mdb_sumsq_maxabs")
+  return out

@@ -1,0 +1,121 @@
+"""Micro-benchmarks of the hot kernels against the measured roofline (CUDA events, L2 flushed).
+
+  python -m maxdiffusion_b200.utils.kernel_bench [gemm] [flash] [rowwise] [--json out.json]
+
+Each case runs 3 warm-up and `iters` timed launches; between timed launches a buffer larger than the
+126 MB L2 is overwritten. Fractions are reported against MEASURED_PEAKS.json when it is present in the
+working directory ("of measured"), else against the fallback 1590 TFLOP/s / 6650 GB/s ("of fallback").
+"""
+from __future__ import annotations
+
+import json
+import os
+import sys
+
+import torch
+
+from maxdiffusion_b200.ops import kernels as K
+
+
+def peaks():
+  try:
+    with open("MEASURED_PEAKS.json") as f:
+      p = json.load(f)
+    return p["bf16_tflops"], p["hbm_gbs"], "measured"
+  except Exception:
+    return 1590.0, 6650.0, "fallback"
+
+
+_FLUSH = None
+
+
+def flush_l2():
+  global _FLUSH
+  if _FLUSH is None:
+    _FLUSH = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device="cuda")
+  _FLUSH.zero_()
+
+
+def time_ms(fn, iters=10, warmup=3):
+  for _ in range(warmup):
+    fn()
+  torch.cuda.synchronize()
+  ts = []
+  for _ in range(iters):
+    flush_l2()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    fn()
+    e1.record()
+    torch.cuda.synchronize()
+    ts.append(e0.elapsed_time(e1))
+  ts.sort()
+  return ts[len(ts) // 2], ts[0]
+
+
+def bench_gemm(results):
+  tf_peak, _, tag = peaks()
+  shapes = [(32760, 5120, 5120), (32760, 13824, 5120), (32760, 5120, 13824), (4096, 5120, 5120), (4608, 9216, 3072)]
+  for M, N, Kd in shapes:
+    a = torch.randn((M, Kd), device="cuda", dtype=torch.bfloat16)
+    b = torch.randn((N, Kd), device="cuda", dtype=torch.bfloat16)
+    out = torch.empty((M, N), device="cuda", dtype=torch.bfloat16)
+    med, best = time_ms(lambda: K.gemm(a, b, out=out))
+    lib_med, _ = time_ms(lambda: torch.matmul(a, b.t(), out=out))
+    fl = 2.0 * M * N * Kd
+    results.append(dict(kernel="gemm_bf16", shape=[M, N, Kd], ms=med, best_ms=best, tflops=fl / med / 1e9,
+                        frac=fl / med / 1e9 / tf_peak, of=tag, cublas_ms=lib_med))
+    print(results[-1], flush=True)
+    del a, b, out
+
+
+def bench_flash(results):
+  tf_peak, _, tag = peaks()
+  for B, H, Sq, Skv in [(1, 40, 4096, 32768), (1, 40, 8192, 8192), (1, 24, 4608, 4608), (1, 40, 32760, 32760)]:
+    q = torch.randn((B, Sq, H, 128), device="cuda", dtype=torch.bfloat16)
+    k = torch.randn((B, Skv, H, 128), device="cuda", dtype=torch.bfloat16)
+    v = torch.randn((B, Skv, H, 128), device="cuda", dtype=torch.bfloat16)
+    med, best = time_ms(lambda: K.flash_fwd(q, k, v), iters=5)
+    fl = 4.0 * B * H * Sq * Skv * 128
+    results.append(dict(kernel="flash_fwd", shape=[B, H, Sq, Skv], ms=med, best_ms=best, tflops=fl / med / 1e9,
+                        frac=fl / med / 1e9 / tf_peak, of=tag))
+    print(results[-1], flush=True)
+    del q, k, v
+
+
+def bench_rowwise(results):
+  _, bw_peak, tag = peaks()
+  B, S, C = 1, 32760, 5120
+  x = torch.randn((B, S, C), device="cuda", dtype=torch.bfloat16)
+  sc = torch.randn((B, C), device="cuda", dtype=torch.float32)
+  med, best = time_ms(lambda: K.ln_fwd(x, None, None, sc, sc))
+  nbytes = 2 * x.numel() * 2
+  results.append(dict(kernel="ln_mod_fwd", shape=[B, S, C], ms=med, gbs=nbytes / med / 1e6,
+                      frac=nbytes / med / 1e6 / bw_peak, of=tag))
+  print(results[-1], flush=True)
+  w = torch.randn((C,), device="cuda", dtype=torch.bfloat16)
+  cos = torch.rand((S, 64), device="cuda")
+  med, best = time_ms(lambda: K.rms_rope_fwd(x, w, cos, cos, heads=40))
+  results.append(dict(kernel="rms_rope_fwd", shape=[B, S, C], ms=med, gbs=nbytes / med / 1e6,
+                      frac=nbytes / med / 1e6 / bw_peak, of=tag))
+  print(results[-1], flush=True)
+
+
+def main(argv):
+  which = [a for a in argv if not a.startswith("--")] or ["gemm", "flash", "rowwise"]
+  results = []
+  if "gemm" in which:
+    bench_gemm(results)
+  if "flash" in which:
+    bench_flash(results)
+  if "rowwise" in which:
+    bench_rowwise(results)
+  if "--json" in argv:
+    path = argv[argv.index("--json") + 1]
+    os.makedirs(os.path.dirname(path) or ".", exist_ok=True)
+    with open(path, "w") as f:
+      json.dump(results, f, indent=1)
+
+
+if __name__ == "__main__":
+  main(sys.argv[1:])

@@ -1,0 +1,210 @@
+"""Numerics of every hand-written CUDA kernel against a plain PyTorch fp32 reference of the same op."""
+import math
+
+import pytest
+import torch
+
+from maxdiffusion_b200.ops import _lib, kernels as K, ref
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+
+
+def _rel(a, b):
+  a, b = a.float(), b.float()
+  return ((a - b).norm() / (b.norm() + 1e-12)).item()
+
+
+def _report(name, out, want, rel_tol=6e-3, abs_frac=3e-2):
+  rel = _rel(out, want)
+  err = (out.float() - want.float()).abs()
+  mx = err.max().item()
+  scale = want.float().abs().max().item()
+  bad = (err > abs_frac * scale).nonzero()
+  msg = f"{name}: rel={rel:.3e} max_abs={mx:.3e} ref_max={scale:.3e} bad={bad.shape[0]} first_bad={bad[:4].tolist()}"
+  print(msg)
+  assert math.isfinite(rel) and rel < rel_tol and mx <= abs_frac * scale, msg
+  _lib.raise_on_device_status()
+
+
+@pytest.mark.parametrize("a_mn,b_mn", [(False, False), (False, True), (True, False), (True, True)])
+@pytest.mark.parametrize("M,N,K", [(128, 256, 64), (256, 512, 256), (300, 264, 136), (1000, 1536, 1024)])
+def test_gemm_layouts(M, N, K, a_mn, b_mn):
+  torch.manual_seed(0)
+  a = torch.randn((K, M) if a_mn else (M, K), device=DEV, dtype=torch.bfloat16)
+  b = torch.randn((K, N) if b_mn else (N, K), device=DEV, dtype=torch.bfloat16)
+  out = K.gemm(a, b, a_mn=a_mn, b_mn=b_mn)
+  want = ref.gemm(a, b, a_mn=a_mn, b_mn=b_mn, out_dtype=torch.float32)
+  _report(f"gemm {M}x{N}x{K} a_mn={a_mn} b_mn={b_mn}", out, want)
+
+
+@pytest.mark.parametrize("epi", ["none", "gelu_tanh", "silu", "gated_res", "add_res"])
+@pytest.mark.parametrize("f32", [False, True])
+def test_gemm_epilogues(epi, f32):
+  torch.manual_seed(1)
+  B, S, N, Kd = 2, 200, 520, 320
+  M = B * S
+  a = torch.randn((M, Kd), device=DEV, dtype=torch.bfloat16)
+  b = torch.randn((N, Kd), device=DEV, dtype=torch.bfloat16) * 0.05
+  bias = torch.randn((N,), device=DEV, dtype=torch.bfloat16)
+  res = torch.randn((M, N), device=DEV, dtype=torch.bfloat16)
+  gate = torch.randn((B, N), device=DEV, dtype=torch.float32)
+  kw = dict(bias=bias, epi=epi, residual=res if epi in ("gated_res", "add_res") else None,
+            gate=gate if epi == "gated_res" else None, rows_per_batch=S, alpha=0.5)
+  out = K.gemm(a, b, out_dtype=torch.float32 if f32 else torch.bfloat16, **kw)
+  want = ref.gemm(a, b, out_dtype=torch.float32, **kw)
+  _report(f"gemm epi={epi} f32={f32}", out, want)
+
+
+def test_gemm_large_persistent():
+  torch.manual_seed(2)
+  M, N, Kd = 4095, 5120, 5120
+  a = torch.randn((M, Kd), device=DEV, dtype=torch.bfloat16)
+  b = torch.randn((N, Kd), device=DEV, dtype=torch.bfloat16) * 0.02
+  out = K.gemm(a, b)
+  want = (a.float() @ b.float().t())
+  _report("gemm 4095x5120x5120", out, want)
+
+
+@pytest.mark.parametrize("B,H,Sq,Skv", [(1, 2, 128, 128), (1, 2, 256, 384), (2, 3, 300, 200), (1, 4, 1000, 1111),
+                                         (1, 2, 77, 512)])
+def test_flash_fwd(B, H, Sq, Skv):
+  torch.manual_seed(3)
+  q = torch.randn((B, Sq, H, 128), device=DEV, dtype=torch.bfloat16)
+  k = torch.randn((B, Skv, H, 128), device=DEV, dtype=torch.bfloat16)
+  v = torch.randn((B, Skv, H, 128), device=DEV, dtype=torch.bfloat16)
+  out, lse = K.flash_fwd(q, k, v)
+  want, want_lse = ref.attention(q, k, v, return_lse=True)
+  _report(f"flash_fwd B{B} H{H} Sq{Sq} Skv{Skv}", out, want.float(), rel_tol=2e-2, abs_frac=5e-2)
+  assert (lse - want_lse).abs().max().item() < 2e-2
+
+
+def test_flash_fwd_segments_and_strided():
+  """KV given as three segments (ring hops) inside a fused [B,S,3,H,D] projection buffer."""
+  torch.manual_seed(4)
+  B, H, Sq = 1, 4, 520
+  qkv = torch.randn((B, Sq, 3, H, 128), device=DEV, dtype=torch.bfloat16)
+  q, k, v = qkv[:, :, 0], qkv[:, :, 1], qkv[:, :, 2]
+  others = [torch.randn((B, Sq, 3, H, 128), device=DEV, dtype=torch.bfloat16) for _ in range(2)]
+  k_list = [k] + [o[:, :333, 1] for o in others]
+  v_list = [v] + [o[:, :333, 2] for o in others]
+  out, lse = K.flash_fwd(q, k_list, v_list)
+  want, want_lse = ref.attention(q, k_list, v_list, return_lse=True)
+  _report("flash_fwd 3 segments strided", out, want.float(), rel_tol=2e-2, abs_frac=5e-2)
+  assert (lse - want_lse).abs().max().item() < 2e-2
+
+
+def test_flash_fwd_large_magnitude():
+  """Scores with a large dynamic range exercise the lazy rescale path."""
+  torch.manual_seed(5)
+  B, H, S = 1, 2, 640
+  q = torch.randn((B, S, H, 128), device=DEV, dtype=torch.bfloat16) * 4
+  k = torch.randn((B, S, H, 128), device=DEV, dtype=torch.bfloat16) * 4
+  k[:, 400:] *= 3
+  v = torch.randn((B, S, H, 128), device=DEV, dtype=torch.bfloat16)
+  out, _ = K.flash_fwd(q, k, v)
+  want = ref.attention(q, k, v)
+  _report("flash_fwd large magnitude", out, want.float(), rel_tol=2e-2, abs_frac=5e-2)
+
+
+@pytest.mark.parametrize("C", [1536, 5120, 3072])
+@pytest.mark.parametrize("mode", ["mod", "affine", "plain"])
+def test_layer_norm_fwd_bwd(C, mode):
+  torch.manual_seed(6)
+  B, S = 2, 333
+  x = torch.randn((B, S, C), device=DEV, dtype=torch.bfloat16) * 2 + 0.5
+  gamma = torch.randn((C,), device=DEV, dtype=torch.bfloat16) if mode == "affine" else None
+  beta = torch.randn((C,), device=DEV, dtype=torch.bfloat16) if mode == "affine" else None
+  scale = torch.randn((B, C), device=DEV, dtype=torch.float32) * 0.3 if mode == "mod" else None
+  shift = torch.randn((B, C), device=DEV, dtype=torch.float32) if mode == "mod" else None
+  y, mean, rstd = K.ln_fwd(x, gamma, beta, scale, shift, save_stats=True)
+  xr = x.float().requires_grad_(True)
+  gr = gamma.float().requires_grad_(True) if gamma is not None else None
+  br = beta.float().requires_grad_(True) if beta is not None else None
+  sr = scale.clone().requires_grad_(True) if scale is not None else None
+  hr = shift.clone().requires_grad_(True) if shift is not None else None
+  want = ref.layer_norm_mod(xr, gr, br, sr, hr)
+  _report(f"ln_fwd C={C} {mode}", y, want.detach(), rel_tol=5e-3)
+  dy = torch.randn_like(x)
+  want.backward(dy.float())
+  dx, sums = K.ln_bwd(dy, x, mean, rstd, gamma, scale)
+  _report(f"ln_bwd dx C={C} {mode}", dx, xr.grad, rel_tol=8e-3)
+  if mode == "mod":
+    _report("ln_bwd dscale", sums[:, 0], sr.grad, rel_tol=5e-3)
+    _report("ln_bwd dshift", sums[:, 1], hr.grad, rel_tol=5e-3)
+  if mode == "affine":
+    _report("ln_bwd dgamma", sums[:, 0].sum(0), gr.grad, rel_tol=5e-3)
+    _report("ln_bwd dbeta", sums[:, 1].sum(0), br.grad, rel_tol=5e-3)
+
+
+@pytest.mark.parametrize("per_head", [False, True])
+@pytest.mark.parametrize("rope", [False, True])
+def test_rms_rope_fwd_bwd(per_head, rope):
+  torch.manual_seed(7)
+  B, S, H = 2, 257, 12
+  C = H * 128
+  x = torch.randn((B, S, C), device=DEV, dtype=torch.bfloat16)
+  w = (torch.randn((128 if per_head else C,), device=DEV) * 0.2 + 1).to(torch.bfloat16)
+  ang = torch.rand((S, 64), device=DEV) * 6.28
+  cos, sin = (ang.cos().contiguous(), ang.sin().contiguous()) if rope else (None, None)
+  y, rstd = K.rms_rope_fwd(x, w, cos, sin, heads=H, per_head=per_head, save_stats=True)
+  xr = x.float().requires_grad_(True)
+  wr = w.float().requires_grad_(True)
+  want = ref.rms_norm_rope(xr, wr, cos, sin, heads=H, per_head=per_head)
+  _report(f"rms_rope_fwd per_head={per_head} rope={rope}", y, want.detach(), rel_tol=5e-3)
+  dy = torch.randn_like(y)
+  want.backward(dy.float())
+  dx, dw = K.rms_rope_bwd(dy, x, rstd, w, cos, sin, per_head=per_head)
+  _report("rms_rope_bwd dx", dx, xr.grad, rel_tol=8e-3)
+  _report("rms_rope_bwd dw", dw, wr.grad, rel_tol=5e-3)
+
+
+def test_gated_residual_gelu_colsum():
+  torch.manual_seed(8)
+  B, S, C = 2, 301, 1536
+  res = torch.randn((B, S, C), device=DEV, dtype=torch.bfloat16)
+  y = torch.randn((B, S, C), device=DEV, dtype=torch.bfloat16)
+  gate = torch.randn((B, C), device=DEV, dtype=torch.float32)
+  out = K.gated_res_fwd(res, y, gate)
+  _report("gated_res_fwd", out, ref.gated_residual(res.float(), y.float(), gate), rel_tol=5e-3)
+  dout = torch.randn_like(y)
+  dy, dgate = K.gated_res_bwd(dout, y, gate)
+  _report("gated_res_bwd dy", dy, dout.float() * gate[:, None, :], rel_tol=5e-3)
+  _report("gated_res_bwd dgate", dgate, (dout.float() * y.float()).sum(1), rel_tol=5e-3)
+  u = torch.randn((B, S, C), device=DEV, dtype=torch.bfloat16) * 2
+  _report("gelu_fwd", K.gelu_fwd(u), ref.gelu_tanh(u.float()), rel_tol=5e-3)
+  ur = u.float().requires_grad_(True)
+  torch.nn.functional.gelu(ur, approximate="tanh").backward(dout.float())
+  _report("gelu_bwd", K.gelu_bwd(dout, u), ur.grad, rel_tol=5e-3)
+  _report("colsum", K.colsum(y.view(B * S, C)), y.float().view(B * S, C).sum(0), rel_tol=1e-4)
+
+
+@pytest.mark.parametrize("state_dtype", [torch.float32, torch.bfloat16])
+def test_adamw_and_norms(state_dtype):
+  torch.manual_seed(9)
+  n = 1_000_003
+  p = torch.randn((n,), device=DEV, dtype=torch.bfloat16)
+  g = torch.randn((n,), device=DEV, dtype=torch.bfloat16)
+  m = torch.zeros((n,), device=DEV, dtype=state_dtype)
+  v = torch.zeros((n,), device=DEV, dtype=state_dtype)
+  p2, m2, v2 = p.clone(), m.clone(), v.clone()
+  hp = dict(lr=1e-2, b1=0.9, b2=0.999, eps=1e-8, wd=0.01)
+  for step in (1, 2):
+    K.adamw(p, g, m, v, step=step, stochastic=False, **hp)
+    ref.adamw_step(p2, g, m2, v2, step=step, **hp)
+  _report("adamw p", p, p2, rel_tol=1e-2, abs_frac=2e-2)
+  _report("adamw m", m, m2, rel_tol=1e-2, abs_frac=2e-2)
+  out = K.sumsq_maxabs(g)
+  want = ref.sumsq_maxabs(g)
+  assert abs(out[0].item() - want[0].item()) / want[0].item() < 1e-4 and out[1].item() == want[1].item()
+
+
+def test_adamw_stochastic_rounding_is_unbiased():
+  n = 1 << 20
+  p = torch.ones((n,), device=DEV, dtype=torch.bfloat16)
+  g = torch.ones((n,), device=DEV, dtype=torch.bfloat16)
+  m = torch.zeros((n,), device=DEV, dtype=torch.float32)
+  v = torch.zeros((n,), device=DEV, dtype=torch.float32)
+  K.adamw(p, g, m, v, lr=1e-4, b1=0.9, b2=0.999, eps=1e-8, wd=0.0, step=1, seed=123, stochastic=True)
+  # the exact update is 1 - 1e-4, far below the bf16 spacing (2^-8 below 1): the mean must still move by it
+  assert abs((1.0 - p.float().mean().item()) - 1e-4) < 2e-5
