@@ -1,0 +1,466 @@
+// Flash-attention backward for head_dim 128 on sm_100a (tcgen05 + TMEM + TMA), as two
+// deterministic passes built from one kernel template:
+//
+//   DKV pass : a CTA keeps one 128-key block (K_j, V_j) resident and streams 64-row blocks of
+//              (Q_i, dO_i):  S^T = K Q^T, dP^T = V dO^T  ->  P^T, dS^T  ->  dV += P^T dO, dK += dS^T Q
+//   DQ  pass : a CTA keeps one 128-row block (Q_i, dO_i) resident and streams 64-key blocks of
+//              (K_j, V_j) over every KV segment:  S = Q K^T, dP = dO V^T -> dS -> dQ += dS K
+//
+// with P = exp2(S*c - lse2) and dS = P * (dP - delta), delta = rowsum(dO * O). No atomics and no
+// cross-CTA reduction are needed, so results are bitwise reproducible. The two score tiles of a
+// step are double buffered in TMEM so the elementwise warps (8 warps, each warp group owns half of
+// the 64 columns) overlap with the tensor core. The streamed tile is used twice from the same
+// shared memory: as a K-major operand of the score MMAs and as an MN-major operand of the
+// accumulating MMAs whose A operand (P^T / dS as packed bf16) is read from TMEM.
+//
+// Replaces the reference's fused Pallas-TPU backward `_flash_attention_dkv_kernel`
+// (src/maxdiffusion/kernels/splash_attention/splash_attention_kernel.py:1394-1602, launcher :1605-1995)
+// and the ring backward around it (ring_attention_kernel.py:181-289).
+#include "host_common.h"
+
+namespace mdb {
+namespace fab {
+
+constexpr int D = 128;
+constexpr int BX = 128;   // resident rows
+constexpr int BY = 64;    // streamed rows per step
+constexpr int Y_STAGES = 3;
+constexpr int X_TILE_BYTES = BX * D * 2;        // 32 KiB (two 16 KiB chunks)
+constexpr int X_CHUNK_BYTES = BX * 128;         // 16 KiB
+constexpr int Y_TILE_BYTES = BY * D * 2;        // 16 KiB (two 8 KiB chunks)
+constexpr int Y_CHUNK_BYTES = BY * 128;         // 8 KiB
+constexpr int MAX_SEGMENTS = 8;
+constexpr int NUM_THREADS = 384;                // warp 0 TMA, warp 1 MMA, warps 4-11 elementwise
+constexpr int SMEM_BYTES = 2 * X_TILE_BYTES + Y_STAGES * 2 * Y_TILE_BYTES + Y_STAGES * 128 * 4 + 1024 + 256;
+
+struct Maps {
+  CUtensorMap x1, x2;
+  CUtensorMap y1[MAX_SEGMENTS];
+  CUtensorMap y2[MAX_SEGMENTS];
+};
+
+struct Params {
+  int B, H;
+  int x_len;                       // resident-side sequence length (kv_len for DKV, q_len for DQ)
+  int num_segments;
+  int y_len[MAX_SEGMENTS];         // streamed-side lengths (q_len for DKV; kv_len per segment for DQ)
+  const float* lse;                // [B, H, q_len] log2 domain
+  const float* delta;              // [B, H, q_len]
+  int q_len;
+  void* out0;                      // DKV: dV, DQ: dQ
+  void* out1;                      // DKV: dK
+  long long o0_sb, o0_ss, o0_sh, o1_sb, o1_ss, o1_sh;
+  int out_f32;
+  float scale, scale_log2;
+  DeviceStatus* status;
+};
+
+template <bool DKV>
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+flash_bwd_kernel(const __grid_constant__ Maps maps, const Params p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* sx1 = smem;
+  uint8_t* sx2 = smem + X_TILE_BYTES;
+  uint8_t* sy = smem + 2 * X_TILE_BYTES;  // [Y_STAGES][y1 | y2]
+  float* stat_s = reinterpret_cast<float*>(sy + Y_STAGES * 2 * Y_TILE_BYTES);  // [Y_STAGES][lse 64 | delta 64]
+  uint64_t* bars = reinterpret_cast<uint64_t*>(stat_s + Y_STAGES * 128);
+  uint64_t* x_full = bars;          // [1]
+  uint64_t* y_full = bars + 1;      // [3]
+  uint64_t* y_empty = bars + 4;     // [3]
+  uint64_t* t_full = bars + 7;      // [2]
+  uint64_t* ps_full = bars + 9;     // [2]
+  uint64_t* acc_final = bars + 11;  // [1]
+  uint32_t* tmem_ptr_smem = reinterpret_cast<uint32_t*>(bars + 12);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_ptr_smem + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int x0 = blockIdx.x * BX;
+  const int head = blockIdx.y;
+  const int batch = blockIdx.z;
+
+  int total_steps = 0;
+  for (int s = 0; s < p.num_segments; ++s) total_steps += (p.y_len[s] + BY - 1) / BY;
+
+  if (threadIdx.x == 0) {
+    mbar_init(x_full, 1);
+    for (int i = 0; i < Y_STAGES; ++i) {
+      mbar_init(&y_full[i], DKV ? 33 : 1);  // TMA transaction (+ 32 lanes staging lse / delta)
+      mbar_init(&y_empty[i], 1);
+    }
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&t_full[i], 1);
+      mbar_init(&ps_full[i], 256);
+    }
+    mbar_init(acc_final, 1);
+    *abort_flag = 0;
+    fence_mbar_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_ptr_smem, 512);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_ptr_smem;
+  // TMEM columns: T1[b] = b*64, T2[b] = 128 + b*64, acc0 = 256, acc1 = 384.
+
+  if (warp == 0) {
+    // ------------------------------ TMA producer ------------------------------
+    // Lane 0 issues the TMA loads; in the DKV pass all 32 lanes also stage lse / delta of the 64
+    // streamed query rows next to the tile, so their lifetime is that of the stage.
+    if (total_steps > 0) {
+      if (lane == 0) {
+        mbar_expect_tx(x_full, 2 * X_TILE_BYTES);
+        for (int c = 0; c < 2; ++c) {
+          tma_load_4d(sx1 + c * X_CHUNK_BYTES, &maps.x1, x_full, c * 64, head, x0, batch);
+          tma_load_4d(sx2 + c * X_CHUNK_BYTES, &maps.x2, x_full, c * 64, head, x0, batch);
+        }
+      }
+      const long long stat_base = (static_cast<long long>(batch) * p.H + head) * p.q_len;
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int seg = 0; seg < p.num_segments && ok; ++seg) {
+        const int nblk = (p.y_len[seg] + BY - 1) / BY;
+        for (int jb = 0; jb < nblk; ++jb) {
+          if (!mbar_wait(&y_empty[stage], phase ^ 1u, abort_flag, p.status, 70)) { ok = false; break; }
+          if (lane == 0) {
+            uint8_t* d1 = sy + stage * 2 * Y_TILE_BYTES;
+            uint8_t* d2 = d1 + Y_TILE_BYTES;
+            mbar_expect_tx(&y_full[stage], 2 * Y_TILE_BYTES);
+            for (int c = 0; c < 2; ++c) {
+              tma_load_4d(d1 + c * Y_CHUNK_BYTES, &maps.y1[seg], &y_full[stage], c * 64, head, jb * BY, batch);
+              tma_load_4d(d2 + c * Y_CHUNK_BYTES, &maps.y2[seg], &y_full[stage], c * 64, head, jb * BY, batch);
+            }
+          }
+          if (DKV) {
+            float* st = stat_s + stage * 128;
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+              const int qi = lane + 32 * h;
+              const int q = jb * BY + qi;
+              st[qi] = (q < p.q_len) ? p.lse[stat_base + q] : 0.0f;
+              st[64 + qi] = (q < p.q_len) ? p.delta[stat_base + q] : 0.0f;
+            }
+            mbar_arrive(&y_full[stage]);
+          }
+          if (++stage == Y_STAGES) { stage = 0; phase ^= 1u; }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------ MMA issuer --------------------------------
+    if (lane == 0 && total_steps > 0) {
+      constexpr uint32_t idesc_t = make_idesc_bf16(128, BY, false, false);   // score tiles, N = 64
+      constexpr uint32_t idesc_acc = make_idesc_bf16(128, 128, false, true); // accumulators, B MN-major
+      bool ok = mbar_wait(x_full, 0, abort_flag, p.status, 80);
+      tc_fence_after_sync();
+      const uint32_t x1a = smem_u32(sx1), x2a = smem_u32(sx2);
+      auto issue_scores = [&](int stage, int b) {
+        const uint32_t y1a = smem_u32(sy + stage * 2 * Y_TILE_BYTES);
+        const uint32_t y2a = y1a + Y_TILE_BYTES;
+#pragma unroll
+        for (int k = 0; k < D / 16; ++k) {
+          const uint32_t xo = (k >> 2) * X_CHUNK_BYTES + (k & 3) * 32;
+          const uint32_t yo = (k >> 2) * Y_CHUNK_BYTES + (k & 3) * 32;
+          umma_ss(tmem_base + b * 64, make_smem_desc(x1a + xo, 16, 1024), make_smem_desc(y1a + yo, 16, 1024),
+                  idesc_t, k > 0 ? 1u : 0u);
+        }
+#pragma unroll
+        for (int k = 0; k < D / 16; ++k) {
+          const uint32_t xo = (k >> 2) * X_CHUNK_BYTES + (k & 3) * 32;
+          const uint32_t yo = (k >> 2) * Y_CHUNK_BYTES + (k & 3) * 32;
+          umma_ss(tmem_base + 128 + b * 64, make_smem_desc(x2a + xo, 16, 1024), make_smem_desc(y2a + yo, 16, 1024),
+                  idesc_t, k > 0 ? 1u : 0u);
+        }
+        umma_commit(&t_full[b]);
+      };
+      auto issue_acc = [&](int stage, int b, bool first) {
+        const uint32_t y1a = smem_u32(sy + stage * 2 * Y_TILE_BYTES);
+        const uint32_t y2a = y1a + Y_TILE_BYTES;
+#pragma unroll
+        for (int k = 0; k < BY / 16; ++k) {
+          const uint32_t acol = (k >> 1) * 32 + (k & 1) * 8;  // packed bf16 columns of this K-step
+          if (DKV) {
+            // dV += P^T dO_i
+            umma_ts(tmem_base + 256, tmem_base + b * 64 + acol, make_smem_desc(y2a + k * 2048, Y_CHUNK_BYTES, 1024),
+                    idesc_acc, (!first || k > 0) ? 1u : 0u);
+            // dK += dS^T Q_i
+            umma_ts(tmem_base + 384, tmem_base + 128 + b * 64 + acol,
+                    make_smem_desc(y1a + k * 2048, Y_CHUNK_BYTES, 1024), idesc_acc, (!first || k > 0) ? 1u : 0u);
+          } else {
+            // dQ += dS K_j
+            umma_ts(tmem_base + 256, tmem_base + 128 + b * 64 + acol,
+                    make_smem_desc(y1a + k * 2048, Y_CHUNK_BYTES, 1024), idesc_acc, (!first || k > 0) ? 1u : 0u);
+          }
+        }
+        umma_commit(&y_empty[stage]);
+      };
+      int stage = 0;
+      uint32_t phase = 0;
+      int prev_stage = 0;
+      for (int i = 0; i < total_steps && ok; ++i) {
+        const int b = i & 1;
+        if (!mbar_wait(&y_full[stage], phase, abort_flag, p.status, 81)) { ok = false; break; }
+        tc_fence_after_sync();
+        issue_scores(stage, b);
+        if (i > 0) {
+          if (!mbar_wait(&ps_full[b ^ 1], ((i - 1) >> 1) & 1, abort_flag, p.status, 82)) { ok = false; break; }
+          tc_fence_after_sync();
+          issue_acc(prev_stage, b ^ 1, i == 1);
+        }
+        prev_stage = stage;
+        if (++stage == Y_STAGES) { stage = 0; phase ^= 1u; }
+      }
+      if (ok) {
+        const int last = total_steps - 1;
+        if (mbar_wait(&ps_full[last & 1], (last >> 1) & 1, abort_flag, p.status, 83)) {
+          tc_fence_after_sync();
+          issue_acc(prev_stage, last & 1, last == 0);
+          umma_commit(acc_final);
+        }
+      }
+    }
+  } else if (warp >= 4) {
+    // ------------------------------ Elementwise + epilogue --------------------
+    const int wg = (warp - 4) >> 2;       // column half: 0 -> [0,32), 1 -> [32,64)
+    const int quarter = warp & 3;
+    const int row_in_tile = quarter * 32 + lane;
+    const int x_row = x0 + row_in_tile;
+    const bool row_ok = x_row < p.x_len;
+    const uint32_t lane_off = static_cast<uint32_t>(quarter * 32) << 16;
+    if (total_steps > 0) {
+      const long long stat_base = (static_cast<long long>(batch) * p.H + head) * p.q_len;
+      float lse_r = 0.0f, delta_r = 0.0f;
+      if (!DKV && row_ok) {
+        lse_r = p.lse[stat_base + x_row];
+        delta_r = p.delta[stat_base + x_row];
+      }
+      bool ok = true;
+      int i = 0;
+      for (int seg = 0; seg < p.num_segments && ok; ++seg) {
+        const int nblk = (p.y_len[seg] + BY - 1) / BY;
+        for (int jb = 0; jb < nblk; ++jb, ++i) {
+          const int b = i & 1;
+          const int valid = min(BY, p.y_len[seg] - jb * BY);
+          const int ystage = i % Y_STAGES;
+          const float* st = stat_s + ystage * 128;
+          if (DKV) {
+            if (!mbar_wait(&y_full[ystage], (i / Y_STAGES) & 1, abort_flag, p.status, 92)) { ok = false; break; }
+          }
+          if (!mbar_wait(&t_full[b], (i >> 1) & 1, abort_flag, p.status, 90)) { ok = false; break; }
+          tc_fence_after_sync();
+          uint32_t t1[32], t2[32];
+          tmem_ld_x32(tmem_base + lane_off + b * 64 + wg * 32, t1);
+          tmem_ld_x32(tmem_base + lane_off + 128 + b * 64 + wg * 32, t2);
+          tmem_wait_ld();
+          uint32_t pp[16], ds[16];
+#pragma unroll
+          for (int c = 0; c < 16; ++c) {
+            float pv[2], dv[2];
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+              const int col = wg * 32 + 2 * c + h;
+              const float lse = DKV ? st[col] : lse_r;
+              const float del = DKV ? st[64 + col] : delta_r;
+              float pe = fast_exp2(__uint_as_float(t1[2 * c + h]) * p.scale_log2 - lse);
+              if (!row_ok || col >= valid) pe = 0.0f;
+              pv[h] = pe;
+              dv[h] = pe * (__uint_as_float(t2[2 * c + h]) - del);
+            }
+            pp[c] = pack_bf16x2(pv[0], pv[1]);
+            ds[c] = pack_bf16x2(dv[0], dv[1]);
+          }
+          if (DKV) tmem_st_x16(tmem_base + lane_off + b * 64 + wg * 32, pp);
+          tmem_st_x16(tmem_base + lane_off + 128 + b * 64 + wg * 32, ds);
+          tmem_wait_st();
+          tc_fence_before_sync();
+          mbar_arrive(&ps_full[b]);
+        }
+      }
+      if (ok && mbar_wait(acc_final, 0, abort_flag, p.status, 91)) {
+        tc_fence_after_sync();
+        // each warp group writes 64 of the 128 output columns of every accumulator
+        const int n_acc = DKV ? 2 : 1;
+        for (int a = 0; a < n_acc; ++a) {
+          const float mul = (DKV && a == 0) ? 1.0f : p.scale;
+          void* outp = a == 0 ? p.out0 : p.out1;
+          const long long sb = a == 0 ? p.o0_sb : p.o1_sb, ss = a == 0 ? p.o0_ss : p.o1_ss,
+                          sh = a == 0 ? p.o0_sh : p.o1_sh;
+          const long long off = batch * sb + static_cast<long long>(x_row) * ss + head * sh;
+#pragma unroll 1
+          for (int c = 0; c < 2; ++c) {
+            const int col0 = wg * 64 + c * 32;
+            uint32_t r[32];
+            tmem_ld_x32(tmem_base + lane_off + 256 + a * 128 + col0, r);
+            tmem_wait_ld();
+            if (row_ok) {
+              if (p.out_f32) {
+                float* o = reinterpret_cast<float*>(outp) + off + col0;
+#pragma unroll
+                for (int v = 0; v < 8; ++v) {
+                  *reinterpret_cast<float4*>(o + v * 4) =
+                      make_float4(__uint_as_float(r[v * 4]) * mul, __uint_as_float(r[v * 4 + 1]) * mul,
+                                  __uint_as_float(r[v * 4 + 2]) * mul, __uint_as_float(r[v * 4 + 3]) * mul);
+                }
+              } else {
+                __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(outp) + off + col0;
+#pragma unroll
+                for (int v = 0; v < 4; ++v) {
+                  uint4 ov;
+                  ov.x = pack_bf16x2(__uint_as_float(r[v * 8 + 0]) * mul, __uint_as_float(r[v * 8 + 1]) * mul);
+                  ov.y = pack_bf16x2(__uint_as_float(r[v * 8 + 2]) * mul, __uint_as_float(r[v * 8 + 3]) * mul);
+                  ov.z = pack_bf16x2(__uint_as_float(r[v * 8 + 4]) * mul, __uint_as_float(r[v * 8 + 5]) * mul);
+                  ov.w = pack_bf16x2(__uint_as_float(r[v * 8 + 6]) * mul, __uint_as_float(r[v * 8 + 7]) * mul);
+                  *reinterpret_cast<uint4*>(o + v * 8) = ov;
+                }
+              }
+            }
+          }
+        }
+      }
+    }
+  }
+
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem_base, 512);
+  }
+}
+
+// delta[b,h,s] = sum_d dO[b,s,h,d] * O[b,s,h,d]; one warp per (b,s,h) row of 128 elements.
+__global__ void delta_kernel(const __nv_bfloat16* __restrict__ o, const __nv_bfloat16* __restrict__ d_o,
+                             float* __restrict__ delta, int B, int S, int H, long long o_sb, long long o_ss,
+                             long long o_sh, long long g_sb, long long g_ss, long long g_sh) {
+  const long long row = (blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  const long long total = static_cast<long long>(B) * S * H;
+  if (row >= total) return;
+  const int h = static_cast<int>(row % H);
+  const long long bs = row / H;
+  const int s = static_cast<int>(bs % S);
+  const int b = static_cast<int>(bs / S);
+  const uint2 ov = *reinterpret_cast<const uint2*>(o + b * o_sb + s * o_ss + h * o_sh + lane * 4);
+  const uint2 gv = *reinterpret_cast<const uint2*>(d_o + b * g_sb + s * g_ss + h * g_sh + lane * 4);
+  const float2 o0 = unpack_bf16x2(ov.x), o1 = unpack_bf16x2(ov.y);
+  const float2 g0 = unpack_bf16x2(gv.x), g1 = unpack_bf16x2(gv.y);
+  float acc = o0.x * g0.x + o0.y * g0.y + o1.x * g1.x + o1.y * g1.y;
+#pragma unroll
+  for (int off = 16; off > 0; off >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, off);
+  if (lane == 0) delta[(static_cast<long long>(b) * H + h) * S + s] = acc;
+}
+
+static int make_map(CUtensorMap* map, const void* ptr, int B, int S, int H, long long sb, long long ss, long long sh,
+                    int box_rows) {
+  uint64_t dims[4] = {static_cast<uint64_t>(D), static_cast<uint64_t>(H), static_cast<uint64_t>(S),
+                      static_cast<uint64_t>(B)};
+  uint64_t str[3] = {static_cast<uint64_t>(sh) * 2, static_cast<uint64_t>(ss) * 2, static_cast<uint64_t>(sb) * 2};
+  uint32_t box[4] = {64, 1, static_cast<uint32_t>(box_rows), 1};
+  return encode_tmap_bf16(map, ptr, 4, dims, str, box);
+}
+
+}  // namespace fab
+}  // namespace mdb
+
+using namespace mdb;
+using namespace mdb::fab;
+
+extern "C" int mdb_flash_delta(const void* o, const void* d_o, float* delta, int B, int S, int H, long long o_sb,
+                               long long o_ss, long long o_sh, long long g_sb, long long g_ss, long long g_sh,
+                               void* stream) {
+  if ((o_sb | o_ss | o_sh | g_sb | g_ss | g_sh) & 3) return 3301;
+  const long long rows = static_cast<long long>(B) * S * H;
+  if (rows <= 0) return 0;
+  const int blocks = static_cast<int>((rows * 32 + 255) / 256);
+  delta_kernel<<<blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const __nv_bfloat16*>(o), static_cast<const __nv_bfloat16*>(d_o), delta, B, S, H, o_sb, o_ss, o_sh,
+      g_sb, g_ss, g_sh);
+  return static_cast<int>(cudaGetLastError());
+}
+
+// dK, dV of one KV segment from all local queries. Strides in elements (batch, seq, head).
+// q/dO share q strides `qs`, k/v share `ks`; outputs share `os`. out_f32 selects fp32 outputs.
+extern "C" int mdb_flash_bwd_dkv(const void* q, const void* d_o, const void* k, const void* v, const float* lse,
+                                 const float* delta, void* dk, void* dv, int B, int H, int q_len, int kv_len,
+                                 const long long* qs, const long long* gs, const long long* ks, const long long* vs,
+                                 const long long* dks, const long long* dvs, float softmax_scale, int out_f32,
+                                 void* stream) {
+  if (B <= 0 || H <= 0 || q_len <= 0 || kv_len <= 0) return 0;
+  Maps maps;
+  Params p;
+  int rc = make_map(&maps.x1, k, B, kv_len, H, ks[0], ks[1], ks[2], BX);
+  if (rc) return rc;
+  rc = make_map(&maps.x2, v, B, kv_len, H, vs[0], vs[1], vs[2], BX);
+  if (rc) return rc;
+  for (int s = 0; s < MAX_SEGMENTS; ++s) {
+    rc = make_map(&maps.y1[s], q, B, q_len, H, qs[0], qs[1], qs[2], BY);
+    if (rc) return rc;
+    rc = make_map(&maps.y2[s], d_o, B, q_len, H, gs[0], gs[1], gs[2], BY);
+    if (rc) return rc;
+    p.y_len[s] = s == 0 ? q_len : 0;
+  }
+  p.B = B; p.H = H; p.x_len = kv_len; p.num_segments = 1;
+  p.lse = lse; p.delta = delta; p.q_len = q_len;
+  p.out0 = dv; p.out1 = dk;
+  p.o0_sb = dvs[0]; p.o0_ss = dvs[1]; p.o0_sh = dvs[2];
+  p.o1_sb = dks[0]; p.o1_ss = dks[1]; p.o1_sh = dks[2];
+  p.out_f32 = out_f32;
+  p.scale = softmax_scale;
+  p.scale_log2 = softmax_scale * 1.4426950408889634f;
+  p.status = status_buffer();
+  static bool configured = false;
+  if (!configured) {
+    MDB_CHECK_CUDA(cudaFuncSetAttribute(flash_bwd_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
+    configured = true;
+  }
+  dim3 grid((kv_len + BX - 1) / BX, H, B);
+  flash_bwd_kernel<true><<<grid, NUM_THREADS, SMEM_BYTES, static_cast<cudaStream_t>(stream)>>>(maps, p);
+  return static_cast<int>(cudaGetLastError());
+}
+
+// dQ of the local queries over every KV segment.
+extern "C" int mdb_flash_bwd_dq(const void* q, const void* d_o, const void* const* k_ptrs, const void* const* v_ptrs,
+                                const float* lse, const float* delta, void* dq, int B, int H, int q_len,
+                                int num_segments, const int* kv_lens, const long long* qs, const long long* gs,
+                                const long long* ks, const long long* vs, const long long* dqs, float softmax_scale,
+                                int out_f32, void* stream) {
+  if (B <= 0 || H <= 0 || q_len <= 0) return 0;
+  if (num_segments < 1 || num_segments > MAX_SEGMENTS) return 3302;
+  Maps maps;
+  Params p;
+  int rc = make_map(&maps.x1, q, B, q_len, H, qs[0], qs[1], qs[2], BX);
+  if (rc) return rc;
+  rc = make_map(&maps.x2, d_o, B, q_len, H, gs[0], gs[1], gs[2], BX);
+  if (rc) return rc;
+  for (int s = 0; s < MAX_SEGMENTS; ++s) {
+    const int src = s < num_segments ? s : 0;
+    const int len = kv_lens[src] > 0 ? kv_lens[src] : 1;
+    rc = make_map(&maps.y1[s], k_ptrs[src], B, len, H, ks[0], ks[1], ks[2], BY);
+    if (rc) return rc;
+    rc = make_map(&maps.y2[s], v_ptrs[src], B, len, H, vs[0], vs[1], vs[2], BY);
+    if (rc) return rc;
+    p.y_len[s] = s < num_segments ? kv_lens[s] : 0;
+  }
+  p.B = B; p.H = H; p.x_len = q_len; p.num_segments = num_segments;
+  p.lse = lse; p.delta = delta; p.q_len = q_len;
+  p.out0 = dq; p.out1 = nullptr;
+  p.o0_sb = dqs[0]; p.o0_ss = dqs[1]; p.o0_sh = dqs[2];
+  p.o1_sb = p.o1_ss = p.o1_sh = 0;
+  p.out_f32 = out_f32;
+  p.scale = softmax_scale;
+  p.scale_log2 = softmax_scale * 1.4426950408889634f;
+  p.status = status_buffer();
+  static bool configured = false;
+  if (!configured) {
+    MDB_CHECK_CUDA(cudaFuncSetAttribute(flash_bwd_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
+    configured = true;
+  }
+  dim3 grid((q_len + BX - 1) / BX, H, B);
+  flash_bwd_kernel<false><<<grid, NUM_THREADS, SMEM_BYTES, static_cast<cudaStream_t>(stream)>>>(maps, p);
+  return static_cast<int>(cudaGetLastError());
+}

@@ -125,6 +125,15 @@ def _declare(L: ctypes.CDLL) -> None:
   L.mdb_adamw.restype = c_int
   L.mdb_sumsq_maxabs.argtypes = [c_void_p, c_ll, c_int, c_void_p, c_void_p, c_int, c_void_p]
   L.mdb_sumsq_maxabs.restype = c_int
+  c_llp = ctypes.POINTER(c_ll)
+  L.mdb_flash_delta.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int] + [c_ll] * 6 + [c_void_p]
+  L.mdb_flash_delta.restype = c_int
+  L.mdb_flash_bwd_dkv.argtypes = [c_void_p] * 8 + [c_int] * 4 + [c_llp] * 6 + [c_float, c_int, c_void_p]
+  L.mdb_flash_bwd_dkv.restype = c_int
+  L.mdb_flash_bwd_dq.argtypes = ([c_void_p, c_void_p, ctypes.POINTER(c_void_p), ctypes.POINTER(c_void_p), c_void_p,
+                                  c_void_p, c_void_p] + [c_int] * 4 + [ctypes.POINTER(c_int)] + [c_llp] * 5 +
+                                 [c_float, c_int, c_void_p])
+  L.mdb_flash_bwd_dq.restype = c_int
   for name, fn in _OPTIONAL.items():
     if hasattr(L, name):
       fn(L)

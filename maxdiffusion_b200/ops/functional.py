@@ -1,0 +1,359 @@
+"""Differentiable ops of the framework.
+
+Dispatch rule: CUDA bf16 tensors run the hand-written sm_100a kernels (`ops.kernels`) inside
+`torch.autograd.Function`s whose backward passes are kernels as well; every other tensor (CPU, fp32)
+runs the PyTorch reference (`ops.ref`) under ordinary autograd. There is no silent fallback for CUDA
+bf16 inputs: if the kernel library cannot be loaded the call raises.
+
+Selective rematerialisation: inside `remat.record()` the self-attention forward stores (O, LSE) and inside
+`remat.replay()` it reuses them instead of running the forward kernel again, which is the
+"save attention, recompute the rest" policy (the reference spells such policies as lists of checkpoint
+names, src/maxdiffusion/models/gradient_checkpoint.py:30-103).
+"""
+from __future__ import annotations
+
+import contextlib
+import math
+import threading
+from typing import Sequence
+
+import torch
+import torch.nn.functional as F
+
+from . import kernels as K
+from . import ref
+
+
+def _fast(t: torch.Tensor) -> bool:
+  return t.is_cuda and t.dtype == torch.bfloat16
+
+
+# ---------------------------------------------------------------------------------------------
+# remat bookkeeping for attention outputs
+# ---------------------------------------------------------------------------------------------
+class _RematState(threading.local):
+
+  def __init__(self):
+    self.mode = None  # None | "record" | "replay"
+    self.store = None
+    self.cursor = 0
+
+
+_remat = _RematState()
+
+
+class remat:
+  """Context managers used by `checkpoint_block`."""
+
+  @staticmethod
+  @contextlib.contextmanager
+  def record(store: list):
+    prev = (_remat.mode, _remat.store, _remat.cursor)
+    _remat.mode, _remat.store, _remat.cursor = "record", store, 0
+    try:
+      yield
+    finally:
+      _remat.mode, _remat.store, _remat.cursor = prev
+
+  @staticmethod
+  @contextlib.contextmanager
+  def replay(store: list):
+    prev = (_remat.mode, _remat.store, _remat.cursor)
+    _remat.mode, _remat.store, _remat.cursor = "replay", store, 0
+    try:
+      yield
+    finally:
+      _remat.mode, _remat.store, _remat.cursor = prev
+
+
+# ---------------------------------------------------------------------------------------------
+# linear (+ bias, + GELU-tanh / SiLU), the GEMM family
+# ---------------------------------------------------------------------------------------------
+class _LinearFn(torch.autograd.Function):
+
+  @staticmethod
+  def forward(ctx, x, w, b, act):
+    x2 = x.reshape(-1, x.shape[-1])
+    need_grad = any(ctx.needs_input_grad[:3])
+    ctx.act = act
+    ctx.x_shape = x.shape
+    ctx.has_bias = b is not None
+    if act in ("gelu_tanh",) and need_grad:
+      u = K.gemm(x2, w, bias=b)
+      y = K.gelu_fwd(u)
+      ctx.save_for_backward(x2, w, u)
+    else:
+      y = K.gemm(x2, w, bias=b, epi=act or "none")
+      if act == "silu" and need_grad:
+        raise NotImplementedError("silu epilogue has no fused backward; apply silu as a separate op when training")
+      ctx.save_for_backward(x2, w, None)
+    return y.view(*x.shape[:-1], w.shape[0])
+
+  @staticmethod
+  def backward(ctx, dy):
+    x2, w, u = ctx.saved_tensors
+    dy2 = dy.reshape(-1, dy.shape[-1])
+    if not dy2.is_contiguous():
+      dy2 = dy2.contiguous()
+    if u is not None:
+      dy2 = K.gelu_bwd(dy2, u)
+    dx = dw = db = None
+    if ctx.needs_input_grad[0]:
+      dx = K.gemm(dy2, w, b_mn=True).view(ctx.x_shape)       # dX = dY · W
+    if ctx.needs_input_grad[1]:
+      dw = K.gemm(dy2, x2, a_mn=True, b_mn=True)              # dW = dYᵀ · X
+    if ctx.has_bias and ctx.needs_input_grad[2]:
+      db = K.colsum(dy2).to(torch.bfloat16)
+    return dx, dw, db, None
+
+
+def linear(x, weight, bias=None, activation: str | None = None):
+  """y = act(x @ weightᵀ + bias); weight is [out, in] (PyTorch / diffusers orientation)."""
+  if _fast(x) and x.shape[-1] % 8 == 0 and weight.shape[0] % 8 == 0:
+    if weight.dtype != torch.bfloat16:
+      weight = weight.to(torch.bfloat16)
+    if bias is not None and bias.dtype != torch.bfloat16:
+      bias = bias.to(torch.bfloat16)
+    return _LinearFn.apply(x, weight, bias, activation)
+  y = F.linear(x, weight.to(x.dtype), None if bias is None else bias.to(x.dtype))
+  if activation == "gelu_tanh":
+    y = F.gelu(y, approximate="tanh")
+  elif activation == "silu":
+    y = F.silu(y)
+  return y
+
+
+def linear_gated_residual(x, weight, bias, residual, gate):
+  """residual + gate[:,None,:] * (x @ weightᵀ + bias), the output projection of an AdaLN-gated branch.
+
+  Without autograd the gate and the residual add run in the GEMM epilogue; with autograd the product is
+  materialised because the gate's gradient needs it.
+  """
+  if _fast(x) and not torch.is_grad_enabled():
+    B, S, _ = x.shape
+    out = K.gemm(x.reshape(B * S, -1), weight, bias=bias, epi="gated_res" if gate is not None else "add_res",
+                 residual=residual.reshape(B * S, -1), gate=gate, rows_per_batch=S)
+    return out.view(B, S, -1)
+  return gated_residual(residual, linear(x, weight, bias), gate)
+
+
+# ---------------------------------------------------------------------------------------------
+# attention
+# ---------------------------------------------------------------------------------------------
+class _AttentionFn(torch.autograd.Function):
+
+  @staticmethod
+  def forward(ctx, q, scale, n_seg, *kv):
+    ks, vs = list(kv[:n_seg]), list(kv[n_seg:])
+    saved = None
+    if _remat.mode == "replay":
+      saved = _remat.store[_remat.cursor]
+      _remat.cursor += 1
+    if saved is not None:
+      out, lse = saved
+    else:
+      out, lse = K.flash_fwd(q, ks, vs, scale)
+      if _remat.mode == "record":
+        _remat.store.append((out, lse))
+    ctx.scale, ctx.n_seg = scale, n_seg
+    ctx.save_for_backward(q, out, lse, *ks, *vs)
+    return out
+
+  @staticmethod
+  def backward(ctx, d_o):
+    q, out, lse, *kv = ctx.saved_tensors
+    n = ctx.n_seg
+    ks, vs = kv[:n], kv[n:]
+    if d_o.stride(-1) != 1:
+      d_o = d_o.contiguous()
+    delta = K.flash_delta(out, d_o)
+    dq = K.flash_bwd_dq(q, d_o, ks, vs, lse, delta, ctx.scale)
+    dks, dvs = [], []
+    for k, v in zip(ks, vs):
+      dk, dv = K.flash_bwd_dkv(q, d_o, k, v, lse, delta, ctx.scale)
+      dks.append(dk)
+      dvs.append(dv)
+    return (dq, None, None, *dks, *dvs)
+
+
+def attention(q, k, v, scale: float | None = None):
+  """Softmax attention, no mask. q: [B,Sq,H,D]; k, v: [B,Skv,H,D] or equal-length lists of KV segments."""
+  ks = list(k) if isinstance(k, (list, tuple)) else [k]
+  vs = list(v) if isinstance(v, (list, tuple)) else [v]
+  D = q.shape[-1]
+  scale = scale if scale is not None else 1.0 / math.sqrt(D)
+  if _fast(q) and D == 128:
+    if _remat.mode == "record" and torch.is_grad_enabled() is False:
+      pass
+    return _AttentionFn.apply(q, scale, len(ks), *ks, *vs)
+  kc = torch.cat(ks, dim=1) if len(ks) > 1 else ks[0]
+  vc = torch.cat(vs, dim=1) if len(vs) > 1 else vs[0]
+  out = F.scaled_dot_product_attention(q.transpose(1, 2), kc.transpose(1, 2), vc.transpose(1, 2), scale=scale)
+  return out.transpose(1, 2)
+
+
+# ---------------------------------------------------------------------------------------------
+# norms
+# ---------------------------------------------------------------------------------------------
+class _LayerNormModFn(torch.autograd.Function):
+
+  @staticmethod
+  def forward(ctx, x, gamma, beta, scale, shift, eps):
+    need = any(ctx.needs_input_grad[:5])
+    if need:
+      y, mean, rstd = K.ln_fwd(x, gamma, beta, scale, shift, eps, save_stats=True)
+      ctx.save_for_backward(x, mean, rstd, gamma, scale)
+    else:
+      y = K.ln_fwd(x, gamma, beta, scale, shift, eps)
+    return y
+
+  @staticmethod
+  def backward(ctx, dy):
+    x, mean, rstd, gamma, scale = ctx.saved_tensors
+    if not dy.is_contiguous():
+      dy = dy.contiguous()
+    need_sums = any(ctx.needs_input_grad[1:5])
+    dx, sums = K.ln_bwd(dy, x, mean, rstd, gamma, scale, need_sums=need_sums)
+    dgamma = dbeta = dscale = dshift = None
+    if sums is not None:
+      if gamma is not None:
+        # with affine the first sum is d/dgamma only when there is no modulation on top
+        dgamma = sums[:, 0].sum(0).to(gamma.dtype) if ctx.needs_input_grad[1] else None
+        dbeta = sums[:, 1].sum(0).to(gamma.dtype) if ctx.needs_input_grad[2] else None
+      if scale is not None:
+        dscale = sums[:, 0] if ctx.needs_input_grad[3] else None
+        dshift = sums[:, 1] if ctx.needs_input_grad[4] else None
+    return dx, dgamma, dbeta, dscale, dshift, None
+
+
+def layer_norm_mod(x, gamma=None, beta=None, scale=None, shift=None, eps: float = 1e-6):
+  """fp32 LayerNorm with optional affine (gamma, beta) xor AdaLN modulation (scale, shift: fp32 [B, C])."""
+  if _fast(x) and x.dim() == 3 and x.shape[-1] % 8 == 0 and x.shape[-1] <= 8192 and not (gamma is not None and scale is not None):
+    x = x if x.is_contiguous() else x.contiguous()
+    if scale is not None:
+      scale = scale.float() if scale.dtype != torch.float32 else scale
+      shift = shift.float() if shift.dtype != torch.float32 else shift
+      if scale.stride(-1) != 1 or shift.stride(-1) != 1 or scale.stride(0) != shift.stride(0):
+        scale, shift = scale.contiguous(), shift.contiguous()
+    return _LayerNormModFn.apply(x, gamma, beta, scale, shift, eps)
+  return ref.layer_norm_mod(x, gamma, beta, scale, shift, eps)
+
+
+class _RmsRopeFn(torch.autograd.Function):
+
+  @staticmethod
+  def forward(ctx, x, w, cos, sin, heads, per_head, eps):
+    need = ctx.needs_input_grad[0] or ctx.needs_input_grad[1]
+    ctx.per_head = per_head
+    ctx.has_rope = cos is not None
+    if need:
+      y, rstd = K.rms_rope_fwd(x, w, cos, sin, heads, per_head, eps, save_stats=True)
+      ctx.save_for_backward(x, rstd, w, cos, sin)
+    else:
+      y = K.rms_rope_fwd(x, w, cos, sin, heads, per_head, eps)
+    return y
+
+  @staticmethod
+  def backward(ctx, dy):
+    x, rstd, w, cos, sin = ctx.saved_tensors
+    dx, dw = K.rms_rope_bwd(dy, x, rstd, w, cos, sin, per_head=ctx.per_head, need_dw=ctx.needs_input_grad[1])
+    if dw is not None:
+      dw = dw.to(w.dtype)
+    return dx, dw, None, None, None, None, None
+
+
+def rms_norm_rope(x, weight=None, cos=None, sin=None, heads: int = 1, per_head: bool = False, eps: float = 1e-6):
+  """RMSNorm (across all channels or per 128-wide head) then RoPE on interleaved pairs. [B,S,C] -> [B,S,H,D]."""
+  B, S, C = x.shape
+  if _fast(x) and C % 128 == 0 and C // heads == 128 and C <= 8192 and x.stride(-1) == 1 and x.stride(0) == S * x.stride(1):
+    if cos is not None:
+      cos = cos.float().contiguous() if (cos.dtype != torch.float32 or not cos.is_contiguous()) else cos
+      sin = sin.float().contiguous() if (sin.dtype != torch.float32 or not sin.is_contiguous()) else sin
+    return _RmsRopeFn.apply(x, weight, cos, sin, heads, per_head, eps)
+  return ref.rms_norm_rope(x, weight, cos, sin, heads, per_head, eps)
+
+
+# ---------------------------------------------------------------------------------------------
+# elementwise
+# ---------------------------------------------------------------------------------------------
+class _GatedResFn(torch.autograd.Function):
+
+  @staticmethod
+  def forward(ctx, res, y, gate):
+    ctx.save_for_backward(y if ctx.needs_input_grad[2] else None, gate)
+    return K.gated_res_fwd(res, y, gate)
+
+  @staticmethod
+  def backward(ctx, dout):
+    y, gate = ctx.saved_tensors
+    if not dout.is_contiguous():
+      dout = dout.contiguous()
+    if gate is None:
+      return dout, dout, None
+    if y is not None:
+      dy, dgate = K.gated_res_bwd(dout, y, gate)
+    else:
+      dy, dgate = (dout.float() * gate.unsqueeze(1)).to(dout.dtype), None
+    return dout, dy, dgate
+
+
+def gated_residual(res, y, gate=None):
+  """res + gate[:, None, :] * y with one rounding; gate is fp32 [B, C] (None means 1)."""
+  if _fast(res) and res.dim() == 3 and res.shape[-1] % 8 == 0 and res.shape[-1] <= 8192:
+    res = res if res.is_contiguous() else res.contiguous()
+    y = y if y.is_contiguous() else y.contiguous()
+    if gate is not None and (gate.dtype != torch.float32 or gate.stride(-1) != 1):
+      gate = gate.float().contiguous()
+    return _GatedResFn.apply(res, y, gate)
+  return ref.gated_residual(res, y, gate)
+
+
+# ---------------------------------------------------------------------------------------------
+# block-level rematerialisation
+# ---------------------------------------------------------------------------------------------
+class _CheckpointFn(torch.autograd.Function):
+
+  @staticmethod
+  def forward(ctx, fn, save_attention, n_tensors, *args):
+    ctx.fn = fn
+    ctx.store = [] if save_attention else None
+    tensors = args[:n_tensors]
+    ctx.rest = args[n_tensors:]
+    ctx.save_for_backward(*tensors)
+    with torch.no_grad():
+      if ctx.store is not None:
+        with remat.record(ctx.store):
+          out = fn(*args)
+      else:
+        out = fn(*args)
+    return out
+
+  @staticmethod
+  def backward(ctx, *douts):
+    tensors = [t.detach().requires_grad_(t.requires_grad) if t is not None else None for t in ctx.saved_tensors]
+    # only tensors that took part in autograd need gradients; floating point inputs are assumed to
+    inputs = []
+    for t, orig in zip(tensors, ctx.saved_tensors):
+      if t is not None and orig.is_floating_point():
+        t.requires_grad_(True)
+      inputs.append(t)
+    with torch.enable_grad():
+      if ctx.store is not None:
+        with remat.replay(ctx.store):
+          out = ctx.fn(*inputs, *ctx.rest)
+      else:
+        out = ctx.fn(*inputs, *ctx.rest)
+    outs = out if isinstance(out, tuple) else (out,)
+    torch.autograd.backward([o for o in outs if o.requires_grad], [g for o, g in zip(outs, douts) if o.requires_grad])
+    ctx.store = None
+    grads = [t.grad if (t is not None and t.is_floating_point()) else None for t in inputs]
+    return (None, None, None, *grads, *([None] * len(ctx.rest)))
+
+
+def checkpoint_block(fn, *tensor_args, extra_args: Sequence = (), save_attention: bool = False):
+  """Runs `fn(*tensor_args, *extra_args)` storing only its tensor inputs; the backward pass recomputes it.
+
+  Parameters used inside `fn` receive their gradients during the recomputation. With `save_attention`
+  the flash-attention outputs of the first pass are kept and not recomputed.
+  """
+  return _CheckpointFn.apply(fn, save_attention, len(tensor_args), *tensor_args, *extra_args)

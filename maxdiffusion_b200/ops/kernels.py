@@ -80,6 +80,58 @@ def flash_fwd(q: torch.Tensor, k_list: Sequence[torch.Tensor], v_list: Sequence[
   return (out, lse) if return_lse else out
 
 
+def _strides3(t):
+  return (ctypes.c_longlong * 3)(t.stride(0), t.stride(1), t.stride(2))
+
+
+def flash_delta(o, d_o):
+  """delta[b,h,s] = sum_d dO*O (fp32), the row term of the softmax backward."""
+  B, S, H, D = o.shape
+  assert D == 128 and o.stride(-1) == 1 and d_o.stride(-1) == 1
+  delta = torch.empty((B, H, S), device=o.device, dtype=torch.float32)
+  rc = _lib.lib().mdb_flash_delta(_lib.ptr(o), _lib.ptr(d_o), _lib.ptr(delta), B, S, H, o.stride(0), o.stride(1),
+                                  o.stride(2), d_o.stride(0), d_o.stride(1), d_o.stride(2), _lib.stream())
+  _lib.check(rc, "mdb_flash_delta")
+  return delta
+
+
+def flash_bwd_dkv(q, d_o, k, v, lse, delta, scale=None, out_dtype=torch.bfloat16):
+  """dK, dV of one KV segment [B,Skv,H,128] from the local queries q/dO [B,Sq,H,128]."""
+  B, Sq, H, D = q.shape
+  Skv = k.shape[1]
+  assert D == 128 and all(t.stride(-1) == 1 for t in (q, d_o, k, v))
+  dk = torch.empty((B, Skv, H, D), device=q.device, dtype=out_dtype)
+  dv = torch.empty((B, Skv, H, D), device=q.device, dtype=out_dtype)
+  scale = scale if scale is not None else 1.0 / math.sqrt(D)
+  rc = _lib.lib().mdb_flash_bwd_dkv(_lib.ptr(q), _lib.ptr(d_o), _lib.ptr(k), _lib.ptr(v), _lib.ptr(lse),
+                                    _lib.ptr(delta), _lib.ptr(dk), _lib.ptr(dv), B, H, Sq, Skv, _strides3(q),
+                                    _strides3(d_o), _strides3(k), _strides3(v), _strides3(dk), _strides3(dv),
+                                    float(scale), int(out_dtype == torch.float32), _lib.stream())
+  _lib.check(rc, "mdb_flash_bwd_dkv")
+  return dk, dv
+
+
+def flash_bwd_dq(q, d_o, k_list, v_list, lse, delta, scale=None, out_dtype=torch.bfloat16):
+  """dQ of the local queries over every KV segment."""
+  if isinstance(k_list, torch.Tensor):
+    k_list, v_list = [k_list], [v_list]
+  B, Sq, H, D = q.shape
+  k0, v0 = k_list[0], v_list[0]
+  for k, v in zip(k_list, v_list):
+    assert k.stride() == k0.stride() and v.stride() == v0.stride() and k.stride(-1) == 1 and v.stride(-1) == 1
+  n = len(k_list)
+  dq = torch.empty((B, Sq, H, D), device=q.device, dtype=out_dtype)
+  kp = (ctypes.c_void_p * n)(*[k.data_ptr() for k in k_list])
+  vp = (ctypes.c_void_p * n)(*[v.data_ptr() for v in v_list])
+  lens = (ctypes.c_int * n)(*[k.shape[1] for k in k_list])
+  scale = scale if scale is not None else 1.0 / math.sqrt(D)
+  rc = _lib.lib().mdb_flash_bwd_dq(_lib.ptr(q), _lib.ptr(d_o), kp, vp, _lib.ptr(lse), _lib.ptr(delta), _lib.ptr(dq), B,
+                                   H, Sq, n, lens, _strides3(q), _strides3(d_o), _strides3(k0), _strides3(v0),
+                                   _strides3(dq), float(scale), int(out_dtype == torch.float32), _lib.stream())
+  _lib.check(rc, "mdb_flash_bwd_dq")
+  return dq
+
+
 def ln_fwd(x, gamma=None, beta=None, scale=None, shift=None, eps=1e-6, save_stats=False):
   """x: [B,S,C] bf16 contiguous; scale/shift: fp32 [B,C] (row stride arbitrary)."""
   assert x.dtype == torch.bfloat16 and x.is_contiguous()

@@ -83,6 +83,25 @@ def bench_flash(results):
     del q, k, v
 
 
+def bench_flash_bwd(results):
+  tf_peak, _, tag = peaks()
+  for B, H, Sq, Skv in [(1, 40, 4096, 4096), (1, 40, 8192, 8192), (1, 40, 32760, 32760)]:
+    q = torch.randn((B, Sq, H, 128), device="cuda", dtype=torch.bfloat16)
+    k = torch.randn((B, Skv, H, 128), device="cuda", dtype=torch.bfloat16)
+    v = torch.randn((B, Skv, H, 128), device="cuda", dtype=torch.bfloat16)
+    d_o = torch.randn((B, Sq, H, 128), device="cuda", dtype=torch.bfloat16)
+    out, lse = K.flash_fwd(q, k, v)
+    delta = K.flash_delta(out, d_o)
+    med_kv, _ = time_ms(lambda: K.flash_bwd_dkv(q, d_o, k, v, lse, delta), iters=5)
+    med_q, _ = time_ms(lambda: K.flash_bwd_dq(q, d_o, k, v, lse, delta), iters=5)
+    fl = 10.0 * B * H * Sq * Skv * 128  # algorithmic backward FLOPs (5 GEMMs)
+    results.append(dict(kernel="flash_bwd", shape=[B, H, Sq, Skv], dkv_ms=med_kv, dq_ms=med_q,
+                        tflops_algorithmic=fl / (med_kv + med_q) / 1e9, frac=fl / (med_kv + med_q) / 1e9 / tf_peak,
+                        tflops_issued=14.0 * B * H * Sq * Skv * 128 / (med_kv + med_q) / 1e9, of=tag))
+    print(results[-1], flush=True)
+    del q, k, v, d_o, out
+
+
 def bench_rowwise(results):
   _, bw_peak, tag = peaks()
   B, S, C = 1, 32760, 5120
@@ -108,6 +127,8 @@ def main(argv):
     bench_gemm(results)
   if "flash" in which:
     bench_flash(results)
+  if "flash_bwd" in which:
+    bench_flash_bwd(results)
   if "rowwise" in which:
     bench_rowwise(results)
   if "--json" in argv:

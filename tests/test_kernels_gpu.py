@@ -28,14 +28,14 @@ def _report(name, out, want, rel_tol=6e-3, abs_frac=3e-2):
 
 
 @pytest.mark.parametrize("a_mn,b_mn", [(False, False), (False, True), (True, False), (True, True)])
-@pytest.mark.parametrize("M,N,K", [(128, 256, 64), (256, 512, 256), (300, 264, 136), (1000, 1536, 1024)])
-def test_gemm_layouts(M, N, K, a_mn, b_mn):
+@pytest.mark.parametrize("M,N,Kd", [(128, 256, 64), (256, 512, 256), (304, 264, 136), (1000, 1536, 1024)])
+def test_gemm_layouts(M, N, Kd, a_mn, b_mn):
   torch.manual_seed(0)
-  a = torch.randn((K, M) if a_mn else (M, K), device=DEV, dtype=torch.bfloat16)
-  b = torch.randn((K, N) if b_mn else (N, K), device=DEV, dtype=torch.bfloat16)
+  a = torch.randn((Kd, M) if a_mn else (M, Kd), device=DEV, dtype=torch.bfloat16)
+  b = torch.randn((Kd, N) if b_mn else (N, Kd), device=DEV, dtype=torch.bfloat16)
   out = K.gemm(a, b, a_mn=a_mn, b_mn=b_mn)
   want = ref.gemm(a, b, a_mn=a_mn, b_mn=b_mn, out_dtype=torch.float32)
-  _report(f"gemm {M}x{N}x{K} a_mn={a_mn} b_mn={b_mn}", out, want)
+  _report(f"gemm {M}x{N}x{Kd} a_mn={a_mn} b_mn={b_mn}", out, want)
 
 
 @pytest.mark.parametrize("epi", ["none", "gelu_tanh", "silu", "gated_res", "add_res"])
@@ -105,6 +105,44 @@ def test_flash_fwd_large_magnitude():
   out, _ = K.flash_fwd(q, k, v)
   want = ref.attention(q, k, v)
   _report("flash_fwd large magnitude", out, want.float(), rel_tol=2e-2, abs_frac=5e-2)
+
+
+@pytest.mark.parametrize("B,H,Sq,Skv", [(1, 2, 128, 128), (1, 2, 256, 192), (2, 3, 300, 200), (1, 2, 1000, 1111),
+                                         (1, 2, 77, 512)])
+def test_flash_bwd(B, H, Sq, Skv):
+  torch.manual_seed(11)
+  q = torch.randn((B, Sq, H, 128), device=DEV, dtype=torch.bfloat16)
+  k = torch.randn((B, Skv, H, 128), device=DEV, dtype=torch.bfloat16)
+  v = torch.randn((B, Skv, H, 128), device=DEV, dtype=torch.bfloat16)
+  d_o = torch.randn((B, Sq, H, 128), device=DEV, dtype=torch.bfloat16)
+  out, lse = K.flash_fwd(q, k, v)
+  delta = K.flash_delta(out, d_o)
+  _report("flash_delta", delta, (out.float() * d_o.float()).sum(-1).permute(0, 2, 1), rel_tol=1e-3)
+  dk, dv = K.flash_bwd_dkv(q, d_o, k, v, lse, delta)
+  dq = K.flash_bwd_dq(q, d_o, k, v, lse, delta)
+  wq, wk, wv = ref.attention_bwd(q, k, v, out, d_o, lse)
+  _report(f"flash_bwd dv {Sq}x{Skv}", dv, wv.float(), rel_tol=2e-2, abs_frac=5e-2)
+  _report(f"flash_bwd dk {Sq}x{Skv}", dk, wk.float(), rel_tol=2e-2, abs_frac=5e-2)
+  _report(f"flash_bwd dq {Sq}x{Skv}", dq, wq.float(), rel_tol=2e-2, abs_frac=5e-2)
+
+
+def test_flash_bwd_segments_match_concat():
+  """dQ over three KV segments equals dQ over their concatenation; dK/dV per segment likewise."""
+  torch.manual_seed(12)
+  B, H, Sq = 1, 2, 320
+  q = torch.randn((B, Sq, H, 128), device=DEV, dtype=torch.bfloat16)
+  d_o = torch.randn((B, Sq, H, 128), device=DEV, dtype=torch.bfloat16)
+  ks = [torch.randn((B, n, H, 128), device=DEV, dtype=torch.bfloat16) for n in (200, 200, 200)]
+  vs = [torch.randn((B, n, H, 128), device=DEV, dtype=torch.bfloat16) for n in (200, 200, 200)]
+  out, lse = K.flash_fwd(q, ks, vs)
+  delta = K.flash_delta(out, d_o)
+  dq = K.flash_bwd_dq(q, d_o, ks, vs, lse, delta)
+  kc, vc = torch.cat(ks, 1), torch.cat(vs, 1)
+  wq, wk, wv = ref.attention_bwd(q, kc, vc, out, d_o, lse)
+  _report("flash_bwd dq segments", dq, wq.float(), rel_tol=2e-2, abs_frac=5e-2)
+  dk1, dv1 = K.flash_bwd_dkv(q, d_o, ks[1], vs[1], lse, delta, out_dtype=torch.float32)
+  _report("flash_bwd dk segment 1 (fp32 out)", dk1, wk[:, 200:400].float(), rel_tol=2e-2, abs_frac=5e-2)
+  _report("flash_bwd dv segment 1 (fp32 out)", dv1, wv[:, 200:400].float(), rel_tol=2e-2, abs_frac=5e-2)
 
 
 @pytest.mark.parametrize("C", [1536, 5120, 3072])
