@@ -1,0 +1,190 @@
+"""Headline benchmark: Wan2.1-14B text-to-video TRAINING tokens/s (480x832x81 frames = 32 760 tokens).
+
+  python bench.py --gpus 1 --steps 3 --warmup 3
+  python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 --master-port P \
+      bench.py --gpus N --steps K --warmup W
+
+One sample per step (global batch 1, strong scaling): on N GPUs the sequence is context-parallel over all N ranks
+(ring schedule) and the weights + AdamW moments are sharded over the same ranks. bf16 compute, random-init weights
+of the real 40-layer architecture, synthetic latents / text embeddings of the named shape, remat per block, AdamW
+step inside the timed region. Prints ONE JSON line (rank 0).
+
+Two timed regions of K steps each, both after W warm-up steps:
+  * `value`: CUDA events around K steps with the batch already on the device (max over ranks);
+  * `e2e`: the public `WanTrainer.train_step(host_batch)` path — pinned host batch -> device copy every step and a
+    device -> host read of the loss every step — timed by the host clock between barriers + synchronize.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+BASELINE_TOKENS_PER_S = 2100.0  # reference README: 36.0 s/step at 75 600 tokens on TPU v5p-8 (4 chips)
+
+
+def reference_arm():
+  print(json.dumps({"impl": "reference",
+                    "unavailable": "reference needs jax/flax/orbax and the hatchling build backend; none is in the "
+                                   "image or the offline wheelhouse (pip install --no-index failed: No module named 'hatchling')"}))
+  return 0
+
+
+class ClockSampler:
+  """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+
+  def __init__(self, index: int):
+    self.index = index
+    self.samples, self.max_mhz, self.reasons = [], None, set()
+    self._stop = threading.Event()
+    self.thread = threading.Thread(target=self._run, daemon=True)
+
+  def _run(self):
+    q = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+    names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+    while not self._stop.is_set():
+      try:
+        out = subprocess.run(["nvidia-smi", f"--query-gpu={q}", "--format=csv,noheader,nounits", "-i", str(self.index)],
+                             capture_output=True, text=True, timeout=5).stdout.strip().splitlines()[0]
+        f = [x.strip() for x in out.split(",")]
+        self.samples.append(float(f[0]))
+        self.max_mhz = float(f[1])
+        for n, v in zip(names, f[2:6]):
+          if v.lower().startswith("active"):
+            self.reasons.add(n)
+      except Exception:
+        pass
+      self._stop.wait(0.2)
+
+  def start(self):
+    self.thread.start()
+
+  def stop(self) -> dict:
+    self._stop.set()
+    self.thread.join(timeout=10)
+    return {"sm_mhz": statistics.median(self.samples) if self.samples else None, "sm_max_mhz": self.max_mhz,
+            "reasons": sorted(self.reasons), "samples": len(self.samples)}
+
+
+def main() -> int:
+  ap = argparse.ArgumentParser()
+  ap.add_argument("--gpus", type=int, default=1)
+  ap.add_argument("--steps", type=int, default=3)
+  ap.add_argument("--warmup", type=int, default=3)
+  ap.add_argument("--impl", default="ours")
+  ap.add_argument("--remat", default="SAVE_ATTENTION", help="FULL | SAVE_ATTENTION")
+  ap.add_argument("--preset", default="wan2.1-t2v-14b", help="model preset (anything but the default is a smoke run)")
+  ap.add_argument("--height", type=int, default=480)
+  ap.add_argument("--width", type=int, default=832)
+  ap.add_argument("--frames", type=int, default=81)
+  ap.add_argument("--attention", default="tokamax_ring")
+  args = ap.parse_args()
+  if args.impl == "reference":
+    return reference_arm()
+  if args.warmup < 3:
+    args.warmup = 3
+
+  import torch
+  import torch.distributed as dist
+
+  here = os.path.dirname(os.path.abspath(__file__))
+  sys.path.insert(0, here)
+  from maxdiffusion_b200 import pyconfig
+  from maxdiffusion_b200.ops import _lib
+  from maxdiffusion_b200.parallel.mesh import create_device_mesh, init_distributed
+  from maxdiffusion_b200.trainers.wan_trainer import WanTrainer
+
+  rank, world, local_rank = init_distributed()
+  if world != args.gpus:
+    if rank == 0:
+      print(f"warning: --gpus {args.gpus} but WORLD_SIZE is {world}; using {world}", file=sys.stderr)
+  n = world
+  config = pyconfig.initialize(
+      ["bench", os.path.join(here, "maxdiffusion_b200", "configs", "base_wan_14b.yml"), "run_name=bench",
+       f"height={args.height}", f"width={args.width}", f"num_frames={args.frames}", "dataset_type=synthetic",
+       f"per_device_batch_size={1.0 / n}", f"attention={args.attention}", f"remat_policy={args.remat}",
+       f"wan_preset={args.preset}", "warmup_steps_fraction=0.0", "max_train_steps=1000000", "log_config=false",
+       "write_metrics=false", "flow_shift=5.0"])
+  mesh = create_device_mesh(config)
+  trainer = WanTrainer(config, mesh=mesh)
+  data = trainer.load_dataset()
+  seq_len = trainer.seq_len()
+
+  def barrier_sync():
+    if world > 1:
+      dist.barrier()
+    torch.cuda.synchronize()
+
+  # ---- warm-up (through the public path)
+  for _ in range(args.warmup):
+    m = trainer.train_step(next(data))
+    float(m["learning/loss"])
+  _lib.raise_on_device_status()
+
+  # ---- region 1: device-timed, inputs resident on the device
+  dev_batches = [trainer.to_device(next(data)) for _ in range(args.steps)]
+  sampler = ClockSampler(local_rank)
+  barrier_sync()
+  sampler.start()
+  launches0 = _lib.launch_count()
+  e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+  e0.record()
+  for b in dev_batches:
+    m = trainer.train_step(b, host_inputs=False)
+  e1.record()
+  barrier_sync()
+  clocks = sampler.stop()
+  launches = _lib.launch_count() - launches0
+  ms = torch.tensor([e0.elapsed_time(e1)], device="cuda")
+  if world > 1:
+    dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+  ms_per_step = ms.item() / args.steps
+  last_loss = float(m["learning/loss"])
+  _lib.raise_on_device_status()
+
+  # ---- region 2: end to end through the public API (H2D of the batch and D2H of the loss every step)
+  host_batches = [next(data) for _ in range(args.steps)]
+  h2d = sum(t.numel() * t.element_size() for t in host_batches[0].values() if torch.is_tensor(t))
+  barrier_sync()
+  t0 = time.perf_counter()
+  for b in host_batches:
+    m = trainer.train_step(b)
+    last_loss = float(m["learning/loss"])  # device -> host read of the step's result
+  barrier_sync()
+  e2e_s = torch.tensor([time.perf_counter() - t0], device="cuda")
+  if world > 1:
+    dist.all_reduce(e2e_s, op=dist.ReduceOp.MAX)
+  e2e_tokens_per_s = seq_len * args.steps / e2e_s.item()
+
+  value = seq_len * 1000.0 / ms_per_step
+  official = args.preset == "wan2.1-t2v-14b" and (args.height, args.width, args.frames) == (480, 832, 81)
+  if rank == 0:
+    print(json.dumps({
+        "metric": "Wan-14B train tokens/s" if official else f"{args.preset} train tokens/s (smoke, not the headline config)",
+        "value": value, "unit": "tokens/s", "n_gpus": n, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong",
+        "vs_baseline": value / BASELINE_TOKENS_PER_S, "dtype": "bf16", "data": "synthetic",
+        "config": {"model": "Wan2.1-T2V-14B (40 layers, dim 5120, 40 heads, ffn 13824), random init" if official else args.preset,
+                   "global_batch": 1, "seq_len": seq_len,
+                   "parallelism": f"cp{n} ring x fsdp over the same {n} ranks" if n > 1 else "single GPU",
+                   "video": f"{args.height}x{args.width}x{args.frames}", "remat": f"per block ({args.remat})",
+                   "optimizer": "AdamW, bf16 moments, stochastic rounding, step inside the timed region",
+                   "l2": "inputs larger than L2 (activations and weights of every block exceed 126 MB)",
+                   "baseline_note": "BASELINE.md P2': 2100 tokens/s on TPU v5p-8 at 720p (75 600 tokens)"},
+        "clocks": clocks,
+        "e2e": {"value": e2e_tokens_per_s, "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 4,
+                "seconds_per_step": e2e_s.item() / args.steps},
+        "gpu_launches": launches, "loss": last_loss, "impl": "ours"}))
+  if world > 1:
+    dist.destroy_process_group()
+  return 0
+
+
+if __name__ == "__main__":
+  sys.exit(main())

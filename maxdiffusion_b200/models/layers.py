@@ -1,0 +1,69 @@
+"""Small building blocks shared by the model families."""
+from __future__ import annotations
+
+import math
+
+import torch
+import torch.nn as nn
+
+from ..ops import functional as OF
+
+
+class Linear(nn.Module):
+  """y = x @ Wᵀ + b with W stored [out, in] (the diffusers / PyTorch checkpoint orientation).
+
+  CUDA bf16 inputs run on the tcgen05 GEMM through `ops.functional.linear`.
+  """
+
+  def __init__(self, in_features: int, out_features: int, bias: bool = True):
+    super().__init__()
+    self.in_features, self.out_features = in_features, out_features
+    self.weight = nn.Parameter(torch.empty(out_features, in_features))
+    self.bias = nn.Parameter(torch.zeros(out_features)) if bias else None
+    nn.init.normal_(self.weight, std=1.0 / math.sqrt(in_features))
+
+  def forward(self, x, activation: str | None = None):
+    return OF.linear(x, self.weight, self.bias, activation)
+
+  def extra_repr(self) -> str:
+    return f"in_features={self.in_features}, out_features={self.out_features}, bias={self.bias is not None}"
+
+
+def sinusoidal_embedding(timesteps: torch.Tensor, dim: int, flip_sin_to_cos: bool = True, freq_shift: float = 0.0,
+                         max_period: float = 10000.0, scale: float = 1.0) -> torch.Tensor:
+  """Sinusoidal timestep features [N, dim] in fp32 (reference: src/maxdiffusion/models/embeddings_flax.py:28-62)."""
+  half = dim // 2
+  exponent = -math.log(max_period) * torch.arange(half, dtype=torch.float32, device=timesteps.device) / (half - freq_shift)
+  emb = scale * timesteps.float()[:, None] * torch.exp(exponent)[None, :]
+  emb = torch.cat([emb.cos(), emb.sin()], dim=-1) if flip_sin_to_cos else torch.cat([emb.sin(), emb.cos()], dim=-1)
+  if dim % 2 == 1:
+    emb = torch.nn.functional.pad(emb, (0, 1))
+  return emb
+
+
+class RMSNorm(nn.Module):
+
+  def __init__(self, dim: int, eps: float = 1e-6, elementwise_affine: bool = True):
+    super().__init__()
+    self.eps = eps
+    self.weight = nn.Parameter(torch.ones(dim)) if elementwise_affine else None
+
+  def forward(self, x):
+    xf = x.float()
+    y = xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + self.eps)
+    if self.weight is not None:
+      y = y * self.weight.float()
+    return y.to(x.dtype)
+
+
+class FP32LayerNorm(nn.Module):
+  """LayerNorm with statistics in fp32 (reference: src/maxdiffusion/models/normalization_flax.py:160-180)."""
+
+  def __init__(self, dim: int, eps: float = 1e-6, elementwise_affine: bool = True):
+    super().__init__()
+    self.eps = eps
+    self.weight = nn.Parameter(torch.ones(dim)) if elementwise_affine else None
+    self.bias = nn.Parameter(torch.zeros(dim)) if elementwise_affine else None
+
+  def forward(self, x):
+    return OF.layer_norm_mod(x, gamma=self.weight, beta=self.bias, eps=self.eps)

@@ -140,20 +140,25 @@ def linear_gated_residual(x, weight, bias, residual, gate):
 # ---------------------------------------------------------------------------------------------
 # attention
 # ---------------------------------------------------------------------------------------------
+# attention outputs are kept across the rematerialisation of a block only when recomputing them is expensive
+_REMAT_MIN_KV = 2048
+
+
 class _AttentionFn(torch.autograd.Function):
 
   @staticmethod
   def forward(ctx, q, scale, n_seg, *kv):
     ks, vs = list(kv[:n_seg]), list(kv[n_seg:])
     saved = None
-    if _remat.mode == "replay":
+    keep = _remat.mode is not None and sum(k.shape[1] for k in ks) >= _REMAT_MIN_KV
+    if keep and _remat.mode == "replay":
       saved = _remat.store[_remat.cursor]
       _remat.cursor += 1
     if saved is not None:
       out, lse = saved
     else:
       out, lse = K.flash_fwd(q, ks, vs, scale)
-      if _remat.mode == "record":
+      if keep and _remat.mode == "record":
         _remat.store.append((out, lse))
     ctx.scale, ctx.n_seg = scale, n_seg
     ctx.save_for_backward(q, out, lse, *ks, *vs)
@@ -183,8 +188,6 @@ def attention(q, k, v, scale: float | None = None):
   D = q.shape[-1]
   scale = scale if scale is not None else 1.0 / math.sqrt(D)
   if _fast(q) and D == 128:
-    if _remat.mode == "record" and torch.is_grad_enabled() is False:
-      pass
     return _AttentionFn.apply(q, scale, len(ks), *ks, *vs)
   kc = torch.cat(ks, dim=1) if len(ks) > 1 else ks[0]
   vc = torch.cat(vs, dim=1) if len(vs) > 1 else vs[0]
@@ -314,8 +317,9 @@ def gated_residual(res, y, gate=None):
 class _CheckpointFn(torch.autograd.Function):
 
   @staticmethod
-  def forward(ctx, fn, save_attention, n_tensors, *args):
+  def forward(ctx, fn, save_attention, on_backward_done, n_tensors, *args):
     ctx.fn = fn
+    ctx.on_backward_done = on_backward_done
     ctx.store = [] if save_attention else None
     tensors = args[:n_tensors]
     ctx.rest = args[n_tensors:]
@@ -347,13 +351,17 @@ class _CheckpointFn(torch.autograd.Function):
     torch.autograd.backward([o for o in outs if o.requires_grad], [g for o, g in zip(outs, douts) if o.requires_grad])
     ctx.store = None
     grads = [t.grad if (t is not None and t.is_floating_point()) else None for t in inputs]
-    return (None, None, None, *grads, *([None] * len(ctx.rest)))
+    if ctx.on_backward_done is not None:
+      ctx.on_backward_done()
+    return (None, None, None, None, *grads, *([None] * len(ctx.rest)))
 
 
-def checkpoint_block(fn, *tensor_args, extra_args: Sequence = (), save_attention: bool = False):
+def checkpoint_block(fn, *tensor_args, extra_args: Sequence = (), save_attention: bool = False,
+                     on_backward_done=None):
   """Runs `fn(*tensor_args, *extra_args)` storing only its tensor inputs; the backward pass recomputes it.
 
   Parameters used inside `fn` receive their gradients during the recomputation. With `save_attention`
-  the flash-attention outputs of the first pass are kept and not recomputed.
+  the flash-attention outputs of the first pass are kept and not recomputed. `on_backward_done()` is called
+  once the parameter gradients of the block are complete (the FSDP engine reduces and applies them there).
   """
-  return _CheckpointFn.apply(fn, save_attention, len(tensor_args), *tensor_args, *extra_args)
+  return _CheckpointFn.apply(fn, save_attention, on_backward_done, len(tensor_args), *tensor_args, *extra_args)

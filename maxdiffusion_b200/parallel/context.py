@@ -1,0 +1,209 @@
+"""Context (sequence) parallelism for self-attention: gather/ring, Ulysses, and 2-D Ulysses x ring.
+
+Strategy names follow the reference's attention-kernel registry
+(src/maxdiffusion/models/attention_flax.py:1589-1867; dispatch in `common_types.ATTENTION_KERNELS`):
+
+  gather / ring : every rank keeps its query shard; the K/V shards of all ranks are presented to ONE flash
+                  kernel launch as KV segments, so the running (O, m, l) never leaves the SM between hops (the
+                  reference merges per-hop partial results through HBM, ring_attention_kernel.py:1099-1131).
+                  Backward: dQ over all segments in one launch, dK/dV per segment, then a reduce-scatter returns
+                  the partial sums to the owners (reference: ring_attention_kernel.py:181-289).
+  ulysses       : all-to-all heads <-> sequence, local full-sequence attention on H/U heads, all-to-all back
+                  (reference: attention_flax.py:817-1061).
+  usp           : Ulysses inside `ulysses` groups, gather/ring across `ring` groups (reference: :1064-1254).
+
+Cross-attention never communicates: K/V are the 512 text tokens, replicated (reference: :2405-2437).
+This module is the NCCL baseline; `parallel.symm` provides the peer-memory transport used on NVLink.
+"""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+import torch.distributed as dist
+
+from ..ops import functional as OF
+from ..ops import kernels as K
+from . import collectives as C
+
+
+class _GatherSeq(torch.autograd.Function):
+  """all-gather along a new leading axis; backward returns each owner the sum of the partial gradients."""
+
+  @staticmethod
+  def forward(ctx, x, group):
+    ctx.group = group
+    return C.all_gather_stack(x, group)
+
+  @staticmethod
+  def backward(ctx, g):
+    return C.reduce_scatter_stack(g.contiguous(), ctx.group), None
+
+
+class _HeadsToSeq(torch.autograd.Function):
+
+  @staticmethod
+  def forward(ctx, x, group):
+    ctx.group = group
+    return C.all_to_all_heads_to_seq(x, group)
+
+  @staticmethod
+  def backward(ctx, g):
+    return C.all_to_all_seq_to_heads(g.contiguous(), ctx.group), None
+
+
+class _SeqToHeads(torch.autograd.Function):
+
+  @staticmethod
+  def forward(ctx, x, group):
+    ctx.group = group
+    return C.all_to_all_seq_to_heads(x, group)
+
+  @staticmethod
+  def backward(ctx, g):
+    return C.all_to_all_heads_to_seq(g.contiguous(), ctx.group), None
+
+
+class _SegmentAttentionFn(torch.autograd.Function):
+  """Kernel path of gather/ring attention: local q against the stacked K/V shards [n, B, S_loc, H, D]."""
+
+  @staticmethod
+  def forward(ctx, q, k, v, scale, group, valid_lens):
+    kg = C.all_gather_stack(k, group)
+    vg = C.all_gather_stack(v, group)
+    n = kg.shape[0]
+    ks = [kg[i][:, :valid_lens[i]] for i in range(n)]
+    vs = [vg[i][:, :valid_lens[i]] for i in range(n)]
+    state = OF._remat
+    saved = None
+    if state.mode == "replay":
+      saved = state.store[state.cursor]
+      state.cursor += 1
+    if saved is not None:
+      out, lse = saved
+    else:
+      out, lse = K.flash_fwd(q, ks, vs, scale)
+      if state.mode == "record":
+        state.store.append((out, lse))
+    ctx.scale, ctx.group, ctx.valid_lens = scale, group, valid_lens
+    ctx.save_for_backward(q, out, lse, kg, vg)
+    return out
+
+  @staticmethod
+  def backward(ctx, d_o):
+    q, out, lse, kg, vg = ctx.saved_tensors
+    n = kg.shape[0]
+    lens = ctx.valid_lens
+    if d_o.stride(-1) != 1:
+      d_o = d_o.contiguous()
+    ks = [kg[i][:, :lens[i]] for i in range(n)]
+    vs = [vg[i][:, :lens[i]] for i in range(n)]
+    delta = K.flash_delta(out, d_o)
+    dq = K.flash_bwd_dq(q, d_o, ks, vs, lse, delta, ctx.scale)
+    dkg = torch.zeros_like(kg) if min(lens) < kg.shape[2] else torch.empty_like(kg)
+    dvg = torch.zeros_like(vg) if min(lens) < vg.shape[2] else torch.empty_like(vg)
+    for i in range(n):
+      dk, dv = K.flash_bwd_dkv(q, d_o, ks[i], vs[i], lse, delta, ctx.scale)
+      dkg[i][:, :lens[i]].copy_(dk)
+      dvg[i][:, :lens[i]].copy_(dv)
+    dk = C.reduce_scatter_stack(dkg, ctx.group)
+    dv = C.reduce_scatter_stack(dvg, ctx.group)
+    return dq, dk, dv, None, None, None
+
+
+class ContextParallel:
+  """Sequence sharding + the self-attention strategy of one rank.
+
+  `mesh` is a `parallel.mesh.DeviceMesh`; `strategy` one of local / gather / ring / ulysses / usp.
+  """
+
+  def __init__(self, mesh, strategy: str = "ring"):
+    self.mesh = mesh
+    self.strategy = strategy
+    self.group = mesh.group("context")
+    self.size = mesh.size("context")
+    self.rank = mesh.index_in("context") if self.size > 1 else 0
+    self.ulysses_group = mesh.group("ulysses")
+    self.ring_group = mesh.group("ring")
+    self.ulysses_size = len(mesh.ranks("ulysses"))
+    self.ring_size = len(mesh.ranks("ring"))
+    self.ring_rank = mesh.index_in("ring") if self.ring_size > 1 else 0
+    self.full_len: Optional[int] = None
+    self.local_len: Optional[int] = None
+
+  # ---- sequence layout ---------------------------------------------------------------------
+  def shard_sequence(self, x: torch.Tensor, dim: int = 1) -> torch.Tensor:
+    """Local shard of a full-length tensor; the length is padded (zeros) to a multiple of the axis size."""
+    if self.size == 1:
+      return x
+    S = x.shape[dim]
+    per = (S + self.size - 1) // self.size
+    self.full_len, self.local_len = S, per
+    if per * self.size != S:
+      pad = [0, 0] * (x.dim() - dim - 1) + [0, per * self.size - S]
+      x = torch.nn.functional.pad(x, pad)
+    return x.narrow(dim, self.rank * per, per).contiguous()
+
+  def valid_lengths(self, ranks: int, per: int, group_stride: int = 1) -> list[int]:
+    """Unpadded length of every shard along an axis of `ranks` shards of `per` tokens."""
+    if self.full_len is None:
+      return [per] * ranks
+    out = []
+    for r in range(ranks):
+      start = r * per
+      out.append(max(0, min(per, self.full_len - start)))
+    return out
+
+  def unshard_sequence(self, x: torch.Tensor, dim: int = 1) -> torch.Tensor:
+    """Inverse of `shard_sequence` (no gradient flows through it; training takes its loss on the shard)."""
+    if self.size == 1:
+      return x
+    with torch.no_grad():
+      full = C.all_gather_cat(x.transpose(0, dim).contiguous(), self.group, dim=0).transpose(0, dim)
+    return full.narrow(dim, 0, self.full_len) if self.full_len is not None else full
+
+  # ---- attention ---------------------------------------------------------------------------
+  def _segment_attention(self, q, k, v, group, n, valid_lens, scale=None):
+    if n == 1:
+      return OF.attention(q, k, v, scale)
+    D = q.shape[-1]
+    scale = scale if scale is not None else D ** -0.5
+    if q.is_cuda and q.dtype == torch.bfloat16 and D == 128:
+      return _SegmentAttentionFn.apply(q, k, v, scale, group, tuple(valid_lens))
+    kg = _GatherSeq.apply(k, group)
+    vg = _GatherSeq.apply(v, group)
+    ks = [kg[i][:, :valid_lens[i]] for i in range(n)]
+    vs = [vg[i][:, :valid_lens[i]] for i in range(n)]
+    return OF.attention(q, ks, vs, scale)
+
+  def self_attention(self, q, k, v, scale=None):
+    """q, k, v: [B, S_loc, H, D] (sequence-sharded). Returns the attention output with the same layout."""
+    if self.size == 1 or self.strategy == "local":
+      return OF.attention(q, k, v, scale)
+    per = q.shape[1]
+    if self.strategy in ("gather", "ring"):
+      return self._segment_attention(q, k, v, self.group, self.size, self.valid_lengths(self.size, per), scale)
+    if self.strategy == "ulysses":
+      H = q.shape[2]
+      if H % self.size != 0:
+        raise ValueError(f"Ulysses needs heads ({H}) divisible by the context axis ({self.size})")
+      qh, kh, vh = (_HeadsToSeq.apply(t, self.group) for t in (q, k, v))
+      if self.full_len is not None and self.full_len < per * self.size:
+        kh, vh = kh[:, :self.full_len], vh[:, :self.full_len]
+      o = OF.attention(qh, kh, vh, scale)
+      return _SeqToHeads.apply(o, self.group)
+    if self.strategy == "usp":
+      H = q.shape[2]
+      U, R = self.ulysses_size, self.ring_size
+      if H % U != 0:
+        raise ValueError(f"ulysses_shards ({U}) must divide the number of heads ({H})")
+      qh, kh, vh = (_HeadsToSeq.apply(t, self.ulysses_group) for t in (q, k, v))
+      # after the exchange a rank holds U consecutive shards of the sequence: the ring segment r covers the
+      # global tokens [r*U*per, (r+1)*U*per)
+      seg = per * U
+      lens = [seg] * R
+      if self.full_len is not None:
+        lens = [max(0, min(seg, self.full_len - r * seg)) for r in range(R)]
+      o = self._segment_attention(qh, kh, vh, self.ring_group, R, lens, scale)
+      return _SeqToHeads.apply(o, self.ulysses_group)
+    raise ValueError(f"unknown context strategy {self.strategy}")

@@ -1,0 +1,111 @@
+"""Training-side utilities: config validation, metric names, and the metrics writer.
+
+The writer keeps the reference's behaviour (src/maxdiffusion/train_utils.py:106-209): scalars are pushed to a
+queue drained by a writer thread (TensorBoard when `torch.utils.tensorboard` is importable, plus an optional
+JSONL `metrics_file` consumed by `end_to_end/eval_assert.py`), and a console line
+`completed step: N, seconds: ..., TFLOP/s/device: ..., loss: ...` is printed by rank 0.
+"""
+from __future__ import annotations
+
+import json
+import os
+import queue
+import threading
+from typing import Optional
+
+import torch
+
+from . import max_logging
+
+
+def validate_train_config(config) -> None:
+  """Fail early on settings that cannot train (reference: train_utils.py:38-76)."""
+  if not config.get("run_name", ""):
+    raise ValueError("run_name must be set for training (it names the output sub-directories)")
+  if int(config.get("max_train_steps", 0)) <= 0 and int(config.get("num_train_epochs", 0)) <= 0:
+    raise ValueError("max_train_steps or num_train_epochs must be positive")
+  if str(config.get("dataset_type", "")) not in ("tfrecord", "hf", "tf", "grain", "synthetic"):
+    raise ValueError(f"unknown dataset_type {config.get('dataset_type')}")
+
+
+def compute_snr(alphas_cumprod: torch.Tensor, timesteps: torch.Tensor) -> torch.Tensor:
+  """SNR(t) = alpha_bar / (1 - alpha_bar) (reference: train_utils.py:217)."""
+  a = alphas_cumprod.to(timesteps.device)[timesteps.long()]
+  return a / (1.0 - a)
+
+
+def generate_timestep_weights(config, num_timesteps: int) -> torch.Tensor:
+  """Sampling weights over timesteps for `timestep_bias` strategies later/earlier/range/none."""
+  bias = config.get("timestep_bias", {"strategy": "none"}) or {"strategy": "none"}
+  w = torch.ones(num_timesteps)
+  strategy = bias.get("strategy", "none")
+  if strategy == "none":
+    return w / w.sum()
+  n_bias = int(float(bias.get("portion", 0.25)) * num_timesteps)
+  mult = float(bias.get("multiplier", 1.0))
+  if strategy == "later":
+    w[-n_bias:] *= mult
+  elif strategy == "earlier":
+    w[:n_bias] *= mult
+  elif strategy == "range":
+    w[int(bias.get("begin", 0)):int(bias.get("end", num_timesteps))] *= mult
+  else:
+    raise ValueError(f"unknown timestep_bias strategy {strategy}")
+  return w / w.sum()
+
+
+class MetricsWriter:
+
+  def __init__(self, config, rank: int = 0):
+    self.config = config
+    self.rank = rank
+    self.queue: "queue.Queue" = queue.Queue()
+    self.tb = None
+    self.file = None
+    if rank == 0:
+      tb_dir = config.get("tensorboard_dir", "")
+      if tb_dir and config.get("write_metrics", True):
+        try:
+          from torch.utils.tensorboard import SummaryWriter
+
+          os.makedirs(tb_dir, exist_ok=True)
+          self.tb = SummaryWriter(tb_dir)
+        except Exception as e:  # tensorboard is optional
+          max_logging.log(f"TensorBoard writer unavailable ({e}); metrics go to the console / metrics_file only")
+      path = config.get("metrics_file", "")
+      if path:
+        os.makedirs(os.path.dirname(os.path.abspath(path)), exist_ok=True)
+        self.file = open(path, "a", encoding="utf-8")
+    self.thread = threading.Thread(target=self._worker, daemon=True)
+    self.thread.start()
+
+  def _worker(self) -> None:
+    while True:
+      item = self.queue.get()
+      if item is None:
+        break
+      step, scalars = item
+      if self.rank != 0:
+        continue
+      max_logging.log("completed step: {}, seconds: {:.3f}, TFLOP/s/device: {:.3f}, loss: {:.3f}".format(
+          step, scalars.get("perf/step_time_seconds", 0.0), scalars.get("perf/per_device_tflops_per_sec", 0.0),
+          scalars.get("learning/loss", float("nan"))))
+      if self.tb is not None:
+        for k, v in scalars.items():
+          self.tb.add_scalar(k, v, step)
+        if step % max(1, int(self.config.get("log_period", 100))) == 0:
+          self.tb.flush()
+      if self.file is not None:
+        self.file.write(json.dumps({"step": step, **scalars}) + "\n")
+        self.file.flush()
+
+  def write(self, step: int, scalars: dict) -> None:
+    self.queue.put((step, dict(scalars)))
+
+  def close(self) -> None:
+    self.queue.put(None)
+    self.thread.join(timeout=30)
+    if self.tb is not None:
+      self.tb.close()
+    if self.file is not None:
+      self.file.close()

@@ -1,0 +1,215 @@
+"""Wan 2.1 text-to-video training: flow-matching MSE, per-block remat, FSDP x context parallelism.
+
+Flow of one step (reference: src/maxdiffusion/trainers/wan_trainer.py:136-189 and
+src/maxdiffusion/trainers/base_wan_trainer.py:256-374):
+  host batch (pinned) -> device, sample shifted timesteps, noise, `apply_flow_match` -> model forward on this
+  rank's token shard -> weighted MSE against the sharded target -> backward, during which every block's
+  gradients are reduce-scattered and its AdamW update applied (`parallel.fsdp`) -> replicated root parameters ->
+  metrics (`learning/loss`, `learning/max_grad_norm`, `learning/max_abs_grad`, step time, TFLOP/s).
+"""
+from __future__ import annotations
+
+import os
+import time
+from concurrent.futures import ThreadPoolExecutor
+from typing import Optional
+
+import torch
+import torch.distributed as dist
+
+from .. import max_logging
+from ..input_pipeline.synthetic_data_iterator import make_synthetic_iterator
+from ..models.wan.transformer_wan import WAN_PRESETS, WanConfig, WanModel
+from ..parallel.context import ContextParallel
+from ..parallel.fsdp import AdamWConfig, FSDPEngine, lr_schedule
+from ..parallel.mesh import DeviceMesh, create_device_mesh
+from ..schedulers.scheduling_flow_match import FlowMatchScheduler
+
+
+def wan_train_tflops(cfg: WanConfig, seq_len: int, batch: float, text_len: int = 512) -> float:
+  """Analytic training TFLOPs per step (3x forward), the reference's own model
+  (src/maxdiffusion/trainers/base_wan_trainer.py:107-155)."""
+  d = cfg.dim
+  attn = (3 * 2 * seq_len * d * d + 2 * 2 * seq_len * seq_len * d + 3 * 2 * text_len * d * d + 2 * seq_len * d * d +
+          2 * 2 * seq_len * text_len * d + 2 * 2 * seq_len * d * d)
+  ffn = 2 * 2 * seq_len * d * cfg.ffn_dim
+  return 3 * batch * (attn + ffn) * cfg.num_layers / 1e12
+
+
+def resolve_wan_config(config) -> WanConfig:
+  preset = str(config.get("wan_preset", "") or "")
+  if not preset:
+    name = str(config.get("pretrained_model_name_or_path", "")).lower()
+    preset = "wan2.1-t2v-1.3b" if "1.3b" in name else ("wan2.1-i2v-14b" if "i2v" in name else "wan2.1-t2v-14b")
+  cfg = dict(WAN_PRESETS[preset])
+  override = config.get("wan_config_overrides", None)
+  if override:
+    cfg.update(override)
+  return WanConfig(**cfg)
+
+
+class WanTrainer:
+
+  def __init__(self, config, mesh: Optional[DeviceMesh] = None, model: Optional[WanModel] = None, device=None):
+    self.config = config
+    self.device = torch.device(device) if device is not None else torch.device(
+        "cuda", torch.cuda.current_device()) if torch.cuda.is_available() else torch.device("cpu")
+    self.mesh = mesh if mesh is not None else create_device_mesh(config)
+    self.dtype = config.weights_dtype if self.device.type == "cuda" else torch.float32
+    self.wan_cfg = model.cfg if model is not None else resolve_wan_config(config)
+    seed = int(config.get("seed", 0))
+    remat = str(config.get("remat_policy", "NONE")).upper()
+    if self.mesh.world_size > 1 and remat == "NONE":
+      remat = "SAVE_ATTENTION"  # sharded weights are only resident around a block's (re)computation
+    if model is None:
+      torch.manual_seed(seed)
+      prev = torch.get_default_dtype()
+      torch.set_default_dtype(self.dtype)
+      try:
+        with torch.device(self.device):
+          model = WanModel(self.wan_cfg, remat_policy=remat)
+      finally:
+        torch.set_default_dtype(prev)
+    else:
+      model = model.to(device=self.device, dtype=self.dtype)
+      model.remat_policy = remat
+    self.model = model
+
+    opt = AdamWConfig(
+        lr=float(config.get("learning_rate", 1e-5)), b1=float(config.get("adam_b1", 0.9)),
+        b2=float(config.get("adam_b2", 0.999)), eps=float(config.get("adam_eps", 1e-8)),
+        weight_decay=float(config.get("adam_weight_decay", 0.0)),
+        clip_value=float(config.get("max_grad_value", 1.0)) if config.get("opt_enable_grad_clipping", False) else 0.0,
+        clip_global_norm=float(config.get("max_grad_norm", 1.0)) if config.get("opt_enable_grad_global_norm_clipping", False) else 0.0,
+        state_dtype=config.get("opt_state_dtype", self.dtype) if self.device.type == "cuda" else torch.float32,
+        stochastic_rounding=bool(config.get("stochastic_rounding", True)))
+    block_param_ids = {id(p) for b in model.blocks for p in b.parameters()}
+    root_params = [p for p in model.parameters() if id(p) not in block_param_ids]
+    shard_group = self.mesh.group("shard")
+    replica_group = self.mesh.group("replica")
+    self.engine = FSDPEngine(model.blocks, root_params, opt, group=shard_group, replica_group=replica_group,
+                             device=self.device, param_dtype=self.dtype, seed=seed)
+    model.block_hook = self.engine.block_hook
+    self.pctx = ContextParallel(self.mesh, str(config.get("context_strategy", "ring"))) if self.mesh.size("context") > 1 else None
+
+    self.scheduler = FlowMatchScheduler(num_train_timesteps=1000, shift=float(config.get("flow_shift", 3.0)))
+    self.scheduler_state = self.scheduler.set_timesteps(self.scheduler.create_state(), 1000, training=True, device=self.device)
+    self.gen = torch.Generator(device=self.device).manual_seed(seed + 1 + 7919 * (self.mesh.coords.get('data', 0) * self.mesh.size('fsdp') + self.mesh.coords.get('fsdp', 0)))
+    self.step = 0
+    self.base_lr = opt.lr
+    self.schedule_steps = int(config.get("learning_rate_schedule_steps", 0) or config.get("max_train_steps", 1))
+    self.warmup_fraction = float(config.get("warmup_steps_fraction", 0.0))
+    self.use_weights = not bool(config.get("disable_training_weights", False))
+    # samples per (data, fsdp) replica: the context x tensor ranks of a replica work on the same samples
+    self.batch_size = max(1, int(round(float(config.get("per_device_batch_size", 1)) * self.mesh.size("context") *
+                                       self.mesh.size("tensor"))))
+
+  # ------------------------------------------------------------------ data
+  def load_dataset(self):
+    dataset_type = str(self.config.get("dataset_type", "synthetic"))
+    if dataset_type == "synthetic":
+      return make_synthetic_iterator(self.config, self.batch_size, seed=int(self.config.get("seed", 0)) + 17)
+    from ..input_pipeline.input_pipeline_interface import make_data_iterator
+
+    return make_data_iterator(self.config, self.mesh, self.batch_size)
+
+  def to_device(self, batch: dict) -> dict:
+    out = {}
+    for k, v in batch.items():
+      if torch.is_tensor(v):
+        out[k] = v.to(self.device, non_blocking=True)
+      else:
+        out[k] = v
+    return out
+
+  # ------------------------------------------------------------------ step
+  def train_step(self, batch: dict, host_inputs: bool = True) -> dict:
+    """One optimizer step. `batch` holds host (pinned) or device tensors; returns device-side metrics."""
+    cfg = self.wan_cfg
+    if host_inputs:
+      batch = self.to_device(batch)
+    latents = batch["latents"].to(self.dtype)
+    text = batch["encoder_hidden_states"].to(self.dtype)
+    B = latents.shape[0]
+    lr = lr_schedule(self.step, self.base_lr, self.schedule_steps, self.warmup_fraction)
+    self.engine.begin_step(lr)
+
+    timesteps = self.scheduler.sample_timesteps(B, generator=self.gen, device=self.device)
+    noise = torch.randn(latents.shape, generator=self.gen, device=self.device, dtype=torch.float32).to(self.dtype)
+    noisy, target, weights = self.scheduler.apply_flow_match(noise.float(), latents.float(), timesteps, self.scheduler_state)
+
+    pred = self.model(noisy.to(self.dtype), timesteps, text, pctx=self.pctx, return_tokens=True)  # [B,S_loc,P]
+    tgt_tokens, _ = self.model.patchify(target, channel_last=True)
+    total = tgt_tokens.numel()
+    if self.pctx is not None:
+      full_len = tgt_tokens.shape[1]
+      tgt_tokens = self.pctx.shard_sequence(tgt_tokens)
+      valid = self.pctx.valid_lengths(self.pctx.size, tgt_tokens.shape[1])[self.pctx.rank]
+      pred, tgt_tokens = pred[:, :valid], tgt_tokens[:, :valid]
+    err = (tgt_tokens.float() - pred.float()) ** 2
+    if self.use_weights:
+      err = err * weights.to(err.device).reshape(-1, 1, 1)
+    loss = err.sum() / total
+    loss.backward()
+    stats = self.engine.finish_step(model_group=self.mesh.group("model"))
+    loss_value = loss.detach()
+    if self.mesh.group("model") is not None:
+      loss_value = loss_value.clone()
+      dist.all_reduce(loss_value, group=self.mesh.group("model"))
+    self.step += 1
+    return {"learning/loss": loss_value, "learning/max_grad_norm": stats["grad_norm"],
+            "learning/max_abs_grad": stats["max_abs_grad"], "learning/current_learning_rate": lr}
+
+  # ------------------------------------------------------------------ loop
+  def seq_len(self) -> int:
+    c = self.config
+    pt, ph, pw = self.wan_cfg.patch_size
+    return ((int(c.get("num_frames", 81)) - 1) // 4 + 1) // pt * (int(c.get("height", 480)) // 8 // ph) * (int(c.get("width", 832)) // 8 // pw)
+
+  def start_training(self):
+    from ..train_utils import MetricsWriter
+
+    config = self.config
+    data = self.load_dataset()
+    writer = MetricsWriter(config, self.mesh.rank)
+    tflops = wan_train_tflops(self.wan_cfg, self.seq_len(), float(self.batch_size) * self.mesh.size("data") * self.mesh.size("fsdp"))
+    per_device = tflops / self.mesh.world_size
+    max_logging.log(f"Calculated TFLOPs per pass: {tflops:.4f} ({per_device:.4f} per device)")
+    max_steps = int(config.get("max_train_steps", 1))
+    pool = ThreadPoolExecutor(max_workers=1)
+    nxt = pool.submit(lambda: next(data))
+    checkpointer = None
+    if int(config.get("checkpoint_every", -1)) > 0 or config.get("save_final_checkpoint", False):
+      from ..checkpointing.wan_checkpointer import WanCheckpointer
+
+      checkpointer = WanCheckpointer(config)
+      restored = checkpointer.maybe_restore(self)
+      if restored is not None:
+        self.step = restored
+    profiler = None
+    if config.get("enable_profiler", False):
+      from ..max_utils import Profiler
+
+      profiler = Profiler(config)
+    while self.step < max_steps:
+      batch = nxt.result()
+      nxt = pool.submit(lambda: next(data))
+      if profiler is not None:
+        profiler.maybe_start(self.step)
+      t0 = time.perf_counter()
+      metrics = self.train_step(batch)
+      loss = float(metrics["learning/loss"])  # device -> host, ends the step
+      dt = time.perf_counter() - t0
+      if profiler is not None:
+        profiler.maybe_stop(self.step)
+      scalars = {k: float(v) for k, v in metrics.items()}
+      scalars.update({"perf/step_time_seconds": dt, "perf/per_device_tflops": per_device,
+                      "perf/per_device_tflops_per_sec": per_device / dt})
+      writer.write(self.step, scalars)
+      if checkpointer is not None and int(config.get("checkpoint_every", -1)) > 0 and self.step % int(config.checkpoint_every) == 0:
+        checkpointer.save(self.step, self)
+    if checkpointer is not None and config.get("save_final_checkpoint", False):
+      checkpointer.save(self.step, self)
+    writer.close()
+    pool.shutdown(wait=False, cancel_futures=True)
+    return self
