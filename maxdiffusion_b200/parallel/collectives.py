@@ -22,9 +22,7 @@ def all_gather_cat(x: torch.Tensor, group, dim: int = 0) -> torch.Tensor:
   n = group_size(group)
   if n == 1:
     return x
-  x = x.contiguous()
-  out = torch.empty((n,) + tuple(x.shape), dtype=x.dtype, device=x.device)
-  dist.all_gather_into_tensor(out, x, group=group)
+  out = all_gather_stack(x, group)
   if dim == 0:
     return out.reshape((n * x.shape[0],) + tuple(x.shape[1:]))
   return torch.cat(list(out.unbind(0)), dim=dim)
@@ -36,9 +34,12 @@ def all_gather_stack(x: torch.Tensor, group) -> torch.Tensor:
   x = x.contiguous()
   if n == 1:
     return x.unsqueeze(0)
-  out = torch.empty((n,) + tuple(x.shape), dtype=x.dtype, device=x.device)
+  if x.dim() == 0:
+    x = x.reshape(1)
+  # the concatenated form of the output is the one every backend accepts
+  out = torch.empty((n * x.shape[0],) + tuple(x.shape[1:]), dtype=x.dtype, device=x.device)
   dist.all_gather_into_tensor(out, x, group=group)
-  return out
+  return out.view((n,) + tuple(x.shape))
 
 
 def reduce_scatter_stack(x: torch.Tensor, group) -> torch.Tensor:

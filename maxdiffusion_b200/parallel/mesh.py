@@ -85,6 +85,8 @@ def split_context(context_ranks: Sequence[int], ulysses_shards: int) -> tuple[li
   """Splits one context group into Ulysses groups (adjacent ranks) and ring groups (strided ranks)."""
   n = len(context_ranks)
   u = ulysses_shards if ulysses_shards and ulysses_shards > 0 else 1
+  if n == 1:
+    u = 1
   if n % u != 0:
     raise ValueError(f"ulysses_shards={u} does not divide the context axis ({n})")
   ulysses = [list(context_ranks[i:i + u]) for i in range(0, n, u)]
