@@ -8,7 +8,7 @@
 //
 // with P = exp2(S*c - lse2) and dS = P * (dP - delta), delta = rowsum(dO * O). No atomics and no
 // cross-CTA reduction are needed, so results are bitwise reproducible. The two score tiles of a
-// step are double buffered in TMEM so the elementwise warps (8 warps, each warp group owns half of
+// step are double buffered in TMEM so the elementwise warps (16 warps, each warp group owns 16 of
 // the 64 columns) overlap with the tensor core. The streamed tile is used twice from the same
 // shared memory: as a K-major operand of the score MMAs and as an MN-major operand of the
 // accumulating MMAs whose A operand (P^T / dS as packed bf16) is read from TMEM.
@@ -30,7 +30,8 @@ constexpr int X_CHUNK_BYTES = BX * 128;         // 16 KiB
 constexpr int Y_TILE_BYTES = BY * D * 2;        // 16 KiB (two 8 KiB chunks)
 constexpr int Y_CHUNK_BYTES = BY * 128;         // 8 KiB
 constexpr int MAX_SEGMENTS = 8;
-constexpr int NUM_THREADS = 384;                // warp 0 TMA, warp 1 MMA, warps 4-11 elementwise
+constexpr int EW_GROUPS = 4;                    // elementwise warp groups, 16 of the 64 columns each
+constexpr int NUM_THREADS = 128 + EW_GROUPS * 128;  // warp 0 TMA, warp 1 MMA, warps 4.. elementwise
 constexpr int SMEM_BYTES = 2 * X_TILE_BYTES + Y_STAGES * 2 * Y_TILE_BYTES + Y_STAGES * 128 * 4 + 1024 + 256;
 
 struct Maps {
@@ -91,7 +92,7 @@ flash_bwd_kernel(const __grid_constant__ Maps maps, const Params p) {
     }
     for (int i = 0; i < 2; ++i) {
       mbar_init(&t_full[i], 1);
-      mbar_init(&ps_full[i], 256);
+      mbar_init(&ps_full[i], EW_GROUPS * 128);
     }
     mbar_init(acc_final, 1);
     *abort_flag = 0;
@@ -183,7 +184,7 @@ flash_bwd_kernel(const __grid_constant__ Maps maps, const Params p) {
         const uint32_t y2a = y1a + Y_TILE_BYTES;
 #pragma unroll
         for (int k = 0; k < BY / 16; ++k) {
-          const uint32_t acol = (k >> 1) * 32 + (k & 1) * 8;  // packed bf16 columns of this K-step
+          const uint32_t acol = k * 16;  // packed bf16 columns of this K-step (written by column group k)
           if (DKV) {
             // dV += P^T dO_i
             umma_ts(tmem_base + 256, tmem_base + b * 64 + acol, make_smem_desc(y2a + k * 2048, Y_CHUNK_BYTES, 1024),
@@ -226,7 +227,7 @@ flash_bwd_kernel(const __grid_constant__ Maps maps, const Params p) {
     }
   } else if (warp >= 4) {
     // ------------------------------ Elementwise + epilogue --------------------
-    const int wg = (warp - 4) >> 2;       // column half: 0 -> [0,32), 1 -> [32,64)
+    const int wg = (warp - 4) >> 2;       // column group: 16 * wg .. +15
     const int quarter = warp & 3;
     const int row_in_tile = quarter * 32 + lane;
     const int x_row = x0 + row_in_tile;
@@ -253,29 +254,60 @@ flash_bwd_kernel(const __grid_constant__ Maps maps, const Params p) {
           }
           if (!mbar_wait(&t_full[b], (i >> 1) & 1, abort_flag, p.status, 90)) { ok = false; break; }
           tc_fence_after_sync();
-          uint32_t t1[32], t2[32];
-          tmem_ld_x32(tmem_base + lane_off + b * 64 + wg * 32, t1);
-          tmem_ld_x32(tmem_base + lane_off + 128 + b * 64 + wg * 32, t2);
+          uint32_t t1[16], t2[16];
+          tmem_ld_x16(tmem_base + lane_off + b * 64 + wg * 16, t1);
+          tmem_ld_x16(tmem_base + lane_off + 128 + b * 64 + wg * 16, t2);
           tmem_wait_ld();
-          uint32_t pp[16], ds[16];
+          uint32_t pp[8], ds[8];
+          const bool full_tile = (valid == BY) && (x0 + BX <= p.x_len);  // uniform over the CTA
+          if (full_tile) {
+            if (DKV) {
+              const float4* lse4 = reinterpret_cast<const float4*>(st + wg * 16);
+              const float4* del4 = reinterpret_cast<const float4*>(st + 64 + wg * 16);
 #pragma unroll
-          for (int c = 0; c < 16; ++c) {
-            float pv[2], dv[2];
+              for (int c4 = 0; c4 < 4; ++c4) {
+                const float4 l = lse4[c4];
+                const float4 d = del4[c4];
+                const float p0 = fast_exp2(__uint_as_float(t1[4 * c4 + 0]) * p.scale_log2 - l.x);
+                const float p1 = fast_exp2(__uint_as_float(t1[4 * c4 + 1]) * p.scale_log2 - l.y);
+                const float p2 = fast_exp2(__uint_as_float(t1[4 * c4 + 2]) * p.scale_log2 - l.z);
+                const float p3 = fast_exp2(__uint_as_float(t1[4 * c4 + 3]) * p.scale_log2 - l.w);
+                pp[2 * c4] = pack_bf16x2(p0, p1);
+                pp[2 * c4 + 1] = pack_bf16x2(p2, p3);
+                ds[2 * c4] = pack_bf16x2(p0 * (__uint_as_float(t2[4 * c4 + 0]) - d.x),
+                                         p1 * (__uint_as_float(t2[4 * c4 + 1]) - d.y));
+                ds[2 * c4 + 1] = pack_bf16x2(p2 * (__uint_as_float(t2[4 * c4 + 2]) - d.z),
+                                             p3 * (__uint_as_float(t2[4 * c4 + 3]) - d.w));
+              }
+            } else {
 #pragma unroll
-            for (int h = 0; h < 2; ++h) {
-              const int col = wg * 32 + 2 * c + h;
-              const float lse = DKV ? st[col] : lse_r;
-              const float del = DKV ? st[64 + col] : delta_r;
-              float pe = fast_exp2(__uint_as_float(t1[2 * c + h]) * p.scale_log2 - lse);
-              if (!row_ok || col >= valid) pe = 0.0f;
-              pv[h] = pe;
-              dv[h] = pe * (__uint_as_float(t2[2 * c + h]) - del);
+              for (int c = 0; c < 8; ++c) {
+                const float p0 = fast_exp2(__uint_as_float(t1[2 * c]) * p.scale_log2 - lse_r);
+                const float p1 = fast_exp2(__uint_as_float(t1[2 * c + 1]) * p.scale_log2 - lse_r);
+                ds[c] = pack_bf16x2(p0 * (__uint_as_float(t2[2 * c]) - delta_r),
+                                    p1 * (__uint_as_float(t2[2 * c + 1]) - delta_r));
+              }
             }
-            pp[c] = pack_bf16x2(pv[0], pv[1]);
-            ds[c] = pack_bf16x2(dv[0], dv[1]);
+          } else {
+#pragma unroll
+            for (int c = 0; c < 8; ++c) {
+              float pv[2], dv[2];
+#pragma unroll
+              for (int h = 0; h < 2; ++h) {
+                const int col = wg * 16 + 2 * c + h;
+                const float lse = DKV ? st[col] : lse_r;
+                const float del = DKV ? st[64 + col] : delta_r;
+                float pe = fast_exp2(__uint_as_float(t1[2 * c + h]) * p.scale_log2 - lse);
+                if (!row_ok || col >= valid) pe = 0.0f;
+                pv[h] = pe;
+                dv[h] = pe * (__uint_as_float(t2[2 * c + h]) - del);
+              }
+              pp[c] = pack_bf16x2(pv[0], pv[1]);
+              ds[c] = pack_bf16x2(dv[0], dv[1]);
+            }
           }
-          if (DKV) tmem_st_x16(tmem_base + lane_off + b * 64 + wg * 32, pp);
-          tmem_st_x16(tmem_base + lane_off + 128 + b * 64 + wg * 32, ds);
+          if (DKV) tmem_st_x8(tmem_base + lane_off + b * 64 + wg * 16, pp);
+          tmem_st_x8(tmem_base + lane_off + 128 + b * 64 + wg * 16, ds);
           tmem_wait_st();
           tc_fence_before_sync();
           mbar_arrive(&ps_full[b]);
@@ -283,7 +315,7 @@ flash_bwd_kernel(const __grid_constant__ Maps maps, const Params p) {
       }
       if (ok && mbar_wait(acc_final, 0, abort_flag, p.status, 91)) {
         tc_fence_after_sync();
-        // each warp group writes 64 of the 128 output columns of every accumulator
+        // each column group writes 32 of the 128 output columns of every accumulator
         const int n_acc = DKV ? 2 : 1;
         for (int a = 0; a < n_acc; ++a) {
           const float mul = (DKV && a == 0) ? 1.0f : p.scale;
@@ -292,8 +324,8 @@ flash_bwd_kernel(const __grid_constant__ Maps maps, const Params p) {
                           sh = a == 0 ? p.o0_sh : p.o1_sh;
           const long long off = batch * sb + static_cast<long long>(x_row) * ss + head * sh;
 #pragma unroll 1
-          for (int c = 0; c < 2; ++c) {
-            const int col0 = wg * 64 + c * 32;
+          for (int c = 0; c < 1; ++c) {
+            const int col0 = wg * 32;
             uint32_t r[32];
             tmem_ld_x32(tmem_base + lane_off + 256 + a * 128 + col0, r);
             tmem_wait_ld();

@@ -236,24 +236,26 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
           const int valid = min(BKV, p.kv_len[seg] - jb * BKV);
           if (!mbar_wait(&s_full[t], j & 1, abort_flag, p.status, 60)) { ok = false; break; }
           tc_fence_after_sync();
-          // pass 1: row maximum
+          // the whole 128-column row of S goes to registers with one wait, so the TMEM latency is paid once
+          uint32_t sv[4][32];
+          tmem_ld_x32(s_addr, sv[0]);
+          tmem_ld_x32(s_addr + 32, sv[1]);
+          tmem_ld_x32(s_addr + 64, sv[2]);
+          tmem_ld_x32(s_addr + 96, sv[3]);
+          tmem_wait_ld();
           float mx = -INFINITY;
-#pragma unroll 1
-          for (int c = 0; c < 4; ++c) {
-            uint32_t r[32];
-            tmem_ld_x32(s_addr + c * 32, r);
-            tmem_wait_ld();
+          if (valid == BKV) {
 #pragma unroll
-            if (valid == BKV) {
+            for (int c = 0; c < 4; ++c)
 #pragma unroll
-              for (int i = 0; i < 32; ++i) mx = fmaxf(mx, __uint_as_float(r[i]));
-            } else {
+              for (int i = 0; i < 32; ++i) mx = fmaxf(mx, __uint_as_float(sv[c][i]));
+          } else {
+#pragma unroll
+            for (int c = 0; c < 4; ++c)
 #pragma unroll
               for (int i = 0; i < 32; ++i) {
-                const float v = (c * 32 + i < valid) ? __uint_as_float(r[i]) : -INFINITY;
-                mx = fmaxf(mx, v);
+                if (c * 32 + i < valid) mx = fmaxf(mx, __uint_as_float(sv[c][i]));
               }
-            }
           }
           const float m_new = fmaxf(m, mx * p.scale_log2);
           if (j == 0) {
@@ -276,23 +278,30 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
               tmem_wait_st();
             }
           }
-          // pass 2: probabilities, written over S as packed bf16
+          // probabilities, written over S as packed bf16
           float rowsum = 0.0f;
-#pragma unroll 1
-          for (int c = 0; c < 4; ++c) {
-            uint32_t r[32];
-            tmem_ld_x32(s_addr + c * 32, r);
-            tmem_wait_ld();
-            uint32_t pk[16];
 #pragma unroll
-            for (int i = 0; i < 16; ++i) {
-              const int col = c * 32 + 2 * i;
-              float p0 = fast_exp2(__uint_as_float(r[2 * i]) * p.scale_log2 - m);
-              float p1 = fast_exp2(__uint_as_float(r[2 * i + 1]) * p.scale_log2 - m);
-              if (col >= valid) p0 = 0.0f;
-              if (col + 1 >= valid) p1 = 0.0f;
-              rowsum += p0 + p1;
-              pk[i] = pack_bf16x2(p0, p1);
+          for (int c = 0; c < 4; ++c) {
+            uint32_t pk[16];
+            if (valid == BKV) {
+#pragma unroll
+              for (int i = 0; i < 16; ++i) {
+                const float p0 = fast_exp2(__uint_as_float(sv[c][2 * i]) * p.scale_log2 - m);
+                const float p1 = fast_exp2(__uint_as_float(sv[c][2 * i + 1]) * p.scale_log2 - m);
+                rowsum += p0 + p1;
+                pk[i] = pack_bf16x2(p0, p1);
+              }
+            } else {
+#pragma unroll
+              for (int i = 0; i < 16; ++i) {
+                const int col = c * 32 + 2 * i;
+                float p0 = fast_exp2(__uint_as_float(sv[c][2 * i]) * p.scale_log2 - m);
+                float p1 = fast_exp2(__uint_as_float(sv[c][2 * i + 1]) * p.scale_log2 - m);
+                if (col >= valid) p0 = 0.0f;
+                if (col + 1 >= valid) p1 = 0.0f;
+                rowsum += p0 + p1;
+                pk[i] = pack_bf16x2(p0, p1);
+              }
             }
             tmem_st_x16(s_addr + c * 16, pk);
           }

@@ -120,7 +120,31 @@ def bench_rowwise(results):
   print(results[-1], flush=True)
 
 
+def profile_case():
+  """One launch of each hot kernel on a mid-size case (inputs larger than L2, < 1 GB resident) for `ncu`."""
+  M, N, Kd = 8192, 5120, 5120
+  a = torch.randn((M, Kd), device="cuda", dtype=torch.bfloat16)
+  b = torch.randn((N, Kd), device="cuda", dtype=torch.bfloat16)
+  K.gemm(a, b)
+  B, H, S = 1, 16, 8192
+  q = torch.randn((B, S, H, 128), device="cuda", dtype=torch.bfloat16)
+  k = torch.randn((B, S, H, 128), device="cuda", dtype=torch.bfloat16)
+  v = torch.randn((B, S, H, 128), device="cuda", dtype=torch.bfloat16)
+  d_o = torch.randn((B, S, H, 128), device="cuda", dtype=torch.bfloat16)
+  out, lse = K.flash_fwd(q, k, v)
+  delta = K.flash_delta(out, d_o)
+  K.flash_bwd_dkv(q, d_o, k, v, lse, delta)
+  K.flash_bwd_dq(q, d_o, k, v, lse, delta)
+  x = torch.randn((1, 32760, 5120), device="cuda", dtype=torch.bfloat16)
+  sc = torch.randn((1, 5120), device="cuda", dtype=torch.float32)
+  K.ln_fwd(x, None, None, sc, sc)
+  torch.cuda.synchronize()
+  print("profile case done")
+
+
 def main(argv):
+  if "profile" in argv:
+    return profile_case()
   which = [a for a in argv if not a.startswith("--")] or ["gemm", "flash", "rowwise"]
   results = []
   if "gemm" in which:
