@@ -1,0 +1,269 @@
+// Peer-memory communication kernels over NVLink / NVSwitch. All pointers named "peer" are device
+// addresses of other GPUs' symmetric buffers mapped into this process; they are accessed with plain
+// loads / stores (and st.release.sys / ld.acquire.sys for flags) — never through a TMA multicast.
+//
+//   signal_peers   : publish an epoch number in a slot of every peer's signal pad
+//   wait_flags     : bounded wait until a set of local signal slots reached an epoch (status on timeout)
+//   set_flag       : stream-ordered release store of one flag (marks a staged segment as ready)
+//   rs_adamw       : fused gradient reduce-scatter + statistics + AdamW. The owner of a parameter slice
+//                    pulls that slice of every rank's gradient buffer, sums the ranks in a fixed order
+//                    (bitwise reproducible), accumulates sum-of-squares / max-abs of the reduced gradient
+//                    and applies AdamW to its slice of weights and moments in the same pass.
+//   peer_copy      : pull copy peer -> local with 16-byte vectors (used where a copy engine is not wanted)
+//
+// rs_adamw replaces NCCL reduce-scatter followed by the optax update of the reference
+// (src/maxdiffusion/trainers/wan_trainer.py:169-189, src/maxdiffusion/max_utils.py:683-696).
+#include "host_common.h"
+
+namespace mdb {
+namespace comm {
+
+constexpr int MAX_RANKS = 16;
+
+struct PeerPtrs {
+  const void* p[MAX_RANKS];
+};
+struct PeerFlagPtrs {
+  unsigned int* p[MAX_RANKS];
+};
+
+__device__ __forceinline__ void st_release_sys(unsigned int* addr, unsigned int v) {
+  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(addr), "r"(v) : "memory");
+}
+__device__ __forceinline__ unsigned int ld_acquire_sys(const unsigned int* addr) {
+  unsigned int v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(addr) : "memory");
+  return v;
+}
+
+__global__ void signal_peers_kernel(PeerFlagPtrs flags, int n, int slot, unsigned int value) {
+  const int i = threadIdx.x;
+  if (i < n && flags.p[i] != nullptr) {
+    __threadfence_system();
+    st_release_sys(flags.p[i] + slot, value);
+  }
+}
+
+// Thread i waits until flags[i * stride] >= target. A wait that runs out of its budget reports
+// {where = 100, detail = i} in the status word; the host turns that into an exception.
+__global__ void wait_flags_kernel(const unsigned int* flags, int n, int stride, unsigned int target,
+                                  unsigned long long budget_ns, DeviceStatus* status) {
+  const int i = threadIdx.x;
+  if (i >= n) return;
+  const uint64_t t0 = global_timer_ns();
+  unsigned int spins = 0;
+  while (ld_acquire_sys(flags + static_cast<long long>(i) * stride) < target) {
+    if ((++spins & 0x3fu) == 0u) {
+      __nanosleep(200);
+      if (global_timer_ns() - t0 > budget_ns) {
+        report_status(status, kStatusFlagTimeout, 100, static_cast<unsigned int>(i));
+        return;
+      }
+    }
+  }
+}
+
+__global__ void set_flag_kernel(unsigned int* flag, unsigned int value) {
+  if (threadIdx.x == 0) {
+    __threadfence_system();
+    st_release_sys(flag, value);
+  }
+}
+
+__global__ void peer_copy_kernel(const uint4* __restrict__ src, uint4* __restrict__ dst, long long nvec) {
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < nvec;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    dst[i] = src[i];
+  }
+}
+
+struct AdamArgs {
+  float lr, b1, b2, eps, wd, bc1, bc2, grad_scale, clip_value;
+  unsigned long long seed;
+  int stochastic;
+};
+
+__device__ __forceinline__ uint32_t hash32(uint64_t x) {
+  x ^= x >> 33; x *= 0xff51afd7ed558ccdULL;
+  x ^= x >> 33; x *= 0xc4ceb9fe1a85ec53ULL;
+  x ^= x >> 33;
+  return static_cast<uint32_t>(x);
+}
+__device__ __forceinline__ __nv_bfloat16 round_bf16(float v, int stochastic, uint64_t key) {
+  if (!stochastic) return __float2bfloat16_rn(v);
+  uint32_t bits = __float_as_uint(v);
+  if ((bits & 0x7f800000u) == 0x7f800000u) return __float2bfloat16_rn(v);
+  bits += hash32(key) & 0xffffu;
+  return __ushort_as_bfloat16(static_cast<unsigned short>(bits >> 16));
+}
+
+template <typename ST> __device__ __forceinline__ float st_to_f(ST v);
+template <> __device__ __forceinline__ float st_to_f<float>(float v) { return v; }
+template <> __device__ __forceinline__ float st_to_f<__nv_bfloat16>(__nv_bfloat16 v) { return __bfloat162float(v); }
+template <typename ST> __device__ __forceinline__ ST f_to_st(float v);
+template <> __device__ __forceinline__ float f_to_st<float>(float v) { return v; }
+template <> __device__ __forceinline__ __nv_bfloat16 f_to_st<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
+
+// grads.p[r] points at rank r's bf16 gradient buffer, already offset to this owner's slice.
+// n is a multiple of 8. partial[block] = {sum g^2, max |g|} of the reduced gradient. When `apply` is 0
+// only the reduced gradient (bf16, to `reduced_out`) and the statistics are produced.
+template <typename ST>
+__global__ void __launch_bounds__(512)
+rs_adamw_kernel(PeerPtrs grads, int world, long long n, __nv_bfloat16* __restrict__ p, ST* __restrict__ m,
+                ST* __restrict__ v, __nv_bfloat16* __restrict__ reduced_out, float2* __restrict__ partial,
+                int apply, AdamArgs a) {
+  float sq = 0.0f, mx = 0.0f;
+  const long long nvec = n >> 3;
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < nvec;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    float g[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) g[j] = 0.0f;
+    uint4 buf[MAX_RANKS];
+#pragma unroll
+    for (int r = 0; r < MAX_RANKS; ++r) {
+      if (r < world) buf[r] = reinterpret_cast<const uint4*>(grads.p[r])[i];
+    }
+#pragma unroll
+    for (int r = 0; r < MAX_RANKS; ++r) {
+      if (r < world) {
+        const uint32_t w[4] = {buf[r].x, buf[r].y, buf[r].z, buf[r].w};
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float2 f = unpack_bf16x2(w[j]);
+          g[2 * j] += f.x;
+          g[2 * j + 1] += f.y;
+        }
+      }
+    }
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      g[j] *= a.grad_scale;
+      sq += g[j] * g[j];
+      mx = fmaxf(mx, fabsf(g[j]));
+    }
+    if (reduced_out != nullptr) {
+      uint4 o;
+      o.x = pack_bf16x2(g[0], g[1]); o.y = pack_bf16x2(g[2], g[3]);
+      o.z = pack_bf16x2(g[4], g[5]); o.w = pack_bf16x2(g[6], g[7]);
+      reinterpret_cast<uint4*>(reduced_out)[i] = o;
+    }
+    if (apply) {
+      const long long e0 = i * 8;
+      const uint4 pw = reinterpret_cast<const uint4*>(p)[i];
+      const uint32_t pwv[4] = {pw.x, pw.y, pw.z, pw.w};
+      float w8[8];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float2 f = unpack_bf16x2(pwv[j]);
+        w8[2 * j] = f.x;
+        w8[2 * j + 1] = f.y;
+      }
+      __nv_bfloat16 outw[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        float gj = g[j];
+        if (a.clip_value > 0.0f) gj = fminf(fmaxf(gj, -a.clip_value), a.clip_value);
+        const float mi = a.b1 * st_to_f<ST>(m[e0 + j]) + (1.0f - a.b1) * gj;
+        const float vi = a.b2 * st_to_f<ST>(v[e0 + j]) + (1.0f - a.b2) * gj * gj;
+        m[e0 + j] = f_to_st<ST>(mi);
+        v[e0 + j] = f_to_st<ST>(vi);
+        float w = w8[j];
+        w -= a.lr * ((mi / a.bc1) / (sqrtf(vi / a.bc2) + a.eps) + a.wd * w);
+        outw[j] = round_bf16(w, a.stochastic, a.seed + static_cast<uint64_t>(e0 + j));
+      }
+      reinterpret_cast<uint4*>(p)[i] = *reinterpret_cast<uint4*>(outw);
+    }
+  }
+  __shared__ float ss[16], sm[16];
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    sq += __shfl_xor_sync(0xffffffffu, sq, o);
+    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+  }
+  if ((threadIdx.x & 31) == 0) { ss[threadIdx.x >> 5] = sq; sm[threadIdx.x >> 5] = mx; }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    float ts = 0.0f, tm = 0.0f;
+    for (int i = 0; i < (blockDim.x >> 5); ++i) { ts += ss[i]; tm = fmaxf(tm, sm[i]); }
+    partial[blockIdx.x] = make_float2(ts, tm);
+  }
+}
+
+__global__ void fold_stats_kernel(const float2* __restrict__ partial, int n, float* __restrict__ out) {
+  if (threadIdx.x == 0 && blockIdx.x == 0) {
+    float ts = 0.0f, tm = 0.0f;
+    for (int i = 0; i < n; ++i) { ts += partial[i].x; tm = fmaxf(tm, partial[i].y); }
+    out[0] += ts;
+    out[1] = fmaxf(out[1], tm);
+  }
+}
+
+}  // namespace comm
+}  // namespace mdb
+
+using namespace mdb;
+using namespace mdb::comm;
+
+extern "C" int mdb_signal_peers(const unsigned long long* peer_flag_ptrs, int n, int slot, unsigned int value,
+                                void* stream) {
+  if (n < 0 || n > MAX_RANKS) return 3401;
+  PeerFlagPtrs f;
+  for (int i = 0; i < MAX_RANKS; ++i) f.p[i] = i < n ? reinterpret_cast<unsigned int*>(peer_flag_ptrs[i]) : nullptr;
+  signal_peers_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(f, n, slot, value);
+  return static_cast<int>(cudaGetLastError());
+}
+
+extern "C" int mdb_wait_flags(const unsigned int* flags, int n, int stride, unsigned int target, double budget_s,
+                              void* stream) {
+  if (n <= 0) return 0;
+  if (n > 32) return 3402;
+  wait_flags_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(
+      flags, n, stride, target, static_cast<unsigned long long>(budget_s * 1e9), status_buffer());
+  return static_cast<int>(cudaGetLastError());
+}
+
+extern "C" int mdb_set_flag(unsigned int* flag, unsigned int value, void* stream) {
+  set_flag_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(flag, value);
+  return static_cast<int>(cudaGetLastError());
+}
+
+extern "C" int mdb_peer_copy(const void* src, void* dst, long long nbytes, int ctas, void* stream) {
+  if (nbytes & 15) return 3403;
+  if (nbytes == 0) return 0;
+  peer_copy_kernel<<<ctas, 512, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const uint4*>(src), static_cast<uint4*>(dst), nbytes >> 4);
+  return static_cast<int>(cudaGetLastError());
+}
+
+// Copy-engine copy between two device addresses of this process (local or peer-mapped); no SM is used.
+extern "C" int mdb_memcpy_async(void* dst, const void* src, long long nbytes, void* stream) {
+  if (nbytes <= 0) return 0;
+  return static_cast<int>(cudaMemcpyAsync(dst, src, static_cast<size_t>(nbytes), cudaMemcpyDeviceToDevice,
+                                          static_cast<cudaStream_t>(stream)));
+}
+
+// grad_ptrs[r]: address of rank r's gradient slice for this owner (bf16, n elements, n % 8 == 0).
+// stats: fp32 [2] accumulated in place; scratch: 2 * ctas floats.
+extern "C" int mdb_rs_adamw(const unsigned long long* grad_ptrs, int world, long long n, void* p, void* m, void* v,
+                            void* reduced_out, float* stats, float* scratch, int apply, float lr, float b1, float b2,
+                            float eps, float wd, float bc1, float bc2, float grad_scale, float clip_value,
+                            unsigned long long seed, int stochastic, int state_f32, int ctas, void* stream) {
+  if (world < 1 || world > MAX_RANKS || (n & 7)) return 3404;
+  if (n == 0) return 0;
+  PeerPtrs g;
+  for (int i = 0; i < MAX_RANKS; ++i) g.p[i] = i < world ? reinterpret_cast<const void*>(grad_ptrs[i]) : nullptr;
+  AdamArgs a{lr, b1, b2, eps, wd, bc1, bc2, grad_scale, clip_value, seed, stochastic};
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  float2* part = reinterpret_cast<float2*>(scratch);
+  if (state_f32)
+    rs_adamw_kernel<float><<<ctas, 512, 0, st>>>(g, world, n, static_cast<__nv_bfloat16*>(p), static_cast<float*>(m),
+                                                 static_cast<float*>(v), static_cast<__nv_bfloat16*>(reduced_out), part,
+                                                 apply, a);
+  else
+    rs_adamw_kernel<__nv_bfloat16><<<ctas, 512, 0, st>>>(
+        g, world, n, static_cast<__nv_bfloat16*>(p), static_cast<__nv_bfloat16*>(m), static_cast<__nv_bfloat16*>(v),
+        static_cast<__nv_bfloat16*>(reduced_out), part, apply, a);
+  fold_stats_kernel<<<1, 32, 0, st>>>(part, ctas, stats);
+  return static_cast<int>(cudaGetLastError());
+}

@@ -11,6 +11,14 @@
 // A segment can be guarded by a ready flag in global memory that the loader warp waits on
 // (bounded) before its first TMA load of that segment.
 //
+// The kernel is persistent: at most one CTA per SM, each compute CTA walks a static list of
+// (q-block, head, batch) tiles. When the K/V segments of other ranks have to be fetched (ring /
+// context-parallel attention) the last `n_copy` CTAs of the same launch are copy CTAs: they wait for
+// the owner's epoch flag, pull its K/V shard over NVLink with 16-byte loads into this GPU's staging
+// buffer, and raise the segment's ready flag; afterwards they acknowledge to the owners. Transfer and
+// math therefore overlap segment by segment inside ONE kernel whose CTAs are all co-resident, and no
+// remote tile crosses NVLink more than once.
+//
 // Layout: q, k, v, o are [B, S, H, 128] bf16 with arbitrary (16-byte aligned) strides for
 // B, S, H, so the [B, S, H*D] projections are consumed without a transpose.
 // Ragged tails: rows >= q_len are not stored, keys >= kv_len of a segment are masked.
@@ -19,6 +27,8 @@
 // (src/maxdiffusion/kernels/custom_splash_attention.py:69-320) and the per-hop ring variant
 // (:568-685) plus the online-softmax merge around it
 // (src/maxdiffusion/kernels/splash_attention/ring_attention_kernel.py:1099-1131).
+#include <string.h>
+
 #include "host_common.h"
 
 namespace mdb {
@@ -38,6 +48,23 @@ constexpr float kRescaleThreshold = 8.0f;
 struct KVMaps {
   CUtensorMap k[MAX_SEGMENTS];
   CUtensorMap v[MAX_SEGMENTS];
+};
+
+constexpr int MAX_REMOTE = MAX_SEGMENTS - 1;
+
+// Work of the copy CTAs: remote segment i (KV segment 1 + i of the launch) is pulled from src to dst.
+struct CopyPlan {
+  int n_remote;                         // 0: no copy CTAs
+  int n_copy_ctas;
+  const uint4* src[MAX_REMOTE][2];      // peer addresses of K and V
+  uint4* dst[MAX_REMOTE][2];            // local staging
+  long long nvec;                       // 16-byte vectors per tensor
+  const unsigned int* ready[MAX_REMOTE];  // local signal-pad slot the owner raises
+  unsigned int epoch;
+  unsigned int* counters;               // [MAX_SEGMENTS], zero at launch
+  unsigned int* seg_flags;              // flag 1 + i is raised once segment i is staged
+  unsigned int* ack[MAX_SEGMENTS];      // peers' pad slots to acknowledge into (n_ack entries)
+  int n_ack;
 };
 
 struct Params {
@@ -72,8 +99,76 @@ __device__ __forceinline__ bool wait_flag(const unsigned int* flag, unsigned int
   }
 }
 
+__device__ __forceinline__ void copy_cta(const CopyPlan& cp, int ci, DeviceStatus* status) {
+  __shared__ int ok_s;
+  for (int i = 0; i < cp.n_remote; ++i) {
+    if (threadIdx.x == 0) {
+      int ok = 1;
+      const uint64_t t0 = global_timer_ns();
+      unsigned int spins = 0;
+      while (true) {
+        unsigned int v;
+        asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(cp.ready[i]) : "memory");
+        if (v >= cp.epoch) break;
+        if ((++spins & 0xffu) == 0u && global_timer_ns() - t0 > kWaitBudgetNs) {
+          report_status(status, kStatusFlagTimeout, 45, static_cast<unsigned int>(i));
+          ok = 0;
+          break;
+        }
+      }
+      ok_s = ok;
+    }
+    __syncthreads();
+    if (!ok_s) return;
+    const long long per = (cp.nvec + cp.n_copy_ctas - 1) / cp.n_copy_ctas;
+    const long long begin = static_cast<long long>(ci) * per;
+    const long long end = begin + per < cp.nvec ? begin + per : cp.nvec;
+    for (int t = 0; t < 2; ++t) {
+      const uint4* src = cp.src[i][t];
+      uint4* dst = cp.dst[i][t];
+      long long v = begin + threadIdx.x;
+      // 8 independent 16-byte loads in flight per thread; peer data bypasses L1 (the addresses are reused)
+      for (; v + 7 * NUM_THREADS < end; v += 8 * NUM_THREADS) {
+        uint4 r[8];
+#pragma unroll
+        for (int u = 0; u < 8; ++u) r[u] = __ldcg(src + v + u * NUM_THREADS);
+#pragma unroll
+        for (int u = 0; u < 8; ++u) dst[v + u * NUM_THREADS] = r[u];
+      }
+      for (; v < end; v += NUM_THREADS) dst[v] = __ldcg(src + v);
+    }
+    asm volatile("fence.proxy.async.global;" ::: "memory");  // staged data is read back through TMA
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      const unsigned int old = atomicAdd(cp.counters + i, 1u);
+      if (old == static_cast<unsigned int>(cp.n_copy_ctas - 1)) {
+        __threadfence();
+        asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(cp.seg_flags + 1 + i), "r"(cp.epoch) : "memory");
+      }
+    }
+  }
+  if (threadIdx.x == 0) {
+    const unsigned int old = atomicAdd(cp.counters + MAX_REMOTE, 1u);
+    if (old == static_cast<unsigned int>(cp.n_copy_ctas - 1)) {
+      // every remote shard has been read: tell the owners that their buffer may be overwritten
+      for (int a = 0; a < cp.n_ack; ++a) {
+        asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(cp.ack[a]), "r"(cp.epoch) : "memory");
+      }
+    }
+  }
+}
+
 __global__ void __launch_bounds__(NUM_THREADS, 1)
-flash_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ KVMaps maps, const Params p) {
+flash_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ KVMaps maps, const Params p,
+                 const __grid_constant__ CopyPlan cp) {
+  const int n_copy = cp.n_remote > 0 ? cp.n_copy_ctas : 0;
+  const int n_compute = static_cast<int>(gridDim.x) - n_copy;
+  if (static_cast<int>(blockIdx.x) >= n_compute) {
+    copy_cta(cp, static_cast<int>(blockIdx.x) - n_compute, p.status);
+    return;
+  }
+
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* sq = smem;                                  // [2 tiles][2 chunks][128][128 B]
@@ -88,21 +183,21 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
   uint64_t* s_full = bars + 9;        // [2] per q tile
   uint64_t* p_full = bars + 11;       // [2] per q tile
   uint64_t* o_final = bars + 13;      // [2] per q tile
-  uint32_t* tmem_ptr_smem = reinterpret_cast<uint32_t*>(bars + 15);
+  uint64_t* q_empty = bars + 15;      // [1]
+  uint32_t* tmem_ptr_smem = reinterpret_cast<uint32_t*>(bars + 16);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_ptr_smem + 1);
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
-  const int q0 = blockIdx.x * 2 * BQ;
-  const int head = blockIdx.y;
-  const int batch = blockIdx.z;
-  const int n_tiles = (p.q_len - q0 > BQ) ? 2 : 1;
+  const int n_qb = (p.q_len + 2 * BQ - 1) / (2 * BQ);
+  const int total_work = n_qb * p.H * p.B;
 
   int total_blocks = 0;
   for (int s = 0; s < p.num_segments; ++s) total_blocks += (p.kv_len[s] + BKV - 1) / BKV;
 
   if (threadIdx.x == 0) {
     mbar_init(q_full, 1);
+    mbar_init(q_empty, 1);
     for (int i = 0; i < 2; ++i) {
       mbar_init(&k_full[i], 1);
       mbar_init(&k_empty[i], 1);
@@ -129,34 +224,46 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
   if (warp == 0) {
     // ------------------------------ TMA producer ------------------------------
     if (lane == 0 && total_blocks > 0) {
-      mbar_expect_tx(q_full, n_tiles * TILE_BYTES);
-      for (int t = 0; t < n_tiles; ++t) {
-        for (int c = 0; c < 2; ++c) {
-          tma_load_4d(sq + t * TILE_BYTES + c * CHUNK_BYTES, &tmap_q, q_full, c * 64, head, q0 + t * BQ, batch);
-        }
-      }
       int stage = 0;
       uint32_t phase = 0;
+      uint32_t seen = 0;  // segments whose ready flag has been observed
       bool ok = true;
-      for (int seg = 0; seg < p.num_segments && ok; ++seg) {
-        const int nblk = (p.kv_len[seg] + BKV - 1) / BKV;
-        if (nblk > 0 && p.seg_flags != nullptr) {
-          if (!wait_flag(p.seg_flags + seg, p.flag_target, abort_flag, p.status, seg)) { ok = false; break; }
+      int it = 0;
+      for (int work = blockIdx.x; work < total_work && ok; work += n_compute, ++it) {
+        const int qb = work % n_qb;
+        const int head = (work / n_qb) % p.H;
+        const int batch = work / (n_qb * p.H);
+        const int q0 = qb * 2 * BQ;
+        const int n_tiles = (p.q_len - q0 > BQ) ? 2 : 1;
+        if (!mbar_wait(q_empty, (it & 1) ^ 1u, abort_flag, p.status, 43)) { ok = false; break; }
+        mbar_expect_tx(q_full, n_tiles * TILE_BYTES);
+        for (int t = 0; t < n_tiles; ++t) {
+          for (int c = 0; c < 2; ++c) {
+            tma_load_4d(sq + t * TILE_BYTES + c * CHUNK_BYTES, &tmap_q, q_full, c * 64, head, q0 + t * BQ, batch);
+          }
         }
-        for (int jb = 0; jb < nblk; ++jb) {
-          if (!mbar_wait(&k_empty[stage], phase ^ 1u, abort_flag, p.status, 41)) { ok = false; break; }
-          mbar_expect_tx(&k_full[stage], TILE_BYTES);
-          for (int c = 0; c < 2; ++c) {
-            tma_load_4d(sk + stage * TILE_BYTES + c * CHUNK_BYTES, &maps.k[seg], &k_full[stage], c * 64, head,
-                        jb * BKV, batch);
+        for (int seg = 0; seg < p.num_segments && ok; ++seg) {
+          const int nblk = (p.kv_len[seg] + BKV - 1) / BKV;
+          if (nblk > 0 && p.seg_flags != nullptr && !((seen >> seg) & 1u)) {
+            if (!wait_flag(p.seg_flags + seg, p.flag_target, abort_flag, p.status, seg)) { ok = false; break; }
+            asm volatile("fence.proxy.async.global;" ::: "memory");
+            seen |= 1u << seg;
           }
-          if (!mbar_wait(&v_empty[stage], phase ^ 1u, abort_flag, p.status, 42)) { ok = false; break; }
-          mbar_expect_tx(&v_full[stage], TILE_BYTES);
-          for (int c = 0; c < 2; ++c) {
-            tma_load_4d(sv + stage * TILE_BYTES + c * CHUNK_BYTES, &maps.v[seg], &v_full[stage], c * 64, head,
-                        jb * BKV, batch);
+          for (int jb = 0; jb < nblk; ++jb) {
+            if (!mbar_wait(&k_empty[stage], phase ^ 1u, abort_flag, p.status, 41)) { ok = false; break; }
+            mbar_expect_tx(&k_full[stage], TILE_BYTES);
+            for (int c = 0; c < 2; ++c) {
+              tma_load_4d(sk + stage * TILE_BYTES + c * CHUNK_BYTES, &maps.k[seg], &k_full[stage], c * 64, head,
+                          jb * BKV, batch);
+            }
+            if (!mbar_wait(&v_empty[stage], phase ^ 1u, abort_flag, p.status, 42)) { ok = false; break; }
+            mbar_expect_tx(&v_full[stage], TILE_BYTES);
+            for (int c = 0; c < 2; ++c) {
+              tma_load_4d(sv + stage * TILE_BYTES + c * CHUNK_BYTES, &maps.v[seg], &v_full[stage], c * 64, head,
+                          jb * BKV, batch);
+            }
+            if (++stage == KV_STAGES) { stage = 0; phase ^= 1u; }
           }
-          if (++stage == KV_STAGES) { stage = 0; phase ^= 1u; }
         }
       }
     }
@@ -165,8 +272,6 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
     if (lane == 0 && total_blocks > 0) {
       constexpr uint32_t idesc_s = make_idesc_bf16(128, 128, false, false);
       constexpr uint32_t idesc_pv = make_idesc_bf16(128, 128, false, true);
-      bool ok = mbar_wait(q_full, 0, abort_flag, p.status, 50);
-      tc_fence_after_sync();
       auto issue_s = [&](int t, int stage) {
         const uint32_t qa = smem_u32(sq + t * TILE_BYTES);
         const uint32_t ka = smem_u32(sk + stage * TILE_BYTES);
@@ -178,43 +283,55 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
         }
         umma_commit(&s_full[t]);
       };
-      if (ok) ok = mbar_wait(&k_full[0], 0, abort_flag, p.status, 51);
-      if (ok) {
-        tc_fence_after_sync();
-        for (int t = 0; t < n_tiles; ++t) issue_s(t, 0);
-        umma_commit(&k_empty[0]);  // K block 0 is free once both S MMAs have read it
-      }
       int stage = 0;
       uint32_t phase = 0;
-      for (int j = 0; j < total_blocks && ok; ++j) {
-        const int nstage = (stage + 1 == KV_STAGES) ? 0 : stage + 1;
-        const uint32_t nphase = (stage + 1 == KV_STAGES) ? (phase ^ 1u) : phase;
-        if (!mbar_wait(&v_full[stage], phase, abort_flag, p.status, 52)) { ok = false; break; }
+      uint32_t pc[2] = {0u, 0u};  // blocks consumed per q-tile slot (parity of p_full)
+      bool ok = true;
+      int it = 0;
+      for (int work = blockIdx.x; work < total_work && ok; work += n_compute, ++it) {
+        const int q0 = (work % n_qb) * 2 * BQ;
+        const int n_tiles = (p.q_len - q0 > BQ) ? 2 : 1;
+        if (!mbar_wait(q_full, it & 1, abort_flag, p.status, 50)) { ok = false; break; }
+        if (!mbar_wait(&k_full[stage], phase, abort_flag, p.status, 51)) { ok = false; break; }
         tc_fence_after_sync();
-        const uint32_t va = smem_u32(sv + stage * TILE_BYTES);
-        for (int t = 0; t < n_tiles && ok; ++t) {
-          if (!mbar_wait(&p_full[t], j & 1, abort_flag, p.status, 53)) { ok = false; break; }
+        for (int t = 0; t < n_tiles; ++t) issue_s(t, stage);
+        umma_commit(&k_empty[stage]);  // this K block is free once the S MMAs have read it
+        if (total_blocks == 1) umma_commit(q_empty);
+        for (int j = 0; j < total_blocks && ok; ++j) {
+          const int nstage = (stage + 1 == KV_STAGES) ? 0 : stage + 1;
+          const uint32_t nphase = (stage + 1 == KV_STAGES) ? (phase ^ 1u) : phase;
+          if (!mbar_wait(&v_full[stage], phase, abort_flag, p.status, 52)) { ok = false; break; }
           tc_fence_after_sync();
+          const uint32_t va = smem_u32(sv + stage * TILE_BYTES);
+          for (int t = 0; t < n_tiles && ok; ++t) {
+            if (!mbar_wait(&p_full[t], pc[t] & 1u, abort_flag, p.status, 53)) { ok = false; break; }
+            ++pc[t];
+            tc_fence_after_sync();
 #pragma unroll
-          for (int k = 0; k < BKV / 16; ++k) {
-            umma_ts(tmem_base + 256 + t * 128, tmem_base + t * 128 + k * 8,
-                    make_smem_desc(va + k * 2048, CHUNK_BYTES, 1024), idesc_pv, (j > 0 || k > 0) ? 1u : 0u);
-          }
-          if (j + 1 < total_blocks) {
-            if (t == 0) {
-              if (!mbar_wait(&k_full[nstage], nphase, abort_flag, p.status, 54)) { ok = false; break; }
-              tc_fence_after_sync();
+            for (int k = 0; k < BKV / 16; ++k) {
+              umma_ts(tmem_base + 256 + t * 128, tmem_base + t * 128 + k * 8,
+                      make_smem_desc(va + k * 2048, CHUNK_BYTES, 1024), idesc_pv, (j > 0 || k > 0) ? 1u : 0u);
             }
-            issue_s(t, nstage);
-            if (t == n_tiles - 1) umma_commit(&k_empty[nstage]);
-          } else {
-            umma_commit(&o_final[t]);
+            if (j + 1 < total_blocks) {
+              if (t == 0) {
+                if (!mbar_wait(&k_full[nstage], nphase, abort_flag, p.status, 54)) { ok = false; break; }
+                tc_fence_after_sync();
+              }
+              issue_s(t, nstage);
+              if (t == n_tiles - 1) {
+                umma_commit(&k_empty[nstage]);
+                // the S MMAs of the last block are the last readers of the Q tiles: free them for the next work item
+                if (j + 2 == total_blocks) umma_commit(q_empty);
+              }
+            } else {
+              umma_commit(&o_final[t]);
+            }
           }
+          if (!ok) break;
+          umma_commit(&v_empty[stage]);
+          stage = nstage;
+          phase = nphase;
         }
-        if (!ok) break;
-        umma_commit(&v_empty[stage]);
-        stage = nstage;
-        phase = nphase;
       }
     }
   } else if (warp >= 4) {
@@ -222,39 +339,47 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
     const int t = (warp - 4) >> 2;         // q tile of this warp group
     const int quarter = warp & 3;          // TMEM lanes 32*quarter..+31
     const int row_in_tile = quarter * 32 + lane;
-    const int q_row = q0 + t * BQ + row_in_tile;
-    if (t < n_tiles && total_blocks > 0) {
-      const uint32_t lane_off = static_cast<uint32_t>(quarter * 32) << 16;
-      const uint32_t s_addr = tmem_base + lane_off + t * 128;
-      const uint32_t o_addr = tmem_base + lane_off + 256 + t * 128;
+    const uint32_t lane_off = static_cast<uint32_t>(quarter * 32) << 16;
+    const uint32_t s_addr = tmem_base + lane_off + t * 128;
+    const uint32_t o_addr = tmem_base + lane_off + 256 + t * 128;
+    uint32_t sc = 0, oc = 0;  // parities of s_full / o_final for this slot
+    bool ok = total_blocks > 0;
+    for (int work = blockIdx.x; work < total_work && ok; work += n_compute) {
+      const int qb = work % n_qb;
+      const int head = (work / n_qb) % p.H;
+      const int batch = work / (n_qb * p.H);
+      const int q0 = qb * 2 * BQ;
+      const int n_tiles = (p.q_len - q0 > BQ) ? 2 : 1;
+      if (t >= n_tiles) continue;
+      const int q_row = q0 + t * BQ + row_in_tile;
       float m = -INFINITY, l = 0.0f;
-      bool ok = true;
       int j = 0;
       for (int seg = 0; seg < p.num_segments && ok; ++seg) {
         const int nblk = (p.kv_len[seg] + BKV - 1) / BKV;
         for (int jb = 0; jb < nblk; ++jb, ++j) {
           const int valid = min(BKV, p.kv_len[seg] - jb * BKV);
-          if (!mbar_wait(&s_full[t], j & 1, abort_flag, p.status, 60)) { ok = false; break; }
+          if (!mbar_wait(&s_full[t], sc & 1u, abort_flag, p.status, 60)) { ok = false; break; }
+          ++sc;
           tc_fence_after_sync();
           // the whole 128-column row of S goes to registers with one wait, so the TMEM latency is paid once
-          uint32_t sv[4][32];
-          tmem_ld_x32(s_addr, sv[0]);
-          tmem_ld_x32(s_addr + 32, sv[1]);
-          tmem_ld_x32(s_addr + 64, sv[2]);
-          tmem_ld_x32(s_addr + 96, sv[3]);
+          uint32_t sv4[4][32];
+          tmem_ld_x32(s_addr, sv4[0]);
+          tmem_ld_x32(s_addr + 32, sv4[1]);
+          tmem_ld_x32(s_addr + 64, sv4[2]);
+          tmem_ld_x32(s_addr + 96, sv4[3]);
           tmem_wait_ld();
           float mx = -INFINITY;
           if (valid == BKV) {
 #pragma unroll
             for (int c = 0; c < 4; ++c)
 #pragma unroll
-              for (int i = 0; i < 32; ++i) mx = fmaxf(mx, __uint_as_float(sv[c][i]));
+              for (int i = 0; i < 32; ++i) mx = fmaxf(mx, __uint_as_float(sv4[c][i]));
           } else {
 #pragma unroll
             for (int c = 0; c < 4; ++c)
 #pragma unroll
               for (int i = 0; i < 32; ++i) {
-                if (c * 32 + i < valid) mx = fmaxf(mx, __uint_as_float(sv[c][i]));
+                if (c * 32 + i < valid) mx = fmaxf(mx, __uint_as_float(sv4[c][i]));
               }
           }
           const float m_new = fmaxf(m, mx * p.scale_log2);
@@ -286,8 +411,8 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
             if (valid == BKV) {
 #pragma unroll
               for (int i = 0; i < 16; ++i) {
-                const float p0 = fast_exp2(__uint_as_float(sv[c][2 * i]) * p.scale_log2 - m);
-                const float p1 = fast_exp2(__uint_as_float(sv[c][2 * i + 1]) * p.scale_log2 - m);
+                const float p0 = fast_exp2(__uint_as_float(sv4[c][2 * i]) * p.scale_log2 - m);
+                const float p1 = fast_exp2(__uint_as_float(sv4[c][2 * i + 1]) * p.scale_log2 - m);
                 rowsum += p0 + p1;
                 pk[i] = pack_bf16x2(p0, p1);
               }
@@ -295,8 +420,8 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
 #pragma unroll
               for (int i = 0; i < 16; ++i) {
                 const int col = c * 32 + 2 * i;
-                float p0 = fast_exp2(__uint_as_float(sv[c][2 * i]) * p.scale_log2 - m);
-                float p1 = fast_exp2(__uint_as_float(sv[c][2 * i + 1]) * p.scale_log2 - m);
+                float p0 = fast_exp2(__uint_as_float(sv4[c][2 * i]) * p.scale_log2 - m);
+                float p1 = fast_exp2(__uint_as_float(sv4[c][2 * i + 1]) * p.scale_log2 - m);
                 if (col >= valid) p0 = 0.0f;
                 if (col + 1 >= valid) p1 = 0.0f;
                 rowsum += p0 + p1;
@@ -311,33 +436,36 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
           mbar_arrive(&p_full[t]);
         }
       }
-      if (ok && mbar_wait(&o_final[t], 0, abort_flag, p.status, 61)) {
-        tc_fence_after_sync();
-        const float inv = (l > 0.0f) ? 1.0f / l : 0.0f;
-        const bool row_ok = q_row < p.q_len;
-        __nv_bfloat16* orow = p.out + batch * p.o_stride_b + static_cast<long long>(q_row) * p.o_stride_s +
-                              head * p.o_stride_h;
+      if (!ok) break;
+      if (!mbar_wait(&o_final[t], oc & 1u, abort_flag, p.status, 61)) { ok = false; break; }
+      ++oc;
+      tc_fence_after_sync();
+      const float inv = (l > 0.0f) ? 1.0f / l : 0.0f;
+      const bool row_ok = q_row < p.q_len;
+      __nv_bfloat16* orow = p.out + batch * p.o_stride_b + static_cast<long long>(q_row) * p.o_stride_s +
+                            head * p.o_stride_h;
 #pragma unroll 1
-        for (int c = 0; c < 4; ++c) {
-          uint32_t r[32];
-          tmem_ld_x32(o_addr + c * 32, r);
-          tmem_wait_ld();
-          if (row_ok) {
+      for (int c = 0; c < 4; ++c) {
+        uint32_t r[32];
+        tmem_ld_x32(o_addr + c * 32, r);
+        tmem_wait_ld();
+        if (row_ok) {
 #pragma unroll
-            for (int v = 0; v < 4; ++v) {
-              uint4 ov;
-              ov.x = pack_bf16x2(__uint_as_float(r[v * 8 + 0]) * inv, __uint_as_float(r[v * 8 + 1]) * inv);
-              ov.y = pack_bf16x2(__uint_as_float(r[v * 8 + 2]) * inv, __uint_as_float(r[v * 8 + 3]) * inv);
-              ov.z = pack_bf16x2(__uint_as_float(r[v * 8 + 4]) * inv, __uint_as_float(r[v * 8 + 5]) * inv);
-              ov.w = pack_bf16x2(__uint_as_float(r[v * 8 + 6]) * inv, __uint_as_float(r[v * 8 + 7]) * inv);
-              *reinterpret_cast<uint4*>(orow + c * 32 + v * 8) = ov;
-            }
+          for (int v = 0; v < 4; ++v) {
+            uint4 ov;
+            ov.x = pack_bf16x2(__uint_as_float(r[v * 8 + 0]) * inv, __uint_as_float(r[v * 8 + 1]) * inv);
+            ov.y = pack_bf16x2(__uint_as_float(r[v * 8 + 2]) * inv, __uint_as_float(r[v * 8 + 3]) * inv);
+            ov.z = pack_bf16x2(__uint_as_float(r[v * 8 + 4]) * inv, __uint_as_float(r[v * 8 + 5]) * inv);
+            ov.w = pack_bf16x2(__uint_as_float(r[v * 8 + 6]) * inv, __uint_as_float(r[v * 8 + 7]) * inv);
+            *reinterpret_cast<uint4*>(orow + c * 32 + v * 8) = ov;
           }
         }
-        if (row_ok && p.lse != nullptr) {
-          p.lse[(static_cast<long long>(batch) * p.H + head) * p.q_len + q_row] = m + log2f(l);
-        }
       }
+      if (row_ok && p.lse != nullptr) {
+        p.lse[(static_cast<long long>(batch) * p.H + head) * p.q_len + q_row] = m + log2f(l);
+      }
+      // the next tile's first P*V overwrites O only after this warp group has arrived on p_full again
+      tc_fence_before_sync();
     }
   }
 
@@ -361,15 +489,31 @@ static int make_map(CUtensorMap* map, const void* ptr, int B, int S, int H, long
 }  // namespace fa
 }  // namespace mdb
 
+// Host-side description of the copy CTAs' work (all addresses as integers); see CopyPlan.
+struct MdbCopyPlan {
+  int n_remote;
+  int n_copy_ctas;
+  unsigned long long src[7][2];
+  unsigned long long dst[7][2];
+  long long nbytes;                 // per tensor, multiple of 16
+  unsigned long long ready[7];
+  unsigned int epoch;
+  unsigned long long counters;      // device uint32[8], zero at launch
+  unsigned long long seg_flags;     // device uint32[num_segments]
+  unsigned long long ack[8];
+  int n_ack;
+};
+
 // q: [B, q_len, H, 128]; k/v segment s: [B, kv_len[s], H, 128]; out like q. Strides are in elements
 // (batch, sequence, head); the head_dim stride is 1. Every segment shares the k strides / v strides
-// given here. Returns 0 or an error code.
+// given here. `plan` (may be null) adds copy CTAs that stage the remote segments 1.. from peer memory.
+// Returns 0 or an error code.
 extern "C" int mdb_flash_fwd(const void* q, const void* const* k_ptrs, const void* const* v_ptrs, void* out,
                              float* lse, int B, int H, int q_len, int num_segments, const int* kv_lens,
                              long long q_sb, long long q_ss, long long q_sh, long long k_sb, long long k_ss,
                              long long k_sh, long long v_sb, long long v_ss, long long v_sh, long long o_sb,
                              long long o_ss, long long o_sh, float softmax_scale, const unsigned int* seg_flags,
-                             unsigned int flag_target, void* stream_ptr) {
+                             unsigned int flag_target, const MdbCopyPlan* plan, void* stream_ptr) {
   using namespace mdb;
   using namespace mdb::fa;
   if (B <= 0 || H <= 0 || q_len <= 0) return 0;
@@ -398,12 +542,39 @@ extern "C" int mdb_flash_fwd(const void* q, const void* const* k_ptrs, const voi
   p.seg_flags = seg_flags;
   p.flag_target = flag_target;
   p.status = status_buffer();
+  CopyPlan cp;
+  memset(&cp, 0, sizeof(cp));
+  if (plan != nullptr && plan->n_remote > 0) {
+    if (plan->n_remote > MAX_REMOTE || plan->n_remote != num_segments - 1 || (plan->nbytes & 15) ||
+        plan->n_copy_ctas < 1 || plan->n_ack > MAX_SEGMENTS || seg_flags == nullptr)
+      return 3103;
+    cp.n_remote = plan->n_remote;
+    cp.n_copy_ctas = plan->n_copy_ctas;
+    for (int i = 0; i < plan->n_remote; ++i) {
+      for (int t = 0; t < 2; ++t) {
+        cp.src[i][t] = reinterpret_cast<const uint4*>(plan->src[i][t]);
+        cp.dst[i][t] = reinterpret_cast<uint4*>(plan->dst[i][t]);
+      }
+      cp.ready[i] = reinterpret_cast<const unsigned int*>(plan->ready[i]);
+    }
+    cp.nvec = plan->nbytes >> 4;
+    cp.epoch = plan->epoch;
+    cp.counters = reinterpret_cast<unsigned int*>(plan->counters);
+    cp.seg_flags = reinterpret_cast<unsigned int*>(plan->seg_flags);
+    cp.n_ack = plan->n_ack;
+    for (int a = 0; a < plan->n_ack; ++a) cp.ack[a] = reinterpret_cast<unsigned int*>(plan->ack[a]);
+  }
   static bool configured = false;
   if (!configured) {
     MDB_CHECK_CUDA(cudaFuncSetAttribute(flash_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
     configured = true;
   }
-  dim3 grid((q_len + 2 * BQ - 1) / (2 * BQ), H, B);
-  flash_fwd_kernel<<<grid, NUM_THREADS, SMEM_BYTES, static_cast<cudaStream_t>(stream_ptr)>>>(tq, maps, p);
+  const int n_qb = (q_len + 2 * BQ - 1) / (2 * BQ);
+  const long long total_work = static_cast<long long>(n_qb) * H * B;
+  const int n_copy = cp.n_remote > 0 ? cp.n_copy_ctas : 0;
+  int n_compute = sm_count() - n_copy;
+  if (n_compute < 1) return 3104;
+  if (total_work < n_compute) n_compute = static_cast<int>(total_work);
+  flash_fwd_kernel<<<n_compute + n_copy, NUM_THREADS, SMEM_BYTES, static_cast<cudaStream_t>(stream_ptr)>>>(tq, maps, p, cp);
   return static_cast<int>(cudaGetLastError());
 }

@@ -25,6 +25,15 @@ class KernelError(RuntimeError):
   pass
 
 
+class CopyPlan(ctypes.Structure):
+  """Work list of the copy CTAs of `mdb_flash_fwd` (mirrors `MdbCopyPlan` in csrc/flash_fwd.cu)."""
+  _fields_ = [("n_remote", ctypes.c_int), ("n_copy_ctas", ctypes.c_int),
+              ("src", (ctypes.c_ulonglong * 2) * 7), ("dst", (ctypes.c_ulonglong * 2) * 7),
+              ("nbytes", ctypes.c_longlong), ("ready", ctypes.c_ulonglong * 7), ("epoch", ctypes.c_uint),
+              ("counters", ctypes.c_ulonglong), ("seg_flags", ctypes.c_ulonglong), ("ack", ctypes.c_ulonglong * 8),
+              ("n_ack", ctypes.c_int)]
+
+
 def lib() -> ctypes.CDLL:
   global _LIB
   if _LIB is not None:
@@ -98,7 +107,7 @@ def _declare(L: ctypes.CDLL) -> None:
   L.mdb_gemm_bf16.restype = c_int
   L.mdb_flash_fwd.argtypes = ([c_void_p, ctypes.POINTER(c_void_p), ctypes.POINTER(c_void_p), c_void_p, c_void_p]
                               + [c_int] * 4 + [ctypes.POINTER(c_int)] + [c_ll] * 12 + [c_float, c_void_p, ctypes.c_uint,
-                                                                                      c_void_p])
+                                                                                      c_void_p, c_void_p])
   L.mdb_flash_fwd.restype = c_int
   L.mdb_ln_fwd.argtypes = [c_void_p] * 6 + [c_ll, c_int, c_int, c_int, c_float, c_void_p, c_void_p, c_int, c_void_p]
   L.mdb_ln_fwd.restype = c_int
@@ -134,10 +143,16 @@ def _declare(L: ctypes.CDLL) -> None:
                                   c_void_p, c_void_p] + [c_int] * 4 + [ctypes.POINTER(c_int)] + [c_llp] * 5 +
                                  [c_float, c_int, c_void_p])
   L.mdb_flash_bwd_dq.restype = c_int
-  for name, fn in _OPTIONAL.items():
-    if hasattr(L, name):
-      fn(L)
+  for fn in _EXTRA:
+    fn(L)
 
 
-# symbols added by later kernels register their signatures here
-_OPTIONAL: dict = {}
+# modules that own further entry points register a declarer here
+_EXTRA: list = []
+
+
+def register(declare_fn) -> None:
+  """Registers a function that sets argtypes/restype of more entry points; applied now if the library is loaded."""
+  _EXTRA.append(declare_fn)
+  if _LIB is not None:
+    declare_fn(_LIB)

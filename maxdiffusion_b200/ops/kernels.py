@@ -54,8 +54,11 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = F
 
 
 def flash_fwd(q: torch.Tensor, k_list: Sequence[torch.Tensor], v_list: Sequence[torch.Tensor], scale: float | None = None,
-              return_lse: bool = True, seg_flags: torch.Tensor | None = None, flag_target: int = 0):
-  """Flash attention forward over KV segments. q: [B,Sq,H,128]; k/v: lists of [B,Skv_i,H,128] sharing strides."""
+              return_lse: bool = True, seg_flags: torch.Tensor | None = None, flag_target: int = 0, plan=None):
+  """Flash attention forward over KV segments. q: [B,Sq,H,128]; k/v: lists of [B,Skv_i,H,128] sharing strides.
+
+  `seg_flags` gates segment i on flags[i] >= flag_target; `plan` (an `_lib.CopyPlan`) adds copy CTAs that stage
+  the remote segments from peer memory inside the same launch."""
   if isinstance(k_list, torch.Tensor):
     k_list, v_list = [k_list], [v_list]
   B, Sq, H, D = q.shape
@@ -75,7 +78,8 @@ def flash_fwd(q: torch.Tensor, k_list: Sequence[torch.Tensor], v_list: Sequence[
       _lib.ptr(q), kp, vp, _lib.ptr(out), _lib.ptr(lse), B, H, Sq, n, lens,
       q.stride(0), q.stride(1), q.stride(2), k0.stride(0), k0.stride(1), k0.stride(2),
       v0.stride(0), v0.stride(1), v0.stride(2), out.stride(0), out.stride(1), out.stride(2),
-      float(scale), _lib.ptr(seg_flags), int(flag_target), _lib.stream())
+      float(scale), _lib.ptr(seg_flags), int(flag_target), ctypes.byref(plan) if plan is not None else None,
+      _lib.stream())
   _lib.check(rc, "mdb_flash_fwd")
   return (out, lse) if return_lse else out
 

@@ -68,24 +68,36 @@ class _SegmentAttentionFn(torch.autograd.Function):
   """Kernel path of gather/ring attention: local q against the stacked K/V shards [n, B, S_loc, H, D]."""
 
   @staticmethod
-  def forward(ctx, q, k, v, scale, group, valid_lens):
-    kg = C.all_gather_stack(k, group)
-    vg = C.all_gather_stack(v, group)
-    n = kg.shape[0]
-    ks = [kg[i][:, :valid_lens[i]] for i in range(n)]
-    vs = [vg[i][:, :valid_lens[i]] for i in range(n)]
+  def forward(ctx, q, k, v, scale, group, valid_lens, exchange):
     state = OF._remat
     saved = None
     if state.mode == "replay":
       saved = state.store[state.cursor]
       state.cursor += 1
+    flags, epoch, plan, keep = None, 0, None, None
+    if exchange is not None:
+      # peer-memory transport: segments in ring order (own shard first)
+      order = exchange.order()
+      if saved is None:
+        kg, vg, flags, epoch, plan, keep = exchange.plan(k.contiguous(), v.contiguous())
+      else:
+        kg, vg = exchange.gather(k.contiguous(), v.contiguous())
+    else:
+      kg = C.all_gather_stack(k, group)
+      vg = C.all_gather_stack(v, group)
+      order = list(range(kg.shape[0]))
+    n = kg.shape[0]
+    lens = tuple(valid_lens[r] for r in order)
+    ks = [kg[i][:, :lens[i]] for i in range(n)]
+    vs = [vg[i][:, :lens[i]] for i in range(n)]
     if saved is not None:
       out, lse = saved
     else:
-      out, lse = K.flash_fwd(q, ks, vs, scale)
+      # with a plan the copy CTAs of this launch stage the remote segments while the math starts on the own one
+      out, lse = K.flash_fwd(q, ks, vs, scale, seg_flags=flags, flag_target=epoch, plan=plan)
       if state.mode == "record":
         state.store.append((out, lse))
-    ctx.scale, ctx.group, ctx.valid_lens = scale, group, valid_lens
+    ctx.scale, ctx.group, ctx.valid_lens, ctx.order = scale, group, lens, order
     ctx.save_for_backward(q, out, lse, kg, vg)
     return out
 
@@ -103,12 +115,13 @@ class _SegmentAttentionFn(torch.autograd.Function):
     dkg = torch.zeros_like(kg) if min(lens) < kg.shape[2] else torch.empty_like(kg)
     dvg = torch.zeros_like(vg) if min(lens) < vg.shape[2] else torch.empty_like(vg)
     for i in range(n):
+      # partial gradients are stored by OWNER rank so that the reduce-scatter returns each owner its sum
       dk, dv = K.flash_bwd_dkv(q, d_o, ks[i], vs[i], lse, delta, ctx.scale)
-      dkg[i][:, :lens[i]].copy_(dk)
-      dvg[i][:, :lens[i]].copy_(dv)
+      dkg[ctx.order[i]][:, :lens[i]].copy_(dk)
+      dvg[ctx.order[i]][:, :lens[i]].copy_(dv)
     dk = C.reduce_scatter_stack(dkg, ctx.group)
     dv = C.reduce_scatter_stack(dvg, ctx.group)
-    return dq, dk, dv, None, None, None
+    return dq, dk, dv, None, None, None, None
 
 
 class ContextParallel:
@@ -117,9 +130,12 @@ class ContextParallel:
   `mesh` is a `parallel.mesh.DeviceMesh`; `strategy` one of local / gather / ring / ulysses / usp.
   """
 
-  def __init__(self, mesh, strategy: str = "ring"):
+  def __init__(self, mesh, strategy: str = "ring", peer_memory: bool = False):
     self.mesh = mesh
     self.strategy = strategy
+    self.peer_memory = peer_memory
+    self._exchanges: dict = {}
+    self._peers: dict = {}
     self.group = mesh.group("context")
     self.size = mesh.size("context")
     self.rank = mesh.index_in("context") if self.size > 1 else 0
@@ -130,6 +146,24 @@ class ContextParallel:
     self.ring_rank = mesh.index_in("ring") if self.ring_size > 1 else 0
     self.full_len: Optional[int] = None
     self.local_len: Optional[int] = None
+
+  def _exchange_for(self, group, k):
+    """The peer-memory K/V transport of `group` (created on first use), or None for the NCCL path."""
+    if not self.peer_memory or group is None:
+      return None
+    key = id(group)
+    ex = self._exchanges.get(key)
+    if ex is None or ex.numel < k.numel():
+      from . import symm
+
+      if not symm.peer_memory_available(group):
+        self._exchanges[key] = None
+        return None
+      if key not in self._peers:
+        self._peers[key] = symm.PeerGroup(group)
+      ex = symm.PeerKVExchange(self._peers[key], k.numel(), k.dtype)
+      self._exchanges[key] = ex
+    return ex
 
   # ---- sequence layout ---------------------------------------------------------------------
   def shard_sequence(self, x: torch.Tensor, dim: int = 1) -> torch.Tensor:
@@ -169,7 +203,7 @@ class ContextParallel:
     D = q.shape[-1]
     scale = scale if scale is not None else D ** -0.5
     if q.is_cuda and q.dtype == torch.bfloat16 and D == 128:
-      return _SegmentAttentionFn.apply(q, k, v, scale, group, tuple(valid_lens))
+      return _SegmentAttentionFn.apply(q, k, v, scale, group, tuple(valid_lens), self._exchange_for(group, k))
     kg = _GatherSeq.apply(k, group)
     vg = _GatherSeq.apply(v, group)
     ks = [kg[i][:, :valid_lens[i]] for i in range(n)]

@@ -69,6 +69,15 @@ class FlatParamGroup:
     self.numel = max(unit, (off + unit - 1) // unit * unit)
     self.dtype, self.device, self.world = dtype, device, world
     self.shard_numel = self.numel // world
+    # alignment gaps and the tail are not covered by any parameter; they are zeroed whenever gradients are packed
+    self.gaps = []
+    for p, o in zip(self.params, self.offsets):
+      end = o + p.numel()
+      nxt = (end + _ALIGN - 1) // _ALIGN * _ALIGN
+      if nxt > end:
+        self.gaps.append((end, nxt))
+    if self.numel > off:
+      self.gaps.append((off, self.numel))
 
   def pack_from_params(self) -> torch.Tensor:
     flat = torch.zeros(self.numel, dtype=self.dtype, device=self.device)
@@ -95,6 +104,8 @@ class FlatParamGroup:
         src.append(p.grad.to(flat_grad.dtype) if p.grad.dtype != flat_grad.dtype else p.grad)
     if dst:
       torch._foreach_copy_(dst, src)
+    for a, b in self.gaps:
+      flat_grad[a:b].zero_()
     for p in self.params:
       p.grad = None
 
@@ -103,7 +114,7 @@ class FSDPEngine:
 
   def __init__(self, blocks: Sequence[nn.Module], root_params: Sequence[nn.Parameter], opt: AdamWConfig, *,
                group=None, replica_group=None, device=None, param_dtype=torch.bfloat16, seed: int = 0,
-               train: bool = True):
+               train: bool = True, peer_memory: bool = False):
     self.blocks = list(blocks)
     self.opt = opt
     self.group, self.replica_group = group, replica_group
@@ -140,9 +151,26 @@ class FSDPEngine:
       self.grad_stats = torch.zeros(2, dtype=torch.float32, device=self.device)
       self.pending: list[tuple[int, torch.Tensor]] = []  # shard grads kept for global-norm clipping
 
+    self.peer = None
     if self.world > 1:
       self.slots = [torch.empty(self.max_numel, dtype=param_dtype, device=self.device) for _ in range(2)]
-      self.grad_slots = [torch.empty(self.max_numel, dtype=param_dtype, device=self.device) for _ in range(2)] if train else []
+      self.grad_slots = [torch.zeros(self.max_numel, dtype=param_dtype, device=self.device) for _ in range(2)] if train else []
+      if peer_memory and train and self.on_cuda and param_dtype == torch.bfloat16:
+        from . import symm
+
+        if symm.peer_memory_available(group):
+          self.peer = symm.PeerGroup(group)
+          self.sym_grad, self.sym_grad_ptrs = [], []
+          for _ in range(2):
+            t, ptrs, _h = self.peer.alloc(self.max_numel, param_dtype)
+            t.zero_()
+            self.sym_grad.append(t)
+            self.sym_grad_ptrs.append(ptrs)
+          self.grad_slots = self.sym_grad
+          self.rs_scratch = torch.empty(2 * 64, dtype=torch.float32, device=self.device)
+          self.grad_epoch = 0
+          torch.cuda.synchronize()
+          dist.barrier(group=group)
       self.comm_stream = torch.cuda.Stream() if self.on_cuda else None
       self.gather_done = [None, None]
       self.slot_block = [-1, -1]
@@ -235,6 +263,8 @@ class FSDPEngine:
       else:
         self._adamw(self.shards[i], flat, self.m[i], self.v[i], 1.0, i)
       return
+    if self.peer is not None:
+      return self._reduce_and_step_peer(i)
     slot = self.grad_use % 2
     self.grad_use += 1
     full = self.grad_slots[slot][:g.numel]
@@ -275,6 +305,44 @@ class FSDPEngine:
       for s in range(2):
         if self.slot_block[s] == i:
           self.slot_block[s] = -1
+
+  def _reduce_and_step_peer(self, i: int) -> None:
+    """Peer-memory path: gradients are packed into a symmetric buffer and every owner pulls, sums and applies its
+    slice with one fused kernel (`symm.rs_adamw`); no NCCL collective is involved."""
+    from . import symm
+
+    g = self.groups[i]
+    deferred = self.opt.clip_global_norm > 0
+    self.grad_epoch += 1
+    e = self.grad_epoch
+    slot = e % 2
+    self.peer.wait(symm.FLAG_GRAD_ACK, e - 2)           # everyone has consumed the previous content of this slot
+    g.pack_grads(self.sym_grad[slot][:g.numel])
+    self.peer.signal(symm.FLAG_GRAD_READY, e)
+    ready = torch.cuda.Event()
+    ready.record()
+    o = self.opt
+    with torch.cuda.stream(self.comm_stream):
+      self.comm_stream.wait_event(ready)
+      self.peer.wait(symm.FLAG_GRAD_READY, e)
+      off_bytes = self.rank * g.shard_numel * 2
+      ptrs = [base + off_bytes for base in self.sym_grad_ptrs[slot]]
+      reduced = None
+      if deferred:
+        reduced = torch.empty(g.shard_numel, dtype=self.param_dtype, device=self.device)
+        reduced.record_stream(self.comm_stream)
+      symm.rs_adamw(ptrs, g.shard_numel, self.shards[i], self.m[i], self.v[i], self.grad_stats, self.rs_scratch,
+                    lr=self.lr, b1=o.b1, b2=o.b2, eps=o.eps, wd=o.weight_decay, step=self.step_count,
+                    clip_value=o.clip_value, seed=(self.seed * 1000003 + self.step_count) * 4099 + i,
+                    stochastic=o.stochastic_rounding, apply=not deferred, reduced_out=reduced, ctas=64)
+      self.peer.signal(symm.FLAG_GRAD_ACK, e)
+      if deferred:
+        if self.replica_group is not None:
+          dist.all_reduce(reduced, group=self.replica_group)
+        self.pending.append((i, reduced))
+    for s in range(2):
+      if self.slot_block[s] == i:
+        self.slot_block[s] = -1
 
   def finish_step(self, model_group=None) -> dict:
     """Root (replicated) parameters, deferred clipped updates, and the step's gradient metrics."""

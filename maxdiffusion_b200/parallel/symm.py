@@ -1,0 +1,235 @@
+"""Symmetric peer memory over NVLink: buffers every rank of a group can load from / store to directly.
+
+Allocation and the exchange of the memory handles are plumbing and go through
+`torch.distributed._symmetric_memory`; everything that moves data or synchronises — epoch flags with
+release/acquire semantics at system scope, bounded waits, pull copies, the fused reduce-scatter + AdamW — is this
+repository's own kernels (`csrc/comm.cu`). Flags are monotonically increasing epoch numbers, so buffers are reused
+without reset barriers; every device-side wait gives up after a time budget and records the failure in the device
+status word, which the host raises as an exception at the next check.
+
+The reference has no counterpart: its collectives are inserted by XLA and run through NCCL on GPUs
+(src/maxdiffusion/max_utils.py:925-955, gpu_multi_process_run.sh:18-77).
+"""
+from __future__ import annotations
+
+import ctypes
+from typing import Optional, Sequence
+
+import torch
+import torch.distributed as dist
+
+from ..ops import _lib
+
+# flag kinds (rows of the signal pad); each row has one slot per source rank
+FLAG_GRAD_READY = 0
+FLAG_GRAD_ACK = 1
+FLAG_KV_READY = 2
+FLAG_KV_ACK = 3
+FLAG_SHARD_READY = 4
+FLAG_USER = 5
+NUM_FLAG_KINDS = 8
+WAIT_BUDGET_S = 5.0
+
+
+def _declare(L):
+  c_void_p, c_int, c_ll, c_float, c_uint = ctypes.c_void_p, ctypes.c_int, ctypes.c_longlong, ctypes.c_float, ctypes.c_uint
+  ullp = ctypes.POINTER(ctypes.c_ulonglong)
+  L.mdb_signal_peers.argtypes = [ullp, c_int, c_int, c_uint, c_void_p]
+  L.mdb_signal_peers.restype = c_int
+  L.mdb_wait_flags.argtypes = [c_void_p, c_int, c_int, c_uint, ctypes.c_double, c_void_p]
+  L.mdb_wait_flags.restype = c_int
+  L.mdb_set_flag.argtypes = [c_void_p, c_uint, c_void_p]
+  L.mdb_set_flag.restype = c_int
+  L.mdb_peer_copy.argtypes = [c_void_p, c_void_p, c_ll, c_int, c_void_p]
+  L.mdb_peer_copy.restype = c_int
+  L.mdb_memcpy_async.argtypes = [c_void_p, c_void_p, c_ll, c_void_p]
+  L.mdb_memcpy_async.restype = c_int
+  L.mdb_rs_adamw.argtypes = ([ullp, c_int, c_ll] + [c_void_p] * 6 + [c_int] + [c_float] * 9 +
+                             [ctypes.c_ulonglong, c_int, c_int, c_int, c_void_p])
+  L.mdb_rs_adamw.restype = c_int
+
+
+_lib.register(_declare)
+
+
+def peer_memory_available(group) -> bool:
+  """Peer kernels need CUDA, a multi-rank NCCL group on one node, and the symmetric-memory allocator."""
+  if group is None or not torch.cuda.is_available() or dist.get_backend(group) != "nccl":
+    return False
+  try:
+    import importlib
+
+    importlib.import_module("torch.distributed._symmetric_memory")
+  except Exception:
+    return False
+  return True
+
+
+class PeerGroup:
+  """A group of ranks with a shared signal pad and symmetric buffers."""
+
+  def __init__(self, group):
+    import torch.distributed._symmetric_memory as symm_mem
+
+    self._symm = symm_mem
+    self.group = group
+    self.world = dist.get_world_size(group)
+    self.rank = dist.get_rank(group)
+    self.device = torch.device("cuda", torch.cuda.current_device())
+    self.flags = symm_mem.empty(NUM_FLAG_KINDS * self.world, dtype=torch.int32, device=self.device)
+    self.flags.zero_()
+    self._flags_hdl = symm_mem.rendezvous(self.flags, group)
+    self.flag_ptrs = [int(p) for p in self._flags_hdl.buffer_ptrs]
+    self._buffers = []
+    torch.cuda.synchronize()
+    dist.barrier(group=group)
+
+  # ---- buffers ----------------------------------------------------------------------------
+  def alloc(self, numel: int, dtype: torch.dtype):
+    """Symmetric buffer of `numel` elements; returns (local tensor, [address of the buffer on every rank])."""
+    t = self._symm.empty(numel, dtype=dtype, device=self.device)
+    hdl = self._symm.rendezvous(t, self.group)
+    self._buffers.append((t, hdl))
+    return t, [int(p) for p in hdl.buffer_ptrs], hdl
+
+  # ---- flags ------------------------------------------------------------------------------
+  def signal(self, kind: int, value: int, stream=None, peers: Optional[Sequence[int]] = None) -> None:
+    """Stores `value` into slot (kind, my rank) of every peer's pad (all ranks by default, self included)."""
+    ranks = list(range(self.world)) if peers is None else list(peers)
+    arr = (ctypes.c_ulonglong * len(ranks))(*[self.flag_ptrs[r] for r in ranks])
+    rc = _lib.lib().mdb_signal_peers(arr, len(ranks), kind * self.world + self.rank, int(value) & 0xffffffff,
+                                     stream if stream is not None else _lib.stream())
+    _lib.check(rc, "mdb_signal_peers")
+
+  def wait(self, kind: int, value: int, sources: Optional[Sequence[int]] = None, stream=None) -> None:
+    """Waits (bounded) until the slots (kind, src) of MY pad reached `value`, for every src (all by default)."""
+    if value <= 0:
+      return
+    base = self.flags.data_ptr() + 4 * kind * self.world
+    if sources is None:
+      rc = _lib.lib().mdb_wait_flags(ctypes.c_void_p(base), self.world, 1, int(value), WAIT_BUDGET_S,
+                                     stream if stream is not None else _lib.stream())
+      _lib.check(rc, "mdb_wait_flags")
+    else:
+      for s in sources:
+        rc = _lib.lib().mdb_wait_flags(ctypes.c_void_p(base + 4 * s), 1, 1, int(value), WAIT_BUDGET_S,
+                                       stream if stream is not None else _lib.stream())
+        _lib.check(rc, "mdb_wait_flags")
+
+
+def set_flag(flag_tensor: torch.Tensor, index: int, value: int, stream=None) -> None:
+  rc = _lib.lib().mdb_set_flag(ctypes.c_void_p(flag_tensor.data_ptr() + 4 * index), int(value),
+                               stream if stream is not None else _lib.stream())
+  _lib.check(rc, "mdb_set_flag")
+
+
+def peer_copy(src_ptr: int, dst: torch.Tensor, nbytes: int, ctas: int = 16, stream=None) -> None:
+  rc = _lib.lib().mdb_peer_copy(ctypes.c_void_p(src_ptr), ctypes.c_void_p(dst.data_ptr()), nbytes, ctas,
+                                stream if stream is not None else _lib.stream())
+  _lib.check(rc, "mdb_peer_copy")
+
+
+def memcpy_async(dst_ptr: int, src_ptr: int, nbytes: int, stream=None) -> None:
+  """Copy-engine copy (local or peer source); occupies no SM, so it can run beside a kernel that fills the GPU."""
+  rc = _lib.lib().mdb_memcpy_async(ctypes.c_void_p(dst_ptr), ctypes.c_void_p(src_ptr), nbytes,
+                                   stream if stream is not None else _lib.stream())
+  _lib.check(rc, "mdb_memcpy_async")
+
+
+class PeerKVExchange:
+  """Ring-schedule K/V exchange for context-parallel attention over peer memory.
+
+  Every rank publishes its K/V shard in a symmetric buffer and raises an epoch flag on all peers. The attention
+  kernel is then launched with a copy plan: its last CTAs wait for the owners' flags, pull the other shards
+  straight from their owners over NVLink (no store-and-forward chain: through NVSwitch every peer is one hop away)
+  into a local staging tensor and raise each staged segment's ready flag, while the compute CTAs of the same
+  launch start on the rank's own shard and wait — bounded — on a segment's flag before its first TMA load. The
+  transfer of hop h+1 thus overlaps the math of hop h, the running (O, m, l) never leave the SM, and nothing
+  but this one kernel is involved; afterwards the copy CTAs acknowledge to the owners so the buffers can be
+  reused two epochs later without a barrier.
+  """
+
+  def __init__(self, peer: "PeerGroup", max_numel_per_tensor: int, dtype=torch.bfloat16, copy_ctas: int = 12):
+    self.peer = peer
+    self.n, self.rank = peer.world, peer.rank
+    self.numel = max_numel_per_tensor
+    self.copy_ctas = copy_ctas
+    self.slots, self.slot_ptrs = [], []
+    for _ in range(2):
+      t, ptrs, _h = peer.alloc(2 * max_numel_per_tensor, dtype)
+      self.slots.append(t)
+      self.slot_ptrs.append(ptrs)
+    self.epoch = 0
+    self.elem = torch.tensor([], dtype=dtype).element_size()
+    torch.cuda.synchronize()
+    dist.barrier(group=peer.group)
+
+  def order(self):
+    """Ranks in the order the segments are consumed: own shard, then the ring predecessors."""
+    return [(self.rank - h) % self.n for h in range(self.n)]
+
+  def publish(self, k: torch.Tensor, v: torch.Tensor):
+    """Copies this rank's shard into the symmetric slot of a new epoch and raises KV_READY on every peer."""
+    numel = k.numel()
+    assert numel == v.numel() and numel <= self.numel and k.dtype == self.slots[0].dtype
+    self.epoch += 1
+    e = self.epoch
+    slot = e % 2
+    sym = self.slots[slot]
+    self.peer.wait(FLAG_KV_ACK, e - 2)              # the previous content of this slot has been pulled by all
+    sym[:numel].view(k.shape).copy_(k)
+    sym[self.numel:self.numel + numel].view(v.shape).copy_(v)
+    self.peer.signal(FLAG_KV_READY, e)
+    kg = torch.empty((self.n,) + tuple(k.shape), dtype=k.dtype, device=k.device)
+    vg = torch.empty((self.n,) + tuple(v.shape), dtype=v.dtype, device=v.device)
+    kg[0].copy_(k)
+    vg[0].copy_(v)
+    return kg, vg, e, slot, numel * self.elem
+
+  def plan(self, k: torch.Tensor, v: torch.Tensor):
+    """Returns (kg, vg, flags, epoch, plan) for a fused launch: staging tensors [n, *k.shape] in consumption order,
+    the int32 ready flags (flag 0, the own shard, is already raised) and the copy plan for `kernels.flash_fwd`."""
+    kg, vg, e, slot, nbytes = self.publish(k, v)
+    state = torch.zeros(self.n + 8, dtype=torch.int32, device=k.device)  # [flags (n) | counters (8)]
+    flags = state[:self.n]
+    set_flag(flags, 0, e)
+    plan = _lib.CopyPlan()
+    plan.n_remote = self.n - 1
+    plan.n_copy_ctas = self.copy_ctas
+    pad = self.peer.flags.data_ptr()
+    for i, src in enumerate(self.order()[1:]):
+      base = self.slot_ptrs[slot][src]
+      plan.src[i][0], plan.src[i][1] = base, base + self.numel * self.elem
+      plan.dst[i][0], plan.dst[i][1] = kg[i + 1].data_ptr(), vg[i + 1].data_ptr()
+      plan.ready[i] = pad + 4 * (FLAG_KV_READY * self.n + src)
+    plan.nbytes = nbytes
+    plan.epoch = e
+    plan.counters = state.data_ptr() + 4 * self.n
+    plan.seg_flags = flags.data_ptr()
+    plan.n_ack = self.n
+    for r in range(self.n):
+      plan.ack[r] = self.peer.flag_ptrs[r] + 4 * (FLAG_KV_ACK * self.n + self.rank)
+    return kg, vg, flags, e, plan, state
+
+  def gather(self, k: torch.Tensor, v: torch.Tensor):
+    """Stand-alone variant (no attention kernel to fuse with): waits for every owner, pulls, acknowledges."""
+    kg, vg, e, slot, nbytes = self.publish(k, v)
+    self.peer.wait(FLAG_KV_READY, e)
+    for i, src in enumerate(self.order()[1:]):
+      base = self.slot_ptrs[slot][src]
+      peer_copy(base, kg[i + 1], nbytes, ctas=32)
+      peer_copy(base + self.numel * self.elem, vg[i + 1], nbytes, ctas=32)
+    self.peer.signal(FLAG_KV_ACK, e)
+    return kg, vg
+
+
+def rs_adamw(grad_ptrs: Sequence[int], n: int, p, m, v, stats, scratch, *, lr, b1, b2, eps, wd, step, grad_scale=1.0,
+             clip_value=0.0, seed=0, stochastic=True, apply=True, reduced_out=None, ctas=32, stream=None) -> None:
+  """Fused reduce-scatter + statistics + AdamW on this rank's parameter slice (see csrc/comm.cu)."""
+  arr = (ctypes.c_ulonglong * len(grad_ptrs))(*grad_ptrs)
+  rc = _lib.lib().mdb_rs_adamw(arr, len(grad_ptrs), n, _lib.ptr(p), _lib.ptr(m), _lib.ptr(v), _lib.ptr(reduced_out),
+                               _lib.ptr(stats), _lib.ptr(scratch), int(apply), float(lr), float(b1), float(b2),
+                               float(eps), float(wd), float(1 - b1 ** step), float(1 - b2 ** step), float(grad_scale),
+                               float(clip_value), int(seed) & (2 ** 64 - 1), int(stochastic),
+                               int(m.dtype == torch.float32), ctas, stream if stream is not None else _lib.stream())
+  _lib.check(rc, "mdb_rs_adamw")

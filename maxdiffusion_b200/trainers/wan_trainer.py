@@ -88,9 +88,13 @@ class WanTrainer:
     shard_group = self.mesh.group("shard")
     replica_group = self.mesh.group("replica")
     self.engine = FSDPEngine(model.blocks, root_params, opt, group=shard_group, replica_group=replica_group,
-                             device=self.device, param_dtype=self.dtype, seed=seed)
+                             device=self.device, param_dtype=self.dtype, seed=seed,
+                             peer_memory=bool(config.get("peer_memory_transport", True)))
     model.block_hook = self.engine.block_hook
-    self.pctx = ContextParallel(self.mesh, str(config.get("context_strategy", "ring"))) if self.mesh.size("context") > 1 else None
+    self.pctx = None
+    if self.mesh.size("context") > 1:
+      self.pctx = ContextParallel(self.mesh, str(config.get("context_strategy", "ring")),
+                                  peer_memory=bool(config.get("peer_memory_transport", True)) and self.device.type == "cuda")
 
     self.scheduler = FlowMatchScheduler(num_train_timesteps=1000, shift=float(config.get("flow_shift", 3.0)))
     self.scheduler_state = self.scheduler.set_timesteps(self.scheduler.create_state(), 1000, training=True, device=self.device)

@@ -1,0 +1,184 @@
+"""Peer-memory kernels on 2 GPUs (NCCL ranks as child processes): fused reduce-scatter + AdamW, the flag-gated K/V
+exchange feeding one flash-attention launch, and a training step that must agree with the NCCL path."""
+import os
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+CFG = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "maxdiffusion_b200", "configs",
+                   "base_wan_14b.yml")
+
+
+def _spawn(fn, world, *args):
+  import socket
+
+  import torch.multiprocessing as mp
+
+  with socket.socket() as s:
+    s.bind(("127.0.0.1", 0))
+    port = s.getsockname()[1]
+  ctx = mp.get_context("spawn")
+  q = ctx.Queue()
+  procs = [ctx.Process(target=_entry, args=(r, world, port, fn, args, q)) for r in range(world)]
+  for p in procs:
+    p.start()
+  out = {}
+  try:
+    for _ in range(world):
+      rank, status, payload = q.get(timeout=600)
+      if status != "ok":
+        raise RuntimeError(f"rank {rank} failed:\n{payload}")
+      out[rank] = payload
+  finally:
+    for p in procs:
+      p.join(timeout=30)
+      if p.is_alive():
+        p.kill()
+  return [out[r] for r in range(world)]
+
+
+def _entry(rank, world, port, fn, args, q):
+  import traceback
+
+  import torch.distributed as dist
+
+  os.environ.update({"MASTER_ADDR": "127.0.0.1", "MASTER_PORT": str(port), "RANK": str(rank), "WORLD_SIZE": str(world),
+                     "LOCAL_RANK": str(rank), "NCCL_NVLS_ENABLE": "0"})
+  try:
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    out = fn(rank, world, *args)
+    torch.cuda.synchronize()
+    from maxdiffusion_b200.ops import _lib
+
+    _lib.raise_on_device_status()
+    q.put((rank, "ok", out))
+  except Exception:
+    q.put((rank, "error", traceback.format_exc()))
+  finally:
+    if dist.is_initialized():
+      dist.destroy_process_group()
+
+
+def _rs_adamw(rank, world):
+  import torch.distributed as dist
+
+  from maxdiffusion_b200.ops import ref
+  from maxdiffusion_b200.parallel import symm
+
+  peer = symm.PeerGroup(dist.group.WORLD)
+  n_full = 8 * 1024 * 64 * world
+  shard = n_full // world
+  torch.manual_seed(100 + rank)
+  sym, ptrs, _ = peer.alloc(n_full, torch.bfloat16)
+  grads = torch.randn(n_full, device="cuda", dtype=torch.bfloat16)
+  sym.copy_(grads)
+  torch.manual_seed(7)
+  p = torch.randn(shard, device="cuda", dtype=torch.bfloat16)
+  m = torch.zeros(shard, device="cuda", dtype=torch.float32)
+  v = torch.zeros(shard, device="cuda", dtype=torch.float32)
+  p2, m2, v2 = p.clone(), m.clone(), v.clone()
+  stats = torch.zeros(2, device="cuda")
+  scratch = torch.empty(128, device="cuda")
+  hp = dict(lr=1e-2, b1=0.9, b2=0.999, eps=1e-8, wd=0.01)
+  peer.signal(symm.FLAG_GRAD_READY, 1)
+  peer.wait(symm.FLAG_GRAD_READY, 1)
+  symm.rs_adamw([b + rank * shard * 2 for b in ptrs], shard, p, m, v, stats, scratch, step=1, stochastic=False, ctas=64, **hp)
+  peer.signal(symm.FLAG_GRAD_ACK, 1)
+  peer.wait(symm.FLAG_GRAD_ACK, 1)
+  # reference: NCCL reduce-scatter in fp32, then the plain AdamW
+  full32 = grads.float()
+  red = torch.empty(shard, device="cuda")
+  dist.reduce_scatter_tensor(red, full32)
+  ref.adamw_step(p2, red, m2, v2, step=1, **hp)
+  torch.cuda.synchronize()
+  err_p = (p.float() - p2.float()).abs().max().item()
+  err_m = (m - m2).abs().max().item()
+  want_sq = (red * red).sum().item()
+  return err_p, err_m, stats[0].item(), want_sq, stats[1].item(), red.abs().max().item()
+
+
+def test_rs_adamw_matches_nccl_reduce_scatter_then_adamw():
+  if torch.cuda.device_count() < 2:
+    pytest.skip("needs 2 GPUs")
+  for err_p, err_m, sq, want_sq, mx, want_mx in _spawn(_rs_adamw, 2):
+    assert err_p <= 2e-2 and err_m < 1e-3
+    assert abs(sq - want_sq) / want_sq < 1e-3 and abs(mx - want_mx) < 1e-2
+
+
+def _kv_exchange(rank, world):
+  import torch.distributed as dist
+
+  from maxdiffusion_b200.ops import kernels as K, ref
+  from maxdiffusion_b200.parallel import collectives as C, symm
+
+  peer = symm.PeerGroup(dist.group.WORLD)
+  B, S, H = 1, 520, 4
+  ex = symm.PeerKVExchange(peer, B * S * H * 128)
+  errs = []
+  for it in range(3):  # three epochs exercise both slots and the ack protocol
+    torch.manual_seed(1000 * it + rank)
+    q = torch.randn((B, S, H, 128), device="cuda", dtype=torch.bfloat16)
+    k = torch.randn((B, S, H, 128), device="cuda", dtype=torch.bfloat16)
+    v = torch.randn((B, S, H, 128), device="cuda", dtype=torch.bfloat16)
+    if it == 1:
+      kg, vg = ex.gather(k, v)                     # stand-alone pull (the recomputation path)
+      out, _ = K.flash_fwd(q, list(kg), list(vg))
+    else:
+      kg, vg, flags, epoch, plan, keep = ex.plan(k, v)   # copy CTAs fused into the attention launch
+      out, _ = K.flash_fwd(q, list(kg), list(vg), seg_flags=flags, flag_target=epoch, plan=plan)
+    k_all = C.all_gather_stack(k, dist.group.WORLD)
+    v_all = C.all_gather_stack(v, dist.group.WORLD)
+    want = ref.attention(q, list(k_all), list(v_all))
+    errs.append((out.float() - want.float()).abs().max().item())
+    order = ex.order()
+    assert all(torch.equal(kg[j], k_all[order[j]]) for j in range(world))
+  # full-occupancy case: more tiles than SMs, 42 MB per shard -- the copy CTAs must make progress while every
+  # other SM holds a compute CTA; compared bit for bit with the same kernel on NCCL-gathered K/V
+  B, S, H = 1, 4096, 40
+  big = symm.PeerKVExchange(peer, B * S * H * 128)
+  torch.manual_seed(rank)
+  q = torch.randn((B, S, H, 128), device="cuda", dtype=torch.bfloat16)
+  k = torch.randn((B, S, H, 128), device="cuda", dtype=torch.bfloat16)
+  v = torch.randn((B, S, H, 128), device="cuda", dtype=torch.bfloat16)
+  kg, vg, flags, epoch, plan, keep = big.plan(k, v)
+  out, _ = K.flash_fwd(q, list(kg), list(vg), seg_flags=flags, flag_target=epoch, plan=plan)
+  k_all = C.all_gather_stack(k, dist.group.WORLD)
+  v_all = C.all_gather_stack(v, dist.group.WORLD)
+  order = big.order()
+  want, _ = K.flash_fwd(q, [k_all[r] for r in order], [v_all[r] for r in order])
+  errs.append((out.float() - want.float()).abs().max().item() * 1e3)
+  return errs
+
+
+def test_flag_gated_kv_exchange_feeds_flash_attention():
+  if torch.cuda.device_count() < 2:
+    pytest.skip("needs 2 GPUs")
+  for errs in _spawn(_kv_exchange, 2):
+    assert max(errs) < 3e-2
+
+
+def _train(rank, world, peer):
+  from maxdiffusion_b200 import pyconfig
+  from maxdiffusion_b200.parallel.mesh import create_device_mesh
+  from maxdiffusion_b200.trainers.wan_trainer import WanTrainer
+
+  config = pyconfig.initialize(
+      ["t", CFG, "run_name=t", "height=128", "width=128", "num_frames=9", "dataset_type=synthetic", "wan_preset=tiny",
+       'wan_config_overrides={"num_layers": 2, "ffn_dim": 1024}', "remat_policy=SAVE_ATTENTION",
+       "warmup_steps_fraction=0.0", "log_config=false", "write_metrics=false", "attention=tokamax_ring",
+       f"per_device_batch_size={1.0 / world}", f"peer_memory_transport={'true' if peer else 'false'}",
+       "stochastic_rounding=false"], unittest=True)
+  tr = WanTrainer(config, mesh=create_device_mesh(config))
+  data = tr.load_dataset()
+  return [float(tr.train_step(next(data))["learning/loss"]) for _ in range(3)]
+
+
+def test_training_step_peer_transport_matches_nccl():
+  if torch.cuda.device_count() < 2:
+    pytest.skip("needs 2 GPUs")
+  a = _spawn(_train, 2, True)[0]
+  b = _spawn(_train, 2, False)[0]
+  assert a == pytest.approx(b, rel=3e-2, abs=3e-2)
