@@ -670,3 +670,49 @@ extern "C" int mdb_gelu_bwd(const void* dy, const void* u, void* du, long long n
       nvec);
   return static_cast<int>(cudaGetLastError());
 }
+
+// ---------------------------------------------------------------------------------------
+// Allocation-free column sums (declared and documented in no_alloc.h).
+// ---------------------------------------------------------------------------------------
+#include "no_alloc.h"
+
+namespace {
+// Scratch of the allocation-free entry point: one partial row per CTA. Device code may name the array directly;
+// host code must not pass `g_colsum_scratch` to a kernel (in host code the name is only a stand-in for the
+// symbol) and uses the address obtained with cudaGetSymbolAddress below.
+static __device__ __align__(256) float g_colsum_scratch[MDB_COLSUM_NOALLOC_CTAS * MDB_COLSUM_NOALLOC_MAX_COLS];
+
+constexpr int kNoAllocMaxDevices = 64;
+float* g_colsum_scratch_addr[kNoAllocMaxDevices] = {nullptr};
+}  // namespace
+
+extern "C" const char* mdb_colsum_noalloc_strerror(int code) {
+  switch (code) {
+    case MDB_NOALLOC_OK: return "ok";
+    case MDB_NOALLOC_ERR_TOO_WIDE: return "mdb_colsum_noalloc: more than 8192 columns do not fit the built-in scratch array";
+    case MDB_NOALLOC_ERR_BAD_SHAPE: return "mdb_colsum_noalloc: cols must be a positive multiple of 8 and ldx >= cols";
+    case MDB_NOALLOC_ERR_SETUP: return "mdb_colsum_noalloc: cudaGetSymbolAddress failed for the scratch array";
+    default: return code > 0 ? cudaGetErrorString(static_cast<cudaError_t>(code)) : "mdb_colsum_noalloc: unknown code";
+  }
+}
+
+extern "C" int mdb_colsum_noalloc(const void* x, long long ldx, int rows, int cols, float* out, void* stream) {
+  if (cols > MDB_COLSUM_NOALLOC_MAX_COLS) return MDB_NOALLOC_ERR_TOO_WIDE;
+  if (cols <= 0 || (cols & 7) || ldx < cols) return MDB_NOALLOC_ERR_BAD_SHAPE;
+  if (rows <= 0) return MDB_NOALLOC_OK;
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kNoAllocMaxDevices) return MDB_NOALLOC_ERR_SETUP;
+  float* scratch = g_colsum_scratch_addr[dev];
+  if (scratch == nullptr) {
+    // set-up, once per device and with that device current: translate the symbol into its device address
+    void* addr = nullptr;
+    if (cudaGetSymbolAddress(&addr, g_colsum_scratch) != cudaSuccess || addr == nullptr) return MDB_NOALLOC_ERR_SETUP;
+    scratch = static_cast<float*>(addr);
+    g_colsum_scratch_addr[dev] = scratch;
+  }
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const int ctas = rows < MDB_COLSUM_NOALLOC_CTAS ? rows : MDB_COLSUM_NOALLOC_CTAS;
+  colsum_kernel<<<dim3(ctas, 1), THREADS, 0, st>>>(static_cast<const __nv_bfloat16*>(x), ldx, rows, cols, scratch);
+  fold_partials_kernel<<<dim3((cols + 255) / 256, 1), 256, 0, st>>>(scratch, out, ctas, 1, cols, 0);
+  return static_cast<int>(cudaGetLastError());
+}
