@@ -1,0 +1,78 @@
+"""Wan pipeline, VAE chunking and cache policies on CPU (fp32, tiny random-init models)."""
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from maxdiffusion_b200 import pyconfig
+from maxdiffusion_b200.models.wan.autoencoder_kl_wan import AutoencoderKLWan, WanVAEConfig
+from maxdiffusion_b200.pipelines.wan import cache_policies as CP
+from maxdiffusion_b200.pipelines.wan.wan_pipeline import WanPipeline2_1, WanPipeline2_2
+
+CFG = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "maxdiffusion_b200", "configs")
+TINY = '{"num_attention_heads": 2, "attention_head_dim": 32, "ffn_dim": 64, "num_layers": 2, "text_dim": 32, "freq_dim": 32}'
+VAE = '{"base_dim": 8, "z_dim": 16}'
+
+
+def _config(name="base_wan_14b.yml", *extra):
+  return pyconfig.initialize(["t", os.path.join(CFG, name), "run_name=t", "height=32", "width=32", "num_frames=9",
+                              "wan_preset=tiny", f"wan_config_overrides={TINY}", f"vae_config_overrides={VAE}",
+                              "num_inference_steps=6", "log_config=false", *extra], unittest=True)
+
+
+def test_vae_chunked_decode_and_encode_match_whole_clip():
+  torch.manual_seed(0)
+  vae = AutoencoderKLWan(WanVAEConfig(base_dim=8))
+  z = torch.randn(1, 16, 3, 4, 4)
+  full = vae.decode_full(z)
+  assert full.shape == (1, 3, 9, 32, 32)
+  assert torch.allclose(vae.decode(z, chunk=1), full, atol=1e-5)
+  assert torch.allclose(vae.decode(z, chunk=2), full, atol=1e-5)
+  x = torch.randn(1, 3, 9, 32, 32)
+  assert torch.allclose(vae.encode(x, chunk=4).mean, vae.encode_full(x).mean, atol=1e-5)
+  assert vae.encode(x).mean.shape == (1, 16, 3, 4, 4)
+
+
+def test_pipeline_runs_and_caches_change_little():
+  config = _config()
+  pipe = WanPipeline2_1.from_config(config, device="cpu")
+  emb = torch.randn(1, 8, 32)
+  neg = torch.randn(1, 8, 32)
+  g = lambda: torch.Generator().manual_seed(3)
+  video = pipe(prompt_embeds=emb, negative_prompt_embeds=neg, generator=g())
+  assert video.shape == (1, 9, 32, 32, 3) and video.dtype == torch.uint8
+  base = pipe(prompt_embeds=emb, negative_prompt_embeds=neg, generator=g(), output_type="latent")
+  kv = pipe(prompt_embeds=emb, negative_prompt_embeds=neg, generator=g(), output_type="latent", use_kv_cache=True)
+  assert torch.allclose(base, kv, atol=1e-4)  # the K/V cache is exact
+  for kw in (dict(use_cfg_cache=True), dict(use_magcache=True)):
+    out = pipe(prompt_embeds=emb, negative_prompt_embeds=neg, generator=g(), output_type="latent", **kw)
+    assert torch.isfinite(out).all()
+
+
+def test_wan22_switches_experts_and_sen_cache_runs():
+  config = _config("base_wan_27b.yml")
+  pipe = WanPipeline2_2.from_config(config, device="cpu", load_vae=False)
+  emb, neg = torch.randn(1, 8, 32), torch.randn(1, 8, 32)
+  calls = {"high": 0, "low": 0}
+  f1, f2 = pipe.transformer.forward, pipe.transformer_2.forward
+  pipe.transformer.forward = lambda *a, **k: (calls.__setitem__("high", calls["high"] + 1), f1(*a, **k))[1]
+  pipe.transformer_2.forward = lambda *a, **k: (calls.__setitem__("low", calls["low"] + 1), f2(*a, **k))[1]
+  out = pipe(prompt_embeds=emb, negative_prompt_embeds=neg, output_type="latent", num_inference_steps=10)
+  assert calls["high"] > 0 and calls["low"] > 0 and calls["high"] + calls["low"] == 10
+  out = pipe(prompt_embeds=emb, negative_prompt_embeds=neg, output_type="latent", num_inference_steps=10, use_sen_cache=True)
+  assert torch.isfinite(out).all()
+
+
+def test_cache_schedules():
+  sched = CP.cfg_cache_schedule(50, 720)
+  assert not any(sched[:16]) and not any(sched[45:]) and sum(sched) > 15 and not sched[16]
+  mag = CP.magcache_schedule(40, np.ones(80) * 0.999, thresh=0.12, K=2, retention_ratio=0.2)
+  assert not any(mag[:8]) and sum(mag) > 10
+  # never more than K consecutive skips
+  run = 0
+  for s in mag:
+    run = run + 1 if s else 0
+    assert run <= 2
+  x = torch.randn(1, 4, 2, 16, 18)
+  assert torch.allclose(CP.fft_compensate(x, x, x, 1.2, 1.0), x, atol=1e-5)  # zero bias -> identity
