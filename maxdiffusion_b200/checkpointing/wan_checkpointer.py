@@ -1,0 +1,134 @@
+"""Wan checkpointing: periodic / final saves of the transformer (+ optimizer) and resume, and the
+pretrained-weights cache in checkpoint layout.
+
+Reference: `WanCheckpointer` and its 2.1 / 2.2 / I2V / VACE subclasses
+(src/maxdiffusion/checkpointing/wan_checkpointer.py:54-231, wan_checkpointer_2_1.py:26-82,
+wan_checkpointer_2_2.py:26-106). Items: `wan_config` (JSON of the transformer config) and `wan_state` (2.2:
+`high_noise_transformer_state`, `low_noise_transformer_state`) holding the parameters under the reference's flax
+tree paths; with `save_optimizer` the AdamW moments of every rank are stored next to them and re-sharded on restore,
+so a run can resume on a different number of GPUs. Unlike the reference, whose restored optimizer state is dropped
+(src/maxdiffusion/trainers/base_wan_trainer.py:267 discards the result of `state.replace`), the moments and the
+step counter are installed.
+"""
+from __future__ import annotations
+
+import os
+from typing import Optional
+
+import torch
+import torch.distributed as dist
+
+from .. import max_logging
+from ..loaders.wan_loader import diffusers_to_flax_tree, diffusers_to_ours, flax_tree_to_diffusers, ours_to_diffusers
+from .checkpointing_utils import WAN_CHECKPOINT, create_checkpoint_manager
+
+
+def _param_names(trainer):
+  names = [[n for n, _ in b.named_parameters()] for b in trainer.model.blocks]
+  block_ids = {id(p) for b in trainer.model.blocks for p in b.parameters()}
+  root = [n for n, p in trainer.model.named_parameters() if id(p) not in block_ids]
+  return names, root
+
+
+class WanCheckpointer:
+
+  def __init__(self, config, checkpoint_type: str = WAN_CHECKPOINT):
+    self.config = config
+    rank = dist.get_rank() if dist.is_available() and dist.is_initialized() else 0
+    self.rank = rank
+    self.world = dist.get_world_size() if dist.is_available() and dist.is_initialized() else 1
+    self.manager = create_checkpoint_manager(config.get("checkpoint_dir", ""), checkpoint_type,
+                                             enable_async=bool(config.get("enable_async_checkpointing", True)),
+                                             dataset_type=str(config.get("dataset_type", "")), rank=rank)
+
+  # ---- training state ----------------------------------------------------------------------
+  def save(self, step: int, trainer) -> None:
+    names, root = _param_names(trainer)
+    eng = trainer.engine
+    full = {}
+    for i, (g, blk_names) in enumerate(zip(eng.groups, names)):
+      flat = eng.full_block_flat(i)  # collective when sharded
+      for n, v in zip(blk_names, g.views(flat)):
+        full[f"blocks.{i}.{n}"] = v.clone()
+    for n, v in zip(root, eng.root.views(eng.root_flat)):
+      full[n] = v.clone()
+    cfg = trainer.wan_cfg
+    tree = diffusers_to_flax_tree(ours_to_diffusers(full, cfg.in_channels, tuple(cfg.patch_size)),
+                                  scan_layers=bool(self.config.get("scan_layers", True)))
+    items = {"wan_config": cfg.to_dict(), "wan_state": tree}
+    sharded = None
+    if self.config.get("save_optimizer", False):
+      st = eng.optimizer_state()
+      shard = {"step": torch.tensor([st["step"]]), "root_m": st["root_m"], "root_v": st["root_v"]}
+      for i, (m, v) in enumerate(zip(st["m"], st["v"])):
+        shard[f"m.{i}"], shard[f"v.{i}"] = m, v
+      items["wan_config"]["_train_step"] = int(step)
+      sharded = {"wan_state": shard}
+    self.manager.save(step, items, sharded=sharded, world_size=self.world)
+    max_logging.log(f"saved checkpoint for step {step} to {self.manager.directory}")
+
+  def maybe_restore(self, trainer) -> Optional[int]:
+    """Restores the latest step into the trainer (weights, and moments when present). Returns the step or None."""
+    self.manager.wait_until_finished()
+    step = self.manager.latest_step()
+    if step is None:
+      return None
+    tree = {k: v.numpy() if v.dtype != torch.bfloat16 else v.float().numpy() for k, v in self.manager.restore_state(step, "wan_state").items()}
+    ours = diffusers_to_ours(flax_tree_to_diffusers(tree))
+    names, root = _param_names(trainer)
+    eng = trainer.engine
+    for i, blk_names in enumerate(names):
+      eng.load_full_block(i, [ours[f"blocks.{i}.{n}"].to(eng.device, eng.param_dtype) for n in blk_names])
+    for n, view in zip(root, eng.root.views(eng.root_flat)):
+      view.copy_(ours[n].to(eng.device, eng.param_dtype).reshape(view.shape))
+    if os.path.exists(os.path.join(self.manager.directory, str(step), "wan_state", "_sharding")):
+      shards = self.manager.restore_sharded(step, "wan_state")
+      state = {"step": int(shards[0]["step"][0]), "root_m": shards[0]["root_m"], "root_v": shards[0]["root_v"], "m": [], "v": []}
+      for i, g in enumerate(eng.groups):
+        for key in ("m", "v"):
+          full = torch.cat([s[f"{key}.{i}"] for s in shards])  # flat moments of the whole block
+          state[key].append(full[eng.rank * g.shard_numel:(eng.rank + 1) * g.shard_numel] if eng.world > 1 else full[:g.numel])
+      eng.load_optimizer_state(state)
+    max_logging.log(f"restored checkpoint of step {step} from {self.manager.directory}")
+    return int(step)
+
+  # ---- inference ---------------------------------------------------------------------------
+  def restore_into_pipeline(self, pipe, step: Optional[int] = None) -> None:
+    step = step if step is not None else self.manager.latest_step()
+    if step is None:
+      raise FileNotFoundError(f"no checkpoint under {self.manager.directory}")
+    pairs = [("wan_state", pipe.transformer)]
+    if pipe.transformer_2 is not None:
+      pairs = [("high_noise_transformer_state", pipe.transformer), ("low_noise_transformer_state", pipe.transformer_2)]
+    for item, model in pairs:
+      tree = {k: (v.float().numpy() if v.dtype == torch.bfloat16 else v.numpy()) for k, v in self.manager.restore_state(step, item).items()}
+      ours = diffusers_to_ours(flax_tree_to_diffusers(tree))
+      dtype = next(model.parameters()).dtype
+      model.load_state_dict({k: v.to(dtype) for k, v in ours.items()})
+
+  def save_pipeline(self, step: int, pipe) -> None:
+    cfg = pipe.transformer.cfg
+    def tree(m):
+      return diffusers_to_flax_tree(ours_to_diffusers(m.state_dict(), cfg.in_channels, tuple(cfg.patch_size)))
+    items = {"wan_config": cfg.to_dict()}
+    if pipe.transformer_2 is not None:
+      items["high_noise_transformer_state"], items["low_noise_transformer_state"] = tree(pipe.transformer), tree(pipe.transformer_2)
+    else:
+      items["wan_state"] = tree(pipe.transformer)
+    self.manager.save(step, items)
+    self.manager.wait_until_finished()
+
+  def load_pretrained_pipeline_or_diffusers(self, pipeline_cls, device=None):
+    """`pretrained_orbax_dir` cache: restore from it when it holds a checkpoint, else load the diffusers weights and
+    write the cache for the next start (reference: wan_checkpointer.py:61-174)."""
+    cache_dir = self.config.get("pretrained_orbax_dir", "")
+    if cache_dir:
+      cache = WanCheckpointer(self.config.replace(checkpoint_dir=cache_dir))
+      if cache.manager.latest_step() is not None:
+        pipe = pipeline_cls.from_config(self.config, device=device)
+        cache.restore_into_pipeline(pipe)
+        return pipe
+    pipe = pipeline_cls.from_pretrained(self.config, device=device)
+    if cache_dir and self.rank == 0:
+      WanCheckpointer(self.config.replace(checkpoint_dir=cache_dir)).save_pipeline(0, pipe)
+    return pipe
