@@ -414,3 +414,65 @@ class FSDPEngine:
       dst.copy_(src)
     self.root_m.copy_(state["root_m"])
     self.root_v.copy_(state["root_v"])
+
+
+class FlatShardedOptimizer:
+  """AdamW over ALL parameters of a model as one flat buffer, with gradient and optimizer-state sharding (ZeRO-2).
+
+  For models without a uniform block structure (UNet, VAE, text encoders): parameters stay resident (replicated),
+  gradients are packed, reduce-scattered over `group`, every rank updates its slice with the fused AdamW kernel and
+  the updated slices are all-gathered back into the flat parameter buffer. With one rank it is a plain fused AdamW.
+  """
+
+  def __init__(self, params: Sequence[nn.Parameter], opt: AdamWConfig, group=None, seed: int = 0):
+    params = [p for p in params if p.requires_grad]
+    self.opt, self.group, self.seed = opt, group, seed
+    self.world = dist.get_world_size(group) if group is not None else 1
+    self.rank = dist.get_rank(group) if group is not None else 0
+    device, dtype = params[0].device, params[0].dtype
+    self.flat_group = FlatParamGroup(params, self.world, dtype, device)
+    self.flat = self.flat_group.pack_from_params()
+    self.flat_group.point_params_to(self.flat)
+    n = self.flat_group.shard_numel
+    self.m = torch.zeros(n, dtype=opt.state_dtype if dtype == torch.bfloat16 else torch.float32, device=device)
+    self.v = torch.zeros_like(self.m)
+    self.grad = torch.zeros(self.flat_group.numel, dtype=dtype, device=device)
+    self.step_count = 0
+    self.lr = opt.lr
+
+  def step(self, lr: Optional[float] = None) -> dict:
+    from . import collectives as C
+
+    self.step_count += 1
+    if lr is not None:
+      self.lr = lr
+    g = self.flat_group
+    g.pack_grads(self.grad)
+    n = g.shard_numel
+    if self.world > 1:
+      shard_grad = torch.empty(n, dtype=self.grad.dtype, device=self.grad.device)
+      C.reduce_scatter_flat(shard_grad, self.grad, self.group)
+      shard_grad.div_(self.world)
+    else:
+      shard_grad = self.grad
+    stats = K.sumsq_maxabs(shard_grad) if shard_grad.is_cuda and shard_grad.dtype in (torch.bfloat16, torch.float32) else ref.sumsq_maxabs(shard_grad)
+    if self.group is not None:
+      sq, mx = stats[0:1].clone(), stats[1:2].clone()
+      dist.all_reduce(sq, group=self.group)
+      dist.all_reduce(mx, op=dist.ReduceOp.MAX, group=self.group)
+      stats = torch.cat([sq, mx])
+    norm = stats[0].sqrt()
+    scale = 1.0
+    if self.opt.clip_global_norm > 0:
+      scale = float(min(1.0, self.opt.clip_global_norm / (norm.item() + 1e-6)))
+    p = self.flat[self.rank * n:(self.rank + 1) * n]
+    o = self.opt
+    kw = dict(lr=self.lr, b1=o.b1, b2=o.b2, eps=o.eps, wd=o.weight_decay, step=self.step_count, grad_scale=scale,
+              clip_value=o.clip_value)
+    if p.is_cuda and p.dtype == torch.bfloat16:
+      K.adamw(p, shard_grad, self.m, self.v, seed=self.seed * 7919 + self.step_count, stochastic=o.stochastic_rounding, **kw)
+    else:
+      ref.adamw_step(p, shard_grad, self.m, self.v, **kw)
+    if self.world > 1:
+      dist.all_gather_into_tensor(self.flat, p.clone(), group=self.group)
+    return {"grad_norm": norm, "max_abs_grad": stats[1]}

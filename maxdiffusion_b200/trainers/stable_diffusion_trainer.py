@@ -1,0 +1,174 @@
+"""SD 1.x / 2.x and SDXL UNet training (DDPM noise scheduler, epsilon / v-prediction MSE, optional min-SNR weights and
+timestep-bias sampling), and the Dreambooth variant with prior preservation.
+
+Reference: `BaseStableDiffusionTrainer.start_training` (src/maxdiffusion/trainers/base_stable_diffusion_trainer.py:115-197),
+SDXL `_train_step` (sdxl_trainer.py:294-391: `add_time_ids`, timestep bias :326-335, min-SNR :371-378), SD `_train_step`
+(stable_diffusion_trainer.py:253-358) and Dreambooth prior-preservation loss (dreambooth_trainer.py:252-337).
+The batch holds either cached latents + text embeddings (`cache_latents_text_encoder_outputs`) or pixels + token ids
+that go through the frozen VAE / text encoders first.
+"""
+from __future__ import annotations
+
+import time
+from typing import Optional
+
+import torch
+import torch.distributed as dist
+import torch.nn.functional as F
+
+from .. import max_logging
+from ..max_utils import create_optimizer
+from ..models.unet_2d_condition import UNET_PRESETS, UNet2DConditionModel, UNetConfig
+from ..parallel.fsdp import FlatShardedOptimizer, lr_schedule
+from ..parallel.mesh import create_device_mesh
+from ..schedulers.scheduling_ddpm import DDPMScheduler
+from ..train_utils import MetricsWriter, compute_snr, generate_timestep_weights
+
+
+def get_add_time_ids(original_size, crops_coords_top_left, target_size, batch: int, device=None, dtype=torch.float32):
+  """SDXL micro-conditioning ids [B, 6] (reference: maxdiffusion_utils.py:143)."""
+  ids = torch.tensor(list(original_size) + list(crops_coords_top_left) + list(target_size), device=device, dtype=dtype)
+  return ids[None].expand(batch, -1)
+
+
+def resolve_unet_config(config) -> UNetConfig:
+  preset = str(config.get("unet_preset", "") or ("sdxl" if "xl" in str(config.get("pretrained_model_name_or_path", "")).lower() else "sd15"))
+  d = dict(UNET_PRESETS[preset])
+  d.update(config.get("unet_config_overrides", None) or {})
+  return UNetConfig(**d)
+
+
+class StableDiffusionTrainer:
+  is_xl = False
+
+  def __init__(self, config, mesh=None, unet: Optional[UNet2DConditionModel] = None, vae=None, text_encoders=(), device=None):
+    self.config = config
+    self.mesh = mesh if mesh is not None else create_device_mesh(config)
+    self.device = torch.device(device) if device is not None else (
+        torch.device("cuda", torch.cuda.current_device()) if torch.cuda.is_available() else torch.device("cpu"))
+    self.dtype = config.weights_dtype if self.device.type == "cuda" else torch.float32
+    seed = int(config.get("seed", 0))
+    if unet is None:
+      torch.manual_seed(seed)
+      prev = torch.get_default_dtype()
+      torch.set_default_dtype(self.dtype)
+      try:
+        with torch.device(self.device):
+          unet = UNet2DConditionModel(resolve_unet_config(config))
+      finally:
+        torch.set_default_dtype(prev)
+    self.unet = unet.to(self.device, self.dtype)
+    self.vae, self.text_encoders = vae, list(text_encoders)
+    group = self.mesh.group("replica") if self.mesh.size("fsdp") == 1 else dist.group.WORLD if dist.is_initialized() else None
+    self.optimizer = FlatShardedOptimizer(list(self.unet.parameters()), create_optimizer(config), group=group, seed=seed)
+    sc = dict(config.get("diffusion_scheduler_config", {}) or {})
+    self.prediction_type = sc.get("prediction_type", "epsilon")
+    self.scheduler = DDPMScheduler(beta_start=0.00085, beta_end=0.012, beta_schedule="scaled_linear",
+                                   prediction_type=self.prediction_type,
+                                   rescale_zero_terminal_snr=bool(sc.get("rescale_zero_terminal_snr", False)))
+    self.sched_state = self.scheduler.create_state()
+    self.timestep_weights = generate_timestep_weights(config, 1000)
+    self.gen = torch.Generator(device=self.device).manual_seed(seed + 1 + 7919 * self.mesh.rank)
+    self.step = 0
+    self.snr_gamma = float(config.get("snr_gamma", -1.0))
+    self.batch_size = max(1, int(float(config.get("per_device_batch_size", 1))))
+
+  # ---- conditioning -----------------------------------------------------------------------
+  def encode_batch(self, batch: dict) -> dict:
+    """Latents and text embeddings from pixels / token ids when they are not cached in the dataset."""
+    out = dict(batch)
+    if "latents" not in out:
+      with torch.no_grad():
+        dist_ = self.vae.encode(out["pixel_values"].to(self.device, next(self.vae.parameters()).dtype))
+        out["latents"] = self.vae.scale_latents(dist_.sample(self.gen))
+    if "encoder_hidden_states" not in out:
+      with torch.no_grad():
+        hs, pooled = [], None
+        for i, enc in enumerate(self.text_encoders):
+          o = enc(out[f"input_ids{'' if i == 0 else '_2'}"].to(self.device), output_hidden_states=True)
+          hs.append(o.hidden_states[-2] if self.is_xl else o.last_hidden_state)
+          pooled = getattr(o, "text_embeds", None) if i == len(self.text_encoders) - 1 else pooled
+        out["encoder_hidden_states"] = torch.cat(hs, dim=-1)
+        if pooled is not None:
+          out["text_embeds"] = pooled
+    return out
+
+  # ---- step -------------------------------------------------------------------------------
+  def loss(self, batch: dict) -> torch.Tensor:
+    latents = batch["latents"].to(self.device, torch.float32)
+    B = latents.shape[0]
+    noise = torch.randn(latents.shape, generator=self.gen, device=self.device)
+    w = self.timestep_weights.to(self.device)
+    timesteps = torch.multinomial(w, B, replacement=True, generator=self.gen)
+    noisy = self.scheduler.add_noise(self.sched_state, latents, noise, timesteps)
+    added = None
+    if self.is_xl:
+      res = int(self.config.get("resolution", 1024))
+      time_ids = batch.get("time_ids")
+      if time_ids is None:
+        time_ids = get_add_time_ids((res, res), (0, 0), (res, res), B, self.device)
+      added = {"text_embeds": batch["text_embeds"].to(self.device), "time_ids": time_ids.to(self.device)}
+    pred = self.unet(noisy.to(self.dtype), timesteps, batch["encoder_hidden_states"].to(self.device), added).float()
+    if self.prediction_type == "epsilon":
+      target = noise
+    elif self.prediction_type == "v_prediction":
+      target = self.scheduler.get_velocity(self.sched_state, latents, noise, timesteps)
+    else:
+      raise ValueError(self.prediction_type)
+    loss = (target - pred) ** 2
+    if self.snr_gamma > 0:
+      snr = compute_snr(self.sched_state.common.alphas_cumprod, timesteps)
+      weights = torch.minimum(snr, torch.full_like(snr, self.snr_gamma)) / snr
+      if self.prediction_type == "v_prediction":
+        weights = weights * snr / (snr + 1)
+      loss = loss.mean(dim=(1, 2, 3)) * weights
+    return loss.mean()
+
+  def train_step(self, batch: dict) -> dict:
+    batch = self.encode_batch({k: (v.to(self.device, non_blocking=True) if torch.is_tensor(v) else v) for k, v in batch.items()})
+    lr = lr_schedule(self.step, float(self.config.learning_rate), int(self.config.learning_rate_schedule_steps),
+                     float(self.config.warmup_steps_fraction))
+    loss = self.loss(batch)
+    loss.backward()
+    stats = self.optimizer.step(lr)
+    self.step += 1
+    return {"learning/loss": loss.detach(), "learning/grad_norm": stats["grad_norm"], "learning/current_learning_rate": lr}
+
+  def synthetic_batch(self) -> dict:
+    cfg = self.unet.cfg
+    g = torch.Generator().manual_seed(self.step + 17)
+    lat = int(self.config.get("resolution", 1024)) // 8
+    b = {"latents": torch.randn((self.batch_size, cfg.in_channels, lat, lat), generator=g),
+         "encoder_hidden_states": torch.randn((self.batch_size, 77, cfg.cross_attention_dim), generator=g)}
+    if self.is_xl:
+      b["text_embeds"] = torch.randn((self.batch_size, cfg.projection_class_embeddings_input_dim - 6 * cfg.addition_time_embed_dim), generator=g)
+    return {k: (v.pin_memory() if torch.cuda.is_available() else v) for k, v in b.items()}
+
+  def start_training(self, data=None):
+    writer = MetricsWriter(self.config, self.mesh.rank)
+    max_steps = int(self.config.max_train_steps)
+    while self.step < max_steps:
+      batch = next(data) if data is not None else self.synthetic_batch()
+      t0 = time.perf_counter()
+      m = self.train_step(batch)
+      loss = float(m["learning/loss"])
+      dt = time.perf_counter() - t0
+      writer.write(self.step, {**{k: float(v) for k, v in m.items()}, "perf/step_time_seconds": dt})
+    writer.close()
+    return self
+
+
+class StableDiffusionXLTrainer(StableDiffusionTrainer):
+  is_xl = True
+
+
+class DreamboothTrainer(StableDiffusionTrainer):
+  """Instance + class (prior-preservation) batches: the two halves of the batch get separate MSE terms and the
+  class term is weighted by `prior_loss_weight`."""
+
+  def loss(self, batch: dict) -> torch.Tensor:
+    if "class_latents" not in batch:
+      return super().loss(batch)
+    inst = {k: v for k, v in batch.items() if not k.startswith("class_")}
+    cls = {k[len("class_"):]: v for k, v in batch.items() if k.startswith("class_")}
+    return super().loss(inst) + float(self.config.get("prior_loss_weight", 1.0)) * super().loss(cls)
