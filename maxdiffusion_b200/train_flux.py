@@ -1,0 +1,22 @@
+"""python -m maxdiffusion_b200.train_flux <config.yml> key=value ...   (reference: src/maxdiffusion/train_flux.py)"""
+import sys
+
+from . import pyconfig
+from .parallel.mesh import create_device_mesh, init_distributed
+from .train_utils import validate_train_config
+from .trainers.flux_trainer import FluxTrainer
+
+
+def train(config):
+  return FluxTrainer(config, mesh=create_device_mesh(config)).start_training()
+
+
+def main(argv=None):
+  init_distributed()
+  config = pyconfig.initialize(list(sys.argv if argv is None else argv), validate_training=True)
+  validate_train_config(config)
+  train(config)
+
+
+if __name__ == "__main__":
+  main()
