@@ -1,0 +1,193 @@
+"""LoRA: parsing of the common file styles, merge-into-weights (Wan, LTX-2) and run-time adapters (SD / SDXL / Flux).
+
+Two mechanisms as in the reference:
+  * merge: W += scale * (alpha / rank) * up @ down (+ `.diff` weight deltas, `.diff_b` bias deltas), applied once
+    after loading (src/maxdiffusion/models/lora_nnx.py:31-245; loaders/wan_lora_nnx_loader.py:25-111);
+  * run-time adapters: extra low-rank branches evaluated next to the wrapped Linear, several adapters at once
+    (src/maxdiffusion/models/lora.py:31-125; loaders/lora_pipeline.py:136-170, flux_lora_pipeline.py:57-94).
+Key styles understood by `parse_lora_dict`: diffusers-PEFT (`lora_A` / `lora_B`), Kohya / XLabs / SGM
+(`lora_down` / `lora_up`, `.alpha`), with `diffusion_model.` / `transformer.` / `lora_unet_` prefixes
+(src/maxdiffusion/loaders/lora_conversion_utils.py:22-705).
+"""
+from __future__ import annotations
+
+import os
+import re
+from typing import Dict, Optional
+
+import torch
+import torch.nn as nn
+
+_PREFIXES = ("diffusion_model.", "transformer.", "model.diffusion_model.", "unet.", "lora_unet_", "lora_transformer_")
+
+
+def parse_lora_dict(sd: Dict[str, torch.Tensor]) -> Dict[str, dict]:
+  """module path -> {down, up, alpha, diff, diff_b}."""
+  out: Dict[str, dict] = {}
+  for key, t in sd.items():
+    k = key
+    for p in _PREFIXES:
+      if k.startswith(p):
+        k = k[len(p):]
+    m = re.match(r"(.*)\.(lora_A|lora_down)(?:\.default)?\.weight$", k)
+    if m:
+      out.setdefault(m.group(1), {})["down"] = t
+      continue
+    m = re.match(r"(.*)\.(lora_B|lora_up)(?:\.default)?\.weight$", k)
+    if m:
+      out.setdefault(m.group(1), {})["up"] = t
+      continue
+    m = re.match(r"(.*)\.alpha$", k)
+    if m:
+      out.setdefault(m.group(1), {})["alpha"] = float(t)
+      continue
+    m = re.match(r"(.*)\.diff_b$", k)
+    if m:
+      out.setdefault(m.group(1), {})["diff_b"] = t
+      continue
+    m = re.match(r"(.*)\.diff$", k)
+    if m:
+      out.setdefault(m.group(1), {})["diff"] = t
+  return out
+
+
+def lora_delta(entry: dict, scale: float = 1.0) -> Optional[torch.Tensor]:
+  if "down" not in entry or "up" not in entry:
+    return None
+  down, up = entry["down"].float(), entry["up"].float()
+  rank = down.shape[0]
+  alpha = entry.get("alpha", rank)
+  if down.dim() == 4:  # LoCon: conv k x k down, 1 x 1 up
+    delta = torch.einsum("or,rikl->oikl", up.flatten(1), down)
+  else:
+    delta = up @ down
+  return delta * (scale * alpha / rank)
+
+
+# diffusers Wan module path -> (our parameter, row slice of a fused matrix as (index, parts))
+def _wan_target(path: str):
+  m = re.match(r"blocks\.(\d+)\.(attn[12])\.(to_q|to_k|to_v|to_out\.0|add_k_proj|add_v_proj)$", path)
+  if m:
+    i, attn, proj = m.groups()
+    if proj == "to_out.0":
+      return f"blocks.{i}.{attn}.to_out", None
+    if attn == "attn1":
+      return f"blocks.{i}.attn1.to_qkv", (("to_q", "to_k", "to_v").index(proj), 3)
+    if proj == "to_q":
+      return f"blocks.{i}.attn2.to_q", None
+    if proj in ("to_k", "to_v"):
+      return f"blocks.{i}.attn2.to_kv", (("to_k", "to_v").index(proj), 2)
+    return f"blocks.{i}.attn2.add_kv_proj", (("add_k_proj", "add_v_proj").index(proj), 2)
+  m = re.match(r"blocks\.(\d+)\.ffn\.net\.(0\.proj|2)$", path)
+  if m:
+    return f"blocks.{m.group(1)}.{'ffn_in' if m.group(2) != '2' else 'ffn_out'}", None
+  m = re.match(r"blocks\.(\d+)\.(self_attn|cross_attn)\.(q|k|v|o)$", path)  # original Wan repo naming
+  if m:
+    i, attn, proj = m.groups()
+    mapped = {"q": "to_q", "k": "to_k", "v": "to_v", "o": "to_out.0"}[proj]
+    return _wan_target(f"blocks.{i}.{'attn1' if attn == 'self_attn' else 'attn2'}.{mapped}")
+  m = re.match(r"blocks\.(\d+)\.ffn\.(0|2)$", path)
+  if m:
+    return f"blocks.{m.group(1)}.{'ffn_in' if m.group(2) == '0' else 'ffn_out'}", None
+  return None, None
+
+
+@torch.no_grad()
+def merge_lora_into_wan(model, lora_sd: Dict[str, torch.Tensor], scale: float = 1.0) -> int:
+  """Adds the LoRA deltas to the (fused) Wan weights in place. Returns the number of merged modules."""
+  params = dict(model.named_parameters())
+  merged = 0
+  for path, entry in parse_lora_dict(lora_sd).items():
+    target, part = _wan_target(path)
+    if target is None or target + ".weight" not in params:
+      continue
+    w = params[target + ".weight"]
+    rows = slice(None)
+    if part is not None:
+      n = w.shape[0] // part[1]
+      rows = slice(part[0] * n, (part[0] + 1) * n)
+    delta = lora_delta(entry, scale)
+    if delta is not None:
+      w[rows] += delta.to(w.device, w.dtype)
+      merged += 1
+    if "diff" in entry:
+      w[rows] += entry["diff"].to(w.device, w.dtype) * scale
+    if "diff_b" in entry and target + ".bias" in params:
+      params[target + ".bias"][rows] += entry["diff_b"].to(w.device, w.dtype) * scale
+  return merged
+
+
+def merge_wan_loras(pipe, config) -> None:
+  from safetensors.torch import load_file
+
+  lc = config.lora_config
+  for path, name, scale in zip(lc["lora_model_name_or_path"], lc["weight_name"], lc.get("scale", [1.0] * 99)):
+    sd = load_file(os.path.join(path, name) if os.path.isdir(path) else path)
+    for m in filter(None, (pipe.transformer, pipe.transformer_2)):
+      merge_lora_into_wan(m, sd, float(scale))
+
+
+class LoRALinear(nn.Module):
+  """Run-time adapter around a Linear-like module: y = base(x) + sum_a scale_a * up_a(down_a(x))."""
+
+  def __init__(self, base: nn.Module):
+    super().__init__()
+    self.base = base
+    self.adapters = nn.ModuleDict()
+    self.scales: Dict[str, float] = {}
+
+  def add_adapter(self, name: str, down: torch.Tensor, up: torch.Tensor, scale: float):
+    a = nn.ModuleDict({"down": nn.Linear(down.shape[1], down.shape[0], bias=False), "up": nn.Linear(up.shape[1], up.shape[0], bias=False)})
+    w = self.base.weight
+    a["down"].weight.data = down.to(w.device, w.dtype)
+    a["up"].weight.data = up.to(w.device, w.dtype)
+    self.adapters[name] = a
+    self.scales[name] = scale
+
+  @property
+  def weight(self):
+    return self.base.weight
+
+  @property
+  def bias(self):
+    return self.base.bias
+
+  def forward(self, x, *args, **kw):
+    y = self.base(x, *args, **kw)
+    for name, a in self.adapters.items():
+      y = y + self.scales[name] * a["up"](a["down"](x))
+    return y
+
+
+def add_runtime_adapters(model: nn.Module, lora_sd: Dict[str, torch.Tensor], adapter_name: str, scale: float = 1.0,
+                         rename=lambda p: p) -> int:
+  """Wraps every targeted Linear of `model` with a `LoRALinear` (or adds one more adapter to an existing wrapper)."""
+  modules = dict(model.named_modules())
+  n = 0
+  for path, entry in parse_lora_dict(lora_sd).items():
+    target = rename(path.replace("_", ".") if path not in modules and path.replace("_", ".") in modules else path)
+    if target not in modules or "down" not in entry:
+      continue
+    mod = modules[target]
+    if not isinstance(mod, LoRALinear):
+      parent_name, _, leaf = target.rpartition(".")
+      parent = modules[parent_name] if parent_name else model
+      wrapped = LoRALinear(mod)
+      if leaf.isdigit():
+        parent[int(leaf)] = wrapped
+      else:
+        setattr(parent, leaf, wrapped)
+      modules[target] = mod = wrapped
+    rank = entry["down"].shape[0]
+    mod.add_adapter(adapter_name, entry["down"].flatten(1), entry["up"].flatten(1), scale * entry.get("alpha", rank) / rank)
+    n += 1
+  return n
+
+
+def apply_flux_loras(pipe, config) -> None:
+  from safetensors.torch import load_file
+
+  lc = config.lora_config
+  for path, name, adapter, scale in zip(lc["lora_model_name_or_path"], lc["weight_name"], lc["adapter_name"], lc.get("scale", [1.0] * 99)):
+    sd = load_file(os.path.join(path, name) if os.path.isdir(path) else path)
+    add_runtime_adapters(pipe.transformer, sd, adapter, float(scale))
