@@ -1,0 +1,49 @@
+"""Tile-search logic on the host: candidate ladders, timing that excludes warm-up, rank aggregation, CSV, cache."""
+import csv
+import os
+
+from maxdiffusion_b200.utils import tile_size_grid_search as T
+
+
+def test_candidate_math():
+  assert T.padding_of(4095, 128) == 1 and T.padding_of(4096, 128) == 0
+  assert T.block_for_count(4095, 16) == 256
+  assert T.feasible(T.Candidate(256, 128, 2)) and not T.feasible(T.Candidate(512, 256, 4))
+  assert T.tmem_columns(T.Candidate(256, 128)) == 512
+  grid = T.smart_grid(4095, 32760, n_ranks=8)
+  assert grid and all(T.feasible(c) for c in grid) and {c.copy_ctas for c in grid} == {8, 12, 16}
+
+
+def test_time_callable_excludes_warmup():
+  ticks = iter(range(1000))
+  calls = []
+  t = T.time_callable(lambda: calls.append(1), iters=4, warmup=3, timer=lambda: next(ticks))
+  assert len(calls) == 7 and t == 0.25
+
+
+def test_rank_aggregation():
+  assert T.aggregate_across_ranks([1.0, 3.0, 2.0]) == 3.0
+  assert T.aggregate_across_ranks([1.0, None]) is None
+
+
+class _MockBench:
+  """Synthetic cost model: cost falls with block_kv, one candidate fails."""
+
+  def setup(self, c):
+    if c.block_kv == 256:
+      raise MemoryError("synthetic out of memory")
+    import time
+    return lambda: time.sleep(0.001 * (3 - c.block_kv // 64))
+
+  def teardown(self):
+    pass
+
+
+def test_grid_search_csv_and_cache(tmp_path):
+  cands = [T.Candidate(256, 64), T.Candidate(256, 128), T.Candidate(128, 256)]
+  cache = str(tmp_path / "cache.json")
+  best = T.grid_search(_MockBench(), cands, iters=2, out_dir=str(tmp_path), cache_path=cache, cache_key="k", gather=lambda v: [v])
+  assert best == T.Candidate(256, 128)
+  rows = list(csv.DictReader(open(os.path.join(tmp_path, "tile_search.csv"))))
+  assert len(rows) == 3 and rows[2]["seconds"] == "failed"
+  assert T.grid_search(_MockBench(), [], cache_path=cache, cache_key="k") == best  # served from the cache
