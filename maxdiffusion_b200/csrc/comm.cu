@@ -9,6 +9,12 @@
 //                    pulls that slice of every rank's gradient buffer, sums the ranks in a fixed order
 //                    (bitwise reproducible), accumulates sum-of-squares / max-abs of the reduced gradient
 //                    and applies AdamW to its slice of weights and moments in the same pass.
+//   small_allreduce: one-shot all-reduce (sum / max) of a few KB: every rank publishes its vector in its own
+//                    symmetric buffer, signals, waits (bounded) for the others and reduces all vectors in rank order,
+//                    so every rank gets bitwise the same result. One launch, one CTA; two buffer halves alternate by
+//                    epoch so that a fast rank cannot overwrite data a slow rank still reads. Replaces the scalar
+//                    NCCL all-reduces of the gradient norm / max-abs / loss (reference: optax global-norm clipping,
+//                    src/maxdiffusion/max_utils.py:683-696) and the `process_allgather` of tile-search timings.
 //   peer_copy      : pull copy peer -> local with 16-byte vectors (used where a copy engine is not wanted)
 //
 // rs_adamw replaces NCCL reduce-scatter followed by the optax update of the reference
@@ -74,6 +80,54 @@ __global__ void peer_copy_kernel(const uint4* __restrict__ src, uint4* __restric
   for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < nvec;
        i += static_cast<long long>(gridDim.x) * blockDim.x) {
     dst[i] = src[i];
+  }
+}
+
+__device__ __forceinline__ float ld_relaxed_sys_f32(const float* addr) {
+  float v;
+  asm volatile("ld.relaxed.sys.global.f32 %0, [%1];" : "=f"(v) : "l"(addr) : "memory");
+  return v;
+}
+
+// bufs.p[r]: rank r's symmetric float buffer of 2 * cap elements; flags.p[r]: rank r's signal pad.
+// op 0 = sum, 1 = max. A wait that runs out reports {where = 110, detail = source rank} and leaves `out` untouched.
+__global__ void __launch_bounds__(256)
+small_allreduce_kernel(const float* __restrict__ in, float* __restrict__ out, int n, int op, PeerPtrs bufs,
+                       PeerFlagPtrs flags, int world, int rank, int slot_base, int cap, unsigned int epoch,
+                       unsigned long long budget_ns, DeviceStatus* status) {
+  __shared__ int failed;
+  if (threadIdx.x == 0) failed = 0;
+  const int half = static_cast<int>(epoch & 1u) * cap;
+  float* mine = const_cast<float*>(static_cast<const float*>(bufs.p[rank])) + half;
+  for (int i = threadIdx.x; i < n; i += blockDim.x) mine[i] = in[i];
+  __syncthreads();
+  if (threadIdx.x < world) {
+    __threadfence_system();
+    st_release_sys(flags.p[threadIdx.x] + slot_base + rank, epoch);
+    const unsigned int* my_flag = flags.p[rank] + slot_base + threadIdx.x;
+    const uint64_t t0 = global_timer_ns();
+    unsigned int spins = 0;
+    while (ld_acquire_sys(my_flag) < epoch) {
+      if ((++spins & 0x3fu) == 0u) {
+        __nanosleep(100);
+        if (global_timer_ns() - t0 > budget_ns) {
+          report_status(status, kStatusFlagTimeout, 110, threadIdx.x);
+          atomicExch(&failed, 1);
+          break;
+        }
+      }
+    }
+    __threadfence_system();
+  }
+  __syncthreads();
+  if (failed) return;
+  for (int i = threadIdx.x; i < n; i += blockDim.x) {
+    float acc = ld_relaxed_sys_f32(static_cast<const float*>(bufs.p[0]) + half + i);
+    for (int r = 1; r < world; ++r) {
+      const float v = ld_relaxed_sys_f32(static_cast<const float*>(bufs.p[r]) + half + i);
+      acc = op == 0 ? acc + v : fmaxf(acc, v);
+    }
+    out[i] = acc;
   }
 }
 
@@ -241,6 +295,24 @@ extern "C" int mdb_memcpy_async(void* dst, const void* src, long long nbytes, vo
   if (nbytes <= 0) return 0;
   return static_cast<int>(cudaMemcpyAsync(dst, src, static_cast<size_t>(nbytes), cudaMemcpyDeviceToDevice,
                                           static_cast<cudaStream_t>(stream)));
+}
+
+// buf_ptrs / flag_ptrs: `world` device addresses (this rank's own included). n <= cap floats; epoch must grow by
+// one per call on every rank of the group.
+extern "C" int mdb_small_allreduce(const float* in, float* out, int n, int op, const unsigned long long* buf_ptrs,
+                                   const unsigned long long* flag_ptrs, int world, int rank, int slot_base, int cap,
+                                   unsigned int epoch, double budget_s, void* stream) {
+  if (world < 1 || world > MAX_RANKS || n < 1 || n > cap || rank < 0 || rank >= world || epoch == 0) return 3405;
+  PeerPtrs b;
+  PeerFlagPtrs f;
+  for (int i = 0; i < MAX_RANKS; ++i) {
+    b.p[i] = i < world ? reinterpret_cast<const void*>(buf_ptrs[i]) : nullptr;
+    f.p[i] = i < world ? reinterpret_cast<unsigned int*>(flag_ptrs[i]) : nullptr;
+  }
+  small_allreduce_kernel<<<1, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      in, out, n, op, b, f, world, rank, slot_base, cap, epoch, static_cast<unsigned long long>(budget_s * 1e9),
+      status_buffer());
+  return static_cast<int>(cudaGetLastError());
 }
 
 // grad_ptrs[r]: address of rank r's gradient slice for this owner (bf16, n elements, n % 8 == 0).

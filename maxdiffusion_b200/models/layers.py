@@ -56,6 +56,15 @@ class RMSNorm(nn.Module):
     return y.to(x.dtype)
 
 
+class GroupNorm(nn.GroupNorm):
+  """GroupNorm with an optional fused SiLU (`act=True`); parameter names are those of `torch.nn.GroupNorm`.
+
+  reference: the GroupNorm -> swish pairs of src/maxdiffusion/models/resnet_flax.py:150-176."""
+
+  def forward(self, x, act: bool = False):
+    return OF.group_norm(x, self.num_groups, self.weight, self.bias, self.eps, act)
+
+
 class FP32LayerNorm(nn.Module):
   """LayerNorm with statistics in fp32 (reference: src/maxdiffusion/models/normalization_flax.py:160-180)."""
 

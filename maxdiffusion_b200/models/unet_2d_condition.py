@@ -7,7 +7,7 @@ parameter names follow the diffusers `UNet2DConditionModel` checkpoint so that i
 
 GEMMs (projections, GEGLU feed-forward, attention in/out) run on the tcgen05 GEMM through `ops.functional.linear`
 for bf16 CUDA tensors; attention with head_dim 128 uses the flash kernel, other head sizes (64 for SDXL, 40..160
-for SD 1.x/2.x) go through `scaled_dot_product_attention`; convolutions and GroupNorm use cuDNN / PyTorch.
+for SD 1.x/2.x) go through `scaled_dot_product_attention`; convolutions use cuDNN; GroupNorm(+SiLU) is the fused kernel of `ops.functional.group_norm`.
 """
 from __future__ import annotations
 
@@ -19,7 +19,7 @@ import torch.nn as nn
 import torch.nn.functional as F
 
 from ..ops import functional as OF
-from .layers import Linear, sinusoidal_embedding
+from .layers import GroupNorm, Linear, sinusoidal_embedding
 from .vae import ResnetBlock2D
 
 
@@ -129,7 +129,7 @@ class Transformer2DModel(nn.Module):
   def __init__(self, dim, heads, depth, cross_dim, groups, linear_proj):
     super().__init__()
     self.linear_proj = linear_proj
-    self.norm = nn.GroupNorm(groups, dim, eps=1e-6)
+    self.norm = GroupNorm(groups, dim, eps=1e-6)
     self.proj_in = Linear(dim, dim) if linear_proj else nn.Conv2d(dim, dim, 1)
     self.transformer_blocks = nn.ModuleList([BasicTransformerBlock(dim, heads, cross_dim) for _ in range(depth)])
     self.proj_out = Linear(dim, dim) if linear_proj else nn.Conv2d(dim, dim, 1)
@@ -265,7 +265,7 @@ class UNet2DConditionModel(nn.Module):
       ups.append(UpBlock(cin_skip, cout, prev, temb, cfg.layers_per_block + 1, g, attn(j) if "CrossAttn" in kind else None, add_up=i < n - 1))
       prev = cout
     self.up_blocks = nn.ModuleList(ups)
-    self.conv_norm_out = nn.GroupNorm(g, ch[0], eps=1e-5)
+    self.conv_norm_out = GroupNorm(g, ch[0], eps=1e-5)
     self.conv_out = nn.Conv2d(ch[0], cfg.out_channels, 3, padding=1)
 
   def time_embed(self, timesteps, dtype, added_cond_kwargs=None):
@@ -298,4 +298,4 @@ class UNet2DConditionModel(nn.Module):
       x = x + mid_block_additional_residual
     for blk in self.up_blocks:
       x = blk(x, skips, emb, ctx)
-    return self.conv_out(F.silu(self.conv_norm_out(x)))
+    return self.conv_out(self.conv_norm_out(x, act=True))

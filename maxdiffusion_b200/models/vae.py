@@ -1,7 +1,7 @@
 """AutoencoderKL for SD 1.x / 2.x / SDXL (4 latent channels) and Flux (16 channels, shift + scale).
 
 Reference: `FlaxAutoencoderKL` and `FlaxDiagonalGaussianDistribution` (src/maxdiffusion/models/vae_flax.py:723-1020).
-Module and parameter names follow the diffusers `AutoencoderKL` checkpoint. Convolutions and GroupNorm run through
+Module and parameter names follow the diffusers `AutoencoderKL` checkpoint. Convolutions run through
 cuDNN / PyTorch; the single-head mid-block attention uses `ops.functional.attention`.
 """
 from __future__ import annotations
@@ -14,6 +14,7 @@ import torch.nn as nn
 import torch.nn.functional as F
 
 from ..ops import functional as OF
+from .layers import GroupNorm
 
 
 @dataclass
@@ -47,18 +48,18 @@ class ResnetBlock2D(nn.Module):
 
   def __init__(self, cin, cout, groups=32, temb_channels: Optional[int] = None, eps=1e-6):
     super().__init__()
-    self.norm1 = nn.GroupNorm(groups, cin, eps=eps)
+    self.norm1 = GroupNorm(groups, cin, eps=eps)
     self.conv1 = nn.Conv2d(cin, cout, 3, padding=1)
     self.time_emb_proj = nn.Linear(temb_channels, cout) if temb_channels else None
-    self.norm2 = nn.GroupNorm(groups, cout, eps=eps)
+    self.norm2 = GroupNorm(groups, cout, eps=eps)
     self.conv2 = nn.Conv2d(cout, cout, 3, padding=1)
     self.conv_shortcut = nn.Conv2d(cin, cout, 1) if cin != cout else None
 
   def forward(self, x, temb=None):
-    h = self.conv1(F.silu(self.norm1(x)))
+    h = self.conv1(self.norm1(x, act=True))
     if self.time_emb_proj is not None and temb is not None:
       h = h + self.time_emb_proj(F.silu(temb))[:, :, None, None]
-    h = self.conv2(F.silu(self.norm2(h)))
+    h = self.conv2(self.norm2(h, act=True))
     return (self.conv_shortcut(x) if self.conv_shortcut is not None else x) + h
 
 
@@ -66,7 +67,7 @@ class SpatialSelfAttention(nn.Module):
 
   def __init__(self, dim, groups=32, eps=1e-6):
     super().__init__()
-    self.group_norm = nn.GroupNorm(groups, dim, eps=eps)
+    self.group_norm = GroupNorm(groups, dim, eps=eps)
     self.to_q, self.to_k, self.to_v = nn.Linear(dim, dim), nn.Linear(dim, dim), nn.Linear(dim, dim)
     self.to_out = nn.ModuleList([nn.Linear(dim, dim)])
 
@@ -132,14 +133,14 @@ class Encoder(nn.Module):
         _Block(ch[max(i - 1, 0)], ch[i], cfg.layers_per_block, cfg.norm_num_groups, down=True if i < len(ch) - 1 else None)
         for i in range(len(ch))])
     self.mid_block = _Mid(ch[-1], cfg.norm_num_groups)
-    self.conv_norm_out = nn.GroupNorm(cfg.norm_num_groups, ch[-1], eps=1e-6)
+    self.conv_norm_out = GroupNorm(cfg.norm_num_groups, ch[-1], eps=1e-6)
     self.conv_out = nn.Conv2d(ch[-1], 2 * cfg.latent_channels, 3, padding=1)
 
   def forward(self, x):
     x = self.conv_in(x)
     for b in self.down_blocks:
       x = b(x)
-    return self.conv_out(F.silu(self.conv_norm_out(self.mid_block(x))))
+    return self.conv_out(self.conv_norm_out(self.mid_block(x), act=True))
 
 
 class Decoder(nn.Module):
@@ -152,14 +153,14 @@ class Decoder(nn.Module):
     self.up_blocks = nn.ModuleList([
         _Block(ch[max(i - 1, 0)], ch[i], cfg.layers_per_block + 1, cfg.norm_num_groups, down=False if i < len(ch) - 1 else None)
         for i in range(len(ch))])
-    self.conv_norm_out = nn.GroupNorm(cfg.norm_num_groups, ch[-1], eps=1e-6)
+    self.conv_norm_out = GroupNorm(cfg.norm_num_groups, ch[-1], eps=1e-6)
     self.conv_out = nn.Conv2d(ch[-1], cfg.out_channels, 3, padding=1)
 
   def forward(self, z):
     x = self.mid_block(self.conv_in(z))
     for b in self.up_blocks:
       x = b(x)
-    return self.conv_out(F.silu(self.conv_norm_out(x)))
+    return self.conv_out(self.conv_norm_out(x, act=True))
 
 
 class DiagonalGaussianDistribution:

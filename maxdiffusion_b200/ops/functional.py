@@ -365,3 +365,64 @@ def checkpoint_block(fn, *tensor_args, extra_args: Sequence = (), save_attention
   once the parameter gradients of the block are complete (the FSDP engine reduces and applies them there).
   """
   return _CheckpointFn.apply(fn, save_attention, on_backward_done, len(tensor_args), *tensor_args, *extra_args)
+
+
+# ---------------------------------------------------------------------------------------------
+# GroupNorm (+SiLU) and the elementwise step family
+# ---------------------------------------------------------------------------------------------
+class _GroupNormFn(torch.autograd.Function):
+
+  @staticmethod
+  def forward(ctx, x, gamma, beta, groups, eps, act):
+    y, stats = K.groupnorm_fwd(x, groups, gamma, beta, eps, act)
+    ctx.save_for_backward(x, gamma, beta, stats)
+    ctx.groups, ctx.act = groups, act
+    return y
+
+  @staticmethod
+  def backward(ctx, dy):
+    x, gamma, beta, stats = ctx.saved_tensors
+    dx, dgamma, dbeta = K.groupnorm_bwd(dy, x, stats, ctx.groups, gamma, beta, ctx.act)
+    return (dx, dgamma.to(gamma.dtype) if gamma is not None else None,
+            dbeta.to(beta.dtype) if beta is not None else None, None, None, None)
+
+
+def group_norm(x, groups: int, gamma=None, beta=None, eps: float = 1e-6, act: bool = False):
+  """GroupNorm over a channels-first tensor [N, C, *spatial] with optional fused SiLU."""
+  if x.is_cuda and x.dtype in (torch.bfloat16, torch.float32):
+    x = x if x.is_contiguous() else x.contiguous()
+    return _GroupNormFn.apply(x, gamma, beta, groups, eps, act)
+  return ref.group_norm(x, groups, gamma, beta, eps, act)
+
+
+def lincomb(xs, coefs, out_dtype=None):
+  """sum_i coefs[(b,) i] * xs[i]; no gradient (sampling-loop updates)."""
+  x0 = xs[0]
+  per = x0.numel() // (len(coefs) if isinstance(coefs[0], (list, tuple)) else 1)
+  if x0.is_cuda and per % 8 == 0 and all(x.dtype in (torch.bfloat16, torch.float32) for x in xs):
+    return K.lincomb(list(xs), coefs, out_dtype=out_dtype)
+  return ref.lincomb(xs, coefs, out_dtype)
+
+
+class _MseFn(torch.autograd.Function):
+
+  @staticmethod
+  def forward(ctx, pred, target, weights):
+    loss, dpred = K.mse_fwd_bwd(pred, target, weights, need_grad=True)
+    ctx.save_for_backward(dpred)
+    return loss
+
+  @staticmethod
+  def backward(ctx, dloss):
+    (dpred,) = ctx.saved_tensors
+    return dpred * dloss.to(dpred.dtype), None, None
+
+
+def weighted_mse(pred, target, weights=None):
+  """mean over all elements of w_b * (pred - target)^2; the gradient with respect to pred comes from the same pass."""
+  B = pred.shape[0]
+  if (pred.is_cuda and pred.dtype in (torch.bfloat16, torch.float32) and target.dtype in (torch.bfloat16, torch.float32)
+      and B <= 16 and (pred.numel() // B) % 8 == 0):
+    w = None if weights is None else [float(v) for v in (weights.tolist() if torch.is_tensor(weights) else weights)]
+    return _MseFn.apply(pred, target.detach(), w)
+  return ref.weighted_mse(pred, target, weights)

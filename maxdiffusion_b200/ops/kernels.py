@@ -281,3 +281,186 @@ def sumsq_maxabs(x, out=None, accumulate=False):
                                    _lib.ptr(scratch), int(accumulate), _lib.stream())
   _lib.check(rc, "mdb_sumsq_maxabs")
   return out
+
+
+# ---------------------------------------------------------------------------------------------
+# elementwise step family and GroupNorm
+# ---------------------------------------------------------------------------------------------
+def _declare_extra(L):
+  c_void_p, c_int, c_ll, c_float = ctypes.c_void_p, ctypes.c_int, ctypes.c_longlong, ctypes.c_float
+  L.mdb_lincomb.argtypes = [c_void_p, c_int, c_int, ctypes.POINTER(c_void_p), ctypes.POINTER(c_int),
+                            ctypes.POINTER(c_float), c_int, c_ll, c_void_p, c_int, c_void_p]
+  L.mdb_lincomb.restype = c_int
+  L.mdb_mse_fwd_bwd.argtypes = [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, ctypes.POINTER(c_float), c_int, c_ll,
+                                c_float, c_void_p, c_int, c_void_p]
+  L.mdb_mse_fwd_bwd.restype = c_int
+  L.mdb_channel_affine.argtypes = [c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_int, c_ll, c_int, c_ll,
+                                   c_void_p]
+  L.mdb_channel_affine.restype = c_int
+  L.mdb_to_uint8.argtypes = [c_void_p, c_int, c_void_p, c_ll, c_void_p]
+  L.mdb_to_uint8.restype = c_int
+  L.mdb_blend_ramp.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_ll, ctypes.POINTER(c_ll), c_int, c_ll, c_void_p]
+  L.mdb_blend_ramp.restype = c_int
+  L.mdb_groupnorm_fwd.argtypes = [c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_ll,
+                                  c_int, c_float, c_int, c_void_p, c_void_p, c_void_p]
+  L.mdb_groupnorm_fwd.restype = c_int
+  L.mdb_groupnorm_bwd.argtypes = [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int,
+                                  c_int, c_ll, c_int, c_int, c_void_p, c_void_p, c_void_p]
+  L.mdb_groupnorm_bwd.restype = c_int
+
+
+_lib.register(_declare_extra)
+
+_PARTIAL_BLOCKS = 148 * 4
+
+
+def _is_f32(t):
+  assert t.dtype in (torch.float32, torch.bfloat16), t.dtype
+  return int(t.dtype == torch.float32)
+
+
+def lincomb(xs: Sequence[torch.Tensor], coefs, out_dtype=None, out=None, want_sumsq: bool = False):
+  """out = sum_i coefs[b][i] * xs[i]. `coefs` is [n_in] (shared) or [B][n_in] (per sample along dim 0).
+
+  All inputs share one shape (bf16 or fp32 each). Returns out, or (out, sum(out^2) as a 0-d fp32 tensor)."""
+  x0 = xs[0]
+  n_in = len(xs)
+  assert 1 <= n_in <= 6
+  xs = [x if x.is_contiguous() else x.contiguous() for x in xs]
+  for x in xs:
+    assert x.shape == x0.shape
+  rows = list(coefs) if isinstance(coefs[0], (list, tuple)) else [list(coefs)]
+  B = len(rows)
+  assert B <= 16 and (B == 1 or B == x0.shape[0])
+  n = x0.numel()
+  per_batch = n // B
+  assert per_batch % 8 == 0, "element count per sample must be a multiple of 8"
+  if out is None:
+    out = torch.empty(x0.shape, device=x0.device, dtype=out_dtype or x0.dtype)
+  assert out.is_contiguous()
+  ptrs = (ctypes.c_void_p * n_in)(*[x.data_ptr() for x in xs])
+  f32s = (ctypes.c_int * n_in)(*[_is_f32(x) for x in xs])
+  flat = [float(c) for r in rows for c in r]
+  cf = (ctypes.c_float * len(flat))(*flat)
+  partial = torch.empty((_PARTIAL_BLOCKS,), device=x0.device, dtype=torch.float32) if want_sumsq else None
+  rc = _lib.lib().mdb_lincomb(_lib.ptr(out), _is_f32(out), n_in, ptrs, f32s, cf, B, per_batch, _lib.ptr(partial),
+                              _PARTIAL_BLOCKS, _lib.stream())
+  _lib.check(rc, "mdb_lincomb")
+  return (out, partial.sum()) if want_sumsq else out
+
+
+def mse_fwd_bwd(pred, target, weights=None, need_grad: bool = True, grad_dtype=None):
+  """loss = sum_b w_b * sum (pred-target)^2 / numel and d(loss)/d(pred) in one pass. Returns (loss, dpred)."""
+  pred = pred if pred.is_contiguous() else pred.contiguous()
+  target = target if target.is_contiguous() else target.contiguous()
+  assert pred.shape == target.shape
+  B = pred.shape[0] if weights is not None else 1
+  w = [float(x) for x in weights] if weights is not None else [1.0]
+  assert len(w) == B and B <= 16
+  n = pred.numel()
+  per_batch = n // B
+  assert per_batch % 8 == 0
+  dpred = torch.empty(pred.shape, device=pred.device, dtype=grad_dtype or pred.dtype) if need_grad else None
+  partial = torch.empty((_PARTIAL_BLOCKS,), device=pred.device, dtype=torch.float32)
+  wf = (ctypes.c_float * B)(*w)
+  rc = _lib.lib().mdb_mse_fwd_bwd(_lib.ptr(pred), _is_f32(pred), _lib.ptr(target), _is_f32(target), _lib.ptr(dpred),
+                                  _is_f32(dpred) if need_grad else 0, wf, B, per_batch, 2.0 / n, _lib.ptr(partial),
+                                  _PARTIAL_BLOCKS, _lib.stream())
+  _lib.check(rc, "mdb_mse_fwd_bwd")
+  return partial.sum() / n, dpred
+
+
+def channel_affine(x, mean, scale, channel_dim: int, denorm: bool = False, out_dtype=None):
+  """(x - mean[c]) * scale[c], or x * scale[c] + mean[c] with `denorm`; c indexes `channel_dim`."""
+  x = x if x.is_contiguous() else x.contiguous()
+  C = x.shape[channel_dim]
+  inner = 1
+  for d in x.shape[channel_dim + 1:]:
+    inner *= d
+  out = torch.empty(x.shape, device=x.device, dtype=out_dtype or x.dtype)
+  mean = mean.to(device=x.device, dtype=torch.float32).contiguous()
+  scale = scale.to(device=x.device, dtype=torch.float32).contiguous()
+  assert mean.numel() == C and scale.numel() == C
+  rc = _lib.lib().mdb_channel_affine(_lib.ptr(x), _is_f32(x), _lib.ptr(out), _is_f32(out), _lib.ptr(mean),
+                                     _lib.ptr(scale), C, inner, int(denorm), x.numel(), _lib.stream())
+  _lib.check(rc, "mdb_channel_affine")
+  return out
+
+
+def to_uint8(x):
+  """clamp(x/2 + 0.5, 0, 1) * 255, rounded to uint8."""
+  x = x if x.is_contiguous() else x.contiguous()
+  n = x.numel()
+  assert n % 8 == 0
+  out = torch.empty(x.shape, device=x.device, dtype=torch.uint8)
+  _lib.check(_lib.lib().mdb_to_uint8(_lib.ptr(x), _is_f32(x), _lib.ptr(out), n, _lib.stream()), "mdb_to_uint8")
+  return out
+
+
+def blend_ramp(a, b, dim: int):
+  """a * (1 - i/extent) + b * (i/extent) along `dim` (i the index along it); a and b are views of equal shape whose
+  dims after `dim` are contiguous and whose dims before `dim` collapse to one stride."""
+  assert a.shape == b.shape and a.dtype == b.dtype
+  extent = a.shape[dim]
+  inner = 1
+  for d in a.shape[dim + 1:]:
+    inner *= d
+  outer = a.numel() // (extent * inner)
+
+  def strides(t):
+    tt = t.reshape(outer, extent, inner) if t.is_contiguous() else None
+    if tt is None:
+      tt = t.contiguous().reshape(outer, extent, inner)
+    return tt, tt.stride(0), tt.stride(1)
+
+  a3, ao, ae = strides(a)
+  b3, bo, be = strides(b)
+  out = torch.empty((outer, extent, inner), device=a.device, dtype=a.dtype)
+  st = (ctypes.c_longlong * 6)(ao, bo, out.stride(0), ae, be, out.stride(1))
+  rc = _lib.lib().mdb_blend_ramp(_lib.ptr(a3), _lib.ptr(b3), _lib.ptr(out), _is_f32(a), outer, st, extent, inner,
+                                 _lib.stream())
+  _lib.check(rc, "mdb_blend_ramp")
+  return out.reshape(a.shape)
+
+
+def _gn_splits(N, C, hw):
+  rows = N * C
+  s = max(1, min((_TARGET_CTAS + rows - 1) // rows, hw // 2048))
+  return int(min(s, 64))
+
+
+def groupnorm_fwd(x, groups, gamma=None, beta=None, eps=1e-6, act: bool = False, save_stats: bool = True):
+  """GroupNorm over [N, C, *spatial] (contiguous), optional fused SiLU. Returns (y, mean_rstd [N, G, 2] or None)."""
+  assert x.is_contiguous()
+  N, C = x.shape[:2]
+  hw = x.numel() // (N * C)
+  S = _gn_splits(N, C, hw)
+  y = torch.empty_like(x)
+  partial = torch.empty((N * C * S, 2), device=x.device, dtype=torch.float32)
+  stats = torch.empty((N, groups, 2), device=x.device, dtype=torch.float32) if save_stats else None
+  g32 = gamma.float().contiguous() if gamma is not None else None
+  b32 = beta.float().contiguous() if beta is not None else None
+  rc = _lib.lib().mdb_groupnorm_fwd(_lib.ptr(x), _is_f32(x), _lib.ptr(y), _is_f32(y), _lib.ptr(g32), _lib.ptr(b32), N, C,
+                                    groups, hw, S, float(eps), int(act), _lib.ptr(partial), _lib.ptr(stats),
+                                    _lib.stream())
+  _lib.check(rc, "mdb_groupnorm_fwd")
+  return y, stats
+
+
+def groupnorm_bwd(dy, x, stats, groups, gamma=None, beta=None, act: bool = False):
+  """Returns (dx, dgamma fp32 [C], dbeta fp32 [C])."""
+  assert x.is_contiguous()
+  dy = dy if dy.is_contiguous() else dy.contiguous()
+  N, C = x.shape[:2]
+  hw = x.numel() // (N * C)
+  S = _gn_splits(N, C, hw)
+  dx = torch.empty_like(x)
+  partial = torch.empty((N, C, S, 2), device=x.device, dtype=torch.float32)
+  g32 = gamma.float().contiguous() if gamma is not None else None
+  b32 = beta.float().contiguous() if beta is not None else None
+  rc = _lib.lib().mdb_groupnorm_bwd(_lib.ptr(dy), _is_f32(dy), _lib.ptr(x), _is_f32(x), _lib.ptr(dx), _is_f32(dx),
+                                    _lib.ptr(g32), _lib.ptr(b32), N, C, groups, hw, S, int(act), _lib.ptr(stats),
+                                    _lib.ptr(partial), _lib.stream())
+  _lib.check(rc, "mdb_groupnorm_bwd")
+  sums = partial.sum(dim=(0, 2))
+  return dx, sums[:, 1], sums[:, 0]

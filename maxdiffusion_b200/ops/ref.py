@@ -157,3 +157,51 @@ def adamw_step(p, g, m, v, *, lr, b1, b2, eps, wd, step, grad_scale=1.0, clip_va
 def sumsq_maxabs(x):
   xf = x.float()
   return torch.stack([(xf * xf).sum(), xf.abs().max()])
+
+
+def group_norm(x, groups, gamma=None, beta=None, eps=1e-6, act=False):
+  y = torch.nn.functional.group_norm(x.float(), groups, None if gamma is None else gamma.float(),
+                                     None if beta is None else beta.float(), eps)
+  if act:
+    y = torch.nn.functional.silu(y)
+  return y.to(x.dtype)
+
+
+def lincomb(xs, coefs, out_dtype=None):
+  x0 = xs[0]
+  rows = list(coefs) if isinstance(coefs[0], (list, tuple)) else [list(coefs)]
+  c = torch.tensor(rows, dtype=torch.float32, device=x0.device)  # [B or 1, n_in]
+  shape = [c.shape[0]] + [1] * (x0.dim() - 1)
+  acc = torch.zeros(x0.shape, dtype=torch.float32, device=x0.device)
+  for i, x in enumerate(xs):
+    acc = acc + c[:, i].reshape(shape) * x.float()
+  return acc.to(out_dtype or x0.dtype)
+
+
+def weighted_mse(pred, target, weights=None):
+  e = (pred.float() - target.float()) ** 2
+  if weights is not None:
+    w = torch.as_tensor(weights, dtype=torch.float32, device=pred.device)
+    e = e * w.reshape([-1] + [1] * (pred.dim() - 1))
+  return e.mean()
+
+
+def to_uint8(x):
+  return ((x.float() * 0.5 + 0.5).clamp(0, 1) * 255.0).round().to(torch.uint8)
+
+
+def channel_affine(x, mean, scale, channel_dim, denorm=False, out_dtype=None):
+  shape = [1] * x.dim()
+  shape[channel_dim] = -1
+  m = mean.float().to(x.device).reshape(shape)
+  s = scale.float().to(x.device).reshape(shape)
+  y = x.float() * s + m if denorm else (x.float() - m) * s
+  return y.to(out_dtype or x.dtype)
+
+
+def blend_ramp(a, b, dim):
+  n = a.shape[dim]
+  shape = [1] * a.dim()
+  shape[dim] = n
+  w = (torch.arange(n, device=a.device, dtype=torch.float32) / n).reshape(shape)
+  return (a.float() * (1 - w) + b.float() * w).to(a.dtype)

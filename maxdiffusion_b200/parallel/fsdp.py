@@ -152,6 +152,7 @@ class FSDPEngine:
       self.pending: list[tuple[int, torch.Tensor]] = []  # shard grads kept for global-norm clipping
 
     self.peer = None
+    self._small_ar = None
     if self.world > 1:
       self.slots = [torch.empty(self.max_numel, dtype=param_dtype, device=self.device) for _ in range(2)]
       self.grad_slots = [torch.zeros(self.max_numel, dtype=param_dtype, device=self.device) for _ in range(2)] if train else []
@@ -160,6 +161,7 @@ class FSDPEngine:
 
         if symm.peer_memory_available(group):
           self.peer = symm.PeerGroup(group)
+          self._small_ar = symm.SmallAllReduce(self.peer)
           self.sym_grad, self.sym_grad_ptrs = [], []
           for _ in range(2):
             t, ptrs, _h = self.peer.alloc(self.max_numel, param_dtype)
@@ -355,7 +357,10 @@ class FSDPEngine:
     if self.replica_group is not None:
       dist.all_reduce(root_grad, group=self.replica_group)
     stats = self.grad_stats.clone()
-    if self.group is not None:
+    if self.group is not None and self.peer is not None:
+      # one-launch peer-memory all-reduces (sum of squares, max-abs); identical bits on every rank
+      stats = torch.cat([self._small_ar(stats[0:1].contiguous(), "sum"), self._small_ar(stats[1:2].contiguous(), "max")])
+    elif self.group is not None:
       sq, mx = stats[0:1].clone(), stats[1:2].clone()
       dist.all_reduce(sq, group=self.group)
       dist.all_reduce(mx, op=dist.ReduceOp.MAX, group=self.group)

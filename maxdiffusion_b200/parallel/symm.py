@@ -27,6 +27,7 @@ FLAG_KV_READY = 2
 FLAG_KV_ACK = 3
 FLAG_SHARD_READY = 4
 FLAG_USER = 5
+FLAG_SMALL_AR = 6
 NUM_FLAG_KINDS = 8
 WAIT_BUDGET_S = 5.0
 
@@ -47,6 +48,9 @@ def _declare(L):
   L.mdb_rs_adamw.argtypes = ([ullp, c_int, c_ll] + [c_void_p] * 6 + [c_int] + [c_float] * 9 +
                              [ctypes.c_ulonglong, c_int, c_int, c_int, c_void_p])
   L.mdb_rs_adamw.restype = c_int
+  L.mdb_small_allreduce.argtypes = [c_void_p, c_void_p, c_int, c_int, ullp, ullp, c_int, c_int, c_int, c_int, c_uint,
+                                    ctypes.c_double, c_void_p]
+  L.mdb_small_allreduce.restype = c_int
 
 
 _lib.register(_declare)
@@ -115,6 +119,36 @@ class PeerGroup:
         rc = _lib.lib().mdb_wait_flags(ctypes.c_void_p(base + 4 * s), 1, 1, int(value), WAIT_BUDGET_S,
                                        stream if stream is not None else _lib.stream())
         _lib.check(rc, "mdb_wait_flags")
+
+
+class SmallAllReduce:
+  """One-launch all-reduce (sum or max) of up to `capacity` fp32 values over peer memory.
+
+  Every rank reduces all ranks' vectors in rank order, so the result is bitwise identical everywhere. Calls must be
+  made by every rank of the group in the same order (each call advances the epoch by one)."""
+
+  def __init__(self, peers: "PeerGroup", capacity: int = 4096):
+    self.peers = peers
+    self.capacity = capacity
+    self.buf, self.buf_ptrs, self._hdl = peers.alloc(2 * capacity, torch.float32)
+    self.buf.zero_()
+    self.epoch = 0
+    n = peers.world
+    self._bufs = (ctypes.c_ulonglong * n)(*self.buf_ptrs)
+    self._flags = (ctypes.c_ulonglong * n)(*peers.flag_ptrs)
+    torch.cuda.synchronize()
+    dist.barrier(group=peers.group)
+
+  def __call__(self, x: torch.Tensor, op: str = "sum", out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    assert x.dtype == torch.float32 and x.is_contiguous() and 0 < x.numel() <= self.capacity
+    out = torch.empty_like(x) if out is None else out
+    self.epoch += 1
+    rc = _lib.lib().mdb_small_allreduce(_lib.ptr(x), _lib.ptr(out), x.numel(), {"sum": 0, "max": 1}[op], self._bufs,
+                                        self._flags, self.peers.world, self.peers.rank,
+                                        FLAG_SMALL_AR * self.peers.world, self.capacity, self.epoch, WAIT_BUDGET_S,
+                                        _lib.stream())
+    _lib.check(rc, "mdb_small_allreduce")
+    return out
 
 
 def set_flag(flag_tensor: torch.Tensor, index: int, value: int, stream=None) -> None:

@@ -16,6 +16,7 @@ import torch
 from ...models.controlnet import ControlNetModel
 from ...models.unet_2d_condition import UNet2DConditionModel
 from ...models.vae import VAE_PRESETS, AutoencoderKL, VAEConfig
+from ...ops import functional as OF
 from ...schedulers import SCHEDULERS
 from ...trainers.stable_diffusion_trainer import get_add_time_ids, resolve_unet_config
 
@@ -124,7 +125,7 @@ class StableDiffusionPipeline:
       noise = self.unet(x.to(self.dtype), tt, embeds, added, **extra).float()
       if do_cfg:
         uncond, text = noise.chunk(2)
-        noise = uncond + g_scale * (text - uncond)
+        noise = OF.lincomb([text, uncond], [g_scale, 1.0 - g_scale])
         if g_rescale > 0:
           noise = rescale_noise_cfg(noise, text, g_rescale)
       latents, state = self.scheduler.step(state, noise, t, latents)

@@ -23,6 +23,7 @@ import torch.distributed as dist
 from ... import max_logging
 from ...models.wan.autoencoder_kl_wan import AutoencoderKLWan, WanVAEConfig, postprocess_video
 from ...models.wan.transformer_wan import WAN_PRESETS, WanConfig, WanModel, wan_rope_tables
+from ...ops import functional as OF
 from ...parallel.context import ContextParallel
 from ...parallel.mesh import DeviceMesh, create_device_mesh
 from ...schedulers.scheduling_unipc_multistep import UniPCMultistepScheduler
@@ -245,7 +246,7 @@ class WanPipeline:
         cond = self._forward(model, lat_in, t, prompt_embeds, image_embeds, kv_cache=None, rope=rope).float()
         w1, w2 = CP.cfg_cache_weights(i, steps)
         uncond = CP.fft_compensate(cond, cached_cond, cached_uncond, w1, w2)
-        noise = uncond + g_scale * (cond - uncond)
+        noise = OF.lincomb([cond, uncond], [g_scale, 1.0 - g_scale])
         cached_cond = cond
       else:
         skip = mag_sched[i] and cached_residual is not None
@@ -262,12 +263,12 @@ class WanPipeline:
         out = out.float()
         if do_cfg and not cfg_split:
           cond, uncond = out[:B], out[B:]
-          noise = uncond + g_scale * (cond - uncond)
+          noise = OF.lincomb([cond, uncond], [g_scale, 1.0 - g_scale])
           cached_cond, cached_uncond = cond, uncond
         elif cfg_split:
           both = [torch.empty_like(out) for _ in range(2)]
           dist.all_gather(both, out.contiguous(), group=self.mesh.group("data"))
-          noise = both[1] + g_scale * (both[0] - both[1])
+          noise = OF.lincomb([both[0], both[1]], [g_scale, 1.0 - g_scale])
         else:
           noise = out
         if sen is not None:

@@ -17,6 +17,8 @@ from typing import Optional
 import torch
 import torch.distributed as dist
 
+from ..ops import functional as OF
+
 from .. import max_logging
 from ..input_pipeline.synthetic_data_iterator import make_synthetic_iterator
 from ..models.wan.transformer_wan import WAN_PRESETS, WanConfig, WanModel
@@ -150,10 +152,10 @@ class WanTrainer:
       tgt_tokens = self.pctx.shard_sequence(tgt_tokens)
       valid = self.pctx.valid_lengths(self.pctx.size, tgt_tokens.shape[1])[self.pctx.rank]
       pred, tgt_tokens = pred[:, :valid], tgt_tokens[:, :valid]
-    err = (tgt_tokens.float() - pred.float()) ** 2
-    if self.use_weights:
-      err = err * weights.to(err.device).reshape(-1, 1, 1)
-    loss = err.sum() / total
+    # weighted squared error and its gradient in one fused pass; normalised by the global element count so that
+    # the per-rank losses of a sequence-sharded step add up to the mean
+    local = OF.weighted_mse(pred, tgt_tokens, weights.tolist() if self.use_weights else None)
+    loss = local * (pred.numel() / total)
     loss.backward()
     stats = self.engine.finish_step(model_group=self.mesh.group("model"))
     loss_value = loss.detach()

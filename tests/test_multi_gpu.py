@@ -182,3 +182,34 @@ def test_training_step_peer_transport_matches_nccl():
   a = _spawn(_train, 2, True)[0]
   b = _spawn(_train, 2, False)[0]
   assert a == pytest.approx(b, rel=3e-2, abs=3e-2)
+
+
+def _small_allreduce(rank, world):
+  import torch.distributed as dist
+
+  from maxdiffusion_b200.parallel import symm
+
+  peer = symm.PeerGroup(dist.group.WORLD)
+  ar = symm.SmallAllReduce(peer, capacity=1024)
+  outs = []
+  for it in range(6):  # more calls than buffer halves: exercises the epoch alternation
+    torch.manual_seed(1000 * it + rank)
+    x = torch.randn(1 + 170 * it, device="cuda")
+    got_sum, got_max = ar(x, "sum"), ar(x, "max")
+    want_sum, want_max = x.clone(), x.clone()
+    dist.all_reduce(want_sum)
+    dist.all_reduce(want_max, op=dist.ReduceOp.MAX)
+    outs.append(((got_sum - want_sum).abs().max().item(), (got_max - want_max).abs().max().item(),
+                 got_sum.sum().item()))
+  return outs
+
+
+def test_small_allreduce_matches_nccl_and_is_identical_across_ranks():
+  if torch.cuda.device_count() < 2:
+    pytest.skip("needs 2 GPUs")
+  res = _spawn(_small_allreduce, 2)
+  for per_rank in res:
+    for err_sum, err_max, _ in per_rank:
+      assert err_sum < 1e-5 and err_max == 0.0
+  for a, b in zip(res[0], res[1]):
+    assert a[2] == b[2]  # bitwise identical sums on both ranks
