@@ -41,7 +41,7 @@ def diffusers_to_ours(sd: Dict[str, torch.Tensor]) -> Dict[str, torch.Tensor]:
   out: Dict[str, torch.Tensor] = {}
   fuse: Dict[str, Dict[str, torch.Tensor]] = {}
   for key, t in sd.items():
-    if key.startswith("patch_embedding."):
+    if key.startswith("patch_embedding.") or key.startswith("vace_patch_embedding."):
       out[key] = t.reshape(t.shape[0], -1) if key.endswith("weight") else t
       continue
     hit = False
@@ -55,12 +55,12 @@ def diffusers_to_ours(sd: Dict[str, torch.Tensor]) -> Dict[str, torch.Tensor]:
     if key == "condition_embedder.image_embedder.pos_embed":
       out[key] = t
       continue
-    m = re.match(r"blocks\.(\d+)\.(.*)", key)
+    m = re.match(r"((?:vace_)?blocks)\.(\d+)\.(.*)", key)
     if not m:
       out[key] = t  # proj_out.*, scale_shift_table
       continue
-    i, rest = m.group(1), m.group(2)
-    pre = f"blocks.{i}."
+    i, rest = m.group(2), m.group(3)
+    pre = f"{m.group(1)}.{i}."
     m2 = re.match(r"(attn[12])\.(to_q|to_k|to_v|add_k_proj|add_v_proj)\.(weight|bias)", rest)
     if m2:
       attn, proj, kind = m2.groups()
@@ -89,6 +89,9 @@ def ours_to_diffusers(sd: Dict[str, torch.Tensor], in_channels: int = 16, patch=
     if key == "patch_embedding.weight":
       out[key] = t.reshape(t.shape[0], in_channels, *patch)
       continue
+    if key == "vace_patch_embedding.weight":
+      out[key] = t.reshape(t.shape[0], -1, *patch)
+      continue
     hit = False
     for src, dst in inv.items():
       if key.startswith(src + "."):
@@ -97,11 +100,11 @@ def ours_to_diffusers(sd: Dict[str, torch.Tensor], in_channels: int = 16, patch=
         break
     if hit:
       continue
-    m = re.match(r"blocks\.(\d+)\.(.*)", key)
+    m = re.match(r"((?:vace_)?blocks)\.(\d+)\.(.*)", key)
     if not m:
       out[key] = t
       continue
-    pre, rest = f"blocks.{m.group(1)}.", m.group(2)
+    pre, rest = f"{m.group(1)}.{m.group(2)}.", m.group(3)
     m2 = re.match(r"(attn[12])\.(to_qkv|to_kv|add_kv_proj)\.(weight|bias)", rest)
     if m2:
       attn, group, kind = m2.groups()
@@ -121,7 +124,7 @@ def diffusers_to_flax_tree(sd: Dict[str, torch.Tensor], scan_layers: bool = True
   def rename(k: str) -> str:
     k = k.replace("condition_embedder.time_embedder.linear_1", "condition_embedder.time_embedder.linear_1")
     k = k.replace("condition_embedder.text_embedder.linear_1", "condition_embedder.text_embedder.linear_1")
-    k = k.replace(".scale_shift_table", ".adaln_scale_shift_table") if k.startswith("blocks.") else k
+    k = k.replace(".scale_shift_table", ".adaln_scale_shift_table") if k.startswith(("blocks.", "vace_blocks.")) else k
     k = k.replace("to_out.0", "proj_attn").replace("ffn.net.0.proj", "ffn.act_fn.proj").replace("ffn.net.2", "ffn.proj_out")
     k = k.replace("to_q.", "query.").replace("to_k.", "key.").replace("to_v.", "value.")
     k = re.sub(r"norm2\.(weight|bias)$", r"norm2.layer_norm.\1", k)

@@ -291,7 +291,7 @@ class WanModel(nn.Module):
   # ---- forward ------------------------------------------------------------------------------
   def forward(self, hidden_states, timestep, encoder_hidden_states, encoder_hidden_states_image=None, pctx=None,
               skip_blocks: bool = False, cached_residual=None, return_residual: bool = False, kv_cache=None,
-              rope=None, return_tokens: bool = False):
+              rope=None, return_tokens: bool = False, hints: Optional[dict] = None, block_post=None):
     """hidden_states: latents [B,C,F,H,W]; timestep: [B]; encoder_hidden_states: [B,T,text_dim]. Returns [B,C,F,H,W].
 
     With a context-parallel `pctx` every rank passes the full latents and receives the output of its own
@@ -321,7 +321,10 @@ class WanModel(nn.Module):
         raise ValueError("cached_residual must be provided when skip_blocks is True")
       x = x + cached_residual
     else:
-      x = self.run_blocks(x, context, temb6, rope, pctx, context_image, kv_cache)
+      if callable(hints):
+        # control branches (VACE) need the embedded tokens and conditioning: they are computed here, once
+        hints = hints(x, context, temb6, rope, pctx)
+      x = self.run_blocks(x, context, temb6, rope, pctx, context_image, kv_cache, hints, block_post)
     residual = (x - x_in) if return_residual else None
 
     shift, scale = (self.scale_shift_table.float() + temb.float().unsqueeze(1)).unbind(1)
@@ -335,7 +338,9 @@ class WanModel(nn.Module):
     out = self.unpatchify(x, grid)
     return (out, residual) if return_residual else out
 
-  def run_blocks(self, x, context, temb6, rope, pctx, context_image, kv_cache):
+  def run_blocks(self, x, context, temb6, rope, pctx, context_image, kv_cache, hints=None, block_post=None):
+    """`hints` {block index: tensor} are added to the stream after that block (VACE); `block_post(i, x)` may
+    transform the stream after block i (Wan-Animate face adapter)."""
     policy = self.remat_policy.upper() if torch.is_grad_enabled() else "NONE"
     for i, blk in enumerate(self.blocks):
       if self.block_hook is not None:
@@ -353,4 +358,8 @@ class WanModel(nn.Module):
         if self.block_hook is not None:
           done = (lambda idx=i: self.block_hook(idx, "backward_done"))
         x = OF.checkpoint_block(run, x, context, temb6, save_attention=(policy != "FULL"), on_backward_done=done)
+      if hints is not None and i in hints:
+        x = x + hints[i].to(x.dtype)
+      if block_post is not None:
+        x = block_post(i, x)
     return x

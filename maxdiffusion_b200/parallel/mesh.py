@@ -121,7 +121,7 @@ def create_device_mesh(config=None, shape: Optional[dict[str, int]] = None, ulys
 
   Groups: one per axis (`data`, `fsdp`, `context`, `tensor`), `shard` = fsdp x context (the ranks a Wan
   weight is sharded over: the reference maps `embed -> ('context', 'fsdp')`, configs/base_wan_14b.yml:217),
-  `replica` = data (gradient averaging), and `ulysses` / `ring` inside the context axis.
+  `replica` = data (gradient averaging), `batch` = data x fsdp (ranks that hold different samples), and `ulysses` / `ring` inside the context axis.
   """
   initialized = dist.is_available() and dist.is_initialized()
   world = dist.get_world_size() if initialized else 1
@@ -147,6 +147,7 @@ def create_device_mesh(config=None, shape: Optional[dict[str, int]] = None, ulys
   make("shard", (FSDP, CONTEXT))
   make("replica", (DATA,))
   make("model", (FSDP, CONTEXT, TENSOR))
+  make("batch", (DATA, FSDP))
   for ctx_ranks in axis_groups(shape, (CONTEXT,)):
     ul, rg = split_context(ctx_ranks, ulysses_shards)
     for name, sub in (("ulysses", ul), ("ring", rg)):

@@ -48,6 +48,13 @@ class PromptCache:
 class WanPipeline:
   model_name = "wan2.1"
   is_i2v = False
+  transformer_cls = WanModel
+
+  @staticmethod
+  def resolve_transformer_config(config):
+    from ...trainers.wan_trainer import resolve_wan_config
+
+    return resolve_wan_config(config)
 
   def __init__(self, config, transformer: WanModel, vae: Optional[AutoencoderKLWan], scheduler: UniPCMultistepScheduler,
                tokenizer=None, text_encoder=None, transformer_2: Optional[WanModel] = None,
@@ -65,24 +72,23 @@ class WanPipeline:
                                   peer_memory=bool(config.get("peer_memory_transport", True)) and self.device.type == "cuda")
     self.prompt_cache = PromptCache()
     self.vae_scale_factor_temporal, self.vae_scale_factor_spatial = 4, 8
+    self.extra_model_kwargs: dict = {}  # set by subclasses for the duration of a call (control latents, ...)
 
   # ------------------------------------------------------------------ construction
   @classmethod
   def from_config(cls, config, device=None, dtype=None, load_vae: bool = True, **kw):
     """Random-initialised pipeline of the configured architecture (benchmarks, tests)."""
-    from ...trainers.wan_trainer import resolve_wan_config
-
     device = torch.device(device) if device is not None else (
         torch.device("cuda", torch.cuda.current_device()) if torch.cuda.is_available() else torch.device("cpu"))
     dtype = dtype or (config.weights_dtype if device.type == "cuda" else torch.float32)
-    wcfg = resolve_wan_config(config)
+    wcfg = cls.resolve_transformer_config(config)
     torch.manual_seed(int(config.get("seed", 0)))
     prev = torch.get_default_dtype()
     torch.set_default_dtype(dtype)
     try:
       with torch.device(device):
-        transformer = WanModel(wcfg)
-        transformer_2 = WanModel(wcfg) if cls.model_name == "wan2.2" else None
+        transformer = cls.transformer_cls(wcfg)
+        transformer_2 = cls.transformer_cls(wcfg) if cls.model_name == "wan2.2" else None
     finally:
       torch.set_default_dtype(prev)
     vae = None
@@ -157,6 +163,10 @@ class WanPipeline:
 
   def _forward(self, model, latents, t, embeds, image_embeds=None, kv_cache=None, rope=None, **kw):
     ts = torch.full((latents.shape[0],), float(t), device=self.device, dtype=torch.float32)
+    for name, val in self.extra_model_kwargs.items():
+      if torch.is_tensor(val) and val.dim() > 1 and val.shape[0] != latents.shape[0]:
+        val = val.repeat(latents.shape[0] // val.shape[0], *([1] * (val.dim() - 1)))  # CFG doubles the batch
+      kw[name] = val
     return model(latents.to(self.dtype), ts, embeds, encoder_hidden_states_image=image_embeds, pctx=self.pctx,
                  kv_cache=kv_cache, rope=rope, **kw)
 

@@ -51,6 +51,12 @@ def resolve_wan_config(config) -> WanConfig:
 
 
 class WanTrainer:
+  model_cls = WanModel
+  resolve_config = staticmethod(resolve_wan_config)
+
+  def model_kwargs(self, batch: dict) -> dict:
+    """Extra keyword arguments of the model call taken from the batch (subclasses: control latents)."""
+    return {}
 
   def __init__(self, config, mesh: Optional[DeviceMesh] = None, model: Optional[WanModel] = None, device=None):
     self.config = config
@@ -58,7 +64,7 @@ class WanTrainer:
         "cuda", torch.cuda.current_device()) if torch.cuda.is_available() else torch.device("cpu")
     self.mesh = mesh if mesh is not None else create_device_mesh(config)
     self.dtype = config.weights_dtype if self.device.type == "cuda" else torch.float32
-    self.wan_cfg = model.cfg if model is not None else resolve_wan_config(config)
+    self.wan_cfg = model.cfg if model is not None else self.resolve_config(config)
     seed = int(config.get("seed", 0))
     remat = str(config.get("remat_policy", "NONE")).upper()
     if self.mesh.world_size > 1 and remat == "NONE":
@@ -69,7 +75,7 @@ class WanTrainer:
       torch.set_default_dtype(self.dtype)
       try:
         with torch.device(self.device):
-          model = WanModel(self.wan_cfg, remat_policy=remat)
+          model = self.model_cls(self.wan_cfg, remat_policy=remat)
       finally:
         torch.set_default_dtype(prev)
     else:
@@ -144,7 +150,8 @@ class WanTrainer:
     noise = torch.randn(latents.shape, generator=self.gen, device=self.device, dtype=torch.float32).to(self.dtype)
     noisy, target, weights = self.scheduler.apply_flow_match(noise.float(), latents.float(), timesteps, self.scheduler_state)
 
-    pred = self.model(noisy.to(self.dtype), timesteps, text, pctx=self.pctx, return_tokens=True)  # [B,S_loc,P]
+    pred = self.model(noisy.to(self.dtype), timesteps, text, pctx=self.pctx, return_tokens=True,
+                      **self.model_kwargs(batch))  # [B,S_loc,P]
     tgt_tokens, _ = self.model.patchify(target, channel_last=True)
     total = tgt_tokens.numel()
     if self.pctx is not None:
@@ -212,6 +219,9 @@ class WanTrainer:
       scalars.update({"perf/step_time_seconds": dt, "perf/per_device_tflops": per_device,
                       "perf/per_device_tflops_per_sec": per_device / dt})
       writer.write(self.step, scalars)
+      eval_every = int(config.get("eval_every", -1))
+      if eval_every > 0 and self.step % eval_every == 0 and str(config.get("dataset_type", "synthetic")) != "synthetic":
+        self.eval(self.step, writer)
       if checkpointer is not None and int(config.get("checkpoint_every", -1)) > 0 and self.step % int(config.checkpoint_every) == 0:
         checkpointer.save(self.step, self)
     if checkpointer is not None and config.get("save_final_checkpoint", False):
