@@ -148,6 +148,9 @@ class WanCrossAttention(nn.Module):
 
   def compute_kv(self, context, context_image=None):
     """K/V of the conditioning tokens; constant over the denoising loop, so pipelines cache it per prompt."""
+    if context_image is not None and not self.has_image:
+      # no separate image K/V projection (Wan-Animate): the image tokens join the text tokens
+      context = torch.cat([context_image, context], dim=1)
     B, T, C = context.shape[0], context.shape[1], self.to_q.weight.shape[0]
     k, v = split_fused(self.to_kv(context), 2)
     k = OF.rms_norm_rope(k, self.norm_k, heads=self.heads, eps=self.eps)
@@ -291,7 +294,7 @@ class WanModel(nn.Module):
   # ---- forward ------------------------------------------------------------------------------
   def forward(self, hidden_states, timestep, encoder_hidden_states, encoder_hidden_states_image=None, pctx=None,
               skip_blocks: bool = False, cached_residual=None, return_residual: bool = False, kv_cache=None,
-              rope=None, return_tokens: bool = False, hints: Optional[dict] = None, block_post=None):
+              rope=None, return_tokens: bool = False, hints: Optional[dict] = None, block_post=None, token_bias=None):
     """hidden_states: latents [B,C,F,H,W]; timestep: [B]; encoder_hidden_states: [B,T,text_dim]. Returns [B,C,F,H,W].
 
     With a context-parallel `pctx` every rank passes the full latents and receives the output of its own
@@ -306,6 +309,8 @@ class WanModel(nn.Module):
       tokens = pctx.shard_sequence(tokens)
       rope = (pctx.shard_sequence(rope[0], dim=0), pctx.shard_sequence(rope[1], dim=0))
     x = self.patch_embedding(tokens)
+    if token_bias is not None:  # pose embedding of Wan-Animate, added to the embedded patches
+      x = x + (pctx.shard_sequence(token_bias) if pctx is not None else token_bias).to(x.dtype)
 
     temb, tproj = self.condition_embedder.time(timestep, dtype)
     temb6 = tproj.reshape(tproj.shape[0], 6, -1)
