@@ -76,3 +76,27 @@ def test_cache_schedules():
     assert run <= 2
   x = torch.randn(1, 4, 2, 16, 18)
   assert torch.allclose(CP.fft_compensate(x, x, x, 1.2, 1.0), x, atol=1e-5)  # zero bias -> identity
+
+
+def test_wan22_vae_chunked_matches_whole_clip_and_patchify_round_trip():
+  from maxdiffusion_b200.models.wan.autoencoder_kl_wan_2p2 import (AutoencoderKLWan2p2, WanAvgDown3D, WanDupUp3D,
+                                                                    WanVAE2p2Config, patchify, unpatchify)
+
+  torch.manual_seed(0)
+  x = torch.randn(1, 3, 2, 8, 12)
+  p = patchify(x, 2)
+  assert p.shape == (1, 12, 2, 4, 6) and torch.equal(unpatchify(p, 2), x)
+  # channel index = c*4 + w_in_patch*2 + h_in_patch
+  assert torch.equal(p[0, 1 * 4 + 1 * 2 + 0, 0, 1, 2], x[0, 1, 0, 2, 5])
+  down = WanAvgDown3D(4, 8, 2, 2)
+  assert down(torch.randn(1, 4, 1, 4, 4)).shape == (1, 8, 1, 2, 2)  # a single frame is padded in front
+  up = WanDupUp3D(8, 4, 2, 2)
+  assert up(torch.randn(1, 8, 3, 2, 2), True).shape == (1, 4, 5, 4, 4)
+  cfg = WanVAE2p2Config(base_dim=8, base_dec_dim=8, z_dim=6, latents_mean=[0.0] * 6, latents_std=[1.0] * 6)
+  vae = AutoencoderKLWan2p2(cfg).eval()
+  video = torch.rand(1, 3, 9, 32, 32) * 2 - 1
+  with torch.no_grad():
+    z, z_full = vae.encode(video).mode(), vae.encode_full(video).mode()
+    assert z.shape == (1, 6, 3, 2, 2) and torch.allclose(z, z_full, atol=1e-5)
+    out, out_full = vae.decode(z), vae.decode_full(z)
+  assert out.shape == (1, 3, 9, 32, 32) and torch.allclose(out, out_full, atol=1e-5)
