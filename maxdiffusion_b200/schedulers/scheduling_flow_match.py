@@ -33,11 +33,11 @@ class FlowMatchScheduler(SchedulerConfigMixin):
   def __init__(self, num_train_timesteps: int = 1000, shift: float = 3.0, sigma_max: float = 1.0,
                sigma_min: float = 0.003 / 1.002, inverse_timesteps: bool = False, extra_one_step: bool = False,
                reverse_sigmas: bool = False, use_dynamic_shifting: bool = False, time_shift_type: str = "linear",
-               dtype: torch.dtype = torch.float32):
+               shift_terminal: Optional[float] = None, dtype: torch.dtype = torch.float32):
     self.register_to_config(num_train_timesteps=num_train_timesteps, shift=shift, sigma_max=sigma_max,
                             sigma_min=sigma_min, inverse_timesteps=inverse_timesteps, extra_one_step=extra_one_step,
                             reverse_sigmas=reverse_sigmas, use_dynamic_shifting=use_dynamic_shifting,
-                            time_shift_type=time_shift_type)
+                            time_shift_type=time_shift_type, shift_terminal=shift_terminal)
     self.dtype = dtype
 
   def create_state(self) -> FlowMatchSchedulerState:
@@ -69,6 +69,44 @@ class FlowMatchScheduler(SchedulerConfigMixin):
       weights = weights.to(device) if weights is not None else None
     return state.replace(sigmas=sigmas, timesteps=timesteps, linear_timesteps_weights=weights, training=training,
                          num_inference_steps=num_inference_steps)
+
+  def set_timesteps_ltx2(self, state, num_inference_steps: int = 100, shape=None, denoising_strength: float = 1.0,
+                         training: bool = False, shift: Optional[float] = None, timesteps=None, sigmas=None, device=None):
+    """Schedule with caller-provided sigmas / timesteps, exponential dynamic shifting (`shift` is mu) and the
+    terminal stretch `sigma -> 1 - (1 - sigma) * (1 - shift_terminal) / (1 - sigma_last)` (LTX-2, Flux.2-Klein).
+
+    reference: src/maxdiffusion/schedulers/scheduling_flow_match_flax.py:172-236."""
+    c = self.config
+    s = float(shift if shift is not None else c.shift)
+    given_t = timesteps is not None
+    if sigmas is None:
+      if timesteps is None:
+        start = c.sigma_min + (c.sigma_max - c.sigma_min) * denoising_strength
+        n = num_inference_steps + 1 if c.extra_one_step else num_inference_steps
+        sigmas = torch.linspace(start, c.sigma_min, n, dtype=torch.float64)
+        sigmas = sigmas[:-1] if c.extra_one_step else sigmas
+      else:
+        sigmas = torch.as_tensor(timesteps, dtype=torch.float64) / c.num_train_timesteps
+    sigmas = torch.as_tensor(sigmas, dtype=torch.float64)
+    if c.inverse_timesteps:
+      sigmas = sigmas.flip(0)
+    if c.use_dynamic_shifting and c.time_shift_type == "exponential":
+      e = torch.exp(torch.tensor(s, dtype=torch.float64))
+      sigmas = e / (e + (1.0 / sigmas.clamp(1e-7, 1.0) - 1.0))
+    else:
+      sigmas = s * sigmas / (1 + (s - 1) * sigmas)
+    if c.reverse_sigmas:
+      sigmas = 1 - sigmas
+    if c.get("shift_terminal", None) is not None:
+      omz = 1 - sigmas
+      sigmas = 1 - omz / (omz[-1] / (1 - c.shift_terminal))
+    sigmas = sigmas.to(self.dtype)
+    ts = torch.as_tensor(timesteps, dtype=self.dtype) if given_t else sigmas * c.num_train_timesteps
+    weights = self._training_weights(ts, len(ts)) if training else None
+    if device is not None:
+      sigmas, ts = sigmas.to(device), ts.to(device)
+    return state.replace(sigmas=sigmas, timesteps=ts, linear_timesteps_weights=weights, training=training,
+                         num_inference_steps=len(ts))
 
   @staticmethod
   def _training_weights(timesteps: torch.Tensor, n: int) -> torch.Tensor:
@@ -130,3 +168,16 @@ class FlowMatchScheduler(SchedulerConfigMixin):
       sigma_next = state.sigmas[idx + 1]
     prev = sample + model_output * (sigma_next - sigma).to(model_output.dtype)
     return prev, state
+
+
+def compute_empirical_mu(image_seq_len: int, num_steps: int) -> float:
+  """Resolution- and step-count-dependent time shift of the Flux family
+  (reference: src/maxdiffusion/schedulers/scheduling_flow_match_flax.py:422-437)."""
+  a1, b1 = 8.73809524e-05, 1.89833333
+  a2, b2 = 0.00016927, 0.45666666
+  if image_seq_len > 4300:
+    return float(a2 * image_seq_len + b2)
+  m_200 = a2 * image_seq_len + b2
+  m_10 = a1 * image_seq_len + b1
+  a = (m_200 - m_10) / 190.0
+  return float(a * num_steps + (m_200 - 200.0 * a))
