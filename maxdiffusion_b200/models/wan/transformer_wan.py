@@ -214,10 +214,11 @@ class WanImageEmbedding(nn.Module):
       b, s, c = x.shape
       x = (x.reshape(-1, 2 * s, c) + self.pos_embed.to(x.dtype)).reshape(b, s, c) if self.pos_embed.shape[1] == 2 * s \
           else x + self.pos_embed.to(x.dtype)
-    h = self.norm1(x.float()).to(x.dtype)
+    ln = lambda m, t: torch.nn.functional.layer_norm(t.float(), m.normalized_shape, m.weight.float(), m.bias.float(), m.eps)
+    h = ln(self.norm1, x).to(x.dtype)
     h = torch.nn.functional.gelu(self.ff_in(h))
     h = self.ff_out(h)
-    return self.norm2(h.float()).to(x.dtype)
+    return ln(self.norm2, h).to(x.dtype)
 
 
 class WanConditionEmbedder(nn.Module):
