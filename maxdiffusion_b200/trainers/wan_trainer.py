@@ -204,14 +204,22 @@ class WanTrainer:
       from ..max_utils import Profiler
 
       profiler = Profiler(config)
+    monitor = None
+    if self.mesh.world_size > 1 and config.get("enable_health_monitor", True):
+      from ..parallel.health import HealthMonitor
+
+      monitor = HealthMonitor(timeout_s=float(config.get("health_timeout_seconds", 600.0))).start()
+    from ..parallel.health import guarded_step
+
     while self.step < max_steps:
       batch = nxt.result()
       nxt = pool.submit(lambda: next(data))
       if profiler is not None:
         profiler.maybe_start(self.step)
       t0 = time.perf_counter()
-      metrics = self.train_step(batch)
-      loss = float(metrics["learning/loss"])  # device -> host, ends the step
+      with guarded_step(monitor, self.step):  # peers are checked on the host before this step's first launch
+        metrics = self.train_step(batch)
+        loss = float(metrics["learning/loss"])  # device -> host, ends the step
       dt = time.perf_counter() - t0
       if profiler is not None:
         profiler.maybe_stop(self.step)
@@ -227,5 +235,7 @@ class WanTrainer:
     if checkpointer is not None and config.get("save_final_checkpoint", False):
       checkpointer.save(self.step, self)
     writer.close()
+    if monitor is not None:
+      monitor.stop()
     pool.shutdown(wait=False, cancel_futures=True)
     return self
