@@ -231,7 +231,8 @@ class FluxTransformer2DModel(nn.Module):
           if self.block_hook is not None and torch.is_grad_enabled():
             self.block_hook(i, "recompute")
           return blk(a, b, t, rope_img, rope_txt)
-        img, txt = OF.checkpoint_block(run, img, txt, temb, save_attention=(policy != "FULL"), on_backward_done=done)
+        img, txt = OF.checkpoint_block(run, img, txt, temb, save_attention=(not policy.startswith("FULL")), on_backward_done=done,
+                                offload_input=policy.endswith("_OFFLOAD"))
       idx += 1
     x = torch.cat([txt, img], dim=1)
     for blk in self.single_transformer_blocks:
@@ -245,7 +246,8 @@ class FluxTransformer2DModel(nn.Module):
           if self.block_hook is not None and torch.is_grad_enabled():
             self.block_hook(i, "recompute")
           return blk(a, t, rope_all)
-        x = OF.checkpoint_block(run1, x, temb, save_attention=(policy != "FULL"), on_backward_done=done)
+        x = OF.checkpoint_block(run1, x, temb, save_attention=(not policy.startswith("FULL")), on_backward_done=done,
+                                offload_input=policy.endswith("_OFFLOAD"))
       idx += 1
     img = x[:, txt.shape[1]:]
     scale, shift = _modulation(self.norm_out, temb, 2)  # AdaLayerNormContinuous emits (scale, shift)

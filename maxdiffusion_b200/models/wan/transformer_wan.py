@@ -363,7 +363,8 @@ class WanModel(nn.Module):
         done = None
         if self.block_hook is not None:
           done = (lambda idx=i: self.block_hook(idx, "backward_done"))
-        x = OF.checkpoint_block(run, x, context, temb6, save_attention=(policy != "FULL"), on_backward_done=done)
+        x = OF.checkpoint_block(run, x, context, temb6, save_attention=(not policy.startswith("FULL")), on_backward_done=done,
+                                offload_input=policy.endswith("_OFFLOAD"))
       if hints is not None and i in hints:
         x = x + hints[i].to(x.dtype)
       if block_post is not None:

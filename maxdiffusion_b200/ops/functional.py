@@ -320,9 +320,21 @@ class _CheckpointFn(torch.autograd.Function):
   def forward(ctx, fn, save_attention, on_backward_done, n_tensors, *args):
     ctx.fn = fn
     ctx.on_backward_done = on_backward_done
+    offload = save_attention == "offload" or (isinstance(save_attention, tuple) and save_attention[1])
+    save_attention = save_attention[0] if isinstance(save_attention, tuple) else (save_attention is True)
     ctx.store = [] if save_attention else None
     tensors = args[:n_tensors]
     ctx.rest = args[n_tensors:]
+    ctx.offloaded = None
+    if offload and tensors and tensors[0].is_cuda:
+      # the block input (the residual stream) waits for the backward pass in pinned host memory
+      x = tensors[0]
+      host = torch.empty(x.shape, dtype=x.dtype, device="cpu", pin_memory=True)
+      host.copy_(x, non_blocking=True)
+      ctx.offloaded = (host, x.device, x.requires_grad)
+      ctx.offload_event = torch.cuda.Event()
+      ctx.offload_event.record()
+      tensors = (None,) + tuple(tensors[1:])
     ctx.save_for_backward(*tensors)
     with torch.no_grad():
       if ctx.store is not None:
@@ -334,10 +346,16 @@ class _CheckpointFn(torch.autograd.Function):
 
   @staticmethod
   def backward(ctx, *douts):
-    tensors = [t.detach().requires_grad_(t.requires_grad) if t is not None else None for t in ctx.saved_tensors]
+    saved = list(ctx.saved_tensors)
+    if ctx.offloaded is not None:
+      host, device, req = ctx.offloaded
+      ctx.offload_event.synchronize()
+      saved[0] = host.to(device, non_blocking=True).requires_grad_(req)
+      ctx.offloaded = None
+    tensors = [t.detach().requires_grad_(t.requires_grad) if t is not None else None for t in saved]
     # only tensors that took part in autograd need gradients; floating point inputs are assumed to
     inputs = []
-    for t, orig in zip(tensors, ctx.saved_tensors):
+    for t, orig in zip(tensors, saved):
       if t is not None and orig.is_floating_point():
         t.requires_grad_(True)
       inputs.append(t)
@@ -357,14 +375,16 @@ class _CheckpointFn(torch.autograd.Function):
 
 
 def checkpoint_block(fn, *tensor_args, extra_args: Sequence = (), save_attention: bool = False,
-                     on_backward_done=None):
+                     on_backward_done=None, offload_input: bool = False):
   """Runs `fn(*tensor_args, *extra_args)` storing only its tensor inputs; the backward pass recomputes it.
 
   Parameters used inside `fn` receive their gradients during the recomputation. With `save_attention`
   the flash-attention outputs of the first pass are kept and not recomputed. `on_backward_done()` is called
   once the parameter gradients of the block are complete (the FSDP engine reduces and applies them there).
+  With `offload_input` the first tensor argument is parked in pinned host memory between the two passes.
   """
-  return _CheckpointFn.apply(fn, save_attention, on_backward_done, len(tensor_args), *tensor_args, *extra_args)
+  mode = (bool(save_attention), True) if offload_input else bool(save_attention)
+  return _CheckpointFn.apply(fn, mode, on_backward_done, len(tensor_args), *tensor_args, *extra_args)
 
 
 # ---------------------------------------------------------------------------------------------

@@ -10,6 +10,8 @@ import time
 from typing import Optional
 
 import torch
+
+from ..models.gradient_checkpoint import resolve_remat
 import torch.distributed as dist
 
 from ..input_pipeline.synthetic_data_iterator import SyntheticFluxIterator
@@ -29,7 +31,8 @@ class FluxTrainer:
         torch.device("cuda", torch.cuda.current_device()) if torch.cuda.is_available() else torch.device("cpu"))
     self.dtype = config.weights_dtype if self.device.type == "cuda" else torch.float32
     seed = int(config.get("seed", 0))
-    remat = str(config.get("remat_policy", "NONE")).upper()
+    remat = resolve_remat(config.get("remat_policy", "NONE"), config.get("names_which_can_be_saved", []) or [],
+                          config.get("names_which_can_be_offloaded", []) or [])
     group = self.mesh.group("fsdp")
     if group is not None and remat == "NONE":
       remat = "SAVE_ATTENTION"

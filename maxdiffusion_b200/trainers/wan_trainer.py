@@ -17,6 +17,7 @@ from typing import Optional
 import torch
 import torch.distributed as dist
 
+from ..models.gradient_checkpoint import resolve_remat
 from ..ops import functional as OF
 
 from .. import max_logging
@@ -66,7 +67,8 @@ class WanTrainer:
     self.dtype = config.weights_dtype if self.device.type == "cuda" else torch.float32
     self.wan_cfg = model.cfg if model is not None else self.resolve_config(config)
     seed = int(config.get("seed", 0))
-    remat = str(config.get("remat_policy", "NONE")).upper()
+    remat = resolve_remat(config.get("remat_policy", "NONE"), config.get("names_which_can_be_saved", []) or [],
+                          config.get("names_which_can_be_offloaded", []) or [])
     if self.mesh.world_size > 1 and remat == "NONE":
       remat = "SAVE_ATTENTION"  # sharded weights are only resident around a block's (re)computation
     if model is None:

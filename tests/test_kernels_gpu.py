@@ -246,3 +246,17 @@ def test_adamw_stochastic_rounding_is_unbiased():
   K.adamw(p, g, m, v, lr=1e-4, b1=0.9, b2=0.999, eps=1e-8, wd=0.0, step=1, seed=123, stochastic=True)
   # the exact update is 1 - 1e-4, far below the bf16 spacing (2^-8 below 1): the mean must still move by it
   assert abs((1.0 - p.float().mean().item()) - 1e-4) < 2e-5
+
+
+def test_checkpoint_block_with_host_offload_matches_plain_autograd():
+  from maxdiffusion_b200.ops import functional as OF
+
+  torch.manual_seed(0)
+  w = torch.randn((256, 256), device=DEV, dtype=torch.bfloat16, requires_grad=True)
+  x = torch.randn((2, 128, 256), device=DEV, dtype=torch.bfloat16, requires_grad=True)
+  fn = lambda t: OF.linear(t, w, None, "gelu_tanh")
+  OF.checkpoint_block(fn, x, offload_input=True).float().sum().backward()
+  gx, gw = x.grad.clone(), w.grad.clone()
+  x.grad, w.grad = None, None
+  fn(x).float().sum().backward()
+  assert torch.equal(gx, x.grad) and torch.equal(gw, w.grad)

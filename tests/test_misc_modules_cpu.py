@@ -1,0 +1,65 @@
+"""Remat policy names, embedding / normalisation layers and the attention-kernel facade."""
+import pytest
+import torch
+
+from maxdiffusion_b200 import kernels
+from maxdiffusion_b200.models.embeddings import (CombinedTimestepGuidanceTextProjEmbeddings, FluxPosEmbed,
+                                                 get_1d_rotary_pos_embed)
+from maxdiffusion_b200.models.gradient_checkpoint import GradientCheckpointType, resolve_remat
+from maxdiffusion_b200.models.normalization import AdaLayerNormContinuous, AdaLayerNormZero, AdaLayerNormZeroSingle
+from maxdiffusion_b200.ops import functional as OF
+
+
+def test_remat_policy_names():
+  assert resolve_remat("NONE") == "NONE" and resolve_remat("full") == "FULL"
+  assert resolve_remat("MATMUL_WITHOUT_BATCH") == resolve_remat("FLUX_OPTIMIZED") == "SAVE_ATTENTION"
+  assert resolve_remat("OFFLOAD_MATMUL_WITHOUT_BATCH") == "SAVE_ATTENTION_OFFLOAD"
+  assert resolve_remat("CUSTOM", ["self_attn"], []) == "SAVE_ATTENTION"
+  assert resolve_remat("CUSTOM", [], ["hidden_states"]) == "FULL_OFFLOAD"
+  with pytest.raises(ValueError):
+    GradientCheckpointType.from_str("bogus")
+
+
+def test_checkpoint_block_gradients_match_plain_autograd():
+  torch.manual_seed(0)
+  lin = torch.nn.Linear(8, 8)
+  x = torch.randn(2, 3, 8, requires_grad=True)
+  fn = lambda t: torch.tanh(lin(t)) * 2
+  y = OF.checkpoint_block(fn, x, offload_input=True)  # on CPU the offload is a no-op; the path must still work
+  y.sum().backward()
+  gx, gw = x.grad.clone(), lin.weight.grad.clone()
+  x.grad, lin.weight.grad = None, None
+  fn(x).sum().backward()
+  assert torch.allclose(gx, x.grad) and torch.allclose(gw, lin.weight.grad)
+
+
+def test_adaptive_norms_match_explicit_formula():
+  torch.manual_seed(0)
+  x, emb = torch.randn(2, 5, 16), torch.randn(2, 16)
+  n = AdaLayerNormZero(16)
+  out, gate_msa, shift_mlp, scale_mlp, gate_mlp = n(x, emb)
+  mod = torch.nn.functional.linear(torch.nn.functional.silu(emb), n.linear.weight, n.linear.bias).chunk(6, dim=-1)
+  want = torch.nn.functional.layer_norm(x, (16,), eps=1e-6) * (1 + mod[1][:, None]) + mod[0][:, None]
+  assert torch.allclose(out, want, atol=1e-5) and torch.allclose(gate_msa, mod[2], atol=1e-6)
+  s = AdaLayerNormZeroSingle(16)
+  o2, g2 = s(x, emb)
+  assert o2.shape == x.shape and g2.shape == (2, 16)
+  c = AdaLayerNormContinuous(16, scale_shift_order="shift_scale")
+  m2 = torch.nn.functional.linear(torch.nn.functional.silu(emb), c.linear.weight, c.linear.bias).chunk(2, dim=-1)
+  want = torch.nn.functional.layer_norm(x, (16,), eps=1e-6) * (1 + m2[1][:, None]) + m2[0][:, None]
+  assert torch.allclose(c(x, emb), want, atol=1e-5)
+
+
+def test_embeddings_and_kernel_facade():
+  e = CombinedTimestepGuidanceTextProjEmbeddings(32, 16)
+  assert e(torch.tensor([1.0, 2.0]), torch.tensor([3.0, 3.0]), torch.randn(2, 16)).shape == (2, 32)
+  cos, sin = get_1d_rotary_pos_embed(8, 4)
+  cplx = get_1d_rotary_pos_embed(8, 4, use_real=False)
+  assert torch.allclose(cplx.real, cos) and torch.allclose(cplx.imag, sin)
+  ids = torch.tensor([[0, 1, 2], [0, 3, 4]])
+  c2, _ = FluxPosEmbed(10000.0, (4, 6, 6))(ids)
+  assert c2.shape == (2, 8)
+  assert set(kernels.KERNEL_REGISTRY) >= {"dot_product", "flash", "tokamax_ring", "ulysses_ring_custom_bidir", "cudnn_flash_te"}
+  q = torch.randn(1, 6, 2, 16)
+  ref = torch.nn.functional.scaled_dot_product_attention(q.transpose(1, 2), q.transpose(1, 2), q.transpose(1, 2)).transpose(1, 2)
+  assert torch.allclose(kernels.get_attention_kernel("tokamax_flash")(q, q, q), ref, atol=1e-5)
