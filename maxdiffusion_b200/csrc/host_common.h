@@ -17,6 +17,10 @@ DeviceStatus* status_buffer();
 int encode_tmap_bf16(CUtensorMap* map, const void* base, int rank, const uint64_t* dims,
                      const uint64_t* strides_bytes, const uint32_t* box);
 
+// Same, for 1-byte elements (fp8 operands), 128-byte swizzle.
+int encode_tmap_u8(CUtensorMap* map, const void* base, int rank, const uint64_t* dims,
+                   const uint64_t* strides_bytes, const uint32_t* box);
+
 // Same, for 4-byte elements (fp32), no swizzle unless box[0]*4 == 128.
 int encode_tmap_f32(CUtensorMap* map, const void* base, int rank, const uint64_t* dims,
                     const uint64_t* strides_bytes, const uint32_t* box, int swizzle128);

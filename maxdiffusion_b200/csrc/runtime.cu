@@ -81,6 +81,12 @@ int encode_tmap_bf16(CUtensorMap* map, const void* base, int rank, const uint64_
                        CU_TENSOR_MAP_SWIZZLE_128B);
 }
 
+int encode_tmap_u8(CUtensorMap* map, const void* base, int rank, const uint64_t* dims,
+                   const uint64_t* strides_bytes, const uint32_t* box) {
+  return encode_common(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, base, rank, dims, strides_bytes, box,
+                       CU_TENSOR_MAP_SWIZZLE_128B);
+}
+
 int encode_tmap_f32(CUtensorMap* map, const void* base, int rank, const uint64_t* dims,
                     const uint64_t* strides_bytes, const uint32_t* box, int swizzle128) {
   return encode_common(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, base, rank, dims, strides_bytes, box,

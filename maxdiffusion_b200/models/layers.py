@@ -29,6 +29,14 @@ class Linear(nn.Module):
     return f"in_features={self.in_features}, out_features={self.out_features}, bias={self.bias is not None}"
 
 
+def project_gated_residual(proj: nn.Module, x, residual, gate):
+  """residual + gate * proj(x). A plain `Linear` takes the fused GEMM-epilogue path; any other projection (e.g. a
+  quantised one) runs as a module followed by the fused gated-residual kernel."""
+  if type(proj) is Linear:
+    return OF.linear_gated_residual(x, proj.weight, proj.bias, residual, gate)
+  return OF.gated_residual(residual, proj(x), gate)
+
+
 def sinusoidal_embedding(timesteps: torch.Tensor, dim: int, flip_sin_to_cos: bool = True, freq_shift: float = 0.0,
                          max_period: float = 10000.0, scale: float = 1.0) -> torch.Tensor:
   """Sinusoidal timestep features [N, dim] in fp32 (reference: src/maxdiffusion/models/embeddings_flax.py:28-62)."""

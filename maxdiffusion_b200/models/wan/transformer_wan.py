@@ -23,7 +23,7 @@ import torch
 import torch.nn as nn
 
 from ...ops import functional as OF
-from ..layers import Linear, sinusoidal_embedding
+from ..layers import Linear, project_gated_residual, sinusoidal_embedding
 
 
 @dataclass
@@ -128,7 +128,7 @@ class WanSelfAttention(nn.Module):
     k = OF.rms_norm_rope(k, self.norm_k, cos, sin, heads=self.heads, eps=self.eps)
     v = v.unflatten(-1, (self.heads, C // self.heads))
     o = pctx.self_attention(q, k, v) if pctx is not None else OF.attention(q, k, v)
-    return OF.linear_gated_residual(o.reshape(B, S, C), self.to_out.weight, self.to_out.bias, residual, gate)
+    return project_gated_residual(self.to_out, o.reshape(B, S, C), residual, gate)
 
 
 class WanCrossAttention(nn.Module):
@@ -168,7 +168,7 @@ class WanCrossAttention(nn.Module):
     o = OF.attention(q, *kv["text"])
     if "image" in kv:
       o = o + OF.attention(q, *kv["image"])
-    return OF.linear_gated_residual(o.reshape(B, S, C), self.to_out.weight, self.to_out.bias, residual, None)
+    return project_gated_residual(self.to_out, o.reshape(B, S, C), residual, None)
 
 
 class WanBlock(nn.Module):
@@ -194,8 +194,8 @@ class WanBlock(nn.Module):
     h = OF.layer_norm_mod(x, gamma=self.norm2_weight, beta=self.norm2_bias, eps=self.eps)
     x = self.attn2(h, context, context_image, residual=x, cached_kv=cached_kv)
     h = OF.layer_norm_mod(x, scale=c_scale, shift=c_shift, eps=self.eps)
-    h = OF.linear(h, self.ffn_in.weight, self.ffn_in.bias, activation="gelu_tanh")
-    return OF.linear_gated_residual(h, self.ffn_out.weight, self.ffn_out.bias, x, c_gate)
+    h = self.ffn_in(h, activation="gelu_tanh")
+    return project_gated_residual(self.ffn_out, h, x, c_gate)
 
 
 class WanImageEmbedding(nn.Module):

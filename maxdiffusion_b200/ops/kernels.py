@@ -464,3 +464,44 @@ def groupnorm_bwd(dy, x, stats, groups, gamma=None, beta=None, act: bool = False
   _lib.check(rc, "mdb_groupnorm_bwd")
   sums = partial.sum(dim=(0, 2))
   return dx, sums[:, 1], sums[:, 0]
+
+
+# ---------------------------------------------------------------------------------------------
+# fp8 GEMM with per-tensor absmax scales
+# ---------------------------------------------------------------------------------------------
+def _declare_fp8(L):
+  c_void_p, c_int, c_ll = ctypes.c_void_p, ctypes.c_int, ctypes.c_longlong
+  L.mdb_gemm_fp8.argtypes = [c_void_p] * 6 + [c_int] * 3 + [c_ll] * 3 + [c_int, c_int, c_void_p]
+  L.mdb_gemm_fp8.restype = c_int
+  L.mdb_quantize_fp8.argtypes = [c_void_p, c_void_p, c_ll, c_void_p, c_void_p, c_int, c_void_p]
+  L.mdb_quantize_fp8.restype = c_int
+
+
+_lib.register(_declare_fp8)
+
+
+def quantize_fp8(x: torch.Tensor, e5m2: bool = False):
+  """Per-tensor absmax quantisation of a bf16 tensor. Returns (q uint8 same shape, scale fp32 [1] on device) with
+  x ~= q * scale; no host synchronisation."""
+  assert x.dtype == torch.bfloat16 and x.is_contiguous() and x.numel() % 8 == 0
+  stats = sumsq_maxabs(x)
+  q = torch.empty(x.shape, device=x.device, dtype=torch.uint8)
+  scale = torch.empty((1,), device=x.device, dtype=torch.float32)
+  rc = _lib.lib().mdb_quantize_fp8(_lib.ptr(x), _lib.ptr(q), x.numel(), _lib.ptr(stats), _lib.ptr(scale), int(e5m2),
+                                   _lib.stream())
+  _lib.check(rc, "mdb_quantize_fp8")
+  return q, scale
+
+
+def gemm_fp8(aq, a_scale, bq, b_scale, bias=None, a_e5m2: bool = False, b_e5m2: bool = False):
+  """bf16 D[M,N] = (a_scale * b_scale) * Aq[M,K] · Bq[N,K]ᵀ + bias on the fp8 tensor-core path (K % 16 == 0)."""
+  assert aq.dtype == torch.uint8 and bq.dtype == torch.uint8 and aq.dim() == 2 and bq.dim() == 2
+  assert aq.stride(-1) == 1 and bq.stride(-1) == 1 and aq.shape[1] == bq.shape[1]
+  M, K = aq.shape
+  N = bq.shape[0]
+  out = torch.empty((M, N), device=aq.device, dtype=torch.bfloat16)
+  rc = _lib.lib().mdb_gemm_fp8(_lib.ptr(aq), _lib.ptr(bq), _lib.ptr(out), _lib.ptr(bias), _lib.ptr(a_scale),
+                               _lib.ptr(b_scale), M, N, K, aq.stride(0), bq.stride(0), out.stride(0), int(a_e5m2),
+                               int(b_e5m2), _lib.stream())
+  _lib.check(rc, "mdb_gemm_fp8")
+  return out

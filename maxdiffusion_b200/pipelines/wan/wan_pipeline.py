@@ -71,6 +71,14 @@ class WanPipeline:
       self.pctx = ContextParallel(self.mesh, str(config.get("context_strategy", "ring")),
                                   peer_memory=bool(config.get("peer_memory_transport", True)) and self.device.type == "cuda")
     self.prompt_cache = PromptCache()
+    from ...models.quantizations import get_quantization_mode, quantize_model
+
+    mode = get_quantization_mode(config)
+    if mode is not None:
+      # reference: qwix rules applied to the transformer(s) at pipeline construction (wan_pipeline.py:569-651)
+      for m in filter(None, (self.transformer, self.transformer_2)):
+        n = quantize_model(m, mode)
+        max_logging.log(f"quantization={mode}: {n} linear layers run on the fp8 tensor-core path")
     self.vae_scale_factor_temporal, self.vae_scale_factor_spatial = 4, 8
     self.extra_model_kwargs: dict = {}  # set by subclasses for the duration of a call (control latents, ...)
 

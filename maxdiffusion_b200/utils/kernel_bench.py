@@ -69,6 +69,22 @@ def bench_gemm(results):
     del a, b, out
 
 
+def bench_gemm_fp8(results):
+  tf_peak, _, tag = peaks()
+  for M, N, Kd in [(32760, 5120, 5120), (32760, 13824, 5120), (4096, 5120, 5120)]:
+    a = torch.randn((M, Kd), device="cuda", dtype=torch.bfloat16)
+    b = torch.randn((N, Kd), device="cuda", dtype=torch.bfloat16)
+    aq, sa = K.quantize_fp8(a)
+    bq, sb = K.quantize_fp8(b)
+    med, best = time_ms(lambda: K.gemm_fp8(aq, sa, bq, sb))
+    qmed, _ = time_ms(lambda: K.quantize_fp8(a))
+    fl = 2.0 * M * N * Kd
+    results.append(dict(kernel="gemm_fp8", shape=[M, N, Kd], ms=med, best_ms=best, tflops=fl / med / 1e9,
+                        frac_of_bf16_peak=fl / med / 1e9 / tf_peak, of=tag, quantize_activation_ms=qmed))
+    print(results[-1], flush=True)
+    del a, b, aq, bq
+
+
 def bench_flash(results):
   tf_peak, _, tag = peaks()
   for B, H, Sq, Skv in [(1, 40, 4096, 32768), (1, 40, 8192, 8192), (1, 24, 4608, 4608), (1, 40, 32760, 32760)]:
@@ -149,6 +165,8 @@ def main(argv):
   results = []
   if "gemm" in which:
     bench_gemm(results)
+  if "gemm_fp8" in which:
+    bench_gemm_fp8(results)
   if "flash" in which:
     bench_flash(results)
   if "flash_bwd" in which:

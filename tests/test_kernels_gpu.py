@@ -260,3 +260,41 @@ def test_checkpoint_block_with_host_offload_matches_plain_autograd():
   x.grad, w.grad = None, None
   fn(x).float().sum().backward()
   assert torch.equal(gx, x.grad) and torch.equal(gw, w.grad)
+
+
+@pytest.mark.parametrize("M,N,Kd", [(128, 256, 128), (520, 264, 400), (1024, 1536, 2048)])
+def test_gemm_fp8_matches_quantised_reference(M, N, Kd):
+  torch.manual_seed(0)
+  a = torch.randn((M, Kd), device=DEV, dtype=torch.bfloat16)
+  b = torch.randn((N, Kd), device=DEV, dtype=torch.bfloat16) * 0.05
+  bias = torch.randn((N,), device=DEV, dtype=torch.bfloat16)
+  aq, sa = K.quantize_fp8(a)
+  bq, sb = K.quantize_fp8(b)
+  # the quantiser itself: bytes reinterpret as e4m3 and reproduce torch's rounding
+  a_deq = aq.view(torch.float8_e4m3fn).float() * sa
+  want_deq = (a.float() / sa).clamp(-448, 448).to(torch.float8_e4m3fn).float() * sa
+  assert torch.equal(a_deq, want_deq) and abs(sa.item() - a.abs().max().item() / 448.0) < 1e-6
+  out = K.gemm_fp8(aq, sa, bq, sb, bias)
+  b_deq = bq.view(torch.float8_e4m3fn).float() * sb
+  want = a_deq @ b_deq.t() + bias.float()
+  _report(f"gemm_fp8 {M}x{N}x{Kd}", out, want)
+  # against the unquantised product the error is the fp8 rounding error
+  assert _rel(out, a.float() @ b.float().t() + bias.float()) < 8e-2
+
+
+def test_fp8_linear_module_and_e5m2_backward():
+  from maxdiffusion_b200.models.layers import Linear
+  from maxdiffusion_b200.models.quantizations import Fp8Linear
+
+  torch.manual_seed(0)
+  base = Linear(256, 512).to(DEV, torch.bfloat16)
+  x = torch.randn((4, 64, 256), device=DEV, dtype=torch.bfloat16, requires_grad=True)
+  dy = torch.randn((4, 64, 512), device=DEV, dtype=torch.bfloat16)
+  want = torch.nn.functional.linear(x.float(), base.weight.float(), base.bias.float())
+  gx_want, gw_want = torch.autograd.grad(want, [x, base.weight], dy.float())
+  for full in (False, True):
+    q = Fp8Linear(base, full=full)
+    y = q(x)
+    gx, gw = torch.autograd.grad(y, [x, base.weight], dy)
+    assert _rel(y, want) < 6e-2 and _rel(gx, gx_want) < (0.2 if full else 2e-2) and _rel(gw, gw_want) < (0.2 if full else 2e-2)
+  _lib.raise_on_device_status()
