@@ -505,3 +505,40 @@ def gemm_fp8(aq, a_scale, bq, b_scale, bias=None, a_e5m2: bool = False, b_e5m2: 
                                int(b_e5m2), _lib.stream())
   _lib.check(rc, "mdb_gemm_fp8")
   return out
+
+
+# ---------------------------------------------------------------------------------------------
+# anti-aliased snake activation (vocoder)
+# ---------------------------------------------------------------------------------------------
+def _declare_snake(L):
+  c_void_p, c_int, c_ll = ctypes.c_void_p, ctypes.c_int, ctypes.c_longlong
+  fp = ctypes.POINTER(ctypes.c_float)
+  L.mdb_snake_aa.argtypes = [c_void_p, c_void_p, c_int, c_void_p, c_void_p, fp, fp, c_ll, c_int, c_int, c_int, c_void_p]
+  L.mdb_snake_aa.restype = c_int
+
+
+_lib.register(_declare_snake)
+
+
+def snake_aa(x, alpha, inv_beta, f_up, f_dn, leaky_slope: float | None = None):
+  """Anti-aliased activation over [B, C, L]: 2x up-sample, snake(alpha, 1/beta) (or leaky ReLU), 2x down-sample.
+  alpha / inv_beta: fp32 [C] on the device; f_up / f_dn: 12 filter taps each (host sequences)."""
+  assert x.dim() == 3 and x.is_contiguous() and x.dtype in (torch.float32, torch.bfloat16)
+  B, C, L = x.shape
+  out = torch.empty_like(x)
+  up = (ctypes.c_float * 12)(*[float(v) for v in f_up])
+  dn = (ctypes.c_float * 12)(*[float(v) for v in f_dn])
+  mode = 0 if leaky_slope is None else 1
+  if mode == 1:
+    alpha = torch.full((1,), float(leaky_slope), device=x.device, dtype=torch.float32)
+    inv_beta = alpha
+  rows, step = B * C, 65535
+  xf, of = x.view(rows, L), out.view(rows, L)
+  for r0 in range(0, rows, step):
+    n = min(step, rows - r0)
+    if r0 % C != 0 and mode == 0:
+      raise ValueError("row chunks must start on a channel boundary")
+    rc = _lib.lib().mdb_snake_aa(_lib.ptr(xf[r0:r0 + n]), _lib.ptr(of[r0:r0 + n]), _is_f32(x), _lib.ptr(alpha), _lib.ptr(inv_beta),
+                                 up, dn, n, C, L, mode, _lib.stream())
+    _lib.check(rc, "mdb_snake_aa")
+  return out

@@ -83,3 +83,21 @@ def test_channel_affine_uint8_blend():
   b = torch.randn((2, 4, 16, 32), device=DEV)
   for dim in (2, 3):
     _close(K.blend_ramp(a, b, dim), ref.blend_ramp(a, b, dim), 1e-5)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("L", [50, 256, 1000])
+def test_fused_antialiased_snake_matches_separable_path(L, dtype):
+  from maxdiffusion_b200.models.ltx2.vocoder_ltx2 import AntiAliasAct1d, SnakeBeta
+
+  torch.manual_seed(0)
+  act = AntiAliasAct1d(SnakeBeta(6)).to(DEV)
+  with torch.no_grad():
+    act.act.alpha.copy_(torch.randn(6) * 0.3)
+    act.act.beta.copy_(torch.randn(6) * 0.3)
+  x = torch.randn((2, 6, L), device=DEV).to(dtype)
+  got = act(x)
+  want = act.downsample(act.act(act.upsample(x.float())))
+  _close(got, want, 2e-2 if dtype == torch.bfloat16 else 2e-5)
+  leaky = AntiAliasAct1d(torch.nn.LeakyReLU(0.1)).to(DEV)
+  _close(leaky(x), leaky.downsample(leaky.act(leaky.upsample(x.float()))), 2e-2 if dtype == torch.bfloat16 else 2e-5)
