@@ -262,8 +262,11 @@ class AutoencoderKLLTX2Audio(nn.Module):
     self.cfg = c = cfg or LTX2AudioVAEConfig()
     self.encoder, self.decoder = LTX2AudioEncoder(c), LTX2AudioDecoder(c)
     self.latent_downsample_factor = 2 ** (len(c.ch_mult) - 1)
-    self.register_buffer("latents_mean", torch.zeros(c.base_channels))
-    self.register_buffer("latents_std", torch.ones(c.base_channels))
+    # statistics of the packed tokens [B, T, latent_channels * mel/4] (128 values for the released model, which is
+    # also its base_channels: the reference sizes them by base_channels)
+    n = c.latent_channels * (c.mel_bins // self.latent_downsample_factor) if c.mel_bins else c.base_channels
+    self.register_buffer("latents_mean", torch.zeros(n))
+    self.register_buffer("latents_std", torch.ones(n))
 
   # patched latents are [B, time, C * F] with channel-major features (reference patchifier :421-445)
   @staticmethod

@@ -98,3 +98,53 @@ def test_sdxl_unet_groupnorm_path_bf16():
     got = gpu(x.cuda().bfloat16(), t.cuda(), e.cuda().bfloat16(),
               added_cond_kwargs={k: v.cuda().bfloat16() for k, v in added.items()})
   assert _rel(got, want) < 6e-2
+
+
+def test_ltx2_transformer_bf16_matches_fp32():
+  from maxdiffusion_b200.models.ltx2.transformer_ltx2 import LTX2Config, LTX2VideoTransformer3DModel
+
+  torch.manual_seed(0)
+  cfg = LTX2Config(in_channels=32, out_channels=32, num_attention_heads=2, attention_head_dim=128, cross_attention_dim=256,
+                   audio_in_channels=16, audio_out_channels=16, audio_num_attention_heads=2, audio_attention_head_dim=64,
+                   audio_cross_attention_dim=128, num_layers=2, caption_channels=48, gated_attn=True,
+                   spatio_temporal_guidance_blocks=(1,))
+  ref, gpu = _pair(LTX2VideoTransformer3DModel(cfg))
+  B, Fr, H, W, Fa = 2, 2, 8, 8, 12
+  x, a, txt = torch.randn(B, Fr * H * W, 32), torch.randn(B, Fa, 16), torch.randn(B, 16, 48)
+  t = torch.tensor([400.0, 400.0])
+  pm = torch.tensor([1.0, 0.0]).view(2, 1, 1)
+  kw = dict(num_frames=Fr, height=H, width=W, audio_num_frames=Fa)
+  with torch.no_grad():
+    want, awant = ref(x, a, txt, txt, t, perturbation_mask=pm, **kw)
+    got, agot = gpu(x.cuda().bfloat16(), a.cuda().bfloat16(), txt.cuda().bfloat16(), txt.cuda().bfloat16(), t.cuda(),
+                    perturbation_mask=pm.cuda(), **kw)
+  assert _rel(got, want) < 6e-2 and _rel(agot, awant) < 6e-2
+  _lib.raise_on_device_status()
+
+
+def test_cuda_graph_cache_captures_once_and_replays(tmp_path):
+  from maxdiffusion_b200 import aot_cache
+  from maxdiffusion_b200.ops import functional as OF
+
+  w = torch.randn((256, 256), device="cuda", dtype=torch.bfloat16)
+
+  @aot_cache.cached_graph(name="test_step")
+  def step(x):
+    return OF.linear(x, w, None, "gelu_tanh")
+
+  aot_cache.install(str(tmp_path), revision="r")
+  try:
+    outs = []
+    for i in range(3):
+      x = torch.randn((128, 256), device="cuda", dtype=torch.bfloat16)
+      outs.append((step(x).clone(), OF.linear(x, w, None, "gelu_tanh")))
+    torch.cuda.synchronize()
+    for got, want in outs:
+      assert torch.equal(got, want)
+    st = aot_cache.stats()["test_step"]
+    assert st["captures"] == 1 and st["hits"] == 2
+    step(torch.randn((64, 256), device="cuda", dtype=torch.bfloat16))  # a new shape is a new graph
+    assert aot_cache.stats()["test_step"]["captures"] == 2
+    assert len(step.known_signatures()) == 2  # recorded on disk for the next process
+  finally:
+    aot_cache.uninstall()
