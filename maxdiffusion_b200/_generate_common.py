@@ -18,7 +18,7 @@ def run_image_pipeline(config, pipe, call_kwargs: dict, prefix: str):
     torch.cuda.synchronize()
   gen = time.perf_counter() - t0
   max_logging.log(f"warm-up: {warm:.2f}s  generation: {gen:.2f}s  ({images.shape[0] / gen:.3f} images/s)")
-  if int(os.environ.get("RANK", "0")) == 0:
+  if int(os.environ.get("RANK", "0")) == 0 or config.get("write_all_ranks", False):
     out_dir = config.get("output_dir", ".") or "."
     os.makedirs(out_dir, exist_ok=True)
     for i in range(images.shape[0]):

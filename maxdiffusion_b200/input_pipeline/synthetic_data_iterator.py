@@ -57,10 +57,12 @@ class SyntheticWanIterator:
 class SyntheticFluxIterator:
   """Packed latents [B, (H/16)*(W/16), 64], T5 embeddings [B,512,4096], CLIP pooled [B,768], position ids."""
 
-  def __init__(self, config, batch_size: int, seed: int = 0, num_samples: Optional[int] = None):
+  def __init__(self, config, batch_size: int, seed: int = 0, num_samples: Optional[int] = None, text_dim: int = 4096,
+               pooled_dim: int = 768, latent_dim: int = 64):
     g = config.get
     self.res = int(g("resolution", 1024))
     self.text_len = int(g("max_sequence_length", 512))
+    self.text_dim, self.pooled_dim, self.latent_dim = text_dim, pooled_dim, latent_dim
     self.batch_size, self.num_samples, self.produced = batch_size, num_samples, 0
     self.gen = torch.Generator().manual_seed(seed)
 
@@ -77,9 +79,9 @@ class SyntheticFluxIterator:
     ids[..., 1] = torch.arange(h)[:, None]
     ids[..., 2] = torch.arange(w)[None, :]
     return {
-        "pixel_values": _pin(torch.randn((B, h * w, 64), generator=self.gen)),
-        "text_embeds": _pin(torch.randn((B, self.text_len, 4096), generator=self.gen)),
-        "prompt_embeds": _pin(torch.randn((B, 768), generator=self.gen)),
+        "pixel_values": _pin(torch.randn((B, h * w, self.latent_dim), generator=self.gen)),
+        "text_embeds": _pin(torch.randn((B, self.text_len, self.text_dim), generator=self.gen)),
+        "prompt_embeds": _pin(torch.randn((B, self.pooled_dim), generator=self.gen)),
         "img_ids": ids.reshape(1, h * w, 3).expand(B, -1, -1).contiguous(),
         "txt_ids": torch.zeros((B, self.text_len, 3)),
     }

@@ -66,6 +66,10 @@ UNET_PRESETS = {
                  up_block_types=("CrossAttnUpBlock2D", "UpBlock2D"), layers_per_block=1, transformer_layers_per_block=(1, 1),
                  attention_head_dim=(2, 2), cross_attention_dim=32, addition_time_embed_dim=8,
                  projection_class_embeddings_input_dim=16 + 6 * 8, norm_num_groups=8),
+    "tiny_sd": dict(sample_size=16, block_out_channels=(32, 64), down_block_types=("DownBlock2D", "CrossAttnDownBlock2D"),
+                    up_block_types=("CrossAttnUpBlock2D", "UpBlock2D"), layers_per_block=1, transformer_layers_per_block=(1, 1),
+                    attention_head_dim=(2, 2), cross_attention_dim=32, addition_embed_type=None, addition_time_embed_dim=None,
+                    projection_class_embeddings_input_dim=None, norm_num_groups=8, use_linear_projection=False),
 }
 
 

@@ -22,7 +22,8 @@ from ...trainers.stable_diffusion_trainer import get_add_time_ids, resolve_unet_
 
 
 def create_scheduler(config, default: str = "FlaxEulerDiscreteScheduler"):
-  sc = dict(config.get("diffusion_scheduler_config", {}) or {})
+  # empty strings in the override mean "keep what the pretrained scheduler config says" (the defaults here)
+  sc = {k: v for k, v in dict(config.get("diffusion_scheduler_config", {}) or {}).items() if v != ""}
   name = sc.pop("_class_name", default)
   cls = SCHEDULERS[name.replace("Flax", "")]
   kwargs = dict(beta_start=0.00085, beta_end=0.012, beta_schedule="scaled_linear")

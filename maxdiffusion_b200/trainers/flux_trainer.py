@@ -62,7 +62,9 @@ class FluxTrainer:
     self.batch_size = max(1, int(float(config.get("per_device_batch_size", 1))))
 
   def load_dataset(self):
-    return SyntheticFluxIterator(self.config, self.batch_size, seed=int(self.config.get("seed", 0)) + 17)
+    cfg = self.model.cfg
+    return SyntheticFluxIterator(self.config, self.batch_size, seed=int(self.config.get("seed", 0)) + 17,
+                                 text_dim=cfg.joint_attention_dim, pooled_dim=cfg.pooled_projection_dim, latent_dim=cfg.in_channels)
 
   def train_step(self, batch: dict) -> dict:
     batch = {k: (v.to(self.device, non_blocking=True) if torch.is_tensor(v) else v) for k, v in batch.items()}

@@ -62,7 +62,7 @@ class StableDiffusionTrainer:
     group = self.mesh.group("replica") if self.mesh.size("fsdp") == 1 else dist.group.WORLD if dist.is_initialized() else None
     self.optimizer = FlatShardedOptimizer(list(self.unet.parameters()), create_optimizer(config), group=group, seed=seed)
     sc = dict(config.get("diffusion_scheduler_config", {}) or {})
-    self.prediction_type = sc.get("prediction_type", "epsilon")
+    self.prediction_type = sc.get("prediction_type") or "epsilon"  # empty = keep the pretrained scheduler's own
     self.scheduler = DDPMScheduler(beta_start=0.00085, beta_end=0.012, beta_schedule="scaled_linear",
                                    prediction_type=self.prediction_type,
                                    rescale_zero_terminal_snr=bool(sc.get("rescale_zero_terminal_snr", False)))
