@@ -132,3 +132,43 @@ class WanCheckpointer:
     if cache_dir and self.rank == 0:
       WanCheckpointer(self.config.replace(checkpoint_dir=cache_dir)).save_pipeline(0, pipe)
     return pipe
+
+  # ---- one call for the generate / train entry points -------------------------------------------
+  pipeline_module, pipeline_name = "maxdiffusion_b200.pipelines.wan.wan_pipeline", "WanPipeline2_1"
+
+  @classmethod
+  def pipeline_cls(cls):
+    import importlib
+
+    return getattr(importlib.import_module(cls.pipeline_module), cls.pipeline_name)
+
+  def load_checkpoint(self, step: Optional[int] = None, device=None):
+    """(pipeline, step): the pipeline of this checkpointer's model variant restored from `checkpoint_dir` at `step`
+    (latest when None) if a checkpoint exists there, else built from the pretrained / cached weights with step None
+    (reference: `WanCheckpointer2_1.load_checkpoint`, src/maxdiffusion/checkpointing/wan_checkpointer_2_1.py)."""
+    pcls = self.pipeline_cls()
+    have = self.manager.latest_step() if self.manager is not None else None
+    if have is not None:
+      pipe = pcls.from_config(self.config, device=device)
+      self.restore_into_pipeline(pipe, step)
+      return pipe, step if step is not None else have
+    if self.config.get("random_init", False):
+      return pcls.from_config(self.config, device=device), None
+    return self.load_pretrained_pipeline_or_diffusers(pcls, device=device), None
+
+
+class WanCheckpointer2_1(WanCheckpointer):
+  pipeline_name = "WanPipeline2_1"
+
+
+class WanCheckpointer2_2(WanCheckpointer):
+  """Two experts: items `high_noise_transformer_state` / `low_noise_transformer_state`."""
+  pipeline_name = "WanPipeline2_2"
+
+
+class WanCheckpointerI2V_2_1(WanCheckpointer):
+  pipeline_name = "WanPipelineI2V_2_1"
+
+
+class WanCheckpointerI2V_2_2(WanCheckpointer):
+  pipeline_name = "WanPipelineI2V_2_2"

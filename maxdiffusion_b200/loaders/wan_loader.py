@@ -217,8 +217,9 @@ def load_wan_transformer(model, folder: str, converted_weights_dir: str = "", dt
   return model
 
 
-def load_wan_pipeline_components(config, model_name: str, device=None) -> dict:
-  """transformer(s), VAE, scheduler, tokenizer and UMT5 text encoder from a local diffusers directory."""
+def load_wan_pipeline_components(config, model_name: str, device=None, load_transformer: bool = True) -> dict:
+  """transformer(s), VAE, scheduler, tokenizer and UMT5 text encoder from a local diffusers directory
+  (`load_transformer=False`: dataset preprocessing only needs the VAE and the text encoder)."""
   from ..models.wan.autoencoder_kl_wan import AutoencoderKLWan, WanVAEConfig
   from ..models.wan.transformer_wan import WanConfig, WanModel
   from ..schedulers.scheduling_unipc_multistep import UniPCMultistepScheduler
@@ -237,8 +238,8 @@ def load_wan_pipeline_components(config, model_name: str, device=None) -> dict:
                          os.path.join(config.converted_weights_dir, sub), dtype)
     return m.to(device)
 
-  out = {"transformer": build("transformer")}
-  if model_name == "wan2.2" and os.path.isdir(os.path.join(root, "transformer_2")):
+  out = {"transformer": build("transformer") if load_transformer else None}
+  if load_transformer and model_name == "wan2.2" and os.path.isdir(os.path.join(root, "transformer_2")):
     out["transformer_2"] = build("transformer_2")
   with open(os.path.join(root, "vae", "config.json")) as f:
     vae = AutoencoderKLWan(WanVAEConfig.from_dict(json.load(f)))

@@ -64,8 +64,9 @@ class WanPipeline:
     self.vae, self.scheduler = vae, scheduler
     self.tokenizer, self.text_encoder, self.image_encoder = tokenizer, text_encoder, image_encoder
     self.mesh = mesh if mesh is not None else create_device_mesh(config)
-    self.device = torch.device(device) if device is not None else next(transformer.parameters()).device
-    self.dtype = next(transformer.parameters()).dtype
+    anchor = transformer if transformer is not None else vae  # preprocessing pipelines carry no transformer
+    self.device = torch.device(device) if device is not None else next(anchor.parameters()).device
+    self.dtype = next(anchor.parameters()).dtype
     self.pctx = None
     if self.mesh.size("context") > 1:
       self.pctx = ContextParallel(self.mesh, str(config.get("context_strategy", "ring")),
@@ -108,11 +109,11 @@ class WanPipeline:
     return cls(config, transformer, vae, scheduler, transformer_2=transformer_2, device=device, **kw)
 
   @classmethod
-  def from_pretrained(cls, config, device=None, **kw):
+  def from_pretrained(cls, config, device=None, load_transformer: bool = True, **kw):
     """Loads diffusers-format weights from `pretrained_model_name_or_path` (a local directory)."""
     from ...loaders.wan_loader import load_wan_pipeline_components
 
-    comps = load_wan_pipeline_components(config, cls.model_name, device=device)
+    comps = load_wan_pipeline_components(config, cls.model_name, device=device, load_transformer=load_transformer)
     return cls(config, device=device, **comps, **kw)
 
   @classmethod

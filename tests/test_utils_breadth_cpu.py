@@ -1,0 +1,213 @@
+"""Utility surface: shared SD helpers, device info, safety checker, dependency check, dataset preprocessing scripts,
+package exports, Wan checkpointer variants."""
+import csv
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from maxdiffusion_b200 import pyconfig
+
+CFG = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "maxdiffusion_b200", "configs")
+
+
+def test_package_exports_resolve():
+  import maxdiffusion_b200 as M
+
+  for n in M.__all__:
+    assert getattr(M, n) is not None, n
+  assert M.FlaxStableDiffusionXLPipeline is M.StableDiffusionXLPipeline
+  assert M.VaceWanPipeline2_1.__name__ == "WanVACEPipeline2_1"
+  assert M.FlaxUniPCMultistepScheduler is M.UniPCMultistepScheduler
+  with pytest.raises(AttributeError):
+    M.NoSuchThing
+
+
+def test_dependency_check():
+  from maxdiffusion_b200.dependency_versions_check import dep_version_check, require_version
+
+  dep_version_check("torch")
+  require_version("numpy>=1.0")
+  with pytest.raises(ImportError):
+    require_version("numpy>=999.0")
+  with pytest.raises(ImportError):
+    require_version("surely_not_a_package_xyz")
+
+
+def test_gpu_utils_cpu():
+  from maxdiffusion_b200 import gpu_utils
+
+  assert gpu_utils.pad_to_alignment(129, 128) == 256 and gpu_utils.pad_to_alignment(128, 128) == 128
+  info = gpu_utils.DeviceInfo("NVIDIA B200", (10, 0), 148, 178.0, 126 << 20)
+  assert info.is_blackwell and info.sequence_alignment == 128
+  if not torch.cuda.is_available():
+    assert gpu_utils.device_info() is None and gpu_utils.print_device_memory() == {}
+    with pytest.raises(RuntimeError):
+      gpu_utils.require_blackwell()
+
+
+def test_safety_checker_thresholds():
+  from maxdiffusion_b200.pipelines.stable_diffusion.safety_checker import StableDiffusionSafetyChecker, run_safety_checker
+
+  class Vision(torch.nn.Module):
+    def forward(self, x):  # pooled output = mean colour, repeated
+      return None, x.mean(dim=(2, 3)).repeat(1, 4)[:, :8]
+
+  ck = StableDiffusionSafetyChecker(Vision(), hidden_size=8, projection_dim=8)
+  with torch.no_grad():
+    ck.visual_projection.weight.copy_(torch.eye(8))
+    ck.concept_embeds.copy_(torch.randn(17, 8, generator=torch.Generator().manual_seed(0)))
+    ck.special_care_embeds.copy_(torch.randn(3, 8, generator=torch.Generator().manual_seed(1)))
+    ck.concept_embeds_weights.fill_(2.0)  # cosine similarity never exceeds 1
+    ck.special_care_embeds_weights.fill_(2.0)
+  imgs = torch.randint(0, 255, (3, 32, 32, 3), dtype=torch.uint8)
+  out, flags = run_safety_checker(ck, imgs)
+  assert not flags.any() and torch.equal(out, imgs)
+  with torch.no_grad():
+    ck.concept_embeds_weights.fill_(-2.0)
+  out, flags = run_safety_checker(ck, imgs)
+  assert flags.all() and int(out.sum()) == 0
+  # the special-care adjustment lowers the threshold by exactly 0.01
+  with torch.no_grad():
+    pooled = Vision()(torch.ones(1, 3, 4, 4))[1]
+    ck.concept_embeds[0].copy_(pooled[0])
+    ck.concept_embeds_weights.fill_(2.0)
+    ck.concept_embeds_weights[0] = 1.005
+    ck.special_care_embeds[0].copy_(pooled[0])
+  assert not bool(ck(torch.ones(1, 3, 4, 4))[0])
+  with torch.no_grad():
+    ck.special_care_embeds_weights[0] = 0.5
+  assert bool(ck(torch.ones(1, 3, 4, 4))[0])
+
+
+def test_maxdiffusion_utils(tmp_path):
+  from maxdiffusion_b200 import maxdiffusion_utils as U
+  from maxdiffusion_b200.models.flux.transformer_flux import FLUX_PRESETS, FluxConfig, FluxTransformer2DModel
+  from maxdiffusion_b200.models.unet_2d_condition import UNET_PRESETS, UNet2DConditionModel, UNetConfig
+  from maxdiffusion_b200.models.vae import AutoencoderKL, VAEConfig
+  from maxdiffusion_b200.models.wan.transformer_wan import WAN_PRESETS, WanConfig, WanModel
+
+  cfg = pyconfig.initialize(["x", os.path.join(CFG, "base_xl.yml"), "resolution=32", "log_config=false", "per_device_batch_size=2"], unittest=True)
+  unet = UNet2DConditionModel(UNetConfig(**UNET_PRESETS["tiny"]))
+  args = U.get_dummy_unet_inputs(cfg, unet)
+  assert args[0].shape == (2, 4, 4, 4) and unet(*args).shape == (2, 4, 4, 4)
+  assert U.calculate_unet_tflops(cfg, unet) > 0
+  fcfg = pyconfig.initialize(["x", os.path.join(CFG, "base_flux_dev.yml"), "resolution=64", "max_sequence_length=8", "log_config=false"], unittest=True)
+  flux = FluxTransformer2DModel(FluxConfig(**FLUX_PRESETS["tiny"]))
+  assert flux(*U.get_dummy_flux_inputs(fcfg, flux)).shape == (1, 16, 64)
+  assert U.calculate_flux_tflops(fcfg, flux, train=False) > 0
+  wcfg = pyconfig.initialize(["x", os.path.join(CFG, "base_wan_14b.yml"), "height=32", "width=32", "num_frames=5", "log_config=false"], unittest=True)
+  wan = WanModel(WanConfig(**WAN_PRESETS["tiny"]))
+  assert wan(*U.get_dummy_wan_inputs(wcfg, wan)).shape == (1, 16, 2, 4, 4)
+  from maxdiffusion_b200.max_utils import calculate_model_tflops
+
+  traced = calculate_model_tflops(wan, *U.get_dummy_wan_inputs(wcfg, wan))
+  assert abs(U.calculate_wan_tflops(wcfg, wan, train=False) / traced - 1) < 0.25  # analytic count skips embedders / head
+  assert U.override_scheduler_config({"prediction_type": "epsilon", "timestep_spacing": "leading"}, cfg)["timestep_spacing"] in ("leading", "trailing")
+  b = U.get_shaped_batch(cfg)
+  assert b["pixel_values"].shape == (2, 4, 4, 4) and b["text_embeds"].shape == (2, 1280)
+  # dataset transforms
+  from PIL import Image
+
+  vae = AutoencoderKL(VAEConfig(block_out_channels=(32, 32), layers_per_block=1, norm_num_groups=8))
+  ex = {"image": [Image.fromarray(np.random.randint(0, 255, (40, 56, 3), np.uint8)) for _ in range(3)]}
+  out = U.transform_images(dict(ex), "image", 32)
+  assert out["pixel_values"][0].shape == (3, 32, 32) and abs(out["pixel_values"][0]).max() <= 1.0
+  out = U.transform_images(dict(ex), "image", 32, vae=vae, generator=torch.Generator().manual_seed(0))
+  assert out["pixel_values"][0].shape == (4, 16, 16)
+
+  class Tok:
+    model_max_length = 6
+
+    def __call__(self, caps, max_length, padding, truncation, return_tensors):
+      class R:
+        input_ids = torch.tensor([[len(c) % 7] * max_length for c in caps])
+      return R
+
+  out = U.tokenize_captions({"text": ["a cat", ["two", "captions"]]}, "text", Tok())
+  assert np.asarray(out["input_ids"]).shape == (2, 6)
+  out = U.tokenize_captions_xl({"text": ["a", "b"]}, "text", [Tok(), Tok()])
+  assert np.asarray(out["input_ids"]).shape == (2, 2, 6)
+
+
+def test_pusav1_to_tfrecords_and_back(tmp_path):
+  from maxdiffusion_b200.data_preprocessing import wan_pusav1_to_tfrecords
+  from maxdiffusion_b200.input_pipeline.input_pipeline_interface import TFRecordIterator
+
+  src = tmp_path / "pusa"
+  (src / "train").mkdir(parents=True)
+  g = torch.Generator().manual_seed(0)
+  lat = {}
+  with open(src / "metadata.csv", "w", newline="") as f:
+    w = csv.writer(f)
+    w.writerow(["file_name", "text"])
+    for i in range(10):
+      name = f"clip{i}.mp4"
+      w.writerow([name, f"caption {i}"])
+      lat[i] = torch.randn((16, 2, 4, 4), generator=g).to(torch.bfloat16)
+      torch.save({"latents": lat[i], "prompt_emb": {"context": torch.randn((1, 8, 32), generator=g).to(torch.bfloat16)}},
+                 src / "train" / f"{name}.tensors.pth")
+  cfg = pyconfig.initialize(["x", os.path.join(CFG, "base_wan_14b.yml"), f"train_data_dir={src}", f"tfrecords_dir={tmp_path}/rec",
+                             "no_records_per_shard=4", "log_config=false"], unittest=True)
+  files = wan_pusav1_to_tfrecords.run(cfg)
+  assert [os.path.basename(f) for f in files] == ["file_00-4.tfrec", "file_01-8.tfrec", "file_02-10.tfrec"]
+  it = TFRecordIterator(f"{tmp_path}/rec", 5, shuffle=False, repeat=False)
+  batches = list(it)
+  assert len(batches) == 2 and batches[0]["latents"].shape == (5, 16, 2, 4, 4) and batches[0]["encoder_hidden_states"].shape == (5, 8, 32)
+  assert torch.equal(batches[0]["latents"][3], lat[3].float())
+  # evaluation split: 6 samples over 3 timesteps, nothing after them
+  cfg = pyconfig.initialize(["x", os.path.join(CFG, "base_wan_14b.yml"), f"train_data_dir={src}", f"tfrecords_dir={tmp_path}/eval",
+                             "no_records_per_shard=100", "enable_eval_timesteps=true", "num_eval_samples=6", "timesteps_list=[100,500,900]",
+                             "log_config=false"], unittest=True)
+  wan_pusav1_to_tfrecords.run(cfg)
+  ev = list(TFRecordIterator(f"{tmp_path}/eval", 6, shuffle=False, repeat=False, with_timesteps=True))
+  assert len(ev) == 1 and ev[0]["timesteps"].tolist() == [100, 100, 500, 500, 900, 900]
+
+
+def test_txt2vid_preprocessing(tmp_path):
+  from maxdiffusion_b200.data_preprocessing import wan_txt2vid_data_preprocessing as P
+  from maxdiffusion_b200.input_pipeline.input_pipeline_interface import TFRecordIterator
+  from maxdiffusion_b200.pipelines.wan.wan_pipeline import WanPipeline
+
+  cfg = pyconfig.initialize(["x", os.path.join(CFG, "base_wan_14b.yml"), "wan_preset=tiny", "random_init=true", "height=32", "width=32",
+                             'vae_config_overrides={"base_dim":8}', f"tfrecords_dir={tmp_path}/rec", "no_records_per_shard=2",
+                             "max_sequence_length=8", "log_config=false"], unittest=True)
+  pipe = WanPipeline.from_config(cfg, device="cpu")
+  pipe.transformer = None
+  pipe.encode_prompt = lambda prompts, max_len: torch.stack([torch.full((max_len, 16), float(len(p))) for p in prompts])
+
+  class DS:
+    rows = [{"text": "a" * (i + 1), "image": np.random.randint(0, 255, (5, 40, 48, 3), np.uint8)} for i in range(3)]
+
+    def __len__(self):
+      return len(self.rows)
+
+    def __getitem__(self, s):
+      rows = self.rows[s]
+      return {"text": [r["text"] for r in rows], "image": [r["image"] for r in rows]}
+
+  files = P.generate_dataset(cfg, pipe, DS(), batch_size=2)
+  assert len(files) == 2
+  b = next(TFRecordIterator(f"{tmp_path}/rec", 3, shuffle=False, repeat=False))
+  assert b["latents"].shape == (3, 16, 2, 4, 4) and b["encoder_hidden_states"][:, 0, 0].tolist() == [1.0, 2.0, 3.0]
+
+
+def test_wan_checkpointer_variants(tmp_path):
+  from maxdiffusion_b200.checkpointing import WanCheckpointer2_1, WanCheckpointer2_2
+
+  args = ["wan_preset=tiny", "random_init=true", f"checkpoint_dir={tmp_path}/ck", 'vae_config_overrides={"base_dim":8}', "log_config=false"]
+  cfg = pyconfig.initialize(["x", os.path.join(CFG, "base_wan_14b.yml"), *args], unittest=True)
+  ck = WanCheckpointer2_1(cfg)
+  pipe, step = ck.load_checkpoint(device="cpu")
+  assert step is None and type(pipe).__name__ == "WanPipeline2_1"
+  ck.save_pipeline(3, pipe)
+  cfg2 = pyconfig.initialize(["x", os.path.join(CFG, "base_wan_14b.yml"), *args, "seed=7"], unittest=True)
+  pipe2, step2 = WanCheckpointer2_1(cfg2).load_checkpoint(device="cpu")
+  assert step2 == 3
+  for (k, a), (_, b) in zip(pipe.transformer.state_dict().items(), pipe2.transformer.state_dict().items()):
+    assert torch.equal(a, b), k
+  cfg3 = pyconfig.initialize(["x", os.path.join(CFG, "base_wan_27b.yml"), "wan_preset=tiny", "random_init=true", f"checkpoint_dir={tmp_path}/ck22",
+                              'vae_config_overrides={"base_dim":8}', "log_config=false"], unittest=True)
+  p3, _ = WanCheckpointer2_2(cfg3).load_checkpoint(device="cpu")
+  assert type(p3).__name__ == "WanPipeline2_2" and p3.transformer_2 is not None
