@@ -51,8 +51,10 @@ class TFRecordIterator:
       for f in files:
         for rec in tfrecord.read_records(f):
           ex = tfrecord.parse_example(rec)
+          # Wan records name the text states `encoder_hidden_states`, Stable Diffusion ones `hidden_states`
+          text_key = "encoder_hidden_states" if "encoder_hidden_states" in ex else "hidden_states"
           item = {"latents": tfrecord.parse_tensor(ex["latents"][0]).astype(np.float32),
-                  "encoder_hidden_states": tfrecord.parse_tensor(ex["encoder_hidden_states"][0]).astype(np.float32)}
+                  "encoder_hidden_states": tfrecord.parse_tensor(ex[text_key][0]).astype(np.float32)}
           if self.with_timesteps and "timesteps" in ex:
             item["timesteps"] = np.asarray(ex["timesteps"], dtype=np.int64)[0]
           yield item

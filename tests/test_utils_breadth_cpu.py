@@ -211,3 +211,56 @@ def test_wan_checkpointer_variants(tmp_path):
                               'vae_config_overrides={"base_dim":8}', "log_config=false"], unittest=True)
   p3, _ = WanCheckpointer2_2(cfg3).load_checkpoint(device="cpu")
   assert type(p3).__name__ == "WanPipeline2_2" and p3.transformer_2 is not None
+
+
+def test_pedagogical_examples(tmp_path):
+  from maxdiffusion_b200.pedagogical_examples import (attention_comparison, checkpoint_params_restore, dataset_tf_cache_to_tfrecord,
+                                                      model_flop_calculation, parameter_count, parameter_shardings)
+
+  r = attention_comparison.run(seq=64, heads=2, dim=32)
+  assert r["sdpa"]["max_abs_err"] < 1e-4
+  c = parameter_count.run("wan2.1-t2v-14b")
+  assert 14.0e9 < c["total"] < 14.6e9
+  assert checkpoint_params_restore.run(str(tmp_path / "ck"))
+  s = parameter_shardings.run("wan2.1-t2v-1.3b", 8)
+  assert s["blocks"] == 30 and s["block_shard"] * 8 >= s["block_numel"]
+  cfg = pyconfig.initialize(["x", os.path.join(CFG, "base_wan_14b.yml"), "wan_preset=tiny", "height=32", "width=32", "num_frames=5",
+                             "max_sequence_length=16", "log_config=false"], unittest=True)
+  f = model_flop_calculation.run(cfg)
+  assert abs(f["analytic"] / f["traced"] - 1) < 0.25
+  # re-sharding keeps every record
+  from maxdiffusion_b200.data_preprocessing.tfrecord_shards import ShardedWriter, create_example
+  from maxdiffusion_b200.input_pipeline.tfrecord import read_records
+
+  w = ShardedWriter(str(tmp_path / "a"), 100)
+  for i in range(7):
+    w.write(create_example(np.full((2, 2), i, np.float32), np.zeros((1, 4), np.float32)))
+  w.close()
+  files = dataset_tf_cache_to_tfrecord.run(str(tmp_path / "a"), str(tmp_path / "b"), 3)
+  assert len(files) == 3 and sum(1 for f in files for _ in read_records(f)) == 7
+
+
+def test_save_sd_checkpoint_example_and_eval_assert(tmp_path):
+  import json
+  import subprocess
+  import sys
+
+  from maxdiffusion_b200.pedagogical_examples import save_sd_checkpoint
+  from maxdiffusion_b200.pipelines.pipeline_utils import load_components
+
+  cfg = pyconfig.initialize(["x", os.path.join(CFG, "base15.yml"), "random_init=True", "unet_preset=tiny_sd", f"output_dir={tmp_path}/out",
+                             'vae_config_overrides={"block_out_channels":[32,32],"layers_per_block":1,"norm_num_groups":8,"latent_channels":4}',
+                             f"checkpoint_dir={tmp_path}/none", "log_config=false"], unittest=True)
+  out = save_sd_checkpoint.run(cfg)
+  comps = load_components(out)
+  assert {"unet", "vae", "scheduler"} <= set(comps)
+  root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+  m = tmp_path / "metrics.txt"
+  with open(m, "w") as f:
+    for i in range(20):
+      f.write(json.dumps({"learning/loss": 1.0 / (i + 1), "perf/step_time_seconds": 0.5, "perf/per_device_tflops_per_sec": 700.0}) + "\n")
+  script = os.path.join(root, "end_to_end", "gpu", "eval_assert.py")
+  assert subprocess.run([sys.executable, script, "final_loss", str(m), "0.1"]).returncode == 0
+  assert subprocess.run([sys.executable, script, "final_loss", str(m), "0.01"], capture_output=True).returncode != 0
+  assert subprocess.run([sys.executable, script, "avg_tflops", str(m), "600"]).returncode == 0
+  assert subprocess.run([sys.executable, script, "avg_step_time", str(m), "0.4"], capture_output=True).returncode != 0
