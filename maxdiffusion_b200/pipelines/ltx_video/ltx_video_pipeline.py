@@ -16,6 +16,8 @@ Behaviour follows the reference (src/maxdiffusion/pipelines/ltx_video/ltx_video_
 """
 from __future__ import annotations
 
+from dataclasses import dataclass
+
 import time
 from typing import List, Optional, Sequence
 
@@ -45,6 +47,18 @@ def _per_step(values, guidance_timesteps, timesteps):
     idx = int(torch.argmin((gt - float(t)).abs()))
     out.append(values[idx])
   return out
+
+
+@dataclass
+class ConditioningItem:
+  """A frame or clip the generated video must contain: `media_item` [B,3,F,H,W] in [-1,1] (F = 1 + 8k), the frame
+  number it starts at, the strength (1 = keep exactly), and an optional top-left position when it is smaller than the
+  frame (reference: src/maxdiffusion/pipelines/ltx_video/ltx_video_pipeline.py:72-88)."""
+  media_item: torch.Tensor
+  media_frame_number: int = 0
+  conditioning_strength: float = 1.0
+  media_x: Optional[int] = None
+  media_y: Optional[int] = None
 
 
 class LTXVideoPipeline:
@@ -78,6 +92,54 @@ class LTXVideoPipeline:
     grid = torch.stack([t_pix, y.float() * self.spatial_ratio, x.float() * self.spatial_ratio]).reshape(3, -1)
     return grid[None].repeat(batch, 1, 1).to(self.device)
 
+  def latent_spatial_position(self, latents, item: ConditioningItem, height: int, width: int, strip_latent_border: bool = True):
+    """Where the item's latents go in the latent frame; latent borders that do not coincide with a frame border are
+    dropped, because they were computed from padding (reference: `get_latent_spatial_position` :533-579)."""
+    r = self.spatial_ratio
+    h, w = item.media_item.shape[-2:]
+    if h > height or w > width or h % r or w % r:
+      raise ValueError(f"conditioning item {h}x{w} must fit {height}x{width} and be a multiple of {r}")
+    x0 = (width - w) // 2 if item.media_x is None else item.media_x
+    y0 = (height - h) // 2 if item.media_y is None else item.media_y
+    if strip_latent_border:
+      xs, xe = (1 if x0 > 0 else 0), (-1 if x0 + w < width else None)
+      ys, ye = (1 if y0 > 0 else 0), (-1 if y0 + h < height else None)
+      latents = latents[..., ys:ye, xs:xe]
+      x0, y0 = x0 + (r if x0 > 0 else 0), y0 + (r if y0 > 0 else 0)
+    return latents, x0 // r, y0 // r
+
+  @torch.no_grad()
+  def prepare_conditioning(self, init_latents, items: Sequence[ConditioningItem], height: int, width: int, num_frames: int,
+                           generator=None):
+    """Blends the VAE latents of every item into `init_latents` [B,C,lf,lh,lw] and returns them with the conditioning
+    mask [B,lf,lh,lw] holding each token's strength (0 = free). Items start at frame 0 (the reference handles no
+    other case either: `prepare_conditioning` :446-531)."""
+    mask = torch.zeros_like(init_latents[:, 0])
+    vp = next(self.vae.parameters())
+    for item in items:
+      m = item.media_item
+      n = m.shape[2]
+      if n % self.temporal_ratio != 1:
+        raise ValueError(f"a conditioning item needs 1 + {self.temporal_ratio}k frames, got {n}")
+      if item.media_frame_number != 0:
+        raise NotImplementedError("conditioning items must start at frame 0")
+      if item.media_frame_number + n > num_frames:
+        raise ValueError("the conditioning item does not fit into the video")
+      if m.shape[-2:] != (height, width) and item.media_x is None and item.media_y is None:
+        flat = m.permute(0, 2, 1, 3, 4).reshape(-1, m.shape[1], *m.shape[-2:])
+        flat = torch.nn.functional.interpolate(flat.float(), size=(height, width), mode="bilinear", align_corners=False)
+        m = flat.reshape(m.shape[0], n, m.shape[1], height, width).permute(0, 2, 1, 3, 4)
+        item = ConditioningItem(m, item.media_frame_number, item.conditioning_strength)
+      mean, _ = self.vae.encode(m.to(vp.device, vp.dtype))
+      z = self.vae.normalize_latents(mean).to(init_latents)
+      z, lx, ly = self.latent_spatial_position(z, item, height, width)
+      _, _, fl, hl, wl = z.shape
+      s = float(item.conditioning_strength)
+      sl = (slice(None), slice(None), slice(0, fl), slice(ly, ly + hl), slice(lx, lx + wl))
+      init_latents[sl] = (1 - s) * init_latents[sl] + s * z
+      mask[:, :fl, ly:ly + hl, lx:lx + wl] = s
+    return init_latents, mask
+
   @torch.no_grad()
   def __call__(self, prompt=None, negative_prompt="", height: int = 512, width: int = 704, num_frames: int = 121,
                frame_rate: float = 30.0, num_inference_steps: int = 30, guidance_scale=3.0, stg_scale=0.0,
@@ -86,7 +148,9 @@ class LTXVideoPipeline:
                skip_final_inference_steps: int = 0, cfg_star_rescale: bool = False, latents=None, seed: int = 0,
                prompt_embeds=None, prompt_attention_mask=None, negative_prompt_embeds=None,
                negative_prompt_attention_mask=None, decode_timestep: float = 0.05, decode_noise_scale: float = 0.025,
-               output_type: str = "uint8", max_sequence_length: int = 512, return_trace: bool = False):
+               output_type: str = "uint8", max_sequence_length: int = 512, return_trace: bool = False,
+               conditioning_items: Optional[Sequence[ConditioningItem]] = None, image_cond_noise_scale: float = 0.0,
+               per_token_timestep: bool = False):
     r, rt = self.spatial_ratio, self.temporal_ratio
     if height % r or width % r:
       raise ValueError(f"`height` and `width` have to be divisible by {r} but are {height} and {width}.")
@@ -109,7 +173,13 @@ class LTXVideoPipeline:
       x = (1 - t_start) * latents.float() + t_start * noise.to(latents.device)
     else:
       x = noise
+    cond_mask = init_tokens = None
+    if conditioning_items:
+      x, cm = self.prepare_conditioning(x.clone(), conditioning_items, height, width, num_frames)
+      cond_mask = cm.reshape(B, lf * lh * lw).to(self.device)
     tokens = x.to(self.device).permute(0, 2, 3, 4, 1).reshape(B, lf * lh * lw, C).contiguous()
+    if cond_mask is not None:
+      init_tokens = tokens.clone()
     grid = self.latent_positions(B, lf, lh, lw, frame_rate)
 
     gs = _per_step(guidance_scale, guidance_timesteps, timesteps)
@@ -130,6 +200,12 @@ class LTXVideoPipeline:
     trace["conditioning"] = time.perf_counter() - t0
     t1 = time.perf_counter()
     for i, t in enumerate(timesteps):
+      if cond_mask is not None and image_cond_noise_scale > 0.0:
+        # fully conditioned tokens get a little timestep-dependent noise so that motion can start from them
+        # (reference: `add_noise_to_image_conditioning_latents_jax` :918-935)
+        hard = (cond_mask > 1.0 - 1e-6)[..., None]
+        n = torch.randn(tokens.shape, generator=g).to(tokens)
+        tokens = torch.where(hard, init_tokens + image_cond_noise_scale * n * float(t) ** 2, tokens)
       x_in = tokens.repeat(num_conds, 1, 1).to(self.dtype)
       sm = None
       if do_stg and sb[i]:
@@ -138,6 +214,9 @@ class LTXVideoPipeline:
         for blk in sb[i]:
           sm[blk, (num_conds - 1) * B:] = 0
       ts = torch.full((B * num_conds,), float(t), device=self.device)
+      if cond_mask is not None and per_token_timestep:
+        # conditioned tokens are presented at their own (lower) noise level; the reference keeps one scalar per sample
+        ts = torch.minimum(ts[:, None], (1.0 - cond_mask).repeat(num_conds, 1))
       pred = self.transformer(x_in, grid.repeat(num_conds, 1, 1), embeds, ts, masks, sm, skip_layer_strategy).float()
       chunks = pred.chunk(num_conds)
       cond = chunks[1] if do_cfg else chunks[0]
@@ -154,7 +233,11 @@ class LTXVideoPipeline:
         if ss[i] > 0.0 and rs[i] != 1.0:
           factor = cond.reshape(B, -1).std(dim=1, keepdim=True) / out.reshape(B, -1).std(dim=1, keepdim=True)
           out = out * (rs[i] * factor + (1 - rs[i])).view(B, 1, 1)
-      tokens, state = self.scheduler.step(state, out, t, tokens)
+      new_tokens, state = self.scheduler.step(state, out, t, tokens)
+      if cond_mask is not None:  # a token is only denoised once the schedule has passed its conditioning level
+        free = (float(t) - 1e-6 < (1.0 - cond_mask))[..., None]
+        new_tokens = torch.where(free, new_tokens, tokens)
+      tokens = new_tokens
     if self.device.type == "cuda":
       torch.cuda.synchronize()
     trace["denoise"] = time.perf_counter() - t1

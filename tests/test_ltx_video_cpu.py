@@ -53,3 +53,103 @@ def test_generate_ltx_video_multi_scale_tiny(tmp_path):
       unittest=True)
   video = G.run(config)
   assert video.shape == (1, 9, 96, 96, 3) and video.dtype == torch.uint8
+
+
+def _tiny_pipe():
+  from maxdiffusion_b200.models.ltx2.autoencoder_kl_ltx2 import LTX2VAEConfig, LTX2VideoAutoencoderKL
+  from maxdiffusion_b200.pipelines.ltx_video.ltx_video_pipeline import LTXVideoPipeline
+
+  torch.manual_seed(0)
+  tr = Transformer3DModel(LTXVideoConfig(**LTXV_PRESETS["tiny"])).eval()
+  vae = LTX2VideoAutoencoderKL(LTX2VAEConfig(latent_channels=8, block_out_channels=(8, 16, 16, 32), decoder_block_out_channels=(8, 16, 32),
+                                             layers_per_block=(1, 1, 1, 1, 1), decoder_layers_per_block=(1, 1, 1, 1),
+                                             timestep_conditioning=True, decoder_causal=True)).eval()
+  return LTXVideoPipeline(tr, vae, device="cpu")
+
+
+def test_conditioning_item_keeps_first_frame_latents():
+  from maxdiffusion_b200.pipelines.ltx_video.ltx_video_pipeline import ConditioningItem
+
+  pipe = _tiny_pipe()
+  img = torch.rand(1, 3, 1, 64, 64) * 2 - 1
+  kw = dict(height=64, width=64, num_frames=9, num_inference_steps=3, guidance_scale=1.0, output_type="latent",
+            prompt_embeds=torch.randn(1, 6, 16), prompt_attention_mask=torch.ones(1, 6, dtype=torch.long))
+  lat = pipe(conditioning_items=[ConditioningItem(img, 0, 1.0)], **kw)
+  mean, _ = pipe.vae.encode(img)
+  want = pipe.vae.normalize_latents(mean)
+  assert lat.shape == (1, 8, 2, 2, 2)
+  assert torch.allclose(lat[:, :, :1], want, atol=1e-5)  # strength 1: never denoised, never noised
+  free = pipe(**kw)
+  assert not torch.allclose(free[:, :, :1], want, atol=1e-2) and not torch.allclose(lat[:, :, 1:], free[:, :, 1:], atol=1e-4)
+  # partial strength: blended start, denoised once t passes 1 - strength
+  soft = pipe(conditioning_items=[ConditioningItem(img, 0, 0.5)], **kw)
+  assert not torch.allclose(soft[:, :, :1], want, atol=1e-3)
+  # per-token timesteps and hard-conditioning noise run and still pin nothing but change the rest
+  noisy = pipe(conditioning_items=[ConditioningItem(img, 0, 1.0)], image_cond_noise_scale=0.15, per_token_timestep=True, **kw)
+  assert torch.isfinite(noisy).all()
+
+
+def test_conditioning_item_position_and_border_strip():
+  from maxdiffusion_b200.pipelines.ltx_video.ltx_video_pipeline import ConditioningItem
+
+  pipe = _tiny_pipe()
+  z = torch.zeros(1, 8, 1, 3, 3)
+  it = ConditioningItem(torch.zeros(1, 3, 1, 96, 96), 0, 1.0, media_x=32, media_y=0)
+  out, lx, ly = pipe.latent_spatial_position(z, it, 128, 160)
+  # left edge is interior (stripped, shifted by one latent), right edge (32+96=128 < 160) too; top touches the border
+  assert out.shape[-2:] == (2, 1) and (lx, ly) == (2, 0)
+  it2 = ConditioningItem(torch.zeros(1, 3, 1, 96, 96), 0, 1.0)
+  out2, lx2, ly2 = pipe.latent_spatial_position(z, it2, 96, 96)
+  assert out2.shape[-2:] == (3, 3) and (lx2, ly2) == (0, 0)
+
+
+def test_prompt_enhancement_and_crf_identity():
+  from maxdiffusion_b200.models.ltx_video.utils import prompt_enhance_utils as PE
+  from maxdiffusion_b200.models.ltx_video.utils.diffusers_config_mapping import diffusers_to_native, native_to_diffusers
+  from maxdiffusion_b200.pipelines.ltx_video import crf_compressor
+  from maxdiffusion_b200.pipelines.ltx_video.ltx_video_pipeline import ConditioningItem
+
+  class Tok:
+    def apply_chat_template(self, msgs, tokenize, add_generation_prompt):
+      return " | ".join(m["content"] for m in msgs)
+
+    def __call__(self, texts, return_tensors, padding=False):
+      self.texts = texts
+      return {"input_ids": torch.zeros(len(texts), 3, dtype=torch.long)}
+
+    def batch_decode(self, ids, skip_special_tokens):
+      return [f"enhanced:{len(i)}" for i in ids]
+
+  class LM:
+    device = "cpu"
+
+    def generate(self, input_ids, max_new_tokens):
+      return torch.zeros(input_ids.shape[0], 3 + 4, dtype=torch.long)
+
+  class Proc:
+    def __call__(self, prompts, images, return_tensors):
+      return {"input_ids": torch.zeros(len(images), 1, dtype=torch.long), "pixel_values": torch.zeros(len(images), 3, 2, 2)}
+
+    def batch_decode(self, ids, skip_special_tokens):
+      return ["a photo"] * len(ids)
+
+  class Cap:
+    device = "cpu"
+
+    def generate(self, **kw):
+      return torch.zeros(kw["input_ids"].shape[0], 2, dtype=torch.long)
+
+  tok = Tok()
+  assert PE.generate_cinematic_prompt(None, None, LM(), tok, "a cat") == ["enhanced:4"]
+  assert "user_prompt: a cat" in tok.texts[0] and "image_caption" not in tok.texts[0]
+  item = ConditioningItem(torch.zeros(1, 3, 1, 8, 8), 0, 1.0)
+  assert PE.generate_cinematic_prompt(Cap(), Proc(), LM(), tok, ["a cat"], [item]) == ["enhanced:4"]
+  assert "image_caption: a photo" in tok.texts[0]
+  late = ConditioningItem(torch.zeros(1, 3, 1, 8, 8), 8, 1.0)
+  assert PE.generate_cinematic_prompt(Cap(), Proc(), LM(), tok, ["a cat"], [late]) == ["a cat"]
+  x = torch.rand(9, 9, 3)
+  assert crf_compressor.compress(x, 0) is x
+  d = {"_class_name": "LTXVideoTransformer3DModel", "num_layers": 48, "num_attention_heads": 32, "attention_head_dim": 128,
+       "cross_attention_dim": 4096, "caption_channels": 4096, "in_channels": 128, "out_channels": 128}
+  n = diffusers_to_native(d)
+  assert n["num_layers"] == 48 and n["qk_norm"] == "rms_norm" and native_to_diffusers(n)["attention_head_dim"] == 128
