@@ -24,7 +24,7 @@ namespace fab {
 constexpr int D = 128;
 constexpr int BX = 128;   // resident rows
 constexpr int BY = 64;    // streamed rows per step
-constexpr int Y_STAGES = 3;
+constexpr int Y_STAGES = 4;
 constexpr int X_TILE_BYTES = BX * D * 2;        // 32 KiB (two 16 KiB chunks)
 constexpr int X_CHUNK_BYTES = BX * 128;         // 16 KiB
 constexpr int Y_TILE_BYTES = BY * D * 2;        // 16 KiB (two 8 KiB chunks)
@@ -67,12 +67,12 @@ flash_bwd_kernel(const __grid_constant__ Maps maps, const Params p) {
   float* stat_s = reinterpret_cast<float*>(sy + Y_STAGES * 2 * Y_TILE_BYTES);  // [Y_STAGES][lse 64 | delta 64]
   uint64_t* bars = reinterpret_cast<uint64_t*>(stat_s + Y_STAGES * 128);
   uint64_t* x_full = bars;          // [1]
-  uint64_t* y_full = bars + 1;      // [3]
-  uint64_t* y_empty = bars + 4;     // [3]
-  uint64_t* t_full = bars + 7;      // [2]
-  uint64_t* ps_full = bars + 9;     // [2]
-  uint64_t* acc_final = bars + 11;  // [1]
-  uint32_t* tmem_ptr_smem = reinterpret_cast<uint32_t*>(bars + 12);
+  uint64_t* y_full = bars + 1;                      // [Y_STAGES]
+  uint64_t* y_empty = y_full + Y_STAGES;            // [Y_STAGES]
+  uint64_t* t_full = y_empty + Y_STAGES;            // [2]
+  uint64_t* ps_full = t_full + 2;                   // [2]
+  uint64_t* acc_final = ps_full + 2;                // [1]
+  uint32_t* tmem_ptr_smem = reinterpret_cast<uint32_t*>(acc_final + 1);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_ptr_smem + 1);
 
   const int warp = threadIdx.x >> 5;
@@ -87,12 +87,12 @@ flash_bwd_kernel(const __grid_constant__ Maps maps, const Params p) {
   if (threadIdx.x == 0) {
     mbar_init(x_full, 1);
     for (int i = 0; i < Y_STAGES; ++i) {
-      mbar_init(&y_full[i], DKV ? 33 : 1);  // TMA transaction (+ 32 lanes staging lse / delta)
+      mbar_init(&y_full[i], 1);  // lane 0 of the producer: TMA transaction bytes (tiles, and lse / delta in the DKV pass)
       mbar_init(&y_empty[i], 1);
     }
     for (int i = 0; i < 2; ++i) {
       mbar_init(&t_full[i], 1);
-      mbar_init(&ps_full[i], EW_GROUPS * 128);
+      mbar_init(&ps_full[i], EW_GROUPS * 4);  // one elected lane per elementwise warp
     }
     mbar_init(acc_final, 1);
     *abort_flag = 0;
@@ -121,6 +121,10 @@ flash_bwd_kernel(const __grid_constant__ Maps maps, const Params p) {
         }
       }
       const long long stat_base = (static_cast<long long>(batch) * p.H + head) * p.q_len;
+      // lse / delta of the streamed query rows ride in the stage. When the rows start on 16-byte boundaries they are
+      // fetched by bulk copies that complete on the stage's barrier; otherwise the lanes copy them by hand.
+      const bool stat_bulk = DKV && (p.q_len % 4 == 0) && ((reinterpret_cast<uintptr_t>(p.lse) & 15) == 0) &&
+                             ((reinterpret_cast<uintptr_t>(p.delta) & 15) == 0);
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
@@ -128,17 +132,9 @@ flash_bwd_kernel(const __grid_constant__ Maps maps, const Params p) {
         const int nblk = (p.y_len[seg] + BY - 1) / BY;
         for (int jb = 0; jb < nblk; ++jb) {
           if (!mbar_wait(&y_empty[stage], phase ^ 1u, abort_flag, p.status, 70)) { ok = false; break; }
-          if (lane == 0) {
-            uint8_t* d1 = sy + stage * 2 * Y_TILE_BYTES;
-            uint8_t* d2 = d1 + Y_TILE_BYTES;
-            mbar_expect_tx(&y_full[stage], 2 * Y_TILE_BYTES);
-            for (int c = 0; c < 2; ++c) {
-              tma_load_4d(d1 + c * Y_CHUNK_BYTES, &maps.y1[seg], &y_full[stage], c * 64, head, jb * BY, batch);
-              tma_load_4d(d2 + c * Y_CHUNK_BYTES, &maps.y2[seg], &y_full[stage], c * 64, head, jb * BY, batch);
-            }
-          }
-          if (DKV) {
-            float* st = stat_s + stage * 128;
+          float* st = stat_s + stage * 128;
+          const uint32_t stat_bytes = stat_bulk ? static_cast<uint32_t>(min(BY, p.q_len - jb * BY)) * 4u : 0u;
+          if (DKV && !stat_bulk) {
 #pragma unroll
             for (int h = 0; h < 2; ++h) {
               const int qi = lane + 32 * h;
@@ -146,7 +142,20 @@ flash_bwd_kernel(const __grid_constant__ Maps maps, const Params p) {
               st[qi] = (q < p.q_len) ? p.lse[stat_base + q] : 0.0f;
               st[64 + qi] = (q < p.q_len) ? p.delta[stat_base + q] : 0.0f;
             }
-            mbar_arrive(&y_full[stage]);
+            __syncwarp();
+          }
+          if (lane == 0) {
+            uint8_t* d1 = sy + stage * 2 * Y_TILE_BYTES;
+            uint8_t* d2 = d1 + Y_TILE_BYTES;
+            mbar_expect_tx(&y_full[stage], 2 * Y_TILE_BYTES + 2 * stat_bytes);
+            for (int c = 0; c < 2; ++c) {
+              tma_load_4d(d1 + c * Y_CHUNK_BYTES, &maps.y1[seg], &y_full[stage], c * 64, head, jb * BY, batch);
+              tma_load_4d(d2 + c * Y_CHUNK_BYTES, &maps.y2[seg], &y_full[stage], c * 64, head, jb * BY, batch);
+            }
+            if (stat_bytes) {
+              bulk_load_1d(st, p.lse + stat_base + jb * BY, stat_bytes, &y_full[stage]);
+              bulk_load_1d(st + 64, p.delta + stat_base + jb * BY, stat_bytes, &y_full[stage]);
+            }
           }
           if (++stage == Y_STAGES) { stage = 0; phase ^= 1u; }
         }
@@ -159,43 +168,44 @@ flash_bwd_kernel(const __grid_constant__ Maps maps, const Params p) {
       constexpr uint32_t idesc_acc = make_idesc_bf16(128, 128, false, true); // accumulators, B MN-major
       bool ok = mbar_wait(x_full, 0, abort_flag, p.status, 80);
       tc_fence_after_sync();
-      const uint32_t x1a = smem_u32(sx1), x2a = smem_u32(sx2);
+      // Shared-memory descriptors are built once: the address field (bits 0-13, units of 16 bytes) of a
+      // descriptor advances by plain addition, so one MMA costs one or two integer adds on the issuing thread.
+      const uint64_t x1d = make_smem_desc(smem_u32(sx1), 16, 1024), x2d = make_smem_desc(smem_u32(sx2), 16, 1024);
+      // streamed tiles: K-major descriptors for the score MMAs, MN-major ones for the accumulating MMAs
+      const uint64_t ys0 = make_smem_desc(smem_u32(sy), 16, 1024), ym0 = make_smem_desc(smem_u32(sy), Y_CHUNK_BYTES, 1024);
+      constexpr uint32_t STAGE_STEP = (2 * Y_TILE_BYTES) >> 4, TILE_STEP = Y_TILE_BYTES >> 4;
       auto issue_scores = [&](int stage, int b) {
-        const uint32_t y1a = smem_u32(sy + stage * 2 * Y_TILE_BYTES);
-        const uint32_t y2a = y1a + Y_TILE_BYTES;
+        const uint64_t y1d = ys0 + stage * STAGE_STEP, y2d = y1d + TILE_STEP;
 #pragma unroll
         for (int k = 0; k < D / 16; ++k) {
-          const uint32_t xo = (k >> 2) * X_CHUNK_BYTES + (k & 3) * 32;
-          const uint32_t yo = (k >> 2) * Y_CHUNK_BYTES + (k & 3) * 32;
-          umma_ss(tmem_base + b * 64, make_smem_desc(x1a + xo, 16, 1024), make_smem_desc(y1a + yo, 16, 1024),
-                  idesc_t, k > 0 ? 1u : 0u);
+          const uint32_t xo = ((k >> 2) * X_CHUNK_BYTES + (k & 3) * 32) >> 4;
+          const uint32_t yo = ((k >> 2) * Y_CHUNK_BYTES + (k & 3) * 32) >> 4;
+          umma_ss(tmem_base + b * 64, x1d + xo, y1d + yo, idesc_t, k > 0 ? 1u : 0u);
         }
 #pragma unroll
         for (int k = 0; k < D / 16; ++k) {
-          const uint32_t xo = (k >> 2) * X_CHUNK_BYTES + (k & 3) * 32;
-          const uint32_t yo = (k >> 2) * Y_CHUNK_BYTES + (k & 3) * 32;
-          umma_ss(tmem_base + 128 + b * 64, make_smem_desc(x2a + xo, 16, 1024), make_smem_desc(y2a + yo, 16, 1024),
-                  idesc_t, k > 0 ? 1u : 0u);
+          const uint32_t xo = ((k >> 2) * X_CHUNK_BYTES + (k & 3) * 32) >> 4;
+          const uint32_t yo = ((k >> 2) * Y_CHUNK_BYTES + (k & 3) * 32) >> 4;
+          umma_ss(tmem_base + 128 + b * 64, x2d + xo, y2d + yo, idesc_t, k > 0 ? 1u : 0u);
         }
         umma_commit(&t_full[b]);
       };
       auto issue_acc = [&](int stage, int b, bool first) {
-        const uint32_t y1a = smem_u32(sy + stage * 2 * Y_TILE_BYTES);
-        const uint32_t y2a = y1a + Y_TILE_BYTES;
+        const uint64_t y1d = ym0 + stage * STAGE_STEP, y2d = y1d + TILE_STEP;
 #pragma unroll
         for (int k = 0; k < BY / 16; ++k) {
           const uint32_t acol = k * 16;  // packed bf16 columns of this K-step (written by column group k)
           if (DKV) {
             // dV += P^T dO_i
-            umma_ts(tmem_base + 256, tmem_base + b * 64 + acol, make_smem_desc(y2a + k * 2048, Y_CHUNK_BYTES, 1024),
-                    idesc_acc, (!first || k > 0) ? 1u : 0u);
+            umma_ts(tmem_base + 256, tmem_base + b * 64 + acol, y2d + k * (2048 >> 4), idesc_acc,
+                    (!first || k > 0) ? 1u : 0u);
             // dK += dS^T Q_i
-            umma_ts(tmem_base + 384, tmem_base + 128 + b * 64 + acol,
-                    make_smem_desc(y1a + k * 2048, Y_CHUNK_BYTES, 1024), idesc_acc, (!first || k > 0) ? 1u : 0u);
+            umma_ts(tmem_base + 384, tmem_base + 128 + b * 64 + acol, y1d + k * (2048 >> 4), idesc_acc,
+                    (!first || k > 0) ? 1u : 0u);
           } else {
             // dQ += dS K_j
-            umma_ts(tmem_base + 256, tmem_base + 128 + b * 64 + acol,
-                    make_smem_desc(y1a + k * 2048, Y_CHUNK_BYTES, 1024), idesc_acc, (!first || k > 0) ? 1u : 0u);
+            umma_ts(tmem_base + 256, tmem_base + 128 + b * 64 + acol, y1d + k * (2048 >> 4), idesc_acc,
+                    (!first || k > 0) ? 1u : 0u);
           }
         }
         umma_commit(&y_empty[stage]);
@@ -295,8 +305,9 @@ flash_bwd_kernel(const __grid_constant__ Maps maps, const Params p) {
 #pragma unroll
               for (int h = 0; h < 2; ++h) {
                 const int col = wg * 16 + 2 * c + h;
-                const float lse = DKV ? st[col] : lse_r;
-                const float del = DKV ? st[64 + col] : delta_r;
+                const bool col_ok = col < valid;
+                const float lse = DKV ? (col_ok ? st[col] : 0.0f) : lse_r;
+                const float del = DKV ? (col_ok ? st[64 + col] : 0.0f) : delta_r;
                 float pe = fast_exp2(__uint_as_float(t1[2 * c + h]) * p.scale_log2 - lse);
                 if (!row_ok || col >= valid) pe = 0.0f;
                 pv[h] = pe;
@@ -310,7 +321,8 @@ flash_bwd_kernel(const __grid_constant__ Maps maps, const Params p) {
           tmem_st_x8(tmem_base + lane_off + 128 + b * 64 + wg * 16, ds);
           tmem_wait_st();
           tc_fence_before_sync();
-          mbar_arrive(&ps_full[b]);
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&ps_full[b]);
         }
       }
       if (ok && mbar_wait(acc_final, 0, abort_flag, p.status, 91)) {

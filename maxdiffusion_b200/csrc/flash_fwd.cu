@@ -204,7 +204,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
       mbar_init(&v_full[i], 1);
       mbar_init(&v_empty[i], 1);
       mbar_init(&s_full[i], 1);
-      mbar_init(&p_full[i], 128);
+      mbar_init(&p_full[i], 4);  // one elected lane per softmax warp
       mbar_init(&o_final[i], 1);
     }
     *abort_flag = 0;
@@ -433,7 +433,8 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
           l += rowsum;
           tmem_wait_st();
           tc_fence_before_sync();
-          mbar_arrive(&p_full[t]);
+          __syncwarp();
+          if ((threadIdx.x & 31) == 0) mbar_arrive(&p_full[t]);
         }
       }
       if (!ok) break;
