@@ -31,7 +31,7 @@ constexpr int Y_TILE_BYTES = BY * D * 2;        // 16 KiB (two 8 KiB chunks)
 constexpr int Y_CHUNK_BYTES = BY * 128;         // 8 KiB
 constexpr int MAX_SEGMENTS = 8;
 constexpr int EW_GROUPS = 4;                    // elementwise warp groups, 16 of the 64 columns each
-constexpr int NUM_THREADS = 128 + EW_GROUPS * 128;  // warp 0 TMA, warp 1 MMA, warps 4.. elementwise
+constexpr int NUM_THREADS = 128 + EW_GROUPS * 128;  // warp 0 TMA, warp 1 score MMAs, warp 2 accumulating MMAs, warps 4.. elementwise
 constexpr int SMEM_BYTES = 2 * X_TILE_BYTES + Y_STAGES * 2 * Y_TILE_BYTES + Y_STAGES * 128 * 4 + 1024 + 256;
 
 struct Maps {
@@ -71,7 +71,8 @@ flash_bwd_kernel(const __grid_constant__ Maps maps, const Params p) {
   uint64_t* y_empty = y_full + Y_STAGES;            // [Y_STAGES]
   uint64_t* t_full = y_empty + Y_STAGES;            // [2]
   uint64_t* ps_full = t_full + 2;                   // [2]
-  uint64_t* acc_final = ps_full + 2;                // [1]
+  uint64_t* t_free = ps_full + 2;                   // [2] accumulating products that read the score buffers completed
+  uint64_t* acc_final = t_free + 2;                 // [1]
   uint32_t* tmem_ptr_smem = reinterpret_cast<uint32_t*>(acc_final + 1);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_ptr_smem + 1);
 
@@ -92,6 +93,7 @@ flash_bwd_kernel(const __grid_constant__ Maps maps, const Params p) {
     }
     for (int i = 0; i < 2; ++i) {
       mbar_init(&t_full[i], 1);
+      mbar_init(&t_free[i], 1);
       mbar_init(&ps_full[i], EW_GROUPS * 4);  // one elected lane per elementwise warp
     }
     mbar_init(acc_final, 1);
@@ -162,20 +164,28 @@ flash_bwd_kernel(const __grid_constant__ Maps maps, const Params p) {
       }
     }
   } else if (warp == 1) {
-    // ------------------------------ MMA issuer --------------------------------
+    // ------------------------------ issuing lane A: score products --------------
+    // Two lanes in different warps feed the tensor pipe: a step's waits, commits and MMA instructions cost the
+    // issuing lane more cycles than the products take to execute, so the score products and the accumulating
+    // products are issued independently. Every dependency between them is an mbarrier.
     if (lane == 0 && total_steps > 0) {
       constexpr uint32_t idesc_t = make_idesc_bf16(128, BY, false, false);   // score tiles, N = 64
-      constexpr uint32_t idesc_acc = make_idesc_bf16(128, 128, false, true); // accumulators, B MN-major
       bool ok = mbar_wait(x_full, 0, abort_flag, p.status, 80);
       tc_fence_after_sync();
       // Shared-memory descriptors are built once: the address field (bits 0-13, units of 16 bytes) of a
-      // descriptor advances by plain addition, so one MMA costs one or two integer adds on the issuing thread.
+      // descriptor advances by plain addition.
       const uint64_t x1d = make_smem_desc(smem_u32(sx1), 16, 1024), x2d = make_smem_desc(smem_u32(sx2), 16, 1024);
-      // streamed tiles: K-major descriptors for the score MMAs, MN-major ones for the accumulating MMAs
-      const uint64_t ys0 = make_smem_desc(smem_u32(sy), 16, 1024), ym0 = make_smem_desc(smem_u32(sy), Y_CHUNK_BYTES, 1024);
+      const uint64_t ys0 = make_smem_desc(smem_u32(sy), 16, 1024);
       constexpr uint32_t STAGE_STEP = (2 * Y_TILE_BYTES) >> 4, TILE_STEP = Y_TILE_BYTES >> 4;
-      auto issue_scores = [&](int stage, int b) {
+      int stage = 0;
+      uint32_t phase = 0;
+      for (int i = 0; i < total_steps && ok; ++i) {
+        const int b = i & 1;
         const uint64_t y1d = ys0 + stage * STAGE_STEP, y2d = y1d + TILE_STEP;
+        if (!mbar_wait(&y_full[stage], phase, abort_flag, p.status, 81)) { ok = false; break; }
+        // the score buffers of step i were last read by the accumulating products of step i - 2
+        if (i >= 2 && !mbar_wait(&t_free[b], ((i >> 1) - 1) & 1, abort_flag, p.status, 82)) { ok = false; break; }
+        tc_fence_after_sync();
 #pragma unroll
         for (int k = 0; k < D / 16; ++k) {
           const uint32_t xo = ((k >> 2) * X_CHUNK_BYTES + (k & 3) * 32) >> 4;
@@ -189,51 +199,38 @@ flash_bwd_kernel(const __grid_constant__ Maps maps, const Params p) {
           umma_ss(tmem_base + 128 + b * 64, x2d + xo, y2d + yo, idesc_t, k > 0 ? 1u : 0u);
         }
         umma_commit(&t_full[b]);
-      };
-      auto issue_acc = [&](int stage, int b, bool first) {
+        if (++stage == Y_STAGES) { stage = 0; phase ^= 1u; }
+      }
+    }
+  } else if (warp == 2) {
+    // ------------------------------ issuing lane B: accumulating products --------
+    if (lane == 0 && total_steps > 0) {
+      constexpr uint32_t idesc_acc = make_idesc_bf16(128, 128, false, true); // B operand MN-major
+      const uint64_t ym0 = make_smem_desc(smem_u32(sy), Y_CHUNK_BYTES, 1024);
+      constexpr uint32_t STAGE_STEP = (2 * Y_TILE_BYTES) >> 4, TILE_STEP = Y_TILE_BYTES >> 4;
+      int stage = 0;
+      bool ok = true;
+      for (int i = 0; i < total_steps && ok; ++i) {
+        const int b = i & 1;
         const uint64_t y1d = ym0 + stage * STAGE_STEP, y2d = y1d + TILE_STEP;
+        if (!mbar_wait(&ps_full[b], (i >> 1) & 1, abort_flag, p.status, 83)) { ok = false; break; }
+        tc_fence_after_sync();
 #pragma unroll
         for (int k = 0; k < BY / 16; ++k) {
           const uint32_t acol = k * 16;  // packed bf16 columns of this K-step (written by column group k)
+          const uint32_t accum = (i > 0 || k > 0) ? 1u : 0u;
           if (DKV) {
-            // dV += P^T dO_i
-            umma_ts(tmem_base + 256, tmem_base + b * 64 + acol, y2d + k * (2048 >> 4), idesc_acc,
-                    (!first || k > 0) ? 1u : 0u);
-            // dK += dS^T Q_i
-            umma_ts(tmem_base + 384, tmem_base + 128 + b * 64 + acol, y1d + k * (2048 >> 4), idesc_acc,
-                    (!first || k > 0) ? 1u : 0u);
+            umma_ts(tmem_base + 256, tmem_base + b * 64 + acol, y2d + k * (2048 >> 4), idesc_acc, accum);        // dV += P^T dO_i
+            umma_ts(tmem_base + 384, tmem_base + 128 + b * 64 + acol, y1d + k * (2048 >> 4), idesc_acc, accum);  // dK += dS^T Q_i
           } else {
-            // dQ += dS K_j
-            umma_ts(tmem_base + 256, tmem_base + 128 + b * 64 + acol, y1d + k * (2048 >> 4), idesc_acc,
-                    (!first || k > 0) ? 1u : 0u);
+            umma_ts(tmem_base + 256, tmem_base + 128 + b * 64 + acol, y1d + k * (2048 >> 4), idesc_acc, accum);  // dQ += dS K_j
           }
         }
+        umma_commit(&t_free[b]);
         umma_commit(&y_empty[stage]);
-      };
-      int stage = 0;
-      uint32_t phase = 0;
-      int prev_stage = 0;
-      for (int i = 0; i < total_steps && ok; ++i) {
-        const int b = i & 1;
-        if (!mbar_wait(&y_full[stage], phase, abort_flag, p.status, 81)) { ok = false; break; }
-        tc_fence_after_sync();
-        issue_scores(stage, b);
-        if (i > 0) {
-          if (!mbar_wait(&ps_full[b ^ 1], ((i - 1) >> 1) & 1, abort_flag, p.status, 82)) { ok = false; break; }
-          tc_fence_after_sync();
-          issue_acc(prev_stage, b ^ 1, i == 1);
-        }
-        prev_stage = stage;
-        if (++stage == Y_STAGES) { stage = 0; phase ^= 1u; }
+        if (++stage == Y_STAGES) stage = 0;
       }
-      if (ok) {
-        const int last = total_steps - 1;
-        if (mbar_wait(&ps_full[last & 1], (last >> 1) & 1, abort_flag, p.status, 83)) {
-          tc_fence_after_sync();
-          issue_acc(prev_stage, last & 1, last == 0);
-          umma_commit(acc_final);
-        }
-      }
+      if (ok) umma_commit(acc_final);
     }
   } else if (warp >= 4) {
     // ------------------------------ Elementwise + epilogue --------------------
