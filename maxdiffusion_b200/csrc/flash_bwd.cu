@@ -59,6 +59,11 @@ struct Params {
 template <bool DKV>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 flash_bwd_kernel(const __grid_constant__ Maps maps, const Params p) {
+  // Score-tile buffers: the hand-over chain score product -> elementwise -> accumulating product -> next score product
+  // of one buffer is several times longer than the tensor work of a step, so the pipe is kept busy by the other
+  // buffers. The DKV pass has TMEM for two (two accumulators), the DQ pass for three.
+  constexpr int NBUF = DKV ? 2 : 3;
+  constexpr uint32_t T2C = NBUF * 64, ACC = 2 * NBUF * 64;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* sx1 = smem;
@@ -69,10 +74,10 @@ flash_bwd_kernel(const __grid_constant__ Maps maps, const Params p) {
   uint64_t* x_full = bars;          // [1]
   uint64_t* y_full = bars + 1;                      // [Y_STAGES]
   uint64_t* y_empty = y_full + Y_STAGES;            // [Y_STAGES]
-  uint64_t* t_full = y_empty + Y_STAGES;            // [2]
-  uint64_t* ps_full = t_full + 2;                   // [2]
-  uint64_t* t_free = ps_full + 2;                   // [2] accumulating products that read the score buffers completed
-  uint64_t* acc_final = t_free + 2;                 // [1]
+  uint64_t* t_full = y_empty + Y_STAGES;            // [NBUF]
+  uint64_t* ps_full = t_full + NBUF;                // [NBUF]
+  uint64_t* t_free = ps_full + NBUF;                // [NBUF] accumulating products that read the score buffers completed
+  uint64_t* acc_final = t_free + NBUF;              // [1]
   uint32_t* tmem_ptr_smem = reinterpret_cast<uint32_t*>(acc_final + 1);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_ptr_smem + 1);
 
@@ -91,8 +96,8 @@ flash_bwd_kernel(const __grid_constant__ Maps maps, const Params p) {
       mbar_init(&y_full[i], 1);  // lane 0 of the producer: TMA transaction bytes (tiles, and lse / delta in the DKV pass)
       mbar_init(&y_empty[i], 1);
     }
-    for (int i = 0; i < 2; ++i) {
-      mbar_init(&t_full[i], 1);
+    for (int i = 0; i < NBUF; ++i) {
+      mbar_init(&t_full[i], 2);  // both score products
       mbar_init(&t_free[i], 1);
       mbar_init(&ps_full[i], EW_GROUPS * 4);  // one elected lane per elementwise warp
     }
@@ -108,7 +113,7 @@ flash_bwd_kernel(const __grid_constant__ Maps maps, const Params p) {
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_ptr_smem;
-  // TMEM columns: T1[b] = b*64, T2[b] = 128 + b*64, acc0 = 256, acc1 = 384.
+  // TMEM columns: T1[b] = b*64, T2[b] = T2C + b*64, accumulators from ACC (DKV: 2 buffers, acc 256 / 384; DQ: 3 buffers, acc 384).
 
   if (warp == 0) {
     // ------------------------------ TMA producer ------------------------------
@@ -163,40 +168,36 @@ flash_bwd_kernel(const __grid_constant__ Maps maps, const Params p) {
         }
       }
     }
-  } else if (warp == 1) {
-    // ------------------------------ issuing lane A: score products --------------
-    // Two lanes in different warps feed the tensor pipe: a step's waits, commits and MMA instructions cost the
-    // issuing lane more cycles than the products take to execute, so the score products and the accumulating
-    // products are issued independently. Every dependency between them is an mbarrier.
+  } else if (warp == 1 || warp == 3) {
+    // ------------------------------ issuing lanes A1 / A2: score products ---------
+    // Three lanes in different warps feed the tensor pipe: a step's waits, commits and MMA instructions cost an
+    // issuing lane more cycles than the products take to execute. Warp 1 issues X1 Y1^T (S), warp 3 issues
+    // X2 Y2^T (dP), warp 2 the accumulating products. Every dependency between them is an mbarrier.
     if (lane == 0 && total_steps > 0) {
       constexpr uint32_t idesc_t = make_idesc_bf16(128, BY, false, false);   // score tiles, N = 64
+      const bool second = warp == 3;
       bool ok = mbar_wait(x_full, 0, abort_flag, p.status, 80);
       tc_fence_after_sync();
       // Shared-memory descriptors are built once: the address field (bits 0-13, units of 16 bytes) of a
       // descriptor advances by plain addition.
-      const uint64_t x1d = make_smem_desc(smem_u32(sx1), 16, 1024), x2d = make_smem_desc(smem_u32(sx2), 16, 1024);
-      const uint64_t ys0 = make_smem_desc(smem_u32(sy), 16, 1024);
-      constexpr uint32_t STAGE_STEP = (2 * Y_TILE_BYTES) >> 4, TILE_STEP = Y_TILE_BYTES >> 4;
+      const uint64_t xd = make_smem_desc(smem_u32(second ? sx2 : sx1), 16, 1024);
+      const uint64_t ys0 = make_smem_desc(smem_u32(sy + (second ? Y_TILE_BYTES : 0)), 16, 1024);
+      const uint32_t tcol = tmem_base + (second ? T2C : 0u);
+      constexpr uint32_t STAGE_STEP = (2 * Y_TILE_BYTES) >> 4;
       int stage = 0;
       uint32_t phase = 0;
       for (int i = 0; i < total_steps && ok; ++i) {
-        const int b = i & 1;
-        const uint64_t y1d = ys0 + stage * STAGE_STEP, y2d = y1d + TILE_STEP;
+        const int b = i % NBUF, use = i / NBUF;
+        const uint64_t yd = ys0 + stage * STAGE_STEP;
         if (!mbar_wait(&y_full[stage], phase, abort_flag, p.status, 81)) { ok = false; break; }
-        // the score buffers of step i were last read by the accumulating products of step i - 2
-        if (i >= 2 && !mbar_wait(&t_free[b], ((i >> 1) - 1) & 1, abort_flag, p.status, 82)) { ok = false; break; }
+        // the score buffers of step i were last read by the accumulating products of step i - NBUF
+        if (use > 0 && !mbar_wait(&t_free[b], (use - 1) & 1, abort_flag, p.status, 82)) { ok = false; break; }
         tc_fence_after_sync();
 #pragma unroll
         for (int k = 0; k < D / 16; ++k) {
           const uint32_t xo = ((k >> 2) * X_CHUNK_BYTES + (k & 3) * 32) >> 4;
           const uint32_t yo = ((k >> 2) * Y_CHUNK_BYTES + (k & 3) * 32) >> 4;
-          umma_ss(tmem_base + b * 64, x1d + xo, y1d + yo, idesc_t, k > 0 ? 1u : 0u);
-        }
-#pragma unroll
-        for (int k = 0; k < D / 16; ++k) {
-          const uint32_t xo = ((k >> 2) * X_CHUNK_BYTES + (k & 3) * 32) >> 4;
-          const uint32_t yo = ((k >> 2) * Y_CHUNK_BYTES + (k & 3) * 32) >> 4;
-          umma_ss(tmem_base + 128 + b * 64, x2d + xo, y2d + yo, idesc_t, k > 0 ? 1u : 0u);
+          umma_ss(tcol + b * 64, xd + xo, yd + yo, idesc_t, k > 0 ? 1u : 0u);
         }
         umma_commit(&t_full[b]);
         if (++stage == Y_STAGES) { stage = 0; phase ^= 1u; }
@@ -211,19 +212,19 @@ flash_bwd_kernel(const __grid_constant__ Maps maps, const Params p) {
       int stage = 0;
       bool ok = true;
       for (int i = 0; i < total_steps && ok; ++i) {
-        const int b = i & 1;
+        const int b = i % NBUF, use = i / NBUF;
         const uint64_t y1d = ym0 + stage * STAGE_STEP, y2d = y1d + TILE_STEP;
-        if (!mbar_wait(&ps_full[b], (i >> 1) & 1, abort_flag, p.status, 83)) { ok = false; break; }
+        if (!mbar_wait(&ps_full[b], use & 1, abort_flag, p.status, 83)) { ok = false; break; }
         tc_fence_after_sync();
 #pragma unroll
         for (int k = 0; k < BY / 16; ++k) {
           const uint32_t acol = k * 16;  // packed bf16 columns of this K-step (written by column group k)
           const uint32_t accum = (i > 0 || k > 0) ? 1u : 0u;
           if (DKV) {
-            umma_ts(tmem_base + 256, tmem_base + b * 64 + acol, y2d + k * (2048 >> 4), idesc_acc, accum);        // dV += P^T dO_i
-            umma_ts(tmem_base + 384, tmem_base + 128 + b * 64 + acol, y1d + k * (2048 >> 4), idesc_acc, accum);  // dK += dS^T Q_i
+            umma_ts(tmem_base + ACC, tmem_base + b * 64 + acol, y2d + k * (2048 >> 4), idesc_acc, accum);        // dV += P^T dO_i
+            umma_ts(tmem_base + ACC + 128, tmem_base + T2C + b * 64 + acol, y1d + k * (2048 >> 4), idesc_acc, accum);  // dK += dS^T Q_i
           } else {
-            umma_ts(tmem_base + 256, tmem_base + 128 + b * 64 + acol, y1d + k * (2048 >> 4), idesc_acc, accum);  // dQ += dS K_j
+            umma_ts(tmem_base + ACC, tmem_base + T2C + b * 64 + acol, y1d + k * (2048 >> 4), idesc_acc, accum);  // dQ += dS K_j
           }
         }
         umma_commit(&t_free[b]);
@@ -252,18 +253,18 @@ flash_bwd_kernel(const __grid_constant__ Maps maps, const Params p) {
       for (int seg = 0; seg < p.num_segments && ok; ++seg) {
         const int nblk = (p.y_len[seg] + BY - 1) / BY;
         for (int jb = 0; jb < nblk; ++jb, ++i) {
-          const int b = i & 1;
+          const int b = i % NBUF, use = i / NBUF;
           const int valid = min(BY, p.y_len[seg] - jb * BY);
           const int ystage = i % Y_STAGES;
           const float* st = stat_s + ystage * 128;
           if (DKV) {
             if (!mbar_wait(&y_full[ystage], (i / Y_STAGES) & 1, abort_flag, p.status, 92)) { ok = false; break; }
           }
-          if (!mbar_wait(&t_full[b], (i >> 1) & 1, abort_flag, p.status, 90)) { ok = false; break; }
+          if (!mbar_wait(&t_full[b], use & 1, abort_flag, p.status, 90)) { ok = false; break; }
           tc_fence_after_sync();
           uint32_t t1[16], t2[16];
           tmem_ld_x16(tmem_base + lane_off + b * 64 + wg * 16, t1);
-          tmem_ld_x16(tmem_base + lane_off + 128 + b * 64 + wg * 16, t2);
+          tmem_ld_x16(tmem_base + lane_off + T2C + b * 64 + wg * 16, t2);
           tmem_wait_ld();
           uint32_t pp[8], ds[8];
           const bool full_tile = (valid == BY) && (x0 + BX <= p.x_len);  // uniform over the CTA
@@ -315,7 +316,7 @@ flash_bwd_kernel(const __grid_constant__ Maps maps, const Params p) {
             }
           }
           if (DKV) tmem_st_x8(tmem_base + lane_off + b * 64 + wg * 16, pp);
-          tmem_st_x8(tmem_base + lane_off + 128 + b * 64 + wg * 16, ds);
+          tmem_st_x8(tmem_base + lane_off + T2C + b * 64 + wg * 16, ds);
           tmem_wait_st();
           tc_fence_before_sync();
           __syncwarp();
@@ -336,7 +337,7 @@ flash_bwd_kernel(const __grid_constant__ Maps maps, const Params p) {
           for (int c = 0; c < 1; ++c) {
             const int col0 = wg * 32;
             uint32_t r[32];
-            tmem_ld_x32(tmem_base + lane_off + 256 + a * 128 + col0, r);
+            tmem_ld_x32(tmem_base + lane_off + ACC + a * 128 + col0, r);
             tmem_wait_ld();
             if (row_ok) {
               if (p.out_f32) {
