@@ -1,12 +1,16 @@
 // Non-causal flash-attention forward for head_dim 128 on sm_100a (tcgen05 + TMEM + TMA).
 //
-// One CTA owns 256 query rows of one (batch, head) as two 128-row tiles that ping-pong on the
-// tensor core: while the softmax warps of tile 0 work on S0, the MMA warp runs tile 1.
-//   S_t = Q_t K_j^T      SS-form UMMA, fp32 in TMEM (128 columns per tile)
+// One CTA owns 256 query rows of one (batch, head) as two 128-row tiles, and streams K / V in blocks of 64 keys:
+//   S_t = Q_t K_j^T      SS-form UMMA, fp32 in TMEM (64 columns), two buffers per tile
 //   P_t = exp2(S_t*c - m) written back over S_t as packed bf16 (tcgen05.st)
 //   O_t += P_t V_j       TS-form UMMA (A from TMEM, V is an MN-major smem operand)
+// The softmax is bound by the exponential unit (16 results per clock and SM, as many cycles per tile as both
+// products together), so the layout keeps the softmax warps of both tiles busy all the time: S of block j+1 is
+// multiplied into the tile's second buffer while block j is exponentiated, and four lanes in different warps issue
+// the products (S and P V of either tile), because the waits, commits and MMA instructions of a block cost one
+// issuing lane more cycles than the products take to run. Every hand-over is an mbarrier.
 // The running row max is refreshed lazily (only when it moves by more than 2^8), so the
-// accumulator rescale is rare. The KV sequence may consist of several segments (one per ring
+// accumulator rescale is rare; it waits for the tile's previous P V product first. The KV sequence may consist of several segments (one per ring
 // hop / context shard); (O, m, l) stay on chip across segments and the merge costs nothing.
 // A segment can be guarded by a ready flag in global memory that the loader warp waits on
 // (bounded) before its first TMA load of that segment.
@@ -36,13 +40,16 @@ namespace fa {
 
 constexpr int D = 128;
 constexpr int BQ = 128;          // rows per q tile
-constexpr int BKV = 128;         // keys per block
-constexpr int KV_STAGES = 2;
-constexpr int TILE_BYTES = 128 * D * 2;  // 32 KiB: two 64-column chunks of 128 rows x 128 B
+constexpr int BKV = 64;          // keys per block
+constexpr int KV_STAGES = 4;
+constexpr int TILE_BYTES = 128 * D * 2;  // Q tile, 32 KiB: two 64-column chunks of 128 rows x 128 B
 constexpr int CHUNK_BYTES = 128 * 128;   // 16 KiB
+constexpr int KV_TILE_BYTES = BKV * D * 2;   // 16 KiB: two chunks of 64 rows x 128 B
+constexpr int KV_CHUNK_BYTES = BKV * 128;    // 8 KiB
 constexpr int MAX_SEGMENTS = 8;
-constexpr int NUM_THREADS = 384;         // warp 0 TMA, warp 1 MMA, warps 4-7 / 8-11 softmax
-constexpr int SMEM_BYTES = 2 * TILE_BYTES + 2 * KV_STAGES * TILE_BYTES + 1024 + 256;
+constexpr int ROLE_WARPS = 5;            // warp 0 TMA, warps 1 / 3 issue S of tile 0 / 1, warps 2 / 4 issue P V of tile 0 / 1
+constexpr int NUM_THREADS = ROLE_WARPS * 32 + 256;  // + softmax warps 5-8 (tile 0), 9-12 (tile 1)
+constexpr int SMEM_BYTES = 2 * TILE_BYTES + 2 * KV_STAGES * KV_TILE_BYTES + 1024 + 512;
 constexpr float kRescaleThreshold = 8.0f;
 
 struct KVMaps {
@@ -172,19 +179,20 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* sq = smem;                                  // [2 tiles][2 chunks][128][128 B]
-  uint8_t* sk = smem + 2 * TILE_BYTES;                 // [KV_STAGES] tiles
-  uint8_t* sv = sk + KV_STAGES * TILE_BYTES;           // [KV_STAGES] tiles
-  uint64_t* bars = reinterpret_cast<uint64_t*>(sv + KV_STAGES * TILE_BYTES);
-  uint64_t* q_full = bars;            // [1]
-  uint64_t* k_full = bars + 1;        // [2]
-  uint64_t* k_empty = bars + 3;       // [2]
-  uint64_t* v_full = bars + 5;        // [2]
-  uint64_t* v_empty = bars + 7;       // [2]
-  uint64_t* s_full = bars + 9;        // [2] per q tile
-  uint64_t* p_full = bars + 11;       // [2] per q tile
-  uint64_t* o_final = bars + 13;      // [2] per q tile
-  uint64_t* q_empty = bars + 15;      // [1]
-  uint32_t* tmem_ptr_smem = reinterpret_cast<uint32_t*>(bars + 16);
+  uint8_t* sk = smem + 2 * TILE_BYTES;                 // [KV_STAGES] tiles of 64 keys
+  uint8_t* sv = sk + KV_STAGES * KV_TILE_BYTES;        // [KV_STAGES] tiles
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sv + KV_STAGES * KV_TILE_BYTES);
+  uint64_t* q_full = bars;                        // [1]
+  uint64_t* q_empty = bars + 1;                   // [1] both S lanes
+  uint64_t* k_full = bars + 2;                    // [KV_STAGES]
+  uint64_t* k_empty = k_full + KV_STAGES;         // [KV_STAGES] both S lanes
+  uint64_t* v_full = k_empty + KV_STAGES;         // [KV_STAGES]
+  uint64_t* v_empty = v_full + KV_STAGES;         // [KV_STAGES] both P V lanes
+  uint64_t* s_full = v_empty + KV_STAGES;         // [2 tiles][2 buffers] S written
+  uint64_t* p_full = s_full + 4;                  // [2][2] P stored over S
+  uint64_t* s_free = p_full + 4;                  // [2][2] P V product that reads the buffer (and adds into O) completed
+  uint64_t* o_final = s_free + 4;                 // [2] per q tile
+  uint32_t* tmem_ptr_smem = reinterpret_cast<uint32_t*>(o_final + 2);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_ptr_smem + 1);
 
   const int warp = threadIdx.x >> 5;
@@ -197,16 +205,20 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
 
   if (threadIdx.x == 0) {
     mbar_init(q_full, 1);
-    mbar_init(q_empty, 1);
-    for (int i = 0; i < 2; ++i) {
+    mbar_init(q_empty, 2);
+    for (int i = 0; i < KV_STAGES; ++i) {
       mbar_init(&k_full[i], 1);
-      mbar_init(&k_empty[i], 1);
+      mbar_init(&k_empty[i], 2);
       mbar_init(&v_full[i], 1);
-      mbar_init(&v_empty[i], 1);
+      mbar_init(&v_empty[i], 2);
+    }
+    for (int i = 0; i < 4; ++i) {
       mbar_init(&s_full[i], 1);
       mbar_init(&p_full[i], 4);  // one elected lane per softmax warp
-      mbar_init(&o_final[i], 1);
+      mbar_init(&s_free[i], 1);
     }
+    mbar_init(&o_final[0], 1);
+    mbar_init(&o_final[1], 1);
     *abort_flag = 0;
     fence_mbar_init();
     prefetch_tensormap(&tmap_q);
@@ -219,7 +231,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_ptr_smem;
-  // TMEM columns: S0 [0,128) S1 [128,256) O0 [256,384) O1 [384,512); P_t aliases S_t.
+  // TMEM columns: S(t, b) = t*128 + b*64 (P aliases it as 32 packed columns), O(t) = 256 + t*128.
 
   if (warp == 0) {
     // ------------------------------ TMA producer ------------------------------
@@ -251,15 +263,15 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
           }
           for (int jb = 0; jb < nblk; ++jb) {
             if (!mbar_wait(&k_empty[stage], phase ^ 1u, abort_flag, p.status, 41)) { ok = false; break; }
-            mbar_expect_tx(&k_full[stage], TILE_BYTES);
+            mbar_expect_tx(&k_full[stage], KV_TILE_BYTES);
             for (int c = 0; c < 2; ++c) {
-              tma_load_4d(sk + stage * TILE_BYTES + c * CHUNK_BYTES, &maps.k[seg], &k_full[stage], c * 64, head,
+              tma_load_4d(sk + stage * KV_TILE_BYTES + c * KV_CHUNK_BYTES, &maps.k[seg], &k_full[stage], c * 64, head,
                           jb * BKV, batch);
             }
             if (!mbar_wait(&v_empty[stage], phase ^ 1u, abort_flag, p.status, 42)) { ok = false; break; }
-            mbar_expect_tx(&v_full[stage], TILE_BYTES);
+            mbar_expect_tx(&v_full[stage], KV_TILE_BYTES);
             for (int c = 0; c < 2; ++c) {
-              tma_load_4d(sv + stage * TILE_BYTES + c * CHUNK_BYTES, &maps.v[seg], &v_full[stage], c * 64, head,
+              tma_load_4d(sv + stage * KV_TILE_BYTES + c * KV_CHUNK_BYTES, &maps.v[seg], &v_full[stage], c * 64, head,
                           jb * BKV, batch);
             }
             if (++stage == KV_STAGES) { stage = 0; phase ^= 1u; }
@@ -267,82 +279,97 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
         }
       }
     }
-  } else if (warp == 1) {
-    // ------------------------------ MMA issuer --------------------------------
+  } else if (warp == 1 || warp == 3) {
+    // ------------------------------ issuing lanes: S_t = Q_t K_j^T --------------
     if (lane == 0 && total_blocks > 0) {
-      constexpr uint32_t idesc_s = make_idesc_bf16(128, 128, false, false);
-      constexpr uint32_t idesc_pv = make_idesc_bf16(128, 128, false, true);
-      auto issue_s = [&](int t, int stage) {
-        const uint32_t qa = smem_u32(sq + t * TILE_BYTES);
-        const uint32_t ka = smem_u32(sk + stage * TILE_BYTES);
-#pragma unroll
-        for (int k = 0; k < D / 16; ++k) {
-          const uint32_t off = (k >> 2) * CHUNK_BYTES + (k & 3) * 32;
-          umma_ss(tmem_base + t * 128, make_smem_desc(qa + off, 16, 1024), make_smem_desc(ka + off, 16, 1024),
-                  idesc_s, k > 0 ? 1u : 0u);
-        }
-        umma_commit(&s_full[t]);
-      };
+      const int t = warp >> 1;  // warp 1 -> tile 0, warp 3 -> tile 1
+      constexpr uint32_t idesc_s = make_idesc_bf16(128, BKV, false, false);
+      // descriptors are built once; the address field (units of 16 bytes) advances by addition
+      const uint64_t qd = make_smem_desc(smem_u32(sq + t * TILE_BYTES), 16, 1024);
+      const uint64_t kd0 = make_smem_desc(smem_u32(sk), 16, 1024);
+      constexpr uint32_t STAGE_STEP = KV_TILE_BYTES >> 4;
       int stage = 0;
       uint32_t phase = 0;
-      uint32_t pc[2] = {0u, 0u};  // blocks consumed per q-tile slot (parity of p_full)
+      uint32_t n = 0;  // blocks of this tile so far, over all work items: buffer n & 1, use n >> 1
       bool ok = true;
       int it = 0;
       for (int work = blockIdx.x; work < total_work && ok; work += n_compute, ++it) {
         const int q0 = (work % n_qb) * 2 * BQ;
-        const int n_tiles = (p.q_len - q0 > BQ) ? 2 : 1;
+        const bool active = t < ((p.q_len - q0 > BQ) ? 2 : 1);
         if (!mbar_wait(q_full, it & 1, abort_flag, p.status, 50)) { ok = false; break; }
-        if (!mbar_wait(&k_full[stage], phase, abort_flag, p.status, 51)) { ok = false; break; }
-        tc_fence_after_sync();
-        for (int t = 0; t < n_tiles; ++t) issue_s(t, stage);
-        umma_commit(&k_empty[stage]);  // this K block is free once the S MMAs have read it
-        if (total_blocks == 1) umma_commit(q_empty);
-        for (int j = 0; j < total_blocks && ok; ++j) {
-          const int nstage = (stage + 1 == KV_STAGES) ? 0 : stage + 1;
-          const uint32_t nphase = (stage + 1 == KV_STAGES) ? (phase ^ 1u) : phase;
-          if (!mbar_wait(&v_full[stage], phase, abort_flag, p.status, 52)) { ok = false; break; }
-          tc_fence_after_sync();
-          const uint32_t va = smem_u32(sv + stage * TILE_BYTES);
-          for (int t = 0; t < n_tiles && ok; ++t) {
-            if (!mbar_wait(&p_full[t], pc[t] & 1u, abort_flag, p.status, 53)) { ok = false; break; }
-            ++pc[t];
+        for (int j = 0; j < total_blocks; ++j) {
+          if (!mbar_wait(&k_full[stage], phase, abort_flag, p.status, 51)) { ok = false; break; }
+          if (active) {
+            const uint32_t b = n & 1u;
+            // the buffer last held P of block n - 2: its P V product must have completed
+            if (n >= 2 && !mbar_wait(&s_free[t * 2 + b], ((n >> 1) - 1) & 1u, abort_flag, p.status, 55)) { ok = false; break; }
             tc_fence_after_sync();
+            const uint64_t kd = kd0 + stage * STAGE_STEP;
+            const uint32_t s_col = tmem_base + t * 128 + b * 64;
 #pragma unroll
-            for (int k = 0; k < BKV / 16; ++k) {
-              umma_ts(tmem_base + 256 + t * 128, tmem_base + t * 128 + k * 8,
-                      make_smem_desc(va + k * 2048, CHUNK_BYTES, 1024), idesc_pv, (j > 0 || k > 0) ? 1u : 0u);
+            for (int k = 0; k < D / 16; ++k) {
+              const uint32_t qo = ((k >> 2) * CHUNK_BYTES + (k & 3) * 32) >> 4;
+              const uint32_t ko = ((k >> 2) * KV_CHUNK_BYTES + (k & 3) * 32) >> 4;
+              umma_ss(s_col, qd + qo, kd + ko, idesc_s, k > 0 ? 1u : 0u);
             }
-            if (j + 1 < total_blocks) {
-              if (t == 0) {
-                if (!mbar_wait(&k_full[nstage], nphase, abort_flag, p.status, 54)) { ok = false; break; }
-                tc_fence_after_sync();
-              }
-              issue_s(t, nstage);
-              if (t == n_tiles - 1) {
-                umma_commit(&k_empty[nstage]);
-                // the S MMAs of the last block are the last readers of the Q tiles: free them for the next work item
-                if (j + 2 == total_blocks) umma_commit(q_empty);
-              }
-            } else {
-              umma_commit(&o_final[t]);
-            }
+            umma_commit(&s_full[t * 2 + b]);
+            umma_commit(&k_empty[stage]);  // this K block is free once the S MMAs have read it
+            // the S MMAs of the last block are the last readers of the Q tile: free it for the next work item
+            if (j + 1 == total_blocks) umma_commit(q_empty);
+            ++n;
+          } else {
+            mbar_arrive(&k_empty[stage]);
+            if (j + 1 == total_blocks) mbar_arrive(q_empty);
           }
-          if (!ok) break;
-          umma_commit(&v_empty[stage]);
-          stage = nstage;
-          phase = nphase;
+          if (++stage == KV_STAGES) { stage = 0; phase ^= 1u; }
         }
       }
     }
-  } else if (warp >= 4) {
+  } else if (warp == 2 || warp == 4) {
+    // ------------------------------ issuing lanes: O_t += P_t V_j ----------------
+    if (lane == 0 && total_blocks > 0) {
+      const int t = (warp >> 1) - 1;  // warp 2 -> tile 0, warp 4 -> tile 1
+      constexpr uint32_t idesc_pv = make_idesc_bf16(128, 128, false, true);
+      const uint64_t vd0 = make_smem_desc(smem_u32(sv), KV_CHUNK_BYTES, 1024);
+      constexpr uint32_t STAGE_STEP = KV_TILE_BYTES >> 4;
+      const uint32_t o_col = tmem_base + 256 + t * 128;
+      int stage = 0;
+      uint32_t phase = 0;
+      uint32_t n = 0;
+      bool ok = true;
+      for (int work = blockIdx.x; work < total_work && ok; work += n_compute) {
+        const int q0 = (work % n_qb) * 2 * BQ;
+        const bool active = t < ((p.q_len - q0 > BQ) ? 2 : 1);
+        for (int j = 0; j < total_blocks; ++j) {
+          if (!mbar_wait(&v_full[stage], phase, abort_flag, p.status, 52)) { ok = false; break; }
+          if (active) {
+            const uint32_t b = n & 1u;
+            if (!mbar_wait(&p_full[t * 2 + b], (n >> 1) & 1u, abort_flag, p.status, 53)) { ok = false; break; }
+            tc_fence_after_sync();
+            const uint64_t vd = vd0 + stage * STAGE_STEP;
+            const uint32_t p_col = tmem_base + t * 128 + b * 64;
+#pragma unroll
+            for (int k = 0; k < BKV / 16; ++k)
+              umma_ts(o_col, p_col + k * 8, vd + k * (2048 >> 4), idesc_pv, (j > 0 || k > 0) ? 1u : 0u);
+            umma_commit(&s_free[t * 2 + b]);
+            umma_commit(&v_empty[stage]);
+            if (j + 1 == total_blocks) umma_commit(&o_final[t]);
+            ++n;
+          } else {
+            mbar_arrive(&v_empty[stage]);
+          }
+          if (++stage == KV_STAGES) { stage = 0; phase ^= 1u; }
+        }
+      }
+    }
+  } else if (warp >= ROLE_WARPS) {
     // ------------------------------ Softmax / correction / epilogue ------------
-    const int t = (warp - 4) >> 2;         // q tile of this warp group
-    const int quarter = warp & 3;          // TMEM lanes 32*quarter..+31
+    const int t = (warp - ROLE_WARPS) >> 2;  // q tile of this warp group
+    const int quarter = warp & 3;            // TMEM lanes 32*quarter..+31
     const int row_in_tile = quarter * 32 + lane;
     const uint32_t lane_off = static_cast<uint32_t>(quarter * 32) << 16;
-    const uint32_t s_addr = tmem_base + lane_off + t * 128;
     const uint32_t o_addr = tmem_base + lane_off + 256 + t * 128;
-    uint32_t sc = 0, oc = 0;  // parities of s_full / o_final for this slot
+    uint32_t n = 0, oc = 0;  // blocks of this tile so far; parity of o_final
     bool ok = total_blocks > 0;
     for (int work = blockIdx.x; work < total_work && ok; work += n_compute) {
       const int qb = work % n_qb;
@@ -356,38 +383,40 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
       int j = 0;
       for (int seg = 0; seg < p.num_segments && ok; ++seg) {
         const int nblk = (p.kv_len[seg] + BKV - 1) / BKV;
-        for (int jb = 0; jb < nblk; ++jb, ++j) {
+        for (int jb = 0; jb < nblk; ++jb, ++j, ++n) {
           const int valid = min(BKV, p.kv_len[seg] - jb * BKV);
-          if (!mbar_wait(&s_full[t], sc & 1u, abort_flag, p.status, 60)) { ok = false; break; }
-          ++sc;
+          const uint32_t b = n & 1u;
+          const uint32_t s_addr = tmem_base + lane_off + t * 128 + b * 64;
+          if (!mbar_wait(&s_full[t * 2 + b], (n >> 1) & 1u, abort_flag, p.status, 60)) { ok = false; break; }
           tc_fence_after_sync();
-          // the whole 128-column row of S goes to registers with one wait, so the TMEM latency is paid once
-          uint32_t sv4[4][32];
-          tmem_ld_x32(s_addr, sv4[0]);
-          tmem_ld_x32(s_addr + 32, sv4[1]);
-          tmem_ld_x32(s_addr + 64, sv4[2]);
-          tmem_ld_x32(s_addr + 96, sv4[3]);
+          uint32_t sv2[2][32];
+          tmem_ld_x32(s_addr, sv2[0]);
+          tmem_ld_x32(s_addr + 32, sv2[1]);
           tmem_wait_ld();
-          float mx = -INFINITY;
+          float mx0 = -INFINITY, mx1 = -INFINITY;  // two chains
           if (valid == BKV) {
 #pragma unroll
-            for (int c = 0; c < 4; ++c)
-#pragma unroll
-              for (int i = 0; i < 32; ++i) mx = fmaxf(mx, __uint_as_float(sv4[c][i]));
+            for (int i = 0; i < 32; ++i) {
+              mx0 = fmaxf(mx0, __uint_as_float(sv2[0][i]));
+              mx1 = fmaxf(mx1, __uint_as_float(sv2[1][i]));
+            }
           } else {
 #pragma unroll
-            for (int c = 0; c < 4; ++c)
+            for (int c = 0; c < 2; ++c)
 #pragma unroll
               for (int i = 0; i < 32; ++i) {
-                if (c * 32 + i < valid) mx = fmaxf(mx, __uint_as_float(sv4[c][i]));
+                if (c * 32 + i < valid) mx0 = fmaxf(mx0, __uint_as_float(sv2[c][i]));
               }
           }
-          const float m_new = fmaxf(m, mx * p.scale_log2);
+          const float m_new = fmaxf(m, fmaxf(mx0, mx1) * p.scale_log2);
           if (j == 0) {
             m = m_new;
           } else {
             const bool need = (m_new - m) > kRescaleThreshold;
             if (__any_sync(0xffffffffu, need)) {
+              // O must be at rest: the P V product of the previous block (the other buffer) has to be complete
+              if (!mbar_wait(&s_free[t * 2 + (b ^ 1u)], ((n - 1) >> 1) & 1u, abort_flag, p.status, 62)) { ok = false; break; }
+              tc_fence_after_sync();
               const float alpha = fast_exp2(m - m_new);
               l *= alpha;
               m = m_new;
@@ -403,38 +432,31 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
               tmem_wait_st();
             }
           }
-          // probabilities, written over S as packed bf16
-          float rowsum = 0.0f;
+          // probabilities, written over S as packed bf16 (32 columns)
+          float rs0 = 0.0f, rs1 = 0.0f;
+          uint32_t pk[32];
 #pragma unroll
-          for (int c = 0; c < 4; ++c) {
-            uint32_t pk[16];
-            if (valid == BKV) {
+          for (int c = 0; c < 2; ++c) {
 #pragma unroll
-              for (int i = 0; i < 16; ++i) {
-                const float p0 = fast_exp2(__uint_as_float(sv4[c][2 * i]) * p.scale_log2 - m);
-                const float p1 = fast_exp2(__uint_as_float(sv4[c][2 * i + 1]) * p.scale_log2 - m);
-                rowsum += p0 + p1;
-                pk[i] = pack_bf16x2(p0, p1);
-              }
-            } else {
-#pragma unroll
-              for (int i = 0; i < 16; ++i) {
+            for (int i = 0; i < 16; ++i) {
+              float p0 = fast_exp2(__uint_as_float(sv2[c][2 * i]) * p.scale_log2 - m);
+              float p1 = fast_exp2(__uint_as_float(sv2[c][2 * i + 1]) * p.scale_log2 - m);
+              if (valid != BKV) {
                 const int col = c * 32 + 2 * i;
-                float p0 = fast_exp2(__uint_as_float(sv4[c][2 * i]) * p.scale_log2 - m);
-                float p1 = fast_exp2(__uint_as_float(sv4[c][2 * i + 1]) * p.scale_log2 - m);
                 if (col >= valid) p0 = 0.0f;
                 if (col + 1 >= valid) p1 = 0.0f;
-                rowsum += p0 + p1;
-                pk[i] = pack_bf16x2(p0, p1);
               }
+              rs0 += p0;
+              rs1 += p1;
+              pk[c * 16 + i] = pack_bf16x2(p0, p1);
             }
-            tmem_st_x16(s_addr + c * 16, pk);
           }
-          l += rowsum;
+          tmem_st_x32(s_addr, pk);
+          l += rs0 + rs1;
           tmem_wait_st();
           tc_fence_before_sync();
           __syncwarp();
-          if ((threadIdx.x & 31) == 0) mbar_arrive(&p_full[t]);
+          if (lane == 0) mbar_arrive(&p_full[t * 2 + b]);
         }
       }
       if (!ok) break;
@@ -478,12 +500,13 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
   }
 }
 
-static int make_map(CUtensorMap* map, const void* ptr, int B, int S, int H, long long sb, long long ss, long long sh) {
+static int make_map(CUtensorMap* map, const void* ptr, int B, int S, int H, long long sb, long long ss, long long sh,
+                    int box_rows) {
   // dims innermost first: (D, H, S, B)
   uint64_t dims[4] = {static_cast<uint64_t>(D), static_cast<uint64_t>(H), static_cast<uint64_t>(S),
                       static_cast<uint64_t>(B)};
   uint64_t str[3] = {static_cast<uint64_t>(sh) * 2, static_cast<uint64_t>(ss) * 2, static_cast<uint64_t>(sb) * 2};
-  uint32_t box[4] = {64, 1, 128, 1};
+  uint32_t box[4] = {64, 1, static_cast<uint32_t>(box_rows), 1};
   return encode_tmap_bf16(map, ptr, 4, dims, str, box);
 }
 
@@ -523,15 +546,15 @@ extern "C" int mdb_flash_fwd(const void* q, const void* const* k_ptrs, const voi
   CUtensorMap tq;
   KVMaps maps;
   Params p;
-  int rc = make_map(&tq, q, B, q_len, H, q_sb, q_ss, q_sh);
+  int rc = make_map(&tq, q, B, q_len, H, q_sb, q_ss, q_sh, BQ);
   if (rc) return rc;
   for (int s = 0; s < MAX_SEGMENTS; ++s) {
     const int src = s < num_segments ? s : 0;
     p.kv_len[s] = s < num_segments ? kv_lens[s] : 0;
     const int len = kv_lens[src] > 0 ? kv_lens[src] : 1;
-    rc = make_map(&maps.k[s], k_ptrs[src], B, len, H, k_sb, k_ss, k_sh);
+    rc = make_map(&maps.k[s], k_ptrs[src], B, len, H, k_sb, k_ss, k_sh, BKV);
     if (rc) return rc;
-    rc = make_map(&maps.v[s], v_ptrs[src], B, len, H, v_sb, v_ss, v_sh);
+    rc = make_map(&maps.v[s], v_ptrs[src], B, len, H, v_sb, v_ss, v_sh, BKV);
     if (rc) return rc;
   }
   p.B = B; p.H = H; p.q_len = q_len;
