@@ -83,6 +83,44 @@ __global__ void peer_copy_kernel(const uint4* __restrict__ src, uint4* __restric
   }
 }
 
+// Owner-side reduce of a reduce-scatter: out[i] = sum over ranks r (in rank order, fp32) of srcs.p[r][i], bf16 in and
+// out. srcs.p[r] is the address, in rank r's symmetric buffer, of the slice that belongs to this rank, so every byte
+// crosses NVLink once and the sum is rounded once. 16-byte loads, 4 ranks in flight per thread.
+__global__ void __launch_bounds__(512) pull_reduce_kernel(PeerFlagPtrs srcs, int world, uint4* __restrict__ out,
+                                                          long long nvec) {
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < nvec;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    float acc[8];
+#pragma unroll
+    for (int e = 0; e < 8; ++e) acc[e] = 0.0f;
+    for (int r0 = 0; r0 < world; r0 += 4) {
+      uint4 v[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        if (r0 + u < world) v[u] = __ldcg(reinterpret_cast<const uint4*>(srcs.p[r0 + u]) + i);
+      }
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        if (r0 + u < world) {
+          const uint32_t w[4] = {v[u].x, v[u].y, v[u].z, v[u].w};
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const float2 f = unpack_bf16x2(w[e]);
+            acc[2 * e] += f.x;
+            acc[2 * e + 1] += f.y;
+          }
+        }
+      }
+    }
+    uint4 o;
+    o.x = pack_bf16x2(acc[0], acc[1]);
+    o.y = pack_bf16x2(acc[2], acc[3]);
+    o.z = pack_bf16x2(acc[4], acc[5]);
+    o.w = pack_bf16x2(acc[6], acc[7]);
+    out[i] = o;
+  }
+}
+
 __device__ __forceinline__ float ld_relaxed_sys_f32(const float* addr) {
   float v;
   asm volatile("ld.relaxed.sys.global.f32 %0, [%1];" : "=f"(v) : "l"(addr) : "memory");
@@ -287,6 +325,23 @@ extern "C" int mdb_peer_copy(const void* src, void* dst, long long nbytes, int c
   if (nbytes == 0) return 0;
   peer_copy_kernel<<<ctas, 512, 0, static_cast<cudaStream_t>(stream)>>>(
       static_cast<const uint4*>(src), static_cast<uint4*>(dst), nbytes >> 4);
+  return static_cast<int>(cudaGetLastError());
+}
+
+// src_ptrs: `world` device addresses (rank order) of this rank's slice in every rank's buffer; n_elems bf16 elements,
+// a multiple of 8. The caller has waited for the producers' ready flags on this stream.
+extern "C" int mdb_pull_reduce(const unsigned long long* src_ptrs, int world, void* out, long long n_elems, int ctas,
+                               void* stream) {
+  if (world < 1 || world > MAX_RANKS) return 3410;
+  if (n_elems & 7) return 3411;
+  if (n_elems == 0) return 0;
+  PeerFlagPtrs srcs;
+  for (int r = 0; r < world; ++r) {
+    if (src_ptrs[r] & 15) return 3412;
+    srcs.p[r] = reinterpret_cast<unsigned int*>(src_ptrs[r]);
+  }
+  pull_reduce_kernel<<<ctas > 0 ? ctas : 64, 512, 0, static_cast<cudaStream_t>(stream)>>>(
+      srcs, world, static_cast<uint4*>(out), n_elems >> 3);
   return static_cast<int>(cudaGetLastError());
 }
 
