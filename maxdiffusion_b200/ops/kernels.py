@@ -99,13 +99,17 @@ def flash_delta(o, d_o):
   return delta
 
 
-def flash_bwd_dkv(q, d_o, k, v, lse, delta, scale=None, out_dtype=torch.bfloat16):
-  """dK, dV of one KV segment [B,Skv,H,128] from the local queries q/dO [B,Sq,H,128]."""
+def flash_bwd_dkv(q, d_o, k, v, lse, delta, scale=None, out_dtype=torch.bfloat16, dk=None, dv=None):
+  """dK, dV of one KV segment [B,Skv,H,128] from the local queries q/dO [B,Sq,H,128]. `dk` / `dv` may be given
+  (e.g. views of a symmetric buffer); they must be [B,Skv,H,128] with unit head_dim stride."""
   B, Sq, H, D = q.shape
   Skv = k.shape[1]
   assert D == 128 and all(t.stride(-1) == 1 for t in (q, d_o, k, v))
-  dk = torch.empty((B, Skv, H, D), device=q.device, dtype=out_dtype)
-  dv = torch.empty((B, Skv, H, D), device=q.device, dtype=out_dtype)
+  if dk is None:
+    dk = torch.empty((B, Skv, H, D), device=q.device, dtype=out_dtype)
+  if dv is None:
+    dv = torch.empty((B, Skv, H, D), device=q.device, dtype=out_dtype)
+  assert dk.shape == (B, Skv, H, D) and dv.shape == (B, Skv, H, D) and dk.dtype == out_dtype and dv.dtype == out_dtype
   scale = scale if scale is not None else 1.0 / math.sqrt(D)
   rc = _lib.lib().mdb_flash_bwd_dkv(_lib.ptr(q), _lib.ptr(d_o), _lib.ptr(k), _lib.ptr(v), _lib.ptr(lse),
                                     _lib.ptr(delta), _lib.ptr(dk), _lib.ptr(dv), B, H, Sq, Skv, _strides3(q),

@@ -68,7 +68,7 @@ class _SegmentAttentionFn(torch.autograd.Function):
   """Kernel path of gather/ring attention: local q against the stacked K/V shards [n, B, S_loc, H, D]."""
 
   @staticmethod
-  def forward(ctx, q, k, v, scale, group, valid_lens, exchange):
+  def forward(ctx, q, k, v, scale, group, valid_lens, exchange, reducer=None):
     state = OF._remat
     saved = None
     if state.mode == "replay":
@@ -97,7 +97,7 @@ class _SegmentAttentionFn(torch.autograd.Function):
       out, lse = K.flash_fwd(q, ks, vs, scale, seg_flags=flags, flag_target=epoch, plan=plan)
       if state.mode == "record":
         state.store.append((out, lse))
-    ctx.scale, ctx.group, ctx.valid_lens, ctx.order = scale, group, lens, order
+    ctx.scale, ctx.group, ctx.valid_lens, ctx.order, ctx.reducer = scale, group, lens, order, reducer
     ctx.save_for_backward(q, out, lse, kg, vg)
     return out
 
@@ -112,6 +112,20 @@ class _SegmentAttentionFn(torch.autograd.Function):
     vs = [vg[i][:, :lens[i]] for i in range(n)]
     delta = K.flash_delta(out, d_o)
     dq = K.flash_bwd_dq(q, d_o, ks, vs, lse, delta, ctx.scale)
+    rs = ctx.reducer
+    if rs is not None:
+      # peer-memory return of the partials: the dK/dV kernels write the partial for owner r straight into slice r of
+      # a symmetric buffer ([dK | dV] per owner), and every owner pulls and sums its slice with one kernel
+      shape = (2,) + tuple(kg.shape[1:])
+      parts = rs.slices(shape)
+      if min(lens) < kg.shape[2]:
+        for part in parts:
+          part.zero_()
+      for i in range(n):
+        part = parts[ctx.order[i]]
+        K.flash_bwd_dkv(q, d_o, ks[i], vs[i], lse, delta, ctx.scale, dk=part[0][:, :lens[i]], dv=part[1][:, :lens[i]])
+      both = rs.reduce()
+      return dq, both[0], both[1], None, None, None, None, None
     dkg = torch.zeros_like(kg) if min(lens) < kg.shape[2] else torch.empty_like(kg)
     dvg = torch.zeros_like(vg) if min(lens) < vg.shape[2] else torch.empty_like(vg)
     for i in range(n):
@@ -121,7 +135,7 @@ class _SegmentAttentionFn(torch.autograd.Function):
       dvg[ctx.order[i]][:, :lens[i]].copy_(dv)
     dk = C.reduce_scatter_stack(dkg, ctx.group)
     dv = C.reduce_scatter_stack(dvg, ctx.group)
-    return dq, dk, dv, None, None, None, None
+    return dq, dk, dv, None, None, None, None, None
 
 
 class ContextParallel:
@@ -136,6 +150,7 @@ class ContextParallel:
     self.peer_memory = peer_memory
     self._exchanges: dict = {}
     self._peers: dict = {}
+    self._reducers: dict = {}
     self.group = mesh.group("context")
     self.size = mesh.size("context")
     self.rank = mesh.index_in("context") if self.size > 1 else 0
@@ -164,6 +179,18 @@ class ContextParallel:
       ex = symm.PeerKVExchange(self._peers[key], k.numel(), k.dtype)
       self._exchanges[key] = ex
     return ex
+
+  def _reducer_for(self, group, k):
+    """The peer-memory reduce-scatter that returns dK / dV partials to their owners (created on first use)."""
+    key = id(group)
+    rs = self._reducers.get(key)
+    need = 2 * k.numel()
+    if rs is None or rs.numel < need:
+      from . import symm
+
+      rs = symm.PeerReduceScatter(self._peers[key], need, k.dtype)
+      self._reducers[key] = rs
+    return rs
 
   # ---- sequence layout ---------------------------------------------------------------------
   def shard_sequence(self, x: torch.Tensor, dim: int = 1) -> torch.Tensor:
@@ -203,7 +230,9 @@ class ContextParallel:
     D = q.shape[-1]
     scale = scale if scale is not None else D ** -0.5
     if q.is_cuda and q.dtype == torch.bfloat16 and D == 128:
-      return _SegmentAttentionFn.apply(q, k, v, scale, group, tuple(valid_lens), self._exchange_for(group, k))
+      ex = self._exchange_for(group, k)
+      rs = self._reducer_for(group, k) if (ex is not None and torch.is_grad_enabled() and k.requires_grad) else None
+      return _SegmentAttentionFn.apply(q, k, v, scale, group, tuple(valid_lens), ex, rs)
     kg = _GatherSeq.apply(k, group)
     vg = _GatherSeq.apply(v, group)
     ks = [kg[i][:, :valid_lens[i]] for i in range(n)]

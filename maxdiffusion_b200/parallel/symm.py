@@ -28,7 +28,9 @@ FLAG_KV_ACK = 3
 FLAG_SHARD_READY = 4
 FLAG_USER = 5
 FLAG_SMALL_AR = 6
-NUM_FLAG_KINDS = 8
+FLAG_RS_READY = 7
+FLAG_RS_ACK = 8
+NUM_FLAG_KINDS = 10
 WAIT_BUDGET_S = 5.0
 
 
@@ -51,6 +53,8 @@ def _declare(L):
   L.mdb_small_allreduce.argtypes = [c_void_p, c_void_p, c_int, c_int, ullp, ullp, c_int, c_int, c_int, c_int, c_uint,
                                     ctypes.c_double, c_void_p]
   L.mdb_small_allreduce.restype = c_int
+  L.mdb_pull_reduce.argtypes = [ullp, c_int, c_void_p, c_ll, c_int, c_void_p]
+  L.mdb_pull_reduce.restype = c_int
 
 
 _lib.register(_declare)
@@ -255,6 +259,56 @@ class PeerKVExchange:
       peer_copy(base + self.numel * self.elem, vg[i + 1], nbytes, ctas=32)
     self.peer.signal(FLAG_KV_ACK, e)
     return kg, vg
+
+
+class PeerReduceScatter:
+  """Reduce-scatter over peer memory for tensors that are produced slice by slice (the dK / dV partials of ring
+  attention's backward, one slice per owner rank).
+
+  Every rank's producers write their partial for owner r straight into slice r of a symmetric bf16 buffer
+  (`slices()` hands out the views). `reduce()` then raises this rank's READY flag on every peer, waits (bounded) for
+  all peers, and ONE kernel pulls this rank's slice from every rank over NVLink in 16-byte loads, sums the partials
+  in rank order in fp32 and writes bf16: every byte crosses NVLink once, the sum is rounded once, and the result is
+  bitwise reproducible. An ACK flag lets the two buffer slots be reused without a barrier.
+  """
+
+  def __init__(self, peer: "PeerGroup", max_slice_numel: int, dtype=torch.bfloat16):
+    assert dtype == torch.bfloat16
+    self.peer, self.n, self.rank = peer, peer.world, peer.rank
+    self.numel = -(-max_slice_numel // 8) * 8
+    self.slots, self.slot_ptrs = [], []
+    for _ in range(2):
+      t, ptrs, _h = peer.alloc(self.n * self.numel, dtype)
+      self.slots.append(t)
+      self.slot_ptrs.append(ptrs)
+    self.epoch = 0
+    torch.cuda.synchronize()
+    dist.barrier(group=peer.group)
+
+  def slices(self, shape):
+    """Starts an epoch: views [n][*shape] of the slot to be filled (slice r = partial for owner r)."""
+    numel = 1
+    for d in shape:
+      numel *= int(d)
+    assert numel <= self.numel and numel % 8 == 0, (numel, self.numel)
+    self.epoch += 1
+    self.peer.wait(FLAG_RS_ACK, self.epoch - 2)  # every owner has pulled the previous content of this slot
+    sym = self.slots[self.epoch % 2]
+    self._shape, self._numel = tuple(shape), numel
+    return [sym[r * self.numel:r * self.numel + numel].view(shape) for r in range(self.n)]
+
+  def reduce(self, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    e, slot = self.epoch, self.epoch % 2
+    self.peer.signal(FLAG_RS_READY, e)
+    self.peer.wait(FLAG_RS_READY, e)
+    if out is None:
+      out = torch.empty(self._shape, dtype=torch.bfloat16, device=self.slots[0].device)
+    off = self.rank * self.numel * 2
+    arr = (ctypes.c_ulonglong * self.n)(*[self.slot_ptrs[slot][r] + off for r in range(self.n)])
+    rc = _lib.lib().mdb_pull_reduce(arr, self.n, _lib.ptr(out), self._numel, 96, _lib.stream())
+    _lib.check(rc, "mdb_pull_reduce")
+    self.peer.signal(FLAG_RS_ACK, e)
+    return out
 
 
 def rs_adamw(grad_ptrs: Sequence[int], n: int, p, m, v, stats, scratch, *, lr, b1, b2, eps, wd, step, grad_scale=1.0,

@@ -213,3 +213,34 @@ def test_small_allreduce_matches_nccl_and_is_identical_across_ranks():
       assert err_sum < 1e-5 and err_max == 0.0
   for a, b in zip(res[0], res[1]):
     assert a[2] == b[2]  # bitwise identical sums on both ranks
+
+
+def _peer_reduce_scatter(rank, world):
+  import torch.distributed as dist
+
+  from maxdiffusion_b200.parallel import symm
+
+  peer = symm.PeerGroup(dist.group.WORLD)
+  rs = symm.PeerReduceScatter(peer, 2 * 3 * 40 * 128)
+  errs = []
+  for it in range(5):  # more epochs than buffer slots
+    shape = (2, 3, 8 * (it + 1), 128)
+    torch.manual_seed(100 * it + rank)
+    parts = [torch.randn(shape, device="cuda").to(torch.bfloat16) for _ in range(world)]
+    views = rs.slices(shape)
+    for v, p in zip(views, parts):
+      v.copy_(p)
+    got = rs.reduce()
+    want = torch.empty(shape, device="cuda")
+    dist.reduce_scatter_tensor(want, torch.stack([p.float() for p in parts]))
+    errs.append(((got.float() - want).abs().max() / want.abs().max()).item())
+  return errs
+
+
+@pytest.mark.gpu
+def test_peer_reduce_scatter_matches_fp32_sum():
+  if torch.cuda.device_count() < 2:
+    pytest.skip("needs 2 GPUs")
+  res = _spawn(_peer_reduce_scatter, 2)
+  for errs in res:
+    assert max(errs) < 1e-2, errs  # one bf16 rounding of an fp32 sum
