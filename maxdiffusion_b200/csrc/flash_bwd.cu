@@ -21,18 +21,19 @@
 namespace mdb {
 namespace fab {
 
-constexpr int D = 128;
 constexpr int BX = 128;   // resident rows
 constexpr int BY = 64;    // streamed rows per step
 constexpr int Y_STAGES = 4;
-constexpr int X_TILE_BYTES = BX * D * 2;        // 32 KiB (two 16 KiB chunks)
+// A tile is stored as head_dim / 64 chunks of 64 columns (128-byte rows, 128-byte swizzle).
 constexpr int X_CHUNK_BYTES = BX * 128;         // 16 KiB
-constexpr int Y_TILE_BYTES = BY * D * 2;        // 16 KiB (two 8 KiB chunks)
 constexpr int Y_CHUNK_BYTES = BY * 128;         // 8 KiB
 constexpr int MAX_SEGMENTS = 8;
 constexpr int EW_GROUPS = 4;                    // elementwise warp groups, 16 of the 64 columns each
 constexpr int NUM_THREADS = 128 + EW_GROUPS * 128;  // warp 0 TMA, warp 1 score MMAs, warp 2 accumulating MMAs, warps 4.. elementwise
-constexpr int SMEM_BYTES = 2 * X_TILE_BYTES + Y_STAGES * 2 * Y_TILE_BYTES + Y_STAGES * 128 * 4 + 1024 + 256;
+template <int HD>
+constexpr int smem_bytes() {
+  return 2 * (HD / 64) * X_CHUNK_BYTES + Y_STAGES * 2 * (HD / 64) * Y_CHUNK_BYTES + Y_STAGES * 128 * 4 + 1024 + 256;
+}
 
 struct Maps {
   CUtensorMap x1, x2;
@@ -56,9 +57,13 @@ struct Params {
   DeviceStatus* status;
 };
 
-template <bool DKV>
+template <bool DKV, int HD>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 flash_bwd_kernel(const __grid_constant__ Maps maps, const Params p) {
+  constexpr int D = HD;                        // head_dim: 64 or 128
+  constexpr int CH = HD / 64;                  // chunks per tile
+  constexpr int X_TILE_BYTES = CH * X_CHUNK_BYTES;
+  constexpr int Y_TILE_BYTES = CH * Y_CHUNK_BYTES;
   // Score-tile buffers: the hand-over chain score product -> elementwise -> accumulating product -> next score product
   // of one buffer is several times longer than the tensor work of a step, so the pipe is kept busy by the other
   // buffers. The DKV pass has TMEM for two (two accumulators), the DQ pass for three.
@@ -122,7 +127,7 @@ flash_bwd_kernel(const __grid_constant__ Maps maps, const Params p) {
     if (total_steps > 0) {
       if (lane == 0) {
         mbar_expect_tx(x_full, 2 * X_TILE_BYTES);
-        for (int c = 0; c < 2; ++c) {
+        for (int c = 0; c < CH; ++c) {
           tma_load_4d(sx1 + c * X_CHUNK_BYTES, &maps.x1, x_full, c * 64, head, x0, batch);
           tma_load_4d(sx2 + c * X_CHUNK_BYTES, &maps.x2, x_full, c * 64, head, x0, batch);
         }
@@ -155,7 +160,7 @@ flash_bwd_kernel(const __grid_constant__ Maps maps, const Params p) {
             uint8_t* d1 = sy + stage * 2 * Y_TILE_BYTES;
             uint8_t* d2 = d1 + Y_TILE_BYTES;
             mbar_expect_tx(&y_full[stage], 2 * Y_TILE_BYTES + 2 * stat_bytes);
-            for (int c = 0; c < 2; ++c) {
+            for (int c = 0; c < CH; ++c) {
               tma_load_4d(d1 + c * Y_CHUNK_BYTES, &maps.y1[seg], &y_full[stage], c * 64, head, jb * BY, batch);
               tma_load_4d(d2 + c * Y_CHUNK_BYTES, &maps.y2[seg], &y_full[stage], c * 64, head, jb * BY, batch);
             }
@@ -206,7 +211,7 @@ flash_bwd_kernel(const __grid_constant__ Maps maps, const Params p) {
   } else if (warp == 2) {
     // ------------------------------ issuing lane B: accumulating products --------
     if (lane == 0 && total_steps > 0) {
-      constexpr uint32_t idesc_acc = make_idesc_bf16(128, 128, false, true); // B operand MN-major
+      constexpr uint32_t idesc_acc = make_idesc_bf16(128, D, false, true); // B operand MN-major
       const uint64_t ym0 = make_smem_desc(smem_u32(sy), Y_CHUNK_BYTES, 1024);
       constexpr uint32_t STAGE_STEP = (2 * Y_TILE_BYTES) >> 4, TILE_STEP = Y_TILE_BYTES >> 4;
       int stage = 0;
@@ -325,7 +330,7 @@ flash_bwd_kernel(const __grid_constant__ Maps maps, const Params p) {
       }
       if (ok && mbar_wait(acc_final, 0, abort_flag, p.status, 91)) {
         tc_fence_after_sync();
-        // each column group writes 32 of the 128 output columns of every accumulator
+        // each column group writes a quarter of the output columns of every accumulator, 16 at a time
         const int n_acc = DKV ? 2 : 1;
         for (int a = 0; a < n_acc; ++a) {
           const float mul = (DKV && a == 0) ? 1.0f : p.scale;
@@ -334,16 +339,16 @@ flash_bwd_kernel(const __grid_constant__ Maps maps, const Params p) {
                           sh = a == 0 ? p.o0_sh : p.o1_sh;
           const long long off = batch * sb + static_cast<long long>(x_row) * ss + head * sh;
 #pragma unroll 1
-          for (int c = 0; c < 1; ++c) {
-            const int col0 = wg * 32;
-            uint32_t r[32];
-            tmem_ld_x32(tmem_base + lane_off + ACC + a * 128 + col0, r);
+          for (int c = 0; c < CH; ++c) {
+            const int col0 = wg * (D / 4) + c * 16;
+            uint32_t r[16];
+            tmem_ld_x16(tmem_base + lane_off + ACC + a * 128 + col0, r);
             tmem_wait_ld();
             if (row_ok) {
               if (p.out_f32) {
                 float* o = reinterpret_cast<float*>(outp) + off + col0;
 #pragma unroll
-                for (int v = 0; v < 8; ++v) {
+                for (int v = 0; v < 4; ++v) {
                   *reinterpret_cast<float4*>(o + v * 4) =
                       make_float4(__uint_as_float(r[v * 4]) * mul, __uint_as_float(r[v * 4 + 1]) * mul,
                                   __uint_as_float(r[v * 4 + 2]) * mul, __uint_as_float(r[v * 4 + 3]) * mul);
@@ -351,7 +356,7 @@ flash_bwd_kernel(const __grid_constant__ Maps maps, const Params p) {
               } else {
                 __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(outp) + off + col0;
 #pragma unroll
-                for (int v = 0; v < 4; ++v) {
+                for (int v = 0; v < 2; ++v) {
                   uint4 ov;
                   ov.x = pack_bf16x2(__uint_as_float(r[v * 8 + 0]) * mul, __uint_as_float(r[v * 8 + 1]) * mul);
                   ov.y = pack_bf16x2(__uint_as_float(r[v * 8 + 2]) * mul, __uint_as_float(r[v * 8 + 3]) * mul);
@@ -375,7 +380,8 @@ flash_bwd_kernel(const __grid_constant__ Maps maps, const Params p) {
   }
 }
 
-// delta[b,h,s] = sum_d dO[b,s,h,d] * O[b,s,h,d]; one warp per (b,s,h) row of 128 elements.
+// delta[b,h,s] = sum_d dO[b,s,h,d] * O[b,s,h,d]; one warp per (b,s,h) row of HD elements.
+template <int HD>
 __global__ void delta_kernel(const __nv_bfloat16* __restrict__ o, const __nv_bfloat16* __restrict__ d_o,
                              float* __restrict__ delta, int B, int S, int H, long long o_sb, long long o_ss,
                              long long o_sh, long long g_sb, long long g_ss, long long g_sh) {
@@ -387,17 +393,25 @@ __global__ void delta_kernel(const __nv_bfloat16* __restrict__ o, const __nv_bfl
   const long long bs = row / H;
   const int s = static_cast<int>(bs % S);
   const int b = static_cast<int>(bs / S);
-  const uint2 ov = *reinterpret_cast<const uint2*>(o + b * o_sb + s * o_ss + h * o_sh + lane * 4);
-  const uint2 gv = *reinterpret_cast<const uint2*>(d_o + b * g_sb + s * g_ss + h * g_sh + lane * 4);
-  const float2 o0 = unpack_bf16x2(ov.x), o1 = unpack_bf16x2(ov.y);
-  const float2 g0 = unpack_bf16x2(gv.x), g1 = unpack_bf16x2(gv.y);
-  float acc = o0.x * g0.x + o0.y * g0.y + o1.x * g1.x + o1.y * g1.y;
+  float acc;
+  if (HD == 128) {
+    const uint2 ov = *reinterpret_cast<const uint2*>(o + b * o_sb + s * o_ss + h * o_sh + lane * 4);
+    const uint2 gv = *reinterpret_cast<const uint2*>(d_o + b * g_sb + s * g_ss + h * g_sh + lane * 4);
+    const float2 o0 = unpack_bf16x2(ov.x), o1 = unpack_bf16x2(ov.y);
+    const float2 g0 = unpack_bf16x2(gv.x), g1 = unpack_bf16x2(gv.y);
+    acc = o0.x * g0.x + o0.y * g0.y + o1.x * g1.x + o1.y * g1.y;
+  } else {
+    const uint32_t ov = *reinterpret_cast<const uint32_t*>(o + b * o_sb + s * o_ss + h * o_sh + lane * 2);
+    const uint32_t gv = *reinterpret_cast<const uint32_t*>(d_o + b * g_sb + s * g_ss + h * g_sh + lane * 2);
+    const float2 o0 = unpack_bf16x2(ov), g0 = unpack_bf16x2(gv);
+    acc = o0.x * g0.x + o0.y * g0.y;
+  }
 #pragma unroll
   for (int off = 16; off > 0; off >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, off);
   if (lane == 0) delta[(static_cast<long long>(b) * H + h) * S + s] = acc;
 }
 
-static int make_map(CUtensorMap* map, const void* ptr, int B, int S, int H, long long sb, long long ss, long long sh,
+static int make_map(CUtensorMap* map, const void* ptr, int D, int B, int S, int H, long long sb, long long ss, long long sh,
                     int box_rows) {
   uint64_t dims[4] = {static_cast<uint64_t>(D), static_cast<uint64_t>(H), static_cast<uint64_t>(S),
                       static_cast<uint64_t>(B)};
@@ -406,20 +420,27 @@ static int make_map(CUtensorMap* map, const void* ptr, int B, int S, int H, long
   return encode_tmap_bf16(map, ptr, 4, dims, str, box);
 }
 
+template <int HD>
+static int make_map_d(CUtensorMap* map, const void* ptr, int B, int S, int H, long long sb, long long ss, long long sh,
+                      int box_rows) {
+  return make_map(map, ptr, HD, B, S, H, sb, ss, sh, box_rows);
+}
+
 }  // namespace fab
 }  // namespace mdb
 
 using namespace mdb;
 using namespace mdb::fab;
 
-extern "C" int mdb_flash_delta(const void* o, const void* d_o, float* delta, int B, int S, int H, long long o_sb,
-                               long long o_ss, long long o_sh, long long g_sb, long long g_ss, long long g_sh,
-                               void* stream) {
+template <int HD>
+static int flash_delta_launch(const void* o, const void* d_o, float* delta, int B, int S, int H, long long o_sb,
+                              long long o_ss, long long o_sh, long long g_sb, long long g_ss, long long g_sh,
+                              void* stream) {
   if ((o_sb | o_ss | o_sh | g_sb | g_ss | g_sh) & 3) return 3301;
   const long long rows = static_cast<long long>(B) * S * H;
   if (rows <= 0) return 0;
   const int blocks = static_cast<int>((rows * 32 + 255) / 256);
-  delta_kernel<<<blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+  delta_kernel<HD><<<blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(
       static_cast<const __nv_bfloat16*>(o), static_cast<const __nv_bfloat16*>(d_o), delta, B, S, H, o_sb, o_ss, o_sh,
       g_sb, g_ss, g_sh);
   return static_cast<int>(cudaGetLastError());
@@ -427,22 +448,23 @@ extern "C" int mdb_flash_delta(const void* o, const void* d_o, float* delta, int
 
 // dK, dV of one KV segment from all local queries. Strides in elements (batch, seq, head).
 // q/dO share q strides `qs`, k/v share `ks`; outputs share `os`. out_f32 selects fp32 outputs.
-extern "C" int mdb_flash_bwd_dkv(const void* q, const void* d_o, const void* k, const void* v, const float* lse,
-                                 const float* delta, void* dk, void* dv, int B, int H, int q_len, int kv_len,
-                                 const long long* qs, const long long* gs, const long long* ks, const long long* vs,
-                                 const long long* dks, const long long* dvs, float softmax_scale, int out_f32,
-                                 void* stream) {
+template <int HD>
+static int flash_bwd_dkv_launch(const void* q, const void* d_o, const void* k, const void* v, const float* lse,
+                                const float* delta, void* dk, void* dv, int B, int H, int q_len, int kv_len,
+                                const long long* qs, const long long* gs, const long long* ks, const long long* vs,
+                                const long long* dks, const long long* dvs, float softmax_scale, int out_f32,
+                                void* stream) {
   if (B <= 0 || H <= 0 || q_len <= 0 || kv_len <= 0) return 0;
   Maps maps;
   Params p;
-  int rc = make_map(&maps.x1, k, B, kv_len, H, ks[0], ks[1], ks[2], BX);
+  int rc = make_map_d<HD>(&maps.x1, k, B, kv_len, H, ks[0], ks[1], ks[2], BX);
   if (rc) return rc;
-  rc = make_map(&maps.x2, v, B, kv_len, H, vs[0], vs[1], vs[2], BX);
+  rc = make_map_d<HD>(&maps.x2, v, B, kv_len, H, vs[0], vs[1], vs[2], BX);
   if (rc) return rc;
   for (int s = 0; s < MAX_SEGMENTS; ++s) {
-    rc = make_map(&maps.y1[s], q, B, q_len, H, qs[0], qs[1], qs[2], BY);
+    rc = make_map_d<HD>(&maps.y1[s], q, B, q_len, H, qs[0], qs[1], qs[2], BY);
     if (rc) return rc;
-    rc = make_map(&maps.y2[s], d_o, B, q_len, H, gs[0], gs[1], gs[2], BY);
+    rc = make_map_d<HD>(&maps.y2[s], d_o, B, q_len, H, gs[0], gs[1], gs[2], BY);
     if (rc) return rc;
     p.y_len[s] = s == 0 ? q_len : 0;
   }
@@ -457,34 +479,35 @@ extern "C" int mdb_flash_bwd_dkv(const void* q, const void* d_o, const void* k, 
   p.status = status_buffer();
   static bool configured = false;
   if (!configured) {
-    MDB_CHECK_CUDA(cudaFuncSetAttribute(flash_bwd_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
+    MDB_CHECK_CUDA(cudaFuncSetAttribute(flash_bwd_kernel<true, HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes<HD>()));
     configured = true;
   }
   dim3 grid((kv_len + BX - 1) / BX, H, B);
-  flash_bwd_kernel<true><<<grid, NUM_THREADS, SMEM_BYTES, static_cast<cudaStream_t>(stream)>>>(maps, p);
+  flash_bwd_kernel<true, HD><<<grid, NUM_THREADS, smem_bytes<HD>(), static_cast<cudaStream_t>(stream)>>>(maps, p);
   return static_cast<int>(cudaGetLastError());
 }
 
 // dQ of the local queries over every KV segment.
-extern "C" int mdb_flash_bwd_dq(const void* q, const void* d_o, const void* const* k_ptrs, const void* const* v_ptrs,
-                                const float* lse, const float* delta, void* dq, int B, int H, int q_len,
-                                int num_segments, const int* kv_lens, const long long* qs, const long long* gs,
-                                const long long* ks, const long long* vs, const long long* dqs, float softmax_scale,
-                                int out_f32, void* stream) {
+template <int HD>
+static int flash_bwd_dq_launch(const void* q, const void* d_o, const void* const* k_ptrs, const void* const* v_ptrs,
+                               const float* lse, const float* delta, void* dq, int B, int H, int q_len,
+                               int num_segments, const int* kv_lens, const long long* qs, const long long* gs,
+                               const long long* ks, const long long* vs, const long long* dqs, float softmax_scale,
+                               int out_f32, void* stream) {
   if (B <= 0 || H <= 0 || q_len <= 0) return 0;
   if (num_segments < 1 || num_segments > MAX_SEGMENTS) return 3302;
   Maps maps;
   Params p;
-  int rc = make_map(&maps.x1, q, B, q_len, H, qs[0], qs[1], qs[2], BX);
+  int rc = make_map_d<HD>(&maps.x1, q, B, q_len, H, qs[0], qs[1], qs[2], BX);
   if (rc) return rc;
-  rc = make_map(&maps.x2, d_o, B, q_len, H, gs[0], gs[1], gs[2], BX);
+  rc = make_map_d<HD>(&maps.x2, d_o, B, q_len, H, gs[0], gs[1], gs[2], BX);
   if (rc) return rc;
   for (int s = 0; s < MAX_SEGMENTS; ++s) {
     const int src = s < num_segments ? s : 0;
     const int len = kv_lens[src] > 0 ? kv_lens[src] : 1;
-    rc = make_map(&maps.y1[s], k_ptrs[src], B, len, H, ks[0], ks[1], ks[2], BY);
+    rc = make_map_d<HD>(&maps.y1[s], k_ptrs[src], B, len, H, ks[0], ks[1], ks[2], BY);
     if (rc) return rc;
-    rc = make_map(&maps.y2[s], v_ptrs[src], B, len, H, vs[0], vs[1], vs[2], BY);
+    rc = make_map_d<HD>(&maps.y2[s], v_ptrs[src], B, len, H, vs[0], vs[1], vs[2], BY);
     if (rc) return rc;
     p.y_len[s] = s < num_segments ? kv_lens[s] : 0;
   }
@@ -499,10 +522,37 @@ extern "C" int mdb_flash_bwd_dq(const void* q, const void* d_o, const void* cons
   p.status = status_buffer();
   static bool configured = false;
   if (!configured) {
-    MDB_CHECK_CUDA(cudaFuncSetAttribute(flash_bwd_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
+    MDB_CHECK_CUDA(cudaFuncSetAttribute(flash_bwd_kernel<false, HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes<HD>()));
     configured = true;
   }
   dim3 grid((q_len + BX - 1) / BX, H, B);
-  flash_bwd_kernel<false><<<grid, NUM_THREADS, SMEM_BYTES, static_cast<cudaStream_t>(stream)>>>(maps, p);
+  flash_bwd_kernel<false, HD><<<grid, NUM_THREADS, smem_bytes<HD>(), static_cast<cudaStream_t>(stream)>>>(maps, p);
   return static_cast<int>(cudaGetLastError());
 }
+
+// C entry points: head_dim 128, and `_d64` for head_dim 64 (Stable Diffusion / SDXL / LTX-Video heads).
+#define MDB_FAB_ENTRY(SUFFIX, HD)                                                                                        \
+  extern "C" int mdb_flash_delta##SUFFIX(const void* o, const void* d_o, float* delta, int B, int S, int H,               \
+                                         long long o_sb, long long o_ss, long long o_sh, long long g_sb, long long g_ss,  \
+                                         long long g_sh, void* stream) {                                                  \
+    return flash_delta_launch<HD>(o, d_o, delta, B, S, H, o_sb, o_ss, o_sh, g_sb, g_ss, g_sh, stream);                    \
+  }                                                                                                                       \
+  extern "C" int mdb_flash_bwd_dkv##SUFFIX(const void* q, const void* d_o, const void* k, const void* v,                  \
+                                           const float* lse, const float* delta, void* dk, void* dv, int B, int H,        \
+                                           int q_len, int kv_len, const long long* qs, const long long* gs,               \
+                                           const long long* ks, const long long* vs, const long long* dks,                \
+                                           const long long* dvs, float softmax_scale, int out_f32, void* stream) {        \
+    return flash_bwd_dkv_launch<HD>(q, d_o, k, v, lse, delta, dk, dv, B, H, q_len, kv_len, qs, gs, ks, vs, dks, dvs,      \
+                                    softmax_scale, out_f32, stream);                                                      \
+  }                                                                                                                       \
+  extern "C" int mdb_flash_bwd_dq##SUFFIX(const void* q, const void* d_o, const void* const* k_ptrs,                      \
+                                          const void* const* v_ptrs, const float* lse, const float* delta, void* dq,      \
+                                          int B, int H, int q_len, int num_segments, const int* kv_lens,                  \
+                                          const long long* qs, const long long* gs, const long long* ks,                  \
+                                          const long long* vs, const long long* dqs, float softmax_scale, int out_f32,    \
+                                          void* stream) {                                                                 \
+    return flash_bwd_dq_launch<HD>(q, d_o, k_ptrs, v_ptrs, lse, delta, dq, B, H, q_len, num_segments, kv_lens, qs, gs,    \
+                                   ks, vs, dqs, softmax_scale, out_f32, stream);                                          \
+  }
+MDB_FAB_ENTRY(, 128)
+MDB_FAB_ENTRY(_d64, 64)

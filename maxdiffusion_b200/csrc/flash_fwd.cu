@@ -38,18 +38,17 @@
 namespace mdb {
 namespace fa {
 
-constexpr int D = 128;
 constexpr int BQ = 128;          // rows per q tile
 constexpr int BKV = 64;          // keys per block
 constexpr int KV_STAGES = 4;
-constexpr int TILE_BYTES = 128 * D * 2;  // Q tile, 32 KiB: two 64-column chunks of 128 rows x 128 B
-constexpr int CHUNK_BYTES = 128 * 128;   // 16 KiB
-constexpr int KV_TILE_BYTES = BKV * D * 2;   // 16 KiB: two chunks of 64 rows x 128 B
-constexpr int KV_CHUNK_BYTES = BKV * 128;    // 8 KiB
+// A tile is stored as head_dim / 64 chunks of 64 columns (128-byte rows, 128-byte swizzle).
+constexpr int CHUNK_BYTES = 128 * 128;       // 16 KiB: one chunk of a 128-row Q tile
+constexpr int KV_CHUNK_BYTES = BKV * 128;    // 8 KiB: one chunk of a 64-key K / V tile
 constexpr int MAX_SEGMENTS = 8;
 constexpr int ROLE_WARPS = 5;            // warp 0 TMA, warps 1 / 3 issue S of tile 0 / 1, warps 2 / 4 issue P V of tile 0 / 1
 constexpr int NUM_THREADS = ROLE_WARPS * 32 + 256;  // + softmax warps 5-8 (tile 0), 9-12 (tile 1)
-constexpr int SMEM_BYTES = 2 * TILE_BYTES + 2 * KV_STAGES * KV_TILE_BYTES + 1024 + 512;
+template <int HD>
+constexpr int smem_bytes() { return 2 * (HD / 64) * CHUNK_BYTES + 2 * KV_STAGES * (HD / 64) * KV_CHUNK_BYTES + 1024 + 512; }
 constexpr float kRescaleThreshold = 8.0f;
 
 struct KVMaps {
@@ -166,6 +165,7 @@ __device__ __forceinline__ void copy_cta(const CopyPlan& cp, int ci, DeviceStatu
   }
 }
 
+template <int HD>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 flash_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ KVMaps maps, const Params p,
                  const __grid_constant__ CopyPlan cp) {
@@ -176,6 +176,10 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
     return;
   }
 
+  constexpr int D = HD;                       // head_dim: 64 or 128
+  constexpr int CH = HD / 64;                 // chunks per tile
+  constexpr int TILE_BYTES = CH * CHUNK_BYTES;        // Q tile of 128 rows
+  constexpr int KV_TILE_BYTES = CH * KV_CHUNK_BYTES;  // K / V tile of 64 keys
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* sq = smem;                                  // [2 tiles][2 chunks][128][128 B]
@@ -250,7 +254,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
         if (!mbar_wait(q_empty, (it & 1) ^ 1u, abort_flag, p.status, 43)) { ok = false; break; }
         mbar_expect_tx(q_full, n_tiles * TILE_BYTES);
         for (int t = 0; t < n_tiles; ++t) {
-          for (int c = 0; c < 2; ++c) {
+          for (int c = 0; c < CH; ++c) {
             tma_load_4d(sq + t * TILE_BYTES + c * CHUNK_BYTES, &tmap_q, q_full, c * 64, head, q0 + t * BQ, batch);
           }
         }
@@ -264,13 +268,13 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
           for (int jb = 0; jb < nblk; ++jb) {
             if (!mbar_wait(&k_empty[stage], phase ^ 1u, abort_flag, p.status, 41)) { ok = false; break; }
             mbar_expect_tx(&k_full[stage], KV_TILE_BYTES);
-            for (int c = 0; c < 2; ++c) {
+            for (int c = 0; c < CH; ++c) {
               tma_load_4d(sk + stage * KV_TILE_BYTES + c * KV_CHUNK_BYTES, &maps.k[seg], &k_full[stage], c * 64, head,
                           jb * BKV, batch);
             }
             if (!mbar_wait(&v_empty[stage], phase ^ 1u, abort_flag, p.status, 42)) { ok = false; break; }
             mbar_expect_tx(&v_full[stage], KV_TILE_BYTES);
-            for (int c = 0; c < 2; ++c) {
+            for (int c = 0; c < CH; ++c) {
               tma_load_4d(sv + stage * KV_TILE_BYTES + c * KV_CHUNK_BYTES, &maps.v[seg], &v_full[stage], c * 64, head,
                           jb * BKV, batch);
             }
@@ -329,7 +333,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
     // ------------------------------ issuing lanes: O_t += P_t V_j ----------------
     if (lane == 0 && total_blocks > 0) {
       const int t = (warp >> 1) - 1;  // warp 2 -> tile 0, warp 4 -> tile 1
-      constexpr uint32_t idesc_pv = make_idesc_bf16(128, 128, false, true);
+      constexpr uint32_t idesc_pv = make_idesc_bf16(128, D, false, true);
       const uint64_t vd0 = make_smem_desc(smem_u32(sv), KV_CHUNK_BYTES, 1024);
       constexpr uint32_t STAGE_STEP = KV_TILE_BYTES >> 4;
       const uint32_t o_col = tmem_base + 256 + t * 128;
@@ -421,7 +425,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
               l *= alpha;
               m = m_new;
 #pragma unroll 1
-              for (int c = 0; c < 4; ++c) {
+              for (int c = 0; c < D / 32; ++c) {
                 uint32_t r[32];
                 tmem_ld_x32(o_addr + c * 32, r);
                 tmem_wait_ld();
@@ -468,7 +472,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
       __nv_bfloat16* orow = p.out + batch * p.o_stride_b + static_cast<long long>(q_row) * p.o_stride_s +
                             head * p.o_stride_h;
 #pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
+      for (int c = 0; c < D / 32; ++c) {
         uint32_t r[32];
         tmem_ld_x32(o_addr + c * 32, r);
         tmem_wait_ld();
@@ -500,7 +504,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
   }
 }
 
-static int make_map(CUtensorMap* map, const void* ptr, int B, int S, int H, long long sb, long long ss, long long sh,
+static int make_map(CUtensorMap* map, const void* ptr, int D, int B, int S, int H, long long sb, long long ss, long long sh,
                     int box_rows) {
   // dims innermost first: (D, H, S, B)
   uint64_t dims[4] = {static_cast<uint64_t>(D), static_cast<uint64_t>(H), static_cast<uint64_t>(S),
@@ -532,12 +536,13 @@ struct MdbCopyPlan {
 // (batch, sequence, head); the head_dim stride is 1. Every segment shares the k strides / v strides
 // given here. `plan` (may be null) adds copy CTAs that stage the remote segments 1.. from peer memory.
 // Returns 0 or an error code.
-extern "C" int mdb_flash_fwd(const void* q, const void* const* k_ptrs, const void* const* v_ptrs, void* out,
-                             float* lse, int B, int H, int q_len, int num_segments, const int* kv_lens,
-                             long long q_sb, long long q_ss, long long q_sh, long long k_sb, long long k_ss,
-                             long long k_sh, long long v_sb, long long v_ss, long long v_sh, long long o_sb,
-                             long long o_ss, long long o_sh, float softmax_scale, const unsigned int* seg_flags,
-                             unsigned int flag_target, const MdbCopyPlan* plan, void* stream_ptr) {
+template <int HD>
+static int flash_fwd_launch(const void* q, const void* const* k_ptrs, const void* const* v_ptrs, void* out,
+                            float* lse, int B, int H, int q_len, int num_segments, const int* kv_lens,
+                            long long q_sb, long long q_ss, long long q_sh, long long k_sb, long long k_ss,
+                            long long k_sh, long long v_sb, long long v_ss, long long v_sh, long long o_sb,
+                            long long o_ss, long long o_sh, float softmax_scale, const unsigned int* seg_flags,
+                            unsigned int flag_target, const MdbCopyPlan* plan, void* stream_ptr) {
   using namespace mdb;
   using namespace mdb::fa;
   if (B <= 0 || H <= 0 || q_len <= 0) return 0;
@@ -546,15 +551,15 @@ extern "C" int mdb_flash_fwd(const void* q, const void* const* k_ptrs, const voi
   CUtensorMap tq;
   KVMaps maps;
   Params p;
-  int rc = make_map(&tq, q, B, q_len, H, q_sb, q_ss, q_sh, BQ);
+  int rc = make_map(&tq, q, HD, B, q_len, H, q_sb, q_ss, q_sh, BQ);
   if (rc) return rc;
   for (int s = 0; s < MAX_SEGMENTS; ++s) {
     const int src = s < num_segments ? s : 0;
     p.kv_len[s] = s < num_segments ? kv_lens[s] : 0;
     const int len = kv_lens[src] > 0 ? kv_lens[src] : 1;
-    rc = make_map(&maps.k[s], k_ptrs[src], B, len, H, k_sb, k_ss, k_sh, BKV);
+    rc = make_map(&maps.k[s], k_ptrs[src], HD, B, len, H, k_sb, k_ss, k_sh, BKV);
     if (rc) return rc;
-    rc = make_map(&maps.v[s], v_ptrs[src], B, len, H, v_sb, v_ss, v_sh, BKV);
+    rc = make_map(&maps.v[s], v_ptrs[src], HD, B, len, H, v_sb, v_ss, v_sh, BKV);
     if (rc) return rc;
   }
   p.B = B; p.H = H; p.q_len = q_len;
@@ -590,7 +595,7 @@ extern "C" int mdb_flash_fwd(const void* q, const void* const* k_ptrs, const voi
   }
   static bool configured = false;
   if (!configured) {
-    MDB_CHECK_CUDA(cudaFuncSetAttribute(flash_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
+    MDB_CHECK_CUDA(cudaFuncSetAttribute(flash_fwd_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes<HD>()));
     configured = true;
   }
   const int n_qb = (q_len + 2 * BQ - 1) / (2 * BQ);
@@ -599,6 +604,29 @@ extern "C" int mdb_flash_fwd(const void* q, const void* const* k_ptrs, const voi
   int n_compute = sm_count() - n_copy;
   if (n_compute < 1) return 3104;
   if (total_work < n_compute) n_compute = static_cast<int>(total_work);
-  flash_fwd_kernel<<<n_compute + n_copy, NUM_THREADS, SMEM_BYTES, static_cast<cudaStream_t>(stream_ptr)>>>(tq, maps, p, cp);
+  flash_fwd_kernel<HD><<<n_compute + n_copy, NUM_THREADS, smem_bytes<HD>(), static_cast<cudaStream_t>(stream_ptr)>>>(tq, maps, p, cp);
   return static_cast<int>(cudaGetLastError());
+}
+
+extern "C" int mdb_flash_fwd(const void* q, const void* const* k_ptrs, const void* const* v_ptrs, void* out,
+                             float* lse, int B, int H, int q_len, int num_segments, const int* kv_lens,
+                             long long q_sb, long long q_ss, long long q_sh, long long k_sb, long long k_ss,
+                             long long k_sh, long long v_sb, long long v_ss, long long v_sh, long long o_sb,
+                             long long o_ss, long long o_sh, float softmax_scale, const unsigned int* seg_flags,
+                             unsigned int flag_target, const MdbCopyPlan* plan, void* stream_ptr) {
+  return flash_fwd_launch<128>(q, k_ptrs, v_ptrs, out, lse, B, H, q_len, num_segments, kv_lens, q_sb, q_ss, q_sh, k_sb,
+                               k_ss, k_sh, v_sb, v_ss, v_sh, o_sb, o_ss, o_sh, softmax_scale, seg_flags, flag_target,
+                               plan, stream_ptr);
+}
+
+// Same for head_dim 64 (Stable Diffusion / SDXL / LTX-Video heads).
+extern "C" int mdb_flash_fwd_d64(const void* q, const void* const* k_ptrs, const void* const* v_ptrs, void* out,
+                                 float* lse, int B, int H, int q_len, int num_segments, const int* kv_lens,
+                                 long long q_sb, long long q_ss, long long q_sh, long long k_sb, long long k_ss,
+                                 long long k_sh, long long v_sb, long long v_ss, long long v_sh, long long o_sb,
+                                 long long o_ss, long long o_sh, float softmax_scale, const unsigned int* seg_flags,
+                                 unsigned int flag_target, const MdbCopyPlan* plan, void* stream_ptr) {
+  return flash_fwd_launch<64>(q, k_ptrs, v_ptrs, out, lse, B, H, q_len, num_segments, kv_lens, q_sb, q_ss, q_sh, k_sb,
+                              k_ss, k_sh, v_sb, v_ss, v_sh, o_sb, o_ss, o_sh, softmax_scale, seg_flags, flag_target,
+                              plan, stream_ptr);
 }

@@ -6,7 +6,7 @@ Reference: `FlaxUNet2DConditionModel` (src/maxdiffusion/models/unet_2d_condition
 parameter names follow the diffusers `UNet2DConditionModel` checkpoint so that its safetensors load directly.
 
 GEMMs (projections, GEGLU feed-forward, attention in/out) run on the tcgen05 GEMM through `ops.functional.linear`
-for bf16 CUDA tensors; attention with head_dim 128 uses the flash kernel, other head sizes (64 for SDXL, 40..160
+for bf16 CUDA tensors; attention with head_dim 64 (SDXL) or 128 uses the flash kernels, other head sizes (40..160
 for SD 1.x/2.x) go through `scaled_dot_product_attention`; convolutions use cuDNN; GroupNorm(+SiLU) is the fused kernel of `ops.functional.group_norm`.
 """
 from __future__ import annotations

@@ -109,6 +109,8 @@ def _declare(L: ctypes.CDLL) -> None:
                               + [c_int] * 4 + [ctypes.POINTER(c_int)] + [c_ll] * 12 + [c_float, c_void_p, ctypes.c_uint,
                                                                                       c_void_p, c_void_p])
   L.mdb_flash_fwd.restype = c_int
+  L.mdb_flash_fwd_d64.argtypes = L.mdb_flash_fwd.argtypes
+  L.mdb_flash_fwd_d64.restype = c_int
   L.mdb_ln_fwd.argtypes = [c_void_p] * 6 + [c_ll, c_int, c_int, c_int, c_float, c_void_p, c_void_p, c_int, c_void_p]
   L.mdb_ln_fwd.restype = c_int
   L.mdb_ln_bwd.argtypes = [c_void_p] * 6 + [c_ll, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p]
@@ -143,6 +145,9 @@ def _declare(L: ctypes.CDLL) -> None:
                                   c_void_p, c_void_p] + [c_int] * 4 + [ctypes.POINTER(c_int)] + [c_llp] * 5 +
                                  [c_float, c_int, c_void_p])
   L.mdb_flash_bwd_dq.restype = c_int
+  for name in ("mdb_flash_delta", "mdb_flash_bwd_dkv", "mdb_flash_bwd_dq"):  # head_dim 64 variants: same signatures
+    getattr(L, name + "_d64").argtypes = getattr(L, name).argtypes
+    getattr(L, name + "_d64").restype = c_int
   for fn in _EXTRA:
     fn(L)
 

@@ -187,7 +187,7 @@ def attention(q, k, v, scale: float | None = None):
   vs = list(v) if isinstance(v, (list, tuple)) else [v]
   D = q.shape[-1]
   scale = scale if scale is not None else 1.0 / math.sqrt(D)
-  if _fast(q) and D == 128:
+  if _fast(q) and D in K.FLASH_HEAD_DIMS:
     return _AttentionFn.apply(q, scale, len(ks), *ks, *vs)
   kc = torch.cat(ks, dim=1) if len(ks) > 1 else ks[0]
   vc = torch.cat(vs, dim=1) if len(vs) > 1 else vs[0]

@@ -53,16 +53,26 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = F
   return out
 
 
+FLASH_HEAD_DIMS = (64, 128)
+
+
+def _flash_entry(name: str, D: int):
+  """The C entry point of an attention kernel for head_dim D (128: `name`, 64: `name_d64`)."""
+  if D not in FLASH_HEAD_DIMS:
+    raise ValueError(f"the flash-attention kernels are built for head_dim {FLASH_HEAD_DIMS}, got {D}")
+  return getattr(_lib.lib(), name if D == 128 else name + "_d64")
+
+
 def flash_fwd(q: torch.Tensor, k_list: Sequence[torch.Tensor], v_list: Sequence[torch.Tensor], scale: float | None = None,
               return_lse: bool = True, seg_flags: torch.Tensor | None = None, flag_target: int = 0, plan=None):
-  """Flash attention forward over KV segments. q: [B,Sq,H,128]; k/v: lists of [B,Skv_i,H,128] sharing strides.
+  """Flash attention forward over KV segments. q: [B,Sq,H,D]; k/v: lists of [B,Skv_i,H,D] sharing strides; D is 64 or 128.
 
   `seg_flags` gates segment i on flags[i] >= flag_target; `plan` (an `_lib.CopyPlan`) adds copy CTAs that stage
   the remote segments from peer memory inside the same launch."""
   if isinstance(k_list, torch.Tensor):
     k_list, v_list = [k_list], [v_list]
   B, Sq, H, D = q.shape
-  assert D == 128 and q.dtype == torch.bfloat16 and q.stride(-1) == 1
+  assert D in FLASH_HEAD_DIMS and q.dtype == torch.bfloat16 and q.stride(-1) == 1
   k0, v0 = k_list[0], v_list[0]
   for k, v in zip(k_list, v_list):
     assert k.dtype == torch.bfloat16 and v.dtype == torch.bfloat16
@@ -74,7 +84,7 @@ def flash_fwd(q: torch.Tensor, k_list: Sequence[torch.Tensor], v_list: Sequence[
   vp = (ctypes.c_void_p * n)(*[v.data_ptr() for v in v_list])
   lens = (ctypes.c_int * n)(*[k.shape[1] for k in k_list])
   scale = scale if scale is not None else 1.0 / math.sqrt(D)
-  rc = _lib.lib().mdb_flash_fwd(
+  rc = _flash_entry("mdb_flash_fwd", D)(
       _lib.ptr(q), kp, vp, _lib.ptr(out), _lib.ptr(lse), B, H, Sq, n, lens,
       q.stride(0), q.stride(1), q.stride(2), k0.stride(0), k0.stride(1), k0.stride(2),
       v0.stride(0), v0.stride(1), v0.stride(2), out.stride(0), out.stride(1), out.stride(2),
@@ -91,27 +101,27 @@ def _strides3(t):
 def flash_delta(o, d_o):
   """delta[b,h,s] = sum_d dO*O (fp32), the row term of the softmax backward."""
   B, S, H, D = o.shape
-  assert D == 128 and o.stride(-1) == 1 and d_o.stride(-1) == 1
+  assert D in FLASH_HEAD_DIMS and o.stride(-1) == 1 and d_o.stride(-1) == 1
   delta = torch.empty((B, H, S), device=o.device, dtype=torch.float32)
-  rc = _lib.lib().mdb_flash_delta(_lib.ptr(o), _lib.ptr(d_o), _lib.ptr(delta), B, S, H, o.stride(0), o.stride(1),
+  rc = _flash_entry("mdb_flash_delta", D)(_lib.ptr(o), _lib.ptr(d_o), _lib.ptr(delta), B, S, H, o.stride(0), o.stride(1),
                                   o.stride(2), d_o.stride(0), d_o.stride(1), d_o.stride(2), _lib.stream())
   _lib.check(rc, "mdb_flash_delta")
   return delta
 
 
 def flash_bwd_dkv(q, d_o, k, v, lse, delta, scale=None, out_dtype=torch.bfloat16, dk=None, dv=None):
-  """dK, dV of one KV segment [B,Skv,H,128] from the local queries q/dO [B,Sq,H,128]. `dk` / `dv` may be given
-  (e.g. views of a symmetric buffer); they must be [B,Skv,H,128] with unit head_dim stride."""
+  """dK, dV of one KV segment [B,Skv,H,D] from the local queries q/dO [B,Sq,H,D]. `dk` / `dv` may be given
+  (e.g. views of a symmetric buffer); they must be [B,Skv,H,D] with unit head_dim stride."""
   B, Sq, H, D = q.shape
   Skv = k.shape[1]
-  assert D == 128 and all(t.stride(-1) == 1 for t in (q, d_o, k, v))
+  assert D in FLASH_HEAD_DIMS and all(t.stride(-1) == 1 for t in (q, d_o, k, v))
   if dk is None:
     dk = torch.empty((B, Skv, H, D), device=q.device, dtype=out_dtype)
   if dv is None:
     dv = torch.empty((B, Skv, H, D), device=q.device, dtype=out_dtype)
   assert dk.shape == (B, Skv, H, D) and dv.shape == (B, Skv, H, D) and dk.dtype == out_dtype and dv.dtype == out_dtype
   scale = scale if scale is not None else 1.0 / math.sqrt(D)
-  rc = _lib.lib().mdb_flash_bwd_dkv(_lib.ptr(q), _lib.ptr(d_o), _lib.ptr(k), _lib.ptr(v), _lib.ptr(lse),
+  rc = _flash_entry("mdb_flash_bwd_dkv", D)(_lib.ptr(q), _lib.ptr(d_o), _lib.ptr(k), _lib.ptr(v), _lib.ptr(lse),
                                     _lib.ptr(delta), _lib.ptr(dk), _lib.ptr(dv), B, H, Sq, Skv, _strides3(q),
                                     _strides3(d_o), _strides3(k), _strides3(v), _strides3(dk), _strides3(dv),
                                     float(scale), int(out_dtype == torch.float32), _lib.stream())
@@ -133,7 +143,7 @@ def flash_bwd_dq(q, d_o, k_list, v_list, lse, delta, scale=None, out_dtype=torch
   vp = (ctypes.c_void_p * n)(*[v.data_ptr() for v in v_list])
   lens = (ctypes.c_int * n)(*[k.shape[1] for k in k_list])
   scale = scale if scale is not None else 1.0 / math.sqrt(D)
-  rc = _lib.lib().mdb_flash_bwd_dq(_lib.ptr(q), _lib.ptr(d_o), kp, vp, _lib.ptr(lse), _lib.ptr(delta), _lib.ptr(dq), B,
+  rc = _flash_entry("mdb_flash_bwd_dq", D)(_lib.ptr(q), _lib.ptr(d_o), kp, vp, _lib.ptr(lse), _lib.ptr(delta), _lib.ptr(dq), B,
                                    H, Sq, n, lens, _strides3(q), _strides3(d_o), _strides3(k0), _strides3(v0),
                                    _strides3(dq), float(scale), int(out_dtype == torch.float32), _lib.stream())
   _lib.check(rc, "mdb_flash_bwd_dq")

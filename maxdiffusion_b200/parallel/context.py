@@ -229,7 +229,7 @@ class ContextParallel:
       return OF.attention(q, k, v, scale)
     D = q.shape[-1]
     scale = scale if scale is not None else D ** -0.5
-    if q.is_cuda and q.dtype == torch.bfloat16 and D == 128:
+    if q.is_cuda and q.dtype == torch.bfloat16 and D in K.FLASH_HEAD_DIMS:
       ex = self._exchange_for(group, k)
       rs = self._reducer_for(group, k) if (ex is not None and torch.is_grad_enabled() and k.requires_grad) else None
       return _SegmentAttentionFn.apply(q, k, v, scale, group, tuple(valid_lens), ex, rs)

@@ -99,6 +99,29 @@ def bench_flash(results):
     del q, k, v
 
 
+def bench_flash_d64(results):
+  """head_dim 64 (SDXL self-attention shapes: batch 8, 10 heads x 4096 tokens and 20 heads x 1024 tokens; LTX-Video
+  2B: 32 heads) forward and backward, with PyTorch SDPA on the same tensors for comparison."""
+  import torch.nn.functional as F
+
+  tf_peak, _, tag = peaks()
+  for B, H, S in [(8, 10, 4096), (8, 20, 1024), (1, 32, 16384)]:
+    q, k, v, d_o = (torch.randn((B, S, H, 64), device="cuda", dtype=torch.bfloat16) for _ in range(4))
+    out, lse = K.flash_fwd(q, k, v)
+    delta = K.flash_delta(out, d_o)
+    fwd, _ = time_ms(lambda: K.flash_fwd(q, k, v), iters=5)
+    dkv, _ = time_ms(lambda: K.flash_bwd_dkv(q, d_o, k, v, lse, delta), iters=5)
+    dq, _ = time_ms(lambda: K.flash_bwd_dq(q, d_o, k, v, lse, delta), iters=5)
+    qt, kt, vt = (t.transpose(1, 2) for t in (q, k, v))
+    sdpa, _ = time_ms(lambda: F.scaled_dot_product_attention(qt, kt, vt), iters=5)
+    fl = 4.0 * B * H * S * S * 64
+    results.append(dict(kernel="flash_d64", shape=[B, H, S], fwd_ms=fwd, dkv_ms=dkv, dq_ms=dq, sdpa_fwd_ms=sdpa,
+                        fwd_tflops=fl / fwd / 1e9, bwd_tflops_algorithmic=2.5 * fl / (dkv + dq) / 1e9,
+                        fwd_frac=fl / fwd / 1e9 / tf_peak, of=tag))
+    print(results[-1], flush=True)
+    del q, k, v, d_o, out
+
+
 def bench_flash_bwd(results):
   tf_peak, _, tag = peaks()
   for B, H, Sq, Skv in [(1, 40, 4096, 4096), (1, 40, 8192, 8192), (1, 40, 32760, 32760)]:
@@ -171,6 +194,8 @@ def main(argv):
     bench_flash(results)
   if "flash_bwd" in which:
     bench_flash_bwd(results)
+  if "flash_d64" in which:
+    bench_flash_d64(results)
   if "rowwise" in which:
     bench_rowwise(results)
   if "--json" in argv:

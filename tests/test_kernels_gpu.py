@@ -66,16 +66,17 @@ def test_gemm_large_persistent():
   _report("gemm 4095x5120x5120", out, want)
 
 
+@pytest.mark.parametrize("D", [128, 64])
 @pytest.mark.parametrize("B,H,Sq,Skv", [(1, 2, 128, 128), (1, 2, 256, 384), (2, 3, 300, 200), (1, 4, 1000, 1111),
                                          (1, 2, 77, 512)])
-def test_flash_fwd(B, H, Sq, Skv):
+def test_flash_fwd(B, H, Sq, Skv, D):
   torch.manual_seed(3)
-  q = torch.randn((B, Sq, H, 128), device=DEV, dtype=torch.bfloat16)
-  k = torch.randn((B, Skv, H, 128), device=DEV, dtype=torch.bfloat16)
-  v = torch.randn((B, Skv, H, 128), device=DEV, dtype=torch.bfloat16)
+  q = torch.randn((B, Sq, H, D), device=DEV, dtype=torch.bfloat16)
+  k = torch.randn((B, Skv, H, D), device=DEV, dtype=torch.bfloat16)
+  v = torch.randn((B, Skv, H, D), device=DEV, dtype=torch.bfloat16)
   out, lse = K.flash_fwd(q, k, v)
   want, want_lse = ref.attention(q, k, v, return_lse=True)
-  _report(f"flash_fwd B{B} H{H} Sq{Sq} Skv{Skv}", out, want.float(), rel_tol=2e-2, abs_frac=5e-2)
+  _report(f"flash_fwd D{D} B{B} H{H} Sq{Sq} Skv{Skv}", out, want.float(), rel_tol=2e-2, abs_frac=5e-2)
   assert (lse - want_lse).abs().max().item() < 2e-2
 
 
@@ -107,14 +108,15 @@ def test_flash_fwd_large_magnitude():
   _report("flash_fwd large magnitude", out, want.float(), rel_tol=2e-2, abs_frac=5e-2)
 
 
+@pytest.mark.parametrize("D", [128, 64])
 @pytest.mark.parametrize("B,H,Sq,Skv", [(1, 2, 128, 128), (1, 2, 256, 192), (2, 3, 300, 200), (1, 2, 1000, 1111),
                                          (1, 2, 77, 512)])
-def test_flash_bwd(B, H, Sq, Skv):
+def test_flash_bwd(B, H, Sq, Skv, D):
   torch.manual_seed(11)
-  q = torch.randn((B, Sq, H, 128), device=DEV, dtype=torch.bfloat16)
-  k = torch.randn((B, Skv, H, 128), device=DEV, dtype=torch.bfloat16)
-  v = torch.randn((B, Skv, H, 128), device=DEV, dtype=torch.bfloat16)
-  d_o = torch.randn((B, Sq, H, 128), device=DEV, dtype=torch.bfloat16)
+  q = torch.randn((B, Sq, H, D), device=DEV, dtype=torch.bfloat16)
+  k = torch.randn((B, Skv, H, D), device=DEV, dtype=torch.bfloat16)
+  v = torch.randn((B, Skv, H, D), device=DEV, dtype=torch.bfloat16)
+  d_o = torch.randn((B, Sq, H, D), device=DEV, dtype=torch.bfloat16)
   out, lse = K.flash_fwd(q, k, v)
   delta = K.flash_delta(out, d_o)
   _report("flash_delta", delta, (out.float() * d_o.float()).sum(-1).permute(0, 2, 1), rel_tol=1e-3)
@@ -298,3 +300,21 @@ def test_fp8_linear_module_and_e5m2_backward():
     gx, gw = torch.autograd.grad(y, [x, base.weight], dy)
     assert _rel(y, want) < 6e-2 and _rel(gx, gx_want) < (0.2 if full else 2e-2) and _rel(gw, gw_want) < (0.2 if full else 2e-2)
   _lib.raise_on_device_status()
+
+
+def test_attention_head_dim_64_autograd_matches_reference():
+  """The differentiable op on SDXL-shaped heads (d = 64) against fp32 autograd of the reference."""
+  from maxdiffusion_b200.ops import functional as OF
+
+  torch.manual_seed(21)
+  B, S, H, D = 2, 1024, 10, 64
+  q, k, v = (torch.randn((B, S, H, D), device=DEV, dtype=torch.bfloat16, requires_grad=True) for _ in range(3))
+  g = torch.randn((B, S, H, D), device=DEV, dtype=torch.bfloat16)
+  out = OF.attention(q, k, v)
+  out.backward(g)
+  qf, kf, vf = (t.detach().float().requires_grad_(True) for t in (q, k, v))
+  want = ref.attention(qf, kf, vf)
+  want.backward(g.float())
+  _report("attention d64 out", out, want.float(), rel_tol=2e-2, abs_frac=5e-2)
+  for name, a, b in (("dq", q.grad, qf.grad), ("dk", k.grad, kf.grad), ("dv", v.grad, vf.grad)):
+    _report(f"attention d64 {name}", a, b, rel_tol=2e-2, abs_frac=5e-2)
