@@ -83,6 +83,23 @@ __global__ void peer_copy_kernel(const uint4* __restrict__ src, uint4* __restric
   }
 }
 
+// All-gather by pulls: dst[r * nvec + i] = srcs.p[r][i] for every rank r; blockIdx.y selects the source, so all
+// peers are read concurrently and every byte crosses NVLink once. 4 loads of 16 bytes in flight per thread.
+__global__ void __launch_bounds__(512) pull_gather_kernel(PeerFlagPtrs srcs, uint4* __restrict__ dst, long long nvec) {
+  const uint4* __restrict__ src = reinterpret_cast<const uint4*>(srcs.p[blockIdx.y]);
+  uint4* __restrict__ out = dst + static_cast<long long>(blockIdx.y) * nvec;
+  const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+  long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x;
+  for (; i + 3 * stride < nvec; i += 4 * stride) {
+    uint4 r[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) r[u] = __ldcg(src + i + u * stride);
+#pragma unroll
+    for (int u = 0; u < 4; ++u) out[i + u * stride] = r[u];
+  }
+  for (; i < nvec; i += stride) out[i] = __ldcg(src + i);
+}
+
 // Owner-side reduce of a reduce-scatter: out[i] = sum over ranks r (in rank order, fp32) of srcs.p[r][i], bf16 in and
 // out. srcs.p[r] is the address, in rank r's symmetric buffer, of the slice that belongs to this rank, so every byte
 // crosses NVLink once and the sum is rounded once. 16-byte loads, 4 ranks in flight per thread.
@@ -342,6 +359,23 @@ extern "C" int mdb_pull_reduce(const unsigned long long* src_ptrs, int world, vo
   }
   pull_reduce_kernel<<<ctas > 0 ? ctas : 64, 512, 0, static_cast<cudaStream_t>(stream)>>>(
       srcs, world, static_cast<uint4*>(out), n_elems >> 3);
+  return static_cast<int>(cudaGetLastError());
+}
+
+// src_ptrs: the address of every rank's shard (rank order, this rank's own included); nbytes per shard, a multiple of
+// 16. The caller has waited for the owners' ready flags on this stream.
+extern "C" int mdb_pull_gather(const unsigned long long* src_ptrs, int world, void* dst, long long nbytes, int ctas,
+                               void* stream) {
+  if (world < 1 || world > MAX_RANKS) return 3420;
+  if (nbytes & 15) return 3421;
+  if (nbytes == 0) return 0;
+  PeerFlagPtrs srcs;
+  for (int r = 0; r < world; ++r) {
+    if (src_ptrs[r] & 15) return 3422;
+    srcs.p[r] = reinterpret_cast<unsigned int*>(src_ptrs[r]);
+  }
+  dim3 grid(ctas > 0 ? ctas : 16, world);
+  pull_gather_kernel<<<grid, 512, 0, static_cast<cudaStream_t>(stream)>>>(srcs, static_cast<uint4*>(dst), nbytes >> 4);
   return static_cast<int>(cudaGetLastError());
 }
 

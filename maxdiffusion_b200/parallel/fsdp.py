@@ -171,6 +171,19 @@ class FSDPEngine:
           self.grad_slots = self.sym_grad
           self.rs_scratch = torch.empty(2 * 64, dtype=torch.float32, device=self.device)
           self.grad_epoch = 0
+          # the owner shards move into one symmetric buffer so that peers can pull them: the parameter all-gather
+          # of a block is then one kernel of this repository (`symm.pull_gather`) instead of an NCCL collective
+          offs, total = [], 0
+          for sh in self.shards:
+            offs.append(total)
+            total += -(-sh.numel() // 8) * 8
+          sym, ptrs, _h = self.peer.alloc(total, param_dtype)
+          for k, sh in enumerate(self.shards):
+            view = sym[offs[k]:offs[k] + sh.numel()]
+            view.copy_(sh)
+            self.shards[k] = view
+          self.sym_shards, self.shard_ptrs, self.shard_offs = sym, ptrs, offs
+          self.shards_version = 0  # optimizer steps whose updates are complete in `sym_shards`
           torch.cuda.synchronize()
           dist.barrier(group=group)
       self.comm_stream = torch.cuda.Stream() if self.on_cuda else None
@@ -195,7 +208,15 @@ class FSDPEngine:
       ready.record()  # everything enqueued so far (the previous user of this slot included)
       with torch.cuda.stream(self.comm_stream):
         self.comm_stream.wait_event(ready)
-        dist.all_gather_into_tensor(full, self.shards[i], group=self.group)
+        if self.peer is not None:
+          from . import symm
+
+          # every owner has finished the optimizer step that this gather must see (the flag carries its step count)
+          self.peer.wait(symm.FLAG_SHARD_READY, self.shards_version)
+          esz = self.shards[i].element_size()
+          symm.pull_gather([p + self.shard_offs[i] * esz for p in self.shard_ptrs], full, g.shard_numel * esz, ctas=12)
+        else:
+          dist.all_gather_into_tensor(full, self.shards[i], group=self.group)
         done = torch.cuda.Event()
         done.record()
       self.gather_done[slot] = done
@@ -376,6 +397,13 @@ class FSDPEngine:
         self._adamw(self.shards[i], sg, self.m[i], self.v[i], scale, i)
       self.pending.clear()
     self._adamw(self.root_flat, root_grad, self.root_m, self.root_v, scale, 7919)
+    if self.world > 1 and self.peer is not None:
+      # every shard of this rank now holds the weights of step `step_count`: peers may gather them. (A peer cannot
+      # still be reading the old values: it published its gradient of a block only after its last use of the block.)
+      from . import symm
+
+      self.shards_version = self.step_count
+      self.peer.signal(symm.FLAG_SHARD_READY, self.shards_version)
     return {"grad_norm": grad_norm, "max_abs_grad": max_abs}
 
   # ------------------------------------------------------------------ state access
@@ -407,6 +435,10 @@ class FSDPEngine:
     else:
       self.shards[i].copy_(flat[self.rank * g.shard_numel:(self.rank + 1) * g.shard_numel])
       self.slot_block = [-1, -1]
+      if self.peer is not None:
+        # peers pull this shard without a collective: it has to be complete before any of them gathers it
+        torch.cuda.synchronize()
+        dist.barrier(group=self.group)
 
   def optimizer_state(self) -> dict:
     return {"step": self.step_count, "m": self.m, "v": self.v, "root_m": self.root_m, "root_v": self.root_v}

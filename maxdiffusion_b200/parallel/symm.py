@@ -55,6 +55,8 @@ def _declare(L):
   L.mdb_small_allreduce.restype = c_int
   L.mdb_pull_reduce.argtypes = [ullp, c_int, c_void_p, c_ll, c_int, c_void_p]
   L.mdb_pull_reduce.restype = c_int
+  L.mdb_pull_gather.argtypes = [ullp, c_int, c_void_p, c_ll, c_int, c_void_p]
+  L.mdb_pull_gather.restype = c_int
 
 
 _lib.register(_declare)
@@ -259,6 +261,14 @@ class PeerKVExchange:
       peer_copy(base + self.numel * self.elem, vg[i + 1], nbytes, ctas=32)
     self.peer.signal(FLAG_KV_ACK, e)
     return kg, vg
+
+
+def pull_gather(src_ptrs: Sequence[int], dst: torch.Tensor, nbytes_per_rank: int, ctas: int = 16, stream=None) -> None:
+  """dst = concatenation over ranks of the `nbytes_per_rank` bytes at src_ptrs[r] (peer addresses), one kernel."""
+  arr = (ctypes.c_ulonglong * len(src_ptrs))(*src_ptrs)
+  rc = _lib.lib().mdb_pull_gather(arr, len(src_ptrs), _lib.ptr(dst), int(nbytes_per_rank), ctas,
+                                  stream if stream is not None else _lib.stream())
+  _lib.check(rc, "mdb_pull_gather")
 
 
 class PeerReduceScatter:

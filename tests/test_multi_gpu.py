@@ -51,6 +51,7 @@ def _entry(rank, world, port, fn, args, q):
     dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
     out = fn(rank, world, *args)
     torch.cuda.synchronize()
+    dist.barrier()  # peers may still be pulling from this rank's symmetric buffers: leave together
     from maxdiffusion_b200.ops import _lib
 
     _lib.raise_on_device_status()
@@ -234,6 +235,8 @@ def _peer_reduce_scatter(rank, world):
     want = torch.empty(shape, device="cuda")
     dist.reduce_scatter_tensor(want, torch.stack([p.float() for p in parts]))
     errs.append(((got.float() - want).abs().max() / want.abs().max()).item())
+  torch.cuda.synchronize()
+  dist.barrier()  # a rank must not free its symmetric buffer while a peer's last pull is still reading it
   return errs
 
 
