@@ -100,6 +100,40 @@ __global__ void __launch_bounds__(512) pull_gather_kernel(PeerFlagPtrs srcs, uin
   for (; i < nvec; i += stride) out[i] = __ldcg(src + i);
 }
 
+// All-to-all by pulls with the layout change fused (the Ulysses exchange). For every source rank r (blockIdx.y) a
+// block of n_b x n_s rows of row_vecs 16-byte vectors is read from srcs.p[r] (row (b, s) at b * src_sb + s * src_ss)
+// and written to dst + r * dst_sr + b * dst_sb + s * dst_ss; all strides in 16-byte vectors. With the right strides
+// this is [B, S, H, D] -> [B, n S, H / n, D] (rows = the H / n heads this rank keeps) and its inverse, without the
+// permute + contiguous passes that a library all-to-all needs on both sides.
+__global__ void __launch_bounds__(512) pull_a2a_kernel(PeerFlagPtrs srcs, uint4* __restrict__ dst, int n_b, int n_s,
+                                                       int row_vecs, long long src_sb, long long src_ss,
+                                                       long long dst_sr, long long dst_sb, long long dst_ss) {
+  const uint4* __restrict__ src = reinterpret_cast<const uint4*>(srcs.p[blockIdx.y]);
+  uint4* __restrict__ out = dst + static_cast<long long>(blockIdx.y) * dst_sr;
+  const long long total = static_cast<long long>(n_b) * n_s * row_vecs;
+  const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total; i += 4 * stride) {
+    uint4 r[4];
+    long long d[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const long long j = i + u * stride;
+      if (j < total) {
+        const int v = static_cast<int>(j % row_vecs);
+        const long long row = j / row_vecs;
+        const int sidx = static_cast<int>(row % n_s);
+        const int b = static_cast<int>(row / n_s);
+        r[u] = __ldcg(src + b * src_sb + sidx * src_ss + v);
+        d[u] = b * dst_sb + sidx * dst_ss + v;
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      if (i + u * stride < total) out[d[u]] = r[u];
+    }
+  }
+}
+
 // Owner-side reduce of a reduce-scatter: out[i] = sum over ranks r (in rank order, fp32) of srcs.p[r][i], bf16 in and
 // out. srcs.p[r] is the address, in rank r's symmetric buffer, of the slice that belongs to this rank, so every byte
 // crosses NVLink once and the sum is rounded once. 16-byte loads, 4 ranks in flight per thread.
@@ -376,6 +410,25 @@ extern "C" int mdb_pull_gather(const unsigned long long* src_ptrs, int world, vo
   }
   dim3 grid(ctas > 0 ? ctas : 16, world);
   pull_gather_kernel<<<grid, 512, 0, static_cast<cudaStream_t>(stream)>>>(srcs, static_cast<uint4*>(dst), nbytes >> 4);
+  return static_cast<int>(cudaGetLastError());
+}
+
+// See pull_a2a_kernel; src_ptrs are peer addresses already offset to the first row this rank pulls.
+extern "C" int mdb_pull_a2a(const unsigned long long* src_ptrs, int world, void* dst, int n_b, int n_s, int row_bytes,
+                            long long src_sb_bytes, long long src_ss_bytes, long long dst_sr_bytes,
+                            long long dst_sb_bytes, long long dst_ss_bytes, int ctas, void* stream) {
+  if (world < 1 || world > MAX_RANKS) return 3430;
+  if ((row_bytes | src_sb_bytes | src_ss_bytes | dst_sr_bytes | dst_sb_bytes | dst_ss_bytes) & 15) return 3431;
+  if (n_b <= 0 || n_s <= 0 || row_bytes <= 0) return 0;
+  PeerFlagPtrs srcs;
+  for (int r = 0; r < world; ++r) {
+    if (src_ptrs[r] & 15) return 3432;
+    srcs.p[r] = reinterpret_cast<unsigned int*>(src_ptrs[r]);
+  }
+  dim3 grid(ctas > 0 ? ctas : 16, world);
+  pull_a2a_kernel<<<grid, 512, 0, static_cast<cudaStream_t>(stream)>>>(
+      srcs, static_cast<uint4*>(dst), n_b, n_s, row_bytes >> 4, src_sb_bytes >> 4, src_ss_bytes >> 4, dst_sr_bytes >> 4,
+      dst_sb_bytes >> 4, dst_ss_bytes >> 4);
   return static_cast<int>(cudaGetLastError());
 }
 

@@ -40,28 +40,36 @@ class _GatherSeq(torch.autograd.Function):
     return C.reduce_scatter_stack(g.contiguous(), ctx.group), None
 
 
+def _a2a(x, group, exch, to_seq: bool):
+  """One Ulysses exchange: over peer memory when an exchange object is given and the tensor qualifies, else NCCL."""
+  if exch is not None and exch.supports(x, exch.n) and x.numel() <= exch.numel:
+    x = x.contiguous()
+    return exch.heads_to_seq(x) if to_seq else exch.seq_to_heads(x)
+  return C.all_to_all_heads_to_seq(x, group) if to_seq else C.all_to_all_seq_to_heads(x, group)
+
+
 class _HeadsToSeq(torch.autograd.Function):
 
   @staticmethod
-  def forward(ctx, x, group):
-    ctx.group = group
-    return C.all_to_all_heads_to_seq(x, group)
+  def forward(ctx, x, group, exch=None):
+    ctx.group, ctx.exch = group, exch
+    return _a2a(x, group, exch, True)
 
   @staticmethod
   def backward(ctx, g):
-    return C.all_to_all_seq_to_heads(g.contiguous(), ctx.group), None
+    return _a2a(g.contiguous(), ctx.group, ctx.exch, False), None, None
 
 
 class _SeqToHeads(torch.autograd.Function):
 
   @staticmethod
-  def forward(ctx, x, group):
-    ctx.group = group
-    return C.all_to_all_seq_to_heads(x, group)
+  def forward(ctx, x, group, exch=None):
+    ctx.group, ctx.exch = group, exch
+    return _a2a(x, group, exch, False)
 
   @staticmethod
   def backward(ctx, g):
-    return C.all_to_all_heads_to_seq(g.contiguous(), ctx.group), None
+    return _a2a(g.contiguous(), ctx.group, ctx.exch, True), None, None
 
 
 class _SegmentAttentionFn(torch.autograd.Function):
@@ -151,6 +159,7 @@ class ContextParallel:
     self._exchanges: dict = {}
     self._peers: dict = {}
     self._reducers: dict = {}
+    self._a2as: dict = {}
     self.group = mesh.group("context")
     self.size = mesh.size("context")
     self.rank = mesh.index_in("context") if self.size > 1 else 0
@@ -178,6 +187,24 @@ class ContextParallel:
         self._peers[key] = symm.PeerGroup(group)
       ex = symm.PeerKVExchange(self._peers[key], k.numel(), k.dtype)
       self._exchanges[key] = ex
+    return ex
+
+  def _a2a_for(self, group, x):
+    """The peer-memory all-to-all of `group` (created on first use), or None for the NCCL path."""
+    if not self.peer_memory or group is None or not x.is_cuda:
+      return None
+    key = id(group)
+    ex = self._a2as.get(key, False)
+    if ex is False or (ex is not None and ex.numel < x.numel()):
+      from . import symm
+
+      if not symm.peer_memory_available(group):
+        self._a2as[key] = None
+        return None
+      if key not in self._peers:
+        self._peers[key] = symm.PeerGroup(group)
+      ex = symm.PeerAllToAll(self._peers[key], x.numel(), x.dtype)
+      self._a2as[key] = ex
     return ex
 
   def _reducer_for(self, group, k):
@@ -250,17 +277,19 @@ class ContextParallel:
       H = q.shape[2]
       if H % self.size != 0:
         raise ValueError(f"Ulysses needs heads ({H}) divisible by the context axis ({self.size})")
-      qh, kh, vh = (_HeadsToSeq.apply(t, self.group) for t in (q, k, v))
+      ex = self._a2a_for(self.group, q)
+      qh, kh, vh = (_HeadsToSeq.apply(t, self.group, ex) for t in (q, k, v))
       if self.full_len is not None and self.full_len < per * self.size:
         kh, vh = kh[:, :self.full_len], vh[:, :self.full_len]
       o = OF.attention(qh, kh, vh, scale)
-      return _SeqToHeads.apply(o, self.group)
+      return _SeqToHeads.apply(o, self.group, ex)
     if self.strategy == "usp":
       H = q.shape[2]
       U, R = self.ulysses_size, self.ring_size
       if H % U != 0:
         raise ValueError(f"ulysses_shards ({U}) must divide the number of heads ({H})")
-      qh, kh, vh = (_HeadsToSeq.apply(t, self.ulysses_group) for t in (q, k, v))
+      ex = self._a2a_for(self.ulysses_group, q)
+      qh, kh, vh = (_HeadsToSeq.apply(t, self.ulysses_group, ex) for t in (q, k, v))
       # after the exchange a rank holds U consecutive shards of the sequence: the ring segment r covers the
       # global tokens [r*U*per, (r+1)*U*per)
       seg = per * U
@@ -268,5 +297,5 @@ class ContextParallel:
       if self.full_len is not None:
         lens = [max(0, min(seg, self.full_len - r * seg)) for r in range(R)]
       o = self._segment_attention(qh, kh, vh, self.ring_group, R, lens, scale)
-      return _SeqToHeads.apply(o, self.ulysses_group)
+      return _SeqToHeads.apply(o, self.ulysses_group, ex)
     raise ValueError(f"unknown context strategy {self.strategy}")

@@ -30,7 +30,9 @@ FLAG_USER = 5
 FLAG_SMALL_AR = 6
 FLAG_RS_READY = 7
 FLAG_RS_ACK = 8
-NUM_FLAG_KINDS = 10
+FLAG_A2A_READY = 9
+FLAG_A2A_ACK = 10
+NUM_FLAG_KINDS = 12
 WAIT_BUDGET_S = 5.0
 
 
@@ -57,6 +59,8 @@ def _declare(L):
   L.mdb_pull_reduce.restype = c_int
   L.mdb_pull_gather.argtypes = [ullp, c_int, c_void_p, c_ll, c_int, c_void_p]
   L.mdb_pull_gather.restype = c_int
+  L.mdb_pull_a2a.argtypes = [ullp, c_int, c_void_p, c_int, c_int, c_int] + [c_ll] * 5 + [c_int, c_void_p]
+  L.mdb_pull_a2a.restype = c_int
 
 
 _lib.register(_declare)
@@ -269,6 +273,71 @@ def pull_gather(src_ptrs: Sequence[int], dst: torch.Tensor, nbytes_per_rank: int
   rc = _lib.lib().mdb_pull_gather(arr, len(src_ptrs), _lib.ptr(dst), int(nbytes_per_rank), ctas,
                                   stream if stream is not None else _lib.stream())
   _lib.check(rc, "mdb_pull_gather")
+
+
+class PeerAllToAll:
+  """The Ulysses exchanges over peer memory: [B, S, H, D] sequence-sharded <-> [B, n S, H / n, D] head-sharded.
+
+  A rank publishes its tensor in a symmetric slot and raises an epoch flag; every rank then pulls, with ONE kernel,
+  the rows it keeps from every peer straight into their final place (`pull_a2a` in csrc/comm.cu), so the layout change
+  rides on the transfer: no permute + contiguous pass before or after, every byte crosses NVLink once. An
+  acknowledge flag lets the two slots be reused without a barrier.
+  """
+
+  def __init__(self, peer: "PeerGroup", max_numel: int, dtype=torch.bfloat16):
+    self.peer, self.n, self.rank = peer, peer.world, peer.rank
+    self.numel = -(-max_numel // 8) * 8
+    self.dtype = dtype
+    self.elem = torch.tensor([], dtype=dtype).element_size()
+    self.slots, self.slot_ptrs = [], []
+    for _ in range(2):
+      t, ptrs, _h = peer.alloc(self.numel, dtype)
+      self.slots.append(t)
+      self.slot_ptrs.append(ptrs)
+    self.epoch = 0
+    torch.cuda.synchronize()
+    dist.barrier(group=peer.group)
+
+  @staticmethod
+  def supports(x: torch.Tensor, n: int) -> bool:
+    return x.is_cuda and x.dim() == 4 and x.dtype == torch.bfloat16 and (x.shape[-1] * x.element_size()) % 16 == 0
+
+  def _publish(self, x: torch.Tensor):
+    assert x.numel() <= self.numel and x.dtype == self.dtype
+    self.epoch += 1
+    e, slot = self.epoch, self.epoch % 2
+    self.peer.wait(FLAG_A2A_ACK, e - 2)  # every peer has pulled the previous content of this slot
+    self.slots[slot][:x.numel()].view(x.shape).copy_(x)
+    self.peer.signal(FLAG_A2A_READY, e)
+    self.peer.wait(FLAG_A2A_READY, e)
+    return e, slot
+
+  def _pull(self, slot, src_off_bytes, out, n_b, n_s, row_bytes, src_sb, src_ss, dst_sr, dst_sb, dst_ss, e):
+    arr = (ctypes.c_ulonglong * self.n)(*[self.slot_ptrs[slot][r] + src_off_bytes for r in range(self.n)])
+    rc = _lib.lib().mdb_pull_a2a(arr, self.n, _lib.ptr(out), n_b, n_s, row_bytes, src_sb, src_ss, dst_sr, dst_sb, dst_ss,
+                                 24, _lib.stream())
+    _lib.check(rc, "mdb_pull_a2a")
+    self.peer.signal(FLAG_A2A_ACK, e)
+    return out
+
+  def heads_to_seq(self, x: torch.Tensor) -> torch.Tensor:
+    """[B, S, H, D] (every rank: its S rows, all heads) -> [B, n S, H / n, D] (all rows, this rank's heads)."""
+    B, S, H, D = x.shape
+    n, hn, es = self.n, H // self.n, self.elem
+    e, slot = self._publish(x)
+    out = torch.empty((B, n * S, hn, D), dtype=x.dtype, device=x.device)
+    row = hn * D * es
+    return self._pull(slot, self.rank * row, out, B, S, row, S * H * D * es, H * D * es, S * row, n * S * row, row, e)
+
+  def seq_to_heads(self, x: torch.Tensor) -> torch.Tensor:
+    """[B, n S, H / n, D] (all rows, this rank's heads) -> [B, S, H, D] (this rank's rows, all heads)."""
+    B, Sf, hn, D = x.shape
+    n, es = self.n, self.elem
+    S, H = Sf // n, hn * n
+    e, slot = self._publish(x)
+    out = torch.empty((B, S, H, D), dtype=x.dtype, device=x.device)
+    row = hn * D * es
+    return self._pull(slot, self.rank * S * row, out, B, S, row, Sf * row, row, row, S * H * D * es, H * D * es, e)
 
 
 class PeerReduceScatter:

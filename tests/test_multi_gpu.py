@@ -247,3 +247,30 @@ def test_peer_reduce_scatter_matches_fp32_sum():
   res = _spawn(_peer_reduce_scatter, 2)
   for errs in res:
     assert max(errs) < 1e-2, errs  # one bf16 rounding of an fp32 sum
+
+
+def _peer_all_to_all(rank, world):
+  import torch.distributed as dist
+
+  from maxdiffusion_b200.parallel import collectives as C
+  from maxdiffusion_b200.parallel import symm
+
+  peer = symm.PeerGroup(dist.group.WORLD)
+  ex = symm.PeerAllToAll(peer, 2 * 160 * 4 * world * 128)
+  same = []
+  for it in range(5):  # more epochs than slots
+    torch.manual_seed(10 * it + rank)
+    B, S, H, D = 1 + it % 2, 32 * (it + 1) - 3, 4 * world, 128
+    x = torch.randn((B, S, H, D), device="cuda").to(torch.bfloat16)
+    a = ex.heads_to_seq(x)
+    want = C.all_to_all_heads_to_seq(x, dist.group.WORLD)
+    back = ex.seq_to_heads(a)
+    same.append((torch.equal(a, want), torch.equal(back, x)))
+  return same
+
+
+def test_peer_all_to_all_equals_nccl_and_round_trips():
+  if torch.cuda.device_count() < 2:
+    pytest.skip("needs 2 GPUs")
+  for res in _spawn(_peer_all_to_all, 2):
+    assert all(a and b for a, b in res), res
