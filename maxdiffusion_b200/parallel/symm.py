@@ -320,24 +320,36 @@ class PeerAllToAll:
     self.peer.signal(FLAG_A2A_ACK, e)
     return out
 
+  @staticmethod
+  def pull_spec(kind: str, shape, n: int, rank: int, es: int) -> dict:
+    """The byte strides of one exchange as the pull kernel takes them (`pull_a2a_kernel`), for a rank of an
+    n-rank group; `kind` is 'heads_to_seq' ([B,S,H,D] -> [B,nS,H/n,D]) or 'seq_to_heads' (the inverse)."""
+    if kind == "heads_to_seq":
+      B, S, H, D = shape
+      hn = H // n
+      row = hn * D * es
+      return dict(out_shape=(B, n * S, hn, D), src_off=rank * row, n_b=B, n_s=S, row=row, src_sb=S * H * D * es,
+                  src_ss=H * D * es, dst_sr=S * row, dst_sb=n * S * row, dst_ss=row)
+    B, Sf, hn, D = shape
+    S, H = Sf // n, hn * n
+    row = hn * D * es
+    return dict(out_shape=(B, S, H, D), src_off=rank * S * row, n_b=B, n_s=S, row=row, src_sb=Sf * row, src_ss=row,
+                dst_sr=row, dst_sb=S * H * D * es, dst_ss=H * D * es)
+
+  def _exchange(self, kind: str, x: torch.Tensor) -> torch.Tensor:
+    sp = self.pull_spec(kind, tuple(x.shape), self.n, self.rank, self.elem)
+    e, slot = self._publish(x)
+    out = torch.empty(sp["out_shape"], dtype=x.dtype, device=x.device)
+    return self._pull(slot, sp["src_off"], out, sp["n_b"], sp["n_s"], sp["row"], sp["src_sb"], sp["src_ss"], sp["dst_sr"],
+                      sp["dst_sb"], sp["dst_ss"], e)
+
   def heads_to_seq(self, x: torch.Tensor) -> torch.Tensor:
     """[B, S, H, D] (every rank: its S rows, all heads) -> [B, n S, H / n, D] (all rows, this rank's heads)."""
-    B, S, H, D = x.shape
-    n, hn, es = self.n, H // self.n, self.elem
-    e, slot = self._publish(x)
-    out = torch.empty((B, n * S, hn, D), dtype=x.dtype, device=x.device)
-    row = hn * D * es
-    return self._pull(slot, self.rank * row, out, B, S, row, S * H * D * es, H * D * es, S * row, n * S * row, row, e)
+    return self._exchange("heads_to_seq", x)
 
   def seq_to_heads(self, x: torch.Tensor) -> torch.Tensor:
     """[B, n S, H / n, D] (all rows, this rank's heads) -> [B, S, H, D] (this rank's rows, all heads)."""
-    B, Sf, hn, D = x.shape
-    n, es = self.n, self.elem
-    S, H = Sf // n, hn * n
-    e, slot = self._publish(x)
-    out = torch.empty((B, S, H, D), dtype=x.dtype, device=x.device)
-    row = hn * D * es
-    return self._pull(slot, self.rank * S * row, out, B, S, row, Sf * row, row, row, S * H * D * es, H * D * es, e)
+    return self._exchange("seq_to_heads", x)
 
 
 class PeerReduceScatter:

@@ -81,3 +81,39 @@ def _collectives(rank, world):
 
 def test_collective_round_trips():
   assert all(run_ranks(_collectives, 2))
+
+
+def test_pull_all_to_all_strides_match_the_collective_semantics():
+  """Index arithmetic of the peer-memory Ulysses exchange, emulated on the CPU: for every rank, pulling rows with the
+  strides of `PeerAllToAll.pull_spec` from every rank's published tensor must give what all_to_all gives."""
+  import numpy as np
+  import torch
+
+  from maxdiffusion_b200.parallel.symm import PeerAllToAll
+
+  def emulate(kind, xs, rank):
+    n, es = len(xs), 2
+    sp = PeerAllToAll.pull_spec(kind, tuple(xs[0].shape), n, rank, es)
+    out = np.zeros(int(np.prod(sp["out_shape"])) * es, dtype=np.uint8)
+    for r in range(n):
+      src = xs[r].view(torch.int16).numpy().view(np.uint8).reshape(-1)
+      for b in range(sp["n_b"]):
+        for s in range(sp["n_s"]):
+          so = sp["src_off"] + b * sp["src_sb"] + s * sp["src_ss"]
+          do = r * sp["dst_sr"] + b * sp["dst_sb"] + s * sp["dst_ss"]
+          out[do:do + sp["row"]] = src[so:so + sp["row"]]
+    return torch.from_numpy(out.view(np.int16)).view(torch.bfloat16).reshape(sp["out_shape"])
+
+  n, B, S, hn, D = 3, 2, 5, 2, 8
+  H = hn * n
+  torch.manual_seed(0)
+  xs = [torch.randn(B, S, H, D).to(torch.bfloat16) for _ in range(n)]
+  head_sharded = []
+  for me in range(n):
+    got = emulate("heads_to_seq", xs, me)
+    want = torch.cat([x[:, :, me * hn:(me + 1) * hn] for x in xs], dim=1)  # all rows, my heads
+    assert torch.equal(got, want)
+    head_sharded.append(got)
+  for me in range(n):
+    back = emulate("seq_to_heads", head_sharded, me)
+    assert torch.equal(back, xs[me])
