@@ -79,10 +79,13 @@ flash_bwd_kernel(const __grid_constant__ Maps maps, const Params p) {
   uint64_t* x_full = bars;          // [1]
   uint64_t* y_full = bars + 1;                      // [Y_STAGES]
   uint64_t* y_empty = y_full + Y_STAGES;            // [Y_STAGES]
-  uint64_t* t_full = y_empty + Y_STAGES;            // [NBUF]
-  uint64_t* ps_full = t_full + NBUF;                // [NBUF]
-  uint64_t* t_free = ps_full + NBUF;                // [NBUF] accumulating products that read the score buffers completed
-  uint64_t* acc_final = t_free + NBUF;              // [1]
+  uint64_t* t1_full = y_empty + Y_STAGES;           // [NBUF] first score tile (S) written
+  uint64_t* t2_full = t1_full + NBUF;               // [NBUF] second score tile (dP) written
+  uint64_t* p_ready = t2_full + NBUF;               // [NBUF] DKV: P^T stored over the first tile
+  uint64_t* ds_ready = p_ready + NBUF;              // [NBUF] dS stored over the second tile
+  uint64_t* t1_free = ds_ready + NBUF;              // [NBUF] first tile may be overwritten (DKV: dV product done; DQ: loaded)
+  uint64_t* t2_free = t1_free + NBUF;               // [NBUF] second tile may be overwritten (dK / dQ product done)
+  uint64_t* acc_final = t2_free + NBUF;             // [1]
   uint32_t* tmem_ptr_smem = reinterpret_cast<uint32_t*>(acc_final + 1);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_ptr_smem + 1);
 
@@ -102,9 +105,12 @@ flash_bwd_kernel(const __grid_constant__ Maps maps, const Params p) {
       mbar_init(&y_empty[i], 1);
     }
     for (int i = 0; i < NBUF; ++i) {
-      mbar_init(&t_full[i], 2);  // both score products
-      mbar_init(&t_free[i], 1);
-      mbar_init(&ps_full[i], EW_GROUPS * 4);  // one elected lane per elementwise warp
+      mbar_init(&t1_full[i], 1);
+      mbar_init(&t2_full[i], 1);
+      mbar_init(&p_ready[i], EW_GROUPS * 4);   // one elected lane per elementwise warp
+      mbar_init(&ds_ready[i], EW_GROUPS * 4);
+      mbar_init(&t1_free[i], DKV ? 1 : EW_GROUPS * 4);
+      mbar_init(&t2_free[i], 1);
     }
     mbar_init(acc_final, 1);
     *abort_flag = 0;
@@ -195,8 +201,9 @@ flash_bwd_kernel(const __grid_constant__ Maps maps, const Params p) {
         const int b = i % NBUF, use = i / NBUF;
         const uint64_t yd = ys0 + stage * STAGE_STEP;
         if (!mbar_wait(&y_full[stage], phase, abort_flag, p.status, 81)) { ok = false; break; }
-        // the score buffers of step i were last read by the accumulating products of step i - NBUF
-        if (use > 0 && !mbar_wait(&t_free[b], (use - 1) & 1, abort_flag, p.status, 82)) { ok = false; break; }
+        // the buffer was last used by step i - NBUF: its reader (a product, or in the DQ pass the elementwise load of
+        // the first tile) must be done
+        if (use > 0 && !mbar_wait(second ? &t2_free[b] : &t1_free[b], (use - 1) & 1, abort_flag, p.status, 82)) { ok = false; break; }
         tc_fence_after_sync();
 #pragma unroll
         for (int k = 0; k < D / 16; ++k) {
@@ -204,7 +211,7 @@ flash_bwd_kernel(const __grid_constant__ Maps maps, const Params p) {
           const uint32_t yo = ((k >> 2) * Y_CHUNK_BYTES + (k & 3) * 32) >> 4;
           umma_ss(tcol + b * 64, xd + xo, yd + yo, idesc_t, k > 0 ? 1u : 0u);
         }
-        umma_commit(&t_full[b]);
+        umma_commit(second ? &t2_full[b] : &t1_full[b]);
         if (++stage == Y_STAGES) { stage = 0; phase ^= 1u; }
       }
     }
@@ -219,20 +226,22 @@ flash_bwd_kernel(const __grid_constant__ Maps maps, const Params p) {
       for (int i = 0; i < total_steps && ok; ++i) {
         const int b = i % NBUF, use = i / NBUF;
         const uint64_t y1d = ym0 + stage * STAGE_STEP, y2d = y1d + TILE_STEP;
-        if (!mbar_wait(&ps_full[b], use & 1, abort_flag, p.status, 83)) { ok = false; break; }
+        if (DKV) {
+          // dV += P^T dO_i as soon as P^T is stored; the first score tile is free afterwards
+          if (!mbar_wait(&p_ready[b], use & 1, abort_flag, p.status, 83)) { ok = false; break; }
+          tc_fence_after_sync();
+#pragma unroll
+          for (int k = 0; k < BY / 16; ++k)  // packed bf16 columns of K-step k were written by column group k
+            umma_ts(tmem_base + ACC, tmem_base + b * 64 + k * 16, y2d + k * (2048 >> 4), idesc_acc, (i > 0 || k > 0) ? 1u : 0u);
+          umma_commit(&t1_free[b]);
+        }
+        if (!mbar_wait(&ds_ready[b], use & 1, abort_flag, p.status, 84)) { ok = false; break; }
         tc_fence_after_sync();
 #pragma unroll
-        for (int k = 0; k < BY / 16; ++k) {
-          const uint32_t acol = k * 16;  // packed bf16 columns of this K-step (written by column group k)
-          const uint32_t accum = (i > 0 || k > 0) ? 1u : 0u;
-          if (DKV) {
-            umma_ts(tmem_base + ACC, tmem_base + b * 64 + acol, y2d + k * (2048 >> 4), idesc_acc, accum);        // dV += P^T dO_i
-            umma_ts(tmem_base + ACC + 128, tmem_base + T2C + b * 64 + acol, y1d + k * (2048 >> 4), idesc_acc, accum);  // dK += dS^T Q_i
-          } else {
-            umma_ts(tmem_base + ACC, tmem_base + T2C + b * 64 + acol, y1d + k * (2048 >> 4), idesc_acc, accum);  // dQ += dS K_j
-          }
-        }
-        umma_commit(&t_free[b]);
+        for (int k = 0; k < BY / 16; ++k)  // DKV: dK += dS^T Q_i;  DQ: dQ += dS K_j
+          umma_ts(tmem_base + ACC + (DKV ? 128 : 0), tmem_base + T2C + b * 64 + k * 16, y1d + k * (2048 >> 4), idesc_acc,
+                  (i > 0 || k > 0) ? 1u : 0u);
+        umma_commit(&t2_free[b]);
         umma_commit(&y_empty[stage]);
         if (++stage == Y_STAGES) stage = 0;
       }
@@ -265,67 +274,99 @@ flash_bwd_kernel(const __grid_constant__ Maps maps, const Params p) {
           if (DKV) {
             if (!mbar_wait(&y_full[ystage], (i / Y_STAGES) & 1, abort_flag, p.status, 92)) { ok = false; break; }
           }
-          if (!mbar_wait(&t_full[b], use & 1, abort_flag, p.status, 90)) { ok = false; break; }
-          tc_fence_after_sync();
-          uint32_t t1[16], t2[16];
-          tmem_ld_x16(tmem_base + lane_off + b * 64 + wg * 16, t1);
-          tmem_ld_x16(tmem_base + lane_off + T2C + b * 64 + wg * 16, t2);
-          tmem_wait_ld();
-          uint32_t pp[8], ds[8];
           const bool full_tile = (valid == BY) && (x0 + BX <= p.x_len);  // uniform over the CTA
+          const uint32_t t1a = tmem_base + lane_off + b * 64 + wg * 16;
+          const uint32_t t2a = tmem_base + lane_off + T2C + b * 64 + wg * 16;
+          // ---- phase 1: P of this thread's 16 columns from the first score tile
+          if (!mbar_wait(&t1_full[b], use & 1, abort_flag, p.status, 90)) { ok = false; break; }
+          if (!DKV) {  // the DQ pass has nothing to hand over between the tiles: one phase, both tiles loaded at once
+            if (!mbar_wait(&t2_full[b], use & 1, abort_flag, p.status, 93)) { ok = false; break; }
+          }
+          tc_fence_after_sync();
+          uint32_t t1[16], t2[16], ds[8];
+          tmem_ld_x16(t1a, t1);
+          if (!DKV) tmem_ld_x16(t2a, t2);
+          tmem_wait_ld();
+          if (!DKV) {  // nothing else reads the first tile in the DQ pass: the next S may be multiplied into it
+            tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&t1_free[b]);
+          }
+          float pr[16];
           if (full_tile) {
             if (DKV) {
               const float4* lse4 = reinterpret_cast<const float4*>(st + wg * 16);
-              const float4* del4 = reinterpret_cast<const float4*>(st + 64 + wg * 16);
 #pragma unroll
               for (int c4 = 0; c4 < 4; ++c4) {
                 const float4 l = lse4[c4];
+                pr[4 * c4 + 0] = fast_exp2(__uint_as_float(t1[4 * c4 + 0]) * p.scale_log2 - l.x);
+                pr[4 * c4 + 1] = fast_exp2(__uint_as_float(t1[4 * c4 + 1]) * p.scale_log2 - l.y);
+                pr[4 * c4 + 2] = fast_exp2(__uint_as_float(t1[4 * c4 + 2]) * p.scale_log2 - l.z);
+                pr[4 * c4 + 3] = fast_exp2(__uint_as_float(t1[4 * c4 + 3]) * p.scale_log2 - l.w);
+              }
+            } else {
+#pragma unroll
+              for (int c = 0; c < 16; ++c) pr[c] = fast_exp2(__uint_as_float(t1[c]) * p.scale_log2 - lse_r);
+            }
+          } else {
+#pragma unroll
+            for (int c = 0; c < 16; ++c) {
+              const int col = wg * 16 + c;
+              const bool col_ok = col < valid;
+              const float lse = DKV ? (col_ok ? st[col] : 0.0f) : lse_r;
+              const float pe = fast_exp2(__uint_as_float(t1[c]) * p.scale_log2 - lse);
+              pr[c] = (row_ok && col_ok) ? pe : 0.0f;
+            }
+          }
+          if (DKV) {
+            uint32_t pp[8];
+#pragma unroll
+            for (int c = 0; c < 8; ++c) pp[c] = pack_bf16x2(pr[2 * c], pr[2 * c + 1]);
+            tmem_st_x8(t1a, pp);
+            tmem_wait_st();
+            tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&p_ready[b]);
+          }
+          // ---- phase 2: dS = P * (dP - delta) over the second score tile
+          if (DKV) {
+            if (!mbar_wait(&t2_full[b], use & 1, abort_flag, p.status, 93)) { ok = false; break; }
+            tc_fence_after_sync();
+            tmem_ld_x16(t2a, t2);
+            tmem_wait_ld();
+          }
+          if (DKV) {
+            if (full_tile) {
+              const float4* del4 = reinterpret_cast<const float4*>(st + 64 + wg * 16);
+#pragma unroll
+              for (int c4 = 0; c4 < 4; ++c4) {
                 const float4 d = del4[c4];
-                const float p0 = fast_exp2(__uint_as_float(t1[4 * c4 + 0]) * p.scale_log2 - l.x);
-                const float p1 = fast_exp2(__uint_as_float(t1[4 * c4 + 1]) * p.scale_log2 - l.y);
-                const float p2 = fast_exp2(__uint_as_float(t1[4 * c4 + 2]) * p.scale_log2 - l.z);
-                const float p3 = fast_exp2(__uint_as_float(t1[4 * c4 + 3]) * p.scale_log2 - l.w);
-                pp[2 * c4] = pack_bf16x2(p0, p1);
-                pp[2 * c4 + 1] = pack_bf16x2(p2, p3);
-                ds[2 * c4] = pack_bf16x2(p0 * (__uint_as_float(t2[4 * c4 + 0]) - d.x),
-                                         p1 * (__uint_as_float(t2[4 * c4 + 1]) - d.y));
-                ds[2 * c4 + 1] = pack_bf16x2(p2 * (__uint_as_float(t2[4 * c4 + 2]) - d.z),
-                                             p3 * (__uint_as_float(t2[4 * c4 + 3]) - d.w));
+                ds[2 * c4] = pack_bf16x2(pr[4 * c4 + 0] * (__uint_as_float(t2[4 * c4 + 0]) - d.x),
+                                         pr[4 * c4 + 1] * (__uint_as_float(t2[4 * c4 + 1]) - d.y));
+                ds[2 * c4 + 1] = pack_bf16x2(pr[4 * c4 + 2] * (__uint_as_float(t2[4 * c4 + 2]) - d.z),
+                                             pr[4 * c4 + 3] * (__uint_as_float(t2[4 * c4 + 3]) - d.w));
               }
             } else {
 #pragma unroll
               for (int c = 0; c < 8; ++c) {
-                const float p0 = fast_exp2(__uint_as_float(t1[2 * c]) * p.scale_log2 - lse_r);
-                const float p1 = fast_exp2(__uint_as_float(t1[2 * c + 1]) * p.scale_log2 - lse_r);
-                ds[c] = pack_bf16x2(p0 * (__uint_as_float(t2[2 * c]) - delta_r),
-                                    p1 * (__uint_as_float(t2[2 * c + 1]) - delta_r));
+                const int col = wg * 16 + 2 * c;
+                const float d0 = col < valid ? st[64 + col] : 0.0f;
+                const float d1 = col + 1 < valid ? st[64 + col + 1] : 0.0f;
+                ds[c] = pack_bf16x2(pr[2 * c] * (__uint_as_float(t2[2 * c]) - d0),
+                                    pr[2 * c + 1] * (__uint_as_float(t2[2 * c + 1]) - d1));
               }
             }
           } else {
 #pragma unroll
-            for (int c = 0; c < 8; ++c) {
-              float pv[2], dv[2];
-#pragma unroll
-              for (int h = 0; h < 2; ++h) {
-                const int col = wg * 16 + 2 * c + h;
-                const bool col_ok = col < valid;
-                const float lse = DKV ? (col_ok ? st[col] : 0.0f) : lse_r;
-                const float del = DKV ? (col_ok ? st[64 + col] : 0.0f) : delta_r;
-                float pe = fast_exp2(__uint_as_float(t1[2 * c + h]) * p.scale_log2 - lse);
-                if (!row_ok || col >= valid) pe = 0.0f;
-                pv[h] = pe;
-                dv[h] = pe * (__uint_as_float(t2[2 * c + h]) - del);
-              }
-              pp[c] = pack_bf16x2(pv[0], pv[1]);
-              ds[c] = pack_bf16x2(dv[0], dv[1]);
-            }
+            for (int c = 0; c < 8; ++c)
+              ds[c] = pack_bf16x2(pr[2 * c] * (__uint_as_float(t2[2 * c]) - delta_r),
+                                  pr[2 * c + 1] * (__uint_as_float(t2[2 * c + 1]) - delta_r));
           }
-          if (DKV) tmem_st_x8(tmem_base + lane_off + b * 64 + wg * 16, pp);
-          tmem_st_x8(tmem_base + lane_off + T2C + b * 64 + wg * 16, ds);
+          tmem_st_x8(t2a, ds);
           tmem_wait_st();
           tc_fence_before_sync();
           __syncwarp();
-          if (lane == 0) mbar_arrive(&ps_full[b]);
+          if (lane == 0) mbar_arrive(&ds_ready[b]);
         }
       }
       if (ok && mbar_wait(acc_final, 0, abort_flag, p.status, 91)) {
