@@ -264,3 +264,15 @@ def test_save_sd_checkpoint_example_and_eval_assert(tmp_path):
   assert subprocess.run([sys.executable, script, "final_loss", str(m), "0.01"], capture_output=True).returncode != 0
   assert subprocess.run([sys.executable, script, "avg_tflops", str(m), "600"]).returncode == 0
   assert subprocess.run([sys.executable, script, "avg_step_time", str(m), "0.4"], capture_output=True).returncode != 0
+
+
+def test_inference_bench_runs_on_tiny_presets(capsys):
+  import json
+
+  from maxdiffusion_b200.utils import inference_bench
+
+  assert inference_bench.main(["wan", "--preset", "tiny", "--height", "64", "--width", "64", "--frames", "5", "--steps", "2"]) == 0
+  assert inference_bench.main(["flux", "--preset", "tiny", "--resolution", "64", "--steps", "2"]) == 0
+  lines = [json.loads(l) for l in capsys.readouterr().out.splitlines() if l.startswith("{")]
+  assert lines[0]["unit"] == "s/step" and lines[0]["value"] > 0 and lines[0]["config"]["tokens"] == 32
+  assert lines[1]["unit"] == "images/s" and lines[1]["value"] > 0
