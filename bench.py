@@ -72,6 +72,17 @@ class ClockSampler:
             "reasons": sorted(self.reasons), "samples": len(self.samples)}
 
 
+def kept_block_bytes(cfg, tokens: int, ranks: int = 1) -> int:
+  """Activation bytes a Wan block holds for its backward when it is not rematerialised (bf16): the residual stream
+  and its three modulated norms, q / k / v before and after RMSNorm + RoPE, the attention output and its projection,
+  the cross-attention query, output and projection, the two FFN hidden tensors, plus fp32 softmax statistics."""
+  d, f = cfg.dim, cfg.ffn_dim
+  per_token = 2 * (4 * d + 3 * d + 3 * d + 2 * d + 3 * d + 2 * f) + 16 * cfg.num_attention_heads
+  if ranks > 1:  # ring attention keeps the gathered K and V of all ranks for its backward
+    per_token += 2 * 2 * ranks * d
+  return int(1.15 * per_token * tokens)
+
+
 def main() -> int:
   ap = argparse.ArgumentParser()
   ap.add_argument("--gpus", type=int, default=1)
@@ -79,6 +90,8 @@ def main() -> int:
   ap.add_argument("--warmup", type=int, default=3)
   ap.add_argument("--impl", default="ours")
   ap.add_argument("--remat", default="SAVE_ATTENTION", help="FULL | SAVE_ATTENTION")
+  ap.add_argument("--keep-blocks", type=int, default=-1,
+                  help="blocks that keep their activations instead of recomputing them (-1: as many as the memory of the GPU allows)")
   ap.add_argument("--preset", default="wan2.1-t2v-14b", help="model preset (anything but the default is a smoke run)")
   ap.add_argument("--height", type=int, default=480)
   ap.add_argument("--width", type=int, default=832)
@@ -109,6 +122,7 @@ def main() -> int:
       ["bench", os.path.join(here, "maxdiffusion_b200", "configs", "base_wan_14b.yml"), "run_name=bench",
        f"height={args.height}", f"width={args.width}", f"num_frames={args.frames}", "dataset_type=synthetic",
        f"per_device_batch_size={1.0 / n}", f"attention={args.attention}", f"remat_policy={args.remat}",
+       f"remat_keep_blocks={max(0, args.keep_blocks)}",
        f"wan_preset={args.preset}", "warmup_steps_fraction=0.0", "max_train_steps=1000000", "log_config=false",
        "write_metrics=false", "flow_shift=5.0"])
   mesh = create_device_mesh(config)
@@ -120,6 +134,23 @@ def main() -> int:
     if world > 1:
       dist.barrier()
     torch.cuda.synchronize()
+
+  # ---- how many blocks may keep their activations: one probing step with full remat, then the memory that is left
+  # over (minus a reserve) is divided by what a kept block holds. Every rank takes the minimum.
+  keep = max(0, args.keep_blocks)
+  if args.keep_blocks < 0:
+    m = trainer.train_step(next(data))
+    float(m["learning/loss"])
+    torch.cuda.synchronize()
+    free, total = torch.cuda.mem_get_info()
+    peak = torch.cuda.max_memory_reserved()
+    per_block = kept_block_bytes(trainer.model.cfg, -(-seq_len // n), n)
+    room = total - peak - int(0.08 * total)
+    keep_t = torch.tensor([max(0, min(len(trainer.model.blocks), room // per_block))], device="cuda")
+    if world > 1:
+      dist.all_reduce(keep_t, op=dist.ReduceOp.MIN)
+    keep = int(keep_t.item())
+    trainer.model.remat_keep_blocks = keep
 
   # ---- warm-up (through the public path)
   for _ in range(args.warmup):
@@ -173,7 +204,9 @@ def main() -> int:
         "config": {"model": "Wan2.1-T2V-14B (40 layers, dim 5120, 40 heads, ffn 13824), random init" if official else args.preset,
                    "global_batch": 1, "seq_len": seq_len,
                    "parallelism": f"cp{n} ring x fsdp over the same {n} ranks" if n > 1 else "single GPU",
-                   "video": f"{args.height}x{args.width}x{args.frames}", "remat": f"per block ({args.remat})",
+                   "video": f"{args.height}x{args.width}x{args.frames}",
+                   "remat": f"per block ({args.remat}); the last {keep} of {len(trainer.model.blocks)} blocks keep their activations "
+                            f"(peak {torch.cuda.max_memory_reserved() / 2**30:.0f} GiB reserved)",
                    "optimizer": "AdamW, bf16 moments, stochastic rounding, step inside the timed region",
                    "l2": "inputs larger than L2 (activations and weights of every block exceed 126 MB)",
                    "baseline_note": "BASELINE.md P2': 2100 tokens/s on TPU v5p-8 at 720p (75 600 tokens)"},

@@ -348,12 +348,23 @@ class WanModel(nn.Module):
     """`hints` {block index: tensor} are added to the stream after that block (VACE); `block_post(i, x)` may
     transform the stream after block i (Wan-Animate face adapter)."""
     policy = self.remat_policy.upper() if torch.is_grad_enabled() else "NONE"
+    # the last `remat_keep_blocks` blocks keep their activations instead of recomputing them (memory permitting)
+    first_kept = len(self.blocks) - int(getattr(self, "remat_keep_blocks", 0) or 0)
     for i, blk in enumerate(self.blocks):
       if self.block_hook is not None:
         self.block_hook(i, "forward")
       layer_kv = kv_cache[i] if kv_cache is not None else None
       if policy == "NONE":
         x = blk(x, context, temb6, rope, pctx, context_image, layer_kv)
+      elif i >= first_kept:
+        def run_keep(x_, context_, temb6_, blk=blk, layer_kv=layer_kv):
+          return blk(x_, context_, temb6_, rope, pctx, context_image, layer_kv)
+
+        pre = done = None
+        if self.block_hook is not None:
+          pre = (lambda idx=i: self.block_hook(idx, "recompute"))
+          done = (lambda idx=i: self.block_hook(idx, "backward_done"))
+        x = OF.keep_block(run_keep, x, context, temb6, pre_backward=pre, on_backward_done=done)
       else:
         def run(x_, context_, temb6_, blk=blk, layer_kv=layer_kv, idx=i):
           if self.block_hook is not None and torch.is_grad_enabled():

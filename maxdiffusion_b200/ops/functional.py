@@ -374,6 +374,41 @@ class _CheckpointFn(torch.autograd.Function):
     return (None, None, None, None, *grads, *([None] * len(ctx.rest)))
 
 
+class _KeepGraphFn(torch.autograd.Function):
+  """A block whose activations are kept (no recomputation) but whose backward still runs as one unit, so that the
+  same hooks as for a rematerialised block fire: `pre_backward()` before it (the FSDP engine gathers the block's
+  weights again) and `on_backward_done()` once its parameter gradients are complete."""
+
+  @staticmethod
+  def forward(ctx, fn, pre_backward, on_backward_done, n_tensors, *args):
+    tensors, rest = args[:n_tensors], args[n_tensors:]
+    inputs = [t.detach().requires_grad_(True) if (t is not None and t.is_floating_point()) else t for t in tensors]
+    with torch.enable_grad():
+      out = fn(*inputs, *rest)
+    ctx.inputs, ctx.out = inputs, out
+    ctx.pre_backward, ctx.on_backward_done, ctx.n_rest = pre_backward, on_backward_done, len(rest)
+    if isinstance(out, tuple):
+      return tuple(o.detach() for o in out)
+    return out.detach()
+
+  @staticmethod
+  def backward(ctx, *douts):
+    if ctx.pre_backward is not None:
+      ctx.pre_backward()
+    outs = ctx.out if isinstance(ctx.out, tuple) else (ctx.out,)
+    torch.autograd.backward([o for o in outs if o.requires_grad], [g for o, g in zip(outs, douts) if o.requires_grad])
+    grads = [t.grad if (t is not None and t.is_floating_point()) else None for t in ctx.inputs]
+    ctx.out, ctx.inputs = None, None
+    if ctx.on_backward_done is not None:
+      ctx.on_backward_done()
+    return (None, None, None, None, *grads, *([None] * ctx.n_rest))
+
+
+def keep_block(fn, *tensor_args, extra_args: Sequence = (), pre_backward=None, on_backward_done=None):
+  """Runs `fn(*tensor_args, *extra_args)` keeping its activations; see `_KeepGraphFn`."""
+  return _KeepGraphFn.apply(fn, pre_backward, on_backward_done, len(tensor_args), *tensor_args, *extra_args)
+
+
 def checkpoint_block(fn, *tensor_args, extra_args: Sequence = (), save_attention: bool = False,
                      on_backward_done=None, offload_input: bool = False):
   """Runs `fn(*tensor_args, *extra_args)` storing only its tensor inputs; the backward pass recomputes it.

@@ -83,6 +83,7 @@ class WanTrainer:
     else:
       model = model.to(device=self.device, dtype=self.dtype)
       model.remat_policy = remat
+    model.remat_keep_blocks = int(config.get("remat_keep_blocks", 0) or 0)
     self.model = model
 
     opt = AdamWConfig(

@@ -12,7 +12,7 @@ CFG = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), 
 TINY = '{"num_attention_heads": 4, "attention_head_dim": 32, "ffn_dim": 96, "num_layers": 2, "text_dim": 48, "freq_dim": 32}'
 
 
-def _make_trainer(attention, world):
+def _make_trainer(attention, world, keep=0):
   from maxdiffusion_b200 import pyconfig
   from maxdiffusion_b200.parallel.mesh import create_device_mesh
   from maxdiffusion_b200.trainers.wan_trainer import WanTrainer
@@ -21,13 +21,14 @@ def _make_trainer(attention, world):
       ["t", CFG, "run_name=t", "height=64", "width=48", "num_frames=9", "dataset_type=synthetic", "wan_preset=tiny",
        f"wan_config_overrides={TINY}", "remat_policy=FULL", "warmup_steps_fraction=0.0", "log_config=false",
        "write_metrics=false", "learning_rate=1e-3", f"attention={attention}", f"per_device_batch_size={1.0 / world}",
-       "synthetic_override_text_dim=48", "max_sequence_length=16", "ulysses_shards=2"], unittest=True)
+       "synthetic_override_text_dim=48", "max_sequence_length=16", "ulysses_shards=2", f"remat_keep_blocks={keep}"],
+      unittest=True)
   return WanTrainer(config, mesh=create_device_mesh(config), device="cpu")
 
 
-def _train(rank, world, attention, steps):
+def _train(rank, world, attention, steps, keep=0):
   torch.manual_seed(0)
-  tr = _make_trainer(attention, world)
+  tr = _make_trainer(attention, world, keep)
   data = tr.load_dataset()
   losses = []
   for _ in range(steps):
@@ -53,6 +54,15 @@ def test_two_rank_training_matches_single_process(attention):
   for losses, digest, gn in out:
     assert losses == pytest.approx(ref_losses, rel=2e-4, abs=1e-5)
     assert gn == pytest.approx(ref_gn, rel=2e-3)
+    for k, v in ref_digest.items():
+      assert digest[k] == pytest.approx(v, rel=1e-4, abs=1e-4), k
+
+
+def test_two_rank_training_with_kept_blocks_matches_single_process():
+  """A block that keeps its activations still gets its weights gathered again before its backward (FSDP, 2 ranks)."""
+  ref_losses, ref_digest, ref_gn = _train(0, 1, "flash", 2)
+  for losses, digest, gn in run_ranks(_train, 2, "tokamax_ring", 2, 1):
+    assert losses == pytest.approx(ref_losses, rel=2e-4, abs=1e-5)
     for k, v in ref_digest.items():
       assert digest[k] == pytest.approx(v, rel=1e-4, abs=1e-4), k
 

@@ -33,6 +33,53 @@ def test_checkpoint_block_gradients_match_plain_autograd():
   assert torch.allclose(gx, x.grad) and torch.allclose(gw, lin.weight.grad)
 
 
+def test_keep_block_runs_hooks_in_order_and_matches_plain_autograd():
+  torch.manual_seed(0)
+  lin = torch.nn.Linear(8, 8)
+  x = torch.randn(2, 3, 8, requires_grad=True)
+  fn = lambda t: torch.tanh(lin(t)) * 2
+  order = []
+
+  def done():
+    order.append(("done", lin.weight.grad is not None))  # parameter gradients are complete when the hook fires
+
+  y = OF.keep_block(fn, x * 1.0, pre_backward=lambda: order.append(("pre", lin.weight.grad is None)), on_backward_done=done)
+  assert y.requires_grad
+  y.sum().backward()
+  assert order == [("pre", True), ("done", True)]
+  gx, gw = x.grad.clone(), lin.weight.grad.clone()
+  x.grad, lin.weight.grad = None, None
+  fn(x).sum().backward()
+  assert torch.allclose(gx, x.grad) and torch.allclose(gw, lin.weight.grad)
+
+
+def test_wan_training_step_is_the_same_with_kept_blocks(tmp_path):
+  """`remat_keep_blocks` changes memory, not numbers: same loss and same updated weights after two steps."""
+  import os
+
+  from maxdiffusion_b200 import pyconfig
+  from maxdiffusion_b200.parallel.mesh import create_device_mesh
+  from maxdiffusion_b200.trainers.wan_trainer import WanTrainer
+
+  cfg_path = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "maxdiffusion_b200", "configs", "base_wan_14b.yml")
+
+  def run(keep):
+    config = pyconfig.initialize(["t", cfg_path, "run_name=t", "height=64", "width=64", "num_frames=5", "dataset_type=synthetic",
+                                  "wan_preset=tiny", "remat_policy=SAVE_ATTENTION", f"remat_keep_blocks={keep}", "warmup_steps_fraction=0.0",
+                                  "log_config=false", "write_metrics=false", "stochastic_rounding=false"], unittest=True)
+    tr = WanTrainer(config, mesh=create_device_mesh(config), device="cpu")
+    data = tr.load_dataset()
+    losses = [float(tr.train_step(next(data))["learning/loss"]) for _ in range(2)]
+    return losses, [p.detach().clone() for p in tr.model.parameters()]
+
+  l0, p0 = run(0)
+  l1, p1 = run(1)
+  l2, p2 = run(99)  # more than there are blocks: every block keeps its activations
+  assert l0 == l1 == l2
+  for a, b, c in zip(p0, p1, p2):
+    assert torch.equal(a, b) and torch.equal(a, c)
+
+
 def test_adaptive_norms_match_explicit_formula():
   torch.manual_seed(0)
   x, emb = torch.randn(2, 5, 16), torch.randn(2, 16)
