@@ -145,7 +145,7 @@ def main() -> int:
     free, total = torch.cuda.mem_get_info()
     peak = torch.cuda.max_memory_reserved()
     per_block = kept_block_bytes(trainer.model.cfg, -(-seq_len // n), n)
-    room = total - peak - int(0.12 * total)
+    room = total - peak - int(0.08 * total)
     keep_t = torch.tensor([max(0, min(len(trainer.model.blocks), room // per_block))], device="cuda")
     if world > 1:
       dist.all_reduce(keep_t, op=dist.ReduceOp.MIN)

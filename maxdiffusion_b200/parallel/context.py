@@ -119,11 +119,11 @@ class _SegmentAttentionFn(torch.autograd.Function):
     ks = [kg[i][:, :lens[i]] for i in range(n)]
     vs = [vg[i][:, :lens[i]] for i in range(n)]
     delta = K.flash_delta(out, d_o)
-    dq = K.flash_bwd_dq(q, d_o, ks, vs, lse, delta, ctx.scale)
     rs = ctx.reducer
     if rs is not None:
       # peer-memory return of the partials: the dK/dV kernels write the partial for owner r straight into slice r of
-      # a symmetric buffer ([dK | dV] per owner), and every owner pulls and sums its slice with one kernel
+      # a symmetric buffer ([dK | dV] per owner), and every owner pulls and sums its slice with one kernel. That
+      # kernel is bound by NVLink, so it runs on a side stream underneath the dQ kernel.
       shape = (2,) + tuple(kg.shape[1:])
       parts = rs.slices(shape)
       if min(lens) < kg.shape[2]:
@@ -132,8 +132,19 @@ class _SegmentAttentionFn(torch.autograd.Function):
       for i in range(n):
         part = parts[ctx.order[i]]
         K.flash_bwd_dkv(q, d_o, ks[i], vs[i], lse, delta, ctx.scale, dk=part[0][:, :lens[i]], dv=part[1][:, :lens[i]])
-      both = rs.reduce()
+      main = torch.cuda.current_stream()
+      produced = torch.cuda.Event()
+      produced.record(main)
+      with torch.cuda.stream(rs.stream):
+        rs.stream.wait_event(produced)
+        both = rs.reduce()
+        reduced = torch.cuda.Event()
+        reduced.record(rs.stream)
+      dq = K.flash_bwd_dq(q, d_o, ks, vs, lse, delta, ctx.scale)
+      main.wait_event(reduced)
+      both.record_stream(main)
       return dq, both[0], both[1], None, None, None, None, None
+    dq = K.flash_bwd_dq(q, d_o, ks, vs, lse, delta, ctx.scale)
     dkg = torch.zeros_like(kg) if min(lens) < kg.shape[2] else torch.empty_like(kg)
     dvg = torch.zeros_like(vg) if min(lens) < vg.shape[2] else torch.empty_like(vg)
     for i in range(n):

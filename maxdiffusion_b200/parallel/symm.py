@@ -373,6 +373,7 @@ class PeerReduceScatter:
       self.slots.append(t)
       self.slot_ptrs.append(ptrs)
     self.epoch = 0
+    self.stream = torch.cuda.Stream()  # callers may run `reduce` here, underneath compute on their own stream
     torch.cuda.synchronize()
     dist.barrier(group=peer.group)
 
@@ -396,7 +397,7 @@ class PeerReduceScatter:
       out = torch.empty(self._shape, dtype=torch.bfloat16, device=self.slots[0].device)
     off = self.rank * self.numel * 2
     arr = (ctypes.c_ulonglong * self.n)(*[self.slot_ptrs[slot][r] + off for r in range(self.n)])
-    rc = _lib.lib().mdb_pull_reduce(arr, self.n, _lib.ptr(out), self._numel, 96, _lib.stream())
+    rc = _lib.lib().mdb_pull_reduce(arr, self.n, _lib.ptr(out), self._numel, 32, _lib.stream())
     _lib.check(rc, "mdb_pull_reduce")
     self.peer.signal(FLAG_RS_ACK, e)
     return out
