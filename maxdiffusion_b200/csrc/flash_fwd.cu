@@ -83,6 +83,11 @@ struct Params {
   float scale_log2;
   const unsigned int* seg_flags;  // [num_segments] or nullptr
   unsigned int flag_target;       // segment s is ready once seg_flags[s] >= flag_target
+  // Fixed-exponent softmax (both nullptr: off). Rows of the heads with fixed_heads[h] != 0 subtract the given
+  // m_fixed[b, h, row] (log2 domain) instead of a running maximum: no row maximum, no accumulator rescale.
+  // The caller guarantees  s*scale_log2 - m_fixed <= 126  for every score of such a head.
+  const float* m_fixed;    // [B, H, q_len]
+  const int* fixed_heads;  // [H]
   DeviceStatus* status;
 };
 
@@ -384,6 +389,10 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
       if (t >= n_tiles) continue;
       const int q_row = q0 + t * BQ + row_in_tile;
       float m = -INFINITY, l = 0.0f;
+      const bool fixed = p.m_fixed != nullptr && p.fixed_heads[head] != 0;  // uniform over the CTA
+      if (fixed) {
+        m = (q_row < p.q_len) ? p.m_fixed[(static_cast<long long>(batch) * p.H + head) * p.q_len + q_row] : 0.0f;
+      }
       int j = 0;
       for (int seg = 0; seg < p.num_segments && ok; ++seg) {
         const int nblk = (p.kv_len[seg] + BKV - 1) / BKV;
@@ -397,43 +406,45 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
           tmem_ld_x32(s_addr, sv2[0]);
           tmem_ld_x32(s_addr + 32, sv2[1]);
           tmem_wait_ld();
-          float mx0 = -INFINITY, mx1 = -INFINITY;  // two chains
-          if (valid == BKV) {
-#pragma unroll
-            for (int i = 0; i < 32; ++i) {
-              mx0 = fmaxf(mx0, __uint_as_float(sv2[0][i]));
-              mx1 = fmaxf(mx1, __uint_as_float(sv2[1][i]));
-            }
-          } else {
-#pragma unroll
-            for (int c = 0; c < 2; ++c)
+          if (!fixed) {
+            float mx0 = -INFINITY, mx1 = -INFINITY;  // two chains
+            if (valid == BKV) {
 #pragma unroll
               for (int i = 0; i < 32; ++i) {
-                if (c * 32 + i < valid) mx0 = fmaxf(mx0, __uint_as_float(sv2[c][i]));
+                mx0 = fmaxf(mx0, __uint_as_float(sv2[0][i]));
+                mx1 = fmaxf(mx1, __uint_as_float(sv2[1][i]));
               }
-          }
-          const float m_new = fmaxf(m, fmaxf(mx0, mx1) * p.scale_log2);
-          if (j == 0) {
-            m = m_new;
-          } else {
-            const bool need = (m_new - m) > kRescaleThreshold;
-            if (__any_sync(0xffffffffu, need)) {
-              // O must be at rest: the P V product of the previous block (the other buffer) has to be complete
-              if (!mbar_wait(&s_free[t * 2 + (b ^ 1u)], ((n - 1) >> 1) & 1u, abort_flag, p.status, 62)) { ok = false; break; }
-              tc_fence_after_sync();
-              const float alpha = fast_exp2(m - m_new);
-              l *= alpha;
-              m = m_new;
-#pragma unroll 1
-              for (int c = 0; c < D / 32; ++c) {
-                uint32_t r[32];
-                tmem_ld_x32(o_addr + c * 32, r);
-                tmem_wait_ld();
+            } else {
 #pragma unroll
-                for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
-                tmem_st_x32(o_addr + c * 32, r);
+              for (int c = 0; c < 2; ++c)
+#pragma unroll
+                for (int i = 0; i < 32; ++i) {
+                  if (c * 32 + i < valid) mx0 = fmaxf(mx0, __uint_as_float(sv2[c][i]));
+                }
+            }
+            const float m_new = fmaxf(m, fmaxf(mx0, mx1) * p.scale_log2);
+            if (j == 0) {
+              m = m_new;
+            } else {
+              const bool need = (m_new - m) > kRescaleThreshold;
+              if (__any_sync(0xffffffffu, need)) {
+                // O must be at rest: the P V product of the previous block (the other buffer) has to be complete
+                if (!mbar_wait(&s_free[t * 2 + (b ^ 1u)], ((n - 1) >> 1) & 1u, abort_flag, p.status, 62)) { ok = false; break; }
+                tc_fence_after_sync();
+                const float alpha = fast_exp2(m - m_new);
+                l *= alpha;
+                m = m_new;
+#pragma unroll 1
+                for (int c = 0; c < D / 32; ++c) {
+                  uint32_t r[32];
+                  tmem_ld_x32(o_addr + c * 32, r);
+                  tmem_wait_ld();
+#pragma unroll
+                  for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
+                  tmem_st_x32(o_addr + c * 32, r);
+                }
+                tmem_wait_st();
               }
-              tmem_wait_st();
             }
           }
           // probabilities, written over S as packed bf16 (32 columns)
@@ -542,7 +553,8 @@ static int flash_fwd_launch(const void* q, const void* const* k_ptrs, const void
                             long long q_sb, long long q_ss, long long q_sh, long long k_sb, long long k_ss,
                             long long k_sh, long long v_sb, long long v_ss, long long v_sh, long long o_sb,
                             long long o_ss, long long o_sh, float softmax_scale, const unsigned int* seg_flags,
-                            unsigned int flag_target, const MdbCopyPlan* plan, void* stream_ptr) {
+                            unsigned int flag_target, const MdbCopyPlan* plan, void* stream_ptr,
+                            const float* m_fixed = nullptr, const int* fixed_heads = nullptr) {
   using namespace mdb;
   using namespace mdb::fa;
   if (B <= 0 || H <= 0 || q_len <= 0) return 0;
@@ -570,6 +582,9 @@ static int flash_fwd_launch(const void* q, const void* const* k_ptrs, const void
   p.scale_log2 = softmax_scale * 1.4426950408889634f;
   p.seg_flags = seg_flags;
   p.flag_target = flag_target;
+  if ((m_fixed == nullptr) != (fixed_heads == nullptr)) return 3105;
+  p.m_fixed = m_fixed;
+  p.fixed_heads = fixed_heads;
   p.status = status_buffer();
   CopyPlan cp;
   memset(&cp, 0, sizeof(cp));
@@ -629,4 +644,32 @@ extern "C" int mdb_flash_fwd_d64(const void* q, const void* const* k_ptrs, const
   return flash_fwd_launch<64>(q, k_ptrs, v_ptrs, out, lse, B, H, q_len, num_segments, kv_lens, q_sb, q_ss, q_sh, k_sb,
                               k_ss, k_sh, v_sb, v_ss, v_sh, o_sb, o_ss, o_sh, softmax_scale, seg_flags, flag_target,
                               plan, stream_ptr);
+}
+
+// The same kernels with the fixed-exponent softmax: m_fixed fp32 [B, H, q_len] (log2 domain), fixed_heads
+// int32 [H] (non-zero: the head uses m_fixed; zero: the head keeps the running maximum).
+extern "C" int mdb_flash_fwd_fixed_m(const void* q, const void* const* k_ptrs, const void* const* v_ptrs, void* out,
+                                     float* lse, int B, int H, int q_len, int num_segments, const int* kv_lens,
+                                     long long q_sb, long long q_ss, long long q_sh, long long k_sb, long long k_ss,
+                                     long long k_sh, long long v_sb, long long v_ss, long long v_sh, long long o_sb,
+                                     long long o_ss, long long o_sh, float softmax_scale,
+                                     const unsigned int* seg_flags, unsigned int flag_target, const MdbCopyPlan* plan,
+                                     void* stream_ptr, const float* m_fixed, const int* fixed_heads) {
+  if (m_fixed == nullptr || fixed_heads == nullptr) return 3105;
+  return flash_fwd_launch<128>(q, k_ptrs, v_ptrs, out, lse, B, H, q_len, num_segments, kv_lens, q_sb, q_ss, q_sh, k_sb,
+                               k_ss, k_sh, v_sb, v_ss, v_sh, o_sb, o_ss, o_sh, softmax_scale, seg_flags, flag_target,
+                               plan, stream_ptr, m_fixed, fixed_heads);
+}
+extern "C" int mdb_flash_fwd_fixed_m_d64(const void* q, const void* const* k_ptrs, const void* const* v_ptrs,
+                                         void* out, float* lse, int B, int H, int q_len, int num_segments,
+                                         const int* kv_lens, long long q_sb, long long q_ss, long long q_sh,
+                                         long long k_sb, long long k_ss, long long k_sh, long long v_sb, long long v_ss,
+                                         long long v_sh, long long o_sb, long long o_ss, long long o_sh,
+                                         float softmax_scale, const unsigned int* seg_flags, unsigned int flag_target,
+                                         const MdbCopyPlan* plan, void* stream_ptr, const float* m_fixed,
+                                         const int* fixed_heads) {
+  if (m_fixed == nullptr || fixed_heads == nullptr) return 3105;
+  return flash_fwd_launch<64>(q, k_ptrs, v_ptrs, out, lse, B, H, q_len, num_segments, kv_lens, q_sb, q_ss, q_sh, k_sb,
+                              k_ss, k_sh, v_sb, v_ss, v_sh, o_sb, o_ss, o_sh, softmax_scale, seg_flags, flag_target,
+                              plan, stream_ptr, m_fixed, fixed_heads);
 }

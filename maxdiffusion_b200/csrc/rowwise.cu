@@ -30,6 +30,15 @@ __device__ __forceinline__ void load8(const __nv_bfloat16* p, float (&x)[8]) {
     x[2 * j + 1] = f.y;
   }
 }
+__device__ __forceinline__ void unpack8(const uint4& v, float (&x)[8]) {
+  const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    float2 f = unpack_bf16x2(w[j]);
+    x[2 * j] = f.x;
+    x[2 * j + 1] = f.y;
+  }
+}
 __device__ __forceinline__ void store8(__nv_bfloat16* p, const float (&x)[8]) {
   uint4 v;
   v.x = pack_bf16x2(x[0], x[1]);
@@ -65,6 +74,23 @@ __device__ __forceinline__ float block_sum(float v, float* red) {
   for (int i = 0; i < THREADS / 32; ++i) t += red[i];
   return t;
 }
+// The same with ONE barrier per call: the warp partials go to red[parity] and the parity flips on every call, so
+// a warp that runs ahead into its next call writes the other half; it can reach the call after that only once
+// every warp has passed the barrier in between, i.e. has finished reading this half. `red` is 2 x 8 float2.
+__device__ __forceinline__ float2 block_sum2(float a, float b, float2 (*red)[THREADS / 32], int& parity) {
+  a = warp_sum(a);
+  b = warp_sum(b);
+  if ((threadIdx.x & 31) == 0) red[parity][threadIdx.x >> 5] = make_float2(a, b);
+  __syncthreads();
+  float2 t = make_float2(0.0f, 0.0f);
+#pragma unroll
+  for (int i = 0; i < THREADS / 32; ++i) {
+    t.x += red[parity][i].x;
+    t.y += red[parity][i].y;
+  }
+  parity ^= 1;
+  return t;
+}
 // Sum over aligned groups of 16 lanes (one 128-channel head).
 __device__ __forceinline__ float half_warp_sum(float v) {
 #pragma unroll
@@ -93,19 +119,23 @@ __device__ __forceinline__ Strip my_strip(int rows_per_batch) {
 // LayerNorm (fp32 statistics) with optional affine (gamma, beta: bf16 [C]) and optional
 // modulation (scale, shift: fp32 [num_batches, mod_ld]):  y = ((x-mean)*rstd*gamma+beta)*(1+scale)+shift
 // ---------------------------------------------------------------------------------------
-__global__ void __launch_bounds__(THREADS)
+// NV = 16-byte vectors per thread (C <= NV*8*THREADS). Four CTAs fit on an SM, so a grid of 4 x 148 is one wave.
+template <int NV>
+__global__ void __launch_bounds__(THREADS, 4)
 ln_fwd_kernel(const __nv_bfloat16* __restrict__ x, __nv_bfloat16* __restrict__ y,
               const __nv_bfloat16* __restrict__ gamma, const __nv_bfloat16* __restrict__ beta,
               const float* __restrict__ scale, const float* __restrict__ shift, long long mod_ld, int rows_per_batch,
               int C, float eps, float* __restrict__ mean_out, float* __restrict__ rstd_out) {
-  __shared__ float red[8];
+  __shared__ float2 red[2][THREADS / 32];
+  int parity = 0;
   const Strip s = my_strip(rows_per_batch);
   const int nvec = C >> 3;
+  const float inv_c = 1.0f / C;
   for (long long row = s.begin; row < s.end; ++row) {
-    float v[MAXV][8];
+    float v[NV][8];
     float sum = 0.0f;
 #pragma unroll
-    for (int k = 0; k < MAXV; ++k) {
+    for (int k = 0; k < NV; ++k) {
       const int vi = threadIdx.x + k * THREADS;
       if (vi < nvec) {
         load8(x + row * C + vi * 8, v[k]);
@@ -113,10 +143,10 @@ ln_fwd_kernel(const __nv_bfloat16* __restrict__ x, __nv_bfloat16* __restrict__ y
         for (int j = 0; j < 8; ++j) sum += v[k][j];
       }
     }
-    const float mean = block_sum(sum, red) / C;
+    const float mean = block_sum2(sum, 0.0f, red, parity).x * inv_c;
     float sq = 0.0f;
 #pragma unroll
-    for (int k = 0; k < MAXV; ++k) {
+    for (int k = 0; k < NV; ++k) {
       const int vi = threadIdx.x + k * THREADS;
       if (vi < nvec) {
 #pragma unroll
@@ -126,13 +156,13 @@ ln_fwd_kernel(const __nv_bfloat16* __restrict__ x, __nv_bfloat16* __restrict__ y
         }
       }
     }
-    const float rstd = rsqrtf(block_sum(sq, red) / C + eps);
+    const float rstd = rsqrtf(block_sum2(sq, 0.0f, red, parity).x * inv_c + eps);
     if (threadIdx.x == 0) {
       if (mean_out) mean_out[row] = mean;
       if (rstd_out) rstd_out[row] = rstd;
     }
 #pragma unroll
-    for (int k = 0; k < MAXV; ++k) {
+    for (int k = 0; k < NV; ++k) {
       const int vi = threadIdx.x + k * THREADS;
       if (vi < nvec) {
         float o[8];
@@ -167,66 +197,90 @@ ln_fwd_kernel(const __nv_bfloat16* __restrict__ x, __nv_bfloat16* __restrict__ y
 //   partial[cta][0][c] = sum_rows dy*xhat (-> dscale, or dgamma when affine)
 //   partial[cta][1][c] = sum_rows dy      (-> dshift, or dbeta)
 // (for the modulated form the first sum is taken after the affine, i.e. d/dscale of y).
-__global__ void __launch_bounds__(THREADS)
+// Between the two passes over a row a thread keeps only the packed bf16 inputs (the fp32 terms are recomputed),
+// which together with the 2*NV*8 column accumulators leaves room for two CTAs per SM; the two row sums share
+// one reduction with one barrier.
+template <int NV>
+__global__ void __launch_bounds__(THREADS, 2)
 ln_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ x,
               const float* __restrict__ mean_in, const float* __restrict__ rstd_in,
               const __nv_bfloat16* __restrict__ gamma, const float* __restrict__ scale, long long mod_ld,
               int rows_per_batch, int C, __nv_bfloat16* __restrict__ dx, float* __restrict__ partial) {
-  __shared__ float red[8];
+  __shared__ float2 red[2][THREADS / 32];
+  int parity = 0;
   const Strip s = my_strip(rows_per_batch);
   const int nvec = C >> 3;
-  float acc0[MAXV][8], acc1[MAXV][8];
+  const float inv_c = 1.0f / C;
+  float acc0[NV][8], acc1[NV][8];
 #pragma unroll
-  for (int k = 0; k < MAXV; ++k)
+  for (int k = 0; k < NV; ++k)
 #pragma unroll
     for (int j = 0; j < 8; ++j) acc0[k][j] = acc1[k][j] = 0.0f;
 
+  // w = (1+scale)*gamma of a vector of 8 columns (re-read from L1 in both passes).
+  auto weights = [&](int vi, float (&w)[8]) {
+#pragma unroll
+    for (int j = 0; j < 8; ++j) w[j] = 1.0f;
+    if (scale) {
+      float sc[8];
+      loadf8(scale + s.batch * mod_ld + vi * 8, sc);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) w[j] = 1.0f + sc[j];
+    }
+    if (gamma) {
+      float gm[8];
+      load8(gamma + vi * 8, gm);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) w[j] *= gm[j];
+    }
+  };
+
   for (long long row = s.begin; row < s.end; ++row) {
     const float mean = mean_in[row], rstd = rstd_in[row];
-    float g[MAXV][8], xh[MAXV][8];
-    float s1 = 0.0f, s2 = 0.0f;
+    uint4 rd[NV], rx[NV];
 #pragma unroll
-    for (int k = 0; k < MAXV; ++k) {
+    for (int k = 0; k < NV; ++k) {
       const int vi = threadIdx.x + k * THREADS;
       if (vi < nvec) {
-        float d[8], xv[8];
-        load8(dy + row * C + vi * 8, d);
-        load8(x + row * C + vi * 8, xv);
-        float w[8];
+        rd[k] = *reinterpret_cast<const uint4*>(dy + row * C + vi * 8);
+        rx[k] = *reinterpret_cast<const uint4*>(x + row * C + vi * 8);
+      }
+    }
+    float s1 = 0.0f, s2 = 0.0f;
 #pragma unroll
-        for (int j = 0; j < 8; ++j) w[j] = 1.0f;
-        if (scale) {
-          float sc[8];
-          loadf8(scale + s.batch * mod_ld + vi * 8, sc);
-#pragma unroll
-          for (int j = 0; j < 8; ++j) w[j] = 1.0f + sc[j];
-        }
-        if (gamma) {
-          float gm[8];
-          load8(gamma + vi * 8, gm);
-#pragma unroll
-          for (int j = 0; j < 8; ++j) w[j] *= gm[j];
-        }
+    for (int k = 0; k < NV; ++k) {
+      const int vi = threadIdx.x + k * THREADS;
+      if (vi < nvec) {
+        float d[8], xv[8], w[8];
+        unpack8(rd[k], d);
+        unpack8(rx[k], xv);
+        weights(vi, w);
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
-          xh[k][j] = (xv[j] - mean) * rstd;
-          g[k][j] = d[j] * w[j];
-          s1 += g[k][j];
-          s2 += g[k][j] * xh[k][j];
-          acc0[k][j] += d[j] * xh[k][j];
+          const float xh = (xv[j] - mean) * rstd;
+          const float g = d[j] * w[j];
+          s1 += g;
+          s2 += g * xh;
+          acc0[k][j] += d[j] * xh;
           acc1[k][j] += d[j];
         }
       }
     }
-    const float m1 = block_sum(s1, red) / C;
-    const float m2 = block_sum(s2, red) / C;
+    const float2 m = block_sum2(s1, s2, red, parity);
+    const float m1 = m.x * inv_c, m2 = m.y * inv_c;
 #pragma unroll
-    for (int k = 0; k < MAXV; ++k) {
+    for (int k = 0; k < NV; ++k) {
       const int vi = threadIdx.x + k * THREADS;
       if (vi < nvec) {
-        float o[8];
+        float d[8], xv[8], w[8], o[8];
+        unpack8(rd[k], d);
+        unpack8(rx[k], xv);
+        weights(vi, w);
 #pragma unroll
-        for (int j = 0; j < 8; ++j) o[j] = rstd * (g[k][j] - m1 - xh[k][j] * m2);
+        for (int j = 0; j < 8; ++j) {
+          const float xh = (xv[j] - mean) * rstd;
+          o[j] = rstd * (d[j] * w[j] - m1 - xh * m2);
+        }
         store8(dx + row * C + vi * 8, o);
       }
     }
@@ -234,7 +288,7 @@ ln_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restr
   if (partial) {
     const long long cta = static_cast<long long>(blockIdx.y) * gridDim.x + blockIdx.x;
 #pragma unroll
-    for (int k = 0; k < MAXV; ++k) {
+    for (int k = 0; k < NV; ++k) {
       const int vi = threadIdx.x + k * THREADS;
       if (vi < nvec) {
         storef8(partial + (cta * 2 + 0) * C + vi * 8, acc0[k]);
@@ -284,21 +338,23 @@ __global__ void __launch_bounds__(256) fold_partials_kernel(const float* __restr
 // learned weight w [C or 128], followed by an optional rotary embedding on interleaved pairs of
 // each 128-wide head: cos/sin are fp32 [rows_per_batch, 64].
 // ---------------------------------------------------------------------------------------
-__global__ void __launch_bounds__(THREADS)
+template <int NV>
+__global__ void __launch_bounds__(THREADS, 4)
 rms_rope_fwd_kernel(const __nv_bfloat16* __restrict__ x, long long ldx, __nv_bfloat16* __restrict__ y, long long ldy,
                     const __nv_bfloat16* __restrict__ w, int w_per_head, const float* __restrict__ cos_t,
                     const float* __restrict__ sin_t, int rows_per_batch, int C, int group, float eps,
                     float* __restrict__ rstd_out) {
-  __shared__ float red[8];
+  __shared__ float2 red[2][THREADS / 32];
+  int parity = 0;
   const Strip s = my_strip(rows_per_batch);
   const int nvec = C >> 3;
   for (long long row = s.begin; row < s.end; ++row) {
     const int pos = static_cast<int>(row - static_cast<long long>(s.batch) * rows_per_batch);
-    float v[MAXV][8];
-    float sq[MAXV];
+    float v[NV][8];
+    float sq[NV];
     float total = 0.0f;
 #pragma unroll
-    for (int k = 0; k < MAXV; ++k) {
+    for (int k = 0; k < NV; ++k) {
       const int vi = threadIdx.x + k * THREADS;
       sq[k] = 0.0f;
       if (vi < nvec) {
@@ -309,9 +365,9 @@ rms_rope_fwd_kernel(const __nv_bfloat16* __restrict__ x, long long ldx, __nv_bfl
       total += sq[k];
     }
     float rstd_all = 0.0f;
-    if (group == C) rstd_all = rsqrtf(block_sum(total, red) / C + eps);
+    if (group == C) rstd_all = rsqrtf(block_sum2(total, 0.0f, red, parity).x / C + eps);
 #pragma unroll
-    for (int k = 0; k < MAXV; ++k) {
+    for (int k = 0; k < NV; ++k) {
       const int vi = threadIdx.x + k * THREADS;
       float rstd = rstd_all;
       if (group != C) rstd = rsqrtf(half_warp_sum(sq[k]) / 128.0f + eps);  // all lanes take part
@@ -354,28 +410,30 @@ rms_rope_fwd_kernel(const __nv_bfloat16* __restrict__ x, long long ldx, __nv_bfl
 
 // Backward: dy is the gradient w.r.t. the rotated output. partial[cta][0][c] = sum_rows dyn*xhat
 // (gradient of w before folding heads when w_per_head).
-__global__ void __launch_bounds__(THREADS)
+template <int NV>
+__global__ void __launch_bounds__(THREADS, 2)
 rms_rope_bwd_kernel(const __nv_bfloat16* __restrict__ dy, long long lddy, const __nv_bfloat16* __restrict__ x,
                     long long ldx, const float* __restrict__ rstd_in, const __nv_bfloat16* __restrict__ w,
                     int w_per_head, const float* __restrict__ cos_t, const float* __restrict__ sin_t,
                     int rows_per_batch, int C, int group, __nv_bfloat16* __restrict__ dx, long long lddx,
                     float* __restrict__ partial) {
-  __shared__ float red[8];
+  __shared__ float2 red[2][THREADS / 32];
+  int parity = 0;
   const Strip s = my_strip(rows_per_batch);
   const int nvec = C >> 3;
-  float acc[MAXV][8];
+  float acc[NV][8];
 #pragma unroll
-  for (int k = 0; k < MAXV; ++k)
+  for (int k = 0; k < NV; ++k)
 #pragma unroll
     for (int j = 0; j < 8; ++j) acc[k][j] = 0.0f;
 
   for (long long row = s.begin; row < s.end; ++row) {
     const int pos = static_cast<int>(row - static_cast<long long>(s.batch) * rows_per_batch);
-    float g[MAXV][8], xh[MAXV][8];
-    float dot[MAXV];
+    float g[NV][8], xh[NV][8];
+    float dot[NV];
     float total = 0.0f;
 #pragma unroll
-    for (int k = 0; k < MAXV; ++k) {
+    for (int k = 0; k < NV; ++k) {
       const int vi = threadIdx.x + k * THREADS;
       dot[k] = 0.0f;
       if (vi < nvec) {
@@ -415,9 +473,9 @@ rms_rope_bwd_kernel(const __nv_bfloat16* __restrict__ dy, long long lddy, const 
       total += dot[k];
     }
     float mean_all = 0.0f;
-    if (group == C) mean_all = block_sum(total, red) / C;
+    if (group == C) mean_all = block_sum2(total, 0.0f, red, parity).x / C;
 #pragma unroll
-    for (int k = 0; k < MAXV; ++k) {
+    for (int k = 0; k < NV; ++k) {
       const int vi = threadIdx.x + k * THREADS;
       float mdot = mean_all;
       if (group != C) mdot = half_warp_sum(dot[k]) / 128.0f;
@@ -433,7 +491,7 @@ rms_rope_bwd_kernel(const __nv_bfloat16* __restrict__ dy, long long lddy, const 
   if (partial) {
     const long long cta = static_cast<long long>(blockIdx.y) * gridDim.x + blockIdx.x;
 #pragma unroll
-    for (int k = 0; k < MAXV; ++k) {
+    for (int k = 0; k < NV; ++k) {
       const int vi = threadIdx.x + k * THREADS;
       if (vi < nvec) storef8(partial + cta * C + vi * 8, acc[k]);
     }
@@ -511,6 +569,7 @@ colsum_kernel(const __nv_bfloat16* __restrict__ x, long long ldx, int rows_per_b
     float acc[8];
 #pragma unroll
     for (int j = 0; j < 8; ++j) acc[j] = 0.0f;
+#pragma unroll 4
     for (long long row = s.begin; row < s.end; ++row) {
       float v[8];
       load8(x + row * ldx + vi * 8, v);
@@ -564,6 +623,7 @@ using namespace mdb;
 using namespace mdb::rw;
 
 static inline int check_c(int C) { return (C <= 0 || (C & 7) || C > THREADS * MAXV * 8) ? 3201 : 0; }
+static inline int vectors_per_thread(int C) { return ((C >> 3) + THREADS - 1) / THREADS; }
 
 extern "C" int mdb_ln_fwd(const void* x, void* y, const void* gamma, const void* beta, const float* scale,
                           const float* shift, long long mod_ld, int num_batches, int rows_per_batch, int C, float eps,
@@ -571,9 +631,17 @@ extern "C" int mdb_ln_fwd(const void* x, void* y, const void* gamma, const void*
   if (int rc = check_c(C)) return rc;
   if (num_batches <= 0 || rows_per_batch <= 0) return 0;
   dim3 grid(ctas_per_batch, num_batches);
-  ln_fwd_kernel<<<grid, THREADS, 0, static_cast<cudaStream_t>(stream)>>>(
-      static_cast<const __nv_bfloat16*>(x), static_cast<__nv_bfloat16*>(y), static_cast<const __nv_bfloat16*>(gamma),
-      static_cast<const __nv_bfloat16*>(beta), scale, shift, mod_ld, rows_per_batch, C, eps, mean_out, rstd_out);
+#define MDB_LN_FWD(NV)                                                                                          \
+  ln_fwd_kernel<NV><<<grid, THREADS, 0, static_cast<cudaStream_t>(stream)>>>(                                   \
+      static_cast<const __nv_bfloat16*>(x), static_cast<__nv_bfloat16*>(y), static_cast<const __nv_bfloat16*>(gamma), \
+      static_cast<const __nv_bfloat16*>(beta), scale, shift, mod_ld, rows_per_batch, C, eps, mean_out, rstd_out)
+  switch (vectors_per_thread(C)) {
+    case 1: MDB_LN_FWD(1); break;
+    case 2: MDB_LN_FWD(2); break;
+    case 3: MDB_LN_FWD(3); break;
+    default: MDB_LN_FWD(4); break;
+  }
+#undef MDB_LN_FWD
   return static_cast<int>(cudaGetLastError());
 }
 
@@ -585,10 +653,19 @@ extern "C" int mdb_ln_bwd(const void* dy, const void* x, const float* mean, cons
   if (num_batches <= 0 || rows_per_batch <= 0) return 0;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   dim3 grid(ctas_per_batch, num_batches);
-  ln_bwd_kernel<<<grid, THREADS, 0, st>>>(static_cast<const __nv_bfloat16*>(dy), static_cast<const __nv_bfloat16*>(x),
-                                          mean, rstd, static_cast<const __nv_bfloat16*>(gamma), scale, mod_ld,
-                                          rows_per_batch, C, static_cast<__nv_bfloat16*>(dx),
-                                          out_sums ? scratch : nullptr);
+#define MDB_LN_BWD(NV)                                                                                          \
+  ln_bwd_kernel<NV><<<grid, THREADS, 0, st>>>(static_cast<const __nv_bfloat16*>(dy),                            \
+                                              static_cast<const __nv_bfloat16*>(x), mean, rstd,                  \
+                                              static_cast<const __nv_bfloat16*>(gamma), scale, mod_ld,           \
+                                              rows_per_batch, C, static_cast<__nv_bfloat16*>(dx),                \
+                                              out_sums ? scratch : nullptr)
+  switch (vectors_per_thread(C)) {
+    case 1: MDB_LN_BWD(1); break;
+    case 2: MDB_LN_BWD(2); break;
+    case 3: MDB_LN_BWD(3); break;
+    default: MDB_LN_BWD(4); break;
+  }
+#undef MDB_LN_BWD
   if (out_sums) {
     dim3 g2((2 * C + 31) / 32, num_batches);
     fold_partials_kernel<<<g2, 256, 0, st>>>(scratch, out_sums, ctas_per_batch, 2, C, 0);
@@ -603,9 +680,17 @@ extern "C" int mdb_rms_rope_fwd(const void* x, long long ldx, void* y, long long
   if ((group != C && group != 128) || (C & 127)) return 3202;
   if (num_batches <= 0 || rows_per_batch <= 0) return 0;
   dim3 grid(ctas_per_batch, num_batches);
-  rms_rope_fwd_kernel<<<grid, THREADS, 0, static_cast<cudaStream_t>(stream)>>>(
-      static_cast<const __nv_bfloat16*>(x), ldx, static_cast<__nv_bfloat16*>(y), ldy,
-      static_cast<const __nv_bfloat16*>(w), w_per_head, cos_t, sin_t, rows_per_batch, C, group, eps, rstd_out);
+#define MDB_RMS_FWD(NV)                                                                                 \
+  rms_rope_fwd_kernel<NV><<<grid, THREADS, 0, static_cast<cudaStream_t>(stream)>>>(                     \
+      static_cast<const __nv_bfloat16*>(x), ldx, static_cast<__nv_bfloat16*>(y), ldy,                   \
+      static_cast<const __nv_bfloat16*>(w), w_per_head, cos_t, sin_t, rows_per_batch, C, group, eps, rstd_out)
+  switch (vectors_per_thread(C)) {
+    case 1: MDB_RMS_FWD(1); break;
+    case 2: MDB_RMS_FWD(2); break;
+    case 3: MDB_RMS_FWD(3); break;
+    default: MDB_RMS_FWD(4); break;
+  }
+#undef MDB_RMS_FWD
   return static_cast<int>(cudaGetLastError());
 }
 
@@ -619,10 +704,18 @@ extern "C" int mdb_rms_rope_bwd(const void* dy, long long lddy, const void* x, l
   if (num_batches <= 0 || rows_per_batch <= 0) return 0;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   dim3 grid(ctas_per_batch, num_batches);
-  rms_rope_bwd_kernel<<<grid, THREADS, 0, st>>>(
-      static_cast<const __nv_bfloat16*>(dy), lddy, static_cast<const __nv_bfloat16*>(x), ldx, rstd,
-      static_cast<const __nv_bfloat16*>(w), w_per_head, cos_t, sin_t, rows_per_batch, C, group,
-      static_cast<__nv_bfloat16*>(dx), lddx, dw_out ? scratch : nullptr);
+#define MDB_RMS_BWD(NV)                                                                                 \
+  rms_rope_bwd_kernel<NV><<<grid, THREADS, 0, st>>>(                                                    \
+      static_cast<const __nv_bfloat16*>(dy), lddy, static_cast<const __nv_bfloat16*>(x), ldx, rstd,     \
+      static_cast<const __nv_bfloat16*>(w), w_per_head, cos_t, sin_t, rows_per_batch, C, group,         \
+      static_cast<__nv_bfloat16*>(dx), lddx, dw_out ? scratch : nullptr)
+  switch (vectors_per_thread(C)) {
+    case 1: MDB_RMS_BWD(1); break;
+    case 2: MDB_RMS_BWD(2); break;
+    case 3: MDB_RMS_BWD(3); break;
+    default: MDB_RMS_BWD(4); break;
+  }
+#undef MDB_RMS_BWD
   if (dw_out) {
     // fold all CTAs of all batches into one [C] vector
     dim3 g2((C + 31) / 32, 1);

@@ -39,11 +39,12 @@ make_custom_ring_attention = make_ring_attention
 
 def get_attention_kernel(name: str, mesh=None, peer_memory: bool = True, scale: Optional[float] = None) -> Callable:
   strategy = context_strategy(name)
-  if strategy == "local" or mesh is None or mesh.size("context") == 1:
+  fixed_m = name in FIXED_M_KERNELS
+  if mesh is None or ((strategy == "local" or mesh.size("context") == 1) and not fixed_m):
     return make_splash_mha(scale)
   from ..parallel.context import ContextParallel
 
-  ctx = ContextParallel(mesh, strategy, peer_memory=peer_memory)
+  ctx = ContextParallel(mesh, strategy, peer_memory=peer_memory, fixed_m=fixed_m)
   return lambda q, k, v: ctx.self_attention(q, k, v, scale)
 
 

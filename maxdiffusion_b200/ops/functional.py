@@ -147,7 +147,7 @@ _REMAT_MIN_KV = 2048
 class _AttentionFn(torch.autograd.Function):
 
   @staticmethod
-  def forward(ctx, q, scale, n_seg, *kv):
+  def forward(ctx, q, scale, n_seg, fixed_m, *kv):
     ks, vs = list(kv[:n_seg]), list(kv[n_seg:])
     saved = None
     keep = _remat.mode is not None and sum(k.shape[1] for k in ks) >= _REMAT_MIN_KV
@@ -157,7 +157,7 @@ class _AttentionFn(torch.autograd.Function):
     if saved is not None:
       out, lse = saved
     else:
-      out, lse = K.flash_fwd(q, ks, vs, scale)
+      out, lse = K.flash_fwd(q, ks, vs, scale, fixed_m=fixed_m)
       if keep and _remat.mode == "record":
         _remat.store.append((out, lse))
     ctx.scale, ctx.n_seg = scale, n_seg
@@ -178,17 +178,21 @@ class _AttentionFn(torch.autograd.Function):
       dk, dv = K.flash_bwd_dkv(q, d_o, k, v, lse, delta, ctx.scale)
       dks.append(dk)
       dvs.append(dv)
-    return (dq, None, None, *dks, *dvs)
+    return (dq, None, None, None, *dks, *dvs)
 
 
-def attention(q, k, v, scale: float | None = None):
-  """Softmax attention, no mask. q: [B,Sq,H,D]; k, v: [B,Skv,H,D] or equal-length lists of KV segments."""
+def attention(q, k, v, scale: float | None = None, fixed_m=None):
+  """Softmax attention, no mask. q: [B,Sq,H,D]; k, v: [B,Skv,H,D] or equal-length lists of KV segments.
+
+  `fixed_m` (from `ops.fixed_m.plan`) runs the marked heads of the flash kernel with a fixed softmax exponent; the
+  result and the saved log-sum-exp are those of the plain softmax, so the backward is unchanged. Paths that do
+  not run the flash kernel ignore it."""
   ks = list(k) if isinstance(k, (list, tuple)) else [k]
   vs = list(v) if isinstance(v, (list, tuple)) else [v]
   D = q.shape[-1]
   scale = scale if scale is not None else 1.0 / math.sqrt(D)
   if _fast(q) and D in K.FLASH_HEAD_DIMS:
-    return _AttentionFn.apply(q, scale, len(ks), *ks, *vs)
+    return _AttentionFn.apply(q, scale, len(ks), fixed_m, *ks, *vs)
   kc = torch.cat(ks, dim=1) if len(ks) > 1 else ks[0]
   vc = torch.cat(vs, dim=1) if len(vs) > 1 else vs[0]
   out = F.scaled_dot_product_attention(q.transpose(1, 2), kc.transpose(1, 2), vc.transpose(1, 2), scale=scale)

@@ -64,11 +64,13 @@ def _flash_entry(name: str, D: int):
 
 
 def flash_fwd(q: torch.Tensor, k_list: Sequence[torch.Tensor], v_list: Sequence[torch.Tensor], scale: float | None = None,
-              return_lse: bool = True, seg_flags: torch.Tensor | None = None, flag_target: int = 0, plan=None):
+              return_lse: bool = True, seg_flags: torch.Tensor | None = None, flag_target: int = 0, plan=None,
+              fixed_m=None):
   """Flash attention forward over KV segments. q: [B,Sq,H,D]; k/v: lists of [B,Skv_i,H,D] sharing strides; D is 64 or 128.
 
   `seg_flags` gates segment i on flags[i] >= flag_target; `plan` (an `_lib.CopyPlan`) adds copy CTAs that stage
-  the remote segments from peer memory inside the same launch."""
+  the remote segments from peer memory inside the same launch. `fixed_m` = (m_fixed fp32 [B,H,Sq] in the log2
+  domain, fixed_heads int32 [H]) switches the marked heads to the fixed-exponent softmax (`ops.fixed_m`)."""
   if isinstance(k_list, torch.Tensor):
     k_list, v_list = [k_list], [v_list]
   B, Sq, H, D = q.shape
@@ -84,12 +86,18 @@ def flash_fwd(q: torch.Tensor, k_list: Sequence[torch.Tensor], v_list: Sequence[
   vp = (ctypes.c_void_p * n)(*[v.data_ptr() for v in v_list])
   lens = (ctypes.c_int * n)(*[k.shape[1] for k in k_list])
   scale = scale if scale is not None else 1.0 / math.sqrt(D)
-  rc = _flash_entry("mdb_flash_fwd", D)(
-      _lib.ptr(q), kp, vp, _lib.ptr(out), _lib.ptr(lse), B, H, Sq, n, lens,
-      q.stride(0), q.stride(1), q.stride(2), k0.stride(0), k0.stride(1), k0.stride(2),
-      v0.stride(0), v0.stride(1), v0.stride(2), out.stride(0), out.stride(1), out.stride(2),
-      float(scale), _lib.ptr(seg_flags), int(flag_target), ctypes.byref(plan) if plan is not None else None,
-      _lib.stream())
+  args = (_lib.ptr(q), kp, vp, _lib.ptr(out), _lib.ptr(lse), B, H, Sq, n, lens,
+          q.stride(0), q.stride(1), q.stride(2), k0.stride(0), k0.stride(1), k0.stride(2),
+          v0.stride(0), v0.stride(1), v0.stride(2), out.stride(0), out.stride(1), out.stride(2),
+          float(scale), _lib.ptr(seg_flags), int(flag_target), ctypes.byref(plan) if plan is not None else None,
+          _lib.stream())
+  if fixed_m is None:
+    rc = _flash_entry("mdb_flash_fwd", D)(*args)
+  else:
+    m_fixed, fixed_heads = fixed_m
+    assert m_fixed.dtype == torch.float32 and m_fixed.shape == (B, H, Sq) and m_fixed.is_contiguous()
+    assert fixed_heads.dtype == torch.int32 and fixed_heads.shape == (H,) and fixed_heads.is_contiguous()
+    rc = _flash_entry("mdb_flash_fwd_fixed_m", D)(*args, _lib.ptr(m_fixed), _lib.ptr(fixed_heads))
   _lib.check(rc, "mdb_flash_fwd")
   return (out, lse) if return_lse else out
 

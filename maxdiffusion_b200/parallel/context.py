@@ -22,6 +22,7 @@ from typing import Optional
 import torch
 import torch.distributed as dist
 
+from ..ops import fixed_m as FM
 from ..ops import functional as OF
 from ..ops import kernels as K
 from . import collectives as C
@@ -76,7 +77,7 @@ class _SegmentAttentionFn(torch.autograd.Function):
   """Kernel path of gather/ring attention: local q against the stacked K/V shards [n, B, S_loc, H, D]."""
 
   @staticmethod
-  def forward(ctx, q, k, v, scale, group, valid_lens, exchange, reducer=None):
+  def forward(ctx, q, k, v, scale, group, valid_lens, exchange, reducer=None, fixed_m=None):
     state = OF._remat
     saved = None
     if state.mode == "replay":
@@ -102,7 +103,7 @@ class _SegmentAttentionFn(torch.autograd.Function):
       out, lse = saved
     else:
       # with a plan the copy CTAs of this launch stage the remote segments while the math starts on the own one
-      out, lse = K.flash_fwd(q, ks, vs, scale, seg_flags=flags, flag_target=epoch, plan=plan)
+      out, lse = K.flash_fwd(q, ks, vs, scale, seg_flags=flags, flag_target=epoch, plan=plan, fixed_m=fixed_m)
       if state.mode == "record":
         state.store.append((out, lse))
     ctx.scale, ctx.group, ctx.valid_lens, ctx.order, ctx.reducer = scale, group, lens, order, reducer
@@ -143,7 +144,7 @@ class _SegmentAttentionFn(torch.autograd.Function):
       dq = K.flash_bwd_dq(q, d_o, ks, vs, lse, delta, ctx.scale)
       main.wait_event(reduced)
       both.record_stream(main)
-      return dq, both[0], both[1], None, None, None, None, None
+      return dq, both[0], both[1], None, None, None, None, None, None
     dq = K.flash_bwd_dq(q, d_o, ks, vs, lse, delta, ctx.scale)
     dkg = torch.zeros_like(kg) if min(lens) < kg.shape[2] else torch.empty_like(kg)
     dvg = torch.zeros_like(vg) if min(lens) < vg.shape[2] else torch.empty_like(vg)
@@ -154,7 +155,7 @@ class _SegmentAttentionFn(torch.autograd.Function):
       dvg[ctx.order[i]][:, :lens[i]].copy_(dv)
     dk = C.reduce_scatter_stack(dkg, ctx.group)
     dv = C.reduce_scatter_stack(dvg, ctx.group)
-    return dq, dk, dv, None, None, None, None, None
+    return dq, dk, dv, None, None, None, None, None, None
 
 
 class ContextParallel:
@@ -163,10 +164,13 @@ class ContextParallel:
   `mesh` is a `parallel.mesh.DeviceMesh`; `strategy` one of local / gather / ring / ulysses / usp.
   """
 
-  def __init__(self, mesh, strategy: str = "ring", peer_memory: bool = False):
+  def __init__(self, mesh, strategy: str = "ring", peer_memory: bool = False, fixed_m: bool = False):
     self.mesh = mesh
     self.strategy = strategy
     self.peer_memory = peer_memory
+    # fixed-exponent softmax (`ops.fixed_m`): keys are smoothed where a rank sees the whole key sequence (local,
+    # Ulysses); ring segments stay unsmoothed and take the halved gate, with the key norms max-reduced over the ring
+    self.fixed_m = fixed_m
     self._exchanges: dict = {}
     self._peers: dict = {}
     self._reducers: dict = {}
@@ -262,15 +266,29 @@ class ContextParallel:
     return full.narrow(dim, 0, self.full_len) if self.full_len is not None else full
 
   # ---- attention ---------------------------------------------------------------------------
+  def _uses_flash(self, q) -> bool:
+    return q.is_cuda and q.dtype == torch.bfloat16 and q.shape[-1] in K.FLASH_HEAD_DIMS
+
+  def _full_attention(self, q, k, v, scale=None):
+    """Attention of a rank that holds the whole key sequence of its heads."""
+    if self.fixed_m and self._uses_flash(q):
+      k = FM.smooth_keys(k)
+      return OF.attention(q, k, v, scale, fixed_m=FM.plan(q, k, scale, smoothed=True))
+    return OF.attention(q, k, v, scale)
+
   def _segment_attention(self, q, k, v, group, n, valid_lens, scale=None):
     if n == 1:
-      return OF.attention(q, k, v, scale)
+      return self._full_attention(q, k, v, scale)
     D = q.shape[-1]
     scale = scale if scale is not None else D ** -0.5
-    if q.is_cuda and q.dtype == torch.bfloat16 and D in K.FLASH_HEAD_DIMS:
+    if self._uses_flash(q):
       ex = self._exchange_for(group, k)
       rs = self._reducer_for(group, k) if (ex is not None and torch.is_grad_enabled() and k.requires_grad) else None
-      return _SegmentAttentionFn.apply(q, k, v, scale, group, tuple(valid_lens), ex, rs)
+      fixed = None
+      if self.fixed_m:
+        # padded tail rows of the own shard are zeros and do not raise the norm maximum
+        fixed = FM.plan(q, k, scale, smoothed=False, group=group)
+      return _SegmentAttentionFn.apply(q, k, v, scale, group, tuple(valid_lens), ex, rs, fixed)
     kg = _GatherSeq.apply(k, group)
     vg = _GatherSeq.apply(v, group)
     ks = [kg[i][:, :valid_lens[i]] for i in range(n)]
@@ -280,7 +298,7 @@ class ContextParallel:
   def self_attention(self, q, k, v, scale=None):
     """q, k, v: [B, S_loc, H, D] (sequence-sharded). Returns the attention output with the same layout."""
     if self.size == 1 or self.strategy == "local":
-      return OF.attention(q, k, v, scale)
+      return self._full_attention(q, k, v, scale)
     per = q.shape[1]
     if self.strategy in ("gather", "ring"):
       return self._segment_attention(q, k, v, self.group, self.size, self.valid_lengths(self.size, per), scale)
@@ -292,7 +310,7 @@ class ContextParallel:
       qh, kh, vh = (_HeadsToSeq.apply(t, self.group, ex) for t in (q, k, v))
       if self.full_len is not None and self.full_len < per * self.size:
         kh, vh = kh[:, :self.full_len], vh[:, :self.full_len]
-      o = OF.attention(qh, kh, vh, scale)
+      o = self._full_attention(qh, kh, vh, scale)
       return _SeqToHeads.apply(o, self.group, ex)
     if self.strategy == "usp":
       H = q.shape[2]

@@ -35,7 +35,18 @@ def cfg_cache_weights(step: int, num_steps: int, alpha: float = 0.2) -> tuple[fl
 
 def fft_compensate(noise_cond, cached_cond, cached_uncond, w1: float, w2: float):
   """uncond ≈ irfft2(rfft2(cond_new) + (low*w1 + high*w2) ⊙ (rfft2(uncond_cached) − rfft2(cond_cached))) over (H, W);
-  the low band is the lowest quarter of the frequencies of each axis (wrap-around rows included)."""
+  the low band is the lowest quarter of the frequencies of each axis (wrap-around rows included).
+
+  The transform pair is linear and the band separable, so this is cond_new plus a band-weighted copy of the
+  cached difference, computed by `ops.dft.band_weighted` as two real GEMMs (no FFT library, any H and W)."""
+  from ...ops import dft
+  delta = cached_uncond.float() - cached_cond.float()
+  approx = noise_cond.float() + dft.band_weighted(delta, w1, w2)
+  return approx.to(noise_cond.dtype)
+
+
+def fft_compensate_reference(noise_cond, cached_cond, cached_uncond, w1: float, w2: float):
+  """The same quantity through `torch.fft`, kept as the oracle of the tests."""
   fc = torch.fft.rfft2(cached_cond.float())
   fu = torch.fft.rfft2(cached_uncond.float())
   bias = fu - fc

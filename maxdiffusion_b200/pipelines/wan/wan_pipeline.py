@@ -68,9 +68,12 @@ class WanPipeline:
     self.device = torch.device(device) if device is not None else next(anchor.parameters()).device
     self.dtype = next(anchor.parameters()).dtype
     self.pctx = None
-    if self.mesh.size("context") > 1:
+    fixed_m = bool(config.get("fixed_m_softmax", False))
+    if self.mesh.size("context") > 1 or fixed_m:
+      # a one-rank context still goes through ContextParallel when the fixed-exponent softmax is selected
       self.pctx = ContextParallel(self.mesh, str(config.get("context_strategy", "ring")),
-                                  peer_memory=bool(config.get("peer_memory_transport", True)) and self.device.type == "cuda")
+                                  peer_memory=bool(config.get("peer_memory_transport", True)) and self.device.type == "cuda",
+                                  fixed_m=fixed_m)
     self.prompt_cache = PromptCache()
     from ...models.quantizations import get_quantization_mode, quantize_model
 

@@ -103,9 +103,12 @@ class WanTrainer:
                              peer_memory=bool(config.get("peer_memory_transport", True)))
     model.block_hook = self.engine.block_hook
     self.pctx = None
-    if self.mesh.size("context") > 1:
+    fixed_m = bool(config.get("fixed_m_softmax", False))
+    if self.mesh.size("context") > 1 or fixed_m:
+      # a one-rank context still goes through ContextParallel when the fixed-exponent softmax is selected
       self.pctx = ContextParallel(self.mesh, str(config.get("context_strategy", "ring")),
-                                  peer_memory=bool(config.get("peer_memory_transport", True)) and self.device.type == "cuda")
+                                  peer_memory=bool(config.get("peer_memory_transport", True)) and self.device.type == "cuda",
+                                  fixed_m=fixed_m)
 
     self.scheduler = FlowMatchScheduler(num_train_timesteps=1000, shift=float(config.get("flow_shift", 3.0)))
     self.scheduler_state = self.scheduler.set_timesteps(self.scheduler.create_state(), 1000, training=True, device=self.device)

@@ -101,3 +101,16 @@ def test_fused_antialiased_snake_matches_separable_path(L, dtype):
   _close(got, want, 2e-2 if dtype == torch.bfloat16 else 2e-5)
   leaky = AntiAliasAct1d(torch.nn.LeakyReLU(0.1)).to(DEV)
   _close(leaky(x), leaky.downsample(leaky.act(leaky.upsample(x.float()))), 2e-2 if dtype == torch.bfloat16 else 2e-5)
+
+
+@pytest.mark.parametrize("shape", [(1, 16, 5, 90, 160), (2, 4, 2, 45, 80), (1, 2, 1, 31, 53)])
+def test_band_filter_gemms_on_the_tensor_cores_match_the_fft_form(shape):
+  """CFG-cache compensation through the tcgen05 GEMM (split-bf16 operands) against torch.fft in fp32."""
+  from maxdiffusion_b200.pipelines.wan import cache_policies as CP
+
+  torch.manual_seed(0)
+  a, b, c = (torch.randn(shape, device=DEV) for _ in range(3))
+  for w1, w2 in ((1.2, 1.0), (1.0, 1.2)):
+    got = CP.fft_compensate(a, b, c, w1, w2)
+    want = CP.fft_compensate_reference(a, b, c, w1, w2)
+    _close(got, want, 2e-4)

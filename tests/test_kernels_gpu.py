@@ -95,6 +95,43 @@ def test_flash_fwd_segments_and_strided():
   assert (lse - want_lse).abs().max().item() < 2e-2
 
 
+@pytest.mark.parametrize("D", [128, 64])
+@pytest.mark.parametrize("B,H,Sq,Skv", [(1, 4, 256, 384), (2, 3, 300, 200), (1, 4, 1000, 1111)])
+def test_flash_fwd_fixed_m(B, H, Sq, Skv, D):
+  """Fixed-exponent softmax on the eligible heads, running maximum on a head over the gate, in one launch: same
+  output and log-sum-exp as the plain kernel and the fp32 reference; gradients flow through the saved lse."""
+  from maxdiffusion_b200.ops import fixed_m as FM
+  from maxdiffusion_b200.ops import functional as OF
+
+  torch.manual_seed(13)
+  q = torch.randn((B, Sq, H, D), device=DEV, dtype=torch.bfloat16)
+  k = torch.randn((B, Skv, H, D), device=DEV, dtype=torch.bfloat16) + 0.25
+  v = torch.randn((B, Skv, H, D), device=DEV, dtype=torch.bfloat16)
+  q[:, :, H - 1] *= 40.0  # a "sink" head whose bound exceeds the gate
+  ks = FM.smooth_keys(k)
+  plan = FM.plan(q, ks)
+  assert plan[1].tolist() == [1] * (H - 1) + [0]
+  out, lse = K.flash_fwd(q, ks, v, fixed_m=plan)
+  base, base_lse = K.flash_fwd(q, ks, v)
+  want = ref.attention(q, k, v)  # smoothing the keys does not change the softmax
+  _report(f"flash_fwd fixed-m D{D} B{B} H{H} Sq{Sq} Skv{Skv}", out, want.float(), rel_tol=2e-2, abs_frac=5e-2)
+  assert (out.float() - base.float()).abs().max().item() < 2e-2
+  assert (lse - base_lse).abs().max().item() < 2e-2
+  # two unsmoothed segments with the halved gate (the ring form)
+  cut = Skv // 3
+  plan2 = FM.plan(q, [k[:, :cut], k[:, cut:]], smoothed=False)
+  out2, _ = K.flash_fwd(q, [k[:, :cut], k[:, cut:]], [v[:, :cut], v[:, cut:]], fixed_m=plan2)
+  _report("flash_fwd fixed-m, two unsmoothed segments", out2, want.float(), rel_tol=2e-2, abs_frac=5e-2)
+  # autograd through functional.attention: the backward kernels only need the true lse
+  qg, kg, vg = (t.clone().requires_grad_(True) for t in (q, ks, v))
+  OF.attention(qg, kg, vg, fixed_m=plan).float().square().sum().backward()
+  qb, kb, vb = (t.clone().requires_grad_(True) for t in (q, ks, v))
+  OF.attention(qb, kb, vb).float().square().sum().backward()
+  for a, b in ((qg, qb), (kg, kb), (vg, vb)):
+    scale = b.grad.float().abs().max().item() + 1e-6
+    assert (a.grad.float() - b.grad.float()).abs().max().item() <= 3e-2 * scale
+
+
 def test_flash_fwd_large_magnitude():
   """Scores with a large dynamic range exercise the lazy rescale path."""
   torch.manual_seed(5)

@@ -110,3 +110,55 @@ def test_embeddings_and_kernel_facade():
   q = torch.randn(1, 6, 2, 16)
   ref = torch.nn.functional.scaled_dot_product_attention(q.transpose(1, 2), q.transpose(1, 2), q.transpose(1, 2)).transpose(1, 2)
   assert torch.allclose(kernels.get_attention_kernel("tokamax_flash")(q, q, q), ref, atol=1e-5)
+
+
+def test_fixed_m_plan_gate_smoothing_and_reference():
+  """Fixed-exponent softmax: the bound dominates every score, heads over the gate stay online, smoothed keys give
+  the same softmax, and the fp32 restatement with the fixed exponents equals plain attention."""
+  import math
+
+  from maxdiffusion_b200.ops import fixed_m as FM
+
+  torch.manual_seed(0)
+  B, S, H, D = 2, 50, 4, 16
+  q = torch.randn(B, S, H, D)
+  k = torch.randn(B, 70, H, D) + 0.5
+  v = torch.randn(B, 70, H, D)
+  q[:, :, 3] *= 30
+  ks = FM.smooth_keys(k)
+  assert ks.mean(dim=1).abs().max() < 1e-5
+  m_fixed, heads = FM.plan(q, ks)
+  assert heads.tolist() == [1, 1, 1, 0] and m_fixed.shape == (B, H, S)
+  c = FM.LOG2E / math.sqrt(D)
+  s = torch.einsum("bqhd,bkhd->bhqk", q, ks) * c
+  assert (s.amax(-1) - m_fixed <= FM.RECENTER).all()  # exp2 never sees more than the re-centring constant
+  assert (s.amax(-1) - m_fixed)[:, :3].min() > -126  # the largest term of a row of an eligible head survives
+  want = torch.nn.functional.scaled_dot_product_attention(q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2)).transpose(1, 2)
+  assert torch.allclose(FM.reference_attention(q, ks, v, None, (m_fixed, heads)), want, atol=1e-4)
+  # unsmoothed segments use the halved gate
+  q2 = q.clone()
+  q2[:, :, 2] *= 9
+  _, heads_smoothed = FM.plan(q2, ks)
+  _, heads_ring = FM.plan(q2, [k[:, :30], k[:, 30:]], smoothed=False)
+  assert heads_ring.sum() <= heads_smoothed.sum()
+  got = FM.reference_attention(q, [k[:, :30], k[:, 30:]], [v[:, :30], v[:, 30:]], None,
+                               FM.plan(q, [k[:, :30], k[:, 30:]], smoothed=False))
+  assert torch.allclose(got, want, atol=1e-4)
+
+
+def test_fixed_m_kernel_names_select_the_fixed_exponent_context():
+  from maxdiffusion_b200 import common_types
+  from maxdiffusion_b200.kernels import get_attention_kernel
+  from maxdiffusion_b200.parallel.context import ContextParallel
+  from maxdiffusion_b200.parallel.mesh import create_device_mesh
+
+  assert set(common_types.FIXED_M_KERNELS) == {"ulysses_custom_fixed_m", "ulysses_ring_custom_fixed_m"}
+  mesh = create_device_mesh()
+  ctx = ContextParallel(mesh, "ulysses", fixed_m=True)
+  assert ctx.fixed_m
+  q = torch.randn(1, 12, 2, 16)
+  # on CPU the exact SDPA path runs; the fixed-exponent option must not change the result
+  want = torch.nn.functional.scaled_dot_product_attention(q.transpose(1, 2), q.transpose(1, 2), q.transpose(1, 2)).transpose(1, 2)
+  assert torch.allclose(ctx.self_attention(q, q, q), want, atol=1e-5)
+  fn = get_attention_kernel("ulysses_custom_fixed_m", mesh)
+  assert torch.allclose(fn(q, q, q), want, atol=1e-5)

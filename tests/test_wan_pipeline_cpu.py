@@ -78,6 +78,38 @@ def test_cache_schedules():
   assert torch.allclose(CP.fft_compensate(x, x, x, 1.2, 1.0), x, atol=1e-5)  # zero bias -> identity
 
 
+@pytest.mark.parametrize("shape", [(1, 4, 3, 90, 160), (2, 3, 2, 45, 80), (1, 2, 1, 31, 53), (1, 1, 1, 3, 5)])
+def test_band_filter_as_two_gemms_matches_the_fft_form(shape):
+  """The GEMM form of the CFG-cache compensation equals rfft2 -> band weights -> irfft2 (even, odd, tiny sizes)."""
+  from maxdiffusion_b200.ops import dft
+
+  torch.manual_seed(0)
+  a, b, c = (torch.randn(shape) for _ in range(3))
+  for w1, w2 in ((1.2, 1.0), (1.0, 1.2), (0.7, 0.7)):
+    got = CP.fft_compensate(a, b, c, w1, w2)
+    want = CP.fft_compensate_reference(a, b, c, w1, w2)
+    assert torch.allclose(got, want, atol=2e-5), (got - want).abs().max()
+  # the projector is idempotent and symmetric, and keeps the mean (frequency 0)
+  p = dft.band_projector(shape[-2], max(1, shape[-2] // 4), False)
+  assert torch.allclose(p @ p, p, atol=1e-5) and torch.allclose(p, p.T, atol=1e-6)
+  assert torch.allclose(p.sum(1), torch.ones(shape[-2]), atol=1e-5)
+
+
+def test_split_bf16_product_keeps_fp32_accuracy():
+  """[x_hi|x_lo|x_hi]·[P_hi|P_hi|P_lo]ᵀ with bf16 operands and fp32 accumulation is within 1e-4 of the fp32 product."""
+  from maxdiffusion_b200.ops import dft
+
+  torch.manual_seed(1)
+  x = torch.randn(64, 160)
+  p = dft.band_projector(160, 20, True)
+  x_hi, x_lo = dft._split_bf16(x)
+  p_hi, p_lo = dft._split_bf16(p)
+  a = torch.cat([x_hi, x_lo, x_hi], 1).float()
+  b = torch.cat([p_hi, p_hi, p_lo], 1).float()
+  assert (a @ b.T - x @ p).abs().max() < 1e-4
+  assert (x_hi.float() @ p_hi.float().T - x @ p).abs().max() > 1e-3  # a single bf16 product is not enough
+
+
 def test_wan22_vae_chunked_matches_whole_clip_and_patchify_round_trip():
   from maxdiffusion_b200.models.wan.autoencoder_kl_wan_2p2 import (AutoencoderKLWan2p2, WanAvgDown3D, WanDupUp3D,
                                                                     WanVAE2p2Config, patchify, unpatchify)
