@@ -153,6 +153,8 @@ class LTX2Attention(nn.Module):
     q4, k4, v4 = q.view(B, S, H, D), k.view(B, k.shape[1], H, D), v.view(B, v.shape[1], H, D)
     if attention_mask is None:
       o = OF.attention(q4, k4, v4)
+    elif attention_mask.dtype == torch.bool and attention_mask.dim() == 2:
+      o = OF.attention(q4, k4, v4, keep_mask=attention_mask)  # kept keys are compacted for the flash kernel
     else:
       o = F.scaled_dot_product_attention(q4.transpose(1, 2), k4.transpose(1, 2), v4.transpose(1, 2),
                                          attn_mask=attention_mask[:, None, None, :]).transpose(1, 2)

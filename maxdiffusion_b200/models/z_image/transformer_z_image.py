@@ -119,6 +119,8 @@ class ZImageAttention(nn.Module):
       q, k = _rope_interleaved(q, cos, sin), _rope_interleaved(k, cos, sin)
     if mask is None:
       o = OF.attention(q, k, v)
+    elif mask.dtype == torch.bool and mask.dim() == 2:
+      o = OF.attention(q, k, v, keep_mask=mask)  # kept keys are compacted for the flash kernel
     else:
       o = F.scaled_dot_product_attention(q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2),
                                          attn_mask=mask[:, None, None, :]).transpose(1, 2)

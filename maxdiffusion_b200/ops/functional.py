@@ -181,17 +181,64 @@ class _AttentionFn(torch.autograd.Function):
     return (dq, None, None, None, *dks, *dvs)
 
 
-def attention(q, k, v, scale: float | None = None, fixed_m=None):
-  """Softmax attention, no mask. q: [B,Sq,H,D]; k, v: [B,Skv,H,D] or equal-length lists of KV segments.
+_KEPT: dict = {}
+
+
+def _kept_indices(keep: torch.Tensor):
+  """Per batch row, the indices of the kept keys (one host synchronisation per mask tensor, then cached on the
+  tensor object and its version counter: the same mask serves every layer and step of a sampling loop)."""
+  import weakref
+
+  hit = _KEPT.get(id(keep))
+  if hit is not None and hit[0]() is keep and hit[1] == keep._version:
+    return hit[2]
+  if len(_KEPT) >= 32:
+    _KEPT.clear()
+  idx = [keep[b].nonzero(as_tuple=True)[0] for b in range(keep.shape[0])]
+  _KEPT[id(keep)] = (weakref.ref(keep), keep._version, idx)
+  return idx
+
+
+def attention(q, k, v, scale: float | None = None, fixed_m=None, keep_mask=None):
+  """Softmax attention. q: [B,Sq,H,D]; k, v: [B,Skv,H,D] or equal-length lists of KV segments.
 
   `fixed_m` (from `ops.fixed_m.plan`) runs the marked heads of the flash kernel with a fixed softmax exponent; the
   result and the saved log-sum-exp are those of the plain softmax, so the backward is unchanged. Paths that do
-  not run the flash kernel ignore it."""
+  not run the flash kernel ignore it.
+
+  `keep_mask` (bool [B,Skv], True = attend) drops keys per batch row. On the flash path the kept keys of a row are
+  compacted and the kernel runs on the shorter sequence (dropped keys cost nothing); a row without kept keys
+  yields zeros. Elsewhere the mask goes to SDPA."""
   ks = list(k) if isinstance(k, (list, tuple)) else [k]
   vs = list(v) if isinstance(v, (list, tuple)) else [v]
   D = q.shape[-1]
   scale = scale if scale is not None else 1.0 / math.sqrt(D)
-  if _fast(q) and D in K.FLASH_HEAD_DIMS:
+  if _fast(q) and D not in K.FLASH_HEAD_DIMS and D < max(K.FLASH_HEAD_DIMS) and D % 8 == 0:
+    # other head sizes (Stable Diffusion 1.x / 2.x: 40, 80) ride the next built size: zero channels add nothing to
+    # q.k and produce zero output channels, which are cut off again; the scale stays that of the true size
+    Dp = min(d for d in K.FLASH_HEAD_DIMS if d > D)
+    pad = lambda t: F.pad(t, (0, Dp - D))
+    out = attention(pad(q), [pad(t) for t in ks], [pad(t) for t in vs], scale, None, keep_mask)
+    return out[..., :D]
+  fast = _fast(q) and D in K.FLASH_HEAD_DIMS
+  if keep_mask is not None:
+    assert keep_mask.dtype == torch.bool and keep_mask.dim() == 2 and len(ks) == 1
+    kc, vc = ks[0], vs[0]
+    if not fast:
+      out = F.scaled_dot_product_attention(q.transpose(1, 2), kc.transpose(1, 2), vc.transpose(1, 2),
+                                           attn_mask=keep_mask[:, None, None, :], scale=scale)
+      return out.transpose(1, 2)
+    rows = []
+    for b, idx in enumerate(_kept_indices(keep_mask)):
+      if idx.numel() == 0:
+        rows.append(torch.zeros_like(q[b:b + 1]))
+      elif idx.numel() == kc.shape[1]:
+        rows.append(_AttentionFn.apply(q[b:b + 1], scale, 1, None, kc[b:b + 1], vc[b:b + 1]))
+      else:
+        rows.append(_AttentionFn.apply(q[b:b + 1], scale, 1, None, kc[b:b + 1].index_select(1, idx),
+                                       vc[b:b + 1].index_select(1, idx)))
+    return rows[0] if len(rows) == 1 else torch.cat(rows, dim=0)
+  if fast:
     return _AttentionFn.apply(q, scale, len(ks), fixed_m, *ks, *vs)
   kc = torch.cat(ks, dim=1) if len(ks) > 1 else ks[0]
   vc = torch.cat(vs, dim=1) if len(vs) > 1 else vs[0]

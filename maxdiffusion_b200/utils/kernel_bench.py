@@ -99,6 +99,27 @@ def bench_flash(results):
     del q, k, v
 
 
+def bench_flash_fixed_m(results):
+  """Plain against fixed-exponent softmax on the same tensors (all heads eligible), plus the cost of the plan."""
+  from ..ops import fixed_m as FM
+
+  tf_peak, _, tag = peaks()
+  for B, H, Sq, Skv in [(1, 40, 8192, 8192), (1, 40, 32760, 32760)]:
+    q = torch.randn((B, Sq, H, 128), device="cuda", dtype=torch.bfloat16)
+    k = FM.smooth_keys(torch.randn((B, Skv, H, 128), device="cuda", dtype=torch.bfloat16))
+    v = torch.randn((B, Skv, H, 128), device="cuda", dtype=torch.bfloat16)
+    plan = FM.plan(q, k)
+    base, _ = time_ms(lambda: K.flash_fwd(q, k, v), iters=5)
+    fixed, _ = time_ms(lambda: K.flash_fwd(q, k, v, fixed_m=plan), iters=5)
+    plan_ms, _ = time_ms(lambda: FM.plan(q, FM.smooth_keys(k)), iters=5)
+    fl = 4.0 * B * H * Sq * Skv * 128
+    results.append(dict(kernel="flash_fwd_fixed_m", shape=[B, H, Sq, Skv], eligible_heads=int(plan[1].sum()),
+                        plain_ms=base, fixed_ms=fixed, plan_and_smoothing_ms=plan_ms, fixed_tflops=fl / fixed / 1e9,
+                        fixed_frac=fl / fixed / 1e9 / tf_peak, of=tag))
+    print(results[-1], flush=True)
+    del q, k, v, plan
+
+
 def bench_flash_d64(results):
   """head_dim 64 (SDXL self-attention shapes: batch 8, 10 heads x 4096 tokens and 20 heads x 1024 tokens; LTX-Video
   2B: 32 heads) forward and backward, with PyTorch SDPA on the same tensors for comparison."""
@@ -157,6 +178,23 @@ def bench_rowwise(results):
   results.append(dict(kernel="rms_rope_fwd", shape=[B, S, C], ms=med, gbs=nbytes / med / 1e6,
                       frac=nbytes / med / 1e6 / bw_peak, of=tag))
   print(results[-1], flush=True)
+  # backward kernels: read dy and x, write dx (3 passes of 2 B/element), column sums folded by a second launch
+  dy = torch.randn_like(x)
+  _, mean, rstd = K.ln_fwd(x, None, None, sc, sc, save_stats=True)
+  med, best = time_ms(lambda: K.ln_bwd(dy, x, mean, rstd, None, sc))
+  nb3 = 3 * x.numel() * 2
+  results.append(dict(kernel="ln_mod_bwd", shape=[B, S, C], ms=med, gbs=nb3 / med / 1e6,
+                      frac=nb3 / med / 1e6 / bw_peak, of=tag))
+  print(results[-1], flush=True)
+  _, rr = K.rms_rope_fwd(x, w, cos, cos, heads=40, save_stats=True)
+  med, best = time_ms(lambda: K.rms_rope_bwd(dy.view(B, S, 40, 128), x, rr, w, cos, cos))
+  results.append(dict(kernel="rms_rope_bwd", shape=[B, S, C], ms=med, gbs=nb3 / med / 1e6,
+                      frac=nb3 / med / 1e6 / bw_peak, of=tag))
+  print(results[-1], flush=True)
+  med, best = time_ms(lambda: K.colsum(x.view(S, C)))
+  results.append(dict(kernel="colsum", shape=[S, C], ms=med, gbs=x.numel() * 2 / med / 1e6,
+                      frac=x.numel() * 2 / med / 1e6 / bw_peak, of=tag))
+  print(results[-1], flush=True)
 
 
 def profile_case():
@@ -184,7 +222,7 @@ def profile_case():
 def main(argv):
   if "profile" in argv:
     return profile_case()
-  which = [a for a in argv if not a.startswith("--")] or ["gemm", "flash", "rowwise"]
+  which = [a for i, a in enumerate(argv) if not a.startswith("--") and (i == 0 or argv[i - 1] != "--json")] or ["gemm", "flash", "rowwise"]
   results = []
   if "gemm" in which:
     bench_gemm(results)
@@ -196,6 +234,8 @@ def main(argv):
     bench_flash_bwd(results)
   if "flash_d64" in which:
     bench_flash_d64(results)
+  if "flash_fixed_m" in which:
+    bench_flash_fixed_m(results)
   if "rowwise" in which:
     bench_rowwise(results)
   if "--json" in argv:

@@ -132,6 +132,50 @@ def test_flash_fwd_fixed_m(B, H, Sq, Skv, D):
     assert (a.grad.float() - b.grad.float()).abs().max().item() <= 3e-2 * scale
 
 
+@pytest.mark.parametrize("D", [128, 64])
+def test_attention_keep_mask_compacts_keys_for_the_flash_kernel(D):
+  """[B,Skv] keep-mask: prefix-, suffix- and scattered-dropped keys, one row fully kept; forward and gradients
+  against fp32 masked softmax."""
+  from maxdiffusion_b200.ops import functional as OF
+
+  torch.manual_seed(17)
+  B, H, Sq, Skv = 3, 4, 200, 333
+  q, k, v = (torch.randn((B, S, H, D), device=DEV, dtype=torch.bfloat16, requires_grad=True) for S in (Sq, Skv, Skv))
+  keep = torch.ones((B, Skv), device=DEV, dtype=torch.bool)
+  keep[0, 250:] = False
+  keep[0, :9] = False
+  keep[1, ::3] = False
+  out = OF.attention(q, k, v, keep_mask=keep)
+  qf, kf, vf = (t.detach().float().requires_grad_(True) for t in (q, k, v))
+  s = torch.einsum("bqhd,bkhd->bhqk", qf, kf) / D ** 0.5
+  s = s.masked_fill(~keep[:, None, None, :], float("-inf"))
+  want = torch.einsum("bhqk,bkhd->bqhd", s.softmax(-1), vf)
+  _report(f"attention keep-mask D{D}", out, want, rel_tol=2e-2, abs_frac=5e-2)
+  g = torch.randn_like(out)
+  out.backward(g)
+  want.backward(g.float())
+  for got, ref_t in ((q, qf), (k, kf), (v, vf)):
+    scale = ref_t.grad.abs().max().item() + 1e-6
+    assert (got.grad.float() - ref_t.grad).abs().max().item() <= 4e-2 * scale
+  assert k.grad[0, 250:].abs().max().item() == 0.0  # dropped keys receive no gradient
+
+
+@pytest.mark.parametrize("D", [40, 80, 96])
+def test_attention_other_head_sizes_ride_the_padded_kernel(D):
+  from maxdiffusion_b200.ops import functional as OF
+
+  torch.manual_seed(19)
+  B, H, Sq, Skv = 2, 5, 260, 77
+  q, k, v = (torch.randn((B, S, H, D), device=DEV, dtype=torch.bfloat16, requires_grad=True) for S in (Sq, Skv, Skv))
+  before = _lib.launch_count()
+  out = OF.attention(q, k, v)
+  assert _lib.launch_count() > before and out.shape == (B, Sq, H, D)
+  want = ref.attention(q.detach(), k.detach(), v.detach())
+  _report(f"attention head_dim {D} (padded)", out, want.float(), rel_tol=2e-2, abs_frac=5e-2)
+  out.float().square().sum().backward()
+  assert q.grad.shape == q.shape and torch.isfinite(q.grad.float()).all() and k.grad.abs().max() > 0
+
+
 def test_flash_fwd_large_magnitude():
   """Scores with a large dynamic range exercise the lazy rescale path."""
   torch.manual_seed(5)
