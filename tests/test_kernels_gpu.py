@@ -113,7 +113,9 @@ def test_flash_fwd_fixed_m(B, H, Sq, Skv, D):
   assert plan[1].tolist() == [1] * (H - 1) + [0]
   out, lse = K.flash_fwd(q, ks, v, fixed_m=plan)
   base, base_lse = K.flash_fwd(q, ks, v)
-  want = ref.attention(q, k, v)  # smoothing the keys does not change the softmax
+  # the oracle sees the same (bf16-rounded) smoothed keys: the sink head's huge logits would amplify the rounding
+  # difference between k and k - mean(k); that smoothing leaves the softmax unchanged is checked in fp32 on the CPU
+  want = ref.attention(q, ks, v)
   _report(f"flash_fwd fixed-m D{D} B{B} H{H} Sq{Sq} Skv{Skv}", out, want.float(), rel_tol=2e-2, abs_frac=5e-2)
   assert (out.float() - base.float()).abs().max().item() < 2e-2
   assert (lse - base_lse).abs().max().item() < 2e-2
@@ -121,7 +123,8 @@ def test_flash_fwd_fixed_m(B, H, Sq, Skv, D):
   cut = Skv // 3
   plan2 = FM.plan(q, [k[:, :cut], k[:, cut:]], smoothed=False)
   out2, _ = K.flash_fwd(q, [k[:, :cut], k[:, cut:]], [v[:, :cut], v[:, cut:]], fixed_m=plan2)
-  _report("flash_fwd fixed-m, two unsmoothed segments", out2, want.float(), rel_tol=2e-2, abs_frac=5e-2)
+  _report("flash_fwd fixed-m, two unsmoothed segments", out2, ref.attention(q, k, v).float(), rel_tol=2e-2,
+          abs_frac=5e-2)
   # autograd through functional.attention: the backward kernels only need the true lse
   qg, kg, vg = (t.clone().requires_grad_(True) for t in (q, ks, v))
   OF.attention(qg, kg, vg, fixed_m=plan).float().square().sum().backward()
