@@ -37,16 +37,18 @@ LOG2E = 1.4426950408889634
 def smooth_keys(k: torch.Tensor) -> torch.Tensor:
   """k - mean over the sequence axis (per batch, head and channel). k: [B, S, H, D]. Softmax over the keys is
   unchanged because every score of a row moves by the same q_i . mean(k)."""
-  return k - k.float().mean(dim=1, keepdim=True).to(k.dtype)
+  return k - k.mean(dim=1, keepdim=True, dtype=torch.float32).to(k.dtype)
 
 
 def head_statistics(q: torch.Tensor, ks: Sequence[torch.Tensor], group=None):
   """(row norms of q as fp32 [B, H, Sq], max row norm of q per head [H], max row norm of the keys per head [H]);
   the two maxima include the margin and are max-reduced over `group`."""
   with torch.no_grad():
-    qn = torch.linalg.vector_norm(q.float(), dim=-1).permute(0, 2, 1).contiguous()  # [B, H, Sq]
+    # fp32 accumulation inside the reduction: no fp32 copy of q or k is materialised
+    qn = torch.linalg.vector_norm(q, dim=-1, dtype=torch.float32).permute(0, 2, 1).contiguous()  # [B, H, Sq]
     qmax = qn.amax(dim=(0, 2))
-    kmax = torch.stack([torch.linalg.vector_norm(k.float(), dim=-1).amax(dim=(0, 1)) for k in ks]).amax(dim=0)
+    kmax = torch.stack([torch.linalg.vector_norm(k, dim=-1, dtype=torch.float32).amax(dim=(0, 1))
+                        for k in ks]).amax(dim=0)
     both = torch.stack([qmax, kmax]) * NORM_MARGIN
     if group is not None and dist.is_initialized() and dist.get_world_size(group) > 1:
       dist.all_reduce(both, op=dist.ReduceOp.MAX, group=group)
