@@ -18,16 +18,16 @@ namespace mdb {
 
 namespace gemm {
 constexpr int BM = 128;
-constexpr int BN = 256;
 constexpr int BK = 64;
-constexpr int STAGES = 4;
 constexpr int A_BYTES = BM * BK * 2;  // 16 KiB
-constexpr int B_BYTES = BN * BK * 2;  // 32 KiB
-constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
 constexpr int NUM_THREADS = 192;
-constexpr int TMEM_COLS = 512;
 constexpr int GROUP_M = 8;
-constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*align slack*/ + 256 /*barriers*/;
+// The tile is 128 x BN with BN = 256 (the default) or 128. The narrower tile has the same tensor-pipe rate per FLOP
+// (a 128 x 128 x 16 instruction takes half the cycles of a 128 x 256 x 16 one) and is chosen by the host when the
+// 256-wide tiling would leave the last wave of the 148 persistent CTAs mostly empty (small M on many GPUs).
+__host__ __device__ constexpr int stages_for(int bn) { return bn == 256 ? 4 : 6; }                    // 4 x 48 KiB or 6 x 32 KiB
+__host__ __device__ constexpr int stage_bytes(int bn) { return A_BYTES + bn * BK * 2; }
+__host__ __device__ constexpr int smem_bytes(int bn) { return stages_for(bn) * stage_bytes(bn) + 1024 /*align slack*/ + 256 /*barriers*/; }
 
 enum Epilogue : int {
   kEpiNone = 0,       // out = acc*alpha + bias
@@ -65,9 +65,12 @@ __device__ __forceinline__ void tile_coords(int tile, int num_m, int num_n, int&
   n_idx = local / rows;
 }
 
-template <bool A_MN, bool B_MN>
+template <bool A_MN, bool B_MN, int BN>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b, const Params p) {
+  constexpr int STAGES = stages_for(BN);
+  constexpr int STAGE_BYTES = stage_bytes(BN);
+  constexpr int TMEM_COLS = 2 * BN;  // two accumulators
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES * STAGE_BYTES);
@@ -281,22 +284,38 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
   }
 }
 
-template <bool A_MN, bool B_MN>
+template <bool A_MN, bool B_MN, int BN>
 int launch(const CUtensorMap& ta, const CUtensorMap& tb, const Params& p, cudaStream_t stream) {
-  auto kern = gemm_kernel<A_MN, B_MN>;
+  auto kern = gemm_kernel<A_MN, B_MN, BN>;
   static bool configured = false;
   if (!configured) {
-    MDB_CHECK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
+    MDB_CHECK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes(BN)));
     configured = true;
   }
   const int num_tiles = ((p.M + BM - 1) / BM) * ((p.N + BN - 1) / BN);
   const int grid = num_tiles < sm_count() ? num_tiles : sm_count();
-  kern<<<grid, NUM_THREADS, SMEM_BYTES, stream>>>(ta, tb, p);
+  kern<<<grid, NUM_THREADS, smem_bytes(BN), stream>>>(ta, tb, p);
   return static_cast<int>(cudaGetLastError());
+}
+
+// Fraction of the persistent CTAs' time that holds work when `tiles` equal tiles run on `sms` CTAs.
+static double wave_efficiency(long long tiles, int sms) {
+  const long long waves = (tiles + sms - 1) / sms;
+  return static_cast<double>(tiles) / static_cast<double>(waves * sms);
+}
+// 256 unless the 128-wide tiling fills the waves at least 5 % better (and there is more than one wave of work).
+static int pick_tile_n(int M, int N) {
+  const int sms = sm_count();
+  const long long m_tiles = (M + BM - 1) / BM;
+  const long long t256 = m_tiles * ((N + 255) / 256), t128 = m_tiles * ((N + 127) / 128);
+  if (t256 < sms) return 256;
+  return wave_efficiency(t128, sms) > wave_efficiency(t256, sms) + 0.05 ? 128 : 256;
 }
 
 }  // namespace gemm
 }  // namespace mdb
+
+static int g_force_tile_n = 0;
 
 // C entry point. A is [M,K] with leading dimension lda (a_mn_major = 0) or [K,M] (a_mn_major = 1);
 // B is [N,K] (b_mn_major = 0) or [K,N] (b_mn_major = 1). All leading dimensions are in elements and
@@ -308,6 +327,7 @@ extern "C" int mdb_gemm_bf16(const void* A, const void* B, void* out, const void
   using namespace mdb;
   using namespace mdb::gemm;
   if (M <= 0 || N <= 0 || K <= 0) return 0;
+  const int BN = g_force_tile_n ? g_force_tile_n : pick_tile_n(M, N);
   if ((N & 7) || (lda & 7) || (ldb & 7) || (ldo & 3) || (!out_f32 && (ldo & 7))) return 3001;
   if ((epi == kEpiGatedRes || epi == kEpiAddRes) && (!residual || (ldr & 7))) return 3002;
   if (epi == kEpiGatedRes && (!gate || (gate_ld & 3))) return 3003;
@@ -333,7 +353,7 @@ extern "C" int mdb_gemm_bf16(const void* A, const void* B, void* out, const void
   } else {
     uint64_t dims[2] = {static_cast<uint64_t>(K), static_cast<uint64_t>(N)};
     uint64_t str[1] = {static_cast<uint64_t>(ldb) * 2};
-    uint32_t box[2] = {BK, BN};
+    uint32_t box[2] = {BK, static_cast<uint32_t>(BN)};
     rc = encode_tmap_bf16(&tb, B, 2, dims, str, box);
   }
   if (rc) return rc;
@@ -351,8 +371,21 @@ extern "C" int mdb_gemm_bf16(const void* A, const void* B, void* out, const void
   p.alpha = alpha;
   p.status = status_buffer();
   cudaStream_t stream = static_cast<cudaStream_t>(stream_ptr);
-  if (a_mn_major) {
-    return b_mn_major ? launch<true, true>(ta, tb, p, stream) : launch<true, false>(ta, tb, p, stream);
+  if (BN == 256) {
+    if (a_mn_major) {
+      return b_mn_major ? launch<true, true, 256>(ta, tb, p, stream) : launch<true, false, 256>(ta, tb, p, stream);
+    }
+    return b_mn_major ? launch<false, true, 256>(ta, tb, p, stream) : launch<false, false, 256>(ta, tb, p, stream);
   }
-  return b_mn_major ? launch<false, true>(ta, tb, p, stream) : launch<false, false>(ta, tb, p, stream);
+  if (a_mn_major) {
+    return b_mn_major ? launch<true, true, 128>(ta, tb, p, stream) : launch<true, false, 128>(ta, tb, p, stream);
+  }
+  return b_mn_major ? launch<false, true, 128>(ta, tb, p, stream) : launch<false, false, 128>(ta, tb, p, stream);
+}
+
+// 0: choose per problem (default); 128 or 256: use that tile width (benchmarks and tests).
+extern "C" int mdb_gemm_force_tile_n(int bn) {
+  if (bn != 0 && bn != 128 && bn != 256) return 3004;
+  g_force_tile_n = bn;
+  return 0;
 }

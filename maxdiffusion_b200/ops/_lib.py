@@ -105,6 +105,8 @@ def _declare(L: ctypes.CDLL) -> None:
   L.mdb_sm_count.restype = c_int
   L.mdb_gemm_bf16.argtypes = [c_void_p] * 6 + [c_int] * 3 + [c_ll] * 5 + [c_int] * 5 + [c_float, c_void_p]
   L.mdb_gemm_bf16.restype = c_int
+  L.mdb_gemm_force_tile_n.argtypes = [c_int]
+  L.mdb_gemm_force_tile_n.restype = c_int
   L.mdb_flash_fwd.argtypes = ([c_void_p, ctypes.POINTER(c_void_p), ctypes.POINTER(c_void_p), c_void_p, c_void_p]
                               + [c_int] * 4 + [ctypes.POINTER(c_int)] + [c_ll] * 12 + [c_float, c_void_p, ctypes.c_uint,
                                                                                       c_void_p, c_void_p])

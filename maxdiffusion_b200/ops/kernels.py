@@ -53,6 +53,12 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = F
   return out
 
 
+def gemm_force_tile_n(bn: int = 0) -> None:
+  """Tile width of the bf16 GEMM: 0 lets the launcher choose per problem (256 unless 128 fills the waves of the
+  persistent CTAs at least 5 % better), 128 / 256 pin it (benchmarks, tests)."""
+  _lib.check(_lib.lib().mdb_gemm_force_tile_n(int(bn)), "mdb_gemm_force_tile_n")
+
+
 FLASH_HEAD_DIMS = (64, 128)
 
 

@@ -69,6 +69,34 @@ def bench_gemm(results):
     del a, b, out
 
 
+def bench_gemm_small_m(results):
+  """The GEMM shapes of one rank of an 8-way sequence split (4095 tokens), 256- against 128-wide tiles, with the
+  launcher's own choice and cuBLAS beside them; forward, dgrad (B stored [K,N]) and wgrad (both operands transposed)."""
+  tf_peak, _, tag = peaks()
+  cases = [(4095, 5120, 5120, False, False), (4095, 15360, 5120, False, False), (4095, 13824, 5120, False, False),
+           (4095, 5120, 13824, False, False), (4095, 5120, 5120, False, True), (5120, 5120, 4095, True, True),
+           (13824, 5120, 4095, True, True), (8190, 5120, 5120, False, False)]
+  for M, N, Kd, a_mn, b_mn in cases:
+    a = torch.randn((Kd, M) if a_mn else (M, Kd), device="cuda", dtype=torch.bfloat16)
+    if a_mn and M % 8:
+      a = torch.randn((Kd, M + 8 - M % 8), device="cuda", dtype=torch.bfloat16)[:, :M]
+    b = torch.randn((Kd, N) if b_mn else (N, Kd), device="cuda", dtype=torch.bfloat16)
+    out = torch.empty((M, N), device="cuda", dtype=torch.bfloat16)
+    ms = {}
+    for bn in (256, 128, 0):
+      K.gemm_force_tile_n(bn)
+      ms[bn], _ = time_ms(lambda: K.gemm(a, b, a_mn=a_mn, b_mn=b_mn, out=out))
+    K.gemm_force_tile_n(0)
+    am, bm = (a.t() if a_mn else a), (b if b_mn else b.t())
+    lib_med, _ = time_ms(lambda: torch.matmul(am, bm, out=out))
+    fl = 2.0 * M * N * Kd
+    results.append(dict(kernel="gemm_bf16_small_m", shape=[M, N, Kd], a_mn=a_mn, b_mn=b_mn, ms_tile256=ms[256],
+                        ms_tile128=ms[128], ms_auto=ms[0], tflops_auto=fl / ms[0] / 1e9,
+                        frac_auto=fl / ms[0] / 1e9 / tf_peak, of=tag, cublas_ms=lib_med))
+    print(results[-1], flush=True)
+    del a, b, out
+
+
 def bench_gemm_fp8(results):
   tf_peak, _, tag = peaks()
   for M, N, Kd in [(32760, 5120, 5120), (32760, 13824, 5120), (4096, 5120, 5120)]:
@@ -226,6 +254,8 @@ def main(argv):
   results = []
   if "gemm" in which:
     bench_gemm(results)
+  if "gemm_small_m" in which:
+    bench_gemm_small_m(results)
   if "gemm_fp8" in which:
     bench_gemm_fp8(results)
   if "flash" in which:
