@@ -22,9 +22,10 @@ constexpr int BK = 64;
 constexpr int A_BYTES = BM * BK * 2;  // 16 KiB
 constexpr int NUM_THREADS = 192;
 constexpr int GROUP_M = 8;
-// The tile is 128 x BN with BN = 256 (the default) or 128. The narrower tile has the same tensor-pipe rate per FLOP
-// (a 128 x 128 x 16 instruction takes half the cycles of a 128 x 256 x 16 one) and is chosen by the host when the
-// 256-wide tiling would leave the last wave of the 148 persistent CTAs mostly empty (small M on many GPUs).
+// The tile is 128 x BN with BN = 256 (the default) or 128 (on request). The narrower tile fills the waves of the
+// 148 persistent CTAs better at small M, but it moves a third more operand bytes per FLOP from L2 into shared
+// memory and measured 1.3-1.5x SLOWER on every shape of an 8-way sequence split (4095 x 5120 x 5120: 0.228 ms
+// against 0.173 ms), so the launcher never picks it by itself: operand traffic, not wave fill, is the limit.
 __host__ __device__ constexpr int stages_for(int bn) { return bn == 256 ? 4 : 6; }                    // 4 x 48 KiB or 6 x 32 KiB
 __host__ __device__ constexpr int stage_bytes(int bn) { return A_BYTES + bn * BK * 2; }
 __host__ __device__ constexpr int smem_bytes(int bn) { return stages_for(bn) * stage_bytes(bn) + 1024 /*align slack*/ + 256 /*barriers*/; }
@@ -298,20 +299,6 @@ int launch(const CUtensorMap& ta, const CUtensorMap& tb, const Params& p, cudaSt
   return static_cast<int>(cudaGetLastError());
 }
 
-// Fraction of the persistent CTAs' time that holds work when `tiles` equal tiles run on `sms` CTAs.
-static double wave_efficiency(long long tiles, int sms) {
-  const long long waves = (tiles + sms - 1) / sms;
-  return static_cast<double>(tiles) / static_cast<double>(waves * sms);
-}
-// 256 unless the 128-wide tiling fills the waves at least 5 % better (and there is more than one wave of work).
-static int pick_tile_n(int M, int N) {
-  const int sms = sm_count();
-  const long long m_tiles = (M + BM - 1) / BM;
-  const long long t256 = m_tiles * ((N + 255) / 256), t128 = m_tiles * ((N + 127) / 128);
-  if (t256 < sms) return 256;
-  return wave_efficiency(t128, sms) > wave_efficiency(t256, sms) + 0.05 ? 128 : 256;
-}
-
 }  // namespace gemm
 }  // namespace mdb
 
@@ -327,7 +314,7 @@ extern "C" int mdb_gemm_bf16(const void* A, const void* B, void* out, const void
   using namespace mdb;
   using namespace mdb::gemm;
   if (M <= 0 || N <= 0 || K <= 0) return 0;
-  const int BN = g_force_tile_n ? g_force_tile_n : pick_tile_n(M, N);
+  const int BN = g_force_tile_n ? g_force_tile_n : 256;
   if ((N & 7) || (lda & 7) || (ldb & 7) || (ldo & 3) || (!out_f32 && (ldo & 7))) return 3001;
   if ((epi == kEpiGatedRes || epi == kEpiAddRes) && (!residual || (ldr & 7))) return 3002;
   if (epi == kEpiGatedRes && (!gate || (gate_ld & 3))) return 3003;
@@ -383,7 +370,7 @@ extern "C" int mdb_gemm_bf16(const void* A, const void* B, void* out, const void
   return b_mn_major ? launch<false, true, 128>(ta, tb, p, stream) : launch<false, false, 128>(ta, tb, p, stream);
 }
 
-// 0: choose per problem (default); 128 or 256: use that tile width (benchmarks and tests).
+// 0: the default width (256); 128 or 256: use that tile width (tile search, benchmarks, tests).
 extern "C" int mdb_gemm_force_tile_n(int bn) {
   if (bn != 0 && bn != 128 && bn != 256) return 3004;
   g_force_tile_n = bn;

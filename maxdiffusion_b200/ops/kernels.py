@@ -54,8 +54,7 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = F
 
 
 def gemm_force_tile_n(bn: int = 0) -> None:
-  """Tile width of the bf16 GEMM: 0 lets the launcher choose per problem (256 unless 128 fills the waves of the
-  persistent CTAs at least 5 % better), 128 / 256 pin it (benchmarks, tests)."""
+  """Tile width of the bf16 GEMM: 0 is the default (256), 128 / 256 pin it (tile search, benchmarks, tests)."""
   _lib.check(_lib.lib().mdb_gemm_force_tile_n(int(bn)), "mdb_gemm_force_tile_n")
 
 

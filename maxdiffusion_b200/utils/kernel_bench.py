@@ -71,7 +71,7 @@ def bench_gemm(results):
 
 def bench_gemm_small_m(results):
   """The GEMM shapes of one rank of an 8-way sequence split (4095 tokens), 256- against 128-wide tiles, with the
-  launcher's own choice and cuBLAS beside them; forward, dgrad (B stored [K,N]) and wgrad (both operands transposed)."""
+  default and cuBLAS beside them; forward, dgrad (B stored [K,N]) and wgrad (both operands transposed)."""
   tf_peak, _, tag = peaks()
   cases = [(4095, 5120, 5120, False, False), (4095, 15360, 5120, False, False), (4095, 13824, 5120, False, False),
            (4095, 5120, 13824, False, False), (4095, 5120, 5120, False, True), (5120, 5120, 4095, True, True),
