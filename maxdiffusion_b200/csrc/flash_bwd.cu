@@ -54,6 +54,12 @@ struct Params {
   long long o0_sb, o0_ss, o0_sh, o1_sb, o1_ss, o1_sh;
   int out_f32;
   float scale, scale_log2;
+  // DKV pass over several stacked KV segments in ONE launch (seg_batches > 0): blockIdx.z = seg * seg_batches + b
+  // selects the K/V rows; queries, dO, lse and delta are those of batch b for every segment; the outputs of segment
+  // seg go to slice (seg + out_rot) % n_seg of the output buffers, slices o_seg_stride elements apart.
+  int seg_batches, n_seg, out_rot;
+  int x_len_seg[MAX_SEGMENTS];
+  long long o_seg_stride;
   DeviceStatus* status;
 };
 
@@ -94,6 +100,15 @@ flash_bwd_kernel(const __grid_constant__ Maps maps, const Params p) {
   const int x0 = blockIdx.x * BX;
   const int head = blockIdx.y;
   const int batch = blockIdx.z;
+  int ybatch = batch;       // batch index of the streamed side, the statistics and the outputs
+  int x_len = p.x_len;      // valid rows of the resident side
+  long long o_base = 0;     // offset of the output slice
+  if (DKV && p.seg_batches > 0) {
+    const int seg = batch / p.seg_batches;
+    ybatch = batch - seg * p.seg_batches;
+    x_len = p.x_len_seg[seg];
+    o_base = static_cast<long long>((seg + p.out_rot) % p.n_seg) * p.o_seg_stride;
+  }
 
   int total_steps = 0;
   for (int s = 0; s < p.num_segments; ++s) total_steps += (p.y_len[s] + BY - 1) / BY;
@@ -138,7 +153,7 @@ flash_bwd_kernel(const __grid_constant__ Maps maps, const Params p) {
           tma_load_4d(sx2 + c * X_CHUNK_BYTES, &maps.x2, x_full, c * 64, head, x0, batch);
         }
       }
-      const long long stat_base = (static_cast<long long>(batch) * p.H + head) * p.q_len;
+      const long long stat_base = (static_cast<long long>(ybatch) * p.H + head) * p.q_len;
       // lse / delta of the streamed query rows ride in the stage. When the rows start on 16-byte boundaries they are
       // fetched by bulk copies that complete on the stage's barrier; otherwise the lanes copy them by hand.
       const bool stat_bulk = DKV && (p.q_len % 4 == 0) && ((reinterpret_cast<uintptr_t>(p.lse) & 15) == 0) &&
@@ -167,8 +182,8 @@ flash_bwd_kernel(const __grid_constant__ Maps maps, const Params p) {
             uint8_t* d2 = d1 + Y_TILE_BYTES;
             mbar_expect_tx(&y_full[stage], 2 * Y_TILE_BYTES + 2 * stat_bytes);
             for (int c = 0; c < CH; ++c) {
-              tma_load_4d(d1 + c * Y_CHUNK_BYTES, &maps.y1[seg], &y_full[stage], c * 64, head, jb * BY, batch);
-              tma_load_4d(d2 + c * Y_CHUNK_BYTES, &maps.y2[seg], &y_full[stage], c * 64, head, jb * BY, batch);
+              tma_load_4d(d1 + c * Y_CHUNK_BYTES, &maps.y1[seg], &y_full[stage], c * 64, head, jb * BY, ybatch);
+              tma_load_4d(d2 + c * Y_CHUNK_BYTES, &maps.y2[seg], &y_full[stage], c * 64, head, jb * BY, ybatch);
             }
             if (stat_bytes) {
               bulk_load_1d(st, p.lse + stat_base + jb * BY, stat_bytes, &y_full[stage]);
@@ -253,10 +268,10 @@ flash_bwd_kernel(const __grid_constant__ Maps maps, const Params p) {
     const int quarter = warp & 3;
     const int row_in_tile = quarter * 32 + lane;
     const int x_row = x0 + row_in_tile;
-    const bool row_ok = x_row < p.x_len;
+    const bool row_ok = x_row < x_len;
     const uint32_t lane_off = static_cast<uint32_t>(quarter * 32) << 16;
     if (total_steps > 0) {
-      const long long stat_base = (static_cast<long long>(batch) * p.H + head) * p.q_len;
+      const long long stat_base = (static_cast<long long>(ybatch) * p.H + head) * p.q_len;
       float lse_r = 0.0f, delta_r = 0.0f;
       if (!DKV && row_ok) {
         lse_r = p.lse[stat_base + x_row];
@@ -274,7 +289,7 @@ flash_bwd_kernel(const __grid_constant__ Maps maps, const Params p) {
           if (DKV) {
             if (!mbar_wait(&y_full[ystage], (i / Y_STAGES) & 1, abort_flag, p.status, 92)) { ok = false; break; }
           }
-          const bool full_tile = (valid == BY) && (x0 + BX <= p.x_len);  // uniform over the CTA
+          const bool full_tile = (valid == BY) && (x0 + BX <= x_len);  // uniform over the CTA
           const uint32_t t1a = tmem_base + lane_off + b * 64 + wg * 16;
           const uint32_t t2a = tmem_base + lane_off + T2C + b * 64 + wg * 16;
           // ---- phase 1: P of this thread's 16 columns from the first score tile
@@ -378,7 +393,7 @@ flash_bwd_kernel(const __grid_constant__ Maps maps, const Params p) {
           void* outp = a == 0 ? p.out0 : p.out1;
           const long long sb = a == 0 ? p.o0_sb : p.o1_sb, ss = a == 0 ? p.o0_ss : p.o1_ss,
                           sh = a == 0 ? p.o0_sh : p.o1_sh;
-          const long long off = batch * sb + static_cast<long long>(x_row) * ss + head * sh;
+          const long long off = o_base + ybatch * sb + static_cast<long long>(x_row) * ss + head * sh;
 #pragma unroll 1
           for (int c = 0; c < CH; ++c) {
             const int col0 = wg * (D / 4) + c * 16;
@@ -494,13 +509,17 @@ static int flash_bwd_dkv_launch(const void* q, const void* d_o, const void* k, c
                                 const float* delta, void* dk, void* dv, int B, int H, int q_len, int kv_len,
                                 const long long* qs, const long long* gs, const long long* ks, const long long* vs,
                                 const long long* dks, const long long* dvs, float softmax_scale, int out_f32,
-                                void* stream) {
+                                void* stream, int n_seg = 0, const int* seg_lens = nullptr, int out_rot = 0,
+                                long long o_seg_stride = 0) {
   if (B <= 0 || H <= 0 || q_len <= 0 || kv_len <= 0) return 0;
+  if (n_seg < 0 || n_seg > MAX_SEGMENTS || (n_seg > 0 && seg_lens == nullptr)) return 3250;
+  // stacked form: K and V are [n_seg * B, kv_len, H, D] with one batch stride across segments
+  const int x_batches = n_seg > 0 ? n_seg * B : B;
   Maps maps;
   Params p;
-  int rc = make_map_d<HD>(&maps.x1, k, B, kv_len, H, ks[0], ks[1], ks[2], BX);
+  int rc = make_map_d<HD>(&maps.x1, k, x_batches, kv_len, H, ks[0], ks[1], ks[2], BX);
   if (rc) return rc;
-  rc = make_map_d<HD>(&maps.x2, v, B, kv_len, H, vs[0], vs[1], vs[2], BX);
+  rc = make_map_d<HD>(&maps.x2, v, x_batches, kv_len, H, vs[0], vs[1], vs[2], BX);
   if (rc) return rc;
   for (int s = 0; s < MAX_SEGMENTS; ++s) {
     rc = make_map_d<HD>(&maps.y1[s], q, B, q_len, H, qs[0], qs[1], qs[2], BY);
@@ -517,13 +536,22 @@ static int flash_bwd_dkv_launch(const void* q, const void* d_o, const void* k, c
   p.out_f32 = out_f32;
   p.scale = softmax_scale;
   p.scale_log2 = softmax_scale * 1.4426950408889634f;
+  p.seg_batches = n_seg > 0 ? B : 0;
+  p.n_seg = n_seg > 0 ? n_seg : 1;
+  p.out_rot = n_seg > 0 ? ((out_rot % n_seg) + n_seg) % n_seg : 0;
+  p.o_seg_stride = o_seg_stride;
+  for (int s = 0; s < MAX_SEGMENTS; ++s) {
+    const int len = (s < n_seg) ? seg_lens[s] : 0;
+    if (len < 0 || len > kv_len) return 3250;
+    p.x_len_seg[s] = len;
+  }
   p.status = status_buffer();
   static bool configured = false;
   if (!configured) {
     MDB_CHECK_CUDA(cudaFuncSetAttribute(flash_bwd_kernel<true, HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes<HD>()));
     configured = true;
   }
-  dim3 grid((kv_len + BX - 1) / BX, H, B);
+  dim3 grid((kv_len + BX - 1) / BX, H, x_batches);
   flash_bwd_kernel<true, HD><<<grid, NUM_THREADS, smem_bytes<HD>(), static_cast<cudaStream_t>(stream)>>>(maps, p);
   return static_cast<int>(cudaGetLastError());
 }
@@ -553,6 +581,8 @@ static int flash_bwd_dq_launch(const void* q, const void* d_o, const void* const
     p.y_len[s] = s < num_segments ? kv_lens[s] : 0;
   }
   p.B = B; p.H = H; p.x_len = q_len; p.num_segments = num_segments;
+  p.seg_batches = 0; p.n_seg = 1; p.out_rot = 0; p.o_seg_stride = 0;
+  for (int s = 0; s < MAX_SEGMENTS; ++s) p.x_len_seg[s] = 0;
   p.lse = lse; p.delta = delta; p.q_len = q_len;
   p.out0 = dq; p.out1 = nullptr;
   p.o0_sb = dqs[0]; p.o0_ss = dqs[1]; p.o0_sh = dqs[2];
@@ -585,6 +615,15 @@ static int flash_bwd_dq_launch(const void* q, const void* d_o, const void* const
                                            const long long* dvs, float softmax_scale, int out_f32, void* stream) {        \
     return flash_bwd_dkv_launch<HD>(q, d_o, k, v, lse, delta, dk, dv, B, H, q_len, kv_len, qs, gs, ks, vs, dks, dvs,      \
                                     softmax_scale, out_f32, stream);                                                      \
+  }                                                                                                                       \
+  extern "C" int mdb_flash_bwd_dkv_stacked##SUFFIX(                                                                      \
+      const void* q, const void* d_o, const void* k, const void* v, const float* lse, const float* delta, void* dk,       \
+      void* dv, int B, int H, int q_len, int kv_len, const long long* qs, const long long* gs, const long long* ks,       \
+      const long long* vs, const long long* dks, const long long* dvs, float softmax_scale, int out_f32, void* stream,    \
+      int n_seg, const int* seg_lens, int out_rot, long long o_seg_stride) {                                              \
+    if (n_seg < 1) return 3250;                                                                                           \
+    return flash_bwd_dkv_launch<HD>(q, d_o, k, v, lse, delta, dk, dv, B, H, q_len, kv_len, qs, gs, ks, vs, dks, dvs,      \
+                                    softmax_scale, out_f32, stream, n_seg, seg_lens, out_rot, o_seg_stride);              \
   }                                                                                                                       \
   extern "C" int mdb_flash_bwd_dq##SUFFIX(const void* q, const void* d_o, const void* const* k_ptrs,                      \
                                           const void* const* v_ptrs, const float* lse, const float* delta, void* dq,      \

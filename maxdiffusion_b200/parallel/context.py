@@ -73,6 +73,15 @@ class _SeqToHeads(torch.autograd.Function):
     return _a2a(g.contiguous(), ctx.group, ctx.exch, True), None, None
 
 
+def _stackable(kg, vg, order) -> bool:
+  """True when the gathered K/V [n, B, S, H, D] can ride one dK/dV launch: stacked with a single batch stride and
+  presented in ring order (segment i belongs to owner (order[0] + i) % n)."""
+  n, B = kg.shape[0], kg.shape[1]
+  if not all(t.stride(-1) == 1 and t.stride(0) == B * t.stride(1) for t in (kg, vg)):
+    return False
+  return all(order[i] == (order[0] + i) % n for i in range(n))
+
+
 class _SegmentAttentionFn(torch.autograd.Function):
   """Kernel path of gather/ring attention: local q against the stacked K/V shards [n, B, S_loc, H, D]."""
 
@@ -130,9 +139,14 @@ class _SegmentAttentionFn(torch.autograd.Function):
       if min(lens) < kg.shape[2]:
         for part in parts:
           part.zero_()
-      for i in range(n):
-        part = parts[ctx.order[i]]
-        K.flash_bwd_dkv(q, d_o, ks[i], vs[i], lse, delta, ctx.scale, dk=part[0][:, :lens[i]], dv=part[1][:, :lens[i]])
+      if _stackable(kg, vg, ctx.order):
+        both_parts = rs.stacked()  # [owner, 2, B, S, H, D]
+        K.flash_bwd_dkv_stacked(q, d_o, kg, vg, lens, lse, delta, ctx.scale, dk=both_parts[:, 0], dv=both_parts[:, 1],
+                                out_rot=ctx.order[0])
+      else:
+        for i in range(n):
+          part = parts[ctx.order[i]]
+          K.flash_bwd_dkv(q, d_o, ks[i], vs[i], lse, delta, ctx.scale, dk=part[0][:, :lens[i]], dv=part[1][:, :lens[i]])
       main = torch.cuda.current_stream()
       produced = torch.cuda.Event()
       produced.record(main)
@@ -148,11 +162,14 @@ class _SegmentAttentionFn(torch.autograd.Function):
     dq = K.flash_bwd_dq(q, d_o, ks, vs, lse, delta, ctx.scale)
     dkg = torch.zeros_like(kg) if min(lens) < kg.shape[2] else torch.empty_like(kg)
     dvg = torch.zeros_like(vg) if min(lens) < vg.shape[2] else torch.empty_like(vg)
-    for i in range(n):
+    if _stackable(kg, vg, ctx.order):
       # partial gradients are stored by OWNER rank so that the reduce-scatter returns each owner its sum
-      dk, dv = K.flash_bwd_dkv(q, d_o, ks[i], vs[i], lse, delta, ctx.scale)
-      dkg[ctx.order[i]][:, :lens[i]].copy_(dk)
-      dvg[ctx.order[i]][:, :lens[i]].copy_(dv)
+      K.flash_bwd_dkv_stacked(q, d_o, kg, vg, lens, lse, delta, ctx.scale, dk=dkg, dv=dvg, out_rot=ctx.order[0])
+    else:
+      for i in range(n):
+        dk, dv = K.flash_bwd_dkv(q, d_o, ks[i], vs[i], lse, delta, ctx.scale)
+        dkg[ctx.order[i]][:, :lens[i]].copy_(dk)
+        dvg[ctx.order[i]][:, :lens[i]].copy_(dv)
     dk = C.reduce_scatter_stack(dkg, ctx.group)
     dv = C.reduce_scatter_stack(dvg, ctx.group)
     return dq, dk, dv, None, None, None, None, None, None
@@ -240,7 +257,9 @@ class ContextParallel:
     if self.size == 1:
       return x
     S = x.shape[dim]
-    per = (S + self.size - 1) // self.size
+    # a multiple of 8 rows per rank keeps every per-row fp32 statistic of the attention kernels (log-sum-exp, delta)
+    # on 16-byte boundaries, which their bulk copies need; 32760 tokens on 8 ranks become 8 x 4096 with 8 pad rows
+    per = ((S + self.size - 1) // self.size + 7) // 8 * 8
     self.full_len, self.local_len = S, per
     if per * self.size != S:
       pad = [0, 0] * (x.dim() - dim - 1) + [0, per * self.size - S]
@@ -278,6 +297,8 @@ class ContextParallel:
 
   def _segment_attention(self, q, k, v, group, n, valid_lens, scale=None):
     if n == 1:
+      if valid_lens[0] < k.shape[1]:  # padded tail rows of the sequence are no keys
+        k, v = k[:, :valid_lens[0]], v[:, :valid_lens[0]]
       return self._full_attention(q, k, v, scale)
     D = q.shape[-1]
     scale = scale if scale is not None else D ** -0.5

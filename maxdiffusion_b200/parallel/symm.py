@@ -389,6 +389,15 @@ class PeerReduceScatter:
     self._shape, self._numel = tuple(shape), numel
     return [sym[r * self.numel:r * self.numel + numel].view(shape) for r in range(self.n)]
 
+  def stacked(self) -> torch.Tensor:
+    """The slices of the current epoch as one strided view [n, *shape] (owner r at index r)."""
+    sym = self.slots[self.epoch % 2]
+    strides, acc = [], 1
+    for d in reversed(self._shape):
+      strides.append(acc)
+      acc *= int(d)
+    return sym.as_strided((self.n,) + self._shape, (self.numel,) + tuple(reversed(strides)))
+
   def reduce(self, out: Optional[torch.Tensor] = None) -> torch.Tensor:
     e, slot = self.epoch, self.epoch % 2
     self.peer.signal(FLAG_RS_READY, e)

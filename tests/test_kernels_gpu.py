@@ -232,6 +232,37 @@ def test_flash_bwd(B, H, Sq, Skv, D):
   _report(f"flash_bwd dq {Sq}x{Skv}", dq, wq.float(), rel_tol=2e-2, abs_frac=5e-2)
 
 
+@pytest.mark.parametrize("D", [128, 64])
+@pytest.mark.parametrize("B", [1, 2])
+def test_flash_bwd_dkv_stacked_matches_per_segment_launches(B, D):
+  """All stacked KV segments in one dK/dV launch: ring order -> owner order rotation, ragged last segment, outputs
+  in slices with a foreign stride (as in a symmetric buffer), untouched rows beyond a segment's length."""
+  torch.manual_seed(23)
+  n, H, Sq, Skv = 3, 2, 200, 192
+  lens = [192, 192, 77]
+  q, d_o = (torch.randn((B, Sq, H, D), device=DEV, dtype=torch.bfloat16) for _ in range(2))
+  kg = torch.randn((n, B, Skv, H, D), device=DEV, dtype=torch.bfloat16)
+  vg = torch.randn((n, B, Skv, H, D), device=DEV, dtype=torch.bfloat16)
+  ks = [kg[i][:, :lens[i]] for i in range(n)]
+  vs = [vg[i][:, :lens[i]] for i in range(n)]
+  out, lse = K.flash_fwd(q, ks, vs)
+  delta = K.flash_delta(out, d_o)
+  rot = 2
+  cap = 2 * B * Skv * H * D + 64  # owner slices [dK | dV] with some slack between them
+  buf = torch.full((n * cap,), 7.0, device=DEV, dtype=torch.bfloat16)
+  both = buf.as_strided((n, 2, B, Skv, H, D), (cap, B * Skv * H * D, Skv * H * D, H * D, D, 1))
+  K.flash_bwd_dkv_stacked(q, d_o, kg, vg, lens, lse, delta, dk=both[:, 0], dv=both[:, 1], out_rot=rot)
+  for i in range(n):
+    dk, dv = K.flash_bwd_dkv(q, d_o, ks[i], vs[i], lse, delta)
+    o = (i + rot) % n
+    assert torch.equal(both[o, 0][:, :lens[i]], dk) and torch.equal(both[o, 1][:, :lens[i]], dv)
+    if lens[i] < Skv:
+      assert (both[o, 0][:, lens[i]:] == 7.0).all() and (both[o, 1][:, lens[i]:] == 7.0).all()
+  # default outputs: allocated, contiguous
+  dk2, dv2 = K.flash_bwd_dkv_stacked(q, d_o, kg, vg, lens, lse, delta)
+  assert torch.equal(dk2[0][:, :lens[0]], both[rot % n, 0][:, :lens[0]])
+
+
 def test_flash_bwd_segments_match_concat():
   """dQ over three KV segments equals dQ over their concatenation; dK/dV per segment likewise."""
   torch.manual_seed(12)
