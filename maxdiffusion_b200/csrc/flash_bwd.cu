@@ -56,8 +56,8 @@ struct Params {
   float scale, scale_log2;
   // DKV pass over several stacked KV segments in ONE launch (seg_batches > 0): blockIdx.z = seg * seg_batches + b
   // selects the K/V rows; queries, dO, lse and delta are those of batch b for every segment; the outputs of segment
-  // seg go to slice (seg + out_rot) % n_seg of the output buffers, slices o_seg_stride elements apart.
-  int seg_batches, n_seg, out_rot;
+  // seg go to slice (out_rot + seg * out_step) % n_seg of the output buffers, slices o_seg_stride elements apart.
+  int seg_batches, n_seg, out_rot, out_step;
   int x_len_seg[MAX_SEGMENTS];
   long long o_seg_stride;
   DeviceStatus* status;
@@ -107,7 +107,7 @@ flash_bwd_kernel(const __grid_constant__ Maps maps, const Params p) {
     const int seg = batch / p.seg_batches;
     ybatch = batch - seg * p.seg_batches;
     x_len = p.x_len_seg[seg];
-    o_base = static_cast<long long>((seg + p.out_rot) % p.n_seg) * p.o_seg_stride;
+    o_base = static_cast<long long>((p.out_rot + seg * p.out_step) % p.n_seg) * p.o_seg_stride;
   }
 
   int total_steps = 0;
@@ -510,7 +510,7 @@ static int flash_bwd_dkv_launch(const void* q, const void* d_o, const void* k, c
                                 const long long* qs, const long long* gs, const long long* ks, const long long* vs,
                                 const long long* dks, const long long* dvs, float softmax_scale, int out_f32,
                                 void* stream, int n_seg = 0, const int* seg_lens = nullptr, int out_rot = 0,
-                                long long o_seg_stride = 0) {
+                                int out_step = 1, long long o_seg_stride = 0) {
   if (B <= 0 || H <= 0 || q_len <= 0 || kv_len <= 0) return 0;
   if (n_seg < 0 || n_seg > MAX_SEGMENTS || (n_seg > 0 && seg_lens == nullptr)) return 3250;
   // stacked form: K and V are [n_seg * B, kv_len, H, D] with one batch stride across segments
@@ -539,6 +539,7 @@ static int flash_bwd_dkv_launch(const void* q, const void* d_o, const void* k, c
   p.seg_batches = n_seg > 0 ? B : 0;
   p.n_seg = n_seg > 0 ? n_seg : 1;
   p.out_rot = n_seg > 0 ? ((out_rot % n_seg) + n_seg) % n_seg : 0;
+  p.out_step = n_seg > 0 ? ((out_step % n_seg) + n_seg) % n_seg : 0;
   p.o_seg_stride = o_seg_stride;
   for (int s = 0; s < MAX_SEGMENTS; ++s) {
     const int len = (s < n_seg) ? seg_lens[s] : 0;
@@ -581,7 +582,7 @@ static int flash_bwd_dq_launch(const void* q, const void* d_o, const void* const
     p.y_len[s] = s < num_segments ? kv_lens[s] : 0;
   }
   p.B = B; p.H = H; p.x_len = q_len; p.num_segments = num_segments;
-  p.seg_batches = 0; p.n_seg = 1; p.out_rot = 0; p.o_seg_stride = 0;
+  p.seg_batches = 0; p.n_seg = 1; p.out_rot = 0; p.out_step = 0; p.o_seg_stride = 0;
   for (int s = 0; s < MAX_SEGMENTS; ++s) p.x_len_seg[s] = 0;
   p.lse = lse; p.delta = delta; p.q_len = q_len;
   p.out0 = dq; p.out1 = nullptr;
@@ -620,10 +621,10 @@ static int flash_bwd_dq_launch(const void* q, const void* d_o, const void* const
       const void* q, const void* d_o, const void* k, const void* v, const float* lse, const float* delta, void* dk,       \
       void* dv, int B, int H, int q_len, int kv_len, const long long* qs, const long long* gs, const long long* ks,       \
       const long long* vs, const long long* dks, const long long* dvs, float softmax_scale, int out_f32, void* stream,    \
-      int n_seg, const int* seg_lens, int out_rot, long long o_seg_stride) {                                              \
+      int n_seg, const int* seg_lens, int out_rot, int out_step, long long o_seg_stride) {                                \
     if (n_seg < 1) return 3250;                                                                                           \
     return flash_bwd_dkv_launch<HD>(q, d_o, k, v, lse, delta, dk, dv, B, H, q_len, kv_len, qs, gs, ks, vs, dks, dvs,      \
-                                    softmax_scale, out_f32, stream, n_seg, seg_lens, out_rot, o_seg_stride);              \
+                                    softmax_scale, out_f32, stream, n_seg, seg_lens, out_rot, out_step, o_seg_stride);    \
   }                                                                                                                       \
   extern "C" int mdb_flash_bwd_dq##SUFFIX(const void* q, const void* d_o, const void* const* k_ptrs,                      \
                                           const void* const* v_ptrs, const float* lse, const float* delta, void* dq,      \

@@ -138,13 +138,22 @@ __device__ __forceinline__ void copy_cta(const CopyPlan& cp, int ci, DeviceStatu
       const uint4* src = cp.src[i][t];
       uint4* dst = cp.dst[i][t];
       long long v = begin + threadIdx.x;
-      // 8 independent 16-byte loads in flight per thread; peer data bypasses L1 (the addresses are reused)
-      for (; v + 7 * NUM_THREADS < end; v += 8 * NUM_THREADS) {
-        uint4 r[8];
+      // 16 independent 16-byte loads in flight per thread (12 copy CTAs then hold about 1.3 MB in flight, which a
+      // round trip of a few microseconds over NVLink turns into some 500 GB/s: on 8 ranks the seven remote segments
+      // have to arrive within the 2.7 ms of math); peer data bypasses L1 (the addresses are reused)
+      for (; v + 15 * NUM_THREADS < end; v += 16 * NUM_THREADS) {
+        uint4 r[16];
 #pragma unroll
-        for (int u = 0; u < 8; ++u) r[u] = __ldcg(src + v + u * NUM_THREADS);
+        for (int u = 0; u < 16; ++u) r[u] = __ldcg(src + v + u * NUM_THREADS);
 #pragma unroll
-        for (int u = 0; u < 8; ++u) dst[v + u * NUM_THREADS] = r[u];
+        for (int u = 0; u < 16; ++u) dst[v + u * NUM_THREADS] = r[u];
+      }
+      for (; v + 3 * NUM_THREADS < end; v += 4 * NUM_THREADS) {
+        uint4 r[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) r[u] = __ldcg(src + v + u * NUM_THREADS);
+#pragma unroll
+        for (int u = 0; u < 4; ++u) dst[v + u * NUM_THREADS] = r[u];
       }
       for (; v < end; v += NUM_THREADS) dst[v] = __ldcg(src + v);
     }
@@ -615,7 +624,14 @@ static int flash_fwd_launch(const void* q, const void* const* k_ptrs, const void
   }
   const int n_qb = (q_len + 2 * BQ - 1) / (2 * BQ);
   const long long total_work = static_cast<long long>(n_qb) * H * B;
-  const int n_copy = cp.n_remote > 0 ? cp.n_copy_ctas : 0;
+  int n_copy = cp.n_remote > 0 ? cp.n_copy_ctas : 0;
+  if (n_copy > 0) {
+    // Copy CTAs that cost no extra wave of work items are free: 640 items (8 ranks, 4096 queries each) take 5 rounds
+    // on anything from 128 to 148 compute CTAs, so the copies may have 20 SMs instead of 12.
+    const auto rounds = [&](int copy) { return (total_work + sm_count() - copy - 1) / (sm_count() - copy); };
+    while (n_copy < 32 && sm_count() - (n_copy + 1) >= 1 && rounds(n_copy + 1) == rounds(cp.n_copy_ctas)) ++n_copy;
+    cp.n_copy_ctas = n_copy;
+  }
   int n_compute = sm_count() - n_copy;
   if (n_compute < 1) return 3104;
   if (total_work < n_compute) n_compute = static_cast<int>(total_work);

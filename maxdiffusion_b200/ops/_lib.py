@@ -150,7 +150,7 @@ def _declare(L: ctypes.CDLL) -> None:
                                   c_void_p, c_void_p] + [c_int] * 4 + [ctypes.POINTER(c_int)] + [c_llp] * 5 +
                                  [c_float, c_int, c_void_p])
   L.mdb_flash_bwd_dq.restype = c_int
-  L.mdb_flash_bwd_dkv_stacked.argtypes = L.mdb_flash_bwd_dkv.argtypes + [c_int, ctypes.POINTER(c_int), c_int, c_ll]
+  L.mdb_flash_bwd_dkv_stacked.argtypes = L.mdb_flash_bwd_dkv.argtypes + [c_int, ctypes.POINTER(c_int), c_int, c_int, c_ll]
   L.mdb_flash_bwd_dkv_stacked.restype = c_int
   for name in ("mdb_flash_delta", "mdb_flash_bwd_dkv", "mdb_flash_bwd_dkv_stacked", "mdb_flash_bwd_dq"):  # head_dim 64 variants: same signatures
     getattr(L, name + "_d64").argtypes = getattr(L, name).argtypes

@@ -143,12 +143,12 @@ def flash_bwd_dkv(q, d_o, k, v, lse, delta, scale=None, out_dtype=torch.bfloat16
 
 
 def flash_bwd_dkv_stacked(q, d_o, kg, vg, lens, lse, delta, scale=None, dk=None, dv=None, out_rot: int = 0,
-                          out_dtype=torch.bfloat16):
+                          out_step: int = 1, out_dtype=torch.bfloat16):
   """dK, dV of ALL stacked KV segments kg / vg [n, B, Skv, H, D] from the local queries in ONE launch (the segments
   ride the batch axis of the grid; a launch per 4k-token segment costs about half as much again).
 
-  `lens[i]` are the valid rows of segment i. The result of segment i is written to dk[(i + out_rot) % n] (ring
-  order -> owner order); dk / dv are [n, B, Skv, H, D] with any stride along the first axis (slices of a symmetric
+  `lens[i]` are the valid rows of segment i. The result of segment i is written to dk[(out_rot + i * out_step) % n]
+  (ring order -> owner order, whichever way the ring turns); dk / dv are [n, B, Skv, H, D] with any stride along the first axis (slices of a symmetric
   buffer) and are allocated when not given. Rows beyond lens[i] are left untouched."""
   n, B, Skv, H, D = kg.shape
   Sq = q.shape[1]
@@ -166,7 +166,8 @@ def flash_bwd_dkv_stacked(q, d_o, kg, vg, lens, lse, delta, scale=None, dk=None,
   rc = _flash_entry("mdb_flash_bwd_dkv_stacked", D)(
       _lib.ptr(q), _lib.ptr(d_o), _lib.ptr(kg), _lib.ptr(vg), _lib.ptr(lse), _lib.ptr(delta), _lib.ptr(dk), _lib.ptr(dv),
       B, H, Sq, Skv, _strides3(q), _strides3(d_o), _strides3(kg[0]), _strides3(vg[0]), _strides3(dk[0]), _strides3(dv[0]),
-      float(scale), int(out_dtype == torch.float32), _lib.stream(), n, seg_lens, int(out_rot), dk.stride(0))
+      float(scale), int(out_dtype == torch.float32), _lib.stream(), n, seg_lens, int(out_rot), int(out_step) % n,
+      dk.stride(0))
   _lib.check(rc, "mdb_flash_bwd_dkv_stacked")
   return dk, dv
 

@@ -73,13 +73,17 @@ class _SeqToHeads(torch.autograd.Function):
     return _a2a(g.contiguous(), ctx.group, ctx.exch, True), None, None
 
 
-def _stackable(kg, vg, order) -> bool:
-  """True when the gathered K/V [n, B, S, H, D] can ride one dK/dV launch: stacked with a single batch stride and
-  presented in ring order (segment i belongs to owner (order[0] + i) % n)."""
+def _stackable(kg, vg, order):
+  """(rot, step) when the gathered K/V [n, B, S, H, D] can ride one dK/dV launch, else None: stacked with a single
+  batch stride, and segment i belongs to owner (rot + i * step) % n (the ring order, whichever way it turns)."""
   n, B = kg.shape[0], kg.shape[1]
   if not all(t.stride(-1) == 1 and t.stride(0) == B * t.stride(1) for t in (kg, vg)):
-    return False
-  return all(order[i] == (order[0] + i) % n for i in range(n))
+    return None
+  rot = order[0]
+  step = (order[1] - order[0]) % n if n > 1 else 0
+  if any(order[i] != (rot + i * step) % n for i in range(n)):
+    return None
+  return rot, step
 
 
 class _SegmentAttentionFn(torch.autograd.Function):
@@ -139,10 +143,11 @@ class _SegmentAttentionFn(torch.autograd.Function):
       if min(lens) < kg.shape[2]:
         for part in parts:
           part.zero_()
-      if _stackable(kg, vg, ctx.order):
+      ring = _stackable(kg, vg, ctx.order)
+      if ring is not None:
         both_parts = rs.stacked()  # [owner, 2, B, S, H, D]
         K.flash_bwd_dkv_stacked(q, d_o, kg, vg, lens, lse, delta, ctx.scale, dk=both_parts[:, 0], dv=both_parts[:, 1],
-                                out_rot=ctx.order[0])
+                                out_rot=ring[0], out_step=ring[1])
       else:
         for i in range(n):
           part = parts[ctx.order[i]]
@@ -162,9 +167,11 @@ class _SegmentAttentionFn(torch.autograd.Function):
     dq = K.flash_bwd_dq(q, d_o, ks, vs, lse, delta, ctx.scale)
     dkg = torch.zeros_like(kg) if min(lens) < kg.shape[2] else torch.empty_like(kg)
     dvg = torch.zeros_like(vg) if min(lens) < vg.shape[2] else torch.empty_like(vg)
-    if _stackable(kg, vg, ctx.order):
+    ring = _stackable(kg, vg, ctx.order)
+    if ring is not None:
       # partial gradients are stored by OWNER rank so that the reduce-scatter returns each owner its sum
-      K.flash_bwd_dkv_stacked(q, d_o, kg, vg, lens, lse, delta, ctx.scale, dk=dkg, dv=dvg, out_rot=ctx.order[0])
+      K.flash_bwd_dkv_stacked(q, d_o, kg, vg, lens, lse, delta, ctx.scale, dk=dkg, dv=dvg, out_rot=ring[0],
+                              out_step=ring[1])
     else:
       for i in range(n):
         dk, dv = K.flash_bwd_dkv(q, d_o, ks[i], vs[i], lse, delta, ctx.scale)

@@ -251,16 +251,18 @@ def test_flash_bwd_dkv_stacked_matches_per_segment_launches(B, D):
   cap = 2 * B * Skv * H * D + 64  # owner slices [dK | dV] with some slack between them
   buf = torch.full((n * cap,), 7.0, device=DEV, dtype=torch.bfloat16)
   both = buf.as_strided((n, 2, B, Skv, H, D), (cap, B * Skv * H * D, Skv * H * D, H * D, D, 1))
-  K.flash_bwd_dkv_stacked(q, d_o, kg, vg, lens, lse, delta, dk=both[:, 0], dv=both[:, 1], out_rot=rot)
+  step = n - 1  # a ring that turns backwards: segment i belongs to owner (rot - i) % n
+  K.flash_bwd_dkv_stacked(q, d_o, kg, vg, lens, lse, delta, dk=both[:, 0], dv=both[:, 1], out_rot=rot, out_step=step)
   for i in range(n):
     dk, dv = K.flash_bwd_dkv(q, d_o, ks[i], vs[i], lse, delta)
-    o = (i + rot) % n
+    o = (rot - i) % n
     assert torch.equal(both[o, 0][:, :lens[i]], dk) and torch.equal(both[o, 1][:, :lens[i]], dv)
     if lens[i] < Skv:
       assert (both[o, 0][:, lens[i]:] == 7.0).all() and (both[o, 1][:, lens[i]:] == 7.0).all()
   # default outputs: allocated, contiguous
   dk2, dv2 = K.flash_bwd_dkv_stacked(q, d_o, kg, vg, lens, lse, delta)
-  assert torch.equal(dk2[0][:, :lens[0]], both[rot % n, 0][:, :lens[0]])
+  for i in range(n):  # default: segment i -> slice i
+    assert torch.equal(dk2[i][:, :lens[i]], both[(rot - i) % n, 0][:, :lens[i]])
 
 
 def test_flash_bwd_segments_match_concat():

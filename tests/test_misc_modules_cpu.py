@@ -162,3 +162,18 @@ def test_fixed_m_kernel_names_select_the_fixed_exponent_context():
   assert torch.allclose(ctx.self_attention(q, q, q), want, atol=1e-5)
   fn = get_attention_kernel("ulysses_custom_fixed_m", mesh)
   assert torch.allclose(fn(q, q, q), want, atol=1e-5)
+
+
+def test_ring_order_to_owner_mapping_of_the_joint_dkv_launch():
+  """Segment i of the gathered K/V belongs to owner order[i]; the joint launch expresses that as (rot + i*step) % n."""
+  from maxdiffusion_b200.parallel.context import _stackable
+
+  kg = torch.zeros(8, 1, 4, 2, 8)
+  for rank in range(8):
+    backwards = [(rank - h) % 8 for h in range(8)]  # peer-memory exchange: own shard, then the ring predecessors
+    rot, step = _stackable(kg, kg, backwards)
+    assert [(rot + i * step) % 8 for i in range(8)] == backwards and step == 7
+  assert _stackable(kg, kg, list(range(8))) == (0, 1)  # all-gather order
+  assert _stackable(kg, kg, [0, 2, 1, 3, 4, 5, 6, 7]) is None  # not a rotation: per-segment launches
+  assert _stackable(kg.transpose(0, 1), kg.transpose(0, 1), [0]) is None  # not stacked with one batch stride
+  assert _stackable(kg[:2], kg[:2], [1, 0]) == (1, 1)
