@@ -20,7 +20,10 @@ def _announced_failure(rank, world):
         raise ValueError("loss is NaN")
   except ValueError:
     out = "raised"
-  if rank == 0:
+  except RankFailure as e:
+    # rank 1 may announce its exception before rank 0 has even entered step 0: then this check already sees it
+    out = f"detected {e.ranks} {e.reasons[1]}"
+  if rank == 0 and out == "none":
     deadline = time.time() + 20
     while time.time() < deadline:
       try:
