@@ -185,6 +185,16 @@ def test_training_step_peer_transport_matches_nccl():
   assert a == pytest.approx(b, rel=3e-2, abs=3e-2)
 
 
+def test_training_step_peer_transport_matches_nccl_on_4_ranks():
+  """On more than 2 ranks the peer-memory exchange presents the K/V segments in backwards ring order while the NCCL
+  path presents them in rank order: the joint dK/dV launch has to return every partial to the right owner in both."""
+  if torch.cuda.device_count() < 4:
+    pytest.skip("needs 4 GPUs")
+  a = _spawn(_train, 4, True)[0]
+  b = _spawn(_train, 4, False)[0]
+  assert a == pytest.approx(b, rel=3e-2, abs=3e-2)
+
+
 def _small_allreduce(rank, world):
   import torch.distributed as dist
 
