@@ -140,9 +140,9 @@ class _SegmentAttentionFn(torch.autograd.Function):
       # kernel is bound by NVLink, so it runs on a side stream underneath the dQ kernel.
       shape = (2,) + tuple(kg.shape[1:])
       parts = rs.slices(shape)
-      if min(lens) < kg.shape[2]:
-        for part in parts:
-          part.zero_()
+      for i in range(n):
+        if lens[i] < kg.shape[2]:  # pad rows of a ragged shard: no kernel writes them, the owner sums them
+          parts[ctx.order[i]][:, :, lens[i]:].zero_()
       ring = _stackable(kg, vg, ctx.order)
       if ring is not None:
         both_parts = rs.stacked()  # [owner, 2, B, S, H, D]
@@ -165,8 +165,11 @@ class _SegmentAttentionFn(torch.autograd.Function):
       both.record_stream(main)
       return dq, both[0], both[1], None, None, None, None, None, None
     dq = K.flash_bwd_dq(q, d_o, ks, vs, lse, delta, ctx.scale)
-    dkg = torch.zeros_like(kg) if min(lens) < kg.shape[2] else torch.empty_like(kg)
-    dvg = torch.zeros_like(vg) if min(lens) < vg.shape[2] else torch.empty_like(vg)
+    dkg, dvg = torch.empty_like(kg), torch.empty_like(vg)
+    for i in range(n):
+      if lens[i] < kg.shape[2]:  # pad rows of a ragged shard: no kernel writes them, the reduce-scatter sums them
+        dkg[ctx.order[i]][:, lens[i]:].zero_()
+        dvg[ctx.order[i]][:, lens[i]:].zero_()
     ring = _stackable(kg, vg, ctx.order)
     if ring is not None:
       # partial gradients are stored by OWNER rank so that the reduce-scatter returns each owner its sum
