@@ -7,11 +7,16 @@ SD/SDXL `{unet_config, vae_config, text_encoder_config, scheduler_config, unet_s
 text_encoder_state, tokenizer_config}` (+ `text_encoder_2_*`), Z-Image `{transformer_state, vae_state,
 text_encoder_state, z_image_config}`, `iter` for the data iterator.
 
-State items are written with Orbax when it is importable. Otherwise (it is not in this image) a state item is a
-directory with `state.safetensors` (keys = '/'-joined tree paths, arrays in the reference's flax orientation),
-`_METADATA` (tree paths, shapes, dtypes) and, for sharded optimizer state, one `process_<rank>.safetensors` per
-rank; JSON items are a single `metadata` file; each step directory carries `_CHECKPOINT_METADATA`. Saves go to a
-temporary directory that is renamed when complete, optionally on a background thread (`enable_async_checkpointing`).
+The layout (directory names, item names, tree paths, array orientation) is the reference's; the bytes are NOT
+Orbax / tensorstore: an Orbax reader cannot open these checkpoints and this manager cannot open Orbax ones. A state
+item is a directory with `state.safetensors` (keys = '/'-joined tree paths, arrays in the reference's flax
+orientation), `_METADATA` (tree paths, shapes, dtypes) and, for sharded optimizer state, one
+`process_<rank>.safetensors` per rank of the shard group plus `_sharding` (group size); JSON items are a single
+`metadata` file; each step directory carries `_CHECKPOINT_METADATA`. Saves go to a temporary directory that rank 0
+creates (the other ranks wait for it through the rendezvous store, or by polling when there is none) and renames
+once every rank's shard file is there; a rank that does not show up within `timeout_s` makes the save raise instead
+of committing a checkpoint with missing files. Optionally the write runs on a background thread
+(`enable_async_checkpointing`).
 """
 from __future__ import annotations
 
@@ -61,8 +66,11 @@ def _to_torch(a):
 class CheckpointManager:
 
   def __init__(self, directory: str, item_names: Sequence[str], enable_async: bool = True, rank: int = 0,
-               save_interval_steps: int = 1, max_to_keep: Optional[int] = None):
+               save_interval_steps: int = 1, max_to_keep: Optional[int] = None, store=None, timeout_s: float = 600.0):
     self.directory = directory
+    self.store = store          # key-value store shared by the ranks (torch.distributed store), or None
+    self.timeout_s = timeout_s
+    self._saves = 0
     self.item_names = tuple(item_names)
     self.enable_async = enable_async
     self.rank = rank
@@ -88,15 +96,16 @@ class CheckpointManager:
 
   # ---- save --------------------------------------------------------------------------------
   def save(self, step: int, items: Dict[str, object], sharded: Optional[Dict[str, Dict[str, torch.Tensor]]] = None,
-           world_size: int = 1) -> None:
+           world_size: int = 1, shard_rank: Optional[int] = None) -> None:
     """`items`: name -> dict (JSON item) or flat {path: array} (state item), written by rank 0.
-    `sharded`: name -> {key: tensor} written by EVERY rank as `process_<rank>.safetensors` inside the item."""
+    `sharded`: name -> {key: tensor}, written as `process_<shard_rank>.safetensors` inside the item by every rank that
+    passes one (`world_size` files are expected in all; `shard_rank` defaults to the manager's rank)."""
     for name in list(items) + list(sharded or {}):
       if name not in self.item_names:
         raise ValueError(f"item '{name}' is not one of {self.item_names}")
     self.wait_until_finished()
     host_items = {}
-    for name, payload in items.items():
+    for name, payload in (items.items() if self.rank == 0 else ()):  # only rank 0 writes the replicated items
       if self._is_json(payload):
         host_items[name] = ("json", payload)
       else:
@@ -105,7 +114,7 @@ class CheckpointManager:
 
     def work():
       try:
-        self._write(step, host_items, host_sharded, world_size)
+        self._write(step, host_items, host_sharded, world_size, self.rank if shard_rank is None else shard_rank)
       except BaseException as e:  # surfaced by wait_until_finished
         self._error = e
 
@@ -120,14 +129,36 @@ class CheckpointManager:
   def _is_json(payload) -> bool:
     return isinstance(payload, dict) and not any(isinstance(v, (torch.Tensor, np.ndarray)) for v in payload.values())
 
-  def _write(self, step, host_items, host_sharded, world_size):
+  def _announce(self, key: str) -> None:
+    if self.store is not None:
+      self.store.set(key, "1")
+
+  def _await(self, key: str, path: str, what: str) -> None:
+    """Waits until `key` is in the store (or, without a store, until `path` exists); raises after `timeout_s`."""
+    deadline = time.time() + self.timeout_s
+    while True:
+      if self.store is not None:
+        try:
+          if self.store.check([key]):
+            return
+        except Exception:
+          pass
+      elif os.path.exists(path):
+        return
+      if time.time() > deadline:
+        raise TimeoutError(f"checkpoint step {what}: not seen within {self.timeout_s:.0f} s")
+      time.sleep(0.05)
+
+  def _write(self, step, host_items, host_sharded, world_size, shard_rank):
     from safetensors.torch import save_file
 
     final = os.path.join(self.directory, str(step))
     tmp = final + ".orbax-checkpoint-tmp"
+    self._saves += 1
+    tag = f"mdb_ckpt/{os.path.abspath(self.directory)}/{step}/{self._saves}"
     if self.rank == 0:
       if os.path.isdir(tmp):
-        shutil.rmtree(tmp)
+        shutil.rmtree(tmp)  # left over from a run that died while saving; nobody writes into it yet
       os.makedirs(tmp, exist_ok=True)
       for name, (kind, payload) in host_items.items():
         d = os.path.join(tmp, name)
@@ -140,24 +171,26 @@ class CheckpointManager:
           meta = {k: {"shape": list(v.shape), "dtype": str(v.dtype).replace("torch.", "")} for k, v in payload.items()}
           with open(os.path.join(d, "_METADATA"), "w") as f:
             json.dump({"tree_metadata": meta, "format": "safetensors-per-item"}, f)
-    else:
-      deadline = time.time() + 600
-      while not os.path.isdir(tmp) and time.time() < deadline:
-        time.sleep(0.05)
+      for name in host_sharded:
+        os.makedirs(os.path.join(tmp, name), exist_ok=True)
+      with open(os.path.join(tmp, "_tmp_ready"), "w") as f:
+        f.write(tag)
+      self._announce(tag + "/tmp")
+    elif host_sharded:
+      self._await(tag + "/tmp", os.path.join(tmp, "_tmp_ready"), f"{step}: temporary directory of rank 0")
     for name, tensors in host_sharded.items():
       d = os.path.join(tmp, name)
-      os.makedirs(d, exist_ok=True)
-      save_file(tensors, os.path.join(d, f"process_{self.rank}.safetensors"))
-      with open(os.path.join(d, f"process_{self.rank}.done"), "w") as f:
+      save_file(tensors, os.path.join(d, f"process_{shard_rank}.safetensors"))
+      with open(os.path.join(d, f"process_{shard_rank}.done"), "w") as f:
         f.write("ok")
+      self._announce(f"{tag}/{name}/{shard_rank}")
     if self.rank == 0:
-      deadline = time.time() + 600
       for name in host_sharded:
         for r in range(world_size):
-          while not os.path.exists(os.path.join(tmp, name, f"process_{r}.done")) and time.time() < deadline:
-            time.sleep(0.05)
+          self._await(f"{tag}/{name}/{r}", os.path.join(tmp, name, f"process_{r}.done"), f"{step}: shard file of rank {r}")
         with open(os.path.join(tmp, name, "_sharding"), "w") as f:
           json.dump({"world_size": world_size}, f)
+      os.remove(os.path.join(tmp, "_tmp_ready"))
       with open(os.path.join(tmp, "_CHECKPOINT_METADATA"), "w") as f:
         json.dump({"step": step, "item_names": list(host_items) + list(host_sharded), "commit_timestamp": time.time()}, f)
       if os.path.isdir(final):
@@ -199,5 +232,5 @@ class CheckpointManager:
 
 
 def create_checkpoint_manager(checkpoint_dir: str, checkpoint_type: str, enable_async: bool = True,
-                              dataset_type: str = "", rank: int = 0) -> CheckpointManager:
-  return CheckpointManager(checkpoint_dir, item_names_for(checkpoint_type, dataset_type), enable_async, rank)
+                              dataset_type: str = "", rank: int = 0, store=None) -> CheckpointManager:
+  return CheckpointManager(checkpoint_dir, item_names_for(checkpoint_type, dataset_type), enable_async, rank, store=store)

@@ -37,9 +37,15 @@ class WanCheckpointer:
     rank = dist.get_rank() if dist.is_available() and dist.is_initialized() else 0
     self.rank = rank
     self.world = dist.get_world_size() if dist.is_available() and dist.is_initialized() else 1
+    store = None
+    if self.world > 1:
+      try:
+        store = dist.distributed_c10d._get_default_store()
+      except Exception:
+        store = None
     self.manager = create_checkpoint_manager(config.get("checkpoint_dir", ""), checkpoint_type,
                                              enable_async=bool(config.get("enable_async_checkpointing", True)),
-                                             dataset_type=str(config.get("dataset_type", "")), rank=rank)
+                                             dataset_type=str(config.get("dataset_type", "")), rank=rank, store=store)
 
   # ---- training state ----------------------------------------------------------------------
   def save(self, step: int, trainer) -> None:
@@ -47,24 +53,36 @@ class WanCheckpointer:
     eng = trainer.engine
     full = {}
     for i, (g, blk_names) in enumerate(zip(eng.groups, names)):
-      flat = eng.full_block_flat(i)  # collective when sharded
-      for n, v in zip(blk_names, g.views(flat)):
-        full[f"blocks.{i}.{n}"] = v.clone()
-    for n, v in zip(root, eng.root.views(eng.root_flat)):
-      full[n] = v.clone()
+      flat = eng.full_block_flat(i)  # collective when sharded: every rank takes part, only rank 0 keeps the result
+      if self.rank == 0:
+        for n, v in zip(blk_names, g.views(flat)):
+          full[f"blocks.{i}.{n}"] = v.to("cpu")
+      del flat
     cfg = trainer.wan_cfg
-    tree = diffusers_to_flax_tree(ours_to_diffusers(full, cfg.in_channels, tuple(cfg.patch_size)),
-                                  scan_layers=bool(self.config.get("scan_layers", True)))
-    items = {"wan_config": cfg.to_dict(), "wan_state": tree}
+    items = {}
+    if self.rank == 0:
+      for n, v in zip(root, eng.root.views(eng.root_flat)):
+        full[n] = v.to("cpu")
+      tree = diffusers_to_flax_tree(ours_to_diffusers(full, cfg.in_channels, tuple(cfg.patch_size)),
+                                    scan_layers=bool(self.config.get("scan_layers", True)))
+      items = {"wan_config": cfg.to_dict(), "wan_state": tree}
     sharded = None
+    writers = 1
     if self.config.get("save_optimizer", False):
-      st = eng.optimizer_state()
-      shard = {"step": torch.tensor([st["step"]]), "root_m": st["root_m"], "root_v": st["root_v"]}
-      for i, (m, v) in enumerate(zip(st["m"], st["v"])):
-        shard[f"m.{i}"], shard[f"v.{i}"] = m, v
-      items["wan_config"]["_train_step"] = int(step)
-      sharded = {"wan_state": shard}
-    self.manager.save(step, items, sharded=sharded, world_size=self.world)
+      # The moments are sharded over the engine's shard group only; replicas (the `data` axis, and `tensor`) hold
+      # identical copies, so exactly one replica writes: the ranks whose shard group contains global rank 0. Files are
+      # numbered by the rank INSIDE the shard group, which is what `maybe_restore` re-shards by.
+      shard_ranks = trainer.mesh.ranks("shard") if eng.world > 1 else [self.rank]
+      writers = eng.world
+      if 0 in shard_ranks or self.world == 1:
+        st = eng.optimizer_state()
+        shard = {"step": torch.tensor([st["step"]]), "root_m": st["root_m"], "root_v": st["root_v"]}
+        for i, (m, v) in enumerate(zip(st["m"], st["v"])):
+          shard[f"m.{i}"], shard[f"v.{i}"] = m, v
+        sharded = {"wan_state": shard}
+      if self.rank == 0:
+        items["wan_config"]["_train_step"] = int(step)
+    self.manager.save(step, items, sharded=sharded, world_size=writers, shard_rank=eng.rank)
     max_logging.log(f"saved checkpoint for step {step} to {self.manager.directory}")
 
   def maybe_restore(self, trainer) -> Optional[int]:

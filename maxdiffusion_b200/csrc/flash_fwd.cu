@@ -19,9 +19,12 @@
 // (q-block, head, batch) tiles. When the K/V segments of other ranks have to be fetched (ring /
 // context-parallel attention) the last `n_copy` CTAs of the same launch are copy CTAs: they wait for
 // the owner's epoch flag, pull its K/V shard over NVLink with 16-byte loads into this GPU's staging
-// buffer, and raise the segment's ready flag; afterwards they acknowledge to the owners. Transfer and
-// math therefore overlap segment by segment inside ONE kernel whose CTAs are all co-resident, and no
-// remote tile crosses NVLink more than once.
+// buffer, and raise ready flags; afterwards they acknowledge to the owners. The shards are pulled in
+// units of (head group, segment), head group outermost, and a unit's flag is raised as soon as it is
+// staged: the compute CTAs walk the work list head by head, so the first round of work items needs only
+// the first group's heads of every segment (a fraction of the bytes) and the later groups arrive while
+// the earlier ones are being multiplied. Transfer and math therefore overlap unit by unit inside ONE
+// kernel whose CTAs are all co-resident, and no remote tile crosses NVLink more than once.
 //
 // Layout: q, k, v, o are [B, S, H, 128] bf16 with arbitrary (16-byte aligned) strides for
 // B, S, H, so the [B, S, H*D] projections are consumed without a transpose.
@@ -57,18 +60,24 @@ struct KVMaps {
 };
 
 constexpr int MAX_REMOTE = MAX_SEGMENTS - 1;
+constexpr int MAX_GROUPS = 8;            // head groups of a copy plan; also the stride of the per-segment flag rows
+constexpr int NUM_COUNTERS = MAX_REMOTE * MAX_GROUPS + 1;
 
-// Work of the copy CTAs: remote segment i (KV segment 1 + i of the launch) is pulled from src to dst.
+// Work of the copy CTAs: remote segment i (KV segment 1 + i of the launch) is pulled from src to dst, as n_groups
+// column slabs (head groups) of the [rows, row_vecs] tensors; slab g covers vectors [g * group_vecs, ...) of a row.
 struct CopyPlan {
   int n_remote;                         // 0: no copy CTAs
   int n_copy_ctas;
+  int n_groups;                         // 1 .. MAX_GROUPS
+  unsigned int rows;                    // token rows per tensor (B * S)
+  unsigned int row_vecs;                // 16-byte vectors per row (H * D * 2 / 16)
+  unsigned int group_vecs;              // vectors per row of one head group (the last group may be narrower)
   const uint4* src[MAX_REMOTE][2];      // peer addresses of K and V
   uint4* dst[MAX_REMOTE][2];            // local staging
-  long long nvec;                       // 16-byte vectors per tensor
   const unsigned int* ready[MAX_REMOTE];  // local signal-pad slot the owner raises
   unsigned int epoch;
-  unsigned int* counters;               // [MAX_SEGMENTS], zero at launch
-  unsigned int* seg_flags;              // flag 1 + i is raised once segment i is staged
+  unsigned int* counters;               // [NUM_COUNTERS], zero at launch
+  unsigned int* seg_flags;              // flag (1 + i) * MAX_GROUPS + g is raised once slab g of segment i is staged
   unsigned int* ack[MAX_SEGMENTS];      // peers' pad slots to acknowledge into (n_ack entries)
   int n_ack;
 };
@@ -81,8 +90,10 @@ struct Params {
   long long o_stride_b, o_stride_s, o_stride_h;
   float* lse;  // [B, H, q_len] in the log2 domain (m + log2 l), may be nullptr
   float scale_log2;
-  const unsigned int* seg_flags;  // [num_segments] or nullptr
-  unsigned int flag_target;       // segment s is ready once seg_flags[s] >= flag_target
+  const unsigned int* seg_flags;  // [num_segments * flag_stride] or nullptr
+  unsigned int flag_target;       // heads [g*hpg, (g+1)*hpg) of segment s are ready once seg_flags[s*flag_stride + g] >= flag_target
+  int flag_stride;                // 1: one flag per segment; MAX_GROUPS: one per (segment, head group)
+  int heads_per_group;            // hpg above (>= H when flag_stride is 1)
   // Fixed-exponent softmax (both nullptr: off). Rows of the heads with fixed_heads[h] != 0 subtract the given
   // m_fixed[b, h, row] (log2 domain) instead of a running maximum: no row maximum, no accumulator rescale.
   // The caller guarantees  s*scale_log2 - m_fixed <= 126  for every score of such a head.
@@ -101,7 +112,7 @@ __device__ __forceinline__ bool wait_flag(const unsigned int* flag, unsigned int
     if (v >= target) return true;
     if ((++spins & 0xffu) == 0u) {
       if (*abort_flag) return false;
-      if (global_timer_ns() - t0 > kWaitBudgetNs) {
+      if (global_timer_ns() - t0 > kPeerWaitBudgetNs + kWaitBudgetNs) {  // outlasts the copy CTAs' own wait
         *abort_flag = 1;
         report_status(st, kStatusFlagTimeout, 40, detail);
         return false;
@@ -110,66 +121,89 @@ __device__ __forceinline__ bool wait_flag(const unsigned int* flag, unsigned int
   }
 }
 
+// One (head group, segment) unit: this CTA's share of slab `g` of both tensors. Vector `idx` of the slab is column
+// idx % gv of row idx / gv; the pair advances by NUM_THREADS per load without a division.
+__device__ __forceinline__ void copy_slab(const uint4* __restrict__ src, uint4* __restrict__ dst, unsigned int begin,
+                                          unsigned int end, unsigned int gv, unsigned int row_vecs, unsigned int col0) {
+  const unsigned int step_row = NUM_THREADS / gv, step_col = NUM_THREADS % gv;
+  unsigned int idx = begin + threadIdx.x;
+  unsigned int row = idx / gv, col = idx % gv;
+  // 16 independent 16-byte loads in flight per thread (a copy CTA then holds about 100 KB in flight, which a round
+  // trip of a few microseconds over NVLink turns into 25-30 GB/s per CTA); peer data bypasses L1
+  while (idx + 15u * NUM_THREADS < end) {
+    uint4 r[16];
+    unsigned long long off[16];
+#pragma unroll
+    for (int u = 0; u < 16; ++u) {
+      off[u] = static_cast<unsigned long long>(row) * row_vecs + col0 + col;
+      r[u] = __ldcg(src + off[u]);
+      row += step_row;
+      col += step_col;
+      if (col >= gv) { col -= gv; ++row; }
+    }
+#pragma unroll
+    for (int u = 0; u < 16; ++u) dst[off[u]] = r[u];
+    idx += 16u * NUM_THREADS;
+  }
+  while (idx < end) {
+    const unsigned long long off = static_cast<unsigned long long>(row) * row_vecs + col0 + col;
+    dst[off] = __ldcg(src + off);
+    row += step_row;
+    col += step_col;
+    if (col >= gv) { col -= gv; ++row; }
+    idx += NUM_THREADS;
+  }
+}
+
 __device__ __forceinline__ void copy_cta(const CopyPlan& cp, int ci, DeviceStatus* status) {
   __shared__ int ok_s;
-  for (int i = 0; i < cp.n_remote; ++i) {
-    if (threadIdx.x == 0) {
-      int ok = 1;
-      const uint64_t t0 = global_timer_ns();
-      unsigned int spins = 0;
-      while (true) {
-        unsigned int v;
-        asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(cp.ready[i]) : "memory");
-        if (v >= cp.epoch) break;
-        if ((++spins & 0xffu) == 0u && global_timer_ns() - t0 > kWaitBudgetNs) {
-          report_status(status, kStatusFlagTimeout, 45, static_cast<unsigned int>(i));
-          ok = 0;
-          break;
+  unsigned int owner_seen = 0;  // remote segments whose owner flag has been observed (uniform over the CTA)
+  const int n_units = cp.n_remote * cp.n_groups;
+  for (int u = 0; u < n_units; ++u) {
+    const int g = u / cp.n_remote;  // head group outermost: every segment's first slab before any second slab
+    const int i = u - g * cp.n_remote;
+    if (!((owner_seen >> i) & 1u)) {
+      if (threadIdx.x == 0) {
+        int ok = 1;
+        const uint64_t t0 = global_timer_ns();
+        unsigned int spins = 0;
+        while (true) {
+          unsigned int v;
+          asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(cp.ready[i]) : "memory");
+          if (v >= cp.epoch) break;
+          if ((++spins & 0xffu) == 0u && global_timer_ns() - t0 > kPeerWaitBudgetNs) {
+            report_status(status, kStatusFlagTimeout, 45, static_cast<unsigned int>(i));
+            ok = 0;
+            break;
+          }
         }
+        ok_s = ok;
       }
-      ok_s = ok;
+      __syncthreads();
+      if (!ok_s) return;
+      owner_seen |= 1u << i;
     }
-    __syncthreads();
-    if (!ok_s) return;
-    const long long per = (cp.nvec + cp.n_copy_ctas - 1) / cp.n_copy_ctas;
-    const long long begin = static_cast<long long>(ci) * per;
-    const long long end = begin + per < cp.nvec ? begin + per : cp.nvec;
-    for (int t = 0; t < 2; ++t) {
-      const uint4* src = cp.src[i][t];
-      uint4* dst = cp.dst[i][t];
-      long long v = begin + threadIdx.x;
-      // 16 independent 16-byte loads in flight per thread (12 copy CTAs then hold about 1.3 MB in flight, which a
-      // round trip of a few microseconds over NVLink turns into some 500 GB/s: on 8 ranks the seven remote segments
-      // have to arrive within the 2.7 ms of math); peer data bypasses L1 (the addresses are reused)
-      for (; v + 15 * NUM_THREADS < end; v += 16 * NUM_THREADS) {
-        uint4 r[16];
-#pragma unroll
-        for (int u = 0; u < 16; ++u) r[u] = __ldcg(src + v + u * NUM_THREADS);
-#pragma unroll
-        for (int u = 0; u < 16; ++u) dst[v + u * NUM_THREADS] = r[u];
-      }
-      for (; v + 3 * NUM_THREADS < end; v += 4 * NUM_THREADS) {
-        uint4 r[4];
-#pragma unroll
-        for (int u = 0; u < 4; ++u) r[u] = __ldcg(src + v + u * NUM_THREADS);
-#pragma unroll
-        for (int u = 0; u < 4; ++u) dst[v + u * NUM_THREADS] = r[u];
-      }
-      for (; v < end; v += NUM_THREADS) dst[v] = __ldcg(src + v);
-    }
+    const unsigned int col0 = static_cast<unsigned int>(g) * cp.group_vecs;
+    const unsigned int gv = min(cp.group_vecs, cp.row_vecs - col0);
+    const unsigned int total = cp.rows * gv;
+    const unsigned int per = (total + cp.n_copy_ctas - 1) / cp.n_copy_ctas;
+    const unsigned int begin = min(total, static_cast<unsigned int>(ci) * per);
+    const unsigned int end = min(total, begin + per);
+    for (int t = 0; t < 2; ++t) copy_slab(cp.src[i][t], cp.dst[i][t], begin, end, gv, cp.row_vecs, col0);
     asm volatile("fence.proxy.async.global;" ::: "memory");  // staged data is read back through TMA
     __threadfence();
     __syncthreads();
     if (threadIdx.x == 0) {
-      const unsigned int old = atomicAdd(cp.counters + i, 1u);
+      const unsigned int old = atomicAdd(cp.counters + u, 1u);
       if (old == static_cast<unsigned int>(cp.n_copy_ctas - 1)) {
         __threadfence();
-        asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(cp.seg_flags + 1 + i), "r"(cp.epoch) : "memory");
+        asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(cp.seg_flags + (1 + i) * MAX_GROUPS + g), "r"(cp.epoch)
+                     : "memory");
       }
     }
   }
   if (threadIdx.x == 0) {
-    const unsigned int old = atomicAdd(cp.counters + MAX_REMOTE, 1u);
+    const unsigned int old = atomicAdd(cp.counters + NUM_COUNTERS - 1, 1u);
     if (old == static_cast<unsigned int>(cp.n_copy_ctas - 1)) {
       // every remote shard has been read: tell the owners that their buffer may be overwritten
       for (int a = 0; a < cp.n_ack; ++a) {
@@ -256,7 +290,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
     if (lane == 0 && total_blocks > 0) {
       int stage = 0;
       uint32_t phase = 0;
-      uint32_t seen = 0;  // segments whose ready flag has been observed
+      unsigned long long seen = 0;  // (segment, head group) flags that have been observed
       bool ok = true;
       int it = 0;
       for (int work = blockIdx.x; work < total_work && ok; work += n_compute, ++it) {
@@ -274,10 +308,13 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
         }
         for (int seg = 0; seg < p.num_segments && ok; ++seg) {
           const int nblk = (p.kv_len[seg] + BKV - 1) / BKV;
-          if (nblk > 0 && p.seg_flags != nullptr && !((seen >> seg) & 1u)) {
-            if (!wait_flag(p.seg_flags + seg, p.flag_target, abort_flag, p.status, seg)) { ok = false; break; }
-            asm volatile("fence.proxy.async.global;" ::: "memory");
-            seen |= 1u << seg;
+          if (nblk > 0 && p.seg_flags != nullptr) {
+            const int fi = seg * p.flag_stride + head / p.heads_per_group;  // < MAX_SEGMENTS * MAX_GROUPS = 64
+            if (!((seen >> fi) & 1ull)) {
+              if (!wait_flag(p.seg_flags + fi, p.flag_target, abort_flag, p.status, fi)) { ok = false; break; }
+              asm volatile("fence.proxy.async.global;" ::: "memory");
+              seen |= 1ull << fi;
+            }
           }
           for (int jb = 0; jb < nblk; ++jb) {
             if (!mbar_wait(&k_empty[stage], phase ^ 1u, abort_flag, p.status, 41)) { ok = false; break; }
@@ -543,13 +580,14 @@ struct MdbCopyPlan {
   int n_copy_ctas;
   unsigned long long src[7][2];
   unsigned long long dst[7][2];
-  long long nbytes;                 // per tensor, multiple of 16
+  long long nbytes;                 // per tensor, multiple of 16; source and staging are contiguous [B, S, H, D]
   unsigned long long ready[7];
   unsigned int epoch;
-  unsigned long long counters;      // device uint32[8], zero at launch
-  unsigned long long seg_flags;     // device uint32[num_segments]
+  unsigned long long counters;      // device uint32[57] (7 segments x 8 head groups + 1), zero at launch
+  unsigned long long seg_flags;     // device uint32[num_segments * 8]: flag seg * 8 + g; row 0 (own shard) raised
   unsigned long long ack[8];
   int n_ack;
+  int n_groups;                     // head groups: 0 lets the launcher choose, 1 copies whole segments in order
 };
 
 // q: [B, q_len, H, 128]; k/v segment s: [B, kv_len[s], H, 128]; out like q. Strides are in elements
@@ -591,6 +629,8 @@ static int flash_fwd_launch(const void* q, const void* const* k_ptrs, const void
   p.scale_log2 = softmax_scale * 1.4426950408889634f;
   p.seg_flags = seg_flags;
   p.flag_target = flag_target;
+  p.flag_stride = 1;
+  p.heads_per_group = H;
   if ((m_fixed == nullptr) != (fixed_heads == nullptr)) return 3105;
   p.m_fixed = m_fixed;
   p.fixed_heads = fixed_heads;
@@ -610,7 +650,6 @@ static int flash_fwd_launch(const void* q, const void* const* k_ptrs, const void
       }
       cp.ready[i] = reinterpret_cast<const unsigned int*>(plan->ready[i]);
     }
-    cp.nvec = plan->nbytes >> 4;
     cp.epoch = plan->epoch;
     cp.counters = reinterpret_cast<unsigned int*>(plan->counters);
     cp.seg_flags = reinterpret_cast<unsigned int*>(plan->seg_flags);
@@ -635,6 +674,26 @@ static int flash_fwd_launch(const void* q, const void* const* k_ptrs, const void
   int n_compute = sm_count() - n_copy;
   if (n_compute < 1) return 3104;
   if (total_work < n_compute) n_compute = static_cast<int>(total_work);
+  if (n_copy > 0) {
+    // Head groups. The compute CTAs take the work list in rounds of n_compute items and the list runs through the
+    // q blocks of head 0, then head 1, ...: a round covers n_compute / n_qb heads. One group per round lets the first
+    // round start after 1 / rounds of the bytes; more than MAX_GROUPS rounds share groups.
+    const long long row_bytes = static_cast<long long>(H) * HD * 2;
+    if (plan->nbytes % row_bytes != 0) return 3106;
+    int hpg = n_compute / n_qb;
+    if (hpg < 1) hpg = 1;
+    if (hpg > H) hpg = H;
+    if ((H + hpg - 1) / hpg > MAX_GROUPS) hpg = (H + MAX_GROUPS - 1) / MAX_GROUPS;
+    if (plan->n_groups == 1) hpg = H;
+    else if (plan->n_groups > 1 && plan->n_groups <= MAX_GROUPS) hpg = (H + plan->n_groups - 1) / plan->n_groups;
+    cp.n_groups = (H + hpg - 1) / hpg;
+    cp.rows = static_cast<unsigned int>(plan->nbytes / row_bytes);
+    cp.row_vecs = static_cast<unsigned int>(row_bytes >> 4);
+    cp.group_vecs = static_cast<unsigned int>((static_cast<long long>(hpg) * HD * 2) >> 4);
+    if (static_cast<long long>(cp.rows) * cp.row_vecs >= (1ll << 31)) return 3107;  // slab indices are 32-bit
+    p.flag_stride = MAX_GROUPS;
+    p.heads_per_group = hpg;
+  }
   flash_fwd_kernel<HD><<<n_compute + n_copy, NUM_THREADS, smem_bytes<HD>(), static_cast<cudaStream_t>(stream_ptr)>>>(tq, maps, p, cp);
   return static_cast<int>(cudaGetLastError());
 }

@@ -48,6 +48,9 @@ __device__ __forceinline__ uint64_t global_timer_ns() {
 
 // Upper bound for any single device-side wait.
 constexpr uint64_t kWaitBudgetNs = 2000ull * 1000ull * 1000ull;  // 2 s
+// Upper bound for a wait on ANOTHER rank (a peer flag, or local data that a peer has to deliver first): ranks may be
+// skewed by host-side phases (first-step allocation, a checkpoint write), so this one is longer.
+constexpr uint64_t kPeerWaitBudgetNs = 10000ull * 1000ull * 1000ull;  // 10 s
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
   return static_cast<uint32_t>(__cvta_generic_to_shared(p));

@@ -813,7 +813,11 @@ extern "C" const char* mdb_colsum_noalloc_strerror(int code) {
 extern "C" int mdb_colsum_noalloc(const void* x, long long ldx, int rows, int cols, float* out, void* stream) {
   if (cols > MDB_COLSUM_NOALLOC_MAX_COLS) return MDB_NOALLOC_ERR_TOO_WIDE;
   if (cols <= 0 || (cols & 7) || ldx < cols) return MDB_NOALLOC_ERR_BAD_SHAPE;
-  if (rows <= 0) return MDB_NOALLOC_OK;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (rows <= 0) {
+    // the sum over no rows is zero: the caller still gets a defined result
+    return static_cast<int>(cudaMemsetAsync(out, 0, sizeof(float) * static_cast<size_t>(cols), st));
+  }
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kNoAllocMaxDevices) return MDB_NOALLOC_ERR_SETUP;
   float* scratch = g_colsum_scratch_addr[dev];
@@ -824,9 +828,10 @@ extern "C" int mdb_colsum_noalloc(const void* x, long long ldx, int rows, int co
     scratch = static_cast<float*>(addr);
     g_colsum_scratch_addr[dev] = scratch;
   }
-  cudaStream_t st = static_cast<cudaStream_t>(stream);
   const int ctas = rows < MDB_COLSUM_NOALLOC_CTAS ? rows : MDB_COLSUM_NOALLOC_CTAS;
   colsum_kernel<<<dim3(ctas, 1), THREADS, 0, st>>>(static_cast<const __nv_bfloat16*>(x), ldx, rows, cols, scratch);
+  const cudaError_t first = cudaGetLastError();  // each launch is checked: the second must not hide the first
+  if (first != cudaSuccess) return static_cast<int>(first);
   fold_partials_kernel<<<dim3((cols + 31) / 32, 1), 256, 0, st>>>(scratch, out, ctas, 1, cols, 0);
   return static_cast<int>(cudaGetLastError());
 }

@@ -31,7 +31,13 @@ class CopyPlan(ctypes.Structure):
               ("src", (ctypes.c_ulonglong * 2) * 7), ("dst", (ctypes.c_ulonglong * 2) * 7),
               ("nbytes", ctypes.c_longlong), ("ready", ctypes.c_ulonglong * 7), ("epoch", ctypes.c_uint),
               ("counters", ctypes.c_ulonglong), ("seg_flags", ctypes.c_ulonglong), ("ack", ctypes.c_ulonglong * 8),
-              ("n_ack", ctypes.c_int)]
+              ("n_ack", ctypes.c_int), ("n_groups", ctypes.c_int)]
+
+
+# layout constants of the copy plan (csrc/flash_fwd.cu): flags are rows of FLAG_STRIDE per KV segment, counters one per
+# (remote segment, head group) plus one
+COPY_FLAG_STRIDE = 8
+COPY_NUM_COUNTERS = 7 * 8 + 1
 
 
 def lib() -> ctypes.CDLL:
@@ -95,6 +101,12 @@ def raise_on_device_status() -> None:
   if code != 0:
     names = {1: "mbarrier wait timed out", 2: "flag wait timed out", 3: "bad argument"}
     raise KernelError(f"device status: {names.get(code, code)} at site {where}, block {block}, detail {detail}")
+
+
+def raise_on_device_status_if_loaded() -> None:
+  """The check the training and sampling loops make once per step: a no-op on CPU-only runs (library never loaded)."""
+  if _LIB is not None and torch.cuda.is_available():
+    raise_on_device_status()
 
 
 def _declare(L: ctypes.CDLL) -> None:

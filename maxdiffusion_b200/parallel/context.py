@@ -227,7 +227,12 @@ class ContextParallel:
         return None
       if key not in self._peers:
         self._peers[key] = symm.PeerGroup(group)
+      old = ex
+      # a larger tensor arrived: the new exchange continues the group's epochs with new buffers; the old buffers go
+      # only after the constructor's device synchronisation + barrier, when no peer can still be reading them
       ex = symm.PeerKVExchange(self._peers[key], k.numel(), k.dtype)
+      if old is not None:
+        old.release()
       self._exchanges[key] = ex
     return ex
 
@@ -245,7 +250,10 @@ class ContextParallel:
         return None
       if key not in self._peers:
         self._peers[key] = symm.PeerGroup(group)
+      old = ex
       ex = symm.PeerAllToAll(self._peers[key], x.numel(), x.dtype)
+      if old:
+        old.release()
       self._a2as[key] = ex
     return ex
 
@@ -257,7 +265,10 @@ class ContextParallel:
     if rs is None or rs.numel < need:
       from . import symm
 
+      old = rs
       rs = symm.PeerReduceScatter(self._peers[key], need, k.dtype)
+      if old is not None:
+        old.release()
       self._reducers[key] = rs
     return rs
 

@@ -335,9 +335,12 @@ class FSDPEngine:
     from . import symm
 
     g = self.groups[i]
+    # With replicas (a `data` axis), the reduced slice still has to be summed over the replica group before the
+    # statistics and the update may see it, so the kernel only reduces and the rest follows the all-reduce.
+    replicated = self.replica_group is not None
     deferred = self.opt.clip_global_norm > 0
-    self.grad_epoch += 1
-    e = self.grad_epoch
+    fused_apply = not deferred and not replicated
+    e = self.grad_epoch = self.peer.next_epoch(symm.FLAG_GRAD_READY)
     slot = e % 2
     self.peer.wait(symm.FLAG_GRAD_ACK, e - 2)           # everyone has consumed the previous content of this slot
     g.pack_grads(self.sym_grad[slot][:g.numel])
@@ -351,18 +354,24 @@ class FSDPEngine:
       off_bytes = self.rank * g.shard_numel * 2
       ptrs = [base + off_bytes for base in self.sym_grad_ptrs[slot]]
       reduced = None
-      if deferred:
+      if not fused_apply:
         reduced = torch.empty(g.shard_numel, dtype=self.param_dtype, device=self.device)
         reduced.record_stream(self.comm_stream)
-      symm.rs_adamw(ptrs, g.shard_numel, self.shards[i], self.m[i], self.v[i], self.grad_stats, self.rs_scratch,
+      # the statistics of a slice that is not final yet (replicas pending) go to a throw-away accumulator
+      stats = self.grad_stats if not replicated else torch.zeros_like(self.grad_stats)
+      symm.rs_adamw(ptrs, g.shard_numel, self.shards[i], self.m[i], self.v[i], stats, self.rs_scratch,
                     lr=self.lr, b1=o.b1, b2=o.b2, eps=o.eps, wd=o.weight_decay, step=self.step_count,
-                    clip_value=o.clip_value, seed=(self.seed * 1000003 + self.step_count) * 4099 + i,
-                    stochastic=o.stochastic_rounding, apply=not deferred, reduced_out=reduced, ctas=64)
+                    clip_value=o.clip_value,
+                    seed=(self.seed * 1000003 + self.step_count) * 4099 + i,
+                    stochastic=o.stochastic_rounding, apply=fused_apply, reduced_out=reduced, ctas=64)
       self.peer.signal(symm.FLAG_GRAD_ACK, e)
+      if replicated:
+        dist.all_reduce(reduced, group=self.replica_group)
+        self._stats(reduced)
       if deferred:
-        if self.replica_group is not None:
-          dist.all_reduce(reduced, group=self.replica_group)
         self.pending.append((i, reduced))
+      elif replicated:
+        self._adamw(self.shards[i], reduced, self.m[i], self.v[i], 1.0, i)
     for s in range(2):
       if self.slot_block[s] == i:
         self.slot_block[s] = -1

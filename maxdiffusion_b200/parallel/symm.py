@@ -33,7 +33,7 @@ FLAG_RS_ACK = 8
 FLAG_A2A_READY = 9
 FLAG_A2A_ACK = 10
 NUM_FLAG_KINDS = 12
-WAIT_BUDGET_S = 5.0
+WAIT_BUDGET_S = 10.0  # waits on other ranks: long enough for host-side skew (first-step allocation, logging)
 
 
 def _declare(L):
@@ -95,8 +95,22 @@ class PeerGroup:
     self._flags_hdl = symm_mem.rendezvous(self.flags, group)
     self.flag_ptrs = [int(p) for p in self._flags_hdl.buffer_ptrs]
     self._buffers = []
+    # One epoch counter per flag kind, owned by the group and not by the exchange objects: the pad keeps the largest
+    # epoch ever signalled, so an object created later (a larger tensor arrived) has to continue from there. An
+    # object that started again at zero would find every one of its waits satisfied by the stale values.
+    self.epochs = [0] * NUM_FLAG_KINDS
     torch.cuda.synchronize()
     dist.barrier(group=group)
+
+  def next_epoch(self, kind: int) -> int:
+    """Advances and returns the epoch of a flag kind (every rank of the group calls it in the same order)."""
+    self.epochs[kind] += 1
+    return self.epochs[kind]
+
+  def release(self, tensors) -> None:
+    """Forgets symmetric buffers handed out by `alloc` (their memory returns to the allocator once unused)."""
+    ids = {id(t) for t in tensors}
+    self._buffers = [(t, h) for (t, h) in self._buffers if id(t) not in ids]
 
   # ---- buffers ----------------------------------------------------------------------------
   def alloc(self, numel: int, dtype: torch.dtype):
@@ -142,7 +156,6 @@ class SmallAllReduce:
     self.capacity = capacity
     self.buf, self.buf_ptrs, self._hdl = peers.alloc(2 * capacity, torch.float32)
     self.buf.zero_()
-    self.epoch = 0
     n = peers.world
     self._bufs = (ctypes.c_ulonglong * n)(*self.buf_ptrs)
     self._flags = (ctypes.c_ulonglong * n)(*peers.flag_ptrs)
@@ -152,7 +165,7 @@ class SmallAllReduce:
   def __call__(self, x: torch.Tensor, op: str = "sum", out: Optional[torch.Tensor] = None) -> torch.Tensor:
     assert x.dtype == torch.float32 and x.is_contiguous() and 0 < x.numel() <= self.capacity
     out = torch.empty_like(x) if out is None else out
-    self.epoch += 1
+    self.epoch = self.peers.next_epoch(FLAG_SMALL_AR)
     rc = _lib.lib().mdb_small_allreduce(_lib.ptr(x), _lib.ptr(out), x.numel(), {"sum": 0, "max": 1}[op], self._bufs,
                                         self._flags, self.peers.world, self.peers.rank,
                                         FLAG_SMALL_AR * self.peers.world, self.capacity, self.epoch, WAIT_BUDGET_S,
@@ -193,20 +206,25 @@ class PeerKVExchange:
   reused two epochs later without a barrier.
   """
 
-  def __init__(self, peer: "PeerGroup", max_numel_per_tensor: int, dtype=torch.bfloat16, copy_ctas: int = 12):
+  def __init__(self, peer: "PeerGroup", max_numel_per_tensor: int, dtype=torch.bfloat16, copy_ctas: int = 12,
+               head_groups: int = 0):
     self.peer = peer
     self.n, self.rank = peer.world, peer.rank
     self.numel = max_numel_per_tensor
     self.copy_ctas = copy_ctas
+    self.head_groups = head_groups  # 0: the launcher picks one head group per round of work items; 1: whole segments
     self.slots, self.slot_ptrs = [], []
     for _ in range(2):
       t, ptrs, _h = peer.alloc(2 * max_numel_per_tensor, dtype)
       self.slots.append(t)
       self.slot_ptrs.append(ptrs)
-    self.epoch = 0
+    self.epoch = peer.epochs[FLAG_KV_READY]
     self.elem = torch.tensor([], dtype=dtype).element_size()
     torch.cuda.synchronize()
     dist.barrier(group=peer.group)
+
+  def release(self) -> None:
+    self.peer.release(self.slots)
 
   def order(self):
     """Ranks in the order the segments are consumed: own shard, then the ring predecessors."""
@@ -216,7 +234,7 @@ class PeerKVExchange:
     """Copies this rank's shard into the symmetric slot of a new epoch and raises KV_READY on every peer."""
     numel = k.numel()
     assert numel == v.numel() and numel <= self.numel and k.dtype == self.slots[0].dtype
-    self.epoch += 1
+    self.epoch = self.peer.next_epoch(FLAG_KV_READY)
     e = self.epoch
     slot = e % 2
     sym = self.slots[slot]
@@ -232,14 +250,17 @@ class PeerKVExchange:
 
   def plan(self, k: torch.Tensor, v: torch.Tensor):
     """Returns (kg, vg, flags, epoch, plan) for a fused launch: staging tensors [n, *k.shape] in consumption order,
-    the int32 ready flags (flag 0, the own shard, is already raised) and the copy plan for `kernels.flash_fwd`."""
+    the int32 ready flags (one row of `COPY_FLAG_STRIDE` head-group flags per segment; row 0, the own shard, is already
+    raised) and the copy plan for `kernels.flash_fwd`."""
     kg, vg, e, slot, nbytes = self.publish(k, v)
-    state = torch.zeros(self.n + 8, dtype=torch.int32, device=k.device)  # [flags (n) | counters (8)]
-    flags = state[:self.n]
-    set_flag(flags, 0, e)
+    fs = _lib.COPY_FLAG_STRIDE
+    state = torch.zeros(self.n * fs + _lib.COPY_NUM_COUNTERS + 7, dtype=torch.int32, device=k.device)  # [flags | counters]
+    flags = state[:self.n * fs]
+    flags[:fs].fill_(e)
     plan = _lib.CopyPlan()
     plan.n_remote = self.n - 1
     plan.n_copy_ctas = self.copy_ctas
+    plan.n_groups = self.head_groups
     pad = self.peer.flags.data_ptr()
     for i, src in enumerate(self.order()[1:]):
       base = self.slot_ptrs[slot][src]
@@ -248,7 +269,7 @@ class PeerKVExchange:
       plan.ready[i] = pad + 4 * (FLAG_KV_READY * self.n + src)
     plan.nbytes = nbytes
     plan.epoch = e
-    plan.counters = state.data_ptr() + 4 * self.n
+    plan.counters = state.data_ptr() + 4 * self.n * fs
     plan.seg_flags = flags.data_ptr()
     plan.n_ack = self.n
     for r in range(self.n):
@@ -294,9 +315,12 @@ class PeerAllToAll:
       t, ptrs, _h = peer.alloc(self.numel, dtype)
       self.slots.append(t)
       self.slot_ptrs.append(ptrs)
-    self.epoch = 0
+    self.epoch = peer.epochs[FLAG_A2A_READY]
     torch.cuda.synchronize()
     dist.barrier(group=peer.group)
+
+  def release(self) -> None:
+    self.peer.release(self.slots)
 
   @staticmethod
   def supports(x: torch.Tensor, n: int) -> bool:
@@ -304,7 +328,7 @@ class PeerAllToAll:
 
   def _publish(self, x: torch.Tensor):
     assert x.numel() <= self.numel and x.dtype == self.dtype
-    self.epoch += 1
+    self.epoch = self.peer.next_epoch(FLAG_A2A_READY)
     e, slot = self.epoch, self.epoch % 2
     self.peer.wait(FLAG_A2A_ACK, e - 2)  # every peer has pulled the previous content of this slot
     self.slots[slot][:x.numel()].view(x.shape).copy_(x)
@@ -372,10 +396,13 @@ class PeerReduceScatter:
       t, ptrs, _h = peer.alloc(self.n * self.numel, dtype)
       self.slots.append(t)
       self.slot_ptrs.append(ptrs)
-    self.epoch = 0
+    self.epoch = peer.epochs[FLAG_RS_READY]
     self.stream = torch.cuda.Stream()  # callers may run `reduce` here, underneath compute on their own stream
     torch.cuda.synchronize()
     dist.barrier(group=peer.group)
+
+  def release(self) -> None:
+    self.peer.release(self.slots)
 
   def slices(self, shape):
     """Starts an epoch: views [n][*shape] of the slot to be filled (slice r = partial for owner r)."""
@@ -383,7 +410,7 @@ class PeerReduceScatter:
     for d in shape:
       numel *= int(d)
     assert numel <= self.numel and numel % 8 == 0, (numel, self.numel)
-    self.epoch += 1
+    self.epoch = self.peer.next_epoch(FLAG_RS_READY)
     self.peer.wait(FLAG_RS_ACK, self.epoch - 2)  # every owner has pulled the previous content of this slot
     sym = self.slots[self.epoch % 2]
     self._shape, self._numel = tuple(shape), numel

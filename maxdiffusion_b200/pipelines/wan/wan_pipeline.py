@@ -23,6 +23,7 @@ import torch.distributed as dist
 from ... import max_logging
 from ...models.wan.autoencoder_kl_wan import AutoencoderKLWan, WanVAEConfig, postprocess_video
 from ...models.wan.transformer_wan import WAN_PRESETS, WanConfig, WanModel, wan_rope_tables
+from ...ops import _lib
 from ...ops import functional as OF
 from ...parallel.context import ContextParallel
 from ...parallel.mesh import DeviceMesh, create_device_mesh
@@ -296,7 +297,11 @@ class WanPipeline:
         if sen is not None:
           sen.record_full(latents, t, noise)
       latents, state = self.scheduler.step(state, noise, t, latents)
+      if self.pctx is not None:
+        # kernels of this step waited (bounded) on other ranks: a wait that ran out must not feed the next step
+        _lib.raise_on_device_status_if_loaded()
     sync()
+    _lib.raise_on_device_status_if_loaded()
     trace["denoise_total"] = time.perf_counter() - t_loop
     trace["denoise_per_step"] = trace["denoise_total"] / max(1, steps)
 

@@ -18,6 +18,7 @@ import torch
 import torch.distributed as dist
 
 from ..models.gradient_checkpoint import resolve_remat
+from ..ops import _lib
 from ..ops import functional as OF
 
 from .. import max_logging
@@ -126,10 +127,16 @@ class WanTrainer:
   def load_dataset(self):
     dataset_type = str(self.config.get("dataset_type", "synthetic"))
     if dataset_type == "synthetic":
-      return make_synthetic_iterator(self.config, self.batch_size, seed=int(self.config.get("seed", 0)) + 17)
+      # ranks along `data` x `fsdp` draw different samples; the context / tensor ranks of a replica draw the same ones
+      return make_synthetic_iterator(self.config, self.batch_size,
+                                     seed=int(self.config.get("seed", 0)) + 17 + 1009 * self.batch_index())
     from ..input_pipeline.input_pipeline_interface import make_data_iterator
 
     return make_data_iterator(self.config, self.mesh, self.batch_size)
+
+  def batch_index(self) -> int:
+    """Index of this rank's replica among the `data` x `fsdp` ranks that hold different samples."""
+    return self.mesh.coords.get("data", 0) * self.mesh.size("fsdp") + self.mesh.coords.get("fsdp", 0)
 
   def to_device(self, batch: dict) -> dict:
     out = {}
@@ -152,8 +159,14 @@ class WanTrainer:
     lr = lr_schedule(self.step, self.base_lr, self.schedule_steps, self.warmup_fraction)
     self.engine.begin_step(lr)
 
-    timesteps = self.scheduler.sample_timesteps(B, generator=self.gen, device=self.device)
-    noise = torch.randn(latents.shape, generator=self.gen, device=self.device, dtype=torch.float32).to(self.dtype)
+    # a batch may bring its own timesteps and noise (evaluation at fixed timesteps, reproducible comparisons)
+    timesteps = batch.get("timesteps")
+    if timesteps is None:
+      timesteps = self.scheduler.sample_timesteps(B, generator=self.gen, device=self.device)
+    noise = batch.get("noise")
+    if noise is None:
+      noise = torch.randn(latents.shape, generator=self.gen, device=self.device, dtype=torch.float32)
+    noise = noise.to(self.dtype)
     noisy, target, weights = self.scheduler.apply_flow_match(noise.float(), latents.float(), timesteps, self.scheduler_state)
 
     pred = self.model(noisy.to(self.dtype), timesteps, text, pctx=self.pctx, return_tokens=True,
@@ -168,16 +181,35 @@ class WanTrainer:
     # weighted squared error and its gradient in one fused pass; normalised by the global element count so that
     # the per-rank losses of a sequence-sharded step add up to the mean
     local = OF.weighted_mse(pred, tgt_tokens, weights.tolist() if self.use_weights else None)
-    loss = local * (pred.numel() / total)
+    # Ranks along `data` and `fsdp` hold different samples and their gradients are summed by the reduce-scatter and
+    # the replica all-reduce, so each rank's share is divided by the number of batch replicas: the applied gradient,
+    # the logged norm and the clipping thresholds then refer to the mean over the global batch, as in the reference
+    # (src/maxdiffusion/trainers/wan_trainer.py:150-168, a mean over the batch axis of the global array).
+    replicas = self.mesh.size("data") * self.mesh.size("fsdp")
+    loss = local * (pred.numel() / total / replicas)
     loss.backward()
     stats = self.engine.finish_step(model_group=self.mesh.group("model"))
     loss_value = loss.detach()
-    if self.mesh.group("model") is not None:
+    if self.mesh.world_size > 1:
       loss_value = loss_value.clone()
-      dist.all_reduce(loss_value, group=self.mesh.group("model"))
+      for name in ("model", "replica"):
+        if self.mesh.group(name) is not None:
+          dist.all_reduce(loss_value, group=self.mesh.group(name))
+      loss_value = loss_value / self.mesh.size("tensor")  # tensor ranks of a replica repeat the same partial loss
     self.step += 1
     return {"learning/loss": loss_value, "learning/max_grad_norm": stats["grad_norm"],
             "learning/max_abs_grad": stats["max_abs_grad"], "learning/current_learning_rate": lr}
+
+  def _save(self, checkpointer, monitor) -> None:
+    """Checkpoint write bracketed by a device-status check and a host-side barrier: saving is a rank-asymmetric host
+    phase (rank 0 writes for seconds), and the peers' next kernels must not start their bounded waits on a rank
+    that is still writing."""
+    _lib.raise_on_device_status_if_loaded()
+    checkpointer.save(self.step, self)
+    if monitor is not None:
+      monitor.barrier()
+    elif self.mesh.world_size > 1:
+      dist.barrier()
 
   # ------------------------------------------------------------------ loop
   def seq_len(self) -> int:
@@ -226,6 +258,9 @@ class WanTrainer:
       with guarded_step(monitor, self.step):  # peers are checked on the host before this step's first launch
         metrics = self.train_step(batch)
         loss = float(metrics["learning/loss"])  # device -> host, ends the step
+        # a device-side wait that ran out (a peer that stopped signalling) left stale data behind: raise here, inside
+        # the guard, so that the peers learn of it and nothing of this step reaches a checkpoint
+        _lib.raise_on_device_status_if_loaded()
       dt = time.perf_counter() - t0
       if profiler is not None:
         profiler.maybe_stop(self.step)
@@ -237,9 +272,9 @@ class WanTrainer:
       if eval_every > 0 and self.step % eval_every == 0 and str(config.get("dataset_type", "synthetic")) != "synthetic":
         self.eval(self.step, writer)
       if checkpointer is not None and int(config.get("checkpoint_every", -1)) > 0 and self.step % int(config.checkpoint_every) == 0:
-        checkpointer.save(self.step, self)
+        self._save(checkpointer, monitor)
     if checkpointer is not None and config.get("save_final_checkpoint", False):
-      checkpointer.save(self.step, self)
+      self._save(checkpointer, monitor)
     writer.close()
     if monitor is not None:
       monitor.stop()

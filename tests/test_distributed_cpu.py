@@ -67,6 +67,55 @@ def test_two_rank_training_with_kept_blocks_matches_single_process():
       assert digest[k] == pytest.approx(v, rel=1e-4, abs=1e-4), k
 
 
+def _train_batch_axes(rank, world, axes, steps):
+  """Global batch of 2 samples with fixed noise / timesteps; `axes` = (data, fsdp) sizes. Every batch replica trains
+  on its own sample; with one process the same two samples form one batch."""
+  from maxdiffusion_b200 import pyconfig
+  from maxdiffusion_b200.parallel.mesh import create_device_mesh
+  from maxdiffusion_b200.trainers.wan_trainer import WanTrainer
+
+  data, fsdp = axes
+  config = pyconfig.initialize(
+      ["t", CFG, "run_name=t", "height=64", "width=48", "num_frames=9", "dataset_type=synthetic", "wan_preset=tiny",
+       f"wan_config_overrides={TINY}", "remat_policy=FULL", "warmup_steps_fraction=0.0", "log_config=false",
+       "write_metrics=false", "learning_rate=1e-3", "attention=flash", f"per_device_batch_size={2 // (data * fsdp)}",
+       "synthetic_override_text_dim=48", "max_sequence_length=16", f"ici_data_parallelism={data}",
+       f"ici_fsdp_parallelism={fsdp}", "ici_context_parallelism=1"], unittest=True)
+  torch.manual_seed(0)
+  tr = WanTrainer(config, mesh=create_device_mesh(config), device="cpu")
+  g = torch.Generator().manual_seed(11)
+  losses = []
+  for _ in range(steps):
+    full = {"latents": torch.randn(2, 16, 3, 8, 6, generator=g), "encoder_hidden_states": torch.randn(2, 16, 48, generator=g),
+            "noise": torch.randn(2, 16, 3, 8, 6, generator=g), "timesteps": torch.tensor([200.0, 700.0])}
+    if data * fsdp == 2:
+      i = tr.batch_index()
+      full = {k: v[i:i + 1] for k, v in full.items()}
+    m = tr.train_step(full)
+    losses.append(float(m["learning/loss"]))
+  names = [[n for n, _ in b.named_parameters()] for b in tr.model.blocks]
+  block_ids = {id(p) for b in tr.model.blocks for p in b.parameters()}
+  root_names = [n for n, p in tr.model.named_parameters() if id(p) not in block_ids]
+  sd = tr.engine.gather_state_dict(names, root_names)
+  digest = {k: v.double().sum().item() for k, v in list(sd.items())[:6]}
+  return losses, digest, float(m["learning/max_grad_norm"])
+
+
+@pytest.mark.parametrize("axes", [(2, 1), (1, 2)])
+def test_ranks_with_different_samples_match_one_process_with_the_whole_batch(axes):
+  """data = 2 (replicated weights, gradient all-reduce) and fsdp = 2 (sharded weights, reduce-scatter): the applied
+  update, the logged loss and the gradient norm are those of the mean over the global batch, and the replicas end
+  up with identical weights."""
+  ref_losses, ref_digest, ref_gn = _train_batch_axes(0, 1, (1, 1), 2)
+  out = run_ranks(_train_batch_axes, 2, axes, 2)
+  for losses, digest, gn in out:
+    assert losses == pytest.approx(ref_losses, rel=2e-4, abs=1e-5)
+    assert gn == pytest.approx(ref_gn, rel=2e-3)
+    for k, v in ref_digest.items():
+      assert digest[k] == pytest.approx(v, rel=1e-4, abs=1e-4), k
+  assert out[0][1] == pytest.approx(out[1][1], rel=1e-9)
+
+
 def _collectives(rank, world):
   import torch.distributed as dist
 

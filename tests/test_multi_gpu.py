@@ -136,6 +136,24 @@ def _kv_exchange(rank, world):
     errs.append((out.float() - want.float()).abs().max().item())
     order = ex.order()
     assert all(torch.equal(kg[j], k_all[order[j]]) for j in range(world))
+  # head-group slabs with a ragged last group (5 heads in groups of 2, 2, 1), two batch rows, on a NEW exchange of the
+  # same peer group: its epochs continue where the first exchange stopped, so no wait is satisfied by a stale flag
+  B, S, H = 2, 392, 5
+  grouped = symm.PeerKVExchange(peer, B * S * H * 128, head_groups=3)
+  for it in range(3):
+    torch.manual_seed(77 * it + rank)
+    q = torch.randn((B, S, H, 128), device="cuda", dtype=torch.bfloat16)
+    k = torch.randn((B, S, H, 128), device="cuda", dtype=torch.bfloat16)
+    v = torch.randn((B, S, H, 128), device="cuda", dtype=torch.bfloat16)
+    kg, vg, flags, epoch, plan, keep = grouped.plan(k, v)
+    out, _ = K.flash_fwd(q, list(kg), list(vg), seg_flags=flags, flag_target=epoch, plan=plan)
+    k_all = C.all_gather_stack(k, dist.group.WORLD)
+    v_all = C.all_gather_stack(v, dist.group.WORLD)
+    order = grouped.order()
+    want = ref.attention(q, [k_all[r] for r in order], [v_all[r] for r in order])
+    errs.append((out.float() - want.float()).abs().max().item())
+    assert all(torch.equal(kg[j], k_all[order[j]]) and torch.equal(vg[j], v_all[order[j]]) for j in range(world))
+  assert grouped.epoch == 6 and peer.epochs[symm.FLAG_KV_READY] == 6
   # full-occupancy case: more tiles than SMs, 42 MB per shard -- the copy CTAs must make progress while every
   # other SM holds a compute CTA; compared bit for bit with the same kernel on NCCL-gathered K/V
   B, S, H = 1, 4096, 40

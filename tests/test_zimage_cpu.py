@@ -45,7 +45,7 @@ def test_sigmas_and_pipeline_and_checkpoint_round_trip(tmp_path):
   from maxdiffusion_b200.checkpointing.z_image_checkpointer import ZImageCheckpointer
 
   argv = ["x", CFG, "random_init=True", "zimage_preset=tiny", f"vae_config_overrides={TINY_VAE}",
-          f"checkpoint_dir={tmp_path}/ckpt", "pretrained_model_name_or_path=/nonexistent"]
+          f"output_dir={tmp_path}/out", "pretrained_model_name_or_path=/nonexistent"]
   config = pyconfig.initialize(argv)
   ck = ZImageCheckpointer(config)
   pipe = ck.load_pipeline()

@@ -54,3 +54,14 @@ def test_no_alloc_colsum_rejects_what_does_not_fit():
   assert rc == -1 and b"8192" in err(rc)
   rc = fn(ctypes.c_void_p(x.data_ptr()), 8, 4, 12, ctypes.c_void_p(out.data_ptr()), stream)
   assert rc == -2
+
+
+def test_no_alloc_colsum_of_no_rows_is_zero():
+  fn, err = _symbols()
+  x = torch.zeros((8, 16), device="cuda", dtype=torch.bfloat16)
+  out = torch.full((16,), float("nan"), device="cuda", dtype=torch.float32)
+  stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+  rc = fn(ctypes.c_void_p(x.data_ptr()), 16, 0, 16, ctypes.c_void_p(out.data_ptr()), stream)
+  assert rc == 0, err(rc).decode()
+  torch.cuda.synchronize()
+  assert torch.equal(out, torch.zeros_like(out))
