@@ -1,0 +1,340 @@
+"""Channels-last convolutions on the implicit-GEMM kernel (`csrc/conv_igemm.cu`) and the row norm that goes with them.
+
+Tensors are channels-last bf16: video `[B, T, H, W, C]`, images `[B, H, W, C]`. A convolution is described to the
+kernel as a table of taps (coordinate shifts + the K range of the tap in the packed weight matrix); this module builds
+the tables and packs the weights:
+
+  conv3d_causal      3x3x3 / (3,1,1) causal convolution with an optional 2-frame history tensor (the reference's
+                     `WanCausalConv3d` and its feature cache, src/maxdiffusion/models/wan/autoencoder_kl_wan.py:70-147)
+  conv2d             3x3 / 1x1, stride 1 or 2 (zero padding given per side; `WanResample` down-sampling pads right /
+                     bottom only, the UNet pads all sides: :245-389, src/maxdiffusion/models/resnet_flax.py:37-95)
+  upsample2x_conv2d  nearest-2x followed by a 3x3 convolution, computed at LOW resolution as four parity classes of
+                     2x2 convolutions with pre-summed weights (2.25x fewer FLOPs, no up-sampled tensor)
+  conv2d_dgrad       gradient of conv2d with respect to its input, as a convolution of dY with the transposed,
+                     flipped weights (stride 2: parity classes of the input)
+  rms_act            `WanRMS_norm` (+ SiLU) over the channel axis
+
+CPU tensors and fp32 run the PyTorch reference (`F.conv3d` / `F.conv2d`), which is also the oracle of the tests.
+"""
+from __future__ import annotations
+
+import ctypes
+from dataclasses import dataclass
+from typing import Optional, Sequence
+
+import torch
+import torch.nn.functional as F
+
+from . import _lib
+
+
+def _declare(L):
+  c_void_p, c_int, c_ll = ctypes.c_void_p, ctypes.c_int, ctypes.c_longlong
+  llp, ip = ctypes.POINTER(c_ll), ctypes.POINTER(c_int)
+  L.mdb_conv_igemm.argtypes = [c_void_p] * 6 + [llp] * 4 + [ip, ip, c_int, c_int, c_ll, c_int, ip, ip, c_int, c_int,
+                                                           llp, llp, c_int, c_void_p]
+  L.mdb_conv_igemm.restype = c_int
+  L.mdb_rms_act_cl.argtypes = [c_void_p, c_ll, c_void_p, c_ll, c_void_p, c_void_p, c_ll, c_int, ctypes.c_float, c_int,
+                               c_void_p]
+  L.mdb_rms_act_cl.restype = c_int
+
+
+_lib.register(_declare)
+
+
+def use_kernel(x: torch.Tensor) -> bool:
+  return x.is_cuda and x.dtype == torch.bfloat16
+
+
+def _round_up(v: int, m: int) -> int:
+  return (v + m - 1) // m * m
+
+
+@dataclass
+class PackedConv:
+  """Weights of one convolution in the kernel's layout, with its tap table."""
+  w: torch.Tensor                 # [N_pad, n_taps * c_pad] bf16, K-major
+  bias: Optional[torch.Tensor]    # [N_pad] bf16 or None
+  taps: list                      # per class: list of (o0, o1, o2, o3, o4) ; koff is the running tap index * c_pad
+  c_in: int                       # channels the activation must have (multiple of 16)
+  c_pad: int                      # K span of a tap (multiple of 64)
+  n_out: int                      # true output channels
+  n_pad: int                      # multiple of 8
+  kind: str
+
+  def tap_arrays(self):
+    flat, begin, k = [], [0], 0
+    for cls in self.taps:
+      for t in cls:
+        flat.extend([*t, k * self.c_pad])
+        k += 1
+      begin.append(k)
+    return (ctypes.c_int * len(flat))(*flat), (ctypes.c_int * len(begin))(*begin), len(self.taps)
+
+
+def _pack(w_taps: torch.Tensor, bias, taps, kind: str) -> PackedConv:
+  """w_taps: [N, n_taps, C] (any float dtype) -> PackedConv with channels padded to 16 / 64 and N padded to 8."""
+  n, n_taps, c = w_taps.shape
+  c_in, c_pad, n_pad = _round_up(c, 16), _round_up(c, 64), _round_up(n, 8)
+  w = torch.zeros((n_pad, n_taps, c_pad), dtype=torch.bfloat16, device=w_taps.device)
+  w[:n, :, :c] = w_taps.to(torch.bfloat16)
+  b = None
+  if bias is not None:
+    b = torch.zeros(n_pad, dtype=torch.bfloat16, device=w_taps.device)
+    b[:n] = bias.to(torch.bfloat16)
+  return PackedConv(w.reshape(n_pad, n_taps * c_pad), b, taps, c_in, c_pad, n, n_pad, kind)
+
+
+def pack_conv3d(weight: torch.Tensor, bias=None) -> PackedConv:
+  """weight [Co, Ci, kt, kh, kw] (causal in time, 'same' in space)."""
+  co, ci, kt, kh, kw = weight.shape
+  taps = [[(0, b - kw // 2, a - kh // 2, t - (kt - 1), 0) for t in range(kt) for a in range(kh) for b in range(kw)]]
+  return _pack(weight.permute(0, 2, 3, 4, 1).reshape(co, kt * kh * kw, ci), bias, taps, "conv3d")
+
+
+def pack_conv2d(weight: torch.Tensor, bias=None, stride: int = 1, pad_top_left: Optional[int] = None) -> PackedConv:
+  """weight [Co, Ci, kh, kw]. `pad_top_left`: zero rows / columns before the image (default k // 2); the far side is
+  padded with whatever the output size needs (out = in for stride 1, in / 2 for stride 2)."""
+  co, ci, kh, kw = weight.shape
+  p = kh // 2 if pad_top_left is None else pad_top_left
+  w = weight.permute(0, 2, 3, 1).reshape(co, kh * kw, ci)
+  if stride == 1:
+    taps = [[(0, b - p, a - p, 0, 0) for a in range(kh) for b in range(kw)]]
+    return _pack(w, bias, taps, "conv2d")
+  assert stride == 2
+  # activation seen as [B, H/2, 2, W/2, 2C]: input row 2*oh + a - p = 2*(oh + dh) + ph
+  c16 = _round_up(ci, 16)
+  taps = [[]]
+  for a in range(kh):
+    dh, ph = divmod(a - p, 2)
+    for b in range(kw):
+      dw, pw = divmod(b - p, 2)
+      taps[0].append((pw * c16, dw, ph, dh, 0))
+  return _pack(w, bias, taps, "conv2d_s2")
+
+
+def _upsample_parity_taps():
+  """For output parity r: which low-resolution shift each of the 3 kernel rows reads: floor((r + a - 1) / 2)."""
+  return {r: [((r + a - 1) // 2) for a in range(3)] for r in (0, 1)}
+
+
+def pack_upsample_conv2d(weight: torch.Tensor, bias=None) -> PackedConv:
+  """nearest-2x + 3x3 'same' conv -> four classes (rh, rw) of 2x2 convolutions on the low-resolution input."""
+  co, ci, kh, kw = weight.shape
+  assert kh == 3 and kw == 3
+  shift = _upsample_parity_taps()
+  w32 = weight.float()
+  mats, taps = [], []
+  for rh in (0, 1):
+    for rw in (0, 1):
+      cls = []
+      for dp in sorted(set(shift[rh])):
+        for dq in sorted(set(shift[rw])):
+          rows = [a for a in range(3) if shift[rh][a] == dp]
+          cols = [b for b in range(3) if shift[rw][b] == dq]
+          mats.append(w32[:, :, rows][:, :, :, cols].sum(dim=(2, 3)))  # [Co, Ci]
+          cls.append((0, dq, dp, 0, 0))
+      taps.append(cls)
+  return _pack(torch.stack(mats, dim=1), bias, taps, "upsample_conv2d")
+
+
+def pack_conv2d_dgrad(weight: torch.Tensor, stride: int = 1, pad_top_left: Optional[int] = None) -> PackedConv:
+  """Weights for dX = conv2d_dgrad(dY): contraction over Co, output channels Ci."""
+  co, ci, kh, kw = weight.shape
+  p = kh // 2 if pad_top_left is None else pad_top_left
+  wt = weight.permute(1, 2, 3, 0)  # [Ci, kh, kw, Co]
+  if stride == 1:
+    # dX[i] = sum_a dY[i + p - a] W[a]
+    taps = [[(0, p - b, p - a, 0, 0) for a in range(kh) for b in range(kw)]]
+    return _pack(wt.reshape(ci, kh * kw, co), None, taps, "conv2d")
+  assert stride == 2
+  # input row 2*u + r receives dY[u + (r + p - a) / 2] W[a] for the a with (r + p - a) even
+  mats, taps = [], []
+  for rh in (0, 1):
+    for rw in (0, 1):
+      cls = []
+      for a in range(kh):
+        if (rh + p - a) % 2:
+          continue
+        for b in range(kw):
+          if (rw + p - b) % 2:
+            continue
+          mats.append(wt[:, a, b, :])
+          cls.append((0, (rw + p - b) // 2, (rh + p - a) // 2, 0, 0))
+      taps.append(cls)
+  return _pack(torch.stack(mats, dim=1), None, taps, "conv2d_dgrad_s2")
+
+
+def _pick_box(e1: int, e2: int, e3: int, allow3: bool):
+  """Tile (b1, b2, b3) with b1 * b2 * b3 = 128 that covers the e1 x e2 x e3 output positions with the least padding;
+  among equals the widest along the fastest axis."""
+  best, best_cost = None, None
+  for l1 in range(8):
+    for l2 in range(8 - l1):
+      l3 = 7 - l1 - l2
+      b1, b2, b3 = 1 << l1, 1 << l2, 1 << l3
+      if b3 > 1 and not allow3:
+        continue
+      cost = _round_up(e1, b1) * _round_up(e2, b2) * _round_up(e3, b3)
+      key = (cost, -b1, -b2)
+      if best_cost is None or key < best_cost:
+        best, best_cost = (b1, b2, b3), key
+  return best
+
+
+def _launch(x, x_alt, pk: PackedConv, dims, strides, alt_dims, alt_strides, box, ext, out, out_strides, class_off,
+            residual, silu, alt_dim=-1, alt_shift=0):
+  taps, begin, n_classes = pk.tap_arrays()
+  LL, I = ctypes.c_longlong, ctypes.c_int
+  arr = lambda T, v: (T * len(v))(*[int(i) for i in v])
+  rc = _lib.lib().mdb_conv_igemm(
+      _lib.ptr(x), _lib.ptr(x_alt), _lib.ptr(pk.w), _lib.ptr(out), _lib.ptr(pk.bias), _lib.ptr(residual),
+      arr(LL, dims), arr(LL, strides), arr(LL, alt_dims if alt_dims else dims), arr(LL, alt_strides if alt_strides else strides),
+      arr(I, box), arr(I, ext), pk.c_in, pk.n_pad, pk.w.shape[1], n_classes, begin, taps, alt_dim, alt_shift,
+      arr(LL, out_strides), arr(LL, class_off), 1 if silu else 0, _lib.stream())
+  _lib.check(rc, "mdb_conv_igemm")
+  return out
+
+
+def _check_cl(x: torch.Tensor, c_in: int):
+  assert x.dtype == torch.bfloat16 and x.stride(-1) == 1, "channels-last bf16 expected"
+  assert x.shape[-1] == c_in, f"activation has {x.shape[-1]} channels, the packed weights expect {c_in} (pad to 16)"
+  assert all(s % 8 == 0 for s in x.stride()[:-1]) and x.data_ptr() % 16 == 0
+
+
+def pad_channels(x: torch.Tensor, c: int) -> torch.Tensor:
+  """Zero-pads the last (channel) axis up to c."""
+  return x if x.shape[-1] == c else F.pad(x, (0, c - x.shape[-1]))
+
+
+def conv3d_causal(x: torch.Tensor, pk: PackedConv, hist: Optional[torch.Tensor] = None,
+                  residual: Optional[torch.Tensor] = None, silu: bool = False) -> torch.Tensor:
+  """x [B, T, H, W, C] -> [B, T, H, W, N]. `hist` [B, 2, H, W, C]: the two frames before x (None: zeros)."""
+  _check_cl(x, pk.c_in)
+  B, T, H, W, C = x.shape
+  out = torch.empty((B, T, H, W, pk.n_pad), dtype=x.dtype, device=x.device)
+  b1, b2, _ = _pick_box(W, H, 1, False)
+  alt_dims = alt_strides = None
+  if hist is not None:
+    _check_cl(hist, pk.c_in)
+    assert hist.shape == (B, 2, H, W, C)
+    alt_dims = [C, W, H, 2, B]
+    alt_strides = [hist.stride(3), hist.stride(2), hist.stride(1), hist.stride(0)]
+  if residual is not None:
+    assert residual.shape == out.shape and residual.is_contiguous()
+  n = pk.n_pad
+  _launch(x, hist, pk, [C, W, H, T, B], [x.stride(3), x.stride(2), x.stride(1), x.stride(0)], alt_dims, alt_strides,
+          [b1, b2, 1], [W, H, T, B], out, [n, W * n, H * W * n, T * H * W * n], [0], residual, silu, alt_dim=3, alt_shift=2)
+  return out if pk.n_pad == pk.n_out else out[..., :pk.n_out]
+
+
+def conv2d(x: torch.Tensor, pk: PackedConv, residual: Optional[torch.Tensor] = None, silu: bool = False) -> torch.Tensor:
+  """x [B, H, W, C] -> [B, Ho, Wo, N] (Ho = H for stride 1, H / 2 for stride 2)."""
+  _check_cl(x, pk.c_in)
+  B, H, W, C = x.shape
+  n = pk.n_pad
+  if pk.kind == "conv2d":
+    out = torch.empty((B, H, W, n), dtype=x.dtype, device=x.device)
+    box = _pick_box(W, H, B, True)
+    dims, strides = [C, W, H, B, 1], [x.stride(2), x.stride(1), x.stride(0), x.stride(0) * B]
+    ext, os_ = [W, H, B, 1], [n, W * n, H * W * n, B * H * W * n]
+  elif pk.kind == "conv2d_s2":
+    assert H % 2 == 0 and W % 2 == 0 and x.stride(2) == C, "stride 2 needs even sizes and dense rows"
+    Ho, Wo = H // 2, W // 2
+    out = torch.empty((B, Ho, Wo, n), dtype=x.dtype, device=x.device)
+    b1, b3, _ = _pick_box(Wo, Ho, 1, False)
+    box = (b1, 1, b3)
+    dims, strides = [2 * C, Wo, 2, Ho, B], [2 * C, x.stride(1), 2 * x.stride(1), x.stride(0)]
+    ext, os_ = [Wo, 1, Ho, B], [n, 0, Wo * n, Ho * Wo * n]
+  else:
+    raise ValueError(f"conv2d cannot run weights packed as {pk.kind}")
+  if residual is not None:
+    assert residual.shape == out.shape and residual.is_contiguous()
+  _launch(x, None, pk, dims, strides, None, None, box, ext, out, os_, [0], residual, silu)
+  return out if pk.n_pad == pk.n_out else out[..., :pk.n_out]
+
+
+def _parity_conv(x, pk, silu=False):
+  """Shared by the fused up-sampling convolution and the stride-2 dgrad: x [B, H, W, C] -> [B, 2H, 2W, N], class
+  (rh, rw) writes the output positions (2p + rh, 2q + rw)."""
+  _check_cl(x, pk.c_in)
+  B, H, W, C = x.shape
+  n = pk.n_pad
+  out = torch.empty((B, 2 * H, 2 * W, n), dtype=x.dtype, device=x.device)
+  box = _pick_box(W, H, B, True)
+  class_off = [rh * 2 * W * n + rw * n for rh in (0, 1) for rw in (0, 1)]
+  _launch(x, None, pk, [C, W, H, B, 1], [x.stride(2), x.stride(1), x.stride(0), x.stride(0) * B], None, None, box,
+          [W, H, B, 1], out, [2 * n, 4 * W * n, 4 * H * W * n, 4 * B * H * W * n], class_off, None, silu)
+  return out if pk.n_pad == pk.n_out else out[..., :pk.n_out]
+
+
+def upsample2x_conv2d(x: torch.Tensor, pk: PackedConv) -> torch.Tensor:
+  assert pk.kind == "upsample_conv2d"
+  return _parity_conv(x, pk)
+
+
+def conv2d_dgrad(dy: torch.Tensor, pk: PackedConv) -> torch.Tensor:
+  """dX for a conv2d whose weights were packed with `pack_conv2d_dgrad` (dy is [B, Ho, Wo, Co], channels-last)."""
+  if pk.kind == "conv2d_dgrad_s2":
+    if any(len(c) == 0 for c in pk.taps):
+      raise ValueError("a 1x1 stride-2 convolution leaves input parities without a tap; use the dense fallback")
+    return _parity_conv(dy, pk)
+  return conv2d(dy, pk)
+
+
+def rms_act(x: torch.Tensor, gamma: torch.Tensor, beta: Optional[torch.Tensor] = None, silu: bool = True,
+            eps: float = 1e-12) -> torch.Tensor:
+  """y = act(x / max(||x||, eps) * sqrt(C) * gamma + beta) over the last axis of a channels-last tensor."""
+  C = x.shape[-1]
+  if not use_kernel(x):
+    y = F.normalize(x.float(), dim=-1, eps=eps) * (C ** 0.5) * gamma.float().reshape(-1)
+    if beta is not None:
+      y = y + beta.float().reshape(-1)
+    return (F.silu(y) if silu else y).to(x.dtype)
+  assert x.is_contiguous()
+  y = torch.empty_like(x)
+  g = gamma.reshape(-1).float().contiguous()
+  b = beta.reshape(-1).float().contiguous() if beta is not None else None
+  rc = _lib.lib().mdb_rms_act_cl(_lib.ptr(x), C, _lib.ptr(y), C, _lib.ptr(g), _lib.ptr(b), x.numel() // C, C, float(eps),
+                                 int(silu), _lib.stream())
+  _lib.check(rc, "mdb_rms_act_cl")
+  return y
+
+
+# ---------------------------------------------------------------------------------------------
+# References (fp32, PyTorch) with the same channels-last signatures: the oracle of the tests and the CPU path.
+# ---------------------------------------------------------------------------------------------
+def ref_conv3d_causal(x, weight, bias=None, hist=None, residual=None, silu=False):
+  xf = x.float().permute(0, 4, 1, 2, 3)
+  kt, kh, kw = weight.shape[2:]
+  if hist is not None and kt > 1:
+    xf = torch.cat([hist.float().permute(0, 4, 1, 2, 3)[:, :, -(kt - 1):], xf], dim=2)
+    xf = F.pad(xf, (kw // 2, kw // 2, kh // 2, kh // 2, 0, 0))
+  else:
+    xf = F.pad(xf, (kw // 2, kw // 2, kh // 2, kh // 2, kt - 1, 0))
+  y = F.conv3d(xf, weight.float(), None if bias is None else bias.float())
+  if silu:
+    y = F.silu(y)
+  y = y.permute(0, 2, 3, 4, 1)
+  return y + residual.float() if residual is not None else y
+
+
+def ref_conv2d(x, weight, bias=None, stride=1, pad_top_left=None, residual=None, silu=False):
+  kh = weight.shape[2]
+  p = kh // 2 if pad_top_left is None else pad_top_left
+  xf = x.float().permute(0, 3, 1, 2)
+  H, W = xf.shape[2:]
+  Ho, Wo = (H, W) if stride == 1 else (H // 2, W // 2)
+  far_h = (Ho - 1) * stride + kh - H - p
+  far_w = (Wo - 1) * stride + kh - W - p
+  xf = F.pad(xf, (p, max(far_w, 0), p, max(far_h, 0)))
+  y = F.conv2d(xf, weight.float(), None if bias is None else bias.float(), stride=stride)[:, :, :Ho, :Wo]
+  if silu:
+    y = F.silu(y)
+  y = y.permute(0, 2, 3, 1)
+  return y + residual.float() if residual is not None else y
+
+
+def ref_upsample2x_conv2d(x, weight, bias=None):
+  xf = F.interpolate(x.float().permute(0, 3, 1, 2), scale_factor=2.0, mode="nearest")
+  return F.conv2d(xf, weight.float(), None if bias is None else bias.float(), padding=1).permute(0, 2, 3, 1)

@@ -1,0 +1,133 @@
+"""Implicit-GEMM convolutions (csrc/conv_igemm.cu) against fp32 PyTorch convolutions of the same bf16 inputs: ragged
+sizes, channel counts that are not multiples of 64, the 2-frame history of the causal conv3d, stride 2 with either
+padding convention, the fused nearest-2x + conv, input gradients, and the channels-last RMS norm + SiLU."""
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _close(got, want, tol=2e-2):
+  got, want = got.float(), want.float()
+  err = (got - want).abs().max().item()
+  scale = want.abs().max().item() + 1e-6
+  assert err <= tol * scale, f"max err {err:.4g} vs scale {scale:.4g}"
+  rel = ((got - want).norm() / (want.norm() + 1e-12)).item()
+  assert rel < 1e-2, f"relative error {rel:.4g}"
+
+
+def _rand(shape, seed, scale=1.0):
+  g = torch.Generator(device="cuda").manual_seed(seed)
+  return (torch.randn(shape, device="cuda", generator=g) * scale).to(torch.bfloat16)
+
+
+@pytest.mark.parametrize("B,T,H,W,Ci,Co", [(1, 2, 8, 16, 16, 16), (1, 3, 9, 20, 96, 96), (2, 1, 12, 10, 192, 96),
+                                          (1, 2, 6, 40, 384, 192), (1, 4, 5, 7, 16, 384), (1, 2, 16, 16, 96, 3)])
+@pytest.mark.parametrize("with_hist", [False, True])
+def test_conv3d_causal_matches_fp32(B, T, H, W, Ci, Co, with_hist):
+  from maxdiffusion_b200.ops import conv as OC
+
+  x = _rand((B, T, H, W, Ci), 1)
+  w = _rand((Co, Ci, 3, 3, 3), 2, scale=(27 * Ci) ** -0.5)
+  b = _rand((Co,), 3)
+  hist = _rand((B, 2, H, W, Ci), 4) if with_hist else None
+  res = _rand((B, T, H, W, (Co + 7) // 8 * 8), 5) if Co % 8 == 0 else None
+  pk = OC.pack_conv3d(w, b)
+  got = OC.conv3d_causal(x, pk, hist=hist, residual=res)
+  want = OC.ref_conv3d_causal(x, w, b, hist=hist, residual=res)
+  assert got.shape == want.shape
+  _close(got, want)
+
+
+def test_time_conv_3x1x1_and_view_inputs():
+  from maxdiffusion_b200.ops import conv as OC
+
+  full = _rand((1, 5, 6, 8, 96), 1)
+  x = full[:, 1:]                      # a view along time: strides of the parent tensor
+  w = _rand((192, 96, 3, 1, 1), 2, scale=0.06)
+  b = _rand((192,), 3)
+  pk = OC.pack_conv3d(w, b)
+  hist = full[:, :1].repeat(1, 2, 1, 1, 1)
+  _close(OC.conv3d_causal(x, pk, hist=hist), OC.ref_conv3d_causal(x, w, b, hist=hist))
+  _close(OC.conv3d_causal(x, pk), OC.ref_conv3d_causal(x, w, b))
+
+
+@pytest.mark.parametrize("B,H,W,Ci,Co,k", [(2, 8, 8, 32, 64, 3), (1, 33, 21, 96, 96, 3), (3, 16, 16, 320, 320, 3),
+                                          (1, 12, 40, 128, 640, 3), (2, 10, 10, 64, 32, 1), (1, 64, 64, 16, 8, 3)])
+def test_conv2d_stride1(B, H, W, Ci, Co, k):
+  from maxdiffusion_b200.ops import conv as OC
+
+  x = _rand((B, H, W, Ci), 1)
+  w = _rand((Co, Ci, k, k), 2, scale=(k * k * Ci) ** -0.5)
+  b = _rand((Co,), 3)
+  res = _rand((B, H, W, Co), 4)
+  pk = OC.pack_conv2d(w, b)
+  _close(OC.conv2d(x, pk, residual=res), OC.ref_conv2d(x, w, b, residual=res))
+  _close(OC.conv2d(x, pk, silu=True), OC.ref_conv2d(x, w, b, silu=True))
+
+
+@pytest.mark.parametrize("pad", [0, 1])
+@pytest.mark.parametrize("B,H,W,Ci,Co", [(1, 8, 8, 32, 32), (2, 18, 30, 96, 96), (1, 32, 32, 320, 320), (1, 6, 10, 192, 64)])
+def test_conv2d_stride2_both_padding_conventions(B, H, W, Ci, Co, pad):
+  from maxdiffusion_b200.ops import conv as OC
+
+  x = _rand((B, H, W, Ci), 1)
+  w = _rand((Co, Ci, 3, 3), 2, scale=(9 * Ci) ** -0.5)
+  b = _rand((Co,), 3)
+  pk = OC.pack_conv2d(w, b, stride=2, pad_top_left=pad)
+  got = OC.conv2d(x, pk)
+  want = OC.ref_conv2d(x, w, b, stride=2, pad_top_left=pad)
+  assert got.shape == (B, H // 2, W // 2, Co)
+  _close(got, want)
+
+
+@pytest.mark.parametrize("B,H,W,Ci,Co", [(1, 4, 4, 32, 16), (2, 9, 15, 96, 48), (1, 20, 12, 384, 192)])
+def test_upsample_conv_fused_matches_upsample_then_conv(B, H, W, Ci, Co):
+  from maxdiffusion_b200.ops import conv as OC
+
+  x = _rand((B, H, W, Ci), 1)
+  w = _rand((Co, Ci, 3, 3), 2, scale=(9 * Ci) ** -0.5)
+  b = _rand((Co,), 3)
+  got = OC.upsample2x_conv2d(x, OC.pack_upsample_conv2d(w, b))
+  want = OC.ref_upsample2x_conv2d(x, w, b)
+  assert got.shape == (B, 2 * H, 2 * W, Co)
+  _close(got, want)
+
+
+@pytest.mark.parametrize("stride,pad", [(1, 1), (2, 1), (2, 0)])
+def test_conv2d_dgrad_matches_autograd(stride, pad):
+  from maxdiffusion_b200.ops import conv as OC
+
+  B, H, W, Ci, Co = 2, 12, 20, 64, 96
+  x = _rand((B, H, W, Ci), 1).float().requires_grad_(True)
+  w = _rand((Co, Ci, 3, 3), 2, scale=(9 * Ci) ** -0.5)
+  y = OC.ref_conv2d(x, w, None, stride=stride, pad_top_left=pad)
+  dy = _rand(tuple(y.shape), 3)
+  (y * dy.float()).sum().backward()
+  got = OC.conv2d_dgrad(dy, OC.pack_conv2d_dgrad(w, stride=stride, pad_top_left=pad))
+  assert got.shape == x.shape
+  _close(got, x.grad)
+
+
+@pytest.mark.parametrize("C", [96, 192, 384, 16, 1024])
+@pytest.mark.parametrize("silu", [False, True])
+def test_rms_act_channels_last(C, silu):
+  from maxdiffusion_b200.ops import conv as OC
+
+  x = _rand((3, 5, 7, C), 1, scale=3.0)
+  gamma = torch.rand(C, device="cuda") + 0.5
+  beta = torch.randn(C, device="cuda") * 0.1
+  got = OC.rms_act(x, gamma, beta, silu=silu)
+  want = OC.rms_act(x.cpu(), gamma.cpu(), beta.cpu(), silu=silu).cuda()
+  _close(got, want)
+
+
+def test_conv_results_are_bitwise_reproducible():
+  from maxdiffusion_b200.ops import conv as OC
+
+  x = _rand((1, 3, 20, 28, 96), 1)
+  w = _rand((96, 96, 3, 3, 3), 2, scale=0.02)
+  pk = OC.pack_conv3d(w, None)
+  a = OC.conv3d_causal(x, pk)
+  b = OC.conv3d_causal(x, pk)
+  assert torch.equal(a, b)
