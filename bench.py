@@ -13,6 +13,16 @@ Two timed regions of K steps each, both after W warm-up steps:
   * `value`: CUDA events around K steps with the batch already on the device (max over ranks);
   * `e2e`: the public `WanTrainer.train_step(host_batch)` path — pinned host batch -> device copy every step and a
     device -> host read of the loss every step — timed by the host clock between barriers + synchronize.
+
+Other arms and workloads:
+  --impl reference   the unmodified reference (prints its `unavailable` line: JAX is not installed here);
+  --impl library     a yardstick, NOT the reference: the same model, trainer and sharding with every kernel of this
+                     repository switched off (`F.linear` = cuBLAS, PyTorch SDPA, eager norms, NCCL all-gather /
+                     reduce-scatter, eager AdamW), so that a same-box end-to-end ratio exists;
+  --workload wan_infer | flux_infer | sdxl_train   the other metrics of the baseline (Wan 720p seconds per denoising
+                     step, Flux-dev images per second, SDXL UNet training step), see `utils/inference_bench.py`.
+  --keep-blocks K    fixes the remat policy (K blocks keep their activations) so that runs at different GPU counts do
+                     the same work; the default keeps as many blocks as memory allows.
 """
 from __future__ import annotations
 
@@ -72,6 +82,20 @@ class ClockSampler:
             "reasons": sorted(self.reasons), "samples": len(self.samples)}
 
 
+def wan_step_flops(cfg, tokens: int, text_len: int, recomputed_blocks: int) -> dict:
+  """FLOPs of one training step of one sample. `algorithmic`: forward + backward of every product (linear layers
+  3 x forward; attention forward + 2.5 x forward for its backward, which recomputes S). `executed` adds what
+  rematerialisation runs again: the linear layers and the cross-attention of the recomputed blocks (the self-attention
+  output is saved, not recomputed)."""
+  d, f, L = cfg.dim, cfg.ffn_dim, cfg.num_layers
+  lin = 2 * tokens * (4 * d * d + 2 * d * d + 2 * d * f) + 2 * text_len * 2 * d * d  # self qkvo, cross q/o, ffn, cross k/v
+  self_attn = 4 * tokens * tokens * d
+  cross_attn = 4 * tokens * text_len * d
+  algorithmic = L * (3 * lin + 3.5 * (self_attn + cross_attn))
+  executed = algorithmic + recomputed_blocks * (lin + cross_attn)
+  return {"algorithmic": float(algorithmic), "executed": float(executed)}
+
+
 def kept_block_bytes(cfg, tokens: int, ranks: int = 1) -> int:
   """Activation bytes a Wan block holds for its backward when it is not rematerialised (bf16): the residual stream
   and its three modulated norms, q / k / v before and after RMSNorm + RoPE, the attention output and its projection,
@@ -83,10 +107,42 @@ def kept_block_bytes(cfg, tokens: int, ranks: int = 1) -> int:
   return int(1.15 * per_token * tokens)
 
 
+def other_workload(args) -> int:
+  """The baseline's other metrics (`utils/inference_bench.py`), printed with the same JSON contract."""
+  import torch
+  import torch.distributed as dist
+
+  here = os.path.dirname(os.path.abspath(__file__))
+  sys.path.insert(0, here)
+  from maxdiffusion_b200.parallel.mesh import init_distributed
+  from maxdiffusion_b200.utils import inference_bench as IB
+
+  if args.impl == "library":
+    from maxdiffusion_b200.ops import functional as OF
+
+    OF.set_library_mode(True)
+  rank, world, local_rank = init_distributed()
+  model = {"wan_infer": "wan", "flux_infer": "flux", "sdxl_train": "sdxl"}[args.workload]
+  if args.workload == "wan_infer" and (args.height, args.width) == (480, 832):
+    args.height, args.width = 720, 1280  # the inference metric is quoted at 720p; --height / --width override it
+  args.preset = None if args.preset == "wan2.1-t2v-14b" and model != "wan" else args.preset
+  args.attention = None if args.attention == "tokamax_ring" else args.attention
+  sampler = ClockSampler(local_rank)
+  sampler.start()
+  out = IB.run_workload(model, args)
+  out["clocks"] = sampler.stop()
+  out["impl"] = args.impl
+  if rank == 0:
+    print(json.dumps(out))
+  if world > 1:
+    dist.destroy_process_group()
+  return 0
+
+
 def main() -> int:
   ap = argparse.ArgumentParser()
   ap.add_argument("--gpus", type=int, default=1)
-  ap.add_argument("--steps", type=int, default=3)
+  ap.add_argument("--steps", type=int, default=None, help="timed steps (default 3; flux_infer: 28 Euler steps, wan_infer: 4)")
   ap.add_argument("--warmup", type=int, default=3)
   ap.add_argument("--impl", default="ours")
   ap.add_argument("--remat", default="SAVE_ATTENTION", help="FULL | SAVE_ATTENTION")
@@ -97,11 +153,23 @@ def main() -> int:
   ap.add_argument("--width", type=int, default=832)
   ap.add_argument("--frames", type=int, default=81)
   ap.add_argument("--attention", default="tokamax_ring")
+  ap.add_argument("--workload", default="wan_train", choices=["wan_train", "wan_infer", "flux_infer", "sdxl_train"])
+  ap.add_argument("--resolution", type=int, default=1024)
+  ap.add_argument("--batch", type=int, default=None)
+  ap.add_argument("--ulysses", type=int, default=-1)
+  ap.add_argument("--decode", action="store_true", help="wan_infer: also time the VAE decode")
   args = ap.parse_args()
   if args.impl == "reference":
     return reference_arm()
+  if args.impl not in ("ours", "library"):
+    print(f"unknown --impl {args.impl}", file=sys.stderr)
+    return 2
   if args.warmup < 3:
     args.warmup = 3
+  if args.workload != "wan_train":
+    return other_workload(args)
+  if args.steps is None:
+    args.steps = 3
 
   import torch
   import torch.distributed as dist
@@ -113,6 +181,10 @@ def main() -> int:
   from maxdiffusion_b200.parallel.mesh import create_device_mesh, init_distributed
   from maxdiffusion_b200.trainers.wan_trainer import WanTrainer
 
+  if args.impl == "library":
+    from maxdiffusion_b200.ops import functional as OF
+
+    OF.set_library_mode(True)
   rank, world, local_rank = init_distributed()
   if world != args.gpus:
     if rank == 0:
@@ -124,7 +196,8 @@ def main() -> int:
        f"per_device_batch_size={1.0 / n}", f"attention={args.attention}", f"remat_policy={args.remat}",
        f"remat_keep_blocks={max(0, args.keep_blocks)}",
        f"wan_preset={args.preset}", "warmup_steps_fraction=0.0", "max_train_steps=1000000", "log_config=false",
-       "write_metrics=false", "flow_shift=5.0"])
+       "write_metrics=false", "flow_shift=5.0",
+       f"peer_memory_transport={'false' if args.impl == 'library' else 'true'}"])
   mesh = create_device_mesh(config)
   trainer = WanTrainer(config, mesh=mesh)
   data = trainer.load_dataset()
@@ -144,7 +217,7 @@ def main() -> int:
     torch.cuda.synchronize()
     free, total = torch.cuda.mem_get_info()
     peak = torch.cuda.max_memory_reserved()
-    per_block = kept_block_bytes(trainer.model.cfg, -(-seq_len // n), n)
+    per_block = kept_block_bytes(trainer.model.cfg, -(-seq_len // n), n) * (2 if args.impl == "library" else 1)
     room = total - peak - int(0.08 * total)
     keep_t = torch.tensor([max(0, min(len(trainer.model.blocks), room // per_block))], device="cuda")
     if world > 1:
@@ -156,7 +229,8 @@ def main() -> int:
   for _ in range(args.warmup):
     m = trainer.train_step(next(data))
     float(m["learning/loss"])
-  _lib.raise_on_device_status()
+  if args.impl == "ours":
+    _lib.raise_on_device_status()
 
   # ---- region 1: device-timed, inputs resident on the device
   dev_batches = [trainer.to_device(next(data)) for _ in range(args.steps)]
@@ -177,7 +251,8 @@ def main() -> int:
     dist.all_reduce(ms, op=dist.ReduceOp.MAX)
   ms_per_step = ms.item() / args.steps
   last_loss = float(m["learning/loss"])
-  _lib.raise_on_device_status()
+  if args.impl == "ours":
+    _lib.raise_on_device_status()
 
   # ---- region 2: end to end through the public API (H2D of the batch and D2H of the loss every step)
   host_batches = [next(data) for _ in range(args.steps)]
@@ -194,6 +269,8 @@ def main() -> int:
   e2e_tokens_per_s = seq_len * args.steps / e2e_s.item()
 
   value = seq_len * 1000.0 / ms_per_step
+  n_blocks = len(trainer.model.blocks)
+  flops = wan_step_flops(trainer.model.cfg, seq_len, 512, 0 if args.remat == "NONE" else n_blocks - keep)
   official = args.preset == "wan2.1-t2v-14b" and (args.height, args.width, args.frames) == (480, 832, 81)
   if rank == 0:
     print(json.dumps({
@@ -213,7 +290,10 @@ def main() -> int:
         "clocks": clocks,
         "e2e": {"value": e2e_tokens_per_s, "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 4,
                 "seconds_per_step": e2e_s.item() / args.steps},
-        "gpu_launches": launches, "loss": last_loss, "impl": "ours"}))
+        "flops_per_step": flops["algorithmic"], "executed_flops_per_step": flops["executed"],
+        "tflops_per_gpu": flops["algorithmic"] / (ms_per_step * 1e-3) / n / 1e12,
+        "executed_tflops_per_gpu": flops["executed"] / (ms_per_step * 1e-3) / n / 1e12,
+        "gpu_launches": launches, "loss": last_loss, "impl": args.impl}))
   if world > 1:
     dist.destroy_process_group()
   return 0

@@ -8,9 +8,10 @@ time conv, :245-389), `WanResidualBlock` (:392-484), single-head spatial `WanAtt
 encoder / decoder (:668-959), and the time-chunked encode / decode loops that carry the caches
 (:1134-1327). Parameter names follow the diffusers checkpoint so that its safetensors load directly.
 
-Convolutions currently run through `torch.nn.functional.conv3d / conv2d` (cuDNN); everything around them
-(norm, activation, cache handling, chunk loop) is plain PyTorch. Width-sharded decoding across ranks splits the
-latent along W with a halo (`decode(..., spatial_group=...)`).
+Two execution paths share the modules and parameters of this file. CUDA bf16 latents are decoded channels-last on
+the implicit-GEMM convolution kernels of this repository (`vae_channels_last.ChannelsLastDecoder`). Everything else
+(CPU, fp32, the encoder) runs the plain PyTorch forward below (`F.conv3d` / `F.conv2d`), which is also the oracle the
+kernel path is tested against.
 """
 from __future__ import annotations
 
@@ -372,6 +373,8 @@ class AutoencoderKLWan(nn.Module):
   @torch.no_grad()
   def decode(self, z, chunk: int = 1):
     """z: [B,16,T',H',W'] (de-normalised latents) -> video [B,3,1+4(T'-1),8H',8W'] clamped to [-1,1]."""
+    if z.is_cuda and z.dtype == torch.bfloat16 and self.cfg.z_dim % 16 == 0:
+      return self.channels_last_decoder().decode(z, chunk)
     self._reset()
     cache = FeatureCache()
     x = self.post_quant_conv(z)
@@ -386,6 +389,14 @@ class AutoencoderKLWan(nn.Module):
       start += n
       first = False
     return torch.cat(outs, dim=2).clamp(-1.0, 1.0)
+
+  def channels_last_decoder(self):
+    """The kernel path of `decode` (created on first use; it re-packs a weight when the parameter changes)."""
+    if getattr(self, "_cl_decoder", None) is None:
+      from .vae_channels_last import ChannelsLastDecoder
+
+      object.__setattr__(self, "_cl_decoder", ChannelsLastDecoder(self))
+    return self._cl_decoder
 
   def decode_full(self, z):
     """Whole-clip decode without chunking (the oracle the chunked path is tested against)."""

@@ -1,0 +1,188 @@
+"""Channels-last execution of the Wan 2.1 VAE decoder on the implicit-GEMM convolution kernels.
+
+`AutoencoderKLWan.decode` hands CUDA bf16 latents to `ChannelsLastDecoder`, which walks the same modules (and therefore
+the same parameters) as the NCDHW PyTorch path but keeps every activation as `[B, T, H, W, C]`:
+
+  * 3x3x3 causal convolutions and the (3,1,1) time convolution run on `ops.conv.conv3d_causal`; the 2-frame feature
+    cache of a convolution is the history tensor the kernel reads its negative-time taps from, so nothing is
+    concatenated in front of a chunk (reference: src/maxdiffusion/models/wan/autoencoder_kl_wan.py:70-147);
+  * `RMS_norm -> SiLU` is one row kernel; bias and the residual add ride in the convolution's epilogue (:452-484);
+  * nearest-2x + 3x3 conv is the fused low-resolution form (`ops.conv.upsample2x_conv2d`), and the time up-sampling
+    writes its two channel halves straight into the even / odd frames of the output (:245-389) -- no interleave pass;
+  * 1x1 convolutions are GEMMs on the tcgen05 GEMM kernel.
+
+The mid-block attention (one head of 384 channels over the H*W positions of a frame, :487-546) runs on PyTorch's SDPA:
+the flash kernels of this repository are built for head sizes 64 and 128.
+"""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+import torch.nn.functional as F
+
+from ...ops import conv as OC
+from ...ops import kernels as K
+
+
+class _Hist:
+  """The last two input frames of every cached convolution, by call order within a pass (channels-last)."""
+
+  def __init__(self):
+    self.slots: list = []
+    self.cursor = 0
+
+  def begin_pass(self):
+    self.cursor = 0
+
+  def next(self) -> int:
+    i = self.cursor
+    self.cursor += 1
+    if i >= len(self.slots):
+      self.slots.append(None)
+    return i
+
+
+def _roll_history(hist: Optional[torch.Tensor], x: torch.Tensor) -> torch.Tensor:
+  """The two frames that precede the NEXT chunk: the tail of [hist | x] (zeros where the clip has not started)."""
+  if x.shape[1] >= 2:
+    return x[:, -2:]
+  prev = hist[:, 1:] if hist is not None else torch.zeros_like(x)
+  return torch.cat([prev, x], dim=1)
+
+
+class ChannelsLastDecoder:
+
+  def __init__(self, vae):
+    self.vae = vae
+    self._packed: dict = {}
+
+  # ---- packed weights (re-packed when a parameter changes) -----------------------------------
+  def _pack(self, key, params, make):
+    ver = tuple((p.data_ptr(), p._version) for p in params if p is not None)
+    hit = self._packed.get(key)
+    if hit is None or hit[0] != ver:
+      hit = (ver, make())
+      self._packed[key] = hit
+    return hit[1]
+
+  def _conv3_pack(self, m):
+    return self._pack(id(m), (m.weight, m.bias), lambda: OC.pack_conv3d(m.weight.detach(), None if m.bias is None else m.bias.detach()))
+
+  # ---- layers ----------------------------------------------------------------------------------
+  def conv3(self, m, x, hist: Optional[_Hist], residual=None, out=None):
+    """A `WanCausalConv3d`: x [B, T, H, W, Ci] -> [B, T, H, W, Co]."""
+    kt = m.weight.shape[2]
+    if tuple(m.weight.shape[2:]) == (1, 1, 1):
+      return self.pointwise(m.weight, m.bias, x, residual)
+    past = None
+    if hist is not None and kt > 1:
+      slot = hist.next()
+      past = hist.slots[slot]
+      hist.slots[slot] = _roll_history(past, x)
+    pk = self._conv3_pack(m)
+    return OC.conv3d_causal(OC.pad_channels(x, pk.c_in), pk, hist=past, residual=residual)
+
+  def pointwise(self, weight, bias, x, residual=None):
+    """1x1(x1) convolution = GEMM over the pixel rows."""
+    co, ci = weight.shape[:2]
+    w2 = self._pack(("pw", id(weight)), (weight, bias),
+                    lambda: (weight.detach().reshape(co, ci).to(torch.bfloat16).contiguous(),
+                             None if bias is None else bias.detach().to(torch.bfloat16).contiguous()))
+    rows = x.reshape(-1, ci)
+    if not OC.use_kernel(x):
+      y = F.linear(rows, weight.reshape(co, ci).to(x.dtype), None if bias is None else bias.to(x.dtype))
+      if residual is not None:
+        y = y + residual.reshape(-1, co)
+    elif ci % 64 or co % 8:
+      y = F.linear(rows, w2[0], w2[1])
+      if residual is not None:
+        y = y + residual.reshape(-1, co)
+    elif residual is not None:
+      y = K.gemm(rows, w2[0], bias=w2[1], epi="add_res", residual=residual.reshape(-1, co))
+    else:
+      y = K.gemm(rows, w2[0], bias=w2[1])
+    return y.reshape(*x.shape[:-1], co)
+
+  def norm(self, m, x, silu: bool):
+    return OC.rms_act(x.contiguous(), m.gamma, m.bias, silu=silu)
+
+  def res_block(self, blk, x, hist):
+    h = self.conv3(blk.conv_shortcut, x, None) if blk.conv_shortcut is not None else x
+    y = self.conv3(blk.conv1, self.norm(blk.norm1, x, True), hist)
+    return self.conv3(blk.conv2, self.norm(blk.norm2, y, True), hist, residual=h.contiguous())
+
+  def attention(self, blk, x):
+    B, T, H, W, C = x.shape
+    y = self.norm(blk.norm, x, False)
+    qkv = self.pointwise(blk.to_qkv.weight, blk.to_qkv.bias, y).reshape(B * T, H * W, 3, C)
+    q, k, v = (qkv[:, :, i].unsqueeze(1) for i in range(3))
+    o = F.scaled_dot_product_attention(q, k, v).squeeze(1).reshape(B, T, H, W, C)
+    return self.pointwise(blk.proj.weight, blk.proj.bias, o, residual=x.contiguous())
+
+  def resample(self, rs, x, hist, first_chunk: bool):
+    B, T, H, W, C = x.shape
+    if rs.mode == "upsample3d":
+      if hist is None:
+        if T > 1:  # whole clip: the first frame stays single, every later frame is doubled
+          x = torch.cat([x[:, :1], self._time_upsample(rs, x[:, 1:], None)], dim=1)
+      elif first_chunk:
+        hist.next()  # the first frame skips the time convolution but keeps the slot order of later chunks
+      else:
+        x = self._time_upsample(rs, x, hist)
+    T2 = x.shape[1]
+    conv = rs.resample[1]
+    pk = self._pack(("up", id(conv)), (conv.weight, conv.bias), lambda: OC.pack_upsample_conv2d(conv.weight.detach(), conv.bias.detach()))
+    y = OC.upsample2x_conv2d(x.reshape(B * T2, H, W, C), pk)
+    return y.reshape(B, T2, 2 * H, 2 * W, y.shape[-1])
+
+  def _time_upsample(self, rs, x, hist: Optional[_Hist]):
+    """(3,1,1) causal conv C -> 2C whose channel halves become the even / odd output frames."""
+    m = rs.time_conv
+    B, T, H, W, C = x.shape
+    halves = self._pack(("tc", id(m)), (m.weight, m.bias),
+                        lambda: [OC.pack_conv3d(m.weight.detach()[j * C:(j + 1) * C], m.bias.detach()[j * C:(j + 1) * C]) for j in range(2)])
+    past = None
+    if hist is not None:
+      slot = hist.next()
+      past = hist.slots[slot]
+      hist.slots[slot] = _roll_history(past, x)
+    out = torch.empty((B, 2 * T, H, W, C), dtype=x.dtype, device=x.device)
+    for j in range(2):
+      OC.conv3d_causal(x, halves[j], hist=past, out=out[:, j::2])
+    return out
+
+  # ---- decoder ---------------------------------------------------------------------------------
+  def decoder(self, x, hist: Optional[_Hist], first_chunk: bool):
+    d = self.vae.decoder
+    x = self.conv3(d.conv_in, x, hist)
+    mid = d.mid_block
+    x = self.res_block(mid.resnets[0], x, hist)
+    x = self.attention(mid.attentions[0], x)
+    x = self.res_block(mid.resnets[1], x, hist)
+    for up in d.up_blocks:
+      for r in up.resnets:
+        x = self.res_block(r, x, hist)
+      if up.upsamplers is not None:
+        x = self.resample(up.upsamplers[0], x, hist, first_chunk)
+    return self.conv3(d.conv_out, self.norm(d.norm_out, x, True), hist)
+
+  @torch.no_grad()
+  def decode(self, z: torch.Tensor, chunk: int = 1, whole_clip: bool = False) -> torch.Tensor:
+    """z [B, 16, T', H', W'] (de-normalised latents, bf16, CUDA) -> video [B, 3, 1 + 4 (T' - 1), 8 H', 8 W'] in [-1, 1]."""
+    vae = self.vae
+    x = z.permute(0, 2, 3, 4, 1).contiguous()  # channels-last
+    x = self.pointwise(vae.post_quant_conv.weight, vae.post_quant_conv.bias, x)
+    if whole_clip:
+      out = self.decoder(x, None, True)
+    else:
+      hist = _Hist()
+      outs, start, first, t = [], 0, True, x.shape[1]
+      while start < t:
+        n = 1 if first else min(chunk, t - start)
+        hist.begin_pass()
+        outs.append(self.decoder(x[:, start:start + n], hist, first))
+        start += n
+        first = False
+      out = torch.cat(outs, dim=1)
+    return out.clamp_(-1.0, 1.0).permute(0, 4, 1, 2, 3)

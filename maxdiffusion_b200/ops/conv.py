@@ -61,6 +61,7 @@ class PackedConv:
   n_out: int                      # true output channels
   n_pad: int                      # multiple of 8
   kind: str
+  src: tuple = ()                 # (weight, bias, stride, pad_top_left) as given: what the PyTorch reference path runs
 
   def tap_arrays(self):
     flat, begin, k = [], [0], 0
@@ -89,7 +90,9 @@ def pack_conv3d(weight: torch.Tensor, bias=None) -> PackedConv:
   """weight [Co, Ci, kt, kh, kw] (causal in time, 'same' in space)."""
   co, ci, kt, kh, kw = weight.shape
   taps = [[(0, b - kw // 2, a - kh // 2, t - (kt - 1), 0) for t in range(kt) for a in range(kh) for b in range(kw)]]
-  return _pack(weight.permute(0, 2, 3, 4, 1).reshape(co, kt * kh * kw, ci), bias, taps, "conv3d")
+  pk = _pack(weight.permute(0, 2, 3, 4, 1).reshape(co, kt * kh * kw, ci), bias, taps, "conv3d")
+  pk.src = (weight, bias, 1, None)
+  return pk
 
 
 def pack_conv2d(weight: torch.Tensor, bias=None, stride: int = 1, pad_top_left: Optional[int] = None) -> PackedConv:
@@ -100,7 +103,9 @@ def pack_conv2d(weight: torch.Tensor, bias=None, stride: int = 1, pad_top_left: 
   w = weight.permute(0, 2, 3, 1).reshape(co, kh * kw, ci)
   if stride == 1:
     taps = [[(0, b - p, a - p, 0, 0) for a in range(kh) for b in range(kw)]]
-    return _pack(w, bias, taps, "conv2d")
+    pk = _pack(w, bias, taps, "conv2d")
+    pk.src = (weight, bias, 1, p)
+    return pk
   assert stride == 2
   # activation seen as [B, H/2, 2, W/2, 2C]: input row 2*oh + a - p = 2*(oh + dh) + ph
   c16 = _round_up(ci, 16)
@@ -110,7 +115,9 @@ def pack_conv2d(weight: torch.Tensor, bias=None, stride: int = 1, pad_top_left: 
     for b in range(kw):
       dw, pw = divmod(b - p, 2)
       taps[0].append((pw * c16, dw, ph, dh, 0))
-  return _pack(w, bias, taps, "conv2d_s2")
+  pk = _pack(w, bias, taps, "conv2d_s2")
+  pk.src = (weight, bias, 2, p)
+  return pk
 
 
 def _upsample_parity_taps():
@@ -135,7 +142,9 @@ def pack_upsample_conv2d(weight: torch.Tensor, bias=None) -> PackedConv:
           mats.append(w32[:, :, rows][:, :, :, cols].sum(dim=(2, 3)))  # [Co, Ci]
           cls.append((0, dq, dp, 0, 0))
       taps.append(cls)
-  return _pack(torch.stack(mats, dim=1), bias, taps, "upsample_conv2d")
+  pk = _pack(torch.stack(mats, dim=1), bias, taps, "upsample_conv2d")
+  pk.src = (weight, bias, 1, 1)
+  return pk
 
 
 def pack_conv2d_dgrad(weight: torch.Tensor, stride: int = 1, pad_top_left: Optional[int] = None) -> PackedConv:
@@ -208,11 +217,26 @@ def pad_channels(x: torch.Tensor, c: int) -> torch.Tensor:
 
 
 def conv3d_causal(x: torch.Tensor, pk: PackedConv, hist: Optional[torch.Tensor] = None,
-                  residual: Optional[torch.Tensor] = None, silu: bool = False) -> torch.Tensor:
-  """x [B, T, H, W, C] -> [B, T, H, W, N]. `hist` [B, 2, H, W, C]: the two frames before x (None: zeros)."""
+                  residual: Optional[torch.Tensor] = None, silu: bool = False,
+                  out: Optional[torch.Tensor] = None) -> torch.Tensor:
+  """x [B, T, H, W, C] -> [B, T, H, W, N]. `hist` [B, 2, H, W, C]: the two frames before x (None: zeros). `out` may be
+  a strided view (e.g. every second frame of a larger tensor) as long as its channels are dense."""
+  if not use_kernel(x):
+    w, b = pk.src[0], pk.src[1]
+    ci = w.shape[1]
+    y = ref_conv3d_causal(x[..., :ci], w, b, hist=None if hist is None else hist[..., :ci], residual=residual,
+                          silu=silu).to(x.dtype)
+    if out is not None:
+      out.copy_(y)
+      return out
+    return y
   _check_cl(x, pk.c_in)
   B, T, H, W, C = x.shape
-  out = torch.empty((B, T, H, W, pk.n_pad), dtype=x.dtype, device=x.device)
+  if out is None:
+    out = torch.empty((B, T, H, W, pk.n_pad), dtype=x.dtype, device=x.device)
+  else:
+    assert out.shape == (B, T, H, W, pk.n_pad) and out.stride(-1) == 1 and out.dtype == x.dtype
+    assert all(s % 8 == 0 for s in out.stride()[:-1]) and residual is None
   b1, b2, _ = _pick_box(W, H, 1, False)
   alt_dims = alt_strides = None
   if hist is not None:
@@ -224,12 +248,16 @@ def conv3d_causal(x: torch.Tensor, pk: PackedConv, hist: Optional[torch.Tensor] 
     assert residual.shape == out.shape and residual.is_contiguous()
   n = pk.n_pad
   _launch(x, hist, pk, [C, W, H, T, B], [x.stride(3), x.stride(2), x.stride(1), x.stride(0)], alt_dims, alt_strides,
-          [b1, b2, 1], [W, H, T, B], out, [n, W * n, H * W * n, T * H * W * n], [0], residual, silu, alt_dim=3, alt_shift=2)
+          [b1, b2, 1], [W, H, T, B], out, [out.stride(3), out.stride(2), out.stride(1), out.stride(0)], [0], residual, silu,
+          alt_dim=3, alt_shift=2)
   return out if pk.n_pad == pk.n_out else out[..., :pk.n_out]
 
 
 def conv2d(x: torch.Tensor, pk: PackedConv, residual: Optional[torch.Tensor] = None, silu: bool = False) -> torch.Tensor:
   """x [B, H, W, C] -> [B, Ho, Wo, N] (Ho = H for stride 1, H / 2 for stride 2)."""
+  if not use_kernel(x):
+    w, b, stride, p = pk.src
+    return ref_conv2d(x[..., :w.shape[1]], w, b, stride=stride, pad_top_left=p, residual=residual, silu=silu).to(x.dtype)
   _check_cl(x, pk.c_in)
   B, H, W, C = x.shape
   n = pk.n_pad
@@ -270,6 +298,8 @@ def _parity_conv(x, pk, silu=False):
 
 def upsample2x_conv2d(x: torch.Tensor, pk: PackedConv) -> torch.Tensor:
   assert pk.kind == "upsample_conv2d"
+  if not use_kernel(x):
+    return ref_upsample2x_conv2d(x[..., :pk.src[0].shape[1]], pk.src[0], pk.src[1]).to(x.dtype)
   return _parity_conv(x, pk)
 
 

@@ -24,8 +24,23 @@ from . import kernels as K
 from . import ref
 
 
+_LIBRARY_MODE = False
+
+
+def set_library_mode(on: bool) -> None:
+  """Yardstick switch: when on, no op of this module (and no optimizer step of `parallel.fsdp`) runs a kernel of this
+  repository; CUDA tensors take the PyTorch path instead (`F.linear` = cuBLAS, `scaled_dot_product_attention`, eager
+  norms and elementwise ops, `torch._foreach` AdamW). Used by `bench.py --impl library` only."""
+  global _LIBRARY_MODE
+  _LIBRARY_MODE = bool(on)
+
+
+def library_mode() -> bool:
+  return _LIBRARY_MODE
+
+
 def _fast(t: torch.Tensor) -> bool:
-  return t.is_cuda and t.dtype == torch.bfloat16
+  return t.is_cuda and t.dtype == torch.bfloat16 and not _LIBRARY_MODE
 
 
 # ---------------------------------------------------------------------------------------------
@@ -495,7 +510,7 @@ class _GroupNormFn(torch.autograd.Function):
 
 def group_norm(x, groups: int, gamma=None, beta=None, eps: float = 1e-6, act: bool = False):
   """GroupNorm over a channels-first tensor [N, C, *spatial] with optional fused SiLU."""
-  if x.is_cuda and x.dtype in (torch.bfloat16, torch.float32):
+  if x.is_cuda and x.dtype in (torch.bfloat16, torch.float32) and not _LIBRARY_MODE:
     x = x if x.is_contiguous() else x.contiguous()
     return _GroupNormFn.apply(x, gamma, beta, groups, eps, act)
   return ref.group_norm(x, groups, gamma, beta, eps, act)
@@ -505,7 +520,7 @@ def lincomb(xs, coefs, out_dtype=None):
   """sum_i coefs[(b,) i] * xs[i]; no gradient (sampling-loop updates)."""
   x0 = xs[0]
   per = x0.numel() // (len(coefs) if isinstance(coefs[0], (list, tuple)) else 1)
-  if x0.is_cuda and per % 8 == 0 and all(x.dtype in (torch.bfloat16, torch.float32) for x in xs):
+  if x0.is_cuda and per % 8 == 0 and all(x.dtype in (torch.bfloat16, torch.float32) for x in xs) and not _LIBRARY_MODE:
     return K.lincomb(list(xs), coefs, out_dtype=out_dtype)
   return ref.lincomb(xs, coefs, out_dtype)
 
@@ -528,7 +543,7 @@ def weighted_mse(pred, target, weights=None):
   """mean over all elements of w_b * (pred - target)^2; the gradient with respect to pred comes from the same pass."""
   B = pred.shape[0]
   if (pred.is_cuda and pred.dtype in (torch.bfloat16, torch.float32) and target.dtype in (torch.bfloat16, torch.float32)
-      and B <= 16 and (pred.numel() // B) % 8 == 0):
+      and B <= 16 and (pred.numel() // B) % 8 == 0 and not _LIBRARY_MODE):
     w = None if weights is None else [float(v) for v in (weights.tolist() if torch.is_tensor(weights) else weights)]
     return _MseFn.apply(pred, target.detach(), w)
   return ref.weighted_mse(pred, target, weights)

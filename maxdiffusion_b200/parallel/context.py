@@ -307,7 +307,7 @@ class ContextParallel:
 
   # ---- attention ---------------------------------------------------------------------------
   def _uses_flash(self, q) -> bool:
-    return q.is_cuda and q.dtype == torch.bfloat16 and q.shape[-1] in K.FLASH_HEAD_DIMS
+    return q.is_cuda and q.dtype == torch.bfloat16 and q.shape[-1] in K.FLASH_HEAD_DIMS and not OF.library_mode()
 
   def _full_attention(self, q, k, v, scale=None):
     """Attention of a rank that holds the whole key sequence of its heads."""

@@ -29,6 +29,12 @@ import torch.nn as nn
 from ..ops import kernels as K
 from ..ops import ref
 
+def _library_mode() -> bool:
+  from ..ops import functional as OF
+
+  return OF.library_mode()
+
+
 _ALIGN = 64  # elements; keeps every parameter view 128-byte aligned (TMA needs 16)
 
 
@@ -257,14 +263,14 @@ class FSDPEngine:
     o = self.opt
     kw = dict(lr=self.lr, b1=o.b1, b2=o.b2, eps=o.eps, wd=o.weight_decay, step=self.step_count, grad_scale=grad_scale,
               clip_value=o.clip_value)
-    if p.is_cuda:
+    if p.is_cuda and not _library_mode():
       K.adamw(p, g, m, v, seed=(self.seed * 1000003 + self.step_count) * 4099 + salt,
               stochastic=o.stochastic_rounding, **kw)
     else:
       ref.adamw_step(p, g, m, v, **kw)
 
   def _stats(self, g: torch.Tensor) -> None:
-    if g.is_cuda:
+    if g.is_cuda and not _library_mode():
       K.sumsq_maxabs(g, out=self.grad_stats, accumulate=True)
     else:
       s = ref.sumsq_maxabs(g)
@@ -395,7 +401,7 @@ class FSDPEngine:
       dist.all_reduce(sq, group=self.group)
       dist.all_reduce(mx, op=dist.ReduceOp.MAX, group=self.group)
       stats = torch.cat([sq, mx])
-    root_stats = K.sumsq_maxabs(root_grad) if root_grad.is_cuda else ref.sumsq_maxabs(root_grad)
+    root_stats = K.sumsq_maxabs(root_grad) if (root_grad.is_cuda and not _library_mode()) else ref.sumsq_maxabs(root_grad)
     total_sq = stats[0] + root_stats[0]
     max_abs = torch.maximum(stats[1], root_stats[1])
     grad_norm = total_sq.sqrt()

@@ -252,6 +252,10 @@ class WanPipeline:
 
     sync()
     t_loop = time.perf_counter()
+    ev = None
+    if self.device.type == "cuda":  # the loop is also timed on the device, by events on the launching stream
+      ev = (torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True))
+      ev[0].record()
     for i, t in enumerate(timesteps):
       model, g_scale, is_high = self._expert(t, boundary)
       if self.transformer_2 is None:
@@ -300,9 +304,11 @@ class WanPipeline:
       if self.pctx is not None:
         # kernels of this step waited (bounded) on other ranks: a wait that ran out must not feed the next step
         _lib.raise_on_device_status_if_loaded()
+    if ev is not None:
+      ev[1].record()
     sync()
     _lib.raise_on_device_status_if_loaded()
-    trace["denoise_total"] = time.perf_counter() - t_loop
+    trace["denoise_total"] = ev[0].elapsed_time(ev[1]) / 1e3 if ev is not None else time.perf_counter() - t_loop
     trace["denoise_per_step"] = trace["denoise_total"] / max(1, steps)
 
     if output_type == "latent" or self.vae is None:
@@ -316,7 +322,13 @@ class WanPipeline:
     return (video, trace) if return_trace else video
 
   def decode_latents(self, latents):
-    z = self.vae.denormalize_latents(latents.to(next(self.vae.parameters()).dtype))
+    z = self.vae.denormalize_latents(latents.float())
+    if z.is_cuda and bool(self.config.get("vae_kernel_decode", True)):
+      # bf16 latents select the channels-last decoder on this repository's convolution kernels (the weights are
+      # packed to bf16 whatever dtype the module keeps them in)
+      z = z.to(torch.bfloat16)
+    else:
+      z = z.to(next(self.vae.parameters()).dtype)
     return self.vae.decode(z, chunk=int(self.config.get("vae_decode_chunk", 1)))
 
 

@@ -132,3 +132,26 @@ def test_wan22_vae_chunked_matches_whole_clip_and_patchify_round_trip():
     assert z.shape == (1, 6, 3, 2, 2) and torch.allclose(z, z_full, atol=1e-5)
     out, out_full = vae.decode(z), vae.decode_full(z)
   assert out.shape == (1, 3, 9, 32, 32) and torch.allclose(out, out_full, atol=1e-5)
+
+
+def test_channels_last_decoder_orchestration_matches_the_ncdhw_path():
+  """The channels-last walk over the decoder (history tensors instead of concatenated caches, channel halves written
+  into even / odd frames, nearest-2x folded into the convolution call) against the plain NCDHW modules, both in fp32
+  on the CPU, chunked and whole-clip."""
+  torch.manual_seed(0)
+  vae = AutoencoderKLWan(WanVAEConfig(base_dim=8)).eval()
+  for p in vae.parameters():
+    torch.nn.init.normal_(p, std=0.2)
+  z = torch.randn(1, 16, 3, 4, 6)
+  from maxdiffusion_b200.models.wan.vae_channels_last import ChannelsLastDecoder
+
+  cl = ChannelsLastDecoder(vae)
+  with torch.no_grad():
+    want = vae.decode(z, chunk=1)
+    got = cl.decode(z, chunk=1)
+    assert got.shape == want.shape == (1, 3, 9, 32, 48)
+    assert (got - want).abs().max() < 1e-4 * (1 + want.abs().max())
+    got2 = cl.decode(z, chunk=2)
+    assert (got2 - want).abs().max() < 1e-4 * (1 + want.abs().max())
+    whole = cl.decode(z, whole_clip=True)
+    assert (whole - vae.decode_full(z)).abs().max() < 1e-4 * (1 + want.abs().max())
