@@ -225,6 +225,87 @@ def bench_rowwise(results):
   print(results[-1], flush=True)
 
 
+def bench_conv(results):
+  """Implicit-GEMM convolutions at the shapes of the Wan VAE decoder (720p: latent 90 x 160, four frames per chunk at
+  the top stage) and of the SDXL UNet (batch 8), each beside cuDNN on the same bf16 tensors in its preferred layout
+  (`channels_last_3d` / `channels_last`). FLOPs count the taps actually needed (27 or 9 per output)."""
+  import torch.nn.functional as F
+
+  from maxdiffusion_b200.ops import conv as OC
+
+  tf_peak, bw_peak, tag = peaks()
+  cases3d = [(1, 4, 720, 1280, 96, 96), (1, 4, 360, 640, 192, 192), (1, 2, 180, 320, 384, 384), (1, 1, 90, 160, 384, 384),
+             (1, 4, 720, 1280, 96, 3)]
+  for B, T, H, W, Ci, Co in cases3d:
+    x = torch.randn((B, T, H, W, Ci), device="cuda", dtype=torch.bfloat16)
+    hist = torch.randn((B, 2, H, W, Ci), device="cuda", dtype=torch.bfloat16)
+    w = torch.randn((Co, Ci, 3, 3, 3), device="cuda", dtype=torch.bfloat16) * (27 * Ci) ** -0.5
+    b = torch.randn((Co,), device="cuda", dtype=torch.bfloat16)
+    pk = OC.pack_conv3d(w, b)
+    med, best = time_ms(lambda: OC.conv3d_causal(x, pk, hist=hist), iters=5)
+    xn = torch.cat([hist, x], dim=1).permute(0, 4, 1, 2, 3).contiguous(memory_format=torch.channels_last_3d)
+    wn = w.contiguous(memory_format=torch.channels_last_3d)
+    lib, _ = time_ms(lambda: F.conv3d(F.pad(xn, (1, 1, 1, 1, 0, 0)), wn, b), iters=5)
+    fl = 2.0 * B * T * H * W * Co * Ci * 27
+    byts = 2.0 * B * T * H * W * (Ci + Co)
+    results.append(dict(kernel="conv3d_causal_igemm", shape=[B, T, H, W, Ci, Co], ms=med, best_ms=best, tflops=fl / med / 1e9,
+                        frac=fl / med / 1e9 / tf_peak, of=tag, gbs=byts / med / 1e6, cudnn_ms=lib))
+    print(results[-1], flush=True)
+    del x, hist, xn
+  cases2d = [(8, 128, 128, 320, 320, "s1"), (8, 64, 64, 640, 640, "s1"), (8, 32, 32, 1280, 1280, "s1"),
+             (8, 128, 128, 320, 320, "s2"), (4, 360, 640, 192, 96, "up"), (8, 64, 64, 640, 640, "dgrad")]
+  for B, H, W, Ci, Co, kind in cases2d:
+    x = torch.randn((B, H, W, Ci), device="cuda", dtype=torch.bfloat16)
+    w = torch.randn((Co, Ci, 3, 3), device="cuda", dtype=torch.bfloat16) * (9 * Ci) ** -0.5
+    b = torch.randn((Co,), device="cuda", dtype=torch.bfloat16)
+    xn = x.permute(0, 3, 1, 2)  # NCHW view of channels-last memory
+    wn = w.contiguous(memory_format=torch.channels_last)
+    if kind == "s1":
+      pk = OC.pack_conv2d(w, b)
+      fn, lib_fn, fl = (lambda: OC.conv2d(x, pk)), (lambda: F.conv2d(xn, wn, b, padding=1)), 2.0 * B * H * W * Co * Ci * 9
+    elif kind == "s2":
+      pk = OC.pack_conv2d(w, b, stride=2, pad_top_left=1)
+      fn, lib_fn, fl = (lambda: OC.conv2d(x, pk)), (lambda: F.conv2d(xn, wn, b, padding=1, stride=2)), 2.0 * B * H * W * Co * Ci * 9 / 4
+    elif kind == "up":
+      pk = OC.pack_upsample_conv2d(w, b)
+      fn = lambda: OC.upsample2x_conv2d(x, pk)
+      lib_fn = lambda: F.conv2d(F.interpolate(xn, scale_factor=2.0, mode="nearest"), wn, b, padding=1)
+      fl = 2.0 * B * 4 * H * W * Co * Ci * 9  # what up-sampling first would cost; the fused form runs 4 / 9 of it
+    else:
+      pk = OC.pack_conv2d_dgrad(w)
+      dy = torch.randn((B, H, W, Co), device="cuda", dtype=torch.bfloat16)
+      dyn = dy.permute(0, 3, 1, 2)
+      fn = lambda: OC.conv2d_dgrad(dy, pk)
+      lib_fn = lambda: torch.nn.grad.conv2d_input((B, Ci, H, W), wn, dyn, padding=1)
+      fl = 2.0 * B * H * W * Co * Ci * 9
+    med, best = time_ms(fn, iters=5)
+    lib, _ = time_ms(lib_fn, iters=5)
+    results.append(dict(kernel=f"conv2d_igemm_{kind}", shape=[B, H, W, Ci, Co], ms=med, best_ms=best, tflops=fl / med / 1e9,
+                        frac=fl / med / 1e9 / tf_peak, of=tag, cudnn_ms=lib))
+    print(results[-1], flush=True)
+  for C in (96, 384):
+    x = torch.randn((4 * 720 * 1280 * 96 // C, C), device="cuda", dtype=torch.bfloat16)
+    g = torch.ones(C, device="cuda")
+    med, best = time_ms(lambda: OC.rms_act(x, g, None, silu=True), iters=5)
+    results.append(dict(kernel="rms_act_cl", shape=list(x.shape), ms=med, gbs=4.0 * x.numel() / med / 1e6,
+                        frac=4.0 * x.numel() / med / 1e6 / bw_peak, of=tag))
+    print(results[-1], flush=True)
+
+
+def conv_profile_case():
+  """One launch of the causal conv3d on a mid-size case (96 channels, 2 x 360 x 640 output positions) for `ncu`."""
+  from maxdiffusion_b200.ops import conv as OC
+
+  x = torch.randn((1, 2, 360, 640, 96), device="cuda", dtype=torch.bfloat16)
+  hist = torch.randn((1, 2, 360, 640, 96), device="cuda", dtype=torch.bfloat16)
+  w = torch.randn((96, 96, 3, 3, 3), device="cuda", dtype=torch.bfloat16) * 0.02
+  pk = OC.pack_conv3d(w, None)
+  for _ in range(3):
+    OC.conv3d_causal(x, pk, hist=hist)
+  torch.cuda.synchronize()
+  print("conv profile case done")
+
+
 def profile_case():
   """One launch of each hot kernel on a mid-size case (inputs larger than L2, < 1 GB resident) for `ncu`."""
   M, N, Kd = 8192, 5120, 5120
@@ -250,6 +331,8 @@ def profile_case():
 def main(argv):
   if "profile" in argv:
     return profile_case()
+  if "conv_profile" in argv:
+    return conv_profile_case()
   which = [a for i, a in enumerate(argv) if not a.startswith("--") and (i == 0 or argv[i - 1] != "--json")] or ["gemm", "flash", "rowwise"]
   results = []
   if "gemm" in which:
@@ -268,6 +351,8 @@ def main(argv):
     bench_flash_fixed_m(results)
   if "rowwise" in which:
     bench_rowwise(results)
+  if "conv" in which:
+    bench_conv(results)
   if "--json" in argv:
     path = argv[argv.index("--json") + 1]
     os.makedirs(os.path.dirname(path) or ".", exist_ok=True)

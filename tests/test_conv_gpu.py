@@ -131,3 +131,24 @@ def test_conv_results_are_bitwise_reproducible():
   a = OC.conv3d_causal(x, pk)
   b = OC.conv3d_causal(x, pk)
   assert torch.equal(a, b)
+
+
+def test_wan_vae_decode_on_the_conv_kernels_matches_the_pytorch_modules():
+  """The channels-last decoder (conv3d with history tensors, fused up-sampling convs, GEMM 1x1s, row norm) against the
+  fp32 PyTorch modules holding the same parameters, chunked frame by frame as the pipeline runs it."""
+  from maxdiffusion_b200.models.wan.autoencoder_kl_wan import AutoencoderKLWan, WanVAEConfig
+
+  torch.manual_seed(0)
+  vae = AutoencoderKLWan(WanVAEConfig(base_dim=32)).cuda().eval()
+  for n, p in vae.named_parameters():
+    if p.dim() > 1:
+      torch.nn.init.normal_(p, std=(p[0].numel()) ** -0.5)
+  z = torch.randn(1, 16, 3, 8, 12, device="cuda")
+  with torch.no_grad():
+    want = vae.decode(z, chunk=1)                       # fp32 latents: the PyTorch path
+    got = vae.decode(z.to(torch.bfloat16), chunk=1)     # bf16 latents: the kernel path
+    got2 = vae.decode(z.to(torch.bfloat16), chunk=2)
+  assert got.shape == want.shape == (1, 3, 9, 64, 96)
+  for g in (got, got2):
+    err = (g.float() - want).abs()
+    assert err.max() < 0.08 and err.mean() < 0.01, (err.max().item(), err.mean().item())
