@@ -177,10 +177,16 @@ class WanTrainer:
       full_len = tgt_tokens.shape[1]
       tgt_tokens = self.pctx.shard_sequence(tgt_tokens)
       valid = self.pctx.valid_lengths(self.pctx.size, tgt_tokens.shape[1])[self.pctx.rank]
+      pred_all = pred
       pred, tgt_tokens = pred[:, :valid], tgt_tokens[:, :valid]
     # weighted squared error and its gradient in one fused pass; normalised by the global element count so that
     # the per-rank losses of a sequence-sharded step add up to the mean
-    local = OF.weighted_mse(pred, tgt_tokens, weights.tolist() if self.use_weights else None)
+    if pred.numel() == 0:
+      # a rank whose shard is padding only (tiny sequences on many ranks): no loss, but the graph still runs so that
+      # every rank takes part in the collectives of the backward pass
+      local = pred_all.float().sum() * 0.0
+    else:
+      local = OF.weighted_mse(pred, tgt_tokens, weights.tolist() if self.use_weights else None)
     # Ranks along `data` and `fsdp` hold different samples and their gradients are summed by the reduce-scatter and
     # the replica all-reduce, so each rank's share is divided by the number of batch replicas: the applied gradient,
     # the logged norm and the clipping thresholds then refer to the mean over the global batch, as in the reference

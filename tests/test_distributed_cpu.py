@@ -176,3 +176,42 @@ def test_pull_all_to_all_strides_match_the_collective_semantics():
   for me in range(n):
     back = emulate("seq_to_heads", head_sharded, me)
     assert torch.equal(back, xs[me])
+
+
+def test_four_rank_two_dimensional_usp_matches_single_process():
+  """Ulysses (2, adjacent ranks) x ring (2, strided ranks) with BOTH axes larger than one: heads are exchanged inside
+  the Ulysses pairs and the K/V segments travel between them (4 heads over 2 Ulysses ranks, 4 sequence shards)."""
+  ref_losses, ref_digest, ref_gn = _train(0, 1, "flash", 2)
+  out = run_ranks(_train, 4, "ulysses_ring", 2, timeout=600.0)
+  for losses, digest, gn in out:
+    assert losses == pytest.approx(ref_losses, rel=2e-4, abs=1e-5)
+    assert gn == pytest.approx(ref_gn, rel=2e-3)
+    for k, v in ref_digest.items():
+      assert digest[k] == pytest.approx(v, rel=1e-4, abs=1e-4), k
+
+
+def _cfg_pipeline(rank, world, data_axis):
+  """Wan sampling with classifier-free guidance: as a batch of two on every rank (data axis 1) or split over the two
+  ranks of the data axis, cond on one and uncond on the other, combined after an all-gather per step."""
+  from maxdiffusion_b200 import pyconfig
+  from maxdiffusion_b200.parallel.mesh import create_device_mesh
+  from maxdiffusion_b200.pipelines.wan.wan_pipeline import WanPipeline2_1
+
+  config = pyconfig.initialize(
+      ["t", CFG, "run_name=t", "random_init=True", "height=32", "width=32", "num_frames=5", "wan_preset=tiny",
+       f"wan_config_overrides={TINY}", "num_inference_steps=3", "log_config=false", "guidance_scale=4.0",
+       f"ici_data_parallelism={data_axis}", "ici_fsdp_parallelism=1", f"ici_context_parallelism={world // data_axis}",
+       "attention=flash" if world // data_axis == 1 else "attention=tokamax_ring"], unittest=True)
+  torch.manual_seed(0)
+  pipe = WanPipeline2_1.from_config(config, load_vae=False, mesh=create_device_mesh(config), device="cpu")
+  g = torch.Generator().manual_seed(3)
+  pe, ne = torch.randn(1, 8, 48, generator=g), torch.randn(1, 8, 48, generator=g)
+  lat = pipe(prompt_embeds=pe, negative_prompt_embeds=ne, output_type="latent", generator=torch.Generator().manual_seed(5))
+  return lat
+
+
+def test_cfg_as_data_parallelism_matches_the_batched_form():
+  want = _cfg_pipeline(0, 1, 1)
+  got = run_ranks(_cfg_pipeline, 2, 2)
+  for lat in got:
+    assert torch.allclose(lat, want, atol=2e-5, rtol=1e-4)

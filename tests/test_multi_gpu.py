@@ -179,7 +179,7 @@ def test_flag_gated_kv_exchange_feeds_flash_attention():
     assert max(errs) < 3e-2
 
 
-def _train(rank, world, peer):
+def _train(rank, world, peer, attention="tokamax_ring"):
   from maxdiffusion_b200 import pyconfig
   from maxdiffusion_b200.parallel.mesh import create_device_mesh
   from maxdiffusion_b200.trainers.wan_trainer import WanTrainer
@@ -187,7 +187,7 @@ def _train(rank, world, peer):
   config = pyconfig.initialize(
       ["t", CFG, "run_name=t", "height=128", "width=128", "num_frames=9", "dataset_type=synthetic", "wan_preset=tiny",
        'wan_config_overrides={"num_layers": 2, "ffn_dim": 1024}', "remat_policy=SAVE_ATTENTION",
-       "warmup_steps_fraction=0.0", "log_config=false", "write_metrics=false", "attention=tokamax_ring",
+       "warmup_steps_fraction=0.0", "log_config=false", "write_metrics=false", f"attention={attention}", "ulysses_shards=2",
        f"per_device_batch_size={1.0 / world}", f"peer_memory_transport={'true' if peer else 'false'}",
        "stochastic_rounding=false"], unittest=True)
   tr = WanTrainer(config, mesh=create_device_mesh(config))
@@ -210,6 +210,16 @@ def test_training_step_peer_transport_matches_nccl_on_4_ranks():
     pytest.skip("needs 4 GPUs")
   a = _spawn(_train, 4, True)[0]
   b = _spawn(_train, 4, False)[0]
+  assert a == pytest.approx(b, rel=3e-2, abs=3e-2)
+
+
+def test_two_dimensional_usp_on_4_ranks_peer_transport_matches_nccl():
+  """Ulysses 2 x ring 2 with both axes larger than one: the peer-memory all-to-all inside the Ulysses pairs feeds the
+  flag-gated ring launch across them; losses must agree with the NCCL transport of the same mesh."""
+  if torch.cuda.device_count() < 4:
+    pytest.skip("needs 4 GPUs")
+  a = _spawn(_train, 4, True, "ulysses_ring")[0]
+  b = _spawn(_train, 4, False, "ulysses_ring")[0]
   assert a == pytest.approx(b, rel=3e-2, abs=3e-2)
 
 
