@@ -106,3 +106,198 @@ extern "C" int mdb_rms_act_cl(const void* x, long long ldx, void* y, long long l
   else rms_act_kernel<32><<<static_cast<int>(blocks), 256, 0, st>>>(xp, ldx, yp, ldy, gamma, beta, rows, C, eps, act);
   return static_cast<int>(cudaGetLastError());
 }
+
+// ---------------------------------------------------------------------------------------------------------------
+// GroupNorm (+ SiLU) for channels-last activations [N, HW, C], forward and backward
+// (UNet ResNet blocks and the image VAE: src/maxdiffusion/models/resnet_flax.py:97-186, vae_flax.py).
+//
+// A group's channels are neither contiguous over a pixel nor aligned to 16-byte vectors (320 channels in 32 groups
+// are 10 channels each), so both passes work per CHANNEL and the groups appear only in a tiny fold in between:
+//   sums  : partial[n, split, c] = {sum f1, sum f2} over a strip of pixels; forward (f1, f2) = (x, x^2), backward
+//           (f1, f2) = (dy', dy' * x) with dy' = dy * silu'(x * scale + shift) when the activation is fused
+//   fold  : (host side, on [N, C]-sized arrays) group statistics -> per-(n, c) coefficients
+//   apply : forward y = act(x * a + b); backward dx = dy' * a + b + x * c, coefficients fp32 [N, C]
+// One strip of pixels per CTA, a thread keeps one 8-channel vector in registers over the rows of the strip; partial
+// sums are combined in a fixed order, so results are bitwise reproducible.
+// ---------------------------------------------------------------------------------------------------------------
+namespace mdb {
+namespace cln {
+
+__device__ __forceinline__ float silu_grad(float z) {
+  const float s = 1.0f / (1.0f + __expf(-z));
+  return s * (1.0f + z * (1.0f - s));
+}
+
+// grid (splits, N), block = rows_per_pass * vecs threads. act_a / act_b: forward coefficients for the fused SiLU of the
+// backward pass (null: none). dy null: forward sums of x.
+__global__ void __launch_bounds__(256)
+gn_cl_sums_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ dy, const float* __restrict__ act_a,
+                  const float* __restrict__ act_b, float2* __restrict__ partial, int HW, int C, int rows_per_pass) {
+  extern __shared__ float red[];  // [rows_per_pass][vecs][16]
+  const int vecs = C >> 3;
+  const int v = threadIdx.x % vecs, r = threadIdx.x / vecs;
+  const int n = blockIdx.y, splits = gridDim.x;
+  const int per = (HW + splits - 1) / splits;
+  const int row0 = blockIdx.x * per, row1 = min(HW, row0 + per);
+  float s1[8], s2[8], a[8], b[8];
+#pragma unroll
+  for (int j = 0; j < 8; ++j) s1[j] = s2[j] = 0.0f;
+  if (dy != nullptr && act_a != nullptr) {
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      a[j] = act_a[static_cast<long long>(n) * C + v * 8 + j];
+      b[j] = act_b[static_cast<long long>(n) * C + v * 8 + j];
+    }
+  }
+  for (int row = row0 + r; row < row1; row += rows_per_pass) {
+    const long long off = (static_cast<long long>(n) * HW + row) * C + v * 8;
+    const uint4 xv = *reinterpret_cast<const uint4*>(x + off);
+    const uint32_t xw[4] = {xv.x, xv.y, xv.z, xv.w};
+    float xf[8];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float2 f = unpack_bf16x2(xw[j]);
+      xf[2 * j] = f.x;
+      xf[2 * j + 1] = f.y;
+    }
+    if (dy == nullptr) {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        s1[j] += xf[j];
+        s2[j] += xf[j] * xf[j];
+      }
+    } else {
+      const uint4 dv = *reinterpret_cast<const uint4*>(dy + off);
+      const uint32_t dw[4] = {dv.x, dv.y, dv.z, dv.w};
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float2 f = unpack_bf16x2(dw[j]);
+        float d0 = f.x, d1 = f.y;
+        if (act_a != nullptr) {
+          d0 *= silu_grad(xf[2 * j] * a[2 * j] + b[2 * j]);
+          d1 *= silu_grad(xf[2 * j + 1] * a[2 * j + 1] + b[2 * j + 1]);
+        }
+        s1[2 * j] += d0;
+        s1[2 * j + 1] += d1;
+        s2[2 * j] += d0 * xf[2 * j];
+        s2[2 * j + 1] += d1 * xf[2 * j + 1];
+      }
+    }
+  }
+  float* mine = red + (static_cast<size_t>(r) * vecs + v) * 16;
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    mine[j] = s1[j];
+    mine[8 + j] = s2[j];
+  }
+  __syncthreads();
+  if (r == 0) {
+    for (int rr = 1; rr < rows_per_pass; ++rr) {  // fixed order
+      const float* o = red + (static_cast<size_t>(rr) * vecs + v) * 16;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        s1[j] += o[j];
+        s2[j] += o[8 + j];
+      }
+    }
+    float2* dst = partial + (static_cast<long long>(n) * splits + blockIdx.x) * C + v * 8;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) dst[j] = make_float2(s1[j], s2[j]);
+  }
+}
+
+// forward: y = act(x * a + b). backward (dy != null): dx = dy' * a + b + x * c, dy' = dy * silu'(x * fa + fb) if fa.
+__global__ void __launch_bounds__(256)
+gn_cl_apply_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ dy, __nv_bfloat16* __restrict__ out,
+                   const float* __restrict__ ca, const float* __restrict__ cb, const float* __restrict__ cc,
+                   const float* __restrict__ fa, const float* __restrict__ fb, long long total_vecs, int HW, int C,
+                   int act) {
+  const int vecs = C >> 3;
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total_vecs;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const int v = static_cast<int>(i % vecs);
+    const long long row = i / vecs;
+    const int n = static_cast<int>(row / HW);
+    const long long cbase = static_cast<long long>(n) * C + v * 8;
+    const uint4 xv = *reinterpret_cast<const uint4*>(x + i * 8);
+    const uint32_t xw[4] = {xv.x, xv.y, xv.z, xv.w};
+    float xf[8], o[8];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float2 f = unpack_bf16x2(xw[j]);
+      xf[2 * j] = f.x;
+      xf[2 * j + 1] = f.y;
+    }
+    const float4 a0 = *reinterpret_cast<const float4*>(ca + cbase), a1 = *reinterpret_cast<const float4*>(ca + cbase + 4);
+    const float4 b0 = *reinterpret_cast<const float4*>(cb + cbase), b1 = *reinterpret_cast<const float4*>(cb + cbase + 4);
+    const float av[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
+    const float bv[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
+    if (dy == nullptr) {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const float z = xf[j] * av[j] + bv[j];
+        o[j] = act ? z / (1.0f + __expf(-z)) : z;
+      }
+    } else {
+      const uint4 dv = *reinterpret_cast<const uint4*>(dy + i * 8);
+      const uint32_t dw[4] = {dv.x, dv.y, dv.z, dv.w};
+      float df[8];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float2 f = unpack_bf16x2(dw[j]);
+        df[2 * j] = f.x;
+        df[2 * j + 1] = f.y;
+      }
+      if (fa != nullptr) {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) df[j] *= silu_grad(xf[j] * fa[cbase + j] + fb[cbase + j]);
+      }
+      const float4 c0 = *reinterpret_cast<const float4*>(cc + cbase), c1 = *reinterpret_cast<const float4*>(cc + cbase + 4);
+      const float cv[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
+#pragma unroll
+      for (int j = 0; j < 8; ++j) o[j] = df[j] * av[j] + bv[j] + xf[j] * cv[j];
+    }
+    uint4 ov;
+    ov.x = pack_bf16x2(o[0], o[1]);
+    ov.y = pack_bf16x2(o[2], o[3]);
+    ov.z = pack_bf16x2(o[4], o[5]);
+    ov.w = pack_bf16x2(o[6], o[7]);
+    *reinterpret_cast<uint4*>(out + i * 8) = ov;
+  }
+}
+
+}  // namespace cln
+}  // namespace mdb
+
+// Per-channel partial sums over `splits` strips of pixels: partial fp32 [N, splits, C, 2]. x (and dy) bf16 [N, HW, C],
+// contiguous, C a multiple of 8 and at most 2048. act_a / act_b (fp32 [N, C], may be null) select the fused-SiLU form
+// of the backward sums.
+extern "C" int mdb_gn_cl_sums(const void* x, const void* dy, const float* act_a, const float* act_b, float* partial, int N,
+                              int HW, int C, int splits, void* stream) {
+  using namespace mdb::cln;
+  if (N <= 0 || HW <= 0) return 0;
+  const int vecs = C >> 3;
+  if ((C & 7) || vecs < 1 || vecs > 256 || splits < 1) return 3702;
+  const int rows_per_pass = 256 / vecs;
+  const int threads = rows_per_pass * vecs;
+  const size_t smem = static_cast<size_t>(threads) * 16 * sizeof(float);
+  gn_cl_sums_kernel<<<dim3(splits, N), threads, smem, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const __nv_bfloat16*>(x), static_cast<const __nv_bfloat16*>(dy), act_a, act_b,
+      reinterpret_cast<float2*>(partial), HW, C, rows_per_pass);
+  return static_cast<int>(cudaGetLastError());
+}
+
+extern "C" int mdb_gn_cl_apply(const void* x, const void* dy, void* out, const float* ca, const float* cb, const float* cc,
+                               const float* fa, const float* fb, int N, int HW, int C, int act, void* stream) {
+  using namespace mdb::cln;
+  if (N <= 0 || HW <= 0) return 0;
+  if ((C & 7) || ca == nullptr || cb == nullptr || (dy != nullptr && cc == nullptr)) return 3703;
+  const long long total = static_cast<long long>(N) * HW * (C >> 3);
+  long long blocks = (total + 255) / 256;
+  const long long cap = static_cast<long long>(mdb::sm_count()) * 16;
+  if (blocks > cap) blocks = cap;
+  gn_cl_apply_kernel<<<static_cast<int>(blocks), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const __nv_bfloat16*>(x), static_cast<const __nv_bfloat16*>(dy), static_cast<__nv_bfloat16*>(out), ca, cb,
+      cc, fa, fb, total, HW, C, act);
+  return static_cast<int>(cudaGetLastError());
+}

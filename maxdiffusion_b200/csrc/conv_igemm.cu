@@ -20,6 +20,9 @@
 // (bias, SiLU, residual add, ragged-edge masking). Accumulators are double buffered in TMEM.
 // Channel counts that are not multiples of 64 (96, 192, 320) cost no tensor work: the last channel block is
 // fetched with zero fill and only its valid 16-wide K steps are issued.
+// The lane that issues the MMAs pays a fixed price per pipeline stage (barrier wait, fence, commit: several hundred
+// cycles) besides the price per instruction, and with few output channels (N <= 128) a stage of one 64-channel block
+// holds less tensor work than that. Narrow tiles therefore put TWO (tap, channel block) units into a stage.
 //
 // Replaces the XLA:GPU / cuDNN convolutions behind the reference's `WanCausalConv3d`, `WanResample`,
 // `WanResidualBlock` (src/maxdiffusion/models/wan/autoencoder_kl_wan.py:70-147, 245-389, 452-484) and the UNet /
@@ -36,7 +39,11 @@ constexpr int NUM_THREADS = 192;
 constexpr int MAX_STAGES = 6;
 constexpr int MAX_TAPS = 36;      // 27 (3x3x3) or 4 classes x 9
 constexpr int MAX_CLASSES = 4;
-constexpr int ACC_COLS = 256;     // TMEM columns per accumulator (two accumulators = all 512 columns)
+// TMEM columns per accumulator: 256 (two accumulators = all 512 columns, one CTA per SM) for wide tiles, 128 for
+// tiles of at most 128 output channels, which run TWO CTAs per SM (256 columns and half the shared memory each).
+// One thread can issue a tcgen05.mma only every ~100 ns whatever its width, so with narrow tiles a single issuing
+// lane leaves the tensor pipe half idle; two co-resident CTAs are two issuing lanes, each tile still accumulated
+// by one thread in a fixed order (bitwise reproducible).
 
 struct Tap {
   int o0;              // added to the channel coordinate (parity * C in the stride-2 view, else 0)
@@ -56,6 +63,8 @@ struct Params {
   int N;                         // output channels, multiple of 8
   int BN;                        // tile width: multiple of 16, <= 256
   int stages;
+  int ups;                       // (tap, channel block) units per pipeline stage: 1 or 2
+  int acc_cols;                  // TMEM columns per accumulator: 128 or 256
   int alt_dim, alt_shift, has_alt;  // a tap whose coordinate along alt_dim is negative reads the second map at +alt_shift
   long long os1, os2, os3, os4;  // output strides (elements) along dims 1..4
   long long class_off[MAX_CLASSES];
@@ -81,14 +90,15 @@ __device__ __forceinline__ TileCoord decode_tile(int tile, const Params& p, int 
   return c;
 }
 
-__global__ void __launch_bounds__(NUM_THREADS, 1)
+__global__ void __launch_bounds__(NUM_THREADS, 2)
 conv_igemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUtensorMap tmap_alt,
                   const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ Params p) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   const int STAGES = p.stages;
   const int B_BYTES = p.BN * BK * 2;
-  const int STAGE_BYTES = A_BYTES + B_BYTES;  // a multiple of 1024: BN is a multiple of 16
+  const int UNIT_BYTES = A_BYTES + B_BYTES;   // a multiple of 1024: BN is a multiple of 16
+  const int STAGE_BYTES = p.ups * UNIT_BYTES;
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES * STAGE_BYTES);
   uint64_t* full_bar = bars;                          // [MAX_STAGES]
   uint64_t* empty_bar = bars + MAX_STAGES;            // [MAX_STAGES]
@@ -120,6 +130,7 @@ conv_igemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_const
     prefetch_tensormap(&tmap_x);
     prefetch_tensormap(&tmap_w);
   }
+  const int ACC_COLS = p.acc_cols;
   if (warp == 1) {
     tmem_alloc(tmem_ptr_smem, 2 * ACC_COLS);
     tmem_relinquish();
@@ -139,25 +150,33 @@ conv_igemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_const
       for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
         const TileCoord tc = decode_tile(tile, p, nt1, nt2, nt3, num_n);
         const int n0 = tc.n_idx * p.BN;
-        for (int ti = p.tap_begin[tc.cls]; ti < p.tap_begin[tc.cls + 1] && ok; ++ti) {
-          const Tap tap = p.taps[ti];
-          int c1 = tc.m1 + tap.o1, c2 = tc.m2 + tap.o2, c3 = tc.m3 + tap.o3, c4 = tc.m4 + tap.o4;
-          const CUtensorMap* map = &tmap_x;
-          if (p.has_alt) {
-            // a tap that reaches before the first position along alt_dim reads the history tensor instead
-            if (p.alt_dim == 3 && c3 < 0) { c3 += p.alt_shift; map = &tmap_alt; }
-            else if (p.alt_dim == 2 && c2 < 0) { c2 += p.alt_shift; map = &tmap_alt; }
-          }
-          for (int kb = 0; kb < num_kb; ++kb) {
-            if (!mbar_wait(&empty_bar[stage], phase ^ 1u, abort_flag, p.status, 110)) { ok = false; break; }
-            uint8_t* sa = smem + stage * STAGE_BYTES;
-            uint8_t* sb = sa + A_BYTES;
-            mbar_expect_tx(&full_bar[stage], STAGE_BYTES);
+        const int t0 = p.tap_begin[tc.cls];
+        const int n_units = (p.tap_begin[tc.cls + 1] - t0) * num_kb;
+        int ti = t0, kb = 0;
+        Tap tap = p.taps[ti];
+        for (int u0 = 0; u0 < n_units && ok; u0 += p.ups) {
+          const int nu = min(p.ups, n_units - u0);
+          if (!mbar_wait(&empty_bar[stage], phase ^ 1u, abort_flag, p.status, 110)) { ok = false; break; }
+          mbar_expect_tx(&full_bar[stage], nu * UNIT_BYTES);
+          uint8_t* sa = smem + stage * STAGE_BYTES;
+          for (int j = 0; j < nu; ++j, sa += UNIT_BYTES) {
+            int c1 = tc.m1 + tap.o1, c2 = tc.m2 + tap.o2, c3 = tc.m3 + tap.o3, c4 = tc.m4 + tap.o4;
+            const CUtensorMap* map = &tmap_x;
+            if (p.has_alt) {
+              // a tap that reaches before the first position along alt_dim reads the history tensor instead
+              if (p.alt_dim == 3 && c3 < 0) { c3 += p.alt_shift; map = &tmap_alt; }
+              else if (p.alt_dim == 2 && c2 < 0) { c2 += p.alt_shift; map = &tmap_alt; }
+            }
             tma_load_5d(sa, map, &full_bar[stage], tap.o0 + kb * BK, c1, c2, c3, c4);
-            tma_load_2d(sb, &tmap_w, &full_bar[stage], tap.koff + kb * BK, n0);
-            ++issued;
-            if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+            tma_load_2d(sa + A_BYTES, &tmap_w, &full_bar[stage], tap.koff + kb * BK, n0);
+            if (++kb == num_kb) {
+              kb = 0;
+              ++ti;
+              if (ti < p.tap_begin[tc.cls + 1]) tap = p.taps[ti];
+            }
           }
+          ++issued;
+          if (++stage == STAGES) { stage = 0; phase ^= 1u; }
         }
       }
       if (!ok) {
@@ -187,22 +206,33 @@ conv_igemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_const
         tc_fence_after_sync();
         const uint32_t d_tmem = tmem_base + acc * ACC_COLS;
         uint32_t accumulate = 0;
-        for (int ti = 0; ti < n_taps && ok; ++ti) {
-          for (int kb = 0; kb < num_kb; ++kb) {
-            if (!mbar_wait(&full_bar[stage], phase, abort_flag, p.status, 121)) { ok = false; break; }
-            tc_fence_after_sync();
-            const uint32_t sa = smem_u32(smem + stage * STAGE_BYTES);
-            const uint32_t sb = sa + A_BYTES;
-            const int left = p.C - kb * BK;           // valid channels of this block (the rest is zero fill)
-            const int ksteps = left >= BK ? BK / 16 : (left + 15) / 16;
-            for (int k = 0; k < ksteps; ++k) {
-              umma_ss(d_tmem, make_smem_desc(sa + k * 32, 16, 1024), make_smem_desc(sb + k * 32, 16, 1024), idesc,
-                      accumulate);
-              accumulate = 1u;
+        const int n_units = n_taps * num_kb;
+        // this lane is the critical resource of the kernel: no divisions, descriptors advance by addition
+        const int last_ksteps = (p.C - (num_kb - 1) * BK + 15) / 16;
+        int kb = 0;
+        for (int u0 = 0; u0 < n_units; u0 += p.ups) {
+          const int nu = min(p.ups, n_units - u0);
+          if (!mbar_wait(&full_bar[stage], phase, abort_flag, p.status, 121)) { ok = false; break; }
+          tc_fence_after_sync();
+          uint32_t sa = smem_u32(smem + stage * STAGE_BYTES);
+          for (int j = 0; j < nu; ++j, sa += UNIT_BYTES) {
+            const uint64_t da = make_smem_desc(sa, 16, 1024);
+            const uint64_t db = make_smem_desc(sa + A_BYTES, 16, 1024);
+            const bool last = (kb + 1 == num_kb);
+            if (!last || last_ksteps == BK / 16) {
+              // one K step (16 bf16 = 32 bytes) advances the descriptors' address field (units of 16 bytes) by 2
+              umma_ss(d_tmem, da, db, idesc, accumulate);
+              umma_ss(d_tmem, da + 2, db + 2, idesc, 1u);
+              umma_ss(d_tmem, da + 4, db + 4, idesc, 1u);
+              umma_ss(d_tmem, da + 6, db + 6, idesc, 1u);
+            } else {
+              for (int k = 0; k < last_ksteps; ++k) umma_ss(d_tmem, da + 2 * k, db + 2 * k, idesc, k ? 1u : accumulate);
             }
-            umma_commit(&empty_bar[stage]);
-            if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+            accumulate = 1u;
+            kb = last ? 0 : kb + 1;
           }
+          umma_commit(&empty_bar[stage]);
+          if (++stage == STAGES) { stage = 0; phase ^= 1u; }
         }
         if (ok) umma_commit(&tmem_full[acc]);
       }
@@ -306,6 +336,18 @@ static int pick_bn(int N) {
 }  // namespace conv
 }  // namespace mdb
 
+// Tuning overrides for the tile search and the benchmarks (0 = the launcher's own choice): units per stage (1 / 2),
+// an upper limit on the pipeline stages, CTAs per SM (1 / 2; 2 only applies to tiles of at most 128 channels).
+static int g_tune_ups = 0, g_tune_stages = 0, g_tune_ctas = 0;
+
+extern "C" int mdb_conv_igemm_tune(int ups, int stages, int ctas_per_sm) {
+  if (ups < 0 || ups > 2 || stages < 0 || stages > 6 || ctas_per_sm < 0 || ctas_per_sm > 2) return 3609;
+  g_tune_ups = ups;
+  g_tune_stages = stages;
+  g_tune_ctas = ctas_per_sm;
+  return 0;
+}
+
 // Generic entry point; `ops/conv.py` builds the descriptions for the concrete convolutions.
 //   x / x_alt : activation tensor and optional history tensor, both seen as 5-D arrays with `dims` / `alt_dims`
 //               (innermost first, dim 0 = channels, contiguous) and element strides `strides` / `alt_strides` of dims 1..4
@@ -355,7 +397,17 @@ extern "C" int mdb_conv_igemm(const void* x, const void* x_alt, const void* w, v
   p.ext1 = ext[0]; p.ext2 = ext[1]; p.ext3 = ext[2]; p.ext4 = ext[3];
   p.C = C; p.N = N;
   p.BN = pick_bn(N);
-  p.stages = p.BN > 128 ? 4 : 6;
+  const int unit_bytes = A_BYTES + p.BN * BK * 2;
+  int ctas_per_sm = p.BN <= 128 ? 2 : 1;
+  if (g_tune_ctas > 0) ctas_per_sm = (g_tune_ctas == 2 && p.BN <= 128) ? 2 : 1;
+  p.acc_cols = ctas_per_sm == 2 ? 128 : 256;
+  const int budget = (ctas_per_sm == 2 ? 112 : 226) * 1024 - 1024 - 256;
+  p.ups = g_tune_ups > 0 ? g_tune_ups : (ctas_per_sm == 2 ? 1 : (p.BN <= 128 ? 2 : 1));
+  if (p.ups < 1 || p.ups > 2) return 3608;
+  p.stages = budget / (p.ups * unit_bytes);
+  if (g_tune_stages > 0 && g_tune_stages < p.stages) p.stages = g_tune_stages;
+  if (p.stages > MAX_STAGES) p.stages = MAX_STAGES;
+  if (p.stages < 2) return 3608;
   p.alt_dim = alt_dim; p.alt_shift = alt_shift; p.has_alt = (x_alt != nullptr && alt_dim >= 2 && alt_dim <= 3) ? 1 : 0;
   p.os1 = out_strides[0]; p.os2 = out_strides[1]; p.os3 = out_strides[2]; p.os4 = out_strides[3];
   p.out = static_cast<__nv_bfloat16*>(out);
@@ -387,8 +439,10 @@ extern "C" int mdb_conv_igemm(const void* x, const void* x_alt, const void* w, v
     rc = encode_tmap_bf16(&tw, w, 2, wd, ws, wb);
     if (rc) return rc;
   }
-  int smem = p.stages * (A_BYTES + p.BN * BK * 2) + 1024 + 256;
-  if (smem < 120 * 1024) smem = 120 * 1024;  // one CTA per SM: every CTA allocates all of TMEM
+  int smem = p.stages * p.ups * unit_bytes + 1024 + 256;
+  // the shared-memory request decides how many CTAs share an SM; it has to agree with the TMEM each one allocates
+  if (ctas_per_sm == 1 && smem < 120 * 1024) smem = 120 * 1024;
+  if (ctas_per_sm == 2 && smem < 80 * 1024) smem = 80 * 1024;
   static bool configured = false;
   if (!configured) {
     MDB_CHECK_CUDA(cudaFuncSetAttribute(conv_igemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
@@ -398,7 +452,8 @@ extern "C" int mdb_conv_igemm(const void* x, const void* x_alt, const void* w, v
   const long long tiles = static_cast<long long>(n_classes) * ext[3] * cdiv(ext[2], box[2]) * cdiv(ext[1], box[1]) *
                           cdiv(ext[0], box[0]) * cdiv(N, p.BN);
   if (tiles >= (1ll << 31)) return 3607;
-  const int grid = tiles < sm_count() ? static_cast<int>(tiles) : sm_count();
+  const long long slots = static_cast<long long>(sm_count()) * ctas_per_sm;
+  const int grid = tiles < slots ? static_cast<int>(tiles) : static_cast<int>(slots);
   conv_igemm_kernel<<<grid, NUM_THREADS, smem, static_cast<cudaStream_t>(stream_ptr)>>>(tx, talt, tw, p);
   return static_cast<int>(cudaGetLastError());
 }

@@ -12,7 +12,7 @@ import torch.nn as nn
 import torch.nn.functional as F
 
 from .unet_2d_condition import DownBlock, MidBlock, UNetConfig, _TimestepEmbedding
-from .layers import sinusoidal_embedding
+from .layers import Conv2d, sinusoidal_embedding
 
 
 class ControlNetConditioningEmbedding(nn.Module):
@@ -20,12 +20,12 @@ class ControlNetConditioningEmbedding(nn.Module):
 
   def __init__(self, out_channels: int, in_channels: int = 3, block_out_channels=(16, 32, 96, 256)):
     super().__init__()
-    self.conv_in = nn.Conv2d(in_channels, block_out_channels[0], 3, padding=1)
+    self.conv_in = Conv2d(in_channels, block_out_channels[0], 3, padding=1)
     blocks = []
     for a, b in zip(block_out_channels[:-1], block_out_channels[1:]):
-      blocks += [nn.Conv2d(a, a, 3, padding=1), nn.Conv2d(a, b, 3, padding=1, stride=2)]
+      blocks += [Conv2d(a, a, 3, padding=1), Conv2d(a, b, 3, padding=1, stride=2)]
     self.blocks = nn.ModuleList(blocks)
-    self.conv_out = nn.Conv2d(block_out_channels[-1], out_channels, 3, padding=1)
+    self.conv_out = Conv2d(block_out_channels[-1], out_channels, 3, padding=1)
     nn.init.zeros_(self.conv_out.weight)
     nn.init.zeros_(self.conv_out.bias)
 
@@ -46,20 +46,20 @@ class ControlNetModel(nn.Module):
     depth = [cfg.transformer_layers_per_block] * n if isinstance(cfg.transformer_layers_per_block, int) else list(cfg.transformer_layers_per_block)
     heads = [cfg.attention_head_dim] * n if isinstance(cfg.attention_head_dim, int) else list(cfg.attention_head_dim)
     temb, g = ch[0] * 4, cfg.norm_num_groups
-    self.conv_in = nn.Conv2d(cfg.in_channels, ch[0], 3, padding=1)
+    self.conv_in = Conv2d(cfg.in_channels, ch[0], 3, padding=1)
     self.time_embedding = _TimestepEmbedding(ch[0], temb)
     if cfg.addition_embed_type == "text_time":
       self.add_embedding = _TimestepEmbedding(cfg.projection_class_embeddings_input_dim, temb)
     self.controlnet_cond_embedding = ControlNetConditioningEmbedding(ch[0], conditioning_channels)
     attn = lambda i: (heads[i], depth[i], cfg.cross_attention_dim, g, cfg.use_linear_projection)
-    downs, zero, cin = [], [nn.Conv2d(ch[0], ch[0], 1)], ch[0]
+    downs, zero, cin = [], [Conv2d(ch[0], ch[0], 1)], ch[0]
     for i, kind in enumerate(cfg.down_block_types):
       downs.append(DownBlock(cin, ch[i], temb, cfg.layers_per_block, g, attn(i) if "CrossAttn" in kind else None, add_down=i < n - 1))
-      zero += [nn.Conv2d(ch[i], ch[i], 1) for _ in range(cfg.layers_per_block + (1 if i < n - 1 else 0))]
+      zero += [Conv2d(ch[i], ch[i], 1) for _ in range(cfg.layers_per_block + (1 if i < n - 1 else 0))]
       cin = ch[i]
     self.down_blocks, self.controlnet_down_blocks = nn.ModuleList(downs), nn.ModuleList(zero)
     self.mid_block = MidBlock(ch[-1], temb, g, attn(n - 1))
-    self.controlnet_mid_block = nn.Conv2d(ch[-1], ch[-1], 1)
+    self.controlnet_mid_block = Conv2d(ch[-1], ch[-1], 1)
     for z in list(self.controlnet_down_blocks) + [self.controlnet_mid_block]:
       nn.init.zeros_(z.weight)
       nn.init.zeros_(z.bias)

@@ -64,6 +64,23 @@ class RMSNorm(nn.Module):
     return y.to(x.dtype)
 
 
+class Conv2d(nn.Conv2d):
+  """3x3 / 1x1 convolution with the parameter names of `torch.nn.Conv2d` (checkpoints load directly).
+
+  CUDA bf16 inputs run on this repository's implicit-GEMM kernels (`ops.functional.conv2d`: forward, input gradient
+  and weight gradient) and come back in channels-last memory, which the GroupNorm and the attention blocks of the
+  UNet / VAE consume as they are. `padding="far"` pads after the image only (the VAE's stride-2 down-sampling);
+  `forward(x, upsample=True)` applies the convolution to the nearest-2x up-sampled input without building it.
+  reference: the `nn.Conv` layers of src/maxdiffusion/models/resnet_flax.py:37-186 and vae_flax.py."""
+
+  def __init__(self, in_channels, out_channels, kernel_size, stride=1, padding=0, bias=True):
+    self.pad_mode = padding
+    super().__init__(in_channels, out_channels, kernel_size, stride=stride, padding=0 if padding == "far" else padding, bias=bias)
+
+  def forward(self, x, upsample: bool = False):
+    return OF.conv2d(x, self.weight, self.bias, stride=self.stride[0], padding=self.pad_mode, upsample=upsample)
+
+
 class GroupNorm(nn.GroupNorm):
   """GroupNorm with an optional fused SiLU (`act=True`); parameter names are those of `torch.nn.GroupNorm`.
 

@@ -7,7 +7,8 @@ parameter names follow the diffusers `UNet2DConditionModel` checkpoint so that i
 
 GEMMs (projections, GEGLU feed-forward, attention in/out) run on the tcgen05 GEMM through `ops.functional.linear`
 for bf16 CUDA tensors; attention with head_dim 64 (SDXL) or 128 uses the flash kernels, other head sizes (40..160
-for SD 1.x/2.x) go through `scaled_dot_product_attention`; convolutions use cuDNN; GroupNorm(+SiLU) is the fused kernel of `ops.functional.group_norm`.
+for SD 1.x/2.x) go through `scaled_dot_product_attention`; convolutions (forward, input and weight gradients) run on the implicit-GEMM kernels through `layers.Conv2d` and keep
+the activations in channels-last memory; GroupNorm(+SiLU) is the channels-last kernel of `ops.functional.group_norm`.
 """
 from __future__ import annotations
 
@@ -19,7 +20,7 @@ import torch.nn as nn
 import torch.nn.functional as F
 
 from ..ops import functional as OF
-from .layers import GroupNorm, Linear, sinusoidal_embedding
+from .layers import Conv2d, GroupNorm, Linear, sinusoidal_embedding
 from .vae import ResnetBlock2D
 
 
@@ -134,9 +135,9 @@ class Transformer2DModel(nn.Module):
     super().__init__()
     self.linear_proj = linear_proj
     self.norm = GroupNorm(groups, dim, eps=1e-6)
-    self.proj_in = Linear(dim, dim) if linear_proj else nn.Conv2d(dim, dim, 1)
+    self.proj_in = Linear(dim, dim) if linear_proj else Conv2d(dim, dim, 1)
     self.transformer_blocks = nn.ModuleList([BasicTransformerBlock(dim, heads, cross_dim) for _ in range(depth)])
-    self.proj_out = Linear(dim, dim) if linear_proj else nn.Conv2d(dim, dim, 1)
+    self.proj_out = Linear(dim, dim) if linear_proj else Conv2d(dim, dim, 1)
 
   def forward(self, x, context):
     b, c, h, w = x.shape
@@ -159,7 +160,7 @@ class Downsample2D(nn.Module):
 
   def __init__(self, dim):
     super().__init__()
-    self.conv = nn.Conv2d(dim, dim, 3, stride=2, padding=1)
+    self.conv = Conv2d(dim, dim, 3, stride=2, padding=1)
 
   def forward(self, x):
     return self.conv(x)
@@ -169,10 +170,10 @@ class Upsample2D(nn.Module):
 
   def __init__(self, dim):
     super().__init__()
-    self.conv = nn.Conv2d(dim, dim, 3, padding=1)
+    self.conv = Conv2d(dim, dim, 3, padding=1)
 
   def forward(self, x):
-    return self.conv(F.interpolate(x, scale_factor=2.0, mode="nearest"))
+    return self.conv(x, upsample=True)  # nearest-2x folded into the convolution
 
 
 class DownBlock(nn.Module):
@@ -250,7 +251,7 @@ class UNet2DConditionModel(nn.Module):
     heads = [cfg.attention_head_dim] * n if isinstance(cfg.attention_head_dim, int) else list(cfg.attention_head_dim)
     temb = ch[0] * 4
     g = cfg.norm_num_groups
-    self.conv_in = nn.Conv2d(cfg.in_channels, ch[0], 3, padding=1)
+    self.conv_in = Conv2d(cfg.in_channels, ch[0], 3, padding=1)
     self.time_embedding = _TimestepEmbedding(ch[0], temb)
     if cfg.addition_embed_type == "text_time":
       self.add_embedding = _TimestepEmbedding(cfg.projection_class_embeddings_input_dim, temb)
@@ -270,7 +271,7 @@ class UNet2DConditionModel(nn.Module):
       prev = cout
     self.up_blocks = nn.ModuleList(ups)
     self.conv_norm_out = GroupNorm(g, ch[0], eps=1e-5)
-    self.conv_out = nn.Conv2d(ch[0], cfg.out_channels, 3, padding=1)
+    self.conv_out = Conv2d(ch[0], cfg.out_channels, 3, padding=1)
 
   def time_embed(self, timesteps, dtype, added_cond_kwargs=None):
     cfg = self.cfg

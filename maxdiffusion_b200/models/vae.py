@@ -1,8 +1,9 @@
 """AutoencoderKL for SD 1.x / 2.x / SDXL (4 latent channels) and Flux (16 channels, shift + scale).
 
 Reference: `FlaxAutoencoderKL` and `FlaxDiagonalGaussianDistribution` (src/maxdiffusion/models/vae_flax.py:723-1020).
-Module and parameter names follow the diffusers `AutoencoderKL` checkpoint. Convolutions run through
-cuDNN / PyTorch; the single-head mid-block attention uses `ops.functional.attention`.
+Module and parameter names follow the diffusers `AutoencoderKL` checkpoint. Convolutions run on the implicit-GEMM
+kernels through `layers.Conv2d` (CUDA bf16; PyTorch elsewhere); the single-head mid-block attention uses
+`ops.functional.attention`.
 """
 from __future__ import annotations
 
@@ -14,7 +15,7 @@ import torch.nn as nn
 import torch.nn.functional as F
 
 from ..ops import functional as OF
-from .layers import GroupNorm
+from .layers import Conv2d, GroupNorm
 
 
 @dataclass
@@ -49,11 +50,11 @@ class ResnetBlock2D(nn.Module):
   def __init__(self, cin, cout, groups=32, temb_channels: Optional[int] = None, eps=1e-6):
     super().__init__()
     self.norm1 = GroupNorm(groups, cin, eps=eps)
-    self.conv1 = nn.Conv2d(cin, cout, 3, padding=1)
+    self.conv1 = Conv2d(cin, cout, 3, padding=1)
     self.time_emb_proj = nn.Linear(temb_channels, cout) if temb_channels else None
     self.norm2 = GroupNorm(groups, cout, eps=eps)
-    self.conv2 = nn.Conv2d(cout, cout, 3, padding=1)
-    self.conv_shortcut = nn.Conv2d(cin, cout, 1) if cin != cout else None
+    self.conv2 = Conv2d(cout, cout, 3, padding=1)
+    self.conv_shortcut = Conv2d(cin, cout, 1) if cin != cout else None
 
   def forward(self, x, temb=None):
     h = self.conv1(self.norm1(x, act=True))
@@ -85,12 +86,10 @@ class _Sampler(nn.Module):
   def __init__(self, dim, down: bool):
     super().__init__()
     self.down = down
-    self.conv = nn.Conv2d(dim, dim, 3, stride=2 if down else 1, padding=0 if down else 1)
+    self.conv = Conv2d(dim, dim, 3, stride=2 if down else 1, padding="far" if down else 1)
 
   def forward(self, x):
-    if self.down:
-      return self.conv(F.pad(x, (0, 1, 0, 1)))
-    return self.conv(F.interpolate(x, scale_factor=2.0, mode="nearest"))
+    return self.conv(x) if self.down else self.conv(x, upsample=True)
 
 
 class _Block(nn.Module):
@@ -128,13 +127,13 @@ class Encoder(nn.Module):
   def __init__(self, cfg: VAEConfig):
     super().__init__()
     ch = list(cfg.block_out_channels)
-    self.conv_in = nn.Conv2d(cfg.in_channels, ch[0], 3, padding=1)
+    self.conv_in = Conv2d(cfg.in_channels, ch[0], 3, padding=1)
     self.down_blocks = nn.ModuleList([
         _Block(ch[max(i - 1, 0)], ch[i], cfg.layers_per_block, cfg.norm_num_groups, down=True if i < len(ch) - 1 else None)
         for i in range(len(ch))])
     self.mid_block = _Mid(ch[-1], cfg.norm_num_groups)
     self.conv_norm_out = GroupNorm(cfg.norm_num_groups, ch[-1], eps=1e-6)
-    self.conv_out = nn.Conv2d(ch[-1], 2 * cfg.latent_channels, 3, padding=1)
+    self.conv_out = Conv2d(ch[-1], 2 * cfg.latent_channels, 3, padding=1)
 
   def forward(self, x):
     x = self.conv_in(x)
@@ -148,13 +147,13 @@ class Decoder(nn.Module):
   def __init__(self, cfg: VAEConfig):
     super().__init__()
     ch = list(cfg.block_out_channels)[::-1]
-    self.conv_in = nn.Conv2d(cfg.latent_channels, ch[0], 3, padding=1)
+    self.conv_in = Conv2d(cfg.latent_channels, ch[0], 3, padding=1)
     self.mid_block = _Mid(ch[0], cfg.norm_num_groups)
     self.up_blocks = nn.ModuleList([
         _Block(ch[max(i - 1, 0)], ch[i], cfg.layers_per_block + 1, cfg.norm_num_groups, down=False if i < len(ch) - 1 else None)
         for i in range(len(ch))])
     self.conv_norm_out = GroupNorm(cfg.norm_num_groups, ch[-1], eps=1e-6)
-    self.conv_out = nn.Conv2d(ch[-1], cfg.out_channels, 3, padding=1)
+    self.conv_out = Conv2d(ch[-1], cfg.out_channels, 3, padding=1)
 
   def forward(self, z):
     x = self.mid_block(self.conv_in(z))
@@ -187,8 +186,8 @@ class AutoencoderKL(nn.Module):
     self.cfg = cfg or VAEConfig()
     self.encoder, self.decoder = Encoder(self.cfg), Decoder(self.cfg)
     lc = self.cfg.latent_channels
-    self.quant_conv = nn.Conv2d(2 * lc, 2 * lc, 1) if self.cfg.use_quant_conv else None
-    self.post_quant_conv = nn.Conv2d(lc, lc, 1) if self.cfg.use_post_quant_conv else None
+    self.quant_conv = Conv2d(2 * lc, 2 * lc, 1) if self.cfg.use_quant_conv else None
+    self.post_quant_conv = Conv2d(lc, lc, 1) if self.cfg.use_post_quant_conv else None
 
   def encode(self, x) -> DiagonalGaussianDistribution:
     h = self.encoder(x)

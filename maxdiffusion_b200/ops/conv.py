@@ -37,9 +37,24 @@ def _declare(L):
   L.mdb_rms_act_cl.argtypes = [c_void_p, c_ll, c_void_p, c_ll, c_void_p, c_void_p, c_ll, c_int, ctypes.c_float, c_int,
                                c_void_p]
   L.mdb_rms_act_cl.restype = c_int
+  L.mdb_conv_igemm_tune.argtypes = [c_int, c_int, c_int]
+  L.mdb_conv_igemm_tune.restype = c_int
+  L.mdb_conv_wgrad.argtypes = [c_void_p, c_void_p, c_void_p, c_ll, c_ll, c_int, c_int, c_int, llp, c_int, c_void_p]
+  L.mdb_conv_wgrad.restype = c_int
+  L.mdb_gn_cl_sums.argtypes = [c_void_p] * 5 + [c_int] * 4 + [c_void_p]
+  L.mdb_gn_cl_sums.restype = c_int
+  L.mdb_gn_cl_apply.argtypes = [c_void_p] * 8 + [c_int] * 4 + [c_void_p]
+  L.mdb_gn_cl_apply.restype = c_int
 
 
 _lib.register(_declare)
+
+
+def tune(units_per_stage: int = 0, max_stages: int = 0, ctas_per_sm: int = 0) -> None:
+  """Pins the launch shape of the implicit-GEMM convolution (0 = the launcher's own choice): (tap, channel block)
+  units per pipeline stage, an upper limit on the stages, CTAs per SM (2 applies to tiles of at most 128 output
+  channels). For the tile search and the benchmarks."""
+  _lib.check(_lib.lib().mdb_conv_igemm_tune(int(units_per_stage), int(max_stages), int(ctas_per_sm)), "mdb_conv_igemm_tune")
 
 
 def use_kernel(x: torch.Tensor) -> bool:
@@ -155,7 +170,9 @@ def pack_conv2d_dgrad(weight: torch.Tensor, stride: int = 1, pad_top_left: Optio
   if stride == 1:
     # dX[i] = sum_a dY[i + p - a] W[a]
     taps = [[(0, p - b, p - a, 0, 0) for a in range(kh) for b in range(kw)]]
-    return _pack(wt.reshape(ci, kh * kw, co), None, taps, "conv2d")
+    pk = _pack(wt.reshape(ci, kh * kw, co), None, taps, "conv2d_dgrad_s1")
+    pk.src = (weight, None, 1, p)
+    return pk
   assert stride == 2
   # input row 2*u + r receives dY[u + (r + p - a) / 2] W[a] for the a with (r + p - a) even
   mats, taps = [], []
@@ -171,7 +188,9 @@ def pack_conv2d_dgrad(weight: torch.Tensor, stride: int = 1, pad_top_left: Optio
           mats.append(wt[:, a, b, :])
           cls.append((0, (rw + p - b) // 2, (rh + p - a) // 2, 0, 0))
       taps.append(cls)
-  return _pack(torch.stack(mats, dim=1), None, taps, "conv2d_dgrad_s2")
+  pk = _pack(torch.stack(mats, dim=1), None, taps, "conv2d_dgrad_s2")
+  pk.src = (weight, None, 2, p)
+  return pk
 
 
 def _pick_box(e1: int, e2: int, e3: int, allow3: bool):
@@ -261,7 +280,7 @@ def conv2d(x: torch.Tensor, pk: PackedConv, residual: Optional[torch.Tensor] = N
   _check_cl(x, pk.c_in)
   B, H, W, C = x.shape
   n = pk.n_pad
-  if pk.kind == "conv2d":
+  if pk.kind in ("conv2d", "conv2d_dgrad_s1"):
     out = torch.empty((B, H, W, n), dtype=x.dtype, device=x.device)
     box = _pick_box(W, H, B, True)
     dims, strides = [C, W, H, B, 1], [x.stride(2), x.stride(1), x.stride(0), x.stride(0) * B]
@@ -305,11 +324,77 @@ def upsample2x_conv2d(x: torch.Tensor, pk: PackedConv) -> torch.Tensor:
 
 def conv2d_dgrad(dy: torch.Tensor, pk: PackedConv) -> torch.Tensor:
   """dX for a conv2d whose weights were packed with `pack_conv2d_dgrad` (dy is [B, Ho, Wo, Co], channels-last)."""
+  if not use_kernel(dy):
+    w, _, stride, p = pk.src
+    B, Ho, Wo, _ = dy.shape
+    H, W = Ho * stride, Wo * stride
+    far = max((Ho - 1) * stride + w.shape[2] - H - p, 0)
+    g = torch.nn.grad.conv2d_input((B, w.shape[1], H + p + far, W + p + far), w.float(), dy.float().permute(0, 3, 1, 2)[..., :, :],
+                                   stride=stride)
+    return g[:, :, p:p + H, p:p + W].permute(0, 2, 3, 1).to(dy.dtype)
   if pk.kind == "conv2d_dgrad_s2":
     if any(len(c) == 0 for c in pk.taps):
       raise ValueError("a 1x1 stride-2 convolution leaves input parities without a tap; use the dense fallback")
     return _parity_conv(dy, pk)
   return conv2d(dy, pk)
+
+
+def wgrad_plan(H: int, W: int, k: int, stride: int, pad: int):
+  """How the weight gradient sees its operands: (planes, Hg, Wg, taps) with `planes` the (row parity, column parity)
+  sub-grids of X that are stacked (one for stride 1), Hg x Wg the pixel grid shared by dY and every plane (bordered
+  by one ring of zeros), and per kernel tap (plane index, row shift, column shift)."""
+  if stride == 1:
+    return [(0, 0)], H, W, [(0, a - pad, b - pad) for a in range(k) for b in range(k)]
+  planes = [(ph, pw) for ph in (0, 1) for pw in (0, 1)]
+  taps = []
+  for a in range(k):
+    dh, ph = divmod(a - pad, 2)
+    for b in range(k):
+      dw, pw = divmod(b - pad, 2)
+      taps.append((planes.index((ph, pw)), dh, dw))
+  return planes, H // 2, W // 2, taps
+
+
+def conv2d_wgrad(x: torch.Tensor, dy: torch.Tensor, k: int = 3, stride: int = 1, pad: int = 1) -> torch.Tensor:
+  """dW [Co, Ci, k, k] (fp32) of a conv2d from x [B, H, W, Ci] and dy [B, Ho, Wo, Co], both channels-last."""
+  B, H, W, Ci = x.shape
+  Co = dy.shape[-1]
+  if not use_kernel(x) and _wgrad_launch is _wgrad_launch_kernel:
+    xn = x.float().permute(0, 3, 1, 2)
+    Ho, Wo = dy.shape[1:3]
+    far_h, far_w = (Ho - 1) * stride + k - H - pad, (Wo - 1) * stride + k - W - pad
+    xn = F.pad(xn, (pad, max(far_w, 0), pad, max(far_h, 0)))
+    return torch.nn.grad.conv2d_weight(xn, (Co, Ci, k, k), dy.float().permute(0, 3, 1, 2), stride=stride)
+  planes, Hg, Wg, taps = wgrad_plan(H, W, k, stride, pad)
+  assert dy.shape[1:3] == (Hg, Wg), (dy.shape, Hg, Wg)
+  ci8, co8 = _round_up(Ci, 8), _round_up(Co, 8)
+  ring = lambda t: F.pad(t, (0, 0, 1, 1, 1, 1))  # one zero pixel around every image
+  dyp = ring(pad_channels(dy, co8)).reshape(-1, co8)
+  if stride == 1:
+    xp = ring(pad_channels(x, ci8)).reshape(-1, ci8)
+  else:
+    xp = torch.stack([ring(pad_channels(x[:, ph::2, pw::2], ci8)) for ph, pw in planes]).reshape(-1, ci8)
+  rows = dyp.shape[0]
+  offs = [pl * rows + dh * (Wg + 2) + dw for pl, dh, dw in taps]
+  kb = (rows + 63) // 64
+  items = len(taps) * ((co8 + 127) // 128) * max(1, (ci8 + 255) // 256)
+  splits = max(1, min(kb, (2 * 148 + items - 1) // items))
+  out = _wgrad_launch(dyp, xp, offs, splits)
+  dw = out.sum(dim=1)[:, :Co, :Ci]  # [taps, Co, Ci], splits added in a fixed order
+  return dw.reshape(k, k, Co, Ci).permute(2, 3, 0, 1)
+
+
+def _wgrad_launch_kernel(dyp, xp, offs, splits):
+  """out[tap, split] = sum over the split's rows r of dyp[r, :]^T x xp[r + offs[tap], :] (rows outside xp are zeros)."""
+  out = torch.empty((len(offs), splits, dyp.shape[1], xp.shape[1]), dtype=torch.float32, device=dyp.device)
+  arr = (ctypes.c_longlong * len(offs))(*offs)
+  rc = _lib.lib().mdb_conv_wgrad(_lib.ptr(dyp), _lib.ptr(xp), _lib.ptr(out), dyp.shape[0], xp.shape[0], dyp.shape[1],
+                                 xp.shape[1], len(offs), arr, splits, _lib.stream())
+  _lib.check(rc, "mdb_conv_wgrad")
+  return out
+
+
+_wgrad_launch = _wgrad_launch_kernel
 
 
 def rms_act(x: torch.Tensor, gamma: torch.Tensor, beta: Optional[torch.Tensor] = None, silu: bool = True,
@@ -329,6 +414,71 @@ def rms_act(x: torch.Tensor, gamma: torch.Tensor, beta: Optional[torch.Tensor] =
                                  int(silu), _lib.stream())
   _lib.check(rc, "mdb_rms_act_cl")
   return y
+
+
+# ---------------------------------------------------------------------------------------------
+# GroupNorm (+ SiLU) on channels-last tensors [N, HW, C]: kernels for the two streaming passes, the fold between
+# them (group statistics -> per-(n, c) coefficients) on [N, C]-sized arrays.
+# ---------------------------------------------------------------------------------------------
+def _gn_splits(n: int, hw: int) -> int:
+  """Strips of pixels per image so that the sums pass fills the GPU (about 4 CTAs per SM) without tiny strips."""
+  return max(1, min((4 * 148 + n - 1) // n, (hw + 63) // 64))
+
+
+def _gn_sums(x3, dy3=None, act_a=None, act_b=None):
+  N, HW, C = x3.shape
+  S = _gn_splits(N, HW)
+  partial = torch.empty((N, S, C, 2), device=x3.device, dtype=torch.float32)
+  rc = _lib.lib().mdb_gn_cl_sums(_lib.ptr(x3), _lib.ptr(dy3), _lib.ptr(act_a), _lib.ptr(act_b), _lib.ptr(partial), N, HW, C, S,
+                                 _lib.stream())
+  _lib.check(rc, "mdb_gn_cl_sums")
+  return partial.sum(dim=1)  # [N, C, 2], fixed order
+
+
+def _gn_apply(x3, dy3, ca, cb, cc, fa, fb, act):
+  N, HW, C = x3.shape
+  out = torch.empty_like(x3)
+  rc = _lib.lib().mdb_gn_cl_apply(_lib.ptr(x3), _lib.ptr(dy3), _lib.ptr(out), _lib.ptr(ca), _lib.ptr(cb), _lib.ptr(cc),
+                                  _lib.ptr(fa), _lib.ptr(fb), N, HW, C, int(act), _lib.stream())
+  _lib.check(rc, "mdb_gn_cl_apply")
+  return out
+
+
+def group_norm_cl_fwd(x3: torch.Tensor, groups: int, gamma, beta, eps: float, act: bool):
+  """x3 [N, HW, C] bf16 contiguous -> (y, a, b, mean, rstd): y = act(x * a + b) with a, b fp32 [N, C]."""
+  N, HW, C = x3.shape
+  cg = C // groups
+  s = _gn_sums(x3).view(N, groups, cg, 2).sum(dim=2)  # [N, G, 2]
+  m = float(HW * cg)
+  mean = s[..., 0] / m
+  rstd = torch.rsqrt((s[..., 1] / m - mean * mean).clamp_min(0.0) + eps)
+  g = gamma.float().view(1, groups, cg) if gamma is not None else torch.ones((1, groups, cg), device=x3.device)
+  a = (rstd.unsqueeze(-1) * g)
+  b = -mean.unsqueeze(-1) * a
+  if beta is not None:
+    b = b + beta.float().view(1, groups, cg)
+  a, b = a.reshape(N, C).contiguous(), b.reshape(N, C).contiguous()
+  return _gn_apply(x3, None, a, b, None, None, None, act), a, b, mean, rstd
+
+
+def group_norm_cl_bwd(dy3, x3, groups: int, gamma, a, b, mean, rstd, act: bool):
+  """Returns (dx, dgamma fp32 [C], dbeta fp32 [C]) for y = act(groupnorm(x) * gamma + beta)."""
+  N, HW, C = x3.shape
+  cg = C // groups
+  d = _gn_sums(x3, dy3, a if act else None, b if act else None)   # per channel: sum dy', sum dy' * x
+  d1, d2 = d[..., 0].view(N, groups, cg), d[..., 1].view(N, groups, cg)
+  mean_, rstd_ = mean.unsqueeze(-1), rstd.unsqueeze(-1)
+  dxhat = rstd_ * (d2 - mean_ * d1)              # sum dy' * xhat per channel
+  g = gamma.float().view(1, groups, cg) if gamma is not None else torch.ones((1, groups, cg), device=x3.device)
+  m = float(HW * cg)
+  s1 = (g * d1).sum(dim=2, keepdim=True) / m     # mean over the group of dy' * gamma
+  s2 = (g * dxhat).sum(dim=2, keepdim=True) / m  # mean over the group of dy' * gamma * xhat
+  cc = (-rstd_ * rstd_ * s2).expand(N, groups, cg)
+  cb = (-rstd_ * s1 + mean_ * rstd_ * rstd_ * s2).expand(N, groups, cg)
+  ca = rstd_ * g
+  dx = _gn_apply(x3, dy3, ca.reshape(N, C).contiguous(), cb.reshape(N, C).contiguous(), cc.reshape(N, C).contiguous(),
+                 a if act else None, b if act else None, False)
+  return dx, dxhat.sum(dim=0).reshape(C), d1.sum(dim=0).reshape(C)
 
 
 # ---------------------------------------------------------------------------------------------

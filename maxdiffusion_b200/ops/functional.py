@@ -20,6 +20,7 @@ from typing import Sequence
 import torch
 import torch.nn.functional as F
 
+from . import conv as OC
 from . import kernels as K
 from . import ref
 
@@ -508,12 +509,137 @@ class _GroupNormFn(torch.autograd.Function):
             dbeta.to(beta.dtype) if beta is not None else None, None, None, None)
 
 
+class _GroupNormCLFn(torch.autograd.Function):
+  """GroupNorm (+ SiLU) of an NCHW tensor held in channels-last memory, on the channels-last kernels."""
+
+  @staticmethod
+  def forward(ctx, x, gamma, beta, groups, eps, act):
+    N, C, H, W = x.shape
+    x3 = x.permute(0, 2, 3, 1).reshape(N, H * W, C)  # a view: the memory is [N, H, W, C]
+    y3, a, b, mean, rstd = OC.group_norm_cl_fwd(x3, groups, gamma, beta, eps, act)
+    ctx.save_for_backward(x3, gamma, a, b, mean, rstd)
+    ctx.groups, ctx.act, ctx.shape = groups, act, (N, C, H, W)
+    ctx.has_beta = beta is not None
+    return y3.view(N, H, W, C).permute(0, 3, 1, 2)
+
+  @staticmethod
+  def backward(ctx, dy):
+    x3, gamma, a, b, mean, rstd = ctx.saved_tensors
+    N, C, H, W = ctx.shape
+    dy3 = dy.contiguous(memory_format=torch.channels_last).permute(0, 2, 3, 1).reshape(N, H * W, C)
+    dx3, dgamma, dbeta = OC.group_norm_cl_bwd(dy3, x3, ctx.groups, gamma, a, b, mean, rstd, ctx.act)
+    return (dx3.view(N, H, W, C).permute(0, 3, 1, 2), dgamma.to(gamma.dtype) if gamma is not None else None,
+            dbeta.to(gamma.dtype) if (ctx.has_beta and gamma is not None) else None, None, None, None)
+
+
+def _is_channels_last(x: torch.Tensor) -> bool:
+  return x.dim() == 4 and x.shape[1] > 1 and x.is_contiguous(memory_format=torch.channels_last) and not x.is_contiguous()
+
+
 def group_norm(x, groups: int, gamma=None, beta=None, eps: float = 1e-6, act: bool = False):
-  """GroupNorm over a channels-first tensor [N, C, *spatial] with optional fused SiLU."""
+  """GroupNorm over a channels-first tensor [N, C, *spatial] with optional fused SiLU. A 4-D bf16 tensor in
+  channels-last memory (what `conv2d` produces) stays in that layout."""
+  if _fast(x) and _is_channels_last(x) and x.shape[1] % 8 == 0 and x.shape[1] <= 2048:
+    return _GroupNormCLFn.apply(x, gamma, beta, groups, eps, act)
   if x.is_cuda and x.dtype in (torch.bfloat16, torch.float32) and not _LIBRARY_MODE:
     x = x if x.is_contiguous() else x.contiguous()
     return _GroupNormFn.apply(x, gamma, beta, groups, eps, act)
   return ref.group_norm(x, groups, gamma, beta, eps, act)
+
+
+# ---------------------------------------------------------------------------------------------
+# conv2d (NCHW interface, channels-last memory, implicit-GEMM kernels)
+# ---------------------------------------------------------------------------------------------
+_PACKED: dict = {}
+
+
+def _packed(weight: torch.Tensor, bias, kind: str, make):
+  """Packed form of a convolution weight, re-packed when the parameter changes (optimizer step, load)."""
+  key = (id(weight), kind)
+  ver = (weight.data_ptr(), weight._version, None if bias is None else bias._version)
+  hit = _PACKED.get(key)
+  if hit is None or hit[0] != ver or hit[2]() is not weight:
+    import weakref
+
+    if len(_PACKED) > 4096:
+      _PACKED.clear()
+    hit = (ver, make(), weakref.ref(weight))
+    _PACKED[key] = hit
+  return hit[1]
+
+
+class _Conv2dFn(torch.autograd.Function):
+  """3x3 convolution, stride 1 or 2, optionally preceded by a nearest-2x up-sampling (fused), on channels-last memory.
+  Forward and input gradient run on the implicit-GEMM kernel; the weight gradient on `ops.conv.conv2d_wgrad`."""
+
+  @staticmethod
+  def forward(ctx, x, weight, bias, stride, pad, upsample):
+    N, C, H, W = x.shape
+    xc = x.contiguous(memory_format=torch.channels_last).permute(0, 2, 3, 1)  # [N, H, W, C], dense
+    if upsample:
+      pk = _packed(weight, bias, "up", lambda: OC.pack_upsample_conv2d(weight.detach(), None if bias is None else bias.detach()))
+      y = OC.upsample2x_conv2d(OC.pad_channels(xc, pk.c_in), pk)
+    else:
+      pk = _packed(weight, bias, f"s{stride}p{pad}", lambda: OC.pack_conv2d(weight.detach(), None if bias is None else bias.detach(),
+                                                                           stride=stride, pad_top_left=pad))
+      y = OC.conv2d(OC.pad_channels(xc, pk.c_in), pk)
+    ctx.save_for_backward(xc, weight)
+    ctx.cfg = (stride, pad, upsample, bias is not None)
+    return y.permute(0, 3, 1, 2)
+
+  @staticmethod
+  def backward(ctx, dy):
+    xc, weight = ctx.saved_tensors
+    stride, pad, upsample, has_bias = ctx.cfg
+    dyc = dy.contiguous(memory_format=torch.channels_last).permute(0, 2, 3, 1)  # [N, Ho, Wo, Co]
+    co, ci = weight.shape[:2]
+    dx = dw = db = None
+    if ctx.needs_input_grad[0]:
+      if upsample:
+        pk = _packed(weight, None, "dgrad_s1p1", lambda: OC.pack_conv2d_dgrad(weight.detach(), 1, 1))
+        du = OC.conv2d_dgrad(OC.pad_channels(dyc, pk.c_in), pk)[..., :ci]  # gradient of the up-sampled image
+        n, h2, w2, _ = du.shape
+        dxc = du.reshape(n, h2 // 2, 2, w2 // 2, 2, ci).float().sum(dim=(2, 4)).to(du.dtype)
+      else:
+        pk = _packed(weight, None, f"dgrad_s{stride}p{pad}", lambda: OC.pack_conv2d_dgrad(weight.detach(), stride, pad))
+        dxc = OC.conv2d_dgrad(OC.pad_channels(dyc, pk.c_in), pk)[..., :ci]
+      dx = dxc.permute(0, 3, 1, 2)
+    if ctx.needs_input_grad[1]:
+      xin = xc
+      if upsample:
+        n, h, w, c = xc.shape
+        xin = xc.reshape(n, h, 1, w, 1, c).expand(n, h, 2, w, 2, c).reshape(n, 2 * h, 2 * w, c)
+      dw = OC.conv2d_wgrad(xin, dyc, weight.shape[2], stride, pad).to(weight.dtype)
+    if has_bias and ctx.needs_input_grad[2]:
+      db = K.colsum(dyc.reshape(-1, co)).to(weight.dtype) if co % 8 == 0 else dyc.float().sum(dim=(0, 1, 2)).to(weight.dtype)
+    return dx, dw, db, None, None, None
+
+
+def conv2d(x, weight, bias=None, stride: int = 1, padding=1, upsample: bool = False):
+  """2-D convolution of an NCHW tensor. `padding` is an int (all sides) or "far" (zero rows / columns after the image
+  only: the VAE's stride-2 down-sampling). With `upsample` the input is nearest-2x up-sampled first (fused).
+
+  CUDA bf16 3x3 convolutions run on the implicit-GEMM kernels and return channels-last memory; 1x1 convolutions are
+  GEMMs over the pixel rows; everything else is `torch.nn.functional.conv2d`."""
+  k = weight.shape[-1]
+  pad_tl = 0 if padding == "far" else int(padding)
+  co, ci = weight.shape[:2]
+  if _fast(x) and k == 1 and stride == 1 and pad_tl == 0 and not upsample and ci % 8 == 0 and co % 8 == 0:
+    n, c, h, w = x.shape
+    rows = x.contiguous(memory_format=torch.channels_last).permute(0, 2, 3, 1).reshape(n, h * w, c)
+    y = linear(rows, weight.reshape(co, ci), bias)
+    return y.view(n, h, w, co).permute(0, 3, 1, 2)
+  even = x.shape[2] % 2 == 0 and x.shape[3] % 2 == 0
+  if (_fast(x) and k == 3 and stride in (1, 2) and (stride == 1 or even) and
+      ((stride == 1 and pad_tl == 1) or (stride == 2 and pad_tl in (0, 1)))):
+    if weight.dtype != torch.bfloat16:
+      weight = weight.to(torch.bfloat16)
+    return _Conv2dFn.apply(x, weight, bias, stride, pad_tl, upsample)
+  if upsample:
+    x = F.interpolate(x, scale_factor=2.0, mode="nearest")
+  if padding == "far":
+    x = F.pad(x, (0, 1, 0, 1))
+  return F.conv2d(x, weight.to(x.dtype), None if bias is None else bias.to(x.dtype), stride=stride, padding=pad_tl)
 
 
 def lincomb(xs, coefs, out_dtype=None):

@@ -90,7 +90,7 @@ class _SegmentAttentionFn(torch.autograd.Function):
   """Kernel path of gather/ring attention: local q against the stacked K/V shards [n, B, S_loc, H, D]."""
 
   @staticmethod
-  def forward(ctx, q, k, v, scale, group, valid_lens, exchange, reducer=None, fixed_m=None):
+  def forward(ctx, q, k, v, scale, group, valid_lens, exchange, reducer=None, fixed_m=None, save_kv=True):
     state = OF._remat
     saved = None
     if state.mode == "replay":
@@ -120,12 +120,23 @@ class _SegmentAttentionFn(torch.autograd.Function):
       if state.mode == "record":
         state.store.append((out, lse))
     ctx.scale, ctx.group, ctx.valid_lens, ctx.order, ctx.reducer = scale, group, lens, order, reducer
-    ctx.save_for_backward(q, out, lse, kg, vg)
+    ctx.save_kv, ctx.exchange = save_kv, exchange
+    if save_kv:
+      ctx.save_for_backward(q, out, lse, kg, vg)
+    else:
+      # only this rank's shard waits for the backward pass: the K/V memory of a layer then shrinks with the context
+      # axis; the other shards are fetched again when the backward needs them
+      ctx.save_for_backward(q, out, lse, k, v)
     return out
 
   @staticmethod
   def backward(ctx, d_o):
     q, out, lse, kg, vg = ctx.saved_tensors
+    if not ctx.save_kv:
+      if ctx.exchange is not None:
+        kg, vg = ctx.exchange.gather(kg.contiguous(), vg.contiguous())
+      else:
+        kg, vg = C.all_gather_stack(kg, ctx.group), C.all_gather_stack(vg, ctx.group)
     n = kg.shape[0]
     lens = ctx.valid_lens
     if d_o.stride(-1) != 1:
@@ -163,7 +174,7 @@ class _SegmentAttentionFn(torch.autograd.Function):
       dq = K.flash_bwd_dq(q, d_o, ks, vs, lse, delta, ctx.scale)
       main.wait_event(reduced)
       both.record_stream(main)
-      return dq, both[0], both[1], None, None, None, None, None, None
+      return dq, both[0], both[1], None, None, None, None, None, None, None
     dq = K.flash_bwd_dq(q, d_o, ks, vs, lse, delta, ctx.scale)
     dkg, dvg = torch.empty_like(kg), torch.empty_like(vg)
     for i in range(n):
@@ -182,7 +193,7 @@ class _SegmentAttentionFn(torch.autograd.Function):
         dvg[ctx.order[i]][:, :lens[i]].copy_(dv)
     dk = C.reduce_scatter_stack(dkg, ctx.group)
     dv = C.reduce_scatter_stack(dvg, ctx.group)
-    return dq, dk, dv, None, None, None, None, None, None
+    return dq, dk, dv, None, None, None, None, None, None, None
 
 
 class ContextParallel:
@@ -191,10 +202,14 @@ class ContextParallel:
   `mesh` is a `parallel.mesh.DeviceMesh`; `strategy` one of local / gather / ring / ulysses / usp.
   """
 
-  def __init__(self, mesh, strategy: str = "ring", peer_memory: bool = False, fixed_m: bool = False):
+  def __init__(self, mesh, strategy: str = "ring", peer_memory: bool = False, fixed_m: bool = False,
+               save_remote_kv: bool = True):
     self.mesh = mesh
     self.strategy = strategy
     self.peer_memory = peer_memory
+    # ring / gather attention: keep every rank's K/V of a layer for its backward (fastest), or keep the own shard only
+    # and fetch the others again in the backward (K/V memory per layer then falls with the context axis)
+    self.save_remote_kv = save_remote_kv
     # fixed-exponent softmax (`ops.fixed_m`): keys are smoothed where a rank sees the whole key sequence (local,
     # Ulysses); ring segments stay unsmoothed and take the halved gate, with the key norms max-reduced over the ring
     self.fixed_m = fixed_m
@@ -330,7 +345,7 @@ class ContextParallel:
       if self.fixed_m:
         # padded tail rows of the own shard are zeros and do not raise the norm maximum
         fixed = FM.plan(q, k, scale, smoothed=False, group=group)
-      return _SegmentAttentionFn.apply(q, k, v, scale, group, tuple(valid_lens), ex, rs, fixed)
+      return _SegmentAttentionFn.apply(q, k, v, scale, group, tuple(valid_lens), ex, rs, fixed, self.save_remote_kv)
     kg = _GatherSeq.apply(k, group)
     vg = _GatherSeq.apply(v, group)
     ks = [kg[i][:, :valid_lens[i]] for i in range(n)]

@@ -234,7 +234,7 @@ def bench_conv(results):
   from maxdiffusion_b200.ops import conv as OC
 
   tf_peak, bw_peak, tag = peaks()
-  cases3d = [(1, 4, 720, 1280, 96, 96), (1, 4, 360, 640, 192, 192), (1, 2, 180, 320, 384, 384), (1, 1, 90, 160, 384, 384),
+  cases3d = [(1, 4, 720, 1280, 64, 64), (1, 4, 720, 1280, 128, 128), (1, 4, 720, 1280, 96, 96), (1, 4, 360, 640, 192, 192), (1, 2, 180, 320, 384, 384), (1, 1, 90, 160, 384, 384),
              (1, 4, 720, 1280, 96, 3)]
   for B, T, H, W, Ci, Co in cases3d:
     x = torch.randn((B, T, H, W, Ci), device="cuda", dtype=torch.bfloat16)
@@ -252,6 +252,18 @@ def bench_conv(results):
                         frac=fl / med / 1e9 / tf_peak, of=tag, gbs=byts / med / 1e6, cudnn_ms=lib))
     print(results[-1], flush=True)
     del x, hist, xn
+  # launch shapes of the narrow-tile convolutions: (units per stage, stage limit, CTAs per SM); (0, 0, 0) is the default
+  for Ci in (96, 128):
+    x = torch.randn((1, 4, 720, 1280, Ci), device="cuda", dtype=torch.bfloat16)
+    pk = OC.pack_conv3d(torch.randn((Ci, Ci, 3, 3, 3), device="cuda", dtype=torch.bfloat16) * 0.02, None)
+    for cfg in ((0, 0, 0), (2, 0, 1), (1, 0, 1), (1, 0, 2), (2, 0, 2), (1, 2, 2)):
+      OC.tune(*cfg)
+      med, best = time_ms(lambda: OC.conv3d_causal(x, pk), iters=5)
+      results.append(dict(kernel="conv3d_causal_igemm_tuning", shape=[1, 4, 720, 1280, Ci, Ci], tune=list(cfg), ms=med,
+                          tflops=2.0 * 4 * 720 * 1280 * Ci * Ci * 27 / med / 1e9))
+      print(results[-1], flush=True)
+    OC.tune(0, 0, 0)
+    del x
   cases2d = [(8, 128, 128, 320, 320, "s1"), (8, 64, 64, 640, 640, "s1"), (8, 32, 32, 1280, 1280, "s1"),
              (8, 128, 128, 320, 320, "s2"), (4, 360, 640, 192, 96, "up"), (8, 64, 64, 640, 640, "dgrad")]
   for B, H, W, Ci, Co, kind in cases2d:

@@ -66,6 +66,7 @@ def _emulate(x, x_alt, pk, dims, strides, alt_dims, alt_strides, box, ext, out, 
 def emulated(monkeypatch):
   monkeypatch.setattr(OC, "_launch", _emulate)
   monkeypatch.setattr(OC, "_check_cl", lambda x, c: None)
+  monkeypatch.setattr(OC, "use_kernel", lambda x: True)  # CPU tensors take the kernel path, into the emulator
 
 
 def _rand(shape, seed, scale=1.0):
@@ -131,3 +132,48 @@ def test_box_choice_covers_with_least_padding():
   b = OC._pick_box(8, 8, 4, True)
   assert b == (8, 8, 2)
   assert OC._pick_box(8, 8, 4, False)[2] == 1
+
+
+def _emulate_wgrad(dyp, xp, offs, splits):
+  """The wgrad kernel's contract, literally: rows of xp outside [0, rows) are zeros; K is cut into `splits` ranges of
+  64-row blocks."""
+  rows = dyp.shape[0]
+  kb = (rows + 63) // 64
+  per = (kb + splits - 1) // splits
+  out = torch.zeros((len(offs), splits, dyp.shape[1], xp.shape[1]))
+  for t, off in enumerate(offs):
+    idx = torch.arange(rows) + off
+    ok = (idx >= 0) & (idx < xp.shape[0])
+    shifted = torch.zeros((rows, xp.shape[1]))
+    shifted[ok] = xp[idx[ok]].float()
+    for s_ in range(splits):
+      r0, r1 = min(rows, s_ * per * 64), min(rows, (s_ + 1) * per * 64)
+      out[t, s_] = dyp[r0:r1].float().t() @ shifted[r0:r1]
+  return out
+
+
+@pytest.mark.parametrize("stride,pad", [(1, 1), (2, 1), (2, 0)])
+def test_wgrad_description(monkeypatch, stride, pad):
+  monkeypatch.setattr(OC, "_wgrad_launch", _emulate_wgrad)
+  monkeypatch.setattr(OC, "use_kernel", lambda x: True)
+  x = _rand((2, 6, 8, 16), 1).float().requires_grad_(False)
+  w = _rand((8, 16, 3, 3), 2, 0.1).float().requires_grad_(True)
+  y = OC.ref_conv2d(x, w, None, stride=stride, pad_top_left=pad)
+  dy = _rand(tuple(y.shape), 3)
+  (y * dy.float()).sum().backward()
+  got = OC.conv2d_wgrad(x.to(torch.bfloat16), dy, 3, stride, pad)
+  assert got.shape == w.shape
+  assert (got - w.grad).abs().max() <= 2e-2 * w.grad.abs().max()
+
+
+def test_cpu_reference_paths_of_the_conv_ops():
+  """Without a GPU the ops run PyTorch convolutions; dgrad and wgrad must then equal autograd."""
+  for stride, pad in ((1, 1), (2, 1), (2, 0)):
+    x = _rand((1, 6, 8, 16), 1).float().requires_grad_(True)
+    w = _rand((8, 16, 3, 3), 2, 0.1).float().requires_grad_(True)
+    y = OC.ref_conv2d(x, w, None, stride=stride, pad_top_left=pad)
+    dy = torch.randn(y.shape)
+    (y * dy).sum().backward()
+    _close(OC.conv2d_dgrad(dy, OC.pack_conv2d_dgrad(w.detach(), stride=stride, pad_top_left=pad)), x.grad)
+    got = OC.conv2d_wgrad(x.detach(), dy, 3, stride, pad)
+    assert (got - w.grad).abs().max() <= 1e-4 * (1 + w.grad.abs().max())

@@ -152,3 +152,78 @@ def test_wan_vae_decode_on_the_conv_kernels_matches_the_pytorch_modules():
   for g in (got, got2):
     err = (g.float() - want).abs()
     assert err.max() < 0.08 and err.mean() < 0.01, (err.max().item(), err.mean().item())
+
+
+@pytest.mark.parametrize("stride,pad", [(1, 1), (2, 1), (2, 0)])
+@pytest.mark.parametrize("B,H,W,Ci,Co", [(2, 12, 20, 64, 96), (1, 34, 18, 320, 320), (3, 16, 16, 8, 640)])
+def test_conv2d_wgrad_matches_autograd(B, H, W, Ci, Co, stride, pad):
+  from maxdiffusion_b200.ops import conv as OC
+
+  x = _rand((B, H, W, Ci), 1)
+  w = _rand((Co, Ci, 3, 3), 2, scale=(9 * Ci) ** -0.5).float().requires_grad_(True)
+  y = OC.ref_conv2d(x, w, None, stride=stride, pad_top_left=pad)
+  dy = _rand(tuple(y.shape), 3)
+  (y * dy.float()).sum().backward()
+  got = OC.conv2d_wgrad(x, dy, 3, stride, pad)
+  assert got.shape == w.shape
+  _close(got, w.grad)
+  assert torch.equal(got, OC.conv2d_wgrad(x, dy, 3, stride, pad))  # fixed summation order
+
+
+@pytest.mark.parametrize("C,groups,HW", [(320, 32, (16, 24)), (64, 8, (9, 7)), (1280, 32, (8, 8)), (128, 32, (33, 5))])
+@pytest.mark.parametrize("act", [False, True])
+def test_group_norm_channels_last_fwd_bwd(C, groups, HW, act):
+  from maxdiffusion_b200.ops import functional as OF
+
+  H, W = HW
+  torch.manual_seed(0)
+  x = (torch.randn(3, C, H, W, device="cuda") * 2 + 0.5).to(torch.bfloat16).contiguous(memory_format=torch.channels_last)
+  gamma = (torch.rand(C, device="cuda") + 0.5).to(torch.bfloat16)
+  beta = (torch.randn(C, device="cuda") * 0.2).to(torch.bfloat16)
+  xr = x.float().requires_grad_(True)
+  gr, br = gamma.float().requires_grad_(True), beta.float().requires_grad_(True)
+  want = torch.nn.functional.group_norm(xr, groups, gr, br, 1e-5)
+  if act:
+    want = torch.nn.functional.silu(want)
+  dy = torch.randn_like(want).to(torch.bfloat16).contiguous(memory_format=torch.channels_last)
+  want.backward(dy.float())
+  xk = x.clone().requires_grad_(True)
+  gk, bk = gamma.clone().requires_grad_(True), beta.clone().requires_grad_(True)
+  got = OF.group_norm(xk, groups, gk, bk, 1e-5, act)
+  assert got.is_contiguous(memory_format=torch.channels_last)
+  got.backward(dy)
+  _close(got, want)
+  _close(xk.grad, xr.grad, tol=3e-2)
+  _close(gk.grad, gr.grad, tol=3e-2)
+  _close(bk.grad, br.grad, tol=3e-2)
+
+
+def test_unet_on_the_conv_kernels_matches_fp32_modules_forward_and_backward():
+  """The tiny SDXL-style UNet in bf16 on the kernel path (channels-last convolutions with dgrad / wgrad kernels,
+  channels-last GroupNorm, flash attention) against the same parameters in fp32 through PyTorch convolutions."""
+  from maxdiffusion_b200.models.unet_2d_condition import UNET_PRESETS, UNet2DConditionModel, UNetConfig
+
+  torch.manual_seed(0)
+  cfg = UNetConfig(**{**UNET_PRESETS["tiny"], "block_out_channels": (64, 128), "attention_head_dim": (1, 2), "norm_num_groups": 8})
+  ref = UNet2DConditionModel(cfg).cuda().float()
+  ker = UNet2DConditionModel(cfg).cuda().to(torch.bfloat16)
+  ker.load_state_dict({k: v.to(torch.bfloat16) for k, v in ref.state_dict().items()})
+  ref.load_state_dict({k: v.float() for k, v in ker.state_dict().items()})  # identical (bf16-representable) weights
+  x = torch.randn(2, 4, 16, 16, device="cuda").to(torch.bfloat16)
+  ctx = torch.randn(2, 7, 32, device="cuda").to(torch.bfloat16)
+  add = {"text_embeds": torch.randn(2, 16, device="cuda").to(torch.bfloat16), "time_ids": torch.zeros(2, 6, device="cuda")}
+  t = torch.tensor([10, 500], device="cuda")
+  want = ref(x.float(), t, ctx.float(), {k: v.float() for k, v in add.items()})
+  got = ker(x, t, ctx, add)
+  _close(got, want, tol=6e-2)
+  g = torch.randn_like(want)
+  want.backward(g)
+  got.backward(g.to(torch.bfloat16))
+  checked = 0
+  for (n, p), (_, q) in zip(ker.named_parameters(), ref.named_parameters()):
+    if p.grad is None or q.grad is None or q.grad.abs().max() == 0:
+      continue
+    rel = ((p.grad.float() - q.grad).norm() / (q.grad.norm() + 1e-12)).item()
+    assert rel < 0.12, (n, rel)
+    checked += 1
+  assert checked > 20

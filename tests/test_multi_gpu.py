@@ -179,7 +179,7 @@ def test_flag_gated_kv_exchange_feeds_flash_attention():
     assert max(errs) < 3e-2
 
 
-def _train(rank, world, peer, attention="tokamax_ring"):
+def _train(rank, world, peer, attention="tokamax_ring", save_kv=True):
   from maxdiffusion_b200 import pyconfig
   from maxdiffusion_b200.parallel.mesh import create_device_mesh
   from maxdiffusion_b200.trainers.wan_trainer import WanTrainer
@@ -189,7 +189,7 @@ def _train(rank, world, peer, attention="tokamax_ring"):
        'wan_config_overrides={"num_layers": 2, "ffn_dim": 1024}', "remat_policy=SAVE_ATTENTION",
        "warmup_steps_fraction=0.0", "log_config=false", "write_metrics=false", f"attention={attention}", "ulysses_shards=2",
        f"per_device_batch_size={1.0 / world}", f"peer_memory_transport={'true' if peer else 'false'}",
-       "stochastic_rounding=false"], unittest=True)
+       "stochastic_rounding=false", f"ring_save_remote_kv={'true' if save_kv else 'false'}"], unittest=True)
   tr = WanTrainer(config, mesh=create_device_mesh(config))
   data = tr.load_dataset()
   return [float(tr.train_step(next(data))["learning/loss"]) for _ in range(3)]
@@ -201,6 +201,16 @@ def test_training_step_peer_transport_matches_nccl():
   a = _spawn(_train, 2, True)[0]
   b = _spawn(_train, 2, False)[0]
   assert a == pytest.approx(b, rel=3e-2, abs=3e-2)
+
+
+def test_training_step_that_refetches_remote_kv_in_the_backward_matches():
+  """`ring_save_remote_kv=false`: only the own K/V shard is kept per layer and the others are pulled again for the
+  backward; the losses of the following steps (which see the updated weights) must not move."""
+  if torch.cuda.device_count() < 2:
+    pytest.skip("needs 2 GPUs")
+  a = _spawn(_train, 2, True, "tokamax_ring", False)[0]
+  b = _spawn(_train, 2, True, "tokamax_ring", True)[0]
+  assert a == pytest.approx(b, rel=1e-3, abs=1e-3)
 
 
 def test_training_step_peer_transport_matches_nccl_on_4_ranks():
