@@ -58,16 +58,55 @@ class FluxTrainer:
     self.model.block_hook = self.engine.block_hook if remat != "NONE" or group is not None else None
     self._no_remat = remat == "NONE"
     self.gen = torch.Generator(device=self.device).manual_seed(seed + 1 + 7919 * self.mesh.rank)
+    self.seed = seed
+    self.vae, self.text_encoders, self.tokenizers = None, (), ()  # set by `attach_encoders` for raw image / caption data
     self.step = 0
     self.batch_size = max(1, int(float(config.get("per_device_batch_size", 1))))
 
   def load_dataset(self):
     cfg = self.model.cfg
-    return SyntheticFluxIterator(self.config, self.batch_size, seed=int(self.config.get("seed", 0)) + 17,
-                                 text_dim=cfg.joint_attention_dim, pooled_dim=cfg.pooled_projection_dim, latent_dim=cfg.in_channels)
+    if str(self.config.get("dataset_type", "synthetic")) == "synthetic":
+      return SyntheticFluxIterator(self.config, self.batch_size, seed=int(self.config.get("seed", 0)) + 17 + self.mesh.rank,
+                                   text_dim=cfg.joint_attention_dim, pooled_dim=cfg.pooled_projection_dim, latent_dim=cfg.in_channels)
+    from ..input_pipeline.input_pipeline_interface import make_data_iterator
+
+    return make_data_iterator(self.config, self.mesh, self.batch_size)
+
+  def attach_encoders(self, vae, clip, t5, clip_tokenizer, t5_tokenizer) -> None:
+    """Frozen VAE and text encoders for datasets of raw images and captions (reference: the encoders are applied in
+    the input pipeline, flux_trainer.py:207-353)."""
+    self.vae, self.text_encoders, self.tokenizers = vae, (clip, t5), (clip_tokenizer, t5_tokenizer)
+
+  @torch.no_grad()
+  def encode_batch(self, batch: dict) -> dict:
+    """pixels + captions -> packed latents, T5 embeddings, CLIP pooled vector, position ids (the synthetic layout)."""
+    if "pixel_values" in batch and batch["pixel_values"].dim() == 3:
+      return batch  # already packed latents
+    from ..models.flux.transformer_flux import pack_latents, prepare_latent_image_ids
+
+    if self.vae is None or not self.text_encoders:
+      raise ValueError("raw image / caption batches need `attach_encoders(vae, clip, t5, tokenizers)` first")
+    vdtype = next(self.vae.parameters()).dtype
+    lat = self.vae.scale_latents(self.vae.encode(batch["pixel_values"].to(self.device, vdtype)).sample(self.gen))
+    packed = pack_latents(lat.float())
+    clip, t5 = self.text_encoders
+    ctok, ttok = self.tokenizers
+    caps = list(batch["captions"])
+    ids = ctok(caps, padding="max_length", max_length=77, truncation=True, return_tensors="pt").input_ids
+    pooled = clip(ids.to(next(clip.parameters()).device)).pooler_output
+    ids2 = ttok(caps, padding="max_length", max_length=int(self.config.get("max_sequence_length", 512)), truncation=True,
+                return_tensors="pt").input_ids
+    emb = t5(ids2.to(next(t5.parameters()).device)).last_hidden_state
+    B, _, lh, lw = lat.shape
+    img_ids = prepare_latent_image_ids(lh // 2, lw // 2, self.device)
+    return {"pixel_values": packed, "text_embeds": emb.float(), "prompt_embeds": pooled.float(),
+            "img_ids": img_ids[None].expand(B, -1, -1), "txt_ids": torch.zeros((B, emb.shape[1], 3), device=self.device)}
 
   def train_step(self, batch: dict) -> dict:
+    batch = self.encode_batch(batch)
     batch = {k: (v.to(self.device, non_blocking=True) if torch.is_tensor(v) else v) for k, v in batch.items()}
+    # the noise / timestep stream is a function of (seed, rank, step): a resumed run continues it exactly
+    self.gen.manual_seed(self.seed + 1 + 7919 * self.mesh.rank + 1000003 * self.step)
     lr = lr_schedule(self.step, float(self.config.learning_rate), int(self.config.learning_rate_schedule_steps),
                      float(self.config.warmup_steps_fraction))
     self.engine.begin_step(lr)
@@ -89,13 +128,22 @@ class FluxTrainer:
     self.step += 1
     return {"learning/loss": loss.detach(), "learning/max_grad_norm": stats["grad_norm"], "learning/current_learning_rate": lr}
 
-  def start_training(self):
-    data = self.load_dataset()
-    writer = MetricsWriter(self.config, self.mesh.rank)
-    while self.step < int(self.config.max_train_steps):
-      t0 = time.perf_counter()
-      m = self.train_step(next(data))
-      loss = float(m["learning/loss"])
-      writer.write(self.step, {**{k: float(v) for k, v in m.items()}, "perf/step_time_seconds": time.perf_counter() - t0})
-    writer.close()
-    return self
+  def checkpointer(self):
+    from ..checkpointing.flux_checkpointer import FluxCheckpointer
+
+    c = self.config
+    if int(c.get("checkpoint_every", -1)) > 0 or c.get("save_final_checkpoint", False):
+      return FluxCheckpointer(c)
+    return None
+
+  def start_training(self, data=None):
+    """Resume -> (cached) data -> steps with metrics -> periodic / final checkpoints (reference: flux_trainer.py:355-468)."""
+    from .loop import EncodedBatchCache, run_training_loop
+
+    def build():
+      it = data if data is not None else self.load_dataset()
+      if self.vae is not None and self.config.get("cache_latents_text_encoder_outputs", True):
+        it = EncodedBatchCache(iter(it), self.encode_batch)
+      return it
+
+    return run_training_loop(self, build, self.checkpointer())

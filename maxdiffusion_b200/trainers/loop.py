@@ -1,0 +1,101 @@
+"""The training loop shared by the Stable Diffusion / SDXL / Dreambooth and Flux trainers: resume from the latest
+checkpoint, data prefetch on a host thread, encoded-batch caching, metrics, periodic and final checkpoints, periodic
+evaluation, and the once-per-step device status check.
+
+Reference: `BaseStableDiffusionTrainer.start_training` / `training_loop`
+(src/maxdiffusion/trainers/base_stable_diffusion_trainer.py:115-197, sdxl_trainer.py:178-291) and the same skeleton in
+`FluxTrainer` (flux_trainer.py:355-468): load or restore state, build the (cached) dataset, loop over steps writing
+metrics, save every `checkpoint_every` steps and at the end.
+"""
+from __future__ import annotations
+
+import time
+from concurrent.futures import ThreadPoolExecutor
+from typing import Callable, Iterator, Optional
+
+import torch
+import torch.distributed as dist
+
+from ..ops import _lib
+from ..train_utils import MetricsWriter
+
+
+class EncodedBatchCache:
+  """Keeps the encoded form of every batch of a FINITE dataset on the host, so that the frozen VAE / text encoders run
+  once per sample and later epochs replay their outputs (the reference caches latents and text-encoder outputs in the
+  dataset itself: `cache_latents_text_encoder_outputs`, input_pipeline_interface.py:60-140)."""
+
+  def __init__(self, source: Iterator[dict], encode: Callable[[dict], dict], max_batches: int = 4096):
+    self.source, self.encode, self.max_batches = source, encode, max_batches
+    self.store: list = []
+    self.replay = False
+    self.pos = 0
+
+  def __iter__(self):
+    return self
+
+  def __next__(self) -> dict:
+    if self.replay:
+      if not self.store:
+        raise StopIteration
+      b = self.store[self.pos % len(self.store)]
+      self.pos += 1
+      return b
+    try:
+      raw = next(self.source)
+    except StopIteration:
+      self.replay, self.pos = True, 0
+      return next(self)
+    enc = {k: (v.detach().to("cpu") if torch.is_tensor(v) else v) for k, v in self.encode(raw).items()
+           if k not in ("pixel_values", "captions", "input_ids", "input_ids_2")}
+    if len(self.store) < self.max_batches:
+      self.store.append(enc)
+    return enc
+
+
+def run_training_loop(trainer, data, checkpointer=None, evaluate: Optional[Callable[[int], dict]] = None):
+  """Drives `trainer.train_step` until `max_train_steps`. `trainer` provides `config`, `mesh`, `step` and `train_step`;
+  `checkpointer` provides `maybe_restore(trainer)` and `save(step, trainer)`. `data` is an iterator of batches or a
+  function that builds one; the function is called AFTER the restore, so that it can start at the restored step."""
+  config = trainer.config
+  max_steps = int(config.max_train_steps)
+  every = int(config.get("checkpoint_every", -1))
+  eval_every = int(config.get("eval_every", -1))
+  if checkpointer is not None:
+    restored = checkpointer.maybe_restore(trainer)
+    if restored is not None:
+      trainer.step = int(restored)
+  if callable(data) and not hasattr(data, "__next__"):
+    data = iter(data())
+  writer = MetricsWriter(config, trainer.mesh.rank)
+  pool = ThreadPoolExecutor(max_workers=1)
+  nxt = pool.submit(lambda: next(data))
+  try:
+    while trainer.step < max_steps:
+      batch = nxt.result()
+      nxt = pool.submit(lambda: next(data))
+      t0 = time.perf_counter()
+      m = trainer.train_step(batch)
+      scalars = {k: float(v) for k, v in m.items()}  # device -> host: ends the step
+      _lib.raise_on_device_status_if_loaded()
+      scalars["perf/step_time_seconds"] = time.perf_counter() - t0
+      writer.write(trainer.step, scalars)
+      if evaluate is not None and eval_every > 0 and trainer.step % eval_every == 0:
+        writer.write(trainer.step, {f"eval/{k}": float(v) for k, v in evaluate(trainer.step).items()})
+      if checkpointer is not None and every > 0 and trainer.step % every == 0:
+        _save(checkpointer, trainer)
+    if checkpointer is not None and config.get("save_final_checkpoint", False) and (every <= 0 or trainer.step % every != 0):
+      _save(checkpointer, trainer)
+  finally:
+    writer.close()
+    pool.shutdown(wait=False, cancel_futures=True)
+    if checkpointer is not None and getattr(checkpointer, "manager", None) is not None:
+      checkpointer.manager.wait_until_finished()
+  return trainer
+
+
+def _save(checkpointer, trainer) -> None:
+  _lib.raise_on_device_status_if_loaded()
+  checkpointer.save(trainer.step, trainer)
+  if dist.is_available() and dist.is_initialized() and dist.get_world_size() > 1:
+    dist.barrier()  # saving is rank-asymmetric host work: start the next step together

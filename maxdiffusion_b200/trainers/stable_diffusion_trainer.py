@@ -41,7 +41,8 @@ def resolve_unet_config(config) -> UNetConfig:
 class StableDiffusionTrainer:
   is_xl = False
 
-  def __init__(self, config, mesh=None, unet: Optional[UNet2DConditionModel] = None, vae=None, text_encoders=(), device=None):
+  def __init__(self, config, mesh=None, unet: Optional[UNet2DConditionModel] = None, vae=None, text_encoders=(), device=None,
+               tokenizers=()):
     self.config = config
     self.mesh = mesh if mesh is not None else create_device_mesh(config)
     self.device = torch.device(device) if device is not None else (
@@ -58,9 +59,16 @@ class StableDiffusionTrainer:
       finally:
         torch.set_default_dtype(prev)
     self.unet = unet.to(self.device, self.dtype)
-    self.vae, self.text_encoders = vae, list(text_encoders)
+    self.vae, self.text_encoders, self.tokenizers = vae, list(text_encoders), list(tokenizers)
     group = self.mesh.group("replica") if self.mesh.size("fsdp") == 1 else dist.group.WORLD if dist.is_initialized() else None
-    self.optimizer = FlatShardedOptimizer(list(self.unet.parameters()), create_optimizer(config), group=group, seed=seed)
+    # `train_text_encoder`: the (first) text encoder is trained along with the UNet, in the same flat optimizer
+    # (reference: src/maxdiffusion/trainers/stable_diffusion_trainer.py:84-117, dreambooth_trainer.py:150-170)
+    self.train_text_encoder = bool(config.get("train_text_encoder", False)) and len(self.text_encoders) > 0
+    params = list(self.unet.parameters())
+    if self.train_text_encoder:
+      params += [p for p in self.text_encoders[0].parameters() if p.requires_grad]
+    self.optimizer = FlatShardedOptimizer(params, create_optimizer(config), group=group, seed=seed)
+    self.seed = seed
     sc = dict(config.get("diffusion_scheduler_config", {}) or {})
     self.prediction_type = sc.get("prediction_type") or "epsilon"  # empty = keep the pretrained scheduler's own
     self.scheduler = DDPMScheduler(beta_start=0.00085, beta_end=0.012, beta_schedule="scaled_linear",
@@ -77,12 +85,17 @@ class StableDiffusionTrainer:
   def encode_batch(self, batch: dict) -> dict:
     """Latents and text embeddings from pixels / token ids when they are not cached in the dataset."""
     out = dict(batch)
+    if "captions" in out and "input_ids" not in out and "encoder_hidden_states" not in out:
+      for i, tok in enumerate(self.tokenizers):
+        ids = tok(list(out["captions"]), padding="max_length", max_length=getattr(tok, "model_max_length", 77),
+                  truncation=True, return_tensors="pt").input_ids
+        out[f"input_ids{'' if i == 0 else '_2'}"] = ids
     if "latents" not in out:
       with torch.no_grad():
         dist_ = self.vae.encode(out["pixel_values"].to(self.device, next(self.vae.parameters()).dtype))
         out["latents"] = self.vae.scale_latents(dist_.sample(self.gen))
     if "encoder_hidden_states" not in out:
-      with torch.no_grad():
+      with torch.set_grad_enabled(self.train_text_encoder and torch.is_grad_enabled()):
         hs, pooled = [], None
         for i, enc in enumerate(self.text_encoders):
           o = enc(out[f"input_ids{'' if i == 0 else '_2'}"].to(self.device), output_hidden_states=True)
@@ -128,15 +141,17 @@ class StableDiffusionTrainer:
     batch = self.encode_batch({k: (v.to(self.device, non_blocking=True) if torch.is_tensor(v) else v) for k, v in batch.items()})
     lr = lr_schedule(self.step, float(self.config.learning_rate), int(self.config.learning_rate_schedule_steps),
                      float(self.config.warmup_steps_fraction))
+    # the noise / timestep stream is a function of (seed, rank, step): a resumed run continues it exactly
+    self.gen.manual_seed(self.seed + 1 + 7919 * self.mesh.rank + 1000003 * self.step)
     loss = self.loss(batch)
     loss.backward()
     stats = self.optimizer.step(lr)
     self.step += 1
     return {"learning/loss": loss.detach(), "learning/grad_norm": stats["grad_norm"], "learning/current_learning_rate": lr}
 
-  def synthetic_batch(self) -> dict:
+  def synthetic_batch(self, index: Optional[int] = None) -> dict:
     cfg = self.unet.cfg
-    g = torch.Generator().manual_seed(self.step + 17)
+    g = torch.Generator().manual_seed((self.step if index is None else index) + 17 + 7919 * self.mesh.rank)
     lat = int(self.config.get("resolution", 1024)) // 8
     b = {"latents": torch.randn((self.batch_size, cfg.in_channels, lat, lat), generator=g),
          "encoder_hidden_states": torch.randn((self.batch_size, 77, cfg.cross_attention_dim), generator=g)}
@@ -144,18 +159,39 @@ class StableDiffusionTrainer:
       b["text_embeds"] = torch.randn((self.batch_size, cfg.projection_class_embeddings_input_dim - 6 * cfg.addition_time_embed_dim), generator=g)
     return {k: (v.pin_memory() if torch.cuda.is_available() else v) for k, v in b.items()}
 
+  def load_dataset(self):
+    """The configured input pipeline (`dataset_type`: synthetic, tfrecord, hf, grain), sharded over the data ranks."""
+    if str(self.config.get("dataset_type", "synthetic")) == "synthetic":
+      def synthetic(i=self.step):  # batch i is a function of i alone: a resumed run sees the batches it would have seen
+        while True:
+          yield self.synthetic_batch(i)
+          i += 1
+      return synthetic()
+    from ..input_pipeline.input_pipeline_interface import make_data_iterator
+
+    return make_data_iterator(self.config, self.mesh, self.batch_size)
+
+  def checkpointer(self):
+    from ..checkpointing.base_stable_diffusion_checkpointer import BaseStableDiffusionCheckpointer
+
+    c = self.config
+    if int(c.get("checkpoint_every", -1)) > 0 or c.get("save_final_checkpoint", False):
+      return BaseStableDiffusionCheckpointer(c)
+    return None
+
   def start_training(self, data=None):
-    writer = MetricsWriter(self.config, self.mesh.rank)
-    max_steps = int(self.config.max_train_steps)
-    while self.step < max_steps:
-      batch = next(data) if data is not None else self.synthetic_batch()
-      t0 = time.perf_counter()
-      m = self.train_step(batch)
-      loss = float(m["learning/loss"])
-      dt = time.perf_counter() - t0
-      writer.write(self.step, {**{k: float(v) for k, v in m.items()}, "perf/step_time_seconds": dt})
-    writer.close()
-    return self
+    """Resume -> (cached) data -> steps with metrics -> periodic / final checkpoints
+    (reference: base_stable_diffusion_trainer.py:115-197)."""
+    from .loop import EncodedBatchCache, run_training_loop
+
+    def build():
+      it = data if data is not None else self.load_dataset()
+      if (self.config.get("cache_latents_text_encoder_outputs", False) and self.vae is not None and not self.train_text_encoder
+          and str(self.config.get("dataset_type", "synthetic")) != "synthetic"):
+        it = EncodedBatchCache(iter(it), self.encode_batch)
+      return it
+
+    return run_training_loop(self, build, self.checkpointer())
 
 
 class StableDiffusionXLTrainer(StableDiffusionTrainer):
@@ -165,6 +201,31 @@ class StableDiffusionXLTrainer(StableDiffusionTrainer):
 class DreamboothTrainer(StableDiffusionTrainer):
   """Instance + class (prior-preservation) batches: the two halves of the batch get separate MSE terms and the
   class term is weighted by `prior_loss_weight`."""
+
+  def generate_class_images(self, pipeline, class_dir: Optional[str] = None) -> int:
+    """Fills `class_data_dir` up to `num_class_images` pictures of `class_prompt` sampled from the model being
+    fine-tuned, before training starts (reference: dreambooth_trainer.py:94-147). Returns how many were generated."""
+    import os
+
+    from PIL import Image
+
+    c = self.config
+    class_dir = class_dir or str(c.get("class_data_dir", ""))
+    want = int(c.get("num_class_images", 0))
+    if not class_dir or want <= 0:  # the reference's Dreambooth always trains with prior preservation
+      return 0
+    os.makedirs(class_dir, exist_ok=True)
+    have = len([f for f in os.listdir(class_dir) if f.lower().endswith((".png", ".jpg", ".jpeg"))])
+    made = 0
+    bs = max(1, int(c.get("class_images_batch_size", self.batch_size)))
+    while have + made < want:
+      n = min(bs, want - have - made)
+      imgs = pipeline(prompt=[str(c.get("class_prompt", ""))] * n, seed=int(c.get("seed", 0)) + have + made)
+      imgs = imgs.cpu().numpy() if torch.is_tensor(imgs) else imgs
+      for img in imgs:
+        Image.fromarray(img).save(os.path.join(class_dir, f"class_{have + made:05d}.png"))
+        made += 1
+    return made
 
   def loss(self, batch: dict) -> torch.Tensor:
     if "class_latents" not in batch:

@@ -1,0 +1,123 @@
+"""`start_training` of the Stable Diffusion / SDXL / Dreambooth / Flux trainers on CPU: periodic checkpoints inside the
+loop, and a run that resumes from a checkpoint continues the uninterrupted run (weights, optimizer moments, step
+counter, learning-rate schedule and the noise / timestep stream all come back)."""
+import os
+import shutil
+
+import pytest
+import torch
+
+from maxdiffusion_b200 import pyconfig
+from maxdiffusion_b200.parallel.mesh import create_device_mesh
+
+CFG = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "maxdiffusion_b200", "configs")
+COMMON = ["random_init=True", "log_config=false", "write_metrics=false", "dataset_type=synthetic", "save_optimizer=true",
+          "learning_rate=1e-3", "checkpoint_every=2", "enable_async_checkpointing=false", "warmup_steps_fraction=0.5"]
+SD = ["resolution=32", "per_device_batch_size=2"]
+FLUX = ["flux_preset=tiny", "resolution=64", "max_sequence_length=8"]
+
+
+def _cfg(name, extra, out):
+  return pyconfig.initialize(["x", os.path.join(CFG, name), "run_name=r", f"output_dir={out}", *COMMON, *extra], unittest=True)
+
+
+def _record(trainer):
+  losses = []
+  step = trainer.train_step
+
+  def wrapped(batch):
+    m = step(batch)
+    losses.append(float(m["learning/loss"]))
+    return m
+
+  trainer.train_step = wrapped
+  return losses
+
+
+def _only_step(src_ckpt: str, dst_ckpt: str, step: int):
+  os.makedirs(dst_ckpt, exist_ok=True)
+  shutil.copytree(os.path.join(src_ckpt, str(step)), os.path.join(dst_ckpt, str(step)))
+
+
+@pytest.mark.parametrize("kind,cfg,preset", [("sd", "base15.yml", "tiny_sd"), ("sdxl", "base_xl.yml", "tiny"), ("dreambooth", "base14.yml", "tiny_sd")])
+def test_stable_diffusion_trainers_checkpoint_in_the_loop_and_resume(kind, cfg, preset, tmp_path):
+  from maxdiffusion_b200.trainers.stable_diffusion_trainer import DreamboothTrainer, StableDiffusionTrainer, StableDiffusionXLTrainer
+
+  cls = {"sd": StableDiffusionTrainer, "sdxl": StableDiffusionXLTrainer, "dreambooth": DreamboothTrainer}[kind]
+  extra = SD + [f"unet_preset={preset}", "max_train_steps=4"]
+  ca = _cfg(cfg, extra, tmp_path / "a")
+  a = cls(ca, mesh=create_device_mesh(ca), device="cpu")
+  la = _record(a)
+  a.start_training()
+  assert len(la) == 4 and a.step == 4
+  ckpt_a = ca.checkpoint_dir
+  assert sorted(int(d) for d in os.listdir(ckpt_a) if d.isdigit()) == [2, 4]
+
+  cb = _cfg(cfg, extra, tmp_path / "b")
+  _only_step(ckpt_a, cb.checkpoint_dir, 2)
+  b = cls(cb, mesh=create_device_mesh(cb), device="cpu")
+  with torch.no_grad():
+    for p in b.unet.parameters():
+      p.add_(0.5)  # whatever the new process starts with is overwritten by the checkpoint
+  lb = _record(b)
+  b.start_training()
+  assert b.step == 4 and len(lb) == 2
+  assert lb == pytest.approx(la[2:], rel=1e-5, abs=1e-7)
+  for (n, p), (_, q) in zip(a.unet.named_parameters(), b.unet.named_parameters()):
+    assert torch.allclose(p, q, atol=1e-6), n
+
+
+def test_flux_trainer_checkpoint_in_the_loop_and_resume(tmp_path):
+  from maxdiffusion_b200.trainers.flux_trainer import FluxTrainer
+
+  extra = FLUX + ["max_train_steps=4"]
+  ca = _cfg("base_flux_dev.yml", extra, tmp_path / "a")
+  a = FluxTrainer(ca, mesh=create_device_mesh(ca), device="cpu")
+  data = a.load_dataset()
+  batches = [next(data) for _ in range(6)]
+  la = _record(a)
+  a.start_training(iter(batches))
+  assert len(la) == 4
+  cb = _cfg("base_flux_dev.yml", extra, tmp_path / "b")
+  _only_step(ca.checkpoint_dir, cb.checkpoint_dir, 2)
+  b = FluxTrainer(cb, mesh=create_device_mesh(cb), device="cpu")
+  with torch.no_grad():
+    for p in b.model.parameters():
+      p.add_(0.5)
+  lb = _record(b)
+  b.start_training(iter(batches[2:]))
+  assert b.step == 4 and lb == pytest.approx(la[2:], rel=1e-5, abs=1e-7)
+
+
+def test_encoded_batch_cache_replays_a_finite_dataset():
+  from maxdiffusion_b200.trainers.loop import EncodedBatchCache
+
+  calls = []
+
+  def encode(b):
+    calls.append(int(b["pixel_values"][0]))
+    return {"latents": b["pixel_values"] * 2, "pixel_values": b["pixel_values"], "captions": ["x"]}
+
+  cache = EncodedBatchCache(iter([{"pixel_values": torch.tensor([float(i)])} for i in range(3)]), encode)
+  seen = [float(next(cache)["latents"][0]) for _ in range(8)]
+  assert seen == [0.0, 2.0, 4.0, 0.0, 2.0, 4.0, 0.0, 2.0]
+  assert calls == [0, 1, 2]  # the encoders ran once per batch
+  assert "pixel_values" not in cache.store[0]
+
+
+def test_dreambooth_class_images_are_generated_up_to_the_requested_count(tmp_path):
+  from maxdiffusion_b200.trainers.stable_diffusion_trainer import DreamboothTrainer
+
+  cdir = tmp_path / "class"
+  c = _cfg("base14.yml", SD + ["unet_preset=tiny_sd", "max_train_steps=1", f"class_data_dir={cdir}", "num_class_images=5",
+                             "class_prompt=a photo of a dog"], tmp_path / "o")
+  tr = DreamboothTrainer(c, mesh=create_device_mesh(c), device="cpu")
+  prompts = []
+
+  def fake_pipeline(prompt, seed):
+    prompts.append((tuple(prompt), seed))
+    return torch.zeros((len(prompt), 8, 8, 3), dtype=torch.uint8)
+
+  assert tr.generate_class_images(fake_pipeline) == 5
+  assert len(os.listdir(cdir)) == 5 and all(p[0][0] == "a photo of a dog" for p in prompts)
+  assert tr.generate_class_images(fake_pipeline) == 0  # already there
