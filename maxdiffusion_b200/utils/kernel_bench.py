@@ -256,9 +256,13 @@ def bench_conv(results):
   for Ci in (96, 128):
     x = torch.randn((1, 4, 720, 1280, Ci), device="cuda", dtype=torch.bfloat16)
     pk = OC.pack_conv3d(torch.randn((Ci, Ci, 3, 3, 3), device="cuda", dtype=torch.bfloat16) * 0.02, None)
-    for cfg in ((0, 0, 0), (2, 0, 1), (1, 0, 1), (1, 0, 2), (2, 0, 2), (1, 2, 2)):
+    for cfg in ((0, 0, 0), (2, 0, 1), (1, 0, 1), (1, 0, 2), (1, 2, 2)):
       OC.tune(*cfg)
-      med, best = time_ms(lambda: OC.conv3d_causal(x, pk), iters=5)
+      try:
+        med, best = time_ms(lambda: OC.conv3d_causal(x, pk), iters=5)
+      except Exception as e:  # a launch shape that does not fit the shared-memory budget is rejected by the launcher
+        print(dict(kernel="conv3d_causal_igemm_tuning", tune=list(cfg), rejected=str(e)), flush=True)
+        continue
       results.append(dict(kernel="conv3d_causal_igemm_tuning", shape=[1, 4, 720, 1280, Ci, Ci], tune=list(cfg), ms=med,
                           tflops=2.0 * 4 * 720 * 1280 * Ci * Ci * 27 / med / 1e9))
       print(results[-1], flush=True)
@@ -294,6 +298,26 @@ def bench_conv(results):
     lib, _ = time_ms(lib_fn, iters=5)
     results.append(dict(kernel=f"conv2d_igemm_{kind}", shape=[B, H, W, Ci, Co], ms=med, best_ms=best, tflops=fl / med / 1e9,
                         frac=fl / med / 1e9 / tf_peak, of=tag, cudnn_ms=lib))
+    print(results[-1], flush=True)
+  for B, H, W, Ci, Co, stride in [(8, 128, 128, 320, 320, 1), (8, 64, 64, 640, 640, 1), (8, 32, 32, 1280, 1280, 1), (8, 128, 128, 320, 320, 2)]:
+    x = torch.randn((B, H, W, Ci), device="cuda", dtype=torch.bfloat16)
+    dy = torch.randn((B, H // stride, W // stride, Co), device="cuda", dtype=torch.bfloat16)
+    med, best = time_ms(lambda: OC.conv2d_wgrad(x, dy, 3, stride, 1), iters=5)
+    xn, dyn = x.permute(0, 3, 1, 2), dy.permute(0, 3, 1, 2)
+    lib, _ = time_ms(lambda: torch.nn.grad.conv2d_weight(xn, (Co, Ci, 3, 3), dyn, stride=stride, padding=1), iters=5)
+    fl = 2.0 * B * (H // stride) * (W // stride) * Co * Ci * 9
+    results.append(dict(kernel=f"conv2d_wgrad_s{stride}", shape=[B, H, W, Ci, Co], ms=med, best_ms=best, tflops=fl / med / 1e9,
+                        frac=fl / med / 1e9 / tf_peak, of=tag, cudnn_ms=lib, note="includes the zero-border copies of x and dy and the split fold"))
+    print(results[-1], flush=True)
+  from maxdiffusion_b200.ops import functional as OF
+
+  for N, C, H, W in [(8, 320, 128, 128), (8, 1280, 32, 32)]:
+    x = torch.randn((N, C, H, W), device="cuda", dtype=torch.bfloat16).contiguous(memory_format=torch.channels_last)
+    g = torch.ones(C, device="cuda", dtype=torch.bfloat16)
+    med, best = time_ms(lambda: OF.group_norm(x, 32, g, g, 1e-5, True), iters=5)
+    lib, _ = time_ms(lambda: F.silu(F.group_norm(x, 32, g, g, 1e-5)), iters=5)
+    results.append(dict(kernel="group_norm_silu_cl_fwd", shape=[N, C, H, W], ms=med, gbs=6.0 * x.numel() / med / 1e6,
+                        frac=6.0 * x.numel() / med / 1e6 / bw_peak, of=tag, torch_ms=lib, note="two reads + one write of the activation"))
     print(results[-1], flush=True)
   for C in (96, 384):
     x = torch.randn((4 * 720 * 1280 * 96 // C, C), device="cuda", dtype=torch.bfloat16)
