@@ -43,14 +43,14 @@ namespace fa {
 
 constexpr int BQ = 128;          // rows per q tile
 constexpr int BKV = 64;          // keys per block
-constexpr int KV_STAGES = 4;
+constexpr int DEFAULT_KV_STAGES = 4;  // K / V pipeline depth; 2..5 are built and selectable (tile search)
 // A tile is stored as head_dim / 64 chunks of 64 columns (128-byte rows, 128-byte swizzle).
 constexpr int CHUNK_BYTES = 128 * 128;       // 16 KiB: one chunk of a 128-row Q tile
 constexpr int KV_CHUNK_BYTES = BKV * 128;    // 8 KiB: one chunk of a 64-key K / V tile
 constexpr int MAX_SEGMENTS = 8;
 constexpr int ROLE_WARPS = 5;            // warp 0 TMA, warps 1 / 3 issue S of tile 0 / 1, warps 2 / 4 issue P V of tile 0 / 1
 constexpr int NUM_THREADS = ROLE_WARPS * 32 + 256;  // + softmax warps 5-8 (tile 0), 9-12 (tile 1)
-template <int HD>
+template <int HD, int KV_STAGES>
 constexpr int smem_bytes() { return 2 * (HD / 64) * CHUNK_BYTES + 2 * KV_STAGES * (HD / 64) * KV_CHUNK_BYTES + 1024 + 512; }
 constexpr float kRescaleThreshold = 8.0f;
 
@@ -213,7 +213,7 @@ __device__ __forceinline__ void copy_cta(const CopyPlan& cp, int ci, DeviceStatu
   }
 }
 
-template <int HD>
+template <int HD, int KV_STAGES>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 flash_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ KVMaps maps, const Params p,
                  const __grid_constant__ CopyPlan cp) {
@@ -590,6 +590,38 @@ struct MdbCopyPlan {
   int n_groups;                     // head groups: 0 lets the launcher choose, 1 copies whole segments in order
 };
 
+// Launch-shape overrides for the tile search (0 = default): K / V pipeline stages (2..5) and the number of copy CTAs.
+static int g_tune_stages = 0, g_tune_copy_ctas = 0;
+static int g_last_stages = 0, g_last_copy_ctas = 0;  // what the most recent launch used (for the tile-search tests)
+
+extern "C" int mdb_flash_fwd_last_variant(int* kv_stages, int* copy_ctas) {
+  *kv_stages = g_last_stages;
+  *copy_ctas = g_last_copy_ctas;
+  return 0;
+}
+
+extern "C" int mdb_flash_fwd_tune(int kv_stages, int copy_ctas) {
+  if (kv_stages != 0 && (kv_stages < 2 || kv_stages > 5)) return 3108;
+  if (copy_ctas < 0 || copy_ctas > 64) return 3108;
+  g_tune_stages = kv_stages;
+  g_tune_copy_ctas = copy_ctas;
+  return 0;
+}
+
+template <int HD, int STAGES>
+static int launch_variant(dim3 grid, cudaStream_t st, const CUtensorMap& tq, const mdb::fa::KVMaps& maps, const mdb::fa::Params& p,
+                          const mdb::fa::CopyPlan& cp) {
+  using namespace mdb::fa;
+  static bool configured = false;
+  if (!configured) {
+    MDB_CHECK_CUDA(cudaFuncSetAttribute(flash_fwd_kernel<HD, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                        smem_bytes<HD, STAGES>()));
+    configured = true;
+  }
+  flash_fwd_kernel<HD, STAGES><<<grid, NUM_THREADS, smem_bytes<HD, STAGES>(), st>>>(tq, maps, p, cp);
+  return static_cast<int>(cudaGetLastError());
+}
+
 // q: [B, q_len, H, 128]; k/v segment s: [B, kv_len[s], H, 128]; out like q. Strides are in elements
 // (batch, sequence, head); the head_dim stride is 1. Every segment shares the k strides / v strides
 // given here. `plan` (may be null) adds copy CTAs that stage the remote segments 1.. from peer memory.
@@ -656,11 +688,6 @@ static int flash_fwd_launch(const void* q, const void* const* k_ptrs, const void
     cp.n_ack = plan->n_ack;
     for (int a = 0; a < plan->n_ack; ++a) cp.ack[a] = reinterpret_cast<unsigned int*>(plan->ack[a]);
   }
-  static bool configured = false;
-  if (!configured) {
-    MDB_CHECK_CUDA(cudaFuncSetAttribute(flash_fwd_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes<HD>()));
-    configured = true;
-  }
   const int n_qb = (q_len + 2 * BQ - 1) / (2 * BQ);
   const long long total_work = static_cast<long long>(n_qb) * H * B;
   int n_copy = cp.n_remote > 0 ? cp.n_copy_ctas : 0;
@@ -694,8 +721,23 @@ static int flash_fwd_launch(const void* q, const void* const* k_ptrs, const void
     p.flag_stride = MAX_GROUPS;
     p.heads_per_group = hpg;
   }
-  flash_fwd_kernel<HD><<<n_compute + n_copy, NUM_THREADS, smem_bytes<HD>(), static_cast<cudaStream_t>(stream_ptr)>>>(tq, maps, p, cp);
-  return static_cast<int>(cudaGetLastError());
+  if (g_tune_copy_ctas > 0 && n_copy > 0) {
+    // the tile search pins the number of copy CTAs (the automatic choice above is bypassed)
+    n_copy = g_tune_copy_ctas < sm_count() - 1 ? g_tune_copy_ctas : sm_count() - 1;
+    cp.n_copy_ctas = n_copy;
+    n_compute = sm_count() - n_copy;
+    if (total_work < n_compute) n_compute = static_cast<int>(total_work);
+  }
+  const dim3 grid(n_compute + n_copy);
+  cudaStream_t st = static_cast<cudaStream_t>(stream_ptr);
+  g_last_stages = g_tune_stages > 0 ? g_tune_stages : DEFAULT_KV_STAGES;
+  g_last_copy_ctas = n_copy;
+  switch (g_tune_stages > 0 ? g_tune_stages : DEFAULT_KV_STAGES) {
+    case 2: return launch_variant<HD, 2>(grid, st, tq, maps, p, cp);
+    case 3: return launch_variant<HD, 3>(grid, st, tq, maps, p, cp);
+    case 5: return launch_variant<HD, 5>(grid, st, tq, maps, p, cp);
+    default: return launch_variant<HD, 4>(grid, st, tq, maps, p, cp);
+  }
 }
 
 extern "C" int mdb_flash_fwd(const void* q, const void* const* k_ptrs, const void* const* v_ptrs, void* out,

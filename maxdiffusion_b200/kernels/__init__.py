@@ -22,8 +22,9 @@ KERNEL_REGISTRY = dict(ATTENTION_KERNELS)
 
 
 def make_splash_mha(scale: Optional[float] = None, **unused_block_sizes) -> Callable:
-  """Local attention. Block sizes are accepted for call compatibility; the kernel's tiles are fixed at build time
-  (128-row query tiles x 128-column key tiles, chosen by `utils.tile_size_grid_search` measurements)."""
+  """Local attention. Block sizes are accepted for call compatibility only: the kernel works on pairs of 128-row
+  query tiles against 64-key blocks (its TMEM layout); what `utils.tile_size_grid_search` chooses per shape is the
+  depth of the K / V pipeline and the number of copy CTAs (`ops.kernels.load_flash_tuning`)."""
   return lambda q, k, v: OF.attention(q, k, v, scale)
 
 

@@ -128,6 +128,10 @@ def _declare(L: ctypes.CDLL) -> None:
   for name in ("mdb_flash_fwd_fixed_m", "mdb_flash_fwd_fixed_m_d64"):
     getattr(L, name).argtypes = L.mdb_flash_fwd.argtypes + [c_void_p, c_void_p]
     getattr(L, name).restype = c_int
+  L.mdb_flash_fwd_tune.argtypes = [c_int, c_int]
+  L.mdb_flash_fwd_tune.restype = c_int
+  L.mdb_flash_fwd_last_variant.argtypes = [ctypes.POINTER(c_int), ctypes.POINTER(c_int)]
+  L.mdb_flash_fwd_last_variant.restype = c_int
   L.mdb_ln_fwd.argtypes = [c_void_p] * 6 + [c_ll, c_int, c_int, c_int, c_float, c_void_p, c_void_p, c_int, c_void_p]
   L.mdb_ln_fwd.restype = c_int
   L.mdb_ln_bwd.argtypes = [c_void_p] * 6 + [c_ll, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p]

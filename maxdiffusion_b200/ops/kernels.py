@@ -68,6 +68,49 @@ def _flash_entry(name: str, D: int):
   return getattr(_lib.lib(), name if D == 128 else name + "_d64")
 
 
+# ---------------------------------------------------------------------------------------------
+# launch shapes chosen by the tile search (`utils/tile_size_grid_search.py`): {(q_len, head_dim, heads, segments):
+# (kv_stages, copy_ctas)}; `flash_fwd` applies the entry of its shape before it launches
+# ---------------------------------------------------------------------------------------------
+_FLASH_TUNED: dict = {}
+_FLASH_CURRENT = (0, 0)
+
+
+def flash_tune(kv_stages: int = 0, copy_ctas: int = 0) -> None:
+  """Pins the launch shape of the attention forward: K / V pipeline stages (2..5, 0 = default 4) and the number of
+  copy CTAs of a context-parallel launch (0 = automatic)."""
+  global _FLASH_CURRENT
+  _lib.check(_lib.lib().mdb_flash_fwd_tune(int(kv_stages), int(copy_ctas)), "mdb_flash_fwd_tune")
+  _FLASH_CURRENT = (int(kv_stages), int(copy_ctas))
+
+
+def flash_last_variant() -> tuple:
+  a, b = ctypes.c_int(0), ctypes.c_int(0)
+  _lib.lib().mdb_flash_fwd_last_variant(ctypes.byref(a), ctypes.byref(b))
+  return a.value, b.value
+
+
+def flash_tuned_key(q_len: int, head_dim: int, heads: int, segments: int) -> str:
+  return f"flash:{q_len}:{head_dim}:{heads}:{segments}"
+
+
+def load_flash_tuning(path: str) -> int:
+  """Reads the tile-search cache (`tile_search_cache.json`) and registers its attention entries. Returns how many."""
+  import json
+  import os
+
+  if not path or not os.path.exists(path):
+    return 0
+  with open(path) as f:
+    data = json.load(f)
+  n = 0
+  for key, c in data.items():
+    if key.startswith("flash:"):
+      _FLASH_TUNED[key] = (int(c.get("stages", 0)), int(c.get("copy_ctas", 0)))
+      n += 1
+  return n
+
+
 def flash_fwd(q: torch.Tensor, k_list: Sequence[torch.Tensor], v_list: Sequence[torch.Tensor], scale: float | None = None,
               return_lse: bool = True, seg_flags: torch.Tensor | None = None, flag_target: int = 0, plan=None,
               fixed_m=None):
@@ -80,6 +123,10 @@ def flash_fwd(q: torch.Tensor, k_list: Sequence[torch.Tensor], v_list: Sequence[
     k_list, v_list = [k_list], [v_list]
   B, Sq, H, D = q.shape
   assert D in FLASH_HEAD_DIMS and q.dtype == torch.bfloat16 and q.stride(-1) == 1
+  if _FLASH_TUNED:
+    want = _FLASH_TUNED.get(flash_tuned_key(Sq, D, H, len(k_list)), (0, 0))  # shapes without an entry: the default
+    if want != _FLASH_CURRENT:
+      flash_tune(*want)
   k0, v0 = k_list[0], v_list[0]
   for k, v in zip(k_list, v_list):
     assert k.dtype == torch.bfloat16 and v.dtype == torch.bfloat16

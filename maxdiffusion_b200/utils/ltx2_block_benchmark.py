@@ -1,7 +1,7 @@
 """LTX-2 plug for the attention tile search: times ONE transformer block of the configured size on synthetic tokens.
 
 reference: src/maxdiffusion/utils/ltx2_block_benchmark.py (`LTX2BlockBenchmark`, CLI). Candidates are the launch
-geometries of `utils.tile_size_grid_search`; the block is built once, every candidate only changes the attention
+variants of the attention forward (`utils.wan_block_benchmark.candidates`: K / V pipeline depth); the block is built once, every candidate only changes the attention
 configuration, warm-up is excluded and the maximum over ranks is kept.
 """
 from __future__ import annotations
@@ -40,8 +40,13 @@ class LTX2BlockBenchmark:
     return self.x.shape[1]
 
   def setup(self, candidate: Candidate):
-    if (candidate.block_q, candidate.block_kv, candidate.stages) != (256, 128, 2):
-      raise ValueError("tile shape is fixed in this build")
+    from ..ops import kernels as K
+    from .wan_block_benchmark import kernel_supports
+
+    if not kernel_supports(candidate):
+      raise ValueError(f"the attention kernel is not built with tiles {candidate.block_q} x {candidate.block_kv} / {candidate.stages} stages")
+    if self.device.type == "cuda":
+      K.flash_tune(candidate.stages, candidate.copy_ctas)  # every attention launch of the block uses this variant
     t = torch.full((1,), 500.0, device=self.device)
 
     @torch.no_grad()
@@ -52,7 +57,10 @@ class LTX2BlockBenchmark:
     return step
 
   def teardown(self):
-    pass
+    if self.device.type == "cuda":
+      from ..ops import kernels as K
+
+      K.flash_tune(0, 0)
 
 
 def run_tile_search(config, device=None):
@@ -60,7 +68,9 @@ def run_tile_search(config, device=None):
 
   bench = LTX2BlockBenchmark(config, device)
   seq = bench.sequence_length()
-  grid = smart_grid if str(config.get("tile_search_mode", "smart")) == "smart" else full_grid
+  from .wan_block_benchmark import candidates
+
+  grid = lambda q, kv, n: candidates(n, full=str(config.get("tile_search_mode", "smart")) != "smart")
   cache = os.path.join(config.get("aot_cache_dir", "") or ".", "tile_search_cache.json")
   sync = torch.cuda.synchronize if bench.device.type == "cuda" else None
   best = grid_search(bench, grid(seq, seq, 1), iters=int(config.get("tile_search_iters", 10)),

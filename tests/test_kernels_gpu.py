@@ -455,3 +455,31 @@ def test_attention_head_dim_64_autograd_matches_reference():
   _report("attention d64 out", out, want.float(), rel_tol=2e-2, abs_frac=5e-2)
   for name, a, b in (("dq", q.grad, qf.grad), ("dk", k.grad, kf.grad), ("dv", v.grad, vf.grad)):
     _report(f"attention d64 {name}", a, b, rel_tol=2e-2, abs_frac=5e-2)
+
+
+def test_tile_search_choice_changes_the_launched_attention_variant():
+  """A cached tile-search result for a shape makes `flash_fwd` launch that variant (K / V pipeline depth), other
+  shapes keep the default, and every variant computes the same attention."""
+  from maxdiffusion_b200.ops import ref
+
+  torch.manual_seed(0)
+  q = torch.randn(1, 512, 4, 128, device="cuda").to(torch.bfloat16)
+  k = torch.randn(1, 640, 4, 128, device="cuda").to(torch.bfloat16)
+  v = torch.randn(1, 640, 4, 128, device="cuda").to(torch.bfloat16)
+  want = ref.attention(q, k, v).float()
+  K._FLASH_TUNED.clear()
+  K.flash_tune(0, 0)
+  base, _ = K.flash_fwd(q, k, v)
+  assert K.flash_last_variant()[0] == 4
+  try:
+    for stages in (2, 3, 5):
+      K._FLASH_TUNED[K.flash_tuned_key(512, 128, 4, 1)] = (stages, 0)
+      out, _ = K.flash_fwd(q, k, v)
+      assert K.flash_last_variant()[0] == stages
+      assert torch.equal(out, base)  # the pipeline depth does not change the arithmetic
+      assert (out.float() - want).abs().max() < 2e-2
+    K.flash_fwd(q[:, :256], k, v)  # no entry for this shape: back to the default variant
+    assert K.flash_last_variant()[0] == 4
+  finally:
+    K._FLASH_TUNED.clear()
+    K.flash_tune(0, 0)

@@ -47,3 +47,32 @@ def test_grid_search_csv_and_cache(tmp_path):
   rows = list(csv.DictReader(open(os.path.join(tmp_path, "tile_search.csv"))))
   assert len(rows) == 3 and rows[2]["seconds"] == "failed"
   assert T.grid_search(_MockBench(), [], cache_path=cache, cache_key="k") == best  # served from the cache
+
+
+def test_wan_plug_offers_the_kernels_launch_variants_and_rejects_other_tiles():
+  from maxdiffusion_b200.utils import wan_block_benchmark as W
+
+  one = W.candidates(1)
+  assert [c.stages for c in one] == [2, 3, 4, 5] and all(W.kernel_supports(c) and c.copy_ctas == 0 for c in one)
+  eight = W.candidates(8)
+  assert {c.copy_ctas for c in eight} == {8, 12, 16, 20, 24} and len(eight) == 20
+  extra = [c for c in W.candidates(1, full=True) if not W.kernel_supports(c)]
+  assert extra  # recorded as rejected in the CSV
+  import pytest
+
+  with pytest.raises(ValueError, match="not built"):
+    W.WanBlockBenchmark(4, 256, [256], device="cpu").setup(extra[0])
+
+
+def test_cached_choice_is_registered_for_the_attention_launcher(tmp_path):
+  import json
+
+  from maxdiffusion_b200.ops import kernels as K
+
+  key = K.flash_tuned_key(4096, 128, 40, 8)
+  path = tmp_path / "tile_search_cache.json"
+  path.write_text(json.dumps({key: {"block_q": 256, "block_kv": 64, "stages": 3, "copy_ctas": 16}, "ltx2:32:100": {"stages": 2}}))
+  K._FLASH_TUNED.clear()
+  assert K.load_flash_tuning(str(path)) == 1
+  assert K._FLASH_TUNED[key] == (3, 16)
+  K._FLASH_TUNED.clear()
