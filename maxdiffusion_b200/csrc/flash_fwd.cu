@@ -99,6 +99,11 @@ struct Params {
   // The caller guarantees  s*scale_log2 - m_fixed <= 126  for every score of such a head.
   const float* m_fixed;    // [B, H, q_len]
   const int* fixed_heads;  // [H]
+  // Output scatter (0: off). The reverse Ulysses exchange folded into the epilogue: query row r of this launch is row
+  // r % rows_per_rank of rank r / rows_per_rank, whose output tensor [B, rows_per_rank, heads_total, D] is addressed
+  // with the o strides above; this launch's head h is head out_head_off + h there (16-byte peer stores).
+  int out_scatter_n, out_rows_per_rank, out_head_off;
+  __nv_bfloat16* out_peers[MAX_SEGMENTS];
   DeviceStatus* status;
 };
 
@@ -526,8 +531,16 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
       tc_fence_after_sync();
       const float inv = (l > 0.0f) ? 1.0f / l : 0.0f;
       const bool row_ok = q_row < p.q_len;
-      __nv_bfloat16* orow = p.out + batch * p.o_stride_b + static_cast<long long>(q_row) * p.o_stride_s +
-                            head * p.o_stride_h;
+      __nv_bfloat16* obase = p.out;
+      int orow_idx = q_row, ohead = head;
+      if (p.out_scatter_n > 0) {
+        const int r = min(q_row / p.out_rows_per_rank, p.out_scatter_n - 1);
+        obase = p.out_peers[r];
+        orow_idx = q_row - r * p.out_rows_per_rank;
+        ohead = head + p.out_head_off;
+      }
+      __nv_bfloat16* orow = obase + batch * p.o_stride_b + static_cast<long long>(orow_idx) * p.o_stride_s +
+                            ohead * p.o_stride_h;
 #pragma unroll 1
       for (int c = 0; c < D / 32; ++c) {
         uint32_t r[32];
@@ -573,6 +586,12 @@ static int make_map(CUtensorMap* map, const void* ptr, int D, int B, int S, int 
 
 }  // namespace fa
 }  // namespace mdb
+
+// Host-side description of the output scatter (see Params::out_scatter_n).
+struct MdbOutScatter {
+  int n, rows_per_rank, head_off;
+  unsigned long long ptrs[8];
+};
 
 // Host-side description of the copy CTAs' work (all addresses as integers); see CopyPlan.
 struct MdbCopyPlan {
@@ -633,7 +652,8 @@ static int flash_fwd_launch(const void* q, const void* const* k_ptrs, const void
                             long long k_sh, long long v_sb, long long v_ss, long long v_sh, long long o_sb,
                             long long o_ss, long long o_sh, float softmax_scale, const unsigned int* seg_flags,
                             unsigned int flag_target, const MdbCopyPlan* plan, void* stream_ptr,
-                            const float* m_fixed = nullptr, const int* fixed_heads = nullptr) {
+                            const float* m_fixed = nullptr, const int* fixed_heads = nullptr,
+                            const MdbOutScatter* scatter = nullptr) {
   using namespace mdb;
   using namespace mdb::fa;
   if (B <= 0 || H <= 0 || q_len <= 0) return 0;
@@ -666,6 +686,18 @@ static int flash_fwd_launch(const void* q, const void* const* k_ptrs, const void
   if ((m_fixed == nullptr) != (fixed_heads == nullptr)) return 3105;
   p.m_fixed = m_fixed;
   p.fixed_heads = fixed_heads;
+  p.out_scatter_n = 0;
+  p.out_rows_per_rank = 1;
+  p.out_head_off = 0;
+  for (int i = 0; i < MAX_SEGMENTS; ++i) p.out_peers[i] = nullptr;
+  if (scatter != nullptr && scatter->n > 0) {
+    if (scatter->n > MAX_SEGMENTS || scatter->rows_per_rank <= 0 || lse != nullptr) return 3109;
+    if (static_cast<long long>(scatter->n) * scatter->rows_per_rank < q_len) return 3109;
+    p.out_scatter_n = scatter->n;
+    p.out_rows_per_rank = scatter->rows_per_rank;
+    p.out_head_off = scatter->head_off;
+    for (int i = 0; i < scatter->n; ++i) p.out_peers[i] = reinterpret_cast<__nv_bfloat16*>(scatter->ptrs[i]);
+  }
   p.status = status_buffer();
   CopyPlan cp;
   memset(&cp, 0, sizeof(cp));
@@ -749,6 +781,20 @@ extern "C" int mdb_flash_fwd(const void* q, const void* const* k_ptrs, const voi
   return flash_fwd_launch<128>(q, k_ptrs, v_ptrs, out, lse, B, H, q_len, num_segments, kv_lens, q_sb, q_ss, q_sh, k_sb,
                                k_ss, k_sh, v_sb, v_ss, v_sh, o_sb, o_ss, o_sh, softmax_scale, seg_flags, flag_target,
                                plan, stream_ptr);
+}
+
+// head_dim 128 with the output scattered to the sequence owners (the reverse Ulysses exchange in the epilogue): `out`
+// is unused, the o strides describe every peer's [B, rows_per_rank, heads_total, 128] output, no log-sum-exp is written.
+extern "C" int mdb_flash_fwd_scatter(const void* q, const void* const* k_ptrs, const void* const* v_ptrs, int B, int H,
+                                     int q_len, int num_segments, const int* kv_lens, long long q_sb, long long q_ss,
+                                     long long q_sh, long long k_sb, long long k_ss, long long k_sh, long long v_sb,
+                                     long long v_ss, long long v_sh, long long o_sb, long long o_ss, long long o_sh,
+                                     float softmax_scale, const unsigned int* seg_flags, unsigned int flag_target,
+                                     const MdbCopyPlan* plan, const MdbOutScatter* scatter, void* stream_ptr) {
+  if (scatter == nullptr || scatter->n < 1) return 3109;
+  return flash_fwd_launch<128>(q, k_ptrs, v_ptrs, nullptr, nullptr, B, H, q_len, num_segments, kv_lens, q_sb, q_ss, q_sh, k_sb,
+                               k_ss, k_sh, v_sb, v_ss, v_sh, o_sb, o_ss, o_sh, softmax_scale, seg_flags, flag_target,
+                               plan, stream_ptr, nullptr, nullptr, scatter);
 }
 
 // Same for head_dim 64 (Stable Diffusion / SDXL / LTX-Video heads).

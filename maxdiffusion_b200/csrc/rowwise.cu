@@ -119,6 +119,13 @@ __device__ __forceinline__ Strip my_strip(int rows_per_batch) {
 // LayerNorm (fp32 statistics) with optional affine (gamma, beta: bf16 [C]) and optional
 // modulation (scale, shift: fp32 [num_batches, mod_ld]):  y = ((x-mean)*rstd*gamma+beta)*(1+scale)+shift
 // ---------------------------------------------------------------------------------------
+// Destination of a head-scattering store (the Ulysses all-to-all folded into the producer): n ranks, this rank's
+// index, heads per rank, and every rank's receive buffer [B, n * S, hn, 128].
+struct HeadScatter {
+  int n, me, hn;
+  __nv_bfloat16* base[8];
+};
+
 // NV = 16-byte vectors per thread (C <= NV*8*THREADS). Four CTAs fit on an SM, so a grid of 4 x 148 is one wave.
 template <int NV>
 __global__ void __launch_bounds__(THREADS, 4)
@@ -343,7 +350,7 @@ __global__ void __launch_bounds__(THREADS, 4)
 rms_rope_fwd_kernel(const __nv_bfloat16* __restrict__ x, long long ldx, __nv_bfloat16* __restrict__ y, long long ldy,
                     const __nv_bfloat16* __restrict__ w, int w_per_head, const float* __restrict__ cos_t,
                     const float* __restrict__ sin_t, int rows_per_batch, int C, int group, float eps,
-                    float* __restrict__ rstd_out) {
+                    float* __restrict__ rstd_out, const HeadScatter sc) {
   __shared__ float2 red[2][THREADS / 32];
   int parity = 0;
   const Strip s = my_strip(rows_per_batch);
@@ -364,13 +371,13 @@ rms_rope_fwd_kernel(const __nv_bfloat16* __restrict__ x, long long ldx, __nv_bfl
       }
       total += sq[k];
     }
-    float rstd_all = 0.0f;
+    float rstd_all = 1.0f;  // group == 0: no normalisation (the value projection only changes layout)
     if (group == C) rstd_all = rsqrtf(block_sum2(total, 0.0f, red, parity).x / C + eps);
 #pragma unroll
     for (int k = 0; k < NV; ++k) {
       const int vi = threadIdx.x + k * THREADS;
       float rstd = rstd_all;
-      if (group != C) rstd = rsqrtf(half_warp_sum(sq[k]) / 128.0f + eps);  // all lanes take part
+      if (group != C && group != 0) rstd = rsqrtf(half_warp_sum(sq[k]) / 128.0f + eps);  // all lanes take part
       if (vi < nvec) {
         if (rstd_out) {
           if (group == C) {
@@ -402,7 +409,16 @@ rms_rope_fwd_kernel(const __nv_bfloat16* __restrict__ x, long long ldx, __nv_bfl
             o[2 * j + 1] = a * s4[j] + b * c4[j];
           }
         }
-        store8(y + row * ldy + vi * 8, o);
+        if (sc.n > 0) {
+          // Ulysses exchange folded into the store: head h goes to rank h / hn, where it is head h % hn of the
+          // [B, n * S, hn, 128] tensor, at sequence position me * S + pos (16-byte peer stores over NVLink)
+          const int head = vi >> 4;
+          const int r = head / sc.hn;
+          const long long drow = (static_cast<long long>(s.batch) * sc.n + sc.me) * rows_per_batch + pos;
+          store8(sc.base[r] + (drow * sc.hn + (head - r * sc.hn)) * 128 + (vi & 15) * 8, o);
+        } else {
+          store8(y + row * ldy + vi * 8, o);
+        }
       }
     }
   }
@@ -673,17 +689,15 @@ extern "C" int mdb_ln_bwd(const void* dy, const void* x, const float* mean, cons
   return static_cast<int>(cudaGetLastError());
 }
 
-extern "C" int mdb_rms_rope_fwd(const void* x, long long ldx, void* y, long long ldy, const void* w, int w_per_head,
-                                const float* cos_t, const float* sin_t, int num_batches, int rows_per_batch, int C,
-                                int group, float eps, float* rstd_out, int ctas_per_batch, void* stream) {
-  if (int rc = check_c(C)) return rc;
-  if ((group != C && group != 128) || (C & 127)) return 3202;
-  if (num_batches <= 0 || rows_per_batch <= 0) return 0;
+static int launch_rms_rope_fwd(const void* x, long long ldx, void* y, long long ldy, const void* w, int w_per_head,
+                               const float* cos_t, const float* sin_t, int num_batches, int rows_per_batch, int C, int group,
+                               float eps, float* rstd_out, const mdb::rw::HeadScatter& sc, int ctas_per_batch, void* stream) {
+  using namespace mdb::rw;
   dim3 grid(ctas_per_batch, num_batches);
 #define MDB_RMS_FWD(NV)                                                                                 \
   rms_rope_fwd_kernel<NV><<<grid, THREADS, 0, static_cast<cudaStream_t>(stream)>>>(                     \
       static_cast<const __nv_bfloat16*>(x), ldx, static_cast<__nv_bfloat16*>(y), ldy,                   \
-      static_cast<const __nv_bfloat16*>(w), w_per_head, cos_t, sin_t, rows_per_batch, C, group, eps, rstd_out)
+      static_cast<const __nv_bfloat16*>(w), w_per_head, cos_t, sin_t, rows_per_batch, C, group, eps, rstd_out, sc)
   switch (vectors_per_thread(C)) {
     case 1: MDB_RMS_FWD(1); break;
     case 2: MDB_RMS_FWD(2); break;
@@ -692,6 +706,38 @@ extern "C" int mdb_rms_rope_fwd(const void* x, long long ldx, void* y, long long
   }
 #undef MDB_RMS_FWD
   return static_cast<int>(cudaGetLastError());
+}
+
+extern "C" int mdb_rms_rope_fwd(const void* x, long long ldx, void* y, long long ldy, const void* w, int w_per_head,
+                                const float* cos_t, const float* sin_t, int num_batches, int rows_per_batch, int C,
+                                int group, float eps, float* rstd_out, int ctas_per_batch, void* stream) {
+  if (int rc = check_c(C)) return rc;
+  if ((group != C && group != 128) || (C & 127)) return 3202;
+  if (num_batches <= 0 || rows_per_batch <= 0) return 0;
+  HeadScatter sc;
+  sc.n = 0; sc.me = 0; sc.hn = 1;
+  for (int i = 0; i < 8; ++i) sc.base[i] = nullptr;
+  return launch_rms_rope_fwd(x, ldx, y, ldy, w, w_per_head, cos_t, sin_t, num_batches, rows_per_batch, C, group, eps, rstd_out,
+                             sc, ctas_per_batch, stream);
+}
+
+// The same kernel with the Ulysses head <-> sequence exchange folded into its stores: nothing is written locally; head
+// h of row (b, s) goes to peer_ptrs[h / (H / n)], a [B, n * S, H / n, 128] buffer, at sequence position me * S + s.
+// group = C (RMS over the row), 128 (per head) or 0 (no normalisation: the value projection). w / cos_t may be null.
+extern "C" int mdb_rms_rope_fwd_scatter(const void* x, long long ldx, const void* w, int w_per_head, const float* cos_t,
+                                        const float* sin_t, int num_batches, int rows_per_batch, int C, int group,
+                                        float eps, const unsigned long long* peer_ptrs, int n, int me, int ctas_per_batch,
+                                        void* stream) {
+  if (int rc = check_c(C)) return rc;
+  if ((group != C && group != 128 && group != 0) || (C & 127)) return 3202;
+  const int heads = C >> 7;
+  if (n < 1 || n > 8 || me < 0 || me >= n || heads % n != 0) return 3204;
+  if (num_batches <= 0 || rows_per_batch <= 0) return 0;
+  HeadScatter sc;
+  sc.n = n; sc.me = me; sc.hn = heads / n;
+  for (int i = 0; i < 8; ++i) sc.base[i] = i < n ? reinterpret_cast<__nv_bfloat16*>(peer_ptrs[i]) : nullptr;
+  return launch_rms_rope_fwd(x, ldx, nullptr, 0, w, w_per_head, cos_t, sin_t, num_batches, rows_per_batch, C, group, eps,
+                             nullptr, sc, ctas_per_batch, stream);
 }
 
 // dw_out: fp32 [C] summed over batches (accumulated over `num_batches` folds).

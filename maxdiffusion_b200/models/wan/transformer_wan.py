@@ -124,10 +124,15 @@ class WanSelfAttention(nn.Module):
     B, S, C = x.shape
     q, k, v = split_fused(self.to_qkv(x), 3)
     cos, sin = rope
+    if pctx is not None:
+      # the strategy object sees the raw projections: under Ulysses the exchanges ride on the norm / RoPE stores and
+      # on the attention epilogue instead of running as kernels of their own
+      o = pctx.projected_self_attention(q, k, v, self.norm_q, self.norm_k, cos, sin, self.heads, self.eps)
+      return project_gated_residual(self.to_out, o, residual, gate)
     q = OF.rms_norm_rope(q, self.norm_q, cos, sin, heads=self.heads, eps=self.eps)
     k = OF.rms_norm_rope(k, self.norm_k, cos, sin, heads=self.heads, eps=self.eps)
     v = v.unflatten(-1, (self.heads, C // self.heads))
-    o = pctx.self_attention(q, k, v) if pctx is not None else OF.attention(q, k, v)
+    o = OF.attention(q, k, v)
     return project_gated_residual(self.to_out, o.reshape(B, S, C), residual, gate)
 
 

@@ -34,6 +34,11 @@ class CopyPlan(ctypes.Structure):
               ("n_ack", ctypes.c_int), ("n_groups", ctypes.c_int)]
 
 
+class OutScatter(ctypes.Structure):
+  """Destination of the attention epilogue's scattered stores (mirrors `MdbOutScatter` in csrc/flash_fwd.cu)."""
+  _fields_ = [("n", ctypes.c_int), ("rows_per_rank", ctypes.c_int), ("head_off", ctypes.c_int), ("ptrs", ctypes.c_ulonglong * 8)]
+
+
 # layout constants of the copy plan (csrc/flash_fwd.cu): flags are rows of FLAG_STRIDE per KV segment, counters one per
 # (remote segment, head group) plus one
 COPY_FLAG_STRIDE = 8
@@ -128,6 +133,13 @@ def _declare(L: ctypes.CDLL) -> None:
   for name in ("mdb_flash_fwd_fixed_m", "mdb_flash_fwd_fixed_m_d64"):
     getattr(L, name).argtypes = L.mdb_flash_fwd.argtypes + [c_void_p, c_void_p]
     getattr(L, name).restype = c_int
+  L.mdb_flash_fwd_scatter.argtypes = ([c_void_p, ctypes.POINTER(c_void_p), ctypes.POINTER(c_void_p)] + [c_int] * 4 +
+                                      [ctypes.POINTER(c_int)] + [c_ll] * 12 + [c_float, c_void_p, ctypes.c_uint, c_void_p,
+                                                                              c_void_p, c_void_p])
+  L.mdb_flash_fwd_scatter.restype = c_int
+  L.mdb_rms_rope_fwd_scatter.argtypes = [c_void_p, c_ll, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_float,
+                                         ctypes.POINTER(c_ull), c_int, c_int, c_int, c_void_p]
+  L.mdb_rms_rope_fwd_scatter.restype = c_int
   L.mdb_flash_fwd_tune.argtypes = [c_int, c_int]
   L.mdb_flash_fwd_tune.restype = c_int
   L.mdb_flash_fwd_last_variant.argtypes = [ctypes.POINTER(c_int), ctypes.POINTER(c_int)]

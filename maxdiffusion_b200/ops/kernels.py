@@ -154,6 +154,51 @@ def flash_fwd(q: torch.Tensor, k_list: Sequence[torch.Tensor], v_list: Sequence[
   return (out, lse) if return_lse else out
 
 
+def flash_fwd_scatter(q, k_list, v_list, peer_out_ptrs, rows_per_rank: int, heads_total: int, head_off: int,
+                      scale: float | None = None, seg_flags=None, flag_target: int = 0, plan=None) -> None:
+  """Attention forward (head_dim 128) whose epilogue stores the output rows straight into the ranks that own them:
+  query row r of this launch is row r % rows_per_rank of rank r // rows_per_rank, whose tensor at `peer_out_ptrs[rank]`
+  is [B, rows_per_rank, heads_total, 128]; this launch's head h becomes head head_off + h there. The reverse
+  head <-> sequence exchange of Ulysses attention then needs no kernel of its own. Nothing is returned."""
+  if isinstance(k_list, torch.Tensor):
+    k_list, v_list = [k_list], [v_list]
+  B, Sq, H, D = q.shape
+  assert D == 128 and q.dtype == torch.bfloat16 and q.stride(-1) == 1
+  k0, v0 = k_list[0], v_list[0]
+  for k, v in zip(k_list, v_list):
+    assert k.stride() == k0.stride() and v.stride() == v0.stride() and k.stride(-1) == 1 and v.stride(-1) == 1
+  n = len(k_list)
+  kp = (ctypes.c_void_p * n)(*[k.data_ptr() for k in k_list])
+  vp = (ctypes.c_void_p * n)(*[v.data_ptr() for v in v_list])
+  lens = (ctypes.c_int * n)(*[k.shape[1] for k in k_list])
+  sc = _lib.OutScatter()
+  sc.n, sc.rows_per_rank, sc.head_off = len(peer_out_ptrs), int(rows_per_rank), int(head_off)
+  for i, p in enumerate(peer_out_ptrs):
+    sc.ptrs[i] = int(p)
+  scale = scale if scale is not None else 1.0 / math.sqrt(D)
+  rc = _lib.lib().mdb_flash_fwd_scatter(
+      _lib.ptr(q), kp, vp, B, H, Sq, n, lens, q.stride(0), q.stride(1), q.stride(2), k0.stride(0), k0.stride(1), k0.stride(2),
+      v0.stride(0), v0.stride(1), v0.stride(2), rows_per_rank * heads_total * D, heads_total * D, D, float(scale),
+      _lib.ptr(seg_flags), int(flag_target), ctypes.byref(plan) if plan is not None else None, ctypes.byref(sc), _lib.stream())
+  _lib.check(rc, "mdb_flash_fwd_scatter")
+
+
+def rms_rope_scatter(x, peer_ptrs, me: int, w=None, cos=None, sin=None, mode: str = "row", eps: float = 1e-6) -> None:
+  """RMSNorm (+ RoPE) of x [B, S, C] whose stores ARE the Ulysses exchange: head h of row (b, s) lands in rank
+  h // (H / n)'s buffer [B, n S, H / n, 128] at position me * S + s. `mode`: "row" (RMS over all C channels), "head"
+  (per 128-channel head) or "copy" (no normalisation: the value projection)."""
+  B, S, C = x.shape
+  assert x.dtype == torch.bfloat16 and x.stride(-1) == 1 and x.stride(0) == S * x.stride(1)
+  group = {"row": C, "head": 128, "copy": 0}[mode]
+  if cos is not None:
+    assert cos.dtype == torch.float32 and cos.shape == (S, 64) and cos.is_contiguous() and sin.is_contiguous()
+  arr = (ctypes.c_ulonglong * len(peer_ptrs))(*[int(p) for p in peer_ptrs])
+  rc = _lib.lib().mdb_rms_rope_fwd_scatter(_lib.ptr(x), x.stride(1), _lib.ptr(w), int(mode == "head"), _lib.ptr(cos), _lib.ptr(sin),
+                                           B, S, C, group, float(eps), arr, len(peer_ptrs), int(me), _ctas_per_batch(B, S),
+                                           _lib.stream())
+  _lib.check(rc, "mdb_rms_rope_fwd_scatter")
+
+
 def _strides3(t):
   return (ctypes.c_longlong * 3)(t.stride(0), t.stride(1), t.stride(2))
 

@@ -217,6 +217,7 @@ class ContextParallel:
     self._peers: dict = {}
     self._reducers: dict = {}
     self._a2as: dict = {}
+    self._fused: dict = {}
     self.group = mesh.group("context")
     self.size = mesh.size("context")
     self.rank = mesh.index_in("context") if self.size > 1 else 0
@@ -351,6 +352,66 @@ class ContextParallel:
     ks = [kg[i][:, :valid_lens[i]] for i in range(n)]
     vs = [vg[i][:, :valid_lens[i]] for i in range(n)]
     return OF.attention(q, ks, vs, scale)
+
+  # ---- attention from the raw projections (lets the exchanges ride on the producer / consumer kernels) ---------
+  def _fused_ulysses_for(self, group, numel_qkv, numel_out, dtype):
+    key = id(group)
+    ex = self._fused.get(key)
+    if ex is None or ex.qkv_numel < numel_qkv or ex.out_numel < numel_out:
+      from . import symm
+
+      if not symm.peer_memory_available(group):
+        return None
+      if key not in self._peers:
+        self._peers[key] = symm.PeerGroup(group)
+      old = ex
+      ex = symm.PeerFusedUlysses(self._peers[key], numel_qkv, numel_out, dtype)
+      if old is not None:
+        old.release()
+      self._fused[key] = ex
+    return ex
+
+  def projected_self_attention(self, q, k, v, norm_q, norm_k, cos, sin, heads: int, eps: float, scale=None):
+    """Self-attention from the raw q / k / v projections [B, S_loc, C] of this rank's rows: RMSNorm across heads +
+    RoPE on q and k, attention under this object's strategy, output [B, S_loc, C].
+
+    Under Ulysses (and the Ulysses half of the 2-D split), without autograd and over peer memory, neither exchange is
+    a kernel of its own: the norm / RoPE kernel stores every head into the rank that owns it and the attention epilogue
+    stores every output row into the rank that owns it (`symm.PeerFusedUlysses`; the reference runs two XLA
+    all-to-alls around the kernel, src/maxdiffusion/models/attention_flax.py:875-877, 980-986). Everything else takes
+    the generic path: norm + RoPE locally, then `self_attention`."""
+    B, S, C = q.shape
+    D = C // heads
+    group = self.ulysses_group if self.strategy == "usp" else self.group
+    U = self.ulysses_size if self.strategy == "usp" else self.size
+    fused = (self.strategy in ("ulysses", "usp") and self.peer_memory and U > 1 and group is not None and not torch.is_grad_enabled()
+             and not self.fixed_m and q.is_cuda and q.dtype == torch.bfloat16 and D == 128 and heads % U == 0 and U <= 8
+             and not OF.library_mode() and all(t.stride(-1) == 1 and t.stride(0) == S * t.stride(1) for t in (q, k, v)))
+    ex = self._fused_ulysses_for(group, B * U * S * (heads // U) * D, B * S * C, q.dtype) if fused else None
+    if ex is None:
+      qn = OF.rms_norm_rope(q, norm_q, cos, sin, heads=heads, eps=eps)
+      kn = OF.rms_norm_rope(k, norm_k, cos, sin, heads=heads, eps=eps)
+      return self.self_attention(qn, kn, v.unflatten(-1, (heads, D)), scale).reshape(B, S, C)
+    cosf = cos.float().contiguous() if cos is not None else None
+    sinf = sin.float().contiguous() if sin is not None else None
+    qh, kh, vh = ex.scatter_qkv(q, k, v, norm_q, norm_k, cosf, sinf, eps)
+    if self.strategy == "ulysses":
+      if self.full_len is not None and self.full_len < S * U:
+        kh, vh = kh[:, :self.full_len], vh[:, :self.full_len]
+      return ex.attention(qh, kh, vh, heads, scale).reshape(B, S, C)
+    # 2-D: the K / V of the other ring ranks are pulled by the copy CTAs of the same launch
+    R, seg = self.ring_size, S * U
+    lens = [seg] * R
+    if self.full_len is not None:
+      lens = [max(0, min(seg, self.full_len - r * seg)) for r in range(R)]
+    if R == 1:
+      return ex.attention(qh, kh[:, :lens[0]], vh[:, :lens[0]], heads, scale).reshape(B, S, C)
+    rex = self._exchange_for(self.ring_group, kh)
+    order = rex.order()
+    kg, vg, flags, epoch, plan, keep = rex.plan(kh.contiguous(), vh.contiguous())
+    ks = [kg[i][:, :lens[order[i]]] for i in range(R)]
+    vs = [vg[i][:, :lens[order[i]]] for i in range(R)]
+    return ex.attention(qh, ks, vs, heads, scale, seg_flags=flags, flag_target=epoch, plan=plan).reshape(B, S, C)
 
   def self_attention(self, q, k, v, scale=None):
     """q, k, v: [B, S_loc, H, D] (sequence-sharded). Returns the attention output with the same layout."""

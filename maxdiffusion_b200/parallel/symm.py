@@ -32,7 +32,11 @@ FLAG_RS_READY = 7
 FLAG_RS_ACK = 8
 FLAG_A2A_READY = 9
 FLAG_A2A_ACK = 10
-NUM_FLAG_KINDS = 12
+FLAG_O_READY = 11   # fused Ulysses: attention output rows stored into their owners
+FLAG_O_ACK = 12
+FLAG_QKV_READY = 13  # fused Ulysses: q / k / v heads stored into their owners
+FLAG_QKV_ACK = 14
+NUM_FLAG_KINDS = 16
 WAIT_BUDGET_S = 10.0  # waits on other ranks: long enough for host-side skew (first-step allocation, logging)
 
 
@@ -374,6 +378,78 @@ class PeerAllToAll:
   def seq_to_heads(self, x: torch.Tensor) -> torch.Tensor:
     """[B, n S, H / n, D] (all rows, this rank's heads) -> [B, S, H, D] (this rank's rows, all heads)."""
     return self._exchange("seq_to_heads", x)
+
+
+class PeerFusedUlysses:
+  """Both Ulysses exchanges WITHOUT an exchange kernel (inference; nothing is kept for a backward pass).
+
+  Forward exchange: the RMSNorm + RoPE kernel of q and k, and a layout-only pass of the same kernel for v, store every
+  head straight into the receive buffer of the rank that owns it (`kernels.rms_rope_scatter`), already in the
+  [B, n S, H / n, D] layout attention wants. Reverse exchange: the attention epilogue stores every output row straight
+  into the [B, S, H, D] buffer of the rank that owns the row (`kernels.flash_fwd_scatter`). What remains of the
+  collectives are the epoch flags: READY after a rank's stores (peers wait for all of them before they read), ACK after
+  a rank has consumed a receive slot (peers wait for it before they overwrite the slot two epochs later).
+  """
+
+  def __init__(self, peer: "PeerGroup", qkv_numel: int, out_numel: int, dtype=torch.bfloat16):
+    self.peer, self.n, self.rank = peer, peer.world, peer.rank
+    self.qkv_numel, self.out_numel = -(-qkv_numel // 8) * 8, -(-out_numel // 8) * 8
+    self.elem = torch.tensor([], dtype=dtype).element_size()
+    self.recv, self.recv_ptrs, self.out, self.out_ptrs = [], [], [], []
+    for _ in range(2):
+      t, ptrs, _h = peer.alloc(3 * self.qkv_numel, dtype)
+      self.recv.append(t)
+      self.recv_ptrs.append(ptrs)
+      t, ptrs, _h = peer.alloc(self.out_numel, dtype)
+      self.out.append(t)
+      self.out_ptrs.append(ptrs)
+    self._qkv_epoch = self._out_epoch = None
+    torch.cuda.synchronize()
+    dist.barrier(group=peer.group)
+
+  def release(self) -> None:
+    self.peer.release(self.recv + self.out)
+
+  def scatter_qkv(self, q, k, v, norm_q, norm_k, cos, sin, eps: float):
+    """q, k, v: raw projections [B, S, C] of this rank's rows. Returns (qh, kh, vh) [B, n S, H / n, 128]: views of the
+    receive slot, valid until `attention` has consumed them."""
+    from ..ops import kernels as K
+
+    B, S, C = q.shape
+    hn = C // 128 // self.n
+    numel = B * self.n * S * hn * 128
+    assert numel <= self.qkv_numel
+    e = self.peer.next_epoch(FLAG_QKV_READY)
+    slot = e % 2
+    self.peer.wait(FLAG_QKV_ACK, e - 2)  # every peer has consumed what it received in this slot two epochs ago
+    for i, (t, w, rope) in enumerate(((q, norm_q, True), (k, norm_k, True), (v, None, False))):
+      ptrs = [p + i * self.qkv_numel * self.elem for p in self.recv_ptrs[slot]]
+      K.rms_rope_scatter(t, ptrs, self.rank, w, cos if rope else None, sin if rope else None,
+                         mode="row" if rope else "copy", eps=eps)
+    self.peer.signal(FLAG_QKV_READY, e)
+    self.peer.wait(FLAG_QKV_READY, e)    # every peer's stores into MY slot are complete
+    self._qkv_epoch = e
+    views = [self.recv[slot][i * self.qkv_numel:i * self.qkv_numel + numel].view(B, self.n * S, hn, 128) for i in range(3)]
+    return views
+
+  def attention(self, qh, kh, vh, heads_total: int, scale=None, seg_flags=None, flag_target: int = 0, plan=None):
+    """Attention on this rank's heads; the output rows go to their owners. Returns this rank's [B, S, H, 128] output
+    (a view of the receive slot, valid until the call after next)."""
+    from ..ops import kernels as K
+
+    B, Sn, hn, D = qh.shape
+    S = Sn // self.n
+    if self._out_epoch is not None:
+      self.peer.signal(FLAG_O_ACK, self._out_epoch)  # the consumer of the previous output has been enqueued by now
+    e = self.peer.next_epoch(FLAG_O_READY)
+    slot = e % 2
+    self.peer.wait(FLAG_O_ACK, e - 2)
+    K.flash_fwd_scatter(qh, kh, vh, self.out_ptrs[slot], S, heads_total, self.rank * hn, scale, seg_flags, flag_target, plan)
+    self.peer.signal(FLAG_QKV_ACK, self._qkv_epoch)  # q, k, v of this epoch have been read
+    self.peer.signal(FLAG_O_READY, e)
+    self.peer.wait(FLAG_O_READY, e)
+    self._out_epoch = e
+    return self.out[slot][:B * S * heads_total * D].view(B, S, heads_total, D)
 
 
 class PeerReduceScatter:

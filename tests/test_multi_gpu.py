@@ -233,6 +233,47 @@ def test_two_dimensional_usp_on_4_ranks_peer_transport_matches_nccl():
   assert a == pytest.approx(b, rel=3e-2, abs=3e-2)
 
 
+def _fused_ulysses(rank, world, strategy, ulysses):
+  """`projected_self_attention` without autograd (exchanges folded into the norm / RoPE stores and the attention
+  epilogue) against the same call with autograd enabled (norm + RoPE locally, pull all-to-all kernels)."""
+  from maxdiffusion_b200.parallel.context import ContextParallel
+  from maxdiffusion_b200.parallel.mesh import create_device_mesh
+
+  mesh = create_device_mesh(shape={"data": 1, "fsdp": 1, "context": world, "tensor": 1}, ulysses_shards=ulysses)
+  pctx = ContextParallel(mesh, strategy, peer_memory=True)
+  B, S, H, D = 1, 200, 8, 128
+  errs = []
+  for it in range(4):  # more calls than buffer slots
+    full_len = world * S - (5 if it % 2 else 0)
+    pctx.full_len, pctx.local_len = (full_len, S) if it % 2 else (None, None)
+    torch.manual_seed(50 * it + rank)
+    q, k, v = (torch.randn(B, S, H * D, device="cuda").to(torch.bfloat16) for _ in range(3))
+    wq, wk = (torch.rand(H * D, device="cuda") + 0.5).to(torch.bfloat16), (torch.rand(H * D, device="cuda") + 0.5).to(torch.bfloat16)
+    ang = torch.rand(S, D // 2, device="cuda") * 6.28
+    cos, sin = ang.cos().contiguous(), ang.sin().contiguous()
+    with torch.enable_grad():
+      want = pctx.projected_self_attention(q, k, v, wq, wk, cos, sin, H, 1e-6)
+    with torch.no_grad():
+      got = pctx.projected_self_attention(q, k, v, wq, wk, cos, sin, H, 1e-6).clone()
+    errs.append((got.float() - want.float()).abs().max().item())
+  assert pctx._fused, "the fused exchange was not used"
+  return errs
+
+
+def test_ulysses_exchanges_folded_into_producer_and_consumer_kernels():
+  if torch.cuda.device_count() < 2:
+    pytest.skip("needs 2 GPUs")
+  for errs in _spawn(_fused_ulysses, 2, "ulysses", 2):
+    assert max(errs) < 2e-2, errs
+
+
+def test_two_dimensional_usp_with_folded_ulysses_exchanges_on_4_ranks():
+  if torch.cuda.device_count() < 4:
+    pytest.skip("needs 4 GPUs")
+  for errs in _spawn(_fused_ulysses, 4, "usp", 2):
+    assert max(errs) < 2e-2, errs
+
+
 def _small_allreduce(rank, world):
   import torch.distributed as dist
 
