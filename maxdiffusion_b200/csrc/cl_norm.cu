@@ -12,7 +12,9 @@ namespace cln {
 
 constexpr int MAX_VPL = 4;  // vectors (8 bf16) per lane
 
-template <int G>
+// R rows per group and iteration are loaded before any of them is reduced: a memory-bound kernel needs tens of
+// kilobytes in flight per SM, and one 16-byte load per thread is not enough of them.
+template <int G, int VPL, int R>
 __global__ void __launch_bounds__(256)
 rms_act_kernel(const __nv_bfloat16* __restrict__ x, long long ldx, __nv_bfloat16* __restrict__ y, long long ldy,
                const float* __restrict__ gamma, const float* __restrict__ beta, long long rows, int C, float eps,
@@ -23,60 +25,75 @@ rms_act_kernel(const __nv_bfloat16* __restrict__ x, long long ldx, __nv_bfloat16
   const long long n_groups = static_cast<long long>(gridDim.x) * blockDim.x / G;
   const float scale = sqrtf(static_cast<float>(C));
   // every lane of a warp runs the same number of iterations (the shuffles below name all 32 lanes)
-  const long long iters = (rows + n_groups - 1) / n_groups;
+  const long long iters = (rows + n_groups * R - 1) / (n_groups * R);
   for (long long it = 0; it < iters; ++it) {
-    const long long row = group + it * n_groups;
-    const bool on = row < rows;
-    uint4 v[MAX_VPL];
-    float ss = 0.0f;
+    uint4 v[R][VPL];
+    float ss[R];
 #pragma unroll
-    for (int i = 0; i < MAX_VPL; ++i) {
-      const int vi = lane_in_group + i * G;
-      if (on && vi < vecs) {
-        v[i] = *reinterpret_cast<const uint4*>(x + row * ldx + vi * 8);
-        const uint32_t w[4] = {v[i].x, v[i].y, v[i].z, v[i].w};
+    for (int r = 0; r < R; ++r) {
+      const long long row = group + (it * R + r) * n_groups;
+      ss[r] = 0.0f;
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          const float2 f = unpack_bf16x2(w[j]);
-          ss += f.x * f.x + f.y * f.y;
-        }
+      for (int i = 0; i < VPL; ++i) {
+        const int vi = lane_in_group + i * G;
+        if (row < rows && vi < vecs) v[r][i] = *reinterpret_cast<const uint4*>(x + row * ldx + vi * 8);
       }
     }
 #pragma unroll
-    for (int o = G / 2; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
-    const float inv = scale / fmaxf(sqrtf(ss), eps);
+    for (int r = 0; r < R; ++r) {
+      const long long row = group + (it * R + r) * n_groups;
 #pragma unroll
-    for (int i = 0; i < MAX_VPL; ++i) {
-      const int vi = lane_in_group + i * G;
-      if (on && vi < vecs) {
-        const uint32_t w[4] = {v[i].x, v[i].y, v[i].z, v[i].w};
-        float o[8];
+      for (int i = 0; i < VPL; ++i) {
+        const int vi = lane_in_group + i * G;
+        if (row < rows && vi < vecs) {
+          const uint32_t w[4] = {v[r][i].x, v[r][i].y, v[r][i].z, v[r][i].w};
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          const float2 f = unpack_bf16x2(w[j]);
-          o[2 * j] = f.x * inv;
-          o[2 * j + 1] = f.y * inv;
+          for (int j = 0; j < 4; ++j) {
+            const float2 f = unpack_bf16x2(w[j]);
+            ss[r] += f.x * f.x + f.y * f.y;
+          }
         }
-        const float4 g0 = *reinterpret_cast<const float4*>(gamma + vi * 8);
-        const float4 g1 = *reinterpret_cast<const float4*>(gamma + vi * 8 + 4);
-        o[0] *= g0.x; o[1] *= g0.y; o[2] *= g0.z; o[3] *= g0.w;
-        o[4] *= g1.x; o[5] *= g1.y; o[6] *= g1.z; o[7] *= g1.w;
-        if (beta != nullptr) {
-          const float4 b0 = *reinterpret_cast<const float4*>(beta + vi * 8);
-          const float4 b1 = *reinterpret_cast<const float4*>(beta + vi * 8 + 4);
-          o[0] += b0.x; o[1] += b0.y; o[2] += b0.z; o[3] += b0.w;
-          o[4] += b1.x; o[5] += b1.y; o[6] += b1.z; o[7] += b1.w;
-        }
-        if (act) {
+      }
 #pragma unroll
-          for (int j = 0; j < 8; ++j) o[j] = o[j] / (1.0f + __expf(-o[j]));
+      for (int o = G / 2; o > 0; o >>= 1) ss[r] += __shfl_xor_sync(0xffffffffu, ss[r], o);
+    }
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+      const long long row = group + (it * R + r) * n_groups;
+      const float inv = scale / fmaxf(sqrtf(ss[r]), eps);
+#pragma unroll
+      for (int i = 0; i < VPL; ++i) {
+        const int vi = lane_in_group + i * G;
+        if (row < rows && vi < vecs) {
+          const uint32_t w[4] = {v[r][i].x, v[r][i].y, v[r][i].z, v[r][i].w};
+          float o[8];
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const float2 f = unpack_bf16x2(w[j]);
+            o[2 * j] = f.x * inv;
+            o[2 * j + 1] = f.y * inv;
+          }
+          const float4 g0 = *reinterpret_cast<const float4*>(gamma + vi * 8);
+          const float4 g1 = *reinterpret_cast<const float4*>(gamma + vi * 8 + 4);
+          o[0] *= g0.x; o[1] *= g0.y; o[2] *= g0.z; o[3] *= g0.w;
+          o[4] *= g1.x; o[5] *= g1.y; o[6] *= g1.z; o[7] *= g1.w;
+          if (beta != nullptr) {
+            const float4 b0 = *reinterpret_cast<const float4*>(beta + vi * 8);
+            const float4 b1 = *reinterpret_cast<const float4*>(beta + vi * 8 + 4);
+            o[0] += b0.x; o[1] += b0.y; o[2] += b0.z; o[3] += b0.w;
+            o[4] += b1.x; o[5] += b1.y; o[6] += b1.z; o[7] += b1.w;
+          }
+          if (act) {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) o[j] = o[j] / (1.0f + __expf(-o[j]));
+          }
+          uint4 ov;
+          ov.x = pack_bf16x2(o[0], o[1]);
+          ov.y = pack_bf16x2(o[2], o[3]);
+          ov.z = pack_bf16x2(o[4], o[5]);
+          ov.w = pack_bf16x2(o[6], o[7]);
+          *reinterpret_cast<uint4*>(y + row * ldy + vi * 8) = ov;
         }
-        uint4 ov;
-        ov.x = pack_bf16x2(o[0], o[1]);
-        ov.y = pack_bf16x2(o[2], o[3]);
-        ov.z = pack_bf16x2(o[4], o[5]);
-        ov.w = pack_bf16x2(o[6], o[7]);
-        *reinterpret_cast<uint4*>(y + row * ldy + vi * 8) = ov;
       }
     }
   }
@@ -94,16 +111,23 @@ extern "C" int mdb_rms_act_cl(const void* x, long long ldx, void* y, long long l
   if ((C & 7) || C <= 0 || C > 8 * 32 * MAX_VPL || (ldx & 7) || (ldy & 7) || gamma == nullptr) return 3701;
   const int vecs = C >> 3;
   const int G = vecs <= 8 ? 8 : (vecs <= 16 ? 16 : 32);
+  const int vpl = (vecs + G - 1) / G;
   const long long groups_per_block = 256 / G;
-  long long blocks = (rows + groups_per_block - 1) / groups_per_block;
-  const long long cap = static_cast<long long>(mdb::sm_count()) * 16;
+  long long blocks = (rows + groups_per_block * 4 - 1) / (groups_per_block * 4);
+  const long long cap = static_cast<long long>(mdb::sm_count()) * 8;
   if (blocks > cap) blocks = cap;
+  if (blocks < 1) blocks = 1;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   const __nv_bfloat16* xp = static_cast<const __nv_bfloat16*>(x);
   __nv_bfloat16* yp = static_cast<__nv_bfloat16*>(y);
-  if (G == 8) rms_act_kernel<8><<<static_cast<int>(blocks), 256, 0, st>>>(xp, ldx, yp, ldy, gamma, beta, rows, C, eps, act);
-  else if (G == 16) rms_act_kernel<16><<<static_cast<int>(blocks), 256, 0, st>>>(xp, ldx, yp, ldy, gamma, beta, rows, C, eps, act);
-  else rms_act_kernel<32><<<static_cast<int>(blocks), 256, 0, st>>>(xp, ldx, yp, ldy, gamma, beta, rows, C, eps, act);
+  const int nb = static_cast<int>(blocks);
+#define MDB_RMS_ACT(GG, VV, RR) rms_act_kernel<GG, VV, RR><<<nb, 256, 0, st>>>(xp, ldx, yp, ldy, gamma, beta, rows, C, eps, act)
+  if (G == 8) MDB_RMS_ACT(8, 1, 4);
+  else if (G == 16) MDB_RMS_ACT(16, 1, 4);
+  else if (vpl == 1) MDB_RMS_ACT(32, 1, 4);
+  else if (vpl == 2) MDB_RMS_ACT(32, 2, 4);
+  else MDB_RMS_ACT(32, 4, 2);
+#undef MDB_RMS_ACT
   return static_cast<int>(cudaGetLastError());
 }
 
@@ -299,5 +323,106 @@ extern "C" int mdb_gn_cl_apply(const void* x, const void* dy, void* out, const f
   gn_cl_apply_kernel<<<static_cast<int>(blocks), 256, 0, static_cast<cudaStream_t>(stream)>>>(
       static_cast<const __nv_bfloat16*>(x), static_cast<const __nv_bfloat16*>(dy), static_cast<__nv_bfloat16*>(out), ca, cb,
       cc, fa, fb, total, HW, C, act);
+  return static_cast<int>(cudaGetLastError());
+}
+
+// ---------------------------------------------------------------------------------------------------------------
+// Row softmax, in place or out of place: y[r, :] = softmax(x[r, :]) for bf16 rows of up to 32768 columns, fp32 math.
+// One CTA per row, the row lives in registers between the two reductions (one read, one write). It sits between the two
+// GEMMs of attention with a head size the flash kernels are not built for (the Wan VAE's single 384-wide head,
+// src/maxdiffusion/models/wan/autoencoder_kl_wan.py:487-546): scores = Q K^T on the GEMM kernel, this, then P V.
+// ---------------------------------------------------------------------------------------------------------------
+namespace mdb {
+namespace cln {
+
+constexpr int SM_THREADS = 256;
+constexpr int SM_MAX_VPT = 16;  // vectors of 8 per thread
+
+__device__ __forceinline__ float block_reduce(float v, bool is_max, float* red) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const float w = __shfl_xor_sync(0xffffffffu, v, o);
+    v = is_max ? fmaxf(v, w) : v + w;
+  }
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  __syncthreads();  // red may still be read from the previous reduction
+  if (lane == 0) red[warp] = v;
+  __syncthreads();
+  float t = red[0];
+#pragma unroll
+  for (int i = 1; i < SM_THREADS / 32; ++i) t = is_max ? fmaxf(t, red[i]) : t + red[i];
+  return t;
+}
+
+template <int VPT>
+__global__ void __launch_bounds__(SM_THREADS)
+softmax_rows_kernel(const __nv_bfloat16* __restrict__ x, long long ldx, __nv_bfloat16* __restrict__ y, long long ldy, int cols) {
+  __shared__ float red[SM_THREADS / 32];
+  const long long row = blockIdx.x;
+  const int vecs = cols >> 3;
+  float v[VPT][8];
+  float mx = -INFINITY;
+#pragma unroll
+  for (int i = 0; i < VPT; ++i) {
+    const int vi = threadIdx.x + i * SM_THREADS;
+    if (vi < vecs) {
+      const uint4 u = *reinterpret_cast<const uint4*>(x + row * ldx + vi * 8);
+      const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float2 f = unpack_bf16x2(w[j]);
+        v[i][2 * j] = f.x;
+        v[i][2 * j + 1] = f.y;
+        mx = fmaxf(mx, fmaxf(f.x, f.y));
+      }
+    }
+  }
+  mx = block_reduce(mx, true, red);
+  float sum = 0.0f;
+#pragma unroll
+  for (int i = 0; i < VPT; ++i) {
+    const int vi = threadIdx.x + i * SM_THREADS;
+    if (vi < vecs) {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        v[i][j] = __expf(v[i][j] - mx);
+        sum += v[i][j];
+      }
+    }
+  }
+  sum = block_reduce(sum, false, red);
+  const float inv = 1.0f / sum;
+#pragma unroll
+  for (int i = 0; i < VPT; ++i) {
+    const int vi = threadIdx.x + i * SM_THREADS;
+    if (vi < vecs) {
+      uint4 o;
+      o.x = pack_bf16x2(v[i][0] * inv, v[i][1] * inv);
+      o.y = pack_bf16x2(v[i][2] * inv, v[i][3] * inv);
+      o.z = pack_bf16x2(v[i][4] * inv, v[i][5] * inv);
+      o.w = pack_bf16x2(v[i][6] * inv, v[i][7] * inv);
+      *reinterpret_cast<uint4*>(y + row * ldy + vi * 8) = o;
+    }
+  }
+}
+
+}  // namespace cln
+}  // namespace mdb
+
+// x, y: bf16 [rows, cols] with leading dimensions ldx / ldy (multiples of 8); cols a multiple of 8, at most 32768.
+extern "C" int mdb_softmax_rows(const void* x, long long ldx, void* y, long long ldy, long long rows, int cols, void* stream) {
+  using namespace mdb::cln;
+  if (rows <= 0) return 0;
+  if ((cols & 7) || cols <= 0 || cols > 8 * SM_THREADS * SM_MAX_VPT || (ldx & 7) || (ldy & 7) || rows >= (1ll << 31)) return 3704;
+  const int vpt = ((cols >> 3) + SM_THREADS - 1) / SM_THREADS;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const __nv_bfloat16* xp = static_cast<const __nv_bfloat16*>(x);
+  __nv_bfloat16* yp = static_cast<__nv_bfloat16*>(y);
+  const int grid = static_cast<int>(rows);
+  if (vpt <= 1) softmax_rows_kernel<1><<<grid, SM_THREADS, 0, st>>>(xp, ldx, yp, ldy, cols);
+  else if (vpt <= 2) softmax_rows_kernel<2><<<grid, SM_THREADS, 0, st>>>(xp, ldx, yp, ldy, cols);
+  else if (vpt <= 4) softmax_rows_kernel<4><<<grid, SM_THREADS, 0, st>>>(xp, ldx, yp, ldy, cols);
+  else if (vpt <= 8) softmax_rows_kernel<8><<<grid, SM_THREADS, 0, st>>>(xp, ldx, yp, ldy, cols);
+  else softmax_rows_kernel<16><<<grid, SM_THREADS, 0, st>>>(xp, ldx, yp, ldy, cols);
   return static_cast<int>(cudaGetLastError());
 }

@@ -110,6 +110,18 @@ def split_fused(fused: torch.Tensor, n: int):
   return tuple(fused[..., i * c:(i + 1) * c] for i in range(n))
 
 
+def _norm_rope(mod, x, weight, cos=None, sin=None):
+  """RMSNorm across all heads (+ RoPE) of a projection; under tensor parallelism (`mod.tp_group`, set by
+  `parallel.tensor.apply_tensor_parallel_wan`) the projection holds this rank's heads only and the statistic is summed
+  over the tensor group."""
+  tp = getattr(mod, "tp_group", None)
+  if tp is not None:
+    from ...parallel.tensor import tp_rms_norm_rope
+
+    return tp_rms_norm_rope(x, weight, cos, sin, mod.heads, mod.eps, tp, mod.tp_full_dim)
+  return OF.rms_norm_rope(x, weight, cos, sin, heads=mod.heads, eps=mod.eps)
+
+
 class WanSelfAttention(nn.Module):
 
   def __init__(self, dim: int, heads: int, eps: float):
@@ -124,16 +136,16 @@ class WanSelfAttention(nn.Module):
     B, S, C = x.shape
     q, k, v = split_fused(self.to_qkv(x), 3)
     cos, sin = rope
-    if pctx is not None:
+    if pctx is not None and getattr(self, "tp_group", None) is None:
       # the strategy object sees the raw projections: under Ulysses the exchanges ride on the norm / RoPE stores and
       # on the attention epilogue instead of running as kernels of their own
       o = pctx.projected_self_attention(q, k, v, self.norm_q, self.norm_k, cos, sin, self.heads, self.eps)
       return project_gated_residual(self.to_out, o, residual, gate)
-    q = OF.rms_norm_rope(q, self.norm_q, cos, sin, heads=self.heads, eps=self.eps)
-    k = OF.rms_norm_rope(k, self.norm_k, cos, sin, heads=self.heads, eps=self.eps)
-    v = v.unflatten(-1, (self.heads, C // self.heads))
-    o = OF.attention(q, k, v)
-    return project_gated_residual(self.to_out, o.reshape(B, S, C), residual, gate)
+    q = _norm_rope(self, q, self.norm_q, cos, sin)
+    k = _norm_rope(self, k, self.norm_k, cos, sin)
+    v = v.unflatten(-1, (self.heads, v.shape[-1] // self.heads))
+    o = pctx.self_attention(q, k, v) if pctx is not None else OF.attention(q, k, v)
+    return project_gated_residual(self.to_out, o.reshape(B, S, -1), residual, gate)
 
 
 class WanCrossAttention(nn.Module):
@@ -158,22 +170,22 @@ class WanCrossAttention(nn.Module):
       context = torch.cat([context_image, context], dim=1)
     B, T, C = context.shape[0], context.shape[1], self.to_q.weight.shape[0]
     k, v = split_fused(self.to_kv(context), 2)
-    k = OF.rms_norm_rope(k, self.norm_k, heads=self.heads, eps=self.eps)
+    k = _norm_rope(self, k, self.norm_k)
     out = {"text": (k, v.unflatten(-1, (self.heads, C // self.heads)))}
     if self.has_image and context_image is not None:
       ki, vi = split_fused(self.add_kv_proj(context_image), 2)
-      ki = OF.rms_norm_rope(ki, self.norm_added_k, heads=self.heads, eps=self.eps)
+      ki = _norm_rope(self, ki, self.norm_added_k)
       out["image"] = (ki, vi.unflatten(-1, (self.heads, C // self.heads)))
     return out
 
   def forward(self, x, context, context_image, residual, cached_kv=None):
     B, S, C = x.shape
-    q = OF.rms_norm_rope(self.to_q(x), self.norm_q, heads=self.heads, eps=self.eps)
+    q = _norm_rope(self, self.to_q(x), self.norm_q)
     kv = cached_kv if cached_kv is not None else self.compute_kv(context, context_image)
     o = OF.attention(q, *kv["text"])
     if "image" in kv:
       o = o + OF.attention(q, *kv["image"])
-    return project_gated_residual(self.to_out, o.reshape(B, S, C), residual, None)
+    return project_gated_residual(self.to_out, o.reshape(B, S, -1), residual, None)
 
 
 class WanBlock(nn.Module):

@@ -11,8 +11,9 @@ the same parameters) as the NCDHW PyTorch path but keeps every activation as `[B
     writes its two channel halves straight into the even / odd frames of the output (:245-389) -- no interleave pass;
   * 1x1 convolutions are GEMMs on the tcgen05 GEMM kernel.
 
-The mid-block attention (one head of 384 channels over the H*W positions of a frame, :487-546) runs on PyTorch's SDPA:
-the flash kernels of this repository are built for head sizes 64 and 128.
+The mid-block attention (one head of 384 channels over the H*W positions of a frame, :487-546) is two GEMMs around a
+row-softmax kernel (`ops.conv.wide_head_attention`): the flash kernels of this repository are built for head sizes
+64 and 128, and a latent frame has few enough positions for the score matrix to be materialised.
 """
 from __future__ import annotations
 
@@ -116,9 +117,10 @@ class ChannelsLastDecoder:
     B, T, H, W, C = x.shape
     y = self.norm(blk.norm, x, False)
     qkv = self.pointwise(blk.to_qkv.weight, blk.to_qkv.bias, y).reshape(B * T, H * W, 3, C)
-    q, k, v = (qkv[:, :, i].unsqueeze(1) for i in range(3))
-    o = F.scaled_dot_product_attention(q, k, v).squeeze(1).reshape(B, T, H, W, C)
-    return self.pointwise(blk.proj.weight, blk.proj.bias, o, residual=x.contiguous())
+    # one head of C channels over the H * W positions of every frame: GEMM -> row softmax -> GEMM on this
+    # repository's kernels (the flash kernels are built for head sizes 64 and 128)
+    o = torch.stack([OC.wide_head_attention(qkv[f, :, 0], qkv[f, :, 1], qkv[f, :, 2]) for f in range(B * T)])
+    return self.pointwise(blk.proj.weight, blk.proj.bias, o.reshape(B, T, H, W, C), residual=x.contiguous())
 
   def resample(self, rs, x, hist, first_chunk: bool):
     B, T, H, W, C = x.shape

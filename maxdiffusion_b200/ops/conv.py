@@ -41,6 +41,8 @@ def _declare(L):
   L.mdb_conv_igemm_tune.restype = c_int
   L.mdb_conv_wgrad.argtypes = [c_void_p, c_void_p, c_void_p, c_ll, c_ll, c_int, c_int, c_int, llp, c_int, c_void_p]
   L.mdb_conv_wgrad.restype = c_int
+  L.mdb_softmax_rows.argtypes = [c_void_p, c_ll, c_void_p, c_ll, c_ll, c_int, c_void_p]
+  L.mdb_softmax_rows.restype = c_int
   L.mdb_gn_cl_sums.argtypes = [c_void_p] * 5 + [c_int] * 4 + [c_void_p]
   L.mdb_gn_cl_sums.restype = c_int
   L.mdb_gn_cl_apply.argtypes = [c_void_p] * 8 + [c_int] * 4 + [c_void_p]
@@ -414,6 +416,30 @@ def rms_act(x: torch.Tensor, gamma: torch.Tensor, beta: Optional[torch.Tensor] =
                                  int(silu), _lib.stream())
   _lib.check(rc, "mdb_rms_act_cl")
   return y
+
+
+def softmax_rows(x: torch.Tensor) -> torch.Tensor:
+  """Row softmax of a bf16 matrix (fp32 math), in place."""
+  assert x.dim() == 2 and x.dtype == torch.bfloat16 and x.stride(1) == 1
+  rc = _lib.lib().mdb_softmax_rows(_lib.ptr(x), x.stride(0), _lib.ptr(x), x.stride(0), x.shape[0], x.shape[1], _lib.stream())
+  _lib.check(rc, "mdb_softmax_rows")
+  return x
+
+
+def wide_head_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, scale: Optional[float] = None) -> torch.Tensor:
+  """Single-head attention for head sizes the flash kernels are not built for (q, k, v: [T, D], D a multiple of 8):
+  scores on the tcgen05 GEMM, row softmax, P V on the GEMM. The score matrix is materialised in bf16 ([T, T]), which
+  is fine for the few thousand positions of a latent frame."""
+  from . import kernels as K
+
+  T, D = q.shape
+  scale = scale if scale is not None else D ** -0.5
+  if not use_kernel(q) or T % 8 or D % 8 or T > 32768:
+    p = torch.softmax((q.float() @ k.float().t()) * scale, dim=-1)
+    return (p @ v.float()).to(q.dtype)
+  scores = K.gemm(q.contiguous(), k.contiguous(), alpha=scale)         # [T, T] = scale * Q K^T
+  softmax_rows(scores)
+  return K.gemm(scores, v.contiguous(), b_mn=True)                     # [T, D] = P V   (V is [K = T, N = D])
 
 
 # ---------------------------------------------------------------------------------------------

@@ -36,7 +36,9 @@ FLAG_O_READY = 11   # fused Ulysses: attention output rows stored into their own
 FLAG_O_ACK = 12
 FLAG_QKV_READY = 13  # fused Ulysses: q / k / v heads stored into their owners
 FLAG_QKV_ACK = 14
-NUM_FLAG_KINDS = 16
+FLAG_TP_READY = 15   # tensor-parallel partial products (parallel.tensor.PeerAllReduce)
+FLAG_TP_ACK = 16
+NUM_FLAG_KINDS = 18
 WAIT_BUDGET_S = 10.0  # waits on other ranks: long enough for host-side skew (first-step allocation, logging)
 
 

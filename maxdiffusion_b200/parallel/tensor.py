@@ -9,7 +9,12 @@ Here the two halves are explicit:
   * `RowParallelLinear`: weight columns (input features) split; input sharded, partial outputs summed over the
     group. With peer memory the sum is `parallel.symm`'s pull-reduce over symmetric buffers, else an NCCL all-reduce;
   * `shard_attention_heads` / `shard_mlp` split an existing block's fused projections in place.
-GEMMs run on the tcgen05 kernel (`ops.functional.linear`); only the reduction crosses NVLink.
+  * `apply_tensor_parallel_wan` shards the blocks of a `WanModel` in place (heads and FFN units over the group) and
+    is what the trainers and pipelines call when the mesh's `tensor` axis is larger than one.
+GEMMs run on the tcgen05 kernel (`ops.functional.linear`); only the reduction crosses NVLink. With peer memory the
+row-parallel GEMM writes its partial product straight into a symmetric buffer and every rank sums the partials of all
+ranks in rank order with one pull kernel (`PeerAllReduce`: bitwise identical results on every rank, no NCCL call);
+otherwise the reduction is an NCCL all-reduce.
 """
 from __future__ import annotations
 
@@ -18,6 +23,83 @@ import torch.distributed as dist
 import torch.nn as nn
 
 from ..ops import functional as OF
+
+
+class PeerAllReduce:
+  """Sum of one bf16 tensor per rank over peer memory: producers write their partial into `buffer(shape)` (a view of a
+  symmetric slot, e.g. as the `out=` of the row-parallel GEMM), `reduce()` raises the epoch flag, waits (bounded) for
+  the peers and pulls every rank's partial in rank order, adding in fp32 and rounding once."""
+
+  def __init__(self, group, max_numel: int):
+    from . import symm
+
+    self._symm = symm
+    self.peer = symm.PeerGroup(group)
+    self.n, self.rank = self.peer.world, self.peer.rank
+    self.numel = -(-max_numel // 8) * 8
+    self.slots, self.slot_ptrs = [], []
+    for _ in range(2):
+      t, ptrs, _h = self.peer.alloc(self.numel, torch.bfloat16)
+      self.slots.append(t)
+      self.slot_ptrs.append(ptrs)
+    self.epoch = 0
+    torch.cuda.synchronize()
+    dist.barrier(group=group)
+
+  def buffer(self, shape) -> torch.Tensor:
+    numel = 1
+    for d in shape:
+      numel *= int(d)
+    assert numel <= self.numel and numel % 8 == 0
+    self.epoch = self.peer.next_epoch(self._symm.FLAG_TP_READY)
+    self.peer.wait(self._symm.FLAG_TP_ACK, self.epoch - 2)  # every peer has read this slot's previous content
+    self._shape, self._numel = tuple(shape), numel
+    return self.slots[self.epoch % 2][:numel].view(shape)
+
+  def reduce(self) -> torch.Tensor:
+    import ctypes
+
+    from ..ops import _lib
+
+    symm, e = self._symm, self.epoch
+    self.peer.signal(symm.FLAG_TP_READY, e)
+    self.peer.wait(symm.FLAG_TP_READY, e)
+    out = torch.empty(self._shape, dtype=torch.bfloat16, device=self.slots[0].device)
+    arr = (ctypes.c_ulonglong * self.n)(*self.slot_ptrs[e % 2])
+    rc = _lib.lib().mdb_pull_reduce(arr, self.n, _lib.ptr(out), self._numel, 32, _lib.stream())
+    _lib.check(rc, "mdb_pull_reduce")
+    self.peer.signal(symm.FLAG_TP_ACK, e)
+    return out
+
+
+_PEER_AR: dict = {}
+
+
+def _peer_allreduce_for(group, numel: int):
+  """The peer-memory all-reduce of a group (created on first use and grown when a larger tensor arrives), or None."""
+  from . import symm
+
+  if group is None or not symm.peer_memory_available(group):
+    return None
+  ar = _PEER_AR.get(id(group))
+  if ar is None or ar.numel < numel:
+    ar = PeerAllReduce(group, numel)
+    _PEER_AR[id(group)] = ar
+  return ar
+
+
+def all_reduce_sum(x: torch.Tensor, group, peer_memory: bool = True) -> torch.Tensor:
+  """Sum over the group; over peer memory for CUDA bf16 tensors when available, else NCCL / Gloo."""
+  if group is None:
+    return x
+  if peer_memory and x.is_cuda and x.dtype == torch.bfloat16 and x.numel() % 8 == 0:
+    ar = _peer_allreduce_for(group, x.numel())
+    if ar is not None:
+      ar.buffer(x.shape).copy_(x)
+      return ar.reduce()
+  x = x.contiguous()
+  dist.all_reduce(x, group=group)
+  return x
 
 
 class _CopyToGroup(torch.autograd.Function):
@@ -30,10 +112,7 @@ class _CopyToGroup(torch.autograd.Function):
 
   @staticmethod
   def backward(ctx, g):
-    if ctx.group is not None:
-      g = g.contiguous()
-      dist.all_reduce(g, group=ctx.group)
-    return g, None
+    return all_reduce_sum(g, ctx.group), None
 
 
 class _ReduceFromGroup(torch.autograd.Function):
@@ -41,10 +120,7 @@ class _ReduceFromGroup(torch.autograd.Function):
 
   @staticmethod
   def forward(ctx, x, group):
-    if group is not None:
-      x = x.contiguous()
-      dist.all_reduce(x, group=group)
-    return x
+    return all_reduce_sum(x, group)
 
   @staticmethod
   def backward(ctx, g):
@@ -108,6 +184,17 @@ class RowParallelLinear(nn.Module):
         self.bias.copy_(bias)
 
   def forward(self, x):
+    if (self.group is not None and not torch.is_grad_enabled() and x.is_cuda and x.dtype == torch.bfloat16
+        and not OF.library_mode()):
+      # inference: the GEMM writes its partial product straight into the symmetric slot the peers pull from
+      from ..ops import kernels as K
+
+      rows = x.reshape(-1, x.shape[-1])
+      ar = _peer_allreduce_for(self.group, rows.shape[0] * self.out_features)
+      if ar is not None and self.out_features % 8 == 0 and rows.shape[1] % 8 == 0:
+        K.gemm(rows, self.weight.to(torch.bfloat16), out=ar.buffer((rows.shape[0], self.out_features)))
+        y = ar.reduce().view(*x.shape[:-1], self.out_features)
+        return y + self.bias.to(y.dtype) if self.bias is not None else y
     y = _ReduceFromGroup.apply(OF.linear(x, self.weight, None), self.group)
     return y + self.bias.to(y.dtype) if self.bias is not None else y
 
@@ -120,3 +207,88 @@ def parallel_mlp(dim: int, hidden: int, group=None):
 def parallel_attention_projections(dim: int, group=None):
   """(fused qkv, out) projections split by heads: every rank computes attention for heads/n heads."""
   return ColumnParallelLinear(dim, 3 * dim, group=group, chunks=3), RowParallelLinear(dim, dim, group=group)
+
+
+# ---------------------------------------------------------------------------------------------------------------
+# Wan blocks over the tensor axis
+# ---------------------------------------------------------------------------------------------------------------
+class _AllReduceSum(torch.autograd.Function):
+  """Sum over the group in both directions (a statistic every rank needs and every rank contributes to)."""
+
+  @staticmethod
+  def forward(ctx, x, group):
+    ctx.group = group
+    y = x.clone()
+    dist.all_reduce(y, group=group)
+    return y
+
+  @staticmethod
+  def backward(ctx, g):
+    g = g.contiguous().clone()
+    dist.all_reduce(g, group=ctx.group)
+    return g, None
+
+
+def tp_rms_norm_rope(x, w, cos, sin, heads_local: int, eps: float, group, full_dim: int):
+  """RMSNorm over ALL heads of the model (`full_dim` channels, of which this rank holds x.shape[-1]) followed by RoPE:
+  the sum of squares of the local slice is summed over the tensor group (reference: the norm spans the `heads` axis
+  that the `tensor` mesh axis shards, src/maxdiffusion/models/attention_flax.py:2468-2525)."""
+  from ..ops import ref
+
+  B, S, C = x.shape
+  xf = x.float()
+  ss = (xf * xf).sum(-1, keepdim=True)
+  if group is not None:
+    ss = _AllReduceSum.apply(ss, group)
+  y = xf * torch.rsqrt(ss / full_dim + eps)
+  if w is not None:
+    y = y * w.float()
+  y = y.view(B, S, heads_local, C // heads_local)
+  if cos is not None:
+    y = ref.rope_rotate(y, cos, sin)
+  return y.to(x.dtype)
+
+
+def _column(lin, group, chunks=1):
+  new = ColumnParallelLinear(lin.in_features, lin.out_features, bias=lin.bias is not None, group=group, chunks=chunks)
+  new = new.to(device=lin.weight.device, dtype=lin.weight.dtype)
+  new.load_full(lin.weight.data, None if lin.bias is None else lin.bias.data)
+  return new
+
+
+def _row(lin, group):
+  new = RowParallelLinear(lin.in_features, lin.out_features, bias=lin.bias is not None, group=group)
+  new = new.to(device=lin.weight.device, dtype=lin.weight.dtype)
+  new.load_full(lin.weight.data, None if lin.bias is None else lin.bias.data)
+  return new
+
+
+def apply_tensor_parallel_wan(model, group) -> int:
+  """Shards every block of a `WanModel` over `group` in place: attention heads (q / k / v column-parallel, output
+  projection row-parallel, the across-heads RMSNorm with a summed statistic) and FFN units (up column-, down
+  row-parallel). Every rank must hold the same full weights when this is called. Returns the group size."""
+  n, r = _size_rank(group)
+  if n == 1:
+    return 1
+  for blk in model.blocks:
+    for attn, fused, chunks in ((blk.attn1, "to_qkv", 3), (blk.attn2, "to_kv", 2)):
+      heads = attn.heads
+      if heads % n != 0:
+        raise ValueError(f"{heads} attention heads cannot be split over {n} tensor ranks")
+      dim = attn.to_out.in_features
+      setattr(attn, fused, _column(getattr(attn, fused), group, chunks))
+      if fused == "to_kv":
+        attn.to_q = _column(attn.to_q, group)
+        if getattr(attn, "has_image", False):
+          attn.add_kv_proj = _column(attn.add_kv_proj, group, 2)
+          attn.norm_added_k = torch.nn.Parameter(attn.norm_added_k.data[r * dim // n:(r + 1) * dim // n].clone())
+      attn.to_out = _row(attn.to_out, group)
+      for name in ("norm_q", "norm_k"):
+        w = getattr(attn, name)
+        setattr(attn, name, torch.nn.Parameter(w.data[r * dim // n:(r + 1) * dim // n].clone()))
+      attn.heads = heads // n
+      attn.tp_group, attn.tp_full_dim = group, dim
+    blk.ffn_in = _column(blk.ffn_in, group)
+    blk.ffn_out = _row(blk.ffn_out, group)
+  model.tp_group = group
+  return n

@@ -75,6 +75,12 @@ class WanPipeline:
       self.pctx = ContextParallel(self.mesh, str(config.get("context_strategy", "ring")),
                                   peer_memory=bool(config.get("peer_memory_transport", True)) and self.device.type == "cuda",
                                   fixed_m=fixed_m)
+    if self.mesh.size("tensor") > 1:
+      from ...parallel.tensor import apply_tensor_parallel_wan
+
+      for m in filter(None, (self.transformer, self.transformer_2)):
+        if getattr(m, "tp_group", None) is None:
+          apply_tensor_parallel_wan(m, self.mesh.group("tensor"))
     self.prompt_cache = PromptCache()
     from ...models.quantizations import get_quantization_mode, quantize_model
 

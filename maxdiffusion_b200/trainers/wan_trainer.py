@@ -85,6 +85,11 @@ class WanTrainer:
       model = model.to(device=self.device, dtype=self.dtype)
       model.remat_policy = remat
     model.remat_keep_blocks = int(config.get("remat_keep_blocks", 0) or 0)
+    if self.mesh.size("tensor") > 1:
+      # every rank built the same full model (same seed): keep this rank's heads and FFN units of every block
+      from ..parallel.tensor import apply_tensor_parallel_wan
+
+      apply_tensor_parallel_wan(model, self.mesh.group("tensor"))
     self.model = model
 
     opt = AdamWConfig(
@@ -194,7 +199,9 @@ class WanTrainer:
     replicas = self.mesh.size("data") * self.mesh.size("fsdp")
     loss = local * (pred.numel() / total / replicas)
     loss.backward()
-    stats = self.engine.finish_step(model_group=self.mesh.group("model"))
+    # replicated (root) parameters see different tokens / samples on the ranks of the shard group; the tensor ranks of a
+    # replica compute identical gradients for them, so the tensor axis is not summed over
+    stats = self.engine.finish_step(model_group=self.mesh.group("shard"))
     loss_value = loss.detach()
     if self.mesh.world_size > 1:
       loss_value = loss_value.clone()

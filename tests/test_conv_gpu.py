@@ -227,3 +227,16 @@ def test_unet_on_the_conv_kernels_matches_fp32_modules_forward_and_backward():
     assert rel < 0.12, (n, rel)
     checked += 1
   assert checked > 20
+
+
+@pytest.mark.parametrize("T,D", [(96, 128), (1000, 384), (6240, 384)])
+def test_wide_head_attention_matches_fp32(T, D):
+  from maxdiffusion_b200.ops import conv as OC
+
+  q, k, v = _rand((T, D), 1), _rand((T, D), 2), _rand((T, D), 3)
+  got = OC.wide_head_attention(q, k, v)
+  want = torch.softmax((q.float() @ k.float().t()) * D ** -0.5, dim=-1) @ v.float()
+  _close(got, want, tol=3e-2)
+  x = _rand((37, 2048), 4, scale=4.0)
+  want_sm = torch.softmax(x.float(), dim=-1)
+  assert (OC.softmax_rows(x.clone()).float() - want_sm).abs().max() < 2e-3

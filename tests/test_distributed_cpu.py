@@ -215,3 +215,28 @@ def test_cfg_as_data_parallelism_matches_the_batched_form():
   got = run_ranks(_cfg_pipeline, 2, 2)
   for lat in got:
     assert torch.allclose(lat, want, atol=2e-5, rtol=1e-4)
+
+
+def _train_tp(rank, world):
+  """tensor = 2 (heads and FFN units split), through the trainer: losses and the gradient norm must be those of the
+  single-process run (sharded parameters: the norm is the root of the summed squares of the shards)."""
+  from maxdiffusion_b200 import pyconfig
+  from maxdiffusion_b200.parallel.mesh import create_device_mesh
+  from maxdiffusion_b200.trainers.wan_trainer import WanTrainer
+
+  config = pyconfig.initialize(
+      ["t", CFG, "run_name=t", "height=64", "width=48", "num_frames=9", "dataset_type=synthetic", "wan_preset=tiny",
+       f"wan_config_overrides={TINY}", "remat_policy=FULL", "warmup_steps_fraction=0.0", "log_config=false",
+       "write_metrics=false", "learning_rate=1e-3", "attention=flash", f"per_device_batch_size={1.0 / world}",
+       "synthetic_override_text_dim=48", "max_sequence_length=16", "ici_data_parallelism=1", "ici_fsdp_parallelism=1",
+       "ici_context_parallelism=1", f"ici_tensor_parallelism={world}"], unittest=True)
+  torch.manual_seed(0)
+  tr = WanTrainer(config, mesh=create_device_mesh(config), device="cpu")
+  data = tr.load_dataset()
+  return [float(tr.train_step(next(data))["learning/loss"]) for _ in range(2)]
+
+
+def test_tensor_parallel_training_matches_single_process():
+  ref = _train_tp(0, 1)
+  for losses in run_ranks(_train_tp, 2):
+    assert losses == pytest.approx(ref, rel=2e-4, abs=1e-5)

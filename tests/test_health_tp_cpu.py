@@ -119,3 +119,47 @@ def _tp_matches_dense(rank, world):
 def test_tensor_parallel_mlp_matches_dense_forward_and_backward():
   for err_y, err_g, rows_ok in run_ranks(_tp_matches_dense, 2):
     assert err_y < 1e-4 and err_g < 1e-4 and rows_ok
+
+
+def _tp_wan(rank, world):
+  """A Wan model sharded over the tensor group against the unsharded model with the same weights: forward output and
+  the gradients of replicated and sharded parameters."""
+  import torch
+  import torch.distributed as dist
+
+  from maxdiffusion_b200.models.wan.transformer_wan import WanConfig, WanModel
+  from maxdiffusion_b200.parallel.tensor import apply_tensor_parallel_wan
+
+  cfg = WanConfig(num_attention_heads=4, attention_head_dim=32, ffn_dim=96, num_layers=2, text_dim=48, freq_dim=32)
+  torch.manual_seed(0)
+  full = WanModel(cfg)
+  torch.manual_seed(0)
+  tp = WanModel(cfg)
+  assert apply_tensor_parallel_wan(tp, dist.group.WORLD) == world
+  torch.manual_seed(1)
+  lat, text, t = torch.randn(1, 16, 2, 8, 8), torch.randn(1, 6, 48), torch.tensor([321.0])
+  want = full(lat, t, text)
+  got = tp(lat, t, text)
+  err = (got - want).abs().max().item()
+  want.square().mean().backward()
+  got.square().mean().backward()
+  n, r = world, rank
+  g_full = dict(full.named_parameters())
+  g_tp = dict(tp.named_parameters())
+  dim, ffn = cfg.dim, cfg.ffn_dim
+  checks = []
+  # replicated parameter, row-parallel weight (columns), column-parallel fused qkv (rows of every chunk), sharded norm
+  checks.append((g_tp["blocks.0.scale_shift_table"].grad - g_full["blocks.0.scale_shift_table"].grad).abs().max().item())
+  checks.append((g_tp["blocks.1.ffn_out.weight"].grad - g_full["blocks.1.ffn_out.weight"].grad[:, r * ffn // n:(r + 1) * ffn // n]).abs().max().item())
+  per = dim // n
+  rows = torch.cat([g_full["blocks.0.attn1.to_qkv.weight"].grad[c * dim + r * per:c * dim + (r + 1) * per] for c in range(3)])
+  checks.append((g_tp["blocks.0.attn1.to_qkv.weight"].grad - rows).abs().max().item())
+  checks.append((g_tp["blocks.0.attn1.norm_q"].grad - g_full["blocks.0.attn1.norm_q"].grad[r * per:(r + 1) * per]).abs().max().item())
+  checks.append((g_tp["patch_embedding.weight"].grad - g_full["patch_embedding.weight"].grad).abs().max().item())
+  return err, checks
+
+
+def test_wan_blocks_sharded_over_the_tensor_axis_match_the_unsharded_model():
+  for err, checks in run_ranks(_tp_wan, 2):
+    assert err < 2e-5, err
+    assert max(checks) < 2e-5, checks
