@@ -18,7 +18,7 @@ template <int G, int VPL, int R>
 __global__ void __launch_bounds__(256)
 rms_act_kernel(const __nv_bfloat16* __restrict__ x, long long ldx, __nv_bfloat16* __restrict__ y, long long ldy,
                const float* __restrict__ gamma, const float* __restrict__ beta, long long rows, int C, float eps,
-               int act) {
+               int act, int out_w, int out_halo) {
   const int vecs = C >> 3;
   const int lane_in_group = threadIdx.x % G;
   const long long group = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) / G;
@@ -92,7 +92,9 @@ rms_act_kernel(const __nv_bfloat16* __restrict__ x, long long ldx, __nv_bfloat16
           ov.y = pack_bf16x2(o[2], o[3]);
           ov.z = pack_bf16x2(o[4], o[5]);
           ov.w = pack_bf16x2(o[6], o[7]);
-          *reinterpret_cast<uint4*>(y + row * ldy + vi * 8) = ov;
+          // out_w > 0: the output is the interior of a tensor whose width axis carries out_halo extra columns per side
+          const long long yrow = out_w > 0 ? (row / out_w) * (out_w + 2 * out_halo) + out_halo + row % out_w : row;
+          *reinterpret_cast<uint4*>(y + yrow * ldy + vi * 8) = ov;
         }
       }
     }
@@ -103,12 +105,16 @@ rms_act_kernel(const __nv_bfloat16* __restrict__ x, long long ldx, __nv_bfloat16
 }  // namespace mdb
 
 // x, y: bf16 [rows, C] with leading dimensions ldx / ldy (elements, multiples of 8); gamma / beta: fp32 [C]
-// (beta may be null); C a multiple of 8, at most 1024. act: 0 identity, 1 SiLU.
+// (beta may be null); C a multiple of 8, at most 1024. act: 0 identity, 1 SiLU. out_w > 0: x is [.., out_w, C] and y
+// is the interior of a [.., out_w + 2 out_halo, C] tensor (y points at its first row, halo column included).
 extern "C" int mdb_rms_act_cl(const void* x, long long ldx, void* y, long long ldy, const float* gamma,
-                              const float* beta, long long rows, int C, float eps, int act, void* stream) {
+                              const float* beta, long long rows, int C, float eps, int act, int out_w, int out_halo,
+                              void* stream) {
   using namespace mdb::cln;
   if (rows <= 0) return 0;
-  if ((C & 7) || C <= 0 || C > 8 * 32 * MAX_VPL || (ldx & 7) || (ldy & 7) || gamma == nullptr) return 3701;
+  if ((C & 7) || C <= 0 || C > 8 * 32 * MAX_VPL || (ldx & 7) || (ldy & 7) || gamma == nullptr || out_halo < 0 ||
+      (out_w > 0 && rows % out_w))
+    return 3701;
   const int vecs = C >> 3;
   const int G = vecs <= 8 ? 8 : (vecs <= 16 ? 16 : 32);
   const int vpl = (vecs + G - 1) / G;
@@ -121,7 +127,7 @@ extern "C" int mdb_rms_act_cl(const void* x, long long ldx, void* y, long long l
   const __nv_bfloat16* xp = static_cast<const __nv_bfloat16*>(x);
   __nv_bfloat16* yp = static_cast<__nv_bfloat16*>(y);
   const int nb = static_cast<int>(blocks);
-#define MDB_RMS_ACT(GG, VV, RR) rms_act_kernel<GG, VV, RR><<<nb, 256, 0, st>>>(xp, ldx, yp, ldy, gamma, beta, rows, C, eps, act)
+#define MDB_RMS_ACT(GG, VV, RR) rms_act_kernel<GG, VV, RR><<<nb, 256, 0, st>>>(xp, ldx, yp, ldy, gamma, beta, rows, C, eps, act, out_w, out_halo)
   if (G == 8) MDB_RMS_ACT(8, 1, 4);
   else if (G == 16) MDB_RMS_ACT(16, 1, 4);
   else if (vpl == 1) MDB_RMS_ACT(32, 1, 4);

@@ -14,6 +14,13 @@ the same parameters) as the NCDHW PyTorch path but keeps every activation as `[B
 The mid-block attention (one head of 384 channels over the H*W positions of a frame, :487-546) is two GEMMs around a
 row-softmax kernel (`ops.conv.wide_head_attention`): the flash kernels of this repository are built for head sizes
 64 and 128, and a latent frame has few enough positions for the score matrix to be materialised.
+
+Spatial parallelism (`decode(.., spatial=HaloExchange)`): every rank decodes a vertical strip of the frame. The input
+of a 3x3 convolution is produced with one spare column on each side (`ops.conv.rms_act(halo=1)`, or a convolution
+writing into the interior of a wider tensor), the neighbours' edge columns are exchanged into them
+(`parallel.spatial.HaloExchange.fill`) and the convolution reads them without producing output for them. The 2-frame
+histories keep their halos, so a later chunk exchanges only its own frames. The mid-block attention gathers the
+latent frame (a few thousand positions) and every rank keeps its strip of the result.
 """
 from __future__ import annotations
 
@@ -57,6 +64,7 @@ class ChannelsLastDecoder:
   def __init__(self, vae):
     self.vae = vae
     self._packed: dict = {}
+    self.halo = None  # `parallel.spatial.HaloExchange` while a width-sharded decode runs
 
   # ---- packed weights (re-packed when a parameter changes) -----------------------------------
   def _pack(self, key, params, make):
@@ -71,18 +79,23 @@ class ChannelsLastDecoder:
     return self._pack(id(m), (m.weight, m.bias), lambda: OC.pack_conv3d(m.weight.detach(), None if m.bias is None else m.bias.detach()))
 
   # ---- layers ----------------------------------------------------------------------------------
-  def conv3(self, m, x, hist: Optional[_Hist], residual=None, out=None):
-    """A `WanCausalConv3d`: x [B, T, H, W, Ci] -> [B, T, H, W, Co]."""
+  def conv3(self, m, x, hist: Optional[_Hist], residual=None, haloed: bool = False):
+    """A `WanCausalConv3d`: x [B, T, H, W, Ci] -> [B, T, H, W, Co]. Width-sharded: `haloed` says that x already has
+    its two spare columns (still to be filled from the neighbours); otherwise x is copied into a wider tensor."""
     kt = m.weight.shape[2]
     if tuple(m.weight.shape[2:]) == (1, 1, 1):
       return self.pointwise(m.weight, m.bias, x, residual)
+    pk = self._conv3_pack(m)
+    x = OC.pad_channels(x, pk.c_in)
+    spatial = self.halo is not None and m.weight.shape[-1] > 1
+    if spatial:
+      x = self.halo.fill(x) if haloed else self.halo.extend(x)
     past = None
     if hist is not None and kt > 1:
       slot = hist.next()
       past = hist.slots[slot]
-      hist.slots[slot] = _roll_history(past, x)
-    pk = self._conv3_pack(m)
-    return OC.conv3d_causal(OC.pad_channels(x, pk.c_in), pk, hist=past, residual=residual)
+      hist.slots[slot] = _roll_history(past, x)  # with its halo columns: later chunks exchange only their own frames
+    return OC.conv3d_causal(x, pk, hist=past, residual=residual, halo=1 if spatial else 0)
 
   def pointwise(self, weight, bias, x, residual=None):
     """1x1(x1) convolution = GEMM over the pixel rows."""
@@ -105,15 +118,22 @@ class ChannelsLastDecoder:
       y = K.gemm(rows, w2[0], bias=w2[1])
     return y.reshape(*x.shape[:-1], co)
 
-  def norm(self, m, x, silu: bool):
-    return OC.rms_act(x.contiguous(), m.gamma, m.bias, silu=silu)
+  def norm(self, m, x, silu: bool, for_conv: bool = False):
+    """`for_conv`: the result feeds a 3x3 convolution; width-sharded it gets the two spare columns for the halo."""
+    return OC.rms_act(x.contiguous(), m.gamma, m.bias, silu=silu, halo=1 if (for_conv and self.halo is not None) else 0)
 
   def res_block(self, blk, x, hist):
     h = self.conv3(blk.conv_shortcut, x, None) if blk.conv_shortcut is not None else x
-    y = self.conv3(blk.conv1, self.norm(blk.norm1, x, True), hist)
-    return self.conv3(blk.conv2, self.norm(blk.norm2, y, True), hist, residual=h.contiguous())
+    y = self.conv3(blk.conv1, self.norm(blk.norm1, x, True, for_conv=True), hist, haloed=True)
+    return self.conv3(blk.conv2, self.norm(blk.norm2, y, True, for_conv=True), hist, residual=h.contiguous(), haloed=True)
 
   def attention(self, blk, x):
+    if self.halo is not None:
+      # every position attends to the whole frame: gather the strips (latent resolution), keep this rank's columns
+      return self.halo.shard(self._attention(blk, self.halo.gather(x.contiguous())))
+    return self._attention(blk, x)
+
+  def _attention(self, blk, x):
     B, T, H, W, C = x.shape
     y = self.norm(blk.norm, x, False)
     qkv = self.pointwise(blk.to_qkv.weight, blk.to_qkv.bias, y).reshape(B * T, H * W, 3, C)
@@ -135,7 +155,10 @@ class ChannelsLastDecoder:
     T2 = x.shape[1]
     conv = rs.resample[1]
     pk = self._pack(("up", id(conv)), (conv.weight, conv.bias), lambda: OC.pack_upsample_conv2d(conv.weight.detach(), conv.bias.detach()))
-    y = OC.upsample2x_conv2d(x.reshape(B * T2, H, W, C), pk)
+    x = x.reshape(B * T2, H, W, C)
+    if self.halo is not None:
+      x = self.halo.extend(x)
+    y = OC.upsample2x_conv2d(x, pk, halo=0 if self.halo is None else 1)
     return y.reshape(B, T2, 2 * H, 2 * W, y.shape[-1])
 
   def _time_upsample(self, rs, x, hist: Optional[_Hist]):
@@ -167,11 +190,23 @@ class ChannelsLastDecoder:
         x = self.res_block(r, x, hist)
       if up.upsamplers is not None:
         x = self.resample(up.upsamplers[0], x, hist, first_chunk)
-    return self.conv3(d.conv_out, self.norm(d.norm_out, x, True), hist)
+    return self.conv3(d.conv_out, self.norm(d.norm_out, x, True, for_conv=True), hist, haloed=True)
 
   @torch.no_grad()
-  def decode(self, z: torch.Tensor, chunk: int = 1, whole_clip: bool = False) -> torch.Tensor:
-    """z [B, 16, T', H', W'] (de-normalised latents, bf16, CUDA) -> video [B, 3, 1 + 4 (T' - 1), 8 H', 8 W'] in [-1, 1]."""
+  def decode(self, z: torch.Tensor, chunk: int = 1, whole_clip: bool = False, spatial=None) -> torch.Tensor:
+    """z [B, 16, T', H', W'] (de-normalised latents, bf16, CUDA) -> video [B, 3, 1 + 4 (T' - 1), 8 H', 8 W'] in [-1, 1].
+    `spatial` (`parallel.spatial.HaloExchange`): z is replicated over its group, every rank decodes the strip
+    [rank W'/n, (rank + 1) W'/n) of the latent width and all ranks return the whole video."""
+    if spatial is not None and spatial.size > 1 and z.shape[-1] % spatial.size == 0:
+      self.halo = spatial
+      try:
+        strip = self._decode(spatial.shard(z, dim=-1), chunk, whole_clip)
+      finally:
+        self.halo = None
+      return spatial.gather(strip.contiguous(), dim=-1)
+    return self._decode(z, chunk, whole_clip)
+
+  def _decode(self, z, chunk, whole_clip):
     vae = self.vae
     x = z.permute(0, 2, 3, 4, 1).contiguous()  # channels-last
     x = self.pointwise(vae.post_quant_conv.weight, vae.post_quant_conv.bias, x)

@@ -35,7 +35,7 @@ def _declare(L):
                                                            llp, llp, c_int, c_void_p]
   L.mdb_conv_igemm.restype = c_int
   L.mdb_rms_act_cl.argtypes = [c_void_p, c_ll, c_void_p, c_ll, c_void_p, c_void_p, c_ll, c_int, ctypes.c_float, c_int,
-                               c_void_p]
+                               c_int, c_int, c_void_p]
   L.mdb_rms_act_cl.restype = c_int
   L.mdb_conv_igemm_tune.argtypes = [c_int, c_int, c_int]
   L.mdb_conv_igemm_tune.restype = c_int
@@ -80,11 +80,13 @@ class PackedConv:
   kind: str
   src: tuple = ()                 # (weight, bias, stride, pad_top_left) as given: what the PyTorch reference path runs
 
-  def tap_arrays(self):
+  def tap_arrays(self, shift1: int = 0):
+    """ctypes arrays of the tap table; `shift1` is added to every tap's offset along dim 1 (the width): an input
+    that carries `shift1` halo columns on each side produces outputs for its interior columns only."""
     flat, begin, k = [], [0], 0
     for cls in self.taps:
       for t in cls:
-        flat.extend([*t, k * self.c_pad])
+        flat.extend([t[0], t[1] + shift1, t[2], t[3], t[4], k * self.c_pad])
         k += 1
       begin.append(k)
     return (ctypes.c_int * len(flat))(*flat), (ctypes.c_int * len(begin))(*begin), len(self.taps)
@@ -213,8 +215,8 @@ def _pick_box(e1: int, e2: int, e3: int, allow3: bool):
 
 
 def _launch(x, x_alt, pk: PackedConv, dims, strides, alt_dims, alt_strides, box, ext, out, out_strides, class_off,
-            residual, silu, alt_dim=-1, alt_shift=0):
-  taps, begin, n_classes = pk.tap_arrays()
+            residual, silu, alt_dim=-1, alt_shift=0, tap_shift1=0):
+  taps, begin, n_classes = pk.tap_arrays(tap_shift1)
   LL, I = ctypes.c_longlong, ctypes.c_int
   arr = lambda T, v: (T * len(v))(*[int(i) for i in v])
   rc = _lib.lib().mdb_conv_igemm(
@@ -239,20 +241,25 @@ def pad_channels(x: torch.Tensor, c: int) -> torch.Tensor:
 
 def conv3d_causal(x: torch.Tensor, pk: PackedConv, hist: Optional[torch.Tensor] = None,
                   residual: Optional[torch.Tensor] = None, silu: bool = False,
-                  out: Optional[torch.Tensor] = None) -> torch.Tensor:
+                  out: Optional[torch.Tensor] = None, halo: int = 0) -> torch.Tensor:
   """x [B, T, H, W, C] -> [B, T, H, W, N]. `hist` [B, 2, H, W, C]: the two frames before x (None: zeros). `out` may be
-  a strided view (e.g. every second frame of a larger tensor) as long as its channels are dense."""
+  a strided view (e.g. every second frame of a larger tensor) as long as its channels are dense. With `halo` = 1 the
+  input (and `hist`) carry one extra column on each side of W (a width-sharded tensor with its neighbours' edge columns)
+  and the output has W - 2 columns: the halo columns are read, not recomputed."""
   if not use_kernel(x):
     w, b = pk.src[0], pk.src[1]
     ci = w.shape[1]
-    y = ref_conv3d_causal(x[..., :ci], w, b, hist=None if hist is None else hist[..., :ci], residual=residual,
-                          silu=silu).to(x.dtype)
+    y = ref_conv3d_causal(x[..., :ci], w, b, hist=None if hist is None else hist[..., :ci], silu=silu)
+    if halo:
+      y = y[:, :, :, halo:-halo]
+    y = (y + residual.float() if residual is not None else y).to(x.dtype)
     if out is not None:
       out.copy_(y)
       return out
     return y
   _check_cl(x, pk.c_in)
-  B, T, H, W, C = x.shape
+  B, T, H, Win, C = x.shape
+  W = Win - 2 * halo  # output columns
   if out is None:
     out = torch.empty((B, T, H, W, pk.n_pad), dtype=x.dtype, device=x.device)
   else:
@@ -262,15 +269,14 @@ def conv3d_causal(x: torch.Tensor, pk: PackedConv, hist: Optional[torch.Tensor] 
   alt_dims = alt_strides = None
   if hist is not None:
     _check_cl(hist, pk.c_in)
-    assert hist.shape == (B, 2, H, W, C)
-    alt_dims = [C, W, H, 2, B]
+    assert hist.shape == (B, 2, H, Win, C)
+    alt_dims = [C, Win, H, 2, B]
     alt_strides = [hist.stride(3), hist.stride(2), hist.stride(1), hist.stride(0)]
   if residual is not None:
     assert residual.shape == out.shape and residual.is_contiguous()
-  n = pk.n_pad
-  _launch(x, hist, pk, [C, W, H, T, B], [x.stride(3), x.stride(2), x.stride(1), x.stride(0)], alt_dims, alt_strides,
+  _launch(x, hist, pk, [C, Win, H, T, B], [x.stride(3), x.stride(2), x.stride(1), x.stride(0)], alt_dims, alt_strides,
           [b1, b2, 1], [W, H, T, B], out, [out.stride(3), out.stride(2), out.stride(1), out.stride(0)], [0], residual, silu,
-          alt_dim=3, alt_shift=2)
+          alt_dim=3, alt_shift=2, tap_shift1=halo)
   return out if pk.n_pad == pk.n_out else out[..., :pk.n_out]
 
 
@@ -303,25 +309,28 @@ def conv2d(x: torch.Tensor, pk: PackedConv, residual: Optional[torch.Tensor] = N
   return out if pk.n_pad == pk.n_out else out[..., :pk.n_out]
 
 
-def _parity_conv(x, pk, silu=False):
+def _parity_conv(x, pk, silu=False, halo: int = 0):
   """Shared by the fused up-sampling convolution and the stride-2 dgrad: x [B, H, W, C] -> [B, 2H, 2W, N], class
-  (rh, rw) writes the output positions (2p + rh, 2q + rw)."""
+  (rh, rw) writes the output positions (2p + rh, 2q + rw). With `halo` the input carries that many extra columns on
+  each side of W, which are read but produce no output."""
   _check_cl(x, pk.c_in)
-  B, H, W, C = x.shape
+  B, H, Win, C = x.shape
+  W = Win - 2 * halo
   n = pk.n_pad
   out = torch.empty((B, 2 * H, 2 * W, n), dtype=x.dtype, device=x.device)
   box = _pick_box(W, H, B, True)
   class_off = [rh * 2 * W * n + rw * n for rh in (0, 1) for rw in (0, 1)]
-  _launch(x, None, pk, [C, W, H, B, 1], [x.stride(2), x.stride(1), x.stride(0), x.stride(0) * B], None, None, box,
-          [W, H, B, 1], out, [2 * n, 4 * W * n, 4 * H * W * n, 4 * B * H * W * n], class_off, None, silu)
+  _launch(x, None, pk, [C, Win, H, B, 1], [x.stride(2), x.stride(1), x.stride(0), x.stride(0) * B], None, None, box,
+          [W, H, B, 1], out, [2 * n, 4 * W * n, 4 * H * W * n, 4 * B * H * W * n], class_off, None, silu, tap_shift1=halo)
   return out if pk.n_pad == pk.n_out else out[..., :pk.n_out]
 
 
-def upsample2x_conv2d(x: torch.Tensor, pk: PackedConv) -> torch.Tensor:
+def upsample2x_conv2d(x: torch.Tensor, pk: PackedConv, halo: int = 0) -> torch.Tensor:
   assert pk.kind == "upsample_conv2d"
   if not use_kernel(x):
-    return ref_upsample2x_conv2d(x[..., :pk.src[0].shape[1]], pk.src[0], pk.src[1]).to(x.dtype)
-  return _parity_conv(x, pk)
+    y = ref_upsample2x_conv2d(x[..., :pk.src[0].shape[1]], pk.src[0], pk.src[1])
+    return (y[:, :, 2 * halo:y.shape[2] - 2 * halo] if halo else y).to(x.dtype)
+  return _parity_conv(x, pk, halo=halo)
 
 
 def conv2d_dgrad(dy: torch.Tensor, pk: PackedConv) -> torch.Tensor:
@@ -400,20 +409,24 @@ _wgrad_launch = _wgrad_launch_kernel
 
 
 def rms_act(x: torch.Tensor, gamma: torch.Tensor, beta: Optional[torch.Tensor] = None, silu: bool = True,
-            eps: float = 1e-12) -> torch.Tensor:
-  """y = act(x / max(||x||, eps) * sqrt(C) * gamma + beta) over the last axis of a channels-last tensor."""
+            eps: float = 1e-12, halo: int = 0) -> torch.Tensor:
+  """y = act(x / max(||x||, eps) * sqrt(C) * gamma + beta) over the last axis of a channels-last tensor. With `halo`
+  the result [..., W + 2 halo, C] has its interior columns written and its halo columns left for the caller (a
+  width-sharded tensor that is about to receive its neighbours' edge columns)."""
   C = x.shape[-1]
   if not use_kernel(x):
     y = F.normalize(x.float(), dim=-1, eps=eps) * (C ** 0.5) * gamma.float().reshape(-1)
     if beta is not None:
       y = y + beta.float().reshape(-1)
-    return (F.silu(y) if silu else y).to(x.dtype)
+    y = (F.silu(y) if silu else y).to(x.dtype)
+    return F.pad(y, (0, 0, halo, halo)) if halo else y
   assert x.is_contiguous()
-  y = torch.empty_like(x)
+  W = x.shape[-2]
+  y = torch.empty((*x.shape[:-2], W + 2 * halo, C), dtype=x.dtype, device=x.device)
   g = gamma.reshape(-1).float().contiguous()
   b = beta.reshape(-1).float().contiguous() if beta is not None else None
   rc = _lib.lib().mdb_rms_act_cl(_lib.ptr(x), C, _lib.ptr(y), C, _lib.ptr(g), _lib.ptr(b), x.numel() // C, C, float(eps),
-                                 int(silu), _lib.stream())
+                                 int(silu), W if halo else 0, halo, _lib.stream())
   _lib.check(rc, "mdb_rms_act_cl")
   return y
 

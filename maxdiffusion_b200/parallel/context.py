@@ -384,8 +384,10 @@ class ContextParallel:
     D = C // heads
     group = self.ulysses_group if self.strategy == "usp" else self.group
     U = self.ulysses_size if self.strategy == "usp" else self.size
+    # a recorded forward of a rematerialised block also runs without autograd, but its replay expects the attention
+    # output and statistics in the store: only a forward outside any recording takes the folded path
     fused = (self.strategy in ("ulysses", "usp") and self.peer_memory and U > 1 and group is not None and not torch.is_grad_enabled()
-             and not self.fixed_m and q.is_cuda and q.dtype == torch.bfloat16 and D == 128 and heads % U == 0 and U <= 8
+             and OF._remat.mode is None and not self.fixed_m and q.is_cuda and q.dtype == torch.bfloat16 and D == 128 and heads % U == 0 and U <= 8
              and not OF.library_mode() and all(t.stride(-1) == 1 and t.stride(0) == S * t.stride(1) for t in (q, k, v)))
     ex = self._fused_ulysses_for(group, B * U * S * (heads // U) * D, B * S * C, q.dtype) if fused else None
     if ex is None:

@@ -38,7 +38,9 @@ FLAG_QKV_READY = 13  # fused Ulysses: q / k / v heads stored into their owners
 FLAG_QKV_ACK = 14
 FLAG_TP_READY = 15   # tensor-parallel partial products (parallel.tensor.PeerAllReduce)
 FLAG_TP_ACK = 16
-NUM_FLAG_KINDS = 18
+FLAG_HALO_READY = 17  # width-sharded VAE: edge columns published for the neighbours (parallel.spatial.HaloExchange)
+FLAG_HALO_ACK = 18
+NUM_FLAG_KINDS = 20
 WAIT_BUDGET_S = 10.0  # waits on other ranks: long enough for host-side skew (first-step allocation, logging)
 
 

@@ -81,6 +81,19 @@ class WanPipeline:
       for m in filter(None, (self.transformer, self.transformer_2)):
         if getattr(m, "tp_group", None) is None:
           apply_tensor_parallel_wan(m, self.mesh.group("tensor"))
+    # VAE spatial parallelism: the ranks that hold the same latents (the context axis, else the tensor axis) each
+    # decode a vertical strip of the frame (reference: the `vae_spatial` mesh axis, wan_pipeline.py:560-640).
+    # vae_spatial: -1 = over that whole axis, 1 = off.
+    self.vae_spatial = None
+    axis = "context" if self.mesh.size("context") > 1 else "tensor"
+    want = int(config.get("vae_spatial", -1))
+    if vae is not None and self.mesh.size(axis) > 1 and want != 1:
+      if want not in (-1, 0, self.mesh.size(axis)):
+        raise ValueError(f"vae_spatial={want}: the VAE is split over the whole {axis} axis ({self.mesh.size(axis)} ranks) or not at all")
+      from ...parallel.spatial import HaloExchange
+
+      self.vae_spatial = HaloExchange(self.mesh.group(axis),
+                                      peer_memory=bool(config.get("peer_memory_transport", True)) and self.device.type == "cuda")
     self.prompt_cache = PromptCache()
     from ...models.quantizations import get_quantization_mode, quantize_model
 
@@ -335,7 +348,12 @@ class WanPipeline:
       z = z.to(torch.bfloat16)
     else:
       z = z.to(next(self.vae.parameters()).dtype)
-    return self.vae.decode(z, chunk=int(self.config.get("vae_decode_chunk", 1)))
+    chunk = int(self.config.get("vae_decode_chunk", 1))
+    if self.vae_spatial is not None and z.is_cuda and z.dtype == torch.bfloat16:
+      video = self.vae.channels_last_decoder().decode(z, chunk, spatial=self.vae_spatial)
+      _lib.raise_on_device_status_if_loaded()  # the halo exchanges waited (bounded) on the neighbours
+      return video
+    return self.vae.decode(z, chunk=chunk)
 
 
 class WanPipeline2_1(WanPipeline):

@@ -11,7 +11,7 @@ from maxdiffusion_b200.ops import conv as OC
 
 
 def _emulate(x, x_alt, pk, dims, strides, alt_dims, alt_strides, box, ext, out, out_strides, class_off, residual, silu,
-             alt_dim=-1, alt_shift=0):
+             alt_dim=-1, alt_shift=0, tap_shift1=0):
   assert box[0] * box[1] * box[2] == 128
 
   def view5(t, d, s):
@@ -42,7 +42,7 @@ def _emulate(x, x_alt, pk, dims, strides, alt_dims, alt_strides, box, ext, out, 
       wk = w[:, k * pk.c_pad:k * pk.c_pad + C]
       k += 1
       for p4, p3, p2, p1 in itertools.product(range(e4), range(e3), range(e2), range(e1)):
-        c1, c2, c3, c4 = p1 + o1, p2 + o2, p3 + o3, p4 + o4
+        c1, c2, c3, c4 = p1 + o1 + tap_shift1, p2 + o2, p3 + o3, p4 + o4
         arr = main
         if alt is not None and alt_dim == 3 and c3 < 0:
           # the kernel decides per TILE (box3 == 1 along the history axis), which is per position here
@@ -124,6 +124,23 @@ def test_dgrad_description(emulated, stride, pad):
   dy = _rand(tuple(y.shape), 3)
   (y * dy.float()).sum().backward()
   _close(OC.conv2d_dgrad(dy, OC.pack_conv2d_dgrad(w, stride=stride, pad_top_left=pad)), x.grad)
+
+
+def test_halo_columns_are_read_and_produce_no_output(emulated):
+  """Width-sharded tensors: the middle shard of a wide tensor, extended by its neighbours' edge columns, gives exactly
+  the middle columns of the unsharded convolution (causal conv3d with history, and the fused up-sampling conv)."""
+  x = _rand((1, 2, 3, 9, 16), 1)
+  hist = _rand((1, 2, 3, 9, 16), 2)
+  w = _rand((8, 16, 3, 3, 3), 3, 0.1)
+  pk = OC.pack_conv3d(w, None)
+  whole = OC.ref_conv3d_causal(x, w, None, hist=hist)
+  got = OC.conv3d_causal(x[:, :, :, 2:7].contiguous(), pk, hist=hist[:, :, :, 2:7].contiguous(), halo=1)
+  _close(got, whole[:, :, :, 3:6])
+  x2 = _rand((2, 3, 9, 16), 4)
+  w2 = _rand((8, 16, 3, 3), 5, 0.1)
+  whole2 = OC.ref_upsample2x_conv2d(x2, w2, None)
+  got2 = OC.upsample2x_conv2d(x2[:, :, 2:7].contiguous(), OC.pack_upsample_conv2d(w2, None), halo=1)
+  _close(got2, whole2[:, :, 6:12])
 
 
 def test_box_choice_covers_with_least_padding():

@@ -240,3 +240,27 @@ def test_wide_head_attention_matches_fp32(T, D):
   x = _rand((37, 2048), 4, scale=4.0)
   want_sm = torch.softmax(x.float(), dim=-1)
   assert (OC.softmax_rows(x.clone()).float() - want_sm).abs().max() < 2e-3
+
+
+@pytest.mark.parametrize("W0,W1", [(3, 19), (0, 16), (8, 24)])
+def test_halo_columns_are_read_and_produce_no_output(W0, W1):
+  """A width shard extended by its neighbours' edge columns gives the same columns as the unsharded convolution (the
+  first / last shard of a tensor pads its outer side with zeros, which is what the unsharded kernel reads there)."""
+  from maxdiffusion_b200.ops import conv as OC
+
+  x = _rand((1, 3, 10, 24, 96), 1)
+  hist = _rand((1, 2, 10, 24, 96), 2)
+  w = _rand((96, 96, 3, 3, 3), 3, scale=0.02)
+  b = _rand((96,), 4)
+  pk = OC.pack_conv3d(w, b)
+  pad = lambda t: torch.nn.functional.pad(t, (0, 0, 1, 1))
+  xs, hs = pad(x)[:, :, :, W0:W1 + 2].contiguous(), pad(hist)[:, :, :, W0:W1 + 2].contiguous()
+  whole = OC.conv3d_causal(x, pk, hist=hist)
+  got = OC.conv3d_causal(xs, pk, hist=hs, halo=1)
+  assert torch.equal(got, whole[:, :, :, W0:W1])
+  x2 = _rand((3, 10, 24, 96), 5)
+  w2 = _rand((96, 96, 3, 3), 6, scale=0.03)
+  pk2 = OC.pack_upsample_conv2d(w2, b)
+  whole2 = OC.upsample2x_conv2d(x2, pk2)
+  got2 = OC.upsample2x_conv2d(pad(x2)[:, :, W0:W1 + 2].contiguous(), pk2, halo=1)
+  assert torch.equal(got2, whole2[:, :, 2 * W0:2 * W1])

@@ -363,3 +363,38 @@ def test_peer_all_to_all_equals_nccl_and_round_trips():
     pytest.skip("needs 2 GPUs")
   for res in _spawn(_peer_all_to_all, 2):
     assert all(a and b for a, b in res), res
+
+
+def _spatial_vae(rank, world, peer_memory):
+  import torch.distributed as dist
+
+  from maxdiffusion_b200.models.wan.autoencoder_kl_wan import AutoencoderKLWan, WanVAEConfig
+  from maxdiffusion_b200.parallel.spatial import HaloExchange
+
+  torch.manual_seed(0)
+  vae = AutoencoderKLWan(WanVAEConfig(base_dim=32)).eval().cuda()
+  for p in vae.parameters():
+    torch.nn.init.normal_(p, std=0.05)
+  z = torch.randn(1, 16, 4, 6, 8 * world, device="cuda").to(torch.bfloat16)
+  dist.broadcast(z, 0)
+  cl = vae.channels_last_decoder()
+  halo = HaloExchange(dist.group.WORLD, peer_memory=peer_memory)
+  assert (halo.peer is not None) == peer_memory
+  with torch.no_grad():
+    whole = cl.decode(z, chunk=2)
+    split = cl.decode(z, chunk=2, spatial=halo)
+    again = cl.decode(z, chunk=1, spatial=halo)  # buffers and epochs carry over between decodes
+  return (float((whole.float() - split.float()).abs().max()), float((whole.float() - again.float()).abs().max()),
+          float(whole.float().abs().max()), tuple(split.shape), halo.exchanges)
+
+
+@pytest.mark.parametrize("world,peer_memory", [(2, True), (2, False), (4, True)])
+def test_vae_decode_split_over_the_width_with_halo_exchange(world, peer_memory):
+  """Width-sharded Wan VAE decode on the convolution kernels: edge columns over peer memory (flags + pull) or NCCL
+  point-to-point, against the one-GPU decode of the same latents."""
+  if torch.cuda.device_count() < world:
+    pytest.skip(f"needs {world} GPUs")
+  for err, err2, scale, shape, exchanges in _spawn(_spatial_vae, world, peer_memory):
+    assert shape == (1, 3, 13, 48, 64 * world)
+    assert err <= 2e-2 * (1 + scale) and err2 <= 2e-2 * (1 + scale), (err, err2, scale)
+    assert exchanges > 40
