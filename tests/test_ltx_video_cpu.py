@@ -1,4 +1,5 @@
 """LTX-Video on CPU: fractional RoPE, skip-layer strategies, per-phase schedules and the two-pass pipeline."""
+import pytest
 import torch
 
 from maxdiffusion_b200 import pyconfig
@@ -153,3 +154,27 @@ def test_prompt_enhancement_and_crf_identity():
        "cross_attention_dim": 4096, "caption_channels": 4096, "in_channels": 128, "out_channels": 128}
   n = diffusers_to_native(d)
   assert n["num_layers"] == 48 and n["qk_norm"] == "rms_norm" and native_to_diffusers(n)["attention_head_dim"] == 128
+
+
+def test_codec_noise_grows_with_the_rate_factor_and_follows_h264_quantisation():
+  """The on-device model of an H.264 intra frame: the orthonormal core transform inverts itself, the step size doubles
+  every 6 QP, a smooth picture survives better than noise, and the error grows monotonically with the rate factor."""
+  from maxdiffusion_b200.pipelines.ltx_video import crf_compressor as cc
+
+  assert torch.allclose(cc._CORE @ cc._CORE.t(), torch.eye(4), atol=1e-6)
+  assert cc.qstep(0) == 0.625 and cc.qstep(28) == pytest.approx(16.0, rel=1e-6) and cc.qstep(34) == pytest.approx(2 * cc.qstep(28))
+  assert [cc.chroma_qp(q) for q in (20, 29, 30, 40, 51)] == [20, 29, 29, 36, 39]
+  g = torch.Generator().manual_seed(0)
+  yy, xx = torch.meshgrid(torch.linspace(0, 1, 37), torch.linspace(0, 1, 50), indexing="ij")
+  smooth = torch.stack([yy, xx, 0.5 * (yy + xx)], dim=-1)
+  noisy = (smooth + 0.2 * torch.randn(smooth.shape, generator=g)).clamp(0, 1)
+
+  def mse(img, crf):
+    out = cc.compress(img, crf)
+    assert out.shape == (36, 50, 3) and out.dtype == img.dtype and 0 <= out.min() and out.max() <= 1
+    return ((out - img[:36, :50]) ** 2).mean().item()
+
+  errs = [mse(noisy, c) for c in (10, 20, 29, 40, 51)]
+  assert all(a < b for a, b in zip(errs, errs[1:])), errs
+  assert mse(smooth, 29) < 0.1 * mse(noisy, 29)
+  assert mse(smooth, 10) < 2e-4  # near-transparent at a low rate factor
