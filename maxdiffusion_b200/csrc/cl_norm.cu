@@ -2,15 +2,16 @@
 //   rms_act : y = act( x / max(||x||_2, eps) * sqrt(C) * gamma + beta ),  act = identity or SiLU
 // This is the `WanRMS_norm` + SiLU that precedes every convolution of the Wan VAE's residual blocks
 // (src/maxdiffusion/models/wan/autoencoder_kl_wan.py:150-183, 452-484): memory bound, one read and one write of the
-// activation. A row of C channels (96 .. 1024) is handled by a group of G = 8, 16 or 32 lanes, each lane holding up
-// to four 16-byte vectors, so that narrow rows (96 channels = 12 vectors) do not leave most of a warp idle; the
-// sum of squares is reduced with shuffles inside the group, statistics in fp32.
+// activation. A row of C channels (16 .. 1024) is handled by a group of G = 2 .. 32 lanes, each lane holding VPL
+// 16-byte vectors, with G * VPL equal to the row's vector count wherever it factors that way (96 channels = 12
+// vectors = 4 lanes x 3, 384 = 16 x 3, 320 = 8 x 5), so that no lane of a warp is idle; the sum of squares is
+// reduced with shuffles inside the group, statistics in fp32.
 #include "host_common.h"
 
 namespace mdb {
 namespace cln {
 
-constexpr int MAX_VPL = 4;  // vectors (8 bf16) per lane
+constexpr int MAX_VPL = 5;  // vectors (8 bf16) per lane
 
 // R rows per group and iteration are loaded before any of them is reduced: a memory-bound kernel needs tens of
 // kilobytes in flight per SM, and one 16-byte load per thread is not enough of them.
@@ -116,10 +117,17 @@ extern "C" int mdb_rms_act_cl(const void* x, long long ldx, void* y, long long l
       (out_w > 0 && rows % out_w))
     return 3701;
   const int vecs = C >> 3;
-  const int G = vecs <= 8 ? 8 : (vecs <= 16 ? 16 : 32);
-  const int vpl = (vecs + G - 1) / G;
+  // widest group whose lanes are all busy; rows that do not factor fall back to a full warp with a ragged last pass
+  int G = 0, vpl = 0;
+  for (int g = 32; g >= 2 && G == 0; g >>= 1)
+    if (vecs % g == 0 && vecs / g <= MAX_VPL && (vecs / g == 1 || vecs / g == 3 || vecs / g == 5 || g == 32)) G = g, vpl = vecs / g;
+  if (G == 0) {
+    G = vecs <= 8 ? 8 : (vecs <= 16 ? 16 : 32);
+    vpl = (vecs + G - 1) / G;
+  }
+  const int R = vpl <= 2 ? 4 : (vpl <= 4 ? 2 : 1);
   const long long groups_per_block = 256 / G;
-  long long blocks = (rows + groups_per_block * 4 - 1) / (groups_per_block * 4);
+  long long blocks = (rows + groups_per_block * R - 1) / (groups_per_block * R);
   const long long cap = static_cast<long long>(mdb::sm_count()) * 8;
   if (blocks > cap) blocks = cap;
   if (blocks < 1) blocks = 1;
@@ -127,12 +135,28 @@ extern "C" int mdb_rms_act_cl(const void* x, long long ldx, void* y, long long l
   const __nv_bfloat16* xp = static_cast<const __nv_bfloat16*>(x);
   __nv_bfloat16* yp = static_cast<__nv_bfloat16*>(y);
   const int nb = static_cast<int>(blocks);
-#define MDB_RMS_ACT(GG, VV, RR) rms_act_kernel<GG, VV, RR><<<nb, 256, 0, st>>>(xp, ldx, yp, ldy, gamma, beta, rows, C, eps, act, out_w, out_halo)
-  if (G == 8) MDB_RMS_ACT(8, 1, 4);
-  else if (G == 16) MDB_RMS_ACT(16, 1, 4);
-  else if (vpl == 1) MDB_RMS_ACT(32, 1, 4);
-  else if (vpl == 2) MDB_RMS_ACT(32, 2, 4);
-  else MDB_RMS_ACT(32, 4, 2);
+#define MDB_RMS_ACT(GG, VV, RR) \
+  rms_act_kernel<GG, VV, RR><<<nb, 256, 0, st>>>(xp, ldx, yp, ldy, gamma, beta, rows, C, eps, act, out_w, out_halo)
+#define MDB_RMS_ACT_G(GG)                         \
+  if (G == GG) {                                  \
+    if (vpl == 1) MDB_RMS_ACT(GG, 1, 4);          \
+    else if (vpl == 3) MDB_RMS_ACT(GG, 3, 2);     \
+    else if (vpl == 5) MDB_RMS_ACT(GG, 5, 1);     \
+    else return 3701;                             \
+  }
+  if (G == 32) {
+    if (vpl == 1) MDB_RMS_ACT(32, 1, 4);
+    else if (vpl == 2) MDB_RMS_ACT(32, 2, 4);
+    else if (vpl == 3) MDB_RMS_ACT(32, 3, 2);
+    else if (vpl == 4) MDB_RMS_ACT(32, 4, 2);
+    else MDB_RMS_ACT(32, 5, 1);
+  }
+  else MDB_RMS_ACT_G(16)
+  else MDB_RMS_ACT_G(8)
+  else MDB_RMS_ACT_G(4)
+  else MDB_RMS_ACT_G(2)
+  else return 3701;
+#undef MDB_RMS_ACT_G
 #undef MDB_RMS_ACT
   return static_cast<int>(cudaGetLastError());
 }

@@ -109,9 +109,11 @@ def test_conv2d_dgrad_matches_autograd(stride, pad):
   _close(got, x.grad)
 
 
-@pytest.mark.parametrize("C", [96, 192, 384, 16, 1024])
+@pytest.mark.parametrize("C", [96, 192, 384, 16, 1024, 8, 48, 112, 288, 320, 640, 1280])
 @pytest.mark.parametrize("silu", [False, True])
 def test_rms_act_channels_last(C, silu):
+  """Every lane-group shape of the row kernel (exact factorisations of the row's vector count and the ragged
+  fallback), and the variant that writes the interior of a tensor with halo columns."""
   from maxdiffusion_b200.ops import conv as OC
 
   x = _rand((3, 5, 7, C), 1, scale=3.0)
@@ -120,6 +122,8 @@ def test_rms_act_channels_last(C, silu):
   got = OC.rms_act(x, gamma, beta, silu=silu)
   want = OC.rms_act(x.cpu(), gamma.cpu(), beta.cpu(), silu=silu).cuda()
   _close(got, want)
+  wide = OC.rms_act(x, gamma, beta, silu=silu, halo=1)
+  assert wide.shape == (3, 5, 9, C) and torch.equal(wide[:, :, 1:-1], got)
 
 
 def test_conv_results_are_bitwise_reproducible():
