@@ -158,6 +158,7 @@ def main() -> int:
   ap.add_argument("--batch", type=int, default=None)
   ap.add_argument("--ulysses", type=int, default=-1)
   ap.add_argument("--decode", action="store_true", help="wan_infer: also time the VAE decode")
+  ap.add_argument("--eager", action="store_true", help="sdxl_train: issue every kernel instead of replaying a CUDA graph")
   args = ap.parse_args()
   if args.impl == "reference":
     return reference_arm()

@@ -51,11 +51,13 @@ __global__ void signal_peers_kernel(PeerFlagPtrs flags, int n, int slot, unsigne
 }
 
 // Thread i waits until flags[i * stride] >= target. A wait that runs out of its budget reports
-// {where = 100, detail = i} in the status word; the host turns that into an exception.
+// {where = 100, detail = i} in the status word; the host turns that into an exception. Once a failure is recorded
+// every later wait returns at once: a sequence of exchanges queued behind a failed one costs one budget, not one each.
 __global__ void wait_flags_kernel(const unsigned int* flags, int n, int stride, unsigned int target,
                                   unsigned long long budget_ns, DeviceStatus* status) {
   const int i = threadIdx.x;
   if (i >= n) return;
+  if (status != nullptr && *reinterpret_cast<volatile unsigned int*>(&status->code) != 0u) return;
   const uint64_t t0 = global_timer_ns();
   unsigned int spins = 0;
   while (ld_acquire_sys(flags + static_cast<long long>(i) * stride) < target) {

@@ -52,6 +52,12 @@ struct Params {
   int out_f32;
   float alpha;
   DeviceStatus* status;
+  // split-K (weight gradients: a small output with a long contraction): work item w covers k-blocks
+  // [split * kb_per_split, ..) of tile w % num_tiles with split = w / num_tiles and writes fp32 partials
+  // [splits, M, N]; `splitk_fold_kernel` sums them in split order (deterministic, no atomics)
+  int splits;
+  int kb_per_split;
+  float* partial;
 };
 
 __device__ __forceinline__ void tile_coords(int tile, int num_m, int num_n, int& m_idx, int& n_idx) {
@@ -88,6 +94,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
   const int num_n = (p.N + BN - 1) / BN;
   const int num_tiles = num_m * num_n;
   const int num_kb = (p.K + BK - 1) / BK;
+  const int num_work = num_tiles * p.splits;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
@@ -119,11 +126,13 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
       uint32_t phase = 0;
       int issued = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+      for (int work = blockIdx.x; work < num_work && ok; work += gridDim.x) {
         int m_idx, n_idx;
-        tile_coords(tile, num_m, num_n, m_idx, n_idx);
+        const int split = work / num_tiles;
+        tile_coords(work - split * num_tiles, num_m, num_n, m_idx, n_idx);
         const int m0 = m_idx * BM, n0 = n_idx * BN;
-        for (int kb = 0; kb < num_kb; ++kb) {
+        const int kb_begin = split * p.kb_per_split, kb_end = min(num_kb, kb_begin + p.kb_per_split);
+        for (int kb = kb_begin; kb < kb_end; ++kb) {
           if (!mbar_wait(&empty_bar[stage], phase ^ 1u, abort_flag, p.status, 10)) { ok = false; break; }
           uint8_t* sa = smem + stage * STAGE_BYTES;
           uint8_t* sb = sa + A_BYTES;
@@ -163,13 +172,14 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
       uint32_t phase = 0;
       int it = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++it) {
+      for (int work = blockIdx.x; work < num_work && ok; work += gridDim.x, ++it) {
         const int acc = it & 1;
         const uint32_t acc_phase = (it >> 1) & 1u;
         if (!mbar_wait(&tmem_empty[acc], acc_phase ^ 1u, abort_flag, p.status, 20)) { ok = false; break; }
         tc_fence_after_sync();
         const uint32_t d_tmem = tmem_base + acc * BN;
-        for (int kb = 0; kb < num_kb; ++kb) {
+        const int kb_begin = (work / num_tiles) * p.kb_per_split, kb_end = min(num_kb, kb_begin + p.kb_per_split);
+        for (int kb = kb_begin; kb < kb_end; ++kb) {
           if (!mbar_wait(&full_bar[stage], phase, abort_flag, p.status, 21)) { ok = false; break; }
           tc_fence_after_sync();
           const uint32_t sa = smem_u32(smem + stage * STAGE_BYTES);
@@ -180,7 +190,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
                                      : make_smem_desc(sa + k * 32, 16, 1024);
             const uint64_t db = B_MN ? make_smem_desc(sb + k * 2048, BK * 128, 1024)
                                      : make_smem_desc(sb + k * 32, 16, 1024);
-            umma_ss(d_tmem, da, db, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+            umma_ss(d_tmem, da, db, idesc, (kb > kb_begin || k > 0) ? 1u : 0u);
           }
           umma_commit(&empty_bar[stage]);
           if (++stage == STAGES) { stage = 0; phase ^= 1u; }
@@ -194,9 +204,10 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
     const int row_in_tile = quarter * 32 + lane;
     int it = 0;
     bool ok = true;
-    for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++it) {
+    for (int work = blockIdx.x; work < num_work && ok; work += gridDim.x, ++it) {
       int m_idx, n_idx;
-      tile_coords(tile, num_m, num_n, m_idx, n_idx);
+      const int split = work / num_tiles;
+      tile_coords(work - split * num_tiles, num_m, num_n, m_idx, n_idx);
       const int acc = it & 1;
       const uint32_t acc_phase = (it >> 1) & 1u;
       if (!mbar_wait(&tmem_full[acc], acc_phase, abort_flag, p.status, 30)) { ok = false; break; }
@@ -220,6 +231,12 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
             float x[8];
 #pragma unroll
             for (int j = 0; j < 8; ++j) x[j] = __uint_as_float(r[v * 8 + j]) * p.alpha;
+            if (p.splits > 1) {
+              float* o = p.partial + (static_cast<long long>(split) * p.M + row) * p.N + col;
+              *reinterpret_cast<float4*>(o) = make_float4(x[0], x[1], x[2], x[3]);
+              *reinterpret_cast<float4*>(o + 4) = make_float4(x[4], x[5], x[6], x[7]);
+              continue;
+            }
             if (p.bias) {
               const uint4 bv = *reinterpret_cast<const uint4*>(p.bias + col);
               const uint32_t bw[4] = {bv.x, bv.y, bv.z, bv.w};
@@ -285,6 +302,37 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
   }
 }
 
+// out[i] = sum over splits of partial[s][i], in split order; n8 = M * N / 8 vectors of 8 values.
+__global__ void splitk_fold_kernel(const float* __restrict__ partial, void* __restrict__ out, long long ldo, int M, int N,
+                                   int splits, int out_f32) {
+  const long long n8 = static_cast<long long>(M) * N / 8;
+  const int n_vec = N / 8;
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < n8;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    for (int s = 0; s < splits; ++s) {
+      const float4* src = reinterpret_cast<const float4*>(partial + (static_cast<long long>(s) * n8 + i) * 8);
+      const float4 a = src[0], b = src[1];
+      acc[0] += a.x; acc[1] += a.y; acc[2] += a.z; acc[3] += a.w;
+      acc[4] += b.x; acc[5] += b.y; acc[6] += b.z; acc[7] += b.w;
+    }
+    const long long row = i / n_vec;
+    const int col = static_cast<int>(i - row * n_vec) * 8;
+    if (out_f32) {
+      float* o = reinterpret_cast<float*>(out) + row * ldo + col;
+      *reinterpret_cast<float4*>(o) = make_float4(acc[0], acc[1], acc[2], acc[3]);
+      *reinterpret_cast<float4*>(o + 4) = make_float4(acc[4], acc[5], acc[6], acc[7]);
+    } else {
+      uint4 ov;
+      ov.x = pack_bf16x2(acc[0], acc[1]);
+      ov.y = pack_bf16x2(acc[2], acc[3]);
+      ov.z = pack_bf16x2(acc[4], acc[5]);
+      ov.w = pack_bf16x2(acc[6], acc[7]);
+      *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(out) + row * ldo + col) = ov;
+    }
+  }
+}
+
 template <bool A_MN, bool B_MN, int BN>
 int launch(const CUtensorMap& ta, const CUtensorMap& tb, const Params& p, cudaStream_t stream) {
   auto kern = gemm_kernel<A_MN, B_MN, BN>;
@@ -293,9 +341,14 @@ int launch(const CUtensorMap& ta, const CUtensorMap& tb, const Params& p, cudaSt
     MDB_CHECK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes(BN)));
     configured = true;
   }
-  const int num_tiles = ((p.M + BM - 1) / BM) * ((p.N + BN - 1) / BN);
-  const int grid = num_tiles < sm_count() ? num_tiles : sm_count();
+  const int num_work = ((p.M + BM - 1) / BM) * ((p.N + BN - 1) / BN) * p.splits;
+  const int grid = num_work < sm_count() ? num_work : sm_count();
   kern<<<grid, NUM_THREADS, smem_bytes(BN), stream>>>(ta, tb, p);
+  if (p.splits > 1) {
+    const long long n8 = static_cast<long long>(p.M) * p.N / 8;
+    const int blocks = static_cast<int>(n8 / 256 + 1 < sm_count() * 4 ? n8 / 256 + 1 : sm_count() * 4);
+    splitk_fold_kernel<<<blocks, 256, 0, stream>>>(p.partial, p.out, p.ldo, p.M, p.N, p.splits, p.out_f32);
+  }
   return static_cast<int>(cudaGetLastError());
 }
 
@@ -307,10 +360,34 @@ static int g_force_tile_n = 0;
 // C entry point. A is [M,K] with leading dimension lda (a_mn_major = 0) or [K,M] (a_mn_major = 1);
 // B is [N,K] (b_mn_major = 0) or [K,N] (b_mn_major = 1). All leading dimensions are in elements and
 // must be multiples of 8; N must be a multiple of 8. Returns 0 or a CUDA / encoder error code.
+static int gemm_impl(const void* A, const void* B, void* out, const void* bias, const void* residual, const void* gate,
+                     int M, int N, int K, long long lda, long long ldb, long long ldo, long long ldr, long long gate_ld,
+                     int rows_per_batch, int a_mn_major, int b_mn_major, int epi, int out_f32, float alpha,
+                     float* partial, int splits, void* stream_ptr);
+
 extern "C" int mdb_gemm_bf16(const void* A, const void* B, void* out, const void* bias, const void* residual,
                              const void* gate, int M, int N, int K, long long lda, long long ldb, long long ldo,
                              long long ldr, long long gate_ld, int rows_per_batch, int a_mn_major, int b_mn_major,
                              int epi, int out_f32, float alpha, void* stream_ptr) {
+  return gemm_impl(A, B, out, bias, residual, gate, M, N, K, lda, ldb, ldo, ldr, gate_ld, rows_per_batch, a_mn_major,
+                   b_mn_major, epi, out_f32, alpha, nullptr, 1, stream_ptr);
+}
+
+// Split-K form: out = alpha * A B^T with the contraction cut into `splits` ranges that run as separate work items
+// (for products whose output has fewer tiles than the GPU has SMs: weight gradients). `partial` is a caller-provided
+// fp32 workspace of splits * M * N values; no bias / epilogue. The sum over splits runs in split order.
+extern "C" int mdb_gemm_bf16_splitk(const void* A, const void* B, void* out, int M, int N, int K, long long lda,
+                                    long long ldb, long long ldo, int a_mn_major, int b_mn_major, int out_f32,
+                                    float alpha, void* partial, int splits, void* stream_ptr) {
+  if (splits < 1 || splits > 64 || (splits > 1 && partial == nullptr)) return 3005;
+  return gemm_impl(A, B, out, nullptr, nullptr, nullptr, M, N, K, lda, ldb, ldo, 0, 0, 0, a_mn_major, b_mn_major, 0,
+                   out_f32, alpha, static_cast<float*>(partial), splits, stream_ptr);
+}
+
+static int gemm_impl(const void* A, const void* B, void* out, const void* bias, const void* residual, const void* gate,
+                     int M, int N, int K, long long lda, long long ldb, long long ldo, long long ldr, long long gate_ld,
+                     int rows_per_batch, int a_mn_major, int b_mn_major, int epi, int out_f32, float alpha,
+                     float* partial, int splits, void* stream_ptr) {
   using namespace mdb;
   using namespace mdb::gemm;
   if (M <= 0 || N <= 0 || K <= 0) return 0;
@@ -357,6 +434,16 @@ extern "C" int mdb_gemm_bf16(const void* A, const void* B, void* out, const void
   p.out_f32 = out_f32;
   p.alpha = alpha;
   p.status = status_buffer();
+  {
+    // every split gets at least one k-block: the count is recomputed from the rounded-up range
+    const int num_kb = (K + BK - 1) / BK;
+    int per = (num_kb + splits - 1) / splits;
+    if (per < 1) per = 1;
+    p.kb_per_split = per;
+    p.splits = (num_kb + per - 1) / per;
+    p.partial = partial;
+    if (p.splits <= 1) { p.splits = 1; p.kb_per_split = num_kb; }
+  }
   cudaStream_t stream = static_cast<cudaStream_t>(stream_ptr);
   if (BN == 256) {
     if (a_mn_major) {

@@ -22,8 +22,8 @@ class Linear(nn.Module):
     self.bias = nn.Parameter(torch.zeros(out_features)) if bias else None
     nn.init.normal_(self.weight, std=1.0 / math.sqrt(in_features))
 
-  def forward(self, x, activation: str | None = None):
-    return OF.linear(x, self.weight, self.bias, activation)
+  def forward(self, x, activation: str | None = None, residual=None):
+    return OF.linear(x, self.weight, self.bias, activation, residual)
 
   def extra_repr(self) -> str:
     return f"in_features={self.in_features}, out_features={self.out_features}, bias={self.bias is not None}"
@@ -88,6 +88,16 @@ class GroupNorm(nn.GroupNorm):
 
   def forward(self, x, act: bool = False):
     return OF.group_norm(x, self.num_groups, self.weight, self.bias, self.eps, act)
+
+
+class LayerNorm(nn.LayerNorm):
+  """`nn.LayerNorm` (same parameters and checkpoint keys) whose [B, S, C] CUDA bf16 inputs run on this repository's row
+  kernels, forward and backward (`ops.functional.layer_norm_mod`); statistics in fp32."""
+
+  def forward(self, x):
+    if x.dim() == 3 and self.elementwise_affine and len(self.normalized_shape) == 1:
+      return OF.layer_norm_mod(x, self.weight, self.bias, eps=self.eps)
+    return super().forward(x)
 
 
 class FP32LayerNorm(nn.Module):

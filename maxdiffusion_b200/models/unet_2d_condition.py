@@ -20,7 +20,7 @@ import torch.nn as nn
 import torch.nn.functional as F
 
 from ..ops import functional as OF
-from .layers import Conv2d, GroupNorm, Linear, sinusoidal_embedding
+from .layers import Conv2d, GroupNorm, LayerNorm, Linear, sinusoidal_embedding
 from .vae import ResnetBlock2D
 
 
@@ -84,13 +84,13 @@ class Attention(nn.Module):
     self.to_v = Linear(cross_dim or dim, dim, bias=False)
     self.to_out = nn.ModuleList([Linear(dim, dim)])
 
-  def forward(self, x, context=None):
+  def forward(self, x, context=None, residual=None):
     ctx = x if context is None else context
     B, S, C = x.shape
     q = self.to_q(x).view(B, S, self.heads, -1)
     k = self.to_k(ctx).view(B, ctx.shape[1], self.heads, -1)
     v = self.to_v(ctx).view(B, ctx.shape[1], self.heads, -1)
-    return self.to_out[0](OF.attention(q, k, v).reshape(B, S, C))
+    return self.to_out[0](OF.attention(q, k, v).reshape(B, S, C), residual=residual)
 
 
 class GEGLU(nn.Module):
@@ -101,8 +101,7 @@ class GEGLU(nn.Module):
     self.proj = Linear(dim, 2 * inner)
 
   def forward(self, x):
-    h, gate = self.proj(x).chunk(2, dim=-1)
-    return h * F.gelu(gate)
+    return OF.geglu(self.proj(x))
 
 
 class FeedForward(nn.Module):
@@ -111,22 +110,23 @@ class FeedForward(nn.Module):
     super().__init__()
     self.net = nn.ModuleList([GEGLU(dim, dim * mult), nn.Identity(), Linear(dim * mult, dim)])
 
-  def forward(self, x):
-    return self.net[2](self.net[0](x))
+  def forward(self, x, residual=None):
+    return self.net[2](self.net[0](x), residual=residual)
 
 
 class BasicTransformerBlock(nn.Module):
 
   def __init__(self, dim, heads, cross_dim):
     super().__init__()
-    self.norm1, self.norm2, self.norm3 = nn.LayerNorm(dim), nn.LayerNorm(dim), nn.LayerNorm(dim)
+    self.norm1, self.norm2, self.norm3 = LayerNorm(dim), LayerNorm(dim), LayerNorm(dim)
     self.attn1, self.attn2 = Attention(dim, heads), Attention(dim, heads, cross_dim)
     self.ff = FeedForward(dim)
 
   def forward(self, x, context):
-    x = x + self.attn1(self.norm1(x))
-    x = x + self.attn2(self.norm2(x), context)
-    return x + self.ff(self.norm3(x))
+    # the three residual adds ride in the epilogues of the output projections
+    x = self.attn1(self.norm1(x), residual=x)
+    x = self.attn2(self.norm2(x), context, residual=x)
+    return self.ff(self.norm3(x), residual=x)
 
 
 class Transformer2DModel(nn.Module):

@@ -199,6 +199,10 @@ class ChannelsLastDecoder:
     [rank W'/n, (rank + 1) W'/n) of the latent width and all ranks return the whole video."""
     if spatial is not None and spatial.size > 1 and z.shape[-1] % spatial.size == 0:
       self.halo = spatial
+      # the largest edge column of the decode: frames x rows x channels peaks at 4 * 8 * 96 = 4 * 4 * 192 per latent
+      # frame and row (time x 4, height x 8 at 96 channels); 4096 leaves room for the channel padding
+      frames = z.shape[2] if whole_clip else max(1, chunk)
+      spatial.reserve(4096 * z.shape[0] * frames * z.shape[3], z.dtype)
       try:
         strip = self._decode(spatial.shard(z, dim=-1), chunk, whole_clip)
       finally:

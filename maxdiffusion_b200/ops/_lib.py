@@ -122,6 +122,8 @@ def _declare(L: ctypes.CDLL) -> None:
   L.mdb_sm_count.restype = c_int
   L.mdb_gemm_bf16.argtypes = [c_void_p] * 6 + [c_int] * 3 + [c_ll] * 5 + [c_int] * 5 + [c_float, c_void_p]
   L.mdb_gemm_bf16.restype = c_int
+  L.mdb_gemm_bf16_splitk.argtypes = [c_void_p] * 3 + [c_int] * 3 + [c_ll] * 3 + [c_int] * 3 + [c_float, c_void_p, c_int, c_void_p]
+  L.mdb_gemm_bf16_splitk.restype = c_int
   L.mdb_gemm_force_tile_n.argtypes = [c_int]
   L.mdb_gemm_force_tile_n.restype = c_int
   L.mdb_flash_fwd.argtypes = ([c_void_p, ctypes.POINTER(c_void_p), ctypes.POINTER(c_void_p), c_void_p, c_void_p]
@@ -165,6 +167,10 @@ def _declare(L: ctypes.CDLL) -> None:
   L.mdb_gelu_fwd.restype = c_int
   L.mdb_gelu_bwd.argtypes = [c_void_p, c_void_p, c_void_p, c_ll, c_void_p]
   L.mdb_gelu_bwd.restype = c_int
+  L.mdb_geglu_fwd.argtypes = [c_void_p, c_void_p, c_ll, c_int, c_void_p]
+  L.mdb_geglu_fwd.restype = c_int
+  L.mdb_geglu_bwd.argtypes = [c_void_p, c_void_p, c_void_p, c_ll, c_int, c_void_p]
+  L.mdb_geglu_bwd.restype = c_int
   L.mdb_adamw.argtypes = [c_void_p] * 4 + [c_ll] + [c_float] * 9 + [c_ull, c_int, c_int, c_int, c_void_p]
   L.mdb_adamw.restype = c_int
   L.mdb_sumsq_maxabs.argtypes = [c_void_p, c_ll, c_int, c_void_p, c_void_p, c_int, c_void_p]

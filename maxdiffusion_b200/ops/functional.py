@@ -88,13 +88,18 @@ class remat:
 class _LinearFn(torch.autograd.Function):
 
   @staticmethod
-  def forward(ctx, x, w, b, act):
+  def forward(ctx, x, w, b, act, residual=None):
     x2 = x.reshape(-1, x.shape[-1])
     need_grad = any(ctx.needs_input_grad[:3])
     ctx.act = act
     ctx.x_shape = x.shape
     ctx.has_bias = b is not None
-    if act in ("gelu_tanh",) and need_grad:
+    if residual is not None:
+      # y = residual + x W^T + b: the add rides in the GEMM epilogue; its gradient is dy itself
+      r2 = residual.reshape(-1, w.shape[0])
+      y = K.gemm(x2, w, bias=b, epi="add_res", residual=r2 if r2.is_contiguous() else r2.contiguous())
+      ctx.save_for_backward(x2, w, None)
+    elif act in ("gelu_tanh",) and need_grad:
       u = K.gemm(x2, w, bias=b)
       y = K.gelu_fwd(u)
       ctx.save_for_backward(x2, w, u)
@@ -120,23 +125,26 @@ class _LinearFn(torch.autograd.Function):
       dw = K.gemm(dy2, x2, a_mn=True, b_mn=True)              # dW = dYᵀ · X
     if ctx.has_bias and ctx.needs_input_grad[2]:
       db = K.colsum(dy2).to(torch.bfloat16)
-    return dx, dw, db, None
+    return dx, dw, db, None, (dy if ctx.needs_input_grad[4] else None)
 
 
-def linear(x, weight, bias=None, activation: str | None = None):
-  """y = act(x @ weightᵀ + bias); weight is [out, in] (PyTorch / diffusers orientation)."""
+def linear(x, weight, bias=None, activation: str | None = None, residual=None):
+  """y = act(x @ weightᵀ + bias) (+ residual, without activation); weight is [out, in] (PyTorch / diffusers
+  orientation). The residual add runs in the GEMM epilogue."""
   if _fast(x) and x.shape[-1] % 8 == 0 and weight.shape[0] % 8 == 0:
     if weight.dtype != torch.bfloat16:
       weight = weight.to(torch.bfloat16)
     if bias is not None and bias.dtype != torch.bfloat16:
       bias = bias.to(torch.bfloat16)
-    return _LinearFn.apply(x, weight, bias, activation)
+    if residual is not None and (activation is not None or residual.dtype != torch.bfloat16):
+      return residual + _LinearFn.apply(x, weight, bias, activation)
+    return _LinearFn.apply(x, weight, bias, activation, residual)
   y = F.linear(x, weight.to(x.dtype), None if bias is None else bias.to(x.dtype))
   if activation == "gelu_tanh":
     y = F.gelu(y, approximate="tanh")
   elif activation == "silu":
     y = F.silu(y)
-  return y
+  return y if residual is None else residual + y
 
 
 def linear_gated_residual(x, weight, bias, residual, gate):
@@ -307,6 +315,27 @@ def layer_norm_mod(x, gamma=None, beta=None, scale=None, shift=None, eps: float 
         scale, shift = scale.contiguous(), shift.contiguous()
     return _LayerNormModFn.apply(x, gamma, beta, scale, shift, eps)
   return ref.layer_norm_mod(x, gamma, beta, scale, shift, eps)
+
+
+class _GegluFn(torch.autograd.Function):
+
+  @staticmethod
+  def forward(ctx, u):
+    ctx.save_for_backward(u)
+    return K.geglu_fwd(u)
+
+  @staticmethod
+  def backward(ctx, dy):
+    (u,) = ctx.saved_tensors
+    return K.geglu_bwd(dy if dy.is_contiguous() else dy.contiguous(), u)
+
+
+def geglu(u: torch.Tensor) -> torch.Tensor:
+  """u [..., 2 * inner] = (h | gate) -> h * gelu(gate), exact GELU; one kernel forward, one backward."""
+  if _fast(u) and u.shape[-1] % 16 == 0:
+    return _GegluFn.apply(u if u.is_contiguous() else u.contiguous())
+  h, gate = u.chunk(2, dim=-1)
+  return h * torch.nn.functional.gelu(gate)
 
 
 class _RmsRopeFn(torch.autograd.Function):

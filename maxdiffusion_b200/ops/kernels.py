@@ -26,9 +26,36 @@ def _rowmajor(t: torch.Tensor) -> torch.Tensor:
   return t if t.stride(-1) == 1 else t.contiguous()
 
 
+_SM_COUNT = 148
+
+
+def split_k_for(M: int, N: int, K: int, sms: int = _SM_COUNT) -> int:
+  """How many ranges to cut the contraction into (1 = no split). A product whose output has fewer 128 x 256 tiles
+  than the GPU has SMs leaves SMs idle for the whole contraction (weight gradients: K is the token count); splitting
+  K makes more work items at the price of fp32 partials that a fold kernel sums. The model: waves of work items
+  times k-blocks per item (about 0.4 us per k-block), plus the write and read of every partial at HBM speed."""
+  tiles = -(-M // 128) * -(-N // 256)
+  num_kb = -(-K // 64)
+  if tiles * 2 > sms or num_kb < 16:
+    return 1
+  fold_us = M * N * 8 / 5e6  # one partial written and read, in microseconds at 5 TB/s
+  best, best_cost = 1, -(-tiles // sms) * num_kb * 0.41
+  for s in range(2, 33):
+    per = -(-num_kb // s)
+    if per < 4:
+      break
+    s_eff = -(-num_kb // per)
+    cost = -(-tiles * s_eff // sms) * per * 0.41 + s_eff * fold_us + 2.0
+    if cost < best_cost * 0.9:
+      best, best_cost = s_eff, cost
+  return best
+
+
 def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = False, bias=None, epi: str = "none",
-         residual=None, gate=None, rows_per_batch: int = 0, out=None, out_dtype=torch.bfloat16, alpha: float = 1.0):
-  """D[M,N] = epi(alpha * A·Bᵀ + bias) on the tcgen05 GEMM. A: [M,K] (or [K,M] if a_mn); B: [N,K] (or [K,N])."""
+         residual=None, gate=None, rows_per_batch: int = 0, out=None, out_dtype=torch.bfloat16, alpha: float = 1.0,
+         split_k: int = 0):
+  """D[M,N] = epi(alpha * A·Bᵀ + bias) on the tcgen05 GEMM. A: [M,K] (or [K,M] if a_mn); B: [N,K] (or [K,N]).
+  `split_k`: 0 = chosen by `split_k_for` for plain products (no bias / epilogue), 1 = never, n = that many ranges."""
   assert a.dtype == torch.bfloat16 and b.dtype == torch.bfloat16 and a.dim() == 2 and b.dim() == 2
   a, b = _rowmajor(a), _rowmajor(b)
   K, M = (a.shape if a_mn else a.shape[::-1])
@@ -44,6 +71,15 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = F
     assert gate.dtype == torch.float32 and gate.stride(-1) == 1
   if bias is not None:
     assert bias.dtype == torch.bfloat16 and bias.is_contiguous()
+  plain = bias is None and epi == "none" and residual is None and gate is None
+  splits = (split_k_for(M, N, K) if split_k == 0 else split_k) if plain else 1
+  if splits > 1:
+    partial = torch.empty((splits, M, N), device=a.device, dtype=torch.float32)
+    rc = _lib.lib().mdb_gemm_bf16_splitk(_lib.ptr(a), _lib.ptr(b), _lib.ptr(out), M, N, K, a.stride(0), b.stride(0),
+                                         out.stride(0), int(a_mn), int(b_mn), int(out.dtype == torch.float32), float(alpha),
+                                         _lib.ptr(partial), splits, _lib.stream())
+    _lib.check(rc, "mdb_gemm_bf16_splitk")
+    return out
   rc = _lib.lib().mdb_gemm_bf16(
       _lib.ptr(a), _lib.ptr(b), _lib.ptr(out), _lib.ptr(bias), _lib.ptr(residual), _lib.ptr(gate), M, N, K,
       a.stride(0), b.stride(0), out.stride(0), residual.stride(0) if residual is not None else 0,
@@ -406,6 +442,24 @@ def gelu_bwd(dy, u):
   du = torch.empty_like(u)
   _lib.check(_lib.lib().mdb_gelu_bwd(_lib.ptr(dy), _lib.ptr(u), _lib.ptr(du), u.numel(), _lib.stream()),
              "mdb_gelu_bwd")
+  return du
+
+
+def geglu_fwd(u):
+  """u [..., 2 * inner] bf16 (h | gate) -> h * gelu(gate) [..., inner] (exact GELU)."""
+  assert u.is_contiguous() and u.dtype == torch.bfloat16 and u.shape[-1] % 16 == 0
+  inner = u.shape[-1] // 2
+  y = torch.empty((*u.shape[:-1], inner), dtype=u.dtype, device=u.device)
+  _lib.check(_lib.lib().mdb_geglu_fwd(_lib.ptr(u), _lib.ptr(y), u.numel() // (2 * inner), inner, _lib.stream()), "mdb_geglu_fwd")
+  return y
+
+
+def geglu_bwd(dy, u):
+  assert u.is_contiguous() and dy.is_contiguous() and dy.dtype == u.dtype == torch.bfloat16
+  inner = u.shape[-1] // 2
+  du = torch.empty_like(u)
+  _lib.check(_lib.lib().mdb_geglu_bwd(_lib.ptr(dy), _lib.ptr(u), _lib.ptr(du), u.numel() // (2 * inner), inner, _lib.stream()),
+             "mdb_geglu_bwd")
   return du
 
 

@@ -100,16 +100,24 @@ class HaloExchange:
     for col, buf in recv:
       y[..., col, :].copy_(buf)
 
-  def _buffers(self, numel: int, dtype):
-    if self._buf is None or self._cap < numel or self._buf.dtype != dtype:
-      old = self._buf
-      cap = max(numel, 2 * self._cap)
-      # [slot][side][cap]: side 0 = my left edge column (read by the left neighbour), side 1 = my right edge column
-      self._buf, self._ptrs, self._hdl = self.peer.alloc(4 * cap, dtype)
-      self._cap = cap
-      if old is not None:
-        self.peer.release([old])
-    return self._buf.view(2, 2, self._cap)
+  def reserve(self, numel: int, dtype) -> None:
+    """Sizes the symmetric edge buffers for edge columns of up to `numel` elements (every rank of the group, with
+    the same numbers). A decode reserves once for its largest layer, so that no exchange has to grow them."""
+    if self.peer is None or (self._buf is not None and self._cap >= numel and self._buf.dtype == dtype):
+      return
+    old = self._buf
+    if old is not None:
+      # neighbours may still be pulling from the old buffers: every rank drains its stream before any rank lets go
+      torch.cuda.synchronize()
+      dist.barrier(group=self.group)
+    cap = (max(numel, 2 * self._cap) + 7) // 8 * 8
+    # [slot][side][cap]: side 0 = my left edge column (read by the left neighbour), side 1 = my right edge column
+    self._buf, self._ptrs, self._hdl = self.peer.alloc(4 * cap, dtype)
+    self._cap = cap
+    if old is not None:
+      self.peer.release([old])
+    torch.cuda.synchronize()
+    dist.barrier(group=self.group)
 
   def _fill_peer(self, y):
     from . import symm
@@ -117,15 +125,14 @@ class HaloExchange:
     peer = self.peer
     edge = y[..., 0, :]
     n, es = edge.numel(), y.element_size()
-    grew = self._buf is None or self._cap < n or self._buf.dtype != y.dtype
-    buf = self._buffers(n, y.dtype)
+    self.reserve(n, y.dtype)
+    buf = self._buf.view(2, 2, self._cap)
     nbrs = [r for r in (self.left, self.right) if r is not None]
     e = peer.next_epoch(symm.FLAG_HALO_READY)
     slot = e & 1
-    if not grew:
-      # the slot's previous content (exchange e - 2) has been pulled by both neighbours; a fresh buffer has none,
-      # and its allocation was a rendezvous of the whole group
-      peer.wait(symm.FLAG_HALO_ACK, e - 2, sources=nbrs)
+    # the slot's previous content (exchange e - 2) has been pulled by both neighbours (a fresh buffer has none, but
+    # the acknowledgements of the exchanges before it were sent all the same)
+    peer.wait(symm.FLAG_HALO_ACK, e - 2, sources=nbrs)
     buf[slot, 0, :n].view(edge.shape).copy_(y[..., 1, :])
     buf[slot, 1, :n].view(edge.shape).copy_(y[..., -2, :])
     peer.signal(symm.FLAG_HALO_READY, e, peers=nbrs)

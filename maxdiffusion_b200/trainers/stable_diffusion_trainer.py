@@ -78,6 +78,14 @@ class StableDiffusionTrainer:
     self.timestep_weights = generate_timestep_weights(config, 1000)
     self.gen = torch.Generator(device=self.device).manual_seed(seed + 1 + 7919 * self.mesh.rank)
     self.step = 0
+    # forward + backward as one CUDA graph: only for the plain objective (Dreambooth's two-term loss and a trained
+    # text encoder run eagerly) on a GPU
+    self._graphed = None
+    if (bool(config.get("cuda_graph_train_step", False)) and self.device.type == "cuda" and not self.train_text_encoder
+        and type(self).loss is StableDiffusionTrainer.loss):
+      from .graphed_step import GraphedObjective
+
+      self._graphed = GraphedObjective(self.objective, list(self.unet.parameters()))
     self.snr_gamma = float(config.get("snr_gamma", -1.0))
     self.batch_size = max(1, int(float(config.get("per_device_batch_size", 1))))
 
@@ -107,35 +115,48 @@ class StableDiffusionTrainer:
     return out
 
   # ---- step -------------------------------------------------------------------------------
-  def loss(self, batch: dict) -> torch.Tensor:
+  def draw(self, batch: dict) -> dict:
+    """Everything random or data dependent of a step, as tensors: the noised latents, the timesteps, the regression
+    target, the per-sample loss weights and the conditioning. What remains (`objective`) is a fixed sequence of
+    kernels on fixed shapes."""
     latents = batch["latents"].to(self.device, torch.float32)
     B = latents.shape[0]
     noise = torch.randn(latents.shape, generator=self.gen, device=self.device)
     w = self.timestep_weights.to(self.device)
     timesteps = torch.multinomial(w, B, replacement=True, generator=self.gen)
     noisy = self.scheduler.add_noise(self.sched_state, latents, noise, timesteps)
-    added = None
+    out = {"noisy": noisy.to(self.dtype), "timesteps": timesteps,
+           "encoder_hidden_states": batch["encoder_hidden_states"].to(self.device)}
     if self.is_xl:
       res = int(self.config.get("resolution", 1024))
       time_ids = batch.get("time_ids")
       if time_ids is None:
         time_ids = get_add_time_ids((res, res), (0, 0), (res, res), B, self.device)
-      added = {"text_embeds": batch["text_embeds"].to(self.device), "time_ids": time_ids.to(self.device)}
-    pred = self.unet(noisy.to(self.dtype), timesteps, batch["encoder_hidden_states"].to(self.device), added).float()
+      out["text_embeds"], out["time_ids"] = batch["text_embeds"].to(self.device), time_ids.to(self.device)
     if self.prediction_type == "epsilon":
-      target = noise
+      out["target"] = noise
     elif self.prediction_type == "v_prediction":
-      target = self.scheduler.get_velocity(self.sched_state, latents, noise, timesteps)
+      out["target"] = self.scheduler.get_velocity(self.sched_state, latents, noise, timesteps)
     else:
       raise ValueError(self.prediction_type)
-    loss = (target - pred) ** 2
     if self.snr_gamma > 0:
       snr = compute_snr(self.sched_state.common.alphas_cumprod, timesteps)
       weights = torch.minimum(snr, torch.full_like(snr, self.snr_gamma)) / snr
       if self.prediction_type == "v_prediction":
         weights = weights * snr / (snr + 1)
+      out["weights"] = weights
+    return out
+
+  def objective(self, noisy, timesteps, encoder_hidden_states, target, text_embeds=None, time_ids=None, weights=None):
+    added = {"text_embeds": text_embeds, "time_ids": time_ids} if text_embeds is not None else None
+    pred = self.unet(noisy, timesteps, encoder_hidden_states, added).float()
+    loss = (target - pred) ** 2
+    if weights is not None:
       loss = loss.mean(dim=(1, 2, 3)) * weights
     return loss.mean()
+
+  def loss(self, batch: dict) -> torch.Tensor:
+    return self.objective(**self.draw(batch))
 
   def train_step(self, batch: dict) -> dict:
     batch = self.encode_batch({k: (v.to(self.device, non_blocking=True) if torch.is_tensor(v) else v) for k, v in batch.items()})
@@ -143,8 +164,11 @@ class StableDiffusionTrainer:
                      float(self.config.warmup_steps_fraction))
     # the noise / timestep stream is a function of (seed, rank, step): a resumed run continues it exactly
     self.gen.manual_seed(self.seed + 1 + 7919 * self.mesh.rank + 1000003 * self.step)
-    loss = self.loss(batch)
-    loss.backward()
+    if self._graphed is not None:
+      loss = self._graphed(self.draw(batch))  # forward + backward replayed from a CUDA graph
+    else:
+      loss = self.loss(batch)
+      loss.backward()
     stats = self.optimizer.step(lr)
     self.step += 1
     return {"learning/loss": loss.detach(), "learning/grad_norm": stats["grad_norm"], "learning/current_learning_rate": lr}

@@ -180,7 +180,7 @@ def bench_sdxl(args) -> dict:
       ["bench", os.path.join(CFG, "base_xl.yml"), "run_name=bench", f"per_device_batch_size={args.batch}",
        f"resolution={args.resolution}", "max_train_steps=1000000", "log_config=false", "write_metrics=false",
        "dataset_type=synthetic", f"unet_preset={args.preset}", f"ici_data_parallelism={n}", "ici_fsdp_parallelism=1",
-       "ici_context_parallelism=1"])
+       "ici_context_parallelism=1", f"cuda_graph_train_step={'false' if getattr(args, 'eager', False) else 'true'}"])
   tr = StableDiffusionXLTrainer(config, mesh=create_device_mesh(config))
   for _ in range(max(3, args.warmup)):
     float(tr.train_step(tr.synthetic_batch())["learning/loss"])
@@ -250,6 +250,7 @@ def add_arguments(ap: argparse.ArgumentParser) -> None:
   ap.add_argument("--ulysses", type=int, default=-1, help="Ulysses shards of the 2-D context split (-1: chosen from the GPU count)")
   ap.add_argument("--decode", action="store_true", help="wan: also time the VAE decode of the result")
   ap.add_argument("--preset", default=None)
+  ap.add_argument("--eager", action="store_true", help="sdxl: issue every kernel of the step instead of replaying a CUDA graph")
 
 
 def run_workload(model: str, args) -> dict:

@@ -76,7 +76,7 @@ def _sdxl(args):
       ["profile", os.path.join(CFG, "base_xl.yml"), "run_name=profile", f"per_device_batch_size={args.batch or 8}",
        f"resolution={args.resolution}", "max_train_steps=1000000", "log_config=false", "write_metrics=false",
        "dataset_type=synthetic", f"unet_preset={args.preset or 'sdxl'}", f"ici_data_parallelism={n}", "ici_fsdp_parallelism=1",
-       "ici_context_parallelism=1"])
+       "ici_context_parallelism=1", f"cuda_graph_train_step={'true' if args.graph else 'false'}"])
   tr = StableDiffusionXLTrainer(config, mesh=create_device_mesh(config))
   batches = [{k: v.to(tr.device) for k, v in tr.synthetic_batch().items()} for _ in range(args.steps)]
   return tr, (lambda b: tr.train_step(b)), batches
@@ -111,6 +111,7 @@ def main(argv=None) -> int:
   ap.add_argument("--preset", default=None)
   ap.add_argument("--resolution", type=int, default=1024)
   ap.add_argument("--batch", type=int, default=None)
+  ap.add_argument("--graph", action="store_true", help="sdxl_train: replay the step from a CUDA graph")
   ap.add_argument("--rows", type=int, default=25, help="kernel names listed under the family table")
   args = ap.parse_args(argv)
   rank, world, _ = init_distributed()

@@ -114,3 +114,39 @@ def test_band_filter_gemms_on_the_tensor_cores_match_the_fft_form(shape):
     got = CP.fft_compensate(a, b, c, w1, w2)
     want = CP.fft_compensate_reference(a, b, c, w1, w2)
     _close(got, want, 2e-4)
+
+
+@pytest.mark.parametrize("rows,inner", [(37, 64), (4096, 2560), (3, 5120)])
+def test_geglu_forward_and_backward_match_fp32(rows, inner):
+  from maxdiffusion_b200.ops import functional as OF
+
+  g = torch.Generator(device="cuda").manual_seed(0)
+  u = torch.randn((2, rows, 2 * inner), device="cuda", generator=g).to(torch.bfloat16).requires_grad_(True)
+  dy = torch.randn((2, rows, inner), device="cuda", generator=g).to(torch.bfloat16)
+  y = OF.geglu(u)
+  (du,) = torch.autograd.grad(y, u, dy)
+  uf = u.detach().float().requires_grad_(True)
+  h, gate = uf.chunk(2, dim=-1)
+  want = h * torch.nn.functional.gelu(gate)
+  (dwant,) = torch.autograd.grad(want, uf, dy.float())
+  assert (y.float() - want).abs().max() <= 2e-2 * (1 + want.abs().max())
+  assert (du.float() - dwant).abs().max() <= 2e-2 * (1 + dwant.abs().max())
+
+
+def test_linear_with_residual_in_the_epilogue_matches_fp32_forward_and_backward():
+  from maxdiffusion_b200.ops import functional as OF
+
+  g = torch.Generator(device="cuda").manual_seed(1)
+  x = torch.randn((2, 300, 640), device="cuda", generator=g).to(torch.bfloat16).requires_grad_(True)
+  r = torch.randn((2, 300, 320), device="cuda", generator=g).to(torch.bfloat16).requires_grad_(True)
+  w = (torch.randn((320, 640), device="cuda", generator=g) * 0.04).to(torch.bfloat16).requires_grad_(True)
+  b = torch.randn((320,), device="cuda", generator=g).to(torch.bfloat16).requires_grad_(True)
+  dy = torch.randn((2, 300, 320), device="cuda", generator=g).to(torch.bfloat16)
+  y = OF.linear(x, w, b, residual=r)
+  got = torch.autograd.grad(y, (x, r, w, b), dy)
+  xf, rf, wf, bf = (t.detach().float().requires_grad_(True) for t in (x, r, w, b))
+  want_y = rf + torch.nn.functional.linear(xf, wf, bf)
+  want = torch.autograd.grad(want_y, (xf, rf, wf, bf), dy.float())
+  assert (y.float() - want_y).abs().max() <= 2e-2 * (1 + want_y.abs().max())
+  for a, e in zip(got, want):
+    assert (a.float() - e).abs().max() <= 2e-2 * (1 + e.abs().max())

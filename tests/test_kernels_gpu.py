@@ -483,3 +483,24 @@ def test_tile_search_choice_changes_the_launched_attention_variant():
   finally:
     K._FLASH_TUNED.clear()
     K.flash_tune(0, 0)
+
+
+@pytest.mark.parametrize("a_mn,b_mn", [(True, True), (False, False), (False, True)])
+@pytest.mark.parametrize("M,N,Kd,splits", [(640, 640, 4096, 0), (320, 328, 2000, 3), (1280, 1280, 8192, 0), (136, 64, 1024, 16)])
+def test_gemm_split_k_matches_fp32(a_mn, b_mn, M, N, Kd, splits):
+  """The contraction cut into ranges with fp32 partials and an ordered fold (weight-gradient shapes: small output,
+  long K), chosen automatically or forced, bf16 and fp32 outputs, ragged K; and bitwise equal run to run."""
+  g = torch.Generator(device="cuda").manual_seed(0)
+  a = (torch.randn((Kd, M) if a_mn else (M, Kd), device="cuda", generator=g) * 0.5).to(torch.bfloat16)
+  b = (torch.randn((Kd, N) if b_mn else (N, Kd), device="cuda", generator=g) * 0.5).to(torch.bfloat16)
+  want = (a.float().t() if a_mn else a.float()) @ (b.float() if b_mn else b.float().t())
+  if splits == 0:
+    assert K.split_k_for(M, N, Kd) > 1
+  got = K.gemm(a, b, a_mn=a_mn, b_mn=b_mn, split_k=splits)
+  got32 = K.gemm(a, b, a_mn=a_mn, b_mn=b_mn, split_k=splits, out_dtype=torch.float32)
+  one = K.gemm(a, b, a_mn=a_mn, b_mn=b_mn, split_k=1, out_dtype=torch.float32)
+  scale = want.abs().max().item()
+  assert (got.float() - want).abs().max().item() <= 1e-2 * scale
+  assert (got32 - want).abs().max().item() <= 2e-3 * scale
+  assert (got32 - one).abs().max().item() <= 1e-3 * scale
+  assert torch.equal(got, K.gemm(a, b, a_mn=a_mn, b_mn=b_mn, split_k=splits))
