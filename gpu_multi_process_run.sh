@@ -22,5 +22,7 @@ export OMP_NUM_THREADS="${OMP_NUM_THREADS:-8}"
 
 echo "node ${NODE_RANK}/${NNODES}: ${GPUS_PER_NODE} ranks, coordinator ${COORDINATOR_ADDRESS}:${COORDINATOR_PORT}"
 # shellcheck disable=SC2086
+# MAX_RESTARTS > 0: when a rank fails (its own exception, or a peer's seen through the health monitor) every rank is
+# torn down and started again; the trainers resume from the latest checkpoint.
 exec python -m torch.distributed.run --nnodes="$NNODES" --node-rank="$NODE_RANK" --nproc-per-node="$GPUS_PER_NODE" \
-  --master-addr "$COORDINATOR_ADDRESS" --master-port "$COORDINATOR_PORT" $COMMAND
+  --master-addr "$COORDINATOR_ADDRESS" --master-port "$COORDINATOR_PORT" --max-restarts "${MAX_RESTARTS:-0}" $COMMAND

@@ -136,11 +136,13 @@ class HealthMonitor:
     key = f"{self.prefix}/barrier/{self._barrier_round}"
     self.store.add(key, 1)
     deadline = time.time() + (timeout_s if timeout_s is not None else self.timeout_s)
+    nap = 2e-4  # ranks in step arrive within a fraction of a millisecond: poll fast first, back off to poll_s
     while int(self.store.add(key, 0)) < self.world:
       self.check()
       if time.time() > deadline:
         raise TimeoutError(f"barrier {self._barrier_round}: {int(self.store.add(key, 0))}/{self.world} ranks arrived")
-      time.sleep(poll_s)
+      time.sleep(nap)
+      nap = min(poll_s, nap * 2)
 
 
 class guarded_step:

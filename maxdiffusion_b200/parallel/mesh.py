@@ -178,5 +178,13 @@ def init_distributed(backend: Optional[str] = None) -> tuple[int, int, int]:
     kwargs = {}
     if backend == "nccl":
       kwargs["device_id"] = torch.device("cuda", local_rank)
+    if env.get("TORCHELASTIC_USE_AGENT_STORE") == "True" and "MASTER_PORT" in env:
+      # Under a launcher that restarts failed jobs (`torch.distributed.run --max-restarts`) with a fixed master
+      # address, the launcher's store outlives an incarnation and still holds the addresses its ranks published.
+      # Every incarnation therefore works under its own key prefix (sub-groups inherit it from the default group).
+      from datetime import timedelta
+
+      base = dist.TCPStore(env["MASTER_ADDR"], int(env["MASTER_PORT"]), world, is_master=False, timeout=timedelta(minutes=10))
+      kwargs["store"] = dist.PrefixStore(f"/mdb/attempt_{env.get('TORCHELASTIC_RESTART_COUNT', '0')}", base)
     dist.init_process_group(backend=backend, rank=rank, world_size=world, **kwargs)
   return rank, world, local_rank

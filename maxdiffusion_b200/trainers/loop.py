@@ -9,6 +9,7 @@ metrics, save every `checkpoint_every` steps and at the end.
 """
 from __future__ import annotations
 
+import os
 import time
 from concurrent.futures import ThreadPoolExecutor
 from typing import Callable, Iterator, Optional
@@ -53,10 +54,38 @@ class EncodedBatchCache:
     return enc
 
 
+def _health_monitor(config, mesh):
+  """Heartbeats through the rendezvous store for multi-rank runs (`parallel.health`): a rank that raised or fell
+  silent is seen by the others BEFORE their next launch, so they leave with an exception instead of waiting in a
+  collective. Together with a launcher that restarts the ranks (`torch.distributed.run --max-restarts`,
+  `gpu_multi_process_run.sh`) and the restore at the top of this loop, that is the recovery path: fail, tear down,
+  start again from the last checkpoint."""
+  if not (dist.is_available() and dist.is_initialized() and dist.get_world_size() > 1 and config.get("health_monitor", True)):
+    return None
+  from ..parallel.health import HealthMonitor
+
+  # one key space per incarnation of the job: a restarted run must not read the failure that ended the previous one
+  incarnation = os.environ.get("TORCHELASTIC_RESTART_COUNT", "0")
+  return HealthMonitor(timeout_s=float(config.get("health_timeout_s", 120.0)), prefix=f"mdb_health/{incarnation}").start()
+
+
+def _maybe_inject_failure(config, trainer) -> None:
+  """Host-side fault injection for the recovery tests: the configured rank raises before the configured step, in
+  the first incarnation of the job only (a launcher that restarts the ranks counts incarnations in
+  TORCHELASTIC_RESTART_COUNT). Nothing on the device is touched."""
+  at = int(config.get("inject_failure_at_step", -1))
+  if at < 0 or trainer.step != at or int(os.environ.get("TORCHELASTIC_RESTART_COUNT", "0")) != 0:
+    return
+  if trainer.mesh.rank == int(config.get("inject_failure_rank", 0)):
+    raise RuntimeError(f"injected host failure on rank {trainer.mesh.rank} before step {at}")
+
+
 def run_training_loop(trainer, data, checkpointer=None, evaluate: Optional[Callable[[int], dict]] = None):
   """Drives `trainer.train_step` until `max_train_steps`. `trainer` provides `config`, `mesh`, `step` and `train_step`;
   `checkpointer` provides `maybe_restore(trainer)` and `save(step, trainer)`. `data` is an iterator of batches or a
   function that builds one; the function is called AFTER the restore, so that it can start at the restored step."""
+  from ..parallel.health import guarded_step
+
   config = trainer.config
   max_steps = int(config.max_train_steps)
   every = int(config.get("checkpoint_every", -1))
@@ -68,6 +97,8 @@ def run_training_loop(trainer, data, checkpointer=None, evaluate: Optional[Calla
   if callable(data) and not hasattr(data, "__next__"):
     data = iter(data())
   writer = MetricsWriter(config, trainer.mesh.rank)
+  monitor = _health_monitor(config, trainer.mesh)
+  step_barrier = bool(config.get("health_step_barrier", True))
   pool = ThreadPoolExecutor(max_workers=1)
   nxt = pool.submit(lambda: next(data))
   try:
@@ -75,9 +106,15 @@ def run_training_loop(trainer, data, checkpointer=None, evaluate: Optional[Calla
       batch = nxt.result()
       nxt = pool.submit(lambda: next(data))
       t0 = time.perf_counter()
-      m = trainer.train_step(batch)
-      scalars = {k: float(v) for k, v in m.items()}  # device -> host: ends the step
-      _lib.raise_on_device_status_if_loaded()
+      with guarded_step(monitor, trainer.step):  # peers checked first; this rank's exception is announced to them
+        _maybe_inject_failure(config, trainer)
+        if monitor is not None and step_barrier:
+          # every rank has reached this step alive (or its failure report is seen here) before any rank enters the
+          # step's collectives: a few store round trips per step against a collective that would wait out its timeout
+          monitor.barrier(timeout_s=float(config.get("health_timeout_s", 120.0)))
+        m = trainer.train_step(batch)
+        scalars = {k: float(v) for k, v in m.items()}  # device -> host: ends the step
+        _lib.raise_on_device_status_if_loaded()
       scalars["perf/step_time_seconds"] = time.perf_counter() - t0
       writer.write(trainer.step, scalars)
       if evaluate is not None and eval_every > 0 and trainer.step % eval_every == 0:
@@ -88,6 +125,8 @@ def run_training_loop(trainer, data, checkpointer=None, evaluate: Optional[Calla
       _save(checkpointer, trainer)
   finally:
     writer.close()
+    if monitor is not None:
+      monitor.stop()
     pool.shutdown(wait=False, cancel_futures=True)
     if checkpointer is not None and getattr(checkpointer, "manager", None) is not None:
       checkpointer.manager.wait_until_finished()

@@ -215,11 +215,13 @@ def bench_sdxl(args) -> dict:
   def lin_hook(mod, inp, out):
     counted["total"] += 2.0 * out.numel() * mod.weight.shape[-1]
 
+  from ..models.layers import Linear as KernelLinear
+
   hooks = []
   for mod in tr.unet.modules():
     if isinstance(mod, nn.Conv2d):
       hooks.append(mod.register_forward_hook(conv_hook))
-    elif isinstance(mod, nn.Linear):
+    elif isinstance(mod, (nn.Linear, KernelLinear)):
       hooks.append(mod.register_forward_hook(lin_hook))
   with torch.no_grad():
     tr.loss({k: v.to(tr.device) for k, v in host[0].items()})

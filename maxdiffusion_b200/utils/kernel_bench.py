@@ -97,6 +97,41 @@ def bench_gemm_small_m(results):
     del a, b, out
 
 
+def bench_gemm_unet(results):
+  """The GEMM shapes of the SDXL UNet's transformer blocks at batch 8 (short contractions: K = 640 / 1280, where the
+  epilogue weighs as much as the main loop): plain, with bias, with bias + residual add, dgrad, and the weight
+  gradient with and without split-K; cuBLAS (`F.linear` / `torch.matmul` + the separate add) beside each."""
+  import torch.nn.functional as F
+
+  tf_peak, _, tag = peaks()
+  for M, N, Kd in [(8192, 1280, 1280), (8192, 10240, 1280), (8192, 1280, 5120), (32768, 640, 640), (32768, 5120, 640)]:
+    a = torch.randn((M, Kd), device="cuda", dtype=torch.bfloat16)
+    b = torch.randn((N, Kd), device="cuda", dtype=torch.bfloat16) * 0.03
+    bias = torch.randn((N,), device="cuda", dtype=torch.bfloat16)
+    res = torch.randn((M, N), device="cuda", dtype=torch.bfloat16)
+    dy = torch.randn((M, N), device="cuda", dtype=torch.bfloat16)
+    out = torch.empty((M, N), device="cuda", dtype=torch.bfloat16)
+    fl = 2.0 * M * N * Kd
+    row = dict(kernel="gemm_bf16_unet", shape=[M, N, Kd], of=tag)
+    row["plain_ms"], _ = time_ms(lambda: K.gemm(a, b, out=out))
+    row["bias_ms"], _ = time_ms(lambda: K.gemm(a, b, bias=bias, out=out))
+    row["bias_res_ms"], _ = time_ms(lambda: K.gemm(a, b, bias=bias, epi="add_res", residual=res, out=out))
+    row["dgrad_ms"], _ = time_ms(lambda: K.gemm(dy, b, b_mn=True))
+    row["wgrad_ms"], _ = time_ms(lambda: K.gemm(dy, a, a_mn=True, b_mn=True))
+    row["wgrad_nosplit_ms"], _ = time_ms(lambda: K.gemm(dy, a, a_mn=True, b_mn=True, split_k=1))
+    row["wgrad_splits"] = K.split_k_for(N, Kd, M)
+    row["cublas_plain_ms"], _ = time_ms(lambda: torch.matmul(a, b.t(), out=out))
+    row["cublas_bias_ms"], _ = time_ms(lambda: F.linear(a, b, bias))
+    row["cublas_bias_res_ms"], _ = time_ms(lambda: F.linear(a, b, bias).add_(res))
+    row["cublas_dgrad_ms"], _ = time_ms(lambda: torch.matmul(dy, b))
+    row["cublas_wgrad_ms"], _ = time_ms(lambda: torch.matmul(dy.t(), a))
+    row["tflops_plain"] = fl / row["plain_ms"] / 1e9
+    row["frac_plain"] = row["tflops_plain"] / tf_peak
+    results.append(row)
+    print(row, flush=True)
+    del a, b, res, dy, out
+
+
 def bench_gemm_fp8(results):
   tf_peak, _, tag = peaks()
   for M, N, Kd in [(32760, 5120, 5120), (32760, 13824, 5120), (4096, 5120, 5120)]:
@@ -375,6 +410,8 @@ def main(argv):
     bench_gemm(results)
   if "gemm_small_m" in which:
     bench_gemm_small_m(results)
+  if "gemm_unet" in which:
+    bench_gemm_unet(results)
   if "gemm_fp8" in which:
     bench_gemm_fp8(results)
   if "flash" in which:
