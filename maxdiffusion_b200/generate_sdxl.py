@@ -16,6 +16,10 @@ def run(config):
     from .loaders.sd_loader import load_sd_pipeline
 
     pipe = load_sd_pipeline(config, StableDiffusionXLPipeline)
+  if config.get("enable_lora", False):
+    from .loaders.lora_loader import apply_unet_loras
+
+    apply_unet_loras(pipe, config)  # reference: `maybe_load_lora` in generate_sdxl.py:60-110
   kw = {}
   if not pipe.text_encoders:
     g = torch.Generator().manual_seed(int(config.seed))

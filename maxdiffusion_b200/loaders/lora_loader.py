@@ -29,11 +29,11 @@ def parse_lora_dict(sd: Dict[str, torch.Tensor]) -> Dict[str, dict]:
     for p in _PREFIXES:
       if k.startswith(p):
         k = k[len(p):]
-    m = re.match(r"(.*)\.(lora_A|lora_down)(?:\.default)?\.weight$", k)
+    m = re.match(r"(.*)\.(lora_A|lora_down|down)(?:\.default)?\.weight$", k)  # `.down.weight`: XLabs
     if m:
       out.setdefault(m.group(1), {})["down"] = t
       continue
-    m = re.match(r"(.*)\.(lora_B|lora_up)(?:\.default)?\.weight$", k)
+    m = re.match(r"(.*)\.(lora_B|lora_up|up)(?:\.default)?\.weight$", k)
     if m:
       out.setdefault(m.group(1), {})["up"] = t
       continue
@@ -128,7 +128,65 @@ def merge_wan_loras(pipe, config) -> None:
 
 
 class LoRALinear(nn.Module):
-  """Run-time adapter around a Linear-like module: y = base(x) + sum_a scale_a * up_a(down_a(x))."""
+  """Run-time adapter around a Linear-like module: y = base(x) + sum_a scale_a * up_a(down_a(x)). An adapter may
+  write to a row range of the output only (`rows` = (first, count), count -1 = to the end): separate q / k / v adapters
+  on a fused projection."""
+
+  def __init__(self, base: nn.Module):
+    super().__init__()
+    self.base = base
+    self.adapters = nn.ModuleDict()
+    self.scales: Dict[str, float] = {}
+    self.rows: Dict[str, Optional[tuple]] = {}
+
+  def add_adapter(self, name: str, down: torch.Tensor, up: torch.Tensor, scale: float, rows: Optional[tuple] = None):
+    key = name if name not in self.adapters else f"{name}#{len(self.adapters)}"  # q, k and v of one adapter share a name
+    a = nn.ModuleDict({"down": nn.Linear(down.shape[1], down.shape[0], bias=False), "up": nn.Linear(up.shape[1], up.shape[0], bias=False)})
+    w = self.base.weight
+    a["down"].weight.data = down.to(w.device, w.dtype)
+    a["up"].weight.data = up.to(w.device, w.dtype)
+    self.adapters[key] = a
+    self.scales[key] = scale
+    if rows is not None:
+      first, count = rows
+      count = w.shape[0] - first if count < 0 else count
+      if up.shape[0] != count:
+        raise ValueError(f"adapter {name}: {up.shape[0]} output rows for a slice of {count}")
+      rows = (first, count)
+    elif up.shape[0] != w.shape[0]:
+      raise ValueError(f"adapter {name}: {up.shape[0]} output rows for a weight of {w.shape[0]}")
+    self.rows[key] = rows
+
+  @property
+  def weight(self):
+    return self.base.weight
+
+  @property
+  def bias(self):
+    return self.base.bias
+
+  def forward(self, x, activation: Optional[str] = None, residual=None):
+    y = self.base(x)
+    for name, a in self.adapters.items():
+      d = self.scales[name] * a["up"](a["down"](x))
+      if self.rows[name] is None:
+        y = y + d
+      else:
+        first, count = self.rows[name]
+        y = torch.cat([y[..., :first], y[..., first:first + count] + d, y[..., first + count:]], dim=-1)
+    # the adapters act on the pre-activation, so an activation / residual the base would have fused comes after them
+    if activation == "gelu_tanh":
+      y = nn.functional.gelu(y, approximate="tanh")
+    elif activation == "silu":
+      y = nn.functional.silu(y)
+    elif activation is not None:
+      raise ValueError(f"unknown activation {activation}")
+    return y if residual is None else residual + y
+
+
+class LoRAConv2d(nn.Module):
+  """LoCon run-time adapter around a convolution: a k x k down convolution to `rank` channels (with the base's stride
+  and padding) followed by a 1 x 1 up convolution (reference: src/maxdiffusion/models/lora_nnx.py:90-147)."""
 
   def __init__(self, base: nn.Module):
     super().__init__()
@@ -136,11 +194,16 @@ class LoRALinear(nn.Module):
     self.adapters = nn.ModuleDict()
     self.scales: Dict[str, float] = {}
 
-  def add_adapter(self, name: str, down: torch.Tensor, up: torch.Tensor, scale: float):
-    a = nn.ModuleDict({"down": nn.Linear(down.shape[1], down.shape[0], bias=False), "up": nn.Linear(up.shape[1], up.shape[0], bias=False)})
+  def add_adapter(self, name: str, down: torch.Tensor, up: torch.Tensor, scale: float, rows=None):
     w = self.base.weight
-    a["down"].weight.data = down.to(w.device, w.dtype)
-    a["up"].weight.data = up.to(w.device, w.dtype)
+    if down.dim() == 2:
+      down = down[:, :, None, None]
+    if up.dim() == 2:
+      up = up[:, :, None, None]
+    if tuple(down.shape[2:]) not in ((1, 1), tuple(w.shape[2:])) or up.shape[0] != w.shape[0] or down.shape[1] != w.shape[1]:
+      raise ValueError(f"adapter {name}: down {tuple(down.shape)} / up {tuple(up.shape)} do not fit a weight of {tuple(w.shape)}")
+    a = nn.ParameterDict({"down": nn.Parameter(down.to(w.device, w.dtype), requires_grad=False),
+                          "up": nn.Parameter(up.to(w.device, w.dtype), requires_grad=False)})
     self.adapters[name] = a
     self.scales[name] = scale
 
@@ -153,10 +216,34 @@ class LoRALinear(nn.Module):
     return self.base.bias
 
   def forward(self, x, *args, **kw):
+    import torch.nn.functional as F
+
     y = self.base(x, *args, **kw)
+    if kw.get("upsample") or (args and args[0]):
+      x = F.interpolate(x, scale_factor=2.0, mode="nearest")  # the base folded a nearest-2x into its convolution
+    stride = self.base.stride
     for name, a in self.adapters.items():
-      y = y + self.scales[name] * a["up"](a["down"](x))
+      k = a["down"].shape[-1]
+      pad = tuple(p if k > 1 else 0 for p in (self.base.padding if not isinstance(self.base.padding, str) else (k // 2, k // 2)))
+      h = F.conv2d(x, a["down"].to(x.dtype), None, stride, pad)
+      y = y + self.scales[name] * F.conv2d(h, a["up"].to(x.dtype))
     return y
+
+
+def _wrap(model: nn.Module, modules: dict, target: str):
+  """Replaces module `target` of `model` by its adapter wrapper (once) and returns the wrapper."""
+  mod = modules[target]
+  if isinstance(mod, (LoRALinear, LoRAConv2d)):
+    return mod
+  parent_name, _, leaf = target.rpartition(".")
+  parent = modules[parent_name] if parent_name else model
+  wrapped = LoRAConv2d(mod) if isinstance(mod, nn.Conv2d) else LoRALinear(mod)
+  if leaf.isdigit():
+    parent[int(leaf)] = wrapped
+  else:
+    setattr(parent, leaf, wrapped)
+  modules[target] = wrapped
+  return wrapped
 
 
 def add_runtime_adapters(model: nn.Module, lora_sd: Dict[str, torch.Tensor], adapter_name: str, scale: float = 1.0,
@@ -168,20 +255,69 @@ def add_runtime_adapters(model: nn.Module, lora_sd: Dict[str, torch.Tensor], ada
     target = rename(path.replace("_", ".") if path not in modules and path.replace("_", ".") in modules else path)
     if target not in modules or "down" not in entry:
       continue
-    mod = modules[target]
-    if not isinstance(mod, LoRALinear):
-      parent_name, _, leaf = target.rpartition(".")
-      parent = modules[parent_name] if parent_name else model
-      wrapped = LoRALinear(mod)
-      if leaf.isdigit():
-        parent[int(leaf)] = wrapped
-      else:
-        setattr(parent, leaf, wrapped)
-      modules[target] = mod = wrapped
+    mod = _wrap(model, modules, target)
     rank = entry["down"].shape[0]
-    mod.add_adapter(adapter_name, entry["down"].flatten(1), entry["up"].flatten(1), scale * entry.get("alpha", rank) / rank)
+    down, up = (entry["down"], entry["up"]) if isinstance(mod, LoRAConv2d) else (entry["down"].flatten(1), entry["up"].flatten(1))
+    mod.add_adapter(adapter_name, down, up, scale * entry.get("alpha", rank) / rank)
     n += 1
   return n
+
+
+def add_unet_adapters(unet: nn.Module, lora_sd: Dict[str, torch.Tensor], adapter_name: str, scale: float = 1.0,
+                      text_encoders=()) -> dict:
+  """SD / SDXL: a LoRA file in any published naming (diffusers / PEFT, Kohya, Kohya on SGM block numbers; linear and
+  convolution adapters) as run-time adapters on the UNet and, for `lora_te*` entries, on the text encoders.
+  Returns counts: {"unet": n, "text_encoder": n, "unresolved": [paths]}."""
+  from .lora_conversion_utils import convert_unet_lora, module_table
+
+  cfg = getattr(unet, "cfg", None)
+  unet_map, te_map, missed = convert_unet_lora(lora_sd, unet, getattr(cfg, "layers_per_block", 2))
+  modules = dict(unet.named_modules())
+  counts = {"unet": 0, "text_encoder": 0, "unresolved": missed}
+  for target, entry in unet_map.items():
+    if "down" not in entry:
+      continue
+    mod = _wrap(unet, modules, target)
+    rank = entry["down"].shape[0]
+    down, up = (entry["down"], entry["up"]) if isinstance(mod, LoRAConv2d) else (entry["down"].flatten(1), entry["up"].flatten(1))
+    mod.add_adapter(adapter_name, down, up, scale * entry.get("alpha", rank) / rank)
+    counts["unet"] += 1
+  for index, entries in te_map.items():
+    if index >= len(text_encoders) or text_encoders[index] is None:
+      counts["unresolved"].extend(f"lora_te{index + 1}_{k}" for k in entries)
+      continue
+    enc = text_encoders[index]
+    table, mods = module_table(enc), dict(enc.named_modules())
+    for flat, entry in entries.items():
+      target = table.get(flat.replace(".", "_"))
+      if target is None or "down" not in entry or not hasattr(mods[target], "weight"):
+        counts["unresolved"].append(f"lora_te{index + 1}_{flat}")
+        continue
+      rank = entry["down"].shape[0]
+      _wrap(enc, mods, target).add_adapter(adapter_name, entry["down"].flatten(1), entry["up"].flatten(1),
+                                           scale * entry.get("alpha", rank) / rank)
+      counts["text_encoder"] += 1
+  return counts
+
+
+def add_flux_adapters(model: nn.Module, lora_sd: Dict[str, torch.Tensor], adapter_name: str, scale: float = 1.0) -> dict:
+  """Flux: BFL / Kohya, XLabs and diffusers / PEFT files onto the fused projections of `FluxTransformer2DModel`
+  (separate q / k / v adapters become row slices). Returns {"adapters": n, "unresolved": [paths]}."""
+  from .lora_conversion_utils import convert_flux_lora
+
+  cfg = model.cfg
+  items, missed = convert_flux_lora(lora_sd, cfg.num_attention_heads * cfg.attention_head_dim)
+  modules = dict(model.named_modules())
+  n = 0
+  for target, rows, entry in items:
+    if target not in modules or "down" not in entry:
+      missed.append(target)
+      continue
+    rank = entry["down"].shape[0]
+    _wrap(model, modules, target).add_adapter(adapter_name, entry["down"].flatten(1), entry["up"].flatten(1),
+                                              scale * entry.get("alpha", rank) / rank, rows=rows)
+    n += 1
+  return {"adapters": n, "unresolved": missed}
 
 
 def apply_flux_loras(pipe, config) -> None:
@@ -190,4 +326,15 @@ def apply_flux_loras(pipe, config) -> None:
   lc = config.lora_config
   for path, name, adapter, scale in zip(lc["lora_model_name_or_path"], lc["weight_name"], lc["adapter_name"], lc.get("scale", [1.0] * 99)):
     sd = load_file(os.path.join(path, name) if os.path.isdir(path) else path)
-    add_runtime_adapters(pipe.transformer, sd, adapter, float(scale))
+    add_flux_adapters(pipe.transformer, sd, adapter, float(scale))
+
+
+def apply_unet_loras(pipe, config) -> None:
+  """SD / SDXL pipelines (reference: loaders/lora_pipeline.py:136-170)."""
+  from safetensors.torch import load_file
+
+  lc = config.lora_config
+  encoders = [e for e in (getattr(pipe, "text_encoder", None), getattr(pipe, "text_encoder_2", None))]
+  for path, name, adapter, scale in zip(lc["lora_model_name_or_path"], lc["weight_name"], lc["adapter_name"], lc.get("scale", [1.0] * 99)):
+    sd = load_file(os.path.join(path, name) if os.path.isdir(path) else path)
+    add_unet_adapters(pipe.unet, sd, adapter, float(scale), text_encoders=encoders)

@@ -23,7 +23,7 @@ import torch.nn as nn
 import torch.nn.functional as F
 
 from ...ops import functional as OF
-from ..layers import Linear, sinusoidal_embedding
+from ..layers import Linear, project_gated_residual, sinusoidal_embedding
 
 
 @dataclass
@@ -146,12 +146,14 @@ class FluxDoubleBlock(nn.Module):
     v = torch.cat([vt.unflatten(-1, (H, C // H)), vi.unflatten(-1, (H, C // H))], dim=1)
     o = OF.attention(q, k, v).reshape(B, St + Si, C)
     ot, oi = o[:, :St], o[:, St:]
-    img = OF.linear_gated_residual(oi, self.to_out.weight, self.to_out.bias, img, g_i)
-    txt = OF.linear_gated_residual(ot, self.to_add_out.weight, self.to_add_out.bias, txt, g_t)
-    h = OF.linear(OF.layer_norm_mod(img, scale=sc2_i, shift=sh2_i), self.ff_in.weight, self.ff_in.bias, "gelu_tanh")
-    img = OF.linear_gated_residual(h, self.ff_out.weight, self.ff_out.bias, img, g2_i)
-    h = OF.linear(OF.layer_norm_mod(txt, scale=sc2_t, shift=sh2_t), self.ff_context_in.weight, self.ff_context_in.bias, "gelu_tanh")
-    txt = OF.linear_gated_residual(h, self.ff_context_out.weight, self.ff_context_out.bias, txt, g2_t)
+    # projections are called as modules so that wrappers (run-time LoRA adapters, quantised layers) take effect; a
+    # plain `Linear` still gets the gate and the residual add in its GEMM epilogue
+    img = project_gated_residual(self.to_out, oi, img, g_i)
+    txt = project_gated_residual(self.to_add_out, ot, txt, g_t)
+    h = self.ff_in(OF.layer_norm_mod(img, scale=sc2_i, shift=sh2_i), "gelu_tanh")
+    img = project_gated_residual(self.ff_out, h, img, g2_i)
+    h = self.ff_context_in(OF.layer_norm_mod(txt, scale=sc2_t, shift=sh2_t), "gelu_tanh")
+    txt = project_gated_residual(self.ff_context_out, h, txt, g2_t)
     return _clip(img), _clip(txt)
 
 
@@ -176,7 +178,7 @@ class FluxSingleBlock(nn.Module):
     k = OF.rms_norm_rope(k, self.norm_k, *rope, heads=H, per_head=True)
     o = OF.attention(q, k, v.unflatten(-1, (H, C // H))).reshape(B, S, C)
     cat = torch.cat([o, F.gelu(mlp, approximate="tanh")], dim=-1)
-    return _clip(OF.linear_gated_residual(cat, self.proj_out.weight, self.proj_out.bias, x, gate))
+    return _clip(project_gated_residual(self.proj_out, cat, x, gate))
 
 
 class FluxTransformer2DModel(nn.Module):

@@ -398,3 +398,45 @@ def test_vae_decode_split_over_the_width_with_halo_exchange(world, peer_memory):
     assert shape == (1, 3, 13, 48, 64 * world)
     assert err <= 2e-2 * (1 + scale) and err2 <= 2e-2 * (1 + scale), (err, err2, scale)
     assert exchanges > 40
+
+
+def _small_allreduce_peer_absent(rank, world):
+  import torch.distributed as dist
+
+  from maxdiffusion_b200.ops import _lib
+  from maxdiffusion_b200.parallel import symm
+
+  peer = symm.PeerGroup(dist.group.WORLD)
+  ar = symm.SmallAllReduce(peer, capacity=64)
+  x = torch.full((8,), float(rank + 1), device="cuda")
+  before = ar(x).tolist()
+  torch.cuda.synchronize()
+  dist.barrier()
+  raised = None
+  if rank == 0:
+    # the peer sits this call out: with a 50 ms budget the kernel gives up by itself and the host hears why
+    old, symm.WAIT_BUDGET_S = symm.WAIT_BUDGET_S, 0.05
+    try:
+      ar(x)
+      torch.cuda.synchronize()
+      _lib.raise_on_device_status()
+    except _lib.KernelError as e:
+      raised = str(e)
+    finally:
+      symm.WAIT_BUDGET_S = old
+  else:
+    peer.next_epoch(symm.FLAG_SMALL_AR)  # keeps this rank's epoch count in step with the rank that tried
+  dist.barrier()
+  after = ar(x).tolist()  # the group goes on working
+  return before, raised, after
+
+
+def test_small_allreduce_whose_peer_never_joins_times_out_and_the_group_recovers():
+  """Host-made failure on 2 GPUs: one rank does not make the call (it is between steps, nothing of its own in flight);
+  the other rank's wait runs out after 50 ms, the status word names the site, and the next call of both ranks is right."""
+  if torch.cuda.device_count() < 2:
+    pytest.skip("needs 2 GPUs")
+  res = _spawn(_small_allreduce_peer_absent, 2)
+  for rank, (before, raised, after) in enumerate(res):
+    assert before == [3.0] * 8 and after == [3.0] * 8
+    assert (raised is not None and "timed out" in raised) if rank == 0 else raised is None
