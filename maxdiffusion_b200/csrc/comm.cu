@@ -57,12 +57,13 @@ __global__ void wait_flags_kernel(const unsigned int* flags, int n, int stride, 
                                   unsigned long long budget_ns, DeviceStatus* status) {
   const int i = threadIdx.x;
   if (i >= n) return;
-  if (status != nullptr && *reinterpret_cast<volatile unsigned int*>(&status->code) != 0u) return;
+  if (status_failed(status)) return;
   const uint64_t t0 = global_timer_ns();
   unsigned int spins = 0;
   while (ld_acquire_sys(flags + static_cast<long long>(i) * stride) < target) {
     if ((++spins & 0x3fu) == 0u) {
       __nanosleep(200);
+      if (status_failed(status)) return;
       if (global_timer_ns() - t0 > budget_ns) {
         report_status(status, kStatusFlagTimeout, 100, static_cast<unsigned int>(i));
         return;
@@ -201,6 +202,10 @@ small_allreduce_kernel(const float* __restrict__ in, float* __restrict__ out, in
     while (ld_acquire_sys(my_flag) < epoch) {
       if ((++spins & 0x3fu) == 0u) {
         __nanosleep(100);
+        if (status_failed(status)) {
+          atomicExch(&failed, 1);
+          break;
+        }
         if (global_timer_ns() - t0 > budget_ns) {
           report_status(status, kStatusFlagTimeout, 110, threadIdx.x);
           atomicExch(&failed, 1);

@@ -117,6 +117,10 @@ __device__ __forceinline__ bool wait_flag(const unsigned int* flag, unsigned int
     if (v >= target) return true;
     if ((++spins & 0xffu) == 0u) {
       if (*abort_flag) return false;
+      if (status_failed(st)) {
+        *abort_flag = 1;
+        return false;
+      }
       if (global_timer_ns() - t0 > kPeerWaitBudgetNs + kWaitBudgetNs) {  // outlasts the copy CTAs' own wait
         *abort_flag = 1;
         report_status(st, kStatusFlagTimeout, 40, detail);
@@ -176,10 +180,16 @@ __device__ __forceinline__ void copy_cta(const CopyPlan& cp, int ci, DeviceStatu
           unsigned int v;
           asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(cp.ready[i]) : "memory");
           if (v >= cp.epoch) break;
-          if ((++spins & 0xffu) == 0u && global_timer_ns() - t0 > kPeerWaitBudgetNs) {
-            report_status(status, kStatusFlagTimeout, 45, static_cast<unsigned int>(i));
-            ok = 0;
-            break;
+          if ((++spins & 0xffu) == 0u) {
+            if (status_failed(status)) {
+              ok = 0;
+              break;
+            }
+            if (global_timer_ns() - t0 > kPeerWaitBudgetNs) {
+              report_status(status, kStatusFlagTimeout, 45, static_cast<unsigned int>(i));
+              ok = 0;
+              break;
+            }
           }
         }
         ok_s = ok;

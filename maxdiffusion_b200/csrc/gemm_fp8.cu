@@ -36,6 +36,7 @@ struct Params {
   const float* scale_a;  // device scalars
   const float* scale_b;
   int a_e5m2, b_e5m2;
+  int int8;  // 1: operands are signed 8-bit integers (tcgen05 kind::i8, int32 accumulators)
   DeviceStatus* status;
 };
 
@@ -121,7 +122,7 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
     }
   } else if (warp == 1) {
     if (lane == 0) {
-      const uint32_t idesc = make_idesc_f8(BM, BN, p.a_e5m2, p.b_e5m2);
+      const uint32_t idesc = p.int8 ? make_idesc_i8(BM, BN) : make_idesc_f8(BM, BN, p.a_e5m2, p.b_e5m2);
       int stage = 0;
       uint32_t phase = 0;
       int it = 0;
@@ -139,8 +140,9 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
           const uint32_t sb = sa + A_BYTES;
 #pragma unroll
           for (int k = 0; k < BK / 32; ++k) {  // 32 bytes of K per instruction
-            umma_ss_f8(d_tmem, make_smem_desc(sa + k * 32, 16, 1024), make_smem_desc(sb + k * 32, 16, 1024), idesc,
-                       (kb > 0 || k > 0) ? 1u : 0u);
+            const uint64_t da = make_smem_desc(sa + k * 32, 16, 1024), db = make_smem_desc(sb + k * 32, 16, 1024);
+            if (p.int8) umma_ss_i8(d_tmem, da, db, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+            else umma_ss_f8(d_tmem, da, db, idesc, (kb > 0 || k > 0) ? 1u : 0u);
           }
           umma_commit(&empty_bar[stage]);
           if (++stage == STAGES) { stage = 0; phase ^= 1u; }
@@ -178,7 +180,8 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
             if (col >= p.N) break;
             float x[8];
 #pragma unroll
-            for (int j = 0; j < 8; ++j) x[j] = __uint_as_float(r[v * 8 + j]) * alpha;
+            for (int j = 0; j < 8; ++j)
+              x[j] = (p.int8 ? static_cast<float>(static_cast<int>(r[v * 8 + j])) : __uint_as_float(r[v * 8 + j])) * alpha;
             if (p.bias) {
               const uint4 bv = *reinterpret_cast<const uint4*>(p.bias + col);
               const uint32_t bw[4] = {bv.x, bv.y, bv.z, bv.w};
@@ -236,14 +239,57 @@ quantize_fp8_kernel(const __nv_bfloat16* __restrict__ x, uint8_t* __restrict__ q
   }
 }
 
+// q = round(x * 127 / absmax) in [-127, 127]; scale_out = absmax / 127 (symmetric per-tensor int8).
+__global__ void __launch_bounds__(256)
+quantize_int8_kernel(const __nv_bfloat16* __restrict__ x, int8_t* __restrict__ q, long long nvec,
+                     const float* __restrict__ stats, float* __restrict__ scale_out) {
+  const float amax = fmaxf(stats[1], 1e-12f);
+  const float mul = 127.0f / amax;
+  if (blockIdx.x == 0 && threadIdx.x == 0) *scale_out = amax / 127.0f;
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < nvec;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const uint4 u = reinterpret_cast<const uint4*>(x)[i];
+    const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+    uint32_t out[2] = {0u, 0u};
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float2 f = unpack_bf16x2(w[j]);
+      const int a = max(-127, min(127, __float2int_rn(f.x * mul)));
+      const int b = max(-127, min(127, __float2int_rn(f.y * mul)));
+      const uint32_t pair = (static_cast<uint32_t>(a) & 0xffu) | ((static_cast<uint32_t>(b) & 0xffu) << 8);
+      out[j >> 1] |= pair << (16 * (j & 1));
+    }
+    reinterpret_cast<uint2*>(q)[i] = make_uint2(out[0], out[1]);
+  }
+}
+
 }  // namespace gemm8
 }  // namespace mdb
 
 // Aq: [M, K] fp8 bytes (leading dimension lda, a multiple of 16); Bq: [N, K]; out: bf16 [M, N]; N % 8 == 0.
 // scale_a / scale_b: device floats. a_e5m2 / b_e5m2 select the 8-bit format of each operand.
+static int gemm8_impl(const void* Aq, const void* Bq, void* out, const void* bias, const float* scale_a,
+                      const float* scale_b, int M, int N, int K, long long lda, long long ldb, long long ldo, int a_e5m2,
+                      int b_e5m2, int int8, void* stream_ptr);
+
 extern "C" int mdb_gemm_fp8(const void* Aq, const void* Bq, void* out, const void* bias, const float* scale_a,
                             const float* scale_b, int M, int N, int K, long long lda, long long ldb, long long ldo,
                             int a_e5m2, int b_e5m2, void* stream_ptr) {
+  return gemm8_impl(Aq, Bq, out, bias, scale_a, scale_b, M, N, K, lda, ldb, ldo, a_e5m2, b_e5m2, 0, stream_ptr);
+}
+
+// The same kernel on signed 8-bit integers (tcgen05 kind::i8, exact int32 accumulation): Aq [M, K], Bq [N, K] int8,
+// out = scale_a * scale_b * (Aq Bq^T) + bias in bf16. The reference's int8 quantisation modes
+// (src/maxdiffusion/pyconfig.py `quantization: int8`, models/quantizations.py:88-131) run on it.
+extern "C" int mdb_gemm_int8(const void* Aq, const void* Bq, void* out, const void* bias, const float* scale_a,
+                             const float* scale_b, int M, int N, int K, long long lda, long long ldb, long long ldo,
+                             void* stream_ptr) {
+  return gemm8_impl(Aq, Bq, out, bias, scale_a, scale_b, M, N, K, lda, ldb, ldo, 0, 0, 1, stream_ptr);
+}
+
+static int gemm8_impl(const void* Aq, const void* Bq, void* out, const void* bias, const float* scale_a,
+                      const float* scale_b, int M, int N, int K, long long lda, long long ldb, long long ldo, int a_e5m2,
+                      int b_e5m2, int int8, void* stream_ptr) {
   using namespace mdb;
   using namespace mdb::gemm8;
   if (M <= 0 || N <= 0 || K <= 0) return 0;
@@ -268,6 +314,7 @@ extern "C" int mdb_gemm_fp8(const void* Aq, const void* Bq, void* out, const voi
   p.scale_b = scale_b;
   p.a_e5m2 = a_e5m2;
   p.b_e5m2 = b_e5m2;
+  p.int8 = int8;
   p.status = status_buffer();
   static bool configured = false;
   if (!configured) {
@@ -291,5 +338,18 @@ extern "C" int mdb_quantize_fp8(const void* x, void* q, long long n, const float
   const int grid = static_cast<int>(blocks < 1 ? 1 : (blocks > sm_count() * 8 ? sm_count() * 8 : blocks));
   gemm8::quantize_fp8_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream_ptr)>>>(
       static_cast<const __nv_bfloat16*>(x), static_cast<uint8_t*>(q), nvec, stats, scale_out, e5m2);
+  return static_cast<int>(cudaGetLastError());
+}
+
+extern "C" int mdb_quantize_int8(const void* x, void* q, long long n, const float* stats, float* scale_out,
+                                 void* stream_ptr) {
+  using namespace mdb;
+  if (n <= 0) return 0;
+  if (n & 7) return 3102;
+  const long long nvec = n >> 3;
+  long long blocks = (nvec + 1023) / 1024;
+  const int grid = static_cast<int>(blocks < 1 ? 1 : (blocks > sm_count() * 8 ? sm_count() * 8 : blocks));
+  gemm8::quantize_int8_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream_ptr)>>>(
+      static_cast<const __nv_bfloat16*>(x), static_cast<int8_t*>(q), nvec, stats, scale_out);
   return static_cast<int>(cudaGetLastError());
 }

@@ -28,7 +28,13 @@ constexpr int GROUP_M = 8;
 // against 0.173 ms), so the launcher never picks it by itself: operand traffic, not wave fill, is the limit.
 __host__ __device__ constexpr int stages_for(int bn) { return bn == 256 ? 4 : 6; }                    // 4 x 48 KiB or 6 x 32 KiB
 __host__ __device__ constexpr int stage_bytes(int bn) { return A_BYTES + bn * BK * 2; }
-__host__ __device__ constexpr int smem_bytes(int bn) { return stages_for(bn) * stage_bytes(bn) + 1024 /*align slack*/ + 256 /*barriers*/; }
+// Output staging of the epilogue: two 128-row x 128-byte slabs (64 bf16 or 32 fp32 columns each) in the 128-byte
+// swizzle, written by the epilogue warps and drained by TMA stores.
+constexpr int SLAB_BYTES = BM * 128;
+constexpr int STAGING_BYTES = 2 * SLAB_BYTES;
+__host__ __device__ constexpr int smem_bytes(int bn) {
+  return stages_for(bn) * stage_bytes(bn) + STAGING_BYTES + 1024 /*align slack*/ + 256 /*barriers*/;
+}
 
 enum Epilogue : int {
   kEpiNone = 0,       // out = acc*alpha + bias
@@ -58,6 +64,10 @@ struct Params {
   int splits;
   int kb_per_split;
   float* partial;
+  int partial_rows;  // rows per split in `partial` (M rounded up to the tile height when TMA stores write it)
+  // 1: the epilogue stages 128-byte-wide slabs in shared memory and writes them with TMA stores (full lines, clipped
+  // at the edges of the tensor) instead of 16-byte stores from one thread per row
+  int tma_store;
 };
 
 __device__ __forceinline__ void tile_coords(int tile, int num_m, int num_n, int& m_idx, int& n_idx) {
@@ -74,13 +84,15 @@ __device__ __forceinline__ void tile_coords(int tile, int num_m, int num_n, int&
 
 template <bool A_MN, bool B_MN, int BN>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
-gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b, const Params p) {
+gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+            const __grid_constant__ CUtensorMap tmap_c, const Params p) {
   constexpr int STAGES = stages_for(BN);
   constexpr int STAGE_BYTES = stage_bytes(BN);
   constexpr int TMEM_COLS = 2 * BN;  // two accumulators
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES * STAGE_BYTES);
+  uint8_t* staging = smem + STAGES * STAGE_BYTES;  // 1024-byte aligned: every stage is a multiple of 1024 bytes
+  uint64_t* bars = reinterpret_cast<uint64_t*>(staging + STAGING_BYTES);
   uint64_t* full_bar = bars;                    // [STAGES]
   uint64_t* empty_bar = bars + STAGES;          // [STAGES]
   uint64_t* tmem_full = bars + 2 * STAGES;      // [2]
@@ -109,6 +121,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
     fence_mbar_init();
     prefetch_tensormap(&tmap_a);
     prefetch_tensormap(&tmap_b);
+    if (p.tma_store) prefetch_tensormap(&tmap_c);
   }
   if (warp == 1) {
     tmem_alloc(tmem_ptr_smem, TMEM_COLS);
@@ -203,6 +216,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
     const int quarter = warp & 3;  // TMEM lanes 32*quarter .. +31 are reachable from this warp
     const int row_in_tile = quarter * 32 + lane;
     int it = 0;
+    int slab_count = 0;
     bool ok = true;
     for (int work = blockIdx.x; work < num_work && ok; work += gridDim.x, ++it) {
       int m_idx, n_idx;
@@ -216,6 +230,99 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
       const bool row_ok = row < p.M;
       const int batch = (p.rows_per_batch > 0) ? static_cast<int>(row / p.rows_per_batch) : 0;
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc * BN;
+      if (p.tma_store) {
+        // ---- staged epilogue: 128 bytes of every row per slab, swizzled, one TMA store per slab ----
+        const bool f32 = p.out_f32 || p.splits > 1;
+        const int slab_cols = f32 ? 32 : 64;
+        const bool leader = threadIdx.x == 64;  // first epilogue thread issues and tracks the stores
+        const long long out_row0 = (p.splits > 1 ? static_cast<long long>(split) * p.partial_rows : 0) +
+                                   static_cast<long long>(m_idx) * BM;
+        const int sw = row_in_tile & 7;
+#pragma unroll 1
+        for (int c0 = 0; c0 < BN; c0 += slab_cols) {
+          const int col0 = n_idx * BN + c0;
+          if (col0 >= p.N) break;  // uniform across the CTA
+          uint8_t* slab = staging + (slab_count & 1) * SLAB_BYTES;
+          if (leader) tma_store_wait_read<1>();  // the store that read this slab two slabs ago is done with it
+          named_bar_sync(1, 128);
+          uint8_t* my_row = slab + row_in_tile * 128;
+#pragma unroll
+          for (int h = 0; h < 2; ++h) {  // bf16: two 32-column loads per slab; fp32: one
+            if (f32 && h == 1) break;
+            uint32_t r[32];
+            tmem_ld_x32(taddr + c0 + h * 32, r);
+            tmem_wait_ld();
+#pragma unroll
+            for (int v = 0; v < 4; ++v) {
+              const int col = col0 + h * 32 + v * 8;
+              float x[8];
+#pragma unroll
+              for (int j = 0; j < 8; ++j) x[j] = __uint_as_float(r[v * 8 + j]) * p.alpha;
+              if (p.splits == 1 && col < p.N) {
+                if (p.bias) {
+                  const uint4 bv = *reinterpret_cast<const uint4*>(p.bias + col);
+                  const uint32_t bw[4] = {bv.x, bv.y, bv.z, bv.w};
+#pragma unroll
+                  for (int j = 0; j < 4; ++j) {
+                    float2 f = unpack_bf16x2(bw[j]);
+                    x[2 * j] += f.x;
+                    x[2 * j + 1] += f.y;
+                  }
+                }
+                if (p.epi == kEpiGeluTanh) {
+#pragma unroll
+                  for (int j = 0; j < 8; ++j) x[j] = gelu_tanh(x[j]);
+                } else if (p.epi == kEpiSilu) {
+#pragma unroll
+                  for (int j = 0; j < 8; ++j) x[j] = x[j] / (1.0f + __expf(-x[j]));
+                } else if ((p.epi == kEpiGatedRes || p.epi == kEpiAddRes) && row_ok) {
+                  const uint4 rv = *reinterpret_cast<const uint4*>(p.residual + row * p.ldr + col);
+                  const uint32_t rw[4] = {rv.x, rv.y, rv.z, rv.w};
+                  float g[8];
+                  if (p.epi == kEpiGatedRes) {
+                    const float4 g0 = *reinterpret_cast<const float4*>(p.gate + batch * p.gate_ld + col);
+                    const float4 g1 = *reinterpret_cast<const float4*>(p.gate + batch * p.gate_ld + col + 4);
+                    g[0] = g0.x; g[1] = g0.y; g[2] = g0.z; g[3] = g0.w;
+                    g[4] = g1.x; g[5] = g1.y; g[6] = g1.z; g[7] = g1.w;
+                  } else {
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) g[j] = 1.0f;
+                  }
+#pragma unroll
+                  for (int j = 0; j < 4; ++j) {
+                    float2 f = unpack_bf16x2(rw[j]);
+                    x[2 * j] = f.x + g[2 * j] * x[2 * j];
+                    x[2 * j + 1] = f.y + g[2 * j + 1] * x[2 * j + 1];
+                  }
+                }
+              }
+              if (f32) {  // 8 values = two 16-byte chunks of the row's 128 bytes
+                const int ch = v * 2;
+                *reinterpret_cast<float4*>(my_row + (((ch) ^ sw) << 4)) = make_float4(x[0], x[1], x[2], x[3]);
+                *reinterpret_cast<float4*>(my_row + (((ch + 1) ^ sw) << 4)) = make_float4(x[4], x[5], x[6], x[7]);
+              } else {
+                const int ch = h * 4 + v;
+                uint4 ov;
+                ov.x = pack_bf16x2(x[0], x[1]);
+                ov.y = pack_bf16x2(x[2], x[3]);
+                ov.z = pack_bf16x2(x[4], x[5]);
+                ov.w = pack_bf16x2(x[6], x[7]);
+                *reinterpret_cast<uint4*>(my_row + ((ch ^ sw) << 4)) = ov;
+              }
+            }
+          }
+          fence_proxy_async_smem();
+          named_bar_sync(1, 128);
+          if (leader) {
+            tma_store_2d(&tmap_c, slab, col0, static_cast<int>(out_row0));
+            tma_store_commit();
+          }
+          ++slab_count;
+        }
+        tc_fence_before_sync();
+        mbar_arrive(&tmem_empty[acc]);
+        continue;
+      }
 #pragma unroll 1
       for (int c = 0; c < BN / 32; ++c) {
         const int col0 = n_idx * BN + c * 32;
@@ -232,7 +339,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
 #pragma unroll
             for (int j = 0; j < 8; ++j) x[j] = __uint_as_float(r[v * 8 + j]) * p.alpha;
             if (p.splits > 1) {
-              float* o = p.partial + (static_cast<long long>(split) * p.M + row) * p.N + col;
+              float* o = p.partial + (static_cast<long long>(split) * p.partial_rows + row) * p.N + col;
               *reinterpret_cast<float4*>(o) = make_float4(x[0], x[1], x[2], x[3]);
               *reinterpret_cast<float4*>(o + 4) = make_float4(x[4], x[5], x[6], x[7]);
               continue;
@@ -292,6 +399,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
       tc_fence_before_sync();
       mbar_arrive(&tmem_empty[acc]);
     }
+    if (p.tma_store && threadIdx.x == 64) tma_store_wait_read<0>();  // shared memory stays valid until the stores have read it
   }
 
   tc_fence_before_sync();
@@ -304,14 +412,15 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
 
 // out[i] = sum over splits of partial[s][i], in split order; n8 = M * N / 8 vectors of 8 values.
 __global__ void splitk_fold_kernel(const float* __restrict__ partial, void* __restrict__ out, long long ldo, int M, int N,
-                                   int splits, int out_f32) {
+                                   int splits, int out_f32, int partial_rows) {
   const long long n8 = static_cast<long long>(M) * N / 8;
+  const long long split_stride = static_cast<long long>(partial_rows) * N;
   const int n_vec = N / 8;
   for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < n8;
        i += static_cast<long long>(gridDim.x) * blockDim.x) {
     float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
     for (int s = 0; s < splits; ++s) {
-      const float4* src = reinterpret_cast<const float4*>(partial + (static_cast<long long>(s) * n8 + i) * 8);
+      const float4* src = reinterpret_cast<const float4*>(partial + s * split_stride + i * 8);
       const float4 a = src[0], b = src[1];
       acc[0] += a.x; acc[1] += a.y; acc[2] += a.z; acc[3] += a.w;
       acc[4] += b.x; acc[5] += b.y; acc[6] += b.z; acc[7] += b.w;
@@ -334,7 +443,7 @@ __global__ void splitk_fold_kernel(const float* __restrict__ partial, void* __re
 }
 
 template <bool A_MN, bool B_MN, int BN>
-int launch(const CUtensorMap& ta, const CUtensorMap& tb, const Params& p, cudaStream_t stream) {
+int launch(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc, const Params& p, cudaStream_t stream) {
   auto kern = gemm_kernel<A_MN, B_MN, BN>;
   static bool configured = false;
   if (!configured) {
@@ -343,11 +452,11 @@ int launch(const CUtensorMap& ta, const CUtensorMap& tb, const Params& p, cudaSt
   }
   const int num_work = ((p.M + BM - 1) / BM) * ((p.N + BN - 1) / BN) * p.splits;
   const int grid = num_work < sm_count() ? num_work : sm_count();
-  kern<<<grid, NUM_THREADS, smem_bytes(BN), stream>>>(ta, tb, p);
+  kern<<<grid, NUM_THREADS, smem_bytes(BN), stream>>>(ta, tb, tc, p);
   if (p.splits > 1) {
     const long long n8 = static_cast<long long>(p.M) * p.N / 8;
     const int blocks = static_cast<int>(n8 / 256 + 1 < sm_count() * 4 ? n8 / 256 + 1 : sm_count() * 4);
-    splitk_fold_kernel<<<blocks, 256, 0, stream>>>(p.partial, p.out, p.ldo, p.M, p.N, p.splits, p.out_f32);
+    splitk_fold_kernel<<<blocks, 256, 0, stream>>>(p.partial, p.out, p.ldo, p.M, p.N, p.splits, p.out_f32, p.partial_rows);
   }
   return static_cast<int>(cudaGetLastError());
 }
@@ -356,6 +465,14 @@ int launch(const CUtensorMap& ta, const CUtensorMap& tb, const Params& p, cudaSt
 }  // namespace mdb
 
 static int g_force_tile_n = 0;
+static int g_epilogue_mode = 0;  // 0: TMA-store epilogue where the output allows it; 1: always direct stores
+
+// Tile search / benchmarks: 1 pins the direct-store epilogue (one thread per row, 16-byte stores), 0 restores the default.
+extern "C" int mdb_gemm_epilogue_mode(int mode) {
+  if (mode != 0 && mode != 1) return 3006;
+  g_epilogue_mode = mode;
+  return 0;
+}
 
 // C entry point. A is [M,K] with leading dimension lda (a_mn_major = 0) or [K,M] (a_mn_major = 1);
 // B is [N,K] (b_mn_major = 0) or [K,N] (b_mn_major = 1). All leading dimensions are in elements and
@@ -444,17 +561,40 @@ static int gemm_impl(const void* A, const void* B, void* out, const void* bias, 
     p.partial = partial;
     if (p.splits <= 1) { p.splits = 1; p.kb_per_split = num_kb; }
   }
+  // Output map for the TMA-store epilogue: [N (inner), rows], 128-byte-wide boxes of 128 rows. With split-K it
+  // covers the fp32 partials, whose splits are `partial_rows` = M rounded up to the tile height apart, so that a
+  // tile's rows beyond M fall into padding instead of the next split.
+  CUtensorMap tc;
+  p.partial_rows = (M + BM - 1) / BM * BM;
+  {
+    const bool f32 = out_f32 || p.splits > 1;
+    const void* base = p.splits > 1 ? static_cast<const void*>(partial) : out;
+    const long long ld = p.splits > 1 ? N : ldo;
+    const uint64_t rows = p.splits > 1 ? static_cast<uint64_t>(p.splits) * p.partial_rows : static_cast<uint64_t>(M);
+    const int esz = f32 ? 4 : 2;
+    p.tma_store = g_epilogue_mode == 0 && (reinterpret_cast<uintptr_t>(base) & 15) == 0 && ((ld * esz) & 15) == 0;
+    if (p.tma_store) {
+      uint64_t dims[2] = {static_cast<uint64_t>(N), rows};
+      uint64_t str[1] = {static_cast<uint64_t>(ld) * esz};
+      uint32_t box[2] = {static_cast<uint32_t>(128 / esz), BM};
+      rc = f32 ? encode_tmap_f32(&tc, base, 2, dims, str, box, 1) : encode_tmap_bf16(&tc, base, 2, dims, str, box);
+      if (rc) return rc;
+    } else {
+      tc = ta;  // unused by the kernel; any valid map
+      if (p.splits > 1) p.partial_rows = M;
+    }
+  }
   cudaStream_t stream = static_cast<cudaStream_t>(stream_ptr);
   if (BN == 256) {
     if (a_mn_major) {
-      return b_mn_major ? launch<true, true, 256>(ta, tb, p, stream) : launch<true, false, 256>(ta, tb, p, stream);
+      return b_mn_major ? launch<true, true, 256>(ta, tb, tc, p, stream) : launch<true, false, 256>(ta, tb, tc, p, stream);
     }
-    return b_mn_major ? launch<false, true, 256>(ta, tb, p, stream) : launch<false, false, 256>(ta, tb, p, stream);
+    return b_mn_major ? launch<false, true, 256>(ta, tb, tc, p, stream) : launch<false, false, 256>(ta, tb, tc, p, stream);
   }
   if (a_mn_major) {
-    return b_mn_major ? launch<true, true, 128>(ta, tb, p, stream) : launch<true, false, 128>(ta, tb, p, stream);
+    return b_mn_major ? launch<true, true, 128>(ta, tb, tc, p, stream) : launch<true, false, 128>(ta, tb, tc, p, stream);
   }
-  return b_mn_major ? launch<false, true, 128>(ta, tb, p, stream) : launch<false, false, 128>(ta, tb, p, stream);
+  return b_mn_major ? launch<false, true, 128>(ta, tb, tc, p, stream) : launch<false, false, 128>(ta, tb, tc, p, stream);
 }
 
 // 0: the default width (256); 128 or 256: use that tile width (tile search, benchmarks, tests).

@@ -40,6 +40,13 @@ __device__ __forceinline__ void report_status(DeviceStatus* st, unsigned int cod
   }
 }
 
+// True once any kernel on this device has recorded a failure that the host has not read yet. Every bounded wait
+// polls it beside its clock: after the first wait that ran out, the waits queued behind it (same kernel or later
+// launches) give up at once instead of spending their own budgets, so a failure costs one budget in total.
+__device__ __forceinline__ bool status_failed(const DeviceStatus* st) {
+  return st != nullptr && *reinterpret_cast<const volatile unsigned int*>(&st->code) != 0u;
+}
+
 __device__ __forceinline__ uint64_t global_timer_ns() {
   uint64_t t;
   asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
@@ -111,6 +118,10 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
     if (mbar_try_wait(bar, parity)) return true;
     if ((++spins & 0x3ffu) == 0u) {
       if (*abort_flag) return false;
+      if (status_failed(st)) {
+        *abort_flag = 1;
+        return false;
+      }
       if (global_timer_ns() - t0 > kWaitBudgetNs) {
         *abort_flag = 1;
         report_status(st, kStatusMbarTimeout, where, smem_u32(bar));
@@ -140,6 +151,22 @@ __device__ __forceinline__ void tma_load_2d(void* smem_dst, const void* desc, ui
       ::"r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(desc)), "r"(smem_u32(bar)), "r"(c0), "r"(c1)
       : "memory");
 }
+// TMA store of a shared-memory box into a tiled tensor (rows / columns beyond the tensor are clipped); completion is
+// tracked per thread by bulk groups: commit after the store, `wait_read<N>` until at most N groups still read smem.
+__device__ __forceinline__ void tma_store_2d(const void* desc, const void* smem_src, int c0, int c1) {
+  asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];"
+               ::"l"(reinterpret_cast<uint64_t>(desc)), "r"(smem_u32(smem_src)), "r"(c0), "r"(c1)
+               : "memory");
+}
+__device__ __forceinline__ void tma_store_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void tma_store_wait_read() {
+  asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory");
+}
+__device__ __forceinline__ void named_bar_sync(int id, int threads) {
+  asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
+}
+
 __device__ __forceinline__ void tma_load_3d(void* smem_dst, const void* desc, uint64_t* bar, int c0, int c1,
                                             int c2) {
   asm volatile(
@@ -208,6 +235,18 @@ __device__ __forceinline__ void umma_ss_f8(uint32_t d_tmem, uint64_t a_desc, uin
       ".reg .pred p;\n\t"
       "setp.ne.b32 p, %4, 0;\n\t"
       "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], %1, %2, %3, p;\n\t"
+      "}\n" ::"r"(d_tmem),
+      "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// Same for signed 8-bit integer operands with int32 accumulators: K = 32 elements per instruction.
+__device__ __forceinline__ void umma_ss_i8(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                           uint32_t accumulate) {
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, p;\n\t"
       "}\n" ::"r"(d_tmem),
       "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
       : "memory");
@@ -313,6 +352,12 @@ __host__ __device__ constexpr uint32_t make_idesc_bf16(int m, int n, bool a_mn_m
 __host__ __device__ constexpr uint32_t make_idesc_f8(int m, int n, int a_e5m2, int b_e5m2) {
   return (1u << 4) | (static_cast<uint32_t>(a_e5m2) << 7) | (static_cast<uint32_t>(b_e5m2) << 10) |
          (static_cast<uint32_t>(n >> 3) << 17) | (static_cast<uint32_t>(m >> 4) << 24);
+}
+
+// Instruction descriptor for kind::i8 with K-major signed 8-bit operands and int32 accumulation:
+// D format 2 = s32, A / B format 1 = signed.
+__host__ __device__ constexpr uint32_t make_idesc_i8(int m, int n) {
+  return (2u << 4) | (1u << 7) | (1u << 10) | (static_cast<uint32_t>(n >> 3) << 17) | (static_cast<uint32_t>(m >> 4) << 24);
 }
 
 // ----------------------------------------------------------------------------------------

@@ -9,7 +9,8 @@ The reference quantises through libraries around XLA dot_general: AQT int8 for t
   fp8       weights are quantised once (static absmax), activations at every call (dynamic absmax, on the device,
             no host synchronisation); forward product in fp8; the backward pass (if any) runs in bf16
   fp8_full  as fp8, and the two backward products run in fp8 as well with e5m2 gradients
-  int8      served by the fp8 path (same 8-bit storage and 2x tensor-core rate; e4m3 has the wider dynamic range)
+  int8      symmetric per-tensor int8 weights (static) and activations (dynamic) on the integer tensor-core path
+            (tcgen05 kind::i8, exact int32 accumulation); the backward pass (if any) runs in bf16
 
 `quantize_model(model, mode)` swaps the `Linear` layers of the transformer blocks in place and
 `get_quantization_mode(config)` reads the reference's config keys.
@@ -64,9 +65,37 @@ class _Fp8LinearFn(torch.autograd.Function):
     return dx, dw, None, None, db, None
 
 
+def fake_quantize_int8(x: torch.Tensor) -> torch.Tensor:
+  """Plain-PyTorch reference of the int8 quantiser."""
+  amax = x.detach().abs().max().float().clamp_min(1e-12)
+  scale = amax / 127.0
+  return ((x.float() / scale).round().clamp(-127, 127) * scale).to(x.dtype)
+
+
+class _Int8LinearFn(torch.autograd.Function):
+
+  @staticmethod
+  def forward(ctx, x2, w, wq, w_scale, bias):
+    xq, x_scale = K.quantize_int8(x2)
+    ctx.save_for_backward(x2, w)
+    ctx.has_bias = bias is not None
+    return K.gemm_int8(xq, x_scale, wq, w_scale, bias)
+
+  @staticmethod
+  def backward(ctx, dy):
+    x2, w = ctx.saved_tensors
+    dy = dy.contiguous()
+    dx = K.gemm(dy, w, b_mn=True)
+    dw = K.gemm(dy, x2, a_mn=True, b_mn=True)
+    db = K.colsum(dy).to(torch.bfloat16) if ctx.has_bias else None
+    return dx, dw, None, None, db
+
+
 class Fp8Linear(nn.Module):
   """Drop-in for `layers.Linear` with the product in fp8. The bf16 master weight is kept (training, export); its
   quantised copy is refreshed by `requantize()` (after an optimizer step) or lazily when the weight changes."""
+
+  int8 = False
 
   def __init__(self, base: Linear, full: bool = False):
     super().__init__()
@@ -78,14 +107,15 @@ class Fp8Linear(nn.Module):
   def requantize(self) -> None:
     w = self.weight.detach()
     w = w if w.dtype == torch.bfloat16 else w.to(torch.bfloat16)
-    self._wq, self._w_scale = K.quantize_fp8(w.contiguous())
+    self._wq, self._w_scale = (K.quantize_int8 if self.int8 else K.quantize_fp8)(w.contiguous())
     self._version = self.weight._version
 
   def forward(self, x, activation: Optional[str] = None):
     ok = (x.is_cuda and x.dtype == torch.bfloat16 and self.in_features % 16 == 0 and self.out_features % 8 == 0
           and (x.numel() // self.in_features) % 8 == 0)
     if not ok:
-      y = F.linear(x, fake_quantize(self.weight.to(x.dtype)), None if self.bias is None else self.bias.to(x.dtype)) \
+      fq = fake_quantize_int8 if self.int8 else fake_quantize
+      y = F.linear(x, fq(self.weight.to(x.dtype)), None if self.bias is None else self.bias.to(x.dtype)) \
           if not x.is_cuda else F.linear(x, self.weight.to(x.dtype), None if self.bias is None else self.bias.to(x.dtype))
     else:
       if self._wq is None or self._version != self.weight._version:
@@ -93,12 +123,21 @@ class Fp8Linear(nn.Module):
       bias = None if self.bias is None else self.bias.to(torch.bfloat16)
       x2 = x.reshape(-1, self.in_features)
       x2 = x2 if x2.is_contiguous() else x2.contiguous()
-      y = _Fp8LinearFn.apply(x2, self.weight, self._wq, self._w_scale, bias, self.full).view(*x.shape[:-1], self.out_features)
+      if self.int8:
+        y = _Int8LinearFn.apply(x2, self.weight, self._wq, self._w_scale, bias)
+      else:
+        y = _Fp8LinearFn.apply(x2, self.weight, self._wq, self._w_scale, bias, self.full)
+      y = y.view(*x.shape[:-1], self.out_features)
     if activation == "gelu_tanh":
       y = F.gelu(y, approximate="tanh")
     elif activation == "silu":
       y = F.silu(y)
     return y
+
+
+class Int8Linear(Fp8Linear):
+  """Drop-in for `layers.Linear` with the product on the int8 tensor-core path (per-tensor symmetric scales)."""
+  int8 = True
 
 
 def get_quantization_mode(config) -> Optional[str]:
@@ -112,7 +151,7 @@ def get_quantization_mode(config) -> Optional[str]:
 
 
 def quantize_model(model: nn.Module, mode: str = "fp8", predicate: Optional[Callable[[str, nn.Module], bool]] = None) -> int:
-  """Replaces `Linear` layers by `Fp8Linear` in place; returns how many were replaced. By default the layers inside
+  """Replaces `Linear` layers by `Fp8Linear` (`Int8Linear` for mode "int8") in place; returns how many were replaced. By default the layers inside
   transformer blocks are quantised and embedders / output heads keep bf16 (the reference's rules exclude the same
   small layers, wan_pipeline.py:600-640)."""
   if predicate is None:
@@ -123,6 +162,6 @@ def quantize_model(model: nn.Module, mode: str = "fp8", predicate: Optional[Call
     for child_name, child in list(module.named_children()):
       full_name = f"{name}.{child_name}" if name else child_name
       if type(child) is Linear and predicate(full_name, child):
-        setattr(module, child_name, Fp8Linear(child, full))
+        setattr(module, child_name, Int8Linear(child) if mode == "int8" else Fp8Linear(child, full))
         count += 1
   return count

@@ -124,6 +124,8 @@ def _declare(L: ctypes.CDLL) -> None:
   L.mdb_gemm_bf16.restype = c_int
   L.mdb_gemm_bf16_splitk.argtypes = [c_void_p] * 3 + [c_int] * 3 + [c_ll] * 3 + [c_int] * 3 + [c_float, c_void_p, c_int, c_void_p]
   L.mdb_gemm_bf16_splitk.restype = c_int
+  L.mdb_gemm_epilogue_mode.argtypes = [c_int]
+  L.mdb_gemm_epilogue_mode.restype = c_int
   L.mdb_gemm_force_tile_n.argtypes = [c_int]
   L.mdb_gemm_force_tile_n.restype = c_int
   L.mdb_flash_fwd.argtypes = ([c_void_p, ctypes.POINTER(c_void_p), ctypes.POINTER(c_void_p), c_void_p, c_void_p]

@@ -74,7 +74,7 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = F
   plain = bias is None and epi == "none" and residual is None and gate is None
   splits = (split_k_for(M, N, K) if split_k == 0 else split_k) if plain else 1
   if splits > 1:
-    partial = torch.empty((splits, M, N), device=a.device, dtype=torch.float32)
+    partial = torch.empty((splits, -(-M // 128) * 128, N), device=a.device, dtype=torch.float32)  # splits a whole tile apart
     rc = _lib.lib().mdb_gemm_bf16_splitk(_lib.ptr(a), _lib.ptr(b), _lib.ptr(out), M, N, K, a.stride(0), b.stride(0),
                                          out.stride(0), int(a_mn), int(b_mn), int(out.dtype == torch.float32), float(alpha),
                                          _lib.ptr(partial), splits, _lib.stream())
@@ -87,6 +87,12 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = F
       int(out.dtype == torch.float32), float(alpha), _lib.stream())
   _lib.check(rc, "mdb_gemm_bf16")
   return out
+
+
+def gemm_epilogue_mode(direct: bool = False) -> None:
+  """True pins the direct-store epilogue (16-byte stores from one thread per row); False restores the default
+  (128-byte slabs staged in shared memory and written by TMA stores). For benchmarks and tests."""
+  _lib.check(_lib.lib().mdb_gemm_epilogue_mode(int(direct)), "mdb_gemm_epilogue_mode")
 
 
 def gemm_force_tile_n(bn: int = 0) -> None:
@@ -678,6 +684,10 @@ def _declare_fp8(L):
   L.mdb_gemm_fp8.restype = c_int
   L.mdb_quantize_fp8.argtypes = [c_void_p, c_void_p, c_ll, c_void_p, c_void_p, c_int, c_void_p]
   L.mdb_quantize_fp8.restype = c_int
+  L.mdb_gemm_int8.argtypes = [c_void_p] * 6 + [c_int] * 3 + [c_ll] * 3 + [c_void_p]
+  L.mdb_gemm_int8.restype = c_int
+  L.mdb_quantize_int8.argtypes = [c_void_p, c_void_p, c_ll, c_void_p, c_void_p, c_void_p]
+  L.mdb_quantize_int8.restype = c_int
 
 
 _lib.register(_declare_fp8)
@@ -707,6 +717,32 @@ def gemm_fp8(aq, a_scale, bq, b_scale, bias=None, a_e5m2: bool = False, b_e5m2: 
                                _lib.ptr(b_scale), M, N, K, aq.stride(0), bq.stride(0), out.stride(0), int(a_e5m2),
                                int(b_e5m2), _lib.stream())
   _lib.check(rc, "mdb_gemm_fp8")
+  return out
+
+
+def quantize_int8(x: torch.Tensor):
+  """Symmetric per-tensor int8 quantisation of a bf16 tensor: (q int8 same shape, scale fp32 [1] on device) with
+  x ~= q * scale and q in [-127, 127]; no host synchronisation."""
+  assert x.dtype == torch.bfloat16 and x.is_contiguous() and x.numel() % 8 == 0
+  stats = sumsq_maxabs(x)
+  q = torch.empty(x.shape, device=x.device, dtype=torch.int8)
+  scale = torch.empty((1,), device=x.device, dtype=torch.float32)
+  rc = _lib.lib().mdb_quantize_int8(_lib.ptr(x), _lib.ptr(q), x.numel(), _lib.ptr(stats), _lib.ptr(scale), _lib.stream())
+  _lib.check(rc, "mdb_quantize_int8")
+  return q, scale
+
+
+def gemm_int8(aq, a_scale, bq, b_scale, bias=None):
+  """bf16 D[M,N] = (a_scale * b_scale) * Aq[M,K] · Bq[N,K]ᵀ + bias with int8 operands and exact int32 accumulation
+  (tcgen05 kind::i8; K % 16 == 0)."""
+  assert aq.dtype == torch.int8 and bq.dtype == torch.int8 and aq.dim() == 2 and bq.dim() == 2
+  assert aq.stride(-1) == 1 and bq.stride(-1) == 1 and aq.shape[1] == bq.shape[1]
+  M, K = aq.shape
+  N = bq.shape[0]
+  out = torch.empty((M, N), device=aq.device, dtype=torch.bfloat16)
+  rc = _lib.lib().mdb_gemm_int8(_lib.ptr(aq), _lib.ptr(bq), _lib.ptr(out), _lib.ptr(bias), _lib.ptr(a_scale),
+                                _lib.ptr(b_scale), M, N, K, aq.stride(0), bq.stride(0), out.stride(0), _lib.stream())
+  _lib.check(rc, "mdb_gemm_int8")
   return out
 
 

@@ -504,3 +504,73 @@ def test_gemm_split_k_matches_fp32(a_mn, b_mn, M, N, Kd, splits):
   assert (got32 - want).abs().max().item() <= 2e-3 * scale
   assert (got32 - one).abs().max().item() <= 1e-3 * scale
   assert torch.equal(got, K.gemm(a, b, a_mn=a_mn, b_mn=b_mn, split_k=splits))
+
+
+@pytest.mark.parametrize("M,N,Kd", [(300, 328, 192), (4095, 1280, 640), (129, 8, 64), (1024, 2560, 320)])
+@pytest.mark.parametrize("epi", ["none", "gelu_tanh", "add_res", "gated_res"])
+@pytest.mark.parametrize("f32", [False, True])
+def test_gemm_tma_store_epilogue_equals_direct_stores(M, N, Kd, epi, f32):
+  """The epilogue that stages 128-byte slabs in shared memory and writes them with TMA stores against the one that
+  stores from one thread per row: same values bit for bit, ragged edges in M and N, every epilogue, both output types."""
+  g = torch.Generator(device="cuda").manual_seed(0)
+  a = torch.randn((M, Kd), device="cuda", generator=g).to(torch.bfloat16)
+  b = (torch.randn((N, Kd), device="cuda", generator=g) * 0.1).to(torch.bfloat16)
+  bias = torch.randn((N,), device="cuda", generator=g).to(torch.bfloat16)
+  kw = dict(bias=bias, epi=epi, out_dtype=torch.float32 if f32 else torch.bfloat16)
+  if epi in ("add_res", "gated_res"):
+    kw["residual"] = torch.randn((M, N), device="cuda", generator=g).to(torch.bfloat16)
+  if epi == "gated_res":
+    rows = 100 if M % 100 == 0 else M
+    kw["gate"] = torch.randn((M // rows, N), device="cuda", generator=g)
+    kw["rows_per_batch"] = rows
+  try:
+    K.gemm_epilogue_mode(direct=True)
+    want = K.gemm(a, b, **kw)
+  finally:
+    K.gemm_epilogue_mode(direct=False)
+  guard = torch.full((M + 2, N), 7.0, device="cuda", dtype=kw["out_dtype"])  # rows around the output stay untouched
+  got = K.gemm(a, b, out=guard[1:-1], **{k: v for k, v in kw.items() if k != "out_dtype"})
+  assert torch.equal(got, want)
+  assert bool((guard[0] == 7).all()) and bool((guard[-1] == 7).all())
+  ref32 = a.float() @ b.float().t() + bias.float()
+  if epi == "none":
+    assert (got.float() - ref32).abs().max() <= 2e-2 * ref32.abs().max()
+
+
+@pytest.mark.parametrize("M,N,Kd", [(128, 256, 128), (520, 264, 400), (1024, 1536, 2048)])
+def test_gemm_int8_is_exact_on_the_quantised_operands(M, N, Kd):
+  """Integer tensor-core path: the quantiser rounds to nearest in [-127, 127]; the product of the int8 operands is
+  accumulated exactly in int32, so against an int64 reference only the bf16 rounding of the output remains."""
+  torch.manual_seed(0)
+  a = torch.randn((M, Kd), device=DEV, dtype=torch.bfloat16)
+  b = torch.randn((N, Kd), device=DEV, dtype=torch.bfloat16) * 0.05
+  bias = torch.randn((N,), device=DEV, dtype=torch.bfloat16)
+  aq, sa = K.quantize_int8(a)
+  bq, sb = K.quantize_int8(b)
+  assert aq.dtype == torch.int8 and abs(sa.item() - a.abs().max().item() / 127.0) < 1e-6
+  assert torch.equal(aq, (a.float() / sa).round().clamp(-127, 127).to(torch.int8))
+  out = K.gemm_int8(aq, sa, bq, sb, bias)
+  exact = (aq.long() @ bq.long().t()).double() * (sa.double() * sb.double()) + bias.double()
+  assert (out.double() - exact).abs().max() <= 1e-2 * exact.abs().max()
+  assert _rel(out, exact.float()) < 4e-3  # bf16 output rounding only
+  assert _rel(out, a.float() @ b.float().t() + bias.float()) < 5e-2  # int8 rounding of the operands
+  _lib.raise_on_device_status()
+
+
+def test_int8_linear_module_forward_and_bf16_backward():
+  from maxdiffusion_b200.models.layers import Linear
+  from maxdiffusion_b200.models.quantizations import Int8Linear, quantize_model
+
+  torch.manual_seed(0)
+  base = Linear(256, 512).to(DEV, torch.bfloat16)
+  x = torch.randn((4, 64, 256), device=DEV, dtype=torch.bfloat16, requires_grad=True)
+  dy = torch.randn((4, 64, 512), device=DEV, dtype=torch.bfloat16)
+  want = torch.nn.functional.linear(x.float(), base.weight.float(), base.bias.float())
+  gx_want, gw_want = torch.autograd.grad(want, [x, base.weight], dy.float())
+  q = Int8Linear(base)
+  y = q(x)
+  gx, gw = torch.autograd.grad(y, [x, base.weight], dy)
+  assert _rel(y, want) < 4e-2 and _rel(gx, gx_want) < 2e-2 and _rel(gw, gw_want) < 2e-2
+  holder = torch.nn.ModuleDict({"blocks": torch.nn.ModuleList([torch.nn.ModuleDict({"proj": Linear(64, 64)})])})
+  assert quantize_model(holder, "int8") == 1 and isinstance(holder["blocks"][0]["proj"], Int8Linear)
+  _lib.raise_on_device_status()

@@ -33,3 +33,20 @@ def test_mode_from_config():
   assert get_quantization_mode(c) == "fp8_full"
   with pytest.raises(ValueError):
     get_quantization_mode(pyconfig.initialize(base + ["use_qwix_quantization=True", "quantization=int4"], unittest=True))
+
+
+def test_int8_mode_uses_the_integer_layer_and_its_reference_quantiser_rounds_to_127_levels():
+  import torch
+
+  from maxdiffusion_b200.models.layers import Linear
+  from maxdiffusion_b200.models.quantizations import Int8Linear, fake_quantize_int8, quantize_model
+
+  x = torch.linspace(-2.0, 2.0, 1001)
+  q = fake_quantize_int8(x)
+  assert (q - x).abs().max() <= 2.0 / 127 / 2 + 1e-6 and len(torch.unique(q)) <= 255
+  m = torch.nn.ModuleDict({"blocks": torch.nn.ModuleList([torch.nn.ModuleDict({"a": Linear(32, 32)})]), "head": Linear(32, 32)})
+  assert quantize_model(m, "int8") == 1
+  layer = m["blocks"][0]["a"]
+  assert isinstance(layer, Int8Linear) and type(m["head"]) is Linear
+  y = layer(torch.randn(3, 32))  # CPU: the reference quantiser on the weights
+  assert y.shape == (3, 32)
