@@ -356,6 +356,138 @@ extern "C" int mdb_gn_cl_apply(const void* x, const void* dy, void* out, const f
   return static_cast<int>(cudaGetLastError());
 }
 
+// The fold between the two passes, one CTA per sample: per-channel partial sums [N, splits, C, 2] -> group statistics
+// -> per-(n, c) coefficients. The arithmetic is a few thousand values; as PyTorch ops it was a dozen launches per
+// normalisation (twenty in the backward), which at the UNet's 176 normalisations per step cost more than the passes.
+namespace mdb {
+namespace cln {
+
+__device__ __forceinline__ float param_at(const void* p, int is_bf16, int c) {
+  if (p == nullptr) return 1.0f;
+  return is_bf16 ? __bfloat162float(static_cast<const __nv_bfloat16*>(p)[c]) : static_cast<const float*>(p)[c];
+}
+
+// forward: a = rstd * gamma, b = beta - mean * a; also mean / rstd [N, G] for the backward
+__global__ void __launch_bounds__(256)
+gn_cl_fold_fwd_kernel(const float2* __restrict__ partial, int splits, int C, int groups, float count, float eps,
+                      const void* gamma, const void* beta, int params_bf16, float* __restrict__ a, float* __restrict__ b,
+                      float* __restrict__ mean_out, float* __restrict__ rstd_out) {
+  extern __shared__ float sm[];  // [C][2] channel sums, then [G][2] group (mean, rstd)
+  float* ch = sm;
+  float* gr = sm + 2 * C;
+  const int n = blockIdx.x, cg = C / groups;
+  for (int c = threadIdx.x; c < C; c += blockDim.x) {
+    float s1 = 0.0f, s2 = 0.0f;
+    for (int s = 0; s < splits; ++s) {  // fixed order
+      const float2 v = partial[(static_cast<long long>(n) * splits + s) * C + c];
+      s1 += v.x;
+      s2 += v.y;
+    }
+    ch[2 * c] = s1;
+    ch[2 * c + 1] = s2;
+  }
+  __syncthreads();
+  for (int g = threadIdx.x; g < groups; g += blockDim.x) {
+    float s1 = 0.0f, s2 = 0.0f;
+    for (int j = 0; j < cg; ++j) {
+      s1 += ch[2 * (g * cg + j)];
+      s2 += ch[2 * (g * cg + j) + 1];
+    }
+    const float mean = s1 / count;
+    const float rstd = rsqrtf(fmaxf(s2 / count - mean * mean, 0.0f) + eps);
+    gr[2 * g] = mean;
+    gr[2 * g + 1] = rstd;
+    mean_out[n * groups + g] = mean;
+    rstd_out[n * groups + g] = rstd;
+  }
+  __syncthreads();
+  for (int c = threadIdx.x; c < C; c += blockDim.x) {
+    const int g = c / cg;
+    const float av = gr[2 * g + 1] * param_at(gamma, params_bf16, c);
+    a[static_cast<long long>(n) * C + c] = av;
+    b[static_cast<long long>(n) * C + c] = (beta != nullptr ? param_at(beta, params_bf16, c) : 0.0f) - gr[2 * g] * av;
+  }
+}
+
+// backward: from d1 = sum dy', d2 = sum dy' * x per channel: dx = dy' * ca + cb + x * cc, and the per-sample terms of
+// dgamma (sum dy' * xhat) and dbeta (sum dy')
+__global__ void __launch_bounds__(256)
+gn_cl_fold_bwd_kernel(const float2* __restrict__ partial, int splits, int C, int groups, float count, const void* gamma,
+                      int params_bf16, const float* __restrict__ mean_in, const float* __restrict__ rstd_in,
+                      float* __restrict__ ca, float* __restrict__ cb, float* __restrict__ cc, float* __restrict__ dgamma_n,
+                      float* __restrict__ dbeta_n) {
+  extern __shared__ float sm[];  // [C][2]: (d1, dxhat) per channel, then [G][2]: (s1, s2)
+  float* ch = sm;
+  float* gr = sm + 2 * C;
+  const int n = blockIdx.x, cg = C / groups;
+  for (int c = threadIdx.x; c < C; c += blockDim.x) {
+    float d1 = 0.0f, d2 = 0.0f;
+    for (int s = 0; s < splits; ++s) {
+      const float2 v = partial[(static_cast<long long>(n) * splits + s) * C + c];
+      d1 += v.x;
+      d2 += v.y;
+    }
+    const int g = c / cg;
+    const float mean = mean_in[n * groups + g], rstd = rstd_in[n * groups + g];
+    const float dxhat = rstd * (d2 - mean * d1);
+    ch[2 * c] = d1;
+    ch[2 * c + 1] = dxhat;
+    dbeta_n[static_cast<long long>(n) * C + c] = d1;
+    dgamma_n[static_cast<long long>(n) * C + c] = dxhat;
+  }
+  __syncthreads();
+  for (int g = threadIdx.x; g < groups; g += blockDim.x) {
+    float s1 = 0.0f, s2 = 0.0f;
+    for (int j = 0; j < cg; ++j) {
+      const int c = g * cg + j;
+      const float gm = param_at(gamma, params_bf16, c);
+      s1 += gm * ch[2 * c];
+      s2 += gm * ch[2 * c + 1];
+    }
+    gr[2 * g] = s1 / count;
+    gr[2 * g + 1] = s2 / count;
+  }
+  __syncthreads();
+  for (int c = threadIdx.x; c < C; c += blockDim.x) {
+    const int g = c / cg;
+    const float mean = mean_in[n * groups + g], rstd = rstd_in[n * groups + g];
+    const float s1 = gr[2 * g], s2 = gr[2 * g + 1];
+    const long long o = static_cast<long long>(n) * C + c;
+    ca[o] = rstd * param_at(gamma, params_bf16, c);
+    cb[o] = -rstd * s1 + mean * rstd * rstd * s2;
+    cc[o] = -rstd * rstd * s2;
+  }
+}
+
+}  // namespace cln
+}  // namespace mdb
+
+// partial: fp32 [N, splits, C, 2] from mdb_gn_cl_sums; gamma / beta: [C] bf16 (params_bf16 = 1) or fp32, may be null;
+// a, b: fp32 [N, C]; mean, rstd: fp32 [N, groups]. count = pixels * channels per group.
+extern "C" int mdb_gn_cl_fold_fwd(const float* partial, int N, int splits, int C, int groups, float count, float eps,
+                                  const void* gamma, const void* beta, int params_bf16, float* a, float* b, float* mean,
+                                  float* rstd, void* stream) {
+  if (N <= 0) return 0;
+  if (groups <= 0 || C % groups || splits < 1 || C > 8192) return 3704;
+  const size_t smem = (2 * static_cast<size_t>(C) + 2 * groups) * sizeof(float);
+  mdb::cln::gn_cl_fold_fwd_kernel<<<N, 256, smem, static_cast<cudaStream_t>(stream)>>>(
+      reinterpret_cast<const float2*>(partial), splits, C, groups, count, eps, gamma, beta, params_bf16, a, b, mean, rstd);
+  return static_cast<int>(cudaGetLastError());
+}
+
+// ca, cb, cc, dgamma_n, dbeta_n: fp32 [N, C] (the caller sums the last two over N).
+extern "C" int mdb_gn_cl_fold_bwd(const float* partial, int N, int splits, int C, int groups, float count, const void* gamma,
+                                  int params_bf16, const float* mean, const float* rstd, float* ca, float* cb, float* cc,
+                                  float* dgamma_n, float* dbeta_n, void* stream) {
+  if (N <= 0) return 0;
+  if (groups <= 0 || C % groups || splits < 1 || C > 8192) return 3704;
+  const size_t smem = (2 * static_cast<size_t>(C) + 2 * groups) * sizeof(float);
+  mdb::cln::gn_cl_fold_bwd_kernel<<<N, 256, smem, static_cast<cudaStream_t>(stream)>>>(
+      reinterpret_cast<const float2*>(partial), splits, C, groups, count, gamma, params_bf16, mean, rstd, ca, cb, cc, dgamma_n,
+      dbeta_n);
+  return static_cast<int>(cudaGetLastError());
+}
+
 // ---------------------------------------------------------------------------------------------------------------
 // Row softmax, in place or out of place: y[r, :] = softmax(x[r, :]) for bf16 rows of up to 32768 columns, fp32 math.
 // One CTA per row, the row lives in registers between the two reductions (one read, one write). It sits between the two

@@ -32,8 +32,9 @@ __host__ __device__ constexpr int stage_bytes(int bn) { return A_BYTES + bn * BK
 // swizzle, written by the epilogue warps and drained by TMA stores.
 constexpr int SLAB_BYTES = BM * 128;
 constexpr int STAGING_BYTES = 2 * SLAB_BYTES;
+constexpr int BIAS_BYTES = 256 * 4;  // the tile's bias columns as fp32
 __host__ __device__ constexpr int smem_bytes(int bn) {
-  return stages_for(bn) * stage_bytes(bn) + STAGING_BYTES + 1024 /*align slack*/ + 256 /*barriers*/;
+  return stages_for(bn) * stage_bytes(bn) + STAGING_BYTES + BIAS_BYTES + 1024 /*align slack*/ + 256 /*barriers*/;
 }
 
 enum Epilogue : int {
@@ -92,7 +93,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* staging = smem + STAGES * STAGE_BYTES;  // 1024-byte aligned: every stage is a multiple of 1024 bytes
-  uint64_t* bars = reinterpret_cast<uint64_t*>(staging + STAGING_BYTES);
+  float* bias_s = reinterpret_cast<float*>(staging + STAGING_BYTES);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(staging + STAGING_BYTES + BIAS_BYTES);
   uint64_t* full_bar = bars;                    // [STAGES]
   uint64_t* empty_bar = bars + STAGES;          // [STAGES]
   uint64_t* tmem_full = bars + 2 * STAGES;      // [2]
@@ -238,13 +240,44 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
         const long long out_row0 = (p.splits > 1 ? static_cast<long long>(split) * p.partial_rows : 0) +
                                    static_cast<long long>(m_idx) * BM;
         const int sw = row_in_tile & 7;
+        const bool use_bias = p.bias != nullptr && p.splits == 1;
+        const bool res_epi = (p.epi == kEpiGatedRes || p.epi == kEpiAddRes) && p.splits == 1;
+        // bf16 output: the residual slab is fetched by coalesced loads (8 lanes per 128-byte row) and handed to the
+        // row-owning threads through the staging slab; a warp touches only its own 32 rows, so a warp sync suffices
+        const bool res_staged = res_epi && !f32;
+        if (use_bias) {
+          // the tile's bias columns once, as fp32 (the previous tile's readers passed its last slab barrier)
+          for (int c = static_cast<int>(threadIdx.x) - 64; c < BN; c += 128) {
+            const int col = n_idx * BN + c;
+            bias_s[c] = col < p.N ? __bfloat162float(p.bias[col]) : 0.0f;
+          }
+        }
 #pragma unroll 1
         for (int c0 = 0; c0 < BN; c0 += slab_cols) {
           const int col0 = n_idx * BN + c0;
           if (col0 >= p.N) break;  // uniform across the CTA
           uint8_t* slab = staging + (slab_count & 1) * SLAB_BYTES;
+          uint4 rv[8];
+          if (res_staged) {  // issued before the barrier: their latency overlaps the wait for the slab
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+              const int rl = quarter * 32 + i * 4 + (lane >> 3);
+              const long long grow = static_cast<long long>(m_idx) * BM + rl;
+              const int gcol = col0 + (lane & 7) * 8;
+              rv[i] = (grow < p.M && gcol < p.N) ? *reinterpret_cast<const uint4*>(p.residual + grow * p.ldr + gcol)
+                                                 : make_uint4(0u, 0u, 0u, 0u);
+            }
+          }
           if (leader) tma_store_wait_read<1>();  // the store that read this slab two slabs ago is done with it
           named_bar_sync(1, 128);
+          if (res_staged) {
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+              const int rl = quarter * 32 + i * 4 + (lane >> 3);
+              *reinterpret_cast<uint4*>(slab + rl * 128 + ((((lane & 7) ^ (rl & 7))) << 4)) = rv[i];
+            }
+            __syncwarp();
+          }
           uint8_t* my_row = slab + row_in_tile * 128;
 #pragma unroll
           for (int h = 0; h < 2; ++h) {  // bf16: two 32-column loads per slab; fp32: one
@@ -259,15 +292,11 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
 #pragma unroll
               for (int j = 0; j < 8; ++j) x[j] = __uint_as_float(r[v * 8 + j]) * p.alpha;
               if (p.splits == 1 && col < p.N) {
-                if (p.bias) {
-                  const uint4 bv = *reinterpret_cast<const uint4*>(p.bias + col);
-                  const uint32_t bw[4] = {bv.x, bv.y, bv.z, bv.w};
-#pragma unroll
-                  for (int j = 0; j < 4; ++j) {
-                    float2 f = unpack_bf16x2(bw[j]);
-                    x[2 * j] += f.x;
-                    x[2 * j + 1] += f.y;
-                  }
+                if (use_bias) {
+                  const float4 b0 = *reinterpret_cast<const float4*>(bias_s + c0 + h * 32 + v * 8);
+                  const float4 b1 = *reinterpret_cast<const float4*>(bias_s + c0 + h * 32 + v * 8 + 4);
+                  x[0] += b0.x; x[1] += b0.y; x[2] += b0.z; x[3] += b0.w;
+                  x[4] += b1.x; x[5] += b1.y; x[6] += b1.z; x[7] += b1.w;
                 }
                 if (p.epi == kEpiGeluTanh) {
 #pragma unroll
@@ -275,9 +304,10 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
                 } else if (p.epi == kEpiSilu) {
 #pragma unroll
                   for (int j = 0; j < 8; ++j) x[j] = x[j] / (1.0f + __expf(-x[j]));
-                } else if ((p.epi == kEpiGatedRes || p.epi == kEpiAddRes) && row_ok) {
-                  const uint4 rv = *reinterpret_cast<const uint4*>(p.residual + row * p.ldr + col);
-                  const uint32_t rw[4] = {rv.x, rv.y, rv.z, rv.w};
+                } else if (res_epi && row_ok) {
+                  const uint4 rres = res_staged ? *reinterpret_cast<const uint4*>(my_row + (((h * 4 + v) ^ sw) << 4))
+                                                : *reinterpret_cast<const uint4*>(p.residual + row * p.ldr + col);
+                  const uint32_t rw[4] = {rres.x, rres.y, rres.z, rres.w};
                   float g[8];
                   if (p.epi == kEpiGatedRes) {
                     const float4 g0 = *reinterpret_cast<const float4*>(p.gate + batch * p.gate_ld + col);

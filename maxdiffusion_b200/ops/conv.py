@@ -47,6 +47,11 @@ def _declare(L):
   L.mdb_gn_cl_sums.restype = c_int
   L.mdb_gn_cl_apply.argtypes = [c_void_p] * 8 + [c_int] * 4 + [c_void_p]
   L.mdb_gn_cl_apply.restype = c_int
+  c_float = ctypes.c_float
+  L.mdb_gn_cl_fold_fwd.argtypes = [c_void_p, c_int, c_int, c_int, c_int, c_float, c_float, c_void_p, c_void_p, c_int] + [c_void_p] * 5
+  L.mdb_gn_cl_fold_fwd.restype = c_int
+  L.mdb_gn_cl_fold_bwd.argtypes = [c_void_p, c_int, c_int, c_int, c_int, c_float, c_void_p, c_int] + [c_void_p] * 8
+  L.mdb_gn_cl_fold_bwd.restype = c_int
 
 
 _lib.register(_declare)
@@ -464,14 +469,15 @@ def _gn_splits(n: int, hw: int) -> int:
   return max(1, min((4 * 148 + n - 1) // n, (hw + 63) // 64))
 
 
-def _gn_sums(x3, dy3=None, act_a=None, act_b=None):
+def _gn_partial(x3, dy3=None, act_a=None, act_b=None):
+  """Per-channel partial sums fp32 [N, S, C, 2] over S strips of pixels (forward: x, x^2; backward: dy', dy' * x)."""
   N, HW, C = x3.shape
   S = _gn_splits(N, HW)
   partial = torch.empty((N, S, C, 2), device=x3.device, dtype=torch.float32)
   rc = _lib.lib().mdb_gn_cl_sums(_lib.ptr(x3), _lib.ptr(dy3), _lib.ptr(act_a), _lib.ptr(act_b), _lib.ptr(partial), N, HW, C, S,
                                  _lib.stream())
   _lib.check(rc, "mdb_gn_cl_sums")
-  return partial.sum(dim=1)  # [N, C, 2], fixed order
+  return partial
 
 
 def _gn_apply(x3, dy3, ca, cb, cc, fa, fb, act):
@@ -483,41 +489,46 @@ def _gn_apply(x3, dy3, ca, cb, cc, fa, fb, act):
   return out
 
 
+def _gn_params(gamma, beta):
+  """(gamma, beta, is_bf16) in one dtype the fold kernels read: bf16 or fp32, contiguous."""
+  ps = [p for p in (gamma, beta) if p is not None]
+  if not ps:
+    return None, None, 0
+  bf16 = all(p.dtype == torch.bfloat16 for p in ps)
+  conv = (lambda p: p.contiguous()) if bf16 else (lambda p: p.float().contiguous())
+  return (None if gamma is None else conv(gamma)), (None if beta is None else conv(beta)), int(bf16)
+
+
 def group_norm_cl_fwd(x3: torch.Tensor, groups: int, gamma, beta, eps: float, act: bool):
-  """x3 [N, HW, C] bf16 contiguous -> (y, a, b, mean, rstd): y = act(x * a + b) with a, b fp32 [N, C]."""
+  """x3 [N, HW, C] bf16 contiguous -> (y, a, b, mean, rstd): y = act(x * a + b) with a, b fp32 [N, C]. Three launches:
+  per-channel sums, the fold to coefficients (one CTA per sample), the apply pass."""
   N, HW, C = x3.shape
-  cg = C // groups
-  s = _gn_sums(x3).view(N, groups, cg, 2).sum(dim=2)  # [N, G, 2]
-  m = float(HW * cg)
-  mean = s[..., 0] / m
-  rstd = torch.rsqrt((s[..., 1] / m - mean * mean).clamp_min(0.0) + eps)
-  g = gamma.float().view(1, groups, cg) if gamma is not None else torch.ones((1, groups, cg), device=x3.device)
-  a = (rstd.unsqueeze(-1) * g)
-  b = -mean.unsqueeze(-1) * a
-  if beta is not None:
-    b = b + beta.float().view(1, groups, cg)
-  a, b = a.reshape(N, C).contiguous(), b.reshape(N, C).contiguous()
+  partial = _gn_partial(x3)
+  a = torch.empty((N, C), device=x3.device, dtype=torch.float32)
+  b = torch.empty_like(a)
+  mean = torch.empty((N, groups), device=x3.device, dtype=torch.float32)
+  rstd = torch.empty_like(mean)
+  g, bt, bf16 = _gn_params(gamma, beta)
+  rc = _lib.lib().mdb_gn_cl_fold_fwd(_lib.ptr(partial), N, partial.shape[1], C, groups, float(HW * (C // groups)), float(eps),
+                                     _lib.ptr(g), _lib.ptr(bt), bf16, _lib.ptr(a), _lib.ptr(b), _lib.ptr(mean), _lib.ptr(rstd),
+                                     _lib.stream())
+  _lib.check(rc, "mdb_gn_cl_fold_fwd")
   return _gn_apply(x3, None, a, b, None, None, None, act), a, b, mean, rstd
 
 
 def group_norm_cl_bwd(dy3, x3, groups: int, gamma, a, b, mean, rstd, act: bool):
   """Returns (dx, dgamma fp32 [C], dbeta fp32 [C]) for y = act(groupnorm(x) * gamma + beta)."""
   N, HW, C = x3.shape
-  cg = C // groups
-  d = _gn_sums(x3, dy3, a if act else None, b if act else None)   # per channel: sum dy', sum dy' * x
-  d1, d2 = d[..., 0].view(N, groups, cg), d[..., 1].view(N, groups, cg)
-  mean_, rstd_ = mean.unsqueeze(-1), rstd.unsqueeze(-1)
-  dxhat = rstd_ * (d2 - mean_ * d1)              # sum dy' * xhat per channel
-  g = gamma.float().view(1, groups, cg) if gamma is not None else torch.ones((1, groups, cg), device=x3.device)
-  m = float(HW * cg)
-  s1 = (g * d1).sum(dim=2, keepdim=True) / m     # mean over the group of dy' * gamma
-  s2 = (g * dxhat).sum(dim=2, keepdim=True) / m  # mean over the group of dy' * gamma * xhat
-  cc = (-rstd_ * rstd_ * s2).expand(N, groups, cg)
-  cb = (-rstd_ * s1 + mean_ * rstd_ * rstd_ * s2).expand(N, groups, cg)
-  ca = rstd_ * g
-  dx = _gn_apply(x3, dy3, ca.reshape(N, C).contiguous(), cb.reshape(N, C).contiguous(), cc.reshape(N, C).contiguous(),
-                 a if act else None, b if act else None, False)
-  return dx, dxhat.sum(dim=0).reshape(C), d1.sum(dim=0).reshape(C)
+  partial = _gn_partial(x3, dy3, a if act else None, b if act else None)   # per channel: sum dy', sum dy' * x
+  ca = torch.empty((N, C), device=x3.device, dtype=torch.float32)
+  cb, cc, dg, db = (torch.empty_like(ca) for _ in range(4))
+  g, _, bf16 = _gn_params(gamma, None)
+  rc = _lib.lib().mdb_gn_cl_fold_bwd(_lib.ptr(partial), N, partial.shape[1], C, groups, float(HW * (C // groups)), _lib.ptr(g),
+                                     bf16, _lib.ptr(mean), _lib.ptr(rstd), _lib.ptr(ca), _lib.ptr(cb), _lib.ptr(cc),
+                                     _lib.ptr(dg), _lib.ptr(db), _lib.stream())
+  _lib.check(rc, "mdb_gn_cl_fold_bwd")
+  dx = _gn_apply(x3, dy3, ca, cb, cc, a if act else None, b if act else None, False)
+  return dx, dg.sum(dim=0), db.sum(dim=0)
 
 
 # ---------------------------------------------------------------------------------------------

@@ -39,7 +39,7 @@ def _world() -> int:
 
 def _max_over_ranks(x: float) -> float:
   if _world() > 1:
-    t = torch.tensor([x], device="cuda", dtype=torch.float64)
+    t = torch.tensor([x], device="cuda" if torch.cuda.is_available() else "cpu", dtype=torch.float64)
     dist.all_reduce(t, op=dist.ReduceOp.MAX)
     return float(t.item())
   return x
@@ -48,7 +48,8 @@ def _max_over_ranks(x: float) -> float:
 def _barrier_sync() -> None:
   if _world() > 1:
     dist.barrier()
-  torch.cuda.synchronize()
+  if torch.cuda.is_available():
+    torch.cuda.synchronize()
 
 
 def _pinned(t: torch.Tensor) -> torch.Tensor:
@@ -121,7 +122,7 @@ def bench_wan(args) -> dict:
       _barrier_sync()
       t0 = time.perf_counter()
       video = pipe.decode_latents(lat)
-      torch.cuda.synchronize()
+      _barrier_sync()
       out["config"]["vae_decode_seconds"] = time.perf_counter() - t0
       out["config"]["vae_decode_shape"] = list(video.shape)
   return out
