@@ -552,7 +552,8 @@ def test_gemm_int8_is_exact_on_the_quantised_operands(M, N, Kd):
   assert (aq.int() - (a.float() / sa).round().clamp(-127, 127).int()).abs().max() <= 1
   assert aq.int().abs().max() == 127
   out = K.gemm_int8(aq, sa, bq, sb, bias)
-  exact = (aq.long() @ bq.long().t()).double() * (sa.double() * sb.double()) + bias.double()
+  # integer products in float64 are exact at these sizes (|sum| <= 127^2 * K < 2^53)
+  exact = (aq.double() @ bq.double().t()) * (sa.double() * sb.double()) + bias.double()
   assert (out.double() - exact).abs().max() <= 1e-2 * exact.abs().max()
   assert _rel(out, exact.float()) < 4e-3  # bf16 output rounding only
   assert _rel(out, a.float() @ b.float().t() + bias.float()) < 5e-2  # int8 rounding of the operands
@@ -576,3 +577,26 @@ def test_int8_linear_module_forward_and_bf16_backward():
   holder = torch.nn.ModuleDict({"blocks": torch.nn.ModuleList([torch.nn.ModuleDict({"proj": Linear(64, 64)})])})
   assert quantize_model(holder, "int8") == 1 and isinstance(holder["blocks"][0]["proj"], Int8Linear)
   _lib.raise_on_device_status()
+
+
+@pytest.mark.parametrize("C", [96, 320, 640, 1280, 2048, 2056])
+@pytest.mark.parametrize("B,S", [(8, 100), (1, 1031)])
+def test_affine_layer_norm_short_rows_forward_and_backward(C, B, S):
+  """Plain affine LayerNorm on rows of at most 2048 channels runs a warp per row (UNet / DiT blocks); 2056 channels
+  take the CTA-per-row kernels. Forward, input gradient and parameter gradients against fp32 autograd."""
+  from maxdiffusion_b200.ops import functional as OF
+
+  g = torch.Generator(device="cuda").manual_seed(C + S)
+  x = (torch.randn((B, S, C), device="cuda", generator=g) * 2 + 0.5).to(torch.bfloat16).requires_grad_(True)
+  gamma = (torch.rand((C,), device="cuda", generator=g) + 0.5).to(torch.bfloat16).requires_grad_(True)
+  beta = (torch.randn((C,), device="cuda", generator=g) * 0.2).to(torch.bfloat16).requires_grad_(True)
+  dy = torch.randn((B, S, C), device="cuda", generator=g).to(torch.bfloat16)
+  y = OF.layer_norm_mod(x, gamma, beta, eps=1e-5)
+  gx, gg, gb = torch.autograd.grad(y, (x, gamma, beta), dy)
+  xf, gf, bf = (t.detach().float().requires_grad_(True) for t in (x, gamma, beta))
+  want = torch.nn.functional.layer_norm(xf, (C,), gf, bf, 1e-5)
+  wx, wg, wb = torch.autograd.grad(want, (xf, gf, bf), dy.float())
+  assert _rel(y, want) < 1e-2 and _rel(gx, wx) < 1e-2
+  assert _rel(gg, wg) < 2e-2 and _rel(gb, wb) < 2e-2
+  y2 = OF.layer_norm_mod(x, gamma, beta, eps=1e-5)
+  assert torch.equal(y, y2) and torch.equal(gx, torch.autograd.grad(y2, x, dy)[0])  # reproducible
