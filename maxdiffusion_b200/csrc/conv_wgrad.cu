@@ -10,6 +10,12 @@
 // the pixel axis is split: a work item is (tap, K split, M tile, N tile) and writes an fp32 partial tile; the caller
 // sums the splits in a fixed order (bitwise reproducible). Stride-2 convolutions use the same kernel on the four
 // parity planes of X (plane choice = one more row offset).
+//
+// The boxed form (`mdb_conv_wgrad_boxed`) needs no bordered copies at all: a K block is a box of 64 output pixels
+// (BW x BH of one image) fetched from the unpadded channels-last tensors by 5-D TMA; a tap moves X's box by its
+// (row, column) shift and whatever falls outside the image is the tensor map's zero fill, exactly the padding the
+// forward convolution read. Stride 2 views X as [B, H/2, 2, W/2, 2C]: the row parity is a coordinate of its own and
+// the column parity an offset into the doubled channel axis.
 // Roles per CTA (persistent): warp 0 TMA producer, warp 1 TMEM owner + MMA issuer, warps 2..5 epilogue; accumulators
 // double buffered in TMEM.
 //
@@ -36,6 +42,9 @@ struct Params {
   long long b_row_off[MAX_TAPS];
   float* out;               // [n_taps, splits, M, N] fp32
   DeviceStatus* status;
+  // boxed form: K block kb = (image, row block, column block) of the output pixel grid
+  int boxed, BW, BH, n_wb, n_hb;
+  int tap_c[MAX_TAPS], tap_w[MAX_TAPS], tap_par[MAX_TAPS], tap_h[MAX_TAPS];  // channel offset, column shift, row parity, row shift
 };
 
 __global__ void __launch_bounds__(NUM_THREADS, 1)
@@ -103,11 +112,35 @@ conv_wgrad_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
         const int kb0 = split * kb_per_split;
         const int kb1 = min(p.kb_total, kb0 + kb_per_split);
         const long long off = p.b_row_off[tap];
+        // boxed form: (image, row block, column block) of the first K block, advanced without divisions
+        int wb = 0, hb = 0, img = 0;
+        if (p.boxed) {
+          wb = kb0 % p.n_wb;
+          const int t = kb0 / p.n_wb;
+          hb = t % p.n_hb;
+          img = t / p.n_hb;
+        }
         for (int kb = kb0; kb < kb1; ++kb) {
           if (!mbar_wait(&empty_bar[stage], phase ^ 1u, abort_flag, p.status, 140)) { ok = false; break; }
           uint8_t* sa = smem + stage * STAGE_BYTES;
           uint8_t* sb = sa + A_BYTES;
           mbar_expect_tx(&full_bar[stage], STAGE_BYTES);
+          if (p.boxed) {
+            const int w0 = wb * p.BW, h0 = hb * p.BH;
+#pragma unroll
+            for (int c = 0; c < BM / 64; ++c)
+              tma_load_5d(sa + c * (BK * 128), &tmap_a, &full_bar[stage], m_idx * BM + c * 64, w0, 0, h0, img);
+            for (int c = 0; c < p.BN / 64; ++c)
+              tma_load_5d(sb + c * (BK * 128), &tmap_b, &full_bar[stage], p.tap_c[tap] + n_idx * p.BN + c * 64,
+                          w0 + p.tap_w[tap], p.tap_par[tap], h0 + p.tap_h[tap], img);
+            if (++wb == p.n_wb) {
+              wb = 0;
+              if (++hb == p.n_hb) { hb = 0; ++img; }
+            }
+            ++issued;
+            if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+            continue;
+          }
           const int k0 = kb * BK;
 #pragma unroll
           for (int c = 0; c < BM / 64; ++c) tma_load_2d(sa + c * (BK * 128), &tmap_a, &full_bar[stage], m_idx * BM + c * 64, k0);
@@ -242,6 +275,9 @@ extern "C" int mdb_conv_wgrad(const void* dy, const void* x, float* out, long lo
   for (int t = 0; t < MAX_TAPS; ++t) p.b_row_off[t] = t < n_taps ? b_row_off[t] : 0;
   p.out = out;
   p.status = status_buffer();
+  p.boxed = 0;
+  p.BW = p.BH = p.n_wb = p.n_hb = 1;
+  for (int t = 0; t < MAX_TAPS; ++t) p.tap_c[t] = p.tap_w[t] = p.tap_par[t] = p.tap_h[t] = 0;
   CUtensorMap ta, tb;
   {
     uint64_t dims[2] = {static_cast<uint64_t>(M), static_cast<uint64_t>(rows_a)};
@@ -256,6 +292,78 @@ extern "C" int mdb_conv_wgrad(const void* dy, const void* x, float* out, long lo
   }
   int smem = p.stages * (A_BYTES + p.BN * BK * 2) + 1024 + 256;
   if (smem < 120 * 1024) smem = 120 * 1024;  // one CTA per SM: every CTA allocates all of TMEM
+  static bool configured = false;
+  if (!configured) {
+    MDB_CHECK_CUDA(cudaFuncSetAttribute(conv_wgrad_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
+    configured = true;
+  }
+  const long long items = static_cast<long long>(n_taps) * splits * ((M + BM - 1) / BM) * ((N + p.BN - 1) / p.BN);
+  const int grid = items < sm_count() ? static_cast<int>(items) : sm_count();
+  conv_wgrad_kernel<<<grid, NUM_THREADS, smem, static_cast<cudaStream_t>(stream_ptr)>>>(ta, tb, p);
+  return static_cast<int>(cudaGetLastError());
+}
+
+// The same products from the UNPADDED channels-last tensors. dy: [B, Ho, Wo, M] bf16 (strides in elements: dy_sb,
+// dy_sh, dy_sw; channels dense); x: [B, H, W, C] bf16 with strides x_sb, x_sh, x_sw, N = C rounded up to 8 (the
+// tensor itself must hold N channels). stride 1 or 2 (2 needs even H and W). taps: n_taps x {column parity (0 / 1),
+// column shift, row parity, row shift} in units of the (possibly halved) grid of x; a K block is a BW x BH box of
+// output pixels with BW * BH = 64. out: fp32 [n_taps, splits, M, N].
+extern "C" int mdb_conv_wgrad_boxed(const void* dy, const void* x, float* out, int B, int Ho, int Wo, int H, int W, int M,
+                                    int N, long long dy_sb, long long dy_sh, long long dy_sw, long long x_sb,
+                                    long long x_sh, long long x_sw, int stride, int n_taps, const int* taps, int BW, int BH,
+                                    int splits, void* stream_ptr) {
+  using namespace mdb;
+  using namespace mdb::wgrad;
+  if (M <= 0 || N <= 0 || B <= 0 || Ho <= 0 || Wo <= 0) return 0;
+  if ((M & 7) || (N & 7) || n_taps < 1 || n_taps > MAX_TAPS || splits < 1 || BW * BH != BK || BW > 256 || BH > 256) return 3801;
+  if ((stride != 1 && stride != 2) || (stride == 2 && ((H | W) & 1))) return 3803;
+  if ((dy_sb | dy_sh | dy_sw | x_sb | x_sh | x_sw) & 7) return 3804;
+  Params p;
+  p.M = M; p.N = N;
+  int best = 64;
+  double best_cost = -1.0;
+  for (int bn = 64; bn <= 256; bn += 64) {
+    const double cost = static_cast<double>((N + bn - 1) / bn * bn) * (1.0 + 64.0 / bn);
+    if (best_cost < 0 || cost < best_cost - 1e-9 || (cost < best_cost + 1e-9 && bn > best)) { best = bn; best_cost = cost; }
+  }
+  p.BN = best;
+  p.stages = p.BN > 128 ? 4 : 6;
+  p.n_taps = n_taps;
+  p.splits = splits;
+  p.boxed = 1;
+  p.BW = BW; p.BH = BH;
+  p.n_wb = (Wo + BW - 1) / BW;
+  p.n_hb = (Ho + BH - 1) / BH;
+  p.kb_total = B * p.n_hb * p.n_wb;
+  for (int t = 0; t < MAX_TAPS; ++t) {
+    p.b_row_off[t] = 0;
+    p.tap_c[t] = t < n_taps ? taps[4 * t] * N : 0;  // the column parity selects one half of the doubled channel axis
+    p.tap_w[t] = t < n_taps ? taps[4 * t + 1] : 0;
+    p.tap_par[t] = t < n_taps ? taps[4 * t + 2] : 0;
+    p.tap_h[t] = t < n_taps ? taps[4 * t + 3] : 0;
+  }
+  p.out = out;
+  p.status = status_buffer();
+  CUtensorMap ta, tb;
+  {
+    uint64_t dims[5] = {static_cast<uint64_t>(M), static_cast<uint64_t>(Wo), 1, static_cast<uint64_t>(Ho), static_cast<uint64_t>(B)};
+    uint64_t str[4] = {static_cast<uint64_t>(dy_sw) * 2, static_cast<uint64_t>(dy_sh) * 2, static_cast<uint64_t>(dy_sh) * 2,
+                       static_cast<uint64_t>(dy_sb) * 2};
+    uint32_t box[5] = {64, static_cast<uint32_t>(BW), 1, static_cast<uint32_t>(BH), 1};
+    int rc = encode_tmap_bf16(&ta, dy, 5, dims, str, box);
+    if (rc) return rc;
+    // x: stride 1 -> [N, W, 1, H, B]; stride 2 -> [2N (column parity x channel), W/2, 2 (row parity), H/2, B]
+    const int s = stride;
+    uint64_t dimsb[5] = {static_cast<uint64_t>(N) * s, static_cast<uint64_t>(W / s), static_cast<uint64_t>(s),
+                         static_cast<uint64_t>(H / s), static_cast<uint64_t>(B)};
+    uint64_t strb[4] = {static_cast<uint64_t>(x_sw) * s * 2, static_cast<uint64_t>(x_sh) * 2, static_cast<uint64_t>(x_sh) * s * 2,
+                        static_cast<uint64_t>(x_sb) * 2};
+    if (stride == 2 && x_sw != N) return 3805;  // the column parity rides on the channel axis: pixels must be N apart
+    rc = encode_tmap_bf16(&tb, x, 5, dimsb, strb, box);
+    if (rc) return rc;
+  }
+  int smem = p.stages * (A_BYTES + p.BN * BK * 2) + 1024 + 256;
+  if (smem < 120 * 1024) smem = 120 * 1024;
   static bool configured = false;
   if (!configured) {
     MDB_CHECK_CUDA(cudaFuncSetAttribute(conv_wgrad_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));

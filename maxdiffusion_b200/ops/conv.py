@@ -41,6 +41,8 @@ def _declare(L):
   L.mdb_conv_igemm_tune.restype = c_int
   L.mdb_conv_wgrad.argtypes = [c_void_p, c_void_p, c_void_p, c_ll, c_ll, c_int, c_int, c_int, llp, c_int, c_void_p]
   L.mdb_conv_wgrad.restype = c_int
+  L.mdb_conv_wgrad_boxed.argtypes = [c_void_p] * 3 + [c_int] * 7 + [c_ll] * 6 + [c_int, c_int, ip, c_int, c_int, c_int, c_void_p]
+  L.mdb_conv_wgrad_boxed.restype = c_int
   L.mdb_softmax_rows.argtypes = [c_void_p, c_ll, c_void_p, c_ll, c_ll, c_int, c_void_p]
   L.mdb_softmax_rows.restype = c_int
   L.mdb_gn_cl_sums.argtypes = [c_void_p] * 5 + [c_int] * 4 + [c_void_p]
@@ -371,16 +373,101 @@ def wgrad_plan(H: int, W: int, k: int, stride: int, pad: int):
   return planes, H // 2, W // 2, taps
 
 
-def conv2d_wgrad(x: torch.Tensor, dy: torch.Tensor, k: int = 3, stride: int = 1, pad: int = 1) -> torch.Tensor:
-  """dW [Co, Ci, k, k] (fp32) of a conv2d from x [B, H, W, Ci] and dy [B, Ho, Wo, Co], both channels-last."""
+def wgrad_box(Ho: int, Wo: int) -> tuple:
+  """(BW, BH) with BW * BH = 64: the box of output pixels that makes one K block, chosen for the fewest pixels of
+  padding on a Ho x Wo grid (ties: the wider box, whose rows are longer contiguous runs)."""
+  best = None
+  for bw in (64, 32, 16, 8):
+    bh = 64 // bw
+    cost = -(-Wo // bw) * bw * -(-Ho // bh) * bh
+    if best is None or cost < best[0]:
+      best = (cost, bw, bh)
+  return best[1], best[2]
+
+
+def wgrad_splits(items: int, kb: int, out_elems: int, sms: int = 148) -> int:
+  """K splits of the weight gradient: rounds of work items over the SMs times K blocks per item (0.27 us each), plus
+  the write and read of one fp32 partial per split."""
+  fold_us = out_elems * 8 / 5e6
+  best, best_cost = 1, None
+  for s in range(1, 65):
+    per = -(-kb // s)
+    if per < 8 and s > 1:
+      break
+    cost = -(-items * s // sms) * per * 0.27 + s * fold_us
+    if best_cost is None or cost < best_cost * 0.97:
+      best, best_cost = s, cost
+  return best
+
+
+def wgrad_taps_boxed(k: int, stride: int, pad: int) -> list:
+  """Per kernel tap (column parity, column shift, row parity, row shift) on the grid the boxed kernel reads x
+  through: the input pixel of output (ho, wo) is (stride * ho + a - pad, stride * wo + b - pad)."""
+  taps = []
+  for a in range(k):
+    dh, ph = divmod(a - pad, stride) if stride == 2 else (a - pad, 0)
+    for b in range(k):
+      dw, pw = divmod(b - pad, stride) if stride == 2 else (b - pad, 0)
+      taps.append((pw, dw, ph, dh))
+  return taps
+
+
+def _boxed_ok(x, dy, stride) -> bool:
+  B, H, W, Ci = x.shape
+  return (stride == 1 or (H % 2 == 0 and W % 2 == 0)) and x.stride(-1) == 1 and dy.stride(-1) == 1
+
+
+def _conv2d_wgrad_boxed(x, dy, k, stride, pad):
+  """No bordered copies: K blocks are boxes of output pixels read straight from x and dy (see csrc/conv_wgrad.cu)."""
+  B, H, W, Ci = x.shape
+  _, Ho, Wo, Co = dy.shape
+  ci8, co8 = _round_up(Ci, 8), _round_up(Co, 8)
+  x, dy = pad_channels(x, ci8), pad_channels(dy, co8)
+  if stride == 2 and x.stride(2) != ci8:
+    x = x.contiguous()
+  if any(s % 8 for s in (*x.stride()[:3], *dy.stride()[:3])):
+    x, dy = x.contiguous(), dy.contiguous()
+  bw, bh = wgrad_box(Ho, Wo)
+  taps = wgrad_taps_boxed(k, stride, pad)
+  kb = B * -(-Ho // bh) * -(-Wo // bw)
+  items = len(taps) * -(-co8 // 128) * max(1, -(-ci8 // 256))
+  splits = wgrad_splits(items, kb, len(taps) * co8 * ci8)
+  out = _wgrad_launch_boxed(dy, x, taps, (bw, bh), stride, splits)
+  dw = (out.sum(dim=1) if splits > 1 else out[:, 0])[:, :Co, :Ci]
+  return dw.reshape(k, k, Co, Ci).permute(2, 3, 0, 1)
+
+
+def _wgrad_launch_boxed_kernel(dy, x, taps, box, stride, splits):
+  """out[tap, split] = sum over the split's boxes of dy[box]^T x[box moved by the tap] (outside the image: zeros)."""
+  B, Ho, Wo, M = dy.shape
+  _, H, W, N = x.shape
+  out = torch.empty((len(taps), splits, M, N), dtype=torch.float32, device=dy.device)
+  flat = [v for t in taps for v in t]
+  arr = (ctypes.c_int * len(flat))(*flat)
+  rc = _lib.lib().mdb_conv_wgrad_boxed(_lib.ptr(dy), _lib.ptr(x), _lib.ptr(out), B, Ho, Wo, H, W, M, N, dy.stride(0), dy.stride(1),
+                                       dy.stride(2), x.stride(0), x.stride(1), x.stride(2), stride, len(taps), arr, box[0], box[1],
+                                       splits, _lib.stream())
+  _lib.check(rc, "mdb_conv_wgrad_boxed")
+  return out
+
+
+_wgrad_launch_boxed = _wgrad_launch_boxed_kernel
+
+
+def conv2d_wgrad(x: torch.Tensor, dy: torch.Tensor, k: int = 3, stride: int = 1, pad: int = 1, boxed: Optional[bool] = None) -> torch.Tensor:
+  """dW [Co, Ci, k, k] (fp32) of a conv2d from x [B, H, W, Ci] and dy [B, Ho, Wo, Co], both channels-last. `boxed`:
+  None = the pad-free kernel form wherever it applies (stride 2 needs even H and W), False = the bordered form."""
   B, H, W, Ci = x.shape
   Co = dy.shape[-1]
-  if not use_kernel(x) and _wgrad_launch is _wgrad_launch_kernel:
+  emulated = _wgrad_launch is not _wgrad_launch_kernel or _wgrad_launch_boxed is not _wgrad_launch_boxed_kernel
+  if not use_kernel(x) and not emulated:
     xn = x.float().permute(0, 3, 1, 2)
     Ho, Wo = dy.shape[1:3]
     far_h, far_w = (Ho - 1) * stride + k - H - pad, (Wo - 1) * stride + k - W - pad
     xn = F.pad(xn, (pad, max(far_w, 0), pad, max(far_h, 0)))
     return torch.nn.grad.conv2d_weight(xn, (Co, Ci, k, k), dy.float().permute(0, 3, 1, 2), stride=stride)
+  if (boxed is None or boxed) and _boxed_ok(x, dy, stride):
+    return _conv2d_wgrad_boxed(x, dy, k, stride, pad)
   planes, Hg, Wg, taps = wgrad_plan(H, W, k, stride, pad)
   assert dy.shape[1:3] == (Hg, Wg), (dy.shape, Hg, Wg)
   ci8, co8 = _round_up(Ci, 8), _round_up(Co, 8)

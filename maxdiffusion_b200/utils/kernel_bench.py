@@ -338,11 +338,13 @@ def bench_conv(results):
     x = torch.randn((B, H, W, Ci), device="cuda", dtype=torch.bfloat16)
     dy = torch.randn((B, H // stride, W // stride, Co), device="cuda", dtype=torch.bfloat16)
     med, best = time_ms(lambda: OC.conv2d_wgrad(x, dy, 3, stride, 1), iters=5)
+    bordered, _ = time_ms(lambda: OC.conv2d_wgrad(x, dy, 3, stride, 1, boxed=False), iters=5)
     xn, dyn = x.permute(0, 3, 1, 2), dy.permute(0, 3, 1, 2)
     lib, _ = time_ms(lambda: torch.nn.grad.conv2d_weight(xn, (Co, Ci, 3, 3), dyn, stride=stride, padding=1), iters=5)
     fl = 2.0 * B * (H // stride) * (W // stride) * Co * Ci * 9
     results.append(dict(kernel=f"conv2d_wgrad_s{stride}", shape=[B, H, W, Ci, Co], ms=med, best_ms=best, tflops=fl / med / 1e9,
-                        frac=fl / med / 1e9 / tf_peak, of=tag, cudnn_ms=lib, note="includes the zero-border copies of x and dy and the split fold"))
+                        frac=fl / med / 1e9 / tf_peak, of=tag, cudnn_ms=lib, bordered_ms=bordered,
+                        note="boxes of output pixels read from the unpadded tensors, split fold included; bordered_ms = the flat form with its zero-border copies"))
     print(results[-1], flush=True)
   from maxdiffusion_b200.ops import functional as OF
 
@@ -377,6 +379,28 @@ def conv_profile_case():
   print("conv profile case done")
 
 
+def unet_profile_case():
+  """The UNet's kernels on one mid-size case each, for `ncu`: the convolution weight gradient (640 channels at 64^2,
+  batch 8), the forward convolution and the GEMM with bias + residual epilogue at a short contraction."""
+  from ..ops import conv as OC
+
+  x = torch.randn((8, 64, 64, 640), device="cuda", dtype=torch.bfloat16)
+  dy = torch.randn((8, 64, 64, 640), device="cuda", dtype=torch.bfloat16)
+  w = torch.randn((640, 640, 3, 3), device="cuda", dtype=torch.bfloat16) * 0.02
+  pk = OC.pack_conv2d(w, None)
+  for _ in range(2):
+    OC.conv2d_wgrad(x, dy, 3, 1)
+    OC.conv2d(x, pk)
+  a = torch.randn((32768, 640), device="cuda", dtype=torch.bfloat16)
+  b = torch.randn((5120, 640), device="cuda", dtype=torch.bfloat16) * 0.03
+  bias = torch.randn((5120,), device="cuda", dtype=torch.bfloat16)
+  res = torch.randn((32768, 5120), device="cuda", dtype=torch.bfloat16)
+  for _ in range(2):
+    K.gemm(a, b, bias=bias, epi="add_res", residual=res)
+  torch.cuda.synchronize()
+  print("unet profile case done")
+
+
 def profile_case():
   """One launch of each hot kernel on a mid-size case (inputs larger than L2, < 1 GB resident) for `ncu`."""
   M, N, Kd = 8192, 5120, 5120
@@ -404,6 +428,8 @@ def main(argv):
     return profile_case()
   if "conv_profile" in argv:
     return conv_profile_case()
+  if "unet_profile" in argv:
+    return unet_profile_case()
   which = [a for i, a in enumerate(argv) if not a.startswith("--") and (i == 0 or argv[i - 1] != "--json")] or ["gemm", "flash", "rowwise"]
   results = []
   if "gemm" in which:

@@ -169,18 +169,62 @@ def _emulate_wgrad(dyp, xp, offs, splits):
   return out
 
 
+def _emulate_wgrad_boxed(dy, x, taps, box, stride, splits):
+  """The boxed kernel's contract, literally: K block kb is a BW x BH box of output pixels of one image; dy is read at
+  the box, x at the box moved by the tap on its [B, H / s, s (row parity), W / s, s * C] view, out-of-range coordinates
+  of either tensor read as zeros; K blocks are cut into `splits` consecutive ranges."""
+  bw, bh = box
+  B, Ho, Wo, M = dy.shape
+  _, H, W, N = x.shape
+  s = stride
+  xv = x.float().reshape(B, H // s, s, W // s, s * N)
+  n_wb, n_hb = -(-Wo // bw), -(-Ho // bh)
+  kb_total = B * n_hb * n_wb
+  per = -(-kb_total // splits)
+  out = torch.zeros((len(taps), splits, M, N))
+  for t, (pw, dw, ph, dh) in enumerate(taps):
+    for kb in range(kb_total):
+      wb, rest = kb % n_wb, kb // n_wb
+      hb, img = rest % n_hb, rest // n_hb
+      a = torch.zeros((bh, bw, M))
+      b = torch.zeros((bh, bw, N))
+      for i in range(bh):
+        for j in range(bw):
+          h, w = hb * bh + i, wb * bw + j
+          if h < Ho and w < Wo:
+            a[i, j] = dy[img, h, w].float()
+          hx, wx = h + dh, w + dw
+          if 0 <= hx < H // s and 0 <= wx < W // s:
+            b[i, j] = xv[img, hx, ph, wx, pw * N:(pw + 1) * N]
+      out[t, kb // per] += a.reshape(-1, M).t() @ b.reshape(-1, N)
+  return out
+
+
 @pytest.mark.parametrize("stride,pad", [(1, 1), (2, 1), (2, 0)])
-def test_wgrad_description(monkeypatch, stride, pad):
+@pytest.mark.parametrize("boxed", [False, True])
+def test_wgrad_description(monkeypatch, stride, pad, boxed):
   monkeypatch.setattr(OC, "_wgrad_launch", _emulate_wgrad)
+  monkeypatch.setattr(OC, "_wgrad_launch_boxed", _emulate_wgrad_boxed)
   monkeypatch.setattr(OC, "use_kernel", lambda x: True)
   x = _rand((2, 6, 8, 16), 1).float().requires_grad_(False)
   w = _rand((8, 16, 3, 3), 2, 0.1).float().requires_grad_(True)
   y = OC.ref_conv2d(x, w, None, stride=stride, pad_top_left=pad)
   dy = _rand(tuple(y.shape), 3)
   (y * dy.float()).sum().backward()
-  got = OC.conv2d_wgrad(x.to(torch.bfloat16), dy, 3, stride, pad)
+  got = OC.conv2d_wgrad(x.to(torch.bfloat16), dy, 3, stride, pad, boxed=boxed)
   assert got.shape == w.shape
   assert (got - w.grad).abs().max() <= 2e-2 * w.grad.abs().max()
+
+
+def test_wgrad_box_and_split_choices():
+  assert OC.wgrad_box(128, 128) == (64, 1) and OC.wgrad_box(32, 32) == (32, 2) and OC.wgrad_box(16, 16) == (16, 4)
+  assert OC.wgrad_box(8, 8) == (8, 8) and OC.wgrad_box(20, 20)[0] in (32, 16, 8)
+  # 1280 -> 1280 channels at 32^2, batch 8: 450 work items leave the last of 4 rounds a quarter full; splitting K evens it out
+  assert OC.wgrad_splits(450, 128, 9 * 1280 * 1280) >= 1
+  assert OC.wgrad_splits(135, 512, 9 * 640 * 640) == 1  # 135 items already fill 148 SMs to 91 %
+  assert OC.wgrad_splits(27, 2048, 9 * 320 * 320) >= 4  # 27 items on 148 SMs: split K five ways
+  assert OC.wgrad_taps_boxed(3, 1, 1)[0] == (0, -1, 0, -1) and OC.wgrad_taps_boxed(3, 2, 1)[0] == (1, -1, 1, -1)
+  assert OC.wgrad_taps_boxed(3, 2, 0)[4] == (1, 0, 1, 0)
 
 
 def test_cpu_reference_paths_of_the_conv_ops():

@@ -159,8 +159,12 @@ def test_wan_vae_decode_on_the_conv_kernels_matches_the_pytorch_modules():
 
 
 @pytest.mark.parametrize("stride,pad", [(1, 1), (2, 1), (2, 0)])
-@pytest.mark.parametrize("B,H,W,Ci,Co", [(2, 12, 20, 64, 96), (1, 34, 18, 320, 320), (3, 16, 16, 8, 640)])
-def test_conv2d_wgrad_matches_autograd(B, H, W, Ci, Co, stride, pad):
+@pytest.mark.parametrize("B,H,W,Ci,Co", [(2, 12, 20, 64, 96), (1, 34, 18, 320, 320), (3, 16, 16, 8, 640), (8, 32, 32, 256, 128),
+                                        (2, 64, 64, 96, 64), (1, 8, 8, 72, 8)])
+@pytest.mark.parametrize("boxed", [True, False])
+def test_conv2d_wgrad_matches_autograd(B, H, W, Ci, Co, stride, pad, boxed):
+  """Both forms of the weight gradient: boxes of output pixels read from the unpadded tensors (zero fill outside the
+  image, parity coordinates for stride 2), and the bordered flat grid."""
   from maxdiffusion_b200.ops import conv as OC
 
   x = _rand((B, H, W, Ci), 1)
@@ -168,10 +172,10 @@ def test_conv2d_wgrad_matches_autograd(B, H, W, Ci, Co, stride, pad):
   y = OC.ref_conv2d(x, w, None, stride=stride, pad_top_left=pad)
   dy = _rand(tuple(y.shape), 3)
   (y * dy.float()).sum().backward()
-  got = OC.conv2d_wgrad(x, dy, 3, stride, pad)
+  got = OC.conv2d_wgrad(x, dy, 3, stride, pad, boxed=boxed)
   assert got.shape == w.shape
   _close(got, w.grad)
-  assert torch.equal(got, OC.conv2d_wgrad(x, dy, 3, stride, pad))  # fixed summation order
+  assert torch.equal(got, OC.conv2d_wgrad(x, dy, 3, stride, pad, boxed=boxed))  # fixed summation order
 
 
 @pytest.mark.parametrize("C,groups,HW", [(320, 32, (16, 24)), (64, 8, (9, 7)), (1280, 32, (8, 8)), (128, 32, (33, 5))])
