@@ -121,3 +121,24 @@ def test_dreambooth_class_images_are_generated_up_to_the_requested_count(tmp_pat
   assert tr.generate_class_images(fake_pipeline) == 5
   assert len(os.listdir(cdir)) == 5 and all(p[0][0] == "a photo of a dog" for p in prompts)
   assert tr.generate_class_images(fake_pipeline) == 0  # already there
+
+
+def test_graphed_objective_runs_eagerly_without_a_gpu_and_the_objective_split_is_the_loss():
+  """`loss(batch)` is `objective(**draw(batch))`; on a CPU the graphed wrapper is the eager forward + backward."""
+  from maxdiffusion_b200.trainers.graphed_step import GraphedObjective
+  from maxdiffusion_b200.trainers.stable_diffusion_trainer import StableDiffusionXLTrainer
+
+  c = _cfg("base_xl.yml", SD + ["unet_preset=tiny", "max_train_steps=2", "cuda_graph_train_step=true"], "/tmp/unused-output")
+  tr = StableDiffusionXLTrainer(c, mesh=create_device_mesh(c), device="cpu")
+  assert tr._graphed is None  # no CUDA device: the switch is ignored
+  batch = tr.synthetic_batch(0)
+  tr.gen.manual_seed(5)
+  a = tr.loss(batch)
+  tr.gen.manual_seed(5)
+  drawn = tr.draw(batch)
+  b = tr.objective(**drawn)
+  assert torch.equal(a, b)
+  g = GraphedObjective(tr.objective, list(tr.unet.parameters()), eager_calls=0)
+  got = g(drawn)
+  assert torch.allclose(got, a.detach()) and g.replays == 0
+  assert any(p.grad is not None and p.grad.abs().sum() > 0 for p in tr.unet.parameters())
