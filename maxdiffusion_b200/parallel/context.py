@@ -86,6 +86,22 @@ def _stackable(kg, vg, order):
   return rot, step
 
 
+def ulysses_head_chunks(heads: int, shards: int, chunks: int) -> list:
+  """Half-open head ranges for the chunked Ulysses exchange: every range is a whole number of `shards`-sized head
+  groups (each chunk is exchanged on its own, so it must split evenly over the shards); the groups are dealt out
+  floor(groups / chunks) per chunk and the last chunk takes the rest. One range when `chunks` <= 1.
+  (reference: `_ulysses_head_chunk_ranges`, src/maxdiffusion/models/attention_flax.py:483-520)"""
+  if chunks <= 1:
+    return [(0, heads)]
+  if heads % shards:
+    raise ValueError(f"Ulysses needs heads ({heads}) divisible by the shard count ({shards})")
+  groups = heads // shards
+  chunks = min(chunks, groups)
+  per = max(1, groups // chunks)
+  bounds = [min(i * per, groups) for i in range(chunks)] + [groups]
+  return [(a * shards, b * shards) for a, b in zip(bounds, bounds[1:]) if b > a]
+
+
 class _SegmentAttentionFn(torch.autograd.Function):
   """Kernel path of gather/ring attention: local q against the stacked K/V shards [n, B, S_loc, H, D]."""
 
@@ -203,10 +219,14 @@ class ContextParallel:
   """
 
   def __init__(self, mesh, strategy: str = "ring", peer_memory: bool = False, fixed_m: bool = False,
-               save_remote_kv: bool = True):
+               save_remote_kv: bool = True, ulysses_chunks: int = 1):
     self.mesh = mesh
     self.strategy = strategy
     self.peer_memory = peer_memory
+    # Ulysses: exchange and attend in this many head-group chunks (`ulysses_attention_chunks`), so that the exchange
+    # of one chunk can run beside the attention of another; forwards outside autograd over peer memory fold the
+    # exchanges into the producer / consumer kernels instead and ignore it
+    self.ulysses_chunks = max(1, int(ulysses_chunks))
     # ring / gather attention: keep every rank's K/V of a layer for its backward (fastest), or keep the own shard only
     # and fetch the others again in the backward (K/V memory per layer then falls with the context axis)
     self.save_remote_kv = save_remote_kv
@@ -422,6 +442,16 @@ class ContextParallel:
     per = q.shape[1]
     if self.strategy in ("gather", "ring"):
       return self._segment_attention(q, k, v, self.group, self.size, self.valid_lengths(self.size, per), scale)
+    if self.strategy in ("ulysses", "usp") and self.ulysses_chunks > 1:
+      U = self.size if self.strategy == "ulysses" else self.ulysses_size
+      ranges = ulysses_head_chunks(q.shape[2], U, self.ulysses_chunks)
+      if len(ranges) > 1:
+        chunks, self.ulysses_chunks = self.ulysses_chunks, 1
+        try:  # every chunk is a Ulysses attention of its own over fewer heads; the outputs concatenate along heads
+          outs = [self.self_attention(q[:, :, a:b], k[:, :, a:b], v[:, :, a:b], scale) for a, b in ranges]
+        finally:
+          self.ulysses_chunks = chunks
+        return torch.cat(outs, dim=2)
     if self.strategy == "ulysses":
       H = q.shape[2]
       if H % self.size != 0:

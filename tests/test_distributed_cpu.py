@@ -12,7 +12,7 @@ CFG = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), 
 TINY = '{"num_attention_heads": 4, "attention_head_dim": 32, "ffn_dim": 96, "num_layers": 2, "text_dim": 48, "freq_dim": 32}'
 
 
-def _make_trainer(attention, world, keep=0):
+def _make_trainer(attention, world, keep=0, extra=()):
   from maxdiffusion_b200 import pyconfig
   from maxdiffusion_b200.parallel.mesh import create_device_mesh
   from maxdiffusion_b200.trainers.wan_trainer import WanTrainer
@@ -21,14 +21,14 @@ def _make_trainer(attention, world, keep=0):
       ["t", CFG, "run_name=t", "height=64", "width=48", "num_frames=9", "dataset_type=synthetic", "wan_preset=tiny",
        f"wan_config_overrides={TINY}", "remat_policy=FULL", "warmup_steps_fraction=0.0", "log_config=false",
        "write_metrics=false", "learning_rate=1e-3", f"attention={attention}", f"per_device_batch_size={1.0 / world}",
-       "synthetic_override_text_dim=48", "max_sequence_length=16", "ulysses_shards=2", f"remat_keep_blocks={keep}"],
+       "synthetic_override_text_dim=48", "max_sequence_length=16", "ulysses_shards=2", f"remat_keep_blocks={keep}", *extra],
       unittest=True)
   return WanTrainer(config, mesh=create_device_mesh(config), device="cpu")
 
 
-def _train(rank, world, attention, steps, keep=0):
+def _train(rank, world, attention, steps, keep=0, extra=()):
   torch.manual_seed(0)
-  tr = _make_trainer(attention, world, keep)
+  tr = _make_trainer(attention, world, keep, extra)
   data = tr.load_dataset()
   losses = []
   for _ in range(steps):
@@ -270,3 +270,25 @@ def test_vae_decode_split_over_the_width_matches_the_whole_frame(world, chunk):
     assert shape == (1, 3, 9, 32, 48)
     assert err < 1e-4 * (1 + scale)
     assert exchanges > 20  # the strips really exchanged their edges
+
+
+def test_ulysses_head_chunk_ranges():
+  from maxdiffusion_b200.parallel.context import ulysses_head_chunks
+
+  assert ulysses_head_chunks(40, 8, 1) == [(0, 40)]
+  assert ulysses_head_chunks(40, 8, 2) == [(0, 16), (16, 40)]          # 5 groups of 8 heads: 2 + 3
+  assert ulysses_head_chunks(40, 4, 5) == [(0, 8), (8, 16), (16, 24), (24, 32), (32, 40)]
+  assert ulysses_head_chunks(8, 4, 16) == [(0, 4), (4, 8)]             # never more chunks than groups
+  with pytest.raises(ValueError):
+    ulysses_head_chunks(10, 4, 2)
+
+
+def test_chunked_ulysses_training_matches_single_process():
+  """`ulysses_attention_chunks=2`: every head-group chunk is exchanged and attended on its own (forward and backward);
+  the step must equal the unchunked single-process one."""
+  ref_losses, ref_digest, ref_gn = _train(0, 1, "flash", 2)
+  for losses, digest, gn in run_ranks(_train, 2, "ulysses", 2, 0, ("ulysses_attention_chunks=2",)):
+    assert losses == pytest.approx(ref_losses, rel=2e-4, abs=1e-5)
+    assert gn == pytest.approx(ref_gn, rel=2e-3)
+    for k, v in ref_digest.items():
+      assert digest[k] == pytest.approx(v, rel=1e-4, abs=1e-4), k
