@@ -148,3 +148,32 @@ def test_hub_utils_local(tmp_path):
   with pytest.raises(FileNotFoundError):
     resolve_model_path("org/missing", cache_dir=str(tmp_path / "hub"))
   assert os.path.exists(populate_model_card(str(tmp_path / "card"), "demo", "org/name", ["lora"]))
+
+
+def test_custom_pipeline_files_are_loaded_from_a_local_folder(tmp_path):
+  """A pipeline shipped as Python files next to a checkpoint: the file and its relative imports are copied into the
+  modules cache and imported from there; an edited file becomes a new module; missing packages are named."""
+  import pytest
+
+  from maxdiffusion_b200.utils import dynamic_modules_utils as DM
+
+  folder = tmp_path / "my-pipeline"
+  folder.mkdir()
+  (folder / "helpers.py").write_text("def double(x):\n  return 2 * x\n")
+  (folder / "pipeline.py").write_text(
+      "from .helpers import double\n\nclass MyPipeline:\n  @classmethod\n  def from_config(cls, config):\n    return cls()\n"
+      "  def __call__(self, x):\n    return double(x)\n\nclass NotAPipeline:\n  pass\n")
+  cache = str(tmp_path / "cache")
+  assert DM.get_relative_imports(str(folder / "pipeline.py")) == ["helpers"]
+  cls = DM.get_class_from_dynamic_module(str(folder), "pipeline.py", cache_root=cache)
+  assert cls.__name__ == "MyPipeline" and cls()(21) == 42
+  assert DM.get_class_from_dynamic_module(str(folder), "pipeline.py", "NotAPipeline", cache_root=cache).__name__ == "NotAPipeline"
+  first = DM.get_cached_module_file(str(folder), "pipeline.py", cache)
+  (folder / "helpers.py").write_text("def double(x):\n  return 3 * x\n")
+  second = DM.get_cached_module_file(str(folder), "pipeline.py", cache)
+  assert first != second and DM.get_class_from_dynamic_module(str(folder), "pipeline.py", cache_root=cache)()(1) == 3
+  (folder / "broken.py").write_text("import a_package_that_does_not_exist_anywhere\n")
+  with pytest.raises(ImportError, match="a_package_that_does_not_exist_anywhere"):
+    DM.get_cached_module_file(str(folder), "broken.py", cache)
+  with pytest.raises(FileNotFoundError):
+    DM.get_cached_module_file(str(folder), "absent.py", cache)
