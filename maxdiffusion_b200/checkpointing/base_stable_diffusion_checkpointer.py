@@ -72,6 +72,15 @@ class BaseStableDiffusionCheckpointer:
     max_logging.log(f"restored Stable Diffusion training state from step {step}")
     return step
 
+  def restore_iterator(self, data_iterator) -> bool:
+    """Puts a data source that can save its position (`get_state` / `set_state`: grain) back where the latest
+    checkpoint left it (item `iter`)."""
+    step = self.manager.latest_step() if self.manager is not None else None
+    if step is None or not hasattr(data_iterator, "set_state") or not self.manager.has_item(step, "iter"):
+      return False
+    data_iterator.set_state(self.manager.restore_json(step, "iter"))
+    return True
+
   def load_pipeline(self, pipeline_cls, device=None):
     step = self.manager.latest_step() if self.manager is not None else None
     if self.config.get("random_init", False):

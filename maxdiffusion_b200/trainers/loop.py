@@ -96,6 +96,10 @@ def run_training_loop(trainer, data, checkpointer=None, evaluate: Optional[Calla
       trainer.step = int(restored)
   if callable(data) and not hasattr(data, "__next__"):
     data = iter(data())
+  # sources that can save their position (grain) continue where the checkpoint left them
+  source = getattr(data, "source", data)
+  if checkpointer is not None and hasattr(source, "set_state") and hasattr(checkpointer, "restore_iterator"):
+    checkpointer.restore_iterator(source)
   writer = MetricsWriter(config, trainer.mesh.rank)
   monitor = _health_monitor(config, trainer.mesh)
   step_barrier = bool(config.get("health_step_barrier", True))
@@ -120,9 +124,9 @@ def run_training_loop(trainer, data, checkpointer=None, evaluate: Optional[Calla
       if evaluate is not None and eval_every > 0 and trainer.step % eval_every == 0:
         writer.write(trainer.step, {f"eval/{k}": float(v) for k, v in evaluate(trainer.step).items()})
       if checkpointer is not None and every > 0 and trainer.step % every == 0:
-        _save(checkpointer, trainer)
+        _save(checkpointer, trainer, source)
     if checkpointer is not None and config.get("save_final_checkpoint", False) and (every <= 0 or trainer.step % every != 0):
-      _save(checkpointer, trainer)
+      _save(checkpointer, trainer, source)
   finally:
     writer.close()
     if monitor is not None:
@@ -133,8 +137,13 @@ def run_training_loop(trainer, data, checkpointer=None, evaluate: Optional[Calla
   return trainer
 
 
-def _save(checkpointer, trainer) -> None:
+def _save(checkpointer, trainer, source=None) -> None:
   _lib.raise_on_device_status_if_loaded()
-  checkpointer.save(trainer.step, trainer)
+  if source is not None and hasattr(source, "get_state"):
+    # note: the loop prefetches one batch, so the saved position is one batch ahead of the step; a resumed run skips
+    # that batch instead of seeing it twice
+    checkpointer.save(trainer.step, trainer, data_iterator=source)
+  else:
+    checkpointer.save(trainer.step, trainer)
   if dist.is_available() and dist.is_initialized() and dist.get_world_size() > 1:
     dist.barrier()  # saving is rank-asymmetric host work: start the next step together

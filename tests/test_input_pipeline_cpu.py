@@ -1,4 +1,6 @@
 """TFRecord codec (framing + Example + TensorProto), iterators, retry loader, image processor."""
+import os
+
 import numpy as np
 import pytest
 import torch
@@ -61,3 +63,105 @@ def test_image_and_video_processor():
   v = VideoProcessor().preprocess_video([img] * 3, 32, 48)
   assert v.shape == (1, 3, 3, 32, 48)
   assert VideoProcessor().postprocess_video(v).shape == (1, 3, 32, 48, 3)
+
+
+def test_hf_dataset_iterator_shards_shuffles_and_preprocesses(monkeypatch):
+  """`dataset_type=hf` against a stand-in for the `datasets` package: the split is sharded over the data ranks, rows wrap
+  around with a reshuffle, images come out normalised [-1, 1] at the configured resolution, captions as text."""
+  import sys
+  import types
+
+  import numpy as np
+  from PIL import Image
+
+  from maxdiffusion_b200 import pyconfig
+  from maxdiffusion_b200.input_pipeline.input_pipeline_interface import HFDatasetIterator
+
+  class FakeSplit:
+    def __init__(self, rows):
+      self.rows = rows
+
+    def __len__(self):
+      return len(self.rows)
+
+    def __getitem__(self, i):
+      return self.rows[i]
+
+    def shard(self, n, i):
+      return FakeSplit(self.rows[i::n])
+
+  calls = {}
+
+  def load_dataset(name, **kw):
+    calls["args"] = (name, kw)
+    rows = [{"image": Image.fromarray(np.full((40, 56, 3), 10 * j, dtype=np.uint8)), "text": f"caption {j}"} for j in range(6)]
+    return FakeSplit(rows)
+
+  monkeypatch.setitem(sys.modules, "datasets", types.SimpleNamespace(load_dataset=load_dataset))
+  cfg_dir = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "maxdiffusion_b200", "configs")
+  c = pyconfig.initialize(["t", os.path.join(cfg_dir, "base15.yml"), "run_name=t", "dataset_type=hf", "dataset_name=some/set",
+                           "resolution=32", "enable_data_shuffling=false", "log_config=false"], unittest=True)
+  it = HFDatasetIterator(c, batch_size=2, shard_index=1, num_shards=2)
+  assert calls["args"][0] == "some/set" and len(it.ds) == 3
+  b1, b2 = next(it), next(it)
+  assert b1["pixel_values"].shape == (2, 3, 32, 32) and -1.0 <= b1["pixel_values"].min() and b1["pixel_values"].max() <= 1.0
+  assert b1["captions"] == ["caption 1", "caption 3"] and b2["captions"] == ["caption 5", "caption 1"]  # wraps around
+
+
+def test_grain_iterator_parses_records_and_saves_its_position(monkeypatch, tmp_path):
+  """`dataset_type=grain` against a stand-in for `grain.python`: records are `tf.train.Example` bytes parsed by this
+  repository's reader, batches are tensors, and the position round-trips through get_state / set_state."""
+  import sys
+  import types
+
+  import numpy as np
+
+  from maxdiffusion_b200.input_pipeline import _grain, tfrecord
+
+  recs = [tfrecord.make_example({"latents": [tfrecord.serialize_tensor(np.full((2, 3), float(i), np.float32))],
+                                      "encoder_hidden_states": [tfrecord.serialize_tensor(np.full((4,), float(-i), np.float32))]})
+          for i in range(8)]
+
+  class MapTransform:
+    pass
+
+  class Batch:
+    def __init__(self, n, drop_remainder=True):
+      self.n = n
+
+  class DataLoader:
+    def __init__(self, data_source, sampler, operations, worker_count):
+      self.src, self.ops = data_source, operations
+
+    def __iter__(self):
+      loader = self
+
+      class It:
+        pos = 0
+
+        def __next__(self):
+          parse, batch = loader.ops
+          rows = [parse.map(loader.src[(self.pos + j) % len(loader.src)]) for j in range(batch.n)]
+          self.pos += batch.n
+          return {k: np.stack([r[k] for r in rows]) for k in rows[0]}
+
+        def get_state(self):
+          return {"pos": self.pos}
+
+        def set_state(self, s):
+          self.pos = s["pos"]
+
+      return It()
+
+  fake = types.SimpleNamespace(ArrayRecordDataSource=lambda files: recs, MapTransform=MapTransform, Batch=Batch, DataLoader=DataLoader,
+                               IndexSampler=lambda *a, **k: None, ShardOptions=lambda *a, **k: None)
+  monkeypatch.setitem(sys.modules, "grain", types.SimpleNamespace(python=fake))
+  monkeypatch.setitem(sys.modules, "grain.python", fake)
+  cfg = types.SimpleNamespace(train_data_dir=str(tmp_path), seed=0, get=lambda k, d=None: d)
+  it = _grain.make_grain_iterator(cfg, batch_size=2, shard_index=0, num_shards=1)
+  b = next(it)
+  assert b["latents"].shape == (2, 2, 3) and float(b["latents"][1, 0, 0]) == 1.0 and float(b["encoder_hidden_states"][1, 0]) == -1.0
+  state = it.get_state()
+  second = next(it)
+  it.set_state(state)
+  assert torch.equal(next(it)["latents"], second["latents"])
