@@ -442,6 +442,16 @@ class ContextParallel:
     per = q.shape[1]
     if self.strategy in ("gather", "ring"):
       return self._segment_attention(q, k, v, self.group, self.size, self.valid_lengths(self.size, per), scale)
+    if self.strategy in ("ulysses", "usp") and q.shape[0] > 1:
+      # CFG fold: every (batch, head) pair is an attention problem of its own, so a batch that makes the head count
+      # divisible by the Ulysses shards is folded into the head axis around the exchange (40 heads over 8 shards
+      # work with the CFG batch of 2; reference: src/maxdiffusion/models/attention_flax.py:995-1020)
+      U = self.size if self.strategy == "ulysses" else self.ulysses_size
+      B, S, H, D = q.shape
+      if H % U != 0 and (B * H) % U == 0:
+        fold = lambda t: t.permute(1, 0, 2, 3).reshape(1, t.shape[1], B * H, D)
+        o = self.self_attention(fold(q), fold(k), fold(v), scale)
+        return o.reshape(S, B, H, D).permute(1, 0, 2, 3)
     if self.strategy in ("ulysses", "usp") and self.ulysses_chunks > 1:
       U = self.size if self.strategy == "ulysses" else self.ulysses_size
       ranges = ulysses_head_chunks(q.shape[2], U, self.ulysses_chunks)

@@ -292,3 +292,24 @@ def test_chunked_ulysses_training_matches_single_process():
     assert gn == pytest.approx(ref_gn, rel=2e-3)
     for k, v in ref_digest.items():
       assert digest[k] == pytest.approx(v, rel=1e-4, abs=1e-4), k
+
+
+def _cfg_fold(rank, world):
+  from maxdiffusion_b200.ops import functional as OF
+  from maxdiffusion_b200.parallel.context import ContextParallel
+  from maxdiffusion_b200.parallel.mesh import create_device_mesh
+
+  mesh = create_device_mesh(shape={"data": 1, "fsdp": 1, "context": world, "tensor": 1})
+  ctx = ContextParallel(mesh, "ulysses")
+  g = torch.Generator().manual_seed(0)
+  B, S, H, D = 2, 8 * world, 3, 16  # 3 heads do not split over 2 ranks; 2 x 3 do
+  q, k, v = (torch.randn((B, S, H, D), generator=g) for _ in range(3))
+  want = OF.attention(q, k, v)
+  local = lambda t: ctx.shard_sequence(t, dim=1)
+  got = ctx.self_attention(local(q), local(k), local(v))
+  return float((got - local(want)).abs().max())
+
+
+def test_cfg_batch_folds_into_heads_when_the_heads_alone_do_not_split():
+  for err in run_ranks(_cfg_fold, 2):
+    assert err < 1e-5
