@@ -349,7 +349,7 @@ class WanPipeline:
     else:
       z = z.to(next(self.vae.parameters()).dtype)
     chunk = int(self.config.get("vae_decode_chunk", 1))
-    if self.vae_spatial is not None and z.is_cuda and z.dtype == torch.bfloat16:
+    if self.vae_spatial is not None and z.is_cuda and z.dtype == torch.bfloat16 and hasattr(self.vae, "channels_last_decoder"):
       video = self.vae.channels_last_decoder().decode(z, chunk, spatial=self.vae_spatial)
       _lib.raise_on_device_status_if_loaded()  # the halo exchanges waited (bounded) on the neighbours
       return video
