@@ -242,8 +242,19 @@ class AutoencoderKLWan2p2(nn.Module):
 
   @torch.no_grad()
   def decode(self, z, chunk: int = 1):
+    if z.is_cuda and z.dtype == torch.bfloat16 and self.cfg.z_dim % 16 == 0:
+      # CUDA bf16 latents: channels-last on the implicit-GEMM convolution kernels (same modules and parameters)
+      return self.channels_last_decoder().decode(z, chunk)
     out = self._run(self.decoder, self.post_quant_conv(z), chunk)
     return unpatchify(out, self.cfg.patch_size).clamp(-1.0, 1.0)
+
+  def channels_last_decoder(self):
+    """The kernel path of `decode` (`vae_channels_last.ChannelsLastDecoder`, created on first use)."""
+    if getattr(self, "_cl_decoder", None) is None:
+      from .vae_channels_last import ChannelsLastDecoder
+
+      object.__setattr__(self, "_cl_decoder", ChannelsLastDecoder(self))
+    return self._cl_decoder
 
   def encode_full(self, x):
     return DiagonalGaussian(self.quant_conv(self.encoder(patchify(x, self.cfg.patch_size), None, True)))

@@ -177,8 +177,23 @@ class ChannelsLastDecoder:
       OC.conv3d_causal(x, halves[j], hist=past, out=out[:, j::2])
     return out
 
+  @staticmethod
+  def dup_up(sc, x, first_chunk: bool):
+    """`WanDupUp3D` of the 2.2 VAE, channels-last: every input channel is repeated, and the repeated channels are
+    dealt out over a (time factor, 2, 2) block of output positions -- a parameter-free shortcut around an up block
+    (reference: src/maxdiffusion/models/wan/autoencoder_kl_wan.py, `DupUp3D`). x [B, T, H, W, C] ->
+    [B, T ft, 2H, 2W, cout]; the first chunk drops the frames in front of its only real one."""
+    B, T, H, W, C = x.shape
+    ft, fs, co = sc.ft, sc.fs, sc.cout
+    idx = torch.arange(co * ft * fs * fs, device=x.device) // sc.repeats
+    y = x[..., idx].reshape(B, T, H, W, co, ft, fs, fs).permute(0, 1, 5, 2, 6, 3, 7, 4)  # B, T, ft, H, fs, W, fs, co
+    y = y.reshape(B, T * ft, H * fs, W * fs, co)
+    return y[:, ft - 1:] if first_chunk else y
+
   # ---- decoder ---------------------------------------------------------------------------------
   def decoder(self, x, hist: Optional[_Hist], first_chunk: bool):
+    from .autoencoder_kl_wan import WanResample
+
     d = self.vae.decoder
     x = self.conv3(d.conv_in, x, hist)
     mid = d.mid_block
@@ -186,6 +201,13 @@ class ChannelsLastDecoder:
     x = self.attention(mid.attentions[0], x)
     x = self.res_block(mid.resnets[1], x, hist)
     for up in d.up_blocks:
+      if hasattr(up, "avg_shortcut"):
+        # Wan 2.2: residual blocks and the resampler in one list, plus a parameter-free shortcut around the block
+        h = x
+        for layer in up.resnets:
+          h = self.resample(layer, h, hist, first_chunk) if isinstance(layer, WanResample) else self.res_block(layer, h, hist)
+        x = h + self.dup_up(up.avg_shortcut, x, first_chunk or hist is None) if up.avg_shortcut is not None else h
+        continue
       for r in up.resnets:
         x = self.res_block(r, x, hist)
       if up.upsamplers is not None:
@@ -226,4 +248,9 @@ class ChannelsLastDecoder:
         start += n
         first = False
       out = torch.cat(outs, dim=1)
+    p = int(getattr(vae.cfg, "patch_size", 1))
+    if p > 1:
+      # Wan 2.2 folds a p x p pixel patch into the channels: channel c p^2 + r p + q is pixel (q, r) of the patch
+      B, T, H, W, _ = out.shape
+      out = out[..., :3 * p * p].reshape(B, T, H, W, 3, p, p).permute(0, 1, 2, 6, 3, 5, 4).reshape(B, T, H * p, W * p, 3)
     return out.clamp_(-1.0, 1.0).permute(0, 4, 1, 2, 3)

@@ -272,3 +272,23 @@ def test_halo_columns_are_read_and_produce_no_output(W0, W1):
   whole2 = OC.upsample2x_conv2d(x2, pk2)
   got2 = OC.upsample2x_conv2d(pad(x2)[:, :, W0:W1 + 2].contiguous(), pk2, halo=1)
   assert torch.equal(got2, whole2[:, :, 2 * W0:2 * W1])
+
+
+def test_wan_2p2_vae_decode_on_the_conv_kernels_matches_the_pytorch_modules():
+  """The Wan 2.2 VAE (resampler inside the up block, channel-duplicating shortcut, 2 x 2 pixel patches) on the
+  channels-last kernel path against its fp32 PyTorch modules."""
+  from maxdiffusion_b200.models.wan.autoencoder_kl_wan_2p2 import AutoencoderKLWan2p2, WanVAE2p2Config
+
+  torch.manual_seed(0)
+  cfg = WanVAE2p2Config(base_dim=32, base_dec_dim=32, z_dim=16, latents_mean=[0.0] * 16, latents_std=[1.0] * 16)
+  vae = AutoencoderKLWan2p2(cfg).cuda().eval()
+  for n, p in vae.named_parameters():
+    if p.dim() > 1:
+      torch.nn.init.normal_(p, std=(p[0].numel()) ** -0.5)
+  z = torch.randn(1, 16, 3, 4, 6, device="cuda")
+  with torch.no_grad():
+    want = vae.decode(z, chunk=1)                       # fp32 latents: the PyTorch path
+    got = vae.decode(z.to(torch.bfloat16), chunk=1)     # bf16 latents: the kernel path
+  assert got.shape == want.shape == (1, 3, 9, 64, 96)
+  err = (got.float() - want).abs()
+  assert err.max() < 0.08 and err.mean() < 0.01, (err.max().item(), err.mean().item())

@@ -155,3 +155,27 @@ def test_channels_last_decoder_orchestration_matches_the_ncdhw_path():
     assert (got2 - want).abs().max() < 1e-4 * (1 + want.abs().max())
     whole = cl.decode(z, whole_clip=True)
     assert (whole - vae.decode_full(z)).abs().max() < 1e-4 * (1 + want.abs().max())
+
+
+def test_channels_last_decoder_walks_the_wan_2p2_vae_like_the_ncdhw_path():
+  """Wan 2.2 VAE on the channels-last decoder: up blocks with the resampler inside the layer list, the parameter-free
+  channel-duplicating shortcut around every up block, and the 2 x 2 pixel patches unfolded at the end; fp32 on the CPU
+  against the NCDHW modules, chunked and whole-clip."""
+  from maxdiffusion_b200.models.wan.autoencoder_kl_wan_2p2 import AutoencoderKLWan2p2, WanVAE2p2Config
+  from maxdiffusion_b200.models.wan.vae_channels_last import ChannelsLastDecoder
+
+  torch.manual_seed(0)
+  cfg = WanVAE2p2Config(base_dim=8, base_dec_dim=8, z_dim=16, latents_mean=[0.0] * 16, latents_std=[1.0] * 16)
+  vae = AutoencoderKLWan2p2(cfg).eval()
+  for p in vae.parameters():
+    torch.nn.init.normal_(p, std=0.2)
+  z = torch.randn(1, 16, 3, 2, 3)
+  cl = ChannelsLastDecoder(vae)
+  with torch.no_grad():
+    want = vae.decode(z, chunk=1)
+    got = cl.decode(z, chunk=1)
+    assert got.shape == want.shape == (1, 3, 9, 32, 48)
+    tol = 1e-4 * (1 + want.abs().max())
+    assert (got - want).abs().max() < tol
+    assert (cl.decode(z, chunk=2) - want).abs().max() < tol
+    assert (cl.decode(z, whole_clip=True) - vae.decode_full(z)).abs().max() < tol
