@@ -20,9 +20,12 @@ from .tfrecord_shards import ShardedWriter, create_example
 def vae_encode(video: torch.Tensor, vae, generator=None) -> torch.Tensor:
   """[B,3,F,H,W] in [-1,1] -> normalised latents [B,z,F',H/8,W/8] sampled from the posterior."""
   p = next(vae.parameters())
+  # on a GPU bf16 frames select the encoder on this repository's convolution kernels
+  dtype = torch.bfloat16 if p.is_cuda and hasattr(vae, "channels_last_decoder") else p.dtype
   with torch.no_grad():
-    z = vae.encode(video.to(p.device, p.dtype)).sample(generator)
-    return vae.normalize_latents(z)
+    moments = vae.encode(video.to(p.device, dtype))
+    moments.mean, moments.logvar = moments.mean.float(), moments.logvar.float()
+    return vae.normalize_latents(moments.sample(generator))
 
 
 def _batches(ds, caption_column: str, video_column: str, batch_size: int) -> Iterable[Tuple[list, list]]:

@@ -355,6 +355,9 @@ class AutoencoderKLWan(nn.Module):
   @torch.no_grad()
   def encode(self, x, chunk: int = 4) -> DiagonalGaussian:
     """x: [B,3,T,H,W] in [-1,1], T = 1 + 4k. Frames go through in chunks (first frame alone) with cached history."""
+    if x.is_cuda and x.dtype == torch.bfloat16:
+      # CUDA bf16 frames: channels-last on the implicit-GEMM convolution kernels (same modules and parameters)
+      return DiagonalGaussian(self.channels_last_decoder().encode(x, chunk))
     self._reset()
     cache = FeatureCache()
     t = x.shape[2]

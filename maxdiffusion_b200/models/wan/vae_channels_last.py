@@ -214,6 +214,76 @@ class ChannelsLastDecoder:
         x = self.resample(up.upsamplers[0], x, hist, first_chunk)
     return self.conv3(d.conv_out, self.norm(d.norm_out, x, True, for_conv=True), hist, haloed=True)
 
+  # ---- encoder ---------------------------------------------------------------------------------
+  def downsample(self, rs, x, state: dict, chunked: bool, first_chunk: bool):
+    """`WanResample` in a down mode: 3x3 stride-2 convolution with the padding on the far side (`ZeroPad2d((0,1,0,1))`),
+    then for `downsample3d` the (3,1,1) time convolution with stride 2 over [last frame of the previous chunk | this
+    chunk] (reference: src/maxdiffusion/models/wan/autoencoder_kl_wan.py:245-389). The strided time convolution is the
+    causal one evaluated at every second frame: output j reads frames (2j-1, 2j, 2j+1) of the chunk, frame -1 being
+    the remembered one."""
+    B, T, H, W, C = x.shape
+    conv = rs.resample[1]
+    pk = self._pack(("down", id(conv)), (conv.weight, conv.bias),
+                    lambda: OC.pack_conv2d(conv.weight.detach(), conv.bias.detach(), stride=2, pad_top_left=0))
+    y = OC.conv2d(x.reshape(B * T, H, W, C), pk)
+    y = y.reshape(B, T, H // 2, W // 2, y.shape[-1])
+    if rs.mode != "downsample3d":
+      return y
+    m = rs.time_conv
+    tk = self._pack(("tdown", id(m)), (m.weight, m.bias), lambda: OC.pack_conv3d(m.weight.detach(), m.bias.detach()))
+    if chunked and first_chunk:
+      state[id(rs)] = y[:, -1:].clone()
+      return y
+    if chunked:
+      last, body = state[id(rs)], y
+      state[id(rs)] = y[:, -1:].clone()
+    else:
+      if T == 1:
+        return y
+      last, body = y[:, :1], y[:, 1:]
+    out = OC.conv3d_causal(body.contiguous(), tk, hist=torch.cat([last, last], dim=1).contiguous())[:, 1::2]
+    return out if chunked else torch.cat([y[:, :1], out], dim=1)
+
+  def encoder(self, x, hist: Optional[_Hist], state: dict, first_chunk: bool):
+    from .autoencoder_kl_wan import WanResample, WanResidualBlock
+
+    e = self.vae.encoder
+    x = self.conv3(e.conv_in, x, hist)
+    for blk in e.down_blocks:
+      if isinstance(blk, WanResample):
+        x = self.downsample(blk, x, state, hist is not None, first_chunk)
+      elif isinstance(blk, WanResidualBlock):
+        x = self.res_block(blk, x, hist)
+      else:
+        x = self.attention(blk, x)
+    mid = e.mid_block
+    x = self.res_block(mid.resnets[0], x, hist)
+    x = self.attention(mid.attentions[0], x)
+    x = self.res_block(mid.resnets[1], x, hist)
+    return self.conv3(e.conv_out, self.norm(e.norm_out, x, True), hist)
+
+  @torch.no_grad()
+  def encode(self, x: torch.Tensor, chunk: int = 4, whole_clip: bool = False) -> torch.Tensor:
+    """x [B, 3, T, H, W] in [-1, 1] (T = 1 + 4k) -> the moments [B, 2 z, T', H / 8, W / 8] that `DiagonalGaussian`
+    takes: the encoder on the convolution kernels, frames in chunks of `chunk` after the first one."""
+    vae = self.vae
+    x = x.permute(0, 2, 3, 4, 1).contiguous()
+    state: dict = {}
+    if whole_clip:
+      h = self.encoder(x, None, state, True)
+    else:
+      hist = _Hist()
+      outs, start, first, t = [], 0, True, x.shape[1]
+      while start < t:
+        n = 1 if first else min(chunk, t - start)
+        hist.begin_pass()
+        outs.append(self.encoder(x[:, start:start + n], hist, state, first))
+        start += n
+        first = False
+      h = torch.cat(outs, dim=1)
+    h = self.pointwise(vae.quant_conv.weight, vae.quant_conv.bias, h.contiguous())
+    return h.permute(0, 4, 1, 2, 3)
+
   @torch.no_grad()
   def decode(self, z: torch.Tensor, chunk: int = 1, whole_clip: bool = False, spatial=None) -> torch.Tensor:
     """z [B, 16, T', H', W'] (de-normalised latents, bf16, CUDA) -> video [B, 3, 1 + 4 (T' - 1), 8 H', 8 W'] in [-1, 1].

@@ -376,7 +376,9 @@ class _I2VMixin:
     video = torch.zeros((B, 3, num_frames, height, width), device=image.device, dtype=image.dtype)
     video[:, :, 0] = image
     vae_dtype = next(self.vae.parameters()).dtype
-    lat = self.vae.normalize_latents(self.vae.encode(video.to(vae_dtype)).mode())
+    if video.is_cuda and bool(self.config.get("vae_kernel_decode", True)) and hasattr(self.vae, "channels_last_decoder"):
+      vae_dtype = torch.bfloat16  # bf16 frames select the encoder on this repository's convolution kernels
+    lat = self.vae.normalize_latents(self.vae.encode(video.to(vae_dtype)).mode().float())
     tl = (num_frames - 1) // 4 + 1
     mask = torch.zeros((B, 4, tl, height // 8, width // 8), device=image.device, dtype=lat.dtype)
     mask[:, :, 0] = 1.0

@@ -292,3 +292,22 @@ def test_wan_2p2_vae_decode_on_the_conv_kernels_matches_the_pytorch_modules():
   assert got.shape == want.shape == (1, 3, 9, 64, 96)
   err = (got.float() - want).abs()
   assert err.max() < 0.08 and err.mean() < 0.01, (err.max().item(), err.mean().item())
+
+
+def test_wan_vae_encode_on_the_conv_kernels_matches_the_pytorch_modules():
+  """The channels-last encoder (far-side padded stride-2 convolutions, the strided time convolution read off the causal
+  one) against the fp32 PyTorch modules holding the same parameters."""
+  from maxdiffusion_b200.models.wan.autoencoder_kl_wan import AutoencoderKLWan, WanVAEConfig
+
+  torch.manual_seed(0)
+  vae = AutoencoderKLWan(WanVAEConfig(base_dim=32)).cuda().eval()
+  for n, p in vae.named_parameters():
+    if p.dim() > 1:
+      torch.nn.init.normal_(p, std=(p[0].numel()) ** -0.5)
+  x = torch.randn(1, 3, 9, 32, 48, device="cuda").clamp(-1, 1)
+  with torch.no_grad():
+    want = vae.encode(x, chunk=4).mean                       # fp32 frames: the PyTorch path
+    got = vae.encode(x.to(torch.bfloat16), chunk=4).mean     # bf16 frames: the kernel path
+  assert got.shape == want.shape == (1, 16, 3, 4, 6)
+  err = (got.float() - want).abs()
+  assert err.max() < 0.08 * (1 + want.abs().max()) and err.mean() < 0.01 * (1 + want.abs().mean()), (err.max().item(), err.mean().item())

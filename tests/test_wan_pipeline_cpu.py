@@ -179,3 +179,25 @@ def test_channels_last_decoder_walks_the_wan_2p2_vae_like_the_ncdhw_path():
     assert (got - want).abs().max() < tol
     assert (cl.decode(z, chunk=2) - want).abs().max() < tol
     assert (cl.decode(z, whole_clip=True) - vae.decode_full(z)).abs().max() < tol
+
+
+def test_channels_last_encoder_orchestration_matches_the_ncdhw_path():
+  """The encoder on the channels-last walk: stride-2 convolutions padded on the far side, the strided time convolution
+  as every second output of the causal one with the remembered frame as history, chunked (first frame alone, then
+  chunks of 4 or 8: the two strided time convolutions need a multiple of 4) and whole-clip; fp32 on the CPU against the NCDHW modules."""
+  from maxdiffusion_b200.models.wan.vae_channels_last import ChannelsLastDecoder
+
+  torch.manual_seed(0)
+  vae = AutoencoderKLWan(WanVAEConfig(base_dim=8)).eval()
+  for p in vae.parameters():
+    torch.nn.init.normal_(p, std=0.2)
+  x = torch.randn(1, 3, 9, 16, 24)
+  cl = ChannelsLastDecoder(vae)
+  with torch.no_grad():
+    want = vae.encode(x, chunk=4).mean
+    for chunk in (4, 8):
+      got = cl.encode(x, chunk=chunk).chunk(2, dim=1)[0]
+      assert got.shape == want.shape == (1, 16, 3, 2, 3)
+      assert (got - want).abs().max() < 1e-4 * (1 + want.abs().max())
+    whole = cl.encode(x, whole_clip=True).chunk(2, dim=1)[0]
+    assert (whole - vae.encode_full(x).mean).abs().max() < 1e-4 * (1 + want.abs().max())
