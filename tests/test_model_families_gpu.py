@@ -148,3 +148,28 @@ def test_cuda_graph_cache_captures_once_and_replays(tmp_path):
     assert len(step.known_signatures()) == 2  # recorded on disk for the next process
   finally:
     aot_cache.uninstall()
+
+
+def test_flux_bf16_matches_fp32_forward_and_trains():
+  """Flux at head width 128: the bf16 kernel path (modulations on the GEMM with fp32 output, fused q/k/v, gated
+  residual epilogues) against the fp32 CPU path; then one backward through the same model (the modulation takes its
+  differentiable form under autograd)."""
+  from maxdiffusion_b200.models.flux.transformer_flux import FluxConfig, FluxTransformer2DModel, prepare_latent_image_ids
+
+  torch.manual_seed(0)
+  cfg = FluxConfig(num_layers=1, num_single_layers=2, num_attention_heads=2, attention_head_dim=128, joint_attention_dim=64,
+                   pooled_projection_dim=32, axes_dims_rope=(16, 56, 56))
+  ref, gpu = _pair(FluxTransformer2DModel(cfg))
+  B, T = 2, 8
+  x, txt, pooled = torch.randn(B, 64, 64), torch.randn(B, T, 64), torch.randn(B, 32)
+  t, g = torch.tensor([0.25, 0.8]), torch.tensor([3.5, 2.0])
+  img_ids, txt_ids = prepare_latent_image_ids(8, 8), torch.zeros(T, 3)
+  with torch.no_grad():
+    want = ref(x, txt, pooled, t, img_ids, txt_ids, g)
+    got = gpu(x.cuda().bfloat16(), txt.cuda().bfloat16(), pooled.cuda().bfloat16(), t.cuda(), img_ids.cuda(), txt_ids.cuda(), g.cuda())
+  assert _rel(got, want) < 6e-2
+  out = gpu(x.cuda().bfloat16(), txt.cuda().bfloat16(), pooled.cuda().bfloat16(), t.cuda(), img_ids.cuda(), txt_ids.cuda(), g.cuda())
+  out.float().pow(2).mean().backward()
+  mod = gpu.transformer_blocks[0].norm1.weight.grad
+  assert mod is not None and torch.isfinite(mod.float()).all() and mod.float().abs().sum() > 0
+  _lib.raise_on_device_status()
