@@ -8,7 +8,8 @@
 // Either operand may be "MN-major" (stored transposed, i.e. A as [K,M] or B as [K,N]); this is what
 // lets dgrad (dX = dY * W) and wgrad (dW = dY^T * X) run on the same kernel without transposes.
 //
-// Roles:  warp 0 = TMA producer, warp 1 = TMEM owner + MMA issuer, warps 2..5 = epilogue.
+// Roles:  warp 0 = TMA producer, warp 1 = TMEM owner + MMA issuer, warps 2..5 and 6..9 = two epilogue groups, each
+// taking one column half of every tile (own staging slab, named barrier and TMA-store issuing thread).
 // Covers the reference's XLA:GPU / cuBLAS matmuls behind every Dense layer
 // (src/maxdiffusion/models/attention_flax.py:2471-2525, models/wan/transformers/transformer_wan.py:220-330)
 // together with the elementwise fusions XLA places after them (bias, GELU-tanh, gated residual).
@@ -20,7 +21,7 @@ namespace gemm {
 constexpr int BM = 128;
 constexpr int BK = 64;
 constexpr int A_BYTES = BM * BK * 2;  // 16 KiB
-constexpr int NUM_THREADS = 192;
+constexpr int NUM_THREADS = 320;  // warp 0 TMA, warp 1 MMA, warps 2..5 and 6..9: two epilogue groups (one column half each)
 constexpr int GROUP_M = 8;
 // The tile is 128 x BN with BN = 256 (the default) or 128 (on request). The narrower tile fills the waves of the
 // 148 persistent CTAs better at small M, but it moves a third more operand bytes per FLOP from L2 into shared
@@ -28,8 +29,8 @@ constexpr int GROUP_M = 8;
 // against 0.173 ms), so the launcher never picks it by itself: operand traffic, not wave fill, is the limit.
 __host__ __device__ constexpr int stages_for(int bn) { return bn == 256 ? 4 : 6; }                    // 4 x 48 KiB or 6 x 32 KiB
 __host__ __device__ constexpr int stage_bytes(int bn) { return A_BYTES + bn * BK * 2; }
-// Output staging of the epilogue: two 128-row x 128-byte slabs (64 bf16 or 32 fp32 columns each) in the 128-byte
-// swizzle, written by the epilogue warps and drained by TMA stores.
+// Output staging of the epilogue: one 128-row x 128-byte slab (64 bf16 or 32 fp32 columns) per epilogue group in the
+// 128-byte swizzle, written by the group's warps and drained by its TMA stores.
 constexpr int SLAB_BYTES = BM * 128;
 constexpr int STAGING_BYTES = 2 * SLAB_BYTES;
 constexpr int BIAS_BYTES = 256 * 4;  // the tile's bias columns as fp32
@@ -117,7 +118,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
     }
     for (int a = 0; a < 2; ++a) {
       mbar_init(&tmem_full[a], 1);
-      mbar_init(&tmem_empty[a], 128);
+      mbar_init(&tmem_empty[a], 256);  // both epilogue groups have read the accumulator
     }
     *abort_flag = 0;
     fence_mbar_init();
@@ -215,10 +216,15 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
     }
   } else {
     // ------------------------------ Epilogue ----------------------------------
+    // Two groups of four warps share a tile: group g takes the columns [g BN/2, (g + 1) BN/2). With short
+    // contractions (10-20 K blocks) a tile's epilogue lasts as long as its main loop; two groups halve it. Each group
+    // has its own staging slab, named barrier and store-issuing thread.
     const int quarter = warp & 3;  // TMEM lanes 32*quarter .. +31 are reachable from this warp
     const int row_in_tile = quarter * 32 + lane;
+    const int egroup = (warp - 2) >> 2;
+    const int group_thread = static_cast<int>(threadIdx.x) - 64 - egroup * 128;
+    const int col_begin = egroup * (BN / 2), col_end = col_begin + BN / 2;
     int it = 0;
-    int slab_count = 0;
     bool ok = true;
     for (int work = blockIdx.x; work < num_work && ok; work += gridDim.x, ++it) {
       int m_idx, n_idx;
@@ -236,7 +242,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
         // ---- staged epilogue: 128 bytes of every row per slab, swizzled, one TMA store per slab ----
         const bool f32 = p.out_f32 || p.splits > 1;
         const int slab_cols = f32 ? 32 : 64;
-        const bool leader = threadIdx.x == 64;  // first epilogue thread issues and tracks the stores
+        const bool leader = group_thread == 0;  // the group's first thread issues and tracks its stores
         const long long out_row0 = (p.splits > 1 ? static_cast<long long>(split) * p.partial_rows : 0) +
                                    static_cast<long long>(m_idx) * BM;
         const int sw = row_in_tile & 7;
@@ -247,16 +253,16 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
         const bool res_staged = res_epi && !f32;
         if (use_bias) {
           // the tile's bias columns once, as fp32 (the previous tile's readers passed its last slab barrier)
-          for (int c = static_cast<int>(threadIdx.x) - 64; c < BN; c += 128) {
+          for (int c = col_begin + group_thread; c < col_end; c += 128) {
             const int col = n_idx * BN + c;
             bias_s[c] = col < p.N ? __bfloat162float(p.bias[col]) : 0.0f;
           }
         }
 #pragma unroll 1
-        for (int c0 = 0; c0 < BN; c0 += slab_cols) {
+        for (int c0 = col_begin; c0 < col_end; c0 += slab_cols) {
           const int col0 = n_idx * BN + c0;
-          if (col0 >= p.N) break;  // uniform across the CTA
-          uint8_t* slab = staging + (slab_count & 1) * SLAB_BYTES;
+          if (col0 >= p.N) break;  // uniform across the group
+          uint8_t* slab = staging + egroup * SLAB_BYTES;
           uint4 rv[8];
           if (res_staged) {  // issued before the barrier: their latency overlaps the wait for the slab
 #pragma unroll
@@ -268,8 +274,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
                                                  : make_uint4(0u, 0u, 0u, 0u);
             }
           }
-          if (leader) tma_store_wait_read<1>();  // the store that read this slab two slabs ago is done with it
-          named_bar_sync(1, 128);
+          if (leader) tma_store_wait_read<0>();  // the group's previous store is done reading the slab
+          named_bar_sync(1 + egroup, 128);
           if (res_staged) {
 #pragma unroll
             for (int i = 0; i < 8; ++i) {
@@ -342,21 +348,20 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
             }
           }
           fence_proxy_async_smem();
-          named_bar_sync(1, 128);
+          named_bar_sync(1 + egroup, 128);
           if (leader) {
             tma_store_2d(&tmap_c, slab, col0, static_cast<int>(out_row0));
             tma_store_commit();
           }
-          ++slab_count;
         }
         tc_fence_before_sync();
         mbar_arrive(&tmem_empty[acc]);
         continue;
       }
 #pragma unroll 1
-      for (int c = 0; c < BN / 32; ++c) {
+      for (int c = egroup * (BN / 64); c < (egroup + 1) * (BN / 64); ++c) {
         const int col0 = n_idx * BN + c * 32;
-        if (col0 >= p.N) break;  // uniform across the CTA
+        if (col0 >= p.N) break;  // uniform across the group
         uint32_t r[32];
         tmem_ld_x32(taddr + c * 32, r);
         tmem_wait_ld();
@@ -429,7 +434,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
       tc_fence_before_sync();
       mbar_arrive(&tmem_empty[acc]);
     }
-    if (p.tma_store && threadIdx.x == 64) tma_store_wait_read<0>();  // shared memory stays valid until the stores have read it
+    if (p.tma_store && group_thread == 0) tma_store_wait_read<0>();  // shared memory stays valid until the stores have read it
   }
 
   tc_fence_before_sync();

@@ -185,7 +185,25 @@ class FluxSingleBlock(nn.Module):
     B, S, C = x.shape
     H = self.heads
     shift, scale, gate = _modulation(self.norm, temb, 3)
-    f = self.qkv_mlp(OF.layer_norm_mod(x, scale=scale, shift=shift))
+    h = OF.layer_norm_mod(x, scale=scale, shift=shift)
+    w = self.qkv_mlp.weight if type(self.qkv_mlp) is Linear else None
+    if (w is not None and not torch.is_grad_enabled() and h.is_cuda and h.dtype == torch.bfloat16 and w.dtype == torch.bfloat16
+        and not OF.library_mode() and C % 8 == 0 and self.hidden % 8 == 0):
+      # Inference: the fused projection as two products over row slices of its matrix, so that the MLP half gets its
+      # GELU in the GEMM epilogue and lands directly in the (attention | mlp) buffer the output projection reads --
+      # no separate GELU pass and no concatenation copy (together 3 % of a denoising step).
+      from ...ops import kernels as K
+
+      b = self.qkv_mlp.bias
+      h2 = h.reshape(B * S, C)
+      f = K.gemm(h2, w[:3 * C], bias=None if b is None else b[:3 * C].contiguous()).view(B, S, 3 * C)
+      cat = torch.empty((B, S, C + self.hidden), device=h.device, dtype=h.dtype)
+      K.gemm(h2, w[3 * C:], bias=None if b is None else b[3 * C:].contiguous(), epi="gelu_tanh", out=cat.view(B * S, -1)[:, C:])
+      q = OF.rms_norm_rope(f[..., :C], self.norm_q, *rope, heads=H, per_head=True)
+      k = OF.rms_norm_rope(f[..., C:2 * C], self.norm_k, *rope, heads=H, per_head=True)
+      cat[..., :C] = OF.attention(q, k, f[..., 2 * C:].unflatten(-1, (H, C // H))).reshape(B, S, C)
+      return _clip(project_gated_residual(self.proj_out, cat, x, gate))
+    f = self.qkv_mlp(h)
     q, k, v, mlp = f[..., :C], f[..., C:2 * C], f[..., 2 * C:3 * C], f[..., 3 * C:]
     q = OF.rms_norm_rope(q, self.norm_q, *rope, heads=H, per_head=True)
     k = OF.rms_norm_rope(k, self.norm_k, *rope, heads=H, per_head=True)
