@@ -153,6 +153,8 @@ def main() -> int:
   ap.add_argument("--width", type=int, default=832)
   ap.add_argument("--frames", type=int, default=81)
   ap.add_argument("--attention", default="tokamax_ring")
+  ap.add_argument("--ring-kv-transport", default=None, choices=["sm", "dma"],
+                  help="wan_train: how ring attention stages remote K/V (default: the configuration's `ring_kv_transport`)")
   ap.add_argument("--workload", default="wan_train", choices=["wan_train", "wan_infer", "flux_infer", "sdxl_train"])
   ap.add_argument("--resolution", type=int, default=1024)
   ap.add_argument("--batch", type=int, default=None)
@@ -198,7 +200,8 @@ def main() -> int:
        f"remat_keep_blocks={max(0, args.keep_blocks)}",
        f"wan_preset={args.preset}", "warmup_steps_fraction=0.0", "max_train_steps=1000000", "log_config=false",
        "write_metrics=false", "flow_shift=5.0",
-       f"peer_memory_transport={'false' if args.impl == 'library' else 'true'}"])
+       f"peer_memory_transport={'false' if args.impl == 'library' else 'true'}"]
+      + ([f"ring_kv_transport={args.ring_kv_transport}"] if args.ring_kv_transport else []))
   mesh = create_device_mesh(config)
   trainer = WanTrainer(config, mesh=mesh)
   data = trainer.load_dataset()
@@ -282,6 +285,7 @@ def main() -> int:
         "config": {"model": "Wan2.1-T2V-14B (40 layers, dim 5120, 40 heads, ffn 13824), random init" if official else args.preset,
                    "global_batch": 1, "seq_len": seq_len,
                    "parallelism": f"cp{n} ring x fsdp over the same {n} ranks" if n > 1 else "single GPU",
+                   "ring_kv_transport": str(config.get("ring_kv_transport", "sm")) if n > 1 else None,
                    "video": f"{args.height}x{args.width}x{args.frames}",
                    "remat": f"per block ({args.remat}); the last {keep} of {len(trainer.model.blocks)} blocks keep their activations "
                             f"(peak {torch.cuda.max_memory_reserved() / 2**30:.0f} GiB reserved)",

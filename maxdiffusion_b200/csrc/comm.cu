@@ -446,6 +446,26 @@ extern "C" int mdb_memcpy_async(void* dst, const void* src, long long nbytes, vo
                                           static_cast<cudaStream_t>(stream)));
 }
 
+// 32-bit store into device memory, issued by the stream itself (a stream memory operation: no kernel, no SM). It runs
+// after every earlier operation of the stream, behind a system-wide fence, so a kernel of another stream that polls the
+// word with an acquire load sees the copies that precede it in this stream.
+extern "C" int mdb_stream_write_value32(void* addr, unsigned int value, void* stream) {
+  typedef CUresult (*WriteFn)(CUstream, CUdeviceptr, cuuint32_t, unsigned int);
+  static WriteFn fn = nullptr;
+  if (fn == nullptr) {
+    void* f = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuStreamWriteValue32", &f, cudaEnableDefault, &qres) != cudaSuccess ||
+        qres != cudaDriverEntryPointSuccess || f == nullptr) {
+      return 3407;
+    }
+    fn = reinterpret_cast<WriteFn>(f);
+  }
+  if (addr == nullptr || (reinterpret_cast<uintptr_t>(addr) & 3u) != 0) return 3408;
+  const CUresult r = fn(static_cast<CUstream>(stream), reinterpret_cast<CUdeviceptr>(addr), value, 0u);
+  return r == CUDA_SUCCESS ? 0 : 3409;
+}
+
 // buf_ptrs / flag_ptrs: `world` device addresses (this rank's own included). n <= cap floats; epoch must grow by
 // one per call on every rank of the group.
 extern "C" int mdb_small_allreduce(const float* in, float* out, int n, int op, const unsigned long long* buf_ptrs,

@@ -219,8 +219,11 @@ class ContextParallel:
   """
 
   def __init__(self, mesh, strategy: str = "ring", peer_memory: bool = False, fixed_m: bool = False,
-               save_remote_kv: bool = True, ulysses_chunks: int = 1):
+               save_remote_kv: bool = True, ulysses_chunks: int = 1, kv_transport: str = "sm"):
     self.mesh = mesh
+    # ring K/V over peer memory: "sm" stages the remote shards with copy CTAs of the attention launch itself, "dma" with
+    # copy-engine copies and stream memory operations on a side stream (every CTA of the launch then computes)
+    self.kv_transport = kv_transport
     self.strategy = strategy
     self.peer_memory = peer_memory
     # Ulysses: exchange and attend in this many head-group chunks (`ulysses_attention_chunks`), so that the exchange
@@ -266,7 +269,7 @@ class ContextParallel:
       old = ex
       # a larger tensor arrived: the new exchange continues the group's epochs with new buffers; the old buffers go
       # only after the constructor's device synchronisation + barrier, when no peer can still be reading them
-      ex = symm.PeerKVExchange(self._peers[key], k.numel(), k.dtype)
+      ex = symm.PeerKVExchange(self._peers[key], k.numel(), k.dtype, transport=self.kv_transport)
       if old is not None:
         old.release()
       self._exchanges[key] = ex

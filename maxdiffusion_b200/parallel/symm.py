@@ -201,6 +201,14 @@ def memcpy_async(dst_ptr: int, src_ptr: int, nbytes: int, stream=None) -> None:
   _lib.check(rc, "mdb_memcpy_async")
 
 
+def stream_write_value32(addr: int, value: int, stream=None) -> None:
+  """Stream memory operation: the stream stores `value` at device address `addr` once its earlier work is done; no
+  kernel is launched, so the store lands even while a persistent kernel holds every SM."""
+  rc = _lib.lib().mdb_stream_write_value32(ctypes.c_void_p(addr), int(value) & 0xffffffff,
+                                           stream if stream is not None else _lib.stream())
+  _lib.check(rc, "mdb_stream_write_value32")
+
+
 class PeerKVExchange:
   """Ring-schedule K/V exchange for context-parallel attention over peer memory.
 
@@ -215,12 +223,16 @@ class PeerKVExchange:
   """
 
   def __init__(self, peer: "PeerGroup", max_numel_per_tensor: int, dtype=torch.bfloat16, copy_ctas: int = 12,
-               head_groups: int = 0):
+               head_groups: int = 0, transport: str = "sm"):
+    if transport not in ("sm", "dma"):
+      raise ValueError(f"ring K/V transport must be 'sm' (copy CTAs of the attention launch) or 'dma' (copy engines), got {transport!r}")
+    self.transport = transport
     self.peer = peer
     self.n, self.rank = peer.world, peer.rank
     self.numel = max_numel_per_tensor
     self.copy_ctas = copy_ctas
     self.head_groups = head_groups  # 0: the launcher picks one head group per round of work items; 1: whole segments
+    self._dma_stream = None
     self.slots, self.slot_ptrs = [], []
     for _ in range(2):
       t, ptrs, _h = peer.alloc(2 * max_numel_per_tensor, dtype)
@@ -259,7 +271,11 @@ class PeerKVExchange:
   def plan(self, k: torch.Tensor, v: torch.Tensor):
     """Returns (kg, vg, flags, epoch, plan) for a fused launch: staging tensors [n, *k.shape] in consumption order,
     the int32 ready flags (one row of `COPY_FLAG_STRIDE` head-group flags per segment; row 0, the own shard, is already
-    raised) and the copy plan for `kernels.flash_fwd`."""
+    raised) and the copy plan for `kernels.flash_fwd`. With the copy-engine transport the plan is None and there is one
+    flag per segment (`stage_dma`)."""
+    if self.transport == "dma":
+      kg, vg, flags, e = self.stage_dma(k, v)
+      return kg, vg, flags, e, None, flags
     kg, vg, e, slot, nbytes = self.publish(k, v)
     fs = _lib.COPY_FLAG_STRIDE
     state = torch.zeros(self.n * fs + _lib.COPY_NUM_COUNTERS + 7, dtype=torch.int32, device=k.device)  # [flags | counters]
@@ -283,6 +299,35 @@ class PeerKVExchange:
     for r in range(self.n):
       plan.ack[r] = self.peer.flag_ptrs[r] + 4 * (FLAG_KV_ACK * self.n + self.rank)
     return kg, vg, flags, e, plan, state
+
+  def stage_dma(self, k: torch.Tensor, v: torch.Tensor):
+    """Copy-engine transport. Returns (kg, vg, flags, epoch): staging tensors in consumption order and one int32 ready
+    flag per segment (flag 0, the own shard, already raised) for `kernels.flash_fwd(..., seg_flags=, flag_target=)`.
+
+    Once every owner has published, a side stream pulls the remote shards in ring order with copy-engine copies and,
+    after each segment's pair of copies, stores the epoch into that segment's flag with a stream memory operation.
+    Neither the copies nor the flag stores need an SM, so every CTA of the attention launch computes, and the only
+    thing its bounded flag waits depend on is the DMA engines. The acknowledgement to the owners follows the last
+    copy on the side stream."""
+    kg, vg, e, slot, nbytes = self.publish(k, v)
+    flags = torch.zeros(self.n, dtype=torch.int32, device=k.device)
+    flags[:1].fill_(e)
+    self.peer.wait(FLAG_KV_READY, e)
+    main = torch.cuda.current_stream()
+    if self._dma_stream is None:
+      self._dma_stream = torch.cuda.Stream(device=k.device)
+    side = self._dma_stream
+    side.wait_stream(main)
+    sp = ctypes.c_void_p(side.cuda_stream)
+    for i, src in enumerate(self.order()[1:]):
+      base = self.slot_ptrs[slot][src]
+      memcpy_async(kg[i + 1].data_ptr(), base, nbytes, stream=sp)
+      memcpy_async(vg[i + 1].data_ptr(), base + self.numel * self.elem, nbytes, stream=sp)
+      stream_write_value32(flags.data_ptr() + 4 * (i + 1), e, stream=sp)
+    self.peer.signal(FLAG_KV_ACK, e, stream=sp)
+    for t in (kg, vg, flags):
+      t.record_stream(side)
+    return kg, vg, flags, e
 
   def gather(self, k: torch.Tensor, v: torch.Tensor):
     """Stand-alone variant (no attention kernel to fuse with): waits for every owner, pulls, acknowledges."""

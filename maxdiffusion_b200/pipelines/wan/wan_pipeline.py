@@ -74,7 +74,8 @@ class WanPipeline:
       # a one-rank context still goes through ContextParallel when the fixed-exponent softmax is selected
       self.pctx = ContextParallel(self.mesh, str(config.get("context_strategy", "ring")),
                                   peer_memory=bool(config.get("peer_memory_transport", True)) and self.device.type == "cuda",
-                                  fixed_m=fixed_m, ulysses_chunks=int(config.get("ulysses_attention_chunks", 1)))
+                                  fixed_m=fixed_m, ulysses_chunks=int(config.get("ulysses_attention_chunks", 1)),
+                                  kv_transport=str(config.get("ring_kv_transport", "sm")))
     if self.mesh.size("tensor") > 1:
       from ...parallel.tensor import apply_tensor_parallel_wan
 

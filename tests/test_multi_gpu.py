@@ -179,7 +179,55 @@ def test_flag_gated_kv_exchange_feeds_flash_attention():
     assert max(errs) < 3e-2
 
 
-def _train(rank, world, peer, attention="tokamax_ring", save_kv=True):
+def _kv_exchange_dma(rank, world):
+  import torch.distributed as dist
+
+  from maxdiffusion_b200.ops import kernels as K
+  from maxdiffusion_b200.parallel import collectives as C, symm
+
+  peer = symm.PeerGroup(dist.group.WORLD)
+  errs = []
+  # small shards over four epochs (both slots, the acknowledgement from the side stream), then a full-occupancy case:
+  # more tiles than SMs and 42 MB per shard, where nothing but copy engines and stream memory operations may move the data
+  for (B, S, H, reps) in ((2, 392, 5, 4), (1, 4096, 40, 2)):
+    ex = symm.PeerKVExchange(peer, B * S * H * 128, transport="dma")
+    for it in range(reps):
+      torch.manual_seed(31 * it + rank)
+      q = torch.randn((B, S, H, 128), device="cuda", dtype=torch.bfloat16)
+      k = torch.randn((B, S, H, 128), device="cuda", dtype=torch.bfloat16)
+      v = torch.randn((B, S, H, 128), device="cuda", dtype=torch.bfloat16)
+      kg, vg, flags, epoch, plan, keep = ex.plan(k, v)
+      assert plan is None and flags.numel() == world
+      out, _ = K.flash_fwd(q, list(kg), list(vg), seg_flags=flags, flag_target=epoch)
+      k_all = C.all_gather_stack(k, dist.group.WORLD)
+      v_all = C.all_gather_stack(v, dist.group.WORLD)
+      order = ex.order()
+      want, _ = K.flash_fwd(q, [k_all[r] for r in order], [v_all[r] for r in order])
+      errs.append((out.float() - want.float()).abs().max().item())
+      assert all(torch.equal(kg[j], k_all[order[j]]) and torch.equal(vg[j], v_all[order[j]]) for j in range(world))
+      assert flags.tolist() == [epoch] * world
+  return errs
+
+
+def test_copy_engine_kv_transport_feeds_flash_attention_bit_for_bit():
+  """`ring_kv_transport=dma`: remote K/V arrive by copy-engine copies on a side stream, each segment's ready flag by a
+  stream memory operation behind them; the attention launch has no copy CTAs and must equal the same kernel on
+  NCCL-gathered K/V exactly."""
+  if torch.cuda.device_count() < 2:
+    pytest.skip("needs 2 GPUs")
+  for errs in _spawn(_kv_exchange_dma, 2):
+    assert max(errs) == 0.0
+
+
+def test_training_step_with_copy_engine_kv_transport_matches():
+  if torch.cuda.device_count() < 2:
+    pytest.skip("needs 2 GPUs")
+  a = _spawn(_train, 2, True, "tokamax_ring", True, "dma")[0]
+  b = _spawn(_train, 2, True, "tokamax_ring", True, "sm")[0]
+  assert a == pytest.approx(b, rel=1e-3, abs=1e-3)
+
+
+def _train(rank, world, peer, attention="tokamax_ring", save_kv=True, kv_transport="sm"):
   from maxdiffusion_b200 import pyconfig
   from maxdiffusion_b200.parallel.mesh import create_device_mesh
   from maxdiffusion_b200.trainers.wan_trainer import WanTrainer
@@ -189,7 +237,8 @@ def _train(rank, world, peer, attention="tokamax_ring", save_kv=True):
        'wan_config_overrides={"num_layers": 2, "ffn_dim": 1024}', "remat_policy=SAVE_ATTENTION",
        "warmup_steps_fraction=0.0", "log_config=false", "write_metrics=false", f"attention={attention}", "ulysses_shards=2",
        f"per_device_batch_size={1.0 / world}", f"peer_memory_transport={'true' if peer else 'false'}",
-       "stochastic_rounding=false", f"ring_save_remote_kv={'true' if save_kv else 'false'}"], unittest=True)
+       "stochastic_rounding=false", f"ring_save_remote_kv={'true' if save_kv else 'false'}",
+       f"ring_kv_transport={kv_transport}"], unittest=True)
   tr = WanTrainer(config, mesh=create_device_mesh(config))
   data = tr.load_dataset()
   return [float(tr.train_step(next(data))["learning/loss"]) for _ in range(3)]
