@@ -20,6 +20,7 @@ import torch.distributed as dist
 
 from .. import max_logging
 from ..loaders.wan_loader import diffusers_to_flax_tree, diffusers_to_ours, flax_tree_to_diffusers, ours_to_diffusers
+from ..parallel.tensor import full_from_shards, gather_full, shard_of_full, tensor_parallel_specs
 from .checkpointing_utils import WAN_CHECKPOINT, create_checkpoint_manager
 
 
@@ -28,6 +29,62 @@ def _param_names(trainer):
   block_ids = {id(p) for b in trainer.model.blocks for p in b.parameters()}
   root = [n for n, p in trainer.model.named_parameters() if id(p) not in block_ids]
   return names, root
+
+
+def _tensor_axis(trainer):
+  """(size, this rank's index, group, per-block {parameter name: slice spec}) of the trainer's tensor axis."""
+  T = trainer.mesh.size("tensor")
+  if T == 1:
+    return 1, 0, None, [{} for _ in trainer.model.blocks]
+  return (T, trainer.mesh.index_in("tensor"), trainer.mesh.group("tensor"),
+          [tensor_parallel_specs(b) for b in trainer.model.blocks])
+
+
+def _specs_by_name(trainer, i, blk_names):
+  """Slice specs of block i's parameters for a run that is NOT tensor parallel itself (it restores the moments of one
+  that was): which parameters a tensor-parallel run splits follows from the block's structure alone."""
+  out = []
+  for n in blk_names:
+    leaf = n.rsplit(".", 1)[-1]
+    if n.endswith(("to_qkv.weight", "to_qkv.bias")):
+      out.append(("col", 3))
+    elif n.endswith(("to_kv.weight", "to_kv.bias", "add_kv_proj.weight", "add_kv_proj.bias")):
+      out.append(("col", 2))
+    elif n.endswith(("to_q.weight", "to_q.bias", "ffn_in.weight", "ffn_in.bias")) or leaf in ("norm_q", "norm_k", "norm_added_k"):
+      out.append(("col", 1))
+    elif n.endswith(("to_out.weight", "ffn_out.weight")):
+      out.append(("row", 1))
+    else:
+      out.append(None)
+  return out
+
+
+def _reshard_flat_over_tensor_axis(flats, full_shapes, specs, group, T: int, t_rank: int) -> torch.Tensor:
+  """Flat per-block moments written by `len(flats)` tensor ranks -> the flat buffer of tensor rank `t_rank` of `T`.
+
+  Every saved buffer is cut into its per-parameter views (the slice shapes follow from the full shapes and the specs,
+  the offsets from the flat layout's alignment rule), the slices are joined into full tensors and cut again for the
+  restoring run; `group` is the restoring run's flat layout of the block."""
+  from ..parallel.fsdp import _ALIGN
+
+  saved_t = len(flats)
+  fulls = []
+  offs = [0] * saved_t
+  for shape, spec in zip(full_shapes, specs):
+    parts = []
+    for t in range(saved_t):
+      local = shard_of_full(torch.empty(shape, device="meta"), spec, saved_t, t).shape
+      numel = 1
+      for d in local:
+        numel *= d
+      parts.append(flats[t][offs[t]:offs[t] + numel].view(local))
+      offs[t] += (numel + _ALIGN - 1) // _ALIGN * _ALIGN
+    fulls.append(full_from_shards(parts, spec) if spec is not None else parts[0])
+  out = flats[0].new_zeros(group.numel)
+  for full, spec, off in zip(fulls, specs, group.offsets):
+    piece = shard_of_full(full, spec, T, t_rank).reshape(-1)
+    out[off:off + piece.numel()].copy_(piece)
+  return out
 
 
 class WanCheckpointer:
@@ -49,16 +106,17 @@ class WanCheckpointer:
 
   # ---- training state ----------------------------------------------------------------------
   def save(self, step: int, trainer) -> None:
-    if trainer.mesh.size("tensor") > 1:
-      raise NotImplementedError("checkpoints of tensor-parallel runs are not written: the block weights of a rank hold "
-                                "its heads / FFN units only and there is no gather over the tensor axis yet")
     names, root = _param_names(trainer)
     eng = trainer.engine
+    T, t_rank, t_group, specs = _tensor_axis(trainer)
     full = {}
     for i, (g, blk_names) in enumerate(zip(eng.groups, names)):
       flat = eng.full_block_flat(i)  # collective when sharded: every rank takes part, only rank 0 keeps the result
-      if self.rank == 0:
-        for n, v in zip(blk_names, g.views(flat)):
+      for n, v in zip(blk_names, g.views(flat)):
+        if T > 1 and specs[i].get(n) is not None:
+          # a tensor-parallel rank holds its heads / FFN units only: the full parameter is assembled over the tensor axis
+          v = gather_full(v, specs[i][n], t_group)
+        if self.rank == 0:
           full[f"blocks.{i}.{n}"] = v.to("cpu")
       del flat
     cfg = trainer.wan_cfg
@@ -75,9 +133,12 @@ class WanCheckpointer:
       # The moments are sharded over the engine's shard group only; replicas (the `data` axis, and `tensor`) hold
       # identical copies, so exactly one replica writes: the ranks whose shard group contains global rank 0. Files are
       # numbered by the rank INSIDE the shard group, which is what `maybe_restore` re-shards by.
+      # The ranks of the tensor axis hold the moments of different slices, so every one of them writes too: file
+      # t * (ranks of a shard group) + (rank inside the shard group) for tensor rank t.
       shard_ranks = trainer.mesh.ranks("shard") if eng.world > 1 else [self.rank]
-      writers = eng.world
-      if 0 in shard_ranks or self.world == 1:
+      writers = eng.world * T
+      first_replica = trainer.mesh.coords.get("data", 0) == 0 if T > 1 else (0 in shard_ranks or self.world == 1)
+      if first_replica:
         st = eng.optimizer_state()
         shard = {"step": torch.tensor([st["step"]]), "root_m": st["root_m"], "root_v": st["root_v"]}
         for i, (m, v) in enumerate(zip(st["m"], st["v"])):
@@ -85,7 +146,8 @@ class WanCheckpointer:
         sharded = {"wan_state": shard}
       if self.rank == 0:
         items["wan_config"]["_train_step"] = int(step)
-    self.manager.save(step, items, sharded=sharded, world_size=writers, shard_rank=eng.rank)
+        items["wan_config"]["_tensor_parallel"] = int(T)
+    self.manager.save(step, items, sharded=sharded, world_size=writers, shard_rank=t_rank * eng.world + eng.rank)
     max_logging.log(f"saved checkpoint for step {step} to {self.manager.directory}")
 
   def maybe_restore(self, trainer) -> Optional[int]:
@@ -98,16 +160,29 @@ class WanCheckpointer:
     ours = diffusers_to_ours(flax_tree_to_diffusers(tree))
     names, root = _param_names(trainer)
     eng = trainer.engine
+    T, t_rank, _t_group, specs = _tensor_axis(trainer)
     for i, blk_names in enumerate(names):
-      eng.load_full_block(i, [ours[f"blocks.{i}.{n}"].to(eng.device, eng.param_dtype) for n in blk_names])
+      eng.load_full_block(i, [shard_of_full(ours[f"blocks.{i}.{n}"], specs[i].get(n), T, t_rank).to(eng.device, eng.param_dtype)
+                              for n in blk_names])
     for n, view in zip(root, eng.root.views(eng.root_flat)):
       view.copy_(ours[n].to(eng.device, eng.param_dtype).reshape(view.shape))
     if os.path.exists(os.path.join(self.manager.directory, str(step), "wan_state", "_sharding")):
       shards = self.manager.restore_sharded(step, "wan_state")
+      saved_t = int(self.manager.restore_json(step, "wan_config").get("_tensor_parallel", 1))
+      per_t = len(shards) // saved_t  # files of one tensor rank of the saving run: the ranks of its shard group
       state = {"step": int(shards[0]["step"][0]), "root_m": shards[0]["root_m"], "root_v": shards[0]["root_v"], "m": [], "v": []}
-      for i, g in enumerate(eng.groups):
+      for i, (g, blk_names) in enumerate(zip(eng.groups, names)):
         for key in ("m", "v"):
-          full = torch.cat([s[f"{key}.{i}"] for s in shards])  # flat moments of the whole block
+          # flat moments of the whole block as every tensor rank of the saving run held them
+          flats = [torch.cat([s[f"{key}.{i}"] for s in shards[t * per_t:(t + 1) * per_t]]) for t in range(saved_t)]
+          if saved_t == T:
+            full = flats[t_rank]
+          else:
+            full = _reshard_flat_over_tensor_axis(flats, [ours[f"blocks.{i}.{n}"].shape for n in blk_names],
+                                                  [specs[i].get(n) for n in blk_names] if T > 1 else
+                                                  _specs_by_name(trainer, i, blk_names), g, T, t_rank)
+          if full.numel() < g.numel:
+            full = torch.cat([full, full.new_zeros(g.numel - full.numel())])
           state[key].append(full[eng.rank * g.shard_numel:(eng.rank + 1) * g.shard_numel] if eng.world > 1 else full[:g.numel])
       eng.load_optimizer_state(state)
     max_logging.log(f"restored checkpoint of step {step} from {self.manager.directory}")

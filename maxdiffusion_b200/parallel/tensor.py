@@ -292,3 +292,58 @@ def apply_tensor_parallel_wan(model, group) -> int:
     blk.ffn_out = _row(blk.ffn_out, group)
   model.tp_group = group
   return n
+
+
+# ---- full <-> per-rank parameter layout (checkpoints of tensor-parallel runs) -----------------------------------------
+def tensor_parallel_specs(block) -> dict:
+  """name -> (kind, chunks) for every parameter of `block` that holds a slice of the full tensor: "col" = rows
+  [out, ...] split (per chunk of a fused projection), "row" = columns split. Parameters that are not listed are
+  replicated over the tensor ranks."""
+  specs = {}
+  for mod_name, mod in block.named_modules():
+    prefix = f"{mod_name}." if mod_name else ""
+    if isinstance(mod, ColumnParallelLinear):
+      specs[prefix + "weight"] = ("col", mod.chunks)
+      if mod.bias is not None:
+        specs[prefix + "bias"] = ("col", mod.chunks)
+    elif isinstance(mod, RowParallelLinear):
+      specs[prefix + "weight"] = ("row", 1)
+    if getattr(mod, "tp_group", None) is not None:
+      for nm in ("norm_q", "norm_k", "norm_added_k"):
+        if isinstance(getattr(mod, nm, None), nn.Parameter):
+          specs[prefix + nm] = ("col", 1)
+  return specs
+
+
+def shard_of_full(full: torch.Tensor, spec, n: int, r: int) -> torch.Tensor:
+  """Rank r's slice (of n) of a full parameter."""
+  if spec is None or n == 1:
+    return full
+  kind, chunks = spec
+  if kind == "row":
+    loc = full.shape[1] // n
+    return full[:, r * loc:(r + 1) * loc]
+  per = full.shape[0] // chunks
+  loc = per // n
+  return torch.cat([full[c * per + r * loc:c * per + (r + 1) * loc] for c in range(chunks)], dim=0)
+
+
+def full_from_shards(parts, spec) -> torch.Tensor:
+  """Inverse of `shard_of_full` over the slices of all ranks, in rank order."""
+  if spec is None or len(parts) == 1:
+    return parts[0]
+  kind, chunks = spec
+  if kind == "row":
+    return torch.cat(list(parts), dim=1)
+  loc = parts[0].shape[0] // chunks
+  return torch.cat([p[c * loc:(c + 1) * loc] for c in range(chunks) for p in parts], dim=0)
+
+
+def gather_full(local: torch.Tensor, spec, group) -> torch.Tensor:
+  """All ranks of `group` call this with their slice; every rank gets the full parameter."""
+  n, _ = _size_rank(group)
+  if spec is None or n == 1:
+    return local
+  parts = [torch.empty_like(local) for _ in range(n)]
+  dist.all_gather(parts, local.contiguous(), group=group)
+  return full_from_shards(parts, spec)

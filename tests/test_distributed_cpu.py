@@ -242,6 +242,57 @@ def test_tensor_parallel_training_matches_single_process():
     assert losses == pytest.approx(ref, rel=2e-4, abs=1e-5)
 
 
+def _tp_checkpoint(rank, world, tmp, phase):
+  """phase "save": two steps on `world` tensor ranks, checkpoint, two more steps (the uninterrupted run).
+  phase "resume": a trainer on `world` tensor ranks whose weights were moved away restores and takes the same two steps."""
+  from maxdiffusion_b200 import pyconfig
+  from maxdiffusion_b200.checkpointing.wan_checkpointer import WanCheckpointer
+  from maxdiffusion_b200.parallel.mesh import create_device_mesh
+  from maxdiffusion_b200.trainers.wan_trainer import WanTrainer
+
+  config = pyconfig.initialize(
+      ["t", CFG, "run_name=tpck", f"output_dir={tmp}", "height=64", "width=48", "num_frames=9", "dataset_type=synthetic",
+       "wan_preset=tiny", f"wan_config_overrides={TINY}", "remat_policy=FULL", "warmup_steps_fraction=0.0", "log_config=false",
+       "write_metrics=false", "learning_rate=1e-3", "attention=flash", f"per_device_batch_size={1.0 / world}",
+       "synthetic_override_text_dim=48", "max_sequence_length=16", "ici_data_parallelism=1", "ici_fsdp_parallelism=1",
+       "ici_context_parallelism=1", f"ici_tensor_parallelism={world}", "save_optimizer=true",
+       "enable_async_checkpointing=false"], unittest=True)
+  torch.manual_seed(0)
+  tr = WanTrainer(config, mesh=create_device_mesh(config), device="cpu")
+  data = tr.load_dataset()
+  batches = [next(data) for _ in range(4)]
+  ck = WanCheckpointer(config)
+  if phase == "save":
+    for b in batches[:2]:
+      tr.train_step(b)
+    ck.save(2, tr)
+    ck.manager.wait_until_finished()
+  else:
+    with torch.no_grad():  # everything must come from the checkpoint
+      for flat in list(tr.engine.shards) + [tr.engine.root_flat]:
+        flat.add_(0.25)
+    assert ck.maybe_restore(tr) == 2
+    tr.step = 2
+  tr.gen = torch.Generator().manual_seed(1)
+  return [float(tr.train_step(b)["learning/loss"]) for b in batches[2:]]
+
+
+def test_tensor_parallel_checkpoint_resumes_on_the_same_and_on_another_tensor_axis(tmp_path):
+  """A tensor-parallel run writes full parameters (gathered over the tensor axis) and every tensor rank's moments;
+  restoring on 2 tensor ranks, on 1, and restoring a single-process checkpoint on 2 continues the uninterrupted run."""
+  import json
+
+  tmp = str(tmp_path / "tp2")
+  ref = run_ranks(_tp_checkpoint, 2, tmp, "save")[0]
+  meta = json.load(open(os.path.join(tmp, "tpck", "checkpoints", "2", "wan_state", "_METADATA")))["tree_metadata"]
+  assert meta["blocks/attn1/query/kernel"]["shape"] == [2, 128, 128] and meta["blocks/ffn/proj_out/kernel"]["shape"] == [2, 96, 128]
+  assert run_ranks(_tp_checkpoint, 2, tmp, "resume")[0] == pytest.approx(ref, rel=1e-5, abs=1e-7)
+  assert _tp_checkpoint(0, 1, tmp, "resume") == pytest.approx(ref, rel=2e-4, abs=1e-5)
+  tmp1 = str(tmp_path / "tp1")
+  ref1 = _tp_checkpoint(0, 1, tmp1, "save")
+  assert run_ranks(_tp_checkpoint, 2, tmp1, "resume")[0] == pytest.approx(ref1, rel=2e-4, abs=1e-5)
+
+
 def _spatial_decode(rank, world, chunk):
   import torch.distributed as dist
 
