@@ -285,7 +285,7 @@ def main() -> int:
         "config": {"model": "Wan2.1-T2V-14B (40 layers, dim 5120, 40 heads, ffn 13824), random init" if official else args.preset,
                    "global_batch": 1, "seq_len": seq_len,
                    "parallelism": f"cp{n} ring x fsdp over the same {n} ranks" if n > 1 else "single GPU",
-                   "ring_kv_transport": str(config.get("ring_kv_transport", "sm")) if n > 1 else None,
+                   "ring_kv_transport": str(config.get("ring_kv_transport", "dma")) if n > 1 else None,
                    "video": f"{args.height}x{args.width}x{args.frames}",
                    "remat": f"per block ({args.remat}); the last {keep} of {len(trainer.model.blocks)} blocks keep their activations "
                             f"(peak {torch.cuda.max_memory_reserved() / 2**30:.0f} GiB reserved)",

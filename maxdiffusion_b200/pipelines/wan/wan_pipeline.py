@@ -75,7 +75,7 @@ class WanPipeline:
       self.pctx = ContextParallel(self.mesh, str(config.get("context_strategy", "ring")),
                                   peer_memory=bool(config.get("peer_memory_transport", True)) and self.device.type == "cuda",
                                   fixed_m=fixed_m, ulysses_chunks=int(config.get("ulysses_attention_chunks", 1)),
-                                  kv_transport=str(config.get("ring_kv_transport", "sm")))
+                                  kv_transport=str(config.get("ring_kv_transport", "dma")))
     if self.mesh.size("tensor") > 1:
       from ...parallel.tensor import apply_tensor_parallel_wan
 

@@ -115,7 +115,7 @@ class WanTrainer:
       self.pctx = ContextParallel(self.mesh, str(config.get("context_strategy", "ring")),
                                   peer_memory=bool(config.get("peer_memory_transport", True)) and self.device.type == "cuda",
                                   fixed_m=fixed_m, save_remote_kv=bool(config.get("ring_save_remote_kv", True)), ulysses_chunks=int(config.get("ulysses_attention_chunks", 1)),
-                                  kv_transport=str(config.get("ring_kv_transport", "sm")))
+                                  kv_transport=str(config.get("ring_kv_transport", "dma")))
 
     self.scheduler = FlowMatchScheduler(num_train_timesteps=1000, shift=float(config.get("flow_shift", 3.0)))
     self.scheduler_state = self.scheduler.set_timesteps(self.scheduler.create_state(), 1000, training=True, device=self.device)
