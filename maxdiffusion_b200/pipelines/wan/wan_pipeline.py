@@ -204,6 +204,23 @@ class WanPipeline:
                  kv_cache=kv_cache, rope=rope, **kw)
 
   # ------------------------------------------------------------------ call
+  def check_inputs(self, prompt, negative_prompt, height: int, width: int, num_frames: int, prompt_embeds=None,
+                   negative_prompt_embeds=None) -> None:
+    """Argument rules shared by the Wan pipelines (reference: src/maxdiffusion/pipelines/wan/wan_vace_pipeline_2_1.py:
+    387-425): a prompt or its embedding but not both, text as str or list, a frame size the VAE stride times the patch
+    size divides, a positive frame count."""
+    for name, text, emb in (("prompt", prompt, prompt_embeds), ("negative_prompt", negative_prompt, negative_prompt_embeds)):
+      if text is not None and emb is not None:
+        raise ValueError(f"pass `{name}` or `{name}_embeds`, not both")
+      if text is not None and not isinstance(text, (str, list)):
+        raise ValueError(f"`{name}` has to be a str or a list but is {type(text)}")
+    patch = tuple(self.transformer.cfg.patch_size) if self.transformer is not None else (1, 2, 2)
+    base_h, base_w = self.vae_scale_factor_spatial * patch[1], self.vae_scale_factor_spatial * patch[2]
+    if height % base_h or width % base_w:
+      raise ValueError(f"`height` and `width` have to be divisible by {base_h} and {base_w} but are {height} and {width}")
+    if num_frames < 1:
+      raise ValueError(f"`num_frames` must be positive, got {num_frames}")
+
   @torch.no_grad()
   def __call__(self, prompt=None, negative_prompt=None, height: Optional[int] = None, width: Optional[int] = None,
                num_frames: Optional[int] = None, num_inference_steps: Optional[int] = None,
@@ -222,6 +239,7 @@ class WanPipeline:
     use_magcache = bool(c.get("use_magcache", False)) if use_magcache is None else use_magcache
     use_sen_cache = bool(c.get("use_sen_cache", False)) if use_sen_cache is None else use_sen_cache
     use_kv_cache = bool(c.get("use_kv_cache", False)) if use_kv_cache is None else use_kv_cache
+    self.check_inputs(prompt, negative_prompt, height, width, num_frames, prompt_embeds, negative_prompt_embeds)
     if sum([use_cfg_cache, use_magcache, use_sen_cache]) > 1:
       raise ValueError("use_cfg_cache, use_magcache and use_sen_cache are mutually exclusive")
     if use_sen_cache and self.transformer_2 is None:

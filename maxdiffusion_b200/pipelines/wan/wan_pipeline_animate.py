@@ -101,6 +101,43 @@ class WanAnimatePipeline(WanPipeline):
     return torch.cat([mask, cond], dim=1)
 
   # ---- call --------------------------------------------------------------------------------
+  def check_inputs(self, image, pose_video, face_video, background_video, mask_video, prompt, negative_prompt, height,
+                   width, prompt_embeds=None, negative_prompt_embeds=None, image_embeds=None, mode="animate",
+                   prev_segment_conditioning_frames=5) -> None:
+    """The user-facing argument rules (reference: src/maxdiffusion/pipelines/wan/wan_pipeline_animate.py:338-413):
+    a prompt or its embedding but not both, the reference image, both driving videos present and non-empty with as many frames as each
+    other, background + mask in replace mode, sizes divisible by 16, 1 or 5 conditioning frames."""
+    def one_of(a, b, name):
+      if a is not None and b is not None:
+        raise ValueError(f"pass `{name}` or `{name}_embeds`, not both")
+    one_of(prompt, prompt_embeds, "prompt")
+    one_of(negative_prompt, negative_prompt_embeds, "negative_prompt")
+    if image is None:
+      raise ValueError("provide `image`: the reference latents are encoded from it (`image_embeds` only replaces the "
+                       "image encoder's output)")
+    for name, v in (("pose_video", pose_video), ("face_video", face_video)):
+      if v is None:
+        raise ValueError(f"provide `{name}`")
+      if not torch.is_tensor(v) or v.dim() != 5 or v.shape[2] == 0:
+        raise ValueError(f"`{name}` must be a [B, 3, T, H, W] tensor with at least one frame")
+    if pose_video.shape[2] != face_video.shape[2]:
+      raise ValueError(f"`pose_video` has {pose_video.shape[2]} frames and `face_video` {face_video.shape[2]}")
+    if mode not in ("animate", "replace"):
+      raise ValueError(f"mode must be 'animate' or 'replace', got {mode!r}")
+    if mode == "replace":
+      for name, v in (("background_video", background_video), ("mask_video", mask_video)):
+        if v is None:
+          raise ValueError("`background_video` and `mask_video` are required for replace mode")
+        if not torch.is_tensor(v) or v.dim() != 5 or v.shape[2] != pose_video.shape[2]:
+          raise ValueError(f"`{name}` must be a 5-D tensor with the {pose_video.shape[2]} frames of `pose_video`")
+    if height % 16 or width % 16:
+      raise ValueError(f"`height` and `width` have to be divisible by 16 but are {height} and {width}")
+    for name, v in (("prompt", prompt), ("negative_prompt", negative_prompt)):
+      if v is not None and not isinstance(v, (str, list)):
+        raise ValueError(f"`{name}` has to be a str or a list but is {type(v)}")
+    if not isinstance(prev_segment_conditioning_frames, int) or prev_segment_conditioning_frames not in (1, 5):
+      raise ValueError(f"`prev_segment_conditioning_frames` has to be 1 or 5, got {prev_segment_conditioning_frames!r}")
+
   @torch.no_grad()
   def __call__(self, image: torch.Tensor, pose_video: torch.Tensor, face_video: torch.Tensor,
                background_video: Optional[torch.Tensor] = None, mask_video: Optional[torch.Tensor] = None, prompt=None,
@@ -112,10 +149,8 @@ class WanAnimatePipeline(WanPipeline):
     c = self.config
     height, width = height or int(c.get("height", 720)), width or int(c.get("width", 1280))
     steps = num_inference_steps or int(c.get("num_inference_steps", 20))
-    if mode not in ("animate", "replace"):
-      raise ValueError(f"mode must be 'animate' or 'replace', got {mode}")
-    if mode == "replace" and (background_video is None or mask_video is None):
-      raise ValueError("`background_video` and `mask_video` are required for replace mode.")
+    self.check_inputs(image, pose_video, face_video, background_video, mask_video, prompt, negative_prompt, height, width,
+                      prompt_embeds, negative_prompt_embeds, image_embeds, mode, prev_segment_conditioning_frames)
     s = self.vae_scale_factor_temporal
     if segment_frame_length % s != 1:
       segment_frame_length = max(1, segment_frame_length // s * s + 1)

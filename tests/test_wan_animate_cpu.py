@@ -64,3 +64,21 @@ def test_pipeline_two_segments(tmp_path):
   mk = (torch.rand((1, 1, 13, 32, 32), generator=g) > 0.5).float()
   video2 = pipe(image, pose, face, background_video=bg, mask_video=mk, mode="replace", **kw)
   assert video2.shape == (1, 13, 32, 32, 3)
+
+
+def test_check_inputs_rejects_what_the_segment_loop_cannot_run():
+  import pytest
+
+  pipe = WanAnimatePipeline.__new__(WanAnimatePipeline)
+  img, pose, face = torch.zeros(1, 3, 32, 32), torch.zeros(1, 3, 9, 32, 32), torch.zeros(1, 3, 9, 16, 16)
+  ok = dict(image=img, pose_video=pose, face_video=face, background_video=None, mask_video=None, prompt="a", negative_prompt=None,
+            height=32, width=32)
+  pipe.check_inputs(**ok)
+  for change, match in (({"prompt_embeds": torch.zeros(1, 4, 8)}, "not both"), ({"image": None}, "provide `image`"),
+                        ({"face_video": None}, "face_video"), ({"face_video": face[:, :, :5]}, "frames"),
+                        ({"mode": "replace"}, "replace mode"), ({"mode": "swap"}, "mode must be"),
+                        ({"height": 40}, "divisible by 16"), ({"prompt": 3}, "str or a list"),
+                        ({"prev_segment_conditioning_frames": 3}, "1 or 5"),
+                        ({"mode": "replace", "background_video": pose, "mask_video": pose[:, :1, :4]}, "mask_video")):
+    with pytest.raises(ValueError, match=match):
+      pipe.check_inputs(**{**ok, **change})

@@ -201,3 +201,21 @@ def test_channels_last_encoder_orchestration_matches_the_ncdhw_path():
       assert (got - want).abs().max() < 1e-4 * (1 + want.abs().max())
     whole = cl.encode(x, whole_clip=True).chunk(2, dim=1)[0]
     assert (whole - vae.encode_full(x).mean).abs().max() < 1e-4 * (1 + want.abs().max())
+
+
+def test_check_inputs_of_the_wan_pipelines():
+  import types
+
+  import pytest
+
+  pipe = WanPipeline2_1.__new__(WanPipeline2_1)
+  pipe.transformer = types.SimpleNamespace(cfg=types.SimpleNamespace(patch_size=(1, 2, 2)))
+  pipe.vae_scale_factor_spatial = 8
+  pipe.check_inputs("a cat", None, 480, 832, 81)
+  pipe.check_inputs(None, None, 480, 832, 81, prompt_embeds=torch.zeros(1, 4, 8))
+  for args, kw, match in ((("a", None, 480, 832, 81), {"prompt_embeds": torch.zeros(1, 4, 8)}, "not both"),
+                          ((None, "b", 480, 832, 81), {"negative_prompt_embeds": torch.zeros(1, 4, 8)}, "not both"),
+                          ((3, None, 480, 832, 81), {}, "str or a list"), (("a", None, 488, 832, 81), {}, "divisible by 16"),
+                          (("a", None, 480, 832, 0), {}, "positive")):
+    with pytest.raises(ValueError, match=match):
+      pipe.check_inputs(*args, **kw)
