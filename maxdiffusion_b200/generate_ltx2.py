@@ -26,6 +26,7 @@ def call_pipeline(config, pipe, **extra):
             audio_modality_scale=float(config.audio_modality_scale), decode_timestep=float(config.decode_timestep),
             decode_noise_scale=float(config.decode_noise_scale), max_sequence_length=int(config.max_sequence_length),
             use_cross_timestep=bool(config.use_cross_timestep), use_kv_cache=bool(config.get("use_kv_cache", False)) or True,
+            noise_scale=float(config.noise_scale) if config.get("noise_scale", None) is not None else None,
             generator=torch.Generator().manual_seed(int(config.seed)))
   kw.update(extra)
   if pipe.text_encoder is None:

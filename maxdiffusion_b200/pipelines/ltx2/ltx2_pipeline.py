@@ -127,11 +127,81 @@ class LTX2Pipeline:
       neg, neg_mask = self.text_encoder(negs, max_sequence_length)
     return embeds, mask, neg, neg_mask
 
+  def check_inputs(self, prompt, height: int, width: int, prompt_embeds=None, negative_prompt_embeds=None,
+                   prompt_attention_mask=None, negative_prompt_attention_mask=None) -> None:
+    """Argument rules (reference: src/maxdiffusion/pipelines/ltx2/ltx2_pipeline.py:1365-1417): a frame size the VAE's
+    spatial stride divides, a prompt or its embedding (not both, not neither), a mask with every embedding, and
+    positive / negative embeddings and masks of equal shape when both are passed."""
+    r = self.vae_spatial_compression_ratio
+    if height % r or width % r:
+      raise ValueError(f"`height` and `width` have to be divisible by {r} but are {height} and {width}.")
+    if prompt is not None and prompt_embeds is not None:
+      raise ValueError("pass `prompt` or `prompt_embeds`, not both")
+    if prompt is None and prompt_embeds is None:
+      raise ValueError("provide either `prompt` or `prompt_embeds`")
+    if prompt is not None and not isinstance(prompt, (str, list)):
+      raise ValueError(f"`prompt` has to be a str or a list but is {type(prompt)}")
+    if prompt_embeds is not None and prompt_attention_mask is None:
+      raise ValueError("`prompt_attention_mask` is required with `prompt_embeds`")
+    if negative_prompt_embeds is not None and negative_prompt_attention_mask is None:
+      raise ValueError("`negative_prompt_attention_mask` is required with `negative_prompt_embeds`")
+    if prompt_embeds is not None and negative_prompt_embeds is not None:
+      if prompt_embeds.shape != negative_prompt_embeds.shape:
+        raise ValueError(f"`prompt_embeds` {tuple(prompt_embeds.shape)} and `negative_prompt_embeds` "
+                         f"{tuple(negative_prompt_embeds.shape)} must have the same shape")
+      if prompt_attention_mask.shape != negative_prompt_attention_mask.shape:
+        raise ValueError(f"`prompt_attention_mask` {tuple(prompt_attention_mask.shape)} and `negative_prompt_attention_mask` "
+                         f"{tuple(negative_prompt_attention_mask.shape)} must have the same shape")
+
+  @staticmethod
+  def _noised(x: torch.Tensor, noise_scale: float, generator) -> torch.Tensor:
+    noise = torch.randn(x.shape, generator=generator, dtype=torch.float32).to(x.device)
+    return noise_scale * noise + (1.0 - noise_scale) * x.float()
+
+  def prepare_latents(self, batch: int, lf: int, lh: int, lw: int, generator, latents=None,
+                      noise_scale: Optional[float] = None) -> torch.Tensor:
+    """Packed fp32 video tokens [B, N, C] the loop starts from (reference: ltx2_pipeline.py:1678-1727).
+
+    Without `latents`: unit noise. With `latents` and `noise_scale=None` they are the start state as given (5-D
+    tensors are packed). With a number, the reference's re-noising applies: 5-D latents are VAE latents and are
+    normalised with the VAE's statistics first, then start = noise_scale * noise + (1 - noise_scale) * latents --
+    how a second, higher-resolution pass continues from up-sampled latents."""
+    if latents is None:
+      z = torch.randn((batch, self.transformer.cfg.in_channels, lf, lh, lw), generator=generator, dtype=torch.float32)
+      return self.pack_latents(z, self.patch, self.patch_t).to(self.device)
+    if latents.dim() == 5:
+      if noise_scale is not None and self.vae is not None:
+        latents = self.vae.normalize_latents(latents.float())
+      latents = self.pack_latents(latents.float(), self.patch, self.patch_t)
+    if latents.dim() != 3:
+      raise ValueError(f"`latents` must be [B, C, F, H, W] or packed [B, N, C], got {tuple(latents.shape)}")
+    latents = latents.to(self.device, torch.float32)
+    return latents if noise_scale is None else self._noised(latents, float(noise_scale), generator)
+
+  def prepare_audio_latents(self, batch: int, channels: int, frames: int, mel_bins: int, generator, latents=None,
+                            noise_scale: Optional[float] = None) -> torch.Tensor:
+    """The audio counterpart (reference: ltx2_pipeline.py:1729-1772): 4-D [B, C, T, mel] latents are packed, normalised
+    with the audio VAE's statistics and re-noised when `noise_scale` is a number."""
+    if latents is None:
+      z = torch.randn((batch, channels, frames, mel_bins), generator=generator, dtype=torch.float32)
+      return self.pack_audio_latents(z).to(self.device)
+    if latents.dim() == 4:
+      latents = self.pack_audio_latents(latents.float())
+    if latents.dim() != 3:
+      raise ValueError(f"`audio_latents` must be [B, C, T, mel] or packed [B, T, C * mel], got {tuple(latents.shape)}")
+    latents = latents.to(self.device, torch.float32)
+    if noise_scale is None:
+      return latents
+    if self.audio_vae is not None:
+      latents = self.audio_vae.normalize_latents(latents)
+    return self._noised(latents, float(noise_scale), generator)
+
   # ---- call ----------------------------------------------------------------------------------
   @torch.no_grad()
   def __call__(self, prompt=None, negative_prompt=None, height: int = 512, width: int = 768, num_frames: int = 121,
                frame_rate: float = 24.0, num_inference_steps: int = 40, sigmas: Optional[Sequence[float]] = None,
-               guidance_scale: float = 3.0, guidance_rescale: float = 0.0, stg_scale: float = 1.0,
+               timesteps: Optional[Sequence[float]] = None, noise_scale: Optional[float] = None,
+               num_videos_per_prompt: int = 1, guidance_scale: float = 3.0, guidance_rescale: float = 0.0, stg_scale: float = 1.0,
                modality_scale: float = 1.0, audio_guidance_scale=None, audio_guidance_rescale: float = 0.0,
                audio_stg_scale=None, audio_modality_scale=None, generator: Optional[torch.Generator] = None,
                latents=None, audio_latents=None, prompt_embeds=None, negative_prompt_embeds=None,
@@ -139,8 +209,8 @@ class LTX2Pipeline:
                decode_noise_scale: Optional[float] = None, max_sequence_length: int = 1024, output_type: str = "uint8",
                use_cross_timestep: bool = False, use_kv_cache: bool = True):
     r, rt = self.vae_spatial_compression_ratio, self.vae_temporal_compression_ratio
-    if height % r or width % r:
-      raise ValueError(f"`height` and `width` have to be divisible by {r} but are {height} and {width}.")
+    self.check_inputs(prompt, height, width, prompt_embeds, negative_prompt_embeds, prompt_attention_mask,
+                      negative_prompt_attention_mask)
     if stg_scale > 0.0 and guidance_scale <= 1.0:
       raise ValueError("Spatio-temporal guidance requires guidance_scale > 1.0.")
     timings, t0 = {}, time.perf_counter()
@@ -149,9 +219,16 @@ class LTX2Pipeline:
     if prompt_embeds is None:
       prompt_embeds, prompt_attention_mask, negative_prompt_embeds, negative_prompt_attention_mask = self.encode_prompt(
           prompt, negative_prompt, do_cfg, max_sequence_length)
-    B = prompt_embeds.shape[0]
     if prompt_attention_mask is None:
       prompt_attention_mask = torch.ones(prompt_embeds.shape[:2], dtype=torch.long)
+    if do_cfg and negative_prompt_embeds is not None and negative_prompt_attention_mask is None:
+      negative_prompt_attention_mask = torch.ones(negative_prompt_embeds.shape[:2], dtype=torch.long)
+    if num_videos_per_prompt > 1:
+      # every prompt's embeddings and mask are repeated in place: videos [i * n, (i + 1) * n) belong to prompt i
+      rep = lambda t: None if t is None else t.repeat_interleave(int(num_videos_per_prompt), dim=0)
+      prompt_embeds, prompt_attention_mask = rep(prompt_embeds), rep(prompt_attention_mask)
+      negative_prompt_embeds, negative_prompt_attention_mask = rep(negative_prompt_embeds), rep(negative_prompt_attention_mask)
+    B = prompt_embeds.shape[0]
     if do_cfg:
       if negative_prompt_embeds is None:
         raise ValueError("classifier-free guidance needs `negative_prompt_embeds`")
@@ -172,17 +249,18 @@ class LTX2Pipeline:
     lh, lw, lf = height // r, width // r, (num_frames - 1) // rt + 1
     g = generator if generator is not None else torch.Generator().manual_seed(int(self.config.get("seed", 1)) if self.config is not None else 1)
     tc = self.transformer.cfg
-    if latents is None:
-      latents = torch.randn((B, tc.in_channels, lf, lh, lw), generator=g, dtype=torch.float32)
-    tokens = self.pack_latents(latents, self.patch, self.patch_t).to(self.device, torch.float32) if latents.dim() == 5 else latents.to(self.device, torch.float32)
+    tokens = self.prepare_latents(B, lf, lh, lw, g, latents, noise_scale)
     audio_lps = self.audio_sampling_rate / self.audio_hop_length / float(self.audio_temporal_ratio)
     audio_frames = round(num_frames / frame_rate * audio_lps)
     mel_bins = (self.audio_vae.cfg.mel_bins if self.audio_vae is not None else 64) // self.audio_mel_ratio
     a_ch = self.audio_vae.cfg.latent_channels if self.audio_vae is not None else tc.audio_in_channels // mel_bins
-    if audio_latents is None:
-      audio_latents = torch.randn((B, a_ch, audio_frames, mel_bins), generator=g, dtype=torch.float32)
-    a_tokens = (self.pack_audio_latents(audio_latents) if audio_latents.dim() == 4 else audio_latents).to(self.device, torch.float32)
+    a_tokens = self.prepare_audio_latents(B, a_ch, audio_frames, mel_bins, g, audio_latents, noise_scale)
 
+    if timesteps is not None and sigmas is not None:
+      raise ValueError("only one of `timesteps` and `sigmas` can be passed")
+    if timesteps is not None:
+      # custom timesteps are sigmas on the scheduler's 0..num_train_timesteps axis
+      sigmas = [float(t) / float(self.scheduler.config.num_train_timesteps) for t in timesteps]
     sig = torch.linspace(1.0, 1.0 / num_inference_steps, num_inference_steps) if sigmas is None else torch.as_tensor(sigmas, dtype=torch.float32)
     s = self.schedule_shift
     mu = calculate_shift(min(6144, lf * lh * lw), s["base_image_seq_len"], s["max_image_seq_len"], s["base_shift"], s["max_shift"])
@@ -236,9 +314,15 @@ class LTX2Pipeline:
     temb = None
     if self.vae.cfg.timestep_conditioning:
       noise = torch.randn(lat.shape, generator=g, dtype=torch.float32).to(lat)
-      ns = decode_timestep if decode_noise_scale is None else decode_noise_scale
+      # a number applies to the whole batch, a list gives one value per video
+      per_video = lambda v: torch.as_tensor(list(v) if isinstance(v, (list, tuple)) else [float(v)] * B, dtype=torch.float32)
+      dt = per_video(decode_timestep)
+      ns = dt if decode_noise_scale is None else per_video(decode_noise_scale)
+      if dt.numel() != B or ns.numel() != B:
+        raise ValueError(f"`decode_timestep` / `decode_noise_scale` lists need one value per video ({B})")
+      ns = ns.to(lat).view(B, 1, 1, 1, 1)
       lat = (1 - ns) * lat + ns * noise
-      temb = torch.full((B,), float(decode_timestep), device=self.device, dtype=vdtype)
+      temb = dt.to(self.device, vdtype)
     video = self.vae.decode(lat, temb)
     sync()
     timings["vae_decode"] = time.perf_counter() - t2

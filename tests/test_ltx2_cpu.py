@@ -1,6 +1,7 @@
 """LTX-2 on CPU: rotary embeddings, transformer caches and guidance masks, VAEs, vocoder, connectors, pipeline."""
 import math
 
+import pytest
 import torch
 
 from maxdiffusion_b200 import aot_cache, pyconfig
@@ -164,6 +165,78 @@ def test_generate_ltx2_tiny_and_checkpoint(tmp_path):
   pipe2 = LTX2Checkpointer(config).load_pipeline(device="cpu")
   for (n, p), (_, q) in zip(pipe.transformer.state_dict().items(), pipe2.transformer.state_dict().items()):
     assert torch.equal(p, q), n
+
+
+def test_pipeline_argument_rules_renoising_and_videos_per_prompt(tmp_path):
+  """`check_inputs`, `noise_scale` (start = s * noise + (1 - s) * normalised latents), `num_videos_per_prompt`, custom
+  `timesteps` and per-video `decode_timestep` lists of the LTX-2 pipeline."""
+  from maxdiffusion_b200.checkpointing.ltx2_checkpointer import LTX2Checkpointer
+
+  tcfg = ('{"in_channels": 8, "out_channels": 8, "num_attention_heads": 2, "attention_head_dim": 32, "cross_attention_dim": 64, '
+          '"audio_in_channels": 16, "audio_out_channels": 16, "audio_num_attention_heads": 2, "audio_attention_head_dim": 16, '
+          '"audio_cross_attention_dim": 32, "num_layers": 1, "caption_channels": 32}')
+  comps = ('{"vae": {"latent_channels": 8, "block_out_channels": [8, 16, 16, 32], "decoder_block_out_channels": [8, 16, 32], '
+           '"layers_per_block": [1, 1, 1, 1, 1], "decoder_layers_per_block": [1, 1, 1, 1]}, '
+           '"audio_vae": {"base_channels": 8, "mel_bins": 16, "resolution": 16, "latent_channels": 4}, '
+           '"vocoder": {"in_channels": 32, "hidden_channels": 32, "upsample_kernel_sizes": [4, 4], "upsample_factors": [2, 2]}, '
+           '"connectors": {"text_proj_in_factor": 3, "video_connector_attention_head_dim": 16, '
+           '"video_connector_num_attention_heads": 2, "video_connector_num_learnable_registers": 4, '
+           '"audio_connector_attention_head_dim": 16, "audio_connector_num_attention_heads": 2, '
+           '"audio_connector_num_learnable_registers": 4}}')
+  config = pyconfig.initialize(
+      ["x", "maxdiffusion_b200/configs/ltx2_video.yml", "random_init=True", "ltx2_preset=tiny", f"ltx2_config_overrides={tcfg}",
+       f"ltx2_component_overrides={comps}", "max_sequence_length=8", "use_bwe=False", f"output_dir={tmp_path}/out",
+       "log_config=false", "pretrained_model_name_or_path=/nonexistent"], unittest=True)
+  pipe = LTX2Checkpointer(config).load_pipeline(device="cpu")
+  fe = pipe.connectors.feature_extractor
+  dim = (fe.linear if hasattr(fe, "linear") else fe.video_linear).in_features // 3
+  g = torch.Generator().manual_seed(0)
+  emb = lambda n: torch.randn((n, 8, dim, 3), generator=g)
+  ones = lambda n: torch.ones((n, 8), dtype=torch.long)
+  kw = dict(height=64, width=64, num_frames=9, num_inference_steps=2, guidance_scale=1.0, stg_scale=0.0, output_type="latent")
+  pe = emb(1)
+
+  with pytest.raises(ValueError, match="divisible"):
+    pipe(prompt_embeds=pe, prompt_attention_mask=ones(1), **{**kw, "height": 70})
+  with pytest.raises(ValueError, match="not both"):
+    pipe(prompt="a", prompt_embeds=pe, prompt_attention_mask=ones(1), **kw)
+  with pytest.raises(ValueError, match="either"):
+    pipe(**kw)
+  with pytest.raises(ValueError, match="prompt_attention_mask` is required"):
+    pipe(prompt_embeds=pe, **kw)
+  with pytest.raises(ValueError, match="same shape"):
+    pipe(prompt_embeds=pe, prompt_attention_mask=ones(1), negative_prompt_embeds=emb(2), negative_prompt_attention_mask=ones(2), **kw)
+  with pytest.raises(ValueError, match="only one of"):
+    pipe(prompt_embeds=pe, prompt_attention_mask=ones(1), timesteps=[1000.0, 500.0], sigmas=[1.0, 0.5], **kw)
+
+  # two videos for one prompt; custom timesteps equal the same values given as sigmas
+  two = pipe(prompt_embeds=pe, prompt_attention_mask=ones(1), num_videos_per_prompt=2, generator=torch.Generator().manual_seed(3), **kw)
+  assert two.frames.shape[0] == 2 and not torch.equal(two.frames[0], two.frames[1])
+  a = pipe(prompt_embeds=pe, prompt_attention_mask=ones(1), timesteps=[1000.0, 400.0], generator=torch.Generator().manual_seed(3), **kw)
+  b = pipe(prompt_embeds=pe, prompt_attention_mask=ones(1), sigmas=[1.0, 0.4], generator=torch.Generator().manual_seed(3), **kw)
+  assert torch.equal(a.frames, b.frames)
+
+  # re-noising: the start state of a continued pass
+  lat = torch.randn((1, 8, 2, 2, 2), generator=g) * 3 + 1
+  start0 = pipe.prepare_latents(1, 2, 2, 2, torch.Generator().manual_seed(5), lat, noise_scale=0.0)
+  assert torch.allclose(start0, pipe.pack_latents(pipe.vae.normalize_latents(lat), pipe.patch, pipe.patch_t), atol=1e-6)
+  start1 = pipe.prepare_latents(1, 2, 2, 2, torch.Generator().manual_seed(5), lat, noise_scale=1.0)
+  noise = torch.randn(start0.shape, generator=torch.Generator().manual_seed(5))
+  assert torch.allclose(start1, noise)
+  half = pipe.prepare_latents(1, 2, 2, 2, torch.Generator().manual_seed(5), lat, noise_scale=0.25)
+  assert torch.allclose(half, 0.25 * noise + 0.75 * start0, atol=1e-6)
+  assert torch.equal(pipe.prepare_latents(1, 2, 2, 2, None, lat), pipe.pack_latents(lat, pipe.patch, pipe.patch_t))  # as given
+  packed_audio = torch.randn((1, 3, 4 * 4), generator=g)
+  assert torch.allclose(pipe.prepare_audio_latents(1, 4, 3, 4, None, packed_audio, noise_scale=0.0),
+                        pipe.audio_vae.normalize_latents(packed_audio))
+
+  # per-video decode timesteps need one value per video
+  dec = dict(kw, output_type="pt")
+  if pipe.vae.cfg.timestep_conditioning:
+    with pytest.raises(ValueError, match="one value per video"):
+      pipe(prompt_embeds=pe, prompt_attention_mask=ones(1), decode_timestep=[0.05, 0.05], **dec)
+    out = pipe(prompt_embeds=pe, prompt_attention_mask=ones(1), decode_timestep=[0.05], decode_noise_scale=[0.025], **dec)
+    assert out.frames.shape[:2] == (1, 3)
 
 
 def test_aot_cache_is_a_pass_through_on_cpu_and_fingerprints_revisions(tmp_path):
