@@ -206,7 +206,10 @@ class UniPCMultistepScheduler(SchedulerConfigMixin):
     """One denoising step. Returns (prev_sample, new_state)."""
     c = self.config
     if state.step_index is None:
-      state = state.replace(step_index=0)
+      # a loop may start in the middle of the schedule (image-to-image: noise added at `timesteps[k]`, then steps from
+      # k on): the first step's position is where its timestep sits in the schedule, the last position if it is absent
+      match = (state.timesteps.to(torch.float64) == float(timestep)).nonzero()
+      state = state.replace(step_index=int(match[0]) if match.numel() else len(state.timesteps) - 1)
     i = state.step_index
     work_dtype = torch.float32
     sample = sample.to(work_dtype)

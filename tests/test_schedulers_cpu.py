@@ -177,3 +177,126 @@ def test_unipc_flow_trajectory_matches_the_closed_form_and_its_order(order, min_
   assert math.log2(e1 / e2) > min_rate, (order, e1, e2)
   if order > 1:  # a higher order is more accurate at the same number of steps
     assert e2 < _run_flow_sampler(lambda: UniPCMultistepScheduler(solver_order=1, flow_shift=3.0), 48)
+
+
+# Entries 17 + 2731 k (k = 0..11) of the flattened [1, 256, 128] sample after each of the five steps, then its mean and
+# mean absolute value: read from the trajectories stored with the reference's scheduler test
+# (src/maxdiffusion/tests/legacy_hf_tests/schedulers/rf_scheduler_test_ref/step_01..05.npy), which were produced by the
+# original PyTorch scheduler of LTX-Video. Procedure of that test: torch.Generator seeded with 42 draws the sample and then
+# one "model output" per step; sampler LinearQuadratic, no shifting, 5 steps.
+_RF_GOLDEN = (
+    ([-0.175802, 1.459738, -1.672742, -0.964861, -0.964565, -1.910584, -0.73948, 0.875368, -1.86244, 0.401301, -0.481901, -1.324342], 0.0030629, 0.801981),
+    ([-0.184602, 1.460864, -1.678226, -0.956433, -0.976795, -1.927391, -0.729426, 0.87471, -1.865385, 0.391484, -0.495163, -1.336622], 0.0029942, 0.802161),
+    ([-0.378744, 1.623711, -1.907421, -0.847355, -1.149233, -1.85593, -0.821218, 0.864833, -2.015669, 0.416599, -0.427006, -1.442634], 0.0035431, 0.808093),
+    ([0.386029, 1.70213, -1.655608, -1.16029, -1.218508, -1.766913, -0.563438, 0.828621, -2.053754, -0.07025, -0.451482, -1.080794], 0.0015037, 0.849606),
+    ([0.458059, 0.971902, -1.366318, -1.079545, -1.289791, -0.756919, -0.886947, 0.711523, -1.528732, -0.300032, -0.87654, -0.912497], 0.0054846, 0.95287),
+)
+
+
+def test_rectified_flow_reproduces_the_stored_trajectory_of_the_original_scheduler():
+  from maxdiffusion_b200.schedulers.scheduling_rectified_flow import RectifiedFlowMultistepScheduler, linear_quadratic_schedule
+
+  shape = (1, 256, 128)
+  g = torch.Generator().manual_seed(42)
+  sch = RectifiedFlowMultistepScheduler(num_train_timesteps=1000, shifting=None, base_resolution=None, sampler="LinearQuadratic")
+  state = sch.set_timesteps(sch.create_state(), 5, shape)
+  assert torch.allclose(state.timesteps, torch.tensor([1.0, 0.9875, 0.975, 0.858333, 0.533333]), atol=1e-5)
+  x = torch.randn(shape, generator=g)
+  idx = [17 + 2731 * k for k in range(12)]
+  for t, (vals, mean, mean_abs) in zip(state.timesteps, _RF_GOLDEN):
+    x, state = sch.step(state, torch.randn(shape, generator=g), t, x)
+    flat = x.reshape(-1).double()
+    assert torch.allclose(flat[idx], torch.tensor(vals, dtype=torch.float64), atol=2e-6)
+    assert abs(float(flat.mean()) - mean) < 1e-6 and abs(float(flat.abs().mean()) - mean_abs) < 2e-6
+  # the schedule is 1 - sigma, ends one step short of 0, and is a single value for one step
+  assert linear_quadratic_schedule(1).tolist() == [1.0]
+  lq = linear_quadratic_schedule(40)
+  assert lq[0] == 1.0 and bool((lq[1:] < lq[:-1]).all()) and abs(float(lq[20]) - 0.975) < 1e-6
+
+
+def test_rectified_flow_samplers_and_resolution_shifts():
+  from maxdiffusion_b200.schedulers.scheduling_rectified_flow import RectifiedFlowMultistepScheduler, time_shift
+
+  uni = torch.linspace(1.0, 0.25, 4)
+  const = RectifiedFlowMultistepScheduler(sampler="Constant", shift=1.5)
+  assert torch.allclose(const.set_timesteps(const.create_state(), 4).timesteps, time_shift(1.5, 1.0, uni))
+  with pytest.raises(ValueError, match="shift"):
+    RectifiedFlowMultistepScheduler(sampler="Constant").set_timesteps(RectifiedFlowMultistepScheduler().create_state(), 4)
+  with pytest.raises(ValueError, match="not supported"):
+    RectifiedFlowMultistepScheduler(sampler="Cosine").set_timesteps(RectifiedFlowMultistepScheduler().create_state(), 4)
+  # SimpleDiffusion: logit(t) + log(tokens / base): more tokens than the base resolution push every timestep up
+  sd = RectifiedFlowMultistepScheduler(shifting="SimpleDiffusion", base_resolution=32 * 32)
+  ts = sd.set_timesteps(sd.create_state(), 4, (1, 8, 4, 32, 32)).timesteps
+  want = torch.sigmoid(torch.logit(uni.clamp(max=1 - 1e-8)) + math.log(4 * 32 * 32 / (32 * 32)))
+  assert torch.allclose(ts[1:], want[1:], atol=1e-6) and bool((ts[1:] > uni[1:]).all())
+  same = sd.set_timesteps(sd.create_state(), 4, (1, 8, 1, 32, 32)).timesteps
+  assert torch.allclose(same[1:], uni[1:], atol=1e-6)
+  # SD3 with a terminal value: the last timestep lands on it; without SD3 shifting the terminal is not applied
+  sd3 = RectifiedFlowMultistepScheduler(shifting="SD3", target_shift_terminal=0.1)
+  assert abs(float(sd3.set_timesteps(sd3.create_state(), 6, (1, 2048, 64)).timesteps[-1]) - 0.1) < 1e-6
+  plain = RectifiedFlowMultistepScheduler(target_shift_terminal=0.1)
+  assert torch.allclose(plain.set_timesteps(plain.create_state(), 4, (1, 2048, 64)).timesteps, uni)
+
+
+# Full-loop values asserted by the reference's scheduler tests (src/maxdiffusion/tests/legacy_hf_tests/schedulers/
+# test_scheduler_flax.py:607-643,903-939 and test_scheduler_unipc.py:445-465,500-531), which go back to the PyTorch
+# implementations the reference was ported from. Procedure there: the sample is arange(768) / 768 laid out as
+# [3, 8, 8, 4] and moved to [4, 3, 8, 8]; the "model" is x * t / (t + 1); 10 inference steps on the linear beta schedule.
+def _deterministic_sample(reverse=False):
+  n = 4 * 3 * 8 * 8
+  base = torch.arange(n, dtype=torch.float32)
+  return ((base.flip(-1) if reverse else base).reshape(3, 8, 8, 4) / n).permute(3, 0, 1, 2).contiguous()
+
+
+def _full_loop(sch, start=0, noise=None):
+  state = sch.set_timesteps(sch.create_state(), 10, (4, 3, 8, 8))
+  x = _deterministic_sample()
+  ts = state.timesteps[start:]
+  if noise is not None:
+    x = sch.add_noise(state, x, noise, ts[:1])
+  for t in ts:
+    x, state = sch.step(state, x * t / (t + 1), t, x)
+  return float(x.abs().sum()), float(x.abs().mean())
+
+
+@pytest.mark.parametrize("kw,want_sum,want_mean", [({}, 172.0067, 0.223967),
+                                                   ({"set_alpha_to_one": True, "beta_start": 0.01}, 149.8295, 0.1951),
+                                                   ({"set_alpha_to_one": False, "beta_start": 0.01}, 149.0784, 0.1941)])
+def test_ddim_full_loop_matches_the_reference_values(kw, want_sum, want_mean):
+  cfg = dict(num_train_timesteps=1000, beta_start=0.0001, beta_end=0.02, beta_schedule="linear")
+  got_sum, got_mean = _full_loop(DDIMScheduler(**{**cfg, **kw}))
+  assert abs(got_sum - want_sum) < 1e-2 and abs(got_mean - want_mean) < 1e-3
+
+
+@pytest.mark.parametrize("kw,want_sum,want_mean", [({}, 198.1318, 0.2580),
+                                                   ({"set_alpha_to_one": True, "beta_start": 0.01}, 186.9466, 0.24342),
+                                                   ({"set_alpha_to_one": False, "beta_start": 0.01}, 186.9482, 0.2434)])
+def test_pndm_with_runge_kutta_warm_up_matches_the_reference_values(kw, want_sum, want_mean):
+  cfg = dict(num_train_timesteps=1000, beta_start=0.0001, beta_end=0.02, beta_schedule="linear", skip_prk_steps=False)
+  sch = PNDMScheduler(**{**cfg, **kw})
+  state = sch.set_timesteps(sch.create_state(), 10, (4, 3, 8, 8))
+  assert state.prk_timesteps.tolist() == [900, 850, 850, 800, 800, 750, 750, 700, 700, 650, 650, 600]
+  assert state.plms_timesteps.tolist() == [600, 500, 400, 300, 200, 100, 0]
+  got_sum, got_mean = _full_loop(sch)
+  assert abs(got_sum - want_sum) < 1e-2 and abs(got_mean - want_mean) < 1e-3
+  with pytest.raises(ValueError, match="three earlier model outputs"):
+    sch.step_plms(state, torch.zeros(1), 100, torch.zeros(1))
+
+
+def test_unipc_on_the_beta_schedule_matches_the_reference_values():
+  cfg = dict(num_train_timesteps=1000, beta_start=0.0001, beta_end=0.02, beta_schedule="linear", solver_order=2,
+             solver_type="bh2", final_sigmas_type="sigma_min", use_flow_sigmas=False)
+  assert abs(_full_loop(UniPCMultistepScheduler(prediction_type="epsilon", **cfg))[1] - 0.2464) < 1e-3
+  assert abs(_full_loop(UniPCMultistepScheduler(prediction_type="v_prediction", **cfg))[1] - 0.1014) < 1e-3
+  # image-to-image: noise is added at the 9th timestep and the loop runs from there -- the first step has to find its
+  # place in the schedule from its timestep
+  got_sum, got_mean = _full_loop(UniPCMultistepScheduler(prediction_type="epsilon", **cfg), start=8,
+                                 noise=_deterministic_sample(reverse=True))
+  assert abs(got_sum - 315.5757) < 1e-2 and abs(got_mean - 0.4109) < 1e-3
+
+
+def test_ddpm_variance_matches_the_reference_values():
+  sch = DDPMScheduler()
+  state = sch.create_state()
+  for t, want in ((0, 0.0), (487, 0.00979), (999, 0.02)):
+    assert abs(float(sch._variance(state, t, t - 1)) - want) < 1e-5
