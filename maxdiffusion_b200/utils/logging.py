@@ -31,12 +31,24 @@ class _RankFilter(_logging.Filter):
     return int(os.environ.get("RANK", "0")) == 0
 
 
+class _StderrHandler(_logging.StreamHandler):
+  """Writes to whatever `sys.stderr` is when a record is emitted, so that a redirection installed after the first
+  logger was created (a test's capture, a launcher's per-rank log file) still receives the output."""
+
+  def __init__(self):
+    _logging.Handler.__init__(self)
+
+  @property
+  def stream(self):
+    return sys.stderr
+
+
 def _configure() -> None:
   global _handler
   with _lock:
     if _handler is not None:
       return
-    _handler = _logging.StreamHandler(sys.stderr)
+    _handler = _StderrHandler()
     _handler.addFilter(_RankFilter())
     root = _logging.getLogger(_ROOT)
     root.addHandler(_handler)
