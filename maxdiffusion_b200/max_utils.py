@@ -107,15 +107,83 @@ def get_flash_block_sizes(config) -> Optional[dict]:
   return dict(sizes) if sizes else None
 
 
+@contextlib.contextmanager
+def _count_kernel_path_flops(total: list):
+  """While active, the products that this package runs on its own CUDA kernels add their FLOPs to `total[0]`.
+
+  Those kernels are called through ctypes and never reach PyTorch's dispatcher, so `FlopCounterMode` cannot see them.
+  The entry points of `ops.functional` are wrapped for the duration; a call that falls back to PyTorch operators
+  (CPU tensors, other dtypes) is left to `FlopCounterMode`, so nothing is counted twice."""
+  from .ops import functional as OF
+
+  saved = {name: getattr(OF, name) for name in ("linear", "linear_gated_residual", "attention", "conv2d")}
+
+  def rows_of(x):
+    return x.numel() // x.shape[-1]
+
+  def linear(x, weight, *a, **k):
+    if OF._fast(x) and x.shape[-1] % 8 == 0 and weight.shape[0] % 8 == 0:
+      total[0] += 2 * rows_of(x) * weight.shape[0] * weight.shape[1]
+    return saved["linear"](x, weight, *a, **k)
+
+  def linear_gated_residual(x, weight, *a, **k):
+    if OF._fast(x):
+      total[0] += 2 * rows_of(x) * weight.shape[0] * weight.shape[1]
+    return saved["linear_gated_residual"](x, weight, *a, **k)
+
+  def attention(q, k, v, *a, **kw):
+    if OF._fast(q) and q.shape[-1] % 8 == 0:
+      ks = list(k) if isinstance(k, (list, tuple)) else [k]
+      keys = sum(t.shape[1] for t in ks)
+      B, Sq, H, D = q.shape
+      total[0] += 4 * B * H * Sq * keys * D  # q.k and p.v
+    return saved["attention"](q, k, v, *a, **kw)
+
+  def conv2d(x, weight, bias=None, stride=1, padding=1, upsample=False):
+    y = saved["conv2d"](x, weight, bias, stride, padding, upsample)
+    kk = weight.shape[-1]
+    if OF._fast(x) and kk == 3:
+      # the 1x1 form goes through `linear` above; everything that is not the 3x3 kernel path is torch.conv2d
+      even = x.shape[2] % 2 == 0 and x.shape[3] % 2 == 0
+      pad = 0 if padding == "far" else int(padding)
+      if stride in (1, 2) and (stride == 1 or even) and ((stride == 1 and pad == 1) or (stride == 2 and pad in (0, 1))):
+        total[0] += 2 * y.shape[0] * y.shape[2] * y.shape[3] * weight.shape[0] * weight.shape[1] * kk * kk
+    return y
+
+  wrappers = {"linear": linear, "linear_gated_residual": linear_gated_residual, "attention": attention, "conv2d": conv2d}
+  try:
+    for name, fn in wrappers.items():
+      setattr(OF, name, fn)
+    yield
+  finally:
+    for name, fn in saved.items():
+      setattr(OF, name, fn)
+
+
+def _sdpa_cpu_flops(query_shape, key_shape, value_shape, *args, out_shape=None, **kwargs) -> int:
+  """q.k and p.v of the CPU flash kernel behind `scaled_dot_product_attention`; `FlopCounterMode` hands a formula the
+  SHAPES of the operands ([B, H, S, D])."""
+  B, H, Sq, D = query_shape
+  return 2 * B * H * Sq * key_shape[2] * D + 2 * B * H * Sq * key_shape[2] * value_shape[3]
+
+
 def calculate_model_tflops(module: torch.nn.Module, *example_inputs, train: bool = False, **example_kwargs) -> float:
-  """TFLOPs of one forward (x3 for training) counted by running the module under FlopCounterMode on meta-free CPU
-  or CUDA inputs; falls back to a traversal of Linear / Conv weights when the counter is unavailable."""
+  """TFLOPs of one forward (x3 for training: the backward runs two products per forward product), counted by running
+  the module once. PyTorch operators are counted by `FlopCounterMode` (with the CPU attention kernel added to its
+  table); the products that run on this package's own kernels are counted at their entry points. Falls back to a
+  traversal of Linear / Conv weights when the counter is unavailable.
+  Reference: src/maxdiffusion/max_utils.py:851-900 (`calculate_model_tflops`)."""
+  own = [0]
   try:
     from torch.utils.flop_counter import FlopCounterMode
 
-    with FlopCounterMode(display=False) as counter, torch.no_grad():
+    table = {}
+    cpu_sdpa = getattr(torch.ops.aten, "_scaled_dot_product_flash_attention_for_cpu", None)
+    if cpu_sdpa is not None:
+      table[cpu_sdpa] = _sdpa_cpu_flops
+    with FlopCounterMode(display=False, custom_mapping=table) as counter, torch.no_grad(), _count_kernel_path_flops(own):
       module(*example_inputs, **example_kwargs)
-    flops = counter.get_total_flops()
+    flops = counter.get_total_flops() + own[0]
   except Exception:
     flops = 0
     for m in module.modules():
