@@ -42,6 +42,32 @@ def block_for_count(length: int, count: int, align: int = 128) -> int:
   return -(-per // align) * align
 
 
+def local_tiled_seq_len(seq_len: int, attention: str, context_shards: int = 1, ulysses_shards: int = -1,
+                        row_multiple: int = 8) -> int:
+  """Key / query rows ONE attention launch of a rank tiles over, for a sequence of `seq_len` tokens split the way
+  production splits it (reference: src/maxdiffusion/utils/tile_size_grid_search.py `local_tiled_seq_len`).
+
+  The context axis holds `context_shards` ranks; every rank keeps ceil(seq_len / shards) tokens rounded up to
+  `row_multiple` (`ContextParallel.shard_sequence`: a shard has to start on a 16-byte boundary for the bulk copies).
+  ring: a launch sees one shard per segment; Ulysses: the whole padded sequence of a head group; Ulysses x ring: the
+  `ulysses_shards` shards of a Ulysses group joined; gather / local: the whole sequence."""
+  from ..common_types import context_strategy
+
+  strategy = context_strategy(attention)
+  if context_shards <= 1 or strategy in ("local", "gather"):
+    return seq_len
+  per = -(-seq_len // context_shards)
+  per = -(-per // row_multiple) * row_multiple
+  if strategy == "ring":
+    return per
+  if strategy == "ulysses":
+    return per * context_shards
+  u = ulysses_shards if ulysses_shards and ulysses_shards > 0 else 1
+  if context_shards % u != 0:
+    raise ValueError(f"the context axis ({context_shards} ranks) must be divisible by ulysses_shards ({u})")
+  return per * u
+
+
 def smem_bytes(c: Candidate, head_dim: int = 128, elem: int = 2) -> int:
   return (c.block_q + 2 * c.stages * c.block_kv) * head_dim * elem + 2048
 

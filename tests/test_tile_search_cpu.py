@@ -76,3 +76,19 @@ def test_cached_choice_is_registered_for_the_attention_launcher(tmp_path):
   assert K.load_flash_tuning(str(path)) == 1
   assert K._FLASH_TUNED[key] == (3, 16)
   K._FLASH_TUNED.clear()
+
+
+def test_local_tiled_sequence_length_follows_the_production_split():
+  import pytest
+
+  assert T.local_tiled_seq_len(6144, "tokamax_ring", context_shards=8) == 768
+  assert T.local_tiled_seq_len(6144, "ulysses_ring", context_shards=8, ulysses_shards=2) == 1536
+  assert T.local_tiled_seq_len(6144, "ulysses", context_shards=8) == 6144
+  assert T.local_tiled_seq_len(6144, "flash", context_shards=8) == 6144
+  # shards are padded to 8 rows (16-byte starts for the bulk copies): 32760 tokens on 8 ranks are 8 x 4096
+  assert T.local_tiled_seq_len(32760, "tokamax_ring", context_shards=8) == 4096
+  assert T.local_tiled_seq_len(10, "tokamax_ring", context_shards=4) == 8
+  assert T.local_tiled_seq_len(10, "tokamax_ring", context_shards=4, row_multiple=1) == 3
+  assert T.local_tiled_seq_len(10, "ulysses_ring", context_shards=4, ulysses_shards=2, row_multiple=1) == 6
+  with pytest.raises(ValueError, match="must be divisible"):
+    T.local_tiled_seq_len(6144, "ulysses_ring_custom", context_shards=8, ulysses_shards=3)
