@@ -69,6 +69,22 @@ def test_guidance_algebra():
   assert abs(calculate_shift(4096, 1024, 4096, 0.95, 2.05) - 2.05) < 1e-9
 
 
+def test_guidance_and_shift_reproduce_the_values_of_the_reference_tests():
+  """src/maxdiffusion/tests/ltx2/test_pipeline_ltx2.py:46-118: the shift at the ends and the middle of the token range,
+  two-way CFG on [unconditional, conditional] rows, and the four-way CFG + STG + modality combination."""
+  assert abs(calculate_shift(256) - 0.5) < 1e-12 and abs(calculate_shift(4096) - 1.15) < 1e-12
+  assert abs(calculate_shift((256 + 4096) / 2) - (0.5 + 1.15) / 2) < 1e-12
+  lat, alat = torch.tensor([[10.0]]), torch.tensor([[20.0]])
+  v, a = apply_ltx2_guidance(torch.tensor([[1.0], [3.0]]), torch.tensor([[2.0], [4.0]]), lat, alat, 2.0, 2.0, 0.0, 1.0, 0.0,
+                             None, None, None, 0.0, True, False)
+  assert v.tolist() == [[5.0]] and a.tolist() == [[6.0]]
+  four = torch.tensor([[1.0], [3.0], [4.0], [5.0]])
+  v, a = apply_ltx2_guidance(four, four, lat, lat, 2.0, 2.0, 1.0, 2.0, 0.0, None, None, None, 0.0, True, True)
+  assert torch.allclose(v, torch.tensor([[2.0]])) and torch.allclose(a, torch.tensor([[2.0]]))
+  cfg = torch.tensor([[[1.0, 2.0], [3.0, 4.0]]])
+  assert torch.equal(rescale_noise_cfg(cfg, torch.ones_like(cfg), 0.0), cfg)
+
+
 def test_video_vae_shapes_tiling_and_patch_order():
   torch.manual_seed(0)
   v = LTX2VideoAutoencoderKL(LTX2VAEConfig(**TINY_VAE)).eval()
