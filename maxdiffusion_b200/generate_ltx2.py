@@ -55,6 +55,11 @@ def run(config):
   t0 = time.perf_counter()
   pipe = LTX2Checkpointer(config).load_pipeline()
   max_logging.log(f"load_time: {time.perf_counter() - t0:.1f}s")
+  lora = config.get("lora_config", None) or {}
+  if config.get("enable_lora", False) and lora.get("lora_model_name_or_path"):
+    from .loaders.lora_loader import merge_ltx2_loras
+
+    merge_ltx2_loras(pipe, config)
   t0 = time.perf_counter()
   call_pipeline(config, pipe, num_inference_steps=2, output_type="latent")  # warm-up
   max_logging.log(f"warmup_time: {time.perf_counter() - t0:.1f}s")

@@ -117,6 +117,84 @@ def merge_lora_into_wan(model, lora_sd: Dict[str, torch.Tensor], scale: float = 
   return merged
 
 
+# first component of a module path in the original LTX-2 checkpoint (the namespace LoRA files use) -> this package's
+# (diffusers-named) module; everything else -- `transformer_blocks.N.*`, the caption projections, `proj_out` -- has the
+# same name on both sides (reference: src/maxdiffusion/loaders/lora_conversion_utils.py:708-823)
+_LTX2_ROOTS = {
+    "patchify_proj": "proj_in", "audio_patchify_proj": "audio_proj_in", "adaln_single": "time_embed",
+    "audio_adaln_single": "audio_time_embed", "av_ca_a2v_gate_adaln_single": "av_cross_attn_video_a2v_gate",
+    "av_ca_v2a_gate_adaln_single": "av_cross_attn_audio_v2a_gate",
+    "av_ca_audio_scale_shift_adaln_single": "av_cross_attn_audio_scale_shift",
+    "av_ca_video_scale_shift_adaln_single": "av_cross_attn_video_scale_shift", "prompt_adaln_single": "prompt_adaln",
+    "audio_prompt_adaln_single": "audio_prompt_adaln",
+}
+_LTX2_CONNECTOR_PREFIX = "text_embedding_projection."
+
+
+def _ltx2_target(path: str) -> str:
+  head, _, rest = path.partition(".")
+  return (_LTX2_ROOTS[head] + ("." + rest if rest else "")) if head in _LTX2_ROOTS else path
+
+
+@torch.no_grad()
+def _merge_entry(params: dict, target: str, entry: dict, scale: float) -> bool:
+  w = params.get(target + ".weight")
+  if w is None:
+    return False
+  delta = lora_delta(entry, scale)
+  if delta is not None:
+    if delta.shape != w.shape:
+      raise ValueError(f"LoRA delta of {target} has shape {tuple(delta.shape)}, the weight {tuple(w.shape)}")
+    w += delta.to(w.device, w.dtype)
+  if "diff" in entry:
+    w += entry["diff"].to(w.device, w.dtype) * scale
+  if "diff_b" in entry and target + ".bias" in params:
+    params[target + ".bias"] += entry["diff_b"].to(w.device, w.dtype) * scale
+  return delta is not None or "diff" in entry or "diff_b" in entry
+
+
+@torch.no_grad()
+def merge_lora_into_ltx2(transformer, lora_sd: Dict[str, torch.Tensor], scale: float = 1.0, connectors=None) -> dict:
+  """Adds the deltas of an LTX-2 LoRA file to the transformer (keys under `diffusion_model.`, original module names or
+  diffusers names) and to the text connectors (keys under `text_embedding_projection.`: `aggregate_embed` is the feature
+  extractor's projection). Returns {"transformer": merged modules, "connectors": merged modules, "unmatched": [paths]}
+  (reference: src/maxdiffusion/loaders/ltx2_lora_nnx_loader.py:32-83)."""
+  t_params = dict(transformer.named_parameters())
+  c_params = dict(connectors.named_parameters()) if connectors is not None else {}
+  report = {"transformer": 0, "connectors": 0, "unmatched": []}
+  for path, entry in parse_lora_dict(lora_sd).items():
+    if path.startswith(_LTX2_CONNECTOR_PREFIX):
+      inner = path[len(_LTX2_CONNECTOR_PREFIX):]
+      names = ["feature_extractor.linear", "feature_extractor.video_linear"] if inner == "aggregate_embed" else [inner]
+      done = any(_merge_entry(c_params, n, entry, scale) for n in names)
+      report["connectors" if done else "unmatched"] = (report["connectors"] + 1) if done else report["unmatched"] + [path]
+      continue
+    done = _merge_entry(t_params, _ltx2_target(path), entry, scale)
+    if done:
+      report["transformer"] += 1
+    else:
+      report["unmatched"].append(path)
+  return report
+
+
+def merge_ltx2_loras(pipe, config) -> list:
+  """Merges every file of `lora_config` (`lora_model_name_or_path`, `weight_name`, `scale`) into the pipeline."""
+  from safetensors.torch import load_file
+
+  from .. import max_logging
+
+  lc = config.lora_config
+  paths = lc["lora_model_name_or_path"]
+  reports = []
+  for path, name, scale in zip(paths, lc.get("weight_name", [None] * len(paths)), lc.get("scale", [1.0] * len(paths))):
+    file = os.path.join(path, name) if (name and os.path.isdir(path)) else path
+    rep = merge_lora_into_ltx2(pipe.transformer, load_file(file), float(scale), getattr(pipe, "connectors", None))
+    max_logging.log(f"LoRA {file}: {rep['transformer']} transformer and {rep['connectors']} connector modules merged"
+                    + (f", {len(rep['unmatched'])} key(s) routed to no module: {rep['unmatched'][:8]}" if rep["unmatched"] else ""))
+    reports.append(rep)
+  return reports
+
+
 def merge_wan_loras(pipe, config) -> None:
   from safetensors.torch import load_file
 

@@ -144,3 +144,69 @@ def test_flux_adapters_in_three_namings_equal_the_merged_fused_weights(style):
     got = model(x, txt, pooled, tt, img_ids, txt_ids, guidance)
     want = merged(x, txt, pooled, tt, img_ids, txt_ids, guidance)
   assert torch.allclose(got, want, atol=2e-4, rtol=1e-3)
+
+
+def test_ltx2_lora_in_the_original_key_namespace_merges_into_transformer_and_connectors(tmp_path):
+  """Keys as LTX-2 LoRA files carry them: `diffusion_model.` + the ORIGINAL module names (`patchify_proj`,
+  `adaln_single`, `av_ca_*_adaln_single`, blocks as they are) and `text_embedding_projection.aggregate_embed` for the
+  connectors' feature projection. Every delta must land as W + scale * alpha / rank * up @ down."""
+  from safetensors.torch import save_file
+
+  from maxdiffusion_b200 import pyconfig
+  from maxdiffusion_b200.loaders.lora_loader import merge_lora_into_ltx2, merge_ltx2_loras
+  from maxdiffusion_b200.models.ltx2.transformer_ltx2 import LTX2Config, LTX2VideoTransformer3DModel
+
+  torch.manual_seed(0)
+  cfg = LTX2Config(in_channels=8, out_channels=8, num_attention_heads=2, attention_head_dim=32, cross_attention_dim=64,
+                   audio_in_channels=16, audio_out_channels=16, audio_num_attention_heads=2, audio_attention_head_dim=16,
+                   audio_cross_attention_dim=32, num_layers=2, caption_channels=32)
+  model = LTX2VideoTransformer3DModel(cfg)
+  connectors = torch.nn.Module()
+  connectors.feature_extractor = torch.nn.Module()
+  connectors.feature_extractor.linear = torch.nn.Linear(24, 16, bias=False)
+  before = {n: p.detach().clone() for n, p in model.named_parameters()}
+  c_before = connectors.feature_extractor.linear.weight.detach().clone()
+  ours_to_file = {"proj_in": "patchify_proj", "audio_proj_in": "audio_patchify_proj", "time_embed.linear": "adaln_single.linear",
+                  "audio_time_embed.emb.timestep_embedder.linear_1": "audio_adaln_single.emb.timestep_embedder.linear_1",
+                  "av_cross_attn_video_a2v_gate.linear": "av_ca_a2v_gate_adaln_single.linear",
+                  "av_cross_attn_audio_scale_shift.linear": "av_ca_audio_scale_shift_adaln_single.linear",
+                  "transformer_blocks.1.attn1.to_out.0": "transformer_blocks.1.attn1.to_out.0",
+                  "transformer_blocks.0.audio_to_video_attn.to_q": "transformer_blocks.0.audio_to_video_attn.to_q",
+                  "transformer_blocks.1.ff.net.0.proj": "transformer_blocks.1.ff.net.0.proj",
+                  "transformer_blocks.0.audio_ff.net.2": "transformer_blocks.0.audio_ff.net.2",
+                  "caption_projection.linear_2": "caption_projection.linear_2", "proj_out": "proj_out"}
+  rank, alpha, scale = 4, 2.0, 0.5
+  sd, want = {}, {}
+  for ours, theirs in ours_to_file.items():
+    w = before[ours + ".weight"]
+    down, up = torch.randn(rank, w.shape[1]) * 0.1, torch.randn(w.shape[0], rank) * 0.1
+    sd[f"diffusion_model.{theirs}.lora_A.weight"], sd[f"diffusion_model.{theirs}.lora_B.weight"] = down, up
+    sd[f"diffusion_model.{theirs}.alpha"] = torch.tensor(alpha)
+    want[ours] = w + scale * alpha / rank * up @ down
+  cd, cu = torch.randn(rank, 24) * 0.1, torch.randn(16, rank) * 0.1
+  sd["text_embedding_projection.aggregate_embed.lora_A.weight"], sd["text_embedding_projection.aggregate_embed.lora_B.weight"] = cd, cu
+  sd["diffusion_model.not_a_module.lora_A.weight"], sd["diffusion_model.not_a_module.lora_B.weight"] = cd, cu
+  rep = merge_lora_into_ltx2(model, sd, scale, connectors)
+  assert rep == {"transformer": len(ours_to_file), "connectors": 1, "unmatched": ["not_a_module"]}
+  after = dict(model.named_parameters())
+  for ours in ours_to_file:
+    assert torch.allclose(after[ours + ".weight"], want[ours], atol=1e-6), ours
+  untouched = [n for n in before if n.rsplit(".", 1)[0] not in ours_to_file]
+  assert untouched and all(torch.equal(after[n], before[n]) for n in untouched)
+  assert torch.allclose(connectors.feature_extractor.linear.weight, c_before + scale * cu @ cd, atol=1e-6)  # alpha = rank
+
+  # through the configuration: a folder + file name, scale from `lora_config`
+  save_file({k: v.clone().contiguous() for k, v in sd.items()}, str(tmp_path / "cam.safetensors"))
+  config = pyconfig.initialize(
+      ["x", "maxdiffusion_b200/configs/ltx2_video.yml", "log_config=false", "enable_lora=True",
+       'lora_config={"lora_model_name_or_path": ["%s"], "weight_name": ["cam.safetensors"], "scale": [0.5], "rank": [4], '
+       '"adapter_name": ["cam"], "from_pt": []}' % tmp_path], unittest=True)
+  pipe = torch.nn.Module()
+  pipe.transformer, pipe.connectors = LTX2VideoTransformer3DModel(cfg), connectors
+  pipe.transformer.load_state_dict(before)
+  merge_ltx2_loras(pipe, config)
+  again = dict(pipe.transformer.named_parameters())
+  assert all(torch.allclose(again[o + ".weight"], want[o], atol=1e-6) for o in ours_to_file)
+  with pytest.raises(ValueError, match="has shape"):
+    merge_lora_into_ltx2(model, {"diffusion_model.proj_out.lora_A.weight": torch.zeros(2, 3),
+                                 "diffusion_model.proj_out.lora_B.weight": torch.zeros(5, 2)})
