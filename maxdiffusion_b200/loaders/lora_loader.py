@@ -81,10 +81,10 @@ def _wan_target(path: str):
   m = re.match(r"blocks\.(\d+)\.ffn\.net\.(0\.proj|2)$", path)
   if m:
     return f"blocks.{m.group(1)}.{'ffn_in' if m.group(2) != '2' else 'ffn_out'}", None
-  m = re.match(r"blocks\.(\d+)\.(self_attn|cross_attn)\.(q|k|v|o)$", path)  # original Wan repo naming
+  m = re.match(r"blocks\.(\d+)\.(self_attn|cross_attn)\.(q|k|v|o|k_img|v_img)$", path)  # original Wan repo naming
   if m:
     i, attn, proj = m.groups()
-    mapped = {"q": "to_q", "k": "to_k", "v": "to_v", "o": "to_out.0"}[proj]
+    mapped = {"q": "to_q", "k": "to_k", "v": "to_v", "o": "to_out.0", "k_img": "add_k_proj", "v_img": "add_v_proj"}[proj]
     return _wan_target(f"blocks.{i}.{'attn1' if attn == 'self_attn' else 'attn2'}.{mapped}")
   m = re.match(r"blocks\.(\d+)\.ffn\.(0|2)$", path)
   if m:
@@ -92,28 +92,93 @@ def _wan_target(path: str):
   return None, None
 
 
+# modules outside the blocks: original Wan name (and the diffusers name) -> module of this package
+_WAN_ROOT_MODULES = {
+    "text_embedding.0": "condition_embedder.text_in", "text_embedding.2": "condition_embedder.text_out",
+    "time_embedding.0": "condition_embedder.time_in", "time_embedding.2": "condition_embedder.time_out",
+    "time_projection.1": "condition_embedder.time_proj", "patch_embedding": "patch_embedding", "head.head": "proj_out",
+    "img_emb.proj.0": "condition_embedder.image_embedder.norm1", "img_emb.proj.1": "condition_embedder.image_embedder.ff_in",
+    "img_emb.proj.3": "condition_embedder.image_embedder.ff_out", "img_emb.proj.4": "condition_embedder.image_embedder.norm2",
+    "condition_embedder.text_embedder.linear_1": "condition_embedder.text_in",
+    "condition_embedder.text_embedder.linear_2": "condition_embedder.text_out",
+    "condition_embedder.time_embedder.linear_1": "condition_embedder.time_in",
+    "condition_embedder.time_embedder.linear_2": "condition_embedder.time_out",
+    "condition_embedder.time_proj": "condition_embedder.time_proj",
+    "condition_embedder.image_embedder.norm1": "condition_embedder.image_embedder.norm1",
+    "condition_embedder.image_embedder.ff.net.0.proj": "condition_embedder.image_embedder.ff_in",
+    "condition_embedder.image_embedder.ff.net.2": "condition_embedder.image_embedder.ff_out",
+    "condition_embedder.image_embedder.norm2": "condition_embedder.image_embedder.norm2", "proj_out": "proj_out",
+}
+
+
+def _wan_plain_parameter(path: str):
+  """LoRA paths whose target is a bare parameter (a `.diff` adds to it): q/k norm weights, the affine norm of a block
+  and the modulation tables. Returns (parameter for `.diff`, parameter for `.diff_b`)."""
+  if path in ("head.modulation", "head", "scale_shift_table"):      # `head.diff_m` arrives as `head.modulation.diff`
+    return "scale_shift_table", None
+  m = re.match(r"blocks\.(\d+)\.(.+)$", path)
+  if not m:
+    return None, None
+  i, rest = m.groups()
+  names = {"self_attn.norm_q": "attn1.norm_q", "self_attn.norm_k": "attn1.norm_k", "cross_attn.norm_q": "attn2.norm_q",
+           "cross_attn.norm_k": "attn2.norm_k", "cross_attn.norm_k_img": "attn2.norm_added_k", "attn1.norm_q": "attn1.norm_q",
+           "attn1.norm_k": "attn1.norm_k", "attn2.norm_q": "attn2.norm_q", "attn2.norm_k": "attn2.norm_k",
+           "attn2.norm_added_k": "attn2.norm_added_k", "modulation": "scale_shift_table", "scale_shift_table": "scale_shift_table"}
+  if rest in names:
+    return f"blocks.{i}.{names[rest]}", None
+  if rest in ("norm3", "norm2"):                                     # the affine LayerNorm before cross-attention
+    return f"blocks.{i}.norm2_weight", f"blocks.{i}.norm2_bias"
+  return None, None
+
+
+def preprocess_wan_lora_dict(sd: Dict[str, torch.Tensor]) -> Dict[str, torch.Tensor]:
+  """`<module>.diff_m` (a delta of the module's modulation table) becomes `<module>.modulation.diff`
+  (reference: src/maxdiffusion/loaders/lora_conversion_utils.py:613-624)."""
+  return {(k[:-len(".diff_m")] + ".modulation.diff" if k.endswith(".diff_m") else k): v for k, v in sd.items()}
+
+
 @torch.no_grad()
 def merge_lora_into_wan(model, lora_sd: Dict[str, torch.Tensor], scale: float = 1.0) -> int:
-  """Adds the LoRA deltas to the (fused) Wan weights in place. Returns the number of merged modules."""
+  """Adds the LoRA deltas to the (fused) Wan weights in place. Returns the number of merged modules.
+
+  Targets: the attention and FFN projections of every block (low-rank pairs, `.diff`, `.diff_b`), the embedders, the
+  time projection, the patch embedding and the output head, and the `.diff` deltas of bare parameters: q/k norm
+  weights, the affine norm of a block, the modulation tables of the blocks and of the head
+  (reference: src/maxdiffusion/loaders/lora_conversion_utils.py:627-705)."""
   params = dict(model.named_parameters())
   merged = 0
-  for path, entry in parse_lora_dict(lora_sd).items():
+  for path, entry in parse_lora_dict(preprocess_wan_lora_dict(lora_sd)).items():
     target, part = _wan_target(path)
+    if target is None and path in _WAN_ROOT_MODULES:
+      target = _WAN_ROOT_MODULES[path]
     if target is None or target + ".weight" not in params:
+      p_diff, p_bias = _wan_plain_parameter(path)
+      done = False
+      if p_diff in params and "diff" in entry:
+        params[p_diff] += entry["diff"].to(params[p_diff].device, params[p_diff].dtype).reshape(params[p_diff].shape) * scale
+        done = True
+      if p_bias in params and "diff_b" in entry:
+        params[p_bias] += entry["diff_b"].to(params[p_bias].device, params[p_bias].dtype).reshape(params[p_bias].shape) * scale
+        done = True
+      merged += int(done)
       continue
     w = params[target + ".weight"]
     rows = slice(None)
     if part is not None:
       n = w.shape[0] // part[1]
       rows = slice(part[0] * n, (part[0] + 1) * n)
+    done = False
     delta = lora_delta(entry, scale)
     if delta is not None:
-      w[rows] += delta.to(w.device, w.dtype)
-      merged += 1
+      w[rows] += delta.to(w.device, w.dtype).reshape(w[rows].shape)     # the patch embedding is a flattened conv kernel
+      done = True
     if "diff" in entry:
-      w[rows] += entry["diff"].to(w.device, w.dtype) * scale
+      w[rows] += entry["diff"].to(w.device, w.dtype).reshape(w[rows].shape) * scale
+      done = True
     if "diff_b" in entry and target + ".bias" in params:
       params[target + ".bias"][rows] += entry["diff_b"].to(w.device, w.dtype) * scale
+      done = True
+    merged += int(done)
   return merged
 
 
@@ -196,13 +261,27 @@ def merge_ltx2_loras(pipe, config) -> list:
 
 
 def merge_wan_loras(pipe, config) -> None:
+  """Merges every entry of `lora_config`. Wan 2.1: `weight_name[i]` goes into the transformer. Wan 2.2 (two experts):
+  `high_noise_weight_name[i]` into the high-noise expert and `low_noise_weight_name[i]` into the low-noise one; an entry
+  that only has `weight_name` goes into both (reference: src/maxdiffusion/loaders/wan_lora_nnx_loader.py:25-111)."""
   from safetensors.torch import load_file
 
   lc = config.lora_config
-  for path, name, scale in zip(lc["lora_model_name_or_path"], lc["weight_name"], lc.get("scale", [1.0] * 99)):
-    sd = load_file(os.path.join(path, name) if os.path.isdir(path) else path)
+  paths = lc["lora_model_name_or_path"]
+  pick = lambda key, i: (lc.get(key) or [None] * (i + 1))[i] if i < len(lc.get(key) or []) else None
+  for i, path in enumerate(paths):
+    scale = float((lc.get("scale") or [1.0] * len(paths))[i])
+    resolve = lambda name: os.path.join(path, name) if (name and os.path.isdir(path)) else path
+    high, low, both = pick("high_noise_weight_name", i), pick("low_noise_weight_name", i), pick("weight_name", i)
+    if pipe.transformer_2 is not None and (high or low):
+      if high:
+        merge_lora_into_wan(pipe.transformer, load_file(resolve(high)), scale)
+      if low:
+        merge_lora_into_wan(pipe.transformer_2, load_file(resolve(low)), scale)
+      continue
+    sd = load_file(resolve(both))
     for m in filter(None, (pipe.transformer, pipe.transformer_2)):
-      merge_lora_into_wan(m, sd, float(scale))
+      merge_lora_into_wan(m, sd, scale)
 
 
 class LoRALinear(nn.Module):

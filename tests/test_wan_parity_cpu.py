@@ -235,7 +235,7 @@ def test_lora_merge_equals_w_plus_scaled_up_down():
   assert torch.allclose(lora_delta(parsed["blocks.1.attn2.to_v"], 0.5),
                         0.5 * (2.0 / r) * lora["diffusion_model.blocks.1.attn2.to_v.lora_up.weight"] @ lora["diffusion_model.blocks.1.attn2.to_v.lora_down.weight"])
   n = merge_lora_into_wan(ours, lora, scale=0.5)
-  assert n == 3
+  assert n == 4  # three low-rank pairs and one module with `.diff` / `.diff_b` only
   after = ours.state_dict()
   k_rows = slice(DIM, 2 * DIM)  # to_k inside to_qkv
   d = 0.5 * lora["transformer.blocks.0.attn1.to_k.lora_B.weight"] @ lora["transformer.blocks.0.attn1.to_k.lora_A.weight"]
@@ -251,3 +251,66 @@ def test_lora_merge_equals_w_plus_scaled_up_down():
   untouched = [k for k in before if k not in ("blocks.0.attn1.to_qkv.weight", "blocks.1.attn2.to_kv.weight", "blocks.1.ffn_out.weight",
                                               "blocks.0.attn1.to_out.weight", "blocks.0.attn1.to_out.bias")]
   assert all(torch.equal(before[k], after[k]) for k in untouched)
+
+
+def test_lora_in_the_original_wan_naming_reaches_embedders_norms_and_modulation_tables(tmp_path):
+  """Distilled-step LoRA files of the original repository carry, beside the projections, deltas for the embedders,
+  the head, q/k norm weights (`.diff`), the block norm (`norm3.diff` / `.diff_b`) and the modulation tables
+  (`blocks.N.diff_m`, `head.diff_m`); reference: src/maxdiffusion/loaders/lora_conversion_utils.py:613-705. Wan 2.2
+  entries name one file per expert (wan_lora_nnx_loader.py:64-111)."""
+  import types
+
+  from safetensors.torch import save_file
+
+  from maxdiffusion_b200.loaders.lora_loader import merge_wan_loras
+
+  _, ours, cfg = _models()
+  before = {k: v.clone() for k, v in ours.state_dict().items()}
+  torch.manual_seed(5)
+  r, s = 2, 0.5
+  pair = lambda name: (torch.randn(r, before[name].shape[1]) * 0.1, torch.randn(before[name].shape[0], r) * 0.1)
+  lin = {"text_embedding.0": "condition_embedder.text_in", "text_embedding.2": "condition_embedder.text_out",
+         "time_embedding.0": "condition_embedder.time_in", "time_embedding.2": "condition_embedder.time_out",
+         "time_projection.1": "condition_embedder.time_proj", "head.head": "proj_out", "patch_embedding": "patch_embedding",
+         "blocks.0.self_attn.o": "blocks.0.attn1.to_out", "blocks.1.ffn.0": "blocks.1.ffn_in"}
+  lora, want = {}, {}
+  for theirs, mine in lin.items():
+    down, up = pair(mine + ".weight")
+    lora[f"diffusion_model.{theirs}.lora_down.weight"], lora[f"diffusion_model.{theirs}.lora_up.weight"] = down, up
+    want[mine + ".weight"] = before[mine + ".weight"] + s * up @ down
+  vec = {"blocks.0.self_attn.norm_q": "blocks.0.attn1.norm_q", "blocks.1.cross_attn.norm_k": "blocks.1.attn2.norm_k"}
+  for theirs, mine in vec.items():
+    lora[f"diffusion_model.{theirs}.diff"] = torch.randn_like(before[mine])
+    want[mine] = before[mine] + s * lora[f"diffusion_model.{theirs}.diff"]
+  lora["diffusion_model.blocks.1.norm3.diff"], lora["diffusion_model.blocks.1.norm3.diff_b"] = torch.randn(DIM), torch.randn(DIM)
+  want["blocks.1.norm2_weight"] = before["blocks.1.norm2_weight"] + s * lora["diffusion_model.blocks.1.norm3.diff"]
+  want["blocks.1.norm2_bias"] = before["blocks.1.norm2_bias"] + s * lora["diffusion_model.blocks.1.norm3.diff_b"]
+  lora["diffusion_model.blocks.0.diff_m"], lora["diffusion_model.head.diff_m"] = torch.randn(1, 6, DIM), torch.randn(1, 2, DIM)
+  want["blocks.0.scale_shift_table"] = before["blocks.0.scale_shift_table"] + s * lora["diffusion_model.blocks.0.diff_m"]
+  want["scale_shift_table"] = before["scale_shift_table"] + s * lora["diffusion_model.head.diff_m"]
+  lora["diffusion_model.text_embedding.0.diff_b"] = torch.randn(DIM)
+  want["condition_embedder.text_in.bias"] = before["condition_embedder.text_in.bias"] + s * lora["diffusion_model.text_embedding.0.diff_b"]
+  assert merge_lora_into_wan(ours, lora, scale=s) == len(lin) + len(vec) + 3
+  after = ours.state_dict()
+  for k in before:
+    assert torch.allclose(after[k], want.get(k, before[k]), atol=1e-6), k
+
+  # Wan 2.2: one file per expert; an entry with `weight_name` only goes into both
+  hi, lo = {k: v.clone() for k, v in lora.items() if "text_embedding" in k}, {k: v.clone() for k, v in lora.items() if "head" in k}
+  save_file(hi, str(tmp_path / "high.safetensors"))
+  save_file(lo, str(tmp_path / "low.safetensors"))
+  _, a, _ = _models()
+  _, b, _ = _models()
+  pipe = types.SimpleNamespace(transformer=a, transformer_2=b)
+  config = types.SimpleNamespace(lora_config={"lora_model_name_or_path": [str(tmp_path), str(tmp_path)], "scale": [s, s],
+                                              "high_noise_weight_name": ["high.safetensors", None],
+                                              "low_noise_weight_name": ["low.safetensors", None],
+                                              "weight_name": [None, "low.safetensors"]})
+  merge_wan_loras(pipe, config)
+  sa, sb = a.state_dict(), b.state_dict()
+  assert torch.allclose(sa["condition_embedder.text_in.weight"], want["condition_embedder.text_in.weight"], atol=1e-6)
+  assert torch.equal(sb["condition_embedder.text_in.weight"], before["condition_embedder.text_in.weight"])
+  # the head deltas: once into the high-noise expert (second entry), twice into the low-noise one (first + second entry)
+  d = want["proj_out.weight"] - before["proj_out.weight"]
+  assert torch.allclose(sa["proj_out.weight"], before["proj_out.weight"] + d, atol=1e-6)
+  assert torch.allclose(sb["proj_out.weight"], before["proj_out.weight"] + 2 * d, atol=1e-6)
