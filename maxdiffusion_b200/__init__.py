@@ -91,6 +91,9 @@ _EXPORTS = {
     "make_custom_ring_attention": (".kernels", "make_custom_ring_attention"),
     "KERNEL_REGISTRY": (".kernels", "KERNEL_REGISTRY"),
     "create_device_mesh": (".parallel.mesh", "create_device_mesh"),
+    "ConfigMixin": (".configuration_utils", "ConfigMixin"),
+    "FrozenDict": (".configuration_utils", "FrozenDict"),
+    "register_to_config": (".configuration_utils", "register_to_config"),
 }
 
 def __getattr__(name):

@@ -40,6 +40,22 @@ def _json(folder: str) -> dict:
     return json.load(f)
 
 
+def upsampler_kind_from_filename(filename: str) -> dict:
+  """Constructor arguments of the latent up-sampler that its weights file name implies: which axes it doubles and by
+  what factor (`...spatial-upscaler-x2...`, `...temporal-upscaler...`, `...x1.5...`)."""
+  kw = {}
+  name = filename.lower()
+  if "temporal" in name:
+    kw.update(spatial_upsample=False, temporal_upsample=True)
+  elif "spatial" in name:
+    kw.update(spatial_upsample=True, temporal_upsample=False)
+  if "x1.5" in name:
+    kw["rational_spatial_scale"] = 1.5
+  elif "x2" in name:
+    kw["rational_spatial_scale"] = 2.0
+  return kw
+
+
 class LTX2Checkpointer:
 
   def __init__(self, config):
@@ -111,9 +127,20 @@ class LTX2Checkpointer:
       if os.path.isdir(folder) and not c.get("random_init", False):
         raw = _json(folder)
         kw.update({k: v for k, v in raw.items() if k in LTX2LatentUpsamplerModel.__init__.__code__.co_varnames})
+      # a single weights file beside the components (`upsampler_filename`, the LTX-2.3 layout) names what it does:
+      # "spatial" / "temporal" and the factor (reference: src/maxdiffusion/pipelines/ltx2/ltx2_pipeline.py:876-908)
+      filename = str(c.get("upsampler_filename", "") or "")
+      single = os.path.join(up_root, filename) if filename else ""
+      if filename:
+        kw.update(upsampler_kind_from_filename(filename))
       upsampler = LTX2LatentUpsamplerModel(**kw)
-      if os.path.isdir(folder) and not c.get("random_init", False):
-        self._load(upsampler, folder, torch.float32)
+      if not c.get("random_init", False):
+        if single and os.path.isfile(single):
+          from safetensors.torch import load_file
+
+          upsampler.load_state_dict({k: v.float() for k, v in load_file(single).items()}, strict=False)
+        elif os.path.isdir(folder):
+          self._load(upsampler, folder, torch.float32)
       upsampler = upsampler.to(device).eval()
     text_encoder = None
     if have("text_encoder"):

@@ -122,12 +122,15 @@ class _HyperParameters:
         raise ValueError(f"override '{item}' is not of the form key=value")
       key, text = item.split("=", 1)
       if key not in raw:
+        if key in TPU_ONLY_KEYS:      # steers the TPU runtime only: accepted whether or not the file lists it
+          overrides[key] = yaml.safe_load(text)
+          continue
         raise ValueError(f"Key {key} was passed at the command line but is not in the config file {argv[1]}")
       overrides[key] = _coerce(key, text, raw[key])
     for key, value in kwargs.items():
       if key in ("unittest", "validate_training"):
         continue
-      if key not in raw:
+      if key not in raw and key not in TPU_ONLY_KEYS:
         raise ValueError(f"Key {key} was passed as a keyword but is not in the config file {argv[1]}")
       overrides[key] = value
     raw.update(overrides)

@@ -269,3 +269,47 @@ def test_aot_cache_is_a_pass_through_on_cpu_and_fingerprints_revisions(tmp_path)
   assert torch.equal(f(torch.ones(3), k=3), torch.ones(3) * 3) and len(calls) == 2  # CPU tensors: eager
   aot_cache.uninstall()
   assert aot_cache.source_fingerprint("r1") == aot_cache.source_fingerprint("r1") != aot_cache.source_fingerprint("r2")
+
+
+def test_single_file_upsampler_and_reference_only_config_keys(tmp_path):
+  """`upsampler_filename` (the LTX-2.3 layout: one weights file inside `upsampler_model_path`, its name saying what it
+  up-samples) and the keys that only the reference's runtime reads, which must still parse as overrides."""
+  from safetensors.torch import save_file
+
+  from maxdiffusion_b200.checkpointing.ltx2_checkpointer import LTX2Checkpointer, upsampler_kind_from_filename
+  from maxdiffusion_b200.models.ltx2.latent_upsampler_ltx2 import LTX2LatentUpsamplerModel
+
+  assert upsampler_kind_from_filename("ltx-2.3-spatial-upscaler-x2-1.0.safetensors") == {
+      "spatial_upsample": True, "temporal_upsample": False, "rational_spatial_scale": 2.0}
+  assert upsampler_kind_from_filename("ltx-2-temporal-upscaler-x2.safetensors")["temporal_upsample"] is True
+  assert upsampler_kind_from_filename("spatial-upscaler-x1.5.safetensors")["rational_spatial_scale"] == 1.5
+  assert upsampler_kind_from_filename("weights.safetensors") == {}
+
+  torch.manual_seed(0)
+  src = LTX2LatentUpsamplerModel(in_channels=8, mid_channels=32, num_blocks_per_stage=1)
+  name = "tiny-spatial-upscaler-x2.safetensors"
+  save_file({k: v.contiguous() for k, v in src.state_dict().items()}, str(tmp_path / name))
+  tcfg = ('{"in_channels": 8, "out_channels": 8, "num_attention_heads": 2, "attention_head_dim": 32, "cross_attention_dim": 64, '
+          '"audio_in_channels": 16, "audio_out_channels": 16, "audio_num_attention_heads": 2, "audio_attention_head_dim": 16, '
+          '"audio_cross_attention_dim": 32, "num_layers": 1, "caption_channels": 32}')
+  comps = ('{"vae": {"latent_channels": 8, "block_out_channels": [8, 16, 16, 32], "decoder_block_out_channels": [8, 16, 32], '
+           '"layers_per_block": [1, 1, 1, 1, 1], "decoder_layers_per_block": [1, 1, 1, 1]}, '
+           '"audio_vae": {"base_channels": 8, "mel_bins": 16, "resolution": 16, "latent_channels": 4}, '
+           '"vocoder": {"in_channels": 32, "hidden_channels": 32, "upsample_kernel_sizes": [4, 4], "upsample_factors": [2, 2]}, '
+           '"connectors": {"text_proj_in_factor": 3, "video_connector_attention_head_dim": 16, '
+           '"video_connector_num_attention_heads": 2, "video_connector_num_learnable_registers": 4, '
+           '"audio_connector_attention_head_dim": 16, "audio_connector_num_attention_heads": 2, '
+           '"audio_connector_num_learnable_registers": 4}, "latent_upsampler": {"mid_channels": 32, "num_blocks_per_stage": 1}}')
+  config = pyconfig.initialize(
+      ["x", "maxdiffusion_b200/configs/ltx2_3_video.yml", "ltx2_preset=tiny", f"ltx2_config_overrides={tcfg}",
+       f"ltx2_component_overrides={comps}", "use_bwe=False", "run_latent_upsampler=True", f"upsampler_model_path={tmp_path}",
+       f"upsampler_filename={name}", f"output_dir={tmp_path}/out", "log_config=false", "pretrained_model_name_or_path=/nonexistent",
+       # keys of the reference's runtime: accepted, some of them ignored
+       "run_text_encoder_on_tpu=False", "tile_search_vmem_limit_bytes=67108864", 'sharding={"transformer": "default"}',
+       "config_path=", "global_batch_size_to_train_on=1", "enable_dynamic_vae_sharding=True", "upsampler_spatial_patch_size=1",
+       "upsampler_temporal_patch_size=1", "use_batched_text_encoder=False", "train_new_unet=False", "tensorboard_dir="],
+      unittest=True)
+  pipe = LTX2Checkpointer(config).load_pipeline(device="cpu")
+  got = pipe.latent_upsampler.state_dict()
+  assert all(torch.equal(got[k], v) for k, v in src.state_dict().items())
+  assert pipe.latent_upsampler.spatial and not pipe.latent_upsampler.temporal
