@@ -17,6 +17,7 @@ from typing import Callable, Iterator, Optional
 import torch
 import torch.distributed as dist
 
+from .. import max_logging
 from ..ops import _lib
 from ..train_utils import MetricsWriter
 
@@ -80,6 +81,36 @@ def _maybe_inject_failure(config, trainer) -> None:
     raise RuntimeError(f"injected host failure on rank {trainer.mesh.rank} before step {at}")
 
 
+class PhaseTimer:
+  """Wall-clock duration of the phases around the steps (restore, data set, the loop itself, the final save), written
+  as "Starting: ..." / "Finished: ... - Duration: ... seconds" lines: into `timing_metrics_file` when
+  `write_timing_metrics` is set and the file is named, else into the log; rank 0 only
+  (reference: src/maxdiffusion/trainers/base_stable_diffusion_trainer.py:84-103, `_time_and_log_call`)."""
+
+  def __init__(self, config, rank: int = 0):
+    self.file = str(config.get("timing_metrics_file", "") or "") if config.get("write_timing_metrics", False) else ""
+    self.rank = rank
+    self.durations: dict = {}
+
+  def _emit(self, line: str) -> None:
+    if self.rank != 0:
+      return
+    if self.file:
+      os.makedirs(os.path.dirname(os.path.abspath(self.file)), exist_ok=True)
+      with open(self.file, "a", encoding="utf-8") as f:
+        f.write(line + "\n")
+    else:
+      max_logging.log(line)
+
+  def __call__(self, description: str, fn: Callable, *args, **kwargs):
+    self._emit(f"Starting: {description}...")
+    t0 = time.perf_counter()
+    out = fn(*args, **kwargs)
+    self.durations[description] = time.perf_counter() - t0
+    self._emit(f"Finished: {description} - Duration: {self.durations[description]:.4f} seconds")
+    return out
+
+
 def run_training_loop(trainer, data, checkpointer=None, evaluate: Optional[Callable[[int], dict]] = None):
   """Drives `trainer.train_step` until `max_train_steps`. `trainer` provides `config`, `mesh`, `step` and `train_step`;
   `checkpointer` provides `maybe_restore(trainer)` and `save(step, trainer)`. `data` is an iterator of batches or a
@@ -90,12 +121,14 @@ def run_training_loop(trainer, data, checkpointer=None, evaluate: Optional[Calla
   max_steps = int(config.max_train_steps)
   every = int(config.get("checkpoint_every", -1))
   eval_every = int(config.get("eval_every", -1))
+  timed = PhaseTimer(config, trainer.mesh.rank)
+  trainer.phase_timer = timed
   if checkpointer is not None:
-    restored = checkpointer.maybe_restore(trainer)
+    restored = timed("restore checkpoint", checkpointer.maybe_restore, trainer)
     if restored is not None:
       trainer.step = int(restored)
   if callable(data) and not hasattr(data, "__next__"):
-    data = iter(data())
+    data = iter(timed("load dataset", data))
   # sources that can save their position (grain) continue where the checkpoint left them
   source = getattr(data, "source", data)
   if checkpointer is not None and hasattr(source, "set_state") and hasattr(checkpointer, "restore_iterator"):
@@ -105,6 +138,8 @@ def run_training_loop(trainer, data, checkpointer=None, evaluate: Optional[Calla
   step_barrier = bool(config.get("health_step_barrier", True))
   pool = ThreadPoolExecutor(max_workers=1)
   nxt = pool.submit(lambda: next(data))
+  timed._emit("Starting: training loop...")
+  loop_t0 = time.perf_counter()
   try:
     while trainer.step < max_steps:
       batch = nxt.result()
@@ -125,8 +160,10 @@ def run_training_loop(trainer, data, checkpointer=None, evaluate: Optional[Calla
         writer.write(trainer.step, {f"eval/{k}": float(v) for k, v in evaluate(trainer.step).items()})
       if checkpointer is not None and every > 0 and trainer.step % every == 0:
         _save(checkpointer, trainer, source)
+    timed.durations["training loop"] = time.perf_counter() - loop_t0
+    timed._emit(f"Finished: training loop - Duration: {timed.durations['training loop']:.4f} seconds")
     if checkpointer is not None and config.get("save_final_checkpoint", False) and (every <= 0 or trainer.step % every != 0):
-      _save(checkpointer, trainer, source)
+      timed("final checkpoint", _save, checkpointer, trainer, source)
   finally:
     writer.close()
     if monitor is not None:

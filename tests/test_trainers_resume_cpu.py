@@ -142,3 +142,29 @@ def test_graphed_objective_runs_eagerly_without_a_gpu_and_the_objective_split_is
   got = g(drawn)
   assert torch.allclose(got, a.detach()) and g.replays == 0
   assert any(p.grad is not None and p.grad.abs().sum() > 0 for p in tr.unet.parameters())
+
+
+def test_phases_around_the_steps_are_timed_into_the_timing_file(tmp_path):
+  """`write_timing_metrics` + `timing_metrics_file`: restore, data set, the loop and the final save each leave a
+  "Starting" and a "Finished ... Duration" line; without a file name the lines go to the log."""
+  from maxdiffusion_b200.trainers.loop import PhaseTimer
+  from maxdiffusion_b200.trainers.stable_diffusion_trainer import StableDiffusionTrainer
+
+  log = tmp_path / "timing" / "phases.log"
+  c = _cfg("base15.yml", SD + ["unet_preset=tiny_sd", "max_train_steps=3", "save_final_checkpoint=true", "checkpoint_every=2",
+                                "write_timing_metrics=true", f"timing_metrics_file={log}"], tmp_path / "t")
+  t = StableDiffusionTrainer(c, mesh=create_device_mesh(c), device="cpu")
+  t.start_training()
+  lines = log.read_text().splitlines()
+  for phase in ("restore checkpoint", "load dataset", "training loop", "final checkpoint"):
+    assert f"Starting: {phase}..." in lines
+    done = [ln for ln in lines if ln.startswith(f"Finished: {phase} - Duration: ") and ln.endswith(" seconds")]
+    assert len(done) == 1 and float(done[0].split("Duration: ")[1].split()[0]) >= 0.0
+  assert set(t.phase_timer.durations) == {"restore checkpoint", "load dataset", "training loop", "final checkpoint"}
+  assert lines.index("Starting: training loop...") > lines.index("Starting: load dataset...")
+  # no file named, or the switch off: nothing is written; other ranks stay silent
+  off = PhaseTimer({"write_timing_metrics": False, "timing_metrics_file": str(tmp_path / "no.log")})
+  assert off("x", lambda: 7) == 7 and not (tmp_path / "no.log").exists() and "x" in off.durations
+  quiet = PhaseTimer({"write_timing_metrics": True, "timing_metrics_file": str(tmp_path / "r1.log")}, rank=1)
+  quiet("y", lambda: None)
+  assert not (tmp_path / "r1.log").exists()
