@@ -28,6 +28,22 @@ def cfg_cache_schedule(num_steps: int, height: int) -> List[bool]:
   return [start <= s < end and (s - start) % 5 != 0 for s in range(num_steps)]
 
 
+def cfg_cache_schedule_two_experts(num_steps: int, height: int, step_uses_high: Sequence[bool]) -> List[bool]:
+  """CFG-cache schedule of the two-expert models (Wan 2.2): a step of the high-noise expert is never a cache step, the
+  first low-noise step is always a full step (it fills the cache: the experts' outputs do not carry over), and the
+  window ends one step later than for one expert at below 720p (steps - 1 instead of steps - 2)
+  (reference: src/maxdiffusion/pipelines/wan/wan_pipeline_2_2.py, `run_inference_2_2`)."""
+  start = int(num_steps / 3)
+  end = int(num_steps * 0.9) if height >= 720 else num_steps - 1
+  out, full_seen = [], False
+  for s in range(num_steps):
+    cache = (not step_uses_high[s]) and full_seen and start <= s < end and (s - start) % 5 != 0
+    out.append(cache)
+    if not step_uses_high[s] and not cache:
+      full_seen = True
+  return out
+
+
 def cfg_cache_weights(step: int, num_steps: int, alpha: float = 0.2) -> tuple[float, float]:
   """(w1, w2): boost the low-frequency correction before the midpoint step, the high-frequency one after."""
   return (1.0 + alpha, 1.0) if step < num_steps // 2 else (1.0, 1.0 + alpha)

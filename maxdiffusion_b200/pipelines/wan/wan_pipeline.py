@@ -183,12 +183,16 @@ class WanPipeline:
     return torch.randn(shape, generator=g, dtype=torch.float32, device=g.device).to(self.device)
 
   # ------------------------------------------------------------------ experts / guidance
-  def _expert(self, t: float, boundary: Optional[float]):
+  def _expert(self, t: float, boundary: Optional[float], scale_low: Optional[float] = None, scale_high: Optional[float] = None):
+    """(model, guidance scale, is the high-noise expert) for timestep t; a scale passed to the call wins over the
+    configuration's `guidance_scale_low` / `guidance_scale_high`."""
     if self.transformer_2 is None or boundary is None:
       return self.transformer, float(self.config.get("guidance_scale", 5.0)), False
     if t >= boundary:
-      return self.transformer, float(self.config.get("guidance_scale_high", self.config.get("guidance_scale", 5.0))), True
-    return self.transformer_2, float(self.config.get("guidance_scale_low", self.config.get("guidance_scale", 5.0))), False
+      high = scale_high if scale_high is not None else self.config.get("guidance_scale_high", self.config.get("guidance_scale", 5.0))
+      return self.transformer, float(high), True
+    low = scale_low if scale_low is not None else self.config.get("guidance_scale_low", self.config.get("guidance_scale", 5.0))
+    return self.transformer_2, float(low), False
 
   def _cfg_split(self):
     """With data axis 2 and CFG on, rank coordinate 0 runs cond and 1 runs uncond (CFG as data parallelism)."""
@@ -227,8 +231,9 @@ class WanPipeline:
                guidance_scale: Optional[float] = None, prompt_embeds=None, negative_prompt_embeds=None,
                image_embeds=None, condition=None, latents=None, generator=None, output_type: str = "uint8",
                use_cfg_cache: Optional[bool] = None, use_magcache: Optional[bool] = None,
-               use_sen_cache: Optional[bool] = None, use_kv_cache: Optional[bool] = None, return_trace: bool = False):
-    c = self.config
+               use_sen_cache: Optional[bool] = None, use_kv_cache: Optional[bool] = None, return_trace: bool = False,
+               guidance_scale_low: Optional[float] = None, guidance_scale_high: Optional[float] = None):
+    c = self.config if getattr(self, "config", None) is not None else {}
     height = height or int(c.get("height", 480))
     width = width or int(c.get("width", 832))
     num_frames = num_frames or int(c.get("num_frames", 81))
@@ -239,6 +244,18 @@ class WanPipeline:
     use_magcache = bool(c.get("use_magcache", False)) if use_magcache is None else use_magcache
     use_sen_cache = bool(c.get("use_sen_cache", False)) if use_sen_cache is None else use_sen_cache
     use_kv_cache = bool(c.get("use_kv_cache", False)) if use_kv_cache is None else use_kv_cache
+    two_experts = getattr(self, "transformer_2", None) is not None or self.model_name == "wan2.2"
+    if use_cfg_cache:
+      # the cache reconstructs the unconditional branch: without classifier-free guidance there is nothing to reconstruct
+      if two_experts:
+        low = float(guidance_scale_low if guidance_scale_low is not None else c.get("guidance_scale_low", guidance_scale))
+        high = float(guidance_scale_high if guidance_scale_high is not None else c.get("guidance_scale_high", guidance_scale))
+        if low <= 1.0 or high <= 1.0:
+          raise ValueError(f"use_cfg_cache=True needs guidance_scale_low > 1.0 and guidance_scale_high > 1.0 (got {low}, {high}): "
+                           "the cache skips the unconditional pass of classifier-free guidance")
+      elif guidance_scale <= 1.0:
+        raise ValueError(f"use_cfg_cache=True needs guidance_scale > 1.0 (got {guidance_scale}): the cache skips the "
+                         "unconditional pass of classifier-free guidance")
     self.check_inputs(prompt, negative_prompt, height, width, num_frames, prompt_embeds, negative_prompt_embeds)
     if sum([use_cfg_cache, use_magcache, use_sen_cache]) > 1:
       raise ValueError("use_cfg_cache, use_magcache and use_sen_cache are mutually exclusive")
@@ -281,7 +298,13 @@ class WanPipeline:
       for m in filter(None, (self.transformer, self.transformer_2)):
         kv_caches[id(m)] = m.compute_kv_cache(embeds_all, image_embeds)
 
-    cfg_sched = CP.cfg_cache_schedule(steps, height) if (use_cfg_cache and do_cfg and not cfg_split) else [False] * steps
+    if use_cfg_cache and do_cfg and not cfg_split:
+      if self.transformer_2 is not None and boundary is not None:
+        cfg_sched = CP.cfg_cache_schedule_two_experts(steps, height, [float(t) >= boundary for t in timesteps])
+      else:
+        cfg_sched = CP.cfg_cache_schedule(steps, height)
+    else:
+      cfg_sched = [False] * steps
     mag_sched = CP.magcache_schedule(steps, c.get("mag_ratios_base", [1.0, 1.0]), float(c.get("magcache_thresh", 0.12)),
                                      int(c.get("magcache_K", 2)), float(c.get("retention_ratio", 0.2))) if use_magcache else [False] * steps
     sen = CP.SenCache(steps) if use_sen_cache else None
@@ -295,7 +318,7 @@ class WanPipeline:
       ev = (torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True))
       ev[0].record()
     for i, t in enumerate(timesteps):
-      model, g_scale, is_high = self._expert(t, boundary)
+      model, g_scale, is_high = self._expert(t, boundary, guidance_scale_low, guidance_scale_high)
       if self.transformer_2 is None:
         g_scale = guidance_scale
       at_boundary = prev_high is not None and prev_high != is_high

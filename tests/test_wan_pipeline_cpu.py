@@ -219,3 +219,43 @@ def test_check_inputs_of_the_wan_pipelines():
                           (("a", None, 480, 832, 0), {}, "positive")):
     with pytest.raises(ValueError, match=match):
       pipe.check_inputs(*args, **kw)
+
+
+def test_cfg_cache_needs_guidance_and_the_two_expert_schedule_spares_the_high_noise_expert():
+  """The argument rule and the schedules asserted by the reference's src/maxdiffusion/tests/wan/wan_cfg_cache_test.py:
+  `use_cfg_cache` without classifier-free guidance is an error (one scale for 2.1, both for 2.2); with two experts no
+  high-noise step is a cache step and the first low-noise step is a full one."""
+  for cls, kw in ((WanPipeline2_1, {"guidance_scale": 1.0}), (WanPipeline2_1, {"guidance_scale": 0.0}),
+                  (WanPipeline2_2, {"guidance_scale_low": 1.0, "guidance_scale_high": 1.0}),
+                  (WanPipeline2_2, {"guidance_scale_low": 0.5, "guidance_scale_high": 4.0}),
+                  (WanPipeline2_2, {"guidance_scale_low": 3.0, "guidance_scale_high": 1.0})):
+    with pytest.raises(ValueError, match="use_cfg_cache"):
+      cls.__new__(cls)(prompt=["test"], use_cfg_cache=True, **kw)
+  for cls, kw, cache in ((WanPipeline2_1, {"guidance_scale": 5.0}, True), (WanPipeline2_1, {"guidance_scale": 1.0}, False),
+                         (WanPipeline2_2, {"guidance_scale_low": 3.0, "guidance_scale_high": 4.0}, True),
+                         (WanPipeline2_2, {"guidance_scale_low": 1.0, "guidance_scale_high": 1.0}, False)):
+    try:   # passes the rule and fails later, on the components a bare instance does not have
+      cls.__new__(cls)(prompt=["test"], use_cfg_cache=cache, **kw)
+    except ValueError as e:
+      assert "use_cfg_cache" not in str(e)
+    except Exception:
+      pass
+
+  def two(n, ratio=0.875, height=720):
+    ts = np.linspace(999, 0, n, dtype=np.int32)
+    high = [bool(t >= ratio * 1000) for t in ts]
+    return CP.cfg_cache_schedule_two_experts(n, height, high), high
+
+  cache, high = two(50)
+  assert not any(c for c, h in zip(cache, high) if h)
+  first_low = high.index(False)
+  assert not cache[first_low] and sum(cache) > 0
+  assert sum(two(50, 0.5)[1]) > sum(two(50, 0.9)[1])
+  assert sum(two(50, height=480)[0]) > sum(two(50, height=720)[0])
+  c480, h480 = two(50, height=480)
+  assert all(not c480[s] for s in range(16, 49) if not h480[s] and (s - 16) % 5 == 0) and not c480[49] and c480[48]
+  assert sum(two(3)[0]) == 0 and sum(two(50, 0.0)[0]) == 0 and all(two(50, 0.0)[1])
+  # one expert: starts at a third of the steps, ends 2 steps (480p) or 10 % (720p) before the last, every 5th step full
+  s480, s720 = CP.cfg_cache_schedule(50, 480), CP.cfg_cache_schedule(50, 720)
+  assert not any(s480[:16]) and not any(s480[48:]) and not any(s720[45:]) and sum(s480) > sum(s720) > 0
+  assert all(not s480[s] for s in range(16, 48, 5)) and sum(CP.cfg_cache_schedule(3, 480)) == 0
