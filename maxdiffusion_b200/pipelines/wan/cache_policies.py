@@ -84,14 +84,28 @@ def nearest_interp(src: np.ndarray, target_len: int) -> np.ndarray:
   return src[idx]
 
 
+def magcache_forced_steps(num_steps: int, retention_ratio: float, step_uses_high: Optional[Sequence[bool]] = None) -> List[bool]:
+  """True for the steps that always run the transformer. One expert: the first `retention_ratio * steps` steps. Two
+  experts (`step_uses_high` per step): the first `retention_ratio` fraction of EACH expert's phase, and the step at
+  which the expert changes (its residual does not carry over)
+  (reference: src/maxdiffusion/pipelines/wan/wan_pipeline_2_2.py, MagCache branch of `run_inference_2_2`)."""
+  if step_uses_high is None:
+    return [s < int(num_steps * retention_ratio) for s in range(num_steps)]
+  high = sum(bool(h) for h in step_uses_high)
+  high_end = int(high * retention_ratio)
+  low_end = high + int((num_steps - high) * retention_ratio)
+  return [s < high_end or high <= s < low_end or (s > 0 and bool(step_uses_high[s]) != bool(step_uses_high[s - 1]))
+          for s in range(num_steps)]
+
+
 def magcache_schedule(num_steps: int, mag_ratios_base: Sequence[float], thresh: float, K: int,
-                      retention_ratio: float) -> List[bool]:
+                      retention_ratio: float, step_uses_high: Optional[Sequence[bool]] = None) -> List[bool]:
   """True for the steps whose transformer blocks are skipped (output = input + cached residual).
 
   `mag_ratios_base` interleaves (cond, uncond) magnitude ratios per calibrated step and is resampled to
-  `num_steps`. A step is skipped while the accumulated error |1 - prod ratios| stays below `thresh` for both
-  branches and fewer than K consecutive steps have been skipped; the first `retention_ratio * steps` steps
-  always run.
+  `num_steps`; it is indexed by the global step for both experts. A step is skipped while the accumulated error
+  |1 - prod ratios| stays below `thresh` for both branches and fewer than K consecutive steps have been skipped; the
+  steps of `magcache_forced_steps` always run and restart the accumulation.
   """
   base = np.asarray(mag_ratios_base, dtype=np.float64)
   if len(base) != 2 * num_steps:
@@ -99,14 +113,18 @@ def magcache_schedule(num_steps: int, mag_ratios_base: Sequence[float], thresh: 
     ratios = np.stack([cond, uncond], axis=1).reshape(-1)
   else:
     ratios = base
-  warmup = int(num_steps * retention_ratio)
+  forced = magcache_forced_steps(num_steps, retention_ratio, step_uses_high)
   rc = ru = 1.0
   ec = eu = 0.0
   nc = nu = 0
   out = []
   for s in range(num_steps):
     skip = False
-    if s >= warmup:
+    if forced[s]:
+      rc = ru = 1.0
+      ec = eu = 0.0
+      nc = nu = 0
+    else:
       new_c, new_u = rc * ratios[2 * s], ru * ratios[2 * s + 1]
       dc, du = abs(1.0 - new_c), abs(1.0 - new_u)
       if ec + dc < thresh and nc < K and eu + du < thresh and nu < K:

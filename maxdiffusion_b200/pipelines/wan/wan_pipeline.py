@@ -305,8 +305,10 @@ class WanPipeline:
         cfg_sched = CP.cfg_cache_schedule(steps, height)
     else:
       cfg_sched = [False] * steps
+    phases = [float(t) >= boundary for t in timesteps] if (self.transformer_2 is not None and boundary is not None) else None
     mag_sched = CP.magcache_schedule(steps, c.get("mag_ratios_base", [1.0, 1.0]), float(c.get("magcache_thresh", 0.12)),
-                                     int(c.get("magcache_K", 2)), float(c.get("retention_ratio", 0.2))) if use_magcache else [False] * steps
+                                     int(c.get("magcache_K", 2)), float(c.get("retention_ratio", 0.2)),
+                                     phases) if use_magcache else [False] * steps
     sen = CP.SenCache(steps) if use_sen_cache else None
     cached_cond = cached_uncond = cached_residual = None
     prev_high = None

@@ -259,3 +259,40 @@ def test_cfg_cache_needs_guidance_and_the_two_expert_schedule_spares_the_high_no
   s480, s720 = CP.cfg_cache_schedule(50, 480), CP.cfg_cache_schedule(50, 720)
   assert not any(s480[:16]) and not any(s480[48:]) and not any(s720[45:]) and sum(s480) > sum(s720) > 0
   assert all(not s480[s] for s in range(16, 48, 5)) and sum(CP.cfg_cache_schedule(3, 480)) == 0
+
+
+def test_magcache_two_phase_forced_zones_and_skip_rules():
+  """The host-side MagCache schedule as the reference's src/maxdiffusion/tests/wan/wan2_2_magcache_test.py pins it:
+  a forced (retention) zone at the start of each expert's phase, a forced step where the expert changes, at most K
+  skips in a row, and a skip only when BOTH branches stay under the error budget."""
+  def phases(n, ratio=0.875):
+    return [bool(t >= ratio * 1000) for t in np.linspace(999, 0, n, dtype=np.int32)]
+
+  for n in (20, 40, 80):
+    high = phases(n)
+    hn = sum(high)
+    forced = CP.magcache_forced_steps(n, 0.2, high)
+    assert all(forced[:int(hn * 0.2)]) and all(forced[hn:hn + int((n - hn) * 0.2)])
+    boundaries = [s for s in range(1, n) if high[s] != high[s - 1]]
+    assert len(boundaries) == 1 and forced[boundaries[0]]
+    sched = CP.magcache_schedule(n, list(np.ones(2 * n)), 1.0, 99, 0.2, high)
+    assert not sched[0] and not any(s for s, f in zip(sched, forced) if f) and sum(sched) > 0
+  assert CP.magcache_forced_steps(40, 0.2) == [s < 8 for s in range(40)]
+  # at most K skips in a row even when the error is zero
+  run = best = 0
+  for skip in CP.magcache_schedule(20, list(np.ones(40)), 1.0, 2, 0.0):
+    run = run + 1 if skip else 0
+    best = max(best, run)
+  assert best == 2
+  # a ratio far from 1 in either branch blocks the skip of that step only
+  ratios = np.ones(20)
+  ratios[3 * 2 + 1] = 0.5
+  sched = CP.magcache_schedule(10, list(ratios), 0.04, 99, 0.2)
+  assert not sched[3] and sched[2] and sched[4]
+  assert not any(CP.magcache_schedule(10, list(np.full(20, 0.5)), 0.04, 99, 0.2))
+  # a curve calibrated on another step count is resampled per branch; one of the right length is used as it is
+  assert len(CP.nearest_interp(np.linspace(1.0, 0.8, 20), 40)) == 40
+  base = np.linspace(1.0, 0.9, 10)
+  a = CP.magcache_schedule(5, list(base), 0.2, 3, 0.2)
+  b = CP.magcache_schedule(5, list(np.stack([CP.nearest_interp(base[0::2], 5), CP.nearest_interp(base[1::2], 5)], 1).reshape(-1)), 0.2, 3, 0.2)
+  assert a == b
