@@ -164,12 +164,16 @@ class SenCache:
     self.n, self.threshold, self.max_reuse = num_steps, threshold, max_reuse
     self.alpha_x, self.alpha_t, self.n_train = alpha_x, alpha_t, num_train_timesteps
     self.first_free = int(num_steps * warmup)
-    self.last_free = num_steps - int(num_steps * tail)
+    self.last_free = int(num_steps * (1.0 - tail))
     self.state = SenCacheState()
+
+  def forced(self, step: int, at_boundary: bool = False) -> bool:
+    """Steps that always run the model whatever the score: the first, the first 30 %, the last 10 %, an expert change."""
+    return step == 0 or step < self.first_free or step >= self.last_free or at_boundary
 
   def should_reuse(self, step: int, latents: torch.Tensor, t: float, at_boundary: bool) -> bool:
     st = self.state
-    if step == 0 or step < self.first_free or step >= self.last_free or at_boundary or st.cached_pred is None:
+    if self.forced(step, at_boundary) or st.cached_pred is None:
       return False
     dx = float((latents.float() - st.x_ref.float()).pow(2).mean().sqrt())  # one device -> host scalar per step
     st.score += self.alpha_x * dx + self.alpha_t * abs(t - st.t_ref) / self.n_train

@@ -245,20 +245,20 @@ class WanPipeline:
     use_sen_cache = bool(c.get("use_sen_cache", False)) if use_sen_cache is None else use_sen_cache
     use_kv_cache = bool(c.get("use_kv_cache", False)) if use_kv_cache is None else use_kv_cache
     two_experts = getattr(self, "transformer_2", None) is not None or self.model_name == "wan2.2"
-    if use_cfg_cache:
-      # the cache reconstructs the unconditional branch: without classifier-free guidance there is nothing to reconstruct
-      if two_experts:
-        low = float(guidance_scale_low if guidance_scale_low is not None else c.get("guidance_scale_low", guidance_scale))
-        high = float(guidance_scale_high if guidance_scale_high is not None else c.get("guidance_scale_high", guidance_scale))
-        if low <= 1.0 or high <= 1.0:
-          raise ValueError(f"use_cfg_cache=True needs guidance_scale_low > 1.0 and guidance_scale_high > 1.0 (got {low}, {high}): "
-                           "the cache skips the unconditional pass of classifier-free guidance")
-      elif guidance_scale <= 1.0:
-        raise ValueError(f"use_cfg_cache=True needs guidance_scale > 1.0 (got {guidance_scale}): the cache skips the "
-                         "unconditional pass of classifier-free guidance")
+    chosen = [n for n, on in (("use_cfg_cache", use_cfg_cache), ("use_magcache", use_magcache), ("use_sen_cache", use_sen_cache)) if on]
+    if len(chosen) > 1:
+      raise ValueError(f"{', '.join(chosen)} are mutually exclusive: pick one cache policy")
+    # every policy of the two-expert models, and the CFG cache of the others, reuses a guided prediction or rebuilds the
+    # unconditional branch: without classifier-free guidance there is nothing to reuse
+    if two_experts and chosen:
+      low = float(guidance_scale_low if guidance_scale_low is not None else c.get("guidance_scale_low", guidance_scale))
+      high = float(guidance_scale_high if guidance_scale_high is not None else c.get("guidance_scale_high", guidance_scale))
+      if low <= 1.0 or high <= 1.0:
+        raise ValueError(f"{chosen[0]}=True needs guidance_scale_low > 1.0 and guidance_scale_high > 1.0 (got {low}, {high})")
+    elif use_cfg_cache and guidance_scale <= 1.0:
+      raise ValueError(f"use_cfg_cache=True needs guidance_scale > 1.0 (got {guidance_scale}): the cache skips the "
+                       "unconditional pass of classifier-free guidance")
     self.check_inputs(prompt, negative_prompt, height, width, num_frames, prompt_embeds, negative_prompt_embeds)
-    if sum([use_cfg_cache, use_magcache, use_sen_cache]) > 1:
-      raise ValueError("use_cfg_cache, use_magcache and use_sen_cache are mutually exclusive")
     if use_sen_cache and self.transformer_2 is None:
       raise ValueError("use_sen_cache is a Wan 2.2 option")
     trace = {}

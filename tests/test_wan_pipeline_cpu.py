@@ -231,6 +231,13 @@ def test_cfg_cache_needs_guidance_and_the_two_expert_schedule_spares_the_high_no
                   (WanPipeline2_2, {"guidance_scale_low": 3.0, "guidance_scale_high": 1.0})):
     with pytest.raises(ValueError, match="use_cfg_cache"):
       cls.__new__(cls)(prompt=["test"], use_cfg_cache=True, **kw)
+  for policy in ("use_magcache", "use_sen_cache"):
+    with pytest.raises(ValueError, match=policy):
+      WanPipeline2_2.__new__(WanPipeline2_2)(prompt=["test"], guidance_scale_low=0.5, guidance_scale_high=4.0, **{policy: True})
+  for pair in (("use_cfg_cache", "use_magcache"), ("use_sen_cache", "use_magcache"), ("use_cfg_cache", "use_sen_cache")):
+    with pytest.raises(ValueError, match="mutually exclusive"):
+      WanPipeline2_2.__new__(WanPipeline2_2)(prompt=["test"], guidance_scale_low=3.0, guidance_scale_high=4.0,
+                                             **{pair[0]: True, pair[1]: True})
   for cls, kw, cache in ((WanPipeline2_1, {"guidance_scale": 5.0}, True), (WanPipeline2_1, {"guidance_scale": 1.0}, False),
                          (WanPipeline2_2, {"guidance_scale_low": 3.0, "guidance_scale_high": 4.0}, True),
                          (WanPipeline2_2, {"guidance_scale_low": 1.0, "guidance_scale_high": 1.0}, False)):
@@ -296,3 +303,37 @@ def test_magcache_two_phase_forced_zones_and_skip_rules():
   a = CP.magcache_schedule(5, list(base), 0.2, 3, 0.2)
   b = CP.magcache_schedule(5, list(np.stack([CP.nearest_interp(base[0::2], 5), CP.nearest_interp(base[1::2], 5)], 1).reshape(-1)), 0.2, 3, 0.2)
   assert a == b
+
+
+def test_sencache_forced_zones_score_and_reuse_limit():
+  """The deterministic part of SenCache as src/maxdiffusion/tests/wan/wan_sen_cache_test.py pins it (first step, first
+  30 %, last 10 %, expert change are always computed) and the data-dependent part: the score alpha_x * rms(dx) +
+  alpha_t * |dt| / 1000 accumulates since the last full step, and at most `max_reuse` reuses follow one another."""
+  for n in (20, 25, 50, 100):
+    sc = CP.SenCache(n)
+    forced = [sc.forced(s) for s in range(n)]
+    assert all(forced[:int(n * 0.3)]) and all(forced[int(n * 0.9):]) and forced[0]
+    assert sum(not f for f in forced[int(n * 0.3):int(n * 0.9)]) == int(n * 0.9) - int(n * 0.3)
+  high = [bool(t >= 875) for t in np.linspace(999, 0, 3, dtype=np.int32)]
+  assert all(CP.SenCache(3).forced(s, s > 0 and high[s] != high[s - 1]) for s in range(3))   # too short to cache
+  sc = CP.SenCache(50)
+  assert sc.forced(20, at_boundary=True) and not sc.forced(20)
+
+  x = torch.zeros(4, 4)
+  sc = CP.SenCache(50, threshold=0.1, max_reuse=3)
+  assert not sc.should_reuse(20, x, 600.0, False)            # nothing cached yet
+  sc.record_full(x, 600.0, torch.ones(1))
+  assert sc.should_reuse(21, x + 0.03, 580.0, False)         # 0.03 + 0.02 <= 0.1
+  sc.record_reuse()
+  assert not sc.should_reuse(22, x + 0.03 + 0.5, 560.0, False)   # drift of the latents
+  sc.record_full(x, 560.0, torch.ones(1))
+  assert not sc.should_reuse(23, x + 0.01, 60.0, False)      # drift of the timestep: 0.01 + 0.5
+  sc.record_full(x, 500.0, torch.ones(1))
+  reused = 0
+  for s in range(24, 34):
+    if sc.should_reuse(s, x, 500.0, False):
+      sc.record_reuse()
+      reused += 1
+    else:
+      break
+  assert reused == 3
