@@ -196,6 +196,12 @@ class WanCheckpointer:
     pairs = [("wan_state", pipe.transformer)]
     if pipe.transformer_2 is not None:
       pairs = [("high_noise_transformer_state", pipe.transformer), ("low_noise_transformer_state", pipe.transformer_2)]
+    missing = [item for item, _ in pairs if not self.manager.has_item(step, item)]
+    if missing:
+      # a one-expert checkpoint cannot fill a two-expert pipeline and the other way round: say which item is absent
+      present = [n for n in ("wan_state", "high_noise_transformer_state", "low_noise_transformer_state") if self.manager.has_item(step, n)]
+      raise ValueError(f"checkpoint step {step} under {self.manager.directory} has no {missing} (it holds {present}): the "
+                       "pipeline variant and the checkpoint do not match")
     for item, model in pairs:
       tree = {k: (v.float().numpy() if v.dtype == torch.bfloat16 else v.numpy()) for k, v in self.manager.restore_state(step, item).items()}
       ours = diffusers_to_ours(flax_tree_to_diffusers(tree))

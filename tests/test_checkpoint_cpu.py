@@ -68,3 +68,62 @@ def test_converted_weights_cache_round_trip_and_invalidation(tmp_path):
   assert all(torch.equal(back[k], sd[k]) for k in sd)
   assert wan_loader.load_converted_cache(folder, list(sd) + ["c"], "torch.bfloat16") is None   # key set changed
   assert wan_loader.load_converted_cache(folder, list(sd), "torch.float32") is None            # dtype policy changed
+
+
+def _tiny_pipeline_config(tmp, name="base_wan_14b.yml", **kw):
+  extra = [f"{k}={v}" for k, v in kw.items()]
+  cfg = os.path.join(os.path.dirname(CFG), name)
+  return pyconfig.initialize(
+      ["t", cfg, "run_name=pc", f"output_dir={tmp}", "wan_preset=tiny", f"wan_config_overrides={TINY}", "log_config=false",
+       "enable_async_checkpointing=false", "height=32", "width=32", "num_frames=5", *extra], unittest=True)
+
+
+def test_pretrained_weights_cache_hit_miss_and_disabled(tmp_path):
+  """`pretrained_orbax_dir`: a miss loads the pretrained weights and writes the cache, a hit restores from it without
+  touching the pretrained weights, an empty setting never writes one (the cases of the reference's
+  src/maxdiffusion/tests/wan/wan_checkpointer_test.py:38-86)."""
+  from maxdiffusion_b200.pipelines.wan.wan_pipeline import WanPipeline2_1
+
+  calls = []
+
+  class Pipe(WanPipeline2_1):
+    @classmethod
+    def from_pretrained(cls, config, device=None, **kw):
+      calls.append("from_pretrained")
+      torch.manual_seed(123)
+      return cls.from_config(config, device="cpu", load_vae=False)
+
+  cache = str(tmp_path / "cache")
+  config = _tiny_pipeline_config(str(tmp_path), pretrained_orbax_dir=cache)
+  ck = WanCheckpointer(config)
+  first = ck.load_pretrained_pipeline_or_diffusers(Pipe, device="cpu")
+  assert calls == ["from_pretrained"] and os.path.exists(os.path.join(cache, "0", "wan_state", "state.safetensors"))
+  second = WanCheckpointer(config).load_pretrained_pipeline_or_diffusers(Pipe, device="cpu")
+  assert calls == ["from_pretrained"]                                  # hit: the pretrained weights were not read again
+  for (n, a), (_, b) in zip(first.transformer.state_dict().items(), second.transformer.state_dict().items()):
+    assert torch.equal(a, b), n
+  plain = _tiny_pipeline_config(str(tmp_path / "p"), pretrained_orbax_dir="")
+  WanCheckpointer(plain).load_pretrained_pipeline_or_diffusers(Pipe, device="cpu")
+  assert calls == ["from_pretrained", "from_pretrained"] and not os.path.exists(str(tmp_path / "p" / "cache"))
+
+
+def test_checkpoint_of_one_expert_does_not_fill_a_two_expert_pipeline(tmp_path):
+  """Strict item selection: a Wan 2.1 checkpoint (`wan_state`) restored into a Wan 2.2 pipeline, or the reverse, names
+  the item that is absent instead of loading something else."""
+  import pytest
+
+  from maxdiffusion_b200.pipelines.wan.wan_pipeline import WanPipeline2_1, WanPipeline2_2
+
+  c1 = _tiny_pipeline_config(str(tmp_path / "one"))
+  one = WanPipeline2_1.from_config(c1, device="cpu", load_vae=False)
+  WanCheckpointer(c1).save_pipeline(3, one)
+  c2 = _tiny_pipeline_config(str(tmp_path / "two"), "base_wan_27b.yml").replace(checkpoint_dir=c1.checkpoint_dir)
+  two = WanPipeline2_2.from_config(c2, device="cpu", load_vae=False)
+  with pytest.raises(ValueError, match="high_noise_transformer_state"):
+    WanCheckpointer(c2).restore_into_pipeline(two)
+  c3 = _tiny_pipeline_config(str(tmp_path / "three"), "base_wan_27b.yml")
+  WanCheckpointer(c3).save_pipeline(1, two)
+  c4 = _tiny_pipeline_config(str(tmp_path / "four")).replace(checkpoint_dir=c3.checkpoint_dir)
+  with pytest.raises(ValueError, match="wan_state"):
+    WanCheckpointer(c4).restore_into_pipeline(one)
+  WanCheckpointer(c2.replace(checkpoint_dir=c3.checkpoint_dir)).restore_into_pipeline(two)   # matching variant: fine
