@@ -72,7 +72,41 @@ def load_pipeline(config) -> Flux2KleinPipeline:
                             max_sequence_length=int(config.max_sequence_length))
 
 
-def run(config):
+def _write(config, images, name: str) -> list:
+  out_dir = config.get("output_dir", "output/") or "."
+  os.makedirs(out_dir, exist_ok=True)
+  paths = []
+  for i in range(images.shape[0]):
+    path = os.path.join(out_dir, name if images.shape[0] == 1 else name.replace(".png", f"_b{i}.png"))
+    paths.append(export_to_png(images[i].cpu().numpy(), path))
+    max_logging.log("wrote " + paths[-1])
+  return paths
+
+
+def interactive_loop(config, pipe, kw, read=input) -> int:
+  """Prompts typed at the console (several separated by `||` fill the batch) are generated one after another as
+  `generated_NNN.png` until `exit` / `quit` / end of input; the starting noise is drawn fresh for every request
+  (reference: src/maxdiffusion/generate_flux2klein.py:467-509). Returns how many requests were served."""
+  B = int(config.get("batch_size", 1))
+  max_logging.log(f"interactive mode: batch of {B}; prompts separated by '||'; 'exit' to quit")
+  served = 0
+  while True:
+    try:
+      text = read("\nEnter prompt(s): ")
+    except (KeyboardInterrupt, EOFError):
+      break
+    if text.strip().lower() in ("exit", "quit"):
+      break
+    if not text.strip():
+      continue
+    served += 1
+    images = pipe(**{**kw, "prompt": partition_prompts(text, B), "latents": None, "seed": int(config.seed) + served})
+    if int(os.environ.get("RANK", "0")) == 0:
+      _write(config, images, f"generated_{served:03d}.png")
+  return served
+
+
+def run(config, read=input):
   pipe = load_pipeline(config)
   B = int(config.get("batch_size", 1))
   kw = dict(height=int(config.resolution), width=int(config.resolution), num_inference_steps=int(config.num_inference_steps),
@@ -81,17 +115,33 @@ def run(config):
     g = torch.Generator().manual_seed(int(config.seed))
     kw["prompt_embeds"] = torch.randn((B, int(config.max_sequence_length), pipe.transformer.cfg.joint_attention_dim), generator=g)
   else:
+    if not str(config.get("prompt", "") or "").strip():
+      raise ValueError("a prompt must be given in the configuration file or as prompt='...'")
     kw["prompt"] = partition_prompts(str(config.prompt), B)
   pipe(**{**kw, "num_inference_steps": 1, "output_type": "latent"})   # warm-up
-  images, trace = pipe(**kw, return_trace=True)
-  max_logging.log("  ".join(f"{k}: {v:.4f}s" for k, v in trace.items()))
-  if int(os.environ.get("RANK", "0")) == 0:
-    out_dir = config.get("output_dir", "output/") or "."
-    os.makedirs(out_dir, exist_ok=True)
-    name = str(config.get("output_name", "flux2klein_generated_image.png"))
-    for i in range(images.shape[0]):
-      path = os.path.join(out_dir, name if images.shape[0] == 1 else name.replace(".png", f"_b{i}.png"))
-      max_logging.log("wrote " + export_to_png(images[i].cpu().numpy(), path))
+  if config.get("interactive", False):
+    if pipe.text_encoder is None:
+      raise ValueError("interactive mode needs the text encoder (a pretrained folder with text_encoder/ and tokenizer/)")
+    kw.pop("prompt_embeds", None)
+    return interactive_loop(config, pipe, kw, read)
+  if str(config.get("latents_path", "") or ""):
+    # custom starting noise: [B, 32, H/8, W/8], or already packed [B, tokens, 128]
+    import numpy as np
+
+    max_logging.log(f"loading the starting noise from {config.latents_path}")
+    kw["latents"] = torch.from_numpy(np.load(str(config.latents_path))).float()
+  reps = max(1, int(config.get("num_reps", 1)))
+  traces, images = [], None
+  for rep in range(reps):
+    images, trace = pipe(**kw, return_trace=True)
+    traces.append(trace)
+    max_logging.log((f"[rep {rep + 1}/{reps}] " if reps > 1 else "") + "  ".join(f"{k}: {v:.4f}s" for k, v in trace.items()))
+    if int(os.environ.get("RANK", "0")) == 0:
+      name = str(config.get("output_name", "flux2klein_generated_image.png"))
+      _write(config, images, f"rep_{rep + 1}_{name}" if reps > 1 else name)
+  if reps > 1:
+    max_logging.log("average over the repetitions: " + "  ".join(
+        f"{k}: {sum(t.get(k, 0.0) for t in traces) / reps:.4f}s" for k in traces[0]))
   return images
 
 

@@ -1,4 +1,7 @@
 """Flux.2-Klein on CPU: latent packing, ids, schedule, and a tiny end-to-end generation."""
+import os
+
+import pytest
 import torch
 
 from maxdiffusion_b200 import pyconfig
@@ -62,3 +65,46 @@ def test_generate_tiny(tmp_path):
   assert G.partition_prompts(str(config.prompt), 3)[2].startswith("A detailed vector")
   images = G.run(config)
   assert images.shape == (2, 16, 16, 3) and images.dtype == torch.uint8  # the 2-level test VAE upsamples 2x
+
+
+def test_repetitions_custom_noise_and_interactive_requests(tmp_path):
+  """`num_reps` writes one image per repetition, `latents_path` starts from stored noise (the same file gives the same
+  image), and interactive mode serves typed prompts until `exit` (a stand-in text encoder here)."""
+  import numpy as np
+
+  from maxdiffusion_b200 import generate_flux2klein as G
+
+  base = ["x", "maxdiffusion_b200/configs/base_flux2klein_9B.yml", "random_init=True", "flux_preset=tiny",
+          'vae_config_overrides={"block_out_channels":[32,32],"layers_per_block":1,"norm_num_groups":8}', "resolution=64",
+          "max_sequence_length=8", "log_config=false", "batch_size=1"]
+  noise = tmp_path / "noise.npy"
+  np.save(noise, np.random.default_rng(0).standard_normal((1, 32, 8, 8)).astype(np.float32))
+  torch.manual_seed(0)
+  c = pyconfig.initialize(base + [f"output_dir={tmp_path}/a", "num_reps=2", f"latents_path={noise}", "seed=1"], unittest=True)
+  a = G.run(c)
+  assert sorted(os.listdir(tmp_path / "a")) == ["rep_1_flux2klein_generated_image.png", "rep_2_flux2klein_generated_image.png"]
+  torch.manual_seed(0)
+  c2 = pyconfig.initialize(base + [f"output_dir={tmp_path}/b", f"latents_path={noise}", "seed=1"], unittest=True)
+  b = G.run(c2)                       # the same stored noise: the same picture
+  assert torch.equal(a, b) and os.listdir(tmp_path / "b") == ["flux2klein_generated_image.png"]
+  torch.manual_seed(0)
+  drawn = G.run(pyconfig.initialize(base + [f"output_dir={tmp_path}/d", "seed=1"], unittest=True))
+  assert not torch.equal(a, drawn)    # without the file the noise is drawn from the seed
+
+  # interactive: needs a text encoder; served requests are numbered, blank lines are skipped, `exit` ends the loop
+  c3 = pyconfig.initialize(base + [f"output_dir={tmp_path}/c", "interactive=True"], unittest=True)
+  with pytest.raises(ValueError, match="text encoder"):
+    G.run(c3)
+  pipe = G.load_pipeline(c3)
+  dim = pipe.transformer.cfg.joint_attention_dim
+  pipe.text_encoder = object()
+  pipe.encode_prompt = lambda prompts: torch.randn((len(prompts), 8, dim), generator=torch.Generator().manual_seed(len(prompts[0])))
+  lines = iter(["a red car", "", "a cat || a dog", "exit", "never read"])
+  kw = dict(height=64, width=64, num_inference_steps=2, batch_size=1, seed=0)
+  assert G.interactive_loop(c3, pipe, kw, read=lambda _: next(lines)) == 2
+  assert sorted(os.listdir(tmp_path / "c")) == ["generated_001.png", "generated_002.png"]
+  assert next(lines) == "never read"
+
+  def ended(_):
+    raise EOFError
+  assert G.interactive_loop(c3, pipe, kw, read=ended) == 0
