@@ -48,6 +48,12 @@ class FluxPipeline:
     self.device = torch.device(device) if device is not None else next(transformer.parameters()).device
     self.dtype = next(transformer.parameters()).dtype
     self.engine = None
+    # `offload_encoders`: CLIP and T5 wait in host memory and visit the GPU only while a prompt is encoded, so that
+    # their 10 GB do not sit beside the transformer during the denoising loop (reference: src/maxdiffusion/generate_flux.py:384-386)
+    self.offload_encoders = bool(config.get("offload_encoders", False)) and self.device.type == "cuda"
+    if self.device.type == "cuda" and not self.offload_encoders:
+      self.clip = self.clip.to(self.device) if self.clip is not None else None
+      self.t5 = self.t5.to(self.device) if self.t5 is not None else None
 
   @classmethod
   def from_config(cls, config, device=None, load_vae: bool = True, **kw):
@@ -92,12 +98,19 @@ class FluxPipeline:
       raise ValueError("no text encoders loaded: pass prompt_embeds and pooled_prompt_embeds")
     prompts = [prompt] if isinstance(prompt, str) else list(prompt)
     p2 = prompts if prompt_2 is None else ([prompt_2] if isinstance(prompt_2, str) else list(prompt_2))
+    if self.offload_encoders:
+      self.clip, self.t5 = self.clip.to(self.device), self.t5.to(self.device)
     with torch.no_grad():
       ids = self.clip_tokenizer(prompts, padding="max_length", max_length=77, truncation=True, return_tensors="pt").input_ids
       pooled = self.clip(ids.to(next(self.clip.parameters()).device)).pooler_output
       ids2 = self.t5_tokenizer(p2, padding="max_length", max_length=max_sequence_length, truncation=True, return_tensors="pt").input_ids
       embeds = self.t5(ids2.to(next(self.t5.parameters()).device)).last_hidden_state
-    return embeds.to(self.device, self.dtype), pooled.to(self.device, self.dtype)
+    embeds, pooled = embeds.to(self.device, self.dtype), pooled.to(self.device, self.dtype)
+    if self.offload_encoders:
+      self.clip, self.t5 = self.clip.to("cpu"), self.t5.to("cpu")
+      if torch.cuda.is_available():
+        torch.cuda.empty_cache()
+    return embeds, pooled
 
   @torch.no_grad()
   def __call__(self, prompt=None, prompt_2=None, height: Optional[int] = None, width: Optional[int] = None,

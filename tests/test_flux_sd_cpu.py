@@ -96,3 +96,37 @@ def test_sd_generate_entry_points(tmp_path):
                    (generate_controlnet_replicated, "base14.yml"), (generate_controlnet_sdxl_replicated, "base_xl.yml")):
     img = mod.run(_cfg(cfg, SD + ["per_device_batch_size=1"], tmp_path))
     assert img.shape[0] >= 1 and img.dtype == torch.uint8, (mod.__name__, cfg)
+
+
+def test_flux_text_encoders_visit_the_device_only_while_a_prompt_is_encoded():
+  """`offload_encoders`: CLIP and T5 are moved to the pipeline's device for `encode_prompt` and back to host memory
+  after it; with the switch off they are left where they are."""
+  import types
+
+  from maxdiffusion_b200.pipelines.flux.flux_pipeline import FluxPipeline
+
+  config = _cfg("base_flux_dev.yml", FLUX, "/tmp/unused")
+  pipe = FluxPipeline.from_config(config, device="cpu", load_vae=False)
+  moves = []
+
+  class Encoder(torch.nn.Module):
+    def __init__(self, name, width, pooled):
+      super().__init__()
+      self.name, self.pooled, self.w = name, pooled, torch.nn.Parameter(torch.zeros(width))
+
+    def to(self, where, *a, **k):
+      moves.append((self.name, str(where)))
+      return self
+
+    def forward(self, ids):
+      out = torch.ones(ids.shape[0], ids.shape[1], self.w.numel())
+      return types.SimpleNamespace(pooler_output=out[:, 0], last_hidden_state=out)
+
+  tok = lambda prompts, **kw: types.SimpleNamespace(input_ids=torch.zeros((len(prompts), kw["max_length"]), dtype=torch.long))
+  pipe.clip, pipe.t5, pipe.clip_tokenizer, pipe.t5_tokenizer = Encoder("clip", 6, True), Encoder("t5", 10, False), tok, tok
+  assert pipe.offload_encoders is False            # only a CUDA pipeline offloads
+  e, p = pipe.encode_prompt(["a", "b"], max_sequence_length=8)
+  assert e.shape == (2, 8, 10) and p.shape == (2, 6) and moves == []
+  pipe.offload_encoders = True
+  pipe.encode_prompt("a", max_sequence_length=8)
+  assert moves == [("clip", "cpu"), ("t5", "cpu"), ("clip", "cpu"), ("t5", "cpu")]   # to the (CPU) device, then back to the host
