@@ -276,3 +276,22 @@ def test_inference_bench_runs_on_tiny_presets(capsys):
   lines = [json.loads(l) for l in capsys.readouterr().out.splitlines() if l.startswith("{")]
   assert lines[0]["unit"] == "s/step" and lines[0]["value"] > 0 and lines[0]["config"]["tokens"] == 32
   assert lines[1]["unit"] == "images/s" and lines[1]["value"] > 0
+
+
+def test_names_the_reference_users_import_resolve():
+  """The import lines of the reference's src/maxdiffusion/tests/models_import_test.py with the package name changed, and
+  the head-group chunk ranges its attention test pins (attention_test.py:261-278)."""
+  from maxdiffusion_b200 import (aot_cache, checkpointing, common_types, configuration_utils, max_logging, max_utils,  # noqa: F401
+                                 maxdiffusion_utils, multihost_dataloading, pyconfig, tpu_utils, train_utils)
+  from maxdiffusion_b200.checkpointing.base_stable_diffusion_checkpointer import BaseStableDiffusionCheckpointer  # noqa: F401
+  from maxdiffusion_b200.models import FlaxAutoencoderKL, FlaxControlNetModel, FlaxUNet2DConditionModel
+  from maxdiffusion_b200.models.unet_2d_condition import UNet2DConditionModel
+  from maxdiffusion_b200.parallel.context import ulysses_head_chunks
+  from maxdiffusion_b200.pipelines import FlaxStableDiffusionPipeline, FlaxStableDiffusionXLPipeline  # noqa: F401
+  from maxdiffusion_b200.schedulers import FlaxDDIMScheduler, FlaxDDPMScheduler, FlaxDPMSolverMultistepScheduler  # noqa: F401
+
+  assert FlaxUNet2DConditionModel is UNet2DConditionModel and FlaxAutoencoderKL is not None and FlaxControlNetModel is not None
+  assert "device_info" in tpu_utils.__all__ and callable(tpu_utils.device_info)
+  assert ulysses_head_chunks(40, 8, 2) == [(0, 16), (16, 40)]
+  assert ulysses_head_chunks(40, 8, 5) == [(0, 8), (8, 16), (16, 24), (24, 32), (32, 40)]
+  assert ulysses_head_chunks(40, 8, 3) == [(0, 8), (8, 16), (16, 40)] and ulysses_head_chunks(40, 8, 1) == [(0, 40)]
