@@ -83,12 +83,17 @@ class SyntheticFluxIterator:
         "text_embeds": _pin(torch.randn((B, self.text_len, self.text_dim), generator=self.gen)),
         "prompt_embeds": _pin(torch.randn((B, self.pooled_dim), generator=self.gen)),
         "img_ids": ids.reshape(1, h * w, 3).expand(B, -1, -1).contiguous(),
-        "txt_ids": torch.zeros((B, self.text_len, 3)),
+        "txt_ids": (txt := torch.zeros((B, self.text_len, 3))),
+        "input_ids": txt,  # the reference's name for the text position ids (the same tensor)
     }
 
 
-def make_synthetic_iterator(config, batch_size: int, seed: int = 0, **kw):
+def make_synthetic_iterator(config, batch_size: int, seed: int = 0, is_training: bool = True, **kw):
+  """Random batches of the model family's shapes. `is_training=False` builds evaluation batches: Wan batches then carry
+  the `timesteps` the loss is evaluated at (reference: src/maxdiffusion/input_pipeline/synthetic_data_iterator.py)."""
   name = str(config.get("model_name", "wan2.1"))
   if name.startswith("flux"):
     return SyntheticFluxIterator(config, batch_size, seed, **kw)
+  if not is_training:
+    kw.setdefault("with_timesteps", True)
   return SyntheticWanIterator(config, batch_size, seed, **kw)

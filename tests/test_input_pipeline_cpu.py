@@ -165,3 +165,24 @@ def test_grain_iterator_parses_records_and_saves_its_position(monkeypatch, tmp_p
   second = next(it)
   it.set_state(state)
   assert torch.equal(next(it)["latents"], second["latents"])
+
+
+def test_synthetic_iterators_have_the_shapes_and_keys_the_reference_test_expects():
+  """src/maxdiffusion/tests/input_pipeline_interface_test.py:446-549: Wan evaluation batches at the override size with
+  `timesteps`, Flux batches with packed latents, T5 / CLIP embeddings and position ids."""
+  from maxdiffusion_b200 import pyconfig
+  from maxdiffusion_b200.input_pipeline.synthetic_data_iterator import make_synthetic_iterator
+
+  cfg_dir = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "maxdiffusion_b200", "configs")
+  c = pyconfig.initialize(["t", os.path.join(cfg_dir, "base_wan_14b.yml"), "log_config=false", "synthetic_override_height=720",
+                           "synthetic_override_width=1280", "synthetic_override_num_frames=121"], unittest=True)
+  b = next(make_synthetic_iterator(c, batch_size=2, is_training=False))
+  assert b["latents"].shape == (2, 16, (121 - 1) // 4 + 1, 720 // 8, 1280 // 8)
+  assert b["encoder_hidden_states"].shape == (2, 512, 4096) and b["timesteps"].shape == (2,)
+  assert "timesteps" not in next(make_synthetic_iterator(c, batch_size=2))
+  f = pyconfig.initialize(["t", os.path.join(cfg_dir, "base_flux_dev.yml"), "log_config=false", "resolution=512",
+                           "max_sequence_length=512"], unittest=True)
+  b = next(make_synthetic_iterator(f, batch_size=3))
+  seq = (512 // 16) ** 2
+  assert b["pixel_values"].shape == (3, seq, 64) and b["input_ids"].shape == (3, 512, 3) and b["img_ids"].shape == (3, seq, 3)
+  assert b["text_embeds"].shape == (3, 512, 4096) and b["prompt_embeds"].shape == (3, 768) and b["txt_ids"] is b["input_ids"]
