@@ -57,3 +57,37 @@ def test_sigmas_and_pipeline_and_checkpoint_round_trip(tmp_path):
   a = pipe(prompt_embeds=emb, height=64, width=64, num_inference_steps=2, seed=1, output_type="latent")
   b = pipe2(prompt_embeds=emb, height=64, width=64, num_inference_steps=2, seed=1, output_type="latent")
   assert torch.allclose(a, b, atol=1e-5)
+
+
+def test_qwen3_matches_the_hugging_face_implementation_through_its_own_checkpoint_names():
+  """An outside oracle: `transformers`' Qwen3 with the same tiny configuration. Its state dict loads into this
+  repository's model unchanged (the parameter names are the checkpoint's), and the last hidden state and every
+  intermediate hidden state agree on real tokens, with and without right padding."""
+  import pytest
+
+  transformers = pytest.importorskip("transformers")
+  cfg = QWEN3_PRESETS["tiny"]
+  hf_cfg = transformers.Qwen3Config(
+      vocab_size=cfg.vocab_size, hidden_size=cfg.hidden_size, intermediate_size=cfg.intermediate_size,
+      num_hidden_layers=cfg.num_hidden_layers, num_attention_heads=cfg.num_attention_heads,
+      num_key_value_heads=cfg.num_key_value_heads, head_dim=cfg.head_dim, rms_norm_eps=cfg.rms_norm_eps,
+      rope_theta=cfg.rope_theta, max_position_embeddings=cfg.max_position_embeddings, attention_bias=False,
+      tie_word_embeddings=False, use_sliding_window=False)
+  torch.manual_seed(0)
+  hf = transformers.Qwen3Model(hf_cfg).eval()
+  for p in hf.parameters():          # norm weights start at exactly one: move everything so that they matter
+    torch.nn.init.normal_(p, mean=0.3 if p.dim() == 1 else 0.0, std=0.2)
+  ours = Qwen3Model(cfg).eval()
+  missing, unexpected = ours.load_state_dict({"model." + k: v for k, v in hf.state_dict().items()}, strict=True)
+  assert not missing and not unexpected
+  ids = torch.randint(0, cfg.vocab_size, (2, 12), generator=torch.Generator().manual_seed(1))
+  mask = torch.ones(2, 12, dtype=torch.long)
+  mask[1, 8:] = 0
+  with torch.no_grad():
+    want = hf(input_ids=ids, attention_mask=mask, output_hidden_states=True)
+    got_last, got_all = ours(ids, mask)
+  real = mask.bool()
+  assert torch.allclose(got_last[real], want.last_hidden_state[real], atol=2e-5, rtol=1e-4)
+  assert len(got_all) == cfg.num_hidden_layers + 1
+  for i in range(cfg.num_hidden_layers):    # HF's last entry is after the final norm; the earlier ones are layer outputs
+    assert torch.allclose(got_all[i][real], want.hidden_states[i][real], atol=2e-5, rtol=1e-4), i
