@@ -100,3 +100,76 @@ def export_to_png(image, path: str) -> str:
 
   Image.fromarray(_to_uint8(image)).save(path)
   return path
+
+
+def _temp_path(suffix: str) -> str:
+  import tempfile
+
+  fd, path = tempfile.mkstemp(suffix=suffix)
+  os.close(fd)
+  return path
+
+
+def export_to_gif(images, output_gif_path: str | None = None, fps: float = 10.0) -> str:
+  """Looping GIF from PIL images or a [T, H, W, 3] array (uint8, or floats in [0, 1]); 100 ms per frame by default
+  (reference: src/maxdiffusion/utils/export_utils.py:48-60)."""
+  from PIL import Image
+
+  path = output_gif_path or _temp_path(".gif")
+  if not isinstance(images, (list, tuple)) or not isinstance(images[0], Image.Image):
+    images = [Image.fromarray(f) for f in _to_uint8(images)]
+  images[0].save(path, save_all=True, append_images=list(images[1:]), optimize=False, duration=int(round(1000.0 / fps)), loop=0)
+  return path
+
+
+def _mesh_arrays(mesh):
+  """(vertices [V, 3] float32, faces [F, 3] int or None, colours [V, 3] in [0, 1] or None) of a mesh object with `verts`,
+  `faces` and optionally `vertex_channels` {"R", "G", "B"} (tensors or arrays)."""
+  to_np = lambda t: t.detach().cpu().numpy() if hasattr(t, "detach") else np.asarray(t)
+  verts = to_np(mesh.verts).astype(np.float32)
+  faces = to_np(mesh.faces).astype(np.int64) if getattr(mesh, "faces", None) is not None else None
+  channels = getattr(mesh, "vertex_channels", None)
+  rgb = np.stack([to_np(channels[c]) for c in "RGB"], axis=1).astype(np.float32) if channels else None
+  return verts, faces, rgb
+
+
+def export_to_ply(mesh, output_ply_path: str | None = None) -> str:
+  """Binary little-endian PLY: x y z as float32 (+ red green blue as uchar when the mesh has vertex colours), faces as
+  a uchar count followed by int indices (reference: src/maxdiffusion/utils/export_utils.py:63-112)."""
+  path = output_ply_path or _temp_path(".ply")
+  verts, faces, rgb = _mesh_arrays(mesh)
+  header = ["ply", "format binary_little_endian 1.0", f"element vertex {len(verts)}", "property float x", "property float y",
+            "property float z"]
+  if rgb is not None:
+    header += ["property uchar red", "property uchar green", "property uchar blue"]
+  if faces is not None:
+    header += [f"element face {len(faces)}", "property list uchar int vertex_index"]
+  header.append("end_header")
+  with open(path, "wb") as f:
+    f.write(("\n".join(header) + "\n").encode("ascii"))
+    if rgb is not None:
+      rec = np.empty(len(verts), dtype=[("p", "<f4", 3), ("c", "u1", 3)])
+      rec["p"], rec["c"] = verts, np.clip((rgb * 255.499).round(), 0, 255).astype(np.uint8)
+      f.write(rec.tobytes())
+    else:
+      f.write(verts.astype("<f4").tobytes())
+    if faces is not None:
+      rec = np.empty(len(faces), dtype=[("n", "u1"), ("i", "<i4", faces.shape[1])])
+      rec["n"], rec["i"] = faces.shape[1], faces
+      f.write(rec.tobytes())
+  return path
+
+
+def export_to_obj(mesh, output_obj_path: str | None = None) -> str:
+  """Wavefront OBJ with per-vertex colours (`v x y z r g b`) and 1-based triangle indices
+  (reference: src/maxdiffusion/utils/export_utils.py:115-130)."""
+  path = output_obj_path or _temp_path(".obj")
+  verts, faces, rgb = _mesh_arrays(mesh)
+  lines = []
+  for i, v in enumerate(verts.tolist()):
+    lines.append("v " + " ".join(repr(float(x)) for x in (v + rgb[i].tolist() if rgb is not None else v)))
+  if faces is not None:
+    lines += ["f " + " ".join(str(int(j) + 1) for j in tri) for tri in faces.tolist()]
+  with open(path, "w", encoding="ascii") as f:
+    f.write("\n".join(lines))
+  return path

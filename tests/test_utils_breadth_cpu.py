@@ -295,3 +295,35 @@ def test_names_the_reference_users_import_resolve():
   assert ulysses_head_chunks(40, 8, 2) == [(0, 16), (16, 40)]
   assert ulysses_head_chunks(40, 8, 5) == [(0, 8), (8, 16), (16, 24), (24, 32), (32, 40)]
   assert ulysses_head_chunks(40, 8, 3) == [(0, 8), (8, 16), (16, 40)] and ulysses_head_chunks(40, 8, 1) == [(0, 40)]
+
+
+def test_gif_ply_and_obj_exporters_round_trip(tmp_path):
+  import struct
+  import types
+
+  import numpy as np
+  from PIL import Image
+
+  from maxdiffusion_b200.utils.export_utils import export_to_gif, export_to_obj, export_to_ply
+
+  frames = (np.random.default_rng(0).random((4, 8, 8, 3)) * 255).astype(np.uint8)
+  gif = export_to_gif(frames, str(tmp_path / "a.gif"))
+  with Image.open(gif) as im:
+    assert im.n_frames == 4 and im.size == (8, 8) and im.info["duration"] == 100 and im.info.get("loop") == 0
+  assert os.path.getsize(export_to_gif([Image.fromarray(f) for f in frames])) > 0    # PIL images, temporary file
+
+  verts = torch.tensor([[0.0, 0.0, 0.0], [1.0, 0.0, 0.0], [0.0, 1.0, 0.0], [0.0, 0.0, 1.0]])
+  faces = torch.tensor([[0, 1, 2], [0, 2, 3]])
+  colour = {c: torch.tensor(v) for c, v in zip("RGB", ([0.0, 1.0, 0.5, 0.25], [1.0, 0.0, 0.5, 0.25], [0.0, 0.0, 1.0, 0.25]))}
+  mesh = types.SimpleNamespace(verts=verts, faces=faces, vertex_channels=colour)
+  raw = open(export_to_ply(mesh, str(tmp_path / "m.ply")), "rb").read()
+  head, body = raw.split(b"end_header\n", 1)
+  assert b"element vertex 4" in head and b"element face 2" in head and b"property uchar red" in head
+  assert len(body) == 4 * (12 + 3) + 2 * (1 + 12)
+  assert struct.unpack_from("<3f3B", body, 15) == (1.0, 0.0, 0.0, 255, 0, 0)
+  assert struct.unpack_from("<B3i", body, 4 * 15 + 13) == (3, 0, 2, 3)
+  bare = types.SimpleNamespace(verts=verts, faces=None, vertex_channels=None)
+  assert open(export_to_ply(bare, str(tmp_path / "b.ply")), "rb").read().endswith(verts.numpy().astype("<f4").tobytes())
+
+  lines = open(export_to_obj(mesh, str(tmp_path / "m.obj"))).read().splitlines()
+  assert len(lines) == 6 and lines[1].split() == ["v", "1.0", "0.0", "0.0", "1.0", "0.0", "0.0"] and lines[-1] == "f 1 3 4"
