@@ -177,3 +177,34 @@ def test_custom_pipeline_files_are_loaded_from_a_local_folder(tmp_path):
     DM.get_cached_module_file(str(folder), "broken.py", cache)
   with pytest.raises(FileNotFoundError):
     DM.get_cached_module_file(str(folder), "absent.py", cache)
+
+
+def test_doc_and_offload_hook_helpers():
+  import pytest
+
+  from maxdiffusion_b200.utils.accelerate_utils import apply_forward_hook
+  from maxdiffusion_b200.utils.doc_utils import replace_example_docstring
+
+  @replace_example_docstring("    >>> pipe('a cat')")
+  def call():
+    """Runs the pipeline.
+
+    Examples:
+
+    Returns: frames."""
+
+  assert ">>> pipe('a cat')" in call.__doc__ and "Examples:" not in call.__doc__ and "Returns: frames." in call.__doc__
+  with pytest.raises(ValueError, match="placeholder"):
+    replace_example_docstring("x")(lambda: None)
+
+  seen = []
+
+  class Vae:
+    @apply_forward_hook
+    def decode(self, z):
+      return z + 1
+
+  v = Vae()
+  assert v.decode(1) == 2 and Vae.decode.__name__ == "decode"
+  v._hf_hook = type("Hook", (), {"pre_forward": lambda self, module: seen.append(module)})()
+  assert v.decode(2) == 3 and seen == [v]
