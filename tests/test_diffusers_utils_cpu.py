@@ -208,3 +208,33 @@ def test_doc_and_offload_hook_helpers():
   assert v.decode(1) == 2 and Vae.decode.__name__ == "decode"
   v._hf_hook = type("Hook", (), {"pre_forward": lambda self, module: seen.append(module)})()
   assert v.decode(2) == 3 and seen == [v]
+
+
+def test_local_hub_helpers(tmp_path):
+  import pytest
+
+  from maxdiffusion_b200.utils import hub_utils as H
+
+  h = "0123456789abcdef0123456789abcdef01234567"
+  assert H.extract_commit_hash(f"/c/models--a--b/snapshots/{h}/unet/config.json") == h
+  assert H.extract_commit_hash("/c/models--a--b/snapshots/main/x") is None and H.extract_commit_hash(None, "abc") == "abc"
+  assert H.add_variant("diffusion_pytorch_model.safetensors", "fp16") == "diffusion_pytorch_model.fp16.safetensors"
+  assert H.add_variant("model.bin") == "model.bin"
+  (tmp_path / "unet").mkdir()
+  (tmp_path / "unet" / "w.fp16.safetensors").write_bytes(b"x")
+  (tmp_path / "w.safetensors").write_bytes(b"y")
+  assert H.get_model_file(str(tmp_path), "w.safetensors", subfolder="unet", variant="fp16").endswith("unet/w.fp16.safetensors")
+  assert H.get_model_file(str(tmp_path), "w.safetensors", subfolder="unet") == str(tmp_path / "w.safetensors")
+  assert H.get_model_file(str(tmp_path / "w.safetensors"), "ignored") == str(tmp_path / "w.safetensors")
+  with pytest.raises(EnvironmentError, match="no file named"):
+    H.get_model_file(str(tmp_path), "missing.safetensors")
+  assert H.http_user_agent({"pipeline": "wan"}).startswith("maxdiffusion_b200/") and "pipeline/wan" in H.http_user_agent({"pipeline": "wan"})
+
+  class Thing(H.PushToHubMixin):
+    def save_pretrained(self, folder):
+      open(os.path.join(folder, "config.json"), "w").write("{}")
+
+  out = Thing().push_to_hub("org/my-model", output_dir=str(tmp_path / "export"), commit_message="first version")
+  assert sorted(os.listdir(out)) == ["README.md", "config.json"] and "first version" in open(os.path.join(out, "README.md")).read()
+  with pytest.raises(EnvironmentError, match="network"):
+    Thing().push_to_hub("org/my-model", upload=True)
