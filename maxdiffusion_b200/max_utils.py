@@ -201,3 +201,151 @@ def get_memory_allocations() -> dict:
            "free_gb": free / 2**30, "total_gb": total / 2**30}
   max_logging.log("memory: " + ", ".join(f"{k}={v:.2f}" for k, v in stats.items()))
   return stats
+
+
+# ---- small helpers that scripts written for the reference import from this module --------------------------------------
+def _leaves(tree):
+  """Tensors of a nested dict / list / tuple (or of a module's parameters), depth first."""
+  if isinstance(tree, torch.nn.Module):
+    yield from tree.parameters()
+  elif torch.is_tensor(tree):
+    yield tree
+  elif isinstance(tree, dict):
+    for v in tree.values():
+      yield from _leaves(v)
+  elif isinstance(tree, (list, tuple)):
+    for v in tree:
+      yield from _leaves(v)
+  elif tree is not None and hasattr(tree, "__array__"):
+    yield torch.as_tensor(tree.__array__())
+
+
+def l2norm_pytree(tree) -> float:
+  """sqrt of the sum of squares over every tensor of a nested structure (reference: src/maxdiffusion/max_utils.py:138-140)."""
+  total = 0.0
+  for t in _leaves(tree):
+    total += float(t.detach().double().pow(2).sum())
+  return total ** 0.5
+
+
+def calculate_num_params_from_pytree(params) -> int:
+  return sum(int(t.numel()) for t in _leaves(params))
+
+
+def get_global_batch_size(per_device_batch_size: float) -> float:
+  """Samples per step over all ranks of the job (one rank drives one GPU)."""
+  import torch.distributed as dist
+
+  world = dist.get_world_size() if dist.is_available() and dist.is_initialized() else int(os.environ.get("WORLD_SIZE", "1"))
+  return per_device_batch_size * world
+
+
+def get_precision(config) -> str:
+  """`precision` of the configuration as the name `torch.set_float32_matmul_precision` takes: DEFAULT -> "high" (TF32
+  products for fp32 operands), HIGH -> "high", HIGHEST -> "highest". bf16 operands are unaffected."""
+  return {"HIGHEST": "highest"}.get(str(config.get("precision", "DEFAULT")).upper(), "high")
+
+
+def safe_getattr(obj, name: str, default):
+  return getattr(obj, name, default) if obj is not None else default
+
+
+def profiler_enabled(config) -> bool:
+  return bool(config.get("enable_profiler", False))
+
+
+def is_gpu_backend(raw_keys) -> bool:
+  """Always a GPU backend here; a `hardware` key that says otherwise only steers the reference's runtime."""
+  return True
+
+
+def get_git_commit_hash() -> Optional[str]:
+  """Current commit of the working directory's repository, for run provenance; None outside a repository."""
+  import subprocess
+
+  try:
+    return subprocess.check_output(["git", "rev-parse", "HEAD"], stderr=subprocess.DEVNULL).strip().decode("utf-8")
+  except (subprocess.CalledProcessError, FileNotFoundError):
+    max_logging.log("Warning: could not read a git commit hash (no repository, or no git).")
+    return None
+
+
+def parse_gcs_bucket_and_prefix(destination_gcs_name: str) -> tuple:
+  parts = destination_gcs_name.replace("gs://", "").split("/")
+  return parts[0], "/".join(parts[1:])
+
+
+def _no_object_store(what: str):
+  raise EnvironmentError(f"{what}: object-store paths (gs://...) need network access, which this installation does not "
+                         "use; write to a local or mounted directory and copy from there")
+
+
+def upload_blob(destination_gcs_name: str, source_file_name: str):
+  _no_object_store(f"upload of {source_file_name} to {destination_gcs_name}")
+
+
+def download_blobs(source_gcs_folder: str, local_destination: str):
+  _no_object_store(f"download of {source_gcs_folder}")
+
+
+def delete_file(file_path: str) -> None:
+  try:
+    os.remove(file_path)
+  except FileNotFoundError:
+    max_logging.log(f"File not found: {file_path}")
+  except OSError as e:
+    max_logging.log(f"Error deleting file {file_path}: {e}")
+
+
+def save_images(config, images) -> list:
+  """Writes every image (PIL images or uint8 arrays) next to `output_file` (default `<run_name>_output_<seed>.png`),
+  numbering them when there are several (reference: src/maxdiffusion/max_utils.py:330-344)."""
+  import numpy as np
+  from PIL import Image
+
+  if str(config.get("output_dir", "") or "").startswith("gs://"):
+    _no_object_store("save_images")
+  stem, ext = os.path.splitext(str(config.get("output_file", "") or f"{config.get('run_name', 'run')}_output_{config.get('seed', 0)}.png"))
+  paths = []
+  for i, image in enumerate(images):
+    path = f"{stem}{ext}" if len(images) == 1 else f"{stem}_{i}{ext}"
+    if os.path.dirname(path):
+      os.makedirs(os.path.dirname(path), exist_ok=True)
+    if not isinstance(image, Image.Image):
+      arr = image.detach().cpu().numpy() if torch.is_tensor(image) else np.asarray(image)
+      image = Image.fromarray(arr.astype(np.uint8))
+    image.save(path)
+    paths.append(path)
+  max_logging.log(f"Saved {len(paths)} image(s), first: {paths[0]}")
+  return paths
+
+
+def write_metrics_locally(metrics: dict, step: int, config, file) -> None:
+  """One JSON line per step with the scalars, the step and the run name; the file is emptied at step 0 and closed
+  after the last step (reference: src/maxdiffusion/max_utils.py:223-242)."""
+  import json
+
+  if step == 0:
+    file.seek(0)
+    file.truncate(0)
+  line = {k: float(v) for k, v in metrics.get("scalar", metrics).items()}
+  line.update(step=float(step), run_name=str(config.get("run_name", "")))
+  file.write(json.dumps(line) + "\n")
+  if step == int(config.get("max_train_steps", 0)) - 1:
+    file.close()
+
+
+def initialize_summary_writer(config):
+  """TensorBoard writer on rank 0 (None elsewhere, or when TensorBoard is not installed)."""
+  if int(os.environ.get("RANK", "0")) != 0:
+    return None
+  try:
+    from torch.utils.tensorboard import SummaryWriter
+  except Exception:
+    return None
+  return SummaryWriter(str(config.get("tensorboard_dir", "") or os.path.join(str(config.get("output_dir", ".")), "tensorboard")))
+
+
+def close_summary_writer(summary_writer) -> None:
+  if summary_writer is not None:
+    summary_writer.close()

@@ -327,3 +327,53 @@ def test_gif_ply_and_obj_exporters_round_trip(tmp_path):
 
   lines = open(export_to_obj(mesh, str(tmp_path / "m.obj"))).read().splitlines()
   assert len(lines) == 6 and lines[1].split() == ["v", "1.0", "0.0", "0.0", "1.0", "0.0", "0.0"] and lines[-1] == "f 1 3 4"
+
+
+def test_max_utils_helpers(tmp_path):
+  import io
+  import json
+  import types
+
+  import numpy as np
+  import pytest
+
+  from maxdiffusion_b200 import max_utils as M
+
+  tree = {"a": torch.full((2, 2), 2.0), "b": [torch.ones(3), {"c": torch.zeros(5)}], "d": None}
+  assert abs(M.l2norm_pytree(tree) - (16 + 3) ** 0.5) < 1e-9 and M.calculate_num_params_from_pytree(tree) == 12
+  lin = torch.nn.Linear(3, 2)
+  assert M.calculate_num_params_from_pytree(lin) == 8
+  assert M.get_global_batch_size(0.5) == 0.5 and M.safe_getattr(None, "x", 7) == 7 and M.safe_getattr(lin, "in_features", 0) == 3
+  assert M.get_precision({"precision": "HIGHEST"}) == "highest" and M.get_precision({"precision": "DEFAULT"}) == "high"
+  assert M.profiler_enabled({"enable_profiler": True}) and M.is_gpu_backend({"hardware": "tpu"})
+  assert M.parse_gcs_bucket_and_prefix("gs://bucket/some/prefix") == ("bucket", "some/prefix")
+  with pytest.raises(EnvironmentError, match="network"):
+    M.upload_blob("gs://b/x", "file")
+  h = M.get_git_commit_hash()
+  assert h is None or len(h) == 40
+  (tmp_path / "x").write_text("1")
+  M.delete_file(str(tmp_path / "x"))
+  M.delete_file(str(tmp_path / "x"))               # missing: logged, not raised
+  assert not (tmp_path / "x").exists()
+  cfg = {"output_file": str(tmp_path / "img" / "out.png"), "output_dir": str(tmp_path), "run_name": "r", "seed": 3}
+  imgs = [np.zeros((4, 4, 3), np.uint8), torch.full((4, 4, 3), 255, dtype=torch.uint8)]
+  assert [os.path.basename(p) for p in M.save_images(cfg, imgs)] == ["out_0.png", "out_1.png"]
+  assert os.path.basename(M.save_images({**cfg, "output_file": ""}, imgs[:1])[0]) == "r_output_3.png"
+  os.remove("r_output_3.png")
+  with pytest.raises(EnvironmentError):
+    M.save_images({**cfg, "output_dir": "gs://bucket/x"}, imgs)
+
+  class File(io.StringIO):
+    closed_by_writer = False
+
+    def close(self):
+      self.closed_by_writer = True
+
+  f = File()
+  c = types.SimpleNamespace(get=lambda k, d=None: {"run_name": "r", "max_train_steps": 2}.get(k, d))
+  f.write("stale\n")
+  M.write_metrics_locally({"scalar": {"learning/loss": torch.tensor(0.5)}}, 0, c, f)
+  M.write_metrics_locally({"scalar": {"learning/loss": 0.25}}, 1, c, f)
+  lines = [json.loads(x) for x in f.getvalue().splitlines()]
+  assert len(lines) == 2 and lines[-1] == {"learning/loss": 0.25, "step": 1.0, "run_name": "r"} and f.closed_by_writer
+  M.close_summary_writer(None)
