@@ -139,13 +139,56 @@ def encode_xl(input_ids: Sequence[torch.Tensor], text_encoders: Sequence):
 
 
 def override_scheduler_config(scheduler_config: dict, config) -> dict:
-  """Applies the non-empty entries of `diffusion_scheduler_config` (`timestep_spacing`, `prediction_type`,
-  `rescale_zero_terminal_snr`, `_class_name`) over a pretrained scheduler config."""
+  """Applies the non-empty entries of `diffusion_scheduler_config` over a pretrained scheduler config. The four keys the
+  pipelines rely on always come out defined: an override wins, else the checkpoint's value, else a safe default
+  (`prediction_type` epsilon, `timestep_spacing` leading, `rescale_zero_terminal_snr` False) -- older scheduler files,
+  the SD 1.5 PNDM one for instance, omit some of them (reference: src/maxdiffusion/maxdiffusion_utils.py:149-174)."""
   out = dict(scheduler_config)
-  for k, v in dict(config.get("diffusion_scheduler_config", {}) or {}).items():
-    if v != "" and v is not None:
-      out[k] = v
+  over = {k: v for k, v in dict(config.get("diffusion_scheduler_config", {}) or {}).items() if v != "" and v is not None}
+  out.update(over)
+  for key, default in (("_class_name", ""), ("prediction_type", "epsilon"), ("timestep_spacing", "leading"),
+                       ("rescale_zero_terminal_snr", False)):
+    out.setdefault(key, default)
   return out
+
+
+def create_scheduler(scheduler_config: dict, config):
+  """(scheduler, state) of the class the (overridden) scheduler config names, with or without the reference's `Flax`
+  prefix (reference: src/maxdiffusion/maxdiffusion_utils.py:177-191)."""
+  from . import schedulers
+
+  cfg = override_scheduler_config(scheduler_config, config)
+  name = str(cfg.get("_class_name", ""))
+  cls = getattr(schedulers, name, None) or getattr(schedulers, name[4:] if name.startswith("Flax") else "Flax" + name, None)
+  if cls is None:
+    raise ValueError(f"unknown scheduler class {name!r}")
+  scheduler = cls.from_config({k: v for k, v in cfg.items() if not k.startswith("_")})
+  return scheduler, scheduler.create_state()
+
+
+def rescale_noise_cfg(noise_cfg: torch.Tensor, noise_pred_text: torch.Tensor, guidance_rescale: float = 0.0) -> torch.Tensor:
+  """Pulls the per-sample standard deviation of the guided prediction towards that of the conditional one by the
+  factor `guidance_rescale` (Lin et al., "Common Diffusion Noise Schedules and Sample Steps are Flawed", 3.4;
+  reference: src/maxdiffusion/maxdiffusion_utils.py:194-205)."""
+  dims = list(range(1, noise_cfg.dim()))
+  rescaled = noise_cfg * (noise_pred_text.std(dim=dims, keepdim=True, unbiased=False) / noise_cfg.std(dim=dims, keepdim=True, unbiased=False))
+  return guidance_rescale * rescaled + (1.0 - guidance_rescale) * noise_cfg
+
+
+def get_add_time_ids(original_size, crops_coords_top_left, target_size, bs: int, dtype=torch.float32) -> torch.Tensor:
+  """SDXL micro-conditioning rows [bs, 6]: (original h, w, crop top, left, target h, w)."""
+  return torch.tensor([list(original_size) + list(crops_coords_top_left) + list(target_size)] * bs, dtype=dtype)
+
+
+def convert_dict_to_pil(image):
+  """A dataset image stored as {"bytes": ..., "path": ...} becomes a PIL image; anything else passes through."""
+  if isinstance(image, dict):
+    import io
+
+    from PIL import Image
+
+    return Image.open(io.BytesIO(image["bytes"]))
+  return image
 
 
 # ---- dummy inputs and FLOPs -------------------------------------------------------------------------------------

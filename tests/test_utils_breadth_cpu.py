@@ -377,3 +377,44 @@ def test_max_utils_helpers(tmp_path):
   lines = [json.loads(x) for x in f.getvalue().splitlines()]
   assert len(lines) == 2 and lines[-1] == {"learning/loss": 0.25, "step": 1.0, "run_name": "r"} and f.closed_by_writer
   M.close_summary_writer(None)
+
+
+def test_scheduler_creation_from_a_checkpoint_config_and_small_pipeline_helpers():
+  """`create_scheduler` as the reference's src/maxdiffusion/tests/maxdiffusion_utils_test.py:73 uses it: overrides from
+  `diffusion_scheduler_config` win, keys an old scheduler file omits get safe defaults, the class is found with or
+  without the `Flax` prefix."""
+  import io
+  import types
+
+  from PIL import Image
+
+  from maxdiffusion_b200 import maxdiffusion_utils as U
+  from maxdiffusion_b200.schedulers import DDIMScheduler, PNDMScheduler
+
+  over = types.SimpleNamespace(get=lambda k, d=None: {"diffusion_scheduler_config": {
+      "prediction_type": "v_prediction", "rescale_zero_terminal_snr": True, "timestep_spacing": "trailing", "_class_name": ""}}.get(k, d))
+  ckpt = {"_class_name": "FlaxDDIMScheduler", "_diffusers_version": "0.20", "beta_schedule": "scaled_linear", "beta_start": 0.00085,
+          "beta_end": 0.012, "num_train_timesteps": 1000, "prediction_type": "epsilon"}
+  sched, state = U.create_scheduler(ckpt, over)
+  assert isinstance(sched, DDIMScheduler) and state is not None
+  assert (sched.config.prediction_type, sched.config.timestep_spacing, sched.config.rescale_zero_terminal_snr) == ("v_prediction", "trailing", True)
+  plain = types.SimpleNamespace(get=lambda k, d=None: d)
+  old_file = {"_class_name": "PNDMScheduler", "beta_schedule": "scaled_linear", "beta_start": 0.00085, "beta_end": 0.012,
+              "num_train_timesteps": 1000, "skip_prk_steps": True}
+  cfg = U.override_scheduler_config(old_file, plain)
+  assert (cfg["prediction_type"], cfg["timestep_spacing"], cfg["rescale_zero_terminal_snr"]) == ("epsilon", "leading", False)
+  assert isinstance(U.create_scheduler(old_file, plain)[0], PNDMScheduler) and "prediction_type" not in old_file
+  import pytest
+
+  with pytest.raises(ValueError, match="unknown scheduler"):
+    U.create_scheduler({"_class_name": "NoSuchScheduler"}, plain)
+
+  cfg_noise, text = torch.tensor([[[1.0, 2.0], [3.0, 4.0]]]), torch.ones(1, 2, 2) + torch.tensor([[[0.0, 1.0], [2.0, 3.0]]]) * 0.5
+  assert torch.equal(U.rescale_noise_cfg(cfg_noise, text, 0.0), cfg_noise)
+  full = U.rescale_noise_cfg(cfg_noise, text, 1.0)
+  assert torch.allclose(full.std(unbiased=False), text.std(unbiased=False), atol=1e-6)
+  assert U.get_add_time_ids((1024, 1024), (0, 0), (768, 512), 2).tolist() == [[1024, 1024, 0, 0, 768, 512]] * 2
+  buf = io.BytesIO()
+  Image.new("RGB", (3, 2), (9, 8, 7)).save(buf, format="PNG")
+  img = U.convert_dict_to_pil({"bytes": buf.getvalue(), "path": None})
+  assert img.size == (3, 2) and U.convert_dict_to_pil(img) is img
