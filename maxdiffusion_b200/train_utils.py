@@ -54,6 +54,51 @@ def generate_timestep_weights(config, num_timesteps: int) -> torch.Tensor:
   return w / w.sum()
 
 
+# metric name in the scalars of a step -> short name used by dashboards (reference: src/maxdiffusion/train_utils.py:86-103)
+METRICS_TO_MANAGED = {
+    "learning/loss": "loss", "learning/current_learning_rate": "learning_rate", "learning/grad_norm": "gradient_norm",
+    "learning/total_weights": "total_weights", "perf/step_time_seconds": "step_time",
+    "perf/per_device_tflops_per_sec": "tflops",
+}
+
+
+def get_first_step(state) -> int:
+  """Step a restored state resumes from (`state.step`, an engine's `step_count`, or a plain number)."""
+  for name in ("step", "step_count"):
+    if hasattr(state, name):
+      return int(getattr(state, name))
+  return int(state)
+
+
+def load_next_batch(train_iter, example_batch, config):
+  """The next batch, or -- with `reuse_example_batch` -- the first one again and again: steps then time the model
+  without the input pipeline (reference: src/maxdiffusion/train_utils.py:30-35)."""
+  if config.get("reuse_example_batch", False) and example_batch is not None:
+    return example_batch
+  return next(train_iter)
+
+
+def record_scalar_metrics(metrics: dict, step_time_delta, per_device_tflops: float, lr: float, total_weights=None) -> None:
+  """Adds the per-step performance scalars to `metrics["scalar"]`; `step_time_delta` is seconds or a timedelta."""
+  seconds = step_time_delta.total_seconds() if hasattr(step_time_delta, "total_seconds") else float(step_time_delta)
+  metrics.setdefault("scalar", {}).update({
+      "perf/step_time_seconds": seconds, "perf/per_device_tflops": per_device_tflops,
+      "perf/per_device_tflops_per_sec": per_device_tflops / seconds, "learning/current_learning_rate": lr})
+  if total_weights is not None:
+    metrics["scalar"]["learning/total_weights"] = float(total_weights)
+
+
+def get_params_to_save(params):
+  """Host copies of every tensor of a nested structure (what a checkpoint writes)."""
+  if torch.is_tensor(params):
+    return params.detach().to("cpu")
+  if isinstance(params, dict):
+    return {k: get_params_to_save(v) for k, v in params.items()}
+  if isinstance(params, (list, tuple)):
+    return type(params)(get_params_to_save(v) for v in params)
+  return params
+
+
 class MetricsWriter:
 
   def __init__(self, config, rank: int = 0):

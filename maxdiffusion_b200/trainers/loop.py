@@ -19,7 +19,7 @@ import torch.distributed as dist
 
 from .. import max_logging
 from ..ops import _lib
-from ..train_utils import MetricsWriter
+from ..train_utils import MetricsWriter, load_next_batch
 
 
 class EncodedBatchCache:
@@ -137,13 +137,19 @@ def run_training_loop(trainer, data, checkpointer=None, evaluate: Optional[Calla
   monitor = _health_monitor(config, trainer.mesh)
   step_barrier = bool(config.get("health_step_barrier", True))
   pool = ThreadPoolExecutor(max_workers=1)
-  nxt = pool.submit(lambda: next(data))
+  reuse = {"batch": None}   # `reuse_example_batch`: the first batch is served for every step
+
+  def fetch():
+    reuse["batch"] = load_next_batch(data, reuse["batch"], config)
+    return reuse["batch"]
+
+  nxt = pool.submit(fetch)
   timed._emit("Starting: training loop...")
   loop_t0 = time.perf_counter()
   try:
     while trainer.step < max_steps:
       batch = nxt.result()
-      nxt = pool.submit(lambda: next(data))
+      nxt = pool.submit(fetch)
       t0 = time.perf_counter()
       with guarded_step(monitor, trainer.step):  # peers checked first; this rank's exception is announced to them
         _maybe_inject_failure(config, trainer)

@@ -232,7 +232,7 @@ class WanTrainer:
     return ((int(c.get("num_frames", 81)) - 1) // 4 + 1) // pt * (int(c.get("height", 480)) // 8 // ph) * (int(c.get("width", 832)) // 8 // pw)
 
   def start_training(self):
-    from ..train_utils import MetricsWriter
+    from ..train_utils import MetricsWriter, load_next_batch
 
     config = self.config
     data = self.load_dataset()
@@ -242,7 +242,13 @@ class WanTrainer:
     max_logging.log(f"Calculated TFLOPs per pass: {tflops:.4f} ({per_device:.4f} per device)")
     max_steps = int(config.get("max_train_steps", 1))
     pool = ThreadPoolExecutor(max_workers=1)
-    nxt = pool.submit(lambda: next(data))
+    reuse = {"batch": None}   # `reuse_example_batch`: the first batch is served for every step
+
+    def fetch():
+      reuse["batch"] = load_next_batch(data, reuse["batch"], config)
+      return reuse["batch"]
+
+    nxt = pool.submit(fetch)
     checkpointer = None
     if int(config.get("checkpoint_every", -1)) > 0 or config.get("save_final_checkpoint", False):
       from ..checkpointing.wan_checkpointer import WanCheckpointer
@@ -265,7 +271,7 @@ class WanTrainer:
 
     while self.step < max_steps:
       batch = nxt.result()
-      nxt = pool.submit(lambda: next(data))
+      nxt = pool.submit(fetch)
       if profiler is not None:
         profiler.maybe_start(self.step)
       t0 = time.perf_counter()

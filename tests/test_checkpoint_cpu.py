@@ -127,3 +127,52 @@ def test_checkpoint_of_one_expert_does_not_fill_a_two_expert_pipeline(tmp_path):
   with pytest.raises(ValueError, match="wan_state"):
     WanCheckpointer(c4).restore_into_pipeline(one)
   WanCheckpointer(c2.replace(checkpoint_dir=c3.checkpoint_dir)).restore_into_pipeline(two)   # matching variant: fine
+
+
+def test_train_wan_loop_checkpoints_resumes_and_can_reuse_one_batch(tmp_path):
+  """`train_wan.train`: the loop writes periodic and final checkpoints, a second start in the same output directory
+  resumes from the last one, and `reuse_example_batch` asks the data source for one batch only."""
+  from maxdiffusion_b200 import train_wan
+
+  def config(steps, *extra):
+    return pyconfig.initialize(
+        ["t", CFG, "run_name=loop", f"output_dir={tmp_path}", "height=32", "width=32", "num_frames=5", "dataset_type=synthetic",
+         "wan_preset=tiny", f"wan_config_overrides={TINY}", "warmup_steps_fraction=0.0", "log_config=false", "write_metrics=false",
+         "learning_rate=1e-3", "synthetic_override_text_dim=32", "max_sequence_length=8", "save_optimizer=true",
+         "enable_async_checkpointing=false", "checkpoint_every=2", "save_final_checkpoint=true", f"max_train_steps={steps}",
+         *extra], unittest=True)
+
+  first = train_wan.train(config(3))
+  ckpt = first.config.checkpoint_dir
+  assert first.step == 3 and sorted(int(d) for d in os.listdir(ckpt) if d.isdigit()) == [2, 3]
+  calls = []
+  original = WanTrainer.train_step
+
+  def counted(self, batch):
+    calls.append(self.step)
+    return original(self, batch)
+
+  WanTrainer.train_step = counted
+  try:
+    second = train_wan.train(config(5))                     # picks up at step 3: two steps are left
+  finally:
+    WanTrainer.train_step = original
+  assert len(calls) == 2 and second.step == 5 and second.engine.step_count == 5
+  assert sorted(int(d) for d in os.listdir(ckpt) if d.isdigit()) == [2, 3, 4, 5]
+
+  pulls = []
+  c = config(8, "reuse_example_batch=true", "checkpoint_every=-1", "save_final_checkpoint=false")
+  trainer = WanTrainer(c, mesh=create_device_mesh(c), device="cpu")
+  source = trainer.load_dataset()
+
+  class Counting:
+    def __iter__(self):
+      return self
+
+    def __next__(self):
+      pulls.append(1)
+      return next(source)
+
+  trainer.load_dataset = lambda: Counting()
+  trainer.start_training()
+  assert trainer.step == 8 and len(pulls) == 1

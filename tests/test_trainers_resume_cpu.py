@@ -168,3 +168,43 @@ def test_phases_around_the_steps_are_timed_into_the_timing_file(tmp_path):
   quiet = PhaseTimer({"write_timing_metrics": True, "timing_metrics_file": str(tmp_path / "r1.log")}, rank=1)
   quiet("y", lambda: None)
   assert not (tmp_path / "r1.log").exists()
+
+
+def test_reuse_example_batch_serves_the_first_batch_for_every_step(tmp_path):
+  """`reuse_example_batch=True` takes the input pipeline out of the steps: the loop asks the data source once."""
+  import datetime
+
+  from maxdiffusion_b200 import train_utils as T
+  from maxdiffusion_b200.trainers.stable_diffusion_trainer import StableDiffusionTrainer
+
+  for reuse, want in (("true", 1), ("false", None)):
+    c = _cfg("base15.yml", SD + ["unet_preset=tiny_sd", "max_train_steps=3", "checkpoint_every=-1", f"reuse_example_batch={reuse}"],
+             tmp_path / reuse)
+    t = StableDiffusionTrainer(c, mesh=create_device_mesh(c), device="cpu")
+    pulls = []
+    source = t.load_dataset()
+
+    class Counting:
+      def __iter__(self):
+        return self
+
+      def __next__(self):
+        pulls.append(1)
+        return next(source)
+
+    t.start_training(data=Counting())
+    assert t.step == 3 and (len(pulls) == want if want else len(pulls) >= 3)
+
+  # the small helpers around it
+  assert T.load_next_batch(iter([1, 2]), None, {"reuse_example_batch": True}) == 1
+  assert T.load_next_batch(iter([1, 2]), "kept", {"reuse_example_batch": True}) == "kept"
+  assert T.load_next_batch(iter([1, 2]), "kept", {"reuse_example_batch": False}) == 1
+  import types
+
+  assert T.get_first_step(types.SimpleNamespace(step=torch.tensor(7))) == 7 and T.get_first_step(3) == 3
+  m = {"scalar": {"learning/loss": 0.5}}
+  T.record_scalar_metrics(m, datetime.timedelta(seconds=2), 10.0, 1e-4, total_weights=5)
+  assert m["scalar"]["perf/per_device_tflops_per_sec"] == 5.0 and m["scalar"]["learning/total_weights"] == 5.0
+  assert set(m["scalar"]) - {"perf/per_device_tflops"} <= set(T.METRICS_TO_MANAGED)
+  saved = T.get_params_to_save({"a": torch.ones(2, requires_grad=True), "b": [torch.zeros(1)]})
+  assert saved["a"].device.type == "cpu" and not saved["a"].requires_grad and isinstance(saved["b"], list)
