@@ -278,6 +278,11 @@ class LTX2VideoTransformer3DModel(nn.Module):
     """Text K/V of every block (list of {"attn2": (k, v), "audio_attn2": (k, v)}), reference :1244-1311. Only valid
     without prompt modulation (`cross_attn_mod` changes the text per step)."""
     text, audio_text = self.project_captions(encoder_hidden_states, audio_encoder_hidden_states)
+    if self.cfg.cross_attn_mod:
+      # the prompt is modulated by the timestep (LTX-2.3), so its keys and values change every step and caching them
+      # would bypass the modulation (the reference refuses the call: ltx2 `compute_kv_cache`); what does not depend on
+      # the step -- the caption projections -- is still handed back, and `forward` recomputes K / V from it
+      return None, (text, audio_text)
     return [blk.compute_kv(text, audio_text) for blk in self.transformer_blocks], (text, audio_text)
 
   def rope_tables(self, batch, num_frames, height, width, audio_num_frames, fps=24.0, device=None, video_coords=None,

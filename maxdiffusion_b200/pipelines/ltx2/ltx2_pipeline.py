@@ -269,6 +269,7 @@ class LTX2Pipeline:
 
     # loop constants: rotary tables, text K/V, per-step time embeddings
     rope = self.transformer.rope_tables(1, lf, lh, lw, audio_frames, frame_rate, self.device)
+    # with per-timestep prompt modulation (LTX-2.3) only the caption projections are cached, not the keys / values
     kv = self.transformer.compute_kv_cache(video_text, audio_text) if use_kv_cache else None
     ones = torch.ones((B, 1, 1), device=self.device)
     modality_mask = perturbation_mask = None

@@ -313,3 +313,18 @@ def test_single_file_upsampler_and_reference_only_config_keys(tmp_path):
   got = pipe.latent_upsampler.state_dict()
   assert all(torch.equal(got[k], v) for k, v in src.state_dict().items())
   assert pipe.latent_upsampler.spatial and not pipe.latent_upsampler.temporal
+
+
+def test_prompt_modulation_keeps_text_keys_and_values_out_of_the_cache():
+  """Caching must not bypass the per-timestep prompt modulation of LTX-2.3 (the reference refuses the call,
+  src/maxdiffusion/tests/ltx2/test_transformer_ltx2.py:158): here the cache then holds the caption projections only and
+  the forward pass computes the modulated K / V itself, with the same result as without a cache."""
+  from maxdiffusion_b200.models.ltx2.transformer_ltx2 import LTX2Config, LTX2VideoTransformer3DModel
+
+  cfg = LTX2Config(**{**LTX2_PRESETS["tiny"], "cross_attn_mod": True})
+  model = LTX2VideoTransformer3DModel(cfg).eval()
+  txt = torch.randn(1, 5, 24)
+  layers_kv, (text, audio_text) = model.compute_kv_cache(txt, txt)
+  assert layers_kv is None and text.shape[:2] == (1, 5) and audio_text.shape[:2] == (1, 5)
+  plain = LTX2VideoTransformer3DModel(LTX2Config(**LTX2_PRESETS["tiny"])).eval()
+  assert len(plain.compute_kv_cache(txt, txt)[0]) == plain.cfg.num_layers
