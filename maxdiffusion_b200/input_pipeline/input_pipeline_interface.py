@@ -143,6 +143,65 @@ class HFDatasetIterator:
     return {"pixel_values": _pin(torch.cat(imgs)), "captions": caps}
 
 
+class DreamboothIterator:
+  """Instance + class (prior-preservation) batches for Dreambooth from two image folders.
+
+  There are as many pairs as class images; the instance images are cycled to match (few photographs of the subject
+  against many pictures of its class). A batch carries the instance half under the plain keys and the class half under
+  `class_`-prefixed keys, which is what `DreamboothTrainer.loss` weighs separately
+  (reference: src/maxdiffusion/input_pipeline/input_pipeline_interface.py:127-234, `make_dreambooth_train_iterator`)."""
+
+  EXTENSIONS = (".png", ".jpg", ".jpeg", ".webp", ".bmp")
+
+  def __init__(self, config, batch_size: int, shard_index: int = 0, num_shards: int = 1):
+    def listing(folder, what):
+      files = sorted(f for f in os.listdir(folder) if f.lower().endswith(self.EXTENSIONS)) if os.path.isdir(folder) else []
+      if not files:
+        raise FileNotFoundError(f"no {what} images under {folder!r}")
+      return [os.path.join(folder, f) for f in files]
+
+    self.class_files = listing(str(config.get("class_data_dir", "")), "class")
+    self.instance_files = listing(str(config.get("instance_data_dir", "")), "instance")
+    self.pairs = list(range(len(self.class_files)))[shard_index::num_shards] or list(range(len(self.class_files)))
+    self.config, self.batch_size = config, batch_size
+    self.pos, self.rng = 0, random.Random(int(config.get("seed", 0)) + shard_index)
+
+  def __iter__(self):
+    return self
+
+  def _load(self, path: str) -> torch.Tensor:
+    from PIL import Image
+
+    from ..image_processor import VaeImageProcessor
+
+    res = int(self.config.get("resolution", 512))
+    with Image.open(path) as im:
+      return VaeImageProcessor().preprocess(im.convert("RGB"), res, res, center_crop=bool(self.config.get("center_crop", False)),
+                                            random_flip=bool(self.config.get("random_flip", False)), rng=self.rng)
+
+  def __next__(self) -> dict:
+    inst, cls = [], []
+    for _ in range(self.batch_size):
+      if self.pos >= len(self.pairs):
+        self.pos = 0
+        if self.config.get("enable_data_shuffling", True):
+          self.rng.shuffle(self.pairs)
+      i = self.pairs[self.pos]
+      self.pos += 1
+      inst.append(self._load(self.instance_files[i % len(self.instance_files)]))
+      cls.append(self._load(self.class_files[i]))
+    n = self.batch_size
+    return {"pixel_values": _pin(torch.cat(inst)), "captions": [str(self.config.get("instance_prompt", ""))] * n,
+            "class_pixel_values": _pin(torch.cat(cls)), "class_captions": [str(self.config.get("class_prompt", ""))] * n}
+
+
+def make_dreambooth_train_iterator(config, mesh, batch_size: int):
+  """The Dreambooth iterator of this rank: the pairs are split over the ranks that hold different samples."""
+  shards = mesh.size("data") * mesh.size("fsdp")
+  index = mesh.coords.get("data", 0) * mesh.size("fsdp") + mesh.coords.get("fsdp", 0)
+  return DreamboothIterator(config, batch_size, index, shards)
+
+
 def make_data_iterator(config, mesh, batch_size: int, eval_mode: bool = False):
   kind = str(config.get("dataset_type", "synthetic"))
   dp = mesh.size("data") * mesh.size("fsdp")

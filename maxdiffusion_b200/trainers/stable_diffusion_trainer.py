@@ -251,8 +251,19 @@ class DreamboothTrainer(StableDiffusionTrainer):
         made += 1
     return made
 
+  def load_dataset(self):
+    """Instance / class image folders when `instance_data_dir` and `class_data_dir` are set (the Dreambooth data set of
+    the reference), else the configured input pipeline."""
+    c = self.config
+    if str(c.get("instance_data_dir", "") or "") and str(c.get("class_data_dir", "") or "") and \
+        str(c.get("dataset_type", "synthetic")) != "synthetic":
+      from ..input_pipeline.input_pipeline_interface import make_dreambooth_train_iterator
+
+      return make_dreambooth_train_iterator(c, self.mesh, self.batch_size)
+    return super().load_dataset()
+
   def loss(self, batch: dict) -> torch.Tensor:
-    if "class_latents" not in batch:
+    if not any(k.startswith("class_") for k in batch):
       return super().loss(batch)
     inst = {k: v for k, v in batch.items() if not k.startswith("class_")}
     cls = {k[len("class_"):]: v for k, v in batch.items() if k.startswith("class_")}

@@ -186,3 +186,53 @@ def test_synthetic_iterators_have_the_shapes_and_keys_the_reference_test_expects
   seq = (512 // 16) ** 2
   assert b["pixel_values"].shape == (3, seq, 64) and b["input_ids"].shape == (3, 512, 3) and b["img_ids"].shape == (3, seq, 3)
   assert b["text_embeds"].shape == (3, 512, 4096) and b["prompt_embeds"].shape == (3, 768) and b["txt_ids"] is b["input_ids"]
+
+
+def test_dreambooth_iterator_pairs_every_class_image_with_a_cycled_instance_image(tmp_path):
+  """Two folders -> batches with an instance half (plain keys) and a class half (`class_` keys): as many pairs as
+  class images, instance images cycled; `DreamboothTrainer.loss` weighs the halves separately."""
+  import types
+
+  from PIL import Image
+
+  from maxdiffusion_b200.input_pipeline.input_pipeline_interface import DreamboothIterator, make_dreambooth_train_iterator
+
+  for folder, count, base in (("inst", 2, 40), ("cls", 5, 200)):
+    os.makedirs(tmp_path / folder)
+    for i in range(count):
+      Image.new("RGB", (20, 16), (base + 10 * i, 0, 0)).save(tmp_path / folder / f"{i}.png")
+  (tmp_path / "cls" / "notes.txt").write_text("not an image")
+  cfg = {"instance_data_dir": str(tmp_path / "inst"), "class_data_dir": str(tmp_path / "cls"), "resolution": 8, "seed": 0,
+         "instance_prompt": "a photo of sks dog", "class_prompt": "a photo of a dog", "enable_data_shuffling": False,
+         "center_crop": True}
+  it = DreamboothIterator(types.SimpleNamespace(get=cfg.get), batch_size=2)
+  assert len(it.pairs) == 5 and len(it.instance_files) == 2
+  red = lambda t: [round((float(x[0].mean()) + 1) * 127.5) for x in t]
+  b1, b2, b3 = next(it), next(it), next(it)
+  assert b1["pixel_values"].shape == (2, 3, 8, 8) and b1["class_pixel_values"].shape == (2, 3, 8, 8)
+  assert b1["captions"] == ["a photo of sks dog"] * 2 and b1["class_captions"] == ["a photo of a dog"] * 2
+  assert red(b1["class_pixel_values"]) + red(b2["class_pixel_values"]) + red(b3["class_pixel_values"]) == [200, 210, 220, 230, 240, 200]
+  assert red(b1["pixel_values"]) + red(b2["pixel_values"]) + red(b3["pixel_values"]) == [40, 50, 40, 50, 40, 40]   # cycled, then wraps
+  mesh = types.SimpleNamespace(size=lambda a: {"data": 2, "fsdp": 1}.get(a, 1), coords={"data": 1, "fsdp": 0})
+  sharded = make_dreambooth_train_iterator(types.SimpleNamespace(get=cfg.get), mesh, 1)
+  assert sharded.pairs == [1, 3]
+  import pytest
+
+  with pytest.raises(FileNotFoundError, match="no instance images"):
+    DreamboothIterator(types.SimpleNamespace(get={**cfg, "instance_data_dir": str(tmp_path / "none")}.get), 1)
+
+
+def test_dreambooth_loss_takes_the_class_half_of_a_pixel_batch(monkeypatch):
+  import types
+
+  from maxdiffusion_b200.trainers import stable_diffusion_trainer as T
+
+  seen = []
+  monkeypatch.setattr(T.StableDiffusionTrainer, "loss", lambda self, batch: (seen.append(sorted(batch)), torch.tensor(2.0))[1])
+  stub = T.DreamboothTrainer.__new__(T.DreamboothTrainer)
+  stub.config = {"prior_loss_weight": 0.5}
+  batch = {"pixel_values": torch.zeros(1), "captions": ["a"], "class_pixel_values": torch.zeros(1), "class_captions": ["b"]}
+  assert float(T.DreamboothTrainer.loss(stub, batch)) == 3.0                 # instance term + 0.5 x class term
+  assert seen == [["captions", "pixel_values"], ["captions", "pixel_values"]]
+  seen.clear()
+  assert float(T.DreamboothTrainer.loss(stub, {"latents": torch.zeros(1)})) == 2.0 and len(seen) == 1
