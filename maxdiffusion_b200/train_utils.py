@@ -7,6 +7,7 @@ JSONL `metrics_file` consumed by `end_to_end/eval_assert.py`), and a console lin
 """
 from __future__ import annotations
 
+import contextlib
 import json
 import os
 import queue
@@ -154,3 +155,16 @@ class MetricsWriter:
       self.tb.close()
     if self.file is not None:
       self.file.close()
+
+
+def write_metrics(writer: "MetricsWriter", metrics: dict, step: int, config=None) -> None:
+  """Function form of `MetricsWriter.write` with the reference's argument shape (`metrics["scalar"]` holds the values;
+  the writer thread does the file and TensorBoard work one step behind the loop)."""
+  writer.write(int(step), {k: float(v) for k, v in metrics.get("scalar", metrics).items()})
+
+
+@contextlib.contextmanager
+def transformer_engine_context():
+  """Present for scripts that wrap their training call in it: the reference uses it to tell TransformerEngine about
+  its mesh; nothing here depends on that library, so the block simply runs."""
+  yield

@@ -208,3 +208,19 @@ def test_reuse_example_batch_serves_the_first_batch_for_every_step(tmp_path):
   assert set(m["scalar"]) - {"perf/per_device_tflops"} <= set(T.METRICS_TO_MANAGED)
   saved = T.get_params_to_save({"a": torch.ones(2, requires_grad=True), "b": [torch.zeros(1)]})
   assert saved["a"].device.type == "cpu" and not saved["a"].requires_grad and isinstance(saved["b"], list)
+
+
+def test_write_metrics_function_form(tmp_path):
+  import json
+  import types
+
+  from maxdiffusion_b200 import train_utils as T
+
+  path = tmp_path / "m.jsonl"
+  cfg = {"metrics_file": str(path), "write_metrics": True, "log_period": 1}
+  w = T.MetricsWriter(types.SimpleNamespace(get=cfg.get), rank=0)
+  T.write_metrics(w, {"scalar": {"learning/loss": torch.tensor(0.25)}}, 3)
+  w.close()
+  assert json.loads(path.read_text().splitlines()[-1]) == {"step": 3, "learning/loss": 0.25}
+  with T.transformer_engine_context():
+    pass
