@@ -291,7 +291,7 @@ def main() -> int:
                             f"(peak {torch.cuda.max_memory_reserved() / 2**30:.0f} GiB reserved)",
                    "optimizer": "AdamW, bf16 moments, stochastic rounding, step inside the timed region",
                    "l2": "inputs larger than L2 (activations and weights of every block exceed 126 MB)",
-                   "baseline_note": "BASELINE.md P2': 2100 tokens/s on TPU v5p-8 at 720p (75 600 tokens)"},
+                   "baseline_note": "published reference figure: 2100 tokens/s on TPU v5p-8 at 720p (75 600 tokens)"},
         "clocks": clocks,
         "e2e": {"value": e2e_tokens_per_s, "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 4,
                 "seconds_per_step": e2e_s.item() / args.steps},
