@@ -31,7 +31,8 @@ class BaseStableDiffusionCheckpointer:
     self.world = dist.get_world_size() if init else 1
     self.manager = create_checkpoint_manager(config.get("checkpoint_dir", ""), checkpoint_type,
                                              enable_async=bool(config.get("enable_async_checkpointing", True)),
-                                             dataset_type=str(config.get("dataset_type", "")), rank=self.rank)
+                                             dataset_type=str(config.get("dataset_type", "")), rank=self.rank,
+                                             single_replica=bool(config.get("enable_single_replica_ckpt_restoring", False)))
 
   def save(self, step: int, trainer, data_iterator=None) -> None:
     unet = trainer.unet

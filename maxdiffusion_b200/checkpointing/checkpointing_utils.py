@@ -213,10 +213,32 @@ class CheckpointManager:
     with open(os.path.join(self.directory, str(step), name, "metadata")) as f:
       return json.load(f)
 
+  single_replica = False   # `enable_single_replica_ckpt_restoring`: one rank reads, the others receive
+
   def restore_state(self, step: int, name: str) -> Dict[str, torch.Tensor]:
+    """The tensors of a state item. With `single_replica` and several ranks, rank 0 alone reads the file and
+    broadcasts names, shapes and contents; the other ranks never touch the disk (what the reference's
+    `enable_single_replica_ckpt_restoring` does for replicas on a shared file system,
+    src/maxdiffusion/checkpointing/checkpointing_utils.py:246-267). Every rank has to make the call."""
     from safetensors.torch import load_file
 
-    return load_file(os.path.join(self.directory, str(step), name, "state.safetensors"))
+    path = os.path.join(self.directory, str(step), name, "state.safetensors")
+    import torch.distributed as dist
+
+    if not (self.single_replica and dist.is_available() and dist.is_initialized() and dist.get_world_size() > 1):
+      return load_file(path)
+    src = 0
+    state = load_file(path) if dist.get_rank() == src else None
+    meta = [[(k, tuple(v.shape), v.dtype) for k, v in state.items()] if state is not None else None]
+    dist.broadcast_object_list(meta, src=src)
+    # collectives of the default group run on its own device type
+    device = torch.device("cuda", torch.cuda.current_device()) if dist.get_backend() == "nccl" else torch.device("cpu")
+    out = {}
+    for key, shape, dtype in meta[0]:
+      t = state[key].to(device) if state is not None else torch.empty(shape, dtype=dtype, device=device)
+      dist.broadcast(t, src=src)
+      out[key] = t.cpu()
+    return out
 
   def restore_sharded(self, step: int, name: str) -> list[Dict[str, torch.Tensor]]:
     """Every rank's shard file, in rank order (the caller re-shards for the current topology)."""
@@ -232,5 +254,7 @@ class CheckpointManager:
 
 
 def create_checkpoint_manager(checkpoint_dir: str, checkpoint_type: str, enable_async: bool = True,
-                              dataset_type: str = "", rank: int = 0, store=None) -> CheckpointManager:
-  return CheckpointManager(checkpoint_dir, item_names_for(checkpoint_type, dataset_type), enable_async, rank, store=store)
+                              dataset_type: str = "", rank: int = 0, store=None, single_replica: bool = False) -> CheckpointManager:
+  mgr = CheckpointManager(checkpoint_dir, item_names_for(checkpoint_type, dataset_type), enable_async, rank, store=store)
+  mgr.single_replica = bool(single_replica)
+  return mgr

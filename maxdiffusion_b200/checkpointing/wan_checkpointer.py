@@ -102,7 +102,8 @@ class WanCheckpointer:
         store = None
     self.manager = create_checkpoint_manager(config.get("checkpoint_dir", ""), checkpoint_type,
                                              enable_async=bool(config.get("enable_async_checkpointing", True)),
-                                             dataset_type=str(config.get("dataset_type", "")), rank=rank, store=store)
+                                             dataset_type=str(config.get("dataset_type", "")), rank=rank, store=store,
+                                             single_replica=bool(config.get("enable_single_replica_ckpt_restoring", False)))
 
   # ---- training state ----------------------------------------------------------------------
   def save(self, step: int, trainer) -> None:

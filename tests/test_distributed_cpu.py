@@ -364,3 +364,33 @@ def _cfg_fold(rank, world):
 def test_cfg_batch_folds_into_heads_when_the_heads_alone_do_not_split():
   for err in run_ranks(_cfg_fold, 2):
     assert err < 1e-5
+
+
+def _single_replica_restore(rank, world, folder):
+  """Rank 0 reads the state file; rank 1 is forbidden to open it and still ends up with the same tensors."""
+  import safetensors.torch as st
+
+  from maxdiffusion_b200.checkpointing.checkpointing_utils import WAN_CHECKPOINT, create_checkpoint_manager
+
+  mgr = create_checkpoint_manager(folder, WAN_CHECKPOINT, enable_async=False, rank=rank, single_replica=True)
+  if rank != 0:
+    def forbidden(*a, **k):
+      raise AssertionError("this rank must not read the checkpoint file")
+    st.load_file = forbidden
+  state = mgr.restore_state(mgr.latest_step(), "wan_state")
+  return {k: (v.dtype, v.tolist()) for k, v in state.items()}
+
+
+def test_single_replica_restore_reads_on_one_rank_and_broadcasts(tmp_path):
+  from maxdiffusion_b200.checkpointing.checkpointing_utils import WAN_CHECKPOINT, create_checkpoint_manager
+
+  mgr = create_checkpoint_manager(str(tmp_path), WAN_CHECKPOINT, enable_async=False)
+  want = {"a/kernel": torch.arange(6, dtype=torch.float32).reshape(2, 3), "b/scale": torch.tensor([1.5, -2.0]).to(torch.bfloat16),
+          "c/steps": torch.tensor([7], dtype=torch.int64)}
+  mgr.save(4, {"wan_config": {"dim": 8}, "wan_state": want})
+  mgr.wait_until_finished()
+  got = run_ranks(_single_replica_restore, 2, str(tmp_path))
+  expect = {k: (v.dtype, v.tolist()) for k, v in want.items()}
+  assert got[0] == expect and got[1] == expect
+  # one process, or the switch off: a plain read
+  assert {k: v.tolist() for k, v in mgr.restore_state(4, "wan_state").items()} == {k: v.tolist() for k, v in want.items()}
