@@ -214,6 +214,77 @@ class WanTrainer:
     return {"learning/loss": loss_value, "learning/max_grad_norm": stats["grad_norm"],
             "learning/max_abs_grad": stats["max_abs_grad"], "learning/current_learning_rate": lr}
 
+  # ------------------------------------------------------------------ evaluation
+  @torch.no_grad()
+  def eval_step(self, batch: dict, host_inputs: bool = True) -> torch.Tensor:
+    """Per-sample loss [B] of a batch that brings its own `timesteps`, without touching the weights: the training
+    objective (flow-matching target, timestep weights unless `disable_training_weights`) averaged over everything but
+    the batch axis (reference: src/maxdiffusion/trainers/wan_trainer.py:192-243, `eval_step`)."""
+    if host_inputs:
+      batch = self.to_device(batch)
+    latents = batch["latents"].to(self.dtype)
+    text = batch["encoder_hidden_states"].to(self.dtype)
+    timesteps = batch["timesteps"].to(self.device)
+    noise = batch.get("noise")
+    if noise is None:
+      noise = torch.randn(latents.shape, generator=self.gen, device=self.device, dtype=torch.float32)
+    noisy, target, weights = self.scheduler.apply_flow_match(noise.float(), latents.float(), timesteps, self.scheduler_state)
+    was_training = self.model.training
+    self.model.eval()
+    try:
+      pred = self.model(noisy.to(self.dtype), timesteps, text, pctx=self.pctx, return_tokens=True, **self.model_kwargs(batch))
+    finally:
+      self.model.train(was_training)
+    tgt, _ = self.model.patchify(target, channel_last=True)
+    total = tgt[0].numel()
+    if self.pctx is not None:
+      tgt = self.pctx.shard_sequence(tgt)
+      valid = self.pctx.valid_lengths(self.pctx.size, tgt.shape[1])[self.pctx.rank]
+      pred, tgt = pred[:, :valid], tgt[:, :valid]
+    err = (pred.float() - tgt.float()).pow(2).flatten(1).sum(dim=1) / total   # this rank's share of every sample's mean
+    if self.use_weights:
+      err = err * weights.to(err)
+    if self.mesh.world_size > 1 and self.mesh.group("model") is not None:
+      dist.all_reduce(err, group=self.mesh.group("model"))                 # the sequence / tensor shards of a sample
+      err = err / self.mesh.size("tensor")
+    return err
+
+  def eval(self, step: int, writer=None) -> Optional[float]:
+    """Evaluation pass over the evaluation split: the per-sample losses are grouped by timestep, every group is cut to
+    `eval_max_number_of_samples_in_bucket` samples and averaged, and the mean of the group means is logged as
+    `learning/eval_loss` (reference: src/maxdiffusion/trainers/base_wan_trainer.py:209-255)."""
+    from ..input_pipeline.input_pipeline_interface import make_data_iterator
+
+    data = make_data_iterator(self.config, self.mesh, self.batch_size, eval_mode=True)
+    by_t: dict = {}
+    for batch in data:
+      t0 = time.perf_counter()
+      losses, ts = self.eval_step(batch), batch["timesteps"].to(self.device)
+      replicas = self.mesh.group("replica")
+      if self.mesh.world_size > 1 and replicas is not None:
+        n = dist.get_world_size(replicas)
+        all_l = [torch.empty_like(losses) for _ in range(n)]
+        all_t = [torch.empty_like(ts) for _ in range(n)]
+        dist.all_gather(all_l, losses, group=replicas)
+        dist.all_gather(all_t, ts, group=replicas)
+        losses, ts = torch.cat(all_l), torch.cat(all_t)
+      for t, l in zip(ts.flatten().tolist(), losses.flatten().tolist()):
+        by_t.setdefault(int(t), []).append(float(l))
+      max_logging.log(f"Eval time: {time.perf_counter() - t0:.2f} seconds.")
+    if not by_t:
+      return None
+    cap = int(self.config.get("eval_max_number_of_samples_in_bucket", 60))
+    means = []
+    for t, values in sorted(by_t.items()):
+      values = values[:min(cap, len(values))] if cap > 0 else values
+      means.append(sum(values) / len(values))
+      max_logging.log(f"  Mean eval loss for timestep {t}: {means[-1]:.4f}")
+    final = sum(means) / len(means)
+    max_logging.log(f"Step {step}, Final Average Eval loss: {final:.4f}")
+    if writer is not None:
+      writer.write(step, {"learning/eval_loss": final})
+    return final
+
   def _save(self, checkpointer, monitor) -> None:
     """Checkpoint write bracketed by a device-status check and a host-side barrier: saving is a rank-asymmetric host
     phase (rank 0 writes for seconds), and the peers' next kernels must not start their bounded waits on a rank

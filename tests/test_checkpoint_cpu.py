@@ -176,3 +176,48 @@ def test_train_wan_loop_checkpoints_resumes_and_can_reuse_one_batch(tmp_path):
   trainer.load_dataset = lambda: Counting()
   trainer.start_training()
   assert trainer.step == 8 and len(pulls) == 1
+
+
+def test_wan_eval_groups_losses_by_timestep_and_runs_inside_the_loop(tmp_path):
+  """`eval_every` with a TFRecord evaluation split: per-sample losses at the records' own timesteps, grouped by
+  timestep, every group cut to `eval_max_number_of_samples_in_bucket`, mean of the group means as `learning/eval_loss`."""
+  import json
+
+  import numpy as np
+
+  from maxdiffusion_b200.input_pipeline import tfrecord
+
+  rng = np.random.default_rng(0)
+  ts = [100, 100, 100, 500, 500, 900]
+  recs = [tfrecord.make_example({"latents": [tfrecord.serialize_tensor(rng.standard_normal((16, 2, 4, 4)).astype(np.float32))],
+                                 "encoder_hidden_states": [tfrecord.serialize_tensor(rng.standard_normal((8, 32)).astype(np.float32))],
+                                 "timesteps": np.array([t], dtype=np.int64)}) for t in ts]
+  os.makedirs(tmp_path / "eval")
+  tfrecord.write_records(str(tmp_path / "eval" / "e.tfrecord"), recs)
+  metrics = tmp_path / "metrics.jsonl"
+  config = pyconfig.initialize(
+      ["t", CFG, "run_name=ev", f"output_dir={tmp_path}", "height=32", "width=32", "num_frames=5", "dataset_type=tfrecord",
+       f"train_data_dir={tmp_path}/eval", f"eval_data_dir={tmp_path}/eval", "wan_preset=tiny", f"wan_config_overrides={TINY}",
+       "warmup_steps_fraction=0.0", "log_config=false", "learning_rate=1e-3", "max_sequence_length=8", "per_device_batch_size=2",
+       "eval_every=2", "max_train_steps=2", "eval_max_number_of_samples_in_bucket=2", f"metrics_file={metrics}",
+       "checkpoint_every=-1", "enable_async_checkpointing=false"], unittest=True)
+  tr = WanTrainer(config, mesh=create_device_mesh(config), device="cpu")
+  tr.gen = torch.Generator().manual_seed(3)
+  got = tr.eval(0)
+  # by hand: the same noise stream, one batch of two after another
+  from maxdiffusion_b200.input_pipeline.input_pipeline_interface import make_data_iterator
+
+  tr.gen = torch.Generator().manual_seed(3)
+  buckets = {}
+  for batch in make_data_iterator(config, tr.mesh, tr.batch_size, eval_mode=True):
+    for t, l in zip(batch["timesteps"].tolist(), tr.eval_step(batch).tolist()):
+      buckets.setdefault(int(t), []).append(l)
+  assert sorted(buckets) == [100, 500, 900] and len(buckets[100]) == 3
+  want = sum(sum(v[:2]) / len(v[:2]) for v in buckets.values()) / 3      # the 100 bucket is cut to two samples
+  assert abs(got - want) < 1e-6 and got > 0
+  before = [p.detach().clone() for p in tr.model.parameters()]
+  tr.eval(0)
+  assert all(torch.equal(a, b) for a, b in zip(before, tr.model.parameters()))   # evaluation leaves the weights alone
+  tr.start_training()                                                            # step 2 triggers an evaluation
+  lines = [json.loads(x) for x in metrics.read_text().splitlines()]
+  assert any("learning/eval_loss" in ln and ln["step"] == 2 for ln in lines)
