@@ -241,7 +241,7 @@ class DreamboothTrainer(StableDiffusionTrainer):
     os.makedirs(class_dir, exist_ok=True)
     have = len([f for f in os.listdir(class_dir) if f.lower().endswith((".png", ".jpg", ".jpeg"))])
     made = 0
-    bs = max(1, int(c.get("class_images_batch_size", self.batch_size)))
+    bs = max(1, int(c.get("class_images_batch_size", 0) or self.batch_size))
     while have + made < want:
       n = min(bs, want - have - made)
       imgs = pipeline(prompt=[str(c.get("class_prompt", ""))] * n, seed=int(c.get("seed", 0)) + have + made)
