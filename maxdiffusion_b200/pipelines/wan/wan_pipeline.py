@@ -194,6 +194,18 @@ class WanPipeline:
     low = scale_low if scale_low is not None else self.config.get("guidance_scale_low", self.config.get("guidance_scale", 5.0))
     return self.transformer_2, float(low), False
 
+  def vae_encode_chunk(self, num_frames: int) -> int:
+    """Frames per VAE encoder pass after the first frame: `vae_encode_chunk` of the configuration, a multiple of the
+    temporal stride (4); -1 takes the rest of the clip in one pass (reference:
+    src/maxdiffusion/models/wan/autoencoder_kl_wan.py:1063-1077,1144-1149)."""
+    stride = self.vae_scale_factor_temporal
+    chunk = int(self.config.get("vae_encode_chunk", stride)) if self.config is not None else stride
+    if chunk == -1:
+      return max(stride, -(-max(1, num_frames - 1) // stride) * stride)
+    if chunk < 1 or chunk % stride:
+      raise ValueError(f"vae_encode_chunk ({chunk}) must be -1 or a positive multiple of the temporal stride ({stride})")
+    return chunk
+
   def _cfg_split(self):
     """With data axis 2 and CFG on, rank coordinate 0 runs cond and 1 runs uncond (CFG as data parallelism)."""
     return self.mesh.size("data") == 2
@@ -422,7 +434,7 @@ class _I2VMixin:
     vae_dtype = next(self.vae.parameters()).dtype
     if video.is_cuda and bool(self.config.get("vae_kernel_decode", True)) and hasattr(self.vae, "channels_last_decoder"):
       vae_dtype = torch.bfloat16  # bf16 frames select the encoder on this repository's convolution kernels
-    lat = self.vae.normalize_latents(self.vae.encode(video.to(vae_dtype)).mode().float())
+    lat = self.vae.normalize_latents(self.vae.encode(video.to(vae_dtype), self.vae_encode_chunk(video.shape[2])).mode().float())
     tl = (num_frames - 1) // 4 + 1
     mask = torch.zeros((B, 4, tl, height // 8, width // 8), device=image.device, dtype=lat.dtype)
     mask[:, :, 0] = 1.0

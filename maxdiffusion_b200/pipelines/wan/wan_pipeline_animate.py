@@ -66,7 +66,7 @@ class WanAnimatePipeline(WanPipeline):
   @torch.no_grad()
   def _encode(self, video):
     vae_dtype = next(self.vae.parameters()).dtype
-    return self.vae.normalize_latents(self.vae.encode(video.to(self.device, vae_dtype)).mode())
+    return self.vae.normalize_latents(self.vae.encode(video.to(self.device, vae_dtype), self.vae_encode_chunk(video.shape[2])).mode())
 
   def prepare_reference_image_latents(self, image, batch):
     lat = self._encode(image[:, :, None] if image.dim() == 4 else image)

@@ -73,7 +73,7 @@ class WanVACEPipeline2_1(WanPipeline):
   def prepare_video_latents(self, video: torch.Tensor, mask: torch.Tensor, refs: List[torch.Tensor]) -> torch.Tensor:
     vae_dtype = next(self.vae.parameters()).dtype
     video, mask = video.to(self.device, vae_dtype), (mask > 0.5).to(self.device, vae_dtype)
-    enc = lambda v: self.vae.normalize_latents(self.vae.encode(v).mode())
+    enc = lambda v: self.vae.normalize_latents(self.vae.encode(v, self.vae_encode_chunk(v.shape[2])).mode())
     latents = torch.cat([enc(video * (1 - mask)), enc(video * mask)], dim=1)  # [B,32,T',h,w]
     for img in refs:
       ref = enc(img.to(self.device, vae_dtype)[None, :, None])  # one frame

@@ -337,3 +337,17 @@ def test_sencache_forced_zones_score_and_reuse_limit():
     else:
       break
   assert reused == 3
+
+
+def test_vae_encode_chunk_comes_from_the_configuration():
+  import types
+
+  pipe = WanPipeline2_1.__new__(WanPipeline2_1)
+  pipe.vae_scale_factor_temporal = 4
+  for value, frames, want in ((4, 81, 4), (8, 81, 8), (-1, 81, 80), (-1, 1, 4), (-1, 10, 12)):
+    pipe.config = types.SimpleNamespace(get=lambda k, d=None, v=value: v if k == "vae_encode_chunk" else d)
+    assert pipe.vae_encode_chunk(frames) == want
+  for bad in (0, 3, 6):
+    pipe.config = types.SimpleNamespace(get=lambda k, d=None, v=bad: v)
+    with pytest.raises(ValueError, match="multiple of the temporal stride"):
+      pipe.vae_encode_chunk(81)
