@@ -168,3 +168,47 @@ def transformer_engine_context():
   """Present for scripts that wrap their training call in it: the reference uses it to tell TransformerEngine about
   its mesh; nothing here depends on that library, so the block simply runs."""
   yield
+
+
+def structural_similarity(a, b, data_range: float = 255.0, win_size: int = 7) -> float:
+  """Mean structural similarity of two arrays [*spatial, C] (an image [H, W, C] or a clip [T, H, W, C]) with a uniform
+  `win_size` window over ALL spatial axes, sample covariances and the border of half a window left out: what
+  `skimage.metrics.structural_similarity(..., channel_axis=-1, data_range=...)` computes with its defaults, which is how
+  the reference scores a clip generated after training against one generated before
+  (src/maxdiffusion/trainers/base_wan_trainer.py:65-81)."""
+  import torch.nn.functional as F
+
+  x = torch.as_tensor(a).double()
+  y = torch.as_tensor(b).double()
+  if x.shape != y.shape or x.dim() not in (3, 4):
+    raise ValueError(f"expected two arrays of one shape [H, W, C] or [T, H, W, C], got {tuple(x.shape)} and {tuple(y.shape)}")
+  nd = x.dim() - 1
+  if min(x.shape[:-1]) < win_size:
+    raise ValueError(f"every spatial axis must be at least win_size = {win_size} long, got {tuple(x.shape[:-1])}")
+  pool = F.avg_pool2d if nd == 2 else F.avg_pool3d
+  mean = lambda t: pool(t.movedim(-1, 0).unsqueeze(0), win_size, stride=1)[0]      # [C, *valid]
+  n = float(win_size ** nd)
+  cov_norm = n / (n - 1.0)
+  ux, uy = mean(x), mean(y)
+  vx = cov_norm * (mean(x * x) - ux * ux)
+  vy = cov_norm * (mean(y * y) - uy * uy)
+  vxy = cov_norm * (mean(x * y) - ux * uy)
+  c1, c2 = (0.01 * data_range) ** 2, (0.03 * data_range) ** 2
+  s = ((2 * ux * uy + c1) * (2 * vxy + c2)) / ((ux * ux + uy * uy + c1) * (vx + vy + c2))
+  return float(s.flatten(1).mean(dim=1).mean())
+
+
+def print_ssim(pretrained_video, posttrained_video) -> float:
+  """Logs and returns the SSIM of two clips given as uint8 arrays [T, H, W, C] or as paths of video files."""
+  def frames(v):
+    if isinstance(v, (str, os.PathLike)):
+      from .utils.loading_utils import load_video
+
+      import numpy as np
+
+      return np.stack([np.asarray(f) for f in load_video(os.fspath(v))])
+    return v
+
+  score = structural_similarity(frames(pretrained_video), frames(posttrained_video), data_range=255.0)
+  max_logging.log(f"SSIM score after training is {score}")
+  return score

@@ -224,3 +224,39 @@ def test_write_metrics_function_form(tmp_path):
   assert json.loads(path.read_text().splitlines()[-1]) == {"step": 3, "learning/loss": 0.25}
   with T.transformer_engine_context():
     pass
+
+
+def test_structural_similarity_matches_a_filter_based_restatement():
+  """The clip-level SSIM against a restatement on scipy's uniform filter (window over time, height and width, sample
+  covariances, border cropped)."""
+  import numpy as np
+  from scipy.ndimage import uniform_filter
+
+  from maxdiffusion_b200 import train_utils as T
+
+  rng = np.random.default_rng(0)
+  a = rng.integers(0, 256, (9, 12, 10, 3)).astype(np.uint8)
+  b = np.clip(a.astype(np.int32) + rng.integers(-40, 41, a.shape), 0, 255).astype(np.uint8)
+
+  def restated(x, y, R=255.0, win=7):
+    out = []
+    for c in range(x.shape[-1]):
+      p, q = x[..., c].astype(np.float64), y[..., c].astype(np.float64)
+      f = lambda t: uniform_filter(t, size=win)
+      n = win ** p.ndim
+      k = n / (n - 1)
+      up, uq = f(p), f(q)
+      vp, vq, vpq = k * (f(p * p) - up * up), k * (f(q * q) - uq * uq), k * (f(p * q) - up * uq)
+      c1, c2 = (0.01 * R) ** 2, (0.03 * R) ** 2
+      s = ((2 * up * uq + c1) * (2 * vpq + c2)) / ((up * up + uq * uq + c1) * (vp + vq + c2))
+      pad = (win - 1) // 2
+      out.append(s[tuple(slice(pad, d - pad) for d in s.shape)].mean())
+    return float(np.mean(out))
+
+  got = T.structural_similarity(a, b)
+  assert abs(got - restated(a, b)) < 1e-9 and 0.0 < got < 1.0
+  assert abs(T.structural_similarity(a, a) - 1.0) < 1e-12
+  assert abs(T.structural_similarity(a[0], b[0]) - restated(a[0], b[0])) < 1e-9      # a single image
+  assert T.print_ssim(a, b) == got
+  with pytest.raises(ValueError, match="win_size"):
+    T.structural_similarity(a[:3], b[:3])
